@@ -1,0 +1,76 @@
+"""Paged KV pool: one slab per layer, ``[num_blocks, Hkv, block_size, D]``.
+
+A block id addresses the same slot in every layer, so a sequence has one block table for the
+whole model. ``kv_bits=8`` stores uint8 values plus a bf16 (scale, bias) pair per 64 elements
+(``--kv-bits 8 --kv-group-size 64`` of the reference, src/cli/batch_quant_args.rs:33-80), written
+by the fused RoPE+append kernel and dequantized inside the attention kernels.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import KVLayer
+
+
+class KVPool:
+    def __init__(self, cfg: ModelConfig, num_blocks: int, block_size: int = 16, *, kv_bits: int = 16,
+                 device="cpu", dtype=torch.bfloat16, tp_size: int = 1, num_layers: int | None = None):
+        if kv_bits not in (16, 8):
+            raise ValueError("kv_bits must be 16 or 8")
+        self.cfg, self.num_blocks, self.block_size, self.kv_bits = cfg, num_blocks, block_size, kv_bits
+        self.Hkv = max(1, cfg.num_key_value_heads // tp_size)
+        self.D = cfg.head_dim
+        L = cfg.num_hidden_layers if num_layers is None else num_layers
+        shape = (num_blocks, self.Hkv, block_size, self.D)
+        self.layers: list[KVLayer] = []
+        for _ in range(L):
+            if kv_bits == 16:
+                k = torch.zeros(shape, dtype=dtype, device=device)
+                v = torch.zeros(shape, dtype=dtype, device=device)
+                km = vm = None
+            else:
+                if self.D % 64:
+                    raise ValueError("8-bit KV needs head_dim % 64 == 0")
+                k = torch.zeros(shape, dtype=torch.uint8, device=device)
+                v = torch.zeros(shape, dtype=torch.uint8, device=device)
+                mshape = (num_blocks, self.Hkv, block_size, self.D // 64, 2)
+                km = torch.zeros(mshape, dtype=torch.bfloat16, device=device)
+                vm = torch.zeros(mshape, dtype=torch.bfloat16, device=device)
+            self.layers.append(KVLayer(k, v, km, vm, block_size, kv_bits))
+
+    @staticmethod
+    def bytes_per_block(cfg: ModelConfig, block_size: int, kv_bits: int = 16, tp_size: int = 1,
+                        num_layers: int | None = None) -> int:
+        Hkv = max(1, cfg.num_key_value_heads // tp_size)
+        L = cfg.num_hidden_layers if num_layers is None else num_layers
+        per_tok = Hkv * cfg.head_dim * (2 if kv_bits == 16 else 1)
+        if kv_bits == 8:
+            per_tok += Hkv * (cfg.head_dim // 64) * 4
+        return 2 * per_tok * block_size * L
+
+    def copy_blocks(self, pairs: list[tuple[int, int]]) -> None:
+        """Copy-on-write support: duplicate block contents ``src -> dst`` in every layer."""
+        if not pairs:
+            return
+        src = torch.tensor([p[0] for p in pairs], device=self.layers[0].k.device)
+        dst = torch.tensor([p[1] for p in pairs], device=self.layers[0].k.device)
+        for l in self.layers:
+            for t in (l.k, l.v, l.k_meta, l.v_meta):
+                if t is not None:
+                    t[dst] = t[src]
+
+    def extract_blocks(self, block_ids: list[int]) -> list[dict]:
+        """Host copies of blocks (KV handoff / snapshot)."""
+        idx = torch.tensor(block_ids, device=self.layers[0].k.device)
+        out = []
+        for l in self.layers:
+            out.append({n: getattr(l, n)[idx].cpu() for n in ("k", "v", "k_meta", "v_meta")
+                        if getattr(l, n) is not None})
+        return out
+
+    def restore_blocks(self, block_ids: list[int], data: list[dict]) -> None:
+        idx = torch.tensor(block_ids, device=self.layers[0].k.device)
+        for l, d in zip(self.layers, data):
+            for n, t in d.items():
+                getattr(l, n)[idx] = t.to(getattr(l, n).device)

@@ -1,0 +1,382 @@
+"""Model configuration: ``config.json`` → one normalised :class:`ModelConfig`.
+
+The reference detects ~190 model types and gives each its own struct
+(src/models/detection.rs:787,1236; src/models/registry.rs:1064). Here one record describes the
+decoder-only transformer design space (attention variant, norm variant, MLP variant, MoE, RoPE
+scaling, sliding windows, sinks, quantization) and model families are entries of
+:data:`FAMILIES` that set flags on it.
+"""
+from __future__ import annotations
+
+import json
+import math
+from dataclasses import dataclass, field, asdict
+from pathlib import Path
+from typing import Any
+
+
+@dataclass
+class QuantConfig:
+    """Checkpoint weight quantization (MLX formats, src/lib/mlxcel-core/src/layers.rs:1885-1933)."""
+
+    mode: str = "none"  # none | affine | mxfp4 | mxfp8 | nvfp4
+    bits: int = 16
+    group_size: int = 64
+    # per-module overrides: module path -> {"bits":..,"group_size":..,"mode":..} or False (unquantized)
+    overrides: dict[str, Any] = field(default_factory=dict)
+
+    @staticmethod
+    def from_dict(d: dict | None) -> "QuantConfig":
+        if not d:
+            return QuantConfig()
+        mode = d.get("mode")
+        bits = int(d.get("bits", 4))
+        group = int(d.get("group_size", 64))
+        if mode is None:
+            mode = "affine"
+        overrides = {k: v for k, v in d.items()
+                     if isinstance(v, (dict, bool)) and k not in ("mode", "bits", "group_size")}
+        return QuantConfig(mode=mode, bits=bits, group_size=group, overrides=overrides)
+
+    def for_module(self, path: str) -> "QuantConfig | None":
+        """Effective quantization of one module (``None`` = stored unquantized)."""
+        ov = self.overrides.get(path)
+        if ov is False:
+            return None
+        if isinstance(ov, dict):
+            return QuantConfig(mode=ov.get("mode", self.mode), bits=int(ov.get("bits", self.bits)),
+                               group_size=int(ov.get("group_size", self.group_size)))
+        if self.mode == "none":
+            return None
+        return self
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "llama"
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 32
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-5
+    max_position_embeddings: int = 8192
+    tie_word_embeddings: bool = False
+    # rope
+    rope_theta: float = 10000.0
+    rope_scaling: dict | None = None
+    rope_traditional: bool = False
+    partial_rotary_factor: float = 1.0
+    # attention variants
+    attention_bias: bool = False
+    mlp_bias: bool = False
+    qk_norm: bool = False               # per-head RMSNorm on q and k (Qwen3, OLMo2-style)
+    sliding_window: int = 0
+    layer_types: list[str] | None = None  # per layer: "full_attention" | "sliding_attention"
+    attention_sinks: bool = False       # gpt-oss per-head sink logits
+    attn_logit_softcap: float = 0.0
+    final_logit_softcap: float = 0.0
+    query_pre_attn_scalar: float | None = None
+    # norms / residual layout
+    norm_weight_bias: float = 0.0       # 1.0 for Gemma's (1 + w)
+    post_norms: bool = False            # Gemma2/3: post-attention and post-ffn norms
+    embed_scale: float = 1.0
+    # mlp
+    hidden_act: str = "silu"            # silu | gelu_tanh | clipped_swiglu
+    swiglu_alpha: float = 1.702
+    swiglu_limit: float = 7.0
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    moe_route_mode: str = "topk_softmax"  # topk_softmax (mixtral, gpt-oss) | softmax_topk (qwen-moe)
+    norm_topk_prob: bool = True
+    shared_expert_intermediate_size: int = 0
+    expert_bias: bool = False
+    router_bias: bool = False
+    # MTP / drafter
+    num_nextn_predict_layers: int = 0
+    # misc
+    bos_token_id: int | None = None
+    eos_token_id: Any = None
+    quantization: QuantConfig = field(default_factory=QuantConfig)
+    dtype: str = "bfloat16"
+    extra: dict = field(default_factory=dict)
+
+    # ------------------------------------------------------------------ derived
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def rot_dim(self) -> int:
+        r = int(self.head_dim * self.partial_rotary_factor)
+        return r - (r % 2)
+
+    @property
+    def attn_scale(self) -> float:
+        if self.query_pre_attn_scalar:
+            return 1.0 / math.sqrt(self.query_pre_attn_scalar)
+        return 1.0 / math.sqrt(self.head_dim)
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_window(self, layer: int) -> int:
+        """Sliding-window size of a layer (0 = full attention)."""
+        if self.layer_types:
+            return self.sliding_window if self.layer_types[layer] == "sliding_attention" else 0
+        return self.sliding_window
+
+    def eos_ids(self) -> list[int]:
+        e = self.eos_token_id
+        if e is None:
+            return []
+        return [int(x) for x in e] if isinstance(e, (list, tuple)) else [int(e)]
+
+    def kv_bytes_per_token(self, kv_bits: int = 16) -> int:
+        per = self.num_key_value_heads * self.head_dim
+        if kv_bits == 16:
+            b = per * 2
+        else:
+            b = per * kv_bits // 8 + (per // 64) * 4
+        return 2 * b * self.num_hidden_layers
+
+    def param_count(self) -> int:
+        h, i, L = self.hidden_size, self.intermediate_size, self.num_hidden_layers
+        attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        if self.is_moe:
+            mi = self.moe_intermediate_size or i
+            mlp = self.num_experts * 3 * h * mi + h * self.num_experts
+            if self.shared_expert_intermediate_size:
+                mlp += 3 * h * self.shared_expert_intermediate_size
+        else:
+            mlp = 3 * h * i
+        emb = self.vocab_size * h * (1 if self.tie_word_embeddings else 2)
+        return L * (attn + mlp + 2 * h) + emb + h
+
+    def to_dict(self) -> dict:
+        d = asdict(self)
+        return d
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def from_dict(raw: dict) -> "ModelConfig":
+        raw = dict(raw)
+        if "text_config" in raw and isinstance(raw["text_config"], dict):
+            # VLM wrappers keep the language model under text_config
+            inner = dict(raw["text_config"])
+            for k in ("quantization", "quantization_config"):
+                if k in raw and k not in inner:
+                    inner[k] = raw[k]
+            inner.setdefault("model_type", raw.get("model_type", "llama"))
+            raw = inner
+        mt = raw.get("model_type", "llama")
+        fam = FAMILIES.get(mt)
+        if fam is None:
+            raise ValueError(f"unsupported model_type {mt!r}; supported: {sorted(FAMILIES)}")
+        c = ModelConfig(model_type=mt)
+        g = raw.get
+        c.vocab_size = int(g("vocab_size", c.vocab_size))
+        c.hidden_size = int(g("hidden_size", g("n_embd", c.hidden_size)))
+        c.num_hidden_layers = int(g("num_hidden_layers", g("n_layer", c.num_hidden_layers)))
+        c.num_attention_heads = int(g("num_attention_heads", g("n_head", c.num_attention_heads)))
+        c.num_key_value_heads = int(g("num_key_value_heads", c.num_attention_heads))
+        c.head_dim = int(g("head_dim") or c.hidden_size // c.num_attention_heads)
+        c.intermediate_size = int(g("intermediate_size", g("ffn_dim", 4 * c.hidden_size)))
+        c.rms_norm_eps = float(g("rms_norm_eps", g("layer_norm_epsilon", 1e-5)))
+        c.max_position_embeddings = int(g("max_position_embeddings", 8192))
+        c.tie_word_embeddings = bool(g("tie_word_embeddings", False))
+        c.rope_theta = float(g("rope_theta", 10000.0))
+        c.rope_scaling = g("rope_scaling")
+        c.rope_traditional = bool(g("rope_traditional", False))
+        c.partial_rotary_factor = float(g("partial_rotary_factor", 1.0))
+        c.attention_bias = bool(g("attention_bias", g("qkv_bias", False)))
+        c.mlp_bias = bool(g("mlp_bias", False))
+        c.sliding_window = int(g("sliding_window") or 0)
+        c.layer_types = g("layer_types")
+        c.hidden_act = {"silu": "silu", "swish": "silu", "gelu_pytorch_tanh": "gelu_tanh",
+                        "gelu_tanh": "gelu_tanh", "gelu": "gelu_tanh"}.get(
+                            g("hidden_act", g("hidden_activation", "silu")), "silu")
+        c.num_experts = int(g("num_local_experts", g("num_experts", g("n_routed_experts", 0))) or 0)
+        c.num_experts_per_tok = int(g("num_experts_per_tok", g("experts_per_token", 0)) or 0)
+        c.moe_intermediate_size = int(g("moe_intermediate_size", 0) or 0)
+        c.norm_topk_prob = bool(g("norm_topk_prob", True))
+        c.shared_expert_intermediate_size = int(g("shared_expert_intermediate_size", 0) or 0)
+        c.num_nextn_predict_layers = int(g("num_nextn_predict_layers", g("mtp_num_hidden_layers", 0)) or 0)
+        c.bos_token_id = g("bos_token_id")
+        c.eos_token_id = g("eos_token_id")
+        c.attn_logit_softcap = float(g("attn_logit_softcapping") or 0.0)
+        c.final_logit_softcap = float(g("final_logit_softcapping") or 0.0)
+        c.query_pre_attn_scalar = g("query_pre_attn_scalar")
+        c.quantization = QuantConfig.from_dict(g("quantization") or g("quantization_config"))
+        c.dtype = str(g("torch_dtype", g("dtype", "bfloat16")))
+        fam(c, raw)
+        if c.is_moe and not c.moe_intermediate_size:
+            c.moe_intermediate_size = c.intermediate_size
+        if c.layer_types is not None and len(c.layer_types) != c.num_hidden_layers:
+            raise ValueError("layer_types length does not match num_hidden_layers")
+        if c.num_attention_heads % c.num_key_value_heads:
+            raise ValueError("num_attention_heads must be a multiple of num_key_value_heads")
+        return c
+
+    @staticmethod
+    def from_path(path: str | Path) -> "ModelConfig":
+        p = Path(path)
+        if p.is_dir():
+            p = p / "config.json"
+        return ModelConfig.from_dict(json.loads(p.read_text()))
+
+
+# ----------------------------------------------------------------------------- families
+def _plain(c: ModelConfig, raw: dict) -> None:
+    pass
+
+
+def _qwen2(c: ModelConfig, raw: dict) -> None:
+    c.attention_bias = True
+    if not raw.get("use_sliding_window", False):
+        c.sliding_window = 0
+
+
+def _qwen3(c: ModelConfig, raw: dict) -> None:
+    c.qk_norm = True
+    c.sliding_window = 0 if not raw.get("use_sliding_window", False) else c.sliding_window
+
+
+def _qwen_moe(c: ModelConfig, raw: dict) -> None:
+    if c.model_type.startswith("qwen3"):
+        _qwen3(c, raw)
+    else:
+        _qwen2(c, raw)
+    c.moe_route_mode = "softmax_topk"
+    c.norm_topk_prob = bool(raw.get("norm_topk_prob", False))
+
+
+def _mixtral(c: ModelConfig, raw: dict) -> None:
+    c.moe_route_mode = "topk_softmax"
+    c.moe_intermediate_size = c.intermediate_size
+
+
+def _gemma(c: ModelConfig, raw: dict) -> None:
+    c.norm_weight_bias = 1.0
+    c.embed_scale = math.sqrt(c.hidden_size)
+    c.hidden_act = "gelu_tanh"
+    c.tie_word_embeddings = True
+
+
+def _gemma2(c: ModelConfig, raw: dict) -> None:
+    _gemma(c, raw)
+    c.post_norms = True
+    n = c.num_hidden_layers
+    if c.layer_types is None and c.sliding_window:
+        c.layer_types = ["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(n)]
+
+
+def _gemma3(c: ModelConfig, raw: dict) -> None:
+    _gemma(c, raw)
+    c.post_norms = True
+    c.qk_norm = True
+    n = c.num_hidden_layers
+    pat = int(raw.get("sliding_window_pattern", 6) or 6)
+    if c.layer_types is None and c.sliding_window:
+        c.layer_types = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention" for i in range(n)]
+
+
+def _gpt_oss(c: ModelConfig, raw: dict) -> None:
+    c.attention_sinks = True
+    c.attention_bias = True
+    c.hidden_act = "clipped_swiglu"
+    c.swiglu_limit = float(raw.get("swiglu_limit", 7.0))
+    c.moe_route_mode = "topk_softmax"
+    c.expert_bias = True
+    c.router_bias = True
+    c.moe_intermediate_size = c.intermediate_size
+    if c.layer_types is None and c.sliding_window:
+        c.layer_types = ["sliding_attention" if i % 2 == 0 else "full_attention"
+                         for i in range(c.num_hidden_layers)]
+
+
+def _phi3(c: ModelConfig, raw: dict) -> None:
+    pass  # fused qkv_proj / gate_up_proj names are handled by the weight-name sanitizer
+
+
+def _olmo2(c: ModelConfig, raw: dict) -> None:
+    c.qk_norm = True
+    c.extra["qk_norm_full"] = True   # norm over the whole projection, not per head
+    c.extra["post_norm_only"] = True  # norms after attention / mlp instead of before
+
+
+def _granite(c: ModelConfig, raw: dict) -> None:
+    c.embed_scale = float(raw.get("embedding_multiplier", 1.0))
+    c.extra["residual_multiplier"] = float(raw.get("residual_multiplier", 1.0))
+    c.extra["logits_scaling"] = float(raw.get("logits_scaling", 1.0))
+    if raw.get("attention_multiplier"):
+        c.query_pre_attn_scalar = 1.0 / float(raw["attention_multiplier"]) ** 2
+
+
+FAMILIES = {
+    "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _plain, "seed_oss": _plain,
+    "helium": _plain, "internlm3": _plain, "exaone4": _qwen3, "hunyuan_v1_dense": _qwen3,
+    "ernie4_5": _plain, "apertus": _plain, "minicpm": _plain, "mimo": _qwen2, "yi": _plain,
+    "qwen2": _qwen2, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
+    "mixtral": _mixtral, "phimoe": _mixtral, "olmoe": _qwen_moe,
+    "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
+    "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
+    "granite": _granite, "starcoder2": _plain, "stablelm": _plain, "cohere": _plain,
+}
+
+
+# ----------------------------------------------------------------------------- presets
+def preset(name: str) -> ModelConfig:
+    """Architectures named by the benchmark configurations (random-init, synthetic runs)."""
+    if name == "tiny-llama":
+        return ModelConfig.from_dict(dict(
+            model_type="llama", num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=64, intermediate_size=688, rms_norm_eps=1e-5,
+            rope_theta=10000.0, vocab_size=1024, tie_word_embeddings=True,
+            max_position_embeddings=2048))
+    if name == "llama-3.1-8b":
+        return ModelConfig.from_dict(dict(
+            model_type="llama", num_hidden_layers=32, hidden_size=4096, num_attention_heads=32,
+            num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
+            rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=131072,
+            rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                              high_freq_factor=4.0, original_max_position_embeddings=8192)))
+    if name == "qwen3-32b":
+        return ModelConfig.from_dict(dict(
+            model_type="qwen3", num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
+            num_key_value_heads=8, head_dim=128, intermediate_size=25600, vocab_size=151936,
+            rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=40960))
+    if name == "gpt-oss-120b":
+        return ModelConfig.from_dict(dict(
+            model_type="gpt_oss", num_hidden_layers=36, hidden_size=2880, num_attention_heads=64,
+            num_key_value_heads=8, head_dim=64, intermediate_size=2880, vocab_size=201088,
+            num_local_experts=128, num_experts_per_tok=4, sliding_window=128, rms_norm_eps=1e-5,
+            rope_theta=150000.0, max_position_embeddings=131072,
+            rope_scaling=dict(rope_type="yarn", factor=32.0, beta_fast=32.0, beta_slow=1.0,
+                              original_max_position_embeddings=4096, truncate=False)))
+    if name == "tiny-moe":
+        return ModelConfig.from_dict(dict(
+            model_type="mixtral", num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=1024,
+            num_local_experts=8, num_experts_per_tok=2, max_position_embeddings=2048))
+    if name == "tiny-gpt-oss":
+        return ModelConfig.from_dict(dict(
+            model_type="gpt_oss", num_hidden_layers=4, hidden_size=256, num_attention_heads=8,
+            num_key_value_heads=2, head_dim=64, intermediate_size=256, vocab_size=1024,
+            num_local_experts=8, num_experts_per_tok=2, sliding_window=32,
+            max_position_embeddings=4096))
+    if name == "tiny-qwen3":
+        return ModelConfig.from_dict(dict(
+            model_type="qwen3", num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=1024,
+            rms_norm_eps=1e-6, max_position_embeddings=2048))
+    raise KeyError(name)

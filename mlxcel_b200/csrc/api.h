@@ -1,0 +1,168 @@
+// C ABI of libmlxcel_b200.so. Every function takes raw device pointers and a CUDA stream
+// (as void*), launches asynchronously on that stream and returns 0 on success, a negative
+// value for a rejected argument, or a positive cudaError_t from the launch.
+//
+// Workspace convention: kernels that need scratch memory (split-K partial sums, tile
+// counters, the device status word) receive one caller-owned buffer `workspace` of
+// `ws_bytes` bytes laid out as
+//   [0, 256)            device status word (int) + padding; 0 = no error
+//   [256, 256 + 64 KiB) tile arrival counters (int), must be zero before the first use and
+//                       are returned to zero by every kernel that completes
+//   [128 KiB, ws_bytes) fp32 partial tiles
+// The buffer must be zero-initialised once by the caller.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MX_WS_STATUS_OFFSET 0
+#define MX_WS_COUNTER_OFFSET 256
+#define MX_WS_COUNTER_BYTES 65536
+#define MX_WS_PARTIAL_OFFSET 131072
+
+// Epilogues of mx_gemm_bf16.
+#define MX_EPI_NONE 0
+#define MX_EPI_BIAS 1            // out = acc + bias[n]
+#define MX_EPI_RESIDUAL 2        // out = acc + residual[m, n] (+ bias[n] when bias != NULL)
+#define MX_EPI_SWIGLU 3          // out = silu(acc_gate) * acc_up
+#define MX_EPI_GEGLU 4           // out = gelu_tanh(acc_gate) * acc_up
+#define MX_EPI_CLIPPED_SWIGLU 5  // gpt-oss: (min(g,l)) * sigmoid(a*g) * (clamp(u,-l,l) + 1)
+
+// out[M, N] = epilogue(x[M, K] @ w[N(+N), K]^T). bf16 operands, fp32 accumulation on the
+// 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operand tiles brought by TMA).
+// For the gated epilogues `w` holds gate rows at [0, N) and up rows at [glu_offset, glu_offset + N).
+// K, ldx, ldw must be multiples of 8. force_mode: 0 auto, 1 token-rows-on-lanes, 2 weight-rows-on-lanes.
+int mx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual,
+                 int M, int N, int K, int ldx, int ldw, int ldo, int ldr, int epilogue,
+                 int out_fp32, int glu_offset, float glu_alpha, float glu_limit, void* workspace,
+                 long long ws_bytes, int force_mode, int force_splits, void* stream);
+
+// Bytes of workspace the no-scratch-allocation path needs at most for mx_gemm_bf16.
+long long mx_gemm_workspace_bytes(void);
+
+// h = x + residual (when residual != NULL; written to residual_out), y = rmsnorm(h) * (w + w_bias).
+// rows x dim bf16; one row per CTA group. eps as given; w_bias = 1.0 for Gemma-style norms.
+int mx_add_rmsnorm(const void* x, const void* residual, const void* weight, void* y,
+                   void* residual_out, int rows, int dim, float eps, float w_bias, void* stream);
+
+// Per-head RMSNorm over the last dimension of [tokens, heads, head_dim] (Qwen3 q/k norm), in place.
+int mx_head_rmsnorm(void* x, const void* weight, int tokens, int heads, int head_dim,
+                    long long token_stride, float eps, void* stream);
+
+// RoPE on q and k (in place on q; k written roped into the paged pool) + KV append.
+// qkv: [T, (Hq + 2 Hkv) * D] bf16. positions: [T] int32. slot_mapping: [T] int64/int32 slot
+// index (= block_id * block_size + offset); negative slots are skipped.
+// inv_freq: [D/2] fp32 (already scaled for llama3 / yarn), mscale multiplies q and k after
+// rotation. rope_mode: 0 = half-split (non-traditional), 1 = interleaved (traditional).
+// k_pool / v_pool layout: [num_blocks, Hkv, block_size, D] (bf16, kv_bits = 16) or int8 with
+// per (token, head, group of 64) scale+bias sidecars (kv_bits = 8) of layout
+// [num_blocks, Hkv, block_size, D/64, 2] bf16.
+// q_norm_w / k_norm_w: optional per-head RMSNorm weights [D] applied before RoPE (Qwen3).
+int mx_rope_append(void* qkv, const int* positions, const int* slot_mapping, const float* inv_freq,
+                   void* k_pool, void* v_pool, void* k_meta, void* v_meta, const void* q_norm_w,
+                   const void* k_norm_w, float norm_eps, int T, int Hq, int Hkv, int D,
+                   int rot_dim, int block_size, int rope_mode, float mscale, int kv_bits,
+                   void* stream);
+
+// Paged decode attention (one query token per sequence), split-KV with an in-kernel merge.
+// q: rows of [Hq * D] bf16 with stride q_stride elements; out: [B, Hq * D] bf16.
+// block_tables: [B, max_blocks] int32; context_lens: [B] int32 (tokens visible, including the
+// one just appended). window > 0 limits attention to the last `window` tokens; sinks: optional
+// [Hq] fp32 logits added to the softmax denominator. scratch: fp32 buffer of
+// mx_paged_decode_scratch_floats(B, Hq, D, max_splits) floats.
+int mx_paged_decode(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
+                    const void* k_meta, const void* v_meta, const int* block_tables,
+                    const int* context_lens, const float* sinks, void* out, float* scratch,
+                    int B, int Hq, int Hkv, int D, int block_size, int max_blocks, int window,
+                    float scale, float softcap, int kv_bits, int num_splits, void* stream);
+long long mx_paged_decode_scratch_floats(int B, int Hq, int D, int num_splits);
+
+// Chunked causal prefill attention over the paged KV pool. Sequence s owns query rows
+// [cu_q[s], cu_q[s+1]) of q (row stride q_stride) which are the LAST q_len tokens of its
+// context_lens[s] visible tokens. K/V are read from the pool (they were appended first).
+int mx_paged_prefill(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
+                     const void* k_meta, const void* v_meta, const int* block_tables,
+                     const int* cu_q, const int* context_lens, const float* sinks, void* out,
+                     int num_seqs, int total_q, int max_q_len, int Hq, int Hkv, int D,
+                     int block_size, int max_blocks, int window, float scale, float softcap,
+                     int kv_bits, void* stream);
+
+// Embedding gather: out[t, :] = table[ids[t], :] (bf16), ids outside [0, vocab) give zeros.
+int mx_embedding(const int* ids, const void* table, void* out, int T, int dim, int vocab,
+                 float scale, void* stream);
+
+// Greedy argmax over [B, V] logits (bf16 or fp32) -> int32 tokens (ties: lowest index).
+int mx_argmax(const void* logits, int logits_fp32, long long row_stride, int* out, int B, int V,
+              void* stream);
+
+// Fused sampler over [B, V] logits. Per-row parameters: temperature (0 = greedy), top_k
+// (0 = off), top_p (1 = off), min_p (0 = off). Filters are evaluated on the untempered
+// softmax, the draw uses Gumbel-max noise from a Philox-4x32-10 stream keyed by
+// (seed[row], step[row]). logit_bias: optional [B, V] or NULL. out_logprob: optional [B].
+int mx_sample(const void* logits, int logits_fp32, long long row_stride, const float* temperature,
+              const int* top_k, const float* top_p, const float* min_p,
+              const unsigned long long* seeds, const unsigned long long* steps, int* out_tokens,
+              float* out_logprob, float* scratch, int B, int V, void* stream);
+long long mx_sample_scratch_floats(int B, int V);
+
+// Repetition / frequency / presence penalties applied in place to fp32 or bf16 logits, given
+// per-row token histories [B, max_hist] (int32, -1 padded).
+int mx_apply_penalties(void* logits, int logits_fp32, long long row_stride, const int* history,
+                       int max_hist, const float* rep, const float* freq, const float* pres, int B,
+                       int V, void* stream);
+
+// Speculative verify: target argmax over [B, K, V] logits vs draft tokens [B, K-1];
+// accept_len[b] = first mismatch index, next_token[b] = target token at that index,
+// target_tokens: [B, K].
+int mx_spec_verify(const void* logits, int logits_fp32, long long row_stride, const int* draft,
+                   int* target_tokens, int* accept_len, int* next_token, int B, int K, int V,
+                   void* stream);
+
+// Affine group-quantized (MLX layout) matmul: out[M, N] = x[M, K] @ dequant(w)[N, K]^T.
+// w: uint32 [N, K * bits / 32], scales/biases bf16 [N, K / group]. bits in {4, 8}.
+// M <= 16 uses the GEMV kernel (weights read once for all rows); larger M dequantizes tiles
+// into shared memory and runs tcgen05 MMAs.
+int mx_qmm_affine(const void* x, const void* w, const void* scales, const void* biases,
+                  void* out, const void* residual, int M, int N, int K, int bits, int group,
+                  int ldx, int ldo, void* workspace, long long ws_bytes, void* stream);
+
+// Dequantize affine / mxfp4 / mxfp8 weights to bf16 (load-time and test helper).
+// mode: 0 affine, 1 mxfp4 (e2m1 + e8m0 per 32), 2 mxfp8 (e4m3 + e8m0 per 32).
+int mx_dequantize(const void* w, const void* scales, const void* biases, void* out, long long N,
+                  int K, int bits, int group, int mode, void* stream);
+
+// SiLU(gate) * up on a fused [T, 2I] tensor -> [T, I] (used by unfused fallbacks and MoE).
+int mx_swiglu(const void* gate_up, void* out, int T, int I, int mode, float alpha, float limit,
+              void* stream);
+
+// MoE router: logits [T, E] (bf16) -> top-k expert ids [T, k] int32 and weights [T, k] fp32.
+// mode 0: softmax over all experts then top-k (renormalised when norm_topk != 0);
+// mode 1: top-k on logits then softmax over the k logits (gpt-oss / mixtral).
+int mx_moe_route(const void* logits, int* topk_ids, float* topk_w, int T, int E, int k, int mode,
+                 int norm_topk, void* stream);
+
+// MoE token permutation helpers: count tokens per expert, exclusive scan, scatter rows.
+int mx_moe_align(const int* topk_ids, int* expert_offsets, int* sorted_row, int* sorted_token,
+                 int T, int k, int E, int e_begin, int e_end, void* stream);
+int mx_moe_gather_rows(const void* x, const int* sorted_token, void* out, int rows, int dim,
+                       void* stream);
+int mx_moe_combine(const void* y, const int* sorted_row, const float* topk_w, void* out,
+                   const void* residual, int T, int k, int dim, int accumulate, void* stream);
+
+// Grouped GEMM over experts: for expert e rows [off[e], off[e+1]) of x use w[e] ([E, N, K]).
+int mx_grouped_gemm_bf16(const void* x, const void* w, void* out, const void* bias,
+                         const int* expert_offsets, int E, int N, int K, int max_rows,
+                         int epilogue, int glu_offset, float glu_alpha, float glu_limit,
+                         void* workspace, long long ws_bytes, void* stream);
+
+// Reads and clears the device status word of a workspace (host-synchronous).
+int mx_read_status(void* workspace, int clear);
+
+// Library / build information.
+const char* mx_build_info(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,612 @@
+// Dense bf16 GEMM for sm_100a: out[M, N] = epilogue(x[M, K] @ w[N, K]^T).
+//
+// One persistent CTA per SM, 6 warps with fixed roles:
+//   warp 0     TMA producer: brings 64-wide K slices of both operands into a ring of
+//              128-byte-swizzled shared-memory stages (cp.async.bulk.tensor, mbarrier tx count)
+//   warp 1     MMA issuer: one thread issues tcgen05.mma (M = 128, N = BN, K = 16) into one of
+//              two TMEM accumulators and commits stage/accumulator barriers
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (one TMEM lane = one thread), apply
+//              bias / residual / gated activation, store bf16 or fp32
+// The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Two operand placements share the kernel:
+//   token-rows-on-lanes  (prefill, M large): lanes = 128 tokens, columns = BN features
+//   weight-rows-on-lanes (decode, M <= 256): lanes = 128 features, columns = BN tokens, so a
+//     16..128-token batch still fills the 128-lane MMA; split-K spreads the weight stream over
+//     all SMs, partial tiles go to an fp32 workspace and the last CTA to arrive for a tile
+//     reduces them in split order (deterministic) and applies the epilogue.
+// Gated epilogues keep gate and up in two accumulators fed by two weight tiles (rows n and
+// glu_offset + n) so no weight interleaving is needed at load time.
+//
+// Replaces the reference's cuBLASLt call (mlx/backend/cuda/matmul.cpp:133 in its MLX overlay)
+// and the compiled swiglu graph that follows it (src/lib/mlxcel-core/src/layers.rs:4407).
+#include <mutex>
+#include <unordered_map>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace mx {
+
+constexpr int kBK = 64;          // K elements per stage (128 bytes of bf16)
+constexpr int kLaneRows = 128;   // UMMA M
+constexpr int kMaxStages = 8;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  void* out;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  float* partials;
+  int* counters;
+  int* status;
+  int M, N, K;
+  int ldo, ldr;
+  int glu_offset;
+  int splits, kb_per_split, num_kb;
+  int tiles_lane, tiles_col;
+  int stages;
+  int epilogue;
+  int out_fp32;
+  float glu_alpha, glu_limit;
+};
+
+__device__ __forceinline__ float act_glu(int epilogue, float g, float u, float alpha, float limit) {
+  if (epilogue == MX_EPI_SWIGLU) {
+    return g / (1.0f + __expf(-g)) * u;
+  } else if (epilogue == MX_EPI_GEGLU) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    float t = tanhf(k0 * (g + k1 * g * g * g));
+    return 0.5f * g * (1.0f + t) * u;
+  } else {  // MX_EPI_CLIPPED_SWIGLU
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + __expf(-alpha * g)) * (u + 1.0f);
+  }
+}
+
+template <int BN, bool SWAP, bool GLU>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
+                 const __grid_constant__ CUtensorMap map_col, const GemmParams p) {
+  constexpr int LANE_TILES = (SWAP && GLU) ? 2 : 1;
+  constexpr int COL_TILES = (!SWAP && GLU) ? 2 : 1;
+  constexpr int LANE_BYTES = kLaneRows * kBK * 2;
+  constexpr int COL_BYTES = BN * kBK * 2;
+  constexpr int STAGE_BYTES = LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
+  constexpr int ACC_COLS = GLU ? 2 * BN : BN;
+  constexpr int TMEM_COLS = (2 * ACC_COLS <= 32)    ? 32
+                            : (2 * ACC_COLS <= 64)  ? 64
+                            : (2 * ACC_COLS <= 128) ? 128
+                            : (2 * ACC_COLS <= 256) ? 256
+                                                    : 512;
+  constexpr int CW = (BN >= 32) ? 32 : 16;  // columns per tcgen05.ld
+  static_assert(BN % CW == 0 && BN >= 16 && BN <= 256, "unsupported BN");
+  static_assert(2 * ACC_COLS <= 512, "accumulators exceed TMEM");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* ctrl = smem + p.stages * STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* tmem_full = empty_bar + kMaxStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  int* last_flag = reinterpret_cast<int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_work = p.tiles_lane * p.tiles_col * p.splits;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&map_lane);
+    tma_prefetch_desc(&map_col);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_full[1], 1);
+    mbar_init(&tmem_empty[0], 4);
+    mbar_init(&tmem_empty[1], 4);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      // Weights are streamed once (evict first); activations are re-read by every tile.
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      const uint64_t pol_lane = SWAP ? pol_w : pol_x;
+      const uint64_t pol_col = SWAP ? pol_x : pol_w;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int tile = w / p.splits, split = w - tile * p.splits;
+        const int lane_t = tile % p.tiles_lane, col_t = tile / p.tiles_lane;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        const int lane_row0 = lane_t * kLaneRows, col_row0 = col_t * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kErrProducerWait)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          uint8_t* s = smem + stage * STAGE_BYTES;
+          tma_load_2d(s, &map_lane, &full_bar[stage], kb * kBK, lane_row0, pol_lane);
+          if (LANE_TILES == 2)
+            tma_load_2d(s + LANE_BYTES, &map_lane, &full_bar[stage], kb * kBK,
+                        lane_row0 + p.glu_offset, pol_lane);
+          uint8_t* sc = s + LANE_TILES * LANE_BYTES;
+          tma_load_2d(sc, &map_col, &full_bar[stage], kb * kBK, col_row0, pol_col);
+          if (COL_TILES == 2)
+            tma_load_2d(sc + COL_BYTES, &map_col, &full_bar[stage], kb * kBK,
+                        col_row0 + p.glu_offset, pol_col);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BN, false, false);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int tile = w / p.splits, split = w - tile * p.splits;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, p.status, kErrMmaWaitTmem)) break;
+        tc_fence_after_sync();
+        const uint32_t d0 = tmem_base + acc * ACC_COLS;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, kErrMmaWaitFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + LANE_TILES * LANE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            const uint32_t accum = (kb > kb0 || kk > 0) ? 1u : 0u;
+            const uint64_t da = umma_desc_k_sw128(sa + kk * 32);
+            const uint64_t db = umma_desc_k_sw128(sb + kk * 32);
+            umma_bf16(d0, da, db, idesc, accum);
+            if (GLU) {
+              if (SWAP) {
+                const uint64_t da2 = umma_desc_k_sw128(sa + LANE_BYTES + kk * 32);
+                umma_bf16(d0 + BN, da2, db, idesc, accum);
+              } else {
+                const uint64_t db2 = umma_desc_k_sw128(sb + COL_BYTES + kk * 32);
+                umma_bf16(d0 + BN, da, db2, idesc, accum);
+              }
+            }
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (128 threads)
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;       // accumulator row (TMEM lane) of this thread
+    const int epi_tid = threadIdx.x - 64;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool glu = GLU;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      const int tile = w / p.splits, split = w - tile * p.splits;
+      const int lane_t = tile % p.tiles_lane, col_t = tile / p.tiles_lane;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kErrEpilogueWait)) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * ACC_COLS;
+      bool reduce_from_ws = false;
+      float* ws_tile = nullptr;
+      if (p.splits > 1) {
+        // Stage 1: park this split's partial tile (column-major: 128 rows contiguous).
+        ws_tile = p.partials + static_cast<size_t>(tile) * p.splits * (kLaneRows * ACC_COLS);
+        float* mine = ws_tile + static_cast<size_t>(split) * (kLaneRows * ACC_COLS);
+#pragma unroll 1
+        for (int c = 0; c < ACC_COLS / CW; ++c) {
+          uint32_t r[CW];
+          if constexpr (CW == 32) tmem_ld_32x32(taddr + c * CW, r);
+          else tmem_ld_32x16(taddr + c * CW, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CW; ++j) mine[(c * CW + j) * kLaneRows + row] = __uint_as_float(r[j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        __threadfence();
+        named_bar_sync(1, 128);
+        if (epi_tid == 0) {
+          const int prev = atomicAdd(&p.counters[tile], 1);
+          const int last = (prev == p.splits - 1) ? 1 : 0;
+          if (last) atomicExch(&p.counters[tile], 0);
+          *last_flag = last;
+        }
+        named_bar_sync(1, 128);
+        reduce_from_ws = (*last_flag != 0);
+        if (!reduce_from_ws) {
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
+          continue;
+        }
+        __threadfence();
+      }
+
+      // Stage 2: final values -> epilogue -> global.
+      const int lane_idx = lane_t * kLaneRows + row;  // token (normal) or feature (SWAP)
+      const int lane_lim = SWAP ? p.N : p.M;
+      float bias_g = 0.f, bias_u = 0.f;
+      if (SWAP && p.bias != nullptr && lane_idx < p.N) {
+        bias_g = __bfloat162float(p.bias[lane_idx]);
+        if (glu) bias_u = __bfloat162float(p.bias[p.glu_offset + lane_idx]);
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / CW; ++c) {
+        float v[CW], u[CW];
+        if (!reduce_from_ws) {
+          uint32_t r[CW];
+          if constexpr (CW == 32) tmem_ld_32x32(taddr + c * CW, r);
+          else tmem_ld_32x16(taddr + c * CW, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]);
+          if (glu) {
+            if constexpr (CW == 32) tmem_ld_32x32(taddr + BN + c * CW, r);
+            else tmem_ld_32x16(taddr + BN + c * CW, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < CW; ++j) u[j] = __uint_as_float(r[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < CW; ++j) {
+            v[j] = 0.f;
+            u[j] = 0.f;
+          }
+          for (int s = 0; s < p.splits; ++s) {
+            const float* part = ws_tile + static_cast<size_t>(s) * (kLaneRows * ACC_COLS);
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              v[j] += __ldcg(&part[(c * CW + j) * kLaneRows + row]);
+              if (glu) u[j] += __ldcg(&part[(BN + c * CW + j) * kLaneRows + row]);
+            }
+          }
+        }
+        if (lane_idx < lane_lim) {
+          if constexpr (SWAP) {
+            // thread = feature n, columns = tokens
+            const int n = lane_idx;
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              const int t = col_t * BN + c * CW + j;
+              if (t < p.M) {
+                float val;
+                if (glu) {
+                  val = act_glu(p.epilogue, v[j] + bias_g, u[j] + bias_u, p.glu_alpha, p.glu_limit);
+                } else {
+                  val = v[j] + bias_g;
+                  if (p.residual != nullptr)
+                    val += __bfloat162float(p.residual[static_cast<size_t>(t) * p.ldr + n]);
+                }
+                if (p.out_fp32)
+                  reinterpret_cast<float*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = val;
+                else
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] =
+                      __float2bfloat16(val);
+              }
+            }
+          } else {
+            // thread = token m, columns = features
+            const int m = lane_idx;
+            const int n0 = col_t * BN + c * CW;
+#pragma unroll
+            for (int j8 = 0; j8 < CW; j8 += 8) {
+              const int n = n0 + j8;
+              if (n >= p.N) break;
+              float o[8];
+              const bool full8 = (n + 8 <= p.N);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float val = v[j8 + j];
+                const bool in = full8 || (n + j < p.N);
+                if (glu) {
+                  float g = val, uu = u[j8 + j];
+                  if (p.bias != nullptr && in) {
+                    g += __bfloat162float(p.bias[n + j]);
+                    uu += __bfloat162float(p.bias[p.glu_offset + n + j]);
+                  }
+                  val = act_glu(p.epilogue, g, uu, p.glu_alpha, p.glu_limit);
+                } else {
+                  if (p.bias != nullptr && in) val += __bfloat162float(p.bias[n + j]);
+                  if (p.residual != nullptr && in)
+                    val += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n + j]);
+                }
+                o[j] = val;
+              }
+              const size_t off = static_cast<size_t>(m) * p.ldo + n;
+              if (p.out_fp32) {
+                float* dst = reinterpret_cast<float*>(p.out) + off;
+                if (full8 && ((off & 3) == 0)) {
+                  reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
+                  reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
+                } else {
+                  for (int j = 0; j < 8 && n + j < p.N; ++j) dst[j] = o[j];
+                }
+              } else {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
+                if (full8 && ((off & 7) == 0)) {
+                  uint4 pk;
+                  pk.x = pack_bf16(o[0], o[1]);
+                  pk.y = pack_bf16(o[2], o[3]);
+                  pk.z = pack_bf16(o[4], o[5]);
+                  pk.w = pack_bf16(o[6], o[7]);
+                  *reinterpret_cast<uint4*>(dst) = pk;
+                } else {
+                  for (int j = 0; j < 8 && n + j < p.N; ++j) dst[j] = __float2bfloat16(o[j]);
+                }
+              }
+            }
+          }
+        }
+      }
+      if (!reduce_from_ws) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows, box_cols;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
+           box_rows == o.box_rows && box_cols == o.box_cols;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ k.rows;
+    h = h * 1000003u ^ k.cols;
+    h = h * 1000003u ^ k.ld;
+    h = h * 1000003u ^ (static_cast<size_t>(k.box_rows) << 16 | k.box_cols);
+    return h;
+  }
+};
+
+// 2-D bf16 row-major tensor [rows, cols] with leading dimension ld (elements); box is
+// {box_cols (inner, 64 = 128 bytes), box_rows}; 128-byte swizzle; out-of-range reads give 0.
+bool make_tensor_map_bf16(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols,
+                          uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{ptr, rows, cols, ld, box_rows, box_cols};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 65536) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+int device_sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    sms[dev] = n > 0 ? n : 148;
+  }
+  return sms[dev];
+}
+
+template <int BN, bool SWAP, bool GLU>
+static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams p, int grid,
+                       cudaStream_t stream) {
+  constexpr int LANE_TILES = (SWAP && GLU) ? 2 : 1;
+  constexpr int COL_TILES = (!SWAP && GLU) ? 2 : 1;
+  constexpr int STAGE_BYTES = LANE_TILES * kLaneRows * kBK * 2 + COL_TILES * BN * kBK * 2;
+  constexpr int kSmemBudget = 227 * 1024 - 1024 /*align*/ - 256 /*ctrl*/;
+  int stages = kSmemBudget / STAGE_BYTES;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return -3;
+  p.stages = stages;
+  const int smem = stages * STAGE_BYTES + 1024 + 256;
+  auto kern = gemm_bf16_kernel<BN, SWAP, GLU>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, smem, stream>>>(ml, mc, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace mx
+
+using namespace mx;
+
+extern "C" long long mx_gemm_workspace_bytes(void) { return 64ll << 20; }
+
+extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void* bias,
+                            const void* residual, int M, int N, int K, int ldx, int ldw, int ldo,
+                            int ldr, int epilogue, int out_fp32, int glu_offset, float glu_alpha,
+                            float glu_limit, void* workspace, long long ws_bytes, int force_mode,
+                            int force_splits, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if ((K % 8) || (ldx % 8) || (ldw % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
+  if (workspace == nullptr || ws_bytes < MX_WS_PARTIAL_OFFSET) return -2;
+  const bool glu = epilogue == MX_EPI_SWIGLU || epilogue == MX_EPI_GEGLU ||
+                   epilogue == MX_EPI_CLIPPED_SWIGLU;
+  const bool swap = force_mode == 2 || (force_mode == 0 && M <= 256);
+  const int w_rows = glu ? (glu_offset + N) : N;
+
+  GemmParams p{};
+  p.out = out;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = (epilogue == MX_EPI_RESIDUAL) ? static_cast<const __nv_bfloat16*>(residual) : nullptr;
+  if (epilogue == MX_EPI_NONE) p.bias = nullptr;
+  p.status = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + MX_WS_STATUS_OFFSET);
+  p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + MX_WS_COUNTER_OFFSET);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + MX_WS_PARTIAL_OFFSET);
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldo = ldo;
+  p.ldr = ldr;
+  p.glu_offset = glu_offset;
+  p.epilogue = epilogue;
+  p.out_fp32 = out_fp32;
+  p.glu_alpha = glu_alpha;
+  p.glu_limit = glu_limit;
+  p.num_kb = (K + kBK - 1) / kBK;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+
+  const int sms = device_sm_count();
+  int bn;
+  if (swap) {
+    bn = (M <= 16) ? 16 : (M <= 32) ? 32 : (M <= 64) ? 64 : 128;
+    p.tiles_lane = (N + kLaneRows - 1) / kLaneRows;
+    p.tiles_col = (M + bn - 1) / bn;
+    const int tiles = p.tiles_lane * p.tiles_col;
+    int splits = force_splits > 0 ? force_splits : sms / tiles;
+    if (splits > p.num_kb / 4) splits = p.num_kb / 4;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+    const int acc_cols = glu ? 2 * bn : bn;
+    const long long ws_floats = (ws_bytes - MX_WS_PARTIAL_OFFSET) / 4;
+    while (splits > 1 && (static_cast<long long>(tiles) * splits * kLaneRows * acc_cols > ws_floats ||
+                          tiles > MX_WS_COUNTER_BYTES / 4))
+      --splits;
+    p.kb_per_split = (p.num_kb + splits - 1) / splits;
+    p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+  } else {
+    bn = glu ? 128 : (N > 128 ? 256 : 128);
+    p.tiles_lane = (M + kLaneRows - 1) / kLaneRows;
+    p.tiles_col = (N + bn - 1) / bn;
+  }
+  const long long total = static_cast<long long>(p.tiles_lane) * p.tiles_col * p.splits;
+  const int grid = static_cast<int>(total < sms ? total : sms);
+
+  CUtensorMap map_x, map_w;
+  const uint32_t x_box = swap ? bn : kLaneRows;
+  const uint32_t w_box = swap ? kLaneRows : bn;
+  if (!make_tensor_map_bf16(&map_x, x, M, K, ldx, x_box, kBK)) return -4;
+  if (!make_tensor_map_bf16(&map_w, w, w_rows, K, ldw, w_box, kBK)) return -4;
+  const CUtensorMap& ml = swap ? map_w : map_x;
+  const CUtensorMap& mc = swap ? map_x : map_w;
+
+#define MX_LAUNCH(BN_, SWAP_, GLU_) return launch_gemm<BN_, SWAP_, GLU_>(ml, mc, p, grid, stream)
+  if (swap) {
+    if (glu) {
+      switch (bn) {
+        case 16: MX_LAUNCH(16, true, true);
+        case 32: MX_LAUNCH(32, true, true);
+        case 64: MX_LAUNCH(64, true, true);
+        default: MX_LAUNCH(128, true, true);
+      }
+    } else {
+      switch (bn) {
+        case 16: MX_LAUNCH(16, true, false);
+        case 32: MX_LAUNCH(32, true, false);
+        case 64: MX_LAUNCH(64, true, false);
+        default: MX_LAUNCH(128, true, false);
+      }
+    }
+  } else {
+    if (glu) MX_LAUNCH(128, false, true);
+    if (bn == 256) MX_LAUNCH(256, false, false);
+    MX_LAUNCH(128, false, false);
+  }
+#undef MX_LAUNCH
+}

@@ -1,0 +1,395 @@
+// Memory-bound row kernels: residual-add + RMSNorm, per-head RMSNorm, RoPE + paged KV append
+// (with optional 8-bit affine KV quantization), embedding gather, gated activations.
+//
+// Parity targets in the reference: fused_add_rms_norm (src/lib/mlxcelverse/kernels/fused_norm.h:17-77),
+// fused_rope_qk_append (src/lib/mlxcelverse/kernels/fused_rope_append.h:17-114) and the per-token
+// int8 KV quantizer (src/lib/mlxcel-core/src/cache.rs:366-412). Unlike the reference's append
+// kernel this one writes straight into the paged block pool.
+#include "api.h"
+#include "common.cuh"
+
+namespace mx {
+
+// ----------------------------------------------------------------------------- add + rmsnorm
+// One CTA per row; 16-byte vector loads; values stay in registers between the two passes
+// (up to 4 vectors per thread), so each row is read once and written once per output.
+template <int VPT>
+__global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,
+                                   const __nv_bfloat16* __restrict__ residual,
+                                   const __nv_bfloat16* __restrict__ weight,
+                                   __nv_bfloat16* __restrict__ y,
+                                   __nv_bfloat16* __restrict__ residual_out, int dim, float eps,
+                                   float w_bias) {
+  const int row = blockIdx.x;
+  const int nvec = dim >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * dim);
+  const uint4* rr =
+      residual ? reinterpret_cast<const uint4*>(residual + static_cast<size_t>(row) * dim) : nullptr;
+  uint4* ro = residual_out
+                  ? reinterpret_cast<uint4*>(residual_out + static_cast<size_t>(row) * dim)
+                  : nullptr;
+  float vals[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      uint4 a = xr[v];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        f[2 * j] = bf16_lo(aw[j]);
+        f[2 * j + 1] = bf16_hi(aw[j]);
+      }
+      if (rr) {
+        uint4 b = rr[v];
+        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          f[2 * j] += bf16_lo(bw[j]);
+          f[2 * j + 1] += bf16_hi(bw[j]);
+        }
+      }
+      if (ro) {
+        // The residual stream is kept in bf16; the norm sees the rounded value so that the
+        // fused and the unfused paths agree bit for bit.
+        uint4 o;
+        o.x = pack_bf16(f[0], f[1]);
+        o.y = pack_bf16(f[2], f[3]);
+        o.z = pack_bf16(f[4], f[5]);
+        o.w = pack_bf16(f[6], f[7]);
+        ro[v] = o;
+        const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          f[2 * j] = bf16_lo(ow[j]);
+          f[2 * j + 1] = bf16_hi(ow[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        vals[i][j] = f[j];
+        ss += f[j] * f[j];
+      }
+    }
+  }
+  __shared__ float red[32];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) red[0] = t;
+  }
+  __syncthreads();
+  const float rstd = rsqrtf(red[0] / static_cast<float>(dim) + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * dim);
+  const uint4* wr = reinterpret_cast<const uint4*>(weight);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      uint4 wv = wr[v];
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o[2 * j] = vals[i][2 * j] * rstd * (bf16_lo(ww[j]) + w_bias);
+        o[2 * j + 1] = vals[i][2 * j + 1] * rstd * (bf16_hi(ww[j]) + w_bias);
+      }
+      uint4 ov;
+      ov.x = pack_bf16(o[0], o[1]);
+      ov.y = pack_bf16(o[2], o[3]);
+      ov.z = pack_bf16(o[4], o[5]);
+      ov.w = pack_bf16(o[6], o[7]);
+      yr[v] = ov;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- head rmsnorm
+// One warp per (token, head).
+__global__ void head_rmsnorm_kernel(__nv_bfloat16* __restrict__ x,
+                                    const __nv_bfloat16* __restrict__ weight, int tokens, int heads,
+                                    int head_dim, long long token_stride, float eps) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= tokens * heads) return;
+  const int t = gw / heads, h = gw - t * heads;
+  __nv_bfloat16* p = x + static_cast<size_t>(t) * token_stride + static_cast<size_t>(h) * head_dim;
+  float ss = 0.f;
+  for (int i = lane; i < head_dim; i += 32) {
+    float v = __bfloat162float(p[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / head_dim + eps);
+  for (int i = lane; i < head_dim; i += 32)
+    p[i] = __float2bfloat16(__bfloat162float(p[i]) * rstd * __bfloat162float(weight[i]));
+}
+
+// ----------------------------------------------------------------------------- rope + append
+// One warp per (token, head slot); slots are [0,Hq) q heads, [Hq,Hq+Hkv) k heads, then v heads.
+// The head's D values are staged in shared memory as fp32 so that any rotary pairing
+// (half-split or interleaved, partial rotary) is a plain indexed read.
+constexpr int kRopeWarps = 4;
+constexpr int kMaxHeadDim = 256;
+
+template <int KV_BITS>
+__global__ void rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                   const int* __restrict__ slot_mapping,
+                                   const float* __restrict__ inv_freq, void* __restrict__ k_pool,
+                                   void* __restrict__ v_pool, __nv_bfloat16* __restrict__ k_meta,
+                                   __nv_bfloat16* __restrict__ v_meta,
+                                   const __nv_bfloat16* __restrict__ q_norm_w,
+                                   const __nv_bfloat16* __restrict__ k_norm_w, float norm_eps, int T,
+                                   int Hq, int Hkv, int D, int rot_dim, int block_size,
+                                   int rope_mode, float mscale) {
+  __shared__ float stage[kRopeWarps][kMaxHeadDim];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = Hq + 2 * Hkv;
+  const long long gw = static_cast<long long>(blockIdx.x) * kRopeWarps + warp;
+  if (gw >= static_cast<long long>(T) * slots) return;
+  const int t = static_cast<int>(gw / slots);
+  const int s = static_cast<int>(gw - static_cast<long long>(t) * slots);
+  const bool is_q = s < Hq;
+  const bool is_k = !is_q && s < Hq + Hkv;
+  const int kvh = is_q ? 0 : (is_k ? s - Hq : s - Hq - Hkv);
+  __nv_bfloat16* src = qkv + static_cast<size_t>(t) * slots * D + static_cast<size_t>(s) * D;
+  float* st = stage[warp];
+
+  const int slot = slot_mapping[t];
+  if (!is_q && slot < 0) return;  // padded token: nothing to append
+
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    float v = __bfloat162float(src[i]);
+    st[i] = v;
+    ss += v * v;
+  }
+  const __nv_bfloat16* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+  if (nw != nullptr) {
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / D + norm_eps);
+    __syncwarp();
+    for (int i = lane; i < D; i += 32) {
+      // Round through bf16 like an unfused norm would, then rotate in fp32.
+      st[i] = __bfloat162float(__float2bfloat16(st[i] * rstd * __bfloat162float(nw[i])));
+    }
+  }
+  __syncwarp();
+
+  if (is_q || is_k) {
+    const float pos = static_cast<float>(positions[t]);
+    const int half = rot_dim >> 1;
+    // Each lane rotates pairs p = lane, lane + 32, ...; results go back to the stage.
+    float r1[kMaxHeadDim / 64], r2[kMaxHeadDim / 64];
+    int n = 0;
+    for (int p = lane; p < half; p += 32, ++n) {
+      const int i1 = rope_mode == 0 ? p : 2 * p;
+      const int i2 = rope_mode == 0 ? p + half : 2 * p + 1;
+      float sn, cs;
+      sincosf(pos * inv_freq[p], &sn, &cs);
+      const float a = st[i1], b = st[i2];
+      r1[n] = (a * cs - b * sn) * mscale;
+      r2[n] = (b * cs + a * sn) * mscale;
+    }
+    __syncwarp();
+    n = 0;
+    for (int p = lane; p < half; p += 32, ++n) {
+      const int i1 = rope_mode == 0 ? p : 2 * p;
+      const int i2 = rope_mode == 0 ? p + half : 2 * p + 1;
+      st[i1] = r1[n];
+      st[i2] = r2[n];
+    }
+    if (mscale != 1.0f) {
+      for (int i = rot_dim + lane; i < D; i += 32) st[i] *= mscale;
+    }
+    __syncwarp();
+  }
+
+  if (is_q) {
+    for (int i = lane; i < D; i += 32) src[i] = __float2bfloat16(st[i]);
+    return;
+  }
+
+  const int blk = slot / block_size, off = slot - blk * block_size;
+  const size_t row = (static_cast<size_t>(blk) * Hkv + kvh) * block_size + off;
+  if (KV_BITS == 16) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(is_k ? k_pool : v_pool) + row * D;
+    for (int i = lane; i < D; i += 32) dst[i] = __float2bfloat16(st[i]);
+  } else {
+    // 8-bit affine, groups of 64 along D: q = round((x - min) / scale), scale = (max - min) / 255.
+    uint8_t* dst = reinterpret_cast<uint8_t*>(is_k ? k_pool : v_pool) + row * D;
+    __nv_bfloat16* meta = (is_k ? k_meta : v_meta) + row * (D / 64) * 2;
+    for (int g = 0; g < D / 64; ++g) {
+      const float a = st[g * 64 + lane], b = st[g * 64 + 32 + lane];
+      float mn = fminf(a, b), mxv = fmaxf(a, b);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mxv = fmaxf(mxv, __shfl_xor_sync(0xffffffffu, mxv, o));
+      }
+      // Scale and bias are stored in bf16; quantize against the rounded values so that
+      // dequantization reproduces what the quantizer saw.
+      float scale = __bfloat162float(__float2bfloat16((mxv - mn) / 255.0f));
+      const float bias = __bfloat162float(__float2bfloat16(mn));
+      if (scale == 0.f) scale = 1.0f;
+      const float inv = 1.0f / scale;
+      const int qa = min(255, max(0, __float2int_rn((a - bias) * inv)));
+      const int qb = min(255, max(0, __float2int_rn((b - bias) * inv)));
+      dst[g * 64 + lane] = static_cast<uint8_t>(qa);
+      dst[g * 64 + 32 + lane] = static_cast<uint8_t>(qb);
+      if (lane == 0) {
+        meta[g * 2] = __float2bfloat16(scale);
+        meta[g * 2 + 1] = __float2bfloat16(bias);
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- embedding
+__global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                 __nv_bfloat16* __restrict__ out, int dim, int vocab, float scale) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const int nvec = dim >> 3;
+  uint4* o = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * dim);
+  if (id < 0 || id >= vocab) {
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) o[v] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * dim);
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    uint4 a = src[v];
+    if (scale != 1.0f) {
+      uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = pack_bf16(bf16_lo(w[j]) * scale, bf16_hi(w[j]) * scale);
+      a = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    o[v] = a;
+  }
+}
+
+// ----------------------------------------------------------------------------- gated act
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gate_up,
+                              __nv_bfloat16* __restrict__ out, long long total, int I, int mode,
+                              float alpha, float limit) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / I;
+  const int i = static_cast<int>(idx - t * I);
+  float g = __bfloat162float(gate_up[t * 2 * I + i]);
+  float u = __bfloat162float(gate_up[t * 2 * I + I + i]);
+  float r;
+  if (mode == 0) {
+    r = g / (1.0f + __expf(-g)) * u;
+  } else if (mode == 1) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    r = 0.5f * g * (1.0f + tanhf(k0 * (g + k1 * g * g * g))) * u;
+  } else {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    r = g / (1.0f + __expf(-alpha * g)) * (u + 1.0f);
+  }
+  out[idx] = __float2bfloat16(r);
+}
+
+}  // namespace mx
+
+using namespace mx;
+
+extern "C" int mx_add_rmsnorm(const void* x, const void* residual, const void* weight, void* y,
+                              void* residual_out, int rows, int dim, float eps, float w_bias,
+                              void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows <= 0) return 0;
+  if (dim % 8 != 0 || dim > 32768) return -1;
+  const int nvec = dim / 8;
+  int threads = ((nvec + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  const int vpt = (nvec + threads - 1) / threads;
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto R = static_cast<const __nv_bfloat16*>(residual);
+  auto W = static_cast<const __nv_bfloat16*>(weight);
+  auto Y = static_cast<__nv_bfloat16*>(y);
+  auto RO = static_cast<__nv_bfloat16*>(residual_out);
+  if (vpt <= 1)
+    add_rmsnorm_kernel<1><<<rows, threads, 0, stream>>>(X, R, W, Y, RO, dim, eps, w_bias);
+  else if (vpt <= 2)
+    add_rmsnorm_kernel<2><<<rows, threads, 0, stream>>>(X, R, W, Y, RO, dim, eps, w_bias);
+  else
+    add_rmsnorm_kernel<4><<<rows, threads, 0, stream>>>(X, R, W, Y, RO, dim, eps, w_bias);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mx_head_rmsnorm(void* x, const void* weight, int tokens, int heads, int head_dim,
+                               long long token_stride, float eps, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long warps = static_cast<long long>(tokens) * heads;
+  if (warps <= 0) return 0;
+  const int threads = 128;
+  const int blocks = static_cast<int>((warps * 32 + threads - 1) / threads);
+  head_rmsnorm_kernel<<<blocks, threads, 0, stream>>>(static_cast<__nv_bfloat16*>(x),
+                                                      static_cast<const __nv_bfloat16*>(weight),
+                                                      tokens, heads, head_dim, token_stride, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mx_rope_append(void* qkv, const int* positions, const int* slot_mapping,
+                              const float* inv_freq, void* k_pool, void* v_pool, void* k_meta,
+                              void* v_meta, const void* q_norm_w, const void* k_norm_w,
+                              float norm_eps, int T, int Hq, int Hkv, int D, int rot_dim,
+                              int block_size, int rope_mode, float mscale, int kv_bits,
+                              void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (T <= 0) return 0;
+  if (D > kMaxHeadDim || D % 2 || rot_dim > D || rot_dim % 2) return -1;
+  if (kv_bits == 8 && D % 64) return -1;
+  if (kv_bits != 16 && kv_bits != 8) return -1;
+  const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
+  const int blocks = static_cast<int>((warps + kRopeWarps - 1) / kRopeWarps);
+  auto Q = static_cast<__nv_bfloat16*>(qkv);
+  auto KM = static_cast<__nv_bfloat16*>(k_meta);
+  auto VM = static_cast<__nv_bfloat16*>(v_meta);
+  auto QN = static_cast<const __nv_bfloat16*>(q_norm_w);
+  auto KN = static_cast<const __nv_bfloat16*>(k_norm_w);
+  if (kv_bits == 16)
+    rope_append_kernel<16><<<blocks, kRopeWarps * 32, 0, stream>>>(
+        Q, positions, slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv,
+        D, rot_dim, block_size, rope_mode, mscale);
+  else
+    rope_append_kernel<8><<<blocks, kRopeWarps * 32, 0, stream>>>(
+        Q, positions, slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv,
+        D, rot_dim, block_size, rope_mode, mscale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mx_embedding(const int* ids, const void* table, void* out, int T, int dim, int vocab,
+                            float scale, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (T <= 0) return 0;
+  if (dim % 8) return -1;
+  int threads = dim / 8;
+  if (threads > 256) threads = 256;
+  if (threads < 32) threads = 32;
+  embedding_kernel<<<T, threads, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table),
+                                              static_cast<__nv_bfloat16*>(out), dim, vocab, scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mx_swiglu(const void* gate_up, void* out, int T, int I, int mode, float alpha,
+                         float limit, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long total = static_cast<long long>(T) * I;
+  if (total <= 0) return 0;
+  const int threads = 256;
+  const int blocks = static_cast<int>((total + threads - 1) / threads);
+  swiglu_kernel<<<blocks, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up),
+                                                static_cast<__nv_bfloat16*>(out), total, I, mode,
+                                                alpha, limit);
+  return static_cast<int>(cudaGetLastError());
+}

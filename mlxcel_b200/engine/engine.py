@@ -1,0 +1,491 @@
+"""Engine: continuous batching over the paged KV pool.
+
+The engine owns the model executor, the KV pool and the C++ block manager and is the only
+path to a model forward (the role of ``Engine<M>`` in the reference,
+src/lib/mlxcel-core/src/engine/mod.rs:148-540). One :meth:`Engine.step` forms a batch (all
+decoding rows + prefill chunks under a token budget, admission under the block watermark,
+preemption by recompute under block pressure), runs one forward pass, samples, and applies the
+shared finish step (EOS / stop ids / max tokens / loop detection,
+src/lib/mlxcel-core/src/decode_finish.rs).
+
+Pure decode steps replay CUDA graphs captured per padded batch size; every buffer a captured
+kernel reads is a persistent device tensor that the host refreshes from pinned memory.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.kv_pool import KVPool
+from ..config import ModelConfig
+from ..host_runtime import BlockManager, TickAction, TickState, decide_tick, prefill_piece
+from ..models.decoder import DecoderModel, StepBatch
+from .params import FinishReason, SamplingParams, SeqStatus
+from .sampler import Sampler
+
+
+@dataclass
+class Sequence:
+    seq_id: int
+    prompt: list[int]
+    params: SamplingParams
+    output: list[int] = field(default_factory=list)
+    logprobs: list[float] = field(default_factory=list)
+    num_computed: int = 0          # tokens whose KV is in the pool
+    num_cached: int = 0            # prompt tokens adopted from the prefix cache
+    status: SeqStatus = SeqStatus.QUEUED
+    finish_reason: FinishReason | None = None
+    arrival: float = 0.0
+    first_token_time: float | None = None
+    finish_time: float | None = None
+    preemptions: int = 0
+    on_token: Callable | None = None
+    mask_fn: Callable | None = None   # structured output: fn(seq) -> bool mask [V] or None
+    user_data: object = None
+
+    @property
+    def tokens(self) -> list[int]:
+        return self.prompt + self.output
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+
+@dataclass
+class EngineConfig:
+    max_batch: int = 64                  # concurrent decoding rows (--parallel)
+    max_num_batched_tokens: int = 8192   # token budget of one forward pass
+    prefill_chunk_alone: int = 2048      # DEFAULT_PREFILL_CHUNK (prefill_plan.rs:65)
+    prefill_chunk_contended: int = 512   # CONTENDED_PREFILL_CHUNK (prefill_plan.rs:72)
+    max_prefill_seqs: int = 8            # prefill cohort size per step
+    block_size: int = 16
+    num_blocks: int = 0                  # 0 = size from free memory
+    kv_bits: int = 16
+    gpu_memory_utilization: float = 0.90
+    watermark: float = 0.01
+    prefix_cache: bool = True
+    max_queue_depth: int = 4096
+    max_model_len: int = 8192
+    cuda_graphs: bool = True
+    prefill_grant_interval: int = 16
+    mixed_steps: bool = True
+    preemption: bool = True
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, cfg: ModelConfig, ecfg: EngineConfig | None = None):
+        self.model, self.cfg = model, cfg
+        self.ecfg = ecfg or EngineConfig()
+        e = self.ecfg
+        self.device = model.device
+        self.is_cuda = self.device.type == "cuda"
+        tp = model.comm.tp_size
+        nl = len(model.w.layers)
+        if e.num_blocks <= 0:
+            e.num_blocks = self._auto_num_blocks(tp, nl)
+        self.pool = KVPool(cfg, e.num_blocks, e.block_size, kv_bits=e.kv_bits, device=self.device,
+                           tp_size=tp, num_layers=nl)
+        self.bm = BlockManager(e.num_blocks, e.block_size, e.prefix_cache, e.watermark)
+        self.sampler = Sampler(cfg.vocab_size, self.device)
+        self.max_blocks_per_seq = (e.max_model_len + e.block_size - 1) // e.block_size
+        self.waiting: deque[Sequence] = deque()
+        self.running: list[Sequence] = []      # PREFILLING or DECODING, in admission order
+        self.seqs: dict[int, Sequence] = {}
+        self._next_id = 0
+        self._decode_ticks_since_grant = 0
+        self._graphs: dict[tuple, tuple] = {}
+        self._alloc_buffers()
+        self.stats = dict(steps=0, decode_steps=0, prefill_tokens=0, decode_tokens=0, preemptions=0,
+                          graph_replays=0, prefix_hit_tokens=0)
+
+    # ------------------------------------------------------------------ setup
+    def _auto_num_blocks(self, tp: int, nl: int) -> int:
+        e = self.ecfg
+        per_block = KVPool.bytes_per_block(self.cfg, e.block_size, e.kv_bits, tp, nl)
+        if self.is_cuda:
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = free - (1.0 - e.gpu_memory_utilization) * total - (6 << 30)
+            n = int(max(budget, 1 << 30) // per_block)
+        else:
+            n = 2048
+        need = (e.max_model_len // e.block_size + 2) * e.max_batch * 2
+        return max(64, min(n, need))
+
+    def _alloc_buffers(self) -> None:
+        e = self.ecfg
+        T, B, MB = e.max_num_batched_tokens, e.max_batch, self.max_blocks_per_seq
+        S = e.max_prefill_seqs
+        pin = self.is_cuda
+
+        def host(shape, dtype):
+            t = torch.zeros(shape, dtype=dtype)
+            return t.pin_memory() if pin else t
+
+        def dev(shape, dtype):
+            return torch.zeros(shape, dtype=dtype, device=self.device)
+
+        self.h_tokens, self.d_tokens = host(T, torch.int32), dev(T, torch.int32)
+        self.h_pos, self.d_pos = host(T, torch.int32), dev(T, torch.int32)
+        self.h_slots, self.d_slots = host(T, torch.int32), dev(T, torch.int32)
+        self.h_dec_tables, self.d_dec_tables = host((B, MB), torch.int32), dev((B, MB), torch.int32)
+        self.h_dec_lens, self.d_dec_lens = host(B, torch.int32), dev(B, torch.int32)
+        self.h_pf_tables, self.d_pf_tables = host((S, MB), torch.int32), dev((S, MB), torch.int32)
+        self.h_pf_lens, self.d_pf_lens = host(S, torch.int32), dev(S, torch.int32)
+        self.h_cu, self.d_cu = host(S + 1, torch.int32), dev(S + 1, torch.int32)
+        self.h_rows, self.d_rows = host(B + S, torch.int64), dev(B + S, torch.int64)
+        self.h_out, self.d_out = host(B + S, torch.int32), dev(B + S, torch.int32)
+        self.np_dec_tables = self.h_dec_tables.numpy()
+        self.np_pf_tables = self.h_pf_tables.numpy()
+        self.np_slots = self.h_slots.numpy()
+
+    # ------------------------------------------------------------------ request API
+    def add_request(self, prompt: list[int], params: SamplingParams | None = None,
+                    on_token: Callable | None = None, mask_fn: Callable | None = None,
+                    user_data=None) -> int:
+        if not prompt:
+            raise ValueError("empty prompt")
+        params = params or SamplingParams()
+        if len(prompt) + 1 > self.ecfg.max_model_len:
+            raise ValueError(f"prompt of {len(prompt)} tokens exceeds max_model_len {self.ecfg.max_model_len}")
+        if len(self.waiting) >= self.ecfg.max_queue_depth:
+            raise RuntimeError("queue full")
+        sid = self._next_id
+        self._next_id += 1
+        s = Sequence(sid, list(prompt), params, arrival=time.perf_counter(), on_token=on_token,
+                     mask_fn=mask_fn, user_data=user_data)
+        self.seqs[sid] = s
+        if params.priority > 0:
+            # priority lanes: insert before the first lower-priority request
+            idx = next((i for i, w in enumerate(self.waiting) if w.params.priority < params.priority),
+                       len(self.waiting))
+            self.waiting.insert(idx, s)
+        else:
+            self.waiting.append(s)
+        return sid
+
+    def abort(self, seq_id: int) -> None:
+        s = self.seqs.get(seq_id)
+        if s is None or s.status == SeqStatus.FINISHED:
+            return
+        self._finish(s, FinishReason.CANCELLED)
+        if s in self.waiting:
+            self.waiting.remove(s)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def release(self, seq_id: int) -> Sequence | None:
+        """Forget a finished sequence (its blocks were already returned to the pool)."""
+        return self.seqs.pop(seq_id, None)
+
+    # ------------------------------------------------------------------ scheduling
+    def _finish(self, s: Sequence, reason: FinishReason) -> None:
+        s.status, s.finish_reason, s.finish_time = SeqStatus.FINISHED, reason, time.perf_counter()
+        if self.bm.has_seq(s.seq_id):
+            # donate computed full blocks to the prefix cache, then drop our references
+            toks = np.asarray(s.tokens[: s.num_computed], dtype=np.int32)
+            self.bm.commit(s.seq_id, toks, s.num_computed)
+            self.bm.free_seq(s.seq_id)
+        if s in self.running:
+            self.running.remove(s)
+
+    def _preempt_one(self) -> bool:
+        """Reclaim blocks by recompute-preempting the least progressed running row
+        (reclaim order of the reference: cached prefixes are evicted first by the block manager
+        itself, docs/CONTINUOUS_BATCHING.md:358-363)."""
+        cands = [s for s in self.running]
+        if len(cands) <= 1:
+            return False
+        victim = min(cands, key=lambda s: (len(s.output), -s.seq_id))
+        self.running.remove(victim)
+        self.bm.free_seq(victim.seq_id)
+        victim.num_computed = 0
+        victim.status = SeqStatus.PREEMPTED
+        victim.preemptions += 1
+        self.stats["preemptions"] += 1
+        self.waiting.appendleft(victim)
+        return True
+
+    def _schedule(self):
+        """Returns (decode_seqs, [(seq, start, count)] prefill pieces)."""
+        e = self.ecfg
+        decode = [s for s in self.running if s.status == SeqStatus.DECODING]
+        # reserve the next slot of every decoding row; preempt under pressure
+        i = 0
+        while i < len(decode):
+            s = decode[i]
+            if self.bm.reserve(s.seq_id, s.total_len):
+                i += 1
+                continue
+            if not (e.preemption and self._preempt_one()):
+                raise RuntimeError("KV pool exhausted and nothing to preempt")
+            decode = [s for s in self.running if s.status == SeqStatus.DECODING]
+            i = 0
+        parked = [s for s in self.running if s.status == SeqStatus.PREFILLING]
+        st = TickState()
+        st.active_rows = len(decode)
+        st.max_batch = e.max_batch
+        st.queued = len(self.waiting)
+        st.parked_prefill = bool(parked)
+        st.decode_ticks_since_prefill_grant = self._decode_ticks_since_grant
+        st.prefill_grant_interval = e.prefill_grant_interval
+        st.mixed_steps = e.mixed_steps
+        if self.waiting:
+            nxt = self.waiting[0]
+            st.blocks_available = self.bm.can_allocate(
+                self.bm.blocks_needed(nxt.seq_id, nxt.total_len + 1) if self.bm.has_seq(nxt.seq_id)
+                else (nxt.total_len + e.block_size) // e.block_size, True)
+        d = decide_tick(st)
+        pieces: list[tuple[Sequence, int, int]] = []
+        run_decode = d.action in (TickAction.Decode, TickAction.MixedStep)
+        run_prefill = d.action in (TickAction.Prefill, TickAction.MixedStep)
+        if not run_decode:
+            decode_rows = []
+        else:
+            decode_rows = decode
+        if run_prefill:
+            budget = e.max_num_batched_tokens - len(decode_rows)
+            n_dec = len(decode_rows)
+            # continue parked prefills first, then admit from the queue
+            cands = list(parked)
+            while (self.waiting and len(cands) < e.max_prefill_seqs and
+                   len(self.running) + (len(cands) - len(parked)) < e.max_batch):
+                s = self.waiting[0]
+                need_blocks = (s.total_len + e.block_size) // e.block_size
+                if not self.bm.can_allocate(need_blocks, True) and (self.running or cands):
+                    break
+                self.waiting.popleft()
+                if not self.bm.has_seq(s.seq_id):
+                    self.bm.create(s.seq_id, 0)
+                    toks = np.asarray(s.tokens, dtype=np.int32)
+                    hit = self.bm.match_prefix(s.seq_id, toks)
+                    s.num_computed = s.num_cached = hit
+                    self.stats["prefix_hit_tokens"] += hit
+                s.status = SeqStatus.PREFILLING
+                cands.append(s)
+            for s in cands:
+                if budget <= 0:
+                    break
+                remaining = s.total_len - s.num_computed
+                piece = prefill_piece(budget + n_dec, n_dec, max(e.prefill_chunk_alone, 1),
+                                      max(e.prefill_chunk_contended, 1), remaining)
+                piece = min(piece, budget)
+                if piece <= 0:
+                    break
+                if not self.bm.reserve(s.seq_id, s.num_computed + piece):
+                    if s not in self.running:
+                        # could not get blocks after all: back to the queue
+                        self.bm.free_seq(s.seq_id)
+                        s.status, s.num_computed = SeqStatus.QUEUED, 0
+                        self.waiting.appendleft(s)
+                    break
+                if s not in self.running:
+                    self.running.append(s)
+                pieces.append((s, s.num_computed, piece))
+                budget -= piece
+            # admitted but unscheduled candidates stay parked in `running`
+            for s in cands:
+                if s.status == SeqStatus.PREFILLING and s not in self.running and self.bm.has_seq(s.seq_id):
+                    self.running.append(s)
+            self._decode_ticks_since_grant = 0
+        elif run_decode:
+            self._decode_ticks_since_grant += 1
+        return decode_rows, pieces
+
+    # ------------------------------------------------------------------ batch building
+    def _build_batch(self, decode: list[Sequence], pieces) -> tuple[StepBatch, int]:
+        nd = len(decode)
+        t = 0
+        tok, pos = self.h_tokens.numpy(), self.h_pos.numpy()
+        for i, s in enumerate(decode):
+            L = s.total_len
+            tok[i] = s.output[-1] if s.output else s.prompt[-1]
+            pos[i] = L - 1
+            self.bm.fill_slots(s.seq_id, L - 1, 1, self.np_slots, i)
+            self.h_dec_lens[i] = L
+        max_len = max((s.total_len for s in decode), default=0)
+        if nd:
+            self.bm.fill_tables([s.seq_id for s in decode], self.np_dec_tables)
+        t = nd
+        cu = [0]
+        max_q = 0
+        rows: list[int] = list(range(nd))
+        for j, (s, start, count) in enumerate(pieces):
+            toks = s.tokens
+            tok[t:t + count] = toks[start:start + count]
+            pos[t:t + count] = np.arange(start, start + count, dtype=np.int32)
+            self.bm.fill_slots(s.seq_id, start, count, self.np_slots, t)
+            self.h_pf_lens[j] = start + count
+            t += count
+            cu.append(t - nd)
+            max_q = max(max_q, count)
+            if start + count >= s.total_len:
+                rows.append(t - 1)
+        if pieces:
+            self.bm.fill_tables([p[0].seq_id for p in pieces], self.np_pf_tables)
+            self.h_cu[: len(cu)] = torch.tensor(cu, dtype=torch.int32)
+        R = len(rows)
+        self.h_rows[:R] = torch.tensor(rows, dtype=torch.int64)
+        nb = self.is_cuda
+        sp = len(pieces)
+        self.d_tokens[:t].copy_(self.h_tokens[:t], non_blocking=nb)
+        self.d_pos[:t].copy_(self.h_pos[:t], non_blocking=nb)
+        self.d_slots[:t].copy_(self.h_slots[:t], non_blocking=nb)
+        if nd:
+            self.d_dec_tables[:nd].copy_(self.h_dec_tables[:nd], non_blocking=nb)
+            self.d_dec_lens[:nd].copy_(self.h_dec_lens[:nd], non_blocking=nb)
+        if sp:
+            self.d_pf_tables[:sp].copy_(self.h_pf_tables[:sp], non_blocking=nb)
+            self.d_pf_lens[:sp].copy_(self.h_pf_lens[:sp], non_blocking=nb)
+            self.d_cu[: sp + 1].copy_(self.h_cu[: sp + 1], non_blocking=nb)
+        self.d_rows[:R].copy_(self.h_rows[:R], non_blocking=nb)
+        b = StepBatch(token_ids=self.d_tokens[:t], positions=self.d_pos[:t],
+                      slot_mapping=self.d_slots[:t], num_decode=nd,
+                      dec_block_tables=self.d_dec_tables[:nd] if nd else None,
+                      dec_context_lens=self.d_dec_lens[:nd] if nd else None, dec_max_len=max_len,
+                      num_prefill_seqs=sp, pf_block_tables=self.d_pf_tables[:sp] if sp else None,
+                      pf_cu_q=self.d_cu[: sp + 1] if sp else None,
+                      pf_context_lens=self.d_pf_lens[:sp] if sp else None, pf_max_q_len=max_q,
+                      logits_rows=self.d_rows[:R])
+        return b, R
+
+    # ------------------------------------------------------------------ cuda graphs
+    def _decode_graph(self, nd: int, max_len: int) -> torch.Tensor | None:
+        """Replay (capturing on first use) the decode graph for the padded batch size.
+        Returns the logits tensor [Bpad, V] owned by the graph, or None when graphs are off."""
+        e = self.ecfg
+        if not (self.is_cuda and e.cuda_graphs):
+            return None
+        bp = 1
+        while bp < nd:
+            bp *= 2
+        bp = min(bp, e.max_batch) if e.max_batch >= nd else nd
+        if bp < nd:
+            return None
+        splits = ops.decode_splits(bp, self.model.Hkv, max(max_len, 1))
+        key = (bp, splits)
+        # padding rows: no KV append, zero context
+        if bp > nd:
+            self.d_tokens[nd:bp].zero_()
+            self.d_pos[nd:bp].zero_()
+            self.d_slots[nd:bp].fill_(-1)
+            self.d_dec_lens[nd:bp].zero_()
+            self.d_dec_tables[nd:bp].zero_()
+        ent = self._graphs.get(key)
+        if ent is None:
+            b = StepBatch(token_ids=self.d_tokens[:bp], positions=self.d_pos[:bp],
+                          slot_mapping=self.d_slots[:bp], num_decode=bp,
+                          dec_block_tables=self.d_dec_tables[:bp], dec_context_lens=self.d_dec_lens[:bp],
+                          dec_max_len=max_len, logits_rows=None)
+            fwd = lambda: self.model.forward(b, self.pool.layers)  # noqa: E731
+            # warm-up outside capture (sets function attributes, fills descriptor caches)
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                fwd()
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                logits = fwd()
+            ent = (g, logits, splits)
+            self._graphs[key] = ent
+        ent[0].replay()
+        self.stats["graph_replays"] += 1
+        return ent[1]
+
+    # ------------------------------------------------------------------ step
+    @torch.inference_mode()
+    def step(self) -> list[Sequence]:
+        """One scheduling tick + forward + sample. Returns the sequences that finished."""
+        decode, pieces = self._schedule()
+        if not decode and not pieces:
+            return []
+        b, R = self._build_batch(decode, pieces)
+        nd = len(decode)
+        logits = None
+        if not pieces and nd:
+            gl = self._decode_graph(nd, b.dec_max_len)
+            if gl is not None:
+                logits = gl[:nd]
+                self.stats["decode_steps"] += 1
+        if logits is None:
+            logits = self.model.forward(b, self.pool.layers)
+        # rows: decode rows first, then prefill rows that completed their prompt
+        sample_seqs = list(decode) + [s for (s, start, cnt) in pieces if start + cnt >= s.total_len]
+        toks, lps = self.sampler.sample(logits, sample_seqs)
+        self.stats["steps"] += 1
+        self.stats["decode_tokens"] += nd
+        self.stats["prefill_tokens"] += sum(p[2] for p in pieces)
+        finished: list[Sequence] = []
+        for s, _, cnt in pieces:
+            s.num_computed += cnt
+        for s in decode:
+            s.num_computed = s.total_len
+        now = time.perf_counter()
+        for i, s in enumerate(sample_seqs):
+            tok = int(toks[i])
+            if s.status == SeqStatus.PREFILLING:
+                s.status = SeqStatus.DECODING
+            if s.first_token_time is None:
+                s.first_token_time = now
+            reason = self._finish_step(s, tok, lps[i] if lps is not None else None)
+            if s.on_token is not None and (reason is None or reason == FinishReason.LENGTH):
+                s.on_token(s, tok)
+            if reason is not None:
+                self._finish(s, reason)
+                finished.append(s)
+        return finished
+
+    def _finish_step(self, s: Sequence, tok: int, lp) -> FinishReason | None:
+        """Shared finish rule: an EOS / stop token is not pushed to the output
+        (src/lib/mlxcel-core/src/engine/mod.rs:441-450)."""
+        p = s.params
+        n_out = len(s.output)
+        if not p.ignore_eos and n_out >= p.min_tokens:
+            if tok in self.cfg.eos_ids() or tok in p.stop_token_ids:
+                return FinishReason.STOP
+        s.output.append(tok)
+        if lp is not None and p.logprobs:
+            s.logprobs.append(float(lp))
+        if len(s.output) >= p.max_tokens:
+            return FinishReason.LENGTH
+        if s.total_len + 1 > self.ecfg.max_model_len:
+            return FinishReason.LENGTH
+        if p.loop_max_pattern > 0 and _tail_loop(s.output, p.loop_min_pattern, p.loop_max_pattern,
+                                                 p.loop_min_count):
+            return FinishReason.REPETITION_LOOP
+        return None
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams] | None = None
+                 ) -> list[Sequence]:
+        """Run the given prompts to completion (continuous batching) and return them in order."""
+        if not isinstance(params, list):
+            params = [params or SamplingParams()] * len(prompts)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while self.has_work():
+            self.step()
+        return [self.seqs[i] for i in ids]
+
+
+def _tail_loop(out: list[int], min_pat: int, max_pat: int, min_count: int) -> bool:
+    n = len(out)
+    for pat in range(max(1, min_pat), max_pat + 1):
+        if pat * min_count > n:
+            break
+        tail = out[n - pat:]
+        ok = True
+        for r in range(2, min_count + 1):
+            if out[n - r * pat: n - (r - 1) * pat] != tail:
+                ok = False
+                break
+        if ok:
+            return True
+    return False

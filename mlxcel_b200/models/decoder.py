@@ -1,0 +1,210 @@
+"""Decoder-only transformer executor over the kernel library.
+
+One class runs every supported family: the per-family differences (q/k norm, biases, sinks,
+sliding windows, Gemma norms, MoE routing, gated activation) are flags of
+:class:`mlxcel_b200.config.ModelConfig`. A forward pass takes a flat token batch that may mix
+decode rows (one token per sequence) and prefill chunks, vLLM-style, because on B200 a 64-row
+decode step and a 512-token prefill chunk fit in the same set of GEMM launches.
+
+Reference behaviour being matched: Llama-3 forward (src/models/llama3.rs:685-807,1112-1320),
+Qwen3 q/k norm (src/models/qwen3.rs:309-338), GPT-OSS attention sinks / clipped SwiGLU / top-k
+softmax routing (src/models/gpt_oss.rs:51-476), MoE switch layers
+(src/models/switch_layers.rs:98-220).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import ops
+from ..config import ModelConfig
+from ..ops import KVLayer
+from ..ops.reference import rope_inv_freq
+from .weights import LayerWeights, ModelWeights, QuantizedTensor
+
+
+@dataclass
+class StepBatch:
+    """Device-side description of one forward pass.
+
+    Token layout: the first ``num_decode`` rows are decode rows (sequence i ↔ row i); the rest
+    are prefill chunks laid back to back (``cu_q`` is relative to the start of that region)."""
+
+    token_ids: torch.Tensor          # [T] int32
+    positions: torch.Tensor          # [T] int32
+    slot_mapping: torch.Tensor       # [T] int32 (-1 = padding row, nothing appended)
+    num_decode: int = 0
+    dec_block_tables: torch.Tensor | None = None   # [Bd, max_blocks] int32
+    dec_context_lens: torch.Tensor | None = None   # [Bd] int32 (including the new token)
+    dec_max_len: int = 0
+    num_prefill_seqs: int = 0
+    pf_block_tables: torch.Tensor | None = None    # [Sp, max_blocks]
+    pf_cu_q: torch.Tensor | None = None            # [Sp+1] int32
+    pf_context_lens: torch.Tensor | None = None    # [Sp] int32 (prefix + chunk)
+    pf_max_q_len: int = 0
+    logits_rows: torch.Tensor | None = None        # [R] int64 rows of the hidden state to project
+    embeds: torch.Tensor | None = None             # optional [T, H] input embeddings (VLM / MTP)
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.token_ids.shape[0])
+
+
+class LocalComm:
+    """Single-GPU communication context (world size 1): every collective is the identity."""
+
+    tp_size = 1
+    tp_rank = 0
+    ep_size = 1
+    ep_rank = 0
+
+    def row_parallel_linear(self, x, w, bias, residual):
+        return ops.linear(x, w, bias=bias, residual=residual, out=residual)
+
+    def gather_logits(self, logits):
+        return logits
+
+    def embed(self, ids, table, scale, vocab_start=0):
+        return ops.embedding(ids, table, scale)
+
+    def all_reduce(self, x):
+        return x
+
+
+def _linear_any(x, w, bias=None, residual=None, out=None):
+    if isinstance(w, QuantizedTensor):
+        from ..ops import quant
+        return quant.qlinear(x, w, bias=bias, residual=residual, out=out)
+    return ops.linear(x, w, bias=bias, residual=residual, out=out)
+
+
+def _glu_any(x, w, inter, act, bias, alpha, limit):
+    if isinstance(w, QuantizedTensor):
+        from ..ops import quant
+        y = quant.qlinear(x, w, bias=bias)
+        return ops.swiglu(y, inter, act, alpha, limit)
+    return ops.glu_linear(x, w, inter, act, bias=bias, alpha=alpha, limit=limit)
+
+
+class DecoderModel:
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, comm=None, kv_bits: int = 16,
+                 layer_range: range | None = None, first_stage: bool = True,
+                 last_stage: bool = True):
+        self.cfg = cfg
+        self.w = weights
+        self.comm = comm or LocalComm()
+        self.kv_bits = kv_bits
+        self.layer_range = layer_range or range(cfg.num_hidden_layers)
+        self.first_stage, self.last_stage = first_stage, last_stage
+        tp = self.comm.tp_size
+        self.Hq = cfg.num_attention_heads // tp
+        self.Hkv = max(1, cfg.num_key_value_heads // tp)
+        self.D = cfg.head_dim
+        self.I = cfg.intermediate_size // tp
+        dev = weights.final_norm.device
+        inv, ms = rope_inv_freq(cfg.rot_dim, cfg.rope_theta, cfg.rope_scaling)
+        self.inv_freq = inv.to(dev)
+        self.mscale = ms
+        self.device = dev
+
+    # ------------------------------------------------------------------ blocks
+    def _attention(self, li: int, lw: LayerWeights, x: torch.Tensor, b: StepBatch,
+                   kv: KVLayer) -> torch.Tensor:
+        cfg = self.cfg
+        qkv = _linear_any(x, lw.wqkv, bias=lw.bqkv)
+        ops.rope_append(qkv, b.positions, b.slot_mapping, self.inv_freq, kv, Hq=self.Hq,
+                        Hkv=self.Hkv, D=self.D, rot_dim=cfg.rot_dim,
+                        traditional=cfg.rope_traditional, mscale=self.mscale,
+                        q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, norm_eps=cfg.rms_norm_eps)
+        T = qkv.shape[0]
+        attn = torch.empty(T, self.Hq * self.D, dtype=qkv.dtype, device=qkv.device)
+        window = cfg.layer_window(self.layer_range[li] if li < len(self.layer_range) else li)
+        q = qkv[:, : self.Hq * self.D]
+        nd = b.num_decode
+        common = dict(Hq=self.Hq, Hkv=self.Hkv, D=self.D, scale=cfg.attn_scale, window=window,
+                      sinks=lw.sinks, softcap=cfg.attn_logit_softcap)
+        if nd > 0:
+            o = ops.paged_decode(q[:nd], kv, b.dec_block_tables, b.dec_context_lens,
+                                 max_len=b.dec_max_len, out=attn[:nd] if attn.is_cuda else None,
+                                 **common)
+            if not attn.is_cuda:
+                attn[:nd] = o
+        if b.num_prefill_seqs > 0:
+            o = ops.paged_prefill(q[nd:], kv, b.pf_block_tables, b.pf_cu_q, b.pf_context_lens,
+                                  max_q_len=b.pf_max_q_len, out=attn[nd:] if attn.is_cuda else None,
+                                  **common)
+            if not attn.is_cuda:
+                attn[nd:] = o
+        return attn
+
+    def _mlp(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        return _glu_any(x, lw.w_gate_up, self.I, cfg.hidden_act, lw.b_gate_up, cfg.swiglu_alpha,
+                        cfg.swiglu_limit)
+
+    def _moe(self, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        from .moe import moe_forward
+        return moe_forward(self.cfg, lw, x, h, self.comm)
+
+    # ------------------------------------------------------------------ forward
+    def forward_hidden(self, b: StepBatch, kv_layers: list[KVLayer],
+                       hidden_in: torch.Tensor | None = None) -> torch.Tensor:
+        """Runs this stage's layers. Returns the residual stream [T, H] (before the final norm)."""
+        cfg, w = self.cfg, self.w
+        if hidden_in is not None:
+            h = hidden_in
+        elif b.embeds is not None:
+            h = b.embeds
+        else:
+            h = self.comm.embed(b.token_ids, w.embed, cfg.embed_scale)
+        eps, wb = cfg.rms_norm_eps, cfg.norm_weight_bias
+        res_mult = cfg.extra.get("residual_multiplier", 1.0)
+        for li, lw in enumerate(w.layers):
+            kv = kv_layers[li]
+            x = ops.rmsnorm(h, lw.ln1, eps, wb)
+            a = self._attention(li, lw, x, b, kv)
+            if cfg.post_norms or res_mult != 1.0:
+                o = self.comm.row_parallel_linear(a, lw.wo, lw.bo, None)
+                if cfg.post_norms:
+                    o = ops.rmsnorm(o, lw.post_attn_norm, eps, wb)
+                if res_mult != 1.0:
+                    o = (o.float() * res_mult).to(o.dtype)
+                x, h = ops.add_rmsnorm(o, h, lw.ln2, eps, wb)
+            else:
+                h = self.comm.row_parallel_linear(a, lw.wo, lw.bo, h)
+                x = ops.rmsnorm(h, lw.ln2, eps, wb)
+            if cfg.is_moe:
+                h = self._moe(lw, x, h)
+            else:
+                m = self._mlp(lw, x)
+                if cfg.post_norms or res_mult != 1.0:
+                    o = self.comm.row_parallel_linear(m, lw.w_down, lw.b_down, None)
+                    if cfg.post_norms:
+                        o = ops.rmsnorm(o, lw.post_mlp_norm, eps, wb)
+                    if res_mult != 1.0:
+                        o = (o.float() * res_mult).to(o.dtype)
+                    h = (h.float() + o.float()).to(h.dtype) if not h.is_cuda else h.add_(o)
+                else:
+                    h = self.comm.row_parallel_linear(m, lw.w_down, lw.b_down, h)
+        return h
+
+    def logits(self, h: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:
+        """Final norm + LM head on the selected rows → fp32-comparable logits [R, V]."""
+        cfg, w = self.cfg, self.w
+        if rows is not None:
+            h = h.index_select(0, rows)
+        x = ops.rmsnorm(h, w.final_norm, cfg.rms_norm_eps, cfg.norm_weight_bias)
+        lg = _linear_any(x, w.lm_head)
+        lg = self.comm.gather_logits(lg)
+        ls = cfg.extra.get("logits_scaling", 1.0)
+        if ls != 1.0:
+            lg = (lg.float() / ls).to(lg.dtype)
+        if cfg.final_logit_softcap > 0:
+            c = cfg.final_logit_softcap
+            lg = (torch.tanh(lg.float() / c) * c).to(lg.dtype)
+        return lg
+
+    def forward(self, b: StepBatch, kv_layers: list[KVLayer]) -> torch.Tensor:
+        h = self.forward_hidden(b, kv_layers)
+        return self.logits(h, b.logits_rows)

@@ -1,0 +1,152 @@
+"""ctypes binding of ``lib/libmlxcel_b200.so`` (the sm_100a kernel library).
+
+The library is the only GPU code path: when a CUDA device is present and the library cannot
+be loaded, every op raises instead of falling back to PyTorch, so a missing build can not
+pass silently.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LIB_ERR: str | None = None
+_PKG = Path(__file__).resolve().parent.parent
+
+
+def lib_path() -> Path:
+    return _PKG / "lib" / "libmlxcel_b200.so"
+
+
+def load(required: bool = True):
+    """Return the loaded kernel library (building it when sources are newer and nvcc exists)."""
+    global _LIB, _LIB_ERR
+    if _LIB is not None:
+        return _LIB
+    path = lib_path()
+    if not path.exists() or os.environ.get("MLXCEL_B200_REBUILD") == "1":
+        try:
+            from .. import _build
+
+            _build.build_cuda()
+        except Exception as e:  # pragma: no cover - build environment specific
+            _LIB_ERR = f"build failed: {e}"
+    if path.exists():
+        try:
+            _LIB = ctypes.CDLL(str(path))
+            _declare(_LIB)
+            return _LIB
+        except OSError as e:
+            _LIB_ERR = str(e)
+    if required:
+        raise RuntimeError(
+            f"mlxcel_b200 CUDA kernel library is not available ({_LIB_ERR or 'not built'}); "
+            "run `python -c 'import __graft_entry__ as g; g.build()'`")
+    return None
+
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_ll = ctypes.c_longlong
+_f = ctypes.c_float
+
+
+def _declare(lib) -> None:
+    sig = {
+        "mx_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f,
+                         _vp, _ll, _i, _i, _vp],
+        "mx_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
+        "mx_head_rmsnorm": [_vp, _vp, _i, _i, _i, _ll, _f, _vp],
+        "mx_rope_append": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i,
+                           _i, _i, _i, _f, _i, _vp],
+        "mx_paged_decode": [_vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                            _i, _i, _i, _f, _f, _i, _i, _vp],
+        "mx_paged_prefill": [_vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                             _i, _i, _i, _i, _i, _f, _f, _i, _vp],
+        "mx_embedding": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
+        "mx_argmax": [_vp, _i, _ll, _vp, _i, _i, _vp],
+        "mx_sample": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+        "mx_apply_penalties": [_vp, _i, _ll, _vp, _i, _vp, _vp, _vp, _i, _i, _vp],
+        "mx_spec_verify": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+        "mx_swiglu": [_vp, _vp, _i, _i, _i, _f, _f, _vp],
+        "mx_read_status": [_vp, _i],
+        "mx_qmm_affine": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _ll, _vp],
+        "mx_dequantize": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
+        "mx_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+        "mx_moe_align": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+        "mx_moe_gather_rows": [_vp, _vp, _vp, _i, _i, _vp],
+        "mx_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+        "mx_grouped_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _ll,
+                                 _vp],
+    }
+    for name, args in sig.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue
+        fn.argtypes = args
+        fn.restype = _i
+    for name in ("mx_gemm_workspace_bytes",):
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.restype = _ll
+            fn.argtypes = []
+    fn = getattr(lib, "mx_paged_decode_scratch_floats", None)
+    if fn is not None:
+        fn.restype = _ll
+        fn.argtypes = [_i, _i, _i, _i]
+    fn = getattr(lib, "mx_build_info", None)
+    if fn is not None:
+        fn.restype = ctypes.c_char_p
+        fn.argtypes = []
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def check(rc: int, name: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{name} failed with code {rc}")
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+# ----------------------------------------------------------------------------- workspaces
+_WS: dict[int, torch.Tensor] = {}
+_LAUNCHES = 0
+
+
+def workspace(device: torch.device) -> torch.Tensor:
+    """Per-device scratch buffer (status word, tile counters, split-K partials), zeroed once."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _WS.get(idx)
+    if ws is None:
+        nbytes = int(load().mx_gemm_workspace_bytes())
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=torch.device("cuda", idx))
+        _WS[idx] = ws
+    return ws
+
+
+def count_launch(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+def launches() -> int:
+    """Number of kernel launches issued through this library since import."""
+    return _LAUNCHES
+
+
+def read_status(device: torch.device, clear: bool = True) -> int:
+    """Device status word of the workspace (0 = no kernel reported a bounded-wait failure)."""
+    ws = workspace(device)
+    return int(load().mx_read_status(ws.data_ptr(), 1 if clear else 0))
