@@ -103,7 +103,8 @@ class Engine:
         self._graphs: dict[tuple, tuple] = {}
         self._alloc_buffers()
         self.stats = dict(steps=0, decode_steps=0, prefill_tokens=0, decode_tokens=0, preemptions=0,
-                          graph_replays=0, prefix_hit_tokens=0)
+                          graph_replays=0, prefix_hit_tokens=0, h2d_bytes=0, d2h_bytes=0,
+                          graph_kernel_launches=0)
 
     # ------------------------------------------------------------------ setup
     def _auto_num_blocks(self, tp: int, nl: int) -> int:
@@ -346,6 +347,9 @@ class Engine:
             self.d_pf_lens[:sp].copy_(self.h_pf_lens[:sp], non_blocking=nb)
             self.d_cu[: sp + 1].copy_(self.h_cu[: sp + 1], non_blocking=nb)
         self.d_rows[:R].copy_(self.h_rows[:R], non_blocking=nb)
+        mb4 = self.max_blocks_per_seq * 4 + 4
+        self.stats["h2d_bytes"] += 12 * t + nd * mb4 + sp * mb4 + (sp + 1) * 4 + R * 8
+        self.stats["d2h_bytes"] += R * 4
         b = StepBatch(token_ids=self.d_tokens[:t], positions=self.d_pos[:t],
                       slot_mapping=self.d_slots[:t], num_decode=nd,
                       dec_block_tables=self.d_dec_tables[:nd] if nd else None,
@@ -391,13 +395,16 @@ class Engine:
             with torch.cuda.stream(s):
                 fwd()
             torch.cuda.current_stream().wait_stream(s)
+            from ..ops import _lib
+            n0 = _lib.launches()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 logits = fwd()
-            ent = (g, logits, splits)
+            ent = (g, logits, _lib.launches() - n0)
             self._graphs[key] = ent
         ent[0].replay()
         self.stats["graph_replays"] += 1
+        self.stats["graph_kernel_launches"] += ent[2]
         return ent[1]
 
     # ------------------------------------------------------------------ step

@@ -1,0 +1,65 @@
+"""Public in-process API: :class:`LLM` wraps weights + executor + engine.
+
+``LLM.generate`` is the call a user makes (the in-process analogue of the reference's
+``mlxcel.LLM(model).generate(...)`` Python client, python/src/mlxcel/_client.py, and of its
+``DirectEngine``, src/lib/mlxcel-core/src/engine/direct.rs:192-655).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from .config import ModelConfig, preset
+from .engine import Engine, EngineConfig, SamplingParams, Sequence
+from .models.decoder import DecoderModel
+from .models.weights import ModelWeights, random_weights
+
+
+class LLM:
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, engine_config: EngineConfig | None = None,
+                 comm=None, tokenizer=None):
+        self.cfg = cfg
+        self.model = DecoderModel(cfg, weights, comm=comm,
+                                  kv_bits=(engine_config.kv_bits if engine_config else 16))
+        self.engine = Engine(self.model, cfg, engine_config)
+        self.tokenizer = tokenizer
+
+    # ------------------------------------------------------------------ constructors
+    @staticmethod
+    def from_preset(name: str, *, device="cuda", seed: int = 0, engine_config: EngineConfig | None = None,
+                    comm=None, dtype=torch.bfloat16) -> "LLM":
+        cfg = preset(name)
+        tp = comm.tp_size if comm is not None else 1
+        rank = comm.tp_rank if comm is not None else 0
+        w = random_weights(cfg, seed=seed, dtype=dtype, device=device, tp_rank=rank, tp_size=tp,
+                           ep_rank=getattr(comm, "ep_rank", 0), ep_size=getattr(comm, "ep_size", 1))
+        return LLM(cfg, w, engine_config, comm=comm)
+
+    @staticmethod
+    def from_pretrained(path: str | Path, *, device="cuda", engine_config: EngineConfig | None = None,
+                        comm=None, dequantize: bool = False) -> "LLM":
+        from .loading.checkpoint import load_model_weights
+        from .tokenizer import load_tokenizer
+
+        cfg = ModelConfig.from_path(path)
+        w = load_model_weights(path, cfg, device=device, comm=comm, dequantize=dequantize)
+        tok = load_tokenizer(path)
+        return LLM(cfg, w, engine_config, comm=comm, tokenizer=tok)
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts=None, sampling_params: SamplingParams | list[SamplingParams] | None = None,
+                 prompt_token_ids: list[list[int]] | None = None) -> list[Sequence]:
+        if prompt_token_ids is None:
+            if self.tokenizer is None:
+                raise ValueError("text prompts need a tokenizer; pass prompt_token_ids")
+            if isinstance(prompts, str):
+                prompts = [prompts]
+            prompt_token_ids = [self.tokenizer.encode(p) for p in prompts]
+        outs = self.engine.generate(prompt_token_ids, sampling_params)
+        for s in outs:
+            self.engine.release(s.seq_id)
+        return outs
+
+    def decode(self, token_ids: list[int]) -> str:
+        return self.tokenizer.decode(token_ids) if self.tokenizer else " ".join(map(str, token_ids))

@@ -1,0 +1,318 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+
+from mlxcel_b200 import ops
+from mlxcel_b200.ops import KVLayer, reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _bf(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device=DEV) * scale).to(torch.bfloat16)
+
+
+def _close(got, want, rtol=2e-2, atol=2e-2):
+    got, want = got.float(), want.float()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{bad}/{err.numel()} mismatches, max err {err.max().item():.4g}, ref max {want.abs().max().item():.4g}"
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    torch.cuda.synchronize()
+    from mlxcel_b200.ops import _lib
+    assert _lib.read_status(torch.device(DEV)) == 0
+
+
+# ----------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("M,N,K", [
+    (1, 128, 64), (16, 256, 128), (17, 384, 512), (64, 4096, 4096), (64, 1024, 1096),
+    (128, 6144, 4096), (200, 512, 256), (256, 1000, 512), (257, 512, 512), (300, 768, 1024),
+    (1024, 4096, 4096), (1000, 1032, 520), (4096, 256, 8192),
+])
+def test_gemm_plain(M, N, K):
+    x, w = _bf(M, K, seed=1), _bf(N, K, scale=0.05, seed=2)
+    got = ops.linear(x, w)
+    _close(got, ref.linear(x, w), atol=2e-2 * math.sqrt(K) * 0.05)
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("M", [48, 130])
+def test_gemm_forced_modes(mode, M):
+    x, w = _bf(M, 512, seed=3), _bf(640, 512, scale=0.05, seed=4)
+    got = ops.linear(x, w, force_mode=mode)
+    _close(got, ref.linear(x, w))
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4, 7])
+def test_gemm_split_k_deterministic(splits):
+    x, w = _bf(32, 4096, seed=5), _bf(512, 4096, scale=0.05, seed=6)
+    a = ops.linear(x, w, force_mode=2, force_splits=splits)
+    b = ops.linear(x, w, force_mode=2, force_splits=splits)
+    _close(a, ref.linear(x, w), atol=5e-2)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("M", [8, 64, 512])
+def test_gemm_bias_residual_fp32(M):
+    x, w = _bf(M, 1024, seed=7), _bf(768, 1024, scale=0.05, seed=8)
+    bias, res = _bf(768, seed=9), _bf(M, 768, seed=10)
+    _close(ops.linear(x, w, bias=bias), ref.linear(x, w, bias))
+    _close(ops.linear(x, w, bias=bias, residual=res), ref.linear(x, w, bias, res))
+    _close(ops.linear(x, w, out_fp32=True), ref.linear(x, w, out_dtype=torch.float32))
+    # in-place residual accumulate
+    h = res.clone()
+    ops.linear(x, w, residual=h, out=h)
+    _close(h, ref.linear(x, w, None, res))
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh", "clipped_swiglu"])
+@pytest.mark.parametrize("M", [4, 64, 128, 700])
+def test_gemm_glu(act, M):
+    I, K = 896, 512
+    x, w = _bf(M, K, seed=11), _bf(2 * I, K, scale=0.08, seed=12)
+    bias = _bf(2 * I, scale=0.1, seed=13) if act == "clipped_swiglu" else None
+    got = ops.glu_linear(x, w, I, act, bias=bias)
+    want = ref.glu_linear(x, w, I, ops._ACT_TO_EPI[act], bias)
+    _close(got, want)
+
+
+# ----------------------------------------------------------------------------- norms
+@pytest.mark.parametrize("rows,dim", [(1, 256), (64, 4096), (33, 5120), (7, 2880), (3, 16384)])
+def test_add_rmsnorm(rows, dim):
+    x, r, w = _bf(rows, dim, seed=1), _bf(rows, dim, seed=2), _bf(dim, seed=3)
+    y, h = ops.add_rmsnorm(x, r, w, 1e-5)
+    yr, hr = ref.add_rmsnorm(x, r, w, 1e-5)
+    assert torch.equal(h, hr)
+    _close(y, yr, rtol=1e-2, atol=1e-2)
+    y2 = ops.rmsnorm(x, w, 1e-6, 1.0)
+    _close(y2, ref.add_rmsnorm(x, None, w, 1e-6, 1.0)[0], rtol=1e-2, atol=1e-2)
+
+
+# ----------------------------------------------------------------------------- rope + append
+def _pool(nb, Hkv, bs, D, bits):
+    if bits == 16:
+        return KVLayer(torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device=DEV),
+                       torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device=DEV), None, None, bs, 16)
+    return KVLayer(torch.zeros(nb, Hkv, bs, D, dtype=torch.uint8, device=DEV),
+                   torch.zeros(nb, Hkv, bs, D, dtype=torch.uint8, device=DEV),
+                   torch.zeros(nb, Hkv, bs, D // 64, 2, dtype=torch.bfloat16, device=DEV),
+                   torch.zeros(nb, Hkv, bs, D // 64, 2, dtype=torch.bfloat16, device=DEV), bs, 8)
+
+
+def _clone_pool(kv):
+    c = lambda t: None if t is None else t.clone()  # noqa: E731
+    return KVLayer(c(kv.k), c(kv.v), c(kv.k_meta), c(kv.v_meta), kv.block_size, kv.kv_bits)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,rot,trad,qk", [
+    (8, 2, 128, 128, False, False), (4, 4, 64, 64, True, False), (8, 1, 128, 64, False, True),
+    (16, 2, 64, 64, False, True),
+])
+@pytest.mark.parametrize("bits", [16, 8])
+def test_rope_append(Hq, Hkv, D, rot, trad, qk, bits):
+    T, bs, nb = 37, 16, 12
+    qkv = _bf(T, (Hq + 2 * Hkv) * D, seed=4)
+    pos = torch.randint(0, 5000, (T,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(nb * bs, device=DEV)[:T].to(torch.int32)
+    slots[5] = -1
+    inv, ms = ref.rope_inv_freq(rot, 500000.0, dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                                                    high_freq_factor=4.0,
+                                                    original_max_position_embeddings=8192))
+    inv = inv.to(DEV)
+    qn = _bf(D, seed=5) if qk else None
+    kn = _bf(D, seed=6) if qk else None
+    kv = _pool(nb, Hkv, bs, D, bits)
+    kv_ref = _clone_pool(kv)
+    q_ref = qkv.clone()
+    ops.rope_append(qkv, pos, slots, inv, kv, Hq=Hq, Hkv=Hkv, D=D, rot_dim=rot, traditional=trad,
+                    mscale=1.1, q_norm_w=qn, k_norm_w=kn, norm_eps=1e-6)
+    ref.rope_append(q_ref, pos, slots, inv, kv_ref, Hq=Hq, Hkv=Hkv, D=D, rot_dim=rot, traditional=trad,
+                    mscale=1.1, q_norm_w=qn, k_norm_w=kn, norm_eps=1e-6)
+    _close(qkv[:, : Hq * D], q_ref[:, : Hq * D], rtol=2e-2, atol=3e-2)
+    if bits == 16:
+        _close(kv.k, kv_ref.k, rtol=2e-2, atol=3e-2)
+        assert torch.equal(kv.v, kv_ref.v)
+    else:
+        _close(ref.dequantize_kv8(kv.k, kv.k_meta), ref.dequantize_kv8(kv_ref.k, kv_ref.k_meta),
+               rtol=3e-2, atol=6e-2)
+        _close(ref.dequantize_kv8(kv.v, kv.v_meta), ref.dequantize_kv8(kv_ref.v, kv_ref.v_meta),
+               rtol=3e-2, atol=6e-2)
+
+
+# ----------------------------------------------------------------------------- attention
+def _fill_pool(kv, seed):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    if kv.kv_bits == 16:
+        kv.k.copy_(torch.randn(kv.k.shape, generator=g, device=DEV))
+        kv.v.copy_(torch.randn(kv.v.shape, generator=g, device=DEV))
+    else:
+        for t, m in ((kv.k, kv.k_meta), (kv.v, kv.v_meta)):
+            q, meta = ref.quantize_kv8(torch.randn(t.shape, generator=g, device=DEV))
+            t.copy_(q)
+            m.copy_(meta)
+
+
+def _tables(lens, bs, nb, width):
+    B = len(lens)
+    perm = torch.randperm(nb)
+    tab = torch.zeros(B, width, dtype=torch.int32)
+    o = 0
+    for i, n in enumerate(lens):
+        k = (n + bs - 1) // bs
+        tab[i, :k] = perm[o:o + k].to(torch.int32)
+        o += k
+    return tab.to(DEV)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (8, 8, 64), (8, 1, 128), (16, 2, 64)])
+@pytest.mark.parametrize("bits,window,sinks,splits", [
+    (16, 0, False, 1), (16, 0, False, 4), (16, 48, True, 3), (8, 0, False, 2), (8, 100, True, 1)])
+def test_paged_decode(Hq, Hkv, D, bits, window, sinks, splits):
+    bs, nb = 16, 256
+    lens = [1, 15, 16, 17, 130, 513, 700, 64]
+    B = len(lens)
+    kv = _pool(nb, Hkv, bs, D, bits)
+    _fill_pool(kv, 3)
+    tab = _tables(lens, bs, nb, 48)
+    cl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    qkv = _bf(B, (Hq + 2 * Hkv) * D, seed=9)
+    q = qkv[:, : Hq * D]
+    sk = torch.randn(Hq, device=DEV) if sinks else None
+    scale = 1.0 / math.sqrt(D)
+    got = ops.paged_decode(q, kv, tab, cl, Hq=Hq, Hkv=Hkv, D=D, scale=scale, window=window,
+                           sinks=sk, num_splits=splits)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    want = ref.paged_attention(q, kv, tab, cl, cu, Hq=Hq, Hkv=Hkv, D=D, scale=scale, window=window,
+                               sinks=sk)
+    _close(got, want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 4, 64), (8, 1, 128), (16, 2, 64)])
+@pytest.mark.parametrize("bits,window,sinks", [(16, 0, False), (16, 40, True), (8, 0, False)])
+def test_paged_prefill(Hq, Hkv, D, bits, window, sinks):
+    bs, nb = 16, 256
+    ctx = [70, 300, 33, 129]       # total visible tokens per sequence
+    qlen = [70, 45, 1, 129]        # the last qlen of them are queries
+    S = len(ctx)
+    kv = _pool(nb, Hkv, bs, D, bits)
+    _fill_pool(kv, 5)
+    tab = _tables(ctx, bs, nb, 24)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0] + list(torch.tensor(qlen).cumsum(0)), dtype=torch.int32, device=DEV)
+    T = sum(qlen)
+    qkv = _bf(T, (Hq + 2 * Hkv) * D, seed=10)
+    q = qkv[:, : Hq * D]
+    sk = torch.randn(Hq, device=DEV) if sinks else None
+    scale = 1.0 / math.sqrt(D)
+    got = ops.paged_prefill(q, kv, tab, cu, cl, Hq=Hq, Hkv=Hkv, D=D, scale=scale, max_q_len=max(qlen),
+                            window=window, sinks=sk)
+    want = ref.paged_attention(q, kv, tab, cl, cu, Hq=Hq, Hkv=Hkv, D=D, scale=scale, window=window,
+                               sinks=sk)
+    _close(got, want, rtol=2e-2, atol=2e-2)
+
+
+# ----------------------------------------------------------------------------- misc + sampling
+def test_embedding_argmax():
+    table = _bf(1000, 256, seed=1)
+    ids = torch.tensor([0, 999, 5, -1, 1000, 17], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops.embedding(ids, table), ref.embedding(ids, table))
+    _close(ops.embedding(ids, table, 16.0), ref.embedding(ids, table, 16.0), rtol=1e-2, atol=1e-2)
+    for V in (1000, 128256, 201088 + 3):
+        lg = _bf(5, V, seed=V)
+        lg[2, V - 1] = 100.0
+        lg[3, 0] = float("nan")
+        assert torch.equal(ops.argmax(lg), ref.argmax(lg))
+        lf = lg.float()
+        assert torch.equal(ops.argmax(lf), ref.argmax(lf))
+
+
+def test_sample_matches_reference_stream():
+    B, V = 6, 5000
+    lg = (torch.randn(B, V, device=DEV) * 3).float()
+    temp = torch.tensor([0.0, 1.0, 0.7, 1.3, 1.0, 0.5], device=DEV)
+    tk = torch.tensor([0, 0, 40, 0, 1, 5], dtype=torch.int32, device=DEV)
+    tp = torch.tensor([1.0, 1.0, 1.0, 0.9, 1.0, 0.8], device=DEV)
+    mp = torch.tensor([0.0, 0.0, 0.0, 0.05, 0.0, 0.0], device=DEV)
+    seeds = torch.tensor([1, 2, 3, 4, 5, 6], dtype=torch.int64, device=DEV)
+    for step in (0, 1, 77):
+        steps = torch.full((B,), step, dtype=torch.int64, device=DEV)
+        got, lp = ops.sample(lg, temp, tk, tp, mp, seeds, steps)
+        want, lpr = ref.sample(lg, temp, tk, tp, mp, seeds, steps)
+        assert got.tolist() == want.tolist()
+        _close(lp, lpr, rtol=1e-3, atol=1e-3)
+
+
+def test_sample_distribution_chi_square():
+    V, N = 16, 4000
+    probs = torch.softmax(torch.randn(V), 0)
+    lg = torch.log(probs).to(DEV)[None].repeat(N, 1).contiguous()
+    ones = torch.ones(N, device=DEV)
+    got, _ = ops.sample(lg, ones, torch.zeros(N, dtype=torch.int32, device=DEV), ones,
+                        torch.zeros(N, device=DEV), torch.arange(N, dtype=torch.int64, device=DEV),
+                        torch.zeros(N, dtype=torch.int64, device=DEV))
+    counts = torch.bincount(got.cpu().long(), minlength=V).float()
+    chi2 = ((counts - N * probs) ** 2 / (N * probs)).sum().item()
+    assert chi2 < 45.0, chi2  # 15 dof: P(chi2 > 45) < 1e-4
+
+
+def test_penalties_and_verify():
+    B, V = 3, 300
+    lg = torch.randn(B, V, device=DEV)
+    hist = torch.tensor([[1, 2, 2, -1], [5, 5, 5, 5], [-1, -1, -1, -1]], dtype=torch.int32, device=DEV)
+    rep = torch.tensor([1.3, 1.0, 1.2], device=DEV)
+    fr = torch.tensor([0.0, 0.5, 0.0], device=DEV)
+    pr = torch.tensor([0.2, 0.0, 0.0], device=DEV)
+    want = ref.apply_penalties(lg, hist, rep, fr, pr)
+    got = ops.apply_penalties(lg.clone(), hist, rep, fr, pr)
+    _close(got, want, rtol=1e-5, atol=1e-5)
+    K = 4
+    logits = torch.randn(B, K, V, device=DEV)
+    tgt = logits.argmax(-1).to(torch.int32)
+    draft = tgt[:, : K - 1].clone()
+    draft[1, 1] = (draft[1, 1] + 1) % V
+    draft[2, 0] = (draft[2, 0] + 1) % V
+    t, a, n = ops.spec_verify(logits, draft)
+    assert torch.equal(t, tgt) and a.tolist() == [3, 1, 0]
+    assert n.tolist() == [int(tgt[0, 3]), int(tgt[1, 1]), int(tgt[2, 0])]
+
+
+# ----------------------------------------------------------------------------- end to end
+def test_tiny_llama_gpu_matches_cpu_reference():
+    """bf16 CUDA executor vs the fp32 CPU executor: greedy tokens on a tiny model agree while the
+    top-2 logit margin is not a near tie."""
+    from mlxcel_b200.config import preset
+    from mlxcel_b200.engine import Engine, EngineConfig, SamplingParams
+    from mlxcel_b200.models.decoder import DecoderModel
+    from mlxcel_b200.models.weights import random_weights
+    import copy
+
+    cfg = preset("tiny-llama")
+    w32 = random_weights(cfg, seed=3, dtype=torch.float32, std=0.05)
+    w16 = copy.deepcopy(w32)
+    for lw in [w16, *w16.layers]:
+        for k, v in vars(lw).items():
+            if isinstance(v, torch.Tensor):
+                setattr(lw, k, v.to(torch.bfloat16).to(DEV) if v.dtype == torch.float32 and k != "sinks" else v.to(DEV))
+    w16.lm_head = w16.embed
+    ec = dict(max_batch=4, max_num_batched_tokens=256, num_blocks=64, max_model_len=256)
+    cpu = Engine(DecoderModel(cfg, w32), cfg, EngineConfig(cuda_graphs=False, **ec))
+    gpu = Engine(DecoderModel(cfg, w16), cfg, EngineConfig(cuda_graphs=True, **ec))
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (20, 7, 33)]
+    sp = SamplingParams(max_tokens=12, ignore_eos=True)
+    a = [s.output for s in cpu.generate(prompts, sp)]
+    b = [s.output for s in gpu.generate(prompts, sp)]
+    agree = sum(x == y for sa, sb in zip(a, b) for x, y in zip(sa, sb))
+    total = sum(len(s) for s in a)
+    # a bf16 executor may flip a near tie and then diverge; require the first tokens and most to agree
+    assert all(sa[0] == sb[0] for sa, sb in zip(a, b))
+    assert agree >= 0.6 * total, (a, b)
