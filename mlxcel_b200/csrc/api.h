@@ -39,6 +39,18 @@ int mx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, cons
                  int out_fp32, int glu_offset, float glu_alpha, float glu_limit, void* workspace,
                  long long ws_bytes, int force_mode, int force_splits, void* stream);
 
+// Fused GEMM + collective over a symmetric heap of peer-mapped memory (tensor parallelism).
+// mode 1: one-shot all-reduce (M <= 256): out = residual + bias + sum over ranks of x_r @ w_r^T.
+// mode 2: two-shot all-reduce (any M): tile owners reduce and store into every out_peer.
+// mode 3: all-gather of output columns (M <= 256): out_peer[r][t, rank * N + n].
+// flags_peer / recv_peer / out_peer: host arrays of `world` device addresses of the same heap
+// offset on each rank; ctl (16 words) / expect (8200 words): this rank's channel words (zeroed).
+int mx_gemm_comm(const void* x, const void* w, void* out, const void* bias, const void* residual,
+                 int M, int N, int K, int ldx, int ldw, int ldo, int ldr, int mode, int rank,
+                 int world, const void* const* flags_peer, const void* const* recv_peer,
+                 const void* const* out_peer, void* ctl, void* expect, long long parity_stride,
+                 long long rank_stride, void* workspace, long long ws_bytes, void* stream);
+
 // Bytes of workspace the no-scratch-allocation path needs at most for mx_gemm_bf16.
 long long mx_gemm_workspace_bytes(void);
 

@@ -605,6 +605,347 @@ paged_prefill_kernel(const PrefillParams p) {
   }
 }
 
+// ============================================================================= decode (tensor core)
+// Flash-decoding with GQA packing: the G query heads of one kv head form the rows of a 16-row
+// MMA tile, so K and V are read once per kv head and the score / value products run on tensor
+// cores (mma.sync m16n8k16; the kernel is bound by the KV stream, not by math).
+// A CTA owns (sequence, kv head, KV split). Its 4 warps are independent streams: warp w takes
+// the 16-key groups w, w+4, ... of the split, each through its own 3-stage cp.async ring in
+// shared memory (no CTA-wide barrier inside the loop), keeps its own online-softmax state and
+// the warps merge once at the end.
+constexpr int kDmWarps = 4;
+constexpr int kDmThreads = kDmWarps * 32;
+constexpr int kDmStages = 3;
+constexpr int kDmKeys = 16;  // keys per group (one MMA k-step of P V)
+
+template <int D, int KV_BITS, bool BS16>
+__global__ void __launch_bounds__(kDmThreads)
+paged_decode_mma_kernel(const DecodeParams p, const int G) {
+  constexpr int CH = D / 8;
+  constexpr int TILE_BYTES = kDmKeys * D * 2;            // one K (or V) group in bf16
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;            // K + V
+  constexpr int WARP_BYTES = kDmStages * STAGE_BYTES;
+  extern __shared__ __align__(128) uint8_t dm_smem[];
+  uint8_t* q_sm = dm_smem;                               // [16][D] bf16 (swizzled)
+  uint8_t* kv_sm = dm_smem + 16 * D * 2;                 // 4 warps x stages x (K, V)
+  __shared__ float m_s[kDmWarps][16], l_s[kDmWarps][16];
+  __shared__ int last_s;
+
+  const int split = blockIdx.x % p.num_splits;
+  const int bh = blockIdx.x / p.num_splits;
+  const int h = bh % p.Hkv, b = bh / p.Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int len = p.context_lens[b];
+  int begin = 0;
+  if (p.window > 0 && len > p.window) begin = len - p.window;
+  const int g_begin = begin / kDmKeys;                          // first key group
+  const int g_end = (len + kDmKeys - 1) / kDmKeys;              // one past the last key group
+  const int n_groups = max(0, g_end - g_begin);
+  int per = (n_groups + p.num_splits - 1) / p.num_splits;
+  per = ((per + kDmWarps - 1) / kDmWarps) * kDmWarps;
+  const int s_begin = g_begin + split * per;
+  const int s_end = min(g_end, s_begin + per);
+  const int* table = p.block_tables + static_cast<size_t>(b) * p.max_blocks;
+
+  // ---- Q tile (rows >= G are zero)
+  for (int i = threadIdx.x; i < 16 * CH; i += kDmThreads) {
+    const int r = i / CH, c = i - r * CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G)
+      v = *reinterpret_cast<const uint4*>(p.q + static_cast<size_t>(b) * p.q_stride +
+                                          static_cast<size_t>(h * G + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_sm + swz<D>(r, c)) = v;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int chunk = kk * 2 + (lane >> 4);
+    ldmatrix_x4(qf[kk], smem_u32(q_sm) + swz<D>(row, chunk));
+  }
+
+  uint8_t* my_sm = kv_sm + warp * WARP_BYTES;
+  // Per-lane constants of the load pattern: chunk i = lane + 32 * it covers row i / CH,
+  // 16-byte column i % CH of the 16 x D tile.
+  auto load_group = [&](int grp, int stage, int blk16) {
+    // grp: key group index (16 keys); blk16: pool block of the group when block_size == 16.
+    uint8_t* ks = my_sm + stage * STAGE_BYTES;
+    uint8_t* vs = ks + TILE_BYTES;
+    if (grp < s_end) {
+      const size_t row16 = (static_cast<size_t>(blk16) * p.Hkv + h) * kDmKeys;
+      const int rows_ok = len - grp * kDmKeys;  // rows below this index hold real keys
+#pragma unroll
+      for (int it = 0; it < (kDmKeys * CH) / 32; ++it) {
+        const int i = lane + it * 32;
+        const int r = i / CH, c = i - r * CH;
+        const bool ok = r < rows_ok;
+        size_t row;
+        if (BS16) {
+          row = row16 + r;
+        } else {
+          const int key = grp * kDmKeys + r;
+          const int blk = ok ? table[key / p.block_size] : 0;
+          row = (static_cast<size_t>(blk) * p.Hkv + h) * p.block_size + (ok ? key % p.block_size : 0);
+        }
+        if (KV_BITS == 16) {
+          cp_async16(smem_u32(ks) + swz<D>(r, c),
+                     static_cast<const __nv_bfloat16*>(p.k_pool) + row * D + c * 8, ok);
+          cp_async16(smem_u32(vs) + swz<D>(r, c),
+                     static_cast<const __nv_bfloat16*>(p.v_pool) + row * D + c * 8, ok);
+        } else {
+          uint4 ko = make_uint4(0, 0, 0, 0), vo = make_uint4(0, 0, 0, 0);
+          if (ok) {
+            float kf[8], vf[8];
+            load8<8>(p.k_pool, row * D + c * 8, kf);
+            load8<8>(p.v_pool, row * D + c * 8, vf);
+            const int gq = (c * 8) / 64;
+            const __nv_bfloat16* km = p.k_meta + row * (D / 64) * 2 + gq * 2;
+            const __nv_bfloat16* vm = p.v_meta + row * (D / 64) * 2 + gq * 2;
+            const float ksc = __bfloat162float(km[0]), kbi = __bfloat162float(km[1]);
+            const float vsc = __bfloat162float(vm[0]), vbi = __bfloat162float(vm[1]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              kf[j] = kf[j] * ksc + kbi;
+              vf[j] = vf[j] * vsc + vbi;
+            }
+            ko = make_uint4(pack_bf16(kf[0], kf[1]), pack_bf16(kf[2], kf[3]), pack_bf16(kf[4], kf[5]),
+                            pack_bf16(kf[6], kf[7]));
+            vo = make_uint4(pack_bf16(vf[0], vf[1]), pack_bf16(vf[2], vf[3]), pack_bf16(vf[4], vf[5]),
+                            pack_bf16(vf[6], vf[7]));
+          }
+          *reinterpret_cast<uint4*>(ks + swz<D>(r, c)) = ko;
+          *reinterpret_cast<uint4*>(vs + swz<D>(r, c)) = vo;
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  // Block-table entries are fetched one ring slot ahead of the loads that need them.
+  auto table_at = [&](int grp) -> int { return (BS16 && grp < s_end) ? table[grp] : 0; };
+
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+
+  const int first = s_begin + warp;
+#pragma unroll
+  for (int s = 0; s < kDmStages - 1; ++s)
+    load_group(first + s * kDmWarps, s, table_at(first + s * kDmWarps));
+  int blk_next = table_at(first + (kDmStages - 1) * kDmWarps);
+
+  int stage = 0;
+  for (int grp = first; grp < s_end; grp += kDmWarps) {
+    {
+      int ls = stage + kDmStages - 1;
+      if (ls >= kDmStages) ls -= kDmStages;
+      load_group(grp + (kDmStages - 1) * kDmWarps, ls, blk_next);
+      blk_next = table_at(grp + kDmStages * kDmWarps);
+    }
+    cp_async_wait<kDmStages - 1>();
+    __syncwarp();
+    const uint32_t ks = smem_u32(my_sm + stage * STAGE_BYTES);
+    const uint32_t vs = ks + TILE_BYTES;
+    float sacc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t bfr[4];
+      const int row = (lane & 7) + (lane >> 4) * 8;
+      const int chunk = kk * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(bfr, ks + swz<D>(row, chunk));
+      mma_bf16_16816(sacc[0], qf[kk], bfr[0], bfr[1]);
+      mma_bf16_16816(sacc[1], qf[kk], bfr[2], bfr[3]);
+    }
+    const int key0 = grp * kDmKeys;
+    float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+        float v = sacc[nt][e] * p.scale_log2;
+        if (p.softcap > 0.f) v = p.softcap * tanhf(v / (kLog2e * p.softcap)) * kLog2e;
+        v = (key >= begin && key < len) ? v : -INFINITY;
+        sacc[nt][e] = v;
+        if (e < 2) tmax_lo = fmaxf(tmax_lo, v);
+        else tmax_hi = fmaxf(tmax_hi, v);
+      }
+    }
+    tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 1));
+    tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 2));
+    tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 1));
+    tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
+    const float mn_lo = fmaxf(m_lo, tmax_lo), mn_hi = fmaxf(m_hi, tmax_hi);
+    const float sc_lo = (m_lo > -INFINITY) ? exp2f(m_lo - mn_lo) : 0.f;
+    const float sc_hi = (m_hi > -INFINITY) ? exp2f(m_hi - mn_hi) : 0.f;
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float mref = (e < 2) ? mn_lo : mn_hi;
+        const float pr = (mref > -INFINITY) ? exp2f(sacc[nt][e] - mref) : 0.f;
+        sacc[nt][e] = pr;
+        if (e < 2) sum_lo += pr;
+        else sum_hi += pr;
+      }
+    }
+    l_lo = l_lo * sc_lo + sum_lo;
+    l_hi = l_hi * sc_hi + sum_hi;
+    // The running maximum settles after the first groups: skip the 64-register rescale
+    // whenever no row of the warp moved its maximum.
+    if (__any_sync(0xffffffffu, sc_lo != 1.0f || sc_hi != 1.0f)) {
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o_acc[i][0] *= sc_lo;
+        o_acc[i][1] *= sc_lo;
+        o_acc[i][2] *= sc_hi;
+        o_acc[i][3] *= sc_hi;
+      }
+    }
+    uint32_t a[4];
+    a[0] = pack_bf16(sacc[0][0], sacc[0][1]);
+    a[1] = pack_bf16(sacc[0][2], sacc[0][3]);
+    a[2] = pack_bf16(sacc[1][0], sacc[1][1]);
+    a[3] = pack_bf16(sacc[1][2], sacc[1][3]);
+#pragma unroll
+    for (int nt = 0; nt < D / 16; ++nt) {
+      uint32_t bfr[4];
+      const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int chunk = nt * 2 + (lane >> 4);
+      ldmatrix_x4_trans(bfr, vs + swz<D>(row, chunk));
+      mma_bf16_16816(o_acc[nt * 2], a, bfr[0], bfr[1]);
+      mma_bf16_16816(o_acc[nt * 2 + 1], a, bfr[2], bfr[3]);
+    }
+    if (++stage == kDmStages) stage = 0;
+  }
+  cp_async_wait<0>();
+
+  // ---- merge the 4 warps (the KV ring is reused as an fp32 [warp][16][D] buffer)
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  __syncthreads();
+  float* o_s = reinterpret_cast<float*>(kv_sm);
+  {
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    if ((lane & 3) == 0) {
+      m_s[warp][r_lo] = m_lo;
+      l_s[warp][r_lo] = l_lo;
+      m_s[warp][r_hi] = m_hi;
+      l_s[warp][r_hi] = l_hi;
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int col = i * 8 + (lane & 3) * 2;
+      float* dlo = o_s + (warp * 16 + r_lo) * D + col;
+      float* dhi = o_s + (warp * 16 + r_hi) * D + col;
+      dlo[0] = o_acc[i][0];
+      dlo[1] = o_acc[i][1];
+      dhi[0] = o_acc[i][2];
+      dhi[1] = o_acc[i][3];
+    }
+  }
+  __syncthreads();
+  const size_t part_idx = (static_cast<size_t>(b) * p.Hkv + h) * p.num_splits + split;
+  float* part_o = p.scratch_o + part_idx * (static_cast<size_t>(G) * D);
+  float* part_ml = p.scratch_ml + part_idx * (static_cast<size_t>(G) * 2);
+  for (int i = threadIdx.x; i < G * D; i += kDmThreads) {
+    const int g = i / D, d = i - g * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDmWarps; ++w) m = fmaxf(m, m_s[w][g]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDmWarps; ++w) {
+      const float sc = (m_s[w][g] > -INFINITY) ? exp2f(m_s[w][g] - m) : 0.f;
+      l += l_s[w][g] * sc;
+      o += o_s[(w * 16 + g) * D + d] * sc;
+    }
+    if (p.num_splits == 1) {
+      if (p.sinks != nullptr) {
+        const float sk = p.sinks[h * G + g] * kLog2e;
+        const float m2 = fmaxf(m, sk);
+        const float sc = (m > -INFINITY) ? exp2f(m - m2) : 0.f;
+        l = l * sc + exp2f(sk - m2);
+        o *= sc;
+      }
+      const float r = l > 0.f ? o / l : 0.f;
+      p.out[static_cast<size_t>(b) * p.Hq * D + (h * G + g) * D + d] = __float2bfloat16(r);
+    } else {
+      part_o[i] = o;
+      if (d == 0) {
+        part_ml[g * 2] = m;
+        part_ml[g * 2 + 1] = l;
+      }
+    }
+  }
+  if (p.num_splits == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(&p.counters[bh], 1);
+    const int last = prev == p.num_splits - 1;
+    if (last) atomicExch(&p.counters[bh], 0);
+    last_s = last;
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  const size_t base_idx = (static_cast<size_t>(b) * p.Hkv + h) * p.num_splits;
+  for (int i = threadIdx.x; i < G * D; i += kDmThreads) {
+    const int g = i / D, d = i - g * D;
+    float m = -INFINITY;
+    for (int s2 = 0; s2 < p.num_splits; ++s2)
+      m = fmaxf(m, __ldcg(&p.scratch_ml[(base_idx + s2) * (G * 2) + g * 2]));
+    float sk = 0.f;
+    if (p.sinks != nullptr) {
+      sk = p.sinks[h * G + g] * kLog2e;
+      m = fmaxf(m, sk);
+    }
+    float l = 0.f, o = 0.f;
+    for (int s2 = 0; s2 < p.num_splits; ++s2) {
+      const float ms = __ldcg(&p.scratch_ml[(base_idx + s2) * (G * 2) + g * 2]);
+      const float ls = __ldcg(&p.scratch_ml[(base_idx + s2) * (G * 2) + g * 2 + 1]);
+      const float sc = (ms > -INFINITY) ? exp2f(ms - m) : 0.f;
+      l += ls * sc;
+      o += __ldcg(&p.scratch_o[(base_idx + s2) * (static_cast<size_t>(G) * D) + i]) * sc;
+    }
+    if (p.sinks != nullptr) l += exp2f(sk - m);
+    const float r = l > 0.f ? o / l : 0.f;
+    p.out[static_cast<size_t>(b) * p.Hq * D + (h * G + g) * D + d] = __float2bfloat16(r);
+  }
+}
+
+template <int D, int KV_BITS, bool BS16>
+static int launch_decode_mma_bs(const DecodeParams& p, int G, int grid, cudaStream_t st) {
+  constexpr int smem = 16 * D * 2 + kDmWarps * kDmStages * 2 * kDmKeys * D * 2;
+  static_assert(kDmWarps * kDmStages * 2 * kDmKeys * D * 2 >= kDmWarps * 16 * D * 4, "merge buffer");
+  auto kern = paged_decode_mma_kernel<D, KV_BITS, BS16>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    configured = true;
+  }
+  kern<<<grid, kDmThreads, smem, st>>>(p, G);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int D, int KV_BITS>
+static int launch_decode_mma(const DecodeParams& p, int G, int grid, cudaStream_t st) {
+  if (p.block_size == kDmKeys) return launch_decode_mma_bs<D, KV_BITS, true>(p, G, grid, st);
+  return launch_decode_mma_bs<D, KV_BITS, false>(p, G, grid, st);
+}
+
 // ----------------------------------------------------------------------------- dispatch
 template <int KV_BITS>
 static int launch_decode(const DecodeParams& p, int D, int G, int grid, cudaStream_t st) {
@@ -627,6 +968,7 @@ static int launch_prefill_one(const PrefillParams& p, int grid, cudaStream_t st)
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
+    prefer_max_shared(kern);
     configured = true;
   }
   kern<<<grid, kPfThreads, smem, st>>>(p);
@@ -689,6 +1031,16 @@ extern "C" int mx_paged_decode(const void* q, long long q_stride, const void* k_
   p.scale_log2 = scale * kLog2e;
   p.softcap = softcap;
   const int grid = B * Hkv * num_splits;
+  if (G <= 16 && (D == 128 || D == 64) && block_size % 16 == 0 && (q_stride % 8) == 0 &&
+      (reinterpret_cast<uintptr_t>(q) & 15) == 0) {
+    if (kv_bits == 16)
+      return D == 128 ? launch_decode_mma<128, 16>(p, G, grid, stream)
+                      : launch_decode_mma<64, 16>(p, G, grid, stream);
+    if (kv_bits == 8)
+      return D == 128 ? launch_decode_mma<128, 8>(p, G, grid, stream)
+                      : launch_decode_mma<64, 8>(p, G, grid, stream);
+    return -1;
+  }
   if (kv_bits == 16) return launch_decode<16>(p, D, G, grid, stream);
   if (kv_bits == 8) return launch_decode<8>(p, D, G, grid, stream);
   return -1;

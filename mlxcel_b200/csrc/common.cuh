@@ -266,4 +266,18 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Keep every kernel of the library on the same L1/shared-memory split (maximum shared): the
+// GEMM needs ~200 KB of shared memory per CTA, and alternating kernels that prefer different
+// splits makes the SM reconfigure between launches.
+template <typename Kernel>
+inline void prefer_max_shared(Kernel kern) {
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);
+}
+#define MX_PREFER_SHARED(kern)                                   \
+  do {                                                           \
+    static const bool mx_once_ = (::mx::prefer_max_shared(kern), true); \
+    (void)mx_once_;                                              \
+  } while (0)
+
 }  // namespace mx

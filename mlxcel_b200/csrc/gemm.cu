@@ -20,6 +20,7 @@
 //
 // Replaces the reference's cuBLASLt call (mlx/backend/cuda/matmul.cpp:133 in its MLX overlay)
 // and the compiled swiglu graph that follows it (src/lib/mlxcel-core/src/layers.rs:4407).
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -32,6 +33,56 @@ constexpr int kBK = 64;          // K elements per stage (128 bytes of bf16)
 constexpr int kLaneRows = 128;   // UMMA M
 constexpr int kMaxStages = 8;
 constexpr int kGemmThreads = 192;
+
+constexpr int kMaxRanks = 8;
+constexpr int kCommMaxTiles = 8192;   // per-tile arrival flags of one channel
+constexpr int kCommDoneIdx = kCommMaxTiles;  // flag index of the per-call completion counter
+
+// Communication epilogues (one channel = control words + flags + receive area in a symmetric
+// heap, i.e. the same offsets are valid on every rank and `*_peer[r]` are rank r's addresses).
+//   COMM 1  one-shot all-reduce (weight-rows-on-lanes tiles, small M): every rank pushes its
+//           bf16 partial tile into every peer's receive slot, bumps the tile's arrival flag on
+//           each peer, waits for `world` arrivals on its own flag and sums the slots in rank
+//           order (+ bias + residual), so all ranks hold bitwise identical results.
+//   COMM 2  two-shot all-reduce (token-rows-on-lanes tiles, large M): tile t is owned by rank
+//           t % world; partial tiles go to the owner only, the owner reduces (+ bias + residual)
+//           and stores the finished tile into every peer's output buffer; a per-call completion
+//           counter tells each rank when all tiles have landed.
+//   COMM 3  all-gather: the tile is stored into every peer's output at column offset rank * N.
+// Receive areas are double-buffered by call parity: a peer can be at most one call ahead.
+struct CommParams {
+  int rank, world;
+  uint32_t* ctl;      // local: [0] calls completed, [1] finished-CTA counter, [2] completion target
+  uint32_t* expect;   // local: per-tile arrival target already consumed
+  uint32_t* flags_peer[kMaxRanks];
+  __nv_bfloat16* recv_peer[kMaxRanks];
+  __nv_bfloat16* out_peer[kMaxRanks];
+  long long parity_stride;  // elements between the two receive halves
+  long long rank_stride;    // elements between source-rank slots
+};
+
+__device__ __forceinline__ void signal_add_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+// Bounded wait until *addr >= target (wrap-safe). Records kErrPeerFlagWait on time-out.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* addr, uint32_t target, int* status) {
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (static_cast<int32_t>(load_acquire_sys(addr) - target) >= 0) return true;
+    }
+    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (status != nullptr) atomicCAS(status, 0, kErrPeerFlagWait);
+      return false;
+    }
+  }
+}
 
 struct GemmParams {
   void* out;
@@ -49,6 +100,7 @@ struct GemmParams {
   int epilogue;
   int out_fp32;
   float glu_alpha, glu_limit;
+  CommParams comm;
 };
 
 __device__ __forceinline__ float act_glu(int epilogue, float g, float u, float alpha, float limit) {
@@ -65,7 +117,7 @@ __device__ __forceinline__ float act_glu(int epilogue, float g, float u, float a
   }
 }
 
-template <int BN, bool SWAP, bool GLU>
+template <int BN, bool SWAP, bool GLU, int COMM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                  const __grid_constant__ CUtensorMap map_col, const GemmParams p) {
@@ -83,6 +135,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   constexpr int CW = (BN >= 32) ? 32 : 16;  // columns per tcgen05.ld
   static_assert(BN % CW == 0 && BN >= 16 && BN <= 256, "unsupported BN");
   static_assert(2 * ACC_COLS <= 512, "accumulators exceed TMEM");
+  static_assert(COMM == 0 || !GLU, "communication epilogues are for plain projections");
+  static_assert(COMM != 1 || SWAP, "one-shot all-reduce uses weight-rows-on-lanes tiles");
+  static_assert(COMM != 2 || !SWAP, "two-shot all-reduce uses token-rows-on-lanes tiles");
+  static_assert(COMM != 3 || SWAP, "all-gather epilogue uses weight-rows-on-lanes tiles");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -222,6 +278,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool glu = GLU;
+    [[maybe_unused]] uint32_t comm_parity = 0;
+    if constexpr (COMM != 0) comm_parity = *reinterpret_cast<volatile uint32_t*>(p.comm.ctl) & 1u;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       const int tile = w / p.splits, split = w - tile * p.splits;
       const int lane_t = tile % p.tiles_lane, col_t = tile / p.tiles_lane;
@@ -305,7 +363,49 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           }
         }
         if (lane_idx < lane_lim) {
-          if constexpr (SWAP) {
+          if constexpr (COMM == 1) {
+            // push the bf16 partial (no bias / residual yet) into every peer's slot [rank]
+            const int n = lane_idx;
+            const size_t base = comm_parity * static_cast<size_t>(p.comm.parity_stride) +
+                                p.comm.rank * static_cast<size_t>(p.comm.rank_stride);
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              const int t = col_t * BN + c * CW + j;
+              if (t < p.M) {
+                const __nv_bfloat16 b = __float2bfloat16(v[j]);
+                const size_t off = base + static_cast<size_t>(t) * p.N + n;
+                for (int pr = 0; pr < p.comm.world; ++pr) p.comm.recv_peer[pr][off] = b;
+              }
+            }
+          } else if constexpr (COMM == 3) {
+            const int n = lane_idx;
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              const int t = col_t * BN + c * CW + j;
+              if (t < p.M) {
+                const __nv_bfloat16 b = __float2bfloat16(v[j] + bias_g);
+                const size_t off = static_cast<size_t>(t) * p.ldo + static_cast<size_t>(p.comm.rank) * p.N + n;
+                for (int pr = 0; pr < p.comm.world; ++pr) p.comm.out_peer[pr][off] = b;
+              }
+            }
+          } else if constexpr (COMM == 2) {
+            // partial tile row -> the owner's slot [rank][tile / world]
+            const int owner = tile % p.comm.world;
+            __nv_bfloat16* dst = p.comm.recv_peer[owner] +
+                                 comm_parity * static_cast<size_t>(p.comm.parity_stride) +
+                                 p.comm.rank * static_cast<size_t>(p.comm.rank_stride) +
+                                 static_cast<size_t>(tile / p.comm.world) * (kLaneRows * BN) +
+                                 static_cast<size_t>(row) * BN + c * CW;
+#pragma unroll
+            for (int j8 = 0; j8 < CW; j8 += 8) {
+              uint4 pk;
+              pk.x = pack_bf16(v[j8 + 0], v[j8 + 1]);
+              pk.y = pack_bf16(v[j8 + 2], v[j8 + 3]);
+              pk.z = pack_bf16(v[j8 + 4], v[j8 + 5]);
+              pk.w = pack_bf16(v[j8 + 6], v[j8 + 7]);
+              *reinterpret_cast<uint4*>(dst + j8) = pk;
+            }
+          } else if constexpr (SWAP) {
             // thread = feature n, columns = tokens
             const int n = lane_idx;
 #pragma unroll
@@ -386,8 +486,127 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       }
+      if constexpr (COMM == 1) {
+        const CommParams& cm = p.comm;
+        __threadfence_system();
+        named_bar_sync(1, 128);
+        if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + tile, 1u);
+        if (epi_tid == 0) {
+          const uint32_t target = cm.expect[tile] + static_cast<uint32_t>(cm.world);
+          const bool ok = wait_flag_ge(cm.flags_peer[cm.rank] + tile, target, p.status);
+          cm.expect[tile] = target;
+          *last_flag = ok ? 1 : 0;
+        }
+        named_bar_sync(1, 128);
+        if (*last_flag != 0 && lane_idx < p.N) {
+          const int n = lane_idx;
+          const __nv_bfloat16* base = cm.recv_peer[cm.rank] +
+                                      comm_parity * static_cast<size_t>(cm.parity_stride);
+          for (int t = col_t * BN; t < min(p.M, (col_t + 1) * BN); ++t) {
+            float sum = bias_g;
+            for (int r = 0; r < cm.world; ++r) {
+              const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(
+                  base + r * static_cast<size_t>(cm.rank_stride) + static_cast<size_t>(t) * p.N + n));
+              sum += __uint_as_float(static_cast<uint32_t>(raw) << 16);
+            }
+            if (p.residual != nullptr)
+              sum += __bfloat162float(p.residual[static_cast<size_t>(t) * p.ldr + n]);
+            reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] =
+                __float2bfloat16(sum);
+          }
+        }
+      } else if constexpr (COMM == 2) {
+        const CommParams& cm = p.comm;
+        const int owner = tile % cm.world;
+        __threadfence_system();
+        named_bar_sync(1, 128);
+        if (epi_tid == 0) signal_add_sys(cm.flags_peer[owner] + tile, 1u);
+        if (owner == cm.rank) {
+          if (epi_tid == 0) {
+            const uint32_t target = cm.expect[tile] + static_cast<uint32_t>(cm.world);
+            const bool ok = wait_flag_ge(cm.flags_peer[cm.rank] + tile, target, p.status);
+            cm.expect[tile] = target;
+            *last_flag = ok ? 1 : 0;
+          }
+          named_bar_sync(1, 128);
+          const int m = lane_idx;
+          if (*last_flag != 0 && m < p.M) {
+            const __nv_bfloat16* base = cm.recv_peer[cm.rank] +
+                                        comm_parity * static_cast<size_t>(cm.parity_stride) +
+                                        static_cast<size_t>(tile / cm.world) * (kLaneRows * BN) +
+                                        static_cast<size_t>(row) * BN;
+            for (int j8 = 0; j8 < BN; j8 += 8) {
+              const int n = col_t * BN + j8;
+              if (n >= p.N) break;
+              float o[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j] = 0.f;
+              for (int r = 0; r < cm.world; ++r) {
+                const uint4 a = __ldcg(reinterpret_cast<const uint4*>(
+                    base + r * static_cast<size_t>(cm.rank_stride) + j8));
+                const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  o[2 * j] += bf16_lo(w4[j]);
+                  o[2 * j + 1] += bf16_hi(w4[j]);
+                }
+              }
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] += __bfloat162float(p.bias[n + j]);
+              }
+              if (p.residual != nullptr) {
+                const uint4 a = *reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(m) * p.ldr + n);
+                const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  o[2 * j] += bf16_lo(w4[j]);
+                  o[2 * j + 1] += bf16_hi(w4[j]);
+                }
+              }
+              uint4 pk;
+              pk.x = pack_bf16(o[0], o[1]);
+              pk.y = pack_bf16(o[2], o[3]);
+              pk.z = pack_bf16(o[4], o[5]);
+              pk.w = pack_bf16(o[6], o[7]);
+              const size_t off = static_cast<size_t>(m) * p.ldo + n;
+              for (int pr = 0; pr < cm.world; ++pr)
+                *reinterpret_cast<uint4*>(cm.out_peer[pr] + off) = pk;
+            }
+          }
+          __threadfence_system();
+          named_bar_sync(1, 128);
+          if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
+        }
+      } else if constexpr (COMM == 3) {
+        const CommParams& cm = p.comm;
+        __threadfence_system();
+        named_bar_sync(1, 128);
+        if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if constexpr (COMM != 0) {
+      // Per-call completion: every tile of every rank has landed here before the kernel ends,
+      // then the last CTA to finish advances the channel's call counter.
+      if (epi_tid == 0) {
+        const CommParams& cm = p.comm;
+        const uint32_t tiles = static_cast<uint32_t>(p.tiles_lane * p.tiles_col);
+        const uint32_t per_call = (COMM == 2) ? tiles : (COMM == 3 ? tiles * cm.world : 0u);
+        if (per_call != 0u) {
+          const uint32_t target = *reinterpret_cast<volatile uint32_t*>(cm.ctl + 2) + per_call;
+          wait_flag_ge(cm.flags_peer[cm.rank] + kCommDoneIdx, target, p.status);
+        }
+        __threadfence();
+        const uint32_t prev = atomicAdd(cm.ctl + 1, 1u);
+        if (prev == gridDim.x - 1) {
+          cm.ctl[1] = 0u;
+          cm.ctl[2] += per_call;
+          __threadfence();
+          atomicAdd(cm.ctl, 1u);
+        }
+      }
     }
   }
 
@@ -485,7 +704,7 @@ int device_sm_count() {
   return sms[dev];
 }
 
-template <int BN, bool SWAP, bool GLU>
+template <int BN, bool SWAP, bool GLU, int COMM = 0>
 static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams p, int grid,
                        cudaStream_t stream) {
   constexpr int LANE_TILES = (SWAP && GLU) ? 2 : 1;
@@ -494,15 +713,24 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
   constexpr int kSmemBudget = 227 * 1024 - 1024 /*align*/ - 256 /*ctrl*/;
   int stages = kSmemBudget / STAGE_BYTES;
   if (stages > kMaxStages) stages = kMaxStages;
+  {
+    // Tuning knob: cap the stage count (shared-memory footprint) from the environment.
+    static const int cap = [] {
+      const char* e = getenv("MLXCEL_B200_GEMM_STAGES");
+      return e ? atoi(e) : 0;
+    }();
+    if (cap >= 2 && stages > cap) stages = cap;
+  }
   if (stages < 2) return -3;
   p.stages = stages;
   const int smem = stages * STAGE_BYTES + 1024 + 256;
-  auto kern = gemm_bf16_kernel<BN, SWAP, GLU>;
+  auto kern = gemm_bf16_kernel<BN, SWAP, GLU, COMM>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
+    prefer_max_shared(kern);
     configured = true;
   }
   kern<<<grid, kGemmThreads, smem, stream>>>(ml, mc, p);
@@ -609,4 +837,110 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
     MX_LAUNCH(128, false, false);
   }
 #undef MX_LAUNCH
+}
+
+// Fused GEMM + collective over a symmetric heap (see CommParams). mode: 1 one-shot all-reduce
+// (M <= 256), 2 two-shot all-reduce, 3 all-gather of the output columns (M <= 256).
+// `flags_peer`, `recv_peer`, `out_peer` are host arrays of `world` device addresses (the same
+// heap offset on every rank); `ctl` (4 words) and `expect` (8193 words) are this rank's
+// control words of the channel; all of them start at zero.
+//   mode 1: result rows go to `out` (local, ldo), residual/bias are added after the reduction.
+//   mode 2: result tiles are stored into every out_peer (ldo), so `out_peer[rank]` must be the
+//           local view of the replicated output (it may alias `residual`).
+//   mode 3: out_peer[r][t, rank * N + n]; N is this rank's column count.
+extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void* bias,
+                            const void* residual, int M, int N, int K, int ldx, int ldw, int ldo,
+                            int ldr, int mode, int rank, int world, const void* const* flags_peer,
+                            const void* const* recv_peer, const void* const* out_peer, void* ctl,
+                            void* expect, long long parity_stride, long long rank_stride,
+                            void* workspace, long long ws_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+    return -1;
+  if ((K % 8) || (ldx % 8) || (ldw % 8) || (N % 8) || (ldo % 8)) return -1;
+  if (workspace == nullptr || ws_bytes < MX_WS_PARTIAL_OFFSET) return -2;
+  if ((mode == 1 || mode == 3) && M > 256) return -1;
+  if (mode < 1 || mode > 3) return -1;
+  const bool swap = mode != 2;
+
+  GemmParams p{};
+  p.out = out;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.status = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + MX_WS_STATUS_OFFSET);
+  p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + MX_WS_COUNTER_OFFSET);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + MX_WS_PARTIAL_OFFSET);
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldo = ldo;
+  p.ldr = ldr;
+  p.epilogue = residual ? MX_EPI_RESIDUAL : (bias ? MX_EPI_BIAS : MX_EPI_NONE);
+  p.num_kb = (K + kBK - 1) / kBK;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.comm.rank = rank;
+  p.comm.world = world;
+  p.comm.ctl = static_cast<uint32_t*>(ctl);
+  p.comm.expect = static_cast<uint32_t*>(expect);
+  for (int r = 0; r < world; ++r) {
+    p.comm.flags_peer[r] = static_cast<uint32_t*>(const_cast<void*>(flags_peer[r]));
+    p.comm.recv_peer[r] = recv_peer ? static_cast<__nv_bfloat16*>(const_cast<void*>(recv_peer[r])) : nullptr;
+    p.comm.out_peer[r] = out_peer ? static_cast<__nv_bfloat16*>(const_cast<void*>(out_peer[r])) : nullptr;
+  }
+  p.comm.parity_stride = parity_stride;
+  p.comm.rank_stride = rank_stride;
+
+  const int sms = device_sm_count();
+  int bn;
+  if (swap) {
+    bn = (M <= 16) ? 16 : (M <= 32) ? 32 : (M <= 64) ? 64 : 128;
+    p.tiles_lane = (N + kLaneRows - 1) / kLaneRows;
+    p.tiles_col = (M + bn - 1) / bn;
+    const int tiles = p.tiles_lane * p.tiles_col;
+    int splits = sms / tiles;
+    if (splits > p.num_kb / 4) splits = p.num_kb / 4;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+    const long long ws_floats = (ws_bytes - MX_WS_PARTIAL_OFFSET) / 4;
+    while (splits > 1 && static_cast<long long>(tiles) * splits * kLaneRows * bn > ws_floats) --splits;
+    p.kb_per_split = (p.num_kb + splits - 1) / splits;
+    p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+    if (mode == 1 && static_cast<long long>(M) * N > rank_stride) return -5;
+  } else {
+    bn = N > 128 ? 256 : 128;
+    p.tiles_lane = (M + kLaneRows - 1) / kLaneRows;
+    p.tiles_col = (N + bn - 1) / bn;
+    const long long slots = (static_cast<long long>(p.tiles_lane) * p.tiles_col + world - 1) / world;
+    if (slots * kLaneRows * bn > rank_stride) return -5;
+  }
+  if (p.tiles_lane * p.tiles_col > kCommMaxTiles) return -5;
+  const long long total = static_cast<long long>(p.tiles_lane) * p.tiles_col * p.splits;
+  // Every CTA must be resident at once: peers wait on each other's tiles.
+  const int grid = static_cast<int>(total < sms ? total : sms);
+
+  CUtensorMap map_x, map_w;
+  const uint32_t x_box = swap ? bn : kLaneRows;
+  const uint32_t w_box = swap ? kLaneRows : bn;
+  if (!make_tensor_map_bf16(&map_x, x, M, K, ldx, x_box, kBK)) return -4;
+  if (!make_tensor_map_bf16(&map_w, w, N, K, ldw, w_box, kBK)) return -4;
+  const CUtensorMap& ml = swap ? map_w : map_x;
+  const CUtensorMap& mc = swap ? map_x : map_w;
+  if (mode == 1) {
+    switch (bn) {
+      case 16: return launch_gemm<16, true, false, 1>(ml, mc, p, grid, stream);
+      case 32: return launch_gemm<32, true, false, 1>(ml, mc, p, grid, stream);
+      case 64: return launch_gemm<64, true, false, 1>(ml, mc, p, grid, stream);
+      default: return launch_gemm<128, true, false, 1>(ml, mc, p, grid, stream);
+    }
+  } else if (mode == 3) {
+    switch (bn) {
+      case 16: return launch_gemm<16, true, false, 3>(ml, mc, p, grid, stream);
+      case 32: return launch_gemm<32, true, false, 3>(ml, mc, p, grid, stream);
+      case 64: return launch_gemm<64, true, false, 3>(ml, mc, p, grid, stream);
+      default: return launch_gemm<128, true, false, 3>(ml, mc, p, grid, stream);
+    }
+  }
+  if (bn == 256) return launch_gemm<256, false, false, 2>(ml, mc, p, grid, stream);
+  return launch_gemm<128, false, false, 2>(ml, mc, p, grid, stream);
 }

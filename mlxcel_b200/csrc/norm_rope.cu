@@ -317,6 +317,9 @@ extern "C" int mx_add_rmsnorm(const void* x, const void* residual, const void* w
   auto W = static_cast<const __nv_bfloat16*>(weight);
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto RO = static_cast<__nv_bfloat16*>(residual_out);
+  MX_PREFER_SHARED(add_rmsnorm_kernel<1>);
+  MX_PREFER_SHARED(add_rmsnorm_kernel<2>);
+  MX_PREFER_SHARED(add_rmsnorm_kernel<4>);
   if (vpt <= 1)
     add_rmsnorm_kernel<1><<<rows, threads, 0, stream>>>(X, R, W, Y, RO, dim, eps, w_bias);
   else if (vpt <= 2)
@@ -357,6 +360,8 @@ extern "C" int mx_rope_append(void* qkv, const int* positions, const int* slot_m
   auto VM = static_cast<__nv_bfloat16*>(v_meta);
   auto QN = static_cast<const __nv_bfloat16*>(q_norm_w);
   auto KN = static_cast<const __nv_bfloat16*>(k_norm_w);
+  MX_PREFER_SHARED(rope_append_kernel<16>);
+  MX_PREFER_SHARED(rope_append_kernel<8>);
   if (kv_bits == 16)
     rope_append_kernel<16><<<blocks, kRopeWarps * 32, 0, stream>>>(
         Q, positions, slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv,
@@ -376,6 +381,7 @@ extern "C" int mx_embedding(const int* ids, const void* table, void* out, int T,
   int threads = dim / 8;
   if (threads > 256) threads = 256;
   if (threads < 32) threads = 32;
+  MX_PREFER_SHARED(embedding_kernel);
   embedding_kernel<<<T, threads, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table),
                                               static_cast<__nv_bfloat16*>(out), dim, vocab, scale);
   return static_cast<int>(cudaGetLastError());

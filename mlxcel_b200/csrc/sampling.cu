@@ -298,6 +298,8 @@ extern "C" int mx_argmax(const void* logits, int logits_fp32, long long row_stri
                          int V, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (B <= 0) return 0;
+  MX_PREFER_SHARED(argmax_kernel<true>);
+  MX_PREFER_SHARED(argmax_kernel<false>);
   if (logits_fp32)
     argmax_kernel<true><<<B, kSampThreads, 0, stream>>>(logits, row_stride, out, V);
   else

@@ -33,7 +33,8 @@ class LLM:
         tp = comm.tp_size if comm is not None else 1
         rank = comm.tp_rank if comm is not None else 0
         w = random_weights(cfg, seed=seed, dtype=dtype, device=device, tp_rank=rank, tp_size=tp,
-                           ep_rank=getattr(comm, "ep_rank", 0), ep_size=getattr(comm, "ep_size", 1))
+                           ep_rank=getattr(comm, "ep_rank", 0), ep_size=getattr(comm, "ep_size", 1),
+                           vocab_parallel=tp > 1 and cfg.vocab_size % tp == 0)
         return LLM(cfg, w, engine_config, comm=comm)
 
     @staticmethod

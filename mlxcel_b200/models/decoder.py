@@ -65,6 +65,9 @@ class LocalComm:
     def gather_logits(self, logits):
         return logits
 
+    def lm_head(self, x, w):
+        return _linear_any(x, w)
+
     def embed(self, ids, table, scale, vocab_start=0):
         return ops.embedding(ids, table, scale)
 
@@ -195,8 +198,10 @@ class DecoderModel:
         if rows is not None:
             h = h.index_select(0, rows)
         x = ops.rmsnorm(h, w.final_norm, cfg.rms_norm_eps, cfg.norm_weight_bias)
-        lg = _linear_any(x, w.lm_head)
-        lg = self.comm.gather_logits(lg)
+        if isinstance(w.lm_head, QuantizedTensor):
+            lg = self.comm.gather_logits(_linear_any(x, w.lm_head))
+        else:
+            lg = self.comm.lm_head(x, w.lm_head)
         ls = cfg.extra.get("logits_scaling", 1.0)
         if ls != 1.0:
             lg = (lg.float() / ls).to(lg.dtype)

@@ -124,15 +124,19 @@ def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, dev
     Use :func:`mlxcel_b200.loading.shard.shard_weights` on a full model when values must agree
     across ranks (parity tests do)."""
     dev = torch.device(device)
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(seed * 1000003 + tp_rank * 101 + ep_rank)
+    gen = torch.Generator(device=dev)   # sharded tensors: one stream per rank
+    gen.manual_seed(seed * 1000003 + tp_rank * 101 + ep_rank + 1)
+    shared = torch.Generator(device=dev)  # replicated tensors: the same stream on every rank
+    shared.manual_seed(seed * 1000003)
     H, D = cfg.hidden_size, cfg.head_dim
     Hq, Hkv = cfg.num_attention_heads // tp_size, max(1, cfg.num_key_value_heads // tp_size)
     I = cfg.intermediate_size // tp_size
     V = cfg.vocab_size
     ones = lambda n: torch.ones(n, dtype=dtype, device=dev) - cfg.norm_weight_bias  # noqa: E731
     Vl = V // tp_size if vocab_parallel else V
-    embed = _randn((Vl, H), std, gen, dtype, dev)
+    # The embedding table stays replicated (a gather needs no collective); only the LM head is
+    # vocab-parallel.
+    embed = _randn((V, H), std, shared, dtype, dev)
     lws = []
     for li in (layers if layers is not None else range(cfg.num_hidden_layers)):
         lw = LayerWeights(ln1=ones(H), ln2=ones(H),
@@ -141,7 +145,7 @@ def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, dev
         if cfg.attention_bias:
             lw.bqkv = _randn(((Hq + 2 * Hkv) * D,), std, gen, dtype, dev)
             if cfg.model_type == "gpt_oss":
-                lw.bo = _randn((H,), std, gen, dtype, dev)
+                lw.bo = _randn((H,), std, shared, dtype, dev)
         if cfg.qk_norm:
             lw.q_norm, lw.k_norm = ones(D), ones(D)
         if cfg.attention_sinks:
@@ -152,25 +156,30 @@ def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, dev
             E = cfg.num_experts
             El = E // ep_size
             mi = cfg.moe_intermediate_size // tp_size
-            lw.router_w = _randn((E, H), std, gen, dtype, dev)
+            lw.router_w = _randn((E, H), std, shared, dtype, dev)
             if cfg.router_bias:
-                lw.router_b = _randn((E,), std, gen, dtype, dev)
+                lw.router_b = _randn((E,), std, shared, dtype, dev)
             lw.experts_gate_up = _randn((El, 2 * mi, H), std, gen, dtype, dev)
             lw.experts_down = _randn((El, H, mi), std, gen, dtype, dev)
             if cfg.expert_bias:
                 lw.experts_gate_up_b = _randn((El, 2 * mi), std, gen, dtype, dev)
                 lw.experts_down_b = _randn((El, H), std, gen, dtype, dev)
+                if tp_size > 1 and ep_size == 1:
+                    lw.experts_down_b = _randn((El, H), std, shared, dtype, dev)
             if cfg.shared_expert_intermediate_size:
                 si = cfg.shared_expert_intermediate_size // tp_size
                 lw.shared_gate_up = _randn((2 * si, H), std, gen, dtype, dev)
                 lw.shared_down = _randn((H, si), std, gen, dtype, dev)
-                lw.shared_gate = _randn((1, H), std, gen, dtype, dev)
+                lw.shared_gate = _randn((1, H), std, shared, dtype, dev)
         else:
             lw.w_gate_up = _randn((2 * I, H), std, gen, dtype, dev)
             lw.w_down = _randn((H, I), std, gen, dtype, dev)
             if cfg.mlp_bias:
                 lw.b_gate_up = _randn((2 * I,), std, gen, dtype, dev)
-                lw.b_down = _randn((H,), std, gen, dtype, dev)
+                lw.b_down = _randn((H,), std, shared, dtype, dev)
         lws.append(lw)
-    lm_head = embed if cfg.tie_word_embeddings else _randn((Vl, H), std, gen, dtype, dev)
+    if cfg.tie_word_embeddings:
+        lm_head = embed[tp_rank * Vl:(tp_rank + 1) * Vl] if vocab_parallel else embed
+    else:
+        lm_head = _randn((Vl, H), std, gen, dtype, dev)
     return ModelWeights(embed=embed, layers=lws, final_norm=ones(H), lm_head=lm_head)

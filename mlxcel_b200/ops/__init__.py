@@ -138,11 +138,13 @@ def _decode_scratch(device: torch.device, floats: int) -> torch.Tensor:
 
 
 def decode_splits(B: int, Hkv: int, max_len: int, sms: int = 148) -> int:
-    """KV splits per (sequence, kv head) so that the grid fills the SMs with >=128-token pieces."""
-    target = sms * 6
-    s = max(1, -(-target // max(1, B * Hkv)))
-    s = min(s, max(1, max_len // 128), 32)
-    return s
+    """KV splits per (sequence, kv head). Two 4-warp CTAs are resident per SM; when the
+    (sequence, kv head) pairs alone fill the SMs a split only adds merge traffic."""
+    pairs = max(1, B * Hkv)
+    if pairs >= sms:
+        return 1
+    s = -(-2 * sms // pairs)
+    return max(1, min(s, max(1, max_len // 256), 16))
 
 
 def paged_decode(q: torch.Tensor, kv: KVLayer, block_tables: torch.Tensor,

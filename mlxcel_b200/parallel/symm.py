@@ -1,0 +1,169 @@
+"""Symmetric heap over NVLink peer memory and the fused compute+collective ops built on it.
+
+One allocation per rank from ``torch.distributed._symmetric_memory`` (CUDA VMM memory whose
+handles are exchanged at rendezvous) gives every rank the device addresses of every peer's
+buffer. Regions are carved at identical offsets on all ranks, so "the same tensor on rank r" is
+``peer_base[r] + offset``. Kernels use plain peer loads/stores and ``red.release.sys`` /
+``ld.acquire.sys`` flags on these addresses — never TMA from a peer's memory.
+
+Channel layout (per fused op kind): 4 control words + 8193 consumed-arrival words (local use) +
+8193 arrival flags (written by peers) + an optional double-buffered receive area.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+_ELEM = {torch.bfloat16: 2, torch.float16: 2, torch.float32: 4, torch.int32: 4, torch.uint8: 1}
+_MAX_TILES = 8192
+_CTL_WORDS = 16
+_CHANNEL_WORDS = _CTL_WORDS + 2 * (_MAX_TILES + 8)
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class SymmetricHeap:
+    def __init__(self, group, device: torch.device, nbytes: int = 0):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group, self.device = group, device
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.nbytes = _align(nbytes or (768 << 20), 2 << 20)
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group.group_name if hasattr(group, "group_name") else group)
+        self.peer_base = [int(p) for p in self.handle.buffer_ptrs]
+        assert self.peer_base[self.rank] == self.buf.data_ptr()
+        self.offset = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def alloc(self, nbytes: int) -> int:
+        """Reserve ``nbytes`` at the same offset on every rank; returns the offset."""
+        off = self.offset
+        nbytes = _align(nbytes)
+        if off + nbytes > self.nbytes:
+            raise MemoryError(f"symmetric heap exhausted ({off + nbytes} > {self.nbytes})")
+        self.offset = off + nbytes
+        return off
+
+    def view(self, offset: int, shape, dtype) -> torch.Tensor:
+        n = math.prod(shape) * _ELEM[dtype]
+        return self.buf[offset:offset + n].view(dtype).view(*shape)
+
+    def peer_ptrs(self, offset: int):
+        """ctypes array of this region's address on every rank."""
+        arr = (ctypes.c_void_p * self.world)()
+        for r in range(self.world):
+            arr[r] = self.peer_base[r] + offset
+        return arr
+
+
+class _Channel:
+    def __init__(self, heap: SymmetricHeap, recv_bytes: int):
+        self.heap = heap
+        self.ctl_off = heap.alloc(_CHANNEL_WORDS * 4)
+        words = heap.view(self.ctl_off, (_CHANNEL_WORDS,), torch.int32)
+        self.ctl = words[:_CTL_WORDS]
+        self.expect = words[_CTL_WORDS:_CTL_WORDS + _MAX_TILES + 8]
+        self.flags_off = self.ctl_off + 4 * (_CTL_WORDS + _MAX_TILES + 8)
+        self.flags_peer = heap.peer_ptrs(self.flags_off)
+        self.recv_bytes = recv_bytes
+        if recv_bytes:
+            self.recv_off = heap.alloc(2 * recv_bytes)
+            self.recv_peer = heap.peer_ptrs(self.recv_off)
+        else:
+            self.recv_off, self.recv_peer = 0, None
+
+    def reset(self) -> None:
+        self.heap.view(self.ctl_off, (_CHANNEL_WORDS,), torch.int32).zero_()
+
+
+class FusedOps:
+    """GEMM → all-reduce (+bias +residual) and GEMM → all-gather as single kernels."""
+
+    def __init__(self, heap: SymmetricHeap, max_tokens: int = 8192, hidden: int = 8192,
+                 vocab: int = 262144, small_m: int = 256):
+        self.heap = heap
+        W = heap.world
+        self.world, self.rank = W, heap.rank
+        self.small_m, self.max_tokens, self.hidden = small_m, max_tokens, hidden
+        # one-shot: [2][world][small_m * hidden] bf16
+        self.one_stride = small_m * hidden
+        self.ch_one = _Channel(heap, W * self.one_stride * 2)
+        # two-shot: [2][world][ceil(tiles / world) * 128 * 256] bf16 with tiles over max_tokens x hidden
+        tiles = ((max_tokens + 127) // 128) * ((hidden + 255) // 256)
+        self.two_stride = ((tiles + W - 1) // W) * 128 * 256
+        self.ch_two = _Channel(heap, W * self.two_stride * 2)
+        self.ch_ag = _Channel(heap, 0)
+        # replicated residual stream and gathered logits live in the heap
+        self.h_off = heap.alloc(max_tokens * hidden * 2)
+        self.h_peer = heap.peer_ptrs(self.h_off)
+        self.vocab_cap = vocab
+        self.logits_off = heap.alloc(small_m * vocab * 2)
+        self.logits_peer = heap.peer_ptrs(self.logits_off)
+        torch.cuda.synchronize(heap.device)
+        dist.barrier(group=heap.group)
+
+    def reset(self) -> None:
+        """Zero every channel on all ranks (after a bounded wait reported a failure)."""
+        torch.cuda.synchronize(self.heap.device)
+        dist.barrier(group=self.heap.group)
+        for ch in (self.ch_one, self.ch_two, self.ch_ag):
+            ch.reset()
+        torch.cuda.synchronize(self.heap.device)
+        dist.barrier(group=self.heap.group)
+
+    def hidden_buffer(self, tokens: int, hidden: int) -> torch.Tensor:
+        return self.heap.view(self.h_off, (tokens, hidden), torch.bfloat16)
+
+    def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, bias, residual) -> torch.Tensor:
+        """``residual + bias + sum_ranks(x_r @ w_r^T)``; the result is bitwise identical on all
+        ranks and lives in the symmetric residual buffer."""
+        M, K = x.shape
+        N = w.shape[0]
+        lib = _lib.load()
+        ws = _lib.workspace(x.device)
+        out = self.hidden_buffer(M, N)
+        if M <= self.small_m:
+            ch, mode, stride = self.ch_one, 1, self.one_stride
+        else:
+            ch, mode, stride = self.ch_two, 2, self.two_stride
+        if M > self.max_tokens or N > self.hidden:
+            raise ValueError("gemm_allreduce shape exceeds the symmetric buffers")
+        res = residual  # read locally by the reducing rank; may alias `out` (in-place update)
+        rc = lib.mx_gemm_comm(x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias), _lib.ptr(res),
+                              M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                              res.stride(0) if res is not None else 0, mode, self.rank, self.world,
+                              ch.flags_peer, ch.recv_peer, self.h_peer, ch.ctl.data_ptr(),
+                              ch.expect.data_ptr(), self.world * stride, stride, ws.data_ptr(),
+                              ws.numel(), _lib.stream())
+        _lib.count_launch()
+        _lib.check(rc, "mx_gemm_comm")
+        return out
+
+    def gemm_allgather(self, x: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
+        """Vocab-parallel projection: every rank ends with ``[M, world * N]`` logits."""
+        M, K = x.shape
+        N = w.shape[0]
+        if M > self.small_m or self.world * N > self.vocab_cap:
+            raise ValueError("gemm_allgather shape exceeds the symmetric buffers")
+        lib = _lib.load()
+        ws = _lib.workspace(x.device)
+        out = self.heap.view(self.logits_off, (M, self.world * N), torch.bfloat16)
+        ch = self.ch_ag
+        rc = lib.mx_gemm_comm(x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias), None, M, N, K,
+                              x.stride(0), w.stride(0), out.stride(0), 0, 3, self.rank, self.world,
+                              ch.flags_peer, None, self.logits_peer, ch.ctl.data_ptr(),
+                              ch.expect.data_ptr(), 0, 0, ws.data_ptr(), ws.numel(), _lib.stream())
+        _lib.count_launch()
+        _lib.check(rc, "mx_gemm_comm")
+        return out

@@ -1,0 +1,94 @@
+"""Tensor-parallel runtime: one process per GPU, SPMD lockstep.
+
+Every rank runs the same scheduler on the same request stream (the step descriptor is
+deterministic), holds a column/row shard of every projection and 1/tp of the KV heads, and keeps
+the residual stream replicated. Two interchangeable communication back ends:
+
+* ``fused`` (default on NVLink/NVSwitch): the row-parallel projections (o_proj, down_proj) run
+  ONE kernel that computes the GEMM tile on tensor cores and reduces it across ranks by peer
+  stores/loads into a symmetric heap (push partial tile → per-tile arrival flags → ordered sum +
+  residual), and the vocab-parallel LM head pushes its logits tile straight into every peer's
+  logits buffer (GEMM → all-gather). See ``csrc/gemm.cu`` (COMM modes).
+* ``nccl``: cuBLAS-free GEMM kernel + ``torch.distributed`` all-reduce / all-gather. This is the
+  measured baseline the fused path is compared against.
+
+The reference simulates TP inside one process (``reduce_sum`` = a chain of adds,
+src/distributed/tensor_parallel/llama_runtime.rs:3133-3153); its shard plan (column-parallel
+q/k/v/gate/up, row-parallel o/down, src/distributed/tensor_parallel/plan_generator.rs) is what the
+weight sharding here follows.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import _lib
+
+
+class TPComm:
+    def __init__(self, group, device: torch.device, backend: str = "fused", max_tokens: int = 8192,
+                 hidden: int = 8192, vocab: int = 262144, ep: bool = True):
+        self.group = group
+        self.device = device
+        self.tp_size = dist.get_world_size(group)
+        self.tp_rank = dist.get_rank(group)
+        self.ep_size = self.tp_size if ep else 1
+        self.ep_rank = self.tp_rank if ep else 0
+        self.backend = backend
+        self.heap = None
+        self.calls = 0
+        if backend == "fused" and self.tp_size > 1:
+            from .symm import SymmetricHeap, FusedOps
+
+            try:
+                self.heap = SymmetricHeap(group, device)
+                self.fused = FusedOps(self.heap, max_tokens=max_tokens, hidden=hidden, vocab=vocab)
+            except Exception as e:  # symmetric memory unavailable: say so loudly, use NCCL
+                if os.environ.get("MLXCEL_B200_REQUIRE_FUSED") == "1":
+                    raise
+                print(f"[mlxcel_b200] fused TP backend unavailable ({type(e).__name__}: {e}); using NCCL",
+                      flush=True)
+                self.backend = "nccl"
+
+    # ------------------------------------------------------------------ collectives
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp_size > 1:
+            dist.all_reduce(x, group=self.group)
+        return x
+
+    def row_parallel_linear(self, x, w, bias, residual):
+        """``residual + all_reduce(x_shard @ w_shard^T) + bias`` with replicated output."""
+        self.calls += 1
+        if self.tp_size == 1:
+            return ops.linear(x, w, bias=bias, residual=residual, out=residual)
+        if self.backend == "fused" and not isinstance(w, tuple):
+            return self.fused.gemm_allreduce(x, w, bias, residual)
+        first = self.tp_rank == 0
+        y = ops.linear(x, w, bias=bias if first else None, residual=residual if first else None)
+        dist.all_reduce(y, group=self.group)
+        return y
+
+    def gather_logits(self, logits_local: torch.Tensor) -> torch.Tensor:
+        """[R, V/tp] per rank → [R, V] on every rank."""
+        if self.tp_size == 1:
+            return logits_local
+        R, Vl = logits_local.shape
+        out = torch.empty(self.tp_size * R, Vl, dtype=logits_local.dtype, device=logits_local.device)
+        dist.all_gather_into_tensor(out, logits_local.contiguous(), group=self.group)
+        return out.view(self.tp_size, R, Vl).permute(1, 0, 2).reshape(R, self.tp_size * Vl)
+
+    def lm_head(self, x, w):
+        """Vocab-parallel LM head: fused GEMM → all-gather when available."""
+        if self.tp_size > 1 and self.backend == "fused":
+            return self.fused.gemm_allgather(x, w)
+        return self.gather_logits(ops.linear(x, w))
+
+    def embed(self, ids, table, scale, vocab_start: int = 0):
+        return ops.embedding(ids, table, scale)
+
+    def barrier(self):
+        if self.tp_size > 1:
+            dist.barrier(group=self.group)
