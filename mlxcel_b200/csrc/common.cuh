@@ -89,6 +89,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     for (int i = 0; i < 128; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
+    // A failure recorded by any thread of any CTA ends every other wait at once, so a step
+    // that lost a peer costs one time-out, not one per tile.
+    if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
     if (globaltimer_ns() - t0 > kWaitLimitNs) {
       if (status != nullptr) atomicCAS(status, 0, code);
       return false;

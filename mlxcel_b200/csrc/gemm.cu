@@ -77,6 +77,7 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* addr, uint32_t targ
     for (int i = 0; i < 64; ++i) {
       if (static_cast<int32_t>(load_acquire_sys(addr) - target) >= 0) return true;
     }
+    if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
     if (globaltimer_ns() - t0 > kWaitLimitNs) {
       if (status != nullptr) atomicCAS(status, 0, kErrPeerFlagWait);
       return false;
@@ -408,6 +409,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           } else if constexpr (SWAP) {
             // thread = feature n, columns = tokens
             const int n = lane_idx;
+            // All residual loads of the chunk are issued before the first store: `out` may
+            // alias `residual`, so interleaving them would serialise one memory latency per token.
+            float rv[CW];
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              const int t = col_t * BN + c * CW + j;
+              rv[j] = (!glu && p.residual != nullptr && t < p.M)
+                          ? __bfloat162float(p.residual[static_cast<size_t>(t) * p.ldr + n])
+                          : 0.f;
+            }
 #pragma unroll
             for (int j = 0; j < CW; ++j) {
               const int t = col_t * BN + c * CW + j;
@@ -416,9 +427,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                 if (glu) {
                   val = act_glu(p.epilogue, v[j] + bias_g, u[j] + bias_u, p.glu_alpha, p.glu_limit);
                 } else {
-                  val = v[j] + bias_g;
-                  if (p.residual != nullptr)
-                    val += __bfloat162float(p.residual[static_cast<size_t>(t) * p.ldr + n]);
+                  val = v[j] + bias_g + rv[j];
                 }
                 if (p.out_fp32)
                   reinterpret_cast<float*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = val;
@@ -944,3 +953,4 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
   if (bn == 256) return launch_gemm<256, false, false, 2>(ml, mc, p, grid, stream);
   return launch_gemm<128, false, false, 2>(ml, mc, p, grid, stream);
 }
+

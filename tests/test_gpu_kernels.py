@@ -313,6 +313,24 @@ def test_tiny_llama_gpu_matches_cpu_reference():
     b = [s.output for s in gpu.generate(prompts, sp)]
     agree = sum(x == y for sa, sb in zip(a, b) for x, y in zip(sa, sb))
     total = sum(len(s) for s in a)
-    # a bf16 executor may flip a near tie and then diverge; require the first tokens and most to agree
-    assert all(sa[0] == sb[0] for sa, sb in zip(a, b))
+    # a bf16 executor may flip a near tie and then diverge: most tokens must agree, and the
+    # logits of one prefill pass must be close in absolute terms.
     assert agree >= 0.6 * total, (a, b)
+
+    from mlxcel_b200.models.decoder import StepBatch
+    ids = torch.tensor(prompts[0], dtype=torch.int32)
+    T = ids.numel()
+
+    def one_pass(eng, dev):
+        kv = eng.pool.layers
+        batch = StepBatch(token_ids=ids.to(dev), positions=torch.arange(T, dtype=torch.int32, device=dev),
+                          slot_mapping=torch.arange(T, dtype=torch.int32, device=dev), num_decode=0,
+                          num_prefill_seqs=1,
+                          pf_block_tables=torch.arange(8, dtype=torch.int32, device=dev)[None],
+                          pf_cu_q=torch.tensor([0, T], dtype=torch.int32, device=dev),
+                          pf_context_lens=torch.tensor([T], dtype=torch.int32, device=dev), pf_max_q_len=T,
+                          logits_rows=torch.tensor([T - 1], device=dev))
+        return eng.model.forward(batch, kv).float().cpu()
+
+    lc, lg = one_pass(cpu, "cpu"), one_pass(gpu, DEV)
+    assert (lc - lg).abs().max().item() < 0.05 * lc.abs().max().item() + 0.02
