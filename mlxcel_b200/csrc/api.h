@@ -158,10 +158,15 @@ int mx_moe_route(const void* logits, int* topk_ids, float* topk_w, int T, int E,
 // MoE token permutation helpers: count tokens per expert, exclusive scan, scatter rows.
 int mx_moe_align(const int* topk_ids, int* expert_offsets, int* sorted_row, int* sorted_token,
                  int T, int k, int E, int e_begin, int e_end, void* stream);
-int mx_moe_gather_rows(const void* x, const int* sorted_token, void* out, int rows, int dim,
-                       void* stream);
-int mx_moe_combine(const void* y, const int* sorted_row, const float* topk_w, void* out,
-                   const void* residual, int T, int k, int dim, int accumulate, void* stream);
+// Rows are bounded by `max_rows` on the host; the true row count is read on the device from
+// total_rows (= expert_offsets[E_local]) so the MoE block needs no host synchronisation.
+int mx_moe_gather_rows_n(const void* x, const int* sorted_token, const int* total_rows, void* out,
+                         int max_rows, int dim, void* stream);
+// out[t] = (residual[t] | out[t] when accumulate) + sum_slots w[t, slot] * y[row(t, slot)];
+// inv_row: [T * k] int scratch.
+int mx_moe_combine_n(const void* y, const int* sorted_pair, const int* total_rows, int* inv_row,
+                     const float* topk_w, void* out, const void* residual, int T, int k, int dim,
+                     int max_rows, int accumulate, void* stream);
 
 // Grouped GEMM over experts: for expert e rows [off[e], off[e+1]) of x use w[e] ([E, N, K]).
 int mx_grouped_gemm_bf16(const void* x, const void* w, void* out, const void* bias,

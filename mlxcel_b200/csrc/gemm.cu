@@ -102,7 +102,78 @@ struct GemmParams {
   int out_fp32;
   float glu_alpha, glu_limit;
   CommParams comm;
+  // grouped (per-expert) mode: rows [group_offsets[e], group_offsets[e+1]) of x use the weight
+  // rows [e * w_group_rows, ...) and bias [e * bias_group_stride, ...)
+  const int* group_offsets;
+  int num_groups;
+  int w_group_rows;
+  int bias_group_stride;
 };
+
+// One unit of work of the persistent tile loop, in tensor-map coordinates and output indices.
+struct WorkItem {
+  int tile, split;
+  int lane_row0, col_row0;   // first row of the lane-side / column-side operand tile
+  int out_tok0, tok_valid;   // first output token row of the tile and how many are real
+  int feat0, feat_valid;     // first output feature of the tile and how many are real
+  int bias_off;
+};
+struct GroupCursor {
+  int e = 0, base = 0;
+};
+
+// Maps the linear work index to a tile. Dense: (tile, split) over a fixed grid of tiles. Grouped:
+// feature tile fastest, then token tiles of expert 0, 1, ... (tile counts come from the device
+// offsets, so every role advances the same running cursor). Returns false past the end.
+template <int BN, bool SWAP, bool GROUPED>
+__device__ __forceinline__ bool decode_work(const GemmParams& p, int w, GroupCursor& cur, WorkItem& it) {
+  if constexpr (!GROUPED) {
+    if (w >= p.tiles_lane * p.tiles_col * p.splits) return false;
+    it.tile = w / p.splits;
+    it.split = w - it.tile * p.splits;
+    const int lane_t = it.tile % p.tiles_lane, col_t = it.tile / p.tiles_lane;
+    it.lane_row0 = lane_t * kLaneRows;
+    it.col_row0 = col_t * BN;
+    it.bias_off = 0;
+    if (SWAP) {
+      it.feat0 = it.lane_row0;
+      it.feat_valid = p.N - it.feat0;
+      it.out_tok0 = it.col_row0;
+      it.tok_valid = p.M - it.out_tok0;
+    } else {
+      it.out_tok0 = it.lane_row0;
+      it.tok_valid = p.M - it.out_tok0;
+      it.feat0 = it.col_row0;
+      it.feat_valid = p.N - it.feat0;
+    }
+    return true;
+  } else {
+    constexpr int TOK_TILE = SWAP ? BN : kLaneRows;
+    constexpr int FEAT_TILE = SWAP ? kLaneRows : BN;
+    const int F = (p.N + FEAT_TILE - 1) / FEAT_TILE;
+    const int f = w % F, g = w / F;
+    while (cur.e < p.num_groups) {
+      const int rows = p.group_offsets[cur.e + 1] - p.group_offsets[cur.e];
+      const int cnt = (rows + TOK_TILE - 1) / TOK_TILE;
+      if (g < cur.base + cnt) break;
+      cur.base += cnt;
+      ++cur.e;
+    }
+    if (cur.e >= p.num_groups) return false;
+    const int e = cur.e;
+    it.tile = w;
+    it.split = 0;
+    it.out_tok0 = p.group_offsets[e] + (g - cur.base) * TOK_TILE;
+    it.tok_valid = p.group_offsets[e + 1] - it.out_tok0;
+    it.feat0 = f * FEAT_TILE;
+    it.feat_valid = p.N - it.feat0;
+    it.bias_off = e * p.bias_group_stride;
+    const int w_row = e * p.w_group_rows + it.feat0;
+    it.lane_row0 = SWAP ? w_row : it.out_tok0;
+    it.col_row0 = SWAP ? it.out_tok0 : w_row;
+    return true;
+  }
+}
 
 __device__ __forceinline__ float act_glu(int epilogue, float g, float u, float alpha, float limit) {
   if (epilogue == MX_EPI_SWIGLU) {
@@ -118,7 +189,7 @@ __device__ __forceinline__ float act_glu(int epilogue, float g, float u, float a
   }
 }
 
-template <int BN, bool SWAP, bool GLU, int COMM>
+template <int BN, bool SWAP, bool GLU, int COMM, bool GROUPED>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                  const __grid_constant__ CUtensorMap map_col, const GemmParams p) {
@@ -137,6 +208,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   static_assert(BN % CW == 0 && BN >= 16 && BN <= 256, "unsupported BN");
   static_assert(2 * ACC_COLS <= 512, "accumulators exceed TMEM");
   static_assert(COMM == 0 || !GLU, "communication epilogues are for plain projections");
+  static_assert(COMM == 0 || !GROUPED, "grouped GEMMs have no communication epilogue");
   static_assert(COMM != 1 || SWAP, "one-shot all-reduce uses weight-rows-on-lanes tiles");
   static_assert(COMM != 2 || !SWAP, "two-shot all-reduce uses token-rows-on-lanes tiles");
   static_assert(COMM != 3 || SWAP, "all-gather epilogue uses weight-rows-on-lanes tiles");
@@ -154,7 +226,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_work = p.tiles_lane * p.tiles_col * p.splits;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&map_lane);
@@ -189,12 +260,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int tile = w / p.splits, split = w - tile * p.splits;
-        const int lane_t = tile % p.tiles_lane, col_t = tile / p.tiles_lane;
-        const int kb0 = split * p.kb_per_split;
+      GroupCursor cur;
+      WorkItem it;
+      for (int w = blockIdx.x; ok && decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x) {
+        const int kb0 = it.split * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-        const int lane_row0 = lane_t * kLaneRows, col_row0 = col_t * BN;
+        const int lane_row0 = it.lane_row0, col_row0 = it.col_row0;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kErrProducerWait)) {
             ok = false;
@@ -227,9 +298,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int tile = w / p.splits, split = w - tile * p.splits;
-        const int kb0 = split * p.kb_per_split;
+      GroupCursor cur;
+      WorkItem it;
+      for (int w = blockIdx.x; ok && decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x) {
+        const int kb0 = it.split * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, p.status, kErrMmaWaitTmem)) break;
         tc_fence_after_sync();
@@ -281,9 +353,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     const bool glu = GLU;
     [[maybe_unused]] uint32_t comm_parity = 0;
     if constexpr (COMM != 0) comm_parity = *reinterpret_cast<volatile uint32_t*>(p.comm.ctl) & 1u;
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const int tile = w / p.splits, split = w - tile * p.splits;
-      const int lane_t = tile % p.tiles_lane, col_t = tile / p.tiles_lane;
+    GroupCursor cur;
+    WorkItem it;
+    for (int w = blockIdx.x; decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x) {
+      const int tile = it.tile, split = it.split;
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kErrEpilogueWait)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * ACC_COLS;
@@ -324,12 +397,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       }
 
       // Stage 2: final values -> epilogue -> global.
-      const int lane_idx = lane_t * kLaneRows + row;  // token (normal) or feature (SWAP)
-      const int lane_lim = SWAP ? p.N : p.M;
+      // lane_idx: output token (token-rows-on-lanes) or output feature (weight-rows-on-lanes)
+      const int lane_idx = (SWAP ? it.feat0 : it.out_tok0) + row;
+      const bool row_ok = row < (SWAP ? it.feat_valid : it.tok_valid);
+      const __nv_bfloat16* bias_p = p.bias ? p.bias + it.bias_off : nullptr;
       float bias_g = 0.f, bias_u = 0.f;
-      if (SWAP && p.bias != nullptr && lane_idx < p.N) {
-        bias_g = __bfloat162float(p.bias[lane_idx]);
-        if (glu) bias_u = __bfloat162float(p.bias[p.glu_offset + lane_idx]);
+      if (SWAP && bias_p != nullptr && row_ok) {
+        bias_g = __bfloat162float(bias_p[lane_idx]);
+        if (glu) bias_u = __bfloat162float(bias_p[p.glu_offset + lane_idx]);
       }
 #pragma unroll 1
       for (int c = 0; c < BN / CW; ++c) {
@@ -363,7 +438,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
             }
           }
         }
-        if (lane_idx < lane_lim) {
+        if (row_ok) {
           if constexpr (COMM == 1) {
             // push the bf16 partial (no bias / residual yet) into every peer's slot [rank]
             const int n = lane_idx;
@@ -371,8 +446,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                                 p.comm.rank * static_cast<size_t>(p.comm.rank_stride);
 #pragma unroll
             for (int j = 0; j < CW; ++j) {
-              const int t = col_t * BN + c * CW + j;
-              if (t < p.M) {
+              const int t = it.out_tok0 + c * CW + j;
+              if (c * CW + j < it.tok_valid) {
                 const __nv_bfloat16 b = __float2bfloat16(v[j]);
                 const size_t off = base + static_cast<size_t>(t) * p.N + n;
                 for (int pr = 0; pr < p.comm.world; ++pr) p.comm.recv_peer[pr][off] = b;
@@ -382,8 +457,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
             const int n = lane_idx;
 #pragma unroll
             for (int j = 0; j < CW; ++j) {
-              const int t = col_t * BN + c * CW + j;
-              if (t < p.M) {
+              const int t = it.out_tok0 + c * CW + j;
+              if (c * CW + j < it.tok_valid) {
                 const __nv_bfloat16 b = __float2bfloat16(v[j] + bias_g);
                 const size_t off = static_cast<size_t>(t) * p.ldo + static_cast<size_t>(p.comm.rank) * p.N + n;
                 for (int pr = 0; pr < p.comm.world; ++pr) p.comm.out_peer[pr][off] = b;
@@ -414,15 +489,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
             float rv[CW];
 #pragma unroll
             for (int j = 0; j < CW; ++j) {
-              const int t = col_t * BN + c * CW + j;
-              rv[j] = (!glu && p.residual != nullptr && t < p.M)
+              const int t = it.out_tok0 + c * CW + j;
+              rv[j] = (!glu && p.residual != nullptr && c * CW + j < it.tok_valid)
                           ? __bfloat162float(p.residual[static_cast<size_t>(t) * p.ldr + n])
                           : 0.f;
             }
 #pragma unroll
             for (int j = 0; j < CW; ++j) {
-              const int t = col_t * BN + c * CW + j;
-              if (t < p.M) {
+              const int t = it.out_tok0 + c * CW + j;
+              if (c * CW + j < it.tok_valid) {
                 float val;
                 if (glu) {
                   val = act_glu(p.epilogue, v[j] + bias_g, u[j] + bias_u, p.glu_alpha, p.glu_limit);
@@ -439,26 +514,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           } else {
             // thread = token m, columns = features
             const int m = lane_idx;
-            const int n0 = col_t * BN + c * CW;
+            const int nl0 = c * CW;  // first feature of the chunk inside the tile
 #pragma unroll
             for (int j8 = 0; j8 < CW; j8 += 8) {
-              const int n = n0 + j8;
-              if (n >= p.N) break;
+              const int nl = nl0 + j8;
+              const int n = it.feat0 + nl;
+              if (nl >= it.feat_valid) break;
               float o[8];
-              const bool full8 = (n + 8 <= p.N);
+              const bool full8 = (nl + 8 <= it.feat_valid);
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 float val = v[j8 + j];
-                const bool in = full8 || (n + j < p.N);
+                const bool in = full8 || (nl + j < it.feat_valid);
                 if (glu) {
                   float g = val, uu = u[j8 + j];
-                  if (p.bias != nullptr && in) {
-                    g += __bfloat162float(p.bias[n + j]);
-                    uu += __bfloat162float(p.bias[p.glu_offset + n + j]);
+                  if (bias_p != nullptr && in) {
+                    g += __bfloat162float(bias_p[n + j]);
+                    uu += __bfloat162float(bias_p[p.glu_offset + n + j]);
                   }
                   val = act_glu(p.epilogue, g, uu, p.glu_alpha, p.glu_limit);
                 } else {
-                  if (p.bias != nullptr && in) val += __bfloat162float(p.bias[n + j]);
+                  if (bias_p != nullptr && in) val += __bfloat162float(bias_p[n + j]);
                   if (p.residual != nullptr && in)
                     val += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n + j]);
                 }
@@ -471,7 +547,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                   reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
                   reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
                 } else {
-                  for (int j = 0; j < 8 && n + j < p.N; ++j) dst[j] = o[j];
+                  for (int j = 0; j < 8 && nl + j < it.feat_valid; ++j) dst[j] = o[j];
                 }
               } else {
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
@@ -483,7 +559,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                   pk.w = pack_bf16(o[6], o[7]);
                   *reinterpret_cast<uint4*>(dst) = pk;
                 } else {
-                  for (int j = 0; j < 8 && n + j < p.N; ++j) dst[j] = __float2bfloat16(o[j]);
+                  for (int j = 0; j < 8 && nl + j < it.feat_valid; ++j) dst[j] = __float2bfloat16(o[j]);
                 }
               }
             }
@@ -507,11 +583,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           *last_flag = ok ? 1 : 0;
         }
         named_bar_sync(1, 128);
-        if (*last_flag != 0 && lane_idx < p.N) {
+        if (*last_flag != 0 && row_ok) {
           const int n = lane_idx;
           const __nv_bfloat16* base = cm.recv_peer[cm.rank] +
                                       comm_parity * static_cast<size_t>(cm.parity_stride);
-          for (int t = col_t * BN; t < min(p.M, (col_t + 1) * BN); ++t) {
+          for (int t = it.out_tok0; t < it.out_tok0 + min(BN, it.tok_valid); ++t) {
             float sum = bias_g;
             for (int r = 0; r < cm.world; ++r) {
               const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(
@@ -539,14 +615,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           }
           named_bar_sync(1, 128);
           const int m = lane_idx;
-          if (*last_flag != 0 && m < p.M) {
+          if (*last_flag != 0 && row_ok) {
             const __nv_bfloat16* base = cm.recv_peer[cm.rank] +
                                         comm_parity * static_cast<size_t>(cm.parity_stride) +
                                         static_cast<size_t>(tile / cm.world) * (kLaneRows * BN) +
                                         static_cast<size_t>(row) * BN;
             for (int j8 = 0; j8 < BN; j8 += 8) {
-              const int n = col_t * BN + j8;
-              if (n >= p.N) break;
+              const int n = it.feat0 + j8;
+              if (j8 >= it.feat_valid) break;
               float o[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) o[j] = 0.f;
@@ -713,7 +789,7 @@ int device_sm_count() {
   return sms[dev];
 }
 
-template <int BN, bool SWAP, bool GLU, int COMM = 0>
+template <int BN, bool SWAP, bool GLU, int COMM = 0, bool GROUPED = false>
 static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams p, int grid,
                        cudaStream_t stream) {
   constexpr int LANE_TILES = (SWAP && GLU) ? 2 : 1;
@@ -733,7 +809,7 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
   if (stages < 2) return -3;
   p.stages = stages;
   const int smem = stages * STAGE_BYTES + 1024 + 256;
-  auto kern = gemm_bf16_kernel<BN, SWAP, GLU, COMM>;
+  auto kern = gemm_bf16_kernel<BN, SWAP, GLU, COMM, GROUPED>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e =
@@ -954,3 +1030,70 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
   return launch_gemm<128, false, false, 2>(ml, mc, p, grid, stream);
 }
 
+
+// Grouped (per-expert) GEMM: rows [off[e], off[e+1]) of x are multiplied by expert e's weight
+// matrix w[e] ([E, N or 2N, K] contiguous) with the same tcgen05 kernel; the tile schedule is
+// derived on the device from `expert_offsets` ([E + 1] ints in device memory), so the host never
+// needs the routing result. `max_rows` bounds the row count of x / out (allocation size) and
+// `avg_rows_hint` (rows per expert the caller expects) picks the operand placement: few rows per
+// expert stream the expert weights through the MMA lanes (decode), many rows put tokens on lanes.
+extern "C" int mx_grouped_gemm_bf16(const void* x, const void* w, void* out, const void* bias,
+                                    const int* expert_offsets, int E, int N, int K, int max_rows,
+                                    int epilogue, int glu_offset, float glu_alpha, float glu_limit,
+                                    void* workspace, long long ws_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (E <= 0 || N <= 0 || K <= 0 || max_rows <= 0) return 0;
+  if ((K % 8) || (N % 8)) return -1;
+  if (workspace == nullptr || ws_bytes < MX_WS_PARTIAL_OFFSET) return -2;
+  const bool glu = epilogue == MX_EPI_SWIGLU || epilogue == MX_EPI_GEGLU ||
+                   epilogue == MX_EPI_CLIPPED_SWIGLU;
+  const int w_group_rows = glu ? (glu_offset + N) : N;
+  GemmParams p{};
+  p.out = out;
+  p.bias = (epilogue == MX_EPI_NONE) ? nullptr : static_cast<const __nv_bfloat16*>(bias);
+  p.status = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + MX_WS_STATUS_OFFSET);
+  p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + MX_WS_COUNTER_OFFSET);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + MX_WS_PARTIAL_OFFSET);
+  p.M = max_rows;
+  p.N = N;
+  p.K = K;
+  p.ldo = N;
+  p.glu_offset = glu_offset;
+  p.epilogue = epilogue;
+  p.glu_alpha = glu_alpha;
+  p.glu_limit = glu_limit;
+  p.num_kb = (K + kBK - 1) / kBK;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.group_offsets = expert_offsets;
+  p.num_groups = E;
+  p.w_group_rows = w_group_rows;
+  p.bias_group_stride = w_group_rows;
+  const int avg = (max_rows + E - 1) / E;
+  const bool swap = avg <= 96;
+  const int bn = swap ? (avg <= 16 ? 16 : avg <= 32 ? 32 : 64) : (glu ? 128 : (N > 128 ? 256 : 128));
+  const int grid = device_sm_count();
+  CUtensorMap map_x, map_w;
+  const uint32_t x_box = swap ? bn : kLaneRows;
+  const uint32_t w_box = swap ? kLaneRows : bn;
+  if (!make_tensor_map_bf16(&map_x, x, max_rows, K, K, x_box, kBK)) return -4;
+  if (!make_tensor_map_bf16(&map_w, w, static_cast<uint64_t>(E) * w_group_rows, K, K, w_box, kBK))
+    return -4;
+  const CUtensorMap& ml = swap ? map_w : map_x;
+  const CUtensorMap& mc = swap ? map_x : map_w;
+#define MX_GLAUNCH(BN_, SWAP_, GLU_) return launch_gemm<BN_, SWAP_, GLU_, 0, true>(ml, mc, p, grid, stream)
+  if (swap) {
+    if (glu) {
+      if (bn == 16) MX_GLAUNCH(16, true, true);
+      if (bn == 32) MX_GLAUNCH(32, true, true);
+      MX_GLAUNCH(64, true, true);
+    }
+    if (bn == 16) MX_GLAUNCH(16, true, false);
+    if (bn == 32) MX_GLAUNCH(32, true, false);
+    MX_GLAUNCH(64, true, false);
+  }
+  if (glu) MX_GLAUNCH(128, false, true);
+  if (bn == 256) MX_GLAUNCH(256, false, false);
+  MX_GLAUNCH(128, false, false);
+#undef MX_GLAUNCH
+}

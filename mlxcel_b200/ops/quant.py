@@ -1,0 +1,190 @@
+"""MLX quantization formats: quantizers (for random-init checkpoints and tests), the PyTorch
+reference dequantizer, and the quantized linear dispatch.
+
+Layout facts (reference: src/lib/mlxcel-core/src/layers.rs:2322-2522 and
+src/lib/mlxcel-core/cpp/mlx_cxx_kernels.cpp:3073-3152):
+
+* affine: ``w ≈ q * scale + bias`` per group of ``group_size`` inputs; ``q`` packed LSB-first
+  along the input dimension into uint32 (a contiguous little-endian bit stream for 3/5/6 bits);
+  scales/biases ``[out, in/group]`` in the activation dtype;
+  invariant ``packed_in * 32 == bits * in``.
+* mxfp4 / mxfp8: e2m1 / e4m3 values with one e8m0 scale (uint8) per 32 inputs, no biases.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ..models.weights import QuantizedTensor
+
+_E2M1 = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+_MODE_ID = {"affine": 0, "mxfp4": 1, "mxfp8": 2}
+
+
+# ----------------------------------------------------------------------------- bit packing
+def pack_bits(q: torch.Tensor, bits: int) -> torch.Tensor:
+    """q: integer tensor [..., in] with values < 2**bits → uint32 words [..., in*bits/32]."""
+    *lead, n = q.shape
+    assert (n * bits) % 32 == 0
+    qv = q.to(torch.int64).reshape(-1, n)
+    bitpos = torch.arange(n, device=q.device, dtype=torch.int64) * bits
+    words = torch.zeros(qv.shape[0], n * bits // 32 + 1, dtype=torch.int64, device=q.device)
+    wi, sh = bitpos // 32, bitpos % 32
+    lo = (qv << sh) & 0xFFFFFFFF
+    hi = (qv << sh) >> 32
+    words.scatter_add_(1, wi.expand_as(qv), lo)
+    words.scatter_add_(1, (wi + 1).expand_as(qv), hi)
+    words = words[:, :-1] & 0xFFFFFFFF
+    # keep the bit pattern in an int32 tensor (torch has limited uint32 support)
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
+    return words.reshape(*lead, n * bits // 32)
+
+
+def unpack_bits(words: torch.Tensor, bits: int, n: int) -> torch.Tensor:
+    *lead, nw = words.shape
+    w = words.to(torch.int64).reshape(-1, nw) & 0xFFFFFFFF
+    w = torch.cat([w, torch.zeros(w.shape[0], 1, dtype=torch.int64, device=w.device)], dim=1)
+    bitpos = torch.arange(n, device=words.device, dtype=torch.int64) * bits
+    wi, sh = bitpos // 32, bitpos % 32
+    lo = w.gather(1, wi.expand(w.shape[0], n)) >> sh
+    hi = w.gather(1, (wi + 1).expand(w.shape[0], n)) << (32 - sh)
+    return ((lo | hi) & ((1 << bits) - 1)).reshape(*lead, n)
+
+
+# ----------------------------------------------------------------------------- quantizers
+def quantize_affine(w: torch.Tensor, bits: int = 4, group_size: int = 64,
+                    dtype=torch.bfloat16) -> QuantizedTensor:
+    """MLX affine quantization: per group, scale = (max - min) / (2^bits - 1), bias = min
+    (with MLX's sign convention that keeps the larger-magnitude edge exact)."""
+    *lead, out, inn = w.shape
+    g = w.float().reshape(*lead, out, inn // group_size, group_size)
+    wmax, wmin = g.amax(-1, keepdim=True), g.amin(-1, keepdim=True)
+    nlev = float((1 << bits) - 1)
+    # MLX keeps the group edge of larger magnitude exactly representable: the scale is negative
+    # when that edge is the maximum (codes then count down from it).
+    mask = wmin.abs() > wmax.abs()
+    scale = ((wmax - wmin) / nlev).clamp_min(1e-7)
+    scale = torch.where(mask, scale, -scale)
+    edge = torch.where(mask, wmin, wmax)
+    q0 = torch.round(edge / scale)
+    scale = torch.where(q0 != 0, edge / q0, scale)
+    bias = torch.where(q0 == 0, torch.zeros_like(edge), edge)
+    scale = scale.to(dtype).float()
+    bias = bias.to(dtype).float()
+    q = torch.round((g - bias) / scale).clamp(0, nlev).to(torch.int64)
+    packed = pack_bits(q.reshape(*lead, out, inn), bits)
+    return QuantizedTensor(packed, scale.squeeze(-1).to(dtype), bias.squeeze(-1).to(dtype), bits,
+                           group_size, "affine")
+
+
+def quantize_mxfp4(w: torch.Tensor) -> QuantizedTensor:
+    """e2m1 values with e8m0 = ceil-pow2(amax / 6) per 32 inputs."""
+    *lead, out, inn = w.shape
+    g = w.float().reshape(*lead, out, inn // 32, 32)
+    amax = g.abs().amax(-1, keepdim=True).clamp_min(2.0 ** -126)
+    e = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)
+    scale = torch.pow(2.0, e)
+    x = (g / scale).clamp(-6.0, 6.0)
+    tab = _E2M1.to(w.device)
+    idx = (x.abs().unsqueeze(-1) - tab).abs().argmin(-1)
+    code = idx | ((x < 0).to(torch.int64) << 3)
+    packed = pack_bits(code.reshape(*lead, out, inn), 4)
+    s8 = (e + 127).to(torch.uint8).squeeze(-1)
+    return QuantizedTensor(packed, s8, None, 4, 32, "mxfp4")
+
+
+def quantize_mxfp8(w: torch.Tensor) -> QuantizedTensor:
+    *lead, out, inn = w.shape
+    g = w.float().reshape(*lead, out, inn // 32, 32)
+    amax = g.abs().amax(-1, keepdim=True).clamp_min(2.0 ** -126)
+    e = torch.ceil(torch.log2(amax / 448.0)).clamp(-127, 127)
+    scale = torch.pow(2.0, e)
+    x8 = (g / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    code = x8.view(torch.uint8).to(torch.int64)
+    packed = pack_bits(code.reshape(*lead, out, inn), 8)
+    s8 = (e + 127).to(torch.uint8).squeeze(-1)
+    return QuantizedTensor(packed, s8, None, 8, 32, "mxfp8")
+
+
+def quantize(w: torch.Tensor, mode: str = "affine", bits: int = 4, group_size: int = 64,
+             dtype=torch.bfloat16) -> QuantizedTensor:
+    if mode == "affine":
+        return quantize_affine(w, bits, group_size, dtype)
+    if mode == "mxfp4":
+        return quantize_mxfp4(w)
+    if mode == "mxfp8":
+        return quantize_mxfp8(w)
+    raise ValueError(mode)
+
+
+# ----------------------------------------------------------------------------- dequantize
+def dequantize_ref(qt: QuantizedTensor, dtype=torch.float32) -> torch.Tensor:
+    *lead, out, inn = qt.shape
+    q = unpack_bits(qt.packed, qt.bits, inn)
+    g = qt.group_size
+    if qt.mode == "affine":
+        v = q.float().reshape(*lead, out, inn // g, g) * qt.scales.float().unsqueeze(-1) + \
+            qt.biases.float().unsqueeze(-1)
+    else:
+        sc = torch.pow(2.0, qt.scales.float() - 127.0).unsqueeze(-1)
+        if qt.mode == "mxfp4":
+            tab = _E2M1.to(q.device)
+            val = tab[(q & 7)] * torch.where((q & 8) != 0, -1.0, 1.0)
+        else:
+            val = q.to(torch.uint8).view(torch.float8_e4m3fn).float()
+        v = val.reshape(*lead, out, inn // g, g) * sc
+    return v.reshape(*lead, out, inn).to(dtype)
+
+
+def dequantize(qt: QuantizedTensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 dequantization (CUDA kernel on device tensors)."""
+    if not qt.packed.is_cuda:
+        return dequantize_ref(qt, torch.bfloat16)
+    *lead, n, inn = qt.shape
+    rows = n
+    for d in lead:
+        rows *= d
+    if out is None:
+        out = torch.empty(*lead, n, inn, dtype=torch.bfloat16, device=qt.packed.device)
+    lib = _lib.load()
+    rc = lib.mx_dequantize(qt.packed.data_ptr(), qt.scales.data_ptr(), _lib.ptr(qt.biases),
+                           out.data_ptr(), rows, inn, qt.bits, qt.group_size, _MODE_ID[qt.mode],
+                           _lib.stream())
+    _lib.count_launch()
+    _lib.check(rc, "mx_dequantize")
+    return out
+
+
+# ----------------------------------------------------------------------------- linear
+_TMP: dict = {}
+
+
+def qlinear(x: torch.Tensor, qt: QuantizedTensor, bias=None, residual=None, out=None) -> torch.Tensor:
+    """``x @ dequant(w)^T (+ bias) (+ residual)``. M <= 8 rows stream the packed weights once
+    through the GEMV kernel; larger M dequantizes into a reused bf16 buffer and runs the tcgen05
+    GEMM (prefill is compute bound, so the extra pass is small there)."""
+    from . import linear, reference as ref
+
+    if not x.is_cuda:
+        return ref.linear(x, dequantize_ref(qt), bias, residual)
+    M, K = x.shape
+    N = qt.shape[-2]
+    lib = _lib.load()
+    if M <= 8 and qt.bits in (4, 8):
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        rc = lib.mx_qmv(x.data_ptr(), qt.packed.data_ptr(), qt.scales.data_ptr(), _lib.ptr(qt.biases),
+                        out.data_ptr(), _lib.ptr(residual), _lib.ptr(bias), M, N, K, qt.bits,
+                        qt.group_size, _MODE_ID[qt.mode], x.stride(0), out.stride(0), _lib.stream())
+        if rc == 0:
+            _lib.count_launch()
+            return out
+        if rc != -9:
+            _lib.check(rc, "mx_qmv")
+    key = (x.device.index, N, K)
+    tmp = _TMP.get(key)
+    if tmp is None:
+        tmp = torch.empty(N, K, dtype=torch.bfloat16, device=x.device)
+        _TMP[key] = tmp
+    dequantize(qt, tmp)
+    return linear(x, tmp, bias=bias, residual=residual, out=out)
