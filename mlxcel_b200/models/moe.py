@@ -1,0 +1,49 @@
+"""Sparse MoE block of the decoder executor.
+
+Router GEMM → top-k routing → local gather of the routed rows → grouped gate/up GEMM with the
+gated activation fused → grouped down GEMM → weighted combine (+ residual). Under expert
+parallelism every rank holds E / ep experts; tokens are replicated (attention is tensor
+parallel), so the only collective is the all-reduce of the partial outputs.
+Reference: MLPBlock.forward (src/models/gpt_oss.rs:402-446), SwitchGLU
+(src/models/switch_layers.rs:98-220), shared experts of Qwen2-MoE.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import moe as moe_ops
+from .weights import LayerWeights, QuantizedTensor
+
+
+def _dense(w):
+    if isinstance(w, QuantizedTensor):
+        from ..ops import quant
+        return quant.dequantize(w)
+    return w
+
+
+def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -> torch.Tensor:
+    """Returns the new residual stream ``h + moe(x)`` (bf16 [T, H])."""
+    logits = ops.linear(x, lw.router_w, bias=lw.router_b)
+    ids, wts = moe_ops.route(logits, cfg.num_experts_per_tok, cfg.moe_route_mode, cfg.norm_topk_prob)
+    ep, ep_rank = comm.ep_size, comm.ep_rank
+    gate_up, down = _dense(lw.experts_gate_up), _dense(lw.experts_down)
+    El = gate_up.shape[0]
+    inter = gate_up.shape[1] // 2
+    first = ep_rank == 0 or ep == 1
+    out = moe_ops.moe_experts(x, ids, wts, gate_up, down, inter, cfg.hidden_act, lw.experts_gate_up_b,
+                              lw.experts_down_b, e_begin=ep_rank * El, residual=h if first else None,
+                              alpha=cfg.swiglu_alpha, limit=cfg.swiglu_limit)
+    if lw.shared_gate_up is not None:
+        si = lw.shared_gate_up.shape[0] // 2 if not isinstance(lw.shared_gate_up, QuantizedTensor) \
+            else lw.shared_gate_up.shape[-2] // 2
+        a = ops.glu_linear(x, _dense(lw.shared_gate_up), si, cfg.hidden_act)
+        s = ops.linear(a, _dense(lw.shared_down))
+        if lw.shared_gate is not None:
+            g = torch.sigmoid(ops.linear(x, lw.shared_gate).float())
+            s = (s.float() * g).to(s.dtype)
+        out = (out.float() + s.float()).to(out.dtype)
+    if ep > 1:
+        out = comm.all_reduce(out)
+    return out

@@ -208,6 +208,21 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> tor
     return out
 
 
+def swiglu(gate_up: torch.Tensor, inter: int, act: str = "silu", alpha: float = 1.702,
+           limit: float = 7.0) -> torch.Tensor:
+    """Gated activation on a fused ``[T, 2I]`` tensor (gate columns first) → ``[T, I]``."""
+    if not gate_up.is_cuda:
+        return ref.glu_act(_ACT_TO_EPI[act], gate_up[:, :inter].float(), gate_up[:, inter:].float(),
+                           alpha, limit).to(gate_up.dtype)
+    T = gate_up.shape[0]
+    out = torch.empty(T, inter, dtype=gate_up.dtype, device=gate_up.device)
+    if T:
+        mode = {"silu": 0, "gelu_tanh": 1, "clipped_swiglu": 2}[act]
+        _lib_call("mx_swiglu", gate_up.data_ptr(), out.data_ptr(), T, inter, mode, float(alpha),
+                  float(limit), _lib.stream())
+    return out
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     if not logits.is_cuda:
         return ref.argmax(logits)

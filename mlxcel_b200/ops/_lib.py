@@ -79,8 +79,9 @@ def _declare(lib) -> None:
         "mx_dequantize": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
         "mx_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
         "mx_moe_align": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-        "mx_moe_gather_rows": [_vp, _vp, _vp, _i, _i, _vp],
-        "mx_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+        "mx_moe_gather_rows_n": [_vp, _vp, _vp, _vp, _i, _i, _vp],
+        "mx_moe_combine_n": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+        "mx_qmv": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
         "mx_grouped_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _ll,
                                  _vp],
     }

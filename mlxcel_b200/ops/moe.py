@@ -1,0 +1,130 @@
+"""Mixture-of-experts operators: routing, token permutation, grouped expert GEMMs, combine.
+
+CUDA tensors run ``csrc/moe.cu`` + the grouped mode of the tcgen05 GEMM (``csrc/gemm.cu``);
+CPU tensors run the plain PyTorch statements below (also the test oracles).
+Reference behaviour: src/models/switch_layers.rs:98-220,2180-2250 and
+src/models/gpt_oss.rs:402-446 of the reference.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib, reference as ref
+from . import _ACT_TO_EPI
+
+
+# ----------------------------------------------------------------------------- reference
+def route_ref(logits: torch.Tensor, k: int, mode: str, norm_topk: bool):
+    lg = torch.nan_to_num(logits.float(), nan=float("-inf"))
+    if mode == "softmax_topk":
+        p = torch.softmax(lg, -1)
+        w, ids = torch.topk(p, k, dim=-1)
+        if norm_topk:
+            w = w / w.sum(-1, keepdim=True)
+    else:
+        v, ids = torch.topk(lg, k, dim=-1)
+        w = torch.softmax(v, -1)
+    return ids.to(torch.int32), w.float()
+
+
+def moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up=None, b_down=None,
+            e_begin=0, alpha=1.702, limit=7.0, dequant=None):
+    """Dense statement: for every (token, slot) routed to a local expert, run that expert's
+    gated MLP and accumulate the weighted result in fp32. Returns fp32 [T, H]."""
+    T, H = x.shape
+    El = w_gate_up.shape[0]
+    out = torch.zeros(T, w_down.shape[1], dtype=torch.float32, device=x.device)
+    epi = _ACT_TO_EPI[act]
+    for el in range(El):
+        e = e_begin + el
+        tok, slot = torch.nonzero(ids == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        xe = x[tok].float()
+        gu = xe @ w_gate_up[el].float().t()
+        if b_gate_up is not None:
+            gu = gu + b_gate_up[el].float()
+        a = ref.glu_act(epi, gu[:, :inter], gu[:, inter:2 * inter], alpha, limit).to(x.dtype).float()
+        y = a @ w_down[el].float().t()
+        if b_down is not None:
+            y = y + b_down[el].float()
+        y = y.to(x.dtype).float()
+        out.index_add_(0, tok, y * wts[tok, slot].unsqueeze(-1))
+    return out
+
+
+# ----------------------------------------------------------------------------- CUDA
+def route(logits: torch.Tensor, k: int, mode: str = "topk_softmax", norm_topk: bool = True):
+    """Router logits [T, E] → (expert ids [T, k] int32, weights [T, k] fp32)."""
+    if not logits.is_cuda:
+        return route_ref(logits, k, mode, norm_topk)
+    T, E = logits.shape
+    ids = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    wts = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    lib = _lib.load()
+    rc = lib.mx_moe_route(logits.contiguous().data_ptr(), ids.data_ptr(), wts.data_ptr(), T, E, k,
+                          0 if mode == "softmax_topk" else 1, 1 if norm_topk else 0, _lib.stream())
+    _lib.count_launch()
+    _lib.check(rc, "mx_moe_route")
+    return ids, wts
+
+
+def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_out: int,
+                   bias: torch.Tensor | None = None, act: str | None = None, alpha: float = 1.702,
+                   limit: float = 7.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Rows [offsets[e], offsets[e+1]) of ``xs`` times expert e's matrix ``w[e]``. With ``act``
+    the expert matrices hold gate rows then up rows and the gated activation is fused."""
+    rows, K = xs.shape
+    E = w.shape[0]
+    if out is None:
+        out = torch.empty(rows, n_out, dtype=torch.bfloat16, device=xs.device)
+    epi = _ACT_TO_EPI[act] if act else (1 if bias is not None else 0)
+    ws = _lib.workspace(xs.device)
+    lib = _lib.load()
+    rc = lib.mx_grouped_gemm_bf16(xs.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias),
+                                  offsets.data_ptr(), E, n_out, K, rows, epi, n_out if act else 0,
+                                  float(alpha), float(limit), ws.data_ptr(), ws.numel(), _lib.stream())
+    _lib.count_launch()
+    _lib.check(rc, "mx_grouped_gemm_bf16")
+    return out
+
+
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up, w_down, inter: int,
+                act: str, b_gate_up=None, b_down=None, e_begin: int = 0, residual=None,
+                alpha: float = 1.702, limit: float = 7.0) -> torch.Tensor:
+    """Weighted sum over the LOCAL experts [e_begin, e_begin + E_local) of their gated MLPs,
+    plus ``residual`` when given. Returns bf16 [T, H]."""
+    T, H = x.shape
+    k = ids.shape[1]
+    El = w_gate_up.shape[0]
+    if not x.is_cuda:
+        o = moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up, b_down, e_begin, alpha, limit)
+        if residual is not None:
+            o = o + residual.float()
+        return o.to(x.dtype)
+    dev = x.device
+    lib = _lib.load()
+    st = _lib.stream()
+    pairs = T * k
+    offsets = torch.empty(El + 1, dtype=torch.int32, device=dev)
+    sorted_pair = torch.empty(pairs, dtype=torch.int32, device=dev)
+    sorted_token = torch.empty(pairs, dtype=torch.int32, device=dev)
+    rc = lib.mx_moe_align(ids.data_ptr(), offsets.data_ptr(), sorted_pair.data_ptr(),
+                          sorted_token.data_ptr(), T, k, 0, e_begin, e_begin + El, st)
+    _lib.check(rc, "mx_moe_align")
+    total = offsets[El:]
+    xs = torch.empty(pairs, H, dtype=x.dtype, device=dev)
+    rc = lib.mx_moe_gather_rows_n(x.data_ptr(), sorted_token.data_ptr(), total.data_ptr(), xs.data_ptr(),
+                                  pairs, H, st)
+    _lib.check(rc, "mx_moe_gather_rows_n")
+    _lib.count_launch(2)
+    a = grouped_linear(xs, w_gate_up, offsets, inter, b_gate_up, act, alpha, limit)
+    y = grouped_linear(a, w_down, offsets, w_down.shape[1], b_down, None)
+    out = torch.empty(T, w_down.shape[1], dtype=x.dtype, device=dev)
+    inv = torch.empty(pairs, dtype=torch.int32, device=dev)
+    rc = lib.mx_moe_combine_n(y.data_ptr(), sorted_pair.data_ptr(), total.data_ptr(), inv.data_ptr(),
+                              wts.data_ptr(), out.data_ptr(), _lib.ptr(residual), T, k,
+                              w_down.shape[1], pairs, 0, st)
+    _lib.count_launch(3)
+    _lib.check(rc, "mx_moe_combine_n")
+    return out
