@@ -188,6 +188,8 @@ class Engine:
 
     # ------------------------------------------------------------------ scheduling
     def _finish(self, s: Sequence, reason: FinishReason) -> None:
+        if s.status == SeqStatus.FINISHED:
+            return
         s.status, s.finish_reason, s.finish_time = SeqStatus.FINISHED, reason, time.perf_counter()
         if self.bm.has_seq(s.seq_id):
             # donate computed full blocks to the prefix cache, then drop our references
@@ -445,6 +447,8 @@ class Engine:
             reason = self._finish_step(s, tok, lps[i] if lps is not None else None)
             if s.on_token is not None and (reason is None or reason == FinishReason.LENGTH):
                 s.on_token(s, tok)
+                if s.status == SeqStatus.FINISHED:
+                    continue  # the callback ended the sequence (stop string)
             if reason is not None:
                 self._finish(s, reason)
                 finished.append(s)

@@ -173,3 +173,234 @@ def _stack(parts):
                                None if q.biases is None else torch.stack([p.biases for p in parts]),
                                q.bits, q.group_size, q.mode)
     return torch.stack(parts)
+
+
+# ----------------------------------------------------------------------------- assembly
+def _first(g: _Getter, *bases):
+    for b in bases:
+        if g.has(b):
+            return b
+    return None
+
+
+def _load_attention(g: _Getter, cfg: ModelConfig, p: str, lw_kwargs: dict) -> None:
+    a = p + ".self_attn"
+    if g.has(a + ".qkv_proj"):                       # Phi-3 style fused projection
+        lw_kwargs["wqkv"] = g.mat(a + ".qkv_proj")
+        lw_kwargs["bqkv"] = g.vec(a + ".qkv_proj.bias")
+    else:
+        lw_kwargs["wqkv"] = _cat_rows([g.mat(a + ".q_proj"), g.mat(a + ".k_proj"), g.mat(a + ".v_proj")])
+        bs = [g.vec(a + f".{n}_proj.bias") for n in "qkv"]
+        lw_kwargs["bqkv"] = torch.cat(bs) if all(b is not None for b in bs) else None
+    lw_kwargs["wo"] = g.mat(a + ".o_proj")
+    lw_kwargs["bo"] = g.vec(a + ".o_proj.bias")
+    lw_kwargs["q_norm"] = g.vec(a + ".q_norm.weight")
+    lw_kwargs["k_norm"] = g.vec(a + ".k_norm.weight")
+    sinks = g.src.get(a + ".sinks").float() if g.src.has(a + ".sinks") else None
+    lw_kwargs["sinks"] = sinks
+
+
+def _load_dense_mlp(g: _Getter, p: str, lw: LayerWeights) -> None:
+    m = p + ".mlp"
+    if g.has(m + ".gate_up_proj"):
+        lw.w_gate_up = g.mat(m + ".gate_up_proj")
+    else:
+        lw.w_gate_up = _cat_rows([g.mat(m + ".gate_proj"), g.mat(m + ".up_proj")])
+        bg, bu = g.vec(m + ".gate_proj.bias"), g.vec(m + ".up_proj.bias")
+        lw.b_gate_up = torch.cat([bg, bu]) if bg is not None and bu is not None else None
+    lw.w_down = g.mat(m + ".down_proj")
+    lw.b_down = g.vec(m + ".down_proj.bias")
+
+
+def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
+    E = cfg.num_experts
+    # router
+    rb = _first(g, p + ".mlp.router", p + ".mlp.gate", p + ".block_sparse_moe.gate")
+    r = g.mat(rb)
+    if isinstance(r, QuantizedTensor):   # routers are small: keep them dense
+        from ..ops.quant import dequantize_ref
+        r = dequantize_ref(r, g.dtype)
+    lw.router_w = r
+    lw.router_b = g.vec(rb + ".bias")
+    # experts: stacked MLX switch layers, GPT-OSS fused tensors, or per-expert HF modules
+    sw = _first(g, p + ".mlp.switch_mlp.gate_proj", p + ".block_sparse_moe.switch_mlp.gate_proj",
+                p + ".mlp.experts.gate_proj")
+    if sw is not None:
+        root = sw[: -len(".gate_proj")]
+        gate, up, down = g.mat(root + ".gate_proj"), g.mat(root + ".up_proj"), g.mat(root + ".down_proj")
+        lw.experts_gate_up = _cat_rows([gate, up])
+        lw.experts_down = down
+        bg, bu, bd = g.vec(root + ".gate_proj.bias"), g.vec(root + ".up_proj.bias"), g.vec(root + ".down_proj.bias")
+        if bg is not None and bu is not None:
+            lw.experts_gate_up_b = torch.cat([bg, bu], dim=-1)
+        lw.experts_down_b = bd
+    elif g.src.has(p + ".mlp.experts.gate_up_proj"):
+        # GPT-OSS HF layout: [E, H, 2I] with gate/up interleaved along the last dim
+        gu = g.src.get(p + ".mlp.experts.gate_up_proj").to(g.dtype)
+        gate, up = gu[..., 0::2], gu[..., 1::2]
+        lw.experts_gate_up = torch.cat([gate, up], dim=-1).transpose(1, 2).contiguous()
+        lw.experts_down = g.src.get(p + ".mlp.experts.down_proj").to(g.dtype).transpose(1, 2).contiguous()
+        if g.src.has(p + ".mlp.experts.gate_up_proj_bias"):
+            b = g.src.get(p + ".mlp.experts.gate_up_proj_bias").to(g.dtype)
+            lw.experts_gate_up_b = torch.cat([b[..., 0::2], b[..., 1::2]], dim=-1).contiguous()
+            lw.experts_down_b = g.src.get(p + ".mlp.experts.down_proj_bias").to(g.dtype)
+    else:
+        names = (("w1", "w3", "w2") if g.has(p + ".block_sparse_moe.experts.0.w1")
+                 else ("gate_proj", "up_proj", "down_proj"))
+        root = p + (".block_sparse_moe.experts" if names[0] == "w1" else ".mlp.experts")
+        gus, downs = [], []
+        for e in range(E):
+            gus.append(_cat_rows([g.mat(f"{root}.{e}.{names[0]}"), g.mat(f"{root}.{e}.{names[1]}")]))
+            downs.append(g.mat(f"{root}.{e}.{names[2]}"))
+        lw.experts_gate_up, lw.experts_down = _stack(gus), _stack(downs)
+    sh = p + ".mlp.shared_expert"
+    if g.has(sh + ".gate_proj"):
+        lw.shared_gate_up = _cat_rows([g.mat(sh + ".gate_proj"), g.mat(sh + ".up_proj")])
+        lw.shared_down = g.mat(sh + ".down_proj")
+        sg = g.mat(p + ".mlp.shared_expert_gate")
+        lw.shared_gate = sg if not isinstance(sg, QuantizedTensor) else None
+
+
+def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, dequantize: bool = False,
+                      layers: range | None = None) -> ModelWeights:
+    """Read a checkpoint directory into host memory in the executor's fused layout."""
+    src = TensorSource(path)
+    g = _Getter(src, cfg, dtype, dequantize)
+    pre = "model." if any(k.startswith("model.") for k in src.keys()) else ""
+    if any(k.startswith("language_model.model.") for k in src.keys()):
+        pre = "language_model.model."
+    emb = g.mat(pre + "embed_tokens")
+    if isinstance(emb, QuantizedTensor):
+        from ..ops.quant import dequantize_ref
+        emb_q, emb = emb, dequantize_ref(emb, dtype)
+    else:
+        emb_q = None
+    lws = []
+    for i in (layers if layers is not None else range(cfg.num_hidden_layers)):
+        p = f"{pre}layers.{i}"
+        kw: dict = {}
+        _load_attention(g, cfg, p, kw)
+        ln1 = g.vec(p + ".input_layernorm.weight")
+        ln2 = g.vec(_first_name(src, p + ".post_attention_layernorm.weight", p + ".pre_feedforward_layernorm.weight"))
+        lw = LayerWeights(ln1=ln1, ln2=ln2, **kw)
+        if cfg.post_norms:
+            lw.post_attn_norm = g.vec(p + ".post_attention_layernorm.weight")
+            lw.ln2 = g.vec(p + ".pre_feedforward_layernorm.weight")
+            lw.post_mlp_norm = g.vec(p + ".post_feedforward_layernorm.weight")
+        if cfg.is_moe and _first(g, p + ".mlp.router", p + ".mlp.gate", p + ".block_sparse_moe.gate"):
+            _load_moe(g, cfg, p, lw)
+        else:
+            _load_dense_mlp(g, p, lw)
+        lws.append(lw)
+    final_norm = g.vec(pre + "norm.weight")
+    head_base = "lm_head" if g.has("lm_head") else ("language_model.lm_head" if g.has("language_model.lm_head") else None)
+    if head_base is not None and not cfg.tie_word_embeddings:
+        lm_head = g.mat(head_base)
+    else:
+        lm_head = emb_q if (emb_q is not None and not dequantize) else emb
+    return ModelWeights(embed=emb, layers=lws, final_norm=final_norm, lm_head=lm_head)
+
+
+def _first_name(src: TensorSource, *names):
+    for n in names:
+        if src.has(n):
+            return n
+    return names[0]
+
+
+def _to_device(w: ModelWeights, device) -> ModelWeights:
+    def mv(x):
+        if isinstance(x, (torch.Tensor, QuantizedTensor)):
+            return x.to(device)
+        return x
+
+    tied = w.lm_head is w.embed
+    w.embed, w.final_norm = mv(w.embed), mv(w.final_norm)
+    w.lm_head = w.embed if tied else mv(w.lm_head)
+    for lw in w.layers:
+        for k, v in list(vars(lw).items()):
+            setattr(lw, k, mv(v))
+    return w
+
+
+def load_model_weights(path: str | Path, cfg: ModelConfig, device="cuda", comm=None, dequantize: bool = False,
+                       layers: range | None = None, dtype=torch.bfloat16) -> ModelWeights:
+    """Load, shard for this rank (tensor / expert parallel, pipeline layer range) and upload."""
+    full = load_full_weights(path, cfg, dtype=dtype, dequantize=dequantize, layers=layers)
+    tp = comm.tp_size if comm is not None else 1
+    if tp > 1:
+        full = shard_weights(cfg, full, comm.tp_rank, tp, ep=getattr(comm, "ep_size", tp))
+    return _to_device(full, device)
+
+
+def save_checkpoint(path: str | Path, cfg_dict: dict, w: ModelWeights, quantization: dict | None = None) -> None:
+    """Write an MLX/HF-style checkpoint directory (used by tests, `split-mtp` and the random-init tool)."""
+    from safetensors.torch import save_file
+
+    out = Path(path)
+    out.mkdir(parents=True, exist_ok=True)
+    cfg = ModelConfig.from_dict(cfg_dict)
+    t: dict[str, torch.Tensor] = {}
+
+    def put(base: str, v):
+        if v is None:
+            return
+        if isinstance(v, QuantizedTensor):
+            t[base + ".weight"] = v.packed.contiguous().cpu()
+            t[base + ".scales"] = v.scales.contiguous().cpu()
+            if v.biases is not None:
+                t[base + ".biases"] = v.biases.contiguous().cpu()
+        else:
+            t[base + ".weight"] = v.contiguous().cpu()
+
+    def rows(v, lo, hi):
+        from .shard import _rows
+        return _rows(v, lo, hi)
+
+    D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    put("model.embed_tokens", w.embed)
+    t["model.norm.weight"] = w.final_norm.cpu()
+    if not cfg.tie_word_embeddings:
+        put("lm_head", w.lm_head)
+    for i, lw in enumerate(w.layers):
+        p = f"model.layers.{i}"
+        t[p + ".input_layernorm.weight"] = lw.ln1.cpu()
+        t[p + ".post_attention_layernorm.weight"] = lw.ln2.cpu()
+        q1, k1 = Hq * D, (Hq + Hkv) * D
+        put(p + ".self_attn.q_proj", rows(lw.wqkv, 0, q1))
+        put(p + ".self_attn.k_proj", rows(lw.wqkv, q1, k1))
+        put(p + ".self_attn.v_proj", rows(lw.wqkv, k1, k1 + Hkv * D))
+        put(p + ".self_attn.o_proj", lw.wo)
+        if lw.bqkv is not None:
+            t[p + ".self_attn.q_proj.bias"] = lw.bqkv[:q1].cpu()
+            t[p + ".self_attn.k_proj.bias"] = lw.bqkv[q1:k1].cpu()
+            t[p + ".self_attn.v_proj.bias"] = lw.bqkv[k1:].cpu()
+        if lw.bo is not None:
+            t[p + ".self_attn.o_proj.bias"] = lw.bo.cpu()
+        if lw.q_norm is not None:
+            t[p + ".self_attn.q_norm.weight"] = lw.q_norm.cpu()
+            t[p + ".self_attn.k_norm.weight"] = lw.k_norm.cpu()
+        if lw.sinks is not None:
+            t[p + ".self_attn.sinks"] = lw.sinks.cpu()
+        if lw.w_gate_up is not None:
+            I = cfg.intermediate_size
+            put(p + ".mlp.gate_proj", rows(lw.w_gate_up, 0, I))
+            put(p + ".mlp.up_proj", rows(lw.w_gate_up, I, 2 * I))
+            put(p + ".mlp.down_proj", lw.w_down)
+        if lw.router_w is not None:
+            mi = cfg.moe_intermediate_size
+            put(p + ".mlp.router", lw.router_w)
+            if lw.router_b is not None:
+                t[p + ".mlp.router.bias"] = lw.router_b.cpu()
+            put(p + ".mlp.switch_mlp.gate_proj", rows(lw.experts_gate_up, 0, mi))
+            put(p + ".mlp.switch_mlp.up_proj", rows(lw.experts_gate_up, mi, 2 * mi))
+            put(p + ".mlp.switch_mlp.down_proj", lw.experts_down)
+            if lw.experts_gate_up_b is not None:
+                t[p + ".mlp.switch_mlp.gate_proj.bias"] = lw.experts_gate_up_b[:, :mi].contiguous().cpu()
+                t[p + ".mlp.switch_mlp.up_proj.bias"] = lw.experts_gate_up_b[:, mi:].contiguous().cpu()
+                t[p + ".mlp.switch_mlp.down_proj.bias"] = lw.experts_down_b.cpu()
+    save_file(t, str(out / "model.safetensors"))
+    cd = dict(cfg_dict)
+    if quantization:
+        cd["quantization"] = quantization
+    (out / "config.json").write_text(json.dumps(cd, indent=1))

@@ -62,12 +62,15 @@ class TPComm:
     def row_parallel_linear(self, x, w, bias, residual):
         """``residual + all_reduce(x_shard @ w_shard^T) + bias`` with replicated output."""
         self.calls += 1
+        from ..models.decoder import _linear_any
+        from ..models.weights import QuantizedTensor
+
         if self.tp_size == 1:
-            return ops.linear(x, w, bias=bias, residual=residual, out=residual)
-        if self.backend == "fused" and not isinstance(w, tuple):
+            return _linear_any(x, w, bias=bias, residual=residual, out=residual)
+        if self.backend == "fused" and not isinstance(w, QuantizedTensor):
             return self.fused.gemm_allreduce(x, w, bias, residual)
         first = self.tp_rank == 0
-        y = ops.linear(x, w, bias=bias if first else None, residual=residual if first else None)
+        y = _linear_any(x, w, bias=bias if first else None, residual=residual if first else None)
         dist.all_reduce(y, group=self.group)
         return y
 

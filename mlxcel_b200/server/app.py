@@ -1,0 +1,503 @@
+"""FastAPI application: OpenAI, Anthropic and llama-server compatible routes.
+
+Route inventory follows the reference's (src/server/app.rs:275-560): ``/v1/chat/completions``,
+``/v1/completions``, ``/v1/responses``, ``/v1/messages`` (+ ``/count_tokens``), ``/v1/embeddings``,
+``/v1/models``, native ``/completion``, ``/tokenize``, ``/detokenize``, ``/apply-template``,
+``/infill``, ``/props``, ``/slots``, ``/metrics``, ``/health``, ``/v1/cache/{stats,reset}``,
+``/lora-adapters``. Streaming uses server-sent events.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import time
+import uuid
+
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from ..engine import SamplingParams
+from .chat_template import TemplateRenderError, render_chat
+from .structured import constraint_from_request
+from .tool_calls import ToolCallStreamFilter, parse_tool_calls, split_reasoning
+from .worker import GenRequest, ModelWorker
+
+
+def _err(status: int, message: str, etype: str = "invalid_request_error"):
+    return JSONResponse(status_code=status, content={"error": {"message": message, "type": etype, "code": status}})
+
+
+def sampling_from_body(b: dict, default_max: int = 512) -> SamplingParams:
+    g = b.get
+    stop = g("stop") or []
+    if isinstance(stop, str):
+        stop = [stop]
+    mt = g("max_completion_tokens", g("max_tokens", g("n_predict", default_max)))
+    if mt is None or int(mt) < 0:
+        mt = default_max
+    lb = g("logit_bias") or {}
+    if isinstance(lb, list):   # llama-server form [[id, bias], ...]
+        lb = {int(k): (float("-inf") if v is False else float(v)) for k, v in lb}
+    else:
+        lb = {int(k): float(v) for k, v in lb.items()}
+    return SamplingParams(
+        max_tokens=int(mt), temperature=float(g("temperature", 0.8) if g("temperature") is not None else 0.8),
+        top_k=int(g("top_k", 0) or 0), top_p=float(g("top_p", 1.0) if g("top_p") is not None else 1.0),
+        min_p=float(g("min_p", 0.0) or 0.0), typical_p=float(g("typical_p", g("typ_p", 1.0)) or 1.0),
+        top_n_sigma=float(g("top_n_sigma", 0.0) or 0.0),
+        repetition_penalty=float(g("repetition_penalty", g("repeat_penalty", 1.0)) or 1.0),
+        repetition_context_size=int(g("repetition_context_size", g("repeat_last_n", 64)) or 64),
+        frequency_penalty=float(g("frequency_penalty", 0.0) or 0.0),
+        presence_penalty=float(g("presence_penalty", 0.0) or 0.0),
+        dry_multiplier=float(g("dry_multiplier", 0.0) or 0.0), dry_base=float(g("dry_base", 1.75) or 1.75),
+        dry_allowed_length=int(g("dry_allowed_length", 2) or 2),
+        xtc_probability=float(g("xtc_probability", 0.0) or 0.0), xtc_threshold=float(g("xtc_threshold", 0.1) or 0.1),
+        mirostat=int(g("mirostat", 0) or 0), mirostat_tau=float(g("mirostat_tau", 5.0) or 5.0),
+        mirostat_eta=float(g("mirostat_eta", 0.1) or 0.1), dynatemp_range=float(g("dynatemp_range", 0.0) or 0.0),
+        dynatemp_exponent=float(g("dynatemp_exponent", 1.0) or 1.0),
+        seed=(int(g("seed")) if g("seed") is not None and int(g("seed")) >= 0 else None), stop=list(stop),
+        ignore_eos=bool(g("ignore_eos", False)), logprobs=bool(g("logprobs", False)) or bool(g("n_probs", 0)),
+        top_logprobs=int(g("top_logprobs", 0) or 0), logit_bias=lb, min_tokens=int(g("min_tokens", 0) or 0),
+        loop_max_pattern=int(g("max_pattern_size", 0) or 0), loop_min_pattern=int(g("min_pattern_size", 4) or 4),
+        loop_min_count=int(g("min_count", 8) or 8),
+        thinking_budget=g("thinking_budget_tokens", g("thinking_token_budget", g("thinking_budget"))),
+    )
+
+
+class ServerState:
+    def __init__(self, worker: ModelWorker, tokenizer, model_id: str, api_keys: set[str] | None = None,
+                 chat_template: str | None = None):
+        self.worker, self.tokenizer, self.model_id = worker, tokenizer, model_id
+        self.api_keys = api_keys or set()
+        self.chat_template = chat_template or getattr(tokenizer, "chat_template", None)
+        self.started = time.time()
+        self.responses: dict[str, dict] = {}
+
+    def render(self, messages, tools=None, **kw) -> str:
+        return render_chat(messages, self.chat_template, tools=tools,
+                           bos_token=getattr(self.tokenizer, "bos_token", "") or "",
+                           eos_token=getattr(self.tokenizer, "eos_token", "") or "", **kw)
+
+    def eos_params(self, sp: SamplingParams) -> SamplingParams:
+        ids = [i for i in self.tokenizer.eos_ids() if i is not None]
+        sp.stop_token_ids = sorted(set(sp.stop_token_ids) | set(ids))
+        return sp
+
+
+async def _generate(state: ServerState, prompt_ids, sp, constraint=None):
+    """Async generator of GenEvents for one request."""
+    q: asyncio.Queue = asyncio.Queue()
+    req = GenRequest(prompt_ids=prompt_ids, params=state.eos_params(sp), loop=asyncio.get_running_loop(), out=q,
+                     constraint=constraint, request_id=uuid.uuid4().hex)
+    state.worker.submit(req)
+    try:
+        while True:
+            ev = await q.get()
+            yield ev
+            if ev.kind in ("done", "error"):
+                return
+    finally:
+        if req.seq_id is not None and req.seq_id in state.worker.by_seq:
+            state.worker.cancel(req)
+
+
+def _sse(obj) -> bytes:
+    return f"data: {json.dumps(obj, ensure_ascii=False)}\n\n".encode()
+
+
+def _finish_openai(reason: str, has_tools: bool) -> str:
+    if has_tools:
+        return "tool_calls"
+    return {"stop": "stop", "stop_sequence": "stop", "length": "length", "repetition_loop": "stop",
+            "cancelled": "stop"}.get(reason, "stop")
+
+
+def create_app(state: ServerState) -> FastAPI:
+    app = FastAPI(title="mlxcel_b200", version="0.1.0")
+    tk = state.tokenizer
+
+    @app.middleware("http")
+    async def auth(request: Request, call_next):
+        if state.api_keys and request.url.path not in ("/health", "/metrics"):
+            key = request.headers.get("authorization", "").removeprefix("Bearer ").strip() or \
+                request.headers.get("x-api-key", "")
+            if key not in state.api_keys:
+                return _err(401, "invalid API key", "authentication_error")
+        resp = await call_next(request)
+        resp.headers.setdefault("Access-Control-Allow-Origin", "*")
+        return resp
+
+    # ------------------------------------------------------------------ basic
+    @app.get("/health")
+    async def health():
+        if not state.worker.healthy:
+            return JSONResponse(status_code=503, content={"status": "error"})
+        return {"status": "ok"}
+
+    @app.get("/v1/models")
+    @app.get("/models")
+    async def models():
+        return {"object": "list", "data": [{"id": state.model_id, "object": "model", "created": int(state.started),
+                                            "owned_by": "mlxcel_b200"}]}
+
+    @app.get("/props")
+    async def props():
+        e = state.worker.engine
+        return {"model_path": state.model_id, "total_slots": e.ecfg.max_batch, "chat_template": state.chat_template or "",
+                "default_generation_settings": {"n_ctx": e.ecfg.max_model_len, "params": {}},
+                "build_info": "mlxcel_b200 0.1.0", "bos_token": getattr(tk, "bos_token", None),
+                "eos_token": getattr(tk, "eos_token", None)}
+
+    @app.get("/slots")
+    async def slots():
+        return state.worker.slots()
+
+    @app.get("/metrics")
+    async def metrics():
+        from .metrics import render_metrics
+        return PlainTextResponse(render_metrics(state))
+
+    @app.get("/v1/cache/stats")
+    async def cache_stats():
+        return dict(state.worker.engine.bm.stats())
+
+    @app.post("/v1/cache/reset")
+    async def cache_reset():
+        return {"dropped_blocks": state.worker.engine.bm.reset_prefix_cache()}
+
+    @app.get("/lora-adapters")
+    async def lora_adapters():
+        return []
+
+    @app.post("/tokenize")
+    async def tokenize(body: dict):
+        ids = tk.encode(body.get("content", ""), add_special_tokens=bool(body.get("add_special", False)))
+        if body.get("with_pieces"):
+            return {"tokens": [{"id": i, "piece": tk.decode([i], skip_special_tokens=False)} for i in ids]}
+        return {"tokens": ids}
+
+    @app.post("/detokenize")
+    async def detokenize(body: dict):
+        return {"content": tk.decode(body.get("tokens", []))}
+
+    @app.post("/apply-template")
+    async def apply_template(body: dict):
+        try:
+            return {"prompt": state.render(body.get("messages", []), **(body.get("chat_template_kwargs") or {}))}
+        except TemplateRenderError as e:
+            return _err(400, str(e))
+
+    @app.post("/v1/messages/count_tokens")
+    async def count_tokens(body: dict):
+        msgs = _anthropic_messages(body)
+        return {"input_tokens": len(tk.encode(state.render(msgs)))}
+
+    # ------------------------------------------------------------------ completions
+    async def _run_text(prompt_ids, sp, constraint=None):
+        text, lps, toks, final = [], [], [], None
+        async for ev in _generate(state, prompt_ids, sp, constraint):
+            if ev.kind == "token":
+                text.append(ev.text)
+                toks.append(ev.token_id)
+                if ev.logprob is not None:
+                    lps.append(ev.logprob)
+            elif ev.kind == "done":
+                text.append(ev.text)
+                final = ev
+            elif ev.kind == "error":
+                raise RuntimeError(ev.error)
+        return "".join(text), toks, lps, final
+
+    def _prompt_ids(prompt) -> list[int]:
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+            return prompt
+        if isinstance(prompt, list):
+            prompt = prompt[0] if prompt else ""
+        ids = tk.encode(prompt, add_special_tokens=True)
+        return ids or [getattr(tk, "bos_token_id", 0) or 0]
+
+    @app.post("/v1/completions")
+    async def completions(body: dict):
+        sp = sampling_from_body(body, 16)
+        ids = _prompt_ids(body.get("prompt", ""))
+        cid, created = "cmpl-" + uuid.uuid4().hex[:24], int(time.time())
+        if body.get("stream"):
+            async def gen():
+                async for ev in _generate(state, ids, sp):
+                    if ev.kind == "token" and ev.text:
+                        yield _sse({"id": cid, "object": "text_completion", "created": created, "model": state.model_id,
+                                    "choices": [{"index": 0, "text": ev.text, "finish_reason": None}]})
+                    elif ev.kind == "done":
+                        yield _sse({"id": cid, "object": "text_completion", "created": created, "model": state.model_id,
+                                    "choices": [{"index": 0, "text": ev.text,
+                                                 "finish_reason": _finish_openai(ev.finish_reason, False)}],
+                                    "usage": ev.usage})
+                    elif ev.kind == "error":
+                        yield _sse({"error": {"message": ev.error}})
+                yield b"data: [DONE]\n\n"
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        try:
+            text, toks, lps, fin = await _run_text(ids, sp)
+        except (RuntimeError, ValueError) as e:
+            return _err(400, str(e))
+        choice = {"index": 0, "text": text, "finish_reason": _finish_openai(fin.finish_reason, False)}
+        if sp.logprobs:
+            choice["logprobs"] = {"token_logprobs": lps, "tokens": [tk.decode([t]) for t in toks]}
+        return {"id": cid, "object": "text_completion", "created": created, "model": state.model_id,
+                "choices": [choice], "usage": fin.usage, "timings": fin.timings}
+
+    @app.post("/completion")
+    @app.post("/completions")
+    async def native_completion(body: dict):
+        sp = sampling_from_body(body, 512)
+        ids = _prompt_ids(body.get("prompt", ""))
+        try:
+            constraint = constraint_from_request(tk, grammar=body.get("grammar"), json_schema=body.get("json_schema"))
+        except Exception as e:
+            return _err(400, f"grammar: {e}")
+        if body.get("stream"):
+            async def gen():
+                async for ev in _generate(state, ids, sp, constraint):
+                    if ev.kind == "token":
+                        yield _sse({"content": ev.text, "tokens": [ev.token_id], "stop": False})
+                    elif ev.kind == "done":
+                        yield _sse({"content": ev.text, "stop": True, "stop_type": _stop_type(ev.finish_reason),
+                                    "tokens_predicted": ev.usage["completion_tokens"],
+                                    "tokens_evaluated": ev.usage["prompt_tokens"], "timings": ev.timings})
+                    elif ev.kind == "error":
+                        yield _sse({"error": {"message": ev.error}})
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        try:
+            text, toks, lps, fin = await _run_text(ids, sp, constraint)
+        except (RuntimeError, ValueError) as e:
+            return _err(400, str(e))
+        return {"content": text, "tokens": toks, "id_slot": 0, "stop": True, "model": state.model_id,
+                "stop_type": _stop_type(fin.finish_reason), "stopping_word": "",
+                "tokens_predicted": fin.usage["completion_tokens"], "tokens_evaluated": fin.usage["prompt_tokens"],
+                "tokens_cached": fin.timings["cache_n"], "truncated": False, "timings": fin.timings,
+                "generation_settings": {"n_predict": sp.max_tokens, "temperature": sp.temperature, "top_k": sp.top_k,
+                                        "top_p": sp.top_p, "min_p": sp.min_p, "seed": sp.seed}}
+
+    @app.post("/infill")
+    async def infill(body: dict):
+        fim = getattr(tk, "fim", {}) or {}
+        if not all(fim.get(k) is not None for k in ("prefix", "suffix", "middle")):
+            return _err(501, "this model's tokenizer has no fill-in-the-middle tokens", "not_supported")
+        ids = [fim["prefix"]] + tk.encode(body.get("input_prefix", "")) + [fim["suffix"]] + \
+            tk.encode(body.get("input_suffix", "")) + [fim["middle"]]
+        text, toks, lps, fin = await _run_text(ids, sampling_from_body(body, 128))
+        return {"content": text, "tokens_predicted": fin.usage["completion_tokens"], "timings": fin.timings}
+
+    # ------------------------------------------------------------------ chat completions
+    def _chat_prompt(body: dict):
+        tools = body.get("tools")
+        kwargs = dict(body.get("chat_template_kwargs") or {})
+        if body.get("reasoning_effort"):
+            kwargs.setdefault("reasoning_effort", body["reasoning_effort"])
+        text = state.render(body.get("messages", []), tools=tools, **kwargs)
+        ids = tk.encode(text, add_special_tokens=False)
+        return ids or [getattr(tk, "bos_token_id", 0) or 0], tools
+
+    @app.post("/v1/chat/completions")
+    @app.post("/chat/completions")
+    async def chat_completions(body: dict):
+        try:
+            ids, tools = _chat_prompt(body)
+        except TemplateRenderError as e:
+            return _err(400, str(e))
+        sp = sampling_from_body(body, 512)
+        try:
+            constraint = constraint_from_request(tk, response_format=body.get("response_format"),
+                                                 grammar=body.get("grammar"))
+        except Exception as e:
+            return _err(400, f"response_format: {e}")
+        allowed = {t["function"]["name"] for t in tools or [] if t.get("type") == "function"} or None
+        use_tools = bool(tools) and body.get("tool_choice") != "none"
+        cid, created = "chatcmpl-" + uuid.uuid4().hex[:24], int(time.time())
+        base = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": state.model_id}
+        if body.get("stream"):
+            include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
+
+            async def gen():
+                filt = ToolCallStreamFilter(allowed) if use_tools else None
+                n_calls = 0
+                yield _sse({**base, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""},
+                                                 "finish_reason": None}]})
+                async for ev in _generate(state, ids, sp, constraint):
+                    if ev.kind in ("token", "done"):
+                        text, calls = (filt.feed(ev.text) if filt else (ev.text, []))
+                        if ev.kind == "done" and filt:
+                            t2, c2 = filt.flush()
+                            text, calls = text + t2, calls + c2
+                        if text:
+                            yield _sse({**base, "choices": [{"index": 0, "delta": {"content": text},
+                                                             "finish_reason": None}]})
+                        for c in calls:
+                            yield _sse({**base, "choices": [{"index": 0, "delta": {"tool_calls": [c.to_openai(n_calls)]},
+                                                             "finish_reason": None}]})
+                            n_calls += 1
+                        if ev.kind == "done":
+                            yield _sse({**base, "choices": [{"index": 0, "delta": {},
+                                                             "finish_reason": _finish_openai(ev.finish_reason, n_calls > 0)}],
+                                        "timings": ev.timings})
+                            if include_usage:
+                                yield _sse({**base, "choices": [], "usage": ev.usage})
+                    elif ev.kind == "error":
+                        yield _sse({"error": {"message": ev.error, "type": "server_error"}})
+                yield b"data: [DONE]\n\n"
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        try:
+            text, toks, lps, fin = await _run_text(ids, sp, constraint)
+        except (RuntimeError, ValueError) as e:
+            return _err(400, str(e))
+        reasoning, answer = split_reasoning(text)
+        calls = []
+        if use_tools:
+            answer, calls = parse_tool_calls(answer, allowed)
+        msg = {"role": "assistant", "content": answer if (answer or not calls) else None}
+        if reasoning:
+            msg["reasoning_content"] = reasoning
+        if calls:
+            msg["tool_calls"] = [c.to_openai() for c in calls]
+        choice = {"index": 0, "message": msg, "finish_reason": _finish_openai(fin.finish_reason, bool(calls))}
+        if sp.logprobs:
+            choice["logprobs"] = {"content": [{"token": tk.decode([t]), "logprob": lp} for t, lp in zip(toks, lps)]}
+        return {"id": cid, "object": "chat.completion", "created": created, "model": state.model_id,
+                "choices": [choice], "usage": fin.usage, "timings": fin.timings}
+
+    # ------------------------------------------------------------------ responses API
+    def _responses_messages(body: dict) -> list[dict]:
+        msgs = []
+        if body.get("instructions"):
+            msgs.append({"role": "system", "content": body["instructions"]})
+        prev = body.get("previous_response_id")
+        if prev and prev in state.responses:
+            msgs += state.responses[prev]["_messages"]
+        inp = body.get("input", "")
+        if isinstance(inp, str):
+            msgs.append({"role": "user", "content": inp})
+        else:
+            for item in inp:
+                c = item.get("content", "")
+                if isinstance(c, list):
+                    c = "".join(p.get("text", "") for p in c if isinstance(p, dict))
+                msgs.append({"role": item.get("role", "user"), "content": c})
+        return msgs
+
+    @app.post("/v1/responses")
+    async def responses(body: dict):
+        msgs = _responses_messages(body)
+        try:
+            ids = tk.encode(state.render(msgs), add_special_tokens=False)
+        except TemplateRenderError as e:
+            return _err(400, str(e))
+        b2 = dict(body)
+        b2["max_tokens"] = body.get("max_output_tokens", 512)
+        sp = sampling_from_body(b2, 512)
+        rid = "resp_" + uuid.uuid4().hex[:24]
+        try:
+            text, toks, lps, fin = await _run_text(ids or [0], sp)
+        except (RuntimeError, ValueError) as e:
+            return _err(400, str(e))
+        reasoning, answer = split_reasoning(text)
+        out = {"id": rid, "object": "response", "created_at": int(time.time()), "status": "completed",
+               "model": state.model_id,
+               "output": [{"type": "message", "id": "msg_" + uuid.uuid4().hex[:24], "role": "assistant",
+                           "status": "completed",
+                           "content": [{"type": "output_text", "text": answer, "annotations": []}]}],
+               "output_text": answer,
+               "usage": {"input_tokens": fin.usage["prompt_tokens"], "output_tokens": fin.usage["completion_tokens"],
+                         "total_tokens": fin.usage["total_tokens"]}}
+        if body.get("store", True):
+            state.responses[rid] = {**out, "_messages": msgs + [{"role": "assistant", "content": answer}]}
+            while len(state.responses) > 256:
+                state.responses.pop(next(iter(state.responses)))
+        return out
+
+    @app.get("/v1/responses/{rid}")
+    async def get_response(rid: str):
+        r = state.responses.get(rid)
+        if r is None:
+            return _err(404, "response not found", "not_found_error")
+        return {k: v for k, v in r.items() if not k.startswith("_")}
+
+    @app.post("/v1/responses/input_tokens")
+    async def responses_input_tokens(body: dict):
+        return {"input_tokens": len(tk.encode(state.render(_responses_messages(body))))}
+
+    # ------------------------------------------------------------------ anthropic messages
+    @app.post("/v1/messages")
+    async def messages(body: dict):
+        msgs = _anthropic_messages(body)
+        try:
+            ids = tk.encode(state.render(msgs), add_special_tokens=False)
+        except TemplateRenderError as e:
+            return _err(400, str(e))
+        b2 = dict(body)
+        b2["stop"] = body.get("stop_sequences") or []
+        sp = sampling_from_body(b2, 1024)
+        mid = "msg_" + uuid.uuid4().hex[:24]
+        if body.get("stream"):
+            async def gen():
+                def ev(name, data):
+                    return f"event: {name}\ndata: {json.dumps(data)}\n\n".encode()
+                yield ev("message_start", {"type": "message_start", "message": {
+                    "id": mid, "type": "message", "role": "assistant", "model": state.model_id, "content": [],
+                    "usage": {"input_tokens": len(ids), "output_tokens": 0}}})
+                yield ev("content_block_start", {"type": "content_block_start", "index": 0,
+                                                 "content_block": {"type": "text", "text": ""}})
+                async for e in _generate(state, ids or [0], sp):
+                    if e.kind in ("token", "done") and e.text:
+                        yield ev("content_block_delta", {"type": "content_block_delta", "index": 0,
+                                                         "delta": {"type": "text_delta", "text": e.text}})
+                    if e.kind == "done":
+                        yield ev("content_block_stop", {"type": "content_block_stop", "index": 0})
+                        yield ev("message_delta", {"type": "message_delta",
+                                                   "delta": {"stop_reason": _anthropic_stop(e.finish_reason)},
+                                                   "usage": {"output_tokens": e.usage["completion_tokens"]}})
+                        yield ev("message_stop", {"type": "message_stop"})
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        try:
+            text, toks, lps, fin = await _run_text(ids or [0], sp)
+        except (RuntimeError, ValueError) as e:
+            return _err(400, str(e))
+        return {"id": mid, "type": "message", "role": "assistant", "model": state.model_id,
+                "content": [{"type": "text", "text": text}], "stop_reason": _anthropic_stop(fin.finish_reason),
+                "usage": {"input_tokens": fin.usage["prompt_tokens"], "output_tokens": fin.usage["completion_tokens"]}}
+
+    # ------------------------------------------------------------------ embeddings
+    @app.post("/v1/embeddings")
+    @app.post("/embeddings")
+    async def embeddings(body: dict):
+        from .embeddings import embed_texts
+        inp = body.get("input", body.get("content", ""))
+        texts = [inp] if isinstance(inp, str) else list(inp)
+        vecs, ntok = await asyncio.get_running_loop().run_in_executor(None, embed_texts, state, texts)
+        return {"object": "list", "model": state.model_id,
+                "data": [{"object": "embedding", "index": i, "embedding": v} for i, v in enumerate(vecs)],
+                "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}
+
+    return app
+
+
+def _stop_type(reason: str) -> str:
+    return {"stop": "eos", "stop_sequence": "word", "length": "limit"}.get(reason, "none")
+
+
+def _anthropic_stop(reason: str) -> str:
+    return {"stop": "end_turn", "stop_sequence": "stop_sequence", "length": "max_tokens"}.get(reason, "end_turn")
+
+
+def _anthropic_messages(body: dict) -> list[dict]:
+    msgs = []
+    sysm = body.get("system")
+    if isinstance(sysm, list):
+        sysm = "".join(p.get("text", "") for p in sysm)
+    if sysm:
+        msgs.append({"role": "system", "content": sysm})
+    for m in body.get("messages", []):
+        c = m.get("content", "")
+        if isinstance(c, list):
+            c = "".join(p.get("text", "") for p in c if isinstance(p, dict) and p.get("type") == "text")
+        msgs.append({"role": m.get("role", "user"), "content": c})
+    return msgs
