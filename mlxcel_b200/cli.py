@@ -1,0 +1,261 @@
+"""``mlxcel`` command line (python -m mlxcel_b200.cli ...).
+
+Subcommands follow the reference's CLI (src/main.rs:97-378): ``generate``, ``run`` (chat REPL),
+``serve``, ``inspect`` (memory estimate), ``arch``, ``list``, ``tokenize``, ``embed``, ``bench``,
+``tune``, ``random-init`` (writes a random checkpoint of a preset architecture) and ``split-mtp``.
+Flag names keep llama-server compatibility where one exists (``-m``, ``-c``, ``-n``, ``--parallel``,
+``--temp``, ``--top-k``, ``--top-p``, ``--min-p``, ``--seed``, ``--host``, ``--port``, ``--api-key``,
+``--kv-bits``, ``--prefill-chunk-size``, ``--tp``, ``--pp``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+
+def _add_model_args(p):
+    p.add_argument("-m", "--model", required=True, help="checkpoint directory or preset:<name>")
+    p.add_argument("--device", default=None)
+    p.add_argument("-c", "--ctx-size", type=int, default=8192)
+    p.add_argument("--parallel", "-np", type=int, default=4, help="concurrent sequences (slots)")
+    p.add_argument("--max-batch-tokens", type=int, default=8192)
+    p.add_argument("--prefill-chunk-size", type=int, default=2048)
+    p.add_argument("--kv-bits", type=int, default=0, choices=[0, 8, 16])
+    p.add_argument("--kv-cache-blocks", type=int, default=0)
+    p.add_argument("--block-size", type=int, default=16)
+    p.add_argument("--no-prompt-cache", action="store_true")
+    p.add_argument("--no-cuda-graphs", action="store_true")
+    p.add_argument("--dequantize", action="store_true", help="dequantize quantized checkpoints at load")
+    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--pp", type=int, default=1)
+    p.add_argument("--draft-model", default=None)
+    p.add_argument("--draft-max", type=int, default=4)
+    p.add_argument("--prompt-lookup", action="store_true")
+
+
+def _add_sampling_args(p):
+    p.add_argument("-n", "--n-predict", "--max-tokens", dest="max_tokens", type=int, default=256)
+    p.add_argument("--temp", "--temperature", dest="temperature", type=float, default=0.0)
+    p.add_argument("--top-k", type=int, default=0)
+    p.add_argument("--top-p", type=float, default=1.0)
+    p.add_argument("--min-p", type=float, default=0.0)
+    p.add_argument("--typical-p", type=float, default=1.0)
+    p.add_argument("--repeat-penalty", type=float, default=1.0)
+    p.add_argument("--repeat-last-n", type=int, default=64)
+    p.add_argument("--presence-penalty", type=float, default=0.0)
+    p.add_argument("--frequency-penalty", type=float, default=0.0)
+    p.add_argument("--seed", type=int, default=None)
+    p.add_argument("--ignore-eos", action="store_true")
+
+
+def _sampling(a):
+    from .engine import SamplingParams
+    return SamplingParams(max_tokens=a.max_tokens, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
+                          min_p=a.min_p, typical_p=a.typical_p, repetition_penalty=a.repeat_penalty,
+                          repetition_context_size=a.repeat_last_n, presence_penalty=a.presence_penalty,
+                          frequency_penalty=a.frequency_penalty, seed=a.seed, ignore_eos=a.ignore_eos)
+
+
+def load_llm(a):
+    import torch
+
+    from .engine import EngineConfig
+    from .llm import LLM
+
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    ecfg = EngineConfig(max_batch=a.parallel, max_num_batched_tokens=a.max_batch_tokens,
+                        prefill_chunk_alone=a.prefill_chunk_size, prefill_chunk_contended=min(512, a.prefill_chunk_size),
+                        block_size=a.block_size, kv_bits=a.kv_bits or 16, num_blocks=a.kv_cache_blocks,
+                        prefix_cache=not a.no_prompt_cache, max_model_len=a.ctx_size,
+                        cuda_graphs=not a.no_cuda_graphs and dev != "cpu")
+    comm = None
+    if a.tp > 1:
+        import torch.distributed as dist
+
+        if not dist.is_initialized():
+            raise SystemExit("--tp N needs a launch with torch.distributed.run --nproc-per-node N")
+        from .parallel.tp import TPComm
+        comm = TPComm(dist.group.WORLD, torch.device(dev), backend="fused")
+    if a.model.startswith("preset:"):
+        dtype = torch.bfloat16 if dev != "cpu" else torch.float32
+        llm = LLM.from_preset(a.model.split(":", 1)[1], device=dev, engine_config=ecfg, comm=comm, dtype=dtype)
+        from .tokenizer import ByteTokenizer
+        llm.tokenizer = ByteTokenizer(llm.cfg.vocab_size)
+        return llm
+    return LLM.from_pretrained(a.model, device=dev, engine_config=ecfg, comm=comm, dequantize=a.dequantize)
+
+
+def cmd_generate(a):
+    llm = load_llm(a)
+    tk = llm.tokenizer
+    prompt = a.prompt if a.prompt is not None else sys.stdin.read()
+    if a.chat:
+        from .server.chat_template import render_chat
+        prompt = render_chat([{"role": "user", "content": prompt}], getattr(tk, "chat_template", None))
+    ids = tk.encode(prompt, add_special_tokens=not a.chat)
+    sp = _sampling(a)
+    sp.stop_token_ids = [i for i in tk.eos_ids() if i is not None]
+    from .tokenizer import IncrementalDetokenizer
+    det = IncrementalDetokenizer(tk, ids)
+    t0 = time.perf_counter()
+
+    def on_token(seq, tok):
+        sys.stdout.write(det.push(tok))
+        sys.stdout.flush()
+
+    sid = llm.engine.add_request(ids, sp, on_token=on_token)
+    while llm.engine.has_work():
+        llm.engine.step()
+    s = llm.engine.seqs[sid]
+    sys.stdout.write(det.flush() + "\n")
+    dt = time.perf_counter() - t0
+    ttft = (s.first_token_time - s.arrival) if s.first_token_time else 0.0
+    n = len(s.output)
+    print(f"[prompt {len(ids)} tok, {len(ids) / max(ttft, 1e-9):.1f} tok/s | generated {n} tok, "
+          f"{max(n - 1, 0) / max(dt - ttft, 1e-9):.1f} tok/s | finish: {s.finish_reason.value}]", file=sys.stderr)
+
+
+def cmd_run(a):
+    llm = load_llm(a)
+    tk = llm.tokenizer
+    from .server.chat_template import render_chat
+    from .tokenizer import IncrementalDetokenizer
+    msgs = [{"role": "system", "content": a.system}] if a.system else []
+    print("chat REPL — empty line or /exit to quit", file=sys.stderr)
+    while True:
+        try:
+            line = input("> ")
+        except EOFError:
+            break
+        if not line.strip() or line.strip() == "/exit":
+            break
+        msgs.append({"role": "user", "content": line})
+        ids = tk.encode(render_chat(msgs, getattr(tk, "chat_template", None)))
+        sp = _sampling(a)
+        sp.stop_token_ids = [i for i in tk.eos_ids() if i is not None]
+        det = IncrementalDetokenizer(tk, ids)
+        parts = []
+
+        def on_token(seq, tok):
+            t = det.push(tok)
+            parts.append(t)
+            sys.stdout.write(t)
+            sys.stdout.flush()
+
+        llm.engine.add_request(ids, sp, on_token=on_token)
+        while llm.engine.has_work():
+            llm.engine.step()
+        print()
+        msgs.append({"role": "assistant", "content": "".join(parts)})
+
+
+def cmd_serve(a):
+    import uvicorn
+
+    from .server.app import ServerState, create_app
+    from .server.worker import ModelWorker
+    llm = load_llm(a)
+    worker = ModelWorker(llm.engine, llm.tokenizer, a.alias or os.path.basename(a.model.rstrip("/")))
+    keys = set(a.api_key or [])
+    if a.api_key_file:
+        keys |= {l.strip() for l in open(a.api_key_file) if l.strip()}
+    state = ServerState(worker, llm.tokenizer, worker.model_id, api_keys=keys,
+                        chat_template=open(a.chat_template_file).read() if a.chat_template_file else None)
+    uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="info" if a.verbose else "warning",
+                ssl_certfile=a.ssl_cert_file, ssl_keyfile=a.ssl_key_file)
+
+
+def cmd_inspect(a):
+    from .config import ModelConfig, preset
+    from .utils.memory import estimate_memory
+    cfg = preset(a.model.split(":", 1)[1]) if a.model.startswith("preset:") else ModelConfig.from_path(a.model)
+    est = estimate_memory(cfg, ctx=a.ctx_size, parallel=a.parallel, kv_bits=a.kv_bits or 16, tp=a.tp)
+    print(json.dumps(est, indent=1))
+
+
+def cmd_arch(a):
+    from .config import FAMILIES
+    print(json.dumps({"families": sorted(FAMILIES), "quantization": ["affine", "mxfp4", "mxfp8"],
+                      "kv_bits": [16, 8], "parallelism": ["tp", "ep", "pp"]}, indent=1))
+
+
+def cmd_tokenize(a):
+    from .tokenizer import load_tokenizer
+    print(json.dumps(load_tokenizer(a.model).encode(a.text)))
+
+
+def cmd_random_init(a):
+    import torch
+
+    from .config import preset
+    from .loading.checkpoint import save_checkpoint
+    from .models.weights import random_weights
+    from .ops import quant
+    cfg = preset(a.preset)
+    w = random_weights(cfg, seed=a.seed, dtype=torch.bfloat16)
+    qd = None
+    if a.quantize:
+        mode, bits, group = a.quantize, (8 if a.quantize == "mxfp8" else a.bits), (32 if a.quantize != "affine" else a.group_size)
+        for lw in w.layers:
+            for name in ("wqkv", "wo", "w_gate_up", "w_down", "experts_gate_up", "experts_down"):
+                v = getattr(lw, name)
+                if v is not None and v.shape[-1] % group == 0:   # other shapes stay dense
+                    setattr(lw, name, quant.quantize(v, mode, bits, group))
+        qd = dict(mode=mode, bits=bits, group_size=group)
+    cd = {k: v for k, v in cfg.to_dict().items() if k not in ("quantization", "extra")}
+    save_checkpoint(a.out, cd, w, quantization=qd)
+    print("wrote", a.out)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="mlxcel")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("generate", help="one-shot generation")
+    _add_model_args(p)
+    _add_sampling_args(p)
+    p.add_argument("-p", "--prompt", default=None)
+    p.add_argument("--chat", action="store_true", help="wrap the prompt with the chat template")
+    p.set_defaults(fn=cmd_generate)
+    p = sub.add_parser("run", help="interactive chat")
+    _add_model_args(p)
+    _add_sampling_args(p)
+    p.add_argument("--system", default=None)
+    p.set_defaults(fn=cmd_run)
+    p = sub.add_parser("serve", help="HTTP server")
+    _add_model_args(p)
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=8080)
+    p.add_argument("--api-key", action="append")
+    p.add_argument("--api-key-file", default=None)
+    p.add_argument("--alias", "-a", default=None)
+    p.add_argument("--chat-template-file", default=None)
+    p.add_argument("--ssl-cert-file", default=None)
+    p.add_argument("--ssl-key-file", default=None)
+    p.add_argument("-v", "--verbose", action="store_true")
+    p.set_defaults(fn=cmd_serve)
+    p = sub.add_parser("inspect", help="memory estimate")
+    _add_model_args(p)
+    p.set_defaults(fn=cmd_inspect)
+    p = sub.add_parser("arch", help="supported architectures")
+    p.set_defaults(fn=cmd_arch)
+    p = sub.add_parser("tokenize")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("text")
+    p.set_defaults(fn=cmd_tokenize)
+    p = sub.add_parser("random-init", help="write a random checkpoint of a preset architecture")
+    p.add_argument("preset")
+    p.add_argument("out")
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--quantize", choices=["affine", "mxfp4", "mxfp8"], default=None)
+    p.add_argument("--bits", type=int, default=4)
+    p.add_argument("--group-size", type=int, default=64)
+    p.set_defaults(fn=cmd_random_init)
+    a = ap.parse_args(argv)
+    a.fn(a)
+
+
+if __name__ == "__main__":
+    main()
