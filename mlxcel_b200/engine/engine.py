@@ -101,10 +101,12 @@ class Engine:
         self._next_id = 0
         self._decode_ticks_since_grant = 0
         self._graphs: dict[tuple, tuple] = {}
+        self.drafter = None          # speculative drafter (see mlxcel_b200.speculative)
+        self.spec_k = 4              # block size K: K-1 draft tokens + 1 bonus token per round
         self._alloc_buffers()
         self.stats = dict(steps=0, decode_steps=0, prefill_tokens=0, decode_tokens=0, preemptions=0,
                           graph_replays=0, prefix_hit_tokens=0, h2d_bytes=0, d2h_bytes=0,
-                          graph_kernel_launches=0)
+                          graph_kernel_launches=0, spec_rounds=0, spec_drafted=0, spec_accepted=0)
 
     # ------------------------------------------------------------------ setup
     def _auto_num_blocks(self, tp: int, nl: int) -> int:
@@ -140,7 +142,7 @@ class Engine:
         self.h_pf_tables, self.d_pf_tables = host((S, MB), torch.int32), dev((S, MB), torch.int32)
         self.h_pf_lens, self.d_pf_lens = host(S, torch.int32), dev(S, torch.int32)
         self.h_cu, self.d_cu = host(S + 1, torch.int32), dev(S + 1, torch.int32)
-        self.h_rows, self.d_rows = host(B + S, torch.int64), dev(B + S, torch.int64)
+        self.h_rows, self.d_rows = host(B * 9 + S, torch.int64), dev(B * 9 + S, torch.int64)
         self.h_out, self.d_out = host(B + S, torch.int32), dev(B + S, torch.int32)
         self.np_dec_tables = self.h_dec_tables.numpy()
         self.np_pf_tables = self.h_pf_tables.numpy()
@@ -303,7 +305,10 @@ class Engine:
         return decode_rows, pieces
 
     # ------------------------------------------------------------------ batch building
-    def _build_batch(self, decode: list[Sequence], pieces) -> tuple[StepBatch, int]:
+    def _build_batch(self, decode: list[Sequence], pieces, drafts: dict | None = None,
+                     all_rows: bool = False) -> tuple[StepBatch, int]:
+        """``drafts`` maps seq_id → speculative tokens appended after the sequence's own tokens (verify
+        rounds); ``all_rows`` asks for logits of every row of every piece."""
         nd = len(decode)
         t = 0
         tok, pos = self.h_tokens.numpy(), self.h_pos.numpy()
@@ -321,7 +326,7 @@ class Engine:
         max_q = 0
         rows: list[int] = list(range(nd))
         for j, (s, start, count) in enumerate(pieces):
-            toks = s.tokens
+            toks = s.tokens + drafts[s.seq_id] if (drafts and s.seq_id in drafts) else s.tokens
             tok[t:t + count] = toks[start:start + count]
             pos[t:t + count] = np.arange(start, start + count, dtype=np.int32)
             self.bm.fill_slots(s.seq_id, start, count, self.np_slots, t)
@@ -329,7 +334,9 @@ class Engine:
             t += count
             cu.append(t - nd)
             max_q = max(max_q, count)
-            if start + count >= s.total_len:
+            if all_rows:
+                rows.extend(range(t - count, t))
+            elif start + count >= s.total_len:
                 rows.append(t - 1)
         if pieces:
             self.bm.fill_tables([p[0].seq_id for p in pieces], self.np_pf_tables)
@@ -416,6 +423,9 @@ class Engine:
         decode, pieces = self._schedule()
         if not decode and not pieces:
             return []
+        if (self.drafter is not None and decode and not pieces and
+                all(s.params.greedy and s.mask_fn is None and not s.params.needs_history for s in decode)):
+            return self._spec_step(decode)
         b, R = self._build_batch(decode, pieces)
         nd = len(decode)
         logits = None
@@ -425,7 +435,12 @@ class Engine:
                 logits = gl[:nd]
                 self.stats["decode_steps"] += 1
         if logits is None:
-            logits = self.model.forward(b, self.pool.layers)
+            if self.drafter is not None and getattr(self.drafter, "needs_hidden", False):
+                h = self.model.forward_hidden(b, self.pool.layers)
+                logits = self.model.logits(h, b.logits_rows)
+                self.drafter.on_forward(self, decode, pieces, h)
+            else:
+                logits = self.model.forward(b, self.pool.layers)
         # rows: decode rows first, then prefill rows that completed their prompt
         sample_seqs = list(decode) + [s for (s, start, cnt) in pieces if start + cnt >= s.total_len]
         toks, lps = self.sampler.sample(logits, sample_seqs)
@@ -473,6 +488,75 @@ class Engine:
                                                  p.loop_min_count):
             return FinishReason.REPETITION_LOOP
         return None
+
+    # ------------------------------------------------------------------ speculative decoding
+    def _spec_step(self, decode: list[Sequence]) -> list[Sequence]:
+        """One verify round for every decoding row (the reference's verify_round,
+        src/lib/mlxcel-core/src/engine/verify_round.rs:170-305 and mtp/walk.rs:15-95): forward
+        ``[pending, d0 .. d(K-2)]``, accept drafts while they equal the target argmax, emit the
+        accepted drafts plus the target token at the first mismatch, roll the KV back."""
+        K = self.spec_k
+        props = self.drafter.propose(self, decode, K - 1)
+        drafts, pieces = {}, []
+        for s, d in zip(decode, props):
+            room = min(s.params.max_tokens - len(s.output) - 1, self.ecfg.max_model_len - s.total_len - 1)
+            d = list(d[: max(0, room)])
+            if not self.bm.reserve(s.seq_id, s.total_len + len(d)):
+                d = []
+            drafts[s.seq_id] = d
+            pieces.append((s, s.total_len - 1, 1 + len(d)))
+        b, R = self._build_batch([], pieces, drafts=drafts, all_rows=True)
+        need_h = getattr(self.drafter, "needs_hidden", False)
+        h = self.model.forward_hidden(b, self.pool.layers)
+        logits = self.model.logits(h, b.logits_rows)
+        target = ops.argmax(logits).cpu().tolist()
+        self.stats["steps"] += 1
+        self.stats["spec_rounds"] += 1
+        finished, now, row0 = [], time.perf_counter(), 0
+        accepted_info = []
+        for (s, start, cnt) in pieces:
+            d = drafts[s.seq_id]
+            tgt = target[row0:row0 + cnt]
+            a = 0
+            while a < len(d) and d[a] == tgt[a]:
+                a += 1
+            emitted = d[:a] + [tgt[a]]
+            self.stats["spec_drafted"] += len(d)
+            self.stats["spec_accepted"] += a
+            if hasattr(self.drafter, "record"):
+                self.drafter.record(s.seq_id, len(d), a)
+            L = s.total_len
+            reason = None
+            n_emit = 0
+            if s.first_token_time is None:
+                s.first_token_time = now
+            for tok in emitted:
+                reason = self._finish_step(s, tok, None)
+                n_emit += 1
+                if s.on_token is not None and (reason is None or reason == FinishReason.LENGTH):
+                    s.on_token(s, tok)
+                    if s.status == SeqStatus.FINISHED:
+                        break
+                if reason is not None:
+                    break
+            # KV is valid for the pending token and the accepted drafts actually kept
+            kept = min(a, max(0, n_emit - 1)) if n_emit else 0
+            s.num_computed = L + kept
+            accepted_info.append((s, row0, kept))
+            if s.status != SeqStatus.FINISHED:
+                self.bm.truncate(s.seq_id, L + kept)
+                if reason is not None:
+                    self._finish(s, reason)
+                    finished.append(s)
+            elif s not in finished:
+                finished.append(s)
+            row0 += cnt
+        self.stats["decode_tokens"] += sum(k + 1 for _, _, k in accepted_info)
+        if need_h:
+            self.drafter.on_verify(self, accepted_info, h)
+        for s in finished:
+            self.drafter.release(s.seq_id)
+        return finished
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams] | None = None
