@@ -77,6 +77,7 @@ class EngineConfig:
     prefill_grant_interval: int = 16
     mixed_steps: bool = True
     preemption: bool = True
+    lookahead: bool = True               # submit decode step n+1 before reading step n (greedy rows)
 
 
 class Engine:
@@ -144,6 +145,11 @@ class Engine:
         self.h_cu, self.d_cu = host(S + 1, torch.int32), dev(S + 1, torch.int32)
         self.h_rows, self.d_rows = host(B * 9 + S, torch.int64), dev(B * 9 + S, torch.int64)
         self.h_out, self.d_out = host(B + S, torch.int32), dev(B + S, torch.int32)
+        # second staging set + token read-back buffers for the lookahead pipeline
+        self.la_host = [dict(pos=host(B, torch.int32), slots=host(B, torch.int32), lens=host(B, torch.int32),
+                             tables=host((B, MB), torch.int32), out=host(B, torch.int32)) for _ in range(2)]
+        self._inflight = None
+        self._la_parity = 0
         self.np_dec_tables = self.h_dec_tables.numpy()
         self.np_pf_tables = self.h_pf_tables.numpy()
         self.np_slots = self.h_slots.numpy()
@@ -182,7 +188,7 @@ class Engine:
             self.waiting.remove(s)
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._inflight is not None)
 
     def release(self, seq_id: int) -> Sequence | None:
         """Forget a finished sequence (its blocks were already returned to the pool)."""
@@ -366,7 +372,8 @@ class Engine:
                       num_prefill_seqs=sp, pf_block_tables=self.d_pf_tables[:sp] if sp else None,
                       pf_cu_q=self.d_cu[: sp + 1] if sp else None,
                       pf_context_lens=self.d_pf_lens[:sp] if sp else None, pf_max_q_len=max_q,
-                      logits_rows=self.d_rows[:R])
+                      pf_cu_q_host=cu if sp else None, logits_rows=self.d_rows[:R])
+        b.logits_rows_host = rows
         return b, R
 
     # ------------------------------------------------------------------ cuda graphs
@@ -409,6 +416,10 @@ class Engine:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 logits = fwd()
+                # Greedy token feedback on the device: the step's argmax lands in the token buffer
+                # the next replay reads, so a following step can be submitted before the host has
+                # seen these tokens.
+                ops.argmax(logits, out=self.d_tokens[:bp])
             ent = (g, logits, _lib.launches() - n0)
             self._graphs[key] = ent
         ent[0].replay()
@@ -416,13 +427,120 @@ class Engine:
         self.stats["graph_kernel_launches"] += ent[2]
         return ent[1]
 
+    # ------------------------------------------------------------------ lookahead pipeline
+    # Decode step n+1 is submitted before step n's tokens are read (the reference's lookahead
+    # pipeline, src/server/batch/scheduler/decode_tick.rs:386-485 and :686-794): the host prepares
+    # positions / slots / page tables from what it already knows, the token ids come from the
+    # device (the graph's argmax feeds the token buffer), and reading tokens lags one step.
+    # Eligibility mirrors the reference: every row greedy without history penalties, masks,
+    # logprobs or stop strings to watch mid-step, nothing queued, no prefill parked, no drafter.
+    def _lookahead_eligible(self, decode, pieces) -> bool:
+        e = self.ecfg
+        if not (e.lookahead and self.is_cuda and e.cuda_graphs and decode and not pieces):
+            return False
+        if self.drafter is not None or self.waiting or len(decode) > e.max_batch:
+            return False
+        if any(s.status != SeqStatus.DECODING for s in self.running):
+            return False
+        for s in decode:
+            p = s.params
+            if not (p.greedy and not p.needs_history and not p.logit_bias and s.mask_fn is None
+                    and not p.logprobs):
+                return False
+        return True
+
+    def _can_pipeline(self, inf) -> bool:
+        seqs = inf["seqs"]
+        if not self._lookahead_eligible(seqs, []):
+            return False
+        if len(seqs) != len(self.running) or any(a is not b for a, b in zip(seqs, self.running)):
+            return False
+        for s in seqs:
+            if s.status != SeqStatus.DECODING:
+                return False
+            # the token in flight must not be the one that ends the row by length
+            if len(s.output) + 2 > s.params.max_tokens or s.total_len + 3 > self.ecfg.max_model_len:
+                return False
+        return True
+
+    def _launch_lookahead(self, seqs, from_device: bool):
+        nd = len(seqs)
+        extra = 1 if from_device else 0
+        for s in seqs:
+            if not self.bm.reserve(s.seq_id, s.total_len + extra):
+                return None
+        par = self._la_parity
+        self._la_parity ^= 1
+        hb = self.la_host[par]
+        pos, lens, slots = hb["pos"].numpy(), hb["lens"].numpy(), hb["slots"].numpy()
+        max_len = 0
+        for i, s in enumerate(seqs):
+            L = s.total_len + extra
+            pos[i] = L - 1
+            lens[i] = L
+            self.bm.fill_slots(s.seq_id, L - 1, 1, slots, i)
+            max_len = max(max_len, L)
+        self.bm.fill_tables([s.seq_id for s in seqs], hb["tables"].numpy())
+        if not from_device:
+            tok = self.h_tokens.numpy()
+            for i, s in enumerate(seqs):
+                tok[i] = s.output[-1] if s.output else s.prompt[-1]
+            self.d_tokens[:nd].copy_(self.h_tokens[:nd], non_blocking=True)
+        self.d_pos[:nd].copy_(hb["pos"][:nd], non_blocking=True)
+        self.d_slots[:nd].copy_(hb["slots"][:nd], non_blocking=True)
+        self.d_dec_lens[:nd].copy_(hb["lens"][:nd], non_blocking=True)
+        self.d_dec_tables[:nd].copy_(hb["tables"][:nd], non_blocking=True)
+        mb4 = self.max_blocks_per_seq * 4 + 4
+        self.stats["h2d_bytes"] += nd * (8 + mb4) + (0 if from_device else 4 * nd)
+        self.stats["d2h_bytes"] += 4 * nd
+        if self._decode_graph(nd, max_len) is None:
+            return None
+        hb["out"][:nd].copy_(self.d_tokens[:nd], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.stats["decode_steps"] += 1
+        return dict(seqs=list(seqs), nd=nd, buf=hb["out"], event=ev)
+
+    def _collect_lookahead(self, inf) -> list[Sequence]:
+        inf["event"].synchronize()
+        toks = inf["buf"][: inf["nd"]].tolist()
+        self.stats["steps"] += 1
+        finished: list[Sequence] = []
+        now = time.perf_counter()
+        for s, tok in zip(inf["seqs"], toks):
+            if s.status != SeqStatus.DECODING:
+                continue            # ended while this step was in flight: its row is discarded
+            self.stats["decode_tokens"] += 1
+            s.num_computed = s.total_len
+            if s.first_token_time is None:
+                s.first_token_time = now
+            reason = self._finish_step(s, tok, None)
+            if s.on_token is not None and (reason is None or reason == FinishReason.LENGTH):
+                s.on_token(s, tok)
+                if s.status == SeqStatus.FINISHED:
+                    continue
+            if reason is not None:
+                self._finish(s, reason)
+                finished.append(s)
+        return finished
+
     # ------------------------------------------------------------------ step
     @torch.inference_mode()
     def step(self) -> list[Sequence]:
         """One scheduling tick + forward + sample. Returns the sequences that finished."""
+        if self._inflight is not None:
+            inf = self._inflight
+            nxt = self._launch_lookahead(inf["seqs"], from_device=True) if self._can_pipeline(inf) else None
+            fin = self._collect_lookahead(inf)
+            self._inflight = nxt
+            return fin
         decode, pieces = self._schedule()
         if not decode and not pieces:
             return []
+        if self._lookahead_eligible(decode, pieces):
+            self._inflight = self._launch_lookahead(decode, from_device=False)
+            if self._inflight is not None:
+                return []
         if (self.drafter is not None and decode and not pieces and
                 all(s.params.greedy and s.mask_fn is None and not s.params.needs_history for s in decode)):
             return self._spec_step(decode)

@@ -43,6 +43,7 @@ class StepBatch:
     pf_cu_q: torch.Tensor | None = None            # [Sp+1] int32
     pf_context_lens: torch.Tensor | None = None    # [Sp] int32 (prefix + chunk)
     pf_max_q_len: int = 0
+    pf_cu_q_host: list | None = None               # host copy of pf_cu_q (micro-batch splitting)
     logits_rows: torch.Tensor | None = None        # [R] int64 rows of the hidden state to project
     embeds: torch.Tensor | None = None             # optional [T, H] input embeddings (VLM / MTP)
 
