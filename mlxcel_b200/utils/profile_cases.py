@@ -1,0 +1,156 @@
+"""Small, self-terminating workloads for profiler captures and kernel timing.
+
+    python -m mlxcel_b200.utils.profile_cases gemm_decode      # M=64 projections, 6 distinct weights
+    python -m mlxcel_b200.utils.profile_cases gemm_prefill     # 8192 x 6144 x 4096
+    python -m mlxcel_b200.utils.profile_cases attn_decode      # B=64, ctx 1152, GQA 32/8, D=128
+    python -m mlxcel_b200.utils.profile_cases attn_prefill     # 8 x 1024-token prompts
+    python -m mlxcel_b200.utils.profile_cases decode_steps N   # N eager decode steps of the bench workload
+    python -m mlxcel_b200.utils.profile_cases kbench           # CUDA-event timings of the hot kernels (JSON lines)
+
+Every case holds at most a few GB on the device and launches a handful of kernels, so that a
+capture with ``ncu --set full -k regex:<kernel> -c <n>`` ends by itself. ``decode_steps`` brackets
+the measured steps with cudaProfilerStart/Stop (use ``--profile-from-start off``).
+"""
+from __future__ import annotations
+
+import json
+import math
+import sys
+
+import torch
+
+from .. import ops
+from ..ops import KVLayer
+
+DEV = "cuda"
+
+
+def _bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+def gemm_decode():
+    x = _bf(64, 4096)
+    ws = [_bf(4096, 4096, scale=0.02) for _ in range(6)]     # 192 MB of weights > L2
+    res = _bf(64, 4096)
+    for w in ws:
+        ops.linear(x, w, residual=res)
+    wg = _bf(2 * 14336, 4096, scale=0.02)
+    ops.glu_linear(x, wg, 14336, "silu")
+
+
+def gemm_prefill():
+    x, w = _bf(8192, 4096), _bf(6144, 4096, scale=0.02)
+    for _ in range(3):
+        ops.linear(x, w)
+    wg = _bf(2 * 14336, 4096, scale=0.02)
+    ops.glu_linear(x, wg, 14336, "silu")
+
+
+def _pool(B, ctx, Hkv, D, bs=16):
+    nbs = (ctx + bs - 1) // bs
+    nb = B * nbs + 8
+    kv = KVLayer(_bf(nb, Hkv, bs, D), _bf(nb, Hkv, bs, D), None, None, bs, 16)
+    tab = torch.randperm(nb - 8, device=DEV)[: B * nbs].reshape(B, nbs).to(torch.int32)
+    return kv, tab
+
+
+def attn_decode(B=64, ctx=1152, Hq=32, Hkv=8, D=128, reps=3):
+    kv, tab = _pool(B, ctx, Hkv, D)
+    cl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+    q = _bf(B, Hq * D)
+    for _ in range(reps):
+        ops.paged_decode(q, kv, tab, cl, Hq=Hq, Hkv=Hkv, D=D, scale=1 / math.sqrt(D), max_len=ctx)
+
+
+def attn_prefill(S=8, qlen=1024, Hq=32, Hkv=8, D=128, reps=2):
+    kv, tab = _pool(S, qlen, Hkv, D)
+    cl = torch.full((S,), qlen, dtype=torch.int32, device=DEV)
+    cu = (torch.arange(S + 1, device=DEV) * qlen).to(torch.int32)
+    q = _bf(S * qlen, Hq * D)
+    for _ in range(reps):
+        ops.paged_prefill(q, kv, tab, cu, cl, Hq=Hq, Hkv=Hkv, D=D, scale=1 / math.sqrt(D), max_q_len=qlen)
+
+
+def decode_steps(n_steps=2, requests=64, prompt_len=1024, model="llama-3.1-8b"):
+    from ..engine import EngineConfig, SamplingParams
+    from ..llm import LLM
+    ecfg = EngineConfig(max_batch=requests, max_num_batched_tokens=8192, prefill_chunk_alone=2048,
+                        prefill_chunk_contended=prompt_len, max_prefill_seqs=8, prefix_cache=False,
+                        max_model_len=prompt_len + 300, cuda_graphs=False, lookahead=False,
+                        num_blocks=(prompt_len + 300) // 16 * requests + 128)
+    llm = LLM.from_preset(model, device=DEV, engine_config=ecfg)
+    g = torch.Generator().manual_seed(0)
+    eng = llm.engine
+    for p in torch.randint(0, llm.cfg.vocab_size, (requests, prompt_len), generator=g).tolist():
+        eng.add_request(p, SamplingParams(max_tokens=200, ignore_eos=True))
+    while eng.waiting or any(s.status.value == "prefilling" for s in eng.running):
+        eng.step()
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    for _ in range(n_steps):
+        eng.step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+
+
+def kbench():
+    """CUDA-event medians with an L2 flush between iterations; cuBLAS (torch.matmul) beside each GEMM."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+
+    def timeit(fn, iters=10, warm=3):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2]
+
+    def gemm(M, N, K, glu=False):
+        x, w = _bf(M, K), _bf(N * (2 if glu else 1), K, scale=0.02)
+        t = timeit((lambda: ops.glu_linear(x, w, N, "silu")) if glu else (lambda: ops.linear(x, w)))
+        tc = timeit(lambda: x @ w.t())
+        fl, by = 2 * M * N * K * (2 if glu else 1), (N * K * (2 if glu else 1) + M * K + M * N) * 2
+        print(json.dumps(dict(op="glu" if glu else "gemm", M=M, N=N, K=K, ms=round(t, 4), cublas_ms=round(tc, 4),
+                              tflops=round(fl / t / 1e9, 1), gbs=round(by / t / 1e6, 1))), flush=True)
+
+    for N, K, glu in [(6144, 4096, False), (4096, 4096, False), (14336, 4096, True), (4096, 14336, False)]:
+        gemm(8192, N, K, glu)
+    for N, K, glu in [(6144, 4096, False), (4096, 4096, False), (14336, 4096, True), (4096, 14336, False),
+                      (128256, 4096, False)]:
+        gemm(64, N, K, glu)
+    for B, ctx, Hq, Hkv, D in [(64, 1152, 32, 8, 128), (64, 1152, 4, 1, 128), (128, 2304, 64, 8, 64)]:
+        kv, tab = _pool(B, ctx, Hkv, D)
+        cl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+        q = _bf(B, Hq * D)
+        t = timeit(lambda: ops.paged_decode(q, kv, tab, cl, Hq=Hq, Hkv=Hkv, D=D, scale=1 / math.sqrt(D), max_len=ctx))
+        print(json.dumps(dict(op="attn_decode", B=B, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, ms=round(t, 4),
+                              gbs=round(B * ctx * Hkv * D * 4 / t / 1e6, 1))), flush=True)
+    for S, ql, Hq, Hkv, D in [(8, 1024, 32, 8, 128), (8, 1024, 64, 8, 64)]:
+        kv, tab = _pool(S, ql, Hkv, D)
+        cl = torch.full((S,), ql, dtype=torch.int32, device=DEV)
+        cu = (torch.arange(S + 1, device=DEV) * ql).to(torch.int32)
+        q = _bf(S * ql, Hq * D)
+        t = timeit(lambda: ops.paged_prefill(q, kv, tab, cu, cl, Hq=Hq, Hkv=Hkv, D=D, scale=1 / math.sqrt(D),
+                                             max_q_len=ql))
+        print(json.dumps(dict(op="attn_prefill", S=S, qlen=ql, Hq=Hq, D=D, ms=round(t, 4),
+                              tflops=round(4 * S * Hq * D * ql * ql / 2 / t / 1e9, 1))), flush=True)
+
+
+CASES = dict(gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
+             attn_prefill=attn_prefill, decode_steps=decode_steps, kbench=kbench)
+
+if __name__ == "__main__":
+    name = sys.argv[1] if len(sys.argv) > 1 else "kbench"
+    args = [int(a) for a in sys.argv[2:]]
+    CASES[name](*args)
+    torch.cuda.synchronize()
+    print("done", name)
