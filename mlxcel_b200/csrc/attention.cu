@@ -630,6 +630,8 @@ paged_decode_mma_kernel(const DecodeParams p, const int G) {
   uint8_t* kv_sm = dm_smem + 16 * D * 2;                 // 4 warps x stages x (K, V)
   __shared__ float m_s[kDmWarps][16], l_s[kDmWarps][16];
   __shared__ int last_s;
+  pdl_trigger();
+  pdl_wait();
 
   const int split = blockIdx.x % p.num_splits;
   const int bh = blockIdx.x / p.num_splits;
@@ -936,8 +938,7 @@ static int launch_decode_mma_bs(const DecodeParams& p, int G, int grid, cudaStre
                          cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  kern<<<grid, kDmThreads, smem, st>>>(p, G);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(kern, dim3(grid), dim3(kDmThreads), smem, st, p, G));
 }
 
 template <int D, int KV_BITS>

@@ -248,6 +248,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  // Everything above touched only this CTA's shared memory / TMEM; global memory written by the
+  // previous kernel of the stream is read from here on.
+  pdl_trigger();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -818,8 +822,7 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
     prefer_max_shared(kern);
     configured = true;
   }
-  kern<<<grid, kGemmThreads, smem, stream>>>(ml, mc, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, stream, ml, mc, p));
 }
 
 }  // namespace mx

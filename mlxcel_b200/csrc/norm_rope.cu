@@ -20,6 +20,8 @@ __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,
                                    __nv_bfloat16* __restrict__ y,
                                    __nv_bfloat16* __restrict__ residual_out, int dim, float eps,
                                    float w_bias) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const int nvec = dim >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * dim);
@@ -148,6 +150,8 @@ __global__ void rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* _
                                    int Hq, int Hkv, int D, int rot_dim, int block_size,
                                    int rope_mode, float mscale) {
   __shared__ float stage[kRopeWarps][kMaxHeadDim];
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = Hq + 2 * Hkv;
   const long long gw = static_cast<long long>(blockIdx.x) * kRopeWarps + warp;
@@ -253,6 +257,8 @@ __global__ void rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* _
 // ----------------------------------------------------------------------------- embedding
 __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                  __nv_bfloat16* __restrict__ out, int dim, int vocab, float scale) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const int nvec = dim >> 3;
@@ -321,11 +327,11 @@ extern "C" int mx_add_rmsnorm(const void* x, const void* residual, const void* w
   MX_PREFER_SHARED(add_rmsnorm_kernel<2>);
   MX_PREFER_SHARED(add_rmsnorm_kernel<4>);
   if (vpt <= 1)
-    add_rmsnorm_kernel<1><<<rows, threads, 0, stream>>>(X, R, W, Y, RO, dim, eps, w_bias);
+    launch_kernel(add_rmsnorm_kernel<1>, dim3(rows), dim3(threads), 0, stream, X, R, W, Y, RO, dim, eps, w_bias);
   else if (vpt <= 2)
-    add_rmsnorm_kernel<2><<<rows, threads, 0, stream>>>(X, R, W, Y, RO, dim, eps, w_bias);
+    launch_kernel(add_rmsnorm_kernel<2>, dim3(rows), dim3(threads), 0, stream, X, R, W, Y, RO, dim, eps, w_bias);
   else
-    add_rmsnorm_kernel<4><<<rows, threads, 0, stream>>>(X, R, W, Y, RO, dim, eps, w_bias);
+    launch_kernel(add_rmsnorm_kernel<4>, dim3(rows), dim3(threads), 0, stream, X, R, W, Y, RO, dim, eps, w_bias);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -363,13 +369,13 @@ extern "C" int mx_rope_append(void* qkv, const int* positions, const int* slot_m
   MX_PREFER_SHARED(rope_append_kernel<16>);
   MX_PREFER_SHARED(rope_append_kernel<8>);
   if (kv_bits == 16)
-    rope_append_kernel<16><<<blocks, kRopeWarps * 32, 0, stream>>>(
-        Q, positions, slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv,
-        D, rot_dim, block_size, rope_mode, mscale);
+    launch_kernel(rope_append_kernel<16>, dim3(blocks), dim3(kRopeWarps * 32), 0, stream, Q, positions,
+                  slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv, D, rot_dim,
+                  block_size, rope_mode, mscale);
   else
-    rope_append_kernel<8><<<blocks, kRopeWarps * 32, 0, stream>>>(
-        Q, positions, slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv,
-        D, rot_dim, block_size, rope_mode, mscale);
+    launch_kernel(rope_append_kernel<8>, dim3(blocks), dim3(kRopeWarps * 32), 0, stream, Q, positions,
+                  slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv, D, rot_dim,
+                  block_size, rope_mode, mscale);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -382,8 +388,8 @@ extern "C" int mx_embedding(const int* ids, const void* table, void* out, int T,
   if (threads > 256) threads = 256;
   if (threads < 32) threads = 32;
   MX_PREFER_SHARED(embedding_kernel);
-  embedding_kernel<<<T, threads, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table),
-                                              static_cast<__nv_bfloat16*>(out), dim, vocab, scale);
+  launch_kernel(embedding_kernel, dim3(T), dim3(threads), 0, stream, ids,
+                static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), dim, vocab, scale);
   return static_cast<int>(cudaGetLastError());
 }
 

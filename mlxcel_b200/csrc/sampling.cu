@@ -86,6 +86,8 @@ template <bool FP32>
 __global__ void __launch_bounds__(kSampThreads)
 argmax_kernel(const void* __restrict__ logits, long long row_stride, int* __restrict__ out, int V) {
   __shared__ ArgMax red[32];
+  pdl_trigger();
+  pdl_wait();
   const char* base = static_cast<const char*>(logits) +
                      static_cast<size_t>(blockIdx.x) * row_stride * (FP32 ? 4 : 2);
   ArgMax best{-INFINITY, 0x7fffffff};
@@ -301,10 +303,10 @@ extern "C" int mx_argmax(const void* logits, int logits_fp32, long long row_stri
   MX_PREFER_SHARED(argmax_kernel<true>);
   MX_PREFER_SHARED(argmax_kernel<false>);
   if (logits_fp32)
-    argmax_kernel<true><<<B, kSampThreads, 0, stream>>>(logits, row_stride, out, V);
-  else
-    argmax_kernel<false><<<B, kSampThreads, 0, stream>>>(logits, row_stride, out, V);
-  return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_kernel(argmax_kernel<true>, dim3(B), dim3(kSampThreads), 0, stream, logits,
+                                          row_stride, out, V));
+  return static_cast<int>(launch_kernel(argmax_kernel<false>, dim3(B), dim3(kSampThreads), 0, stream, logits,
+                                        row_stride, out, V));
 }
 
 extern "C" long long mx_sample_scratch_floats(int, int) { return 0; }
