@@ -51,6 +51,14 @@ int mx_gemm_comm(const void* x, const void* w, void* out, const void* bias, cons
                  const void* const* out_peer, void* ctl, void* expect, long long parity_stride,
                  long long rank_stride, void* workspace, long long ws_bytes, void* stream);
 
+// Stand-alone all-reduce over the symmetric heap (same channel protocol as mx_gemm_comm):
+// out = residual + sum over ranks of x, n bf16 elements. mode 1 one-shot (local out), mode 2
+// two-shot (results stored into every out_peer). status: device status word (int).
+int mx_allreduce_comm(const void* x, const void* residual, void* out, long long n, int mode, int rank,
+                      int world, const void* const* flags_peer, const void* const* recv_peer,
+                      const void* const* out_peer, void* ctl, void* expect, long long parity_stride,
+                      long long rank_stride, void* status, void* stream);
+
 // Bytes of workspace the no-scratch-allocation path needs at most for mx_gemm_bf16.
 long long mx_gemm_workspace_bytes(void);
 

@@ -104,6 +104,12 @@ class FusedOps:
         self.two_stride = ((tiles + W - 1) // W) * 128 * 256
         self.ch_two = _Channel(heap, W * self.two_stride * 2)
         self.ch_ag = _Channel(heap, 0)
+        # stand-alone all-reduce channels (MoE combine, quantized GEMV partials)
+        self.ar_one_stride = small_m * hidden
+        self.ch_ar_one = _Channel(heap, W * self.ar_one_stride * 2)
+        chunks = (max_tokens * hidden + 8191) // 8192
+        self.ar_two_stride = ((chunks + W - 1) // W) * 8192
+        self.ch_ar_two = _Channel(heap, W * self.ar_two_stride * 2)
         # replicated residual stream and gathered logits live in the heap
         self.h_off = heap.alloc(max_tokens * hidden * 2)
         self.h_peer = heap.peer_ptrs(self.h_off)
@@ -117,7 +123,7 @@ class FusedOps:
         """Zero every channel on all ranks (after a bounded wait reported a failure)."""
         torch.cuda.synchronize(self.heap.device)
         dist.barrier(group=self.heap.group)
-        for ch in (self.ch_one, self.ch_two, self.ch_ag):
+        for ch in (self.ch_one, self.ch_two, self.ch_ag, self.ch_ar_one, self.ch_ar_two):
             ch.reset()
         torch.cuda.synchronize(self.heap.device)
         dist.barrier(group=self.heap.group)
@@ -148,6 +154,27 @@ class FusedOps:
                               ws.numel(), _lib.stream())
         _lib.count_launch()
         _lib.check(rc, "mx_gemm_comm")
+        return out
+
+    def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """Sum of ``x`` over ranks (+ residual) with the stand-alone peer-memory kernel. Small tensors
+        are reduced in place (one-shot), large ones land in the symmetric residual buffer."""
+        n = x.numel()
+        lib = _lib.load()
+        ws = _lib.workspace(x.device)
+        x = x.contiguous()
+        if n <= self.ar_one_stride:
+            ch, mode, stride, out = self.ch_ar_one, 1, self.ar_one_stride, x
+        else:
+            ch, mode, stride = self.ch_ar_two, 2, self.ar_two_stride
+            if x.dim() != 2 or x.shape[0] > self.max_tokens or x.shape[1] > self.hidden:
+                raise ValueError("all_reduce shape exceeds the symmetric buffers")
+            out = self.hidden_buffer(x.shape[0], x.shape[1])
+        rc = lib.mx_allreduce_comm(x.data_ptr(), _lib.ptr(residual), out.data_ptr(), n, mode, self.rank,
+                                   self.world, ch.flags_peer, ch.recv_peer, self.h_peer, ch.ctl.data_ptr(),
+                                   ch.expect.data_ptr(), self.world * stride, stride, ws.data_ptr(), _lib.stream())
+        _lib.count_launch()
+        _lib.check(rc, "mx_allreduce_comm")
         return out
 
     def gemm_allgather(self, x: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:

@@ -56,6 +56,8 @@ class TPComm:
     # ------------------------------------------------------------------ collectives
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp_size > 1:
+            if self.backend == "fused" and x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+                return self.fused.all_reduce(x)
             dist.all_reduce(x, group=self.group)
         return x
 
@@ -71,8 +73,7 @@ class TPComm:
             return self.fused.gemm_allreduce(x, w, bias, residual)
         first = self.tp_rank == 0
         y = _linear_any(x, w, bias=bias if first else None, residual=residual if first else None)
-        dist.all_reduce(y, group=self.group)
-        return y
+        return self.all_reduce(y)
 
     def gather_logits(self, logits_local: torch.Tensor) -> torch.Tensor:
         """[R, V/tp] per rank → [R, V] on every rank."""

@@ -79,6 +79,14 @@ def test_fused_gemm_allreduce_and_allgather():
                 # bitwise identical on every rank
                 ref0 = got.clone(); dist.broadcast(ref0, 0)
                 assert torch.equal(ref0, got), (M, rep)
+            # stand-alone all-reduce (one-shot for small, two-shot for large tensors)
+            part = torch.randn(M, N, device=dev).to(torch.bfloat16) * (rank + 1)
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part)
+            want_ar = sum(p.float() for p in parts)
+            got_ar = comm.all_reduce(part.clone())
+            torch.cuda.synchronize()
+            assert (got_ar.float() - want_ar).abs().max().item() < 0.1 * world, M
             # all-gather of a vocab-parallel projection
             if M <= 256:
                 Vl = 1024
