@@ -1,0 +1,169 @@
+"""State-space / linear-attention step operators and small element-wise ops (hybrid families:
+Mamba, Mamba2 / Jamba / Nemotron-H, Qwen3-Next GatedDeltaNet, BitNet). CUDA kernels in
+``csrc/recurrent.cu``; the PyTorch statements below are the references and the CPU path."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+_vp, _i, _f, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+_SIG = {
+    "mx_ssm_update": [_vp] * 9 + [_i] * 6 + [_vp],
+    "mx_selective_scan": [_vp] * 8 + [_i] * 5 + [_vp],
+    "mx_gated_delta_update": [_vp] * 7 + [_i, _i, _i, _f, _vp],
+    "mx_bitlinear": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "mx_activation": [_vp, _vp, _ll, _i, _f, _f, _f, _f, _vp],
+    "mx_add3_layernorm": [_vp] * 7 + [_i, _i, _f, _vp],
+}
+
+
+def _fn(name):
+    lib = _lib.load()
+    fn = getattr(lib, name)
+    if fn.argtypes is None or len(fn.argtypes) == 0:
+        fn.argtypes, fn.restype = _SIG[name], _i
+    return fn
+
+
+def _call(name, *args):
+    rc = _fn(name)(*args)
+    _lib.count_launch()
+    _lib.check(rc, name)
+
+
+# ----------------------------------------------------------------------------- Mamba2 step
+def ssm_update_ref(state, x, dt, A, Bm, C, D=None, dt_bias=None, dt_softplus=True):
+    B, H, Dh, N = state.shape
+    G = Bm.shape[1]
+    dtv = dt.float() + (dt_bias.float() if dt_bias is not None else 0.0)
+    if dt_softplus:
+        dtv = F.softplus(dtv)
+    dA = torch.exp(dtv * A.float())                                    # [B, H]
+    Bh = Bm.float().repeat_interleave(H // G, dim=1)                   # [B, H, N]
+    Ch = C.float().repeat_interleave(H // G, dim=1)
+    new = state * dA[..., None, None] + (dtv[..., None] * x.float())[..., None] * Bh[:, :, None, :]
+    y = (new * Ch[:, :, None, :]).sum(-1)
+    if D is not None:
+        y = y + D.float()[None, :, None] * x.float()
+    state.copy_(new)
+    return y.to(x.dtype)
+
+
+def ssm_update(state, x, dt, A, Bm, C, D=None, dt_bias=None, dt_softplus=True):
+    """Mamba2 decode step. state [B,H,Dh,N] fp32 is updated in place; returns y [B,H,Dh]."""
+    if not x.is_cuda:
+        return ssm_update_ref(state, x, dt, A, Bm, C, D, dt_bias, dt_softplus)
+    B, H, Dh, N = state.shape
+    y = torch.empty_like(x)
+    _call("mx_ssm_update", state.data_ptr(), x.data_ptr(), dt.data_ptr(), A.data_ptr(), Bm.data_ptr(), C.data_ptr(),
+          _lib.ptr(D), _lib.ptr(dt_bias), y.data_ptr(), B, H, Dh, N, Bm.shape[1], 1 if dt_softplus else 0,
+          _lib.stream())
+    return y
+
+
+# ----------------------------------------------------------------------------- Mamba1 scan
+def selective_scan_ref(x, dt, A, Bm, C, D, state, dt_softplus=True):
+    Bsz, L, Di = x.shape
+    y = torch.empty(Bsz, L, Di, dtype=torch.float32, device=x.device)
+    s = state.clone()
+    for t in range(L):
+        dtv = dt[:, t].float()
+        if dt_softplus:
+            dtv = F.softplus(dtv)
+        xv = x[:, t].float()
+        s = torch.exp(dtv[..., None] * A.float()[None]) * s + (dtv * xv)[..., None] * Bm[:, t].float()[:, None, :]
+        y[:, t] = (s * C[:, t].float()[:, None, :]).sum(-1) + (D.float()[None] * xv if D is not None else 0.0)
+    state.copy_(s)
+    return y.to(x.dtype)
+
+
+def selective_scan(x, dt, A, Bm, C, D, state, dt_softplus=True):
+    """Mamba1 scan over L steps. state [B,Di,N] fp32 in place; returns y [B,L,Di]."""
+    if not x.is_cuda:
+        return selective_scan_ref(x, dt, A, Bm, C, D, state, dt_softplus)
+    Bsz, L, Di = x.shape
+    y = torch.empty_like(x)
+    _call("mx_selective_scan", x.data_ptr(), dt.data_ptr(), A.data_ptr(), Bm.data_ptr(), C.data_ptr(), _lib.ptr(D),
+          state.data_ptr(), y.data_ptr(), Bsz, L, Di, A.shape[1], 1 if dt_softplus else 0, _lib.stream())
+    return y
+
+
+# ----------------------------------------------------------------------------- gated delta rule
+def gated_delta_update_ref(S, q, k, v, g, beta, q_scale=1.0):
+    Sn = S * torch.exp(g.float())[..., None, None]
+    mem = (Sn * k.float()[..., :, None]).sum(-2)
+    delta = (v.float() - mem) * beta.float()[..., None]
+    Sn = Sn + k.float()[..., :, None] * delta[..., None, :]
+    out = (Sn * (q.float() * q_scale)[..., :, None]).sum(-2)
+    S.copy_(Sn)
+    return out.to(q.dtype)
+
+
+def gated_delta_update(S, q, k, v, g, beta, q_scale=1.0):
+    """GatedDeltaNet decode step. S [B,Hv,Dk,Dv] fp32 in place; q,k [B,Hv,Dk]; v [B,Hv,Dv]; g, beta [B,Hv] fp32."""
+    if not q.is_cuda:
+        return gated_delta_update_ref(S, q, k, v, g, beta, q_scale)
+    B, Hv, Dk, Dv = S.shape
+    out = torch.empty_like(v)
+    _call("mx_gated_delta_update", S.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(),
+          beta.data_ptr(), out.data_ptr(), B * Hv, Dk, Dv, float(q_scale), _lib.stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- BitLinear
+def pack_ternary(w: torch.Tensor) -> torch.Tensor:
+    """{-1,0,1} [N,K] → uint8 [N,K/4] (2 bits per value, code = value + 1, LSB first)."""
+    c = (w.to(torch.int64) + 1).reshape(w.shape[0], -1, 4)
+    return (c[..., 0] | (c[..., 1] << 2) | (c[..., 2] << 4) | (c[..., 3] << 6)).to(torch.uint8)
+
+
+def bitlinear(x, w_packed, scale: float):
+    M, K = x.shape
+    N = w_packed.shape[0]
+    if not x.is_cuda:
+        c = w_packed.to(torch.int64)
+        w = torch.stack([(c >> (2 * j)) & 3 for j in range(4)], dim=-1).reshape(N, K).float() - 1.0
+        return ((x.float() @ w.t()) * scale).to(x.dtype)
+    out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    _call("mx_bitlinear", x.data_ptr(), w_packed.data_ptr(), out.data_ptr(), M, N, K, float(scale), _lib.stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- element-wise
+def gelu_tanh(x):
+    if not x.is_cuda:
+        return F.gelu(x.float(), approximate="tanh").to(x.dtype)
+    y = torch.empty_like(x)
+    _call("mx_activation", x.data_ptr(), y.data_ptr(), x.numel(), 0, 0.0, 0.0, 0.0, 0.0, _lib.stream())
+    return y
+
+
+def xielu_ref(x, ap, an, beta, eps):
+    v = x.float()
+    return torch.where(v > 0, ap * v * v + beta * v, an * (torch.expm1(torch.clamp(v, max=eps)) - v) + beta * v).to(x.dtype)
+
+
+def xielu(x, ap: float, an: float, beta: float = 0.5, eps: float = -1e-6):
+    if not x.is_cuda:
+        return xielu_ref(x, ap, an, beta, eps)
+    y = torch.empty_like(x)
+    _call("mx_activation", x.data_ptr(), y.data_ptr(), x.numel(), 1, float(ap), float(an), float(beta), float(eps),
+          _lib.stream())
+    return y
+
+
+def add3_layernorm(a, b, c, weight, bias=None, eps: float = 1e-5):
+    """(LayerNorm(a + b + c) * weight + bias, a + b + c)."""
+    if not a.is_cuda:
+        s = (a.float() + b.float() + c.float()).to(a.dtype)
+        y = F.layer_norm(s.float(), (s.shape[-1],), weight.float(), None if bias is None else bias.float(), eps)
+        return y.to(a.dtype), s
+    rows, dim = a.shape
+    y, s = torch.empty_like(a), torch.empty_like(a)
+    _call("mx_add3_layernorm", a.data_ptr(), b.data_ptr(), c.data_ptr(), weight.data_ptr(), _lib.ptr(bias),
+          s.data_ptr(), y.data_ptr(), rows, dim, float(eps), _lib.stream())
+    return y, s
