@@ -631,7 +631,6 @@ paged_decode_mma_kernel(const DecodeParams p, const int G) {
   __shared__ float m_s[kDmWarps][16], l_s[kDmWarps][16];
   __shared__ int last_s;
   pdl_trigger();
-  pdl_wait();
 
   const int split = blockIdx.x % p.num_splits;
   const int bh = blockIdx.x / p.num_splits;
@@ -648,6 +647,22 @@ paged_decode_mma_kernel(const DecodeParams p, const int G) {
   const int s_begin = g_begin + split * per;
   const int s_end = min(g_end, s_begin + per);
   const int* table = p.block_tables + static_cast<size_t>(b) * p.max_blocks;
+
+  // Context lengths and block tables are step inputs (uploaded by copies, never written by a
+  // kernel of the step) and every key but the newest is already in the pool: the head of this
+  // CTA's KV stream is requested into L2 while the previous kernel (the one that appends the
+  // newest key and writes q) is still running. L2 is the coherence point, so the newest key is
+  // seen by the loads below whether or not its line was prefetched early.
+  if constexpr (BS16 && KV_BITS == 16) {
+    constexpr int kPrefetchGroups = 8;
+    const int grp = s_begin + static_cast<int>(threadIdx.x);
+    if (threadIdx.x < kPrefetchGroups && grp < s_end) {
+      const size_t row16 = (static_cast<size_t>(table[grp]) * p.Hkv + h) * kDmKeys;
+      bulk_prefetch_l2(static_cast<const __nv_bfloat16*>(p.k_pool) + row16 * D, TILE_BYTES);
+      bulk_prefetch_l2(static_cast<const __nv_bfloat16*>(p.v_pool) + row16 * D, TILE_BYTES);
+    }
+  }
+  pdl_wait();
 
   // ---- Q tile (rows >= G are zero)
   for (int i = threadIdx.x; i < 16 * CH; i += kDmThreads) {

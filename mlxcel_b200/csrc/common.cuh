@@ -114,6 +114,17 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
+// Ask the memory system to bring one tile of a tensor map into L2 (no shared memory, no barrier,
+// fire and forget). Same alignment rule for c0 as the load.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0),
+               "r"(c1)
+               : "memory");
+}
+// Untiled variant: `bytes` (multiple of 16) starting at a 16-byte aligned global address.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gptr), "r"(bytes) : "memory");
+}
 // 2-D tiled load into this CTA's shared memory; c0 is the innermost coordinate and must
 // satisfy (c0 * element size) % 16 == 0.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,

@@ -33,6 +33,7 @@ constexpr int kBK = 64;          // K elements per stage (128 bytes of bf16)
 constexpr int kLaneRows = 128;   // UMMA M
 constexpr int kMaxStages = 8;
 constexpr int kGemmThreads = 192;
+constexpr int kSplitDepartOffset = MX_WS_COUNTER_BYTES / 8;   // second half of the counter area
 
 constexpr int kMaxRanks = 8;
 constexpr int kCommMaxTiles = 8192;   // per-tile arrival flags of one channel
@@ -98,6 +99,9 @@ struct GemmParams {
   int splits, kb_per_split, num_kb;
   int tiles_lane, tiles_col;
   int stages;
+  int vec_ok;           // 16-byte vector epilogue allowed (N, strides and base addresses aligned)
+  unsigned long long* trace;   // optional per-CTA phase timestamps (see MX_WS_TRACE_OFFSET)
+  int l2_prefetch_kb;   // k-blocks of weights (beyond the smem ring) to prefetch into L2 before the wait
   int epilogue;
   int out_fp32;
   float glu_alpha, glu_limit;
@@ -175,18 +179,23 @@ __device__ __forceinline__ bool decode_work(const GemmParams& p, int w, GroupCur
   }
 }
 
+// Gated activations, all of the form num * sigmoid(z) * mult, written branch-light with fast
+// exp / divide (relative error ~1e-6, far below bf16 rounding) so the epilogue stays a few dozen
+// instructions: epilogue code runs once per tile and is instruction-fetch bound.
+//   SwiGLU:          silu(g) * u
+//   GeGLU (tanh):    0.5 g (1 + tanh(k0 (g + k1 g^3))) u  ==  g sigmoid(2 k0 (g + k1 g^3)) u
+//   clipped SwiGLU:  g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, +-limit)
 __device__ __forceinline__ float act_glu(int epilogue, float g, float u, float alpha, float limit) {
-  if (epilogue == MX_EPI_SWIGLU) {
-    return g / (1.0f + __expf(-g)) * u;
-  } else if (epilogue == MX_EPI_GEGLU) {
+  float z = g;
+  if (epilogue == MX_EPI_GEGLU) {
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-    float t = tanhf(k0 * (g + k1 * g * g * g));
-    return 0.5f * g * (1.0f + t) * u;
-  } else {  // MX_EPI_CLIPPED_SWIGLU
+    z = 2.0f * k0 * (g + k1 * g * g * g);
+  } else if (epilogue == MX_EPI_CLIPPED_SWIGLU) {
     g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
-    return g / (1.0f + __expf(-alpha * g)) * (u + 1.0f);
+    u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+    z = alpha * g;
   }
+  return __fdividef(g, 1.0f + __expf(-z)) * u;
 }
 
 template <int BN, bool SWAP, bool GLU, int COMM, bool GROUPED>
@@ -216,7 +225,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* ctrl = smem + p.stages * STAGE_BYTES;
+  constexpr int STAGING_BYTES = SWAP ? BN * kLaneRows * 4 : 0;   // epilogue transpose tile (fp32)
+  [[maybe_unused]] float* staging = reinterpret_cast<float*>(smem + p.stages * STAGE_BYTES);
+  uint8_t* ctrl = smem + p.stages * STAGE_BYTES + STAGING_BYTES;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* tmem_full = empty_bar + kMaxStages;
@@ -226,8 +237,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  unsigned long long* const trace =
+      (p.trace != nullptr && blockIdx.x < MX_WS_TRACE_MAX_CTAS) ? p.trace + blockIdx.x * 16 : nullptr;
+  auto stamp = [&](int slot) {
+    if (trace != nullptr) trace[slot] = globaltimer_ns();
+  };
 
+  // producer state set up by thread 0 before the CTA-wide sync (it is also the producer thread)
+  [[maybe_unused]] uint64_t pol_lane = 0, pol_col = 0;
+  [[maybe_unused]] int pre = 0;   // ring stages whose weight tiles are already in flight
+  auto load_lane = [&](uint8_t* s, uint64_t* bar, int kb, int row0) {
+    tma_load_2d(s, &map_lane, bar, kb * kBK, row0, pol_lane);
+    if (LANE_TILES == 2) tma_load_2d(s + LANE_BYTES, &map_lane, bar, kb * kBK, row0 + p.glu_offset, pol_lane);
+  };
+  auto load_col = [&](uint8_t* s, uint64_t* bar, int kb, int row0) {
+    uint8_t* sc = s + LANE_TILES * LANE_BYTES;
+    tma_load_2d(sc, &map_col, bar, kb * kBK, row0, pol_col);
+    if (COL_TILES == 2) tma_load_2d(sc + COL_BYTES, &map_col, bar, kb * kBK, row0 + p.glu_offset, pol_col);
+  };
   if (threadIdx.x == 0) {
+    stamp(0);
     tma_prefetch_desc(&map_lane);
     tma_prefetch_desc(&map_col);
     for (int s = 0; s < p.stages; ++s) {
@@ -239,6 +268,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     mbar_init(&tmem_empty[0], 4);
     mbar_init(&tmem_empty[1], 4);
     fence_mbar_init();
+    // Weights are streamed once (evict first); activations are re-read by every tile.
+    const uint64_t pol_w = l2_policy_evict_first();
+    const uint64_t pol_x = l2_policy_evict_last();
+    pol_lane = SWAP ? pol_w : pol_x;
+    pol_col = SWAP ? pol_x : pol_w;
+    // Weights never depend on the previous kernel: the weight tiles of the first ring of stages
+    // are requested before waiting for it, so the weight stream of this GEMM starts while the
+    // previous kernel is still in its tail / epilogue. Activation tiles follow after the wait.
+    if constexpr (!GROUPED) {
+      GroupCursor c0;
+      WorkItem it0;
+      if (decode_work<BN, SWAP, false>(p, blockIdx.x, c0, it0)) {
+        const int kb0 = it0.split * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        pre = min(p.stages, kb1 - kb0);
+        for (int i = 0; i < pre; ++i) {
+          mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+          uint8_t* s = smem + i * STAGE_BYTES;
+          if (SWAP) load_lane(s, &full_bar[i], kb0 + i, it0.lane_row0);
+          else load_col(s, &full_bar[i], kb0 + i, it0.col_row0);
+        }
+        // The rest of this CTA's weight slice (up to a budget) goes to L2: HBM keeps streaming
+        // through the previous kernels' epilogues and the small kernels in between, and the
+        // main loop below then runs out of the 126 MB L2 instead of waiting on DRAM.
+        if constexpr (SWAP) {
+          const int kbe = min(kb1, kb0 + pre + p.l2_prefetch_kb);
+          for (int kb = kb0 + pre; kb < kbe; ++kb) {
+            tma_prefetch_l2_2d(&map_lane, kb * kBK, it0.lane_row0);
+            if (LANE_TILES == 2) tma_prefetch_l2_2d(&map_lane, kb * kBK, it0.lane_row0 + p.glu_offset);
+          }
+        }
+      }
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_ptr, TMEM_COLS);
@@ -248,44 +310,42 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
-  // Everything above touched only this CTA's shared memory / TMEM; global memory written by the
-  // previous kernel of the stream is read from here on.
+  // Everything above touched only this CTA's shared memory / TMEM. The next kernel of the stream
+  // may be scheduled from here on; each role below waits for the PREVIOUS kernel (pdl_wait) right
+  // before its first access to memory that kernel may have written.
   pdl_trigger();
-  pdl_wait();
+  if (threadIdx.x == 0) stamp(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      // Weights are streamed once (evict first); activations are re-read by every tile.
-      const uint64_t pol_w = l2_policy_evict_first();
-      const uint64_t pol_x = l2_policy_evict_last();
-      const uint64_t pol_lane = SWAP ? pol_w : pol_x;
-      const uint64_t pol_col = SWAP ? pol_x : pol_w;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       GroupCursor cur;
       WorkItem it;
+      pdl_wait();
+      int seq = 0;
       for (int w = blockIdx.x; ok && decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x) {
         const int kb0 = it.split * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         const int lane_row0 = it.lane_row0, col_row0 = it.col_row0;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kErrProducerWait)) {
-            ok = false;
-            break;
-          }
-          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+        for (int kb = kb0; kb < kb1; ++kb, ++seq) {
           uint8_t* s = smem + stage * STAGE_BYTES;
-          tma_load_2d(s, &map_lane, &full_bar[stage], kb * kBK, lane_row0, pol_lane);
-          if (LANE_TILES == 2)
-            tma_load_2d(s + LANE_BYTES, &map_lane, &full_bar[stage], kb * kBK,
-                        lane_row0 + p.glu_offset, pol_lane);
-          uint8_t* sc = s + LANE_TILES * LANE_BYTES;
-          tma_load_2d(sc, &map_col, &full_bar[stage], kb * kBK, col_row0, pol_col);
-          if (COL_TILES == 2)
-            tma_load_2d(sc + COL_BYTES, &map_col, &full_bar[stage], kb * kBK,
-                        col_row0 + p.glu_offset, pol_col);
+          if (seq < pre) {
+            // weight tile already in flight: only the activation tile is missing
+            if (SWAP) load_col(s, &full_bar[stage], kb, col_row0);
+            else load_lane(s, &full_bar[stage], kb, lane_row0);
+          } else {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kErrProducerWait)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+            load_lane(s, &full_bar[stage], kb, lane_row0);
+            load_col(s, &full_bar[stage], kb, col_row0);
+          }
+          if (seq == 0) stamp(2);
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
@@ -297,6 +357,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(BN, false, false);
+      if constexpr (GROUPED) pdl_wait();   // the tile schedule reads expert offsets written upstream
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -316,6 +377,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
             break;
           }
           tc_fence_after_sync();
+          if (kb == kb0 && w == static_cast<int>(blockIdx.x)) stamp(3);
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + LANE_TILES * LANE_BYTES;
 #pragma unroll
@@ -342,6 +404,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
         }
         if (!ok) break;
         umma_commit(&tmem_full[acc]);
+        stamp(4);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -355,6 +418,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool glu = GLU;
+    pdl_wait();   // bias / residual / workspace / channel words below may come from the previous kernel
     [[maybe_unused]] uint32_t comm_parity = 0;
     if constexpr (COMM != 0) comm_parity = *reinterpret_cast<volatile uint32_t*>(p.comm.ctl) & 1u;
     GroupCursor cur;
@@ -363,8 +427,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       const int tile = it.tile, split = it.split;
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kErrEpilogueWait)) break;
       tc_fence_after_sync();
+      if (epi_tid == 0) stamp(5);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * ACC_COLS;
-      bool reduce_from_ws = false;
+      bool reduce_from_ws = false;   // split-K: final values come from the parked partials
+      bool split_ok = true;          // false when the wait for the other splits timed out
       float* ws_tile = nullptr;
       if (p.splits > 1) {
         // Stage 1: park this split's partial tile (column-major: 128 rows contiguous).
@@ -384,19 +450,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);
         __threadfence();
         named_bar_sync(1, 128);
+        // Every split CTA of the tile reduces and finishes its own share of the token rows, so
+        // the tail after the last MMA is one round of loads instead of a whole-tile reduction by
+        // the last arriver. All split CTAs of a tile are resident together (the host keeps
+        // tiles x splits within one wave), so waiting on the arrival counter cannot deadlock.
         if (epi_tid == 0) {
-          const int prev = atomicAdd(&p.counters[tile], 1);
-          const int last = (prev == p.splits - 1) ? 1 : 0;
-          if (last) atomicExch(&p.counters[tile], 0);
-          *last_flag = last;
+          atomicAdd(&p.counters[tile], 1);
+          *last_flag = wait_flag_ge(reinterpret_cast<const uint32_t*>(&p.counters[tile]),
+                                    static_cast<uint32_t>(p.splits), p.status)
+                           ? 1
+                           : 0;
         }
         named_bar_sync(1, 128);
-        reduce_from_ws = (*last_flag != 0);
-        if (!reduce_from_ws) {
-          acc ^= 1;
-          if (acc == 0) acc_phase ^= 1u;
-          continue;
-        }
+        reduce_from_ws = true;
+        split_ok = (*last_flag != 0);
         __threadfence();
       }
 
@@ -405,206 +472,438 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       const int lane_idx = (SWAP ? it.feat0 : it.out_tok0) + row;
       const bool row_ok = row < (SWAP ? it.feat_valid : it.tok_valid);
       const __nv_bfloat16* bias_p = p.bias ? p.bias + it.bias_off : nullptr;
-      float bias_g = 0.f, bias_u = 0.f;
-      if (SWAP && bias_p != nullptr && row_ok) {
-        bias_g = __bfloat162float(bias_p[lane_idx]);
-        if (glu) bias_u = __bfloat162float(bias_p[p.glu_offset + lane_idx]);
-      }
-#pragma unroll 1
-      for (int c = 0; c < BN / CW; ++c) {
-        float v[CW], u[CW];
+      if constexpr (SWAP) {
+        // The accumulator arrives transposed (thread = output feature, columns = tokens) while the
+        // output is token-major. Phase A turns the tile around through shared memory ([token][128
+        // features] fp32); phase B walks it with 8 consecutive features per thread, so residual
+        // loads, global stores and peer pushes are 16-byte vectors. (Two-byte strided stores issued
+        // straight from the accumulator layout were measured at ~100 ns each: 10 us per tile.)
+        // Split-K partials are parked in exactly the phase-B layout, so the reducing CTA skips
+        // phase A and sums them straight from the workspace.
+        const int toks = min(BN, it.tok_valid);
         if (!reduce_from_ws) {
-          uint32_t r[CW];
-          if constexpr (CW == 32) tmem_ld_32x32(taddr + c * CW, r);
-          else tmem_ld_32x16(taddr + c * CW, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]);
-          if (glu) {
-            if constexpr (CW == 32) tmem_ld_32x32(taddr + BN + c * CW, r);
-            else tmem_ld_32x16(taddr + BN + c * CW, r);
+          float bias_g = 0.f, bias_u = 0.f;
+          if (COMM != 1 && bias_p != nullptr && row_ok) {
+            bias_g = __bfloat162float(bias_p[lane_idx]);
+            if (glu) bias_u = __bfloat162float(bias_p[p.glu_offset + lane_idx]);
+          }
+          // narrow chunks when gated: the activation code is fetched once and re-run from the
+          // instruction cache instead of being unrolled 32 times
+          constexpr int CA = GLU ? 16 : CW;
+#pragma unroll 1
+          for (int c = 0; c < BN / CA; ++c) {
+            uint32_t r[CA];
+            float v[CA];
+            if constexpr (CA == 32) tmem_ld_32x32(taddr + c * CA, r);
+            else tmem_ld_32x16(taddr + c * CA, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < CW; ++j) u[j] = __uint_as_float(r[j]);
-          }
-        } else {
+            for (int j = 0; j < CA; ++j) v[j] = __uint_as_float(r[j]) + bias_g;
+            if (glu) {
+              if constexpr (CA == 32) tmem_ld_32x32(taddr + BN + c * CA, r);
+              else tmem_ld_32x16(taddr + BN + c * CA, r);
+              tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < CW; ++j) {
-            v[j] = 0.f;
-            u[j] = 0.f;
-          }
-          for (int s = 0; s < p.splits; ++s) {
-            const float* part = ws_tile + static_cast<size_t>(s) * (kLaneRows * ACC_COLS);
-#pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              v[j] += __ldcg(&part[(c * CW + j) * kLaneRows + row]);
-              if (glu) u[j] += __ldcg(&part[(BN + c * CW + j) * kLaneRows + row]);
+              for (int j = 0; j < CA; ++j)
+                v[j] = act_glu(p.epilogue, v[j], __uint_as_float(r[j]) + bias_u, p.glu_alpha, p.glu_limit);
             }
+#pragma unroll
+            for (int j = 0; j < CA; ++j) staging[(c * CA + j) * kLaneRows + row] = v[j];
           }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          named_bar_sync(1, 128);
         }
-        if (row_ok) {
-          if constexpr (COMM == 1) {
-            // push the bf16 partial (no bias / residual yet) into every peer's slot [rank]
-            const int n = lane_idx;
-            const size_t base = comm_parity * static_cast<size_t>(p.comm.parity_stride) +
-                                p.comm.rank * static_cast<size_t>(p.comm.rank_stride);
+        if (epi_tid == 0) stamp(8);
+        const int seg = epi_tid & 15, tsub = epi_tid >> 4;   // 16 feature segments x 8 tokens per pass
+        const int nl = seg * 8;
+        const int n = it.feat0 + nl;
+        const int nvalid = min(8, it.feat_valid - nl);
+        const bool vec = p.vec_ok != 0 && nvalid == 8;
+        // Token rows of the tile this CTA finishes: all of them, or its share under split-K.
+        int t_begin = 0, t_end = toks;
+        if (reduce_from_ws) {
+          const int per = (toks + p.splits - 1) / p.splits;
+          t_begin = min(toks, split * per);
+          t_end = split_ok ? min(toks, t_begin + per) : t_begin;
+        }
+        constexpr int PU = GLU ? 1 : 2;   // token rows per thread whose loads are in flight together
+
+        // (token rows tl0 + 8 g + tsub, features n .. n+7) after bias / activation
+        auto tile_values = [&](int tl0, float(&o)[PU][8]) {
+          if (!reduce_from_ws) {
 #pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              const int t = it.out_tok0 + c * CW + j;
-              if (c * CW + j < it.tok_valid) {
-                const __nv_bfloat16 b = __float2bfloat16(v[j]);
-                const size_t off = base + static_cast<size_t>(t) * p.N + n;
-                for (int pr = 0; pr < p.comm.world; ++pr) p.comm.recv_peer[pr][off] = b;
+            for (int g = 0; g < PU; ++g) {
+              const int tl = tl0 + g * 8 + tsub;
+              if (tl < t_end) {
+                const float4 a = *reinterpret_cast<const float4*>(staging + tl * kLaneRows + nl);
+                const float4 b = *reinterpret_cast<const float4*>(staging + tl * kLaneRows + nl + 4);
+                o[g][0] = a.x, o[g][1] = a.y, o[g][2] = a.z, o[g][3] = a.w;
+                o[g][4] = b.x, o[g][5] = b.y, o[g][6] = b.z, o[g][7] = b.w;
               }
             }
-          } else if constexpr (COMM == 3) {
-            const int n = lane_idx;
+            return;
+          }
+          // Split-K: the partials of all splits for these rows are requested together (four
+          // splits per batch) and summed in split order, so the result is deterministic.
+          float u[PU][8];
 #pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              const int t = it.out_tok0 + c * CW + j;
-              if (c * CW + j < it.tok_valid) {
-                const __nv_bfloat16 b = __float2bfloat16(v[j] + bias_g);
-                const size_t off = static_cast<size_t>(t) * p.ldo + static_cast<size_t>(p.comm.rank) * p.N + n;
-                for (int pr = 0; pr < p.comm.world; ++pr) p.comm.out_peer[pr][off] = b;
-              }
-            }
-          } else if constexpr (COMM == 2) {
-            // partial tile row -> the owner's slot [rank][tile / world]
-            const int owner = tile % p.comm.world;
-            __nv_bfloat16* dst = p.comm.recv_peer[owner] +
-                                 comm_parity * static_cast<size_t>(p.comm.parity_stride) +
-                                 p.comm.rank * static_cast<size_t>(p.comm.rank_stride) +
-                                 static_cast<size_t>(tile / p.comm.world) * (kLaneRows * BN) +
-                                 static_cast<size_t>(row) * BN + c * CW;
+          for (int g = 0; g < PU; ++g)
 #pragma unroll
-            for (int j8 = 0; j8 < CW; j8 += 8) {
-              uint4 pk;
-              pk.x = pack_bf16(v[j8 + 0], v[j8 + 1]);
-              pk.y = pack_bf16(v[j8 + 2], v[j8 + 3]);
-              pk.z = pack_bf16(v[j8 + 4], v[j8 + 5]);
-              pk.w = pack_bf16(v[j8 + 6], v[j8 + 7]);
-              *reinterpret_cast<uint4*>(dst + j8) = pk;
-            }
-          } else if constexpr (SWAP) {
-            // thread = feature n, columns = tokens
-            const int n = lane_idx;
-            // All residual loads of the chunk are issued before the first store: `out` may
-            // alias `residual`, so interleaving them would serialise one memory latency per token.
-            float rv[CW];
+            for (int j = 0; j < 8; ++j) o[g][j] = 0.f, u[g][j] = 0.f;
+#pragma unroll 1
+          for (int s0 = 0; s0 < p.splits; s0 += 4) {
+            float4 a[PU][4], b[PU][4];
+            [[maybe_unused]] float4 c4[PU][4], d4[PU][4];
 #pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              const int t = it.out_tok0 + c * CW + j;
-              rv[j] = (!glu && p.residual != nullptr && c * CW + j < it.tok_valid)
-                          ? __bfloat162float(p.residual[static_cast<size_t>(t) * p.ldr + n])
-                          : 0.f;
-            }
+            for (int k = 0; k < 4; ++k) {
+              const float* part = ws_tile + static_cast<size_t>(s0 + k) * (kLaneRows * ACC_COLS);
 #pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              const int t = it.out_tok0 + c * CW + j;
-              if (c * CW + j < it.tok_valid) {
-                float val;
-                if (glu) {
-                  val = act_glu(p.epilogue, v[j] + bias_g, u[j] + bias_u, p.glu_alpha, p.glu_limit);
-                } else {
-                  val = v[j] + bias_g + rv[j];
+              for (int g = 0; g < PU; ++g) {
+                const int tl = tl0 + g * 8 + tsub;
+                if (s0 + k < p.splits && tl < t_end) {
+                  a[g][k] = __ldcg(reinterpret_cast<const float4*>(part + tl * kLaneRows + nl));
+                  b[g][k] = __ldcg(reinterpret_cast<const float4*>(part + tl * kLaneRows + nl + 4));
+                  if (glu) {
+                    c4[g][k] = __ldcg(reinterpret_cast<const float4*>(part + (BN + tl) * kLaneRows + nl));
+                    d4[g][k] = __ldcg(reinterpret_cast<const float4*>(part + (BN + tl) * kLaneRows + nl + 4));
+                  }
                 }
-                if (p.out_fp32)
-                  reinterpret_cast<float*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = val;
-                else
-                  reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] =
-                      __float2bfloat16(val);
               }
             }
-          } else {
-            // thread = token m, columns = features
-            const int m = lane_idx;
-            const int nl0 = c * CW;  // first feature of the chunk inside the tile
 #pragma unroll
-            for (int j8 = 0; j8 < CW; j8 += 8) {
-              const int nl = nl0 + j8;
-              const int n = it.feat0 + nl;
-              if (nl >= it.feat_valid) break;
-              float o[8];
-              const bool full8 = (nl + 8 <= it.feat_valid);
+            for (int k = 0; k < 4; ++k) {
+#pragma unroll
+              for (int g = 0; g < PU; ++g) {
+                const int tl = tl0 + g * 8 + tsub;
+                if (s0 + k < p.splits && tl < t_end) {
+                  o[g][0] += a[g][k].x, o[g][1] += a[g][k].y, o[g][2] += a[g][k].z, o[g][3] += a[g][k].w;
+                  o[g][4] += b[g][k].x, o[g][5] += b[g][k].y, o[g][6] += b[g][k].z, o[g][7] += b[g][k].w;
+                  if (glu) {
+                    u[g][0] += c4[g][k].x, u[g][1] += c4[g][k].y, u[g][2] += c4[g][k].z, u[g][3] += c4[g][k].w;
+                    u[g][4] += d4[g][k].x, u[g][5] += d4[g][k].y, u[g][6] += d4[g][k].z, u[g][7] += d4[g][k].w;
+                  }
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int g = 0; g < PU; ++g) {
+            if (COMM != 1 && bias_p != nullptr) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                float val = v[j8 + j];
-                const bool in = full8 || (nl + j < it.feat_valid);
-                if (glu) {
-                  float g = val, uu = u[j8 + j];
-                  if (bias_p != nullptr && in) {
-                    g += __bfloat162float(bias_p[n + j]);
-                    uu += __bfloat162float(bias_p[p.glu_offset + n + j]);
+                if (j < nvalid) {
+                  o[g][j] += __bfloat162float(bias_p[n + j]);
+                  if (glu) u[g][j] += __bfloat162float(bias_p[p.glu_offset + n + j]);
+                }
+              }
+            }
+            if (glu) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                o[g][j] = act_glu(p.epilogue, o[g][j], u[g][j], p.glu_alpha, p.glu_limit);
+            }
+          }
+        };
+        auto add_bf16x8 = [&](const __nv_bfloat16* src, float(&o)[8]) {
+          if (vec) {
+            const uint4 a = *reinterpret_cast<const uint4*>(src);
+            const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              o[2 * j] += bf16_lo(w4[j]);
+              o[2 * j + 1] += bf16_hi(w4[j]);
+            }
+          } else {
+            for (int j = 0; j < nvalid; ++j) o[j] += __bfloat162float(src[j]);
+          }
+        };
+        auto store_bf16x8 = [&](__nv_bfloat16* dst, const float(&o)[8]) {
+          if (vec) {
+            uint4 pk;
+            pk.x = pack_bf16(o[0], o[1]);
+            pk.y = pack_bf16(o[2], o[3]);
+            pk.z = pack_bf16(o[4], o[5]);
+            pk.w = pack_bf16(o[6], o[7]);
+            *reinterpret_cast<uint4*>(dst) = pk;
+          } else {
+            for (int j = 0; j < nvalid; ++j) dst[j] = __float2bfloat16(o[j]);
+          }
+        };
+        auto store_out = [&](size_t off, const float(&o)[8]) {
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.out) + off;
+            if (vec) {
+              reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
+              reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
+            } else {
+              for (int j = 0; j < nvalid; ++j) dst[j] = o[j];
+            }
+          } else {
+            store_bf16x8(reinterpret_cast<__nv_bfloat16*>(p.out) + off, o);
+          }
+        };
+
+
+        if (nvalid > 0) {
+#pragma unroll 1
+          for (int tl0 = t_begin; tl0 < t_end; tl0 += 8 * PU) {
+            float o[PU][8];
+            tile_values(tl0, o);
+            if constexpr (COMM == 0) {
+              // every residual load of the batch is issued before the first store: `out` may alias
+              // `residual`, and interleaving them would serialise one memory latency per token
+              if (!glu && p.residual != nullptr) {
+#pragma unroll
+                for (int g = 0; g < PU; ++g) {
+                  const int tl = tl0 + g * 8 + tsub;
+                  if (tl < t_end)
+                    add_bf16x8(p.residual + static_cast<size_t>(it.out_tok0 + tl) * p.ldr + n, o[g]);
+                }
+              }
+#pragma unroll
+              for (int g = 0; g < PU; ++g) {
+                const int tl = tl0 + g * 8 + tsub;
+                if (tl < t_end) store_out(static_cast<size_t>(it.out_tok0 + tl) * p.ldo + n, o[g]);
+              }
+            } else if constexpr (COMM == 1) {
+              // bf16 partial (no bias / residual yet) into every peer's slot [rank]
+              const size_t base = comm_parity * static_cast<size_t>(p.comm.parity_stride) +
+                                  p.comm.rank * static_cast<size_t>(p.comm.rank_stride);
+#pragma unroll
+              for (int g = 0; g < PU; ++g) {
+                const int tl = tl0 + g * 8 + tsub;
+                if (tl < t_end) {
+                  const size_t off = base + static_cast<size_t>(it.out_tok0 + tl) * p.N + n;
+                  for (int pr = 0; pr < p.comm.world; ++pr) store_bf16x8(p.comm.recv_peer[pr] + off, o[g]);
+                }
+              }
+            } else {  // COMM == 3: logits tile (+ bias) into every peer's gathered output
+#pragma unroll
+              for (int g = 0; g < PU; ++g) {
+                const int tl = tl0 + g * 8 + tsub;
+                if (tl < t_end) {
+                  const size_t off = static_cast<size_t>(it.out_tok0 + tl) * p.ldo +
+                                     static_cast<size_t>(p.comm.rank) * p.N + n;
+                  for (int pr = 0; pr < p.comm.world; ++pr) store_bf16x8(p.comm.out_peer[pr] + off, o[g]);
+                }
+              }
+            }
+          }
+        }
+        if (epi_tid == 0) stamp(9);
+        if constexpr (COMM == 0) {
+          named_bar_sync(1, 128);   // the staging tile is rewritten by the next work item
+        } else if constexpr (COMM == 1) {
+          const CommParams& cm = p.comm;
+          __threadfence_system();
+          named_bar_sync(1, 128);
+          if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + tile, 1u);
+          // one signal per peer from every split CTA of the tile; expect[] advances once per call
+          // (by this CTA when the tile is not split, else by the last split CTA to leave, below)
+          const uint32_t comm_target = cm.expect[tile] + static_cast<uint32_t>(cm.world * p.splits);
+          if (epi_tid == 0) {
+            const bool ok = wait_flag_ge(cm.flags_peer[cm.rank] + tile, comm_target, p.status);
+            if (p.splits == 1) cm.expect[tile] = comm_target;
+            *last_flag = ok ? 1 : 0;
+          }
+          named_bar_sync(1, 128);
+          if (*last_flag != 0 && nvalid > 0) {
+            // every rank sums the same bf16 partials in rank order: bitwise identical results
+            const __nv_bfloat16* base = cm.recv_peer[cm.rank] +
+                                        comm_parity * static_cast<size_t>(cm.parity_stride);
+            constexpr int GRPC = 2;
+#pragma unroll 1
+            for (int tl0 = t_begin; tl0 < t_end; tl0 += 8 * GRPC) {
+              float o[GRPC][8];
+#pragma unroll
+              for (int g = 0; g < GRPC; ++g) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[g][j] = 0.f;
+                const int tl = tl0 + g * 8 + tsub;
+                if (tl < t_end) {
+                  const __nv_bfloat16* src = base + static_cast<size_t>(it.out_tok0 + tl) * p.N + n;
+                  if (vec) {
+                    uint4 a[kMaxRanks];
+#pragma unroll
+                    for (int r = 0; r < kMaxRanks; ++r)
+                      if (r < cm.world)
+                        a[r] = __ldcg(reinterpret_cast<const uint4*>(src + r * static_cast<size_t>(cm.rank_stride)));
+#pragma unroll
+                    for (int r = 0; r < kMaxRanks; ++r) {
+                      if (r < cm.world) {
+                        const uint32_t w4[4] = {a[r].x, a[r].y, a[r].z, a[r].w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                          o[g][2 * j] += bf16_lo(w4[j]);
+                          o[g][2 * j + 1] += bf16_hi(w4[j]);
+                        }
+                      }
+                    }
+                  } else {
+                    for (int r = 0; r < cm.world; ++r)
+                      for (int j = 0; j < nvalid; ++j) {
+                        const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(
+                            src + r * static_cast<size_t>(cm.rank_stride) + j));
+                        o[g][j] += __uint_as_float(static_cast<uint32_t>(raw) << 16);
+                      }
                   }
-                  val = act_glu(p.epilogue, g, uu, p.glu_alpha, p.glu_limit);
-                } else {
-                  if (bias_p != nullptr && in) val += __bfloat162float(bias_p[n + j]);
-                  if (p.residual != nullptr && in)
-                    val += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n + j]);
+                  if (bias_p != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                      if (j < nvalid) o[g][j] += __bfloat162float(bias_p[n + j]);
+                  }
                 }
-                o[j] = val;
               }
-              const size_t off = static_cast<size_t>(m) * p.ldo + n;
-              if (p.out_fp32) {
-                float* dst = reinterpret_cast<float*>(p.out) + off;
-                if (full8 && ((off & 3) == 0)) {
-                  reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
-                  reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
-                } else {
-                  for (int j = 0; j < 8 && nl + j < it.feat_valid; ++j) dst[j] = o[j];
+              if (p.residual != nullptr) {
+#pragma unroll
+                for (int g = 0; g < GRPC; ++g) {
+                  const int tl = tl0 + g * 8 + tsub;
+                  if (tl < t_end)
+                    add_bf16x8(p.residual + static_cast<size_t>(it.out_tok0 + tl) * p.ldr + n, o[g]);
                 }
-              } else {
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
-                if (full8 && ((off & 7) == 0)) {
-                  uint4 pk;
-                  pk.x = pack_bf16(o[0], o[1]);
-                  pk.y = pack_bf16(o[2], o[3]);
-                  pk.z = pack_bf16(o[4], o[5]);
-                  pk.w = pack_bf16(o[6], o[7]);
-                  *reinterpret_cast<uint4*>(dst) = pk;
+              }
+#pragma unroll
+              for (int g = 0; g < GRPC; ++g) {
+                const int tl = tl0 + g * 8 + tsub;
+                if (tl < t_end) store_out(static_cast<size_t>(it.out_tok0 + tl) * p.ldo + n, o[g]);
+              }
+            }
+          }
+        } else {  // COMM == 3
+          const CommParams& cm = p.comm;
+          __threadfence_system();
+          named_bar_sync(1, 128);
+          if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
+        }
+        if (p.splits > 1) {
+          // Leave the tile: the last split CTA to get here (all of them have read the partials
+          // and the arrival counter by then) re-arms the counters for the next launch.
+          if constexpr (COMM != 0) named_bar_sync(1, 128);
+          if (epi_tid == 0) {
+            const int prev = atomicAdd(&p.counters[kSplitDepartOffset + tile], 1);
+            if (prev == p.splits - 1) {
+              p.counters[tile] = 0;
+              p.counters[kSplitDepartOffset + tile] = 0;
+              if constexpr (COMM == 1)
+                p.comm.expect[tile] += static_cast<uint32_t>(p.comm.world * p.splits);
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / CW; ++c) {
+          float v[CW], u[CW];
+          if (!reduce_from_ws) {
+            uint32_t r[CW];
+            if constexpr (CW == 32) tmem_ld_32x32(taddr + c * CW, r);
+            else tmem_ld_32x16(taddr + c * CW, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]);
+            if (glu) {
+              if constexpr (CW == 32) tmem_ld_32x32(taddr + BN + c * CW, r);
+              else tmem_ld_32x16(taddr + BN + c * CW, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < CW; ++j) u[j] = __uint_as_float(r[j]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              v[j] = 0.f;
+              u[j] = 0.f;
+            }
+            for (int s = 0; s < p.splits; ++s) {
+              const float* part = ws_tile + static_cast<size_t>(s) * (kLaneRows * ACC_COLS);
+#pragma unroll
+              for (int j = 0; j < CW; ++j) {
+                v[j] += __ldcg(&part[(c * CW + j) * kLaneRows + row]);
+                if (glu) u[j] += __ldcg(&part[(BN + c * CW + j) * kLaneRows + row]);
+              }
+            }
+          }
+          if (row_ok) {
+            if constexpr (COMM == 2) {
+              // partial tile row -> the owner's slot [rank][tile / world]
+              const int owner = tile % p.comm.world;
+              __nv_bfloat16* dst = p.comm.recv_peer[owner] +
+                                   comm_parity * static_cast<size_t>(p.comm.parity_stride) +
+                                   p.comm.rank * static_cast<size_t>(p.comm.rank_stride) +
+                                   static_cast<size_t>(tile / p.comm.world) * (kLaneRows * BN) +
+                                   static_cast<size_t>(row) * BN + c * CW;
+#pragma unroll
+              for (int j8 = 0; j8 < CW; j8 += 8) {
+                uint4 pk;
+                pk.x = pack_bf16(v[j8 + 0], v[j8 + 1]);
+                pk.y = pack_bf16(v[j8 + 2], v[j8 + 3]);
+                pk.z = pack_bf16(v[j8 + 4], v[j8 + 5]);
+                pk.w = pack_bf16(v[j8 + 6], v[j8 + 7]);
+                *reinterpret_cast<uint4*>(dst + j8) = pk;
+              }
+            } else {
+              // thread = token m, columns = features
+              const int m = lane_idx;
+              const int nl0 = c * CW;  // first feature of the chunk inside the tile
+#pragma unroll
+              for (int j8 = 0; j8 < CW; j8 += 8) {
+                const int nl = nl0 + j8;
+                const int n = it.feat0 + nl;
+                if (nl >= it.feat_valid) break;
+                float o[8];
+                const bool full8 = (nl + 8 <= it.feat_valid);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  float val = v[j8 + j];
+                  const bool in = full8 || (nl + j < it.feat_valid);
+                  if (glu) {
+                    float g = val, uu = u[j8 + j];
+                    if (bias_p != nullptr && in) {
+                      g += __bfloat162float(bias_p[n + j]);
+                      uu += __bfloat162float(bias_p[p.glu_offset + n + j]);
+                    }
+                    val = act_glu(p.epilogue, g, uu, p.glu_alpha, p.glu_limit);
+                  } else {
+                    if (bias_p != nullptr && in) val += __bfloat162float(bias_p[n + j]);
+                    if (p.residual != nullptr && in)
+                      val += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n + j]);
+                  }
+                  o[j] = val;
+                }
+                const size_t off = static_cast<size_t>(m) * p.ldo + n;
+                if (p.out_fp32) {
+                  float* dst = reinterpret_cast<float*>(p.out) + off;
+                  if (full8 && ((off & 3) == 0)) {
+                    reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
+                    reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
+                  } else {
+                    for (int j = 0; j < 8 && nl + j < it.feat_valid; ++j) dst[j] = o[j];
+                  }
                 } else {
-                  for (int j = 0; j < 8 && nl + j < it.feat_valid; ++j) dst[j] = __float2bfloat16(o[j]);
+                  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
+                  if (full8 && ((off & 7) == 0)) {
+                    uint4 pk;
+                    pk.x = pack_bf16(o[0], o[1]);
+                    pk.y = pack_bf16(o[2], o[3]);
+                    pk.z = pack_bf16(o[4], o[5]);
+                    pk.w = pack_bf16(o[6], o[7]);
+                    *reinterpret_cast<uint4*>(dst) = pk;
+                  } else {
+                    for (int j = 0; j < 8 && nl + j < it.feat_valid; ++j) dst[j] = __float2bfloat16(o[j]);
+                  }
                 }
               }
             }
           }
         }
-      }
-      if (!reduce_from_ws) {
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      }
-      if constexpr (COMM == 1) {
-        const CommParams& cm = p.comm;
-        __threadfence_system();
-        named_bar_sync(1, 128);
-        if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + tile, 1u);
-        if (epi_tid == 0) {
-          const uint32_t target = cm.expect[tile] + static_cast<uint32_t>(cm.world);
-          const bool ok = wait_flag_ge(cm.flags_peer[cm.rank] + tile, target, p.status);
-          cm.expect[tile] = target;
-          *last_flag = ok ? 1 : 0;
+        if (!reduce_from_ws) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
         }
-        named_bar_sync(1, 128);
-        if (*last_flag != 0 && row_ok) {
-          const int n = lane_idx;
-          const __nv_bfloat16* base = cm.recv_peer[cm.rank] +
-                                      comm_parity * static_cast<size_t>(cm.parity_stride);
-          for (int t = it.out_tok0; t < it.out_tok0 + min(BN, it.tok_valid); ++t) {
-            float sum = bias_g;
-            for (int r = 0; r < cm.world; ++r) {
-              const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(
-                  base + r * static_cast<size_t>(cm.rank_stride) + static_cast<size_t>(t) * p.N + n));
-              sum += __uint_as_float(static_cast<uint32_t>(raw) << 16);
-            }
-            if (p.residual != nullptr)
-              sum += __bfloat162float(p.residual[static_cast<size_t>(t) * p.ldr + n]);
-            reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] =
-                __float2bfloat16(sum);
-          }
-        }
-      } else if constexpr (COMM == 2) {
+      }
+      if constexpr (COMM == 2) {
         const CommParams& cm = p.comm;
         const int owner = tile % cm.world;
         __threadfence_system();
@@ -667,11 +966,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           named_bar_sync(1, 128);
           if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
         }
-      } else if constexpr (COMM == 3) {
-        const CommParams& cm = p.comm;
-        __threadfence_system();
-        named_bar_sync(1, 128);
-        if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
@@ -682,7 +976,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       if (epi_tid == 0) {
         const CommParams& cm = p.comm;
         const uint32_t tiles = static_cast<uint32_t>(p.tiles_lane * p.tiles_col);
-        const uint32_t per_call = (COMM == 2) ? tiles : (COMM == 3 ? tiles * cm.world : 0u);
+        const uint32_t per_call =
+            (COMM == 2) ? tiles : (COMM == 3 ? tiles * static_cast<uint32_t>(p.splits) * cm.world : 0u);
         if (per_call != 0u) {
           const uint32_t target = *reinterpret_cast<volatile uint32_t*>(cm.ctl + 2) + per_call;
           wait_flag_ge(cm.flags_peer[cm.rank] + kCommDoneIdx, target, p.status);
@@ -700,11 +995,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   }
 
   // ------------------------------------------------------------------ teardown
+  if (threadIdx.x == 64) stamp(6);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+    if (lane == 0) stamp(7);
   }
 }
 
@@ -780,6 +1077,18 @@ bool make_tensor_map_bf16(CUtensorMap* out, const void* ptr, uint64_t rows, uint
   return true;
 }
 
+// Tuning knob: resident CTAs per SM for the small-M weight-streaming path. With 2, the stage ring
+// of each CTA is halved and twice as many (shorter) split-K pieces are in flight, so one CTA's
+// prologue / epilogue latency overlaps the other's main loop.
+int gemm_ctas_per_sm() {
+  static const int v = [] {
+    const char* e = getenv("MLXCEL_B200_GEMM_CTAS_PER_SM");
+    const int n = e ? atoi(e) : 1;
+    return n == 2 ? 2 : 1;
+  }();
+  return v;
+}
+
 int device_sm_count() {
   static int sms[64] = {0};
   int dev = 0;
@@ -793,14 +1102,21 @@ int device_sm_count() {
   return sms[dev];
 }
 
+constexpr int ACC_COLS_HOST(int bn, bool glu) { return glu ? 2 * bn : bn; }
+
 template <int BN, bool SWAP, bool GLU, int COMM = 0, bool GROUPED = false>
 static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams p, int grid,
                        cudaStream_t stream) {
   constexpr int LANE_TILES = (SWAP && GLU) ? 2 : 1;
   constexpr int COL_TILES = (!SWAP && GLU) ? 2 : 1;
   constexpr int STAGE_BYTES = LANE_TILES * kLaneRows * kBK * 2 + COL_TILES * BN * kBK * 2;
-  constexpr int kSmemBudget = 227 * 1024 - 1024 /*align*/ - 256 /*ctrl*/;
+  constexpr int STAGING_BYTES = SWAP ? BN * kLaneRows * 4 : 0;
+  constexpr int kSmemBudget = 227 * 1024 - 1024 /*align*/ - 256 /*ctrl*/ - STAGING_BYTES;
   int stages = kSmemBudget / STAGE_BYTES;
+  if (SWAP && COMM == 0 && !GROUPED && gemm_ctas_per_sm() == 2 && 2 * (2 * ACC_COLS_HOST(BN, GLU)) <= 512) {
+    const int half = (227 * 1024 / 2 - 2048 - 1024 - 256 - STAGING_BYTES) / STAGE_BYTES;
+    if (half >= 3) stages = half;
+  }
   if (stages > kMaxStages) stages = kMaxStages;
   {
     // Tuning knob: cap the stage count (shared-memory footprint) from the environment.
@@ -810,9 +1126,50 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
     }();
     if (cap >= 2 && stages > cap) stages = cap;
   }
+  {
+    // Opt-in (MLXCEL_B200_GEMM_OVERLAP=1): cap the ring so that two consecutive small-M GEMMs fit
+    // on an SM together and the next one prefetches weights while this one drains. Measured
+    // neutral-to-slower than a deep ring on Llama-8B decode, hence off by default.
+    static const bool overlap = [] {
+      const char* e = getenv("MLXCEL_B200_GEMM_OVERLAP");
+      return e != nullptr && e[0] == '1';
+    }();
+    if (overlap && SWAP && !GROUPED && BN <= 64 && gemm_ctas_per_sm() == 1) {
+      const int cap2 = GLU ? 3 : 4;
+      if (stages > cap2) stages = cap2;
+    }
+  }
   if (stages < 2) return -3;
   p.stages = stages;
-  const int smem = stages * STAGE_BYTES + 1024 + 256;
+  {
+    static const bool trace_on = [] {
+      const char* e = getenv("MLXCEL_B200_GEMM_TRACE");
+      return e != nullptr && e[0] == '1';
+    }();
+    // status, counters and partials share one allocation: the trace area sits between them
+    p.trace = (trace_on && p.status != nullptr)
+                  ? reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(p.status) +
+                                                          (MX_WS_TRACE_OFFSET - MX_WS_STATUS_OFFSET))
+                  : nullptr;
+  }
+  {
+    static const int l2_kb = [] {
+      const char* e = getenv("MLXCEL_B200_GEMM_L2_PREFETCH_KB");
+      return e != nullptr ? atoi(e) : 0;
+    }();
+    p.l2_prefetch_kb = (SWAP && !GROUPED && pdl_enabled()) ? (l2_kb * 1024) / (LANE_TILES * kLaneRows * kBK * 2) : 0;
+  }
+  const int smem = stages * STAGE_BYTES + STAGING_BYTES + 1024 + 256;
+  {
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    bool ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && al16(p.out) &&
+              (p.residual == nullptr || (p.ldr % 8 == 0 && al16(p.residual)));
+    if (COMM != 0) {
+      ok = ok && (p.comm.parity_stride % 8 == 0) && (p.comm.rank_stride % 8 == 0);
+      for (int r = 0; r < p.comm.world; ++r) ok = ok && al16(p.comm.recv_peer[r]) && al16(p.comm.out_peer[r]);
+    }
+    p.vec_ok = ok ? 1 : 0;
+  }
   auto kern = gemm_bf16_kernel<BN, SWAP, GLU, COMM, GROUPED>;
   static bool configured = false;
   if (!configured) {
@@ -875,14 +1232,16 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
     p.tiles_lane = (N + kLaneRows - 1) / kLaneRows;
     p.tiles_col = (M + bn - 1) / bn;
     const int tiles = p.tiles_lane * p.tiles_col;
-    int splits = force_splits > 0 ? force_splits : sms / tiles;
+    const int acc_cols = glu ? 2 * bn : bn;
+    const int per_sm = (gemm_ctas_per_sm() == 2 && 4 * acc_cols <= 512) ? 2 : 1;
+    int splits = force_splits > 0 ? force_splits : (per_sm * sms) / tiles;
     if (splits > p.num_kb / 4) splits = p.num_kb / 4;
     if (splits > 16) splits = 16;
     if (splits < 1) splits = 1;
-    const int acc_cols = glu ? 2 * bn : bn;
     const long long ws_floats = (ws_bytes - MX_WS_PARTIAL_OFFSET) / 4;
     while (splits > 1 && (static_cast<long long>(tiles) * splits * kLaneRows * acc_cols > ws_floats ||
-                          tiles > MX_WS_COUNTER_BYTES / 4))
+                          tiles > MX_WS_COUNTER_BYTES / 8 ||
+                          static_cast<long long>(tiles) * splits > static_cast<long long>(per_sm) * sms))
       --splits;
     p.kb_per_split = (p.num_kb + splits - 1) / splits;
     p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
@@ -892,7 +1251,8 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
     p.tiles_col = (N + bn - 1) / bn;
   }
   const long long total = static_cast<long long>(p.tiles_lane) * p.tiles_col * p.splits;
-  const int grid = static_cast<int>(total < sms ? total : sms);
+  const int cap = (swap && gemm_ctas_per_sm() == 2 && 4 * (glu ? 2 * bn : bn) <= 512) ? 2 * sms : sms;
+  const int grid = static_cast<int>(total < cap ? total : cap);
 
   CUtensorMap map_x, map_w;
   const uint32_t x_box = swap ? bn : kLaneRows;
