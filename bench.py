@@ -106,12 +106,18 @@ def main() -> None:
     ap.add_argument("--kv-bits", type=int, default=16)
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--tp-backend", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--watchdog", type=int, default=1500,
+                    help="seconds without finishing a round before every thread's stack is dumped and the "
+                         "process exits (a stuck multi-rank run then ends by itself)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
     if args.warmup < 3:
         args.warmup = 3
 
+    import faulthandler
+
+    faulthandler.dump_traceback_later(args.watchdog, exit=True)   # re-armed at every round
     import torch
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -161,8 +167,16 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    verbose = os.environ.get("MLXCEL_B200_BENCH_VERBOSE") == "1"
+    n_round = [0]
+
     def run_round(prompts):
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
         outs = llm.generate(prompt_token_ids=prompts, sampling_params=sp)
+        n_round[0] += 1
+        if verbose:
+            print(f"[bench rank {rank}] round {n_round[0]} done, status {_lib.read_status(dev)}",
+                  file=sys.stderr, flush=True)
         return outs
 
     for i in range(args.warmup):
@@ -226,7 +240,7 @@ def main() -> None:
                        "parallelism": f"tp{args.gpus}", "kv_block": 16, "kv_bits": args.kv_bits,
                        "l2": "working set (weights + KV pool, > 16 GB) exceeds the 126 MB L2; no flush needed",
                        "step": "one serving round of global_batch requests",
-                       "cuda_graphs": not args.no_graphs, "tp_backend": args.tp_backend if world > 1 else "none"},
+                       "cuda_graphs": not args.no_graphs, "tp_backend": comm.backend if world > 1 else "none"},
             "p50_ttft_ms": round(statistics.median(ttft), 2) if ttft else None,
             "p50_tpot_ms": round(statistics.median(tpot), 3) if tpot else None,
             "clocks": clocks,
@@ -238,8 +252,12 @@ def main() -> None:
         }
         print(json.dumps(out))
     if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+        # Tearing the NCCL communicator down while the symmetric-memory mappings are alive was
+        # seen to block for minutes; every rank is past its last collective here, so leave directly.
+        barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

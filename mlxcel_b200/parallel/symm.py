@@ -90,6 +90,19 @@ class _Channel:
 class FusedOps:
     """GEMM → all-reduce (+bias +residual) and GEMM → all-gather as single kernels."""
 
+    @staticmethod
+    def required_bytes(world: int, max_tokens: int = 8192, hidden: int = 8192, vocab: int = 262144,
+                       small_m: int = 256) -> int:
+        """Heap bytes the channels and buffers below take (what ``SymmetricHeap`` must be sized for)."""
+        ctl = _align(_CHANNEL_WORDS * 4)
+        one = _align(2 * world * small_m * hidden * 2)
+        tiles = ((max_tokens + 127) // 128) * ((hidden + 255) // 256)
+        two = _align(2 * world * ((tiles + world - 1) // world) * 128 * 256 * 2)
+        chunks = (max_tokens * hidden + 8191) // 8192
+        ar_two = _align(2 * world * ((chunks + world - 1) // world) * 8192 * 2)
+        return (5 * ctl + 2 * one + two + ar_two + _align(max_tokens * hidden * 2) + _align(small_m * vocab * 2)
+                + (4 << 20))
+
     def __init__(self, heap: SymmetricHeap, max_tokens: int = 8192, hidden: int = 8192,
                  vocab: int = 262144, small_m: int = 256):
         self.heap = heap

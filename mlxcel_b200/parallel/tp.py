@@ -44,7 +44,8 @@ class TPComm:
             from .symm import SymmetricHeap, FusedOps
 
             try:
-                self.heap = SymmetricHeap(group, device)
+                self.heap = SymmetricHeap(group, device, FusedOps.required_bytes(
+                    self.tp_size, max_tokens=max_tokens, hidden=hidden, vocab=vocab))
                 self.fused = FusedOps(self.heap, max_tokens=max_tokens, hidden=hidden, vocab=vocab)
             except Exception as e:  # symmetric memory unavailable: say so loudly, use NCCL
                 if os.environ.get("MLXCEL_B200_REQUIRE_FUSED") == "1":
