@@ -6,6 +6,8 @@
     python -m mlxcel_b200.utils.profile_cases attn_prefill     # 8 x 1024-token prompts
     python -m mlxcel_b200.utils.profile_cases decode_steps N   # N eager decode steps of the bench workload
     python -m mlxcel_b200.utils.profile_cases kbench           # CUDA-event timings of the hot kernels (JSON lines)
+    python -m mlxcel_b200.utils.profile_cases gemm_graph       # decode GEMMs back to back inside a CUDA graph, us per kernel
+    python -m mlxcel_b200.utils.profile_cases gemm_phases      # per-CTA phase timestamps of the decode GEMMs
 
 Every case holds at most a few GB on the device and launches a handful of kernels, so that a
 capture with ``ncu --set full -k regex:<kernel> -c <n>`` ends by itself. ``decode_steps`` brackets
@@ -145,7 +147,108 @@ def kbench():
                               tflops=round(4 * S * Hq * D * ql * ql / 2 / t / 1e9, 1))), flush=True)
 
 
-CASES = dict(gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
+def gemm_graph(M=64, full=1):
+    """Decode-shape GEMMs as they run inside a decode step: 24 dependent launches over 6 rotating
+    weight copies (no L2 reuse) captured in one CUDA graph; prints us per kernel for this library
+    (split-K forced to several values when ``full``) and for cuBLAS (torch.matmul) under the same
+    conditions, plus the time the weight stream alone would take at the measured copy bandwidth."""
+    nrep, ncopy = 24, 6
+
+    def graph_time(fn):
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                fn()
+        torch.cuda.synchronize()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(7):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2] * 1e3 / nrep
+
+    def case(N, K, glu=False, splits=(0,)):
+        x = _bf(M, K)
+        ws = [_bf(N * (2 if glu else 1), K, scale=0.02) for _ in range(ncopy)]
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        outc = torch.empty(M, N * (2 if glu else 1), dtype=torch.bfloat16, device=DEV)
+        r = dict(M=M, N=N, K=K, glu=glu, stream_us_at_measured_copy_bw=round(ws[0].numel() * 2 / 6.5514e6, 1))
+        for sp in splits:
+            if glu:
+                f = lambda: [ops.glu_linear(x, ws[i % ncopy], N, "silu", out=out, force_splits=sp) for i in range(nrep)]
+            else:
+                f = lambda: [ops.linear(x, ws[i % ncopy], out=out, force_splits=sp) for i in range(nrep)]
+            r[f"us_splits_{sp or 'auto'}"] = round(graph_time(f), 1)
+        r["us_cublas"] = round(graph_time(lambda: [torch.matmul(x, ws[i % ncopy].t(), out=outc) for i in range(nrep)]), 1)
+        print(json.dumps(r), flush=True)
+
+    sp = (0, 1, 2, 4, 8) if full else (0,)
+    case(6144, 4096, splits=sp)
+    case(4096, 4096, splits=sp)
+    case(4096, 14336, splits=sp)
+    case(14336, 4096, glu=True, splits=(0, 2) if full else (0,))
+    # tensor-parallel 8 shards of the same model
+    case(768, 4096, splits=(0,))
+    case(4096, 512, splits=(0,))
+    case(1792, 4096, glu=True, splits=(0,))
+    case(4096, 1792, splits=(0,))
+
+
+def gemm_phases(M=64):
+    """Where a decode GEMM spends its time: device timestamps (globaltimer) that every CTA records
+    at entry, after set-up, at the first load, when the first tile lands, at the last MMA, when
+    the accumulator is ready, before/after the vector epilogue and at exit
+    (MLXCEL_B200_GEMM_TRACE=1 must be set before the library is loaded)."""
+    import os
+
+    import numpy as np
+
+    from ..ops import _lib
+    if os.environ.get("MLXCEL_B200_GEMM_TRACE") != "1":
+        raise SystemExit("set MLXCEL_B200_GEMM_TRACE=1")
+    names = ["entry", "setup", "loads0", "tile0", "mma_end", "acc_ready", "stored", "exit", "phaseB_begin", "phaseB_end"]
+    off, nb = 98304, 256 * 128
+
+    def case(N, K, glu=False):
+        x = _bf(M, K)
+        ws = [_bf(N * (2 if glu else 1), K, scale=0.02) for _ in range(4)]
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        wsp = _lib.workspace(x.device)
+        f = (lambda w: ops.glu_linear(x, w, N, "silu", out=out)) if glu else (lambda w: ops.linear(x, w, out=out))
+        for w in ws:
+            f(w)
+        torch.cuda.synchronize()
+        wsp[off:off + nb].zero_()
+        for w in ws:
+            f(w)
+        torch.cuda.synchronize()
+        t = wsp[off:off + nb].view(torch.int64).view(256, 16).cpu().numpy()
+        t = t[t[:, 0] > 0]
+        r = (t - t[:, 0].min()) / 1e3
+        print(f"M={M} N={N} K={K} glu={glu} ctas={len(t)} span_us={r[:, 7].max():.2f}")
+        for i, n in enumerate(names):
+            c = r[:, i]
+            c = c[c > -1e6]
+            if len(c):
+                print(f"   {n:13s} min {c.min():7.2f} med {np.median(c):7.2f} max {c.max():7.2f}")
+
+    case(4096, 4096)
+    case(6144, 4096)
+    case(4096, 14336)
+    case(14336, 4096, glu=True)
+
+
+CASES = dict(gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
              attn_prefill=attn_prefill, decode_steps=decode_steps, kbench=kbench)
 
 if __name__ == "__main__":
