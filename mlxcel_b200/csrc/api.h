@@ -115,6 +115,16 @@ int mx_paged_prefill(const void* q, long long q_stride, const void* k_pool, cons
                      int block_size, int max_blocks, int window, float scale, float softcap,
                      int kv_bits, void* stream);
 
+// Same contract on the tcgen05 / TMEM / TMA path: bf16 pool with 16-token blocks, D = 64 or 128,
+// no soft cap. Returns -10 when the configuration is not covered (use mx_paged_prefill then).
+// pool_blocks: blocks in k_pool / v_pool; status: the device status word (bounded waits report
+// there). No counterpart in the reference, whose prefill attention is cuDNN SDPA.
+int mx_paged_prefill_tc(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
+                        long long pool_blocks, const int* block_tables, const int* cu_q,
+                        const int* context_lens, const float* sinks, void* out, int num_seqs,
+                        int total_q, int max_q_len, int Hq, int Hkv, int D, int block_size,
+                        int max_blocks, int window, float scale, void* status, void* stream);
+
 // Embedding gather: out[t, :] = table[ids[t], :] (bf16), ids outside [0, vocab) give zeros.
 int mx_embedding(const int* ids, const void* table, void* out, int T, int dim, int vocab,
                  float scale, void* stream);

@@ -356,7 +356,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BN, false, false);
+      // Gated, token-rows-on-lanes: the gate and up weight tiles sit back to back in the stage
+      // (2 x BN rows of one K-major operand), so ONE MMA of N = 2 BN fills both accumulators.
+      constexpr bool kWideGlu = GLU && !SWAP && 2 * BN <= 256;
+      constexpr uint32_t idesc = umma_idesc_bf16(kWideGlu ? 2 * BN : BN, false, false);
       if constexpr (GROUPED) pdl_wait();   // the tile schedule reads expert offsets written upstream
       int stage = 0;
       uint32_t phase = 0;
@@ -386,7 +389,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
             const uint64_t da = umma_desc_k_sw128(sa + kk * 32);
             const uint64_t db = umma_desc_k_sw128(sb + kk * 32);
             umma_bf16(d0, da, db, idesc, accum);
-            if (GLU) {
+            if (GLU && !kWideGlu) {
               if (SWAP) {
                 const uint64_t da2 = umma_desc_k_sw128(sa + LANE_BYTES + kk * 32);
                 umma_bf16(d0 + BN, da2, db, idesc, accum);

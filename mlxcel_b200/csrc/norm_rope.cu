@@ -148,107 +148,229 @@ __global__ void rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* _
                                    const __nv_bfloat16* __restrict__ q_norm_w,
                                    const __nv_bfloat16* __restrict__ k_norm_w, float norm_eps, int T,
                                    int Hq, int Hkv, int D, int rot_dim, int block_size,
-                                   int rope_mode, float mscale) {
+                                   int rope_mode, float mscale, int heads_per_warp) {
   __shared__ float stage[kRopeWarps][kMaxHeadDim];
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = Hq + 2 * Hkv;
+  // A warp owns (token, chunk of `heads_per_warp` head slots): the rotation angles depend on the
+  // token only, so sin / cos are evaluated once per warp and reused for every head of the chunk.
+  const int chunks = (slots + heads_per_warp - 1) / heads_per_warp;
   const long long gw = static_cast<long long>(blockIdx.x) * kRopeWarps + warp;
-  if (gw >= static_cast<long long>(T) * slots) return;
-  const int t = static_cast<int>(gw / slots);
-  const int s = static_cast<int>(gw - static_cast<long long>(t) * slots);
-  const bool is_q = s < Hq;
-  const bool is_k = !is_q && s < Hq + Hkv;
-  const int kvh = is_q ? 0 : (is_k ? s - Hq : s - Hq - Hkv);
-  __nv_bfloat16* src = qkv + static_cast<size_t>(t) * slots * D + static_cast<size_t>(s) * D;
+  if (gw >= static_cast<long long>(T) * chunks) return;
+  const int t = static_cast<int>(gw / chunks);
+  const int s_begin = static_cast<int>(gw - static_cast<long long>(t) * chunks) * heads_per_warp;
+  const int s_end = min(slots, s_begin + heads_per_warp);
   float* st = stage[warp];
-
   const int slot = slot_mapping[t];
-  if (!is_q && slot < 0) return;  // padded token: nothing to append
-
-  float ss = 0.f;
-  for (int i = lane; i < D; i += 32) {
-    float v = __bfloat162float(src[i]);
-    st[i] = v;
-    ss += v * v;
-  }
-  const __nv_bfloat16* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
-  if (nw != nullptr) {
-    ss = warp_sum(ss);
-    const float rstd = rsqrtf(ss / D + norm_eps);
-    __syncwarp();
-    for (int i = lane; i < D; i += 32) {
-      // Round through bf16 like an unfused norm would, then rotate in fp32.
-      st[i] = __bfloat162float(__float2bfloat16(st[i] * rstd * __bfloat162float(nw[i])));
-    }
-  }
-  __syncwarp();
-
-  if (is_q || is_k) {
+  const int half = rot_dim >> 1;
+  float sn[kMaxHeadDim / 64], cs[kMaxHeadDim / 64];
+  if (s_begin < Hq + Hkv) {
     const float pos = static_cast<float>(positions[t]);
-    const int half = rot_dim >> 1;
-    // Each lane rotates pairs p = lane, lane + 32, ...; results go back to the stage.
-    float r1[kMaxHeadDim / 64], r2[kMaxHeadDim / 64];
     int n = 0;
-    for (int p = lane; p < half; p += 32, ++n) {
-      const int i1 = rope_mode == 0 ? p : 2 * p;
-      const int i2 = rope_mode == 0 ? p + half : 2 * p + 1;
-      float sn, cs;
-      sincosf(pos * inv_freq[p], &sn, &cs);
-      const float a = st[i1], b = st[i2];
-      r1[n] = (a * cs - b * sn) * mscale;
-      r2[n] = (b * cs + a * sn) * mscale;
-    }
-    __syncwarp();
-    n = 0;
-    for (int p = lane; p < half; p += 32, ++n) {
-      const int i1 = rope_mode == 0 ? p : 2 * p;
-      const int i2 = rope_mode == 0 ? p + half : 2 * p + 1;
-      st[i1] = r1[n];
-      st[i2] = r2[n];
-    }
-    if (mscale != 1.0f) {
-      for (int i = rot_dim + lane; i < D; i += 32) st[i] *= mscale;
-    }
-    __syncwarp();
+    for (int p = lane; p < half; p += 32, ++n) sincosf(pos * inv_freq[p], &sn[n], &cs[n]);
   }
+  for (int s = s_begin; s < s_end; ++s) {
+    const bool is_q = s < Hq;
+    const bool is_k = !is_q && s < Hq + Hkv;
+    const int kvh = is_q ? 0 : (is_k ? s - Hq : s - Hq - Hkv);
+    __nv_bfloat16* src = qkv + static_cast<size_t>(t) * slots * D + static_cast<size_t>(s) * D;
+    if (!is_q && slot < 0) continue;  // padded token: nothing to append
+    __syncwarp();
 
-  if (is_q) {
-    for (int i = lane; i < D; i += 32) src[i] = __float2bfloat16(st[i]);
-    return;
-  }
-
-  const int blk = slot / block_size, off = slot - blk * block_size;
-  const size_t row = (static_cast<size_t>(blk) * Hkv + kvh) * block_size + off;
-  if (KV_BITS == 16) {
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(is_k ? k_pool : v_pool) + row * D;
-    for (int i = lane; i < D; i += 32) dst[i] = __float2bfloat16(st[i]);
-  } else {
-    // 8-bit affine, groups of 64 along D: q = round((x - min) / scale), scale = (max - min) / 255.
-    uint8_t* dst = reinterpret_cast<uint8_t*>(is_k ? k_pool : v_pool) + row * D;
-    __nv_bfloat16* meta = (is_k ? k_meta : v_meta) + row * (D / 64) * 2;
-    for (int g = 0; g < D / 64; ++g) {
-      const float a = st[g * 64 + lane], b = st[g * 64 + 32 + lane];
-      float mn = fminf(a, b), mxv = fmaxf(a, b);
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-        mxv = fmaxf(mxv, __shfl_xor_sync(0xffffffffu, mxv, o));
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      float v = __bfloat162float(src[i]);
+      st[i] = v;
+      ss += v * v;
+    }
+    const __nv_bfloat16* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    if (nw != nullptr) {
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / D + norm_eps);
+      __syncwarp();
+      for (int i = lane; i < D; i += 32) {
+        // Round through bf16 like an unfused norm would, then rotate in fp32.
+        st[i] = __bfloat162float(__float2bfloat16(st[i] * rstd * __bfloat162float(nw[i])));
       }
-      // Scale and bias are stored in bf16; quantize against the rounded values so that
-      // dequantization reproduces what the quantizer saw.
-      float scale = __bfloat162float(__float2bfloat16((mxv - mn) / 255.0f));
-      const float bias = __bfloat162float(__float2bfloat16(mn));
-      if (scale == 0.f) scale = 1.0f;
-      const float inv = 1.0f / scale;
-      const int qa = min(255, max(0, __float2int_rn((a - bias) * inv)));
-      const int qb = min(255, max(0, __float2int_rn((b - bias) * inv)));
-      dst[g * 64 + lane] = static_cast<uint8_t>(qa);
-      dst[g * 64 + 32 + lane] = static_cast<uint8_t>(qb);
-      if (lane == 0) {
-        meta[g * 2] = __float2bfloat16(scale);
-        meta[g * 2 + 1] = __float2bfloat16(bias);
+    }
+    __syncwarp();
+
+    if (is_q || is_k) {
+      // Each lane rotates pairs p = lane, lane + 32, ...; results go back to the stage.
+      float r1[kMaxHeadDim / 64], r2[kMaxHeadDim / 64];
+      int n = 0;
+      for (int p = lane; p < half; p += 32, ++n) {
+        const int i1 = rope_mode == 0 ? p : 2 * p;
+        const int i2 = rope_mode == 0 ? p + half : 2 * p + 1;
+        const float a = st[i1], b = st[i2];
+        r1[n] = (a * cs[n] - b * sn[n]) * mscale;
+        r2[n] = (b * cs[n] + a * sn[n]) * mscale;
+      }
+      __syncwarp();
+      n = 0;
+      for (int p = lane; p < half; p += 32, ++n) {
+        const int i1 = rope_mode == 0 ? p : 2 * p;
+        const int i2 = rope_mode == 0 ? p + half : 2 * p + 1;
+        st[i1] = r1[n];
+        st[i2] = r2[n];
+      }
+      if (mscale != 1.0f) {
+        for (int i = rot_dim + lane; i < D; i += 32) st[i] *= mscale;
+      }
+      __syncwarp();
+    }
+
+    if (is_q) {
+      for (int i = lane; i < D; i += 32) src[i] = __float2bfloat16(st[i]);
+      continue;
+    }
+
+    const int blk = slot / block_size, off = slot - blk * block_size;
+    const size_t row = (static_cast<size_t>(blk) * Hkv + kvh) * block_size + off;
+    if (KV_BITS == 16) {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(is_k ? k_pool : v_pool) + row * D;
+      for (int i = lane; i < D; i += 32) dst[i] = __float2bfloat16(st[i]);
+    } else {
+      // 8-bit affine, groups of 64 along D: q = round((x - min) / scale), scale = (max - min) / 255.
+      uint8_t* dst = reinterpret_cast<uint8_t*>(is_k ? k_pool : v_pool) + row * D;
+      __nv_bfloat16* meta = (is_k ? k_meta : v_meta) + row * (D / 64) * 2;
+      for (int g = 0; g < D / 64; ++g) {
+        const float a = st[g * 64 + lane], b = st[g * 64 + 32 + lane];
+        float mn = fminf(a, b), mxv = fmaxf(a, b);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+          mxv = fmaxf(mxv, __shfl_xor_sync(0xffffffffu, mxv, o));
+        }
+        // Scale and bias are stored in bf16; quantize against the rounded values so that
+        // dequantization reproduces what the quantizer saw.
+        float scale = __bfloat162float(__float2bfloat16((mxv - mn) / 255.0f));
+        const float bias = __bfloat162float(__float2bfloat16(mn));
+        if (scale == 0.f) scale = 1.0f;
+        const float inv = 1.0f / scale;
+        const int qa = min(255, max(0, __float2int_rn((a - bias) * inv)));
+        const int qb = min(255, max(0, __float2int_rn((b - bias) * inv)));
+        dst[g * 64 + lane] = static_cast<uint8_t>(qa);
+        dst[g * 64 + 32 + lane] = static_cast<uint8_t>(qb);
+        if (lane == 0) {
+          meta[g * 2] = __float2bfloat16(scale);
+          meta[g * 2 + 1] = __float2bfloat16(bias);
+        }
+      }
+    }
+  }
+}
+
+// Fast path of rope_append: half-split rotation over the whole head (rot_dim == D), bf16 pool,
+// D = 64 or 128. A warp owns (token, chunk of head slots); each lane holds D/32 elements of a
+// head in registers (the pair halves p and p + D/2 sit in the same lane), four heads are loaded
+// before any is stored so the loads overlap, and sin / cos are evaluated once per warp.
+template <int D, bool NORM>
+__global__ void rope_append_fast_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                        const int* __restrict__ slot_mapping,
+                                        const float* __restrict__ inv_freq, __nv_bfloat16* __restrict__ k_pool,
+                                        __nv_bfloat16* __restrict__ v_pool,
+                                        const __nv_bfloat16* __restrict__ q_norm_w,
+                                        const __nv_bfloat16* __restrict__ k_norm_w, float norm_eps, int T,
+                                        int Hq, int Hkv, int block_size, float mscale, int heads_per_warp) {
+  constexpr int E = D / 64;          // elements per lane in each half (1 or 2)
+  constexpr int HALF = D / 2;
+  constexpr int HB = 4;              // heads in flight
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = Hq + 2 * Hkv;
+  const int chunks = (slots + heads_per_warp - 1) / heads_per_warp;
+  const long long gw = static_cast<long long>(blockIdx.x) * kRopeWarps + warp;
+  if (gw >= static_cast<long long>(T) * chunks) return;
+  const int t = static_cast<int>(gw / chunks);
+  const int s_begin = static_cast<int>(gw - static_cast<long long>(t) * chunks) * heads_per_warp;
+  const int s_end = min(slots, s_begin + heads_per_warp);
+  const int slot = slot_mapping[t];
+  float sn[E], cs[E];
+  if (s_begin < Hq + Hkv) {
+    const float pos = static_cast<float>(positions[t]);
+#pragma unroll
+    for (int e = 0; e < E; ++e) sincosf(pos * inv_freq[lane * E + e], &sn[e], &cs[e]);
+  }
+  [[maybe_unused]] float qw[2][E], kw[2][E];   // norm weights of this lane's elements
+  if (NORM) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      qw[0][e] = q_norm_w ? __bfloat162float(q_norm_w[lane * E + e]) : 1.f;
+      qw[1][e] = q_norm_w ? __bfloat162float(q_norm_w[HALF + lane * E + e]) : 1.f;
+      kw[0][e] = k_norm_w ? __bfloat162float(k_norm_w[lane * E + e]) : 1.f;
+      kw[1][e] = k_norm_w ? __bfloat162float(k_norm_w[HALF + lane * E + e]) : 1.f;
+    }
+  }
+  __nv_bfloat16* row = qkv + static_cast<size_t>(t) * slots * D;
+  const int blk = slot >= 0 ? slot / block_size : 0;
+  const int off = slot >= 0 ? slot - blk * block_size : 0;
+  for (int s0 = s_begin; s0 < s_end; s0 += HB) {
+    float a[HB][E], b[HB][E];
+#pragma unroll
+    for (int i = 0; i < HB; ++i) {
+      const int s = s0 + i;
+      if (s < s_end) {
+        const __nv_bfloat16* src = row + static_cast<size_t>(s) * D + lane * E;
+        if constexpr (E == 2) {
+          const uint32_t lo = *reinterpret_cast<const uint32_t*>(src);
+          const uint32_t hi = *reinterpret_cast<const uint32_t*>(src + HALF);
+          a[i][0] = bf16_lo(lo), a[i][1] = bf16_hi(lo);
+          b[i][0] = bf16_lo(hi), b[i][1] = bf16_hi(hi);
+        } else {
+          a[i][0] = __bfloat162float(src[0]);
+          b[i][0] = __bfloat162float(src[HALF]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < HB; ++i) {
+      const int s = s0 + i;
+      if (s >= s_end) break;
+      const bool is_q = s < Hq;
+      const bool is_k = !is_q && s < Hq + Hkv;
+      if (!is_q && slot < 0) continue;   // padded token: nothing to append
+      if (NORM && (is_q ? q_norm_w != nullptr : (is_k && k_norm_w != nullptr))) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) ss += a[i][e] * a[i][e] + b[i][e] * b[i][e];
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / D + norm_eps);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          // round through bf16 like an unfused norm would, then rotate in fp32
+          a[i][e] = __bfloat162float(__float2bfloat16(a[i][e] * rstd * (is_q ? qw[0][e] : kw[0][e])));
+          b[i][e] = __bfloat162float(__float2bfloat16(b[i][e] * rstd * (is_q ? qw[1][e] : kw[1][e])));
+        }
+      }
+      float r1[E], r2[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        if (is_q || is_k) {
+          r1[e] = (a[i][e] * cs[e] - b[i][e] * sn[e]) * mscale;
+          r2[e] = (b[i][e] * cs[e] + a[i][e] * sn[e]) * mscale;
+        } else {
+          r1[e] = a[i][e];
+          r2[e] = b[i][e];
+        }
+      }
+      __nv_bfloat16* dst;
+      if (is_q) {
+        dst = row + static_cast<size_t>(s) * D;
+      } else {
+        const int kvh = is_k ? s - Hq : s - Hq - Hkv;
+        dst = (is_k ? k_pool : v_pool) + ((static_cast<size_t>(blk) * Hkv + kvh) * block_size + off) * D;
+      }
+      dst += lane * E;
+      if constexpr (E == 2) {
+        *reinterpret_cast<uint32_t*>(dst) = pack_bf16(r1[0], r1[1]);
+        *reinterpret_cast<uint32_t*>(dst + HALF) = pack_bf16(r2[0], r2[1]);
+      } else {
+        dst[0] = __float2bfloat16(r1[0]);
+        dst[HALF] = __float2bfloat16(r2[0]);
       }
     }
   }
@@ -359,8 +481,39 @@ extern "C" int mx_rope_append(void* qkv, const int* positions, const int* slot_m
   if (D > kMaxHeadDim || D % 2 || rot_dim > D || rot_dim % 2) return -1;
   if (kv_bits == 8 && D % 64) return -1;
   if (kv_bits != 16 && kv_bits != 8) return -1;
-  const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
+  // Few tokens (decode): few heads per warp for parallelism; many tokens (prefill): all heads of a
+  // token in one warp so the sin / cos evaluation is shared 40-fold.
+  const int slots = Hq + 2 * Hkv;
+  int hpw = 1;
+  while (hpw < slots && static_cast<long long>(T) * ((slots + hpw - 1) / hpw) > 4096) hpw *= 2;
+  if (hpw > slots) hpw = slots;
+  const long long warps = static_cast<long long>(T) * ((slots + hpw - 1) / hpw);
   const int blocks = static_cast<int>((warps + kRopeWarps - 1) / kRopeWarps);
+  if (kv_bits == 16 && rope_mode == 0 && rot_dim == D && (D == 64 || D == 128)) {
+    // register-resident fast path: up to 8 heads per warp (sin / cos shared, 4 heads in flight)
+    int h2 = 1;
+    while (h2 < 8 && static_cast<long long>(T) * ((slots + h2 - 1) / h2) > 65536) h2 *= 2;
+    const long long w2 = static_cast<long long>(T) * ((slots + h2 - 1) / h2);
+    const int b2 = static_cast<int>((w2 + kRopeWarps - 1) / kRopeWarps);
+    auto Qf = static_cast<__nv_bfloat16*>(qkv);
+    auto KP = static_cast<__nv_bfloat16*>(k_pool);
+    auto VP = static_cast<__nv_bfloat16*>(v_pool);
+    auto QNf = static_cast<const __nv_bfloat16*>(q_norm_w);
+    auto KNf = static_cast<const __nv_bfloat16*>(k_norm_w);
+    const bool norm = q_norm_w != nullptr || k_norm_w != nullptr;
+#define MX_ROPE_FAST(D_, N_)                                                                              \
+    launch_kernel(rope_append_fast_kernel<D_, N_>, dim3(b2), dim3(kRopeWarps * 32), 0, stream, Qf, positions, \
+                  slot_mapping, inv_freq, KP, VP, QNf, KNf, norm_eps, T, Hq, Hkv, block_size, mscale, h2)
+    if (D == 128) {
+      if (norm) MX_ROPE_FAST(128, true);
+      else MX_ROPE_FAST(128, false);
+    } else {
+      if (norm) MX_ROPE_FAST(64, true);
+      else MX_ROPE_FAST(64, false);
+    }
+#undef MX_ROPE_FAST
+    return static_cast<int>(cudaGetLastError());
+  }
   auto Q = static_cast<__nv_bfloat16*>(qkv);
   auto KM = static_cast<__nv_bfloat16*>(k_meta);
   auto VM = static_cast<__nv_bfloat16*>(v_meta);
@@ -371,11 +524,11 @@ extern "C" int mx_rope_append(void* qkv, const int* positions, const int* slot_m
   if (kv_bits == 16)
     launch_kernel(rope_append_kernel<16>, dim3(blocks), dim3(kRopeWarps * 32), 0, stream, Q, positions,
                   slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv, D, rot_dim,
-                  block_size, rope_mode, mscale);
+                  block_size, rope_mode, mscale, hpw);
   else
     launch_kernel(rope_append_kernel<8>, dim3(blocks), dim3(kRopeWarps * 32), 0, stream, Q, positions,
                   slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv, D, rot_dim,
-                  block_size, rope_mode, mscale);
+                  block_size, rope_mode, mscale, hpw);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -6,6 +6,8 @@ PyTorch statements in :mod:`mlxcel_b200.ops.reference`, which are also the test 
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 
 import torch
@@ -174,6 +176,9 @@ def paged_decode(q: torch.Tensor, kv: KVLayer, block_tables: torch.Tensor,
     return out
 
 
+_PREFILL_TC = os.environ.get("MLXCEL_B200_PREFILL_TC", "1") != "0"
+
+
 def paged_prefill(q: torch.Tensor, kv: KVLayer, block_tables: torch.Tensor, cu_q: torch.Tensor,
                   context_lens: torch.Tensor, *, Hq: int, Hkv: int, D: int, scale: float,
                   max_q_len: int, window: int = 0, sinks: torch.Tensor | None = None,
@@ -188,6 +193,19 @@ def paged_prefill(q: torch.Tensor, kv: KVLayer, block_tables: torch.Tensor, cu_q
     if T == 0:
         return out
     S = context_lens.shape[0]
+    if (_PREFILL_TC and kv.kv_bits == 16 and kv.block_size == 16 and D in (64, 128) and softcap == 0.0
+            and kv.k.dtype == torch.bfloat16 and q.stride(0) % 8 == 0):
+        # tensor-core (tcgen05) kernel; -10 = configuration not covered, fall through
+        lib = _lib.load()
+        ws = _lib.workspace(q.device)
+        rc = lib.mx_paged_prefill_tc(q.data_ptr(), q.stride(0), kv.k.data_ptr(), kv.v.data_ptr(), kv.k.shape[0],
+                                     block_tables.data_ptr(), cu_q.data_ptr(), context_lens.data_ptr(),
+                                     _lib.ptr(sinks), out.data_ptr(), S, T, max_q_len, Hq, Hkv, D, kv.block_size,
+                                     block_tables.shape[1], window, float(scale), ws.data_ptr(), _lib.stream())
+        if rc != -10:
+            _lib.count_launch()
+            _lib.check(rc, "mx_paged_prefill_tc")
+            return out
     _lib_call("mx_paged_prefill", q.data_ptr(), q.stride(0), kv.k.data_ptr(), kv.v.data_ptr(),
               _lib.ptr(kv.k_meta), _lib.ptr(kv.v_meta), block_tables.data_ptr(), cu_q.data_ptr(),
               context_lens.data_ptr(), _lib.ptr(sinks), out.data_ptr(), S, T, max_q_len, Hq, Hkv, D,

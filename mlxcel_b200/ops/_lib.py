@@ -69,6 +69,8 @@ def _declare(lib) -> None:
                             _i, _i, _i, _f, _f, _i, _i, _vp],
         "mx_paged_prefill": [_vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                              _i, _i, _i, _i, _i, _f, _f, _i, _vp],
+        "mx_paged_prefill_tc": [_vp, _ll, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                _i, _i, _i, _f, _vp, _vp],
         "mx_embedding": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "mx_argmax": [_vp, _i, _ll, _vp, _i, _i, _vp],
         "mx_sample": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],

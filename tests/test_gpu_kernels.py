@@ -220,6 +220,36 @@ def test_paged_prefill(Hq, Hkv, D, bits, window, sinks):
     _close(got, want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("tc", [True, False])
+@pytest.mark.parametrize("Hq,Hkv,D,window,sinks", [(8, 2, 128, 0, False), (4, 1, 64, 300, True), (4, 4, 128, 130, False)])
+def test_paged_prefill_long(monkeypatch, tc, Hq, Hkv, D, window, sinks):
+    """Many key tiles per query tile (running-max rescaling, window edges inside tiles, a prefix
+    longer than the chunk) on the tensor-core kernel and on the fallback."""
+    monkeypatch.setattr(ops, "_PREFILL_TC", tc)
+    bs, nb = 16, 512
+    ctx = [1500, 700, 257]
+    qlen = [900, 700, 130]
+    kv = _pool(nb, Hkv, bs, D, 16)
+    _fill_pool(kv, 7)
+    tab = _tables(ctx, bs, nb, 96)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0] + list(torch.tensor(qlen).cumsum(0)), dtype=torch.int32, device=DEV)
+    T = sum(qlen)
+    # a few large logits so that the running maximum moves by more than the rescaling threshold
+    qkv = _bf(T, (Hq + 2 * Hkv) * D, seed=11)
+    qkv[::37] *= 6.0
+    q = qkv[:, : Hq * D]
+    sk = torch.randn(Hq, device=DEV) if sinks else None
+    scale = 1.0 / math.sqrt(D)
+    got = ops.paged_prefill(q, kv, tab, cu, cl, Hq=Hq, Hkv=Hkv, D=D, scale=scale, max_q_len=max(qlen),
+                            window=window, sinks=sk)
+    want = ref.paged_attention(q, kv, tab, cl, cu, Hq=Hq, Hkv=Hkv, D=D, scale=scale, window=window,
+                               sinks=sk)
+    _close(got, want, rtol=2e-2, atol=2e-2)
+    from mlxcel_b200.ops import _lib
+    assert _lib.read_status(torch.device(DEV)) == 0
+
+
 # ----------------------------------------------------------------------------- misc + sampling
 def test_embedding_argmax():
     table = _bf(1000, 256, seed=1)
