@@ -23,8 +23,8 @@ extern "C" {
 #define MX_WS_PARTIAL_OFFSET 131072
 /* Phase timestamps of the last GEMM launch (MLXCEL_B200_GEMM_TRACE=1): 16 x uint64 (globaltimer ns)
  * per CTA: entry, set-up done, first loads issued, first tile landed, last MMA committed,
- * accumulator ready, results stored, exit; then per epilogue chunk c < 4: [8 + 2c] values loaded,
- * [9 + 2c] stores issued. No counterpart in the reference. */
+ * accumulator ready, results stored, exit; [8] vector epilogue begins, [9] its stores / peer pushes issued,
+ * [10] all peers' partials arrived (fused all-reduce). No counterpart in the reference. */
 #define MX_WS_TRACE_OFFSET 98304
 #define MX_WS_TRACE_MAX_CTAS 256
 

@@ -82,8 +82,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p)
         }
       }
     }
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();   // then one releasing thread per peer signals (release is cumulative)
     if (p.mode == 1) {
       if (threadIdx.x < p.world) ar_signal(p.flags_peer[threadIdx.x] + c);
     } else if (threadIdx.x == 0) {
@@ -138,7 +137,6 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p)
         }
       }
       if (p.mode == 2) {
-        __threadfence_system();
         __syncthreads();
         if (threadIdx.x < p.world) ar_signal(p.flags_peer[threadIdx.x] + kArDoneIdx);
       }

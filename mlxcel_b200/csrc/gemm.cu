@@ -46,7 +46,7 @@ constexpr int kCommDoneIdx = kCommMaxTiles;  // flag index of the per-call compl
 //           each peer, waits for `world` arrivals on its own flag and sums the slots in rank
 //           order (+ bias + residual), so all ranks hold bitwise identical results.
 //   COMM 2  two-shot all-reduce (token-rows-on-lanes tiles, large M): tile t is owned by rank
-//           t % world; partial tiles go to the owner only, the owner reduces (+ bias + residual)
+//           (t + t / 152) % world; partial tiles go to the owner only, the owner reduces (+ bias + residual)
 //           and stores the finished tile into every peer's output buffer; a per-call completion
 //           counter tells each rank when all tiles have landed.
 //   COMM 3  all-gather: the tile is stored into every peer's output at column offset rank * N.
@@ -62,6 +62,10 @@ struct CommParams {
   long long rank_stride;    // elements between source-rank slots
 };
 
+// Release at system scope: the writes of the whole CTA are ordered before the flag update when
+// the CTA meets at a barrier first and one thread then signals (release is cumulative over what
+// the barrier made visible to the signalling thread). One releasing thread per peer replaces a
+// system-scope fence in every thread, which cost several microseconds per tile.
 __device__ __forceinline__ void signal_add_sys(uint32_t* addr, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
@@ -196,6 +200,66 @@ __device__ __forceinline__ float act_glu(int epilogue, float g, float u, float a
     z = alpha * g;
   }
   return __fdividef(g, 1.0f + __expf(-z)) * u;
+}
+
+// Owner rank of a tile in the two-shot all-reduce. A persistent CTA walks tiles b, b + grid,
+// b + 2 grid, ...; with `tile % world` and an even grid it would own either all or none of them
+// (the owner's epilogue is the heavy one). The extra term shifts ownership by one every 152 tiles
+// (152 is a multiple of every supported world size, so the `world` tiles of an aligned group
+// still have distinct owners and `tile / world` stays a valid slot index per owner).
+__device__ __forceinline__ int comm2_owner(int tile, int world) { return (tile + tile / 152) % world; }
+
+// Owner-side reduction of the two-shot all-reduce for one token row: features [j0, j0 + 8 NQ) of
+// the tile (bounded by nfeat), partials of `world` <= WMAX ranks at `base + r * rank_stride`.
+template <int NQ, int WMAX>
+__device__ __forceinline__ void comm2_reduce_span(const __nv_bfloat16* base, long long rank_stride, int world,
+                                                  const __nv_bfloat16* bias_n, const __nv_bfloat16* res_n,
+                                                  __nv_bfloat16* const* out_peer, size_t off0, int j0,
+                                                  int nfeat) {
+  uint4 a[NQ][WMAX];
+  uint4 rs[NQ];
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) {
+    const int j = j0 + q * 8;
+    if (j < nfeat) {
+#pragma unroll
+      for (int r = 0; r < WMAX; ++r)
+        if (r < world)
+          a[q][r] = __ldcg(reinterpret_cast<const uint4*>(base + r * static_cast<size_t>(rank_stride) + j));
+      if (res_n != nullptr) rs[q] = *reinterpret_cast<const uint4*>(res_n + j);
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) {
+    const int j = j0 + q * 8;
+    if (j >= nfeat) break;
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = 0.f;
+#pragma unroll
+    for (int r = 0; r < WMAX; ++r) {
+      if (r < world) {
+        const uint32_t w4[4] = {a[q][r].x, a[q][r].y, a[q][r].z, a[q][r].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[2 * i] += bf16_lo(w4[i]), o[2 * i + 1] += bf16_hi(w4[i]);
+      }
+    }
+    if (bias_n != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] += __bfloat162float(bias_n[j + i]);
+    }
+    if (res_n != nullptr) {
+      const uint32_t w4[4] = {rs[q].x, rs[q].y, rs[q].z, rs[q].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[2 * i] += bf16_lo(w4[i]), o[2 * i + 1] += bf16_hi(w4[i]);
+    }
+    uint4 pk;
+    pk.x = pack_bf16(o[0], o[1]);
+    pk.y = pack_bf16(o[2], o[3]);
+    pk.z = pack_bf16(o[4], o[5]);
+    pk.w = pack_bf16(o[6], o[7]);
+    for (int pr = 0; pr < world; ++pr) *reinterpret_cast<uint4*>(out_peer[pr] + off0 + j) = pk;
+  }
 }
 
 template <int BN, bool SWAP, bool GLU, int COMM, bool GROUPED>
@@ -700,8 +764,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           named_bar_sync(1, 128);   // the staging tile is rewritten by the next work item
         } else if constexpr (COMM == 1) {
           const CommParams& cm = p.comm;
-          __threadfence_system();
           named_bar_sync(1, 128);
+          if (epi_tid == 0) stamp(11);
           if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + tile, 1u);
           // one signal per peer from every split CTA of the tile; expect[] advances once per call
           // (by this CTA when the tile is not split, else by the last split CTA to leave, below)
@@ -712,6 +776,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
             *last_flag = ok ? 1 : 0;
           }
           named_bar_sync(1, 128);
+          if (epi_tid == 0) stamp(10);
           if (*last_flag != 0 && nvalid > 0) {
             // every rank sums the same bf16 partials in rank order: bitwise identical results
             const __nv_bfloat16* base = cm.recv_peer[cm.rank] +
@@ -776,7 +841,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           }
         } else {  // COMM == 3
           const CommParams& cm = p.comm;
-          __threadfence_system();
           named_bar_sync(1, 128);
           if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
         }
@@ -830,7 +894,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           if (row_ok) {
             if constexpr (COMM == 2) {
               // partial tile row -> the owner's slot [rank][tile / world]
-              const int owner = tile % p.comm.world;
+              const int owner = comm2_owner(tile, p.comm.world);
               __nv_bfloat16* dst = p.comm.recv_peer[owner] +
                                    comm_parity * static_cast<size_t>(p.comm.parity_stride) +
                                    p.comm.rank * static_cast<size_t>(p.comm.rank_stride) +
@@ -849,6 +913,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
               // thread = token m, columns = features
               const int m = lane_idx;
               const int nl0 = c * CW;  // first feature of the chunk inside the tile
+              // The residual of the whole chunk is fetched with 16-byte loads before the first
+              // store (`out` may alias it, so loads issued between stores would each wait out a
+              // full memory latency).
+              const bool res_vec = !glu && p.residual != nullptr && p.vec_ok != 0 && nl0 + CW <= it.feat_valid;
+              uint4 rs[CW / 8];
+              if (res_vec) {
+                const __nv_bfloat16* rp = p.residual + static_cast<size_t>(m) * p.ldr + it.feat0 + nl0;
+#pragma unroll
+                for (int q8 = 0; q8 < CW / 8; ++q8) rs[q8] = *reinterpret_cast<const uint4*>(rp + q8 * 8);
+              }
 #pragma unroll
               for (int j8 = 0; j8 < CW; j8 += 8) {
                 const int nl = nl0 + j8;
@@ -856,6 +930,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                 if (nl >= it.feat_valid) break;
                 float o[8];
                 const bool full8 = (nl + 8 <= it.feat_valid);
+                float rv[8];
+                if (res_vec) {
+                  const uint32_t w4[4] = {rs[j8 / 8].x, rs[j8 / 8].y, rs[j8 / 8].z, rs[j8 / 8].w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) rv[2 * j] = bf16_lo(w4[j]), rv[2 * j + 1] = bf16_hi(w4[j]);
+                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                   float val = v[j8 + j];
@@ -869,7 +949,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                     val = act_glu(p.epilogue, g, uu, p.glu_alpha, p.glu_limit);
                   } else {
                     if (bias_p != nullptr && in) val += __bfloat162float(bias_p[n + j]);
-                    if (p.residual != nullptr && in)
+                    if (res_vec)
+                      val += rv[j];
+                    else if (p.residual != nullptr && in)
                       val += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n + j]);
                   }
                   o[j] = val;
@@ -908,8 +990,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       }
       if constexpr (COMM == 2) {
         const CommParams& cm = p.comm;
-        const int owner = tile % cm.world;
-        __threadfence_system();
+        const int owner = comm2_owner(tile, cm.world);
         named_bar_sync(1, 128);
         if (epi_tid == 0) signal_add_sys(cm.flags_peer[owner] + tile, 1u);
         if (owner == cm.rank) {
@@ -926,46 +1007,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                                         comm_parity * static_cast<size_t>(cm.parity_stride) +
                                         static_cast<size_t>(tile / cm.world) * (kLaneRows * BN) +
                                         static_cast<size_t>(row) * BN;
-            for (int j8 = 0; j8 < BN; j8 += 8) {
-              const int n = it.feat0 + j8;
-              if (j8 >= it.feat_valid) break;
-              float o[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) o[j] = 0.f;
-              for (int r = 0; r < cm.world; ++r) {
-                const uint4 a = __ldcg(reinterpret_cast<const uint4*>(
-                    base + r * static_cast<size_t>(cm.rank_stride) + j8));
-                const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  o[2 * j] += bf16_lo(w4[j]);
-                  o[2 * j + 1] += bf16_hi(w4[j]);
-                }
-              }
-              if (p.bias != nullptr) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] += __bfloat162float(p.bias[n + j]);
-              }
-              if (p.residual != nullptr) {
-                const uint4 a = *reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(m) * p.ldr + n);
-                const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  o[2 * j] += bf16_lo(w4[j]);
-                  o[2 * j + 1] += bf16_hi(w4[j]);
-                }
-              }
-              uint4 pk;
-              pk.x = pack_bf16(o[0], o[1]);
-              pk.y = pack_bf16(o[2], o[3]);
-              pk.z = pack_bf16(o[4], o[5]);
-              pk.w = pack_bf16(o[6], o[7]);
-              const size_t off = static_cast<size_t>(m) * p.ldo + n;
-              for (int pr = 0; pr < cm.world; ++pr)
-                *reinterpret_cast<uint4*>(cm.out_peer[pr] + off) = pk;
+            // NQ 8-feature chunks x up to WMAX ranks of partials are requested together (8 loads
+            // of 16 bytes in flight), then summed in rank order, finished and pushed to every peer.
+            const __nv_bfloat16* bias_n = p.bias != nullptr ? p.bias + it.feat0 : nullptr;
+            const __nv_bfloat16* res_n =
+                p.residual != nullptr ? p.residual + static_cast<size_t>(m) * p.ldr + it.feat0 : nullptr;
+            const size_t off0 = static_cast<size_t>(m) * p.ldo + it.feat0;
+            const int nfeat = min(BN, it.feat_valid);
+            if (cm.world <= 2) {
+              for (int j0 = 0; j0 < nfeat; j0 += 32)
+                comm2_reduce_span<4, 2>(base, cm.rank_stride, cm.world, bias_n, res_n, cm.out_peer, off0, j0, nfeat);
+            } else if (cm.world <= 4) {
+              for (int j0 = 0; j0 < nfeat; j0 += 16)
+                comm2_reduce_span<2, 4>(base, cm.rank_stride, cm.world, bias_n, res_n, cm.out_peer, off0, j0, nfeat);
+            } else {
+              for (int j0 = 0; j0 < nfeat; j0 += 8)
+                comm2_reduce_span<1, 8>(base, cm.rank_stride, cm.world, bias_n, res_n, cm.out_peer, off0, j0, nfeat);
             }
           }
-          __threadfence_system();
           named_bar_sync(1, 128);
           if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
         }

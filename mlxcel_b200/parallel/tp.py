@@ -28,6 +28,12 @@ from .. import ops
 from ..ops import _lib
 
 
+# The fused two-shot GEMM -> all-reduce for prefill-sized M (> 256 tokens) is correct but measured
+# slower than GEMM + NCCL all-reduce at 8192 x 4096 (its peer stores are 16-byte pieces of 32
+# different rows per instruction); prefill chunks therefore take the NCCL path unless this is set.
+_FUSED_PREFILL = os.environ.get("MLXCEL_B200_FUSED_PREFILL", "0") == "1"
+
+
 class TPComm:
     def __init__(self, group, device: torch.device, backend: str = "fused", max_tokens: int = 8192,
                  hidden: int = 8192, vocab: int = 262144, ep: bool = True):
@@ -70,7 +76,8 @@ class TPComm:
 
         if self.tp_size == 1:
             return _linear_any(x, w, bias=bias, residual=residual, out=residual)
-        if self.backend == "fused" and not isinstance(w, QuantizedTensor):
+        if self.backend == "fused" and not isinstance(w, QuantizedTensor) and (
+                x.shape[0] <= self.fused.small_m or _FUSED_PREFILL):
             return self.fused.gemm_allreduce(x, w, bias, residual)
         first = self.tp_rank == 0
         y = _linear_any(x, w, bias=bias if first else None, residual=residual if first else None)

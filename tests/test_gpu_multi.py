@@ -79,6 +79,12 @@ def test_fused_gemm_allreduce_and_allgather():
                 # bitwise identical on every rank
                 ref0 = got.clone(); dist.broadcast(ref0, 0)
                 assert torch.equal(ref0, got), (M, rep)
+                if M > 256:   # the fused two-shot kernel (prefill chunks take GEMM + NCCL by default)
+                    got2 = comm.fused.gemm_allreduce(x[:, ks].contiguous(), w[:, ks].contiguous(), bias, res.clone())
+                    torch.cuda.synchronize()
+                    assert (got2.float() - want).abs().max().item() < 0.25, (M, rep)
+                    ref0 = got2.clone(); dist.broadcast(ref0, 0)
+                    assert torch.equal(ref0, got2), (M, rep)
             # stand-alone all-reduce (one-shot for small, two-shot for large tensors)
             part = torch.randn(M, N, device=dev).to(torch.bfloat16) * (rank + 1)
             parts = [torch.empty_like(part) for _ in range(world)]
