@@ -51,6 +51,13 @@ int mx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, cons
 // mode 3: all-gather of output columns (M <= 256): out_peer[r][t, rank * N + n].
 // flags_peer / recv_peer / out_peer: host arrays of `world` device addresses of the same heap
 // offset on each rank; ctl (16 words) / expect (8200 words): this rank's channel words (zeroed).
+/* Deferred RMSNorm for the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread: scale output
+ * rows by the 1/rms that `ssq_in` describes (consumer) and / or leave per-tile sums of squares of
+ * the result in `ssq_out` (producer). Either may be NULL. Buffer layout in gemm.cu. */
+void mx_gemm_set_row_norm(const void* ssq_in, float eps, float inv_dim, void* ssq_out);
+/* Sum of squares of every row of x [rows, dim] (bf16) as a one-partial ssq buffer (see above). */
+int mx_row_ssq(const void* x, int rows, int dim, long long ldx, void* ssq, void* stream);
+
 int mx_gemm_comm(const void* x, const void* w, void* out, const void* bias, const void* residual,
                  int M, int N, int K, int ldx, int ldw, int ldo, int ldr, int mode, int rank,
                  int world, const void* const* flags_peer, const void* const* recv_peer,

@@ -33,6 +33,7 @@ constexpr int kBK = 64;          // K elements per stage (128 bytes of bf16)
 constexpr int kLaneRows = 128;   // UMMA M
 constexpr int kMaxStages = 8;
 constexpr int kGemmThreads = 192;
+constexpr int kCtrlBytes = 256 + 256 * 4;   // barriers + per-token scales of a tile (BN <= 256)
 constexpr int kSplitDepartOffset = MX_WS_COUNTER_BYTES / 8;   // second half of the counter area
 
 constexpr int kMaxRanks = 8;
@@ -103,6 +104,12 @@ struct GemmParams {
   int splits, kb_per_split, num_kb;
   int tiles_lane, tiles_col;
   int stages;
+  // Deferred RMSNorm (see mx_gemm_set_row_norm). ssq buffers: word 0 = number of partial sums per
+  // token, word 1 = tokens per partial row (ld), data from word 8: partial p of token t at
+  // 8 + p * ld + t.
+  const float* ssq_in;  // consumer: every output row t is scaled by rsqrt(sum_p ssq / K_norm + eps)
+  float* ssq_out;       // producer: per (feature tile, token) sum of squares of the bf16 results
+  float ssq_eps, ssq_inv_dim;
   int vec_ok;           // 16-byte vector epilogue allowed (N, strides and base addresses aligned)
   unsigned long long* trace;   // optional per-CTA phase timestamps (see MX_WS_TRACE_OFFSET)
   int l2_prefetch_kb;   // k-blocks of weights (beyond the smem ring) to prefetch into L2 before the wait
@@ -298,6 +305,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   int* last_flag = reinterpret_cast<int*>(tmem_ptr + 1);
+  [[maybe_unused]] float* scale_sm = reinterpret_cast<float*>(ctrl + 256);   // per-token row scales of the tile
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -492,6 +500,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     WorkItem it;
     for (int w = blockIdx.x; decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x) {
       const int tile = it.tile, split = it.split;
+      // Deferred RMSNorm, consumer side: this GEMM reads the un-normalised residual stream (the
+      // norm weight is folded into W) and scales every output row by the row's 1/rms, summed here
+      // from the partial sums the producing kernel left, while the main loop is still running.
+      [[maybe_unused]] float row_scale = 1.0f;   // token-rows-on-lanes: this thread's token
+      if (p.ssq_in != nullptr) {
+        const int parts = reinterpret_cast<const int*>(p.ssq_in)[0];
+        const int ld = reinterpret_cast<const int*>(p.ssq_in)[1];
+        const float* data = p.ssq_in + 8;
+        if constexpr (SWAP) {
+          named_bar_sync(1, 128);   // the previous item's readers of scale_sm are done
+          for (int c = epi_tid; c < BN; c += 128) {
+            const int t = it.out_tok0 + c;
+            float ss = 0.f;
+            if (c < it.tok_valid)
+              for (int pp = 0; pp < parts; ++pp) ss += __ldcg(data + static_cast<size_t>(pp) * ld + t);
+            scale_sm[c] = rsqrtf(ss * p.ssq_inv_dim + p.ssq_eps);
+          }
+          named_bar_sync(1, 128);
+        } else {
+          float ss = 0.f;
+          if (row < it.tok_valid)
+            for (int pp = 0; pp < parts; ++pp)
+              ss += __ldcg(data + static_cast<size_t>(pp) * ld + it.out_tok0 + row);
+          row_scale = rsqrtf(ss * p.ssq_inv_dim + p.ssq_eps);
+        }
+      }
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kErrEpilogueWait)) break;
       tc_fence_after_sync();
       if (epi_tid == 0) stamp(5);
@@ -564,12 +598,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
             if constexpr (CA == 32) tmem_ld_32x32(taddr + c * CA, r);
             else tmem_ld_32x16(taddr + c * CA, r);
             tmem_ld_wait();
+            if (p.ssq_in != nullptr) {
 #pragma unroll
-            for (int j = 0; j < CA; ++j) v[j] = __uint_as_float(r[j]) + bias_g;
+              for (int j = 0; j < CA; ++j) v[j] = __uint_as_float(r[j]) * scale_sm[c * CA + j] + bias_g;
+            } else {
+#pragma unroll
+              for (int j = 0; j < CA; ++j) v[j] = __uint_as_float(r[j]) + bias_g;
+            }
             if (glu) {
               if constexpr (CA == 32) tmem_ld_32x32(taddr + BN + c * CA, r);
               else tmem_ld_32x16(taddr + BN + c * CA, r);
               tmem_ld_wait();
+              if (p.ssq_in != nullptr) {
+#pragma unroll
+                for (int j = 0; j < CA; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * scale_sm[c * CA + j]);
+              }
 #pragma unroll
               for (int j = 0; j < CA; ++j)
                 v[j] = act_glu(p.epilogue, v[j], __uint_as_float(r[j]) + bias_u, p.glu_alpha, p.glu_limit);
@@ -655,6 +698,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
               }
             }
           }
+          if (p.ssq_in != nullptr) {
+#pragma unroll
+            for (int g = 0; g < PU; ++g) {
+              const int tl = tl0 + g * 8 + tsub;
+              const float sc = tl < t_end ? scale_sm[tl] : 1.0f;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[g][j] *= sc, u[g][j] *= sc;
+            }
+          }
 #pragma unroll
           for (int g = 0; g < PU; ++g) {
             if (COMM != 1 && bias_p != nullptr) {
@@ -713,6 +765,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
         };
 
 
+        // Deferred RMSNorm, producer side: sum of squares of the bf16 results of (token tl, this
+        // tile's 128 features), reduced over the 16 threads that share the token row and written
+        // as one partial per (feature tile, token); the consumer adds the partials in tile order,
+        // so the norm is deterministic and identical on every rank. Requires N % 128 == 0 (every
+        // thread of the warp takes part in the shuffles).
+        auto emit_ssq = [&](int tl, const float(&o)[8]) {
+          float sq = 0.f;
+          if (tl < t_end) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float r = p.out_fp32 ? o[j] : __bfloat162float(__float2bfloat16(o[j]));
+              sq += r * r;
+            }
+          }
+          sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+          if (seg == 0 && tl < t_end) {
+            const int ld = reinterpret_cast<const int*>(p.ssq_out)[1];
+            p.ssq_out[8 + static_cast<size_t>(it.feat0 / kLaneRows) * ld + it.out_tok0 + tl] = sq;
+          }
+        };
+        if (p.ssq_out != nullptr && tile == 0 && split == 0 && epi_tid == 0)
+          reinterpret_cast<int*>(p.ssq_out)[0] = p.tiles_lane;
+
         if (nvalid > 0) {
 #pragma unroll 1
           for (int tl0 = t_begin; tl0 < t_end; tl0 += 8 * PU) {
@@ -733,6 +811,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
               for (int g = 0; g < PU; ++g) {
                 const int tl = tl0 + g * 8 + tsub;
                 if (tl < t_end) store_out(static_cast<size_t>(it.out_tok0 + tl) * p.ldo + n, o[g]);
+              }
+              if (p.ssq_out != nullptr) {
+#pragma unroll
+                for (int g = 0; g < PU; ++g) emit_ssq(tl0 + g * 8 + tsub, o[g]);
               }
             } else if constexpr (COMM == 1) {
               // bf16 partial (no bias / residual yet) into every peer's slot [rank]
@@ -837,6 +919,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                 const int tl = tl0 + g * 8 + tsub;
                 if (tl < t_end) store_out(static_cast<size_t>(it.out_tok0 + tl) * p.ldo + n, o[g]);
               }
+              if (p.ssq_out != nullptr) {
+#pragma unroll
+                for (int g = 0; g < GRPC; ++g) emit_ssq(tl0 + g * 8 + tsub, o[g]);
+              }
             }
           }
         } else {  // COMM == 3
@@ -859,6 +945,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           }
         }
       } else {
+        float ssq_acc = 0.f;   // deferred RMSNorm, producer side: this token row over the tile's features
 #pragma unroll 1
         for (int c = 0; c < BN / CW; ++c) {
           float v[CW], u[CW];
@@ -938,10 +1025,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                  float val = v[j8 + j];
+                  float val = v[j8 + j] * row_scale;
                   const bool in = full8 || (nl + j < it.feat_valid);
                   if (glu) {
-                    float g = val, uu = u[j8 + j];
+                    float g = val, uu = u[j8 + j] * row_scale;
                     if (bias_p != nullptr && in) {
                       g += __bfloat162float(bias_p[n + j]);
                       uu += __bfloat162float(bias_p[p.glu_offset + n + j]);
@@ -955,6 +1042,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                       val += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n + j]);
                   }
                   o[j] = val;
+                  if (p.ssq_out != nullptr && in) {
+                    const float r = p.out_fp32 ? val : __bfloat162float(__float2bfloat16(val));
+                    ssq_acc += r * r;
+                  }
                 }
                 const size_t off = static_cast<size_t>(m) * p.ldo + n;
                 if (p.out_fp32) {
@@ -986,6 +1077,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        }
+        if (COMM == 0 && p.ssq_out != nullptr) {
+          const int ld = reinterpret_cast<const int*>(p.ssq_out)[1];
+          if (row_ok) p.ssq_out[8 + static_cast<size_t>(it.feat0 / BN) * ld + it.out_tok0 + row] = ssq_acc;
+          if (tile == 0 && epi_tid == 0) reinterpret_cast<int*>(p.ssq_out)[0] = p.tiles_col;
         }
       }
       if constexpr (COMM == 2) {
@@ -1173,10 +1269,10 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
   constexpr int COL_TILES = (!SWAP && GLU) ? 2 : 1;
   constexpr int STAGE_BYTES = LANE_TILES * kLaneRows * kBK * 2 + COL_TILES * BN * kBK * 2;
   constexpr int STAGING_BYTES = SWAP ? BN * kLaneRows * 4 : 0;
-  constexpr int kSmemBudget = 227 * 1024 - 1024 /*align*/ - 256 /*ctrl*/ - STAGING_BYTES;
+  constexpr int kSmemBudget = 227 * 1024 - 1024 /*align*/ - kCtrlBytes - STAGING_BYTES;
   int stages = kSmemBudget / STAGE_BYTES;
   if (SWAP && COMM == 0 && !GROUPED && gemm_ctas_per_sm() == 2 && 2 * (2 * ACC_COLS_HOST(BN, GLU)) <= 512) {
-    const int half = (227 * 1024 / 2 - 2048 - 1024 - 256 - STAGING_BYTES) / STAGE_BYTES;
+    const int half = (227 * 1024 / 2 - 2048 - 1024 - kCtrlBytes - STAGING_BYTES) / STAGE_BYTES;
     if (half >= 3) stages = half;
   }
   if (stages > kMaxStages) stages = kMaxStages;
@@ -1221,7 +1317,7 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
     }();
     p.l2_prefetch_kb = (SWAP && !GROUPED && pdl_enabled()) ? (l2_kb * 1024) / (LANE_TILES * kLaneRows * kBK * 2) : 0;
   }
-  const int smem = stages * STAGE_BYTES + STAGING_BYTES + 1024 + 256;
+  const int smem = stages * STAGE_BYTES + STAGING_BYTES + 1024 + kCtrlBytes;
   {
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     bool ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && al16(p.out) &&
@@ -1249,6 +1345,47 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
 using namespace mx;
 
 extern "C" long long mx_gemm_workspace_bytes(void) { return 64ll << 20; }
+
+namespace {
+struct PendingRowNorm {
+  const float* ssq_in = nullptr;
+  float* ssq_out = nullptr;
+  float eps = 0.f, inv_dim = 0.f;
+};
+thread_local PendingRowNorm g_row_norm;
+
+// Moves the pending request into the launch parameters (one-shot).
+int take_row_norm(mx::GemmParams& p, bool swap, int N, int comm_mode) {
+  const PendingRowNorm r = g_row_norm;
+  g_row_norm = PendingRowNorm{};
+  p.ssq_in = r.ssq_in;
+  p.ssq_out = r.ssq_out;
+  p.ssq_eps = r.eps;
+  p.ssq_inv_dim = r.inv_dim;
+  if (r.ssq_out != nullptr) {
+    if (comm_mode == 2 || comm_mode == 3) return -6;   // producers: plain and one-shot all-reduce only
+    if (swap && (N % 128) != 0) return -6;
+  }
+  if (r.ssq_in != nullptr && comm_mode != 0) return -6;
+  return 0;
+}
+}  // namespace
+
+// Deferred RMSNorm around the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread.
+//   ssq_in  (consumer): the GEMM input is an un-normalised residual stream whose norm weight was
+//           folded into W; every output row t is multiplied by rsqrt(sum_p ssq_in[p][t] * inv_dim +
+//           eps) before bias / activation.
+//   ssq_out (producer): besides its result the GEMM leaves, per (128- or 256-feature tile, token),
+//           the sum of squares of that part of the result row, for the next consumer.
+// Buffer layout (fp32 words): [0] partial count (written by the producer), [1] tokens per partial
+// row (set by the owner of the buffer), data from word 8. No counterpart in the reference, where
+// the norm is its own kernel (src/lib/mlxcel-core/cpp/fused_norm.cpp).
+extern "C" void mx_gemm_set_row_norm(const void* ssq_in, float eps, float inv_dim, void* ssq_out) {
+  g_row_norm.ssq_in = static_cast<const float*>(ssq_in);
+  g_row_norm.ssq_out = static_cast<float*>(ssq_out);
+  g_row_norm.eps = eps;
+  g_row_norm.inv_dim = inv_dim;
+}
 
 extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void* bias,
                             const void* residual, int M, int N, int K, int ldx, int ldw, int ldo,
@@ -1286,6 +1423,7 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
   p.num_kb = (K + kBK - 1) / kBK;
   p.splits = 1;
   p.kb_per_split = p.num_kb;
+  if (const int rn = take_row_norm(p, swap, N, 0); rn != 0) return rn;
 
   const int sms = device_sm_count();
   int bn;
@@ -1400,6 +1538,7 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
   }
   p.comm.parity_stride = parity_stride;
   p.comm.rank_stride = rank_stride;
+  if (const int rn = take_row_norm(p, swap, N, mode); rn != 0) return rn;
 
   const int sms = device_sm_count();
   int bn;

@@ -376,6 +376,43 @@ __global__ void rope_append_fast_kernel(__nv_bfloat16* __restrict__ qkv, const i
   }
 }
 
+// ----------------------------------------------------------------------------- row sum of squares
+// One warp per row: ssq[8 + row] = sum of x[row, :]^2, partial count (word 0) = 1. Starts a chain
+// of deferred RMSNorms when the residual stream does not come out of a GEMM epilogue (embedding
+// output, an NCCL all-reduce).
+__global__ void row_ssq_kernel(const __nv_bfloat16* __restrict__ x, int rows, int dim, long long ldx,
+                               float* __restrict__ ssq) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<int*>(ssq)[0] = 1;
+  if (row >= rows) return;
+  const __nv_bfloat16* src = x + static_cast<size_t>(row) * ldx;
+  float ss = 0.f;
+  for (int i = lane * 8; i < dim; i += 32 * 8) {
+    const uint4 a = *reinterpret_cast<const uint4*>(src + i);
+    const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = bf16_lo(w4[j]), hi = bf16_hi(w4[j]);
+      ss += lo * lo + hi * hi;
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) ssq[8 + row] = ss;
+}
+
+extern "C" int mx_row_ssq(const void* x, int rows, int dim, long long ldx, void* ssq, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows <= 0) return 0;
+  if (dim % 8 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -1;
+  const int wpb = 4;
+  launch_kernel(row_ssq_kernel, dim3((rows + wpb - 1) / wpb), dim3(wpb * 32), 0, stream,
+                static_cast<const __nv_bfloat16*>(x), rows, dim, ldx, static_cast<float*>(ssq));
+  return static_cast<int>(cudaGetLastError());
+}
+
 // ----------------------------------------------------------------------------- embedding
 __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                  __nv_bfloat16* __restrict__ out, int dim, int vocab, float scale) {

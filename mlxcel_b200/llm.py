@@ -18,10 +18,13 @@ from .models.weights import ModelWeights, random_weights
 
 class LLM:
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, engine_config: EngineConfig | None = None,
-                 comm=None, tokenizer=None):
+                 comm=None, tokenizer=None, fold_norms: bool = False):
+        """``fold_norms``: the weights belong to this object alone, so the executor may fold the
+        RMSNorm weights into the projections in place (deferred RMSNorm, see DecoderModel)."""
         self.cfg = cfg
         self.model = DecoderModel(cfg, weights, comm=comm,
-                                  kv_bits=(engine_config.kv_bits if engine_config else 16))
+                                  kv_bits=(engine_config.kv_bits if engine_config else 16),
+                                  fold_norms=fold_norms)
         self.engine = Engine(self.model, cfg, engine_config)
         self.tokenizer = tokenizer
 
@@ -35,7 +38,7 @@ class LLM:
         w = random_weights(cfg, seed=seed, dtype=dtype, device=device, tp_rank=rank, tp_size=tp,
                            ep_rank=getattr(comm, "ep_rank", 0), ep_size=getattr(comm, "ep_size", 1),
                            vocab_parallel=tp > 1 and cfg.vocab_size % tp == 0)
-        return LLM(cfg, w, engine_config, comm=comm)
+        return LLM(cfg, w, engine_config, comm=comm, fold_norms=True)
 
     @staticmethod
     def from_pretrained(path: str | Path, *, device="cuda", engine_config: EngineConfig | None = None,
@@ -46,7 +49,7 @@ class LLM:
         cfg = ModelConfig.from_path(path)
         w = load_model_weights(path, cfg, device=device, comm=comm, dequantize=dequantize)
         tok = load_tokenizer(path)
-        return LLM(cfg, w, engine_config, comm=comm, tokenizer=tok)
+        return LLM(cfg, w, engine_config, comm=comm, tokenizer=tok, fold_norms=True)
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompts=None, sampling_params: SamplingParams | list[SamplingParams] | None = None,

@@ -13,6 +13,8 @@ softmax routing (src/models/gpt_oss.rs:51-476), MoE switch layers
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 
 import torch
@@ -60,8 +62,8 @@ class LocalComm:
     ep_size = 1
     ep_rank = 0
 
-    def row_parallel_linear(self, x, w, bias, residual):
-        return _linear_any(x, w, bias=bias, residual=residual, out=residual)
+    def row_parallel_linear(self, x, w, bias, residual, ssq_out=None):
+        return _linear_any(x, w, bias=bias, residual=residual, out=residual, ssq_out=ssq_out)
 
     def gather_logits(self, logits):
         return logits
@@ -76,25 +78,30 @@ class LocalComm:
         return x
 
 
-def _linear_any(x, w, bias=None, residual=None, out=None):
+def _linear_any(x, w, bias=None, residual=None, out=None, row_norm=None, ssq_out=None):
     if isinstance(w, QuantizedTensor):
         from ..ops import quant
-        return quant.qlinear(x, w, bias=bias, residual=residual, out=out)
-    return ops.linear(x, w, bias=bias, residual=residual, out=out)
+        assert row_norm is None, "deferred RMSNorm needs dense weights"
+        y = quant.qlinear(x, w, bias=bias, residual=residual, out=out)
+        if ssq_out is not None:
+            ops.row_ssq(y, ssq_out)
+        return y
+    return ops.linear(x, w, bias=bias, residual=residual, out=out, row_norm=row_norm, ssq_out=ssq_out)
 
 
-def _glu_any(x, w, inter, act, bias, alpha, limit):
+def _glu_any(x, w, inter, act, bias, alpha, limit, row_norm=None):
     if isinstance(w, QuantizedTensor):
         from ..ops import quant
+        assert row_norm is None, "deferred RMSNorm needs dense weights"
         y = quant.qlinear(x, w, bias=bias)
         return ops.swiglu(y, inter, act, alpha, limit)
-    return ops.glu_linear(x, w, inter, act, bias=bias, alpha=alpha, limit=limit)
+    return ops.glu_linear(x, w, inter, act, bias=bias, alpha=alpha, limit=limit, row_norm=row_norm)
 
 
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, comm=None, kv_bits: int = 16,
                  layer_range: range | None = None, first_stage: bool = True,
-                 last_stage: bool = True):
+                 last_stage: bool = True, fold_norms: bool = False):
         self.cfg = cfg
         self.w = weights
         self.comm = comm or LocalComm()
@@ -111,12 +118,56 @@ class DecoderModel:
         self.inv_freq = inv.to(dev)
         self.mscale = ms
         self.device = dev
+        self._ssq = None
+        self.fold_attn = self.fold_mlp = False
+        # Folding rewrites the projection weights in place, so only the owner of the weights asks for
+        # it (the LLM front end does; weights shared with another executor must stay untouched).
+        if fold_norms and dev.type == "cuda" and os.environ.get("MLXCEL_B200_FOLD_NORMS", "1") != "0":
+            self._fold_norms()
+
+    # ------------------------------------------------------------------ deferred RMSNorm
+    def _fold_norms(self) -> None:
+        """Pre-norm layers with dense projections: multiply the norm weight into the columns of the
+        projection that consumes the normalised stream. The forward pass then feeds the residual
+        stream itself to that GEMM, whose epilogue applies the per-token 1/rms from the sums of
+        squares the previous GEMM's epilogue (or ``row_ssq``) left — the RMSNorm kernels between
+        the projections disappear (2 per layer). Same math as norm-then-project up to bf16
+        rounding of the folded weight."""
+        cfg = self.cfg
+        if cfg.post_norms or cfg.extra.get("residual_multiplier", 1.0) != 1.0:
+            return
+        H = cfg.hidden_size
+        if H % 128 or H // 128 > 64:
+            return
+        layers = self.w.layers
+        if not layers or any(isinstance(lw.wqkv, QuantizedTensor) or lw.wqkv.dtype != torch.bfloat16 for lw in layers):
+            return
+        fold_mlp = not cfg.is_moe and all(
+            lw.w_gate_up is not None and not isinstance(lw.w_gate_up, QuantizedTensor)
+            and lw.w_gate_up.dtype == torch.bfloat16 for lw in layers)
+        wb = cfg.norm_weight_bias
+
+        def fold(w, ln):
+            if getattr(w, "_norm_folded", False):      # shared between two executors of one model
+                return
+            g = (ln.float() + wb).unsqueeze(0)
+            for r0 in range(0, w.shape[0], 8192):      # bounded fp32 temporaries
+                w[r0:r0 + 8192] = (w[r0:r0 + 8192].float() * g).to(w.dtype)
+            w._norm_folded = True
+
+        with torch.no_grad():
+            for lw in layers:
+                fold(lw.wqkv, lw.ln1)
+                if fold_mlp:
+                    fold(lw.w_gate_up, lw.ln2)
+        self.fold_attn, self.fold_mlp = True, fold_mlp
+        self._ssq = ops.SsqBuffer(16384, H // 128, self.device)
 
     # ------------------------------------------------------------------ blocks
     def _attention(self, li: int, lw: LayerWeights, x: torch.Tensor, b: StepBatch,
-                   kv: KVLayer) -> torch.Tensor:
+                   kv: KVLayer, row_norm=None) -> torch.Tensor:
         cfg = self.cfg
-        qkv = _linear_any(x, lw.wqkv, bias=lw.bqkv)
+        qkv = _linear_any(x, lw.wqkv, bias=lw.bqkv, row_norm=row_norm)
         ops.rope_append(qkv, b.positions, b.slot_mapping, self.inv_freq, kv, Hq=self.Hq,
                         Hkv=self.Hkv, D=self.D, rot_dim=cfg.rot_dim,
                         traditional=cfg.rope_traditional, mscale=self.mscale,
@@ -142,10 +193,10 @@ class DecoderModel:
                 attn[nd:] = o
         return attn
 
-    def _mlp(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+    def _mlp(self, lw: LayerWeights, x: torch.Tensor, row_norm=None) -> torch.Tensor:
         cfg = self.cfg
         return _glu_any(x, lw.w_gate_up, self.I, cfg.hidden_act, lw.b_gate_up, cfg.swiglu_alpha,
-                        cfg.swiglu_limit)
+                        cfg.swiglu_limit, row_norm=row_norm)
 
     def _moe(self, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
         from .moe import moe_forward
@@ -164,6 +215,11 @@ class DecoderModel:
             h = self.comm.embed(b.token_ids, w.embed, cfg.embed_scale)
         eps, wb = cfg.rms_norm_eps, cfg.norm_weight_bias
         res_mult = cfg.extra.get("residual_multiplier", 1.0)
+        if self.fold_attn and h.is_cuda and h.shape[0] <= self._ssq.max_tokens and h.dtype == torch.bfloat16:
+            return self._forward_folded(h, b, kv_layers)
+        if self.fold_attn:
+            raise RuntimeError("norm weights are folded into the projections: this batch cannot take the "
+                               "unfolded path (too many tokens or a non-bf16 stream)")
         for li, lw in enumerate(w.layers):
             kv = kv_layers[li]
             x = ops.rmsnorm(h, lw.ln1, eps, wb)
@@ -191,6 +247,29 @@ class DecoderModel:
                     h = (h.float() + o.float()).to(h.dtype) if not h.is_cuda else h.add_(o)
                 else:
                     h = self.comm.row_parallel_linear(m, lw.w_down, lw.b_down, h)
+        return h
+
+    def _forward_folded(self, h: torch.Tensor, b: StepBatch, kv_layers: list[KVLayer]) -> torch.Tensor:
+        """Layer loop with deferred RMSNorms (see ``_fold_norms``): ``ssq`` always describes the
+        current residual stream ``h``."""
+        cfg, ssq = self.cfg, self._ssq
+        eps, wb = cfg.rms_norm_eps, cfg.norm_weight_bias
+        rn = ops.RowNorm(ssq, eps, cfg.hidden_size)
+        ops.row_ssq(h, ssq)
+        for li, lw in enumerate(self.w.layers):
+            a = self._attention(li, lw, h, b, kv_layers[li], row_norm=rn)
+            h = self.comm.row_parallel_linear(a, lw.wo, lw.bo, h, ssq_out=ssq)
+            if self.fold_mlp:
+                m = self._mlp(lw, h, row_norm=rn)
+                h = self.comm.row_parallel_linear(m, lw.w_down, lw.b_down, h, ssq_out=ssq)
+            else:
+                x = ops.rmsnorm(h, lw.ln2, eps, wb)
+                if cfg.is_moe:
+                    h = self._moe(lw, x, h)
+                else:
+                    h = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, h)
+                if li + 1 < len(self.w.layers):
+                    ops.row_ssq(h, ssq)
         return h
 
     def logits(self, h: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:

@@ -38,12 +38,56 @@ def _lib_call(name: str, *args) -> None:
     _lib.check(rc, name)
 
 
+# ----------------------------------------------------------------------------- deferred RMSNorm
+class SsqBuffer:
+    """Per-token partial sums of squares of a residual stream, left by the kernel that produced it
+    (a GEMM epilogue or ``row_ssq``) for the GEMM that consumes it un-normalised.
+    fp32 words: [0] partial count (device-written), [1] row stride, data from word 8."""
+
+    def __init__(self, max_tokens: int, max_parts: int, device):
+        self.max_tokens, self.max_parts = max_tokens, max_parts
+        self.buf = torch.zeros(8 + max_parts * max_tokens, dtype=torch.float32, device=device)
+        self.buf[:2].view(torch.int32).copy_(torch.tensor([0, max_tokens], dtype=torch.int32))
+
+    def fits(self, tokens: int, features: int) -> bool:
+        return tokens <= self.max_tokens and (features + 127) // 128 <= self.max_parts
+
+
+@dataclass
+class RowNorm:
+    ssq: SsqBuffer
+    eps: float
+    dim: int      # length of the normalised rows (the GEMM's K when nothing is sharded)
+
+
+def _set_row_norm(row_norm, ssq_out) -> None:
+    if row_norm is None and ssq_out is None:
+        return
+    _lib.load().mx_gemm_set_row_norm(row_norm.ssq.buf.data_ptr() if row_norm is not None else None,
+                                     float(row_norm.eps) if row_norm is not None else 0.0,
+                                     1.0 / row_norm.dim if row_norm is not None else 0.0,
+                                     ssq_out.buf.data_ptr() if ssq_out is not None else None)
+
+
+def row_ssq(x: torch.Tensor, ssq: SsqBuffer) -> None:
+    """Starts a deferred-RMSNorm chain: sums of squares of the rows of ``x`` (one partial)."""
+    rows, dim = x.shape
+    assert x.is_cuda and x.stride(1) == 1 and rows <= ssq.max_tokens
+    _lib_call("mx_row_ssq", x.data_ptr(), rows, dim, x.stride(0), ssq.buf.data_ptr(), _lib.stream())
+
+
 # ----------------------------------------------------------------------------- GEMM
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
-           out_fp32: bool = False, force_mode: int = 0, force_splits: int = 0) -> torch.Tensor:
-    """``x[M,K] @ w[N,K]^T (+ bias) (+ residual)`` with bf16 operands, fp32 accumulation."""
+           out_fp32: bool = False, force_mode: int = 0, force_splits: int = 0,
+           row_norm: "RowNorm | None" = None, ssq_out: "SsqBuffer | None" = None) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T (+ bias) (+ residual)`` with bf16 operands, fp32 accumulation.
+
+    ``row_norm``: deferred RMSNorm — ``x`` is un-normalised, the norm weight is folded into ``w`` and
+    every output row is scaled by the 1/rms described by ``row_norm.ssq`` before the bias.
+    ``ssq_out``: the kernel also leaves the per-tile sums of squares of its result rows there."""
     if not x.is_cuda:
+        assert row_norm is None and ssq_out is None, "deferred RMSNorm is a CUDA-only path"
         return ref.linear(x, w, bias, residual, torch.float32 if out_fp32 else None)
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     M, K = x.shape
@@ -55,6 +99,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         return out
     epi = EPI_RESIDUAL if residual is not None else (EPI_BIAS if bias is not None else EPI_NONE)
     ws = _lib.workspace(x.device)
+    _set_row_norm(row_norm, ssq_out)
     _lib_call("mx_gemm_bf16", x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias),
               _lib.ptr(residual), M, N, K, x.stride(0), w.stride(0), out.stride(0),
               residual.stride(0) if residual is not None else 0, epi, 1 if out_fp32 else 0, 0,
@@ -65,7 +110,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
 def glu_linear(x: torch.Tensor, w: torch.Tensor, inter: int, act: str = "silu",
                bias: torch.Tensor | None = None, alpha: float = 1.702, limit: float = 7.0,
                out: torch.Tensor | None = None, force_mode: int = 0,
-               force_splits: int = 0) -> torch.Tensor:
+               force_splits: int = 0, row_norm: "RowNorm | None" = None) -> torch.Tensor:
     """``act(x @ w[:I]^T) * (x @ w[I:2I]^T)`` — gate/up projection with the activation fused
     into the GEMM epilogue (gate and up live in two TMEM accumulators)."""
     epi = _ACT_TO_EPI[act]
@@ -78,6 +123,7 @@ def glu_linear(x: torch.Tensor, w: torch.Tensor, inter: int, act: str = "silu",
     if M == 0:
         return out
     ws = _lib.workspace(x.device)
+    _set_row_norm(row_norm, None)
     _lib_call("mx_gemm_bf16", x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias), None, M,
               inter, K, x.stride(0), w.stride(0), out.stride(0), 0, epi, 0, inter, float(alpha),
               float(limit), ws.data_ptr(), ws.numel(), force_mode, force_splits, _lib.stream())

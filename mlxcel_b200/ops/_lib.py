@@ -61,6 +61,7 @@ def _declare(lib) -> None:
         "mx_gemm_comm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp,
                          _vp, _vp, _vp, _ll, _ll, _vp, _ll, _vp],
         "mx_allreduce_comm": [_vp, _vp, _vp, _ll, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp],
+        "mx_row_ssq": [_vp, _i, _i, _ll, _vp, _vp],
         "mx_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
         "mx_head_rmsnorm": [_vp, _vp, _i, _i, _i, _ll, _f, _vp],
         "mx_rope_append": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i,
@@ -103,6 +104,10 @@ def _declare(lib) -> None:
     if fn is not None:
         fn.restype = _ll
         fn.argtypes = [_i, _i, _i, _i]
+    fn = getattr(lib, "mx_gemm_set_row_norm", None)
+    if fn is not None:
+        fn.restype = None
+        fn.argtypes = [_vp, _f, _f, _vp]
     fn = getattr(lib, "mx_build_info", None)
     if fn is not None:
         fn.restype = ctypes.c_char_p

@@ -144,7 +144,7 @@ class FusedOps:
     def hidden_buffer(self, tokens: int, hidden: int) -> torch.Tensor:
         return self.heap.view(self.h_off, (tokens, hidden), torch.bfloat16)
 
-    def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, bias, residual) -> torch.Tensor:
+    def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, bias, residual, ssq_out=None) -> torch.Tensor:
         """``residual + bias + sum_ranks(x_r @ w_r^T)``; the result is bitwise identical on all
         ranks and lives in the symmetric residual buffer."""
         M, K = x.shape
@@ -159,6 +159,10 @@ class FusedOps:
         if M > self.max_tokens or N > self.hidden:
             raise ValueError("gemm_allreduce shape exceeds the symmetric buffers")
         res = residual  # read locally by the reducing rank; may alias `out` (in-place update)
+        if ssq_out is not None:
+            assert mode == 1, "per-tile sums of squares come out of the one-shot epilogue only"
+            from .. import ops
+            ops._set_row_norm(None, ssq_out)
         rc = lib.mx_gemm_comm(x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias), _lib.ptr(res),
                               M, N, K, x.stride(0), w.stride(0), out.stride(0),
                               res.stride(0) if res is not None else 0, mode, self.rank, self.world,

@@ -68,20 +68,28 @@ class TPComm:
             dist.all_reduce(x, group=self.group)
         return x
 
-    def row_parallel_linear(self, x, w, bias, residual):
-        """``residual + all_reduce(x_shard @ w_shard^T) + bias`` with replicated output."""
+    def row_parallel_linear(self, x, w, bias, residual, ssq_out=None):
+        """``residual + all_reduce(x_shard @ w_shard^T) + bias`` with replicated output.
+        ``ssq_out``: leave the per-token sums of squares of the result there (deferred RMSNorm)."""
         self.calls += 1
         from ..models.decoder import _linear_any
         from ..models.weights import QuantizedTensor
 
         if self.tp_size == 1:
-            return _linear_any(x, w, bias=bias, residual=residual, out=residual)
+            return _linear_any(x, w, bias=bias, residual=residual, out=residual, ssq_out=ssq_out)
         if self.backend == "fused" and not isinstance(w, QuantizedTensor) and (
                 x.shape[0] <= self.fused.small_m or _FUSED_PREFILL):
-            return self.fused.gemm_allreduce(x, w, bias, residual)
+            one_shot = x.shape[0] <= self.fused.small_m
+            y = self.fused.gemm_allreduce(x, w, bias, residual, ssq_out=ssq_out if one_shot else None)
+            if ssq_out is not None and not one_shot:
+                ops.row_ssq(y, ssq_out)
+            return y
         first = self.tp_rank == 0
         y = _linear_any(x, w, bias=bias if first else None, residual=residual if first else None)
-        return self.all_reduce(y)
+        y = self.all_reduce(y)
+        if ssq_out is not None:
+            ops.row_ssq(y, ssq_out)
+        return y
 
     def gather_logits(self, logits_local: torch.Tensor) -> torch.Tensor:
         """[R, V/tp] per rank → [R, V] on every rank."""

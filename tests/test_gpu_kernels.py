@@ -220,6 +220,40 @@ def test_paged_prefill(Hq, Hkv, D, bits, window, sinks):
     _close(got, want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("M", [1, 16, 64, 200, 700])
+def test_gemm_deferred_rmsnorm(M):
+    """producer GEMM (+residual) leaves per-tile sums of squares; consumer GEMMs (plain and gated)
+    fed with the un-normalised stream and norm-folded weights match norm-then-project."""
+    H, N2, I = 1024, 768, 512
+    eps = 1e-5
+    a = _bf(M, 256, seed=1)
+    wo = _bf(H, 256, seed=2, scale=0.05)
+    res = _bf(M, H, seed=3)
+    ln = (1.0 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16)
+    w2 = _bf(N2, H, seed=4, scale=0.05)
+    wg = _bf(2 * I, H, seed=5, scale=0.05)
+    bias = _bf(N2, seed=6)
+    ssq = ops.SsqBuffer(1024, H // 128, DEV)
+    h = ops.linear(a, wo, residual=res.clone(), ssq_out=ssq)
+    want_h = ref.linear(a, wo, None, res)
+    _close(h, want_h, rtol=2e-2, atol=2e-2)
+    parts = int(ssq.buf[:1].view(torch.int32).item())
+    got_ss = ssq.buf[8:8 + parts * ssq.max_tokens].view(parts, ssq.max_tokens)[:, :M].sum(0)
+    _close(got_ss, h.float().pow(2).sum(-1), rtol=1e-3, atol=1e-3)
+    # consumers
+    fold = lambda w: (w.float() * ln.float().unsqueeze(0)).to(torch.bfloat16)
+    rn = ops.RowNorm(ssq, eps, H)
+    x = ref.add_rmsnorm(h, None, ln, eps, 0.0)[0]
+    _close(ops.linear(h, fold(w2), bias=bias, row_norm=rn), ref.linear(x, w2, bias, None), rtol=3e-2, atol=3e-2)
+    # gate * up compounds the rounding differences of two dot products (folded weight in bf16,
+    # normalised input not rounded to bf16): wider absolute tolerance
+    _close(ops.glu_linear(h, fold(wg), I, "silu", row_norm=rn), ref.glu_linear(x, wg, I, ops.EPI_SWIGLU, None, 1.702, 7.0),
+           rtol=5e-2, atol=1e-1)
+    # a chain started by row_ssq (one partial)
+    ops.row_ssq(h, ssq)
+    _close(ops.linear(h, fold(w2), row_norm=rn), ref.linear(x, w2, None, None), rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("tc", [True, False])
 @pytest.mark.parametrize("Hq,Hkv,D,window,sinks", [(8, 2, 128, 0, False), (4, 1, 64, 300, True), (4, 4, 128, 130, False)])
 def test_paged_prefill_long(monkeypatch, tc, Hq, Hkv, D, window, sinks):
@@ -316,9 +350,11 @@ def test_penalties_and_verify():
 
 
 # ----------------------------------------------------------------------------- end to end
-def test_tiny_llama_gpu_matches_cpu_reference():
+@pytest.mark.parametrize("fold", [False, True])
+def test_tiny_llama_gpu_matches_cpu_reference(fold):
     """bf16 CUDA executor vs the fp32 CPU executor: greedy tokens on a tiny model agree while the
-    top-2 logit margin is not a near tie."""
+    top-2 logit margin is not a near tie. ``fold``: RMSNorm weights folded into the projections and
+    the norms deferred into the GEMM epilogues."""
     from mlxcel_b200.config import preset
     from mlxcel_b200.engine import Engine, EngineConfig, SamplingParams
     from mlxcel_b200.models.decoder import DecoderModel
@@ -327,6 +363,10 @@ def test_tiny_llama_gpu_matches_cpu_reference():
 
     cfg = preset("tiny-llama")
     w32 = random_weights(cfg, seed=3, dtype=torch.float32, std=0.05)
+    gn = torch.Generator().manual_seed(5)
+    for lw in w32.layers:      # non-trivial norm weights
+        lw.ln1 = lw.ln1 + 0.2 * torch.randn(lw.ln1.shape, generator=gn)
+        lw.ln2 = lw.ln2 + 0.2 * torch.randn(lw.ln2.shape, generator=gn)
     w16 = copy.deepcopy(w32)
     for lw in [w16, *w16.layers]:
         for k, v in vars(lw).items():
@@ -335,7 +375,8 @@ def test_tiny_llama_gpu_matches_cpu_reference():
     w16.lm_head = w16.embed
     ec = dict(max_batch=4, max_num_batched_tokens=256, num_blocks=64, max_model_len=256)
     cpu = Engine(DecoderModel(cfg, w32), cfg, EngineConfig(cuda_graphs=False, **ec))
-    gpu = Engine(DecoderModel(cfg, w16), cfg, EngineConfig(cuda_graphs=True, **ec))
+    gpu = Engine(DecoderModel(cfg, w16, fold_norms=fold), cfg, EngineConfig(cuda_graphs=True, **ec))
+    assert gpu.model.fold_attn == fold and gpu.model.fold_mlp == fold
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (20, 7, 33)]
     sp = SamplingParams(max_tokens=12, ignore_eos=True)
