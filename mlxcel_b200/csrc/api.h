@@ -51,6 +51,11 @@ int mx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, cons
 // mode 3: all-gather of output columns (M <= 256): out_peer[r][t, rank * N + n].
 // flags_peer / recv_peer / out_peer: host arrays of `world` device addresses of the same heap
 // offset on each rank; ctl (16 words) / expect (8200 words): this rank's channel words (zeroed).
+/* Quantized weights for the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread (`w` = packed
+ * rows, ldw = bytes per packed row); wq: 1 affine 4-bit, 2 affine 8-bit, 3 mxfp4. The call returns
+ * -9 when M > 256 (use dequantise + GEMM). */
+void mx_gemm_set_quant(const void* scales, const void* biases, int group, int wq);
+
 /* Deferred RMSNorm for the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread: scale output
  * rows by the 1/rms that `ssq_in` describes (consumer) and / or leave per-tile sums of squares of
  * the result in `ssq_out` (producer). Either may be NULL. Buffer layout in gemm.cu. */

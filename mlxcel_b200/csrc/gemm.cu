@@ -104,6 +104,11 @@ struct GemmParams {
   int splits, kb_per_split, num_kb;
   int tiles_lane, tiles_col;
   int stages;
+  // Quantized weights (WQ != 0): per-group scales (bf16 for affine, e8m0 bytes for mxfp4), affine
+  // biases, group size (32 / 64 / 128), groups per weight row, number of weight rows.
+  const void* q_scales;
+  const __nv_bfloat16* q_biases;
+  int q_group, q_groups_per_row, q_rows;
   // Deferred RMSNorm (see mx_gemm_set_row_norm). ssq buffers: word 0 = number of partial sums per
   // token, word 1 = tokens per partial row (ld), data from word 8: partial p of token t at
   // 8 + p * ld + t.
@@ -269,15 +274,99 @@ __device__ __forceinline__ void comm2_reduce_span(const __nv_bfloat16* base, lon
   }
 }
 
-template <int BN, bool SWAP, bool GLU, int COMM, bool GROUPED>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// ----------------------------------------------------------------------------- weight dequantisation
+// One thread turns the packed bytes of ONE weight row of a k-block (64 values) into the 128-byte
+// row of the swizzled bf16 MMA tile. Values are q * scale + bias in fp32, rounded once to bf16
+// (the semantics of the stand-alone dequantiser). (s0, b0) applies to values 0..31, (s1, b1) to
+// 32..63 (equal unless the group size is 32).
+__device__ __forceinline__ float e2m1_value(uint32_t nib) {
+  const uint32_t mag = nib & 7u, e = mag >> 1, m = mag & 1u;
+  const uint32_t bits = e ? (((e + 126u) << 23) | (m << 22)) : (m ? 0x3F000000u : 0u);
+  return __uint_as_float(bits | ((nib & 8u) << 28));
+}
+template <int WQ>
+__device__ __forceinline__ void dequant_row_to_tile(const uint8_t* pk_row, float s0, float b0, float s1,
+                                                    float b1, uint8_t* tile, int r, bool valid) {
+  uint8_t* dst = tile + r * 128;
+  if (!valid) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + (c << 4)) = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  if constexpr (WQ == 2) {   // 8-bit: 64 bytes, chunk c = bytes 8c .. 8c+7
+    uint32_t wds[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = *reinterpret_cast<const uint4*>(pk_row + i * 16);
+      wds[4 * i] = v.x, wds[4 * i + 1] = v.y, wds[4 * i + 2] = v.z, wds[4 * i + 3] = v.w;
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float sc = c < 4 ? s0 : s1, bi = c < 4 ? b0 : b1;
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t q = (wds[2 * c + (j >> 2)] >> (8 * (j & 3))) & 0xFFu;
+        f[j] = __uint_as_float(0x4B000000u | q) - 8388608.0f;   // exact int -> float without I2F
+        f[j] = f[j] * sc + bi;
+      }
+      uint4 o;
+      o.x = pack_bf16(f[0], f[1]), o.y = pack_bf16(f[2], f[3]), o.z = pack_bf16(f[4], f[5]), o.w = pack_bf16(f[6], f[7]);
+      *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
+    }
+  } else {                   // 4-bit: 32 bytes, chunk c = word c, nibbles LSB first
+    uint32_t wds[8];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint4 v = *reinterpret_cast<const uint4*>(pk_row + i * 16);
+      wds[4 * i] = v.x, wds[4 * i + 1] = v.y, wds[4 * i + 2] = v.z, wds[4 * i + 3] = v.w;
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float sc = c < 4 ? s0 : s1, bi = c < 4 ? b0 : b1;
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t q = (wds[c] >> (4 * j)) & 0xFu;
+        if constexpr (WQ == 3) {
+          f[j] = e2m1_value(q) * sc;
+        } else {
+          f[j] = __uint_as_float(0x4B000000u | q) - 8388608.0f;
+          f[j] = f[j] * sc + bi;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16(f[0], f[1]), o.y = pack_bf16(f[2], f[3]), o.z = pack_bf16(f[4], f[5]), o.w = pack_bf16(f[6], f[7]);
+      *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
+    }
+  }
+}
+__device__ __forceinline__ float e8m0_scale(uint8_t sv) {
+  if (sv == 255) return __uint_as_float(0x7fc00000u);
+  if (sv == 0) return __uint_as_float(0x00400000u);
+  return __uint_as_float(static_cast<uint32_t>(sv) << 23);
+}
+
+// WQ: weight format of the lane operand. 0 = bf16 (TMA writes the swizzled MMA tile directly);
+// otherwise the packed checkpoint bytes are staged by TMA and four extra "transform" warps
+// dequantise them into the swizzled bf16 tile that the MMA reads (weight-rows-on-lanes only):
+// 1 = affine 4-bit, 2 = affine 8-bit (q * scale + bias per group), 3 = mxfp4 (e2m1 * 2^(s-127)).
+__host__ __device__ constexpr int wq_bits(int wq) { return (wq == 2) ? 8 : 4; }
+__host__ __device__ constexpr int gemm_threads(int wq) { return wq != 0 ? kGemmThreads + 128 : kGemmThreads; }
+
+template <int BN, bool SWAP, bool GLU, int COMM, bool GROUPED, int WQ = 0>
+__global__ void __launch_bounds__(gemm_threads(WQ), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                  const __grid_constant__ CUtensorMap map_col, const GemmParams p) {
   constexpr int LANE_TILES = (SWAP && GLU) ? 2 : 1;
   constexpr int COL_TILES = (!SWAP && GLU) ? 2 : 1;
   constexpr int LANE_BYTES = kLaneRows * kBK * 2;
   constexpr int COL_BYTES = BN * kBK * 2;
-  constexpr int STAGE_BYTES = LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
+  constexpr int PK_ROW_BYTES = WQ != 0 ? kBK * wq_bits(WQ) / 8 : 0;   // packed bytes of one row per k-block
+  constexpr int PK_BYTES = kLaneRows * PK_ROW_BYTES;
+  constexpr int STAGE_BYTES = LANE_TILES * (LANE_BYTES + PK_BYTES) + COL_TILES * COL_BYTES;
+  constexpr int RAW_BYTES = LANE_TILES * PK_BYTES + COL_TILES * COL_BYTES;   // what TMA brings when WQ
+  static_assert(WQ == 0 || (SWAP && !GROUPED), "quantized weights: weight-rows-on-lanes, dense only");
   constexpr int ACC_COLS = GLU ? 2 * BN : BN;
   constexpr int TMEM_COLS = (2 * ACC_COLS <= 32)    ? 32
                             : (2 * ACC_COLS <= 64)  ? 64
@@ -303,7 +392,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* tmem_full = empty_bar + kMaxStages;
   uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  [[maybe_unused]] uint64_t* raw_full = tmem_empty + 2;   // WQ: packed weights + activations landed
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(raw_full + kMaxStages);
   int* last_flag = reinterpret_cast<int*>(tmem_ptr + 1);
   [[maybe_unused]] float* scale_sm = reinterpret_cast<float*>(ctrl + 256);   // per-token row scales of the tile
 
@@ -319,9 +409,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   [[maybe_unused]] uint64_t pol_lane = 0, pol_col = 0;
   [[maybe_unused]] int pre = 0;   // ring stages whose weight tiles are already in flight
   auto load_lane = [&](uint8_t* s, uint64_t* bar, int kb, int row0) {
-    tma_load_2d(s, &map_lane, bar, kb * kBK, row0, pol_lane);
-    if (LANE_TILES == 2) tma_load_2d(s + LANE_BYTES, &map_lane, bar, kb * kBK, row0 + p.glu_offset, pol_lane);
+    if constexpr (WQ != 0) {
+      // packed bytes of 128 weight rows for this k-block (byte-typed tensor map, no swizzle)
+      uint8_t* pk = s + LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
+      tma_load_2d(pk, &map_lane, bar, kb * PK_ROW_BYTES, row0, pol_lane);
+      if (LANE_TILES == 2) tma_load_2d(pk + PK_BYTES, &map_lane, bar, kb * PK_ROW_BYTES, row0 + p.glu_offset, pol_lane);
+    } else {
+      tma_load_2d(s, &map_lane, bar, kb * kBK, row0, pol_lane);
+      if (LANE_TILES == 2) tma_load_2d(s + LANE_BYTES, &map_lane, bar, kb * kBK, row0 + p.glu_offset, pol_lane);
+    }
   };
+  // barrier the TMA loads of a stage complete on: the MMA's when the tile is ready as loaded,
+  // the transform warps' when the weights still have to be dequantised
+  auto load_bar = [&](int stage) -> uint64_t* { return WQ != 0 ? &raw_full[stage] : &full_bar[stage]; };
+  constexpr int TX_BYTES = WQ != 0 ? RAW_BYTES : STAGE_BYTES;
   auto load_col = [&](uint8_t* s, uint64_t* bar, int kb, int row0) {
     uint8_t* sc = s + LANE_TILES * LANE_BYTES;
     tma_load_2d(sc, &map_col, bar, kb * kBK, row0, pol_col);
@@ -332,8 +433,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     tma_prefetch_desc(&map_lane);
     tma_prefetch_desc(&map_col);
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], WQ != 0 ? 4 : 1);
       mbar_init(&empty_bar[s], 1);
+      if constexpr (WQ != 0) mbar_init(&raw_full[s], 1);
     }
     mbar_init(&tmem_full[0], 1);
     mbar_init(&tmem_full[1], 1);
@@ -356,15 +458,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         pre = min(p.stages, kb1 - kb0);
         for (int i = 0; i < pre; ++i) {
-          mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+          mbar_expect_tx(load_bar(i), TX_BYTES);
           uint8_t* s = smem + i * STAGE_BYTES;
-          if (SWAP) load_lane(s, &full_bar[i], kb0 + i, it0.lane_row0);
-          else load_col(s, &full_bar[i], kb0 + i, it0.col_row0);
+          if (SWAP) load_lane(s, load_bar(i), kb0 + i, it0.lane_row0);
+          else load_col(s, load_bar(i), kb0 + i, it0.col_row0);
         }
         // The rest of this CTA's weight slice (up to a budget) goes to L2: HBM keeps streaming
         // through the previous kernels' epilogues and the small kernels in between, and the
         // main loop below then runs out of the 126 MB L2 instead of waiting on DRAM.
-        if constexpr (SWAP) {
+        if constexpr (SWAP && WQ == 0) {
           const int kbe = min(kb1, kb0 + pre + p.l2_prefetch_kb);
           for (int kb = kb0 + pre; kb < kbe; ++kb) {
             tma_prefetch_l2_2d(&map_lane, kb * kBK, it0.lane_row0);
@@ -406,16 +508,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           uint8_t* s = smem + stage * STAGE_BYTES;
           if (seq < pre) {
             // weight tile already in flight: only the activation tile is missing
-            if (SWAP) load_col(s, &full_bar[stage], kb, col_row0);
-            else load_lane(s, &full_bar[stage], kb, lane_row0);
+            if (SWAP) load_col(s, load_bar(stage), kb, col_row0);
+            else load_lane(s, load_bar(stage), kb, lane_row0);
           } else {
             if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kErrProducerWait)) {
               ok = false;
               break;
             }
-            mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-            load_lane(s, &full_bar[stage], kb, lane_row0);
-            load_col(s, &full_bar[stage], kb, col_row0);
+            mbar_expect_tx(load_bar(stage), TX_BYTES);
+            load_lane(s, load_bar(stage), kb, lane_row0);
+            load_col(s, load_bar(stage), kb, col_row0);
           }
           if (seq == 0) stamp(2);
           if (++stage == p.stages) {
@@ -485,6 +587,65 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       }
     }
     __syncwarp();
+  } else if (WQ != 0 && warp >= 6) {
+    // ------------------------------------------------------------------ transform (128 threads)
+    // thread = weight row of the tile: packed bytes (staged by TMA) -> swizzled bf16 MMA tile.
+    if constexpr (WQ != 0) {
+      const int r = static_cast<int>(threadIdx.x) - kGemmThreads;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      GroupCursor cur;
+      WorkItem it;
+      const int gpk = p.q_group >= kBK ? 0 : 1;   // second group inside a k-block (group size 32)
+      for (int w = blockIdx.x; ok && decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x) {
+        const int kb0 = it.split * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          // scales / biases of this k-block are requested before the wait for the packed bytes
+          float sc0[LANE_TILES], bi0[LANE_TILES], sc1[LANE_TILES], bi1[LANE_TILES];
+          bool valid[LANE_TILES];
+#pragma unroll
+          for (int lt = 0; lt < LANE_TILES; ++lt) {
+            const int R = it.lane_row0 + r + lt * p.glu_offset;
+            valid[lt] = R < p.q_rows;
+            sc0[lt] = sc1[lt] = 1.f;
+            bi0[lt] = bi1[lt] = 0.f;
+            if (valid[lt]) {
+              const size_t g0 = static_cast<size_t>(R) * p.q_groups_per_row + (kb * kBK) / p.q_group;
+              if constexpr (WQ == 3) {
+                const uint8_t* sp = static_cast<const uint8_t*>(p.q_scales);
+                sc0[lt] = e8m0_scale(sp[g0]);
+                sc1[lt] = e8m0_scale(sp[g0 + gpk]);
+              } else {
+                const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(p.q_scales);
+                sc0[lt] = __bfloat162float(sp[g0]);
+                sc1[lt] = __bfloat162float(sp[g0 + gpk]);
+                bi0[lt] = __bfloat162float(p.q_biases[g0]);
+                bi1[lt] = __bfloat162float(p.q_biases[g0 + gpk]);
+              }
+            }
+          }
+          if (!mbar_wait(&raw_full[stage], phase, p.status, kErrMmaWaitFull)) {
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + stage * STAGE_BYTES;
+          const uint8_t* pk = st + LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
+#pragma unroll
+          for (int lt = 0; lt < LANE_TILES; ++lt)
+            dequant_row_to_tile<WQ>(pk + lt * PK_BYTES + r * PK_ROW_BYTES, sc0[lt], bi0[lt], sc1[lt], bi1[lt],
+                                    st + lt * LANE_BYTES, r, valid[lt]);
+          fence_proxy_async_smem();   // generic-proxy writes -> visible to the MMA's async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[stage]);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (128 threads)
     const int q = warp & 3;              // TMEM lane quarter this warp may read
@@ -1235,6 +1396,37 @@ bool make_tensor_map_bf16(CUtensorMap* out, const void* ptr, uint64_t rows, uint
   return true;
 }
 
+// 2-D byte tensor [rows, row_bytes] with row stride ld_bytes; box {box_bytes (inner, multiple of
+// 16), box_rows}; no swizzle (packed quantized weights, unpacked by the transform warps).
+bool make_tensor_map_u8(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t row_bytes,
+                        uint64_t ld_bytes, uint32_t box_rows, uint32_t box_bytes) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{ptr, rows, row_bytes, ld_bytes, box_rows, box_bytes};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  cuuint64_t gdim[2] = {row_bytes, rows};
+  cuuint64_t gstride[1] = {ld_bytes};
+  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 65536) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
 // Tuning knob: resident CTAs per SM for the small-M weight-streaming path. With 2, the stage ring
 // of each CTA is halved and twice as many (shorter) split-K pieces are in flight, so one CTA's
 // prologue / epilogue latency overlaps the other's main loop.
@@ -1262,12 +1454,13 @@ int device_sm_count() {
 
 constexpr int ACC_COLS_HOST(int bn, bool glu) { return glu ? 2 * bn : bn; }
 
-template <int BN, bool SWAP, bool GLU, int COMM = 0, bool GROUPED = false>
+template <int BN, bool SWAP, bool GLU, int COMM = 0, bool GROUPED = false, int WQ = 0>
 static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams p, int grid,
                        cudaStream_t stream) {
   constexpr int LANE_TILES = (SWAP && GLU) ? 2 : 1;
   constexpr int COL_TILES = (!SWAP && GLU) ? 2 : 1;
-  constexpr int STAGE_BYTES = LANE_TILES * kLaneRows * kBK * 2 + COL_TILES * BN * kBK * 2;
+  constexpr int PK_BYTES = WQ != 0 ? kLaneRows * kBK * wq_bits(WQ) / 8 : 0;
+  constexpr int STAGE_BYTES = LANE_TILES * (kLaneRows * kBK * 2 + PK_BYTES) + COL_TILES * BN * kBK * 2;
   constexpr int STAGING_BYTES = SWAP ? BN * kLaneRows * 4 : 0;
   constexpr int kSmemBudget = 227 * 1024 - 1024 /*align*/ - kCtrlBytes - STAGING_BYTES;
   int stages = kSmemBudget / STAGE_BYTES;
@@ -1328,7 +1521,7 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
     }
     p.vec_ok = ok ? 1 : 0;
   }
-  auto kern = gemm_bf16_kernel<BN, SWAP, GLU, COMM, GROUPED>;
+  auto kern = gemm_bf16_kernel<BN, SWAP, GLU, COMM, GROUPED, WQ>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e =
@@ -1337,7 +1530,7 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
     prefer_max_shared(kern);
     configured = true;
   }
-  return static_cast<int>(launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, stream, ml, mc, p));
+  return static_cast<int>(launch_kernel(kern, dim3(grid), dim3(gemm_threads(WQ)), smem, stream, ml, mc, p));
 }
 
 }  // namespace mx
@@ -1371,6 +1564,29 @@ int take_row_norm(mx::GemmParams& p, bool swap, int N, int comm_mode) {
 }
 }  // namespace
 
+namespace {
+struct PendingQuant {
+  const void* scales = nullptr;
+  const void* biases = nullptr;
+  int group = 0, wq = 0;
+};
+thread_local PendingQuant g_quant;
+}  // namespace
+
+// Quantized weights for the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread: `w` of that
+// call then points to the packed checkpoint rows (ldw = bytes per packed row) and the kernel
+// dequantises them on the fly in its transform warps (M <= 256 only; the call returns -9 for
+// larger M, which the caller serves by dequantise + GEMM). wq: 1 affine 4-bit, 2 affine 8-bit
+// (bf16 scales and biases per group), 3 mxfp4 (e2m1 values, e8m0 scale bytes, group 32).
+// Replaces the reference's qmm / qmv kernels for M > 8 (mlx/backend/cuda/quantized/qmm_*.cu in its
+// MLX overlay) with a tcgen05 path.
+extern "C" void mx_gemm_set_quant(const void* scales, const void* biases, int group, int wq) {
+  g_quant.scales = scales;
+  g_quant.biases = biases;
+  g_quant.group = group;
+  g_quant.wq = wq;
+}
+
 // Deferred RMSNorm around the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread.
 //   ssq_in  (consumer): the GEMM input is an un-normalised residual stream whose norm weight was
 //           folded into W; every output row t is multiplied by rsqrt(sum_p ssq_in[p][t] * inv_dim +
@@ -1393,10 +1609,18 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
                             float glu_limit, void* workspace, long long ws_bytes, int force_mode,
                             int force_splits, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const PendingQuant quant = g_quant;   // one-shot
+  g_quant = PendingQuant{};
   if (M <= 0 || N <= 0 || K <= 0) return -1;
-  if ((K % 8) || (ldx % 8) || (ldw % 8)) return -1;
+  if ((K % 8) || (ldx % 8) || (quant.wq == 0 && (ldw % 8))) return -1;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
   if (workspace == nullptr || ws_bytes < MX_WS_PARTIAL_OFFSET) return -2;
+  if (quant.wq != 0) {
+    if (M > 256 || force_mode == 1) return -9;   // large M: dequantise + GEMM is the better split
+    if (K % kBK || quant.group < 32 || (quant.group & (quant.group - 1)) || quant.group > K ||
+        quant.wq < 1 || quant.wq > 3 || (ldw % 16))
+      return -1;
+  }
   const bool glu = epilogue == MX_EPI_SWIGLU || epilogue == MX_EPI_GEGLU ||
                    epilogue == MX_EPI_CLIPPED_SWIGLU;
   const bool swap = force_mode == 2 || (force_mode == 0 && M <= 256);
@@ -1424,6 +1648,11 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
   p.splits = 1;
   p.kb_per_split = p.num_kb;
   if (const int rn = take_row_norm(p, swap, N, 0); rn != 0) return rn;
+  p.q_scales = quant.scales;
+  p.q_biases = static_cast<const __nv_bfloat16*>(quant.biases);
+  p.q_group = quant.group;
+  p.q_groups_per_row = quant.wq != 0 ? K / quant.group : 0;
+  p.q_rows = w_rows;
 
   const int sms = device_sm_count();
   int bn;
@@ -1458,6 +1687,33 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
   const uint32_t x_box = swap ? bn : kLaneRows;
   const uint32_t w_box = swap ? kLaneRows : bn;
   if (!make_tensor_map_bf16(&map_x, x, M, K, ldx, x_box, kBK)) return -4;
+  if (quant.wq != 0) {
+    const int bits = wq_bits(quant.wq);
+    if (!make_tensor_map_u8(&map_w, w, w_rows, static_cast<uint64_t>(K) * bits / 8, ldw, kLaneRows, kBK * bits / 8))
+      return -4;
+#define MX_QLAUNCH(BN_, GLU_)                                                                        \
+    switch (quant.wq) {                                                                                \
+      case 1: return launch_gemm<BN_, true, GLU_, 0, false, 1>(map_w, map_x, p, grid, stream);         \
+      case 2: return launch_gemm<BN_, true, GLU_, 0, false, 2>(map_w, map_x, p, grid, stream);         \
+      default: return launch_gemm<BN_, true, GLU_, 0, false, 3>(map_w, map_x, p, grid, stream);        \
+    }
+    if (glu) {
+      switch (bn) {
+        case 16: MX_QLAUNCH(16, true);
+        case 32: MX_QLAUNCH(32, true);
+        case 64: MX_QLAUNCH(64, true);
+        default: MX_QLAUNCH(128, true);
+      }
+    } else {
+      switch (bn) {
+        case 16: MX_QLAUNCH(16, false);
+        case 32: MX_QLAUNCH(32, false);
+        case 64: MX_QLAUNCH(64, false);
+        default: MX_QLAUNCH(128, false);
+      }
+    }
+#undef MX_QLAUNCH
+  }
   if (!make_tensor_map_bf16(&map_w, w, w_rows, K, ldw, w_box, kBK)) return -4;
   const CUtensorMap& ml = swap ? map_w : map_x;
   const CUtensorMap& mc = swap ? map_x : map_w;
@@ -1503,9 +1759,18 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
                             void* expect, long long parity_stride, long long rank_stride,
                             void* workspace, long long ws_bytes, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const PendingQuant quant = g_quant;   // one-shot
+  g_quant = PendingQuant{};
   if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
     return -1;
-  if ((K % 8) || (ldx % 8) || (ldw % 8) || (N % 8) || (ldo % 8)) return -1;
+  if ((K % 8) || (ldx % 8) || (quant.wq == 0 && (ldw % 8)) || (N % 8) || (ldo % 8)) return -1;
+  if (quant.wq != 0) {
+    // quantized row-parallel projection -> all-reduce in one kernel (one-shot only)
+    if (mode != 1) return -9;
+    if (K % kBK || quant.group < 32 || (quant.group & (quant.group - 1)) || quant.group > K ||
+        quant.wq < 1 || quant.wq > 3 || (ldw % 16))
+      return -1;
+  }
   if (workspace == nullptr || ws_bytes < MX_WS_PARTIAL_OFFSET) return -2;
   if ((mode == 1 || mode == 3) && M > 256) return -1;
   if (mode < 1 || mode > 3) return -1;
@@ -1539,6 +1804,11 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
   p.comm.parity_stride = parity_stride;
   p.comm.rank_stride = rank_stride;
   if (const int rn = take_row_norm(p, swap, N, mode); rn != 0) return rn;
+  p.q_scales = quant.scales;
+  p.q_biases = static_cast<const __nv_bfloat16*>(quant.biases);
+  p.q_group = quant.group;
+  p.q_groups_per_row = quant.wq != 0 ? K / quant.group : 0;
+  p.q_rows = N;
 
   const int sms = device_sm_count();
   int bn;
@@ -1572,6 +1842,24 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
   const uint32_t x_box = swap ? bn : kLaneRows;
   const uint32_t w_box = swap ? kLaneRows : bn;
   if (!make_tensor_map_bf16(&map_x, x, M, K, ldx, x_box, kBK)) return -4;
+  if (quant.wq != 0) {
+    const int bits = wq_bits(quant.wq);
+    if (!make_tensor_map_u8(&map_w, w, N, static_cast<uint64_t>(K) * bits / 8, ldw, kLaneRows, kBK * bits / 8))
+      return -4;
+#define MX_QCLAUNCH(BN_)                                                                              \
+    switch (quant.wq) {                                                                                \
+      case 1: return launch_gemm<BN_, true, false, 1, false, 1>(map_w, map_x, p, grid, stream);        \
+      case 2: return launch_gemm<BN_, true, false, 1, false, 2>(map_w, map_x, p, grid, stream);        \
+      default: return launch_gemm<BN_, true, false, 1, false, 3>(map_w, map_x, p, grid, stream);       \
+    }
+    switch (bn) {
+      case 16: MX_QCLAUNCH(16);
+      case 32: MX_QCLAUNCH(32);
+      case 64: MX_QCLAUNCH(64);
+      default: MX_QCLAUNCH(128);
+    }
+#undef MX_QCLAUNCH
+  }
   if (!make_tensor_map_bf16(&map_w, w, N, K, ldw, w_box, kBK)) return -4;
   const CUtensorMap& ml = swap ? map_w : map_x;
   const CUtensorMap& mc = swap ? map_x : map_w;

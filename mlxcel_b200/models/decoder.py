@@ -93,8 +93,7 @@ def _glu_any(x, w, inter, act, bias, alpha, limit, row_norm=None):
     if isinstance(w, QuantizedTensor):
         from ..ops import quant
         assert row_norm is None, "deferred RMSNorm needs dense weights"
-        y = quant.qlinear(x, w, bias=bias)
-        return ops.swiglu(y, inter, act, alpha, limit)
+        return quant.qglu_linear(x, w, inter, act, bias=bias, alpha=alpha, limit=limit)
     return ops.glu_linear(x, w, inter, act, bias=bias, alpha=alpha, limit=limit, row_norm=row_norm)
 
 

@@ -104,6 +104,10 @@ def _declare(lib) -> None:
     if fn is not None:
         fn.restype = _ll
         fn.argtypes = [_i, _i, _i, _i]
+    fn = getattr(lib, "mx_gemm_set_quant", None)
+    if fn is not None:
+        fn.restype = None
+        fn.argtypes = [_vp, _vp, _i, _i]
     fn = getattr(lib, "mx_gemm_set_row_norm", None)
     if fn is not None:
         fn.restype = None

@@ -12,6 +12,8 @@ src/lib/mlxcel-core/cpp/mlx_cxx_kernels.cpp:3073-3152):
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -159,10 +161,68 @@ def dequantize(qt: QuantizedTensor, out: torch.Tensor | None = None) -> torch.Te
 _TMP: dict = {}
 
 
+_FUSED_WQ = {("affine", 4): 1, ("affine", 8): 2, ("mxfp4", 4): 3}
+_FUSED_QGEMM = os.environ.get("MLXCEL_B200_FUSED_QGEMM", "1") != "0"
+_QMV_MAX_M = int(os.environ.get("MLXCEL_B200_QMV_MAX_M", "8"))
+
+
+def fused_wq(qt: QuantizedTensor, M: int, K: int) -> int:
+    """Format code of the fused dequant GEMM for this tensor and batch, 0 when not covered."""
+    if not _FUSED_QGEMM or M > 256 or K % 64 or qt.packed.dim() != 2:
+        return 0
+    if qt.group_size not in (32, 64, 128) or qt.group_size > K:
+        return 0
+    return _FUSED_WQ.get((qt.mode, qt.bits), 0)
+
+
+def set_quant(qt: QuantizedTensor, wq: int) -> None:
+    """Announce packed weights to the next GEMM call (see mx_gemm_set_quant)."""
+    _lib.load().mx_gemm_set_quant(qt.scales.data_ptr(), _lib.ptr(qt.biases), qt.group_size, wq)
+
+
+def _fused_qgemm(x, qt, wq, out, bias, residual, inter=None, act=None, alpha=1.702, limit=7.0):
+    """Packed weights straight into the tcgen05 GEMM (dequantised by its transform warps)."""
+    from . import _ACT_TO_EPI, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
+
+    M, K = x.shape
+    N = qt.shape[-2] if inter is None else inter
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    if inter is None:
+        epi = EPI_RESIDUAL if residual is not None else (EPI_BIAS if bias is not None else EPI_NONE)
+    else:
+        epi = _ACT_TO_EPI[act]
+    ws = _lib.workspace(x.device)
+    lib = _lib.load()
+    set_quant(qt, wq)
+    rc = lib.mx_gemm_bf16(x.data_ptr(), qt.packed.data_ptr(), out.data_ptr(), _lib.ptr(bias), _lib.ptr(residual), M, N, K,
+                          x.stride(0), qt.packed.stride(0) * 4, out.stride(0),
+                          residual.stride(0) if residual is not None else 0, epi, 0, inter or 0, float(alpha),
+                          float(limit), ws.data_ptr(), ws.numel(), 0, 0, _lib.stream())
+    _lib.count_launch()
+    _lib.check(rc, "mx_gemm_bf16 (packed weights)")
+    return out
+
+
+def qglu_linear(x: torch.Tensor, qt: QuantizedTensor, inter: int, act: str, bias=None, alpha=1.702,
+                limit=7.0) -> torch.Tensor:
+    """Gated projection over packed weights: one kernel (dequantise + two accumulators + activation)
+    when the fused path covers the format, else quantized linear followed by the activation."""
+    from . import swiglu
+
+    M, K = x.shape
+    wq = fused_wq(qt, M, K) if x.is_cuda else 0
+    if wq and x.stride(1) == 1 and M > 0:
+        return _fused_qgemm(x, qt, wq, None, bias, None, inter=inter, act=act, alpha=alpha, limit=limit)
+    return swiglu(qlinear(x, qt, bias=bias), inter, act, alpha, limit)
+
+
 def qlinear(x: torch.Tensor, qt: QuantizedTensor, bias=None, residual=None, out=None) -> torch.Tensor:
     """``x @ dequant(w)^T (+ bias) (+ residual)``. M <= 8 rows stream the packed weights once
-    through the GEMV kernel; larger M dequantizes into a reused bf16 buffer and runs the tcgen05
-    GEMM (prefill is compute bound, so the extra pass is small there)."""
+    through the GEMV kernel; up to 256 rows go to the tcgen05 GEMM whose transform warps dequantise
+    the packed tiles in shared memory (weights are read once, at 4 or 8 bits); larger M dequantizes
+    into a reused bf16 buffer and runs the dense GEMM (prefill is compute bound, so the extra pass
+    is small there)."""
     from . import linear, reference as ref
 
     if not x.is_cuda:
@@ -170,6 +230,10 @@ def qlinear(x: torch.Tensor, qt: QuantizedTensor, bias=None, residual=None, out=
     M, K = x.shape
     N = qt.shape[-2]
     lib = _lib.load()
+    if M > _QMV_MAX_M or qt.bits not in (4, 8):
+        wq = fused_wq(qt, M, K)
+        if wq and x.stride(1) == 1 and M > 0:
+            return _fused_qgemm(x, qt, wq, out, bias, residual)
     if M <= 8 and qt.bits in (4, 8):
         if out is None:
             out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)

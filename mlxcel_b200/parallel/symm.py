@@ -147,8 +147,11 @@ class FusedOps:
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, bias, residual, ssq_out=None) -> torch.Tensor:
         """``residual + bias + sum_ranks(x_r @ w_r^T)``; the result is bitwise identical on all
         ranks and lives in the symmetric residual buffer."""
+        from ..models.weights import QuantizedTensor
+
         M, K = x.shape
-        N = w.shape[0]
+        qt = w if isinstance(w, QuantizedTensor) else None
+        N = w.shape[-2] if qt is not None else w.shape[0]
         lib = _lib.load()
         ws = _lib.workspace(x.device)
         out = self.hidden_buffer(M, N)
@@ -163,8 +166,18 @@ class FusedOps:
             assert mode == 1, "per-tile sums of squares come out of the one-shot epilogue only"
             from .. import ops
             ops._set_row_norm(None, ssq_out)
-        rc = lib.mx_gemm_comm(x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias), _lib.ptr(res),
-                              M, N, K, x.stride(0), w.stride(0), out.stride(0),
+        if qt is not None:
+            # packed weights: dequantised by the kernel's transform warps (one-shot all-reduce only),
+            # i.e. quantized GEMV/GEMM -> all-reduce in one kernel
+            from ..ops import quant
+            wq = quant.fused_wq(qt, M, K)
+            assert wq and mode == 1, "fused quantized row-parallel GEMM: covered formats, M <= 256"
+            quant.set_quant(qt, wq)
+            w_ptr, ldw = qt.packed.data_ptr(), qt.packed.stride(0) * 4
+        else:
+            w_ptr, ldw = w.data_ptr(), w.stride(0)
+        rc = lib.mx_gemm_comm(x.data_ptr(), w_ptr, out.data_ptr(), _lib.ptr(bias), _lib.ptr(res),
+                              M, N, K, x.stride(0), ldw, out.stride(0),
                               res.stride(0) if res is not None else 0, mode, self.rank, self.world,
                               ch.flags_peer, ch.recv_peer, self.h_peer, ch.ctl.data_ptr(),
                               ch.expect.data_ptr(), self.world * stride, stride, ws.data_ptr(),

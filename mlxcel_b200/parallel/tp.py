@@ -78,8 +78,12 @@ class TPComm:
 
         if self.tp_size == 1:
             return _linear_any(x, w, bias=bias, residual=residual, out=residual, ssq_out=ssq_out)
-        if self.backend == "fused" and not isinstance(w, QuantizedTensor) and (
-                x.shape[0] <= self.fused.small_m or _FUSED_PREFILL):
+        fused_ok = self.backend == "fused"
+        if fused_ok and isinstance(w, QuantizedTensor):
+            from ..ops import quant
+            fused_ok = (x.is_cuda and x.shape[0] <= self.fused.small_m and w.packed.dim() == 2
+                        and quant.fused_wq(w, x.shape[0], x.shape[1]) != 0)
+        if fused_ok and (x.shape[0] <= self.fused.small_m or _FUSED_PREFILL):
             one_shot = x.shape[0] <= self.fused.small_m
             y = self.fused.gemm_allreduce(x, w, bias, residual, ssq_out=ssq_out if one_shot else None)
             if ssq_out is not None and not one_shot:

@@ -8,6 +8,7 @@
     python -m mlxcel_b200.utils.profile_cases kbench           # CUDA-event timings of the hot kernels (JSON lines)
     python -m mlxcel_b200.utils.profile_cases gemm_graph       # decode GEMMs back to back inside a CUDA graph, us per kernel
     python -m mlxcel_b200.utils.profile_cases gemm_phases      # per-CTA phase timestamps of the decode GEMMs
+    python -m mlxcel_b200.utils.profile_cases qgemm_graph      # 4-bit weights: fused dequant GEMM vs GEMV vs dequantise + GEMM
 
 Every case holds at most a few GB on the device and launches a handful of kernels, so that a
 capture with ``ncu --set full -k regex:<kernel> -c <n>`` ends by itself. ``decode_steps`` brackets
@@ -248,7 +249,64 @@ def gemm_phases(M=64):
     case(14336, 4096, glu=True)
 
 
-CASES = dict(gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
+def qgemm_graph():
+    """Affine 4-bit (group 64) Llama-3.1-8B projections inside a CUDA graph (16 dependent launches over
+    4 rotating weight copies): the fused dequant GEMM (packed weights unpacked by the GEMM's transform
+    warps), the GEMV kernel (M <= 8) and dequantise-then-GEMM, with the time the packed weight stream
+    alone would take at the measured copy bandwidth."""
+    from ..ops import quant
+    nrep, ncopy = 16, 4
+
+    def graph_time(fn):
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                fn()
+        torch.cuda.synchronize()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(7):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2] * 1e3 / nrep
+
+    for N, K in [(6144, 4096), (4096, 4096), (4096, 14336), (28672, 4096)]:
+        qts = []
+        for i in range(ncopy):
+            w = torch.randn(N, K, device=DEV) * 0.02
+            qts.append(quant.quantize(w, "affine", 4, 64))
+            del w
+        packed_bytes = qts[0].nbytes()
+        for M in (1, 8, 32, 64):
+            x = _bf(M, K)
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+            r = dict(M=M, N=N, K=K, packed_MB=round(packed_bytes / 1e6, 1),
+                     stream_us_at_measured_copy_bw=round(packed_bytes / 6.5514e6, 1))
+            old = quant._QMV_MAX_M
+            quant._QMV_MAX_M = 0
+            r["fused_qgemm_us"] = round(graph_time(lambda: [quant.qlinear(x, qts[i % ncopy], out=out) for i in range(nrep)]), 1)
+            quant._QMV_MAX_M = old
+            if M <= 8:
+                r["qmv_us"] = round(graph_time(lambda: [quant.qlinear(x, qts[i % ncopy], out=out) for i in range(nrep)]), 1)
+            quant._FUSED_QGEMM = False
+            if M > 8:
+                r["dequant_then_gemm_us"] = round(
+                    graph_time(lambda: [quant.qlinear(x, qts[i % ncopy], out=out) for i in range(nrep)]), 1)
+            quant._FUSED_QGEMM = True
+            print(json.dumps(r), flush=True)
+
+
+CASES = dict(qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
              attn_prefill=attn_prefill, decode_steps=decode_steps, kbench=kbench)
 
 if __name__ == "__main__":

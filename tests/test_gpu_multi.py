@@ -85,6 +85,20 @@ def test_fused_gemm_allreduce_and_allgather():
                     assert (got2.float() - want).abs().max().item() < 0.25, (M, rep)
                     ref0 = got2.clone(); dist.broadcast(ref0, 0)
                     assert torch.equal(ref0, got2), (M, rep)
+            # quantized row-parallel projection -> all-reduce in one kernel (packed 4-bit shards)
+            if M <= 256:
+                from mlxcel_b200.ops import quant
+                qts = quant.quantize(w[:, ks].float().cpu(), "affine", 4, 64)
+                qts = qts.to(dev)
+                wdq = quant.dequantize_ref(qts).float()
+                parts = [torch.empty(N, 512, device=dev) for _ in range(world)]
+                dist.all_gather(parts, wdq.contiguous())
+                want_q = x.float() @ torch.cat(parts, dim=1).t() + bias.float() + res.float()
+                got_q = comm.row_parallel_linear(x[:, ks].contiguous(), qts, bias, res.clone())
+                torch.cuda.synchronize()
+                assert (got_q.float() - want_q).abs().max().item() < 0.3, (M, "q4")
+                ref0 = got_q.clone(); dist.broadcast(ref0, 0)
+                assert torch.equal(ref0, got_q), (M, "q4")
             # stand-alone all-reduce (one-shot for small, two-shot for large tensors)
             part = torch.randn(M, N, device=dev).to(torch.bfloat16) * (rank + 1)
             parts = [torch.empty_like(part) for _ in range(world)]

@@ -45,6 +45,33 @@ def test_qlinear(mode, bits, group, M):
     _close(got.cpu(), want, rtol=2e-2, atol=6e-2)
 
 
+@pytest.mark.parametrize("mode,bits,group", [("affine", 4, 64), ("affine", 4, 128), ("affine", 8, 32), ("mxfp4", 4, 32)])
+@pytest.mark.parametrize("M", [1, 16, 64, 200])
+def test_fused_dequant_gemm(monkeypatch, mode, bits, group, M):
+    """Packed weights dequantised inside the tcgen05 GEMM (transform warps): plain with bias and
+    residual, and the gated projection, for every batch size the path serves (M <= 256)."""
+    monkeypatch.setattr(quant, "_QMV_MAX_M", 0)      # also M <= 8 through the GEMM path
+    N, K, I = 640, 1536, 384                        # N not a multiple of the 128-row tile
+    g = torch.Generator().manual_seed(M)
+    w = torch.randn(N, K, generator=g) * 0.05
+    qt = quant.quantize(w, mode, bits, group)
+    wd = quant.dequantize_ref(qt)
+    x = (torch.randn(M, K, generator=g)).to(torch.bfloat16)
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g).to(torch.bfloat16)
+    assert quant.fused_wq(_qt_to(qt, DEV), M, K) != 0
+    got = quant.qlinear(x.to(DEV), _qt_to(qt, DEV), residual=res.to(DEV))
+    _close(got.cpu(), x.float() @ wd.t() + res.float(), rtol=2e-2, atol=6e-2)
+    got = quant.qlinear(x.to(DEV), _qt_to(qt, DEV), bias=bias.to(DEV))
+    _close(got.cpu(), x.float() @ wd.t() + bias.float(), rtol=2e-2, atol=6e-2)
+    wg = torch.randn(2 * I, K, generator=g) * 0.05
+    qg = quant.quantize(wg, mode, bits, group)
+    y = x.float() @ quant.dequantize_ref(qg).t()
+    want = torch.nn.functional.silu(y[:, :I]) * y[:, I:]
+    got = quant.qglu_linear(x.to(DEV), _qt_to(qg, DEV), I, "silu")
+    _close(got.cpu(), want, rtol=3e-2, atol=6e-2)
+
+
 @pytest.mark.parametrize("mode,norm", [("topk_softmax", True), ("softmax_topk", True), ("softmax_topk", False)])
 @pytest.mark.parametrize("E,k", [(8, 2), (128, 4), (60, 8)])
 def test_route(mode, norm, E, k):
