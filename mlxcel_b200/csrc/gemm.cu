@@ -352,6 +352,12 @@ __device__ __forceinline__ float e8m0_scale(uint8_t sv) {
 // dequantise them into the swizzled bf16 tile that the MMA reads (weight-rows-on-lanes only):
 // 1 = affine 4-bit, 2 = affine 8-bit (q * scale + bias per group), 3 = mxfp4 (e2m1 * 2^(s-127)).
 __host__ __device__ constexpr int wq_bits(int wq) { return (wq == 2) ? 8 : 4; }
+// Rows of one re-tiled block: 128 weight rows of 64 * bits / 8 bytes, followed by the block's scales
+// ([2 halves][128 rows]) and, for the affine formats, biases, stored as extra rows of the same
+// width so that one TMA box brings values and scales together.
+__host__ __device__ constexpr int wq_block_rows(int wq) {
+  return 128 + (wq == 3 ? 256 : 1024) / (64 * wq_bits(wq) / 8);
+}
 __host__ __device__ constexpr int gemm_threads(int wq) { return wq != 0 ? kGemmThreads + 128 : kGemmThreads; }
 
 template <int BN, bool SWAP, bool GLU, int COMM, bool GROUPED, int WQ = 0>
@@ -363,8 +369,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   constexpr int LANE_BYTES = kLaneRows * kBK * 2;
   constexpr int COL_BYTES = BN * kBK * 2;
   constexpr int PK_ROW_BYTES = WQ != 0 ? kBK * wq_bits(WQ) / 8 : 0;   // packed bytes of one row per k-block
-  constexpr int PK_BYTES = kLaneRows * PK_ROW_BYTES;
-  constexpr int STAGE_BYTES = LANE_TILES * (LANE_BYTES + PK_BYTES) + COL_TILES * COL_BYTES;
+  constexpr int PK_ROWS = WQ != 0 ? wq_block_rows(WQ) : 0;   // weight rows + scale / bias rows
+  constexpr int PK_BYTES = PK_ROWS * PK_ROW_BYTES;
+  // stages start on 1024-byte boundaries (the swizzled MMA tiles need that alignment)
+  constexpr int STAGE_BYTES = (LANE_TILES * (LANE_BYTES + PK_BYTES) + COL_TILES * COL_BYTES + 1023) / 1024 * 1024;
   constexpr int RAW_BYTES = LANE_TILES * PK_BYTES + COL_TILES * COL_BYTES;   // what TMA brings when WQ
   static_assert(WQ == 0 || (SWAP && !GROUPED), "quantized weights: weight-rows-on-lanes, dense only");
   constexpr int ACC_COLS = GLU ? 2 * BN : BN;
@@ -411,9 +419,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   auto load_lane = [&](uint8_t* s, uint64_t* bar, int kb, int row0) {
     if constexpr (WQ != 0) {
       // packed bytes of 128 weight rows for this k-block (byte-typed tensor map, no swizzle)
+      // The packed weights were re-tiled at load time: (128-row tile, k-block) -> one contiguous
+      // block of 128 x PK_ROW_BYTES bytes, so a box is a single 4 / 8 KB run in DRAM (row-major
+      // checkpoint rows would give 128 separate 32-byte pieces per box).
       uint8_t* pk = s + LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
-      tma_load_2d(pk, &map_lane, bar, kb * PK_ROW_BYTES, row0, pol_lane);
-      if (LANE_TILES == 2) tma_load_2d(pk + PK_BYTES, &map_lane, bar, kb * PK_ROW_BYTES, row0 + p.glu_offset, pol_lane);
+      const int t0 = row0 / kLaneRows;
+      tma_load_2d(pk, &map_lane, bar, 0, (t0 * p.num_kb + kb) * PK_ROWS, pol_lane);
+      if (LANE_TILES == 2)
+        tma_load_2d(pk + PK_BYTES, &map_lane, bar, 0, ((t0 + p.glu_offset / kLaneRows) * p.num_kb + kb) * PK_ROWS,
+                    pol_lane);
     } else {
       tma_load_2d(s, &map_lane, bar, kb * kBK, row0, pol_lane);
       if (LANE_TILES == 2) tma_load_2d(s + LANE_BYTES, &map_lane, bar, kb * kBK, row0 + p.glu_offset, pol_lane);
@@ -422,7 +436,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   // barrier the TMA loads of a stage complete on: the MMA's when the tile is ready as loaded,
   // the transform warps' when the weights still have to be dequantised
   auto load_bar = [&](int stage) -> uint64_t* { return WQ != 0 ? &raw_full[stage] : &full_bar[stage]; };
-  constexpr int TX_BYTES = WQ != 0 ? RAW_BYTES : STAGE_BYTES;
+  constexpr int TX_BYTES = WQ != 0 ? RAW_BYTES : LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
   auto load_col = [&](uint8_t* s, uint64_t* bar, int kb, int row0) {
     uint8_t* sc = s + LANE_TILES * LANE_BYTES;
     tma_load_2d(sc, &map_col, bar, kb * kBK, row0, pol_col);
@@ -597,35 +611,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       bool ok = true;
       GroupCursor cur;
       WorkItem it;
-      const int gpk = p.q_group >= kBK ? 0 : 1;   // second group inside a k-block (group size 32)
       for (int w = blockIdx.x; ok && decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x) {
         const int kb0 = it.split * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
-          // scales / biases of this k-block are requested before the wait for the packed bytes
-          float sc0[LANE_TILES], bi0[LANE_TILES], sc1[LANE_TILES], bi1[LANE_TILES];
-          bool valid[LANE_TILES];
-#pragma unroll
-          for (int lt = 0; lt < LANE_TILES; ++lt) {
-            const int R = it.lane_row0 + r + lt * p.glu_offset;
-            valid[lt] = R < p.q_rows;
-            sc0[lt] = sc1[lt] = 1.f;
-            bi0[lt] = bi1[lt] = 0.f;
-            if (valid[lt]) {
-              const size_t g0 = static_cast<size_t>(R) * p.q_groups_per_row + (kb * kBK) / p.q_group;
-              if constexpr (WQ == 3) {
-                const uint8_t* sp = static_cast<const uint8_t*>(p.q_scales);
-                sc0[lt] = e8m0_scale(sp[g0]);
-                sc1[lt] = e8m0_scale(sp[g0 + gpk]);
-              } else {
-                const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(p.q_scales);
-                sc0[lt] = __bfloat162float(sp[g0]);
-                sc1[lt] = __bfloat162float(sp[g0 + gpk]);
-                bi0[lt] = __bfloat162float(p.q_biases[g0]);
-                bi1[lt] = __bfloat162float(p.q_biases[g0 + gpk]);
-              }
-            }
-          }
           if (!mbar_wait(&raw_full[stage], phase, p.status, kErrMmaWaitFull)) {
             ok = false;
             break;
@@ -633,9 +622,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           uint8_t* st = smem + stage * STAGE_BYTES;
           const uint8_t* pk = st + LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
 #pragma unroll
-          for (int lt = 0; lt < LANE_TILES; ++lt)
-            dequant_row_to_tile<WQ>(pk + lt * PK_BYTES + r * PK_ROW_BYTES, sc0[lt], bi0[lt], sc1[lt], bi1[lt],
-                                    st + lt * LANE_BYTES, r, valid[lt]);
+          for (int lt = 0; lt < LANE_TILES; ++lt) {
+            // scales / biases of the block arrived with it: [2 halves][128 rows] after the values
+            const uint8_t* blk = pk + lt * PK_BYTES;
+            const uint8_t* ex = blk + kLaneRows * PK_ROW_BYTES;
+            float sc0, sc1, bi0 = 0.f, bi1 = 0.f;
+            if constexpr (WQ == 3) {
+              sc0 = e8m0_scale(ex[r]);
+              sc1 = e8m0_scale(ex[kLaneRows + r]);
+            } else {
+              const __nv_bfloat16* sp = reinterpret_cast<const __nv_bfloat16*>(ex);
+              sc0 = __bfloat162float(sp[r]);
+              sc1 = __bfloat162float(sp[kLaneRows + r]);
+              bi0 = __bfloat162float(sp[2 * kLaneRows + r]);
+              bi1 = __bfloat162float(sp[3 * kLaneRows + r]);
+            }
+            dequant_row_to_tile<WQ>(blk + r * PK_ROW_BYTES, sc0, bi0, sc1, bi1, st + lt * LANE_BYTES, r, true);
+          }
           fence_proxy_async_smem();   // generic-proxy writes -> visible to the MMA's async proxy
           __syncwarp();
           if (lane == 0) mbar_arrive(&full_bar[stage]);
@@ -1459,8 +1462,9 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
                        cudaStream_t stream) {
   constexpr int LANE_TILES = (SWAP && GLU) ? 2 : 1;
   constexpr int COL_TILES = (!SWAP && GLU) ? 2 : 1;
-  constexpr int PK_BYTES = WQ != 0 ? kLaneRows * kBK * wq_bits(WQ) / 8 : 0;
-  constexpr int STAGE_BYTES = LANE_TILES * (kLaneRows * kBK * 2 + PK_BYTES) + COL_TILES * BN * kBK * 2;
+  constexpr int PK_BYTES = WQ != 0 ? wq_block_rows(WQ) * kBK * wq_bits(WQ) / 8 : 0;
+  constexpr int STAGE_BYTES =
+      (LANE_TILES * (kLaneRows * kBK * 2 + PK_BYTES) + COL_TILES * BN * kBK * 2 + 1023) / 1024 * 1024;
   constexpr int STAGING_BYTES = SWAP ? BN * kLaneRows * 4 : 0;
   constexpr int kSmemBudget = 227 * 1024 - 1024 /*align*/ - kCtrlBytes - STAGING_BYTES;
   int stages = kSmemBudget / STAGE_BYTES;
@@ -1574,10 +1578,15 @@ thread_local PendingQuant g_quant;
 }  // namespace
 
 // Quantized weights for the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread: `w` of that
-// call then points to the packed checkpoint rows (ldw = bytes per packed row) and the kernel
-// dequantises them on the fly in its transform warps (M <= 256 only; the call returns -9 for
-// larger M, which the caller serves by dequantise + GEMM). wq: 1 affine 4-bit, 2 affine 8-bit
-// (bf16 scales and biases per group), 3 mxfp4 (e2m1 values, e8m0 scale bytes, group 32).
+// call then points to the weights RE-TILED for this kernel (built once at load time from the
+// checkpoint tensors, mlxcel_b200.ops.quant.tile_for_gemm): block (t, kb) holds 128 rows x
+// (64 * bits / 8) bytes of packed values (rows zero-padded to a multiple of 128), then the
+// block's scales [2 halves of the k-block][128 rows] and, for affine, biases, as extra rows of
+// the same width; blocks are ordered [row tile t][k-block kb]. One TMA box brings a whole block.
+// `scales` / `biases` / `group` of this call are unused (kept for callers of the row-major
+// kernels); ldw is ignored. The kernel dequantises the blocks in its transform warps (M <= 256
+// only; the call returns -9 for larger M, which the caller serves by dequantise + GEMM).
+// wq: 1 affine 4-bit, 2 affine 8-bit, 3 mxfp4 (e2m1 values, e8m0 scale bytes).
 // Replaces the reference's qmm / qmv kernels for M > 8 (mlx/backend/cuda/quantized/qmm_*.cu in its
 // MLX overlay) with a tcgen05 path.
 extern "C" void mx_gemm_set_quant(const void* scales, const void* biases, int group, int wq) {
@@ -1617,9 +1626,7 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
   if (workspace == nullptr || ws_bytes < MX_WS_PARTIAL_OFFSET) return -2;
   if (quant.wq != 0) {
     if (M > 256 || force_mode == 1) return -9;   // large M: dequantise + GEMM is the better split
-    if (K % kBK || quant.group < 32 || (quant.group & (quant.group - 1)) || quant.group > K ||
-        quant.wq < 1 || quant.wq > 3 || (ldw % 16))
-      return -1;
+    if (K % kBK || quant.wq < 1 || quant.wq > 3) return -1;
   }
   const bool glu = epilogue == MX_EPI_SWIGLU || epilogue == MX_EPI_GEGLU ||
                    epilogue == MX_EPI_CLIPPED_SWIGLU;
@@ -1689,8 +1696,12 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
   if (!make_tensor_map_bf16(&map_x, x, M, K, ldx, x_box, kBK)) return -4;
   if (quant.wq != 0) {
     const int bits = wq_bits(quant.wq);
-    if (!make_tensor_map_u8(&map_w, w, w_rows, static_cast<uint64_t>(K) * bits / 8, ldw, kLaneRows, kBK * bits / 8))
-      return -4;
+    // tiled weights: [ceil(w_rows / 128) * K / 64 blocks][128 rows][pkb bytes], fully contiguous
+    const uint64_t pkb = static_cast<uint64_t>(kBK) * bits / 8;
+    const uint32_t brows = static_cast<uint32_t>(wq_block_rows(quant.wq));
+    const uint64_t trows = static_cast<uint64_t>((w_rows + kLaneRows - 1) / kLaneRows) * p.num_kb * brows;
+    if (glu && (glu_offset % kLaneRows)) return -9;
+    if (!make_tensor_map_u8(&map_w, w, trows, pkb, pkb, brows, static_cast<uint32_t>(pkb))) return -4;
 #define MX_QLAUNCH(BN_, GLU_)                                                                        \
     switch (quant.wq) {                                                                                \
       case 1: return launch_gemm<BN_, true, GLU_, 0, false, 1>(map_w, map_x, p, grid, stream);         \
@@ -1767,9 +1778,7 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
   if (quant.wq != 0) {
     // quantized row-parallel projection -> all-reduce in one kernel (one-shot only)
     if (mode != 1) return -9;
-    if (K % kBK || quant.group < 32 || (quant.group & (quant.group - 1)) || quant.group > K ||
-        quant.wq < 1 || quant.wq > 3 || (ldw % 16))
-      return -1;
+    if (K % kBK || quant.wq < 1 || quant.wq > 3) return -1;
   }
   if (workspace == nullptr || ws_bytes < MX_WS_PARTIAL_OFFSET) return -2;
   if ((mode == 1 || mode == 3) && M > 256) return -1;
@@ -1844,8 +1853,10 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
   if (!make_tensor_map_bf16(&map_x, x, M, K, ldx, x_box, kBK)) return -4;
   if (quant.wq != 0) {
     const int bits = wq_bits(quant.wq);
-    if (!make_tensor_map_u8(&map_w, w, N, static_cast<uint64_t>(K) * bits / 8, ldw, kLaneRows, kBK * bits / 8))
-      return -4;
+    const uint64_t pkb = static_cast<uint64_t>(kBK) * bits / 8;
+    const uint32_t brows = static_cast<uint32_t>(wq_block_rows(quant.wq));
+    const uint64_t trows = static_cast<uint64_t>((N + kLaneRows - 1) / kLaneRows) * p.num_kb * brows;
+    if (!make_tensor_map_u8(&map_w, w, trows, pkb, pkb, brows, static_cast<uint32_t>(pkb))) return -4;
 #define MX_QCLAUNCH(BN_)                                                                              \
     switch (quant.wq) {                                                                                \
       case 1: return launch_gemm<BN_, true, false, 1, false, 1>(map_w, map_x, p, grid, stream);        \

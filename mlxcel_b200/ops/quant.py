@@ -175,9 +175,54 @@ def fused_wq(qt: QuantizedTensor, M: int, K: int) -> int:
     return _FUSED_WQ.get((qt.mode, qt.bits), 0)
 
 
-def set_quant(qt: QuantizedTensor, wq: int) -> None:
-    """Announce packed weights to the next GEMM call (see mx_gemm_set_quant)."""
-    _lib.load().mx_gemm_set_quant(qt.scales.data_ptr(), _lib.ptr(qt.biases), qt.group_size, wq)
+def tile_for_gemm(qt: QuantizedTensor) -> torch.Tensor:
+    """Re-tile a 2-D quantized matrix for the fused dequant GEMM (built once, cached on the tensor).
+
+    The checkpoint keeps every output row's packed values contiguous ([N, K*bits/32] words); a
+    128-row x 64-value MMA operand tile then consists of 128 pieces of 32 (4-bit) or 64 (8-bit)
+    bytes, 2 KB or more apart, and its scales sit in yet another tensor. The kernel wants each
+    (row tile, k-block) as ONE contiguous block that a single TMA box brings in:
+
+        uint8 [T, K/64, 128 + E, W]    W = 64*bits/8 bytes per row, T = ceil(N / 128) (zero-padded)
+        rows 0..127   packed values of the 128 weight rows
+        rows 128..    scales [2 halves of the k-block][128 rows], then biases likewise (affine),
+                      bf16 (affine) or e8m0 bytes (mxfp4)
+    """
+    cached = getattr(qt, "_gemm_tiles", None)
+    if cached is not None:
+        return cached
+    N, K = qt.shape[-2], qt.shape[-1]
+    bits, group = qt.bits, qt.group_size
+    T, nkb, W = (N + 127) // 128, K // 64, 64 * bits // 8
+    pad = T * 128 - N
+    by = qt.packed.contiguous().view(torch.uint8).view(N, nkb, W)
+    if pad:
+        by = torch.cat([by, torch.zeros(pad, nkb, W, dtype=torch.uint8, device=by.device)], 0)
+    vals = by.view(T, 128, nkb, W).permute(0, 2, 1, 3)                     # [T, nkb, 128, W]
+
+    def per_half(v):   # [N, K/group] -> bytes [T, nkb, 2 * 128 * itemsize]
+        halves = torch.arange(2 * nkb, device=v.device) * 32 // group      # group of every 32-value half
+        e = v.index_select(1, halves)                                      # [N, 2*nkb]
+        if pad:
+            e = torch.cat([e, torch.zeros(pad, 2 * nkb, dtype=e.dtype, device=e.device)], 0)
+        e = e.view(T, 128, nkb, 2).permute(0, 2, 3, 1).contiguous()        # [T, nkb, 2, 128]
+        return e.view(torch.uint8).view(T, nkb, -1)
+
+    extra = per_half(qt.scales)
+    if qt.biases is not None:
+        extra = torch.cat([extra, per_half(qt.biases)], dim=-1)
+    assert extra.shape[-1] % W == 0
+    tiles = torch.cat([vals, extra.view(T, nkb, -1, W)], dim=2).contiguous()
+    qt._gemm_tiles = tiles
+    return tiles
+
+
+def set_quant(qt: QuantizedTensor, wq: int):
+    """Announce re-tiled packed weights to the next GEMM call (see mx_gemm_set_quant); returns the
+    pointer to pass as ``w``."""
+    tiles = tile_for_gemm(qt)
+    _lib.load().mx_gemm_set_quant(None, None, qt.group_size, wq)
+    return tiles.data_ptr()
 
 
 def _fused_qgemm(x, qt, wq, out, bias, residual, inter=None, act=None, alpha=1.702, limit=7.0):
@@ -194,9 +239,9 @@ def _fused_qgemm(x, qt, wq, out, bias, residual, inter=None, act=None, alpha=1.7
         epi = _ACT_TO_EPI[act]
     ws = _lib.workspace(x.device)
     lib = _lib.load()
-    set_quant(qt, wq)
-    rc = lib.mx_gemm_bf16(x.data_ptr(), qt.packed.data_ptr(), out.data_ptr(), _lib.ptr(bias), _lib.ptr(residual), M, N, K,
-                          x.stride(0), qt.packed.stride(0) * 4, out.stride(0),
+    w_ptr = set_quant(qt, wq)
+    rc = lib.mx_gemm_bf16(x.data_ptr(), w_ptr, out.data_ptr(), _lib.ptr(bias), _lib.ptr(residual), M, N, K,
+                          x.stride(0), 0, out.stride(0),
                           residual.stride(0) if residual is not None else 0, epi, 0, inter or 0, float(alpha),
                           float(limit), ws.data_ptr(), ws.numel(), 0, 0, _lib.stream())
     _lib.count_launch()
@@ -212,7 +257,7 @@ def qglu_linear(x: torch.Tensor, qt: QuantizedTensor, inter: int, act: str, bias
 
     M, K = x.shape
     wq = fused_wq(qt, M, K) if x.is_cuda else 0
-    if wq and x.stride(1) == 1 and M > 0:
+    if wq and x.stride(1) == 1 and M > 0 and inter % 128 == 0:   # gate / up start on tile boundaries
         return _fused_qgemm(x, qt, wq, None, bias, None, inter=inter, act=act, alpha=alpha, limit=limit)
     return swiglu(qlinear(x, qt, bias=bias), inter, act, alpha, limit)
 

@@ -172,8 +172,7 @@ class FusedOps:
             from ..ops import quant
             wq = quant.fused_wq(qt, M, K)
             assert wq and mode == 1, "fused quantized row-parallel GEMM: covered formats, M <= 256"
-            quant.set_quant(qt, wq)
-            w_ptr, ldw = qt.packed.data_ptr(), qt.packed.stride(0) * 4
+            w_ptr, ldw = quant.set_quant(qt, wq), 0
         else:
             w_ptr, ldw = w.data_ptr(), w.stride(0)
         rc = lib.mx_gemm_comm(x.data_ptr(), w_ptr, out.data_ptr(), _lib.ptr(bias), _lib.ptr(res),

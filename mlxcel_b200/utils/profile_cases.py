@@ -306,7 +306,18 @@ def qgemm_graph():
             print(json.dumps(r), flush=True)
 
 
-CASES = dict(qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
+def qgemm_decode(M=32):
+    """Three launches of the fused dequant GEMM (affine 4-bit, group 64) at M tokens, 4096 x 14336."""
+    from ..ops import quant
+    quant._QMV_MAX_M = 0
+    x = _bf(M, 14336)
+    out = torch.empty(M, 4096, dtype=torch.bfloat16, device=DEV)
+    for _ in range(3):
+        qt = quant.quantize(torch.randn(4096, 14336, device=DEV) * 0.02, "affine", 4, 64)
+        quant.qlinear(x, qt, out=out)
+
+
+CASES = dict(qgemm_decode=qgemm_decode, qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
              attn_prefill=attn_prefill, decode_steps=decode_steps, kbench=kbench)
 
 if __name__ == "__main__":
