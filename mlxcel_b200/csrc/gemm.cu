@@ -284,29 +284,56 @@ __device__ __forceinline__ float e2m1_value(uint32_t nib) {
   const uint32_t bits = e ? (((e + 126u) << 23) | (m << 22)) : (m ? 0x3F000000u : 0u);
   return __uint_as_float(bits | ((nib & 8u) << 28));
 }
+// `half` selects values 0..31 (chunks 0..3) or 32..63 (chunks 4..7) of the row; sc / bi are the
+// scale and bias of that half.
 template <int WQ>
-__device__ __forceinline__ void dequant_row_to_tile(const uint8_t* pk_row, float s0, float b0, float s1,
-                                                    float b1, uint8_t* tile, int r, bool valid) {
+__device__ __forceinline__ void dequant_half_row_to_tile(const uint8_t* pk_row, int half, float sc, float bi,
+                                                         __nv_bfloat16 sb, __nv_bfloat16 bb, uint8_t* tile,
+                                                         int r) {
   uint8_t* dst = tile + r * 128;
-  if (!valid) {
+  if constexpr (WQ == 1) {
+    // affine 4-bit on packed bf16 pairs: (w >> 4i) & 0x000F000F | 0x43004300 is the bf16 pair
+    // (128 + n_i, 128 + n_{i+4}); minus 128 is exact, then one fused multiply-add per pair
+    // (q * scale + bias, rounded once to bf16), and byte permutes restore the value order.
+    const uint4 v = *reinterpret_cast<const uint4*>(pk_row + half * 16);
+    const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+    const __nv_bfloat162 s2 = __halves2bfloat162(sb, sb), b2 = __halves2bfloat162(bb, bb);
+    const uint32_t k128 = 0x43004300u;
+    const __nv_bfloat162 c128 = *reinterpret_cast<const __nv_bfloat162*>(&k128);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + (c << 4)) = make_uint4(0, 0, 0, 0);
+    for (int cc = 0; cc < 4; ++cc) {
+      uint32_t pr[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t raw = ((wds[cc] >> (4 * i)) & 0x000F000Fu) | k128;
+        __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&raw);
+        x = __hfma2(__hsub2(x, c128), s2, b2);
+        pr[i] = *reinterpret_cast<uint32_t*>(&x);   // (n_i, n_{i+4})
+      }
+      uint4 o;
+      o.x = __byte_perm(pr[0], pr[1], 0x5410);   // (n0, n1)
+      o.y = __byte_perm(pr[2], pr[3], 0x5410);   // (n2, n3)
+      o.z = __byte_perm(pr[0], pr[1], 0x7632);   // (n4, n5)
+      o.w = __byte_perm(pr[2], pr[3], 0x7632);   // (n6, n7)
+      const int c = half * 4 + cc;
+      *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
+    }
     return;
   }
-  if constexpr (WQ == 2) {   // 8-bit: 64 bytes, chunk c = bytes 8c .. 8c+7
-    uint32_t wds[16];
+  if constexpr (WQ == 2) {   // 8-bit: 32 bytes per half, chunk = 8 bytes
+    uint32_t wds[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 v = *reinterpret_cast<const uint4*>(pk_row + i * 16);
+    for (int i = 0; i < 2; ++i) {
+      const uint4 v = *reinterpret_cast<const uint4*>(pk_row + half * 32 + i * 16);
       wds[4 * i] = v.x, wds[4 * i + 1] = v.y, wds[4 * i + 2] = v.z, wds[4 * i + 3] = v.w;
     }
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const float sc = c < 4 ? s0 : s1, bi = c < 4 ? b0 : b1;
+    for (int cc = 0; cc < 4; ++cc) {
+      const int c = half * 4 + cc;
       float f[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const uint32_t q = (wds[2 * c + (j >> 2)] >> (8 * (j & 3))) & 0xFFu;
+        const uint32_t q = (wds[2 * cc + (j >> 2)] >> (8 * (j & 3))) & 0xFFu;
         f[j] = __uint_as_float(0x4B000000u | q) - 8388608.0f;   // exact int -> float without I2F
         f[j] = f[j] * sc + bi;
       }
@@ -314,20 +341,16 @@ __device__ __forceinline__ void dequant_row_to_tile(const uint8_t* pk_row, float
       o.x = pack_bf16(f[0], f[1]), o.y = pack_bf16(f[2], f[3]), o.z = pack_bf16(f[4], f[5]), o.w = pack_bf16(f[6], f[7]);
       *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
     }
-  } else {                   // 4-bit: 32 bytes, chunk c = word c, nibbles LSB first
-    uint32_t wds[8];
+  } else {                   // 4-bit: 16 bytes per half, chunk = one word, nibbles LSB first
+    const uint4 v = *reinterpret_cast<const uint4*>(pk_row + half * 16);
+    const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const uint4 v = *reinterpret_cast<const uint4*>(pk_row + i * 16);
-      wds[4 * i] = v.x, wds[4 * i + 1] = v.y, wds[4 * i + 2] = v.z, wds[4 * i + 3] = v.w;
-    }
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const float sc = c < 4 ? s0 : s1, bi = c < 4 ? b0 : b1;
+    for (int cc = 0; cc < 4; ++cc) {
+      const int c = half * 4 + cc;
       float f[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const uint32_t q = (wds[c] >> (4 * j)) & 0xFu;
+        const uint32_t q = (wds[cc] >> (4 * j)) & 0xFu;
         if constexpr (WQ == 3) {
           f[j] = e2m1_value(q) * sc;
         } else {
@@ -371,6 +394,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   constexpr int PK_ROW_BYTES = WQ != 0 ? kBK * wq_bits(WQ) / 8 : 0;   // packed bytes of one row per k-block
   constexpr int PK_ROWS = WQ != 0 ? wq_block_rows(WQ) : 0;   // weight rows + scale / bias rows
   constexpr int PK_BYTES = PK_ROWS * PK_ROW_BYTES;
+  static_assert(PK_BYTES % 256 == 0, "re-tiled blocks are loaded as rows of 256 bytes");
   // stages start on 1024-byte boundaries (the swizzled MMA tiles need that alignment)
   constexpr int STAGE_BYTES = (LANE_TILES * (LANE_BYTES + PK_BYTES) + COL_TILES * COL_BYTES + 1023) / 1024 * 1024;
   constexpr int RAW_BYTES = LANE_TILES * PK_BYTES + COL_TILES * COL_BYTES;   // what TMA brings when WQ
@@ -424,9 +448,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
       // checkpoint rows would give 128 separate 32-byte pieces per box).
       uint8_t* pk = s + LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
       const int t0 = row0 / kLaneRows;
-      tma_load_2d(pk, &map_lane, bar, 0, (t0 * p.num_kb + kb) * PK_ROWS, pol_lane);
+      // (the tensor map views the contiguous blocks as rows of 256 bytes: few, wide TMA requests)
+      constexpr int BOX_ROWS = PK_BYTES / 256;
+      tma_load_2d(pk, &map_lane, bar, 0, (t0 * p.num_kb + kb) * BOX_ROWS, pol_lane);
       if (LANE_TILES == 2)
-        tma_load_2d(pk + PK_BYTES, &map_lane, bar, 0, ((t0 + p.glu_offset / kLaneRows) * p.num_kb + kb) * PK_ROWS,
+        tma_load_2d(pk + PK_BYTES, &map_lane, bar, 0, ((t0 + p.glu_offset / kLaneRows) * p.num_kb + kb) * BOX_ROWS,
                     pol_lane);
     } else {
       tma_load_2d(s, &map_lane, bar, kb * kBK, row0, pol_lane);
@@ -447,7 +473,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     tma_prefetch_desc(&map_lane);
     tma_prefetch_desc(&map_col);
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&full_bar[s], WQ != 0 ? 4 : 1);
+      mbar_init(&full_bar[s], WQ != 0 ? 8 : 1);
       mbar_init(&empty_bar[s], 1);
       if constexpr (WQ != 0) mbar_init(&raw_full[s], 1);
     }
@@ -503,6 +529,44 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   // before its first access to memory that kernel may have written.
   pdl_trigger();
   if (threadIdx.x == 0) stamp(1);
+
+  // Quantized weights: packed block (staged by TMA, scales and biases in its trailing rows) ->
+  // swizzled bf16 MMA tile, for all k-blocks of one work item. Eight warps take part (the four
+  // transform warps and the four epilogue warps, which are idle during the main loop): thread =
+  // (weight row, half of its 64 values); all eight arrive on full_bar per stage.
+  [[maybe_unused]] auto transform_item = [&](const WorkItem& it, int half, int r, int& stage, uint32_t& phase) -> bool {
+    if constexpr (WQ != 0) {
+      const int kb0 = it.split * p.kb_per_split;
+      const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&raw_full[stage], phase, p.status, kErrMmaWaitFull)) return false;
+        uint8_t* st = smem + stage * STAGE_BYTES;
+        const uint8_t* pk = st + LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
+#pragma unroll
+        for (int lt = 0; lt < LANE_TILES; ++lt) {
+          const uint8_t* blk = pk + lt * PK_BYTES;
+          const uint8_t* ex = blk + kLaneRows * PK_ROW_BYTES;   // [2 halves][128 rows] scales, then biases
+          if constexpr (WQ == 3) {
+            dequant_half_row_to_tile<WQ>(blk + r * PK_ROW_BYTES, half, e8m0_scale(ex[half * kLaneRows + r]), 0.f,
+                                         __nv_bfloat16(), __nv_bfloat16(), st + lt * LANE_BYTES, r);
+          } else {
+            const __nv_bfloat16* sp = reinterpret_cast<const __nv_bfloat16*>(ex);
+            const __nv_bfloat16 sb = sp[half * kLaneRows + r], bb = sp[(2 + half) * kLaneRows + r];
+            dequant_half_row_to_tile<WQ>(blk + r * PK_ROW_BYTES, half, __bfloat162float(sb), __bfloat162float(bb),
+                                         sb, bb, st + lt * LANE_BYTES, r);
+          }
+        }
+        fence_proxy_async_smem();   // generic-proxy writes -> visible to the MMA's async proxy
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) mbar_arrive(&full_bar[stage]);
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    return true;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -602,52 +666,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     }
     __syncwarp();
   } else if (WQ != 0 && warp >= 6) {
-    // ------------------------------------------------------------------ transform (128 threads)
-    // thread = weight row of the tile: packed bytes (staged by TMA) -> swizzled bf16 MMA tile.
+    // ------------------------------------------------------------------ transform (first halves)
     if constexpr (WQ != 0) {
       const int r = static_cast<int>(threadIdx.x) - kGemmThreads;
       int stage = 0;
       uint32_t phase = 0;
-      bool ok = true;
       GroupCursor cur;
       WorkItem it;
-      for (int w = blockIdx.x; ok && decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x) {
-        const int kb0 = it.split * p.kb_per_split;
-        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&raw_full[stage], phase, p.status, kErrMmaWaitFull)) {
-            ok = false;
-            break;
-          }
-          uint8_t* st = smem + stage * STAGE_BYTES;
-          const uint8_t* pk = st + LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
-#pragma unroll
-          for (int lt = 0; lt < LANE_TILES; ++lt) {
-            // scales / biases of the block arrived with it: [2 halves][128 rows] after the values
-            const uint8_t* blk = pk + lt * PK_BYTES;
-            const uint8_t* ex = blk + kLaneRows * PK_ROW_BYTES;
-            float sc0, sc1, bi0 = 0.f, bi1 = 0.f;
-            if constexpr (WQ == 3) {
-              sc0 = e8m0_scale(ex[r]);
-              sc1 = e8m0_scale(ex[kLaneRows + r]);
-            } else {
-              const __nv_bfloat16* sp = reinterpret_cast<const __nv_bfloat16*>(ex);
-              sc0 = __bfloat162float(sp[r]);
-              sc1 = __bfloat162float(sp[kLaneRows + r]);
-              bi0 = __bfloat162float(sp[2 * kLaneRows + r]);
-              bi1 = __bfloat162float(sp[3 * kLaneRows + r]);
-            }
-            dequant_row_to_tile<WQ>(blk + r * PK_ROW_BYTES, sc0, bi0, sc1, bi1, st + lt * LANE_BYTES, r, true);
-          }
-          fence_proxy_async_smem();   // generic-proxy writes -> visible to the MMA's async proxy
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full_bar[stage]);
-          if (++stage == p.stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-      }
+      for (int w = blockIdx.x; decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x)
+        if (!transform_item(it, 0, r, stage, phase)) break;
     }
   } else {
     // ------------------------------------------------------------------ epilogue (128 threads)
@@ -662,8 +689,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
     if constexpr (COMM != 0) comm_parity = *reinterpret_cast<volatile uint32_t*>(p.comm.ctl) & 1u;
     GroupCursor cur;
     WorkItem it;
+    [[maybe_unused]] int t_stage = 0;
+    [[maybe_unused]] uint32_t t_phase = 0;
     for (int w = blockIdx.x; decode_work<BN, SWAP, GROUPED>(p, w, cur, it); w += gridDim.x) {
       const int tile = it.tile, split = it.split;
+      if constexpr (WQ != 0) {
+        // second halves of this item's weight rows (these warps have nothing else to do until the
+        // accumulator is ready)
+        if (!transform_item(it, 1, epi_tid, t_stage, t_phase)) break;
+      }
       // Deferred RMSNorm, consumer side: this GEMM reads the un-normalised residual stream (the
       // norm weight is folded into W) and scales every output row by the row's 1/rms, summed here
       // from the partial sums the producing kernel left, while the main loop is still running.
@@ -1698,10 +1732,10 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
     const int bits = wq_bits(quant.wq);
     // tiled weights: [ceil(w_rows / 128) * K / 64 blocks][128 rows][pkb bytes], fully contiguous
     const uint64_t pkb = static_cast<uint64_t>(kBK) * bits / 8;
-    const uint32_t brows = static_cast<uint32_t>(wq_block_rows(quant.wq));
+    const uint32_t brows = static_cast<uint32_t>(wq_block_rows(quant.wq) * pkb / 256);   // 256-byte rows per block
     const uint64_t trows = static_cast<uint64_t>((w_rows + kLaneRows - 1) / kLaneRows) * p.num_kb * brows;
     if (glu && (glu_offset % kLaneRows)) return -9;
-    if (!make_tensor_map_u8(&map_w, w, trows, pkb, pkb, brows, static_cast<uint32_t>(pkb))) return -4;
+    if (!make_tensor_map_u8(&map_w, w, trows, 256, 256, brows, 256)) return -4;
 #define MX_QLAUNCH(BN_, GLU_)                                                                        \
     switch (quant.wq) {                                                                                \
       case 1: return launch_gemm<BN_, true, GLU_, 0, false, 1>(map_w, map_x, p, grid, stream);         \
@@ -1854,9 +1888,9 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
   if (quant.wq != 0) {
     const int bits = wq_bits(quant.wq);
     const uint64_t pkb = static_cast<uint64_t>(kBK) * bits / 8;
-    const uint32_t brows = static_cast<uint32_t>(wq_block_rows(quant.wq));
+    const uint32_t brows = static_cast<uint32_t>(wq_block_rows(quant.wq) * pkb / 256);
     const uint64_t trows = static_cast<uint64_t>((N + kLaneRows - 1) / kLaneRows) * p.num_kb * brows;
-    if (!make_tensor_map_u8(&map_w, w, trows, pkb, pkb, brows, static_cast<uint32_t>(pkb))) return -4;
+    if (!make_tensor_map_u8(&map_w, w, trows, 256, 256, brows, 256)) return -4;
 #define MX_QCLAUNCH(BN_)                                                                              \
     switch (quant.wq) {                                                                                \
       case 1: return launch_gemm<BN_, true, false, 1, false, 1>(map_w, map_x, p, grid, stream);        \

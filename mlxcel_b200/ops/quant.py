@@ -163,7 +163,7 @@ _TMP: dict = {}
 
 _FUSED_WQ = {("affine", 4): 1, ("affine", 8): 2, ("mxfp4", 4): 3}
 _FUSED_QGEMM = os.environ.get("MLXCEL_B200_FUSED_QGEMM", "1") != "0"
-_QMV_MAX_M = int(os.environ.get("MLXCEL_B200_QMV_MAX_M", "8"))
+_QMV_MAX_M = int(os.environ.get("MLXCEL_B200_QMV_MAX_M", "1"))   # rows served by the GEMV kernel
 
 
 def fused_wq(qt: QuantizedTensor, M: int, K: int) -> int:
