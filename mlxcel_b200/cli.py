@@ -85,7 +85,8 @@ def load_llm(a):
         from .tokenizer import ByteTokenizer
         llm.tokenizer = ByteTokenizer(llm.cfg.vocab_size)
         return llm
-    return LLM.from_pretrained(a.model, device=dev, engine_config=ecfg, comm=comm, dequantize=a.dequantize)
+    return LLM.from_pretrained(a.model, device=dev, engine_config=ecfg, comm=comm, dequantize=a.dequantize,
+                               surgery=getattr(a, "surgery", None))
 
 
 def cmd_generate(a):
@@ -164,6 +165,14 @@ def cmd_serve(a):
         keys |= {l.strip() for l in open(a.api_key_file) if l.strip()}
     state = ServerState(worker, llm.tokenizer, worker.model_id, api_keys=keys,
                         chat_template=open(a.chat_template_file).read() if a.chat_template_file else None)
+    from .lora import LoraManager
+    from .models.weights import QuantizedTensor
+    if not any(isinstance(lw.wqkv, QuantizedTensor) for lw in llm.model.w.layers):
+        comm = llm.model.comm
+        state.lora = LoraManager(llm.cfg, llm.model.w, comm.tp_rank, comm.tp_size)
+        for spec in getattr(a, "lora", None) or []:
+            path, _, sc = spec.partition("=")
+            state.lora.add(path, float(sc) if sc else 1.0)
     uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="info" if a.verbose else "warning",
                 ssl_certfile=a.ssl_cert_file, ssl_keyfile=a.ssl_key_file)
 
@@ -232,6 +241,9 @@ def main(argv=None):
     p.add_argument("--api-key-file", default=None)
     p.add_argument("--alias", "-a", default=None)
     p.add_argument("--chat-template-file", default=None)
+    p.add_argument("--lora", action="append", default=None, metavar="DIR[=SCALE]",
+                   help="attach a LoRA adapter directory (repeatable); scales can be changed live via /lora-adapters")
+    p.add_argument("--surgery", default=None, metavar="YAML", help="load-time weight edits (see loading/surgery.py)")
     p.add_argument("--ssl-cert-file", default=None)
     p.add_argument("--ssl-key-file", default=None)
     p.add_argument("-v", "--verbose", action="store_true")

@@ -42,12 +42,12 @@ class LLM:
 
     @staticmethod
     def from_pretrained(path: str | Path, *, device="cuda", engine_config: EngineConfig | None = None,
-                        comm=None, dequantize: bool = False) -> "LLM":
+                        comm=None, dequantize: bool = False, surgery: str | None = None) -> "LLM":
         from .loading.checkpoint import load_model_weights
         from .tokenizer import load_tokenizer
 
         cfg = ModelConfig.from_path(path)
-        w = load_model_weights(path, cfg, device=device, comm=comm, dequantize=dequantize)
+        w = load_model_weights(path, cfg, device=device, comm=comm, dequantize=dequantize, surgery=surgery)
         tok = load_tokenizer(path)
         return LLM(cfg, w, engine_config, comm=comm, tokenizer=tok, fold_norms=True)
 

@@ -57,7 +57,19 @@ class TensorSource:
     def has(self, name: str) -> bool:
         return name in self.index
 
+    def set_edits(self, edits: list[dict]) -> None:
+        """Load-time weight surgery (see ``loading/surgery.py``): applied to every tensor fetched."""
+        self.edits = list(edits)
+
     def get(self, name: str) -> torch.Tensor:
+        t = self._get_raw(name)
+        edits = getattr(self, "edits", None)
+        if edits and t.is_floating_point():
+            from .surgery import apply_edits
+            t = apply_edits(edits, name, t, lambda n: self._get_raw(n) if n in self.index else None)
+        return t
+
+    def _get_raw(self, name: str) -> torch.Tensor:
         f = self.index[name]
         h = self._handles.get(f)
         if h is None:
@@ -262,9 +274,13 @@ def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
 
 
 def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, dequantize: bool = False,
-                      layers: range | None = None) -> ModelWeights:
-    """Read a checkpoint directory into host memory in the executor's fused layout."""
+                      layers: range | None = None, surgery: str | None = None) -> ModelWeights:
+    """Read a checkpoint directory into host memory in the executor's fused layout.
+    ``surgery``: YAML file of load-time weight edits (``loading/surgery.py``)."""
     src = TensorSource(path)
+    if surgery:
+        from .surgery import load_edits
+        src.set_edits(load_edits(surgery))
     g = _Getter(src, cfg, dtype, dequantize)
     pre = "model." if any(k.startswith("model.") for k in src.keys()) else ""
     if any(k.startswith("language_model.model.") for k in src.keys()):
@@ -324,9 +340,9 @@ def _to_device(w: ModelWeights, device) -> ModelWeights:
 
 
 def load_model_weights(path: str | Path, cfg: ModelConfig, device="cuda", comm=None, dequantize: bool = False,
-                       layers: range | None = None, dtype=torch.bfloat16) -> ModelWeights:
+                       layers: range | None = None, dtype=torch.bfloat16, surgery: str | None = None) -> ModelWeights:
     """Load, shard for this rank (tensor / expert parallel, pipeline layer range) and upload."""
-    full = load_full_weights(path, cfg, dtype=dtype, dequantize=dequantize, layers=layers)
+    full = load_full_weights(path, cfg, dtype=dtype, dequantize=dequantize, layers=layers, surgery=surgery)
     tp = comm.tp_size if comm is not None else 1
     if tp > 1:
         full = shard_weights(cfg, full, comm.tp_rank, tp, ep=getattr(comm, "ep_size", tp))

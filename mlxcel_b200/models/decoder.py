@@ -153,6 +153,7 @@ class DecoderModel:
             for r0 in range(0, w.shape[0], 8192):      # bounded fp32 temporaries
                 w[r0:r0 + 8192] = (w[r0:r0 + 8192].float() * g).to(w.dtype)
             w._norm_folded = True
+            w._norm_gain = g.squeeze(0)     # weight deltas applied later (LoRA) must be folded the same way
 
         with torch.no_grad():
             for lw in layers:

@@ -72,6 +72,7 @@ class ServerState:
         self.chat_template = chat_template or getattr(tokenizer, "chat_template", None)
         self.started = time.time()
         self.responses: dict[str, dict] = {}
+        self.lora = None      # LoraManager when the weights are dense
 
     def render(self, messages, tools=None, **kw) -> str:
         return render_chat(messages, self.chat_template, tools=tools,
@@ -167,7 +168,72 @@ def create_app(state: ServerState) -> FastAPI:
 
     @app.get("/lora-adapters")
     async def lora_adapters():
-        return []
+        return state.lora.listing() if state.lora is not None else []
+
+    @app.post("/lora-adapters")
+    async def lora_set(body: list[dict]):
+        """llama-server contract: ``[{"id": 0, "scale": 0.5}, ...]`` sets live adapter scales; an
+        entry with ``"path"`` attaches a new adapter. Applied between engine steps."""
+        if state.lora is None:
+            return _err(400, "the server was started without LoRA support (dense weights are required)")
+
+        def apply():
+            for e in body:
+                if "path" in e and e.get("id") not in state.lora.adapters:
+                    state.lora.add(e["path"], float(e.get("scale", 1.0)), e.get("id"))
+                else:
+                    state.lora.set_scale(int(e["id"]), float(e.get("scale", 1.0)))
+            state.worker.engine.bm.reset_prefix_cache()     # cached KV belongs to the old weights
+            return state.lora.listing()
+
+        try:
+            return await asyncio.get_running_loop().run_in_executor(None, state.worker.run_exclusive, apply)
+        except (KeyError, ValueError, FileNotFoundError) as e:
+            return _err(400, f"{type(e).__name__}: {e}")
+
+    @app.get("/")
+    @app.get("/ui")
+    async def webui():
+        from fastapi.responses import HTMLResponse
+        from .webui import INDEX_HTML
+        return HTMLResponse(INDEX_HTML)
+
+    @app.api_route("/tools", methods=["GET", "POST"])
+    @app.api_route("/cors-proxy", methods=["GET", "POST"])
+    async def disabled_llama_server_routes():
+        return _err(403, "this endpoint is disabled", "forbidden")
+
+    @app.get("/v1/internal/mtp-policy")
+    async def mtp_policy():
+        eng = state.worker.engine
+        dr = getattr(eng, "drafter", None)
+        st = eng.stats
+        return {"drafter": type(dr).__name__ if dr is not None else None,
+                "max_draft": getattr(eng.ecfg, "spec_max_draft", 0),
+                "rounds": st.get("spec_rounds", 0), "drafted": st.get("spec_drafted", 0),
+                "accepted": st.get("spec_accepted", 0),
+                "acceptance": (st.get("spec_accepted", 0) / st["spec_drafted"]) if st.get("spec_drafted") else None}
+
+    @app.post("/v1/rerank")
+    @app.post("/v1/reranking")
+    @app.post("/rerank")
+    async def rerank(body: dict):
+        """Embedding reranker: cosine similarity between the query and every document (the
+        reference's cross-encoder / generative rerankers need their own checkpoints)."""
+        from .embeddings import embed_texts
+        query, docs = body.get("query", ""), list(body.get("documents", []))
+        docs_txt = [d if isinstance(d, str) else d.get("text", "") for d in docs]
+        if not query or not docs_txt:
+            return _err(400, "query and documents are required")
+        vecs, ntok = await asyncio.get_running_loop().run_in_executor(None, embed_texts, state, [query, *docs_txt])
+        qv = vecs[0]
+        scores = [sum(a * b for a, b in zip(qv, v)) for v in vecs[1:]]
+        order = sorted(range(len(scores)), key=lambda i: -scores[i])
+        top_n = int(body.get("top_n") or len(order))
+        res = [{"index": i, "relevance_score": scores[i],
+                **({"document": {"text": docs_txt[i]}} if body.get("return_documents") else {})} for i in order[:top_n]]
+        return {"model": state.model_id, "object": "list", "results": res,
+                "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}
 
     @app.post("/tokenize")
     async def tokenize(body: dict):

@@ -71,6 +71,15 @@ class ModelWorker:
         req.cancelled = True
         self.inbox.put(("cancel", req))
 
+    def run_exclusive(self, fn):
+        """Run ``fn()`` on the worker thread between two engine steps (weight edits, cache resets) and
+        return its result; exceptions propagate to the caller."""
+        import concurrent.futures
+
+        fut: concurrent.futures.Future = concurrent.futures.Future()
+        self.inbox.put(("call", (fn, fut)))
+        return fut.result()
+
     def shutdown(self) -> None:
         self.running = False
         self.inbox.put(("stop", None))
@@ -154,6 +163,12 @@ class ModelWorker:
                     kind, req = item
                     if kind == "stop":
                         return
+                    if kind == "call":
+                        fn, fut = req
+                        try:
+                            fut.set_result(fn())
+                        except BaseException as e:      # hand the failure to the waiting caller
+                            fut.set_exception(e)
                     if kind == "cancel" and req.seq_id is not None and req.seq_id in self.by_seq:
                         eng.abort(req.seq_id)
                         self.by_seq.pop(req.seq_id, None)

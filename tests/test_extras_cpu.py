@@ -1,0 +1,148 @@
+"""LoRA adapters, load-time weight surgery, the Python client and the extra server routes (CPU)."""
+import json
+
+import pytest
+import torch
+
+from mlxcel_b200.config import preset
+from mlxcel_b200.models.weights import random_weights
+
+
+def _write_adapter(tmp_path, cfg, r=4, alpha=8.0, layers=(0, 1)):
+    from safetensors.torch import save_file
+    g = torch.Generator().manual_seed(7)
+    H, D = cfg.hidden_size, cfg.head_dim
+    t = {}
+    for li in layers:
+        base = f"model.layers.{li}.self_attn.q_proj"
+        t[base + ".lora_a"] = torch.randn(H, r, generator=g) * 0.1                      # MLX layout [in, r]
+        t[base + ".lora_b"] = torch.randn(r, cfg.num_attention_heads * D, generator=g) * 0.1
+        base = f"model.layers.{li}.mlp.down_proj"
+        t[base + ".lora_A.weight"] = torch.randn(r, cfg.intermediate_size, generator=g) * 0.1   # PEFT layout
+        t[base + ".lora_B.weight"] = torch.randn(H, r, generator=g) * 0.1
+    d = tmp_path / "adapter"
+    d.mkdir()
+    save_file(t, str(d / "adapters.safetensors"))
+    (d / "adapter_config.json").write_text(json.dumps({"lora_parameters": {"rank": r, "alpha": alpha}}))
+    return d, t
+
+
+def test_lora_fuse_scale_and_detach(tmp_path):
+    from mlxcel_b200.lora import LoraManager
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, seed=1, dtype=torch.float32)
+    q0 = w.layers[0].wqkv.clone()
+    d0 = w.layers[1].w_down.clone()
+    path, t = _write_adapter(tmp_path, cfg)
+    mgr = LoraManager(cfg, w)
+    ad = mgr.add(path, scale=1.0)
+    nq = cfg.num_attention_heads * cfg.head_dim
+    a, b = t["model.layers.0.self_attn.q_proj.lora_a"], t["model.layers.0.self_attn.q_proj.lora_b"]
+    want = q0.clone()
+    want[:nq] += (b.t() @ a.t()) * (8.0 / 4)
+    assert torch.allclose(w.layers[0].wqkv, want, atol=1e-5)
+    assert torch.equal(w.layers[0].wqkv[nq:], q0[nq:])            # k / v rows untouched
+    A, B = t["model.layers.1.mlp.down_proj.lora_A.weight"], t["model.layers.1.mlp.down_proj.lora_B.weight"]
+    assert torch.allclose(w.layers[1].w_down, d0 + (B @ A) * 2.0, atol=1e-5)
+    mgr.set_scale(ad.id, 0.25)
+    assert torch.allclose(w.layers[1].w_down, d0 + (B @ A) * 0.5, atol=1e-5)
+    mgr.set_scale(ad.id, 0.0)                                       # detached: original weights back
+    assert torch.allclose(w.layers[0].wqkv, q0, atol=1e-5) and torch.allclose(w.layers[1].w_down, d0, atol=1e-5)
+    assert mgr.listing() == [{"id": 0, "path": str(path), "scale": 0.0}]
+
+
+def test_lora_tensor_parallel_shards_sum_to_full(tmp_path):
+    from mlxcel_b200.loading.shard import shard_weights
+    from mlxcel_b200.lora import LoraManager
+    cfg = preset("tiny-llama")
+    full = random_weights(cfg, seed=2, dtype=torch.float32)
+    path, _ = _write_adapter(tmp_path, cfg)
+    shards = [shard_weights(cfg, random_weights(cfg, seed=2, dtype=torch.float32), r, 2) for r in range(2)]
+    LoraManager(cfg, full).add(path, 1.0)
+    for r in range(2):
+        LoraManager(cfg, shards[r], tp_rank=r, tp_size=2).add(path, 1.0)
+    ref = [shard_weights(cfg, full, r, 2) for r in range(2)]
+    for r in range(2):
+        assert torch.allclose(shards[r].layers[0].wqkv, ref[r].layers[0].wqkv, atol=1e-5)
+        assert torch.allclose(shards[r].layers[1].w_down, ref[r].layers[1].w_down, atol=1e-5)
+
+
+def test_weight_surgery(tmp_path):
+    from mlxcel_b200.loading.surgery import apply_edits, load_edits
+    y = tmp_path / "edits.yaml"
+    y.write_text("""
+- op: scale
+  match: "model.layers.(0|1).mlp.down_proj.weight"
+  factor: 0.5
+- op: interpolate
+  match: "model.layers.1.(.*)"
+  source: "model.layers.0.\\\\1"
+  t: 0.25
+- op: prune
+  match: "lm_head.weight"
+  threshold: 0.5
+- op: replace
+  match: "model.norm.weight"
+  value: 1.0
+""")
+    edits = load_edits(str(y))
+    store = {"model.layers.0.mlp.down_proj.weight": torch.full((2, 2), 4.0),
+             "model.layers.1.mlp.down_proj.weight": torch.full((2, 2), 8.0),
+             "lm_head.weight": torch.tensor([[0.1, -0.7], [0.6, -0.2]]), "model.norm.weight": torch.zeros(3)}
+    get = lambda n: apply_edits(edits, n, store[n], lambda k: store.get(k))
+    assert torch.equal(get("model.layers.0.mlp.down_proj.weight"), torch.full((2, 2), 2.0))
+    # layer 1: scaled to 4.0, then 0.75 * 4.0 + 0.25 * (raw layer 0 = 4.0) = 4.0
+    assert torch.allclose(get("model.layers.1.mlp.down_proj.weight"), torch.full((2, 2), 4.0))
+    assert torch.equal(get("lm_head.weight"), torch.tensor([[0.0, -0.7], [0.6, 0.0]]))
+    assert torch.equal(get("model.norm.weight"), torch.ones(3))
+    with pytest.raises(ValueError):
+        (tmp_path / "bad.yaml").write_text("- op: explode\n  match: x\n")
+        load_edits(str(tmp_path / "bad.yaml"))
+
+
+class _FakeResp:
+    def __init__(self, payload, status=200, lines=None):
+        self._p, self.status_code, self._lines, self.text = payload, status, lines or [], json.dumps(payload)
+
+    def json(self):
+        return self._p
+
+    def iter_lines(self):
+        return iter(self._lines)
+
+
+class _FakeSession:
+    def __init__(self):
+        self.calls = []
+
+    def post(self, url, json=None, headers=None, timeout=None, stream=False):
+        self.calls.append(("POST", url, json, headers))
+        if url.endswith("/v1/chat/completions") and json.get("stream"):
+            ev = lambda c: ("data: " + __import__("json").dumps({"choices": [{"delta": {"content": c}}]})).encode()
+            return _FakeResp({}, lines=[ev("Hel"), b"", ev("lo"), b"data: [DONE]"])
+        if url.endswith("/v1/chat/completions"):
+            return _FakeResp({"choices": [{"message": {"content": "hi"}}]})
+        if url.endswith("/v1/embeddings"):
+            return _FakeResp({"data": [{"embedding": [1.0, 0.0]}]})
+        if url.endswith("/tokenize"):
+            return _FakeResp({"tokens": [1, 2, 3]})
+        return _FakeResp({"error": "nope"}, status=404)
+
+    def get(self, url, headers=None, timeout=None):
+        self.calls.append(("GET", url, None, headers))
+        if url.endswith("/health"):
+            return _FakeResp({"status": "ok"})
+        return _FakeResp({"data": [{"id": "m"}]})
+
+
+def test_python_client_against_fake_transport():
+    from mlxcel_b200.client import Client, MlxcelError
+    s = _FakeSession()
+    c = Client("http://x:1/", api_key="k", session=s)
+    assert c.health() and c.models() == ["m"]
+    assert c.chat([{"role": "user", "content": "yo"}], max_tokens=4) == "hi"
+    assert "".join(c.chat_stream([{"role": "user", "content": "yo"}])) == "Hello"
+    assert c.embed("a") == [[1.0, 0.0]] and c.tokenize("abc") == [1, 2, 3]
+    assert s.calls[0][3] == {"Authorization": "Bearer k"} and s.calls[2][2]["max_tokens"] == 4
+    with pytest.raises(MlxcelError):
+        c.detokenize([1])

@@ -100,3 +100,54 @@ def test_stop_matcher_and_tool_parsing():
         got += c
     v, c = f.flush()
     assert (vis + v).replace("  ", " ").strip() == "hello bye" and got[0].name == "f"
+
+
+def test_extra_routes_webui_rerank_lora_stubs(client, tmp_path):
+    r = client.get("/")
+    assert r.status_code == 200 and "<title>mlxcel_b200</title>" in r.text and "/v1/chat/completions" in r.text
+    assert client.get("/ui").status_code == 200
+    assert client.get("/tools").status_code == 403 and client.post("/cors-proxy").status_code == 403
+    pol = client.get("/v1/internal/mtp-policy").json()
+    assert pol["drafter"] is None and pol["drafted"] == 0
+    rr = client.post("/v1/rerank", json={"query": "abc", "documents": ["abc", "zzzzzz", "abd"], "top_n": 2,
+                                         "return_documents": True}).json()
+    assert len(rr["results"]) == 2 and rr["results"][0]["index"] == 0        # identical text ranks first
+    assert rr["results"][0]["relevance_score"] > rr["results"][1]["relevance_score"]
+    assert rr["results"][0]["document"]["text"] == "abc"
+    assert client.post("/v1/rerank", json={"query": "", "documents": []}).status_code == 400
+    # LoRA: not enabled on this app -> 400; enabled -> attach, rescale, list
+    assert client.get("/lora-adapters").json() == []
+    assert client.post("/lora-adapters", json=[{"id": 0, "scale": 1.0}]).status_code == 400
+
+
+def test_lora_routes_change_weights_between_steps(tmp_path):
+    import json as _json
+
+    from safetensors.torch import save_file
+
+    from mlxcel_b200.lora import LoraManager
+    cfg = preset("tiny-llama")
+    cfg.vocab_size = 300
+    w = random_weights(cfg, seed=5, dtype=torch.float32)
+    tk = ByteTokenizer(cfg.vocab_size)
+    eng = Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=2, num_blocks=64, max_model_len=128, cuda_graphs=False))
+    worker = ModelWorker(eng, tk, "tiny")
+    state = ServerState(worker, tk, "tiny")
+    state.lora = LoraManager(cfg, w)
+    d = tmp_path / "ad"
+    d.mkdir()
+    g = torch.Generator().manual_seed(3)
+    save_file({"model.layers.0.self_attn.o_proj.lora_a": torch.randn(cfg.num_attention_heads * cfg.head_dim, 2, generator=g),
+               "model.layers.0.self_attn.o_proj.lora_b": torch.randn(2, cfg.hidden_size, generator=g)},
+              str(d / "adapters.safetensors"))
+    (d / "adapter_config.json").write_text(_json.dumps({"lora_parameters": {"rank": 2, "scale": 1.0}}))
+    before = w.layers[0].wo.clone()
+    with TestClient(create_app(state)) as c:
+        out = c.post("/lora-adapters", json=[{"id": 0, "path": str(d), "scale": 0.5}]).json()
+        assert out == [{"id": 0, "path": str(d), "scale": 0.5}]
+        assert not torch.allclose(w.layers[0].wo, before)
+        assert c.get("/lora-adapters").json()[0]["scale"] == 0.5
+        c.post("/lora-adapters", json=[{"id": 0, "scale": 0.0}])
+        assert torch.allclose(w.layers[0].wo, before, atol=1e-5)
+        assert c.post("/lora-adapters", json=[{"id": 9, "scale": 1.0}]).status_code == 400
+    worker.shutdown()
