@@ -109,6 +109,8 @@ struct GemmParams {
   const void* q_scales;
   const __nv_bfloat16* q_biases;
   int q_group, q_groups_per_row, q_rows;
+  int q_tiles_per_group;   // grouped: re-tiled row tiles per expert (gate tiles then up tiles when gated)
+  int q_glu_tiles;         // tile distance from a gate tile to its up tile
   // Deferred RMSNorm (see mx_gemm_set_row_norm). ssq buffers: word 0 = number of partial sums per
   // token, word 1 = tokens per partial row (ld), data from word 8: partial p of token t at
   // 8 + p * ld + t.
@@ -137,6 +139,7 @@ struct WorkItem {
   int out_tok0, tok_valid;   // first output token row of the tile and how many are real
   int feat0, feat_valid;     // first output feature of the tile and how many are real
   int bias_off;
+  int q_tile;                // quantized weights: index of the lane tile in the re-tiled blocks
 };
 struct GroupCursor {
   int e = 0, base = 0;
@@ -155,6 +158,7 @@ __device__ __forceinline__ bool decode_work(const GemmParams& p, int w, GroupCur
     it.lane_row0 = lane_t * kLaneRows;
     it.col_row0 = col_t * BN;
     it.bias_off = 0;
+    it.q_tile = lane_t;
     if (SWAP) {
       it.feat0 = it.lane_row0;
       it.feat_valid = p.N - it.feat0;
@@ -188,6 +192,7 @@ __device__ __forceinline__ bool decode_work(const GemmParams& p, int w, GroupCur
     it.feat0 = f * FEAT_TILE;
     it.feat_valid = p.N - it.feat0;
     it.bias_off = e * p.bias_group_stride;
+    it.q_tile = e * p.q_tiles_per_group + f;
     const int w_row = e * p.w_group_rows + it.feat0;
     it.lane_row0 = SWAP ? w_row : it.out_tok0;
     it.col_row0 = SWAP ? it.out_tok0 : w_row;
@@ -398,7 +403,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   // stages start on 1024-byte boundaries (the swizzled MMA tiles need that alignment)
   constexpr int STAGE_BYTES = (LANE_TILES * (LANE_BYTES + PK_BYTES) + COL_TILES * COL_BYTES + 1023) / 1024 * 1024;
   constexpr int RAW_BYTES = LANE_TILES * PK_BYTES + COL_TILES * COL_BYTES;   // what TMA brings when WQ
-  static_assert(WQ == 0 || (SWAP && !GROUPED), "quantized weights: weight-rows-on-lanes, dense only");
+  static_assert(WQ == 0 || SWAP, "quantized weights: weight-rows-on-lanes tiles only");
   constexpr int ACC_COLS = GLU ? 2 * BN : BN;
   constexpr int TMEM_COLS = (2 * ACC_COLS <= 32)    ? 32
                             : (2 * ACC_COLS <= 64)  ? 64
@@ -440,20 +445,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   // producer state set up by thread 0 before the CTA-wide sync (it is also the producer thread)
   [[maybe_unused]] uint64_t pol_lane = 0, pol_col = 0;
   [[maybe_unused]] int pre = 0;   // ring stages whose weight tiles are already in flight
-  auto load_lane = [&](uint8_t* s, uint64_t* bar, int kb, int row0) {
+  auto load_lane = [&](uint8_t* s, uint64_t* bar, int kb, int row0, [[maybe_unused]] int qtile) {
     if constexpr (WQ != 0) {
       // packed bytes of 128 weight rows for this k-block (byte-typed tensor map, no swizzle)
       // The packed weights were re-tiled at load time: (128-row tile, k-block) -> one contiguous
       // block of 128 x PK_ROW_BYTES bytes, so a box is a single 4 / 8 KB run in DRAM (row-major
       // checkpoint rows would give 128 separate 32-byte pieces per box).
       uint8_t* pk = s + LANE_TILES * LANE_BYTES + COL_TILES * COL_BYTES;
-      const int t0 = row0 / kLaneRows;
       // (the tensor map views the contiguous blocks as rows of 256 bytes: few, wide TMA requests)
       constexpr int BOX_ROWS = PK_BYTES / 256;
-      tma_load_2d(pk, &map_lane, bar, 0, (t0 * p.num_kb + kb) * BOX_ROWS, pol_lane);
+      tma_load_2d(pk, &map_lane, bar, 0, (qtile * p.num_kb + kb) * BOX_ROWS, pol_lane);
       if (LANE_TILES == 2)
-        tma_load_2d(pk + PK_BYTES, &map_lane, bar, 0, ((t0 + p.glu_offset / kLaneRows) * p.num_kb + kb) * BOX_ROWS,
-                    pol_lane);
+        tma_load_2d(pk + PK_BYTES, &map_lane, bar, 0, ((qtile + p.q_glu_tiles) * p.num_kb + kb) * BOX_ROWS, pol_lane);
     } else {
       tma_load_2d(s, &map_lane, bar, kb * kBK, row0, pol_lane);
       if (LANE_TILES == 2) tma_load_2d(s + LANE_BYTES, &map_lane, bar, kb * kBK, row0 + p.glu_offset, pol_lane);
@@ -500,7 +503,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
         for (int i = 0; i < pre; ++i) {
           mbar_expect_tx(load_bar(i), TX_BYTES);
           uint8_t* s = smem + i * STAGE_BYTES;
-          if (SWAP) load_lane(s, load_bar(i), kb0 + i, it0.lane_row0);
+          if (SWAP) load_lane(s, load_bar(i), kb0 + i, it0.lane_row0, it0.q_tile);
           else load_col(s, load_bar(i), kb0 + i, it0.col_row0);
         }
         // The rest of this CTA's weight slice (up to a budget) goes to L2: HBM keeps streaming
@@ -587,14 +590,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           if (seq < pre) {
             // weight tile already in flight: only the activation tile is missing
             if (SWAP) load_col(s, load_bar(stage), kb, col_row0);
-            else load_lane(s, load_bar(stage), kb, lane_row0);
+            else load_lane(s, load_bar(stage), kb, lane_row0, it.q_tile);
           } else {
             if (!mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, kErrProducerWait)) {
               ok = false;
               break;
             }
             mbar_expect_tx(load_bar(stage), TX_BYTES);
-            load_lane(s, load_bar(stage), kb, lane_row0);
+            load_lane(s, load_bar(stage), kb, lane_row0, it.q_tile);
             load_col(s, load_bar(stage), kb, col_row0);
           }
           if (seq == 0) stamp(2);
@@ -668,6 +671,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
   } else if (WQ != 0 && warp >= 6) {
     // ------------------------------------------------------------------ transform (first halves)
     if constexpr (WQ != 0) {
+      if constexpr (GROUPED) pdl_wait();   // the tile schedule reads expert offsets written upstream
       const int r = static_cast<int>(threadIdx.x) - kGemmThreads;
       int stage = 0;
       uint32_t phase = 0;
@@ -1694,6 +1698,7 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
   p.q_group = quant.group;
   p.q_groups_per_row = quant.wq != 0 ? K / quant.group : 0;
   p.q_rows = w_rows;
+  p.q_glu_tiles = glu ? glu_offset / kLaneRows : 0;
 
   const int sms = device_sm_count();
   int bn;
@@ -1939,6 +1944,8 @@ extern "C" int mx_grouped_gemm_bf16(const void* x, const void* w, void* out, con
                                     int epilogue, int glu_offset, float glu_alpha, float glu_limit,
                                     void* workspace, long long ws_bytes, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const PendingQuant quant = g_quant;   // one-shot
+  g_quant = PendingQuant{};
   if (E <= 0 || N <= 0 || K <= 0 || max_rows <= 0) return 0;
   if ((K % 8) || (N % 8)) return -1;
   if (workspace == nullptr || ws_bytes < MX_WS_PARTIAL_OFFSET) return -2;
@@ -1974,6 +1981,32 @@ extern "C" int mx_grouped_gemm_bf16(const void* x, const void* w, void* out, con
   const uint32_t x_box = swap ? bn : kLaneRows;
   const uint32_t w_box = swap ? kLaneRows : bn;
   if (!make_tensor_map_bf16(&map_x, x, max_rows, K, K, x_box, kBK)) return -4;
+  if (quant.wq != 0) {
+    // Expert weights as re-tiled packed blocks (see mx_gemm_set_quant): per expert ceil(N / 128)
+    // row tiles, the gate tiles followed by the up tiles when gated. Few rows per expert only
+    // (decode); the caller dequantises for the token-rows-on-lanes case.
+    if (!swap || (K % kBK) || (quant.wq != 1 && quant.wq != 3)) return -9;
+    const int tN = (N + kLaneRows - 1) / kLaneRows;
+    p.q_tiles_per_group = glu ? 2 * tN : tN;
+    p.q_glu_tiles = glu ? tN : 0;
+    const int bits = wq_bits(quant.wq);
+    const uint64_t pkb = static_cast<uint64_t>(kBK) * bits / 8;
+    const uint32_t brows = static_cast<uint32_t>(wq_block_rows(quant.wq) * pkb / 256);
+    const uint64_t trows = static_cast<uint64_t>(E) * p.q_tiles_per_group * p.num_kb * brows;
+    if (!make_tensor_map_u8(&map_w, w, trows, 256, 256, brows, 256)) return -4;
+#define MX_GQLAUNCH(BN_, GLU_)                                                                        \
+    if (quant.wq == 1) return launch_gemm<BN_, true, GLU_, 0, true, 1>(map_w, map_x, p, grid, stream); \
+    return launch_gemm<BN_, true, GLU_, 0, true, 3>(map_w, map_x, p, grid, stream)
+    if (glu) {
+      if (bn == 16) { MX_GQLAUNCH(16, true); }
+      if (bn == 32) { MX_GQLAUNCH(32, true); }
+      MX_GQLAUNCH(64, true);
+    }
+    if (bn == 16) { MX_GQLAUNCH(16, false); }
+    if (bn == 32) { MX_GQLAUNCH(32, false); }
+    MX_GQLAUNCH(64, false);
+#undef MX_GQLAUNCH
+  }
   if (!make_tensor_map_bf16(&map_w, w, static_cast<uint64_t>(E) * w_group_rows, K, K, w_box, kBK))
     return -4;
   const CUtensorMap& ml = swap ? map_w : map_x;

@@ -28,9 +28,10 @@ def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -
     logits = ops.linear(x, lw.router_w, bias=lw.router_b)
     ids, wts = moe_ops.route(logits, cfg.num_experts_per_tok, cfg.moe_route_mode, cfg.norm_topk_prob)
     ep, ep_rank = comm.ep_size, comm.ep_rank
-    gate_up, down = _dense(lw.experts_gate_up), _dense(lw.experts_down)
+    # packed expert weights stay packed: the grouped GEMM unpacks the tiles of routed experts only
+    gate_up, down = lw.experts_gate_up, lw.experts_down
     El = gate_up.shape[0]
-    inter = gate_up.shape[1] // 2
+    inter = gate_up.shape[-2] // 2
     first = ep_rank == 0 or ep == 1
     out = moe_ops.moe_experts(x, ids, wts, gate_up, down, inter, cfg.hidden_act, lw.experts_gate_up_b,
                               lw.experts_down_b, e_begin=ep_rank * El, residual=h if first else None,

@@ -74,6 +74,9 @@ def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_o
                    limit: float = 7.0, out: torch.Tensor | None = None) -> torch.Tensor:
     """Rows [offsets[e], offsets[e+1]) of ``xs`` times expert e's matrix ``w[e]``. With ``act``
     the expert matrices hold gate rows then up rows and the gated activation is fused."""
+    from ..models.weights import QuantizedTensor
+    from . import quant
+
     rows, K = xs.shape
     E = w.shape[0]
     if out is None:
@@ -81,6 +84,22 @@ def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_o
     epi = _ACT_TO_EPI[act] if act else (1 if bias is not None else 0)
     ws = _lib.workspace(xs.device)
     lib = _lib.load()
+    if isinstance(w, QuantizedTensor):
+        # Packed expert weights go straight into the grouped tcgen05 GEMM (unpacked by its transform
+        # warps) when few rows are routed to each expert; only experts that received tokens are
+        # read, at 4 bits per weight. Otherwise: dequantise all experts, dense grouped GEMM.
+        wq = {("affine", 4): 1, ("mxfp4", 4): 3}.get((w.mode, w.bits), 0)
+        if wq and quant._FUSED_QGEMM and K % 64 == 0 and w.group_size in (32, 64, 128):
+            tiles = quant.tile_experts_for_gemm(w, n_out if act else None)
+            lib.mx_gemm_set_quant(None, None, w.group_size, wq)
+            rc = lib.mx_grouped_gemm_bf16(xs.data_ptr(), tiles.data_ptr(), out.data_ptr(), _lib.ptr(bias),
+                                          offsets.data_ptr(), E, n_out, K, rows, epi, n_out if act else 0,
+                                          float(alpha), float(limit), ws.data_ptr(), ws.numel(), _lib.stream())
+            if rc != -9:
+                _lib.count_launch()
+                _lib.check(rc, "mx_grouped_gemm_bf16 (packed experts)")
+                return out
+        w = quant.dequantize(w)
     rc = lib.mx_grouped_gemm_bf16(xs.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias),
                                   offsets.data_ptr(), E, n_out, K, rows, epi, n_out if act else 0,
                                   float(alpha), float(limit), ws.data_ptr(), ws.numel(), _lib.stream())
@@ -98,6 +117,12 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up
     k = ids.shape[1]
     El = w_gate_up.shape[0]
     if not x.is_cuda:
+        from ..models.weights import QuantizedTensor
+        from . import quant
+        if isinstance(w_gate_up, QuantizedTensor):
+            w_gate_up = quant.dequantize_ref(w_gate_up)
+        if isinstance(w_down, QuantizedTensor):
+            w_down = quant.dequantize_ref(w_down)
         o = moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up, b_down, e_begin, alpha, limit)
         if residual is not None:
             o = o + residual.float()

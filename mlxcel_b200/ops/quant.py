@@ -217,6 +217,48 @@ def tile_for_gemm(qt: QuantizedTensor) -> torch.Tensor:
     return tiles
 
 
+def tile_experts_for_gemm(qt: QuantizedTensor, glu_inter: int | None = None) -> torch.Tensor:
+    """Stacked expert weights ``[E, N, K]`` (``N = 2 * glu_inter`` rows = gate then up when gated) in
+    the block layout of ``tile_for_gemm``, per expert: the row tiles of the gate part followed by
+    those of the up part (each part zero-padded to a multiple of 128 rows on its own, so that a gate
+    tile and its up tile are a fixed number of tiles apart). Returns uint8
+    ``[E, tiles_per_expert, K/64, rows, W]``; cached on the tensor."""
+    cached = getattr(qt, "_gemm_tiles", None)
+    if cached is not None:
+        return cached
+    E, N, K = qt.shape
+    bits, group = qt.bits, qt.group_size
+    nkb, W = K // 64, 64 * bits // 8
+    parts = [(0, N)] if glu_inter is None else [(0, glu_inter), (glu_inter, 2 * glu_inter)]
+    by = qt.packed.contiguous().view(torch.uint8).view(E, N, nkb, W)
+    halves = torch.arange(2 * nkb, device=by.device) * 32 // group
+
+    def half_bytes(v, r0, r1, pad):   # [E, N, K/group] -> [E, T, nkb, bytes]
+        e = v[:, r0:r1].index_select(2, halves)
+        if pad:
+            e = torch.cat([e, torch.zeros(E, pad, 2 * nkb, dtype=e.dtype, device=e.device)], 1)
+        T = e.shape[1] // 128
+        e = e.view(E, T, 128, nkb, 2).permute(0, 1, 3, 4, 2).contiguous()      # [E, T, nkb, 2, 128]
+        return e.view(torch.uint8).view(E, T, nkb, -1)
+
+    out = []
+    for r0, r1 in parts:
+        n = r1 - r0
+        T = (n + 127) // 128
+        pad = T * 128 - n
+        v = by[:, r0:r1]
+        if pad:
+            v = torch.cat([v, torch.zeros(E, pad, nkb, W, dtype=torch.uint8, device=by.device)], 1)
+        vals = v.view(E, T, 128, nkb, W).permute(0, 1, 3, 2, 4)              # [E, T, nkb, 128, W]
+        extra = half_bytes(qt.scales, r0, r1, pad)
+        if qt.biases is not None:
+            extra = torch.cat([extra, half_bytes(qt.biases, r0, r1, pad)], dim=-1)
+        out.append(torch.cat([vals, extra.view(E, T, nkb, -1, W)], dim=3))
+    tiles = torch.cat(out, dim=1).contiguous()
+    qt._gemm_tiles = tiles
+    return tiles
+
+
 def set_quant(qt: QuantizedTensor, wq: int):
     """Announce re-tiled packed weights to the next GEMM call (see mx_gemm_set_quant); returns the
     pointer to pass as ``w``."""

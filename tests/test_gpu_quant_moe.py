@@ -107,6 +107,32 @@ def test_moe_experts(T, E, k, H, I, act, local):
     assert _lib.read_status(torch.device(DEV)) == 0
 
 
+@pytest.mark.parametrize("mode,bits,group", [("mxfp4", 4, 32), ("affine", 4, 64)])
+@pytest.mark.parametrize("T,E,k,H,I,act", [(5, 8, 2, 256, 512, "silu"), (64, 16, 4, 320, 192, "clipped_swiglu"),
+                                           (128, 32, 4, 2880, 384, "clipped_swiglu")])
+def test_moe_experts_packed(mode, bits, group, T, E, k, H, I, act):
+    """Packed (mxfp4 / affine 4-bit) expert weights through the grouped fused dequant GEMM; hidden
+    and expert sizes that are not multiples of the 128-row tile (gpt-oss: 2880)."""
+    g = torch.Generator().manual_seed(T + E)
+    r = lambda *s, sc=1.0: (torch.randn(*s, generator=g) * sc)  # noqa: E731
+    x = r(T, H).to(torch.bfloat16).to(DEV)
+    ids, wts = moe_ops.route(r(T, E).to(torch.bfloat16).to(DEV), k, "topk_softmax", True)
+    qgu = quant.quantize(r(E, 2 * I, H, sc=0.05), mode, bits, group)
+    qd = quant.quantize(r(E, H, I, sc=0.05), mode, bits, group)
+    bias = act == "clipped_swiglu"
+    bgu = r(E, 2 * I, sc=0.1).to(torch.bfloat16).to(DEV) if bias else None
+    bd = r(E, H, sc=0.1).to(torch.bfloat16).to(DEV) if bias else None
+    res = r(T, H).to(torch.bfloat16).to(DEV)
+    wgu_d = quant.dequantize_ref(qgu).to(torch.bfloat16).to(DEV)
+    wd_d = quant.dequantize_ref(qd).to(torch.bfloat16).to(DEV)
+    want = moe_ops.moe_ref(x, ids, wts, wgu_d, wd_d, I, act, bgu, bd) + res.float()
+    got = moe_ops.moe_experts(x, ids, wts, _qt_to(qgu, DEV), _qt_to(qd, DEV), I, act, bgu, bd, residual=res)
+    _close(got, want, rtol=3e-2, atol=6e-2)
+    from mlxcel_b200.ops import _lib
+    torch.cuda.synchronize()
+    assert _lib.read_status(torch.device(DEV)) == 0
+
+
 def test_tiny_moe_models_gpu_vs_cpu_logits():
     from mlxcel_b200.config import preset
     from mlxcel_b200.models.decoder import DecoderModel, StepBatch
