@@ -104,6 +104,7 @@ struct GemmParams {
   int splits, kb_per_split, num_kb;
   int tiles_lane, tiles_col;
   int stages;
+  int raster_gm;        // dense tile order: lane tiles per panel (0 = column-major walk)
   // Quantized weights (WQ != 0): per-group scales (bf16 for affine, e8m0 bytes for mxfp4), affine
   // biases, group size (32 / 64 / 128), groups per weight row, number of weight rows.
   const void* q_scales;
@@ -154,7 +155,20 @@ __device__ __forceinline__ bool decode_work(const GemmParams& p, int w, GroupCur
     if (w >= p.tiles_lane * p.tiles_col * p.splits) return false;
     it.tile = w / p.splits;
     it.split = w - it.tile * p.splits;
-    const int lane_t = it.tile % p.tiles_lane, col_t = it.tile / p.tiles_lane;
+    int lane_t, col_t;
+    if (p.raster_gm > 0) {
+      // Tiles are walked in panels of raster_gm lane tiles x all column tiles, lane tile fastest:
+      // the panel's rows of the lane operand stay in L2 while the column operand streams past
+      // once per panel (instead of the whole lane operand being re-read for every few column tiles).
+      const int per_panel = p.raster_gm * p.tiles_col;
+      const int g = it.tile / per_panel, r = it.tile - g * per_panel;
+      const int lanes = min(p.raster_gm, p.tiles_lane - g * p.raster_gm);
+      lane_t = g * p.raster_gm + r % lanes;
+      col_t = r / lanes;
+    } else {
+      lane_t = it.tile % p.tiles_lane;
+      col_t = it.tile / p.tiles_lane;
+    }
     it.lane_row0 = lane_t * kLaneRows;
     it.col_row0 = col_t * BN;
     it.bias_off = 0;
@@ -1534,6 +1548,13 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
   }
   if (stages < 2) return -3;
   p.stages = stages;
+  {
+    static const int gm = [] {
+      const char* e = getenv("MLXCEL_B200_GEMM_RASTER");
+      return e != nullptr ? atoi(e) : 16;
+    }();
+    p.raster_gm = (!SWAP && !GROUPED && gm > 0 && p.tiles_lane > gm) ? gm : 0;
+  }
   {
     static const bool trace_on = [] {
       const char* e = getenv("MLXCEL_B200_GEMM_TRACE");
