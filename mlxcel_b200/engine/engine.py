@@ -78,6 +78,7 @@ class EngineConfig:
     mixed_steps: bool = True
     preemption: bool = True
     lookahead: bool = True               # submit decode step n+1 before reading step n (greedy rows)
+    status_check_interval: int = 64      # steps between reads of the device status word (0 = never)
 
 
 class Engine:
@@ -526,8 +527,26 @@ class Engine:
 
     # ------------------------------------------------------------------ step
     @torch.inference_mode()
+    def _check_device_status(self) -> None:
+        """Every ``status_check_interval`` steps: read the device status word (bounded waits in the
+        kernels record a code there instead of hanging) and fail the step loudly. One 4-byte
+        read-back per interval, so a lost peer or a broken pipeline surfaces within that many steps."""
+        iv = getattr(self.ecfg, "status_check_interval", 64)
+        if not self.is_cuda or iv <= 0:
+            return
+        self._steps_since_check = getattr(self, "_steps_since_check", 0) + 1
+        if self._steps_since_check < iv:
+            return
+        self._steps_since_check = 0
+        from ..ops import _lib
+        code = _lib.read_status(self.device)
+        if code != 0:
+            raise RuntimeError(f"a kernel reported failure code {code} (bounded wait ran out: 1xx GEMM pipeline, "
+                               f"2xx peer flag, 4xx attention pipeline); the step's results are not valid")
+
     def step(self) -> list[Sequence]:
         """One scheduling tick + forward + sample. Returns the sequences that finished."""
+        self._check_device_status()
         if self._inflight is not None:
             inf = self._inflight
             nxt = self._launch_lookahead(inf["seqs"], from_device=True) if self._can_pipeline(inf) else None
