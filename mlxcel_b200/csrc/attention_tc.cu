@@ -78,7 +78,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   uint64_t* s_empty = s_full + 2;            // [2]
   uint64_t* p_full = s_empty + 2;            // 1
   uint64_t* pv_done = p_full + 1;            // 1
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(pv_done + 1);
+  uint64_t* k_empty = pv_done + 1;           // [stages] K tile consumed (after the score MMA)
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(k_empty + kTcStages);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -109,6 +110,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&kv_empty[i], 1);
+      mbar_init(&k_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
@@ -143,26 +145,34 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     uint32_t phase = 0;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
+      // The K tile of a stage is free as soon as its score MMA has run, the V tile only after the
+      // P V MMA of the same key tile: K of tile j + stages is requested a whole softmax earlier.
+      // one pool block per lane; blocks past the sequence's last one repeat it (masked keys, but
+      // the values multiplied by P = 0 must be finite)
+      int row0 = 0;
+      if (lane < kTcKeys / kTcBlock) {
+        const int b = min((kv_begin + j * kTcKeys) / kTcBlock + lane, last_block);
+        row0 = (table[b] * p.Hkv + hkv) * kTcBlock;
+      }
       if (lane == 0) {
-        ok = mbar_wait(&kv_empty[stage], phase ^ 1u, p.status, kErrAttnProducer);
-        if (ok) {
-          mbar_expect_tx(&k_full[stage], K_BYTES);
-          mbar_expect_tx(&v_full[stage], V_BYTES);
-        }
+        ok = mbar_wait(&k_empty[stage], phase ^ 1u, p.status, kErrAttnProducer);
+        if (ok) mbar_expect_tx(&k_full[stage], K_BYTES);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       if (lane < kTcKeys / kTcBlock) {
-        // one pool block per lane; blocks past the sequence's last one repeat it (masked keys,
-        // but the values multiplied by P = 0 must be finite)
-        const int b = min((kv_begin + j * kTcKeys) / kTcBlock + lane, last_block);
-        const int row0 = (table[b] * p.Hkv + hkv) * kTcBlock;
         uint8_t* kd = k_sm + stage * K_BYTES + lane * (kTcBlock * 128);
+        for (int c = 0; c < DC; ++c) tma_load_2d(kd + c * SUB_BYTES, &map_k, &k_full[stage], c * 64, row0, pol_kv);
+      }
+      if (lane == 0) {
+        ok = mbar_wait(&kv_empty[stage], phase ^ 1u, p.status, kErrAttnProducer);
+        if (ok) mbar_expect_tx(&v_full[stage], V_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      if (lane < kTcKeys / kTcBlock) {
         uint8_t* vd = v_sm + stage * V_BYTES + lane * (kTcBlock * 128);
-        for (int c = 0; c < DC; ++c) {
-          tma_load_2d(kd + c * SUB_BYTES, &map_k, &k_full[stage], c * 64, row0, pol_kv);
-          tma_load_2d(vd + c * SUB_BYTES, &map_v, &v_full[stage], c * 64, row0, pol_kv);
-        }
+        for (int c = 0; c < DC; ++c) tma_load_2d(vd + c * SUB_BYTES, &map_v, &v_full[stage], c * 64, row0, pol_kv);
       }
       __syncwarp();
       if (++stage == kTcStages) {
@@ -191,6 +201,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           umma_bf16(tmem_base + sb * S_COLS, umma_desc_k_sw128(qa + off), umma_desc_k_sw128(kb + off),
                     idesc_qk, kk > 0 ? 1u : 0u);
         }
+        umma_commit(&k_empty[stage]);   // the K tile may be refilled
         umma_commit(&s_full[sb]);
         return true;
       };
@@ -210,7 +221,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           const uint64_t db = umma_desc_mn_sw128(vb + kk * (16 * 128), SUB_BYTES, 1024);
           umma_bf16(tmem_base + O_COL, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[stage]);   // K and V of this stage are consumed
+        umma_commit(&kv_empty[stage]);   // the V tile of this stage is consumed
         umma_commit(pv_done);
       }
     }
