@@ -62,6 +62,10 @@ def _sampling(a):
 def load_llm(a):
     import torch
 
+    if getattr(a, "debug_trace", None):
+        from .utils.tracing import TRACER
+        TRACER.enable(path=a.debug_trace)
+
     from .engine import EngineConfig
     from .llm import LLM
 
@@ -243,6 +247,8 @@ def main(argv=None):
     p.add_argument("--chat-template-file", default=None)
     p.add_argument("--lora", action="append", default=None, metavar="DIR[=SCALE]",
                    help="attach a LoRA adapter directory (repeatable); scales can be changed live via /lora-adapters")
+    p.add_argument("--debug-trace", "--debug-pp-trace", dest="debug_trace", default=None, metavar="FILE",
+                   help="write a Chrome trace of engine steps and pipeline stages (same as MLXCEL_B200_TRACE)")
     p.add_argument("--surgery", default=None, metavar="YAML", help="load-time weight edits (see loading/surgery.py)")
     p.add_argument("--ssl-cert-file", default=None)
     p.add_argument("--ssl-key-file", default=None)

@@ -547,6 +547,13 @@ class Engine:
     def step(self) -> list[Sequence]:
         """One scheduling tick + forward + sample. Returns the sequences that finished."""
         self._check_device_status()
+        from ..utils.tracing import TRACER
+        if TRACER.active:
+            with TRACER.span("engine.step", running=len(self.running), waiting=len(self.waiting)):
+                return self._step()
+        return self._step()
+
+    def _step(self) -> list[Sequence]:
         if self._inflight is not None:
             inf = self._inflight
             nxt = self._launch_lookahead(inf["seqs"], from_device=True) if self._can_pipeline(inf) else None

@@ -101,14 +101,21 @@ class PipelineModel(DecoderModel):
         micro = split_batch(b, self.num_micro)
         h_full = torch.empty(T, self.cfg.hidden_size, dtype=self.w.final_norm.dtype, device=self.device) \
             if ctx.is_last else None
-        for mb, sel in micro:
+        from ..utils.tracing import span
+        for i, (mb, sel) in enumerate(micro):
             ctx.stats["microbatches"] += 1
-            h_in = None if ctx.is_first else self._recv(mb.num_tokens, mb.token_ids)
-            h = self.forward_hidden(mb, kv_layers, hidden_in=h_in)
+            if ctx.is_first:
+                h_in = None
+            else:
+                with span("pp.recv", cat="pipeline", stage=ctx.stage, micro=i, tokens=mb.num_tokens):
+                    h_in = self._recv(mb.num_tokens, mb.token_ids)
+            with span("pp.stage", cat="pipeline", stage=ctx.stage, micro=i, tokens=mb.num_tokens):
+                h = self.forward_hidden(mb, kv_layers, hidden_in=h_in)
             if ctx.is_last:
                 h_full.index_copy_(0, sel, h)
             else:
-                self._send(h)
+                with span("pp.send", cat="pipeline", stage=ctx.stage, micro=i):
+                    self._send(h)
         V = self.cfg.vocab_size
         if ctx.is_last:
             logits = self.logits(h_full, b.logits_rows).contiguous()

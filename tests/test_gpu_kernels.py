@@ -349,6 +349,72 @@ def test_penalties_and_verify():
     assert n.tolist() == [int(tgt[0, 3]), int(tgt[1, 1]), int(tgt[2, 0])]
 
 
+# ----------------------------------------------------------------------------- out-of-bounds canaries
+@pytest.mark.parametrize("M,N,K", [(1, 136, 64), (7, 4096, 512), (65, 520, 192), (200, 1032, 256), (300, 264, 128),
+                                   (1500, 1000, 320)])
+def test_gemm_writes_stay_inside_the_output(M, N, K):
+    """No compute-sanitizer on this pool: every kernel writes into a buffer with sentinel rows above
+    and below and sentinel columns to the right (row stride > N); the sentinels must survive."""
+    pad_r, ld = 3, N + 24
+    SENT = -1234.0
+    x = _bf(M, K, seed=1)
+    w = _bf(N, K, seed=2, scale=0.05)
+    res_full = torch.full((M + 2 * pad_r, ld), SENT, dtype=torch.bfloat16, device=DEV)
+    out = res_full[pad_r:pad_r + M, :N]
+    bias = _bf(N, seed=3)
+    got = ops.linear(x, w, bias=bias, out=out)
+    assert got.data_ptr() == out.data_ptr()
+    _close(out, ref.linear(x, w, bias, None), rtol=2e-2, atol=2e-2)
+    assert (res_full[:pad_r] == SENT).all() and (res_full[pad_r + M:] == SENT).all()
+    assert (res_full[pad_r:pad_r + M, N:] == SENT).all()
+    if N % 16 == 0:
+        I = N // 2
+        g_full = torch.full((M + 2 * pad_r, I + 8), SENT, dtype=torch.bfloat16, device=DEV)
+        go = g_full[pad_r:pad_r + M, :I]
+        ops.glu_linear(x, w, I, "silu", out=go)
+        _close(go, ref.glu_linear(x, w, I, ops.EPI_SWIGLU, None, 1.702, 7.0), rtol=3e-2, atol=3e-2)
+        assert (g_full[:pad_r] == SENT).all() and (g_full[pad_r + M:] == SENT).all()
+        assert (g_full[pad_r:pad_r + M, I:] == SENT).all()
+
+
+def test_attention_and_rope_writes_stay_inside_their_buffers():
+    Hq, Hkv, D, bs, nb = 8, 2, 128, 16, 64
+    SENT = -77.0
+    ctx, qlen = [130, 47], [130, 20]
+    kv = _pool(nb, Hkv, bs, D, 16)
+    _fill_pool(kv, 3)
+    tab = _tables(ctx, bs, nb, 16)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, qlen[0], sum(qlen)], dtype=torch.int32, device=DEV)
+    T = sum(qlen)
+    q = _bf(T, Hq * D, seed=4)
+    full = torch.full((T + 6, Hq * D), SENT, dtype=torch.bfloat16, device=DEV)
+    out = full[3:3 + T]
+    ops.paged_prefill(q, kv, tab, cu, cl, Hq=Hq, Hkv=Hkv, D=D, scale=D ** -0.5, max_q_len=max(qlen), out=out)
+    _close(out, ref.paged_attention(q, kv, tab, cl, cu, Hq=Hq, Hkv=Hkv, D=D, scale=D ** -0.5))
+    assert (full[:3] == SENT).all() and (full[3 + T:] == SENT).all()
+    # decode: B rows
+    B = 2
+    qd = _bf(B, Hq * D, seed=5)
+    fulld = torch.full((B + 4, Hq * D), SENT, dtype=torch.bfloat16, device=DEV)
+    ops.paged_decode(qd, kv, tab, cl, Hq=Hq, Hkv=Hkv, D=D, scale=D ** -0.5, out=fulld[2:2 + B])
+    assert (fulld[:2] == SENT).all() and (fulld[2 + B:] == SENT).all()
+    # rope + append: only the slots named in slot_mapping may change in the pool
+    k_before, v_before = kv.k.clone(), kv.v.clone()
+    Tn = 5
+    qkv = _bf(Tn, (Hq + 2 * Hkv) * D, seed=6)
+    slots = torch.tensor([3, 17, 40, 41, 1000], dtype=torch.int32, device=DEV)
+    pos = torch.arange(Tn, dtype=torch.int32, device=DEV)
+    inv = ref.rope_inv_freq(D, 10000.0, None)[0].to(DEV)
+    ops.rope_append(qkv, pos, slots, inv, kv, Hq=Hq, Hkv=Hkv, D=D, rot_dim=D)
+    touched = torch.zeros(nb * bs, dtype=torch.bool, device=DEV)
+    touched[slots.long()] = True
+    kb = (kv.k != k_before).view(nb, Hkv, bs, D).any(-1).any(1).view(-1)     # [nb * bs] slot changed?
+    vb = (kv.v != v_before).view(nb, Hkv, bs, D).any(-1).any(1).view(-1)
+    assert not (kb & ~touched).any() and not (vb & ~touched).any()
+    assert kb[slots.long()].all()
+
+
 # ----------------------------------------------------------------------------- end to end
 @pytest.mark.parametrize("fold", [False, True])
 def test_tiny_llama_gpu_matches_cpu_reference(fold):
