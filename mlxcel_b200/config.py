@@ -322,6 +322,27 @@ def _granite(c: ModelConfig, raw: dict) -> None:
         c.query_pre_attn_scalar = 1.0 / float(raw["attention_multiplier"]) ** 2
 
 
+def _mamba2(c: ModelConfig, raw: dict) -> None:
+    """Pure state-space model (HF ``Mamba2Config``; reference src/models/mamba2.rs:40-76). The
+    attention geometry is reduced to the minimum the block pool accepts: no layer has attention."""
+    hs = c.hidden_size
+    P = int(raw.get("head_dim", 64))
+    d_inner = int(raw.get("intermediate_size") or raw.get("expand", 2) * hs)
+    if raw.get("num_heads"):
+        d_inner = int(raw["num_heads"]) * P
+    lim = raw.get("time_step_limit") or (0.0, float("inf"))
+    c.extra["mamba"] = dict(d_inner=d_inner, head_dim=P, n_groups=int(raw.get("n_groups", 1)),
+                            d_state=int(raw.get("state_size", raw.get("ssm_state_size", 128))),
+                            d_conv=int(raw.get("conv_kernel", raw.get("d_conv", 4))),
+                            time_step_limit=(float(lim[0]), float(lim[1])),
+                            use_bias=bool(raw.get("use_bias", False)),
+                            use_conv_bias=bool(raw.get("use_conv_bias", True)))
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
+    c.num_attention_heads = c.num_key_value_heads = 1
+    c.head_dim = 16
+    c.intermediate_size = d_inner
+
+
 FAMILIES = {
     "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _plain, "seed_oss": _plain,
     "helium": _plain, "internlm3": _plain, "exaone4": _qwen3, "hunyuan_v1_dense": _qwen3,
@@ -330,7 +351,7 @@ FAMILIES = {
     "mixtral": _mixtral, "phimoe": _mixtral, "olmoe": _qwen_moe,
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
-    "granite": _granite, "starcoder2": _plain, "stablelm": _plain, "cohere": _plain,
+    "mamba2": _mamba2, "granite": _granite, "starcoder2": _plain, "stablelm": _plain, "cohere": _plain,
 }
 
 
@@ -379,4 +400,12 @@ def preset(name: str) -> ModelConfig:
             model_type="qwen3", num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
             num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=1024,
             rms_norm_eps=1e-6, max_position_embeddings=2048))
+    if name == "tiny-mamba2":
+        return ModelConfig.from_dict(dict(
+            model_type="mamba2", num_hidden_layers=2, hidden_size=128, num_heads=8, head_dim=32,
+            state_size=32, conv_kernel=4, n_groups=1, expand=2, vocab_size=1024, layer_norm_epsilon=1e-5))
+    if name == "mamba2-2.7b":
+        return ModelConfig.from_dict(dict(
+            model_type="mamba2", num_hidden_layers=64, hidden_size=2560, num_heads=80, head_dim=64,
+            state_size=128, conv_kernel=4, n_groups=1, expand=2, vocab_size=50288, layer_norm_epsilon=1e-5))
     raise KeyError(name)

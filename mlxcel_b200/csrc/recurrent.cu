@@ -78,6 +78,137 @@ __global__ void selective_scan_kernel(const __nv_bfloat16* __restrict__ x, const
   if (on) state[(static_cast<size_t>(b) * Di + d) * N + lane] = s;
 }
 
+// ----------------------------------------------------------------------------- Mamba2 over a ragged batch
+// One launch serves every sequence piece of an engine step: decode rows are pieces of one token,
+// prefill chunks pieces of many. Piece j covers token rows cu[j] .. cu[j+1]-1 and owns slot
+// slots[j] of the state pools; reset[j] != 0 starts it from a zero state (a new sequence).
+
+// Causal depth-wise convolution (width K <= 8) + bias + SiLU. in: rows of `in_stride` elements of
+// which the first C are convolved; conv_state [slots, K-1, C] fp32 holds the last K-1 inputs of each
+// sequence and is advanced. One thread per (piece, channel); time is walked with the window in
+// registers, neighbouring threads read neighbouring channels.
+__global__ void causal_conv_varlen_kernel(const __nv_bfloat16* __restrict__ in, int in_stride,
+                                          float* __restrict__ conv_state, const int* __restrict__ slots,
+                                          const int* __restrict__ cu, const int* __restrict__ reset,
+                                          const float* __restrict__ w, const float* __restrict__ bias,
+                                          __nv_bfloat16* __restrict__ out, int C, int K, int silu) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int j = blockIdx.y;
+  if (c >= C) return;
+  const int t0 = cu[j], t1 = cu[j + 1];
+  if (t1 <= t0) return;
+  float* cs = conv_state + static_cast<size_t>(slots[j]) * (K - 1) * C + c;
+  float win[8], wk[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    wk[k] = k < K ? w[static_cast<size_t>(c) * K + k] : 0.f;
+    win[k] = (k < K - 1 && !reset[j]) ? cs[static_cast<size_t>(k) * C] : 0.f;
+  }
+  const float bv = bias ? bias[c] : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const float xv = __bfloat162float(in[static_cast<size_t>(t) * in_stride + c]);
+    float acc = bv;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k == K - 1) win[k] = xv;
+      if (k < K) acc += wk[k] * win[k];
+    }
+    if (silu) acc = acc / (1.f + __expf(-acc));
+    out[static_cast<size_t>(t) * C + c] = __float2bfloat16(acc);
+#pragma unroll
+    for (int k = 0; k < 7; ++k)
+      if (k < K - 1) win[k] = win[k + 1];
+  }
+#pragma unroll
+  for (int k = 0; k < 7; ++k)
+    if (k < K - 1) cs[static_cast<size_t>(k) * C] = win[k];
+}
+
+// State-space recurrence  S <- S exp(dt A_h) + dt x (x) B,  y = S C + D_h x  walked over each piece.
+// state [slots, H, P, N] fp32; x rows [H*P] at stride x_stride; Bm, Cm rows [G*N] at stride
+// bc_stride; dt rows [H] at stride dt_stride; y [T, H*P]. One warp per (piece, h, p): lane l keeps
+// state columns l, l+32, ... (N <= 256) in registers for the whole piece.
+__global__ void ssm_scan_varlen_kernel(float* __restrict__ state, const int* __restrict__ slots,
+                                       const int* __restrict__ cu, const int* __restrict__ reset,
+                                       const __nv_bfloat16* __restrict__ x, int x_stride,
+                                       const __nv_bfloat16* __restrict__ dt, int dt_stride,
+                                       const float* __restrict__ A, const __nv_bfloat16* __restrict__ Bm,
+                                       const __nv_bfloat16* __restrict__ Cm, int bc_stride,
+                                       const float* __restrict__ D, const float* __restrict__ dt_bias,
+                                       __nv_bfloat16* __restrict__ y, int H, int P, int N, int G,
+                                       int dt_softplus, float dt_min, float dt_max) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int j = blockIdx.y;
+  if (gw >= H * P) return;
+  const int h = gw / P, p = gw - h * P, g = h / (H / G);
+  const int t0 = cu[j], t1 = cu[j + 1];
+  if (t1 <= t0) return;
+  float* st = state + ((static_cast<size_t>(slots[j]) * H + h) * P + p) * N;
+  float s[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int n = lane + 32 * i;
+    s[i] = (n < N && !reset[j]) ? st[n] : 0.f;
+  }
+  const float a = A[h], dv = D ? D[h] : 0.f, db = dt_bias ? dt_bias[h] : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    float dtv = __bfloat162float(dt[static_cast<size_t>(t) * dt_stride + h]) + db;
+    if (dt_softplus) dtv = softplus_f(dtv);
+    dtv = fminf(fmaxf(dtv, dt_min), dt_max);
+    const float dA = __expf(dtv * a);
+    const float xv = __bfloat162float(x[static_cast<size_t>(t) * x_stride + gw]);
+    const __nv_bfloat16* bp = Bm + static_cast<size_t>(t) * bc_stride + g * N;
+    const __nv_bfloat16* cp = Cm + static_cast<size_t>(t) * bc_stride + g * N;
+    const float dx = dtv * xv;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int n = lane + 32 * i;
+      if (n < N) {
+        s[i] = s[i] * dA + dx * __bfloat162float(bp[n]);
+        acc += s[i] * __bfloat162float(cp[n]);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[static_cast<size_t>(t) * H * P + gw] = __float2bfloat16(acc + dv * xv);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int n = lane + 32 * i;
+    if (n < N) st[n] = s[i];
+  }
+}
+
+// out = RMSNorm(y * silu(z)) * weight over rows of `dim`; z rows at stride z_stride. One CTA per row.
+__global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
+                                     int z_stride, const __nv_bfloat16* __restrict__ weight,
+                                     __nv_bfloat16* __restrict__ out, int dim, float eps) {
+  __shared__ float red[32];
+  const size_t row = blockIdx.x;
+  float ssq = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float zv = __bfloat162float(z[row * z_stride + i]);
+    const float v = __bfloat162float(y[row * dim + i]) * (zv / (1.f + __expf(-zv)));
+    ssq += v * v;
+  }
+  ssq = warp_sum(ssq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ssq;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) red[0] = rsqrtf(t / dim + eps);
+  }
+  __syncthreads();
+  const float r = red[0];
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float zv = __bfloat162float(z[row * z_stride + i]);
+    const float v = __bfloat162float(y[row * dim + i]) * (zv / (1.f + __expf(-zv)));
+    out[row * dim + i] = __float2bfloat16(v * r * __bfloat162float(weight[i]));
+  }
+}
+
 // ----------------------------------------------------------------------------- gated delta rule
 // state S [B, Hv, Dk, Dv] fp32 in place; q, k [B, Hv, Dk]; v [B, Hv, Dv]; g (log decay), beta [B, Hv];
 // out [B, Hv, Dv]. One CTA per (b, h), thread j owns column j of S (Dv <= 1024).
@@ -228,6 +359,48 @@ extern "C" int mx_selective_scan(const void* x, const void* dt, const void* A, c
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dt), static_cast<const float*>(A),
       static_cast<const __nv_bfloat16*>(Bm), static_cast<const __nv_bfloat16*>(C), static_cast<const float*>(D),
       static_cast<float*>(state), static_cast<__nv_bfloat16*>(y), B, L, Di, N, dt_softplus);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mx_causal_conv_varlen(const void* in, int in_stride, void* conv_state, const void* slots,
+                                     const void* cu, const void* reset, const void* w, const void* bias, void* out,
+                                     int pieces, int C, int K, int silu, void* stream) {
+  if (pieces <= 0 || C <= 0) return 0;
+  if (K < 1 || K > 8 || pieces > 65535) return -1;
+  const int threads = 128;
+  const dim3 grid((C + threads - 1) / threads, pieces);
+  causal_conv_varlen_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(in), in_stride, static_cast<float*>(conv_state),
+      static_cast<const int*>(slots), static_cast<const int*>(cu), static_cast<const int*>(reset),
+      static_cast<const float*>(w), static_cast<const float*>(bias), static_cast<__nv_bfloat16*>(out), C, K, silu);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mx_ssm_scan_varlen(void* state, const void* slots, const void* cu, const void* reset, const void* x,
+                                  int x_stride, const void* dt, int dt_stride, const void* A, const void* Bm,
+                                  const void* Cm, int bc_stride, const void* D, const void* dt_bias, void* y,
+                                  int pieces, int H, int P, int N, int G, int dt_softplus, float dt_min,
+                                  float dt_max, void* stream) {
+  if (pieces <= 0 || H <= 0 || P <= 0) return 0;
+  if (N < 1 || N > 256 || G <= 0 || H % G || pieces > 65535) return -1;
+  const int threads = 128;
+  const dim3 grid((H * P * 32 + threads - 1) / threads, pieces);
+  ssm_scan_varlen_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float*>(state), static_cast<const int*>(slots), static_cast<const int*>(cu),
+      static_cast<const int*>(reset), static_cast<const __nv_bfloat16*>(x), x_stride,
+      static_cast<const __nv_bfloat16*>(dt), dt_stride, static_cast<const float*>(A),
+      static_cast<const __nv_bfloat16*>(Bm), static_cast<const __nv_bfloat16*>(Cm), bc_stride,
+      static_cast<const float*>(D), static_cast<const float*>(dt_bias), static_cast<__nv_bfloat16*>(y), H, P, N, G,
+      dt_softplus, dt_min, dt_max);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mx_gated_rmsnorm(const void* y, const void* z, int z_stride, const void* weight, void* out,
+                                int rows, int dim, float eps, void* stream) {
+  if (rows <= 0 || dim <= 0) return 0;
+  gated_rmsnorm_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z), z_stride,
+      static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), dim, eps);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -90,6 +90,11 @@ class Engine:
         self.is_cuda = self.device.type == "cuda"
         tp = model.comm.tp_size
         nl = len(model.w.layers)
+        self.recurrent = bool(getattr(model, "recurrent", False))
+        if self.recurrent:
+            # per-sequence recurrent state lives in the model, not in the block pool: a cached prefix has
+            # no state to resume from, and the state slot indices change from step to step
+            e.prefix_cache = e.cuda_graphs = e.lookahead = False
         if e.num_blocks <= 0:
             e.num_blocks = self._auto_num_blocks(tp, nl)
         self.pool = KVPool(cfg, e.num_blocks, e.block_size, kv_bits=e.kv_bits, device=self.device,
@@ -207,6 +212,8 @@ class Engine:
             self.bm.free_seq(s.seq_id)
         if s in self.running:
             self.running.remove(s)
+        if self.recurrent:
+            self.model.release_seq(s.seq_id)
 
     def _preempt_one(self) -> bool:
         """Reclaim blocks by recompute-preempting the least progressed running row
@@ -218,6 +225,8 @@ class Engine:
         victim = min(cands, key=lambda s: (len(s.output), -s.seq_id))
         self.running.remove(victim)
         self.bm.free_seq(victim.seq_id)
+        if self.recurrent:
+            self.model.release_seq(victim.seq_id)
         victim.num_computed = 0
         victim.status = SeqStatus.PREEMPTED
         victim.preemptions += 1
@@ -375,6 +384,8 @@ class Engine:
                       pf_context_lens=self.d_pf_lens[:sp] if sp else None, pf_max_q_len=max_q,
                       pf_cu_q_host=cu if sp else None, logits_rows=self.d_rows[:R])
         b.logits_rows_host = rows
+        b.seq_ids = [s.seq_id for s in decode] + [p[0].seq_id for p in pieces]
+        b.pf_starts = [p[1] for p in pieces]
         return b, R
 
     # ------------------------------------------------------------------ cuda graphs

@@ -22,9 +22,14 @@ class LLM:
         """``fold_norms``: the weights belong to this object alone, so the executor may fold the
         RMSNorm weights into the projections in place (deferred RMSNorm, see DecoderModel)."""
         self.cfg = cfg
-        self.model = DecoderModel(cfg, weights, comm=comm,
-                                  kv_bits=(engine_config.kv_bits if engine_config else 16),
-                                  fold_norms=fold_norms)
+        if cfg.model_type == "mamba2":
+            from .models.mamba2 import Mamba2Model
+            self.model = Mamba2Model(cfg, weights, comm=comm,
+                                     max_seqs=2 * (engine_config.max_batch if engine_config else EngineConfig().max_batch))
+        else:
+            self.model = DecoderModel(cfg, weights, comm=comm,
+                                      kv_bits=(engine_config.kv_bits if engine_config else 16),
+                                      fold_norms=fold_norms)
         self.engine = Engine(self.model, cfg, engine_config)
         self.tokenizer = tokenizer
 
@@ -33,6 +38,9 @@ class LLM:
     def from_preset(name: str, *, device="cuda", seed: int = 0, engine_config: EngineConfig | None = None,
                     comm=None, dtype=torch.bfloat16) -> "LLM":
         cfg = preset(name)
+        if cfg.model_type == "mamba2":
+            from .models.mamba2 import random_mamba2_weights
+            return LLM(cfg, random_mamba2_weights(cfg, seed=seed, dtype=dtype, device=device), engine_config, comm=comm)
         tp = comm.tp_size if comm is not None else 1
         rank = comm.tp_rank if comm is not None else 0
         w = random_weights(cfg, seed=seed, dtype=dtype, device=device, tp_rank=rank, tp_size=tp,
@@ -47,6 +55,10 @@ class LLM:
         from .tokenizer import load_tokenizer
 
         cfg = ModelConfig.from_path(path)
+        if cfg.model_type == "mamba2":
+            from .models.mamba2 import load_mamba2_weights
+            return LLM(cfg, load_mamba2_weights(path, cfg, device=device), engine_config, comm=comm,
+                       tokenizer=load_tokenizer(path))
         w = load_model_weights(path, cfg, device=device, comm=comm, dequantize=dequantize, surgery=surgery)
         tok = load_tokenizer(path)
         return LLM(cfg, w, engine_config, comm=comm, tokenizer=tok, fold_norms=True)

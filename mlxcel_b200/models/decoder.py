@@ -48,6 +48,8 @@ class StepBatch:
     pf_cu_q_host: list | None = None               # host copy of pf_cu_q (micro-batch splitting)
     logits_rows: torch.Tensor | None = None        # [R] int64 rows of the hidden state to project
     embeds: torch.Tensor | None = None             # optional [T, H] input embeddings (VLM / MTP)
+    seq_ids: list | None = None                    # host: sequence id per decode row, then per prefill piece
+    pf_starts: list | None = None                  # host: first position of every prefill piece
 
     @property
     def num_tokens(self) -> int:

@@ -14,6 +14,9 @@ _vp, _i, _f, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longl
 _SIG = {
     "mx_ssm_update": [_vp] * 9 + [_i] * 6 + [_vp],
     "mx_selective_scan": [_vp] * 8 + [_i] * 5 + [_vp],
+    "mx_causal_conv_varlen": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "mx_ssm_scan_varlen": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp] + [_i] * 6 + [_f, _f, _vp],
+    "mx_gated_rmsnorm": [_vp, _vp, _i, _vp, _vp, _i, _i, _f, _vp],
     "mx_gated_delta_update": [_vp] * 7 + [_i, _i, _i, _f, _vp],
     "mx_bitlinear": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "mx_activation": [_vp, _vp, _ll, _i, _f, _f, _f, _f, _vp],
@@ -90,6 +93,104 @@ def selective_scan(x, dt, A, Bm, C, D, state, dt_softplus=True):
     _call("mx_selective_scan", x.data_ptr(), dt.data_ptr(), A.data_ptr(), Bm.data_ptr(), C.data_ptr(), _lib.ptr(D),
           state.data_ptr(), y.data_ptr(), Bsz, L, Di, A.shape[1], 1 if dt_softplus else 0, _lib.stream())
     return y
+
+
+# ----------------------------------------------------------------------------- Mamba2, ragged batch
+def _pieces(cu):
+    c = cu.tolist()
+    return [(c[j], c[j + 1]) for j in range(len(c) - 1)]
+
+
+def causal_conv_varlen_ref(xin, conv_state, slots, cu, reset, w, bias, silu=True):
+    C, K = w.shape
+    out = torch.empty(xin.shape[0], C, dtype=xin.dtype, device=xin.device)
+    sl, rs = slots.tolist(), reset.tolist()
+    for j, (t0, t1) in enumerate(_pieces(cu)):
+        if t1 <= t0:
+            continue
+        hist = torch.zeros(K - 1, C, device=xin.device) if rs[j] else conv_state[sl[j]].clone()
+        seq = torch.cat([hist, xin[t0:t1, :C].float()], dim=0)                       # [K-1+L, C]
+        y = F.conv1d(seq.t().unsqueeze(0), w.float().unsqueeze(1), None if bias is None else bias.float(), groups=C)
+        y = y[0].t()
+        out[t0:t1] = (F.silu(y) if silu else y).to(xin.dtype)
+        if K > 1:
+            conv_state[sl[j]] = seq[-(K - 1):]
+    return out
+
+
+def causal_conv_varlen(xin, conv_state, slots, cu, reset, w, bias, silu=True):
+    """Causal depth-wise conv + bias (+ SiLU) over a ragged batch of sequence pieces.
+
+    xin [T, >=C] (the first C columns are convolved; may be a column slice with a row stride);
+    conv_state [slots, K-1, C] fp32, advanced in place; slots / reset [S] int32; cu [S+1] int32;
+    w [C, K] fp32; bias [C] fp32 or None. Returns [T, C]."""
+    if not xin.is_cuda:
+        return causal_conv_varlen_ref(xin, conv_state, slots, cu, reset, w, bias, silu)
+    C, K = w.shape
+    assert xin.stride(1) == 1
+    out = torch.empty(xin.shape[0], C, dtype=xin.dtype, device=xin.device)
+    _call("mx_causal_conv_varlen", xin.data_ptr(), xin.stride(0), conv_state.data_ptr(), slots.data_ptr(), cu.data_ptr(),
+          reset.data_ptr(), w.data_ptr(), _lib.ptr(bias), out.data_ptr(), slots.numel(), C, K, 1 if silu else 0,
+          _lib.stream())
+    return out
+
+
+def ssm_scan_varlen_ref(state, slots, cu, reset, x, dt, A, Bm, Cm, D, dt_bias, dt_softplus=True, dt_limit=(0.0, float("inf"))):
+    S, H, P, N = state.shape
+    G = Bm.shape[1] // N
+    y = torch.empty(x.shape[0], H * P, dtype=x.dtype, device=x.device)
+    sl, rs = slots.tolist(), reset.tolist()
+    for j, (t0, t1) in enumerate(_pieces(cu)):
+        if t1 <= t0:
+            continue
+        s = torch.zeros(H, P, N, device=x.device) if rs[j] else state[sl[j]].clone()
+        for t in range(t0, t1):
+            dtv = dt[t].float() + (dt_bias.float() if dt_bias is not None else 0.0)
+            if dt_softplus:
+                dtv = F.softplus(dtv)
+            dtv = dtv.clamp(dt_limit[0], dt_limit[1])
+            xv = x[t].float().reshape(H, P)
+            Bh = Bm[t].float().reshape(G, N).repeat_interleave(H // G, dim=0)
+            Ch = Cm[t].float().reshape(G, N).repeat_interleave(H // G, dim=0)
+            s = s * torch.exp(dtv * A.float())[:, None, None] + (dtv[:, None] * xv)[..., None] * Bh[:, None, :]
+            yt = (s * Ch[:, None, :]).sum(-1)
+            if D is not None:
+                yt = yt + D.float()[:, None] * xv
+            y[t] = yt.reshape(-1).to(x.dtype)
+        state[sl[j]] = s
+    return y
+
+
+def ssm_scan_varlen(state, slots, cu, reset, x, dt, A, Bm, Cm, D=None, dt_bias=None, dt_softplus=True,
+                    dt_limit=(0.0, float("inf"))):
+    """Mamba2 recurrence over a ragged batch (decode rows are pieces of one token).
+
+    state [slots, H, P, N] fp32 in place; x [T, H*P]; dt [T, H]; Bm, Cm [T, G*N] (column slices with a
+    row stride are fine); A, D, dt_bias [H] fp32. Returns y [T, H*P]."""
+    if not x.is_cuda:
+        return ssm_scan_varlen_ref(state, slots, cu, reset, x, dt, A, Bm, Cm, D, dt_bias, dt_softplus, dt_limit)
+    S, H, P, N = state.shape
+    G = Bm.shape[1] // N
+    assert x.stride(1) == 1 and dt.stride(1) == 1 and Bm.stride(1) == 1 and Cm.stride(0) == Bm.stride(0)
+    y = torch.empty(x.shape[0], H * P, dtype=x.dtype, device=x.device)
+    _call("mx_ssm_scan_varlen", state.data_ptr(), slots.data_ptr(), cu.data_ptr(), reset.data_ptr(), x.data_ptr(),
+          x.stride(0), dt.data_ptr(), dt.stride(0), A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(), Bm.stride(0),
+          _lib.ptr(D), _lib.ptr(dt_bias), y.data_ptr(), slots.numel(), H, P, N, G, 1 if dt_softplus else 0,
+          float(dt_limit[0]), float(min(dt_limit[1], 3.0e38)), _lib.stream())
+    return y
+
+
+def gated_rmsnorm(y, z, weight, eps: float):
+    """RMSNorm(y * silu(z)) * weight; z may be a column slice with a row stride."""
+    if not y.is_cuda:
+        v = y.float() * F.silu(z.float())
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(y.dtype)
+    rows, dim = y.shape
+    assert z.stride(1) == 1 and y.is_contiguous()
+    out = torch.empty_like(y)
+    _call("mx_gated_rmsnorm", y.data_ptr(), z.data_ptr(), z.stride(0), weight.data_ptr(), out.data_ptr(), rows, dim,
+          float(eps), _lib.stream())
+    return out
 
 
 # ----------------------------------------------------------------------------- gated delta rule

@@ -76,3 +76,99 @@ def test_bitlinear_and_activations():
     yr, sr = R.add3_layernorm(a.cpu(), b.cpu(), c.cpu(), wt.cpu(), bs.cpu())
     assert torch.equal(s.cpu(), sr)
     _close(y.cpu(), yr, atol=5e-2)
+
+
+def _ragged(lens, n_slots):
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    g = torch.Generator().manual_seed(len(lens))
+    slots = torch.randperm(n_slots, generator=g)[: len(lens)].to(torch.int32)
+    reset = torch.tensor([1 if i % 3 == 1 else 0 for i in range(len(lens))], dtype=torch.int32)
+    return torch.tensor(cu, dtype=torch.int32), slots, reset
+
+
+@pytest.mark.parametrize("C,K,stride_extra", [(320, 4, 72), (96, 3, 0), (1024 + 8, 2, 8)])
+def test_causal_conv_varlen(C, K, stride_extra):
+    lens = [1, 1, 1, 37, 5, 130]
+    cu, slots, reset = _ragged(lens, 9)
+    T = int(cu[-1])
+    full = _bf(T, C + stride_extra)
+    xin = full[:, :C] if stride_extra == 0 else full[:, 8:8 + C]      # column slice with a row stride
+    st = torch.randn(9, K - 1, C, device=DEV)
+    st2 = st.clone().cpu()
+    w, b = torch.randn(C, K, device=DEV) * 0.3, torch.randn(C, device=DEV) * 0.1
+    y = R.causal_conv_varlen(xin, st, slots.to(DEV), cu.to(DEV), reset.to(DEV), w, b)
+    yr = R.causal_conv_varlen_ref(xin.cpu(), st2, slots, cu, reset, w.cpu(), b.cpu())
+    _close(y.cpu(), yr, atol=3e-2)
+    _close(st.cpu(), st2, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("H,P,N,G", [(8, 32, 32, 1), (4, 64, 128, 2), (6, 16, 80, 3), (2, 64, 256, 1)])
+def test_ssm_scan_varlen(H, P, N, G):
+    lens = [1, 1, 44, 1, 9]
+    cu, slots, reset = _ragged(lens, 7)
+    T = int(cu[-1])
+    conv = _bf(T, H * P + 2 * G * N, sc=0.5)
+    x, Bm, Cm = conv[:, :H * P], conv[:, H * P:H * P + G * N], conv[:, H * P + G * N:]
+    dt = _bf(T, H + 8)[:, 8:]
+    A = -torch.rand(H, device=DEV) - 0.1
+    D, db = torch.randn(H, device=DEV), torch.randn(H, device=DEV) * 0.1
+    st = torch.randn(7, H, P, N, device=DEV) * 0.2
+    st2 = st.clone().cpu()
+    lim = (0.01, 0.8)
+    y = R.ssm_scan_varlen(st, slots.to(DEV), cu.to(DEV), reset.to(DEV), x, dt, A, Bm, Cm, D, db, True, lim)
+    yr = R.ssm_scan_varlen_ref(st2, slots, cu, reset, x.cpu(), dt.cpu(), A.cpu(), Bm.cpu(), Cm.cpu(), D.cpu(), db.cpu(),
+                               True, lim)
+    _close(y.cpu(), yr, atol=0.1)
+    _close(st.cpu(), st2, rtol=2e-3, atol=2e-3)
+
+
+def test_gated_rmsnorm():
+    y, full = _bf(77, 640), _bf(77, 1000)
+    z = full[:, 40:680]
+    w = _bf(640, sc=0.2) + 1
+    got = R.gated_rmsnorm(y, z, w, 1e-5)
+    want = R.gated_rmsnorm(y.cpu().float(), z.cpu().float(), w.cpu().float(), 1e-5)
+    _close(got.cpu(), want, atol=3e-2)
+
+
+def test_tiny_mamba2_engine_gpu_matches_cpu():
+    """bf16 kernels on the GPU against the fp32 CPU path, through the engine (chunked prefill + batching)."""
+    import copy
+    from mlxcel_b200.config import preset
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.models.decoder import StepBatch
+    from mlxcel_b200.models.mamba2 import Mamba2Model, random_mamba2_weights
+
+    cfg = preset("tiny-mamba2")
+    w32 = random_mamba2_weights(cfg, seed=4, dtype=torch.float32, std=0.08)
+    w16 = copy.deepcopy(w32)
+    for obj in [w16, *w16.layers]:
+        for k, v in vars(obj).items():
+            if isinstance(v, torch.Tensor):
+                keep32 = k in ("conv_w", "conv_b", "dt_bias", "A_log", "D")
+                setattr(obj, k, (v if keep32 else v.to(torch.bfloat16)).to(DEV))
+    w16.lm_head = w16.embed
+    T = 50
+    ids = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+
+    def logits(w, dev):
+        m = Mamba2Model(cfg, w, max_seqs=4)
+        b = StepBatch(token_ids=ids.to(dev), positions=torch.arange(T, dtype=torch.int32, device=dev),
+                      slot_mapping=torch.arange(T, dtype=torch.int32, device=dev), num_prefill_seqs=1,
+                      pf_cu_q_host=[0, T], pf_max_q_len=T, logits_rows=torch.tensor([T - 1, T // 2], device=dev))
+        b.seq_ids, b.pf_starts = [0], [0]
+        return m.forward(b).float().cpu()
+
+    lc, lg = logits(w32, "cpu"), logits(w16, DEV)
+    assert (lc - lg).abs().max().item() < 0.05 * lc.abs().max().item() + 0.03
+    sp = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
+    eng = Engine(Mamba2Model(cfg, w16, max_seqs=16), cfg,
+                 EngineConfig(num_blocks=64, block_size=16, max_batch=8, max_model_len=256, max_num_batched_tokens=32))
+    outs = eng.generate([ids[:40].tolist(), ids[5:12].tolist()], sp)
+    assert all(len(s.output) == 8 for s in outs) and not eng.model.slot_of
+    from mlxcel_b200.ops import _lib
+    torch.cuda.synchronize()
+    assert _lib.read_status(torch.device(DEV)) == 0
