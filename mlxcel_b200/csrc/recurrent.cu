@@ -85,43 +85,105 @@ __global__ void selective_scan_kernel(const __nv_bfloat16* __restrict__ x, const
 
 // Causal depth-wise convolution (width K <= 8) + bias + SiLU. in: rows of `in_stride` elements of
 // which the first C are convolved; conv_state [slots, K-1, C] fp32 holds the last K-1 inputs of each
-// sequence and is advanced. One thread per (piece, channel); time is walked with the window in
-// registers, neighbouring threads read neighbouring channels.
+// sequence and is advanced. One thread per (piece, CPT neighbouring channels, chunk of kConvChunk
+// steps): the convolution is not recurrent, so time chunks run in parallel. A thread first issues all
+// of its chunk's loads (kConvChunk + KT - 1 rows; the taps sit right-aligned in a window of KT so
+// that every register index is static), then computes. KT = 4 serves K == 4, KT = 8 any K <= 8;
+// CPT = 2 moves channel pairs as 4-byte words. Only the thread of chunk 0 touches the state: it
+// reads the old tail and, after its chunk, writes the new one, so no other thread races it.
+constexpr int kConvChunk = 16;
+
+template <int KT, int CPT>
 __global__ void causal_conv_varlen_kernel(const __nv_bfloat16* __restrict__ in, int in_stride,
                                           float* __restrict__ conv_state, const int* __restrict__ slots,
                                           const int* __restrict__ cu, const int* __restrict__ reset,
                                           const float* __restrict__ w, const float* __restrict__ bias,
                                           __nv_bfloat16* __restrict__ out, int C, int K, int silu) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * CPT;
   const int j = blockIdx.y;
   if (c >= C) return;
   const int t0 = cu[j], t1 = cu[j + 1];
-  if (t1 <= t0) return;
+  const int tb = t0 + blockIdx.z * kConvChunk;
+  if (tb >= t1) return;
+  const bool first = blockIdx.z == 0;
+  const bool fresh = reset[j] != 0;
   float* cs = conv_state + static_cast<size_t>(slots[j]) * (K - 1) * C + c;
-  float win[8], wk[8];
+  const int pad = KT - K;                         // window slots [0, pad) carry zero taps
+  constexpr int W = kConvChunk + KT - 1;
+  float v[W][CPT], wr[KT][CPT];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    wk[k] = k < K ? w[static_cast<size_t>(c) * K + k] : 0.f;
-    win[k] = (k < K - 1 && !reset[j]) ? cs[static_cast<size_t>(k) * C] : 0.f;
-  }
-  const float bv = bias ? bias[c] : 0.f;
-  for (int t = t0; t < t1; ++t) {
-    const float xv = __bfloat162float(in[static_cast<size_t>(t) * in_stride + c]);
-    float acc = bv;
+  for (int m = 0; m < KT; ++m)
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      if (k == K - 1) win[k] = xv;
-      if (k < K) acc += wk[k] * win[k];
+    for (int e = 0; e < CPT; ++e) wr[m][e] = m >= pad ? w[static_cast<size_t>(c + e) * K + (m - pad)] : 0.f;
+  const auto load_row = [&](int tt, float (&dst)[CPT]) {
+    const __nv_bfloat16* src = in + static_cast<size_t>(tt) * in_stride + c;
+    if constexpr (CPT == 2) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src));
+      dst[0] = f.x, dst[1] = f.y;
+    } else {
+      dst[0] = __bfloat162float(*src);
     }
-    if (silu) acc = acc / (1.f + __expf(-acc));
-    out[static_cast<size_t>(t) * C + c] = __float2bfloat16(acc);
+  };
+  const int base = tb - (KT - 1);                 // v[i] is the input at row base + i
+  if (base >= t0 && tb + kConvChunk <= t1) {      // interior chunk: no edge on either side
 #pragma unroll
-    for (int k = 0; k < 7; ++k)
-      if (k < K - 1) win[k] = win[k + 1];
+    for (int i = 0; i < W; ++i) {
+#pragma unroll
+      for (int e = 0; e < CPT; ++e) v[i][e] = 0.f;
+      if (i >= pad) load_row(base + i, v[i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i) {
+      const int tt = base + i;
+#pragma unroll
+      for (int e = 0; e < CPT; ++e) v[i][e] = 0.f;
+      if (i >= pad && tt < t1) {
+        if (tt >= t0) {
+          load_row(tt, v[i]);
+        } else if (first && !fresh) {
+#pragma unroll
+          for (int e = 0; e < CPT; ++e) v[i][e] = cs[static_cast<size_t>(tt - t0 + (K - 1)) * C + e];
+        }
+      }
+    }
   }
+  float bv[CPT];
 #pragma unroll
-  for (int k = 0; k < 7; ++k)
-    if (k < K - 1) cs[static_cast<size_t>(k) * C] = win[k];
+  for (int e = 0; e < CPT; ++e) bv[e] = bias ? bias[c + e] : 0.f;
+#pragma unroll
+  for (int sidx = 0; sidx < kConvChunk; ++sidx) {
+    const int t = tb + sidx;
+    if (t < t1) {
+      float acc[CPT];
+#pragma unroll
+      for (int e = 0; e < CPT; ++e) {
+        acc[e] = bv[e];
+#pragma unroll
+        for (int m = 0; m < KT; ++m) acc[e] += wr[m][e] * v[sidx + m][e];
+        if (silu) acc[e] = acc[e] / (1.f + __expf(-acc[e]));
+      }
+      __nv_bfloat16* dst = out + static_cast<size_t>(t) * C + c;
+      if constexpr (CPT == 2) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc[0], acc[1]);
+      else *dst = __float2bfloat16(acc[0]);
+    }
+  }
+  if (!first) return;
+  // new tail = the K-1 rows before t1; a piece shorter than the tail shifts the old one (reads run
+  // ahead of the writes: entry L + m > m)
+  const int L = t1 - t0;
+  for (int m = 0; m < K - 1; ++m) {
+    const int tt = t1 - (K - 1) + m;
+    float x[CPT];
+    if (tt >= t0) {
+      load_row(tt, x);
+    } else {
+#pragma unroll
+      for (int e = 0; e < CPT; ++e) x[e] = fresh ? 0.f : cs[static_cast<size_t>(L + m) * C + e];
+    }
+#pragma unroll
+    for (int e = 0; e < CPT; ++e) cs[static_cast<size_t>(m) * C + e] = x[e];
+  }
 }
 
 // State-space recurrence  S <- S exp(dt A_h) + dt x (x) B,  y = S C + D_h x  walked over each piece.
@@ -177,6 +239,286 @@ __global__ void ssm_scan_varlen_kernel(float* __restrict__ state, const int* __r
   for (int i = 0; i < 8; ++i) {
     const int n = lane + 32 * i;
     if (n < N) st[n] = s[i];
+  }
+}
+
+// The same recurrence for pieces of ONE token (decode rows), bandwidth-bound on the state: a warp owns
+// kStepRows consecutive rows p of one (piece, head) and lane l the columns 4(l + 32 i) .. +3 of each,
+// moved as float4, so that every lane has kStepRows x 2 independent 16-byte loads in flight and dt,
+// exp(dt A), B and C are worked out once per warp (N % 4 == 0, N <= 256, P % kStepRows == 0; B and C
+// rows 8-byte aligned).
+constexpr int kStepRows = 4;
+
+template <int NV>                               // float4 groups per lane: 1 for N <= 128, 2 up to 256
+__global__ void ssm_step_vec4_kernel(float* __restrict__ state, const int* __restrict__ slots,
+                                     const int* __restrict__ cu, const int* __restrict__ reset,
+                                     const __nv_bfloat16* __restrict__ x, int x_stride,
+                                     const __nv_bfloat16* __restrict__ dt, int dt_stride,
+                                     const float* __restrict__ A, const __nv_bfloat16* __restrict__ Bm,
+                                     const __nv_bfloat16* __restrict__ Cm, int bc_stride,
+                                     const float* __restrict__ D, const float* __restrict__ dt_bias,
+                                     __nv_bfloat16* __restrict__ y, int H, int P, int N, int G,
+                                     int dt_softplus, float dt_min, float dt_max) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int j = blockIdx.y;
+  const int ppw = P / kStepRows;
+  if (gw >= H * ppw) return;
+  const int h = gw / ppw, p0 = (gw - h * ppw) * kStepRows, g = h / (H / G);
+  const int t = cu[j];
+  if (cu[j + 1] <= t) return;
+  float* st = state + ((static_cast<size_t>(slots[j]) * H + h) * P + p0) * N;
+  const bool fresh = reset[j] != 0;
+  float4 s[kStepRows][NV];
+#pragma unroll
+  for (int r = 0; r < kStepRows; ++r)
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int n = 4 * (lane + 32 * i);
+      s[r][i] = (n < N && !fresh) ? *reinterpret_cast<const float4*>(st + static_cast<size_t>(r) * N + n)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  float dtv = __bfloat162float(dt[static_cast<size_t>(t) * dt_stride + h]) + (dt_bias ? dt_bias[h] : 0.f);
+  if (dt_softplus) dtv = softplus_f(dtv);
+  dtv = fminf(fmaxf(dtv, dt_min), dt_max);
+  const float dA = __expf(dtv * A[h]), dv = D ? D[h] : 0.f;
+  const __nv_bfloat16* bp = Bm + static_cast<size_t>(t) * bc_stride + g * N;
+  const __nv_bfloat16* cp = Cm + static_cast<size_t>(t) * bc_stride + g * N;
+  float4 bq[NV], cq[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int n = 4 * (lane + 32 * i);
+    bq[i] = cq[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (n < N) {
+      const uint2 braw = *reinterpret_cast<const uint2*>(bp + n), craw = *reinterpret_cast<const uint2*>(cp + n);
+      const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&braw.x));
+      const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&braw.y));
+      const float2 c0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&craw.x));
+      const float2 c1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&craw.y));
+      bq[i] = make_float4(b0.x, b0.y, b1.x, b1.y);
+      cq[i] = make_float4(c0.x, c0.y, c1.x, c1.y);
+    }
+  }
+  const __nv_bfloat16* xr = x + static_cast<size_t>(t) * x_stride + h * P + p0;
+  float xv[kStepRows], acc[kStepRows];
+#pragma unroll
+  for (int r = 0; r < kStepRows; ++r) {
+    xv[r] = __bfloat162float(xr[r]);
+    const float dx = dtv * xv[r];
+    acc[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      s[r][i].x = s[r][i].x * dA + dx * bq[i].x;
+      s[r][i].y = s[r][i].y * dA + dx * bq[i].y;
+      s[r][i].z = s[r][i].z * dA + dx * bq[i].z;
+      s[r][i].w = s[r][i].w * dA + dx * bq[i].w;
+      acc[r] += s[r][i].x * cq[i].x + s[r][i].y * cq[i].y + s[r][i].z * cq[i].z + s[r][i].w * cq[i].w;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kStepRows; ++r)
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int n = 4 * (lane + 32 * i);
+      if (n < N) *reinterpret_cast<float4*>(st + static_cast<size_t>(r) * N + n) = s[r][i];
+    }
+#pragma unroll
+  for (int r = 0; r < kStepRows; ++r) acc[r] = warp_sum(acc[r]);
+  if (lane < kStepRows) {
+    float a = acc[0], xx = xv[0];
+#pragma unroll
+    for (int r = 1; r < kStepRows; ++r)
+      if (lane == r) a = acc[r], xx = xv[r];
+    y[static_cast<size_t>(t) * H * P + h * P + p0 + lane] = __float2bfloat16(a + dv * xx);
+  }
+}
+
+// The same recurrence for long pieces (prefill chunks). It is bound by instruction issue and by the
+// shared-memory pipe, not by DRAM, so the layout is a register tile: a thread keeps RPT rows x 4V
+// columns of the state, SPLIT neighbouring lanes cover a row's N columns (lane q holds the float4
+// column groups q, q + SPLIT, ...), and every B / C word a thread reads from shared memory feeds RPT
+// rows. A step is 2N FMAs per row; the row sums are completed with a halving exchange (RPT values
+// over SPLIT lanes in log2(RPT) + 2 rounds). A CTA is kScanRows rows of one (piece, head); per chunk
+// of kScanChunk steps it stages B, C (shared by the head's rows), x, dt and exp(dt A) in shared memory
+// as fp32. RPT = SPLIT / 4, so that a CTA of kScanThreads threads always covers kScanRows rows.
+constexpr int kScanChunk = 16;
+constexpr int kScanRows = 32;
+constexpr int kScanThreads = 128;
+
+template <int N, int SPLIT>
+__global__ void __launch_bounds__(kScanThreads)
+ssm_scan_rows_kernel(float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
+                     const int* __restrict__ reset, const __nv_bfloat16* __restrict__ x, int x_stride,
+                     const __nv_bfloat16* __restrict__ dt, int dt_stride, const float* __restrict__ A,
+                     const __nv_bfloat16* __restrict__ Bm, const __nv_bfloat16* __restrict__ Cm, int bc_stride,
+                     const float* __restrict__ D, const float* __restrict__ dt_bias, __nv_bfloat16* __restrict__ y,
+                     int H, int P, int G, int dt_softplus, float dt_min, float dt_max) {
+  constexpr int RPT = SPLIT / 4;              // rows per thread
+  constexpr int V = N / (4 * SPLIT);          // float4 column groups per thread and row
+  static_assert(V >= 1 && RPT >= 1 && (kScanThreads / SPLIT) * RPT == kScanRows, "tile shape");
+  __shared__ __align__(16) float Bs[kScanChunk * N];
+  __shared__ __align__(16) float Cs[kScanChunk * N];
+  __shared__ __align__(16) float xs[kScanChunk * kScanRows];
+  __shared__ float dts[kScanChunk], dAs[kScanChunk];
+  const int row_blocks = (P + kScanRows - 1) / kScanRows;
+  const int h = blockIdx.x / row_blocks, rb = blockIdx.x - h * row_blocks, j = blockIdx.y;
+  const int grp = threadIdx.x / SPLIT, q = threadIdx.x % SPLIT;
+  const int r0 = grp * RPT;                   // first of this thread's rows inside the CTA's rows
+  const int p0 = rb * kScanRows + r0;
+  const int g = h / (H / G);
+  const int t0 = cu[j], t1 = cu[j + 1];
+  if (t1 <= t0) return;
+  float* st = state + (static_cast<size_t>(slots[j]) * H + h) * P * N;
+  float4 s[RPT][V];
+  const bool fresh = reset[j] != 0;
+#pragma unroll
+  for (int k = 0; k < RPT; ++k)
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+      s[k][i] = (p0 + k < P && !fresh)
+                    ? *reinterpret_cast<const float4*>(st + static_cast<size_t>(p0 + k) * N + 4 * (i * SPLIT + q))
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+  const float a = A[h], dv = D ? D[h] : 0.f, db = dt_bias ? dt_bias[h] : 0.f;
+  // the lane that ends up with a row's sum after the exchange below, and where it writes it
+  const int my_row = q / (SPLIT / RPT);
+  const bool writer = q % (SPLIT / RPT) == 0 && p0 + my_row < P;
+  const int HP = H * P;
+  __nv_bfloat16* yp = y + static_cast<size_t>(t0) * HP + h * P + p0 + my_row;
+  for (int c0 = t0; c0 < t1; c0 += kScanChunk) {
+    const int steps = min(kScanChunk, t1 - c0);
+    __syncthreads();                          // the previous chunk has been consumed
+    for (int i = threadIdx.x; i < steps * N; i += kScanThreads) {
+      const int tt = i / N, n = i - tt * N;
+      const size_t off = static_cast<size_t>(c0 + tt) * bc_stride + g * N + n;
+      Bs[i] = __bfloat162float(Bm[off]);
+      Cs[i] = __bfloat162float(Cm[off]);
+    }
+    for (int i = threadIdx.x; i < steps * kScanRows; i += kScanThreads) {
+      const int tt = i / kScanRows, rr = i - tt * kScanRows;
+      const int pp = rb * kScanRows + rr;
+      xs[i] = pp < P ? __bfloat162float(x[static_cast<size_t>(c0 + tt) * x_stride + h * P + pp]) : 0.f;
+    }
+    if (threadIdx.x < steps) {
+      float dtv = __bfloat162float(dt[static_cast<size_t>(c0 + threadIdx.x) * dt_stride + h]) + db;
+      if (dt_softplus) dtv = softplus_f(dtv);
+      dtv = fminf(fmaxf(dtv, dt_min), dt_max);
+      dts[threadIdx.x] = dtv;
+      dAs[threadIdx.x] = __expf(dtv * a);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < steps; ++tt) {
+      const float dA = dAs[tt], dtv = dts[tt];
+      float xv[RPT], dx[RPT], a0[RPT], a1[RPT], acc[RPT];
+      if constexpr (RPT == 4) {
+        const float4 x4 = *reinterpret_cast<const float4*>(xs + tt * kScanRows + r0);
+        xv[0] = x4.x, xv[1] = x4.y, xv[2] = x4.z, xv[3] = x4.w;
+      } else {
+#pragma unroll
+        for (int k = 0; k < RPT; ++k) xv[k] = xs[tt * kScanRows + r0 + k];
+      }
+#pragma unroll
+      for (int k = 0; k < RPT; ++k) dx[k] = dtv * xv[k], a0[k] = 0.f, a1[k] = 0.f;
+      const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * N) + q;
+      const float4* c4 = reinterpret_cast<const float4*>(Cs + tt * N) + q;
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float4 b = b4[i * SPLIT], c = c4[i * SPLIT];
+#pragma unroll
+        for (int k = 0; k < RPT; ++k) {
+          s[k][i].x = fmaf(s[k][i].x, dA, dx[k] * b.x);
+          s[k][i].y = fmaf(s[k][i].y, dA, dx[k] * b.y);
+          s[k][i].z = fmaf(s[k][i].z, dA, dx[k] * b.z);
+          s[k][i].w = fmaf(s[k][i].w, dA, dx[k] * b.w);
+          a0[k] = fmaf(s[k][i].x, c.x, a0[k]);
+          a1[k] = fmaf(s[k][i].y, c.y, a1[k]);
+          a0[k] = fmaf(s[k][i].z, c.z, a0[k]);
+          a1[k] = fmaf(s[k][i].w, c.w, a1[k]);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < RPT; ++k) acc[k] = a0[k] + a1[k];
+      // halving exchange: after the round with lane mask m a lane keeps the rows of its half
+#pragma unroll
+      for (int w = RPT / 2, m = SPLIT / 2; w >= 1; w /= 2, m /= 2) {
+        const bool upper = (q & m) != 0;
+#pragma unroll
+        for (int k = 0; k < w; ++k) {
+          const float send = upper ? acc[k] : acc[k + w];
+          const float keep = upper ? acc[k + w] : acc[k];
+          acc[k] = keep + __shfl_xor_sync(0xffffffffu, send, m);
+        }
+      }
+#pragma unroll
+      for (int m = SPLIT / RPT / 2; m >= 1; m /= 2) acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], m);
+      float xr = xv[0];
+#pragma unroll
+      for (int k = 1; k < RPT; ++k)
+        if (my_row == k) xr = xv[k];
+      if (writer) yp[static_cast<size_t>(tt) * HP] = __float2bfloat16(acc[0] + dv * xr);
+    }
+    yp += static_cast<size_t>(steps) * HP;
+  }
+#pragma unroll
+  for (int k = 0; k < RPT; ++k)
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+      if (p0 + k < P)
+        *reinterpret_cast<float4*>(st + static_cast<size_t>(p0 + k) * N + 4 * (i * SPLIT + q)) = s[k][i];
+}
+
+// out = RMSNorm(y * silu(z)) * weight over rows of `dim`; z rows at stride z_stride. One CTA per row.
+// Vector variant: 16-byte loads, every thread keeps its (up to 16) gated values in registers, so y and
+// z are read once (dim % 8 == 0, dim <= 16 * blockDim, rows of y, z and out 16-byte aligned).
+__global__ void __launch_bounds__(512)
+gated_rmsnorm_vec_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z, int z_stride,
+                         const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, int dim,
+                         float eps) {
+  __shared__ float red[32];
+  const size_t row = blockIdx.x;
+  float v[2][8];
+  float ssq = 0.f;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = (threadIdx.x + r * blockDim.x) * 8;
+    if (i < dim) {
+      const uint4 yr = *reinterpret_cast<const uint4*>(y + row * dim + i);
+      const uint4 zr = *reinterpret_cast<const uint4*>(z + row * z_stride + i);
+      const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&yr);
+      const __nv_bfloat162* z2 = reinterpret_cast<const __nv_bfloat162*>(&zr);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 yv = __bfloat1622float2(y2[q]), zv = __bfloat1622float2(z2[q]);
+        v[r][2 * q] = yv.x * (zv.x / (1.f + __expf(-zv.x)));
+        v[r][2 * q + 1] = yv.y * (zv.y / (1.f + __expf(-zv.y)));
+        ssq += v[r][2 * q] * v[r][2 * q] + v[r][2 * q + 1] * v[r][2 * q + 1];
+      }
+    }
+  }
+  ssq = warp_sum(ssq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ssq;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) red[0] = rsqrtf(t / dim + eps);
+  }
+  __syncthreads();
+  const float rs = red[0];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = (threadIdx.x + r * blockDim.x) * 8;
+    if (i < dim) {
+      const uint4 wr = *reinterpret_cast<const uint4*>(weight + i);
+      const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wr);
+      uint4 o;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 wv = __bfloat1622float2(w2[q]);
+        o2[q] = __floats2bfloat162_rn(v[r][2 * q] * rs * wv.x, v[r][2 * q + 1] * rs * wv.y);
+      }
+      *reinterpret_cast<uint4*>(out + row * dim + i) = o;
+    }
   }
 }
 
@@ -362,45 +704,134 @@ extern "C" int mx_selective_scan(const void* x, const void* dt, const void* A, c
   return static_cast<int>(cudaGetLastError());
 }
 
+// max_len: an upper bound of the longest piece (sizes the grid over time chunks).
 extern "C" int mx_causal_conv_varlen(const void* in, int in_stride, void* conv_state, const void* slots,
                                      const void* cu, const void* reset, const void* w, const void* bias, void* out,
-                                     int pieces, int C, int K, int silu, void* stream) {
-  if (pieces <= 0 || C <= 0) return 0;
-  if (K < 1 || K > 8 || pieces > 65535) return -1;
+                                     int pieces, int max_len, int C, int K, int silu, void* stream) {
+  if (pieces <= 0 || C <= 0 || max_len <= 0) return 0;
+  const int chunks = (max_len + kConvChunk - 1) / kConvChunk;
+  if (K < 1 || K > 8 || pieces > 65535 || chunks > 65535) return -1;
   const int threads = 128;
-  const dim3 grid((C + threads - 1) / threads, pieces);
-  causal_conv_varlen_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(in), in_stride, static_cast<float*>(conv_state),
-      static_cast<const int*>(slots), static_cast<const int*>(cu), static_cast<const int*>(reset),
-      static_cast<const float*>(w), static_cast<const float*>(bias), static_cast<__nv_bfloat16*>(out), C, K, silu);
+  const auto al4 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 4 == 0; };
+  const bool pair = C % 2 == 0 && in_stride % 2 == 0 && al4(in) && al4(out);
+  const int cpt = pair ? 2 : 1;
+  const dim3 grid(((C + cpt - 1) / cpt + threads - 1) / threads, pieces, chunks);
+#define MX_CONV(KT, CPT)                                                                                         \
+  causal_conv_varlen_kernel<KT, CPT><<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(                  \
+      static_cast<const __nv_bfloat16*>(in), in_stride, static_cast<float*>(conv_state),                       \
+      static_cast<const int*>(slots), static_cast<const int*>(cu), static_cast<const int*>(reset),             \
+      static_cast<const float*>(w), static_cast<const float*>(bias), static_cast<__nv_bfloat16*>(out), C, K, silu)
+  if (K == 4) {
+    if (pair) MX_CONV(4, 2);
+    else MX_CONV(4, 1);
+  } else {
+    if (pair) MX_CONV(8, 2);
+    else MX_CONV(8, 1);
+  }
+#undef MX_CONV
   return static_cast<int>(cudaGetLastError());
 }
 
+namespace {
+
+template <int N, int SPLIT>
+int launch_scan_rows(float* state, const int* slots, const int* cu, const int* reset, const __nv_bfloat16* x,
+                     int x_stride, const __nv_bfloat16* dt, int dt_stride, const float* A, const __nv_bfloat16* Bm,
+                     const __nv_bfloat16* Cm, int bc_stride, const float* D, const float* dt_bias, __nv_bfloat16* y,
+                     int pieces, int H, int P, int G, int dt_softplus, float dt_min, float dt_max,
+                     cudaStream_t stream) {
+  const int row_blocks = (P + kScanRows - 1) / kScanRows;
+  ssm_scan_rows_kernel<N, SPLIT><<<dim3(H * row_blocks, pieces), kScanThreads, 0, stream>>>(
+      state, slots, cu, reset, x, x_stride, dt, dt_stride, A, Bm, Cm, bc_stride, D, dt_bias, y, H, P, G, dt_softplus,
+      dt_min, dt_max);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+// The first n_short pieces hold one token each (decode rows) and take the bandwidth-shaped kernel;
+// the others take the row kernel where its shape is covered (N in {16, 32, 64, 128}), else the
+// generic warp-per-row kernel.
 extern "C" int mx_ssm_scan_varlen(void* state, const void* slots, const void* cu, const void* reset, const void* x,
                                   int x_stride, const void* dt, int dt_stride, const void* A, const void* Bm,
                                   const void* Cm, int bc_stride, const void* D, const void* dt_bias, void* y,
-                                  int pieces, int H, int P, int N, int G, int dt_softplus, float dt_min,
+                                  int pieces, int n_short, int H, int P, int N, int G, int dt_softplus, float dt_min,
                                   float dt_max, void* stream) {
   if (pieces <= 0 || H <= 0 || P <= 0) return 0;
-  if (N < 1 || N > 256 || G <= 0 || H % G || pieces > 65535) return -1;
+  if (N < 1 || N > 256 || G <= 0 || H % G || pieces > 65535 || n_short < 0 || n_short > pieces) return -1;
+  auto* st = static_cast<float*>(state);
+  const auto* sl = static_cast<const int*>(slots);
+  const auto* cup = static_cast<const int*>(cu);
+  const auto* rs = static_cast<const int*>(reset);
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  const auto* dtp = static_cast<const __nv_bfloat16*>(dt);
+  const auto* bp = static_cast<const __nv_bfloat16*>(Bm);
+  const auto* cp = static_cast<const __nv_bfloat16*>(Cm);
+  const auto* Ap = static_cast<const float*>(A);
+  const auto* Dp = static_cast<const float*>(D);
+  const auto* dbp = static_cast<const float*>(dt_bias);
+  auto* yp = static_cast<__nv_bfloat16*>(y);
+  auto s = static_cast<cudaStream_t>(stream);
   const int threads = 128;
-  const dim3 grid((H * P * 32 + threads - 1) / threads, pieces);
-  ssm_scan_varlen_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<float*>(state), static_cast<const int*>(slots), static_cast<const int*>(cu),
-      static_cast<const int*>(reset), static_cast<const __nv_bfloat16*>(x), x_stride,
-      static_cast<const __nv_bfloat16*>(dt), dt_stride, static_cast<const float*>(A),
-      static_cast<const __nv_bfloat16*>(Bm), static_cast<const __nv_bfloat16*>(Cm), bc_stride,
-      static_cast<const float*>(D), static_cast<const float*>(dt_bias), static_cast<__nv_bfloat16*>(y), H, P, N, G,
-      dt_softplus, dt_min, dt_max);
+  const int gx = (H * P * 32 + threads - 1) / threads;
+  const bool vec4 = N % 4 == 0 && P % kStepRows == 0 && bc_stride % 4 == 0 && reinterpret_cast<uintptr_t>(Bm) % 8 == 0 &&
+                    reinterpret_cast<uintptr_t>(Cm) % 8 == 0 && reinterpret_cast<uintptr_t>(state) % 16 == 0;
+  const bool rows_ok = (N == 16 || N == 32 || N == 64 || N == 128) && static_cast<long long>(H) * P < (1 << 26) &&
+                       reinterpret_cast<uintptr_t>(state) % 16 == 0;
+  int first_generic = 0, n_generic = pieces;      // what is left for the generic kernel
+  if (n_short > 0 && vec4) {
+    const int gxs = (H * (P / kStepRows) * 32 + threads - 1) / threads;
+    if (N <= 128)
+      ssm_step_vec4_kernel<1><<<dim3(gxs, n_short), threads, 0, s>>>(st, sl, cup, rs, xp, x_stride, dtp, dt_stride, Ap,
+                                                                      bp, cp, bc_stride, Dp, dbp, yp, H, P, N, G,
+                                                                      dt_softplus, dt_min, dt_max);
+    else
+      ssm_step_vec4_kernel<2><<<dim3(gxs, n_short), threads, 0, s>>>(st, sl, cup, rs, xp, x_stride, dtp, dt_stride, Ap,
+                                                                      bp, cp, bc_stride, Dp, dbp, yp, H, P, N, G,
+                                                                      dt_softplus, dt_min, dt_max);
+    first_generic = n_short;
+    n_generic = pieces - n_short;
+  }
+  if (n_generic > 0 && rows_ok && first_generic == n_short) {
+    const int np = pieces - n_short;
+    int rc = 0;
+#define MX_SCAN_ROWS(NN, SP)                                                                                  \
+  rc = launch_scan_rows<NN, SP>(st, sl + n_short, cup + n_short, rs + n_short, xp, x_stride, dtp, dt_stride, Ap, \
+                                bp, cp, bc_stride, Dp, dbp, yp, np, H, P, G, dt_softplus, dt_min, dt_max, s)
+    if (np > 0) {
+      if (N == 16) MX_SCAN_ROWS(16, 4);
+      else if (N == 32) MX_SCAN_ROWS(32, 8);
+      else if (N == 64) MX_SCAN_ROWS(64, 16);
+      else MX_SCAN_ROWS(128, 16);
+    }
+#undef MX_SCAN_ROWS
+    if (rc) return rc;
+    n_generic = 0;
+  }
+  if (n_generic > 0) {
+    ssm_scan_varlen_kernel<<<dim3(gx, n_generic), threads, 0, s>>>(
+        st, sl + first_generic, cup + first_generic, rs + first_generic, xp, x_stride, dtp, dt_stride, Ap, bp, cp,
+        bc_stride, Dp, dbp, yp, H, P, N, G, dt_softplus, dt_min, dt_max);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int mx_gated_rmsnorm(const void* y, const void* z, int z_stride, const void* weight, void* out,
                                 int rows, int dim, float eps, void* stream) {
   if (rows <= 0 || dim <= 0) return 0;
-  gated_rmsnorm_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z), z_stride,
-      static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), dim, eps);
+  const auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec = dim % 8 == 0 && z_stride % 8 == 0 && dim <= 8192 && aligned(y) && aligned(z) &&
+                   aligned(weight) && aligned(out);
+  if (vec) {
+    const int threads = min(512, ((dim / 8 + 1) / 2 + 31) / 32 * 32);
+    gated_rmsnorm_vec_kernel<<<rows, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z), z_stride,
+        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), dim, eps);
+  } else {
+    gated_rmsnorm_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z), z_stride,
+        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), dim, eps);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 

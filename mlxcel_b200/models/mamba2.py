@@ -190,16 +190,17 @@ class Mamba2Model:
 
     # ------------------------------------------------------------------ one mixer
     def _mixer(self, li: int, lw: Mamba2LayerWeights, x: torch.Tensor, pieces) -> torch.Tensor:
-        """x [T, H] normalised input; pieces = (slots, cu, reset) int32 device tensors. Returns the
+        """x [T, H] normalised input; pieces = (slots, cu, reset int32 device tensors, number of decode
+        rows, longest piece). Returns the
         gated, normalised SSM output [T, d_inner] (the input of out_proj)."""
         d = self.d
         di, GN = d["d_inner"], d["G"] * d["N"]
-        slots, cu, reset = pieces
+        slots, cu, reset, nd, max_len = pieces
         proj = ops.linear(x, lw.in_proj)                       # [T, 2*di + 2GN + heads]
         z, xBC, dt = proj[:, :di], proj[:, di:di + d["conv_dim"]], proj[:, di + d["conv_dim"]:]
-        conv = rops.causal_conv_varlen(xBC, self.conv_state[li], slots, cu, reset, lw.conv_w, lw.conv_b, True)
+        conv = rops.causal_conv_varlen(xBC, self.conv_state[li], slots, cu, reset, lw.conv_w, lw.conv_b, True, max_len)
         y = rops.ssm_scan_varlen(self.ssm_state[li], slots, cu, reset, conv[:, :di], dt, self.A[li],
-                                 conv[:, di:di + GN], conv[:, di + GN:], lw.D, lw.dt_bias, True, self.dt_limit)
+                                 conv[:, di:di + GN], conv[:, di + GN:], lw.D, lw.dt_bias, True, self.dt_limit, nd)
         return rops.gated_rmsnorm(y, z, lw.gnorm, self.cfg.rms_norm_eps)
 
     # ------------------------------------------------------------------ forward
@@ -219,7 +220,7 @@ class Mamba2Model:
         slots = [self._slot(i, bool(r)) for i, r in zip(ids, reset)]
         S = len(slots)
         meta = torch.tensor(slots + reset + cu, dtype=torch.int32).to(self.device, non_blocking=True)
-        pieces = (meta[:S], meta[2 * S:], meta[S:2 * S])
+        pieces = (meta[:S], meta[2 * S:], meta[S:2 * S], nd, max(1 if nd else 0, b.pf_max_q_len))
         h = hidden_in if hidden_in is not None else ops.embedding(b.token_ids, self.w.embed, cfg.embed_scale)
         for li, lw in enumerate(self.w.layers):
             x = ops.rmsnorm(h, lw.norm, cfg.rms_norm_eps, 0.0)

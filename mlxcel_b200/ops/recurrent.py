@@ -14,8 +14,8 @@ _vp, _i, _f, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longl
 _SIG = {
     "mx_ssm_update": [_vp] * 9 + [_i] * 6 + [_vp],
     "mx_selective_scan": [_vp] * 8 + [_i] * 5 + [_vp],
-    "mx_causal_conv_varlen": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
-    "mx_ssm_scan_varlen": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp] + [_i] * 6 + [_f, _f, _vp],
+    "mx_causal_conv_varlen": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "mx_ssm_scan_varlen": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp] + [_i] * 7 + [_f, _f, _vp],
     "mx_gated_rmsnorm": [_vp, _vp, _i, _vp, _vp, _i, _i, _f, _vp],
     "mx_gated_delta_update": [_vp] * 7 + [_i, _i, _i, _f, _vp],
     "mx_bitlinear": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
@@ -118,20 +118,23 @@ def causal_conv_varlen_ref(xin, conv_state, slots, cu, reset, w, bias, silu=True
     return out
 
 
-def causal_conv_varlen(xin, conv_state, slots, cu, reset, w, bias, silu=True):
+def causal_conv_varlen(xin, conv_state, slots, cu, reset, w, bias, silu=True, max_len: int | None = None):
     """Causal depth-wise conv + bias (+ SiLU) over a ragged batch of sequence pieces.
 
     xin [T, >=C] (the first C columns are convolved; may be a column slice with a row stride);
     conv_state [slots, K-1, C] fp32, advanced in place; slots / reset [S] int32; cu [S+1] int32;
-    w [C, K] fp32; bias [C] fp32 or None. Returns [T, C]."""
+    w [C, K] fp32; bias [C] fp32 or None; max_len: an upper bound of the longest piece (read back
+    from ``cu`` when not given, which synchronises). Returns [T, C]."""
     if not xin.is_cuda:
         return causal_conv_varlen_ref(xin, conv_state, slots, cu, reset, w, bias, silu)
     C, K = w.shape
     assert xin.stride(1) == 1
+    if max_len is None:
+        max_len = int((cu[1:] - cu[:-1]).max().item()) if slots.numel() else 0
     out = torch.empty(xin.shape[0], C, dtype=xin.dtype, device=xin.device)
     _call("mx_causal_conv_varlen", xin.data_ptr(), xin.stride(0), conv_state.data_ptr(), slots.data_ptr(), cu.data_ptr(),
-          reset.data_ptr(), w.data_ptr(), _lib.ptr(bias), out.data_ptr(), slots.numel(), C, K, 1 if silu else 0,
-          _lib.stream())
+          reset.data_ptr(), w.data_ptr(), _lib.ptr(bias), out.data_ptr(), slots.numel(), int(max_len), C, K,
+          1 if silu else 0, _lib.stream())
     return out
 
 
@@ -162,11 +165,12 @@ def ssm_scan_varlen_ref(state, slots, cu, reset, x, dt, A, Bm, Cm, D, dt_bias, d
 
 
 def ssm_scan_varlen(state, slots, cu, reset, x, dt, A, Bm, Cm, D=None, dt_bias=None, dt_softplus=True,
-                    dt_limit=(0.0, float("inf"))):
+                    dt_limit=(0.0, float("inf")), n_short: int = 0):
     """Mamba2 recurrence over a ragged batch (decode rows are pieces of one token).
 
     state [slots, H, P, N] fp32 in place; x [T, H*P]; dt [T, H]; Bm, Cm [T, G*N] (column slices with a
-    row stride are fine); A, D, dt_bias [H] fp32. Returns y [T, H*P]."""
+    row stride are fine); A, D, dt_bias [H] fp32; n_short: the first n_short pieces hold exactly one
+    token (they take the bandwidth-shaped kernel, the rest the row-per-thread one). Returns y [T, H*P]."""
     if not x.is_cuda:
         return ssm_scan_varlen_ref(state, slots, cu, reset, x, dt, A, Bm, Cm, D, dt_bias, dt_softplus, dt_limit)
     S, H, P, N = state.shape
@@ -175,7 +179,7 @@ def ssm_scan_varlen(state, slots, cu, reset, x, dt, A, Bm, Cm, D=None, dt_bias=N
     y = torch.empty(x.shape[0], H * P, dtype=x.dtype, device=x.device)
     _call("mx_ssm_scan_varlen", state.data_ptr(), slots.data_ptr(), cu.data_ptr(), reset.data_ptr(), x.data_ptr(),
           x.stride(0), dt.data_ptr(), dt.stride(0), A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(), Bm.stride(0),
-          _lib.ptr(D), _lib.ptr(dt_bias), y.data_ptr(), slots.numel(), H, P, N, G, 1 if dt_softplus else 0,
+          _lib.ptr(D), _lib.ptr(dt_bias), y.data_ptr(), slots.numel(), int(n_short), H, P, N, G, 1 if dt_softplus else 0,
           float(dt_limit[0]), float(min(dt_limit[1], 3.0e38)), _lib.stream())
     return y
 

@@ -9,6 +9,7 @@
     python -m mlxcel_b200.utils.profile_cases gemm_graph       # decode GEMMs back to back inside a CUDA graph, us per kernel
     python -m mlxcel_b200.utils.profile_cases gemm_phases      # per-CTA phase timestamps of the decode GEMMs
     python -m mlxcel_b200.utils.profile_cases qgemm_graph      # 4-bit weights: fused dequant GEMM vs GEMV vs dequantise + GEMM
+    python -m mlxcel_b200.utils.profile_cases mamba2           # Mamba2-2.7B mixer kernels (decode B=64, prefill 8 x 1024) + engine run
 
 Every case holds at most a few GB on the device and launches a handful of kernels, so that a
 capture with ``ncu --set full -k regex:<kernel> -c <n>`` ends by itself. ``decode_steps`` brackets
@@ -317,7 +318,84 @@ def qgemm_decode(M=32):
         quant.qlinear(x, qt, out=out)
 
 
-CASES = dict(qgemm_decode=qgemm_decode, qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
+def mamba2(engine_run=1):
+    """Mamba2-2.7B geometry (80 heads x 64, state 128, conv 4): the ragged conv / scan / gated-norm
+    kernels as decode rows (64 pieces of one token) and as prefill chunks (8 pieces of 1024), then
+    64 requests of 1024 prompt + 64 generated tokens through the engine."""
+    import time
+
+    from ..ops import recurrent as R
+
+    H, P, N, G, K, hid = 80, 64, 128, 1, 4, 2560
+    di, cd = H * P, H * P + 2 * G * N
+    slots_n = 128
+    conv_state = torch.zeros(slots_n, K - 1, cd, device=DEV)
+    state = torch.randn(slots_n, H, P, N, device=DEV) * 0.1
+    A = -torch.rand(H, device=DEV) - 0.1
+    D, db = torch.randn(H, device=DEV), torch.randn(H, device=DEV) * 0.1
+    cw, cb = torch.randn(cd, K, device=DEV) * 0.3, torch.randn(cd, device=DEV) * 0.1
+    gw = _bf(di) + 1
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+
+    def timeit(fn, iters=7, warm=3):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2]
+
+    for label, lens in (("decode_b64", [1] * 64), ("prefill_8x1024", [1024] * 8)):
+        T = sum(lens)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+        sl = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+        rs = torch.zeros(len(lens), dtype=torch.int32, device=DEV)
+        proj = _bf(T, 2 * di + 2 * G * N + H, scale=0.5)
+        z, xBC, dt = proj[:, :di], proj[:, di:di + cd], proj[:, di + cd:]
+        ml, ns = max(lens), (len(lens) if max(lens) == 1 else 0)
+        conv = R.causal_conv_varlen(xBC, conv_state, sl, cu, rs, cw, cb, True, ml)
+        y = R.ssm_scan_varlen(state, sl, cu, rs, conv[:, :di], dt, A, conv[:, di:di + G * N], conv[:, di + G * N:], D, db,
+                              n_short=ns)
+        t_conv = timeit(lambda: R.causal_conv_varlen(xBC, conv_state, sl, cu, rs, cw, cb, True, ml))
+        t_scan = timeit(lambda: R.ssm_scan_varlen(state, sl, cu, rs, conv[:, :di], dt, A, conv[:, di:di + G * N],
+                                                  conv[:, di + G * N:], D, db, n_short=ns))
+        t_norm = timeit(lambda: R.gated_rmsnorm(y, z, gw, 1e-5))
+        st_bytes = len(lens) * H * P * N * 4 * 2
+        print(json.dumps(dict(op="mamba2_" + label, conv_us=round(t_conv * 1e3, 1), scan_us=round(t_scan * 1e3, 1),
+                              gated_norm_us=round(t_norm * 1e3, 1),
+                              scan_state_gbs=round(st_bytes / t_scan / 1e6, 1),
+                              scan_us_per_token_step=round(t_scan * 1e3 / max(lens), 3))), flush=True)
+    if not engine_run:
+        return
+    from ..engine.engine import EngineConfig
+    from ..engine.params import SamplingParams
+    from ..llm import LLM
+
+    del state, conv_state
+    llm = LLM.from_preset("mamba2-2.7b", engine_config=EngineConfig(max_batch=64, max_model_len=2048, block_size=16,
+                                                                      max_num_batched_tokens=8192, num_blocks=64 * 132))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 50000, (1024,), generator=g).tolist() for _ in range(64)]
+    sp = SamplingParams(max_tokens=64, temperature=0.0, ignore_eos=True)
+    llm.generate(prompt_token_ids=prompts[:8], sampling_params=SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=sp)
+    torch.cuda.synchronize()
+    dt_s = time.perf_counter() - t0
+    n = sum(len(o.output) for o in outs)
+    print(json.dumps(dict(op="mamba2_2.7b_engine", requests=64, prompt=1024, new_tokens=n, seconds=round(dt_s, 3),
+                          output_tok_s=round(n / dt_s, 1), total_tok_s=round((n + 64 * 1024) / dt_s, 1),
+                          steps=llm.engine.stats["steps"])), flush=True)
+
+
+CASES = dict(mamba2=mamba2, qgemm_decode=qgemm_decode, qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
              attn_prefill=attn_prefill, decode_steps=decode_steps, kbench=kbench)
 
 if __name__ == "__main__":

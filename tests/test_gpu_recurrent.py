@@ -88,9 +88,9 @@ def _ragged(lens, n_slots):
     return torch.tensor(cu, dtype=torch.int32), slots, reset
 
 
-@pytest.mark.parametrize("C,K,stride_extra", [(320, 4, 72), (96, 3, 0), (1024 + 8, 2, 8)])
+@pytest.mark.parametrize("C,K,stride_extra", [(320, 4, 72), (96, 3, 0), (1024 + 8, 2, 8), (77, 4, 11), (75, 7, 0), (64, 8, 0)])
 def test_causal_conv_varlen(C, K, stride_extra):
-    lens = [1, 1, 1, 37, 5, 130]
+    lens = [1, 1, 1, 37, 5, 130, 2, 64]
     cu, slots, reset = _ragged(lens, 9)
     T = int(cu[-1])
     full = _bf(T, C + stride_extra)
@@ -104,9 +104,13 @@ def test_causal_conv_varlen(C, K, stride_extra):
     _close(st.cpu(), st2, rtol=1e-5, atol=1e-5)
 
 
-@pytest.mark.parametrize("H,P,N,G", [(8, 32, 32, 1), (4, 64, 128, 2), (6, 16, 80, 3), (2, 64, 256, 1)])
-def test_ssm_scan_varlen(H, P, N, G):
-    lens = [1, 1, 44, 1, 9]
+@pytest.mark.parametrize("n_short", [0, 3])
+@pytest.mark.parametrize("H,P,N,G", [(8, 32, 32, 1), (4, 64, 128, 2), (6, 16, 80, 3), (2, 64, 256, 1), (3, 40, 64, 1),
+                                     (2, 8, 16, 2), (4, 32, 30, 1)])
+def test_ssm_scan_varlen(H, P, N, G, n_short):
+    """Every kernel behind the entry point: float4 step kernel (short pieces), row-per-thread kernel
+    (N in 16/32/64/128, also with P not a multiple of the warp), generic warp-per-row kernel."""
+    lens = [1, 1, 1, 44, 131, 1, 9]
     cu, slots, reset = _ragged(lens, 7)
     T = int(cu[-1])
     conv = _bf(T, H * P + 2 * G * N, sc=0.5)
@@ -117,7 +121,7 @@ def test_ssm_scan_varlen(H, P, N, G):
     st = torch.randn(7, H, P, N, device=DEV) * 0.2
     st2 = st.clone().cpu()
     lim = (0.01, 0.8)
-    y = R.ssm_scan_varlen(st, slots.to(DEV), cu.to(DEV), reset.to(DEV), x, dt, A, Bm, Cm, D, db, True, lim)
+    y = R.ssm_scan_varlen(st, slots.to(DEV), cu.to(DEV), reset.to(DEV), x, dt, A, Bm, Cm, D, db, True, lim, n_short)
     yr = R.ssm_scan_varlen_ref(st2, slots, cu, reset, x.cpu(), dt.cpu(), A.cpu(), Bm.cpu(), Cm.cpu(), D.cpu(), db.cpu(),
                                True, lim)
     _close(y.cpu(), yr, atol=0.1)
