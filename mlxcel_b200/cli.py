@@ -208,6 +208,11 @@ def cmd_random_init(a):
     from .models.weights import random_weights
     from .ops import quant
     cfg = preset(a.preset)
+    if cfg.model_type == "mamba2":
+        from .models.mamba2 import mamba2_config_dict, random_mamba2_weights, save_mamba2_checkpoint
+        save_mamba2_checkpoint(a.out, mamba2_config_dict(cfg), random_mamba2_weights(cfg, seed=a.seed))
+        print("wrote", a.out)
+        return
     w = random_weights(cfg, seed=a.seed, dtype=torch.bfloat16)
     qd = None
     if a.quantize:

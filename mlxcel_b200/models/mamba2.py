@@ -117,6 +117,19 @@ def load_mamba2_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cp
                          lm_head=embed if head is None else head.to(device))
 
 
+def mamba2_config_dict(cfg: ModelConfig) -> dict:
+    """``config.json`` content (HF ``Mamba2Config`` keys) that :func:`ModelConfig.from_dict` reads back."""
+    d = mamba_dims(cfg)
+    lim = cfg.extra["mamba"].get("time_step_limit", (0.0, float("inf")))
+    out = dict(model_type="mamba2", vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+               num_hidden_layers=cfg.num_hidden_layers, num_heads=d["heads"], head_dim=d["P"], state_size=d["N"],
+               conv_kernel=d["K"], n_groups=d["G"], intermediate_size=d["d_inner"],
+               layer_norm_epsilon=cfg.rms_norm_eps, tie_word_embeddings=cfg.tie_word_embeddings)
+    if lim[1] != float("inf") or lim[0] != 0.0:
+        out["time_step_limit"] = [lim[0], min(lim[1], 3.0e38)]
+    return out
+
+
 def save_mamba2_checkpoint(path, cfg_dict: dict, w: Mamba2Weights) -> None:
     """Write ``config.json`` + ``model.safetensors`` with the HF tensor names (tests, conversions)."""
     import json

@@ -79,3 +79,18 @@ def test_mamba2_two_groups_and_checkpoint_round_trip(tmp_path):
     a = _engine(cfg, w).generate([prompt], sp)[0].output
     b = _engine(cfg2, w2).generate([prompt], sp)[0].output
     assert a == b and len(a) == 5
+
+
+def test_mamba2_cli_random_init_and_llm_front_end(tmp_path):
+    """`random-init tiny-mamba2` writes a checkpoint that the LLM front end loads and generates from."""
+    import argparse
+
+    from mlxcel_b200 import cli
+    from mlxcel_b200.llm import LLM
+
+    cli.cmd_random_init(argparse.Namespace(preset="tiny-mamba2", out=str(tmp_path), seed=0, quantize=None))
+    llm = LLM.from_pretrained(tmp_path, device="cpu",
+                              engine_config=EngineConfig(num_blocks=32, block_size=16, max_batch=4, max_model_len=128))
+    assert type(llm.model).__name__ == "Mamba2Model" and llm.engine.recurrent
+    outs = llm.generate(prompt_token_ids=[[1, 2, 3, 4, 5]], sampling_params=SamplingParams(max_tokens=4, ignore_eos=True))
+    assert len(outs[0].output) == 4
