@@ -213,6 +213,11 @@ def cmd_random_init(a):
         save_mamba2_checkpoint(a.out, mamba2_config_dict(cfg), random_mamba2_weights(cfg, seed=a.seed))
         print("wrote", a.out)
         return
+    if cfg.model_type == "nemotron_h":
+        from .models.hybrid import hybrid_config_dict, random_hybrid_weights, save_hybrid_checkpoint
+        save_hybrid_checkpoint(a.out, hybrid_config_dict(cfg), random_hybrid_weights(cfg, seed=a.seed), cfg)
+        print("wrote", a.out)
+        return
     w = random_weights(cfg, seed=a.seed, dtype=torch.bfloat16)
     qd = None
     if a.quantize:

@@ -343,6 +343,29 @@ def _mamba2(c: ModelConfig, raw: dict) -> None:
     c.intermediate_size = d_inner
 
 
+def _nemotron_h(c: ModelConfig, raw: dict) -> None:
+    """Hybrid Mamba2 / attention / MLP stack chosen per layer by ``hybrid_override_pattern``
+    (reference src/models/nemotron_h.rs). Attention has no positional encoding; the Mamba2 gated
+    norm is applied per B/C group; the MLP is ``down(relu(up(x))^2)``."""
+    hs = c.hidden_size
+    P = int(raw.get("mamba_head_dim", 64))
+    heads = int(raw.get("mamba_num_heads", raw.get("expand", 2) * hs // P))
+    G = int(raw.get("n_groups", 8))
+    lim = raw.get("time_step_limit") or (0.0, float("inf"))
+    c.extra["mamba"] = dict(d_inner=heads * P, head_dim=P, n_groups=G,
+                            d_state=int(raw.get("ssm_state_size", 128)), d_conv=int(raw.get("conv_kernel", 4)),
+                            time_step_limit=(float(lim[0]), float(lim[1])), norm_groups=G,
+                            use_conv_bias=bool(raw.get("use_conv_bias", True)))
+    pat = raw.get("hybrid_override_pattern")
+    if not pat:
+        raise ValueError("nemotron_h config needs hybrid_override_pattern")
+    c.extra["hybrid_pattern"] = str(pat)
+    c.num_hidden_layers = len(pat)
+    c.partial_rotary_factor = 0.0
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", False))
+    c.hidden_act = "relu2"
+
+
 FAMILIES = {
     "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _plain, "seed_oss": _plain,
     "helium": _plain, "internlm3": _plain, "exaone4": _qwen3, "hunyuan_v1_dense": _qwen3,
@@ -351,7 +374,7 @@ FAMILIES = {
     "mixtral": _mixtral, "phimoe": _mixtral, "olmoe": _qwen_moe,
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
-    "mamba2": _mamba2, "granite": _granite, "starcoder2": _plain, "stablelm": _plain, "cohere": _plain,
+    "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _plain, "stablelm": _plain, "cohere": _plain,
 }
 
 
@@ -404,6 +427,11 @@ def preset(name: str) -> ModelConfig:
         return ModelConfig.from_dict(dict(
             model_type="mamba2", num_hidden_layers=2, hidden_size=128, num_heads=8, head_dim=32,
             state_size=32, conv_kernel=4, n_groups=1, expand=2, vocab_size=1024, layer_norm_epsilon=1e-5))
+    if name == "tiny-nemotron-h":
+        return ModelConfig.from_dict(dict(
+            model_type="nemotron_h", hidden_size=128, hybrid_override_pattern="M-M*-M-", mamba_num_heads=8,
+            mamba_head_dim=32, ssm_state_size=32, conv_kernel=4, n_groups=2, intermediate_size=256,
+            num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=1024, layer_norm_epsilon=1e-5))
     if name == "mamba2-2.7b":
         return ModelConfig.from_dict(dict(
             model_type="mamba2", num_hidden_layers=64, hidden_size=2560, num_heads=80, head_dim=64,

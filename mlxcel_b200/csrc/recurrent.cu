@@ -472,17 +472,19 @@ ssm_scan_rows_kernel(float* __restrict__ state, const int* __restrict__ slots, c
 __global__ void __launch_bounds__(512)
 gated_rmsnorm_vec_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z, int z_stride,
                          const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, int dim,
-                         float eps) {
+                         int groups, float eps) {
   __shared__ float red[32];
   const size_t row = blockIdx.x;
+  const size_t tok = row / groups, grp = row - tok * groups;
+  y += row * dim, out += row * dim, z += tok * z_stride + grp * dim, weight += grp * dim;
   float v[2][8];
   float ssq = 0.f;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int i = (threadIdx.x + r * blockDim.x) * 8;
     if (i < dim) {
-      const uint4 yr = *reinterpret_cast<const uint4*>(y + row * dim + i);
-      const uint4 zr = *reinterpret_cast<const uint4*>(z + row * z_stride + i);
+      const uint4 yr = *reinterpret_cast<const uint4*>(y + i);
+      const uint4 zr = *reinterpret_cast<const uint4*>(z + i);
       const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&yr);
       const __nv_bfloat162* z2 = reinterpret_cast<const __nv_bfloat162*>(&zr);
 #pragma unroll
@@ -517,21 +519,25 @@ gated_rmsnorm_vec_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat1
         const float2 wv = __bfloat1622float2(w2[q]);
         o2[q] = __floats2bfloat162_rn(v[r][2 * q] * rs * wv.x, v[r][2 * q + 1] * rs * wv.y);
       }
-      *reinterpret_cast<uint4*>(out + row * dim + i) = o;
+      *reinterpret_cast<uint4*>(out + i) = o;
     }
   }
 }
 
-// out = RMSNorm(y * silu(z)) * weight over rows of `dim`; z rows at stride z_stride. One CTA per row.
+// out = RMSNorm(y * silu(z)) * weight; a token row holds `groups` independently normalised sub-rows
+// of `dim` elements (grouped variant of Nemotron-H; groups == 1: the whole row). z token rows at
+// stride z_stride. One CTA per sub-row.
 __global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
                                      int z_stride, const __nv_bfloat16* __restrict__ weight,
-                                     __nv_bfloat16* __restrict__ out, int dim, float eps) {
+                                     __nv_bfloat16* __restrict__ out, int dim, int groups, float eps) {
   __shared__ float red[32];
   const size_t row = blockIdx.x;
+  const size_t tok = row / groups, grp = row - tok * groups;
+  y += row * dim, out += row * dim, z += tok * z_stride + grp * dim, weight += grp * dim;
   float ssq = 0.f;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-    const float zv = __bfloat162float(z[row * z_stride + i]);
-    const float v = __bfloat162float(y[row * dim + i]) * (zv / (1.f + __expf(-zv)));
+    const float zv = __bfloat162float(z[i]);
+    const float v = __bfloat162float(y[i]) * (zv / (1.f + __expf(-zv)));
     ssq += v * v;
   }
   ssq = warp_sum(ssq);
@@ -545,9 +551,9 @@ __global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const 
   __syncthreads();
   const float r = red[0];
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-    const float zv = __bfloat162float(z[row * z_stride + i]);
-    const float v = __bfloat162float(y[row * dim + i]) * (zv / (1.f + __expf(-zv)));
-    out[row * dim + i] = __float2bfloat16(v * r * __bfloat162float(weight[i]));
+    const float zv = __bfloat162float(z[i]);
+    const float v = __bfloat162float(y[i]) * (zv / (1.f + __expf(-zv)));
+    out[i] = __float2bfloat16(v * r * __bfloat162float(weight[i]));
   }
 }
 
@@ -611,7 +617,7 @@ __global__ void bitlinear_kernel(const __nv_bfloat16* __restrict__ x, const uint
 }
 
 // ----------------------------------------------------------------------------- element-wise
-// mode 0: tanh-GELU; mode 1: xIELU with per-tensor alpha_p, alpha_n, beta, eps.
+// mode 0: tanh-GELU; mode 1: xIELU with per-tensor alpha_p, alpha_n, beta, eps; mode 2: relu(x)^2.
 __global__ void activation_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                   long long n, int mode, float ap, float an, float beta, float eps) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -620,6 +626,8 @@ __global__ void activation_kernel(const __nv_bfloat16* __restrict__ x, __nv_bflo
   float r;
   if (mode == 0) {
     r = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  } else if (mode == 2) {
+    r = v > 0.f ? v * v : 0.f;
   } else {
     r = v > 0.f ? ap * v * v + beta * v : an * (expm1f(fminf(v, eps)) - v) + beta * v;
   }
@@ -816,21 +824,24 @@ extern "C" int mx_ssm_scan_varlen(void* state, const void* slots, const void* cu
   return static_cast<int>(cudaGetLastError());
 }
 
+// rows token rows of groups x dim elements each (y, out contiguous; z token rows at z_stride).
 extern "C" int mx_gated_rmsnorm(const void* y, const void* z, int z_stride, const void* weight, void* out,
-                                int rows, int dim, float eps, void* stream) {
-  if (rows <= 0 || dim <= 0) return 0;
+                                int rows, int dim, int groups, float eps, void* stream) {
+  if (rows <= 0 || dim <= 0 || groups <= 0) return 0;
   const auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec = dim % 8 == 0 && z_stride % 8 == 0 && dim <= 8192 && aligned(y) && aligned(z) &&
                    aligned(weight) && aligned(out);
+  const long long blocks = static_cast<long long>(rows) * groups;
+  if (blocks > 0x7fffffffLL) return -1;
   if (vec) {
     const int threads = min(512, ((dim / 8 + 1) / 2 + 31) / 32 * 32);
-    gated_rmsnorm_vec_kernel<<<rows, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+    gated_rmsnorm_vec_kernel<<<static_cast<int>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z), z_stride,
-        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), dim, eps);
+        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), dim, groups, eps);
   } else {
-    gated_rmsnorm_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    gated_rmsnorm_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z), z_stride,
-        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), dim, eps);
+        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), dim, groups, eps);
   }
   return static_cast<int>(cudaGetLastError());
 }

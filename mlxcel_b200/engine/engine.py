@@ -89,7 +89,7 @@ class Engine:
         self.device = model.device
         self.is_cuda = self.device.type == "cuda"
         tp = model.comm.tp_size
-        nl = len(model.w.layers)
+        nl = getattr(model, "num_kv_layers", len(model.w.layers))
         self.recurrent = bool(getattr(model, "recurrent", False))
         if self.recurrent:
             # per-sequence recurrent state lives in the model, not in the block pool: a cached prefix has

@@ -22,10 +22,12 @@ class LLM:
         """``fold_norms``: the weights belong to this object alone, so the executor may fold the
         RMSNorm weights into the projections in place (deferred RMSNorm, see DecoderModel)."""
         self.cfg = cfg
-        if cfg.model_type == "mamba2":
+        if cfg.model_type in ("mamba2", "nemotron_h"):
+            from .models.hybrid import HybridModel
             from .models.mamba2 import Mamba2Model
-            self.model = Mamba2Model(cfg, weights, comm=comm,
-                                     max_seqs=2 * (engine_config.max_batch if engine_config else EngineConfig().max_batch))
+            cls = Mamba2Model if cfg.model_type == "mamba2" else HybridModel
+            self.model = cls(cfg, weights, comm=comm,
+                             max_seqs=2 * (engine_config.max_batch if engine_config else EngineConfig().max_batch))
         else:
             self.model = DecoderModel(cfg, weights, comm=comm,
                                       kv_bits=(engine_config.kv_bits if engine_config else 16),
@@ -41,6 +43,9 @@ class LLM:
         if cfg.model_type == "mamba2":
             from .models.mamba2 import random_mamba2_weights
             return LLM(cfg, random_mamba2_weights(cfg, seed=seed, dtype=dtype, device=device), engine_config, comm=comm)
+        if cfg.model_type == "nemotron_h":
+            from .models.hybrid import random_hybrid_weights
+            return LLM(cfg, random_hybrid_weights(cfg, seed=seed, dtype=dtype, device=device), engine_config, comm=comm)
         tp = comm.tp_size if comm is not None else 1
         rank = comm.tp_rank if comm is not None else 0
         w = random_weights(cfg, seed=seed, dtype=dtype, device=device, tp_rank=rank, tp_size=tp,
@@ -58,6 +63,10 @@ class LLM:
         if cfg.model_type == "mamba2":
             from .models.mamba2 import load_mamba2_weights
             return LLM(cfg, load_mamba2_weights(path, cfg, device=device), engine_config, comm=comm,
+                       tokenizer=load_tokenizer(path))
+        if cfg.model_type == "nemotron_h":
+            from .models.hybrid import load_hybrid_weights
+            return LLM(cfg, load_hybrid_weights(path, cfg, device=device), engine_config, comm=comm,
                        tokenizer=load_tokenizer(path))
         w = load_model_weights(path, cfg, device=device, comm=comm, dequantize=dequantize, surgery=surgery)
         tok = load_tokenizer(path)

@@ -1,0 +1,245 @@
+"""Hybrid state-space / attention language models (Nemotron-H layout) on the serving engine.
+
+A model is a flat list of pre-norm residual blocks, each with ONE mixer chosen by a pattern string
+(``hybrid_override_pattern``, e.g. ``"M-M-M-M*-M-M-M-M-"``):
+
+* ``M``  Mamba2 mixer (``models/mamba2.py``: per-sequence conv / SSM state slots, ragged kernels),
+* ``*``  grouped-query attention over the paged KV pool, without positional encoding,
+* ``-``  MLP  ``down(relu(up(x))^2)``  (or a gated SwiGLU MLP when the checkpoint has ``gate_proj``).
+
+Reference: src/models/nemotron_h.rs (block kinds and weight names ``backbone.layers.N.mixer.*``),
+src/models/granitemoehybrid.rs and src/models/falcon_h1.rs for the same idea with other layouts.
+
+Only the attention blocks own KV-pool layers (``num_kv_layers``); the engine sizes its pool from
+that. The executor composes the two existing ones: a :class:`Mamba2Model` for the state slots and
+the mixer, a :class:`DecoderModel` for the attention path (RoPE switched off through
+``partial_rotary_factor = 0``). Single GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import ops
+from ..config import ModelConfig
+from ..ops import recurrent as rops
+from .decoder import DecoderModel, LocalComm, StepBatch
+from .mamba2 import Mamba2LayerWeights, Mamba2Model, Mamba2Weights, mamba_dims
+from .weights import LayerWeights, ModelWeights
+
+
+@dataclass
+class HybridBlock:
+    kind: str                                   # "mamba2" | "attention" | "mlp"
+    norm: torch.Tensor
+    mamba: Mamba2LayerWeights | None = None
+    attn: LayerWeights | None = None            # wqkv / wo (+ biases)
+    up: torch.Tensor | None = None              # plain MLP [I, H]; gated MLP: [2I, H] (gate rows first)
+    down: torch.Tensor | None = None            # [H, I]
+    gated: bool = False
+
+
+@dataclass
+class HybridWeights:
+    embed: torch.Tensor
+    blocks: list
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor
+    layers: list = field(default_factory=list)  # the attention blocks' LayerWeights (= KV-pool layers)
+
+
+_KINDS = {"M": "mamba2", "*": "attention", "-": "mlp"}
+
+
+def block_kinds(cfg: ModelConfig) -> list[str]:
+    pat = cfg.extra["hybrid_pattern"]
+    if len(pat) != cfg.num_hidden_layers:
+        raise ValueError(f"hybrid pattern has {len(pat)} entries for {cfg.num_hidden_layers} layers")
+    try:
+        return [_KINDS[c] for c in pat]
+    except KeyError as e:
+        raise ValueError(f"unknown block kind {e.args[0]!r} in hybrid pattern {pat!r}") from None
+
+
+def random_hybrid_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.bfloat16, device="cpu", std: float = 0.02):
+    from .mamba2 import random_mamba2_weights
+
+    g = torch.Generator().manual_seed(seed + 1)
+    r = lambda *s: (torch.randn(*s, generator=g) * std).to(dtype).to(device)  # noqa: E731
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    kinds = block_kinds(cfg)
+    mw = random_mamba2_weights(cfg, seed=seed, dtype=dtype, device=device, std=std)   # one per layer; mamba ones are used
+    one = lambda: torch.ones(H, dtype=dtype, device=device)  # noqa: E731
+    blocks, attn_layers = [], []
+    for i, k in enumerate(kinds):
+        if k == "mamba2":
+            blocks.append(HybridBlock(k, one(), mamba=mw.layers[i]))
+        elif k == "attention":
+            lw = LayerWeights(ln1=one(), ln2=one(), wqkv=r((Hq + 2 * Hkv) * D, H), wo=r(H, Hq * D))
+            attn_layers.append(lw)
+            blocks.append(HybridBlock(k, lw.ln1, attn=lw))
+        else:
+            blocks.append(HybridBlock(k, one(), up=r(I, H), down=r(H, I)))
+    return HybridWeights(embed=mw.embed, blocks=blocks, final_norm=mw.final_norm, lm_head=mw.lm_head,
+                         layers=attn_layers)
+
+
+def load_hybrid_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
+    """Nemotron-H checkpoint names: ``backbone.layers.N.norm.weight`` and ``backbone.layers.N.mixer.*``
+    with ``in_proj / conv1d / A_log / D / dt_bias / norm / out_proj`` (Mamba2), ``q_proj / k_proj /
+    v_proj / o_proj`` (attention) or ``up_proj / down_proj`` (+ ``gate_proj``) (MLP). Quantized
+    projections are dequantised at load."""
+    from ..loading.checkpoint import TensorSource, _Getter
+
+    src = TensorSource(path)
+    g = _Getter(src, cfg, dtype, dequantize=True)
+    d = mamba_dims(cfg)
+    pre = "backbone." if any(k.startswith("backbone.") for k in src.keys()) else "model."
+
+    def need(t, name):
+        if t is None:
+            raise KeyError(f"{path}: missing tensor {name}")
+        return t.to(device)
+
+    blocks, attn_layers = [], []
+    for i, kind in enumerate(block_kinds(cfg)):
+        p = f"{pre}layers.{i}."
+        m = p + "mixer."
+        norm = need(g.vec(p + "norm.weight"), p + "norm.weight")
+        if kind == "mamba2":
+            cw = need(g.vec(m + "conv1d.weight"), m + "conv1d.weight")
+            cw = cw.reshape(d["conv_dim"], d["K"]) if cw.dim() == 2 or cw.shape[1] == 1 else cw.squeeze(-1)
+            cb = g.vec(m + "conv1d.bias")
+            lw = Mamba2LayerWeights(
+                norm=norm, in_proj=need(g.mat(m + "in_proj"), m + "in_proj"), conv_w=cw.float(),
+                conv_b=None if cb is None else cb.float().to(device),
+                dt_bias=need(g.vec(m + "dt_bias"), m + "dt_bias").float(),
+                A_log=need(g.vec(m + "A_log"), m + "A_log").float(), D=need(g.vec(m + "D"), m + "D").float(),
+                gnorm=need(g.vec(m + "norm.weight"), m + "norm.weight"),
+                out_proj=need(g.mat(m + "out_proj"), m + "out_proj"))
+            blocks.append(HybridBlock(kind, norm, mamba=lw))
+        elif kind == "attention":
+            q, k, v = (need(g.mat(m + n), m + n) for n in ("q_proj", "k_proj", "v_proj"))
+            bq, bk, bv = (g.vec(m + n + ".bias") for n in ("q_proj", "k_proj", "v_proj"))
+            bo = g.vec(m + "o_proj.bias")
+            lw = LayerWeights(ln1=norm, ln2=norm, wqkv=torch.cat([q, k, v], 0).contiguous(),
+                              wo=need(g.mat(m + "o_proj"), m + "o_proj"),
+                              bqkv=None if bq is None else torch.cat([bq, bk, bv]).to(device),
+                              bo=None if bo is None else bo.to(device))
+            attn_layers.append(lw)
+            blocks.append(HybridBlock(kind, norm, attn=lw))
+        else:
+            up = need(g.mat(m + "up_proj"), m + "up_proj")
+            gate = g.mat(m + "gate_proj")
+            blocks.append(HybridBlock(kind, norm, up=up if gate is None else torch.cat([gate.to(device), up], 0).contiguous(),
+                                      down=need(g.mat(m + "down_proj"), m + "down_proj"), gated=gate is not None))
+    ename = pre + ("embeddings" if src.has(pre + "embeddings.weight") else "embed_tokens")
+    embed = need(g.mat(ename), ename)
+    head = g.mat("lm_head") if src.has("lm_head.weight") else None
+    return HybridWeights(embed=embed, blocks=blocks,
+                         final_norm=need(g.vec(pre + "norm_f.weight"), pre + "norm_f.weight"),
+                         lm_head=embed if head is None else head.to(device), layers=attn_layers)
+
+
+def hybrid_config_dict(cfg: ModelConfig) -> dict:
+    d = mamba_dims(cfg)
+    return dict(model_type="nemotron_h", vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+                num_hidden_layers=cfg.num_hidden_layers, hybrid_override_pattern=cfg.extra["hybrid_pattern"],
+                mamba_num_heads=d["heads"], mamba_head_dim=d["P"], ssm_state_size=d["N"], conv_kernel=d["K"],
+                n_groups=d["G"], intermediate_size=cfg.intermediate_size,
+                num_attention_heads=cfg.num_attention_heads, num_key_value_heads=cfg.num_key_value_heads,
+                head_dim=cfg.head_dim, layer_norm_epsilon=cfg.rms_norm_eps,
+                tie_word_embeddings=cfg.tie_word_embeddings)
+
+
+def save_hybrid_checkpoint(path, cfg_dict: dict, w: HybridWeights, cfg: ModelConfig) -> None:
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import save_file
+
+    path = Path(path)
+    path.mkdir(parents=True, exist_ok=True)
+    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    t = {"backbone.embeddings.weight": w.embed, "backbone.norm_f.weight": w.final_norm}
+    if w.lm_head is not w.embed:
+        t["lm_head.weight"] = w.lm_head
+    for i, blk in enumerate(w.blocks):
+        p = f"backbone.layers.{i}."
+        m = p + "mixer."
+        t[p + "norm.weight"] = blk.norm
+        if blk.kind == "mamba2":
+            lw = blk.mamba
+            t.update({m + "in_proj.weight": lw.in_proj, m + "conv1d.weight": lw.conv_w.unsqueeze(1),
+                      m + "dt_bias": lw.dt_bias, m + "A_log": lw.A_log, m + "D": lw.D, m + "norm.weight": lw.gnorm,
+                      m + "out_proj.weight": lw.out_proj})
+            if lw.conv_b is not None:
+                t[m + "conv1d.bias"] = lw.conv_b
+        elif blk.kind == "attention":
+            q, k, v = blk.attn.wqkv.split([Hq * D, Hkv * D, Hkv * D], 0)
+            t.update({m + "q_proj.weight": q, m + "k_proj.weight": k, m + "v_proj.weight": v,
+                      m + "o_proj.weight": blk.attn.wo})
+        else:
+            if blk.gated:
+                gate, up = blk.up.chunk(2, 0)
+                t[m + "gate_proj.weight"] = gate
+            else:
+                up = blk.up
+            t.update({m + "up_proj.weight": up, m + "down_proj.weight": blk.down})
+    save_file({k: v.detach().cpu().contiguous() for k, v in t.items()}, str(path / "model.safetensors"))
+    (path / "config.json").write_text(json.dumps(cfg_dict))
+
+
+class HybridModel:
+    """Engine-facing executor (``forward`` / ``forward_hidden`` / ``logits`` / ``release_seq``)."""
+
+    recurrent = True
+
+    def __init__(self, cfg: ModelConfig, weights: HybridWeights, max_seqs: int = 256, comm=None, kv_bits: int = 16):
+        self.cfg, self.w = cfg, weights
+        self.comm = comm or LocalComm()
+        assert self.comm.tp_size == 1, "the hybrid executor is single-GPU"
+        self.device = weights.final_norm.device
+        mamba_layers = [b.mamba for b in weights.blocks if b.kind == "mamba2"]
+        self.ssm = Mamba2Model(cfg, Mamba2Weights(weights.embed, mamba_layers, weights.final_norm, weights.lm_head),
+                               max_seqs=max_seqs, comm=self.comm)
+        self.attn = DecoderModel(cfg, ModelWeights(weights.embed, weights.layers, weights.final_norm, weights.lm_head),
+                                 comm=self.comm, kv_bits=kv_bits)
+        self.Hq, self.Hkv, self.D = self.attn.Hq, self.attn.Hkv, self.attn.D
+        self.num_kv_layers = len(weights.layers)
+        self.layer_range = range(cfg.num_hidden_layers)
+        self.I = cfg.intermediate_size
+
+    def release_seq(self, seq_id: int) -> None:
+        self.ssm.release_seq(seq_id)
+
+    @torch.inference_mode()
+    def forward_hidden(self, b: StepBatch, kv_layers=None, hidden_in: torch.Tensor | None = None) -> torch.Tensor:
+        cfg = self.cfg
+        eps = cfg.rms_norm_eps
+        pieces = self.ssm.pieces(b)
+        h = hidden_in if hidden_in is not None else ops.embedding(b.token_ids, self.w.embed, cfg.embed_scale)
+        mi = ai = 0
+        for blk in self.w.blocks:
+            x = ops.rmsnorm(h, blk.norm, eps, 0.0)
+            if blk.kind == "mamba2":
+                y = self.ssm._mixer(mi, blk.mamba, x, pieces)
+                h = ops.linear(y, blk.mamba.out_proj, residual=h)
+                mi += 1
+            elif blk.kind == "attention":
+                a = self.attn._attention(ai, blk.attn, x, b, kv_layers[ai])
+                h = ops.linear(a, blk.attn.wo, bias=blk.attn.bo, residual=h)
+                ai += 1
+            elif blk.gated:
+                h = ops.linear(ops.glu_linear(x, blk.up, blk.up.shape[0] // 2, "silu"), blk.down, residual=h)
+            else:
+                h = ops.linear(rops.relu2(ops.linear(x, blk.up)), blk.down, residual=h)
+        return h
+
+    def logits(self, h: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:
+        return self.ssm.logits(h, rows)
+
+    def forward(self, b: StepBatch, kv_layers=None) -> torch.Tensor:
+        return self.logits(self.forward_hidden(b, kv_layers), b.logits_rows)

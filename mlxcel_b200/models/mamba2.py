@@ -169,7 +169,7 @@ class Mamba2Model:
         self.Hq = self.Hkv = 1                 # (attention geometry the engine asks for; unused)
         self.D = cfg.head_dim
         self.layer_range = range(cfg.num_hidden_layers)
-        d, L = self.d, cfg.num_hidden_layers
+        d, L = self.d, len(weights.layers)
         self.conv_state = torch.zeros(L, max_seqs, d["K"] - 1, d["conv_dim"], dtype=torch.float32, device=self.device)
         self.ssm_state = torch.zeros(L, max_seqs, d["heads"], d["P"], d["N"], dtype=torch.float32, device=self.device)
         self.slot_of: dict[int, int] = {}
@@ -181,6 +181,7 @@ class Mamba2Model:
             lw.D, lw.dt_bias = lw.D.float().contiguous(), lw.dt_bias.float().contiguous()
         lim = cfg.extra["mamba"].get("time_step_limit", (0.0, float("inf")))
         self.dt_limit = (float(lim[0]), float(lim[1]))
+        self.norm_groups = int(cfg.extra["mamba"].get("norm_groups", 1))   # Nemotron-H: one norm per B/C group
 
     # ------------------------------------------------------------------ state slots
     def _slot(self, seq_id: int, resets: bool) -> int:
@@ -214,12 +215,12 @@ class Mamba2Model:
         conv = rops.causal_conv_varlen(xBC, self.conv_state[li], slots, cu, reset, lw.conv_w, lw.conv_b, True, max_len)
         y = rops.ssm_scan_varlen(self.ssm_state[li], slots, cu, reset, conv[:, :di], dt, self.A[li],
                                  conv[:, di:di + GN], conv[:, di + GN:], lw.D, lw.dt_bias, True, self.dt_limit, nd)
-        return rops.gated_rmsnorm(y, z, lw.gnorm, self.cfg.rms_norm_eps)
+        return rops.gated_rmsnorm(y, z, lw.gnorm, self.cfg.rms_norm_eps, self.norm_groups)
 
-    # ------------------------------------------------------------------ forward
-    @torch.inference_mode()
-    def forward_hidden(self, b: StepBatch, kv_layers=None, hidden_in: torch.Tensor | None = None) -> torch.Tensor:
-        cfg = self.cfg
+    def pieces(self, b: StepBatch):
+        """Per-step description of the ragged batch for the mixer kernels: (slots, cu, reset) as int32
+        device tensors (one host-to-device copy), the number of decode rows and the longest piece.
+        Allocates a state slot for every new sequence."""
         ids = getattr(b, "seq_ids", None)
         if ids is None:
             raise RuntimeError("recurrent models need StepBatch.seq_ids (the engine fills them in)")
@@ -233,7 +234,13 @@ class Mamba2Model:
         slots = [self._slot(i, bool(r)) for i, r in zip(ids, reset)]
         S = len(slots)
         meta = torch.tensor(slots + reset + cu, dtype=torch.int32).to(self.device, non_blocking=True)
-        pieces = (meta[:S], meta[2 * S:], meta[S:2 * S], nd, max(1 if nd else 0, b.pf_max_q_len))
+        return (meta[:S], meta[2 * S:], meta[S:2 * S], nd, max(1 if nd else 0, b.pf_max_q_len))
+
+    # ------------------------------------------------------------------ forward
+    @torch.inference_mode()
+    def forward_hidden(self, b: StepBatch, kv_layers=None, hidden_in: torch.Tensor | None = None) -> torch.Tensor:
+        cfg = self.cfg
+        pieces = self.pieces(b)
         h = hidden_in if hidden_in is not None else ops.embedding(b.token_ids, self.w.embed, cfg.embed_scale)
         for li, lw in enumerate(self.w.layers):
             x = ops.rmsnorm(h, lw.norm, cfg.rms_norm_eps, 0.0)

@@ -16,7 +16,7 @@ _SIG = {
     "mx_selective_scan": [_vp] * 8 + [_i] * 5 + [_vp],
     "mx_causal_conv_varlen": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "mx_ssm_scan_varlen": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp] + [_i] * 7 + [_f, _f, _vp],
-    "mx_gated_rmsnorm": [_vp, _vp, _i, _vp, _vp, _i, _i, _f, _vp],
+    "mx_gated_rmsnorm": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _vp],
     "mx_gated_delta_update": [_vp] * 7 + [_i, _i, _i, _f, _vp],
     "mx_bitlinear": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "mx_activation": [_vp, _vp, _ll, _i, _f, _f, _f, _f, _vp],
@@ -184,16 +184,18 @@ def ssm_scan_varlen(state, slots, cu, reset, x, dt, A, Bm, Cm, D=None, dt_bias=N
     return y
 
 
-def gated_rmsnorm(y, z, weight, eps: float):
-    """RMSNorm(y * silu(z)) * weight; z may be a column slice with a row stride."""
+def gated_rmsnorm(y, z, weight, eps: float, groups: int = 1):
+    """RMSNorm(y * silu(z)) * weight, normalised over each of ``groups`` equal slices of a row
+    (groups == 1: the whole row); z may be a column slice with a row stride."""
     if not y.is_cuda:
-        v = y.float() * F.silu(z.float())
-        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(y.dtype)
+        v = (y.float() * F.silu(z.float())).reshape(y.shape[0], groups, -1)
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+        return (v.reshape(y.shape[0], -1) * weight.float()).to(y.dtype)
     rows, dim = y.shape
-    assert z.stride(1) == 1 and y.is_contiguous()
+    assert z.stride(1) == 1 and y.is_contiguous() and dim % groups == 0
     out = torch.empty_like(y)
-    _call("mx_gated_rmsnorm", y.data_ptr(), z.data_ptr(), z.stride(0), weight.data_ptr(), out.data_ptr(), rows, dim,
-          float(eps), _lib.stream())
+    _call("mx_gated_rmsnorm", y.data_ptr(), z.data_ptr(), z.stride(0), weight.data_ptr(), out.data_ptr(), rows,
+          dim // groups, int(groups), float(eps), _lib.stream())
     return out
 
 
@@ -244,6 +246,16 @@ def gelu_tanh(x):
         return F.gelu(x.float(), approximate="tanh").to(x.dtype)
     y = torch.empty_like(x)
     _call("mx_activation", x.data_ptr(), y.data_ptr(), x.numel(), 0, 0.0, 0.0, 0.0, 0.0, _lib.stream())
+    return y
+
+
+def relu2(x):
+    """relu(x)^2 (the MLP activation of Nemotron-H)."""
+    if not x.is_cuda:
+        return torch.relu(x.float()).square().to(x.dtype)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    _call("mx_activation", x.data_ptr(), y.data_ptr(), x.numel(), 2, 0.0, 0.0, 0.0, 0.0, _lib.stream())
     return y
 
 

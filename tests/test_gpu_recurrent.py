@@ -128,13 +128,62 @@ def test_ssm_scan_varlen(H, P, N, G, n_short):
     _close(st.cpu(), st2, rtol=2e-3, atol=2e-3)
 
 
-def test_gated_rmsnorm():
-    y, full = _bf(77, 640), _bf(77, 1000)
-    z = full[:, 40:680]
-    w = _bf(640, sc=0.2) + 1
-    got = R.gated_rmsnorm(y, z, w, 1e-5)
-    want = R.gated_rmsnorm(y.cpu().float(), z.cpu().float(), w.cpu().float(), 1e-5)
+@pytest.mark.parametrize("dim,groups,off", [(640, 1, 40), (640, 5, 40), (644, 2, 3), (8192, 1, 0)])
+def test_gated_rmsnorm(dim, groups, off):
+    y, full = _bf(77, dim), _bf(77, dim + 360)
+    z = full[:, off:off + dim]
+    w = _bf(dim, sc=0.2) + 1
+    got = R.gated_rmsnorm(y, z, w, 1e-5, groups)
+    want = R.gated_rmsnorm(y.cpu().float(), z.cpu().float(), w.cpu().float(), 1e-5, groups)
     _close(got.cpu(), want, atol=3e-2)
+
+
+def test_relu2():
+    x = _bf(33, 257)
+    _close(R.relu2(x).cpu(), torch.relu(x.float()).square().cpu(), atol=2e-2)
+
+
+def test_tiny_nemotron_h_engine_gpu_matches_cpu():
+    """Hybrid Mamba2 / attention / MLP stack: bf16 GPU kernels against the fp32 CPU path."""
+    import copy
+    from mlxcel_b200.config import preset
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.models.hybrid import HybridModel, random_hybrid_weights
+
+    cfg = preset("tiny-nemotron-h")
+    w32 = random_hybrid_weights(cfg, seed=4, dtype=torch.float32, std=0.08)
+    w16 = copy.deepcopy(w32)
+
+    def conv(obj):
+        for k, v in vars(obj).items():
+            if isinstance(v, torch.Tensor):
+                keep32 = k in ("conv_w", "conv_b", "dt_bias", "A_log", "D")
+                setattr(obj, k, (v if keep32 else v.to(torch.bfloat16)).to(DEV))
+
+    conv(w16)
+    for blk in w16.blocks:
+        conv(blk)
+        for sub in (blk.mamba, blk.attn):
+            if sub is not None:
+                conv(sub)
+    w16.layers = [b.attn for b in w16.blocks if b.kind == "attention"]
+    w16.lm_head = w16.embed
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (45, 9)]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True, logprobs=1)
+    outs = {}
+    for name, w, dev in (("cpu", w32, "cpu"), ("gpu", w16, DEV)):
+        eng = Engine(HybridModel(cfg, w, max_seqs=8), cfg,
+                     EngineConfig(num_blocks=64, block_size=16, max_batch=8, max_model_len=256, max_num_batched_tokens=32))
+        outs[name] = eng.generate(prompts, sp)
+        assert not eng.model.ssm.slot_of
+    for a, b in zip(outs["cpu"], outs["gpu"]):
+        assert len(b.output) == 6
+        assert a.output[0] == b.output[0]          # first token from the same prompt: bf16 noise must not flip it
+    from mlxcel_b200.ops import _lib
+    torch.cuda.synchronize()
+    assert _lib.read_status(torch.device(DEV)) == 0
 
 
 def test_tiny_mamba2_engine_gpu_matches_cpu():
