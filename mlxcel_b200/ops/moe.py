@@ -110,9 +110,10 @@ def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_o
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up, w_down, inter: int,
                 act: str, b_gate_up=None, b_down=None, e_begin: int = 0, residual=None,
-                alpha: float = 1.702, limit: float = 7.0) -> torch.Tensor:
+                alpha: float = 1.702, limit: float = 7.0, out: torch.Tensor | None = None) -> torch.Tensor:
     """Weighted sum over the LOCAL experts [e_begin, e_begin + E_local) of their gated MLPs,
-    plus ``residual`` when given. Returns bf16 [T, H]."""
+    plus ``residual`` when given. Returns bf16 [T, H] (written into ``out`` when given; rows whose
+    experts are all elsewhere come out as the residual, or zero)."""
     T, H = x.shape
     k = ids.shape[1]
     El = w_gate_up.shape[0]
@@ -126,6 +127,9 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up
         o = moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up, b_down, e_begin, alpha, limit)
         if residual is not None:
             o = o + residual.float()
+        if out is not None:
+            out.copy_(o.to(out.dtype))
+            return out
         return o.to(x.dtype)
     dev = x.device
     lib = _lib.load()
@@ -145,7 +149,9 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up
     _lib.count_launch(2)
     a = grouped_linear(xs, w_gate_up, offsets, inter, b_gate_up, act, alpha, limit)
     y = grouped_linear(a, w_down, offsets, w_down.shape[1], b_down, None)
-    out = torch.empty(T, w_down.shape[1], dtype=x.dtype, device=dev)
+    if out is None:
+        out = torch.empty(T, w_down.shape[1], dtype=x.dtype, device=dev)
+    assert out.shape == (T, w_down.shape[1]) and out.is_contiguous() and out.dtype == x.dtype
     inv = torch.empty(pairs, dtype=torch.int32, device=dev)
     rc = lib.mx_moe_combine_n(y.data_ptr(), sorted_pair.data_ptr(), total.data_ptr(), inv.data_ptr(),
                               wts.data_ptr(), out.data_ptr(), _lib.ptr(residual), T, k,

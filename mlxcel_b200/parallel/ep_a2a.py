@@ -1,0 +1,166 @@
+"""Expert-parallel MoE with all-to-all dispatch / combine over peer memory (token-sharded ranks).
+
+Every rank brings its OWN tokens; experts are sharded (expert ``e`` on rank ``e // experts_per_rank``).
+``EpAllToAll.moe`` runs one layer: dispatch kernel (permutation fused with the NVLink transfer: rows
+are stored straight into the owner's receive area), grouped expert GEMMs over the received rows,
+combine kernel (weighted sum fused with the transfer: output rows are loaded straight from the
+owner's memory). Kernels and protocol: ``csrc/ep_a2a.cu``. Reference: the expert-parallel path of
+src/distributed around ``SwitchGLU`` (src/models/switch_layers.rs:98-220).
+
+The symmetric buffer of one rank holds, at the same offsets on every rank::
+
+    recv  [world * cap, H] bf16    rows received, source s in [s * cap, (s + 1) * cap)
+    ret   [world * cap, H] bf16    expert outputs of those rows (read by the sources)
+    meta  [world * cap]    int32   expert id per received row
+    count [world] int32, dflag [world] uint32, cflag [world] uint32
+
+``cap`` bounds the rows one source may send to one destination (worst case ``T_max * k``).
+
+``EpAllToAll.emulated`` builds ``world`` instances over plain buffers of ONE device. Their stages can
+then be run rank after rank in protocol order (all dispatches, all expert stages, all combines), so
+that every flag is already set when a kernel looks at it: this is how the single-GPU test checks
+the index arithmetic without kernels that wait on one another.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import _lib
+from ..ops import moe as moe_ops
+
+_MAX_RANKS = 8
+
+
+class _EpCall(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_int) for n in ("rank", "world", "T", "k", "H", "experts_per_rank", "cap")]
+                + [("epoch", ctypes.c_uint)]
+                + [(n, ctypes.c_ulonglong) for n in ("status", "x", "ids", "wts", "residual", "out", "cnt", "ticket",
+                                                     "route", "ids_eff", "meta", "count", "dflag", "cflag")]
+                + [(n, ctypes.c_ulonglong * _MAX_RANKS) for n in ("recv_peer", "meta_peer", "count_peer",
+                                                                  "dflag_peer", "cflag_peer", "ret_peer")])
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class EpAllToAll:
+    @staticmethod
+    def layout(world: int, hidden: int, cap: int) -> dict:
+        rows = world * cap
+        off, out = 0, {}
+        for name, nbytes in (("recv", rows * hidden * 2), ("ret", rows * hidden * 2), ("meta", rows * 4),
+                             ("count", world * 4), ("dflag", world * 4), ("cflag", world * 4)):
+            out[name] = off
+            off += _align(nbytes)
+        out["bytes"] = off
+        return out
+
+    @staticmethod
+    def required_bytes(world: int, hidden: int, cap: int) -> int:
+        return EpAllToAll.layout(world, hidden, cap)["bytes"]
+
+    def __init__(self, rank: int, world: int, peer_bases: list[int], local: torch.Tensor, hidden: int, cap: int,
+                 experts_per_rank: int, max_tokens: int, k: int):
+        """``local``: this rank's symmetric buffer as a uint8 tensor (at ``peer_bases[rank]``), zeroed."""
+        if world > _MAX_RANKS:
+            raise ValueError(f"at most {_MAX_RANKS} ranks")
+        if hidden % 8:
+            raise ValueError("hidden size must be a multiple of 8")
+        self.rank, self.world, self.H, self.cap, self.epr = rank, world, hidden, cap, experts_per_rank
+        self.max_tokens, self.k = max_tokens, k
+        self.lay = EpAllToAll.layout(world, hidden, cap)
+        assert local.numel() >= self.lay["bytes"] and local.data_ptr() == peer_bases[rank]
+        self.local, self.bases = local, list(peer_bases)
+        dev = local.device
+        rows = world * cap
+        self.recv = local[self.lay["recv"]:self.lay["recv"] + rows * hidden * 2].view(torch.bfloat16).view(rows, hidden)
+        self.ret = local[self.lay["ret"]:self.lay["ret"] + rows * hidden * 2].view(torch.bfloat16).view(rows, hidden)
+        self.cnt = torch.zeros(world + 1, dtype=torch.int32, device=dev)          # [world] counters + ticket
+        self.route = torch.full((max_tokens * k,), -1, dtype=torch.int32, device=dev)
+        self.ids_eff = torch.full((rows, 1), -1, dtype=torch.int32, device=dev)
+        self.ones = torch.ones(rows, 1, dtype=torch.float32, device=dev)
+        self.epoch = 0
+        self._T = 0
+
+    # ------------------------------------------------------------------ constructors
+    @staticmethod
+    def from_heap(heap, hidden: int, cap: int, experts_per_rank: int, max_tokens: int, k: int) -> "EpAllToAll":
+        """Carve the regions out of a :class:`~mlxcel_b200.parallel.symm.SymmetricHeap` (collective)."""
+        nbytes = EpAllToAll.required_bytes(heap.world, hidden, cap)
+        off = heap.alloc(nbytes)
+        local = heap.buf[off:off + nbytes]
+        local.zero_()
+        torch.cuda.synchronize(heap.device)
+        import torch.distributed as dist
+        dist.barrier(group=heap.group)
+        return EpAllToAll(heap.rank, heap.world, [b + off for b in heap.peer_base], local, hidden, cap,
+                          experts_per_rank, max_tokens, k)
+
+    @staticmethod
+    def emulated(world: int, device, hidden: int, cap: int, experts_per_rank: int, max_tokens: int, k: int):
+        nbytes = EpAllToAll.required_bytes(world, hidden, cap)
+        bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(world)]
+        bases = [b.data_ptr() for b in bufs]
+        return [EpAllToAll(r, world, bases, bufs[r], hidden, cap, experts_per_rank, max_tokens, k)
+                for r in range(world)]
+
+    # ------------------------------------------------------------------ stages
+    def _call(self, stage: int, **kw) -> None:
+        c = _EpCall()
+        c.rank, c.world, c.T, c.k, c.H = self.rank, self.world, kw.get("T", self._T), self.k, self.H
+        c.experts_per_rank, c.cap, c.epoch = self.epr, self.cap, self.epoch
+        c.status = _lib.workspace(self.local.device).data_ptr()
+        for name in ("x", "ids", "wts", "residual", "out"):
+            t = kw.get(name)
+            setattr(c, name, 0 if t is None else t.data_ptr())
+        c.cnt, c.ticket = self.cnt.data_ptr(), self.cnt.data_ptr() + 4 * self.world
+        c.route, c.ids_eff = self.route.data_ptr(), self.ids_eff.data_ptr()
+        me = self.bases[self.rank]
+        c.meta, c.count = me + self.lay["meta"], me + self.lay["count"]
+        c.dflag, c.cflag = me + self.lay["dflag"], me + self.lay["cflag"]
+        for r in range(self.world):
+            b = self.bases[r]
+            c.recv_peer[r], c.ret_peer[r] = b + self.lay["recv"], b + self.lay["ret"]
+            c.meta_peer[r], c.count_peer[r] = b + self.lay["meta"], b + self.lay["count"]
+            c.dflag_peer[r], c.cflag_peer[r] = b + self.lay["dflag"], b + self.lay["cflag"]
+        fn = _lib.load().mx_ep_a2a
+        fn.argtypes, fn.restype = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p], ctypes.c_int
+        rc = fn(ctypes.byref(c), stage, _lib.stream())
+        _lib.count_launch()
+        _lib.check(rc, f"mx_ep_a2a stage {stage}")
+
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor) -> None:
+        """Send every (token, k) row of ``x`` [T, H] to the rank that owns expert ``ids[t, k]``."""
+        T, k = ids.shape
+        if k != self.k or T > self.max_tokens or x.shape != (T, self.H):
+            raise ValueError("dispatch shape does not match the buffers")
+        assert x.dtype == torch.bfloat16 and ids.dtype == torch.int32 and x.is_contiguous() and ids.is_contiguous()
+        self.epoch += 1
+        self._T = T
+        self._call(0, x=x, ids=ids, T=T)
+
+    def expert_stage(self, w_gate_up, w_down, inter: int, act: str, b_gate_up=None, b_down=None,
+                     alpha: float = 1.702, limit: float = 7.0) -> None:
+        """Wait for every source's rows, run this rank's experts over them, publish the outputs."""
+        self._call(1)
+        moe_ops.moe_experts(self.recv, self.ids_eff, self.ones, w_gate_up, w_down, inter, act, b_gate_up, b_down,
+                            e_begin=self.rank * self.epr, alpha=alpha, limit=limit, out=self.ret)
+        self._call(2)
+
+    def combine(self, wts: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """out[t] = residual[t] + sum_k wts[t, k] * expert output of row (t, k), read from the owners."""
+        T = self._T
+        assert wts.shape == (T, self.k) and wts.dtype == torch.float32 and wts.is_contiguous()
+        out = torch.empty(T, self.H, dtype=torch.bfloat16, device=self.local.device)
+        self._call(3, wts=wts, residual=residual, out=out, T=T)
+        return out
+
+    def moe(self, x, ids, wts, w_gate_up, w_down, inter: int, act: str, b_gate_up=None, b_down=None,
+            residual=None, alpha: float = 1.702, limit: float = 7.0) -> torch.Tensor:
+        """One expert-parallel MoE layer (collective over the ranks of the heap)."""
+        self.dispatch(x, ids)
+        self.expert_stage(w_gate_up, w_down, inter, act, b_gate_up, b_down, alpha, limit)
+        return self.combine(wts, residual)

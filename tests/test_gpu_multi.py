@@ -39,8 +39,8 @@ def _run(world: int, body: str, timeout: int = 600) -> str:
             print("MULTI_OK")
         dist.destroy_process_group()
     """)
-    path = os.path.join(ROOT, "gpurun_out", f"_multi_{os.getpid()}.py")
-    os.makedirs(os.path.dirname(path), exist_ok=True)
+    import tempfile
+    path = os.path.join(tempfile.mkdtemp(prefix="mlxcel_multi_"), "ranks.py")
     with open(path, "w") as f:
         f.write(script)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", MLXCEL_B200_REQUIRE_FUSED="1")
@@ -145,4 +145,34 @@ def test_tp_engine_fused_matches_nccl_and_single_gpu():
         agree = lambda a, b: sum(x == y for sa, sb in zip(a, b) for x, y in zip(sa, sb)) / sum(map(len, a))
         assert all(a[0] == b[0] for a, b in zip(single, outs["fused"])), (single, outs)
         assert agree(single, outs["fused"]) >= 0.6 and agree(single, outs["nccl"]) >= 0.6, (single, outs)
+    """)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_ep_all_to_all_moe_matches_local_reference():
+    """Token-sharded expert parallelism: dispatch / combine kernels over peer memory, three layers
+    back to back on the same buffers, every rank with its own token count."""
+    _run(_world(), """
+        from mlxcel_b200.ops import moe as moe_ops
+        from mlxcel_b200.parallel.symm import SymmetricHeap
+        from mlxcel_b200.parallel.ep_a2a import EpAllToAll
+        E, k, H, I, Tmax = 16, 2, 512, 256, 96
+        epr = E // world
+        cap = Tmax * k
+        heap = SymmetricHeap(dist.group.WORLD, dev, EpAllToAll.required_bytes(world, H, cap) + (4 << 20))
+        ep = EpAllToAll.from_heap(heap, H, cap, epr, Tmax, k)
+        g = torch.Generator().manual_seed(7)                      # same expert weights on every rank
+        wgu = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        wd = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        lo, hi = rank * epr, (rank + 1) * epr
+        gl = torch.Generator().manual_seed(100 + rank)            # own tokens
+        T = [96, 5, 33, 64, 1, 77, 18, 50][rank]
+        for layer in range(3):
+            x = torch.randn(T, H, generator=gl).to(torch.bfloat16).to(dev)
+            res = torch.randn(T, H, generator=gl).to(torch.bfloat16).to(dev)
+            ids, wts = moe_ops.route(torch.randn(T, E, generator=gl).to(torch.bfloat16).to(dev), k, "topk_softmax", True)
+            got = ep.moe(x, ids, wts, wgu[lo:hi].contiguous(), wd[lo:hi].contiguous(), I, "silu", residual=res)
+            want = moe_ops.moe_ref(x, ids, wts, wgu, wd, I, "silu") + res.float()
+            err = (got.float() - want).abs().max().item()
+            assert err < 0.06, (rank, layer, err)
     """)
