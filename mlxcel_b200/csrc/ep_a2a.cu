@@ -37,7 +37,9 @@ constexpr int kErrEpOverflow = 203;
 
 struct EpParams {
   int rank, world, T, k, H, experts_per_rank, cap;
-  uint32_t epoch;
+  uint32_t* epoch;               // local word: number of the current layer call; the dispatch kernel
+                                 // advances it, the later stages read it (so a captured CUDA graph
+                                 // replays with fresh flag values)
   int* status;
   // local tensors
   const __nv_bfloat16* x;        // [T, H]
@@ -84,16 +86,22 @@ __device__ __forceinline__ bool ep_flag_wait(const uint32_t* addr, uint32_t targ
   }
 }
 
-// One warp per (token, k) row, grid-strided.
+// A CTA takes kEpRowsPerCta (token, k) rows at a time: its first threads draw the slots, then all
+// threads copy the rows as one flat range of 16-byte words (independent loads, peer stores that
+// nobody waits for).
+constexpr int kEpRowsPerCta = 8;
+
 __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams p) {
-  const int lane = threadIdx.x & 31;
-  const int warps = (gridDim.x * kEpThreads) >> 5;
+  __shared__ int s_dst[kEpRowsPerCta], s_slot[kEpRowsPerCta];
   const int vec = p.H >> 3;                       // 16-byte words per row
-  for (int e = (blockIdx.x * kEpThreads + threadIdx.x) >> 5; e < p.T * p.k; e += warps) {
-    int dst = 0, slot = 0, expert = 0;
-    if (lane == 0) {
-      expert = p.ids[e];
-      dst = expert / p.experts_per_rank;
+  const int rows = p.T * p.k;
+  for (int e0 = blockIdx.x * kEpRowsPerCta; e0 < rows; e0 += gridDim.x * kEpRowsPerCta) {
+    const int n = min(kEpRowsPerCta, rows - e0);
+    __syncthreads();                              // the previous batch's slots have been used
+    if (threadIdx.x < n) {
+      const int e = e0 + threadIdx.x;
+      const int expert = p.ids[e];
+      int dst = expert / p.experts_per_rank, slot = 0;
       if (expert < 0 || dst >= p.world) {
         dst = -1;
         atomicCAS(p.status, 0, kErrBadArgument);
@@ -105,22 +113,30 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
         }
       }
       p.route[e] = dst < 0 ? -1 : dst * p.cap + slot;
+      s_dst[threadIdx.x] = dst, s_slot[threadIdx.x] = slot;
+      if (dst >= 0) p.meta_peer[dst][static_cast<size_t>(p.rank) * p.cap + slot] = expert;
     }
-    dst = __shfl_sync(0xffffffffu, dst, 0);
-    slot = __shfl_sync(0xffffffffu, slot, 0);
-    if (dst < 0) continue;
-    const size_t row = static_cast<size_t>(p.rank) * p.cap + slot;
-    const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(e / p.k) * p.H);
-    uint4* dstp = reinterpret_cast<uint4*>(p.recv_peer[dst] + row * p.H);
-    for (int i = lane; i < vec; i += 32) dstp[i] = src[i];
-    if (lane == 0) p.meta_peer[dst][row] = expert;
+    __syncthreads();
+#pragma unroll 4
+    for (int i = threadIdx.x; i < n * vec; i += kEpThreads) {
+      const int r = i / vec, v = i - r * vec;
+      const int dst = s_dst[r];
+      if (dst < 0) continue;
+      const uint4 w = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>((e0 + r) / p.k) * p.H)[v];
+      reinterpret_cast<uint4*>(p.recv_peer[dst] + (static_cast<size_t>(p.rank) * p.cap + s_slot[r]) * p.H)[v] = w;
+    }
   }
   // last CTA: publish the counts and raise the flags (every CTA's rows are fenced before its ticket)
   __shared__ bool last;
+  __shared__ uint32_t epoch;
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
     last = atomicAdd(p.ticket, 1u) == gridDim.x - 1;
+    if (last) {
+      epoch = *p.epoch + 1u;
+      *p.epoch = epoch;
+    }
   }
   __syncthreads();
   if (!last) return;
@@ -131,7 +147,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
     p.count_peer[d][p.rank] = n;
     p.cnt[d] = 0;
     __threadfence_system();
-    ep_flag_store(&p.dflag_peer[d][p.rank], p.epoch);
+    ep_flag_store(&p.dflag_peer[d][p.rank], epoch);
   }
   if (threadIdx.x == 0) *p.ticket = 0u;
 }
@@ -143,7 +159,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_recv_kernel(const EpParams p) {
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if (threadIdx.x < p.world) {
-    if (!ep_flag_wait(&p.dflag[threadIdx.x], p.epoch, p.status)) ok = 0;
+    if (!ep_flag_wait(&p.dflag[threadIdx.x], *p.epoch, p.status)) ok = 0;
     cnt[threadIdx.x] = *reinterpret_cast<const volatile int*>(&p.count[threadIdx.x]);
   }
   __syncthreads();
@@ -157,59 +173,72 @@ __global__ void __launch_bounds__(kEpThreads) ep_recv_kernel(const EpParams p) {
 __global__ void ep_ready_kernel(const EpParams p) {
   if (threadIdx.x < p.world) {
     __threadfence_system();
-    ep_flag_store(&p.cflag_peer[threadIdx.x][p.rank], p.epoch);
+    ep_flag_store(&p.cflag_peer[threadIdx.x][p.rank], *p.epoch);
   }
 }
 
-// One warp per token: out[t] = residual[t] + sum_k w[t, k] * (owner's output row), 8 columns per lane
-// and pass.
+// One thread per 16-byte word of the output: out[t] = residual[t] + sum_k w[t, k] * (owner's output
+// row). The k peer loads of a word are issued together (a peer load is a round trip over NVLink, so
+// the kernel is shaped for loads in flight, not for work per thread).
+constexpr int kEpMaxTopK = 16;
+
 __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p) {
   __shared__ int ok;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if (threadIdx.x < p.world) {
-    if (!ep_flag_wait(&p.cflag[threadIdx.x], p.epoch, p.status)) ok = 0;
+    if (!ep_flag_wait(&p.cflag[threadIdx.x], *p.epoch, p.status)) ok = 0;
   }
   __syncthreads();
   if (!ok) return;
-  const int lane = threadIdx.x & 31;
-  const int warps = (gridDim.x * kEpThreads) >> 5;
   const int vec = p.H >> 3;
-  for (int t = (blockIdx.x * kEpThreads + threadIdx.x) >> 5; t < p.T; t += warps) {
-    for (int v0 = lane; v0 < vec; v0 += 32) {
-      float acc[8];
-      if (p.residual) {
-        const uint4 r = reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(t) * p.H)[v0];
-        const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+  const long long total = static_cast<long long>(p.T) * vec;
+  for (long long i = static_cast<long long>(blockIdx.x) * kEpThreads + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * kEpThreads) {
+    const int t = static_cast<int>(i / vec), v0 = static_cast<int>(i - static_cast<long long>(t) * vec);
+    uint4 y[kEpMaxTopK];
+    float w[kEpMaxTopK];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 f = __bfloat1622float2(r2[q]);
-          acc[2 * q] = f.x, acc[2 * q + 1] = f.y;
-        }
-      } else {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) acc[q] = 0.f;
-      }
-      for (int kk = 0; kk < p.k; ++kk) {
+    for (int kk = 0; kk < kEpMaxTopK; ++kk) {
+      w[kk] = 0.f;
+      y[kk] = make_uint4(0u, 0u, 0u, 0u);
+      if (kk < p.k) {
         const int rt = p.route[t * p.k + kk];
-        if (rt < 0) continue;
-        const int d = rt / p.cap, slot = rt - d * p.cap;
-        const float w = p.wts[t * p.k + kk];
-        const uint4 y = reinterpret_cast<const uint4*>(p.ret_peer[d] +
-                                                       (static_cast<size_t>(p.rank) * p.cap + slot) * p.H)[v0];
-        const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&y);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 f = __bfloat1622float2(y2[q]);
-          acc[2 * q] += w * f.x, acc[2 * q + 1] += w * f.y;
+        if (rt >= 0) {
+          const int d = rt / p.cap, slot = rt - d * p.cap;
+          w[kk] = p.wts[t * p.k + kk];
+          y[kk] = reinterpret_cast<const uint4*>(p.ret_peer[d] +
+                                                 (static_cast<size_t>(p.rank) * p.cap + slot) * p.H)[v0];
         }
       }
-      uint4 o;
-      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-      reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.H)[v0] = o;
     }
+    float acc[8];
+    if (p.residual) {
+      const uint4 r = reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(t) * p.H)[v0];
+      const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(r2[q]);
+        acc[2 * q] = f.x, acc[2 * q + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+    }
+#pragma unroll
+    for (int kk = 0; kk < kEpMaxTopK; ++kk) {
+      const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&y[kk]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(y2[q]);
+        acc[2 * q] += w[kk] * f.x, acc[2 * q + 1] += w[kk] * f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+    reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.H)[v0] = o;
   }
 }
 
@@ -220,8 +249,8 @@ using namespace mx;
 // Plain-C description of one call (pointers as 64-bit integers so that ctypes can fill it).
 struct MxEpCall {
   int rank, world, T, k, H, experts_per_rank, cap;
-  unsigned int epoch;
-  unsigned long long status, x, ids, wts, residual, out, cnt, ticket, route, ids_eff;
+  unsigned int reserved;
+  unsigned long long epoch, status, x, ids, wts, residual, out, cnt, ticket, route, ids_eff;
   unsigned long long meta, count, dflag, cflag;
   unsigned long long recv_peer[kEpMaxRanks], meta_peer[kEpMaxRanks], count_peer[kEpMaxRanks],
       dflag_peer[kEpMaxRanks], cflag_peer[kEpMaxRanks], ret_peer[kEpMaxRanks];
@@ -229,12 +258,14 @@ struct MxEpCall {
 
 static int ep_fill(const MxEpCall* c, EpParams& p) {
   if (c == nullptr || c->world < 1 || c->world > kEpMaxRanks || c->rank < 0 || c->rank >= c->world) return -1;
-  if (c->H <= 0 || c->H % 8 || c->k < 1 || c->cap < 1 || c->experts_per_rank < 1 || c->T < 0) return -1;
+  if (c->H <= 0 || c->H % 8 || c->k < 1 || c->k > kEpMaxTopK || c->cap < 1 || c->experts_per_rank < 1 || c->T < 0) return -1;
   if (static_cast<long long>(c->world) * c->cap > 0x7fffffffLL) return -1;
   p.rank = c->rank, p.world = c->world, p.T = c->T, p.k = c->k, p.H = c->H;
-  p.experts_per_rank = c->experts_per_rank, p.cap = c->cap, p.epoch = c->epoch;
+  p.experts_per_rank = c->experts_per_rank, p.cap = c->cap;
   auto ptr = [](unsigned long long v) { return reinterpret_cast<void*>(static_cast<uintptr_t>(v)); };
   p.status = static_cast<int*>(ptr(c->status));
+  p.epoch = static_cast<uint32_t*>(ptr(c->epoch));
+  if (p.epoch == nullptr || p.status == nullptr) return -1;
   p.x = static_cast<const __nv_bfloat16*>(ptr(c->x));
   p.ids = static_cast<const int*>(ptr(c->ids));
   p.wts = static_cast<const float*>(ptr(c->wts));
@@ -277,8 +308,10 @@ extern "C" int mx_ep_a2a(const void* call, int stage, void* stream_) {
     case 0:
       if (p.cnt == nullptr || p.ticket == nullptr || p.route == nullptr) return -1;
       if (p.T > 0 && (p.x == nullptr || p.ids == nullptr)) return -1;   // T == 0 still raises the flags
-      return static_cast<int>(launch_kernel(ep_dispatch_kernel, dim3(ep_grid(static_cast<long long>(p.T) * p.k)),
-                                            dim3(kEpThreads), 0, stream, p));
+      return static_cast<int>(launch_kernel(
+          ep_dispatch_kernel,
+          dim3(ep_grid((static_cast<long long>(p.T) * p.k + kEpRowsPerCta - 1) / kEpRowsPerCta * (kEpThreads / 32))),
+          dim3(kEpThreads), 0, stream, p));
     case 1:
       if (p.ids_eff == nullptr) return -1;
       return static_cast<int>(launch_kernel(ep_recv_kernel,
@@ -288,7 +321,9 @@ extern "C" int mx_ep_a2a(const void* call, int stage, void* stream_) {
       return static_cast<int>(launch_kernel(ep_ready_kernel, dim3(1), dim3(32), 0, stream, p));
     case 3:
       if (p.T > 0 && (p.out == nullptr || p.wts == nullptr || p.route == nullptr)) return -1;
-      return static_cast<int>(launch_kernel(ep_combine_kernel, dim3(ep_grid(p.T)), dim3(kEpThreads), 0, stream, p));
+      return static_cast<int>(launch_kernel(ep_combine_kernel,
+                                            dim3(ep_grid((static_cast<long long>(p.T) * (p.H >> 3) + 31) / 32)),
+                                            dim3(kEpThreads), 0, stream, p));
     default:
       return -1;
   }

@@ -35,8 +35,8 @@ _MAX_RANKS = 8
 
 class _EpCall(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_int) for n in ("rank", "world", "T", "k", "H", "experts_per_rank", "cap")]
-                + [("epoch", ctypes.c_uint)]
-                + [(n, ctypes.c_ulonglong) for n in ("status", "x", "ids", "wts", "residual", "out", "cnt", "ticket",
+                + [("reserved", ctypes.c_uint)]
+                + [(n, ctypes.c_ulonglong) for n in ("epoch", "status", "x", "ids", "wts", "residual", "out", "cnt", "ticket",
                                                      "route", "ids_eff", "meta", "count", "dflag", "cflag")]
                 + [(n, ctypes.c_ulonglong * _MAX_RANKS) for n in ("recv_peer", "meta_peer", "count_peer",
                                                                   "dflag_peer", "cflag_peer", "ret_peer")])
@@ -78,12 +78,12 @@ class EpAllToAll:
         rows = world * cap
         self.recv = local[self.lay["recv"]:self.lay["recv"] + rows * hidden * 2].view(torch.bfloat16).view(rows, hidden)
         self.ret = local[self.lay["ret"]:self.lay["ret"] + rows * hidden * 2].view(torch.bfloat16).view(rows, hidden)
-        self.cnt = torch.zeros(world + 1, dtype=torch.int32, device=dev)          # [world] counters + ticket
+        self.cnt = torch.zeros(world + 2, dtype=torch.int32, device=dev)          # [world] counters, ticket, epoch
         self.route = torch.full((max_tokens * k,), -1, dtype=torch.int32, device=dev)
         self.ids_eff = torch.full((rows, 1), -1, dtype=torch.int32, device=dev)
         self.ones = torch.ones(rows, 1, dtype=torch.float32, device=dev)
-        self.epoch = 0
         self._T = 0
+        self._build_call()
 
     # ------------------------------------------------------------------ constructors
     @staticmethod
@@ -108,15 +108,14 @@ class EpAllToAll:
                 for r in range(world)]
 
     # ------------------------------------------------------------------ stages
-    def _call(self, stage: int, **kw) -> None:
+    def _build_call(self) -> None:
+        """The call record is filled once; a stage only updates the per-call fields."""
         c = _EpCall()
-        c.rank, c.world, c.T, c.k, c.H = self.rank, self.world, kw.get("T", self._T), self.k, self.H
-        c.experts_per_rank, c.cap, c.epoch = self.epr, self.cap, self.epoch
+        c.rank, c.world, c.k, c.H = self.rank, self.world, self.k, self.H
+        c.experts_per_rank, c.cap = self.epr, self.cap
         c.status = _lib.workspace(self.local.device).data_ptr()
-        for name in ("x", "ids", "wts", "residual", "out"):
-            t = kw.get(name)
-            setattr(c, name, 0 if t is None else t.data_ptr())
         c.cnt, c.ticket = self.cnt.data_ptr(), self.cnt.data_ptr() + 4 * self.world
+        c.epoch = self.cnt.data_ptr() + 4 * (self.world + 1)
         c.route, c.ids_eff = self.route.data_ptr(), self.ids_eff.data_ptr()
         me = self.bases[self.rank]
         c.meta, c.count = me + self.lay["meta"], me + self.lay["count"]
@@ -128,9 +127,20 @@ class EpAllToAll:
             c.dflag_peer[r], c.cflag_peer[r] = b + self.lay["dflag"], b + self.lay["cflag"]
         fn = _lib.load().mx_ep_a2a
         fn.argtypes, fn.restype = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p], ctypes.c_int
-        rc = fn(ctypes.byref(c), stage, _lib.stream())
+        self._c, self._cref, self._fn = c, ctypes.byref(c), fn
+
+    def _call(self, stage: int, x=None, ids=None, wts=None, residual=None, out=None) -> None:
+        c = self._c
+        c.T = self._T
+        c.x = 0 if x is None else x.data_ptr()
+        c.ids = 0 if ids is None else ids.data_ptr()
+        c.wts = 0 if wts is None else wts.data_ptr()
+        c.residual = 0 if residual is None else residual.data_ptr()
+        c.out = 0 if out is None else out.data_ptr()
+        rc = self._fn(self._cref, stage, _lib.stream())
         _lib.count_launch()
-        _lib.check(rc, f"mx_ep_a2a stage {stage}")
+        if rc:
+            _lib.check(rc, f"mx_ep_a2a stage {stage}")
 
     def dispatch(self, x: torch.Tensor, ids: torch.Tensor) -> None:
         """Send every (token, k) row of ``x`` [T, H] to the rank that owns expert ``ids[t, k]``."""
@@ -138,9 +148,8 @@ class EpAllToAll:
         if k != self.k or T > self.max_tokens or x.shape != (T, self.H):
             raise ValueError("dispatch shape does not match the buffers")
         assert x.dtype == torch.bfloat16 and ids.dtype == torch.int32 and x.is_contiguous() and ids.is_contiguous()
-        self.epoch += 1
         self._T = T
-        self._call(0, x=x, ids=ids, T=T)
+        self._call(0, x=x, ids=ids)
 
     def expert_stage(self, w_gate_up, w_down, inter: int, act: str, b_gate_up=None, b_down=None,
                      alpha: float = 1.702, limit: float = 7.0) -> None:
@@ -155,7 +164,7 @@ class EpAllToAll:
         T = self._T
         assert wts.shape == (T, self.k) and wts.dtype == torch.float32 and wts.is_contiguous()
         out = torch.empty(T, self.H, dtype=torch.bfloat16, device=self.local.device)
-        self._call(3, wts=wts, residual=residual, out=out, T=T)
+        self._call(3, wts=wts, residual=residual, out=out)
         return out
 
     def moe(self, x, ids, wts, w_gate_up, w_down, inter: int, act: str, b_gate_up=None, b_down=None,

@@ -1,7 +1,7 @@
 """Multi-rank timing of the fused GEMM + collective kernels against GEMM + NCCL.
 
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 \\
-        -m mlxcel_b200.utils.profile_comm [decode|prefill]
+        -m mlxcel_b200.utils.profile_comm [decode|prefill|ep]
 
 Every case runs 16 dependent launches over 4 rotating weight shards inside one CUDA graph (CUDA
 events around the replay, median of 7, MAX over ranks). Printed per shape: the fused kernel, the
@@ -9,6 +9,11 @@ plain GEMM followed by an NCCL all-reduce (the baseline), the plain GEMM alone, 
 time = max(weight stream at the measured copy bandwidth, FLOPs at the measured bf16 peak, bytes
 that must cross NVLink per GPU at the measured 770 GB/s per direction).
 With MLXCEL_B200_GEMM_TRACE=1 the per-CTA phase timestamps of the fused kernel are printed too.
+
+``ep``: expert-parallel MoE layer with token-sharded ranks (GPT-OSS-120B expert geometry: 128 experts,
+top-4, hidden 2880): the dispatch / combine kernels over peer memory against the same exchange done
+with NCCL (count all-to-all, host read of the counts, two uneven all_to_all_single, torch index ops
+for the permutation and the weighted sum), with and without the expert GEMMs between them.
 """
 from __future__ import annotations
 
@@ -27,6 +32,122 @@ from ..parallel.tp import TPComm
 HBM_GBS, BF16_TFLOPS, NVLINK_GBS = 6551.4, 1658.9, 770.0
 
 
+def ep_main(rank: int, world: int, dev: torch.device) -> None:
+    from ..ops import moe as moe_ops
+    from ..parallel.ep_a2a import EpAllToAll
+    from ..parallel.symm import SymmetricHeap
+
+    E, k, H, I = 128, 4, 2880, 2880
+    epr = E // world
+    Tmax = 1024
+    cap = Tmax * k
+    heap = SymmetricHeap(dist.group.WORLD, dev, EpAllToAll.required_bytes(world, H, cap) + (4 << 20))
+    ep = EpAllToAll.from_heap(heap, H, cap, epr, Tmax, k)
+    g = torch.Generator(device=dev).manual_seed(3 + rank)
+    wgu = (torch.randn(epr, 2 * I, H, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    wd = (torch.randn(epr, H, I, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    layers = 8          # back-to-back layers per timed region (the launches queue up behind the first)
+
+    def timeit(fn, iters=7, warm=2):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(layers):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        t = torch.tensor([sorted(ts)[len(ts) // 2]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]) * 1e3 / layers
+
+    for T in (64, 1024):
+        x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        res = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        ids, wts = moe_ops.route(torch.randn(T, E, device=dev, generator=g).to(torch.bfloat16), k, "topk_softmax", True)
+        ids, wts = ids.contiguous(), wts.contiguous()
+
+        def ours_comm():
+            ep.dispatch(x, ids)
+            ep._call(1)
+            ep._call(2)
+            return ep.combine(wts, res)
+
+        def ours_full():
+            return ep.moe(x, ids, wts, wgu, wd, I, "clipped_swiglu", residual=res)
+
+        def nccl(with_gemm: bool):
+            flat = ids.reshape(-1).long()
+            order = torch.argsort(flat // epr, stable=True)
+            send_counts = torch.bincount(flat // epr, minlength=world)
+            recv_counts = torch.empty_like(send_counts)
+            dist.all_to_all_single(recv_counts, send_counts)
+            sc, rc = send_counts.tolist(), recv_counts.tolist()            # host read of the counts
+            rows = x.index_select(0, order // k)
+            eids = flat.index_select(0, order).to(torch.int32)
+            got = torch.empty(sum(rc), H, dtype=x.dtype, device=dev)
+            got_e = torch.empty(sum(rc), dtype=torch.int32, device=dev)
+            dist.all_to_all_single(got, rows, rc, sc)
+            dist.all_to_all_single(got_e, eids, rc, sc)
+            if with_gemm:
+                y = moe_ops.moe_experts(got, got_e.view(-1, 1), torch.ones(sum(rc), 1, device=dev), wgu, wd, I,
+                                        "clipped_swiglu", e_begin=rank * epr)
+            else:
+                y = got
+            back = torch.empty(T * k, H, dtype=x.dtype, device=dev)
+            dist.all_to_all_single(back, y, sc, rc)
+            unsorted = torch.empty_like(back)
+            unsorted.index_copy_(0, order, back)
+            return (res.float() + (unsorted.view(T, k, H).float() * wts.unsqueeze(-1)).sum(1)).to(x.dtype)
+
+        a, b = ours_full(), nccl(True)
+        torch.cuda.synchronize()
+        err = (a.float() - b.float()).abs().max().item()
+        def graphed(fn):
+            """The same 8 layers inside one CUDA graph (the epoch lives on the device, so a replay
+            raises fresh flags)."""
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                fn()
+                torch.cuda.synchronize()
+                dist.barrier()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=st):
+                    for _ in range(layers):
+                        fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            return timeit(gr.replay) / layers
+
+        t_comm, t_full = timeit(ours_comm), timeit(ours_full)
+        g_comm, g_full = graphed(ours_comm), graphed(ours_full)
+        n_comm, n_full = timeit(lambda: nccl(False)), timeit(lambda: nccl(True))
+        nv = T * k * H * 2 * (world - 1) / world            # bytes leaving one GPU per direction, uniform routing
+        roof = 2 * nv / (NVLINK_GBS * 1e3)
+        if rank == 0:
+            print(json.dumps(dict(case="ep_moe_a2a", world=world, tokens_per_rank=T, top_k=k, hidden=H, experts=E,
+                                  ours_comm_us=round(t_comm, 1), nccl_comm_us=round(n_comm, 1),
+                                  ours_layer_us=round(t_full, 1), nccl_layer_us=round(n_full, 1),
+                                  ours_comm_graph_us=round(g_comm, 1), ours_layer_graph_us=round(g_full, 1),
+                                  nvlink_roofline_us=round(roof, 1), comm_graph_of_roofline=round(roof / g_comm, 3),
+                                  max_abs_diff_vs_nccl_path=round(err, 4))), flush=True)
+    st = _lib.read_status(dev)
+    assert st == 0, f"kernel status {st}"
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    os._exit(0)
+
+
 def main() -> None:
     mode = sys.argv[1] if len(sys.argv) > 1 else "decode"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -34,6 +155,8 @@ def main() -> None:
     torch.cuda.set_device(lr)
     dev = torch.device("cuda", lr)
     dist.init_process_group("nccl", device_id=dev)
+    if mode == "ep":
+        return ep_main(rank, world, dev)
     comm = TPComm(dist.group.WORLD, dev, backend="fused", max_tokens=8192, hidden=4096, vocab=131072)
     assert comm.backend == "fused"
     nrep, ncopy = 16, 4
