@@ -196,6 +196,22 @@ class ModelConfig:
         c.tie_word_embeddings = bool(g("tie_word_embeddings", False))
         c.rope_theta = float(g("rope_theta", 10000.0))
         c.rope_scaling = g("rope_scaling")
+        rp = g("rope_parameters")
+        if isinstance(rp, dict):
+            # transformers >= 5 layout: theta and scaling in one record, or one record per layer type
+            if "full_attention" in rp or "sliding_attention" in rp:
+                loc = rp.get("sliding_attention") or {}
+                if loc.get("rope_theta") is not None:
+                    c.extra["rope_local_theta"] = float(loc["rope_theta"])
+                rp = rp.get("full_attention") or {}
+            if rp.get("rope_theta") is not None:
+                c.rope_theta = float(rp["rope_theta"])
+            if rp.get("rope_type", rp.get("type", "default")) not in (None, "default"):
+                c.rope_scaling = rp
+            if rp.get("partial_rotary_factor") is not None and "partial_rotary_factor" not in raw:
+                raw["partial_rotary_factor"] = rp["partial_rotary_factor"]
+        if g("rope_local_base_freq") is not None:
+            c.extra["rope_local_theta"] = float(g("rope_local_base_freq"))
         c.rope_traditional = bool(g("rope_traditional", False))
         c.partial_rotary_factor = float(g("partial_rotary_factor", 1.0))
         c.attention_bias = bool(g("attention_bias", g("qkv_bias", False)))
@@ -205,6 +221,7 @@ class ModelConfig:
         c.hidden_act = {"silu": "silu", "swish": "silu", "gelu_pytorch_tanh": "gelu_tanh",
                         "gelu_tanh": "gelu_tanh", "gelu": "gelu_tanh"}.get(
                             g("hidden_act", g("hidden_activation", "silu")), "silu")
+        c.extra["act_raw"] = str(g("hidden_act", g("hidden_activation", g("activation_function", "silu"))))
         c.num_experts = int(g("num_local_experts", g("num_experts", g("n_routed_experts", 0))) or 0)
         c.num_experts_per_tok = int(g("num_experts_per_tok", g("experts_per_token", 0)) or 0)
         c.moe_intermediate_size = int(g("moe_intermediate_size", 0) or 0)
@@ -314,12 +331,110 @@ def _olmo2(c: ModelConfig, raw: dict) -> None:
     c.extra["post_norm_only"] = True  # norms after attention / mlp instead of before
 
 
+def _plain_act(c: ModelConfig) -> str:
+    """Activation of a non-gated MLP from the checkpoint's spelling."""
+    a = c.extra.get("act_raw", "gelu")
+    return {"gelu": "gelu", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu_fast": "gelu_tanh",
+            "relu2": "relu2", "silu": "silu", "swish": "silu"}.get(a, "gelu")
+
+
+def _starcoder2(c: ModelConfig, raw: dict) -> None:
+    """LayerNorm with bias, biased projections, plain MLP c_fc -> GELU(tanh) -> c_proj
+    (reference src/models/starcoder2.rs)."""
+    c.extra["norm"] = "layernorm"
+    c.extra["mlp"] = "plain"
+    c.rms_norm_eps = float(raw.get("norm_epsilon", 1e-5))
+    c.attention_bias = c.mlp_bias = bool(raw.get("use_bias", True))
+    c.hidden_act = _plain_act(c)
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
+    c.layer_types = None                         # one window for every layer (sliding_window, may be null)
+
+
+def _stablelm(c: ModelConfig, raw: dict) -> None:
+    """LayerNorm with bias, partial rotary embedding, gated SiLU MLP (reference src/models/stablelm.rs)."""
+    c.extra["norm"] = "layernorm"
+    c.rms_norm_eps = float(raw.get("layer_norm_eps", 1e-5))
+    c.attention_bias = bool(raw.get("use_qkv_bias", False))
+    c.extra["parallel_block"] = bool(raw.get("use_parallel_residual", False))
+    if raw.get("qk_layernorm"):
+        raise ValueError("stablelm with per-head q/k LayerNorm is not supported")
+
+
+def _cohere(c: ModelConfig, raw: dict) -> None:
+    """Bias-free LayerNorm, attention and MLP in parallel from one normed input, interleaved RoPE,
+    logits multiplied by logit_scale (reference src/models/cohere.rs)."""
+    c.extra["norm"] = "layernorm"
+    c.extra["parallel_block"] = True
+    c.rms_norm_eps = float(raw.get("layer_norm_eps", 1e-5))
+    c.rope_traditional = True
+    c.extra["logits_scaling"] = 1.0 / float(raw.get("logit_scale", 0.0625))
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
+    if raw.get("use_qk_norm"):
+        raise ValueError("cohere with q/k LayerNorm is not supported")
+
+
+def _interleaved_rope(c: ModelConfig, raw: dict) -> None:
+    """Llama layout with RoPE on interleaved pairs (Helium, ERNIE 4.5)."""
+    c.rope_traditional = True
+
+
+def _smollm3(c: ModelConfig, raw: dict) -> None:
+    """Llama layout where every ``no_rope_layer_interval``-th layer has no positional encoding
+    (``no_rope_layers[i] == 0``; reference src/models/smollm3.rs)."""
+    flags = raw.get("no_rope_layers")
+    if flags is None:
+        iv = int(raw.get("no_rope_layer_interval", 4))
+        flags = [int((i + 1) % iv != 0) for i in range(c.num_hidden_layers)]
+    c.extra["nope_layers"] = [i for i, f in enumerate(flags) if not f]
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
+
+
+def _exaone4(c: ModelConfig, raw: dict) -> None:
+    """Norms after attention / MLP only, per-head q/k RMSNorm, and (hybrid models) no positional
+    encoding on the full-attention layers (reference src/models/exaone4.rs)."""
+    c.qk_norm = True
+    c.extra["post_norm_only"] = True
+    if c.sliding_window and c.layer_types:
+        c.extra["nope_layers"] = [i for i, t in enumerate(c.layer_types) if t != "sliding_attention"]
+
+
+def _apertus(c: ModelConfig, raw: dict) -> None:
+    """Per-head q/k RMSNorm, plain MLP up -> xIELU -> down with learned per-layer activation
+    parameters (reference src/models/apertus.rs)."""
+    c.qk_norm = True
+    c.extra["mlp"] = "plain"
+    c.hidden_act = "xielu"
+
+
+def _minicpm(c: ModelConfig, raw: dict) -> None:
+    """Llama layout with scaled embeddings, depth-scaled residual branches and width-scaled logits
+    (reference src/models/minicpm.rs)."""
+    c.embed_scale = float(raw.get("scale_emb", 1.0))
+    c.extra["residual_multiplier"] = float(raw.get("scale_depth", 1.0)) / math.sqrt(c.num_hidden_layers)
+    c.extra["logits_scaling"] = c.hidden_size / float(raw.get("dim_model_base", c.hidden_size))
+
+
+def _olmoe(c: ModelConfig, raw: dict) -> None:
+    _qwen_moe(c, raw)
+    c.attention_bias = False
+    c.qk_norm = True
+    c.extra["qk_norm_full"] = True
+    c.norm_topk_prob = bool(raw.get("norm_topk_prob", False))
+
+
 def _granite(c: ModelConfig, raw: dict) -> None:
     c.embed_scale = float(raw.get("embedding_multiplier", 1.0))
     c.extra["residual_multiplier"] = float(raw.get("residual_multiplier", 1.0))
     c.extra["logits_scaling"] = float(raw.get("logits_scaling", 1.0))
     if raw.get("attention_multiplier"):
         c.query_pre_attn_scalar = 1.0 / float(raw["attention_multiplier"]) ** 2
+
+
+def _num(v) -> float:
+    """A JSON number, or HF's spelling of a non-finite one (``{"__float__": "Infinity"}``, ``"inf"``)."""
+    if isinstance(v, dict):
+        v = v.get("__float__", "inf")
+    return float(v)
 
 
 def _mamba2(c: ModelConfig, raw: dict) -> None:
@@ -334,7 +449,7 @@ def _mamba2(c: ModelConfig, raw: dict) -> None:
     c.extra["mamba"] = dict(d_inner=d_inner, head_dim=P, n_groups=int(raw.get("n_groups", 1)),
                             d_state=int(raw.get("state_size", raw.get("ssm_state_size", 128))),
                             d_conv=int(raw.get("conv_kernel", raw.get("d_conv", 4))),
-                            time_step_limit=(float(lim[0]), float(lim[1])),
+                            time_step_limit=(_num(lim[0]), _num(lim[1])),
                             use_bias=bool(raw.get("use_bias", False)),
                             use_conv_bias=bool(raw.get("use_conv_bias", True)))
     c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
@@ -354,7 +469,7 @@ def _nemotron_h(c: ModelConfig, raw: dict) -> None:
     lim = raw.get("time_step_limit") or (0.0, float("inf"))
     c.extra["mamba"] = dict(d_inner=heads * P, head_dim=P, n_groups=G,
                             d_state=int(raw.get("ssm_state_size", 128)), d_conv=int(raw.get("conv_kernel", 4)),
-                            time_step_limit=(float(lim[0]), float(lim[1])), norm_groups=G,
+                            time_step_limit=(_num(lim[0]), _num(lim[1])), norm_groups=G,
                             use_conv_bias=bool(raw.get("use_conv_bias", True)))
     pat = raw.get("hybrid_override_pattern")
     if not pat:
@@ -367,14 +482,14 @@ def _nemotron_h(c: ModelConfig, raw: dict) -> None:
 
 
 FAMILIES = {
-    "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _plain, "seed_oss": _plain,
-    "helium": _plain, "internlm3": _plain, "exaone4": _qwen3, "hunyuan_v1_dense": _qwen3,
-    "ernie4_5": _plain, "apertus": _plain, "minicpm": _plain, "mimo": _qwen2, "yi": _plain,
+    "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _smollm3, "seed_oss": _plain,
+    "helium": _interleaved_rope, "internlm3": _plain, "exaone4": _exaone4,
+    "ernie4_5": _interleaved_rope, "apertus": _apertus, "minicpm": _minicpm, "mimo": _qwen2, "yi": _plain,
     "qwen2": _qwen2, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
-    "mixtral": _mixtral, "phimoe": _mixtral, "olmoe": _qwen_moe,
+    "mixtral": _mixtral, "olmoe": _olmoe,
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
-    "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _plain, "stablelm": _plain, "cohere": _plain,
+    "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
 }
 
 

@@ -617,7 +617,8 @@ __global__ void bitlinear_kernel(const __nv_bfloat16* __restrict__ x, const uint
 }
 
 // ----------------------------------------------------------------------------- element-wise
-// mode 0: tanh-GELU; mode 1: xIELU with per-tensor alpha_p, alpha_n, beta, eps; mode 2: relu(x)^2.
+// mode 0: tanh-GELU; mode 1: xIELU with per-tensor alpha_p, alpha_n, beta, eps; mode 2: relu(x)^2;
+// mode 3: erf-GELU; mode 4: SiLU.
 __global__ void activation_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                   long long n, int mode, float ap, float an, float beta, float eps) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -628,10 +629,49 @@ __global__ void activation_kernel(const __nv_bfloat16* __restrict__ x, __nv_bflo
     r = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
   } else if (mode == 2) {
     r = v > 0.f ? v * v : 0.f;
+  } else if (mode == 3) {
+    r = 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
+  } else if (mode == 4) {
+    r = v / (1.f + __expf(-v));
   } else {
     r = v > 0.f ? ap * v * v + beta * v : an * (expm1f(fminf(v, eps)) - v) + beta * v;
   }
   y[i] = __float2bfloat16(r);
+}
+
+// y = LayerNorm(x) * w + bias (bias optional). One CTA per row; the row is read twice (mean, then
+// centred variance) from L1/L2.
+__global__ void layernorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                 const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y, int dim,
+                                 float eps) {
+  __shared__ float red[33];
+  const __nv_bfloat16* xr = x + static_cast<size_t>(blockIdx.x) * dim;
+  const auto block_sum = [&](float v) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+      t = warp_sum(t);
+      if (threadIdx.x == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+  };
+  float s = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) s += __bfloat162float(xr[i]);
+  const float mean = block_sum(s) / dim;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float d = __bfloat162float(xr[i]) - mean;
+    q += d * d;
+  }
+  const float rstd = rsqrtf(block_sum(q) / dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = (__bfloat162float(xr[i]) - mean) * rstd * __bfloat162float(w[i]);
+    y[static_cast<size_t>(blockIdx.x) * dim + i] = __float2bfloat16(v + (bias ? __bfloat162float(bias[i]) : 0.f));
+  }
 }
 
 // y = LayerNorm(a + b + c) * w + bias; also writes the sum. One CTA per row.
@@ -878,6 +918,17 @@ extern "C" int mx_activation(const void* x, void* y, long long n, int mode, floa
   const int threads = 256;
   activation_kernel<<<static_cast<int>((n + threads - 1) / threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, mode, ap, an, beta, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mx_layernorm(const void* x, const void* w, const void* bias, void* y, int rows, int dim, float eps,
+                            void* stream) {
+  if (rows <= 0 || dim <= 0) return 0;
+  int threads = ((dim + 31) / 32) * 32;
+  if (threads > 512) threads = 512;
+  layernorm_kernel<<<rows, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(y), dim, eps);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -208,12 +208,23 @@ def _load_attention(g: _Getter, cfg: ModelConfig, p: str, lw_kwargs: dict) -> No
     lw_kwargs["bo"] = g.vec(a + ".o_proj.bias")
     lw_kwargs["q_norm"] = g.vec(a + ".q_norm.weight")
     lw_kwargs["k_norm"] = g.vec(a + ".k_norm.weight")
+    if cfg.norm_weight_bias and lw_kwargs["q_norm"] is not None:
+        # Gemma 3 stores the per-head norms as (weight - 1) like its other norms; the fused
+        # q/k-norm + RoPE kernel takes plain gains
+        lw_kwargs["q_norm"] = (lw_kwargs["q_norm"].float() + cfg.norm_weight_bias).to(lw_kwargs["q_norm"].dtype)
+        lw_kwargs["k_norm"] = (lw_kwargs["k_norm"].float() + cfg.norm_weight_bias).to(lw_kwargs["k_norm"].dtype)
     sinks = g.src.get(a + ".sinks").float() if g.src.has(a + ".sinks") else None
     lw_kwargs["sinks"] = sinks
 
 
 def _load_dense_mlp(g: _Getter, p: str, lw: LayerWeights) -> None:
     m = p + ".mlp"
+    plain = next(((a, b) for a, b in ((".c_fc", ".c_proj"), (".fc1", ".fc2"), (".up_proj", ".down_proj"))
+                  if g.has(m + a) and not g.has(m + ".gate_proj") and not g.has(m + ".gate_up_proj")), None)
+    if plain is not None:                                   # non-gated MLP: fc -> act -> proj
+        lw.w_gate_up, lw.b_gate_up = g.mat(m + plain[0]), g.vec(m + plain[0] + ".bias")
+        lw.w_down, lw.b_down = g.mat(m + plain[1]), g.vec(m + plain[1] + ".bias")
+        return
     if g.has(m + ".gate_up_proj"):
         lw.w_gate_up = g.mat(m + ".gate_up_proj")
     else:
@@ -296,9 +307,16 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
         p = f"{pre}layers.{i}"
         kw: dict = {}
         _load_attention(g, cfg, p, kw)
-        ln1 = g.vec(p + ".input_layernorm.weight")
-        ln2 = g.vec(_first_name(src, p + ".post_attention_layernorm.weight", p + ".pre_feedforward_layernorm.weight"))
+        ln1 = g.vec(_first_name(src, p + ".input_layernorm.weight", p + ".attention_layernorm.weight"))
+        ln2 = g.vec(_first_name(src, p + ".post_attention_layernorm.weight", p + ".pre_feedforward_layernorm.weight",
+                                p + ".feedforward_layernorm.weight"))
         lw = LayerWeights(ln1=ln1, ln2=ln2, **kw)
+        lw.ln1_b = g.vec(p + ".input_layernorm.bias")
+        lw.ln2_b = g.vec(p + ".post_attention_layernorm.bias")
+        if cfg.extra.get("post_norm_only"):
+            lw.post_attn_norm = g.vec(p + ".post_attention_layernorm.weight")
+            lw.post_mlp_norm = g.vec(p + ".post_feedforward_layernorm.weight")
+            lw.ln1 = lw.ln2 = lw.post_attn_norm          # placeholders: this layout has no pre-norms
         if cfg.post_norms:
             lw.post_attn_norm = g.vec(p + ".post_attention_layernorm.weight")
             lw.ln2 = g.vec(p + ".pre_feedforward_layernorm.weight")
@@ -307,6 +325,12 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
             _load_moe(g, cfg, p, lw)
         else:
             _load_dense_mlp(g, p, lw)
+        if src.has(p + ".mlp.act_fn.alpha_p"):                 # xIELU (Apertus): stored before softplus
+            sp = torch.nn.functional.softplus
+            beta = float(src.get(p + ".mlp.act_fn.beta")) if src.has(p + ".mlp.act_fn.beta") else 0.5
+            eps_x = float(src.get(p + ".mlp.act_fn.eps")) if src.has(p + ".mlp.act_fn.eps") else -1e-6
+            lw.act_params = (float(sp(src.get(p + ".mlp.act_fn.alpha_p").float())),
+                             beta + float(sp(src.get(p + ".mlp.act_fn.alpha_n").float())), beta, eps_x)
         lws.append(lw)
     final_norm = g.vec(pre + "norm.weight")
     head_base = "lm_head" if g.has("lm_head") else ("language_model.lm_head" if g.has("language_model.lm_head") else None)
@@ -314,7 +338,10 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
         lm_head = g.mat(head_base)
     else:
         lm_head = emb_q if (emb_q is not None and not dequantize) else emb
-    return ModelWeights(embed=emb, layers=lws, final_norm=final_norm, lm_head=lm_head)
+    mw = ModelWeights(embed=emb, layers=lws, final_norm=final_norm, lm_head=lm_head)
+    if g.vec(pre + "norm.bias") is not None:
+        mw.extra["final_norm_b"] = g.vec(pre + "norm.bias")
+    return mw
 
 
 def _first_name(src: TensorSource, *names):

@@ -85,7 +85,14 @@ def shard_layer(cfg: ModelConfig, lw: LayerWeights, rank: int, tp: int, ep_rank:
                        q_norm=lw.q_norm, k_norm=lw.k_norm,
                        sinks=None if lw.sinks is None else lw.sinks[rank * hq:(rank + 1) * hq].contiguous(),
                        post_attn_norm=lw.post_attn_norm, post_mlp_norm=lw.post_mlp_norm)
-    if lw.w_gate_up is not None:
+    out.ln1_b, out.ln2_b = lw.ln1_b, lw.ln2_b
+    if lw.w_gate_up is not None and cfg.extra.get("mlp") == "plain":
+        i = cfg.intermediate_size // tp                 # non-gated MLP: rows of fc, columns of proj
+        out.w_gate_up = _rows(lw.w_gate_up, rank * i, (rank + 1) * i)
+        out.w_down = _cols(lw.w_down, rank * i, (rank + 1) * i)
+        out.b_gate_up = None if lw.b_gate_up is None else lw.b_gate_up[rank * i:(rank + 1) * i].contiguous()
+        out.b_down = lw.b_down
+    elif lw.w_gate_up is not None:
         I = cfg.intermediate_size
         i = I // tp
         out.w_gate_up = _cat_rows([_rows(lw.w_gate_up, rank * i, (rank + 1) * i),

@@ -118,9 +118,17 @@ class DecoderModel:
         inv, ms = rope_inv_freq(cfg.rot_dim, cfg.rope_theta, cfg.rope_scaling)
         self.inv_freq = inv.to(dev)
         self.mscale = ms
+        # sliding-window layers with their own RoPE base (Gemma 3: local 10k, global 1M with scaling)
+        self.inv_freq_local = None
+        if cfg.extra.get("rope_local_theta"):
+            self.inv_freq_local = rope_inv_freq(cfg.rot_dim, cfg.extra["rope_local_theta"], None)[0].to(dev)
         self.device = dev
         self._ssq = None
         self.fold_attn = self.fold_mlp = False
+        self.nope_layers = frozenset(cfg.extra.get("nope_layers", ()))
+        self.layernorm = cfg.extra.get("norm") == "layernorm"
+        self.plain_mlp = cfg.extra.get("mlp") == "plain"
+        self.general = self.layernorm or self.plain_mlp or bool(cfg.extra.get("parallel_block"))
         # Folding rewrites the projection weights in place, so only the owner of the weights asks for
         # it (the LLM front end does; weights shared with another executor must stay untouched).
         if fold_norms and dev.type == "cuda" and os.environ.get("MLXCEL_B200_FOLD_NORMS", "1") != "0":
@@ -135,7 +143,8 @@ class DecoderModel:
         the projections disappear (2 per layer). Same math as norm-then-project up to bf16
         rounding of the folded weight."""
         cfg = self.cfg
-        if cfg.post_norms or cfg.extra.get("residual_multiplier", 1.0) != 1.0:
+        if (cfg.post_norms or cfg.extra.get("residual_multiplier", 1.0) != 1.0 or cfg.extra.get("post_norm_only")
+                or self.general):
             return
         H = cfg.hidden_size
         if H % 128 or H // 128 > 64:
@@ -170,13 +179,26 @@ class DecoderModel:
                    kv: KVLayer, row_norm=None) -> torch.Tensor:
         cfg = self.cfg
         qkv = _linear_any(x, lw.wqkv, bias=lw.bqkv, row_norm=row_norm)
-        ops.rope_append(qkv, b.positions, b.slot_mapping, self.inv_freq, kv, Hq=self.Hq,
-                        Hkv=self.Hkv, D=self.D, rot_dim=cfg.rot_dim,
-                        traditional=cfg.rope_traditional, mscale=self.mscale,
-                        q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, norm_eps=cfg.rms_norm_eps)
+        q_norm, k_norm = lw.q_norm, lw.k_norm
+        if q_norm is not None and cfg.extra.get("qk_norm_full"):
+            # OLMo-2 / OLMoE: RMSNorm over the whole q and k projections (not per head), before RoPE
+            if self.comm.tp_size != 1:
+                raise NotImplementedError("whole-projection q/k norm is not sharded across tensor-parallel ranks")
+            nq, nk = self.Hq * self.D, self.Hkv * self.D
+            qn = ops.rmsnorm(qkv[:, :nq].contiguous(), q_norm, cfg.rms_norm_eps, 0.0)
+            kn = ops.rmsnorm(qkv[:, nq:nq + nk].contiguous(), k_norm, cfg.rms_norm_eps, 0.0)
+            qkv = torch.cat([qn, kn, qkv[:, nq + nk:]], dim=1)
+            q_norm = k_norm = None
+        window = cfg.layer_window(self.layer_range[li] if li < len(self.layer_range) else li)
+        local = window > 0 and self.inv_freq_local is not None
+        layer_index = self.layer_range[li] if li < len(self.layer_range) else li
+        rot_dim = 0 if layer_index in self.nope_layers else cfg.rot_dim    # layers without positional encoding
+        ops.rope_append(qkv, b.positions, b.slot_mapping, self.inv_freq_local if local else self.inv_freq, kv,
+                        Hq=self.Hq, Hkv=self.Hkv, D=self.D, rot_dim=rot_dim,
+                        traditional=cfg.rope_traditional, mscale=1.0 if local else self.mscale,
+                        q_norm_w=q_norm, k_norm_w=k_norm, norm_eps=cfg.rms_norm_eps)
         T = qkv.shape[0]
         attn = torch.empty(T, self.Hq * self.D, dtype=qkv.dtype, device=qkv.device)
-        window = cfg.layer_window(self.layer_range[li] if li < len(self.layer_range) else li)
         q = qkv[:, : self.Hq * self.D]
         nd = b.num_decode
         common = dict(Hq=self.Hq, Hkv=self.Hkv, D=self.D, scale=cfg.attn_scale, window=window,
@@ -195,8 +217,22 @@ class DecoderModel:
                 attn[nd:] = o
         return attn
 
+    def _norm(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
+        """The model's normalisation: RMSNorm (with Gemma's +1) or LayerNorm (bias optional)."""
+        if self.layernorm:
+            from ..ops import recurrent as rops
+            return rops.layernorm(x, w, b, self.cfg.rms_norm_eps)
+        return ops.rmsnorm(x, w, self.cfg.rms_norm_eps, self.cfg.norm_weight_bias)
+
     def _mlp(self, lw: LayerWeights, x: torch.Tensor, row_norm=None) -> torch.Tensor:
         cfg = self.cfg
+        if self.plain_mlp:                      # fc -> activation -> (proj by the caller)
+            from ..ops import recurrent as rops
+            u = _linear_any(x, lw.w_gate_up, bias=lw.b_gate_up)
+            if cfg.hidden_act == "xielu":
+                ap, an, beta, eps_x = lw.act_params or (0.8, 0.8, 0.5, -1e-6)
+                return rops.xielu(u, ap, an, beta, eps_x)
+            return rops.activation(u, cfg.hidden_act)
         return _glu_any(x, lw.w_gate_up, self.I, cfg.hidden_act, lw.b_gate_up, cfg.swiglu_alpha,
                         cfg.swiglu_limit, row_norm=row_norm)
 
@@ -222,6 +258,19 @@ class DecoderModel:
         if self.fold_attn:
             raise RuntimeError("norm weights are folded into the projections: this batch cannot take the "
                                "unfolded path (too many tokens or a non-bf16 stream)")
+        if self.general:
+            return self._forward_general(h, b, kv_layers)
+        if cfg.extra.get("post_norm_only"):
+            # OLMo-2: no norm before the blocks; h += norm(attn(h)); h += norm(mlp(h))
+            for li, lw in enumerate(w.layers):
+                a = self._attention(li, lw, h, b, kv_layers[li])
+                o = self.comm.row_parallel_linear(a, lw.wo, lw.bo, None)
+                h = (h.float() + ops.rmsnorm(o, lw.post_attn_norm, eps, wb).float()).to(h.dtype)
+                if cfg.is_moe:
+                    raise NotImplementedError("post-norm-only MoE blocks")
+                o = self.comm.row_parallel_linear(self._mlp(lw, h), lw.w_down, lw.b_down, None)
+                h = (h.float() + ops.rmsnorm(o, lw.post_mlp_norm, eps, wb).float()).to(h.dtype)
+            return h
         for li, lw in enumerate(w.layers):
             kv = kv_layers[li]
             x = ops.rmsnorm(h, lw.ln1, eps, wb)
@@ -249,6 +298,29 @@ class DecoderModel:
                     h = (h.float() + o.float()).to(h.dtype) if not h.is_cuda else h.add_(o)
                 else:
                     h = self.comm.row_parallel_linear(m, lw.w_down, lw.b_down, h)
+        return h
+
+    def _forward_general(self, h: torch.Tensor, b: StepBatch, kv_layers: list[KVLayer]) -> torch.Tensor:
+        """Layer loop of the less common layouts, without the fusions of the main path: LayerNorm
+        instead of RMSNorm (StarCoder2, StableLM, Cohere), a plain fc -> act -> proj MLP
+        (StarCoder2), attention and MLP in parallel from one normed input (Cohere, StableLM's
+        parallel residual)."""
+        cfg = self.cfg
+        parallel = bool(cfg.extra.get("parallel_block"))
+        for li, lw in enumerate(self.w.layers):
+            x = self._norm(h, lw.ln1, lw.ln1_b)
+            a = self._attention(li, lw, x, b, kv_layers[li])
+            if parallel:
+                o = self.comm.row_parallel_linear(a, lw.wo, lw.bo, None)
+                m = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, None)
+                h = (h.float() + o.float() + m.float()).to(h.dtype)
+            else:
+                h = self.comm.row_parallel_linear(a, lw.wo, lw.bo, h)
+                x = self._norm(h, lw.ln2, lw.ln2_b)
+                if cfg.is_moe:
+                    h = self._moe(lw, x, h)
+                else:
+                    h = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, h)
         return h
 
     def _forward_folded(self, h: torch.Tensor, b: StepBatch, kv_layers: list[KVLayer]) -> torch.Tensor:
@@ -279,7 +351,7 @@ class DecoderModel:
         cfg, w = self.cfg, self.w
         if rows is not None:
             h = h.index_select(0, rows)
-        x = ops.rmsnorm(h, w.final_norm, cfg.rms_norm_eps, cfg.norm_weight_bias)
+        x = self._norm(h, w.final_norm, w.extra.get("final_norm_b"))
         if isinstance(w.lm_head, QuantizedTensor):
             lg = self.comm.gather_logits(_linear_any(x, w.lm_head))
         else:

@@ -61,6 +61,9 @@ class LayerWeights:
     sinks: torch.Tensor | None = None            # fp32 [Hq_local]
     post_attn_norm: torch.Tensor | None = None   # Gemma2/3
     post_mlp_norm: torch.Tensor | None = None
+    ln1_b: torch.Tensor | None = None            # LayerNorm families: norm biases
+    ln2_b: torch.Tensor | None = None
+    act_params: tuple | None = None              # xIELU: (alpha_p, alpha_n, beta, eps) of this layer
     # dense MLP
     w_gate_up: object | None = None
     w_down: object | None = None

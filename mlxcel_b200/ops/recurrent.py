@@ -21,6 +21,7 @@ _SIG = {
     "mx_bitlinear": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "mx_activation": [_vp, _vp, _ll, _i, _f, _f, _f, _f, _vp],
     "mx_add3_layernorm": [_vp] * 7 + [_i, _i, _f, _vp],
+    "mx_layernorm": [_vp, _vp, _vp, _vp, _i, _i, _f, _vp],
 }
 
 
@@ -246,6 +247,34 @@ def gelu_tanh(x):
         return F.gelu(x.float(), approximate="tanh").to(x.dtype)
     y = torch.empty_like(x)
     _call("mx_activation", x.data_ptr(), y.data_ptr(), x.numel(), 0, 0.0, 0.0, 0.0, 0.0, _lib.stream())
+    return y
+
+
+_ACT_MODES = {"gelu_tanh": 0, "relu2": 2, "gelu": 3, "silu": 4}
+
+
+def activation(x, kind: str):
+    """Element-wise activation of a plain (non-gated) MLP: gelu_tanh | gelu (erf) | relu2 | silu."""
+    if not x.is_cuda:
+        v = x.float()
+        r = {"gelu_tanh": lambda: F.gelu(v, approximate="tanh"), "gelu": lambda: F.gelu(v),
+             "relu2": lambda: torch.relu(v).square(), "silu": lambda: F.silu(v)}[kind]()
+        return r.to(x.dtype)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    _call("mx_activation", x.data_ptr(), y.data_ptr(), x.numel(), _ACT_MODES[kind], 0.0, 0.0, 0.0, 0.0, _lib.stream())
+    return y
+
+
+def layernorm(x, weight, bias=None, eps: float = 1e-5):
+    """LayerNorm over the last dimension of a 2-D tensor (bias optional)."""
+    if not x.is_cuda:
+        return F.layer_norm(x.float(), (x.shape[-1],), weight.float(), None if bias is None else bias.float(),
+                            eps).to(x.dtype)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    _call("mx_layernorm", x.data_ptr(), weight.data_ptr(), _lib.ptr(bias), y.data_ptr(), x.shape[0], x.shape[1],
+          float(eps), _lib.stream())
     return y
 
 

@@ -114,9 +114,11 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
                traditional: bool, mscale: float = 1.0) -> torch.Tensor:
     """x: [T, H, D] (any float dtype) → rotated fp32 tensor."""
     xf = x.float()
-    ang = positions.float()[:, None] * inv_freq.float()[None, :]  # [T, half]
-    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
     half = rot_dim // 2
+    if half == 0:                                   # a layer without positional encoding
+        return xf * mscale
+    ang = positions.float()[:, None] * inv_freq.float()[None, :half]  # [T, half]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
     out = xf.clone()
     if traditional:
         a, b = xf[..., 0:rot_dim:2], xf[..., 1:rot_dim:2]

@@ -1,0 +1,90 @@
+"""Architecture parity against Hugging Face transformers (CPU, fp32): for every model family the
+config table claims and transformers ships, a tiny random model is built with transformers, saved
+with ``save_pretrained`` and loaded through this package's own config parser and checkpoint loader;
+the logits of one 24-token prompt must agree to float32 rounding. This pins the family flags (norm
+type and placement, q/k norms, RoPE variant and per-layer bases, sliding patterns, MoE routing,
+logit scaling, ...) to an independent implementation of the published architectures."""
+import tempfile
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from mlxcel_b200.cache.kv_pool import KVPool  # noqa: E402
+from mlxcel_b200.config import ModelConfig  # noqa: E402
+from mlxcel_b200.models.decoder import DecoderModel, StepBatch  # noqa: E402
+
+BASE = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+            vocab_size=300, max_position_embeddings=256)
+SLIDING = dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])
+FAMILIES = {
+    "llama": {}, "mistral": dict(sliding_window=None), "ministral": dict(head_dim=16, sliding_window=8),
+    "qwen2": {}, "qwen3": dict(head_dim=32), "seed_oss": dict(head_dim=16),
+    "smollm3": dict(pad_token_id=0, num_hidden_layers=4, no_rope_layer_interval=2),
+    "helium": dict(head_dim=16), "ernie4_5": dict(head_dim=16), "apertus": {},
+    "gemma": dict(head_dim=16), "gemma2": dict(head_dim=16, sliding_window=8, query_pre_attn_scalar=16),
+    "gemma3_text": dict(head_dim=16, sliding_window=8, query_pre_attn_scalar=16, sliding_window_pattern=2),
+    "phi3": dict(pad_token_id=0), "olmo2": {}, "olmo3": dict(**SLIDING), "exaone4": dict(head_dim=16, **SLIDING),
+    "granite": dict(embedding_multiplier=2.0, residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=3.0),
+    "starcoder2": {}, "stablelm": {}, "cohere": {},
+    "mixtral": dict(num_local_experts=4, num_experts_per_tok=2),
+    "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
+                      shared_expert_intermediate_size=96, decoder_sparse_step=1),
+    "qwen3_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48, head_dim=32,
+                      decoder_sparse_step=1, mlp_only_layers=[]),
+    "olmoe": dict(num_experts=4, num_experts_per_tok=2),
+    "gpt_oss": dict(num_local_experts=4, num_experts_per_tok=2, head_dim=16, **SLIDING),
+    "mamba2": dict(num_heads=8, head_dim=16, state_size=16, n_groups=1, expand=2, conv_kernel=4, chunk_size=8),
+}
+
+
+def _hf_model(name: str):
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    kw = dict(BASE)
+    kw.update(FAMILIES[name])
+    if name == "mamba2":
+        for k in ("intermediate_size", "num_attention_heads", "num_key_value_heads", "max_position_embeddings"):
+            kw.pop(k)
+    torch.manual_seed(0)
+    try:
+        model = AutoModelForCausalLM.from_config(AutoConfig.for_model(name, **kw)).float().eval()
+    except (KeyError, ValueError, ImportError) as e:                 # this transformers has no such family
+        pytest.skip(f"transformers cannot build {name}: {e}")
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.08)                                   # logits with some spread
+            elif ("norm" in n or "ln" in n) and "bias" not in n:
+                p.add_(torch.randn_like(p) * 0.1)                    # gains that are not all one
+    return model
+
+
+@pytest.mark.parametrize("name", sorted(FAMILIES))
+def test_logits_match_transformers(name):
+    model = _hf_model(name)
+    d = tempfile.mkdtemp(prefix=f"parity_{name}_")
+    model.save_pretrained(d, safe_serialization=True)
+    T = 24
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0]
+    cfg = ModelConfig.from_path(d)
+    if cfg.model_type == "mamba2":
+        from mlxcel_b200.models.mamba2 import Mamba2Model, load_mamba2_weights
+        ours = Mamba2Model(cfg, load_mamba2_weights(d, cfg, dtype=torch.float32), max_seqs=2)
+    else:
+        from mlxcel_b200.loading.checkpoint import load_full_weights
+        ours = DecoderModel(cfg, load_full_weights(d, cfg, dtype=torch.float32))
+    pool = KVPool(cfg, 8, 16, device="cpu", dtype=torch.float32, num_layers=len(ours.w.layers))
+    b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
+                  slot_mapping=torch.arange(T, dtype=torch.int32), num_prefill_seqs=1,
+                  pf_block_tables=torch.arange(8, dtype=torch.int32)[None],
+                  pf_cu_q=torch.tensor([0, T], dtype=torch.int32),
+                  pf_context_lens=torch.tensor([T], dtype=torch.int32), pf_max_q_len=T, pf_cu_q_host=[0, T],
+                  logits_rows=torch.arange(T))
+    b.seq_ids, b.pf_starts = [0], [0]
+    got = ours.forward(b, pool.layers).float()
+    err = (got - want).abs().max().item()
+    assert err < 2e-3 * max(want.abs().max().item(), 1.0), f"{name}: max abs error {err:.3e}"
