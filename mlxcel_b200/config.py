@@ -414,6 +414,80 @@ def _minicpm(c: ModelConfig, raw: dict) -> None:
     c.extra["logits_scaling"] = c.hidden_size / float(raw.get("dim_model_base", c.hidden_size))
 
 
+def _phi(c: ModelConfig, raw: dict) -> None:
+    """Phi-1 / Phi-2: one LayerNorm feeding attention and a plain GELU MLP in parallel, partial rotary
+    embedding, biases everywhere including the LM head (reference src/models/phi.rs)."""
+    c.extra["norm"] = "layernorm"
+    c.extra["parallel_block"] = True
+    c.extra["mlp"] = "plain"
+    c.hidden_act = _plain_act(c)
+    c.rms_norm_eps = float(raw.get("layer_norm_eps", 1e-5))
+    c.attention_bias = c.mlp_bias = True
+    if raw.get("qk_layernorm"):
+        raise ValueError("phi with q/k LayerNorm is not supported")
+
+
+def _olmo1(c: ModelConfig, raw: dict) -> None:
+    """OLMo-1: LayerNorm without parameters, otherwise the Llama layout (reference src/models/olmo.rs)."""
+    c.extra["norm"] = "layernorm"
+    c.extra["norm_no_params"] = True
+    c.rms_norm_eps = 1e-5
+    if raw.get("clip_qkv"):
+        raise ValueError("olmo with clip_qkv is not supported")
+
+
+def _granitemoe(c: ModelConfig, raw: dict) -> None:
+    _granite(c, raw)
+    c.moe_route_mode = "topk_softmax"
+    c.moe_intermediate_size = c.intermediate_size
+
+
+def _arcee(c: ModelConfig, raw: dict) -> None:
+    """Llama layout with a plain MLP up -> relu^2 -> down (reference src/models/arcee.rs)."""
+    c.extra["mlp"] = "plain"
+    c.hidden_act = "relu2"
+
+
+def _glm(c: ModelConfig, raw: dict) -> None:
+    """GLM-4 (2024): interleaved RoPE on half of each head, biased q/k/v, fused gate_up projection
+    (reference src/models/glm4.rs)."""
+    c.rope_traditional = True
+    if "partial_rotary_factor" not in raw and not (raw.get("rope_parameters") or {}).get("partial_rotary_factor"):
+        c.partial_rotary_factor = 0.5
+    c.attention_bias = bool(raw.get("attention_bias", True))
+
+
+def _glm4(c: ModelConfig, raw: dict) -> None:
+    """GLM-4-0414: the GLM layout plus norms after attention and after the MLP (sandwich)."""
+    _glm(c, raw)
+    c.post_norms = True
+    c.extra["post_norm_names"] = ("post_self_attn_layernorm", "post_attention_layernorm", "post_mlp_layernorm")
+
+
+def _cohere2(c: ModelConfig, raw: dict) -> None:
+    """Cohere layout with sliding-window layers that rotate and full-attention layers without
+    positional encoding (reference src/models/cohere2.rs)."""
+    _cohere(c, raw)
+    if c.layer_types is None and c.sliding_window:
+        pat = int(raw.get("sliding_window_pattern", 4) or 4)
+        c.layer_types = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention"
+                         for i in range(c.num_hidden_layers)]
+    if c.layer_types:
+        c.extra["nope_layers"] = [i for i, t in enumerate(c.layer_types) if t != "sliding_attention"]
+
+
+def _nemotron(c: ModelConfig, raw: dict) -> None:
+    """Nemotron-4 / Minitron: LayerNorm stored as (weight - 1) with bias, partial rotary embedding,
+    plain MLP up -> relu^2 -> down (reference src/models/nemotron.rs)."""
+    c.extra["norm"] = "layernorm"
+    c.extra["norm_plus_one"] = True
+    c.extra["mlp"] = "plain"
+    c.hidden_act = "relu2"
+    c.rms_norm_eps = float(raw.get("norm_eps", 1e-5))
+    if "partial_rotary_factor" not in raw and not (raw.get("rope_parameters") or {}).get("partial_rotary_factor"):
+        c.partial_rotary_factor = 0.5
+
+
 def _olmoe(c: ModelConfig, raw: dict) -> None:
     _qwen_moe(c, raw)
     c.attention_bias = False
@@ -465,15 +539,19 @@ def _nemotron_h(c: ModelConfig, raw: dict) -> None:
     hs = c.hidden_size
     P = int(raw.get("mamba_head_dim", 64))
     heads = int(raw.get("mamba_num_heads", raw.get("expand", 2) * hs // P))
-    G = int(raw.get("n_groups", 8))
-    lim = raw.get("time_step_limit") or (0.0, float("inf"))
+    G = int(raw.get("n_groups", raw.get("mamba_n_groups", 8)))
+    lim = raw.get("time_step_limit") or raw.get("mamba_dt_limit") or (0.0, float("inf"))
     c.extra["mamba"] = dict(d_inner=heads * P, head_dim=P, n_groups=G,
-                            d_state=int(raw.get("ssm_state_size", 128)), d_conv=int(raw.get("conv_kernel", 4)),
+                            d_state=int(raw.get("ssm_state_size", 128)),
+                            d_conv=int(raw.get("conv_kernel", raw.get("mamba_d_conv", 4))),
                             time_step_limit=(_num(lim[0]), _num(lim[1])), norm_groups=G,
                             use_conv_bias=bool(raw.get("use_conv_bias", True)))
     pat = raw.get("hybrid_override_pattern")
+    if not pat and raw.get("layers_block_type"):      # newer spelling: one word per layer
+        names = {"mamba": "M", "attention": "*", "mlp": "-", "moe": "E"}
+        pat = "".join(names.get(t, "?") for t in raw["layers_block_type"])
     if not pat:
-        raise ValueError("nemotron_h config needs hybrid_override_pattern")
+        raise ValueError("nemotron_h config needs hybrid_override_pattern or layers_block_type")
     c.extra["hybrid_pattern"] = str(pat)
     c.num_hidden_layers = len(pat)
     c.partial_rotary_factor = 0.0
@@ -490,6 +568,7 @@ FAMILIES = {
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
+    "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
 
 

@@ -204,8 +204,9 @@ def _load_attention(g: _Getter, cfg: ModelConfig, p: str, lw_kwargs: dict) -> No
         lw_kwargs["wqkv"] = _cat_rows([g.mat(a + ".q_proj"), g.mat(a + ".k_proj"), g.mat(a + ".v_proj")])
         bs = [g.vec(a + f".{n}_proj.bias") for n in "qkv"]
         lw_kwargs["bqkv"] = torch.cat(bs) if all(b is not None for b in bs) else None
-    lw_kwargs["wo"] = g.mat(a + ".o_proj")
-    lw_kwargs["bo"] = g.vec(a + ".o_proj.bias")
+    ob = a + (".o_proj" if g.has(a + ".o_proj") else ".dense")      # Phi names the output projection "dense"
+    lw_kwargs["wo"] = g.mat(ob)
+    lw_kwargs["bo"] = g.vec(ob + ".bias")
     lw_kwargs["q_norm"] = g.vec(a + ".q_norm.weight")
     lw_kwargs["k_norm"] = g.vec(a + ".k_norm.weight")
     if cfg.norm_weight_bias and lw_kwargs["q_norm"] is not None:
@@ -238,7 +239,8 @@ def _load_dense_mlp(g: _Getter, p: str, lw: LayerWeights) -> None:
 def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
     E = cfg.num_experts
     # router
-    rb = _first(g, p + ".mlp.router", p + ".mlp.gate", p + ".block_sparse_moe.gate")
+    rb = _first(g, p + ".mlp.router", p + ".mlp.gate", p + ".block_sparse_moe.gate",
+                p + ".block_sparse_moe.router.layer")
     r = g.mat(rb)
     if isinstance(r, QuantizedTensor):   # routers are small: keep them dense
         from ..ops.quant import dequantize_ref
@@ -257,6 +259,10 @@ def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
         if bg is not None and bu is not None:
             lw.experts_gate_up_b = torch.cat([bg, bu], dim=-1)
         lw.experts_down_b = bd
+    elif g.src.has(p + ".block_sparse_moe.input_linear.weight"):
+        # GraniteMoE: fused [E, 2I, H] (gate rows first) and [E, H, I]
+        lw.experts_gate_up = g.src.get(p + ".block_sparse_moe.input_linear.weight").to(g.dtype).contiguous()
+        lw.experts_down = g.src.get(p + ".block_sparse_moe.output_linear.weight").to(g.dtype).contiguous()
     elif g.src.has(p + ".mlp.experts.gate_up_proj"):
         # GPT-OSS HF layout: [E, H, 2I] with gate/up interleaved along the last dim
         gu = g.src.get(p + ".mlp.experts.gate_up_proj").to(g.dtype)
@@ -310,6 +316,10 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
         ln1 = g.vec(_first_name(src, p + ".input_layernorm.weight", p + ".attention_layernorm.weight"))
         ln2 = g.vec(_first_name(src, p + ".post_attention_layernorm.weight", p + ".pre_feedforward_layernorm.weight",
                                 p + ".feedforward_layernorm.weight"))
+        if cfg.extra.get("norm_no_params"):                     # OLMo-1: LayerNorm without gain or bias
+            ln1 = ln2 = torch.ones(cfg.hidden_size, dtype=dtype)
+        elif ln2 is None and cfg.extra.get("parallel_block"):
+            ln2 = ln1                                           # one norm feeds both branches
         lw = LayerWeights(ln1=ln1, ln2=ln2, **kw)
         lw.ln1_b = g.vec(p + ".input_layernorm.bias")
         lw.ln2_b = g.vec(p + ".post_attention_layernorm.bias")
@@ -318,13 +328,18 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
             lw.post_mlp_norm = g.vec(p + ".post_feedforward_layernorm.weight")
             lw.ln1 = lw.ln2 = lw.post_attn_norm          # placeholders: this layout has no pre-norms
         if cfg.post_norms:
-            lw.post_attn_norm = g.vec(p + ".post_attention_layernorm.weight")
-            lw.ln2 = g.vec(p + ".pre_feedforward_layernorm.weight")
-            lw.post_mlp_norm = g.vec(p + ".post_feedforward_layernorm.weight")
-        if cfg.is_moe and _first(g, p + ".mlp.router", p + ".mlp.gate", p + ".block_sparse_moe.gate"):
+            names = cfg.extra.get("post_norm_names",
+                                  ("post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"))
+            lw.post_attn_norm = g.vec(f"{p}.{names[0]}.weight")
+            lw.ln2 = g.vec(f"{p}.{names[1]}.weight")
+            lw.post_mlp_norm = g.vec(f"{p}.{names[2]}.weight")
+        if cfg.is_moe and _first(g, p + ".mlp.router", p + ".mlp.gate", p + ".block_sparse_moe.gate",
+                                 p + ".block_sparse_moe.router.layer"):
             _load_moe(g, cfg, p, lw)
         else:
             _load_dense_mlp(g, p, lw)
+        if cfg.extra.get("norm_plus_one"):                      # LayerNorm1P: stored as (weight - 1)
+            lw.ln1, lw.ln2 = lw.ln1 + 1.0, lw.ln2 + 1.0
         if src.has(p + ".mlp.act_fn.alpha_p"):                 # xIELU (Apertus): stored before softplus
             sp = torch.nn.functional.softplus
             beta = float(src.get(p + ".mlp.act_fn.beta")) if src.has(p + ".mlp.act_fn.beta") else 0.5
@@ -332,15 +347,22 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
             lw.act_params = (float(sp(src.get(p + ".mlp.act_fn.alpha_p").float())),
                              beta + float(sp(src.get(p + ".mlp.act_fn.alpha_n").float())), beta, eps_x)
         lws.append(lw)
-    final_norm = g.vec(pre + "norm.weight")
+    final_norm = g.vec(_first_name(src, pre + "norm.weight", pre + "final_layernorm.weight"))
+    if cfg.extra.get("norm_no_params"):
+        final_norm = torch.ones(cfg.hidden_size, dtype=dtype)
+    if cfg.extra.get("norm_plus_one"):
+        final_norm = final_norm + 1.0
     head_base = "lm_head" if g.has("lm_head") else ("language_model.lm_head" if g.has("language_model.lm_head") else None)
     if head_base is not None and not cfg.tie_word_embeddings:
         lm_head = g.mat(head_base)
     else:
         lm_head = emb_q if (emb_q is not None and not dequantize) else emb
     mw = ModelWeights(embed=emb, layers=lws, final_norm=final_norm, lm_head=lm_head)
-    if g.vec(pre + "norm.bias") is not None:
-        mw.extra["final_norm_b"] = g.vec(pre + "norm.bias")
+    fb = g.vec(_first_name(src, pre + "norm.bias", pre + "final_layernorm.bias"))
+    if fb is not None:
+        mw.extra["final_norm_b"] = fb
+    if head_base is not None and g.vec(head_base + ".bias") is not None:
+        mw.extra["lm_head_b"] = g.vec(head_base + ".bias")
     return mw
 
 

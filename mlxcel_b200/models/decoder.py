@@ -285,7 +285,10 @@ class DecoderModel:
             else:
                 h = self.comm.row_parallel_linear(a, lw.wo, lw.bo, h)
                 x = ops.rmsnorm(h, lw.ln2, eps, wb)
-            if cfg.is_moe:
+            if cfg.is_moe and res_mult != 1.0:              # GraniteMoE: scaled expert branch
+                o = self._moe(lw, x, torch.zeros_like(h))
+                h = (h.float() + o.float() * res_mult).to(h.dtype)
+            elif cfg.is_moe:
                 h = self._moe(lw, x, h)
             else:
                 m = self._mlp(lw, x)
@@ -356,6 +359,10 @@ class DecoderModel:
             lg = self.comm.gather_logits(_linear_any(x, w.lm_head))
         else:
             lg = self.comm.lm_head(x, w.lm_head)
+        if w.extra.get("lm_head_b") is not None:
+            if self.comm.tp_size != 1:
+                raise NotImplementedError("LM-head bias with a vocabulary-parallel head")
+            lg = (lg.float() + w.extra["lm_head_b"].float()).to(lg.dtype)
         ls = cfg.extra.get("logits_scaling", 1.0)
         if ls != 1.0:
             lg = (lg.float() / ls).to(lg.dtype)

@@ -135,7 +135,8 @@ def load_hybrid_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cp
             gate = g.mat(m + "gate_proj")
             blocks.append(HybridBlock(kind, norm, up=up if gate is None else torch.cat([gate.to(device), up], 0).contiguous(),
                                       down=need(g.mat(m + "down_proj"), m + "down_proj"), gated=gate is not None))
-    ename = pre + ("embeddings" if src.has(pre + "embeddings.weight") else "embed_tokens")
+    ename = next((pre + n for n in ("embeddings", "embedding", "embed_tokens") if src.has(pre + n + ".weight")),
+                 pre + "embeddings")
     embed = need(g.mat(ename), ename)
     head = g.mat("lm_head") if src.has("lm_head.weight") else None
     return HybridWeights(embed=embed, blocks=blocks,
