@@ -150,7 +150,13 @@ def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, dev
             if cfg.model_type == "gpt_oss":
                 lw.bo = _randn((H,), std, shared, dtype, dev)
         if cfg.qk_norm:
-            lw.q_norm, lw.k_norm = ones(D), ones(D)
+            full = cfg.extra.get("qk_norm_full")              # OLMo-2 / OLMoE: one norm over the projection
+            lw.q_norm, lw.k_norm = (ones(Hq * D), ones(Hkv * D)) if full else (ones(D), ones(D))
+        if cfg.extra.get("norm") == "layernorm" and not cfg.extra.get("norm_no_params") \
+                and cfg.model_type not in ("cohere", "cohere2"):
+            lw.ln1_b, lw.ln2_b = _randn((H,), std, shared, dtype, dev), _randn((H,), std, shared, dtype, dev)
+        if cfg.extra.get("post_norm_only"):
+            lw.post_attn_norm, lw.post_mlp_norm = ones(H), ones(H)
         if cfg.attention_sinks:
             lw.sinks = torch.randn(Hq, generator=gen, device=dev, dtype=torch.float32)
         if cfg.post_norms:
@@ -175,11 +181,14 @@ def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, dev
                 lw.shared_down = _randn((H, si), std, gen, dtype, dev)
                 lw.shared_gate = _randn((1, H), std, shared, dtype, dev)
         else:
-            lw.w_gate_up = _randn((2 * I, H), std, gen, dtype, dev)
+            rows = I if cfg.extra.get("mlp") == "plain" else 2 * I     # plain MLP: fc only, no gate
+            lw.w_gate_up = _randn((rows, H), std, gen, dtype, dev)
             lw.w_down = _randn((H, I), std, gen, dtype, dev)
             if cfg.mlp_bias:
-                lw.b_gate_up = _randn((2 * I,), std, gen, dtype, dev)
+                lw.b_gate_up = _randn((rows,), std, gen, dtype, dev)
                 lw.b_down = _randn((H,), std, shared, dtype, dev)
+            if cfg.hidden_act == "xielu":
+                lw.act_params = (0.8, 0.8, 0.5, -1e-6)
         lws.append(lw)
     if cfg.tie_word_embeddings:
         lm_head = embed[tp_rank * Vl:(tp_rank + 1) * Vl] if vocab_parallel else embed

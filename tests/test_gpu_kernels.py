@@ -471,3 +471,69 @@ def test_tiny_llama_gpu_matches_cpu_reference(fold):
 
     lc, lg = one_pass(cpu, "cpu"), one_pass(gpu, DEV)
     assert (lc - lg).abs().max().item() < 0.05 * lc.abs().max().item() + 0.02
+
+
+@pytest.mark.parametrize("family,extra", [
+    ("starcoder2", {}),                                              # LayerNorm + bias, plain GELU MLP
+    ("cohere", {}),                                                  # parallel block, interleaved RoPE, logit scale
+    ("olmo2", {}),                                                   # post-norm only, whole-projection q/k norm
+    ("nemotron", {}),                                                # LayerNorm1P, partial rotary, relu^2 MLP
+    ("apertus", {}),                                                 # xIELU MLP, per-head q/k norm
+    ("smollm3", dict(num_hidden_layers=4, no_rope_layer_interval=2)),  # layers without positional encoding
+    ("gemma3_text", dict(sliding_window=16, sliding_window_pattern=2, query_pre_attn_scalar=64,
+                         rope_local_base_freq=10000.0, rope_theta=1000000.0)),
+])
+def test_less_common_layouts_gpu_matches_cpu(family, extra):
+    """The layouts outside the main fused path (LayerNorm, plain MLPs, parallel blocks, post-norm only,
+    NoPE layers, per-layer RoPE bases): bf16 GPU kernels against the fp32 CPU statement."""
+    import copy
+
+    from mlxcel_b200.cache.kv_pool import KVPool
+    from mlxcel_b200.config import ModelConfig
+    from mlxcel_b200.models.decoder import DecoderModel, StepBatch
+    from mlxcel_b200.models.weights import random_weights
+    from mlxcel_b200.ops import _lib
+
+    raw = dict(model_type=family, num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
+               head_dim=64, intermediate_size=512, vocab_size=512, max_position_embeddings=512)
+    raw.update(extra)
+    cfg = ModelConfig.from_dict(raw)
+    w32 = random_weights(cfg, seed=5, dtype=torch.float32, std=0.05)
+    w16 = copy.deepcopy(w32)
+    for obj in [w16, *w16.layers]:
+        for k, v in vars(obj).items():
+            if isinstance(v, torch.Tensor):
+                setattr(obj, k, (v.to(torch.bfloat16) if v.dtype == torch.float32 and k != "sinks" else v).to(DEV))
+    if cfg.tie_word_embeddings:
+        w16.lm_head = w16.embed
+    T = 40
+    ids = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+
+    def logits(w, dev, dtype):
+        pool = KVPool(cfg, 8, 16, device=dev, dtype=dtype)
+        b = StepBatch(token_ids=ids.to(dev), positions=torch.arange(T, dtype=torch.int32, device=dev),
+                      slot_mapping=torch.arange(T, dtype=torch.int32, device=dev), num_prefill_seqs=1,
+                      pf_block_tables=torch.arange(8, dtype=torch.int32, device=dev)[None],
+                      pf_cu_q=torch.tensor([0, T], dtype=torch.int32, device=dev),
+                      pf_context_lens=torch.tensor([T], dtype=torch.int32, device=dev), pf_max_q_len=T,
+                      logits_rows=torch.tensor([T - 1, T // 2], device=dev))
+        return DecoderModel(cfg, w).forward(b, pool.layers).float().cpu()
+
+    lc, lg = logits(w32, "cpu", torch.float32), logits(w16, DEV, torch.bfloat16)
+    assert (lc - lg).abs().max().item() < 0.06 * lc.abs().max().item() + 0.03, family
+    torch.cuda.synchronize()
+    assert _lib.read_status(torch.device(DEV)) == 0
+
+
+def test_layernorm_and_activations():
+    from mlxcel_b200.ops import recurrent as R
+    x = (torch.randn(37, 520, device=DEV) * 2 + 0.5).to(torch.bfloat16)
+    w, b = (torch.randn(520, device=DEV) * 0.2 + 1).to(torch.bfloat16), (torch.randn(520, device=DEV) * 0.2).to(torch.bfloat16)
+    for bias in (b, None):
+        got = R.layernorm(x, w, bias, 1e-5)
+        want = R.layernorm(x.cpu().float(), w.cpu().float(), None if bias is None else bias.cpu().float(), 1e-5)
+        assert (got.float().cpu() - want).abs().max().item() < 0.05
+    for kind in ("gelu_tanh", "gelu", "relu2", "silu"):
+        got = R.activation(x, kind)
+        want = R.activation(x.cpu().float(), kind)
+        assert (got.float().cpu() - want).abs().max().item() < 0.05 + 0.01 * want.abs().max().item(), kind
