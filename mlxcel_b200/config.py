@@ -442,6 +442,37 @@ def _granitemoe(c: ModelConfig, raw: dict) -> None:
     c.moe_intermediate_size = c.intermediate_size
 
 
+def _deepseek_routing(c: ModelConfig, raw: dict) -> None:
+    """Sigmoid scores + correction bias + group-limited top-k + scaled weights, shared experts always
+    on, the first ``first_k_dense_replace`` layers dense (DeepSeek-V3 routing; reference
+    src/models/switch_layers.rs group-limited masks, src/models/glm4_moe.rs)."""
+    c.moe_route_mode = "sigmoid_group"
+    c.num_experts = int(raw.get("n_routed_experts", c.num_experts) or 0)
+    c.norm_topk_prob = bool(raw.get("norm_topk_prob", True))
+    c.extra["moe_routing"] = dict(n_group=int(raw.get("n_group", 1) or 1), topk_group=int(raw.get("topk_group", 1) or 1),
+                                  scale=float(raw.get("routed_scaling_factor", 1.0)))
+    c.extra["first_k_dense"] = int(raw.get("first_k_dense_replace", 0) or 0)
+    c.shared_expert_intermediate_size = c.moe_intermediate_size * int(raw.get("n_shared_experts", 0) or 0)
+    c.router_bias = True                         # the correction bias travels in router_b
+
+
+def _glm4_moe(c: ModelConfig, raw: dict) -> None:
+    """GLM-4.5 / 4.6: half-rotary GQA attention with biased q/k/v and optional per-head q/k norm,
+    DeepSeek-V3 style MoE (reference src/models/glm4_moe.rs)."""
+    _deepseek_routing(c, raw)
+    if "partial_rotary_factor" not in raw and not (raw.get("rope_parameters") or {}).get("partial_rotary_factor"):
+        c.partial_rotary_factor = 0.5
+    c.attention_bias = bool(raw.get("attention_bias", False))
+    c.qk_norm = bool(raw.get("use_qk_norm", False))
+
+
+def _dots1(c: ModelConfig, raw: dict) -> None:
+    """dots.llm1: Qwen3-style attention (per-head q/k norm) with DeepSeek-V3 style MoE
+    (reference src/models/dots1.rs)."""
+    _deepseek_routing(c, raw)
+    c.qk_norm = True
+
+
 def _arcee(c: ModelConfig, raw: dict) -> None:
     """Llama layout with a plain MLP up -> relu^2 -> down (reference src/models/arcee.rs)."""
     c.extra["mlp"] = "plain"
@@ -568,7 +599,7 @@ FAMILIES = {
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
-    "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "glm4_moe": _glm4_moe, "dots1": _dots1, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
 
 

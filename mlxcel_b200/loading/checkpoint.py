@@ -247,6 +247,8 @@ def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
         r = dequantize_ref(r, g.dtype)
     lw.router_w = r
     lw.router_b = g.vec(rb + ".bias")
+    if g.src.has(rb + ".e_score_correction_bias"):             # DeepSeek-V3 routing: selection bias (fp32)
+        lw.router_b = g.src.get(rb + ".e_score_correction_bias").float()
     # experts: stacked MLX switch layers, GPT-OSS fused tensors, or per-expert HF modules
     sw = _first(g, p + ".mlp.switch_mlp.gate_proj", p + ".block_sparse_moe.switch_mlp.gate_proj",
                 p + ".mlp.experts.gate_proj")
@@ -282,7 +284,7 @@ def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
             gus.append(_cat_rows([g.mat(f"{root}.{e}.{names[0]}"), g.mat(f"{root}.{e}.{names[1]}")]))
             downs.append(g.mat(f"{root}.{e}.{names[2]}"))
         lw.experts_gate_up, lw.experts_down = _stack(gus), _stack(downs)
-    sh = p + ".mlp.shared_expert"
+    sh = p + (".mlp.shared_experts" if g.has(p + ".mlp.shared_experts.gate_proj") else ".mlp.shared_expert")
     if g.has(sh + ".gate_proj"):
         lw.shared_gate_up = _cat_rows([g.mat(sh + ".gate_proj"), g.mat(sh + ".up_proj")])
         lw.shared_down = g.mat(sh + ".down_proj")

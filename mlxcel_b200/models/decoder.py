@@ -285,10 +285,10 @@ class DecoderModel:
             else:
                 h = self.comm.row_parallel_linear(a, lw.wo, lw.bo, h)
                 x = ops.rmsnorm(h, lw.ln2, eps, wb)
-            if cfg.is_moe and res_mult != 1.0:              # GraniteMoE: scaled expert branch
+            if cfg.is_moe and lw.router_w is not None and res_mult != 1.0:              # GraniteMoE: scaled expert branch
                 o = self._moe(lw, x, torch.zeros_like(h))
                 h = (h.float() + o.float() * res_mult).to(h.dtype)
-            elif cfg.is_moe:
+            elif cfg.is_moe and lw.router_w is not None:
                 h = self._moe(lw, x, h)
             else:
                 m = self._mlp(lw, x)
@@ -320,7 +320,7 @@ class DecoderModel:
             else:
                 h = self.comm.row_parallel_linear(a, lw.wo, lw.bo, h)
                 x = self._norm(h, lw.ln2, lw.ln2_b)
-                if cfg.is_moe:
+                if cfg.is_moe and lw.router_w is not None:
                     h = self._moe(lw, x, h)
                 else:
                     h = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, h)
@@ -341,7 +341,7 @@ class DecoderModel:
                 h = self.comm.row_parallel_linear(m, lw.w_down, lw.b_down, h, ssq_out=ssq)
             else:
                 x = ops.rmsnorm(h, lw.ln2, eps, wb)
-                if cfg.is_moe:
+                if cfg.is_moe and lw.router_w is not None:
                     h = self._moe(lw, x, h)
                 else:
                     h = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, h)

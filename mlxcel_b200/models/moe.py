@@ -25,8 +25,14 @@ def _dense(w):
 
 def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -> torch.Tensor:
     """Returns the new residual stream ``h + moe(x)`` (bf16 [T, H])."""
-    logits = ops.linear(x, lw.router_w, bias=lw.router_b)
-    ids, wts = moe_ops.route(logits, cfg.num_experts_per_tok, cfg.moe_route_mode, cfg.norm_topk_prob)
+    if cfg.moe_route_mode == "sigmoid_group":
+        r = cfg.extra["moe_routing"]
+        logits = x.float() @ lw.router_w.float().t()            # the router runs in fp32
+        ids, wts = moe_ops.route_sigmoid_grouped(logits, cfg.num_experts_per_tok, lw.router_b, r["n_group"],
+                                                 r["topk_group"], cfg.norm_topk_prob, r["scale"])
+    else:
+        logits = ops.linear(x, lw.router_w, bias=lw.router_b)
+        ids, wts = moe_ops.route(logits, cfg.num_experts_per_tok, cfg.moe_route_mode, cfg.norm_topk_prob)
     ep, ep_rank = comm.ep_size, comm.ep_rank
     # packed expert weights stay packed: the grouped GEMM unpacks the tiles of routed experts only
     gate_up, down = lw.experts_gate_up, lw.experts_down

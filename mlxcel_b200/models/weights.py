@@ -161,13 +161,15 @@ def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, dev
             lw.sinks = torch.randn(Hq, generator=gen, device=dev, dtype=torch.float32)
         if cfg.post_norms:
             lw.post_attn_norm, lw.post_mlp_norm = ones(H), ones(H)
-        if cfg.is_moe:
+        if cfg.is_moe and li >= cfg.extra.get("first_k_dense", 0):
             E = cfg.num_experts
             El = E // ep_size
             mi = cfg.moe_intermediate_size // tp_size
             lw.router_w = _randn((E, H), std, shared, dtype, dev)
             if cfg.router_bias:
                 lw.router_b = _randn((E,), std, shared, dtype, dev)
+                if cfg.moe_route_mode == "sigmoid_group":          # selection bias, kept in fp32
+                    lw.router_b = lw.router_b.float() * 5
             lw.experts_gate_up = _randn((El, 2 * mi, H), std, gen, dtype, dev)
             lw.experts_down = _randn((El, H, mi), std, gen, dtype, dev)
             if cfg.expert_bias:
@@ -179,7 +181,8 @@ def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, dev
                 si = cfg.shared_expert_intermediate_size // tp_size
                 lw.shared_gate_up = _randn((2 * si, H), std, gen, dtype, dev)
                 lw.shared_down = _randn((H, si), std, gen, dtype, dev)
-                lw.shared_gate = _randn((1, H), std, shared, dtype, dev)
+                if cfg.moe_route_mode != "sigmoid_group":          # Qwen2-MoE gates its shared expert
+                    lw.shared_gate = _randn((1, H), std, shared, dtype, dev)
         else:
             rows = I if cfg.extra.get("mlp") == "plain" else 2 * I     # plain MLP: fc only, no gate
             lw.w_gate_up = _randn((rows, H), std, gen, dtype, dev)

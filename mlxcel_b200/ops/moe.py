@@ -53,6 +53,28 @@ def moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up=None, b_down=N
     return out
 
 
+def route_sigmoid_grouped(logits: torch.Tensor, k: int, bias: torch.Tensor | None, n_group: int, topk_group: int,
+                          norm_topk: bool, scale: float):
+    """DeepSeek-V3-style routing (GLM-4-MoE, dots1, ...): sigmoid scores; experts are CHOSEN by
+    score + correction bias, restricted to the ``topk_group`` groups with the best sum of their two
+    top biased scores, but WEIGHTED by the unbiased score (normalised over the k, times ``scale``).
+    Plain tensor ops on the small [T, E] matrix (reference src/models/switch_layers.rs group-limited
+    routing masks). Returns (ids int32 [T, k], weights fp32 [T, k])."""
+    T, E = logits.shape
+    scores = torch.sigmoid(logits.float())
+    choice = scores if bias is None else scores + bias.float()
+    if n_group > 1:
+        grp = choice.view(T, n_group, E // n_group)
+        gscore = grp.topk(min(2, E // n_group), dim=-1)[0].sum(-1)
+        keep = torch.zeros_like(gscore).scatter_(1, gscore.topk(topk_group, dim=-1)[1], 1.0)
+        choice = choice.masked_fill(~keep.bool().unsqueeze(-1).expand(T, n_group, E // n_group).reshape(T, E), 0.0)
+    ids = choice.topk(k, dim=-1)[1]
+    w = scores.gather(1, ids)
+    if norm_topk:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return ids.to(torch.int32).contiguous(), (w * scale).contiguous()
+
+
 # ----------------------------------------------------------------------------- CUDA
 def route(logits: torch.Tensor, k: int, mode: str = "topk_softmax", norm_topk: bool = True):
     """Router logits [T, E] → (expert ids [T, k] int32, weights [T, k] fp32)."""

@@ -480,6 +480,8 @@ def test_tiny_llama_gpu_matches_cpu_reference(fold):
     ("nemotron", {}),                                                # LayerNorm1P, partial rotary, relu^2 MLP
     ("apertus", {}),                                                 # xIELU MLP, per-head q/k norm
     ("smollm3", dict(num_hidden_layers=4, no_rope_layer_interval=2)),  # layers without positional encoding
+    ("glm4_moe", dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, n_shared_experts=1,
+                      n_group=2, topk_group=1, first_k_dense_replace=1, routed_scaling_factor=1.5, use_qk_norm=True)),
     ("gemma3_text", dict(sliding_window=16, sliding_window_pattern=2, query_pre_attn_scalar=64,
                          rope_local_base_freq=10000.0, rope_theta=1000000.0)),
 ])

@@ -37,6 +37,11 @@ FAMILIES = {
     "qwen3_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48, head_dim=32,
                       decoder_sparse_step=1, mlp_only_layers=[]),
     "olmoe": dict(num_experts=4, num_experts_per_tok=2),
+    "glm4_moe": dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=48, n_shared_experts=1, n_group=2,
+                     topk_group=1, first_k_dense_replace=1, routed_scaling_factor=1.5, head_dim=16, use_qk_norm=True,
+                     pad_token_id=0, attention_bias=True),
+    "dots1": dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=48, n_shared_experts=2, n_group=2,
+                  topk_group=1, first_k_dense_replace=1, routed_scaling_factor=2.0, head_dim=16),
     "gpt_oss": dict(num_local_experts=4, num_experts_per_tok=2, head_dim=16, **SLIDING),
     "mamba2": dict(num_heads=8, head_dim=16, state_size=16, n_groups=1, expand=2, conv_kernel=4, chunk_size=8),
 }
@@ -56,6 +61,9 @@ def _hf_model(name: str):
     except (KeyError, ValueError, ImportError) as e:                 # this transformers has no such family
         pytest.skip(f"transformers cannot build {name}: {e}")
     with torch.no_grad():
+        for n, buf in model.named_buffers():
+            if "e_score_correction_bias" in n:
+                buf.copy_(torch.randn_like(buf) * 0.2)               # a selection bias that changes the choice
         for n, p in model.named_parameters():
             if p.dim() >= 2:
                 p.normal_(0, 0.08)                                   # logits with some spread
