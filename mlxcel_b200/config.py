@@ -466,6 +466,25 @@ def _glm4_moe(c: ModelConfig, raw: dict) -> None:
     c.qk_norm = bool(raw.get("use_qk_norm", False))
 
 
+def _ernie4_5_moe(c: ModelConfig, raw: dict) -> None:
+    """ERNIE 4.5 MoE: interleaved RoPE, softmax routing with a selection bias, shared experts, dense
+    layers before ``moe_layer_start_index`` (reference src/models/ernie4_5_moe.rs)."""
+    c.rope_traditional = True
+    c.moe_route_mode = "sigmoid_group"
+    c.num_experts = int(raw.get("moe_num_experts", 0) or 0)
+    c.num_experts_per_tok = int(raw.get("moe_k", 2))
+    c.moe_intermediate_size = int(raw.get("moe_intermediate_size", c.intermediate_size))
+    c.norm_topk_prob = True
+    c.extra["moe_routing"] = dict(n_group=1, topk_group=1, scale=1.0, score="softmax",
+                                  norm_min=float(raw.get("moe_norm_min", 1e-12)))
+    c.extra["first_k_dense"] = int(raw.get("moe_layer_start_index", 0) or 0)
+    if int(raw.get("moe_layer_interval", 1) or 1) != 1:
+        raise ValueError("ernie4_5_moe with moe_layer_interval != 1 is not supported")
+    c.shared_expert_intermediate_size = c.moe_intermediate_size * int(raw.get("moe_num_shared_experts", 0) or 0)
+    c.router_bias = True
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
+
+
 def _dots1(c: ModelConfig, raw: dict) -> None:
     """dots.llm1: Qwen3-style attention (per-head q/k norm) with DeepSeek-V3 style MoE
     (reference src/models/dots1.rs)."""
@@ -599,7 +618,7 @@ FAMILIES = {
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
-    "glm4_moe": _glm4_moe, "dots1": _dots1, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
 
 

@@ -29,7 +29,8 @@ def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -
         r = cfg.extra["moe_routing"]
         logits = x.float() @ lw.router_w.float().t()            # the router runs in fp32
         ids, wts = moe_ops.route_sigmoid_grouped(logits, cfg.num_experts_per_tok, lw.router_b, r["n_group"],
-                                                 r["topk_group"], cfg.norm_topk_prob, r["scale"])
+                                                 r["topk_group"], cfg.norm_topk_prob, r["scale"], r.get("score", "sigmoid"),
+                                                 r.get("norm_min", 1e-20))
     else:
         logits = ops.linear(x, lw.router_w, bias=lw.router_b)
         ids, wts = moe_ops.route(logits, cfg.num_experts_per_tok, cfg.moe_route_mode, cfg.norm_topk_prob)

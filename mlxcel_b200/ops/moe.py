@@ -54,15 +54,16 @@ def moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up=None, b_down=N
 
 
 def route_sigmoid_grouped(logits: torch.Tensor, k: int, bias: torch.Tensor | None, n_group: int, topk_group: int,
-                          norm_topk: bool, scale: float):
+                          norm_topk: bool, scale: float, score: str = "sigmoid", norm_min: float = 1e-20):
     """DeepSeek-V3-style routing (GLM-4-MoE, dots1, ...): sigmoid scores; experts are CHOSEN by
     score + correction bias, restricted to the ``topk_group`` groups with the best sum of their two
     top biased scores, but WEIGHTED by the unbiased score (normalised over the k, times ``scale``).
+    ``score="softmax"`` is the ERNIE-4.5-MoE variant (softmax probabilities, the same selection bias).
     Plain tensor ops on the small [T, E] matrix (reference src/models/switch_layers.rs group-limited
     routing masks). Returns (ids int32 [T, k], weights fp32 [T, k])."""
     T, E = logits.shape
-    scores = torch.sigmoid(logits.float())
-    choice = scores if bias is None else scores + bias.float()
+    scores = torch.sigmoid(logits.float()) if score == "sigmoid" else torch.softmax(logits.float(), dim=-1)
+    choice = scores if bias is None else scores + bias.float().reshape(1, E)
     if n_group > 1:
         grp = choice.view(T, n_group, E // n_group)
         gscore = grp.topk(min(2, E // n_group), dim=-1)[0].sum(-1)
@@ -71,7 +72,7 @@ def route_sigmoid_grouped(logits: torch.Tensor, k: int, bias: torch.Tensor | Non
     ids = choice.topk(k, dim=-1)[1]
     w = scores.gather(1, ids)
     if norm_topk:
-        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        w = w / (w.sum(-1, keepdim=True) + norm_min if score == "sigmoid" else w.sum(-1, keepdim=True).clamp(min=norm_min))
     return ids.to(torch.int32).contiguous(), (w * scale).contiguous()
 
 

@@ -40,6 +40,8 @@ FAMILIES = {
     "glm4_moe": dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=48, n_shared_experts=1, n_group=2,
                      topk_group=1, first_k_dense_replace=1, routed_scaling_factor=1.5, head_dim=16, use_qk_norm=True,
                      pad_token_id=0, attention_bias=True),
+    "ernie4_5_moe": dict(moe_num_experts=4, moe_k=2, moe_intermediate_size=48, moe_num_shared_experts=1,
+                         moe_layer_start_index=1, head_dim=16, pad_token_id=0),
     "dots1": dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=48, n_shared_experts=2, n_group=2,
                   topk_group=1, first_k_dense_replace=1, routed_scaling_factor=2.0, head_dim=16),
     "gpt_oss": dict(num_local_experts=4, num_experts_per_tok=2, head_dim=16, **SLIDING),
