@@ -436,6 +436,30 @@ def _olmo1(c: ModelConfig, raw: dict) -> None:
         raise ValueError("olmo with clip_qkv is not supported")
 
 
+def _granitemoehybrid(c: ModelConfig, raw: dict) -> None:
+    """Granite 4 hybrid: every layer is a Mamba2 or an attention mixer followed by a gated shared
+    MLP, with Granite's embedding / residual / attention / logit multipliers; attention carries RoPE
+    only when ``position_embedding_type == "rope"`` (reference src/models/granitemoehybrid.rs).
+    Runs on the hybrid executor as the block pattern ``MG`` / ``*G`` per layer."""
+    _granite(c, raw)
+    if int(raw.get("num_local_experts", 0) or 0) > 0:
+        raise ValueError("granitemoehybrid with routed experts is not supported (dense shared MLP only)")
+    c.num_experts = 0
+    P = int(raw.get("mamba_d_head", 64))
+    heads = int(raw.get("mamba_n_heads", raw.get("mamba_expand", 2) * c.hidden_size // P))
+    lim = raw.get("time_step_limit") or (0.0, float("inf"))
+    c.extra["mamba"] = dict(d_inner=heads * P, head_dim=P, n_groups=int(raw.get("mamba_n_groups", 1)),
+                            d_state=int(raw.get("mamba_d_state", 128)), d_conv=int(raw.get("mamba_d_conv", 4)),
+                            time_step_limit=(_num(lim[0]), _num(lim[1])), norm_groups=1)
+    types = raw.get("layer_types") or ["mamba"] * c.num_hidden_layers
+    c.extra["hybrid_pattern"] = "".join(("M" if t == "mamba" else "*") + "G" for t in types)
+    c.extra["hybrid_layout"] = "granite"
+    c.extra["mlp_size"] = int(raw.get("shared_intermediate_size", c.intermediate_size))
+    c.layer_types = None
+    if raw.get("position_embedding_type") != "rope":
+        c.partial_rotary_factor = 0.0
+
+
 def _granitemoe(c: ModelConfig, raw: dict) -> None:
     _granite(c, raw)
     c.moe_route_mode = "topk_softmax"
@@ -618,7 +642,7 @@ FAMILIES = {
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
-    "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
 
 

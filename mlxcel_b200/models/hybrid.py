@@ -49,12 +49,13 @@ class HybridWeights:
     layers: list = field(default_factory=list)  # the attention blocks' LayerWeights (= KV-pool layers)
 
 
-_KINDS = {"M": "mamba2", "*": "attention", "-": "mlp"}
+_KINDS = {"M": "mamba2", "*": "attention", "-": "mlp", "G": "mlp"}      # G: gated MLP block
 
 
 def block_kinds(cfg: ModelConfig) -> list[str]:
     pat = cfg.extra["hybrid_pattern"]
-    if len(pat) != cfg.num_hidden_layers:
+    per_layer = 2 if cfg.extra.get("hybrid_layout") == "granite" else 1
+    if len(pat) != cfg.num_hidden_layers * per_layer:
         raise ValueError(f"hybrid pattern has {len(pat)} entries for {cfg.num_hidden_layers} layers")
     try:
         return [_KINDS[c] for c in pat]
@@ -144,6 +145,55 @@ def load_hybrid_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cp
                          lm_head=embed if head is None else head.to(device), layers=attn_layers)
 
 
+def load_granite_hybrid_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
+    """Granite 4 hybrid checkpoint: ``model.layers.N.{input_layernorm, mamba.* | self_attn.*,
+    post_attention_layernorm, shared_mlp.input_linear / output_linear}``; each layer becomes a mixer
+    block and a gated-MLP block."""
+    from ..loading.checkpoint import TensorSource, _Getter
+
+    src = TensorSource(path)
+    g = _Getter(src, cfg, dtype, dequantize=True)
+    d = mamba_dims(cfg)
+
+    def need(t, name):
+        if t is None:
+            raise KeyError(f"{path}: missing tensor {name}")
+        return t.to(device)
+
+    blocks, attn_layers = [], []
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        norm = need(g.vec(p + "input_layernorm.weight"), p + "input_layernorm.weight")
+        if src.has(p + "mamba.in_proj.weight"):
+            m = p + "mamba."
+            cw = need(g.vec(m + "conv1d.weight"), m + "conv1d.weight")
+            cw = cw.reshape(d["conv_dim"], d["K"]) if cw.dim() == 2 or cw.shape[1] == 1 else cw.squeeze(-1)
+            cb = g.vec(m + "conv1d.bias")
+            lw = Mamba2LayerWeights(
+                norm=norm, in_proj=need(g.mat(m + "in_proj"), m + "in_proj"), conv_w=cw.float(),
+                conv_b=None if cb is None else cb.float().to(device),
+                dt_bias=need(g.vec(m + "dt_bias"), m + "dt_bias").float(),
+                A_log=need(g.vec(m + "A_log"), m + "A_log").float(), D=need(g.vec(m + "D"), m + "D").float(),
+                gnorm=need(g.vec(m + "norm.weight"), m + "norm.weight"),
+                out_proj=need(g.mat(m + "out_proj"), m + "out_proj"))
+            blocks.append(HybridBlock("mamba2", norm, mamba=lw))
+        else:
+            a = p + "self_attn."
+            q, k, v = (need(g.mat(a + n), a + n) for n in ("q_proj", "k_proj", "v_proj"))
+            lw = LayerWeights(ln1=norm, ln2=norm, wqkv=torch.cat([q, k, v], 0).contiguous(),
+                              wo=need(g.mat(a + "o_proj"), a + "o_proj"))
+            attn_layers.append(lw)
+            blocks.append(HybridBlock("attention", norm, attn=lw))
+        s = p + "shared_mlp."
+        blocks.append(HybridBlock("mlp", need(g.vec(p + "post_attention_layernorm.weight"), p + "post_attention_layernorm"),
+                                  up=need(g.mat(s + "input_linear"), s + "input_linear"),
+                                  down=need(g.mat(s + "output_linear"), s + "output_linear"), gated=True))
+    embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")
+    head = g.mat("lm_head") if src.has("lm_head.weight") and not cfg.tie_word_embeddings else None
+    return HybridWeights(embed=embed, blocks=blocks, final_norm=need(g.vec("model.norm.weight"), "model.norm.weight"),
+                         lm_head=embed if head is None else head.to(device), layers=attn_layers)
+
+
 def hybrid_config_dict(cfg: ModelConfig) -> dict:
     d = mamba_dims(cfg)
     return dict(model_type="nemotron_h", vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
@@ -223,24 +273,31 @@ class HybridModel:
         pieces = self.ssm.pieces(b)
         h = hidden_in if hidden_in is not None else ops.embedding(b.token_ids, self.w.embed, cfg.embed_scale)
         mi = ai = 0
+        rm = float(cfg.extra.get("residual_multiplier", 1.0))     # Granite: every branch is scaled
+
+        def add(branch_in, w, bias=None):
+            if rm == 1.0:
+                return ops.linear(branch_in, w, bias=bias, residual=h)
+            return (h.float() + ops.linear(branch_in, w, bias=bias).float() * rm).to(h.dtype)
+
         for blk in self.w.blocks:
             x = ops.rmsnorm(h, blk.norm, eps, 0.0)
             if blk.kind == "mamba2":
-                y = self.ssm._mixer(mi, blk.mamba, x, pieces)
-                h = ops.linear(y, blk.mamba.out_proj, residual=h)
+                h = add(self.ssm._mixer(mi, blk.mamba, x, pieces), blk.mamba.out_proj)
                 mi += 1
             elif blk.kind == "attention":
-                a = self.attn._attention(ai, blk.attn, x, b, kv_layers[ai])
-                h = ops.linear(a, blk.attn.wo, bias=blk.attn.bo, residual=h)
+                h = add(self.attn._attention(ai, blk.attn, x, b, kv_layers[ai]), blk.attn.wo, blk.attn.bo)
                 ai += 1
             elif blk.gated:
-                h = ops.linear(ops.glu_linear(x, blk.up, blk.up.shape[0] // 2, "silu"), blk.down, residual=h)
+                h = add(ops.glu_linear(x, blk.up, blk.up.shape[0] // 2, "silu"), blk.down)
             else:
-                h = ops.linear(rops.relu2(ops.linear(x, blk.up)), blk.down, residual=h)
+                h = add(rops.relu2(ops.linear(x, blk.up)), blk.down)
         return h
 
     def logits(self, h: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:
-        return self.ssm.logits(h, rows)
+        lg = self.ssm.logits(h, rows)
+        ls = self.cfg.extra.get("logits_scaling", 1.0)
+        return lg if ls == 1.0 else (lg.float() / ls).to(lg.dtype)
 
     def forward(self, b: StepBatch, kv_layers=None) -> torch.Tensor:
         return self.logits(self.forward_hidden(b, kv_layers), b.logits_rows)

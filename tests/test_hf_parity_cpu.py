@@ -149,3 +149,62 @@ def test_nemotron_h_hybrid_matches_transformers():
     got = ours.forward(b, pool.layers).float()
     err = (got - want).abs().max().item()
     assert err < 4e-3 * max(want.abs().max().item(), 1.0), f"max abs error {err:.3e}"
+
+
+@pytest.mark.parametrize("pos", [None, "rope"])
+def test_granite_hybrid_matches_transformers(pos):
+    """Granite 4 hybrid (Mamba2 / attention mixers + gated shared MLP per layer, Granite multipliers,
+    attention with or without RoPE) on the hybrid executor, and a greedy run through the LLM front end."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    from mlxcel_b200.engine.engine import EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.llm import LLM
+    from mlxcel_b200.models.hybrid import HybridModel, load_granite_hybrid_weights
+
+    torch.manual_seed(0)
+    try:
+        hc = AutoConfig.for_model(
+            "granitemoehybrid", hidden_size=64, intermediate_size=128, shared_intermediate_size=96, num_hidden_layers=4,
+            num_attention_heads=4, num_key_value_heads=2, vocab_size=300, max_position_embeddings=256,
+            layer_types=["mamba", "attention", "mamba", "mamba"], num_local_experts=0, mamba_n_heads=8, mamba_d_head=16,
+            mamba_d_state=16, mamba_n_groups=2, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=8,
+            embedding_multiplier=2.0, residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=3.0,
+            position_embedding_type=pos)
+        model = AutoModelForCausalLM.from_config(hc).float().eval()
+    except (KeyError, ValueError, ImportError) as e:
+        pytest.skip(f"transformers cannot build granitemoehybrid: {e}")
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.08)
+            elif "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tempfile.mkdtemp(prefix="parity_granite_hybrid_")
+    model.save_pretrained(d, safe_serialization=True)
+    T = 24
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0]
+    cfg = ModelConfig.from_path(d)
+    assert cfg.extra["hybrid_pattern"] == "MG*GMGMG" and (cfg.rot_dim > 0) == (pos == "rope")
+    ours = HybridModel(cfg, load_granite_hybrid_weights(d, cfg, dtype=torch.float32), max_seqs=2)
+    pool = KVPool(cfg, 8, 16, device="cpu", dtype=torch.float32, num_layers=ours.num_kv_layers)
+    b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
+                  slot_mapping=torch.arange(T, dtype=torch.int32), num_prefill_seqs=1,
+                  pf_block_tables=torch.arange(8, dtype=torch.int32)[None],
+                  pf_cu_q=torch.tensor([0, T], dtype=torch.int32),
+                  pf_context_lens=torch.tensor([T], dtype=torch.int32), pf_max_q_len=T, pf_cu_q_host=[0, T],
+                  logits_rows=torch.arange(T))
+    b.seq_ids, b.pf_starts = [0], [0]
+    got = ours.forward(b, pool.layers).float()
+    err = (got - want).abs().max().item()
+    assert err < 2e-3 * max(want.abs().max().item(), 1.0), f"max abs error {err:.3e}"
+    if pos is None:
+        llm = LLM.from_pretrained(d, device="cpu", engine_config=EngineConfig(num_blocks=32, block_size=16, max_batch=4,
+                                                                               max_model_len=128))
+        out = llm.generate(prompt_token_ids=[ids[:12].tolist()],
+                           sampling_params=SamplingParams(max_tokens=4, ignore_eos=True))[0].output
+        with torch.no_grad():
+            ref = model.generate(ids[None, :12], max_new_tokens=4, do_sample=False)[0, 12:].tolist()
+        assert out == ref
