@@ -169,6 +169,7 @@ def cmd_serve(a):
         keys |= {l.strip() for l in open(a.api_key_file) if l.strip()}
     state = ServerState(worker, llm.tokenizer, worker.model_id, api_keys=keys,
                         chat_template=open(a.chat_template_file).read() if a.chat_template_file else None)
+    state.slot_save_path = a.slot_save_path
     from .lora import LoraManager
     from .models.weights import QuantizedTensor
     if not any(isinstance(lw.wqkv, QuantizedTensor) for lw in llm.model.w.layers):
@@ -179,6 +180,20 @@ def cmd_serve(a):
             state.lora.add(path, float(sc) if sc else 1.0)
     uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="info" if a.verbose else "warning",
                 ssl_certfile=a.ssl_cert_file, ssl_keyfile=a.ssl_key_file)
+
+
+def cmd_router(a):
+    """Router mode: a pool of models behind one listener (see server/router.py)."""
+    import torch
+    import uvicorn
+
+    from .server.router import create_router_app
+    keys = set(a.api_key or [])
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    app = create_router_app(a.models_dir, a.models_preset, a.models_max, device=dev, api_keys=keys,
+                            default=a.default_model,
+                            engine_defaults=dict(ctx_size=a.ctx_size, parallel=a.parallel))
+    uvicorn.run(app, host=a.host, port=a.port, log_level="info" if a.verbose else "warning")
 
 
 def cmd_inspect(a):
@@ -255,6 +270,7 @@ def main(argv=None):
     p.add_argument("--api-key-file", default=None)
     p.add_argument("--alias", "-a", default=None)
     p.add_argument("--chat-template-file", default=None)
+    p.add_argument("--slot-save-path", default=None, help="directory for POST /slots/{id}?action=save|restore")
     p.add_argument("--lora", action="append", default=None, metavar="DIR[=SCALE]",
                    help="attach a LoRA adapter directory (repeatable); scales can be changed live via /lora-adapters")
     p.add_argument("--debug-trace", "--debug-pp-trace", dest="debug_trace", default=None, metavar="FILE",
@@ -264,6 +280,19 @@ def main(argv=None):
     p.add_argument("--ssl-key-file", default=None)
     p.add_argument("-v", "--verbose", action="store_true")
     p.set_defaults(fn=cmd_serve)
+    p = sub.add_parser("router", help="HTTP server over a pool of models (loaded on demand, LRU eviction)")
+    p.add_argument("--models-dir", default=None, help="every sub-directory with a config.json is a model")
+    p.add_argument("--models-preset", default=None, metavar="INI", help="[name] sections: model = <path> + options")
+    p.add_argument("--models-max", type=int, default=1, help="resident models")
+    p.add_argument("--default-model", default=None)
+    p.add_argument("--device", default=None)
+    p.add_argument("-c", "--ctx-size", type=int, default=8192)
+    p.add_argument("--parallel", "-np", type=int, default=4)
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=8080)
+    p.add_argument("--api-key", action="append")
+    p.add_argument("-v", "--verbose", action="store_true")
+    p.set_defaults(fn=cmd_router)
     p = sub.add_parser("inspect", help="memory estimate")
     _add_model_args(p)
     p.set_defaults(fn=cmd_inspect)

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import asyncio
 import json
+import os
 import time
 import uuid
 
@@ -73,6 +74,7 @@ class ServerState:
         self.started = time.time()
         self.responses: dict[str, dict] = {}
         self.lora = None      # LoraManager when the weights are dense
+        self.slot_save_path: str | None = None     # --slot-save-path: directory for /slots/{id}?action=save
 
     def render(self, messages, tools=None, **kw) -> str:
         return render_chat(messages, self.chat_template, tools=tools,
@@ -152,6 +154,53 @@ def create_app(state: ServerState) -> FastAPI:
     @app.get("/slots")
     async def slots():
         return state.worker.slots()
+
+    @app.post("/slots/{slot_id}")
+    async def slot_action(slot_id: int, request: Request, action: str = ""):
+        """llama-server slot persistence (reference src/server/slot_persist.rs:15-60): ``save`` writes the
+        token stream of the slot's last occupant to ``<slot-save-path>/<filename>``, ``restore`` reads
+        one back and prefills it so that its KV blocks are in the prefix cache again, ``erase`` drops
+        the cached prefixes."""
+        if action not in ("save", "restore", "erase"):
+            return _err(400, "action must be save, restore or erase")
+        t0 = time.perf_counter()
+        if action == "erase":
+            n = state.worker.run_exclusive(lambda: state.worker.engine.bm.reset_prefix_cache())
+            return dict(id_slot=slot_id, n_erased=n)
+        if not state.slot_save_path:
+            return _err(501, "This server does not support slots action. Start it with `--slot-save-path`",
+                        "not_supported_error")
+        try:
+            body = await request.json()
+        except Exception:
+            body = {}
+        name = str(body.get("filename", ""))
+        if not name or name != os.path.basename(name) or name.startswith("."):
+            return _err(400, "filename must be a plain file name")
+        path = os.path.join(state.slot_save_path, name)
+        if action == "save":
+            toks = state.worker.recent.get(slot_id)
+            if toks is None:
+                return _err(404, f"slot {slot_id} has no finished sequence to save")
+            data = json.dumps(dict(model=state.model_id, tokens=toks)).encode()
+            os.makedirs(state.slot_save_path, exist_ok=True)
+            with open(path, "wb") as f:
+                f.write(data)
+            return dict(id_slot=slot_id, filename=name, n_saved=len(toks), n_written=len(data),
+                        timings=dict(save_ms=(time.perf_counter() - t0) * 1e3))
+        if not os.path.exists(path):
+            return _err(404, f"no saved slot {name!r}")
+        with open(path, "rb") as f:
+            raw = f.read()
+        saved = json.loads(raw)
+        if saved.get("model") != state.model_id:
+            return _err(400, f"slot file belongs to model {saved.get('model')!r}")
+        toks = [int(t) for t in saved["tokens"]]
+        async for ev in _generate(state, toks, SamplingParams(max_tokens=1, temperature=0.0)):
+            if ev.kind == "error":
+                return _err(500, ev.text or "restore failed", "server_error")
+        return dict(id_slot=slot_id, filename=name, n_restored=len(toks), n_read=len(raw),
+                    timings=dict(restore_ms=(time.perf_counter() - t0) * 1e3))
 
     @app.get("/metrics")
     async def metrics():

@@ -52,6 +52,7 @@ class GenRequest:
 
 class ModelWorker:
     def __init__(self, engine: Engine, tokenizer, model_id: str = "model"):
+        self.recent: dict[int, list[int]] = {}    # slot id -> tokens of its last finished sequence
         self.engine, self.tokenizer, self.model_id = engine, tokenizer, model_id
         self.inbox: "queue.Queue[GenRequest | tuple]" = queue.Queue()
         self.by_seq: dict[int, GenRequest] = {}
@@ -148,6 +149,8 @@ class ModelWorker:
         usage = dict(prompt_tokens=n_prompt, completion_tokens=n_out, total_tokens=n_prompt + n_out,
                      prompt_tokens_details=dict(cached_tokens=seq.num_cached))
         self._emit(req, GenEvent("done", text=tail, finish_reason=reason, usage=usage, timings=timings))
+        # token stream of the slot's last occupant (what /slots/{id}?action=save writes out)
+        self.recent[seq.seq_id % max(1, self.engine.ecfg.max_batch)] = list(seq.prompt) + list(seq.output)
         self.engine.release(seq.seq_id)
 
     def _run(self) -> None:

@@ -151,3 +151,36 @@ def test_lora_routes_change_weights_between_steps(tmp_path):
         assert torch.allclose(w.layers[0].wo, before, atol=1e-5)
         assert c.post("/lora-adapters", json=[{"id": 9, "scale": 1.0}]).status_code == 400
     worker.shutdown()
+
+
+def test_slot_save_restore_erase(tmp_path):
+    """POST /slots/{id}?action=save|restore|erase: the token stream of a finished request is written
+    out, read back (its blocks return to the prefix cache: the same prompt then hits it) and dropped."""
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, seed=0, dtype=torch.float32, std=0.05)
+    eng = Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=4, max_num_batched_tokens=256, num_blocks=128,
+                                                         max_model_len=512, cuda_graphs=False))
+    tk = ByteTokenizer(cfg.vocab_size)
+    worker = ModelWorker(eng, tk, "tiny")
+    state = ServerState(worker, tk, "tiny")
+    with TestClient(create_app(state)) as c:
+        prompt = "The quick brown fox jumps over the lazy dog, again and again and again."
+        r = c.post("/completion", json=dict(prompt=prompt, n_predict=4, temperature=0)).json()
+        slot = next(iter(worker.recent))
+        assert c.post(f"/slots/{slot}?action=save", json=dict(filename="a.bin")).status_code == 501
+        state.slot_save_path = str(tmp_path)
+        assert c.post(f"/slots/{slot}?action=save", json=dict(filename="../a.bin")).status_code == 400
+        sv = c.post(f"/slots/{slot}?action=save", json=dict(filename="a.bin")).json()
+        assert sv["n_saved"] == r["tokens_evaluated"] + r["tokens_predicted"] and (tmp_path / "a.bin").exists()
+        er = c.post(f"/slots/{slot}?action=erase").json()
+        assert er["n_erased"] > 0
+        cold = c.post("/completion", json=dict(prompt=prompt, n_predict=1, temperature=0)).json()
+        assert cold["timings"]["cache_n"] == 0
+        c.post(f"/slots/{slot}?action=erase")
+        rs = c.post(f"/slots/{slot}?action=restore", json=dict(filename="a.bin")).json()
+        assert rs["n_restored"] == sv["n_saved"]
+        warm = c.post("/completion", json=dict(prompt=prompt, n_predict=1, temperature=0)).json()
+        assert warm["timings"]["cache_n"] >= 64
+        assert c.post(f"/slots/{slot}?action=restore", json=dict(filename="missing.bin")).status_code == 404
+        assert c.post(f"/slots/{slot}?action=bogus").status_code == 400
+    worker.shutdown()
