@@ -972,6 +972,7 @@ static int launch_decode(const DecodeParams& p, int D, int G, int grid, cudaStre
   }
   MX_DEC(128, 1) MX_DEC(128, 2) MX_DEC(128, 4) MX_DEC(128, 8)
   MX_DEC(64, 1) MX_DEC(64, 2) MX_DEC(64, 4) MX_DEC(64, 8)
+  MX_DEC(256, 1) MX_DEC(256, 2) MX_DEC(256, 4) MX_DEC(256, 8)      // Gemma-class heads
 #undef MX_DEC
   return -1;
 }
@@ -997,6 +998,7 @@ static int launch_prefill(const PrefillParams& p, int D, int G, int grid, cudaSt
   if (D == D_ && G == G_) return launch_prefill_one<D_, G_, KV_BITS>(p, grid, st);
   MX_PF(128, 1) MX_PF(128, 2) MX_PF(128, 4) MX_PF(128, 8)
   MX_PF(64, 1) MX_PF(64, 2) MX_PF(64, 4) MX_PF(64, 8)
+  MX_PF(256, 1) MX_PF(256, 2) MX_PF(256, 4) MX_PF(256, 8)          // Gemma-class heads
 #undef MX_PF
   return -1;
 }

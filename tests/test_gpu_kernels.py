@@ -115,7 +115,7 @@ def _clone_pool(kv):
 
 @pytest.mark.parametrize("Hq,Hkv,D,rot,trad,qk", [
     (8, 2, 128, 128, False, False), (4, 4, 64, 64, True, False), (8, 1, 128, 64, False, True),
-    (16, 2, 64, 64, False, True),
+    (16, 2, 64, 64, False, True), (4, 2, 256, 256, False, False), (4, 1, 256, 0, False, True),
 ])
 @pytest.mark.parametrize("bits", [16, 8])
 def test_rope_append(Hq, Hkv, D, rot, trad, qk, bits):
@@ -173,7 +173,7 @@ def _tables(lens, bs, nb, width):
     return tab.to(DEV)
 
 
-@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (8, 8, 64), (8, 1, 128), (16, 2, 64)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (8, 8, 64), (8, 1, 128), (16, 2, 64), (8, 4, 256), (4, 1, 256)])
 @pytest.mark.parametrize("bits,window,sinks,splits", [
     (16, 0, False, 1), (16, 0, False, 4), (16, 48, True, 3), (8, 0, False, 2), (8, 100, True, 1)])
 def test_paged_decode(Hq, Hkv, D, bits, window, sinks, splits):
@@ -196,7 +196,7 @@ def test_paged_decode(Hq, Hkv, D, bits, window, sinks, splits):
     _close(got, want, rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 4, 64), (8, 1, 128), (16, 2, 64)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 4, 64), (8, 1, 128), (16, 2, 64), (8, 4, 256), (4, 1, 256)])
 @pytest.mark.parametrize("bits,window,sinks", [(16, 0, False), (16, 40, True), (8, 0, False)])
 def test_paged_prefill(Hq, Hkv, D, bits, window, sinks):
     bs, nb = 16, 256
