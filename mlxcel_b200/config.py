@@ -480,6 +480,56 @@ def _deepseek_routing(c: ModelConfig, raw: dict) -> None:
     c.router_bias = True                         # the correction bias travels in router_b
 
 
+def _yarn_mscale(factor: float, m: float) -> float:
+    return 1.0 if factor <= 1 or not m else 0.1 * m * math.log(factor) + 1.0
+
+
+def _deepseek_mla(c: ModelConfig, raw: dict) -> None:
+    """Multi-head latent attention geometry. The paged pool stores expanded per-head keys and values
+    padded to one head size (64 / 128 / 256), see ``DecoderModel._attention_mla``."""
+    nope, rope_d, vd = int(raw["qk_nope_head_dim"]), int(raw["qk_rope_head_dim"]), int(raw["v_head_dim"])
+    qk = nope + rope_d
+    big = max(qk, vd)
+    if big > 256:
+        raise ValueError("MLA head dimensions above 256 are not supported")
+    c.extra["mla"] = dict(q_lora_rank=raw.get("q_lora_rank"), kv_lora_rank=int(raw["kv_lora_rank"]), nope=nope,
+                          rope=rope_d, v=vd, interleave=bool(raw.get("rope_interleave", True)))
+    c.head_dim = 64 if big <= 64 else 128 if big <= 128 else 256
+    c.num_key_value_heads = c.num_attention_heads
+    scale = qk ** -0.5
+    rs = c.rope_scaling
+    if rs and rs.get("rope_type", rs.get("type")) == "yarn":
+        f = float(rs.get("factor", 1.0))
+        if rs.get("mscale_all_dim"):
+            scale *= _yarn_mscale(f, float(rs["mscale_all_dim"])) ** 2
+            if rs.get("mscale") and rs.get("attention_factor") is None:
+                rs = dict(rs)
+                rs["attention_factor"] = _yarn_mscale(f, float(rs["mscale"])) / _yarn_mscale(f, float(rs["mscale_all_dim"]))
+                c.rope_scaling = rs
+    c.query_pre_attn_scalar = 1.0 / (scale * scale)
+
+
+def _deepseek_v3(c: ModelConfig, raw: dict) -> None:
+    """DeepSeek-V3 / R1 (and Kimi-K2 with the same layout): multi-head latent attention + sigmoid
+    group-limited routing with shared experts (reference src/models/deepseek_v3.rs)."""
+    _deepseek_routing(c, raw)
+    _deepseek_mla(c, raw)
+
+
+def _deepseek_v2(c: ModelConfig, raw: dict) -> None:
+    """DeepSeek-V2 / V2-Lite: multi-head latent attention, softmax routing (greedy or limited to the
+    groups with the best single score), weights not normalised, shared experts
+    (reference src/models/deepseek_v2.rs)."""
+    _deepseek_routing(c, raw)
+    c.router_bias = False
+    c.norm_topk_prob = bool(raw.get("norm_topk_prob", False))
+    r = c.extra["moe_routing"]
+    r.update(score="softmax", group_score="max")
+    if raw.get("topk_method", "greedy") == "greedy":
+        r.update(n_group=1, topk_group=1)
+    _deepseek_mla(c, raw)
+
+
 def _glm4_moe(c: ModelConfig, raw: dict) -> None:
     """GLM-4.5 / 4.6: half-rotary GQA attention with biased q/k/v and optional per-head q/k norm,
     DeepSeek-V3 style MoE (reference src/models/glm4_moe.rs)."""
@@ -642,7 +692,7 @@ FAMILIES = {
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
-    "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
 
 

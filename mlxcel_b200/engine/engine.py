@@ -97,7 +97,10 @@ class Engine:
             e.prefix_cache = e.cuda_graphs = e.lookahead = False
         if e.num_blocks <= 0:
             e.num_blocks = self._auto_num_blocks(tp, nl)
+        # fp32 models (CPU oracles) keep fp32 keys / values; everything else stores bf16 (or 8-bit)
+        wdt = getattr(getattr(model.w, "final_norm", None), "dtype", torch.bfloat16)
         self.pool = KVPool(cfg, e.num_blocks, e.block_size, kv_bits=e.kv_bits, device=self.device,
+                           dtype=torch.float32 if wdt == torch.float32 else torch.bfloat16,
                            tp_size=tp, num_layers=nl)
         self.bm = BlockManager(e.num_blocks, e.block_size, e.prefix_cache, e.watermark)
         self.sampler = Sampler(cfg.vocab_size, self.device)

@@ -197,6 +197,24 @@ def _first(g: _Getter, *bases):
 
 def _load_attention(g: _Getter, cfg: ModelConfig, p: str, lw_kwargs: dict) -> None:
     a = p + ".self_attn"
+    if cfg.extra.get("mla"):
+        # DeepSeek multi-head latent attention: low-rank query path (optional), latent + rotary key
+        # projection, per-head expansion of the latent
+        mla = dict(kv_a=g.mat(a + ".kv_a_proj_with_mqa"), kv_a_b=g.vec(a + ".kv_a_proj_with_mqa.bias"),
+                   kv_a_norm=g.vec(a + ".kv_a_layernorm.weight"), kv_b=g.mat(a + ".kv_b_proj"))
+        if g.has(a + ".q_a_proj"):
+            mla.update(q_a=g.mat(a + ".q_a_proj"), q_a_b=g.vec(a + ".q_a_proj.bias"),
+                       q_a_norm=g.vec(a + ".q_a_layernorm.weight"), q_b=g.mat(a + ".q_b_proj"))
+        else:
+            mla["q"] = g.mat(a + ".q_proj")
+        from ..models.weights import QuantizedTensor as _QT
+        for k_, v_ in list(mla.items()):
+            if isinstance(v_, _QT):
+                from ..ops.quant import dequantize_ref
+                mla[k_] = dequantize_ref(v_, g.dtype)
+        lw_kwargs.update(mla=mla, wqkv=None, bqkv=None, wo=g.mat(a + ".o_proj"), bo=g.vec(a + ".o_proj.bias"),
+                         q_norm=None, k_norm=None, sinks=None)
+        return
     if g.has(a + ".qkv_proj"):                       # Phi-3 style fused projection
         lw_kwargs["wqkv"] = g.mat(a + ".qkv_proj")
         lw_kwargs["bqkv"] = g.vec(a + ".qkv_proj.bias")

@@ -119,6 +119,10 @@ class DecoderModel:
         self.inv_freq = inv.to(dev)
         self.mscale = ms
         # sliding-window layers with their own RoPE base (Gemma 3: local 10k, global 1M with scaling)
+        self.inv_freq_mla = None
+        if cfg.extra.get("mla"):                # rotary part of multi-head latent attention
+            inv_m, self.mscale = rope_inv_freq(cfg.extra["mla"]["rope"], cfg.rope_theta, cfg.rope_scaling)
+            self.inv_freq_mla = inv_m.to(dev)
         self.inv_freq_local = None
         if cfg.extra.get("rope_local_theta"):
             self.inv_freq_local = rope_inv_freq(cfg.rot_dim, cfg.extra["rope_local_theta"], None)[0].to(dev)
@@ -178,6 +182,8 @@ class DecoderModel:
     def _attention(self, li: int, lw: LayerWeights, x: torch.Tensor, b: StepBatch,
                    kv: KVLayer, row_norm=None) -> torch.Tensor:
         cfg = self.cfg
+        if lw.mla is not None:
+            return self._attention_mla(li, lw, x, b, kv)
         qkv = _linear_any(x, lw.wqkv, bias=lw.bqkv, row_norm=row_norm)
         q_norm, k_norm = lw.q_norm, lw.k_norm
         if q_norm is not None and cfg.extra.get("qk_norm_full"):
@@ -197,12 +203,18 @@ class DecoderModel:
                         Hq=self.Hq, Hkv=self.Hkv, D=self.D, rot_dim=rot_dim,
                         traditional=cfg.rope_traditional, mscale=1.0 if local else self.mscale,
                         q_norm_w=q_norm, k_norm_w=k_norm, norm_eps=cfg.rms_norm_eps)
+        return self._attend(qkv, b, kv, window, lw.sinks)
+
+    def _attend(self, qkv: torch.Tensor, b: StepBatch, kv: KVLayer, window: int, sinks) -> torch.Tensor:
+        """Paged attention of the step's rows (decode rows first, then the prefill pieces) over the
+        keys / values just appended; ``qkv`` carries the (rotated) queries in its first Hq * D columns."""
+        cfg = self.cfg
         T = qkv.shape[0]
         attn = torch.empty(T, self.Hq * self.D, dtype=qkv.dtype, device=qkv.device)
         q = qkv[:, : self.Hq * self.D]
         nd = b.num_decode
         common = dict(Hq=self.Hq, Hkv=self.Hkv, D=self.D, scale=cfg.attn_scale, window=window,
-                      sinks=lw.sinks, softcap=cfg.attn_logit_softcap)
+                      sinks=sinks, softcap=cfg.attn_logit_softcap)
         if nd > 0:
             o = ops.paged_decode(q[:nd], kv, b.dec_block_tables, b.dec_context_lens,
                                  max_len=b.dec_max_len, out=attn[:nd] if attn.is_cuda else None,
@@ -216,6 +228,40 @@ class DecoderModel:
             if not attn.is_cuda:
                 attn[nd:] = o
         return attn
+
+    def _attention_mla(self, li: int, lw: LayerWeights, x: torch.Tensor, b: StepBatch, kv: KVLayer) -> torch.Tensor:
+        """Multi-head latent attention (DeepSeek-V2 / V3; reference src/models/deepseek_v3.rs, mla/*) in
+        its expanded form: q from the (optionally low-rank) query path, per-head k_nope and v from the
+        normalised latent through kv_b, one rotary key part shared by all heads. Keys [k_nope | k_rot]
+        and values are zero-padded to the pool's head size and stored per head, so the ordinary paged
+        kernels serve it; the attention output is cut back to v_head_dim. The absorbed form over a
+        latent cache (one 576-wide entry per token instead of 2 * heads * D) is not built."""
+        from ..ops import reference as ref
+
+        cfg, m, w = self.cfg, self.cfg.extra["mla"], lw.mla
+        Hq, Dp = self.Hq, self.D
+        nope, r, vd, lat = m["nope"], m["rope"], m["v"], m["kv_lora_rank"]
+        T = x.shape[0]
+        if w.get("q_a") is not None:
+            q = _linear_any(ops.rmsnorm(_linear_any(x, w["q_a"], bias=w.get("q_a_b")), w["q_a_norm"], 1e-6, 0.0), w["q_b"])
+        else:
+            q = _linear_any(x, w["q"])
+        q = q.view(T, Hq, nope + r)
+        ckv = _linear_any(x, w["kv_a"], bias=w.get("kv_a_b"))
+        kvb = _linear_any(ops.rmsnorm(ckv[:, :lat].contiguous(), w["kv_a_norm"], 1e-6, 0.0), w["kv_b"]).view(T, Hq, nope + vd)
+        q_rot = ref.apply_rope(q[..., nope:], b.positions, self.inv_freq_mla, r, m["interleave"], self.mscale)
+        k_rot = ref.apply_rope(ckv[:, lat:].view(T, 1, r), b.positions, self.inv_freq_mla, r, m["interleave"], self.mscale)
+        qkv = torch.zeros(T, 3 * Hq, Dp, dtype=x.dtype, device=x.device)
+        qkv[:, :Hq, :nope] = q[..., :nope]
+        qkv[:, :Hq, nope:nope + r] = q_rot.to(x.dtype)
+        qkv[:, Hq:2 * Hq, :nope] = kvb[..., :nope]
+        qkv[:, Hq:2 * Hq, nope:nope + r] = k_rot.to(x.dtype).expand(T, Hq, r)
+        qkv[:, 2 * Hq:, :vd] = kvb[..., nope:]
+        qkv = qkv.view(T, 3 * Hq * Dp)
+        ops.rope_append(qkv, b.positions, b.slot_mapping, self.inv_freq, kv, Hq=Hq, Hkv=self.Hkv, D=Dp, rot_dim=0,
+                        traditional=False, mscale=1.0, q_norm_w=None, k_norm_w=None, norm_eps=cfg.rms_norm_eps)
+        attn = self._attend(qkv, b, kv, 0, None)
+        return attn.view(T, Hq, Dp)[..., :vd].reshape(T, Hq * vd)
 
     def _norm(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
         """The model's normalisation: RMSNorm (with Gemma's +1) or LayerNorm (bias optional)."""

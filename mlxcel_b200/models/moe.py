@@ -30,7 +30,7 @@ def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -
         logits = x.float() @ lw.router_w.float().t()            # the router runs in fp32
         ids, wts = moe_ops.route_sigmoid_grouped(logits, cfg.num_experts_per_tok, lw.router_b, r["n_group"],
                                                  r["topk_group"], cfg.norm_topk_prob, r["scale"], r.get("score", "sigmoid"),
-                                                 r.get("norm_min", 1e-20))
+                                                 r.get("norm_min", 1e-20), r.get("group_score", "top2sum"))
     else:
         logits = ops.linear(x, lw.router_w, bias=lw.router_b)
         ids, wts = moe_ops.route(logits, cfg.num_experts_per_tok, cfg.moe_route_mode, cfg.norm_topk_prob)

@@ -63,6 +63,7 @@ class LayerWeights:
     post_mlp_norm: torch.Tensor | None = None
     ln1_b: torch.Tensor | None = None            # LayerNorm families: norm biases
     ln2_b: torch.Tensor | None = None
+    mla: dict | None = None                      # multi-head latent attention projections (DeepSeek)
     act_params: tuple | None = None              # xIELU: (alpha_p, alpha_n, beta, eps) of this layer
     # dense MLP
     w_gate_up: object | None = None
@@ -142,10 +143,27 @@ def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, dev
     embed = _randn((V, H), std, shared, dtype, dev)
     lws = []
     for li in (layers if layers is not None else range(cfg.num_hidden_layers)):
-        lw = LayerWeights(ln1=ones(H), ln2=ones(H),
-                          wqkv=_randn(((Hq + 2 * Hkv) * D, H), std, gen, dtype, dev),
-                          wo=_randn((H, Hq * D), std, gen, dtype, dev))
-        if cfg.attention_bias:
+        if cfg.extra.get("mla"):
+            if tp_size != 1:
+                raise NotImplementedError("tensor-parallel multi-head latent attention")
+            m = cfg.extra["mla"]
+            qk = m["nope"] + m["rope"]
+            mla = dict(kv_a=_randn((m["kv_lora_rank"] + m["rope"], H), std, gen, dtype, dev),
+                       kv_a_norm=torch.ones(m["kv_lora_rank"], dtype=dtype, device=dev),
+                       kv_b=_randn((Hq * (m["nope"] + m["v"]), m["kv_lora_rank"]), std, gen, dtype, dev))
+            if m.get("q_lora_rank"):
+                mla.update(q_a=_randn((m["q_lora_rank"], H), std, gen, dtype, dev),
+                           q_a_norm=torch.ones(m["q_lora_rank"], dtype=dtype, device=dev),
+                           q_b=_randn((Hq * qk, m["q_lora_rank"]), std, gen, dtype, dev))
+            else:
+                mla["q"] = _randn((Hq * qk, H), std, gen, dtype, dev)
+            lw = LayerWeights(ln1=ones(H), ln2=ones(H), wqkv=None, wo=_randn((H, Hq * m["v"]), std, gen, dtype, dev),
+                              mla=mla)
+        else:
+            lw = LayerWeights(ln1=ones(H), ln2=ones(H),
+                              wqkv=_randn(((Hq + 2 * Hkv) * D, H), std, gen, dtype, dev),
+                              wo=_randn((H, Hq * D), std, gen, dtype, dev))
+        if cfg.attention_bias and lw.mla is None:
             lw.bqkv = _randn(((Hq + 2 * Hkv) * D,), std, gen, dtype, dev)
             if cfg.model_type == "gpt_oss":
                 lw.bo = _randn((H,), std, shared, dtype, dev)

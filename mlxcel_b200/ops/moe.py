@@ -54,7 +54,8 @@ def moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up=None, b_down=N
 
 
 def route_sigmoid_grouped(logits: torch.Tensor, k: int, bias: torch.Tensor | None, n_group: int, topk_group: int,
-                          norm_topk: bool, scale: float, score: str = "sigmoid", norm_min: float = 1e-20):
+                          norm_topk: bool, scale: float, score: str = "sigmoid", norm_min: float = 1e-20,
+                          group_score: str = "top2sum"):
     """DeepSeek-V3-style routing (GLM-4-MoE, dots1, ...): sigmoid scores; experts are CHOSEN by
     score + correction bias, restricted to the ``topk_group`` groups with the best sum of their two
     top biased scores, but WEIGHTED by the unbiased score (normalised over the k, times ``scale``).
@@ -66,7 +67,8 @@ def route_sigmoid_grouped(logits: torch.Tensor, k: int, bias: torch.Tensor | Non
     choice = scores if bias is None else scores + bias.float().reshape(1, E)
     if n_group > 1:
         grp = choice.view(T, n_group, E // n_group)
-        gscore = grp.topk(min(2, E // n_group), dim=-1)[0].sum(-1)
+        # a group is ranked by the sum of its two best scores (V3) or by its best score (V2)
+        gscore = grp.topk(min(2, E // n_group), dim=-1)[0].sum(-1) if group_score == "top2sum" else grp.amax(-1)
         keep = torch.zeros_like(gscore).scatter_(1, gscore.topk(topk_group, dim=-1)[1], 1.0)
         choice = choice.masked_fill(~keep.bool().unsqueeze(-1).expand(T, n_group, E // n_group).reshape(T, E), 0.0)
     ids = choice.topk(k, dim=-1)[1]

@@ -482,6 +482,10 @@ def test_tiny_llama_gpu_matches_cpu_reference(fold):
     ("smollm3", dict(num_hidden_layers=4, no_rope_layer_interval=2)),  # layers without positional encoding
     ("glm4_moe", dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, n_shared_experts=1,
                       n_group=2, topk_group=1, first_k_dense_replace=1, routed_scaling_factor=1.5, use_qk_norm=True)),
+    ("deepseek_v3", dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, n_shared_experts=1,
+                         n_group=2, topk_group=1, first_k_dense_replace=1, routed_scaling_factor=2.5, q_lora_rank=96,
+                         kv_lora_rank=64, qk_nope_head_dim=64, qk_rope_head_dim=32, v_head_dim=64,
+                         num_key_value_heads=4)),                      # MLA, keys padded 96 -> 128
     ("gemma3_text", dict(sliding_window=16, sliding_window_pattern=2, query_pre_attn_scalar=64,
                          rope_local_base_freq=10000.0, rope_theta=1000000.0)),
 ])
@@ -506,6 +510,8 @@ def test_less_common_layouts_gpu_matches_cpu(family, extra):
         for k, v in vars(obj).items():
             if isinstance(v, torch.Tensor):
                 setattr(obj, k, (v.to(torch.bfloat16) if v.dtype == torch.float32 and k != "sinks" else v).to(DEV))
+        if getattr(obj, "mla", None):
+            obj.mla = {k: (None if v is None else v.to(torch.bfloat16).to(DEV)) for k, v in obj.mla.items()}
     if cfg.tie_word_embeddings:
         w16.lm_head = w16.embed
     T = 40

@@ -42,6 +42,17 @@ FAMILIES = {
                      pad_token_id=0, attention_bias=True),
     "ernie4_5_moe": dict(moe_num_experts=4, moe_k=2, moe_intermediate_size=48, moe_num_shared_experts=1,
                          moe_layer_start_index=1, head_dim=16, pad_token_id=0),
+    "deepseek_v2": dict(moe_intermediate_size=48, num_key_value_heads=4, n_routed_experts=8, num_experts_per_tok=2,
+                        n_shared_experts=2, topk_method="greedy", first_k_dense_replace=1, routed_scaling_factor=1.5,
+                        q_lora_rank=None, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=24,
+                        pad_token_id=0),
+    "deepseek_v3": dict(moe_intermediate_size=48, num_key_value_heads=4, n_routed_experts=8, num_experts_per_tok=2,
+                        n_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1, routed_scaling_factor=2.5,
+                        q_lora_rank=24, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                        pad_token_id=0, max_position_embeddings=512,
+                        rope_parameters=dict(rope_type="yarn", rope_theta=10000.0, factor=4.0,
+                                             original_max_position_embeddings=128, beta_fast=32, beta_slow=1,
+                                             mscale=1.0, mscale_all_dim=1.0)),
     "dots1": dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=48, n_shared_experts=2, n_group=2,
                   topk_group=1, first_k_dense_replace=1, routed_scaling_factor=2.0, head_dim=16),
     "gpt_oss": dict(num_local_experts=4, num_experts_per_tok=2, head_dim=16, **SLIDING),
@@ -208,3 +219,29 @@ def test_granite_hybrid_matches_transformers(pos):
         with torch.no_grad():
             ref = model.generate(ids[None, :12], max_new_tokens=4, do_sample=False)[0, 12:].tolist()
         assert out == ref
+
+
+@pytest.mark.parametrize("name", ["llama", "gemma3_text", "glm4_moe", "deepseek_v3", "cohere2", "olmo2"])
+def test_greedy_generation_matches_transformers(name):
+    """Prefill + token-by-token decode through the engine (paged KV, chunked prefill of 16 tokens)
+    against transformers: the decode path and the KV bookkeeping of each layout."""
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.loading.checkpoint import load_full_weights
+
+    model = _hf_model(name)
+    d = tempfile.mkdtemp(prefix=f"gen_{name}_")
+    model.save_pretrained(d, safe_serialization=True)
+    ids = torch.randint(3, 300, (37,), generator=torch.Generator().manual_seed(2))
+    cfg = ModelConfig.from_path(d)
+    eng = Engine(DecoderModel(cfg, load_full_weights(d, cfg, dtype=torch.float32)), cfg,
+                 EngineConfig(num_blocks=64, block_size=16, max_batch=4, max_model_len=256, max_num_batched_tokens=16,
+                              cuda_graphs=False))
+    out = eng.generate([ids.tolist()], SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True))[0].output
+    # teacher-forced check (free-running comparison would fork on a float32 near-tie): every token the
+    # engine chose must be transformers' argmax at that position, up to rounding of the logits
+    with torch.no_grad():
+        lg = model(torch.cat([ids, torch.tensor(out)])[None]).logits[0]
+    for i, tok in enumerate(out):
+        row = lg[len(ids) - 1 + i]
+        assert row[tok].item() >= row.max().item() - 2e-3, (i, tok, int(row.argmax()))
