@@ -427,6 +427,42 @@ def _phi(c: ModelConfig, raw: dict) -> None:
         raise ValueError("phi with q/k LayerNorm is not supported")
 
 
+def _gpt_neox(c: ModelConfig, raw: dict) -> None:
+    """GPT-NeoX / Pythia: LayerNorm with bias, attention and MLP in parallel from two norms of the
+    same stream, rotary embedding on a quarter of each head, plain GELU MLP, fused per-head qkv
+    (reference src/models/gpt_neox.rs; re-layout in loading/aliases.py)."""
+    c.extra["norm"] = "layernorm"
+    c.extra["mlp"] = "plain"
+    c.extra["parallel_block"] = bool(raw.get("use_parallel_residual", True))
+    c.hidden_act = _plain_act(c)
+    c.rms_norm_eps = float(raw.get("layer_norm_eps", 1e-5))
+    c.attention_bias = c.mlp_bias = True
+    c.num_key_value_heads = c.num_attention_heads
+    c.head_dim = c.hidden_size // c.num_attention_heads
+    if "partial_rotary_factor" not in raw and not (raw.get("rope_parameters") or {}).get("partial_rotary_factor"):
+        c.partial_rotary_factor = float(raw.get("rotary_pct", 0.25))
+
+
+def _gpt2(c: ModelConfig, raw: dict) -> None:
+    """GPT-2 and GPT-BigCode (StarCoder-1, SantaCoder): learned absolute positions, LayerNorm with
+    bias, plain GELU MLP, fused c_attn (multi-query in BigCode) (reference src/models/gpt2.rs,
+    gpt_bigcode.rs)."""
+    c.extra["norm"] = "layernorm"
+    c.extra["mlp"] = "plain"
+    c.hidden_act = _plain_act(c)
+    c.intermediate_size = int(raw.get("n_inner") or 4 * c.hidden_size)
+    c.rms_norm_eps = float(raw.get("layer_norm_epsilon", 1e-5))
+    c.attention_bias = c.mlp_bias = True
+    c.partial_rotary_factor = 0.0
+    c.max_position_embeddings = int(raw.get("n_positions", c.max_position_embeddings))
+    c.num_key_value_heads = 1 if raw.get("multi_query", c.model_type == "gpt_bigcode") and c.model_type == "gpt_bigcode" \
+        else c.num_attention_heads
+    c.head_dim = c.hidden_size // c.num_attention_heads
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
+    if raw.get("scale_attn_by_inverse_layer_idx"):
+        raise ValueError("gpt2 with scale_attn_by_inverse_layer_idx is not supported")
+
+
 def _olmo1(c: ModelConfig, raw: dict) -> None:
     """OLMo-1: LayerNorm without parameters, otherwise the Llama layout (reference src/models/olmo.rs)."""
     c.extra["norm"] = "layernorm"
@@ -692,7 +728,8 @@ FAMILIES = {
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
-    "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
 
 

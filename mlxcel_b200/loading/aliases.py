@@ -1,0 +1,73 @@
+"""Checkpoint name aliases: families whose tensors are named (or laid out) differently from the
+canonical ``model.layers.N.self_attn.q_proj`` scheme are presented to the loader under canonical
+names, with the layout fixed on the way (reference src/models/sanitize.rs: weight-name remaps and
+re-layouts at load time).
+
+``aliases_for(cfg, keys)`` returns ``{canonical_name: (actual_name, transform | None)}``;
+``TensorSource.set_aliases`` makes those names resolvable.
+"""
+from __future__ import annotations
+
+import re
+
+import torch
+
+
+def _t(w: torch.Tensor) -> torch.Tensor:
+    return w.t().contiguous()
+
+
+def _neox_qkv(heads: int):
+    """GPT-NeoX stores query_key_value per head as [heads, 3, D, ...]; the executor wants all q rows,
+    then all k rows, then all v rows."""
+    def fix(w: torch.Tensor) -> torch.Tensor:
+        rest = w.shape[1:]
+        d = w.shape[0] // (3 * heads)
+        return w.view(heads, 3, d, *rest).transpose(0, 1).reshape(3 * heads * d, *rest).contiguous()
+    return fix
+
+
+def _rules(cfg) -> list[tuple[str, str, object]]:
+    mt = cfg.model_type
+    if mt == "gpt_neox":
+        qkv = _neox_qkv(cfg.num_attention_heads)
+        L = r"gpt_neox\.layers\.(\d+)\."
+        return [(r"gpt_neox\.embed_in\.(\w+)", r"model.embed_tokens.\1", None),
+                (r"gpt_neox\.final_layer_norm\.(\w+)", r"model.norm.\1", None),
+                (r"embed_out\.(\w+)", r"lm_head.\1", None),
+                (L + r"input_layernorm\.(\w+)", r"model.layers.\1.input_layernorm.\2", None),
+                (L + r"post_attention_layernorm\.(\w+)", r"model.layers.\1.post_attention_layernorm.\2", None),
+                (L + r"attention\.query_key_value\.(\w+)", r"model.layers.\1.self_attn.qkv_proj.\2", qkv),
+                (L + r"attention\.dense\.(\w+)", r"model.layers.\1.self_attn.o_proj.\2", None),
+                (L + r"mlp\.dense_h_to_4h\.(\w+)", r"model.layers.\1.mlp.fc1.\2", None),
+                (L + r"mlp\.dense_4h_to_h\.(\w+)", r"model.layers.\1.mlp.fc2.\2", None)]
+    if mt in ("gpt2", "gpt_bigcode"):
+        tr = _t if mt == "gpt2" else None          # GPT-2 keeps Conv1D weights as [in, out]
+        L = r"transformer\.h\.(\d+)\."
+        return [(r"transformer\.wte\.(\w+)", r"model.embed_tokens.\1", None),
+                (r"transformer\.wpe\.(\w+)", r"model.embed_positions.\1", None),
+                (r"transformer\.ln_f\.(\w+)", r"model.norm.\1", None),
+                (L + r"ln_1\.(\w+)", r"model.layers.\1.input_layernorm.\2", None),
+                (L + r"ln_2\.(\w+)", r"model.layers.\1.post_attention_layernorm.\2", None),
+                (L + r"attn\.c_attn\.weight", r"model.layers.\1.self_attn.qkv_proj.weight", tr),
+                (L + r"attn\.c_attn\.bias", r"model.layers.\1.self_attn.qkv_proj.bias", None),
+                (L + r"attn\.c_proj\.weight", r"model.layers.\1.self_attn.o_proj.weight", tr),
+                (L + r"attn\.c_proj\.bias", r"model.layers.\1.self_attn.o_proj.bias", None),
+                (L + r"mlp\.c_fc\.weight", r"model.layers.\1.mlp.fc1.weight", tr),
+                (L + r"mlp\.c_fc\.bias", r"model.layers.\1.mlp.fc1.bias", None),
+                (L + r"mlp\.c_proj\.weight", r"model.layers.\1.mlp.fc2.weight", tr),
+                (L + r"mlp\.c_proj\.bias", r"model.layers.\1.mlp.fc2.bias", None)]
+    return []
+
+
+def aliases_for(cfg, keys) -> dict:
+    rules = [(re.compile("^" + pat + "$"), rep, fn) for pat, rep, fn in _rules(cfg)]
+    out = {}
+    if not rules:
+        return out
+    for k in keys:
+        for pat, rep, fn in rules:
+            if pat.match(k):
+                out[pat.sub(rep, k)] = (k, fn)
+                break
+    return out

@@ -57,6 +57,13 @@ class TensorSource:
     def has(self, name: str) -> bool:
         return name in self.index
 
+    def set_aliases(self, aliases: dict) -> None:
+        """``{canonical: (actual, transform | None)}`` (see ``loading/aliases.py``): the canonical names
+        become resolvable, reading the actual tensor and fixing its layout on the way."""
+        self.aliases = dict(aliases)
+        for canon, (actual, _) in self.aliases.items():
+            self.index[canon] = self.index[actual]
+
     def set_edits(self, edits: list[dict]) -> None:
         """Load-time weight surgery (see ``loading/surgery.py``): applied to every tensor fetched."""
         self.edits = list(edits)
@@ -70,6 +77,10 @@ class TensorSource:
         return t
 
     def _get_raw(self, name: str) -> torch.Tensor:
+        alias = getattr(self, "aliases", {}).get(name)
+        if alias is not None:
+            t = self._get_raw(alias[0])
+            return alias[1](t) if alias[1] is not None else t
         f = self.index[name]
         h = self._handles.get(f)
         if h is None:
@@ -319,6 +330,10 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
     if surgery:
         from .surgery import load_edits
         src.set_edits(load_edits(surgery))
+    from .aliases import aliases_for
+    al = aliases_for(cfg, list(src.keys()))
+    if al:
+        src.set_aliases(al)
     g = _Getter(src, cfg, dtype, dequantize)
     pre = "model." if any(k.startswith("model.") for k in src.keys()) else ""
     if any(k.startswith("language_model.model.") for k in src.keys()):
@@ -379,6 +394,8 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
     else:
         lm_head = emb_q if (emb_q is not None and not dequantize) else emb
     mw = ModelWeights(embed=emb, layers=lws, final_norm=final_norm, lm_head=lm_head)
+    if src.has(pre + "embed_positions.weight"):               # learned absolute positions (GPT-2 family)
+        mw.extra["pos_embed"] = g.vec(pre + "embed_positions.weight")
     fb = g.vec(_first_name(src, pre + "norm.bias", pre + "final_layernorm.bias"))
     if fb is not None:
         mw.extra["final_norm_b"] = fb

@@ -297,6 +297,8 @@ class DecoderModel:
             h = b.embeds
         else:
             h = self.comm.embed(b.token_ids, w.embed, cfg.embed_scale)
+            if w.extra.get("pos_embed") is not None:          # learned absolute positions (GPT-2 family)
+                h = (h.float() + w.extra["pos_embed"].index_select(0, b.positions.long()).float()).to(h.dtype)
         eps, wb = cfg.rms_norm_eps, cfg.norm_weight_bias
         res_mult = cfg.extra.get("residual_multiplier", 1.0)
         if self.fold_attn and h.is_cuda and h.shape[0] <= self._ssq.max_tokens and h.dtype == torch.bfloat16:
@@ -360,8 +362,10 @@ class DecoderModel:
             x = self._norm(h, lw.ln1, lw.ln1_b)
             a = self._attention(li, lw, x, b, kv_layers[li])
             if parallel:
+                # one norm feeds both branches (Cohere, Phi) unless the layer has a second one (GPT-NeoX)
+                xm = x if lw.ln2 is lw.ln1 else self._norm(h, lw.ln2, lw.ln2_b)
                 o = self.comm.row_parallel_linear(a, lw.wo, lw.bo, None)
-                m = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, None)
+                m = self.comm.row_parallel_linear(self._mlp(lw, xm), lw.w_down, lw.b_down, None)
                 h = (h.float() + o.float() + m.float()).to(h.dtype)
             else:
                 h = self.comm.row_parallel_linear(a, lw.wo, lw.bo, h)

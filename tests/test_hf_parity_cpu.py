@@ -27,6 +27,8 @@ FAMILIES = {
     "gemma3_text": dict(head_dim=16, sliding_window=8, query_pre_attn_scalar=16, sliding_window_pattern=2),
     "phi3": dict(pad_token_id=0), "olmo2": {}, "olmo3": dict(**SLIDING), "exaone4": dict(head_dim=16, **SLIDING),
     "granite": dict(embedding_multiplier=2.0, residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=3.0),
+    "gpt_neox": {}, "gpt2": dict(n_embd=64, n_layer=2, n_head=4, n_positions=256, n_inner=128),
+    "gpt_bigcode": dict(n_embd=64, n_layer=2, n_head=4, n_positions=256, n_inner=128),
     "starcoder2": {}, "stablelm": {}, "cohere": {}, "cohere2": dict(**SLIDING), "phi": {}, "olmo": {},
     "arcee": {}, "nemotron": {}, "glm": dict(head_dim=16, pad_token_id=0), "glm4": dict(head_dim=16, pad_token_id=0),
     "granitemoe": dict(num_local_experts=4, num_experts_per_tok=2, embedding_multiplier=2.0, residual_multiplier=0.5,
