@@ -671,6 +671,21 @@ def _num(v) -> float:
     return float(v)
 
 
+def _mamba1(c: ModelConfig, raw: dict) -> None:
+    """First-generation Mamba (HF ``MambaConfig``; reference src/models/mamba.rs). No layer has attention:
+    the attention geometry is the minimum the block pool accepts."""
+    hs = c.hidden_size
+    d_inner = int(raw.get("intermediate_size") or raw.get("expand", 2) * hs)
+    rank = raw.get("time_step_rank", "auto")
+    c.extra["mamba1"] = dict(d_inner=d_inner, d_state=int(raw.get("state_size", 16)),
+                             d_conv=int(raw.get("conv_kernel", 4)),
+                             dt_rank=math.ceil(hs / 16) if rank in ("auto", None, 0) else int(rank))
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
+    c.num_attention_heads = c.num_key_value_heads = 1
+    c.head_dim = 16
+    c.intermediate_size = d_inner
+
+
 def _mamba2(c: ModelConfig, raw: dict) -> None:
     """Pure state-space model (HF ``Mamba2Config``; reference src/models/mamba2.rs:40-76). The
     attention geometry is reduced to the minimum the block pool accepts: no layer has attention."""
@@ -727,7 +742,7 @@ FAMILIES = {
     "mixtral": _mixtral, "olmoe": _olmoe,
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
-    "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
+    "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
     "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
@@ -778,6 +793,10 @@ def preset(name: str) -> ModelConfig:
             model_type="qwen3", num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
             num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=1024,
             rms_norm_eps=1e-6, max_position_embeddings=2048))
+    if name == "tiny-mamba":
+        return ModelConfig.from_dict(dict(
+            model_type="mamba", num_hidden_layers=2, hidden_size=128, state_size=16, conv_kernel=4, expand=2,
+            vocab_size=1024, layer_norm_epsilon=1e-5))
     if name == "tiny-mamba2":
         return ModelConfig.from_dict(dict(
             model_type="mamba2", num_hidden_layers=2, hidden_size=128, num_heads=8, head_dim=32,

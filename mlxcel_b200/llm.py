@@ -22,10 +22,11 @@ class LLM:
         """``fold_norms``: the weights belong to this object alone, so the executor may fold the
         RMSNorm weights into the projections in place (deferred RMSNorm, see DecoderModel)."""
         self.cfg = cfg
-        if cfg.model_type in ("mamba2", "nemotron_h", "granitemoehybrid"):
+        if cfg.model_type in ("mamba", "mamba2", "nemotron_h", "granitemoehybrid"):
             from .models.hybrid import HybridModel
+            from .models.mamba1 import Mamba1Model
             from .models.mamba2 import Mamba2Model
-            cls = Mamba2Model if cfg.model_type == "mamba2" else HybridModel
+            cls = {"mamba": Mamba1Model, "mamba2": Mamba2Model}.get(cfg.model_type, HybridModel)
             self.model = cls(cfg, weights, comm=comm,
                              max_seqs=2 * (engine_config.max_batch if engine_config else EngineConfig().max_batch))
         else:
@@ -43,6 +44,9 @@ class LLM:
         if cfg.model_type == "mamba2":
             from .models.mamba2 import random_mamba2_weights
             return LLM(cfg, random_mamba2_weights(cfg, seed=seed, dtype=dtype, device=device), engine_config, comm=comm)
+        if cfg.model_type == "mamba":
+            from .models.mamba1 import random_mamba1_weights
+            return LLM(cfg, random_mamba1_weights(cfg, seed=seed, dtype=dtype, device=device), engine_config, comm=comm)
         if cfg.model_type == "nemotron_h":
             from .models.hybrid import random_hybrid_weights
             return LLM(cfg, random_hybrid_weights(cfg, seed=seed, dtype=dtype, device=device), engine_config, comm=comm)
@@ -63,6 +67,10 @@ class LLM:
         if cfg.model_type == "mamba2":
             from .models.mamba2 import load_mamba2_weights
             return LLM(cfg, load_mamba2_weights(path, cfg, device=device), engine_config, comm=comm,
+                       tokenizer=load_tokenizer(path))
+        if cfg.model_type == "mamba":
+            from .models.mamba1 import load_mamba1_weights
+            return LLM(cfg, load_mamba1_weights(path, cfg, device=device), engine_config, comm=comm,
                        tokenizer=load_tokenizer(path))
         if cfg.model_type == "nemotron_h":
             from .models.hybrid import load_hybrid_weights

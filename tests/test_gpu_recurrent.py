@@ -236,3 +236,43 @@ def test_tiny_mamba2_engine_gpu_matches_cpu():
     from mlxcel_b200.ops import _lib
     torch.cuda.synchronize()
     assert _lib.read_status(torch.device(DEV)) == 0
+
+
+def test_tiny_mamba1_engine_gpu_matches_cpu():
+    """First-generation Mamba: bf16 GPU kernels (ragged conv, selective scan) against the fp32 CPU path."""
+    import copy
+    from mlxcel_b200.config import preset
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.models.decoder import StepBatch
+    from mlxcel_b200.models.mamba1 import Mamba1Model, random_mamba1_weights
+
+    cfg = preset("tiny-mamba")
+    w32 = random_mamba1_weights(cfg, seed=4, dtype=torch.float32, std=0.08)
+    w16 = copy.deepcopy(w32)
+    for obj in [w16, *w16.layers]:
+        for k, v in vars(obj).items():
+            if isinstance(v, torch.Tensor):
+                keep32 = k in ("conv_w", "conv_b", "A_log", "D")
+                setattr(obj, k, (v if keep32 else v.to(torch.bfloat16)).to(DEV))
+    w16.lm_head = w16.embed
+    T = 50
+    ids = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+
+    def logits(w, dev):
+        m = Mamba1Model(cfg, w, max_seqs=4)
+        b = StepBatch(token_ids=ids.to(dev), positions=torch.arange(T, dtype=torch.int32, device=dev),
+                      slot_mapping=torch.arange(T, dtype=torch.int32, device=dev), num_prefill_seqs=1,
+                      pf_cu_q_host=[0, T], pf_max_q_len=T, logits_rows=torch.tensor([T - 1, T // 2], device=dev))
+        b.seq_ids, b.pf_starts = [0], [0]
+        return m.forward(b).float().cpu()
+
+    lc, lg = logits(w32, "cpu"), logits(w16, DEV)
+    assert (lc - lg).abs().max().item() < 0.05 * lc.abs().max().item() + 0.03
+    eng = Engine(Mamba1Model(cfg, w16, max_seqs=16), cfg,
+                 EngineConfig(num_blocks=64, block_size=16, max_batch=8, max_model_len=256, max_num_batched_tokens=32))
+    outs = eng.generate([ids[:40].tolist(), ids[5:12].tolist()], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
+    assert all(len(s.output) == 8 for s in outs) and not eng.model.slot_of
+    from mlxcel_b200.ops import _lib
+    torch.cuda.synchronize()
+    assert _lib.read_status(torch.device(DEV)) == 0

@@ -247,3 +247,49 @@ def test_greedy_generation_matches_transformers(name):
     for i, tok in enumerate(out):
         row = lg[len(ids) - 1 + i]
         assert row[tok].item() >= row.max().item() - 2e-3, (i, tok, int(row.argmax()))
+
+
+def test_mamba1_matches_transformers():
+    """First-generation Mamba: logits of a prompt, then chunked prefill + batched decode through the
+    engine checked teacher-forced against transformers."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.models.mamba1 import Mamba1Model, load_mamba1_weights
+
+    torch.manual_seed(0)
+    hc = AutoConfig.for_model("mamba", hidden_size=64, num_hidden_layers=2, state_size=16, vocab_size=300, conv_kernel=4,
+                              expand=2, pad_token_id=0)
+    model = AutoModelForCausalLM.from_config(hc).float().eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2 and "A_log" not in n:
+                p.normal_(0, 0.08)
+            elif "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tempfile.mkdtemp(prefix="parity_mamba1_")
+    model.save_pretrained(d, safe_serialization=True)
+    T = 24
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0]
+    cfg = ModelConfig.from_path(d)
+    ours = Mamba1Model(cfg, load_mamba1_weights(d, cfg, dtype=torch.float32), max_seqs=4)
+    b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
+                  slot_mapping=torch.arange(T, dtype=torch.int32), num_prefill_seqs=1, pf_cu_q_host=[0, T],
+                  pf_max_q_len=T, logits_rows=torch.arange(T))
+    b.seq_ids, b.pf_starts = [0], [0]
+    got = ours.forward(b).float()
+    assert (got - want).abs().max().item() < 2e-3 * max(want.abs().max().item(), 1.0)
+    ours.release_seq(0)
+    eng = Engine(ours, cfg, EngineConfig(num_blocks=64, block_size=16, max_batch=4, max_model_len=256,
+                                         max_num_batched_tokens=16))
+    outs = eng.generate([ids.tolist(), ids[:7].tolist()], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
+    for o, n0 in zip(outs, (T, 7)):
+        with torch.no_grad():
+            lg = model(torch.cat([ids[:n0], torch.tensor(o.output)])[None]).logits[0]
+        for i, tok in enumerate(o.output):
+            row = lg[n0 - 1 + i]
+            assert row[tok].item() >= row.max().item() - 2e-3
+    assert not ours.slot_of
