@@ -496,6 +496,32 @@ def _granitemoehybrid(c: ModelConfig, raw: dict) -> None:
         c.partial_rotary_factor = 0.0
 
 
+def _jamba(c: ModelConfig, raw: dict) -> None:
+    """Jamba: first-generation Mamba mixers (with RMSNorm on dt / B / C) and attention without
+    positional encoding, interleaved by ``attn_layer_period / offset``; every layer ends in a gated
+    MLP or, every ``expert_layer_period``-th, a softmax top-k MoE (reference src/models/jamba.rs).
+    Runs on the hybrid executor as the block pattern ``m`` / ``*`` + ``G`` / ``E`` per layer."""
+    n = c.num_hidden_layers
+    ap, ao = int(raw.get("attn_layer_period", 8)), int(raw.get("attn_layer_offset", 4))
+    ep, eo = int(raw.get("expert_layer_period", 2)), int(raw.get("expert_layer_offset", 1))
+    c.num_experts = int(raw.get("num_experts", 0) or 0)
+    c.moe_intermediate_size = c.intermediate_size
+    c.moe_route_mode, c.norm_topk_prob = "softmax_topk", False
+    pat = ""
+    for i in range(n):
+        pat += "*" if i % ap == ao else "m"
+        pat += "E" if (c.num_experts > 1 and i % ep == eo) else "G"
+    c.extra["hybrid_pattern"], c.extra["hybrid_layout"] = pat, "jamba"
+    hs = c.hidden_size
+    rank = raw.get("mamba_dt_rank", "auto")
+    c.extra["mamba1"] = dict(d_inner=int(raw.get("mamba_expand", 2)) * hs, d_state=int(raw.get("mamba_d_state", 16)),
+                             d_conv=int(raw.get("mamba_d_conv", 4)),
+                             dt_rank=math.ceil(hs / 16) if rank in ("auto", None, 0) else int(rank))
+    c.partial_rotary_factor = 0.0
+    c.layer_types = None
+    c.sliding_window = 0
+
+
 def _granitemoe(c: ModelConfig, raw: dict) -> None:
     _granite(c, raw)
     c.moe_route_mode = "topk_softmax"
@@ -744,7 +770,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
 
 

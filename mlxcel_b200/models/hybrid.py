@@ -31,9 +31,10 @@ from .weights import LayerWeights, ModelWeights
 
 @dataclass
 class HybridBlock:
-    kind: str                                   # "mamba2" | "attention" | "mlp"
+    kind: str                                   # "mamba2" | "mamba1" | "attention" | "mlp" | "moe"
     norm: torch.Tensor
-    mamba: Mamba2LayerWeights | None = None
+    mamba: object | None = None                 # Mamba2LayerWeights or Mamba1LayerWeights
+    moe: LayerWeights | None = None             # router + stacked experts (block kind "moe")
     attn: LayerWeights | None = None            # wqkv / wo (+ biases)
     up: torch.Tensor | None = None              # plain MLP [I, H]; gated MLP: [2I, H] (gate rows first)
     down: torch.Tensor | None = None            # [H, I]
@@ -49,12 +50,12 @@ class HybridWeights:
     layers: list = field(default_factory=list)  # the attention blocks' LayerWeights (= KV-pool layers)
 
 
-_KINDS = {"M": "mamba2", "*": "attention", "-": "mlp", "G": "mlp"}      # G: gated MLP block
+_KINDS = {"M": "mamba2", "m": "mamba1", "*": "attention", "-": "mlp", "G": "mlp", "E": "moe"}   # G: gated MLP
 
 
 def block_kinds(cfg: ModelConfig) -> list[str]:
     pat = cfg.extra["hybrid_pattern"]
-    per_layer = 2 if cfg.extra.get("hybrid_layout") == "granite" else 1
+    per_layer = 2 if cfg.extra.get("hybrid_layout") in ("granite", "jamba") else 1
     if len(pat) != cfg.num_hidden_layers * per_layer:
         raise ValueError(f"hybrid pattern has {len(pat)} entries for {cfg.num_hidden_layers} layers")
     try:
@@ -194,6 +195,70 @@ def load_granite_hybrid_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, de
                          lm_head=embed if head is None else head.to(device), layers=attn_layers)
 
 
+def load_jamba_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
+    """Jamba checkpoint: ``model.layers.N.{input_layernorm, mamba.* | self_attn.*, pre_ff_layernorm,
+    feed_forward.(gate|up|down)_proj | feed_forward.router + experts.E.*}``; each layer becomes a mixer
+    block (first-generation Mamba with norms on dt / B / C, or attention without positional encoding)
+    and an MLP or MoE block (reference src/models/jamba.rs)."""
+    from ..loading.checkpoint import TensorSource, _Getter, _cat_rows, _stack
+    from .mamba1 import Mamba1LayerWeights, mamba1_dims
+
+    src = TensorSource(path)
+    g = _Getter(src, cfg, dtype, dequantize=True)
+    d = mamba1_dims(cfg)
+
+    def need(t, name):
+        if t is None:
+            raise KeyError(f"{path}: missing tensor {name}")
+        return t.to(device)
+
+    blocks, attn_layers = [], []
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        norm = need(g.vec(p + "input_layernorm.weight"), p + "input_layernorm.weight")
+        if src.has(p + "mamba.in_proj.weight"):
+            m = p + "mamba."
+            cw = need(g.vec(m + "conv1d.weight"), m + "conv1d.weight")
+            cw = cw.reshape(d["Di"], d["K"]) if cw.dim() == 2 or cw.shape[1] == 1 else cw.squeeze(-1)
+            cb = g.vec(m + "conv1d.bias")
+            opt = lambda n: None if g.vec(n) is None else g.vec(n).to(device)  # noqa: E731
+            lw = Mamba1LayerWeights(
+                norm=norm, in_proj=need(g.mat(m + "in_proj"), m + "in_proj"), in_proj_b=opt(m + "in_proj.bias"),
+                conv_w=cw.float(), conv_b=None if cb is None else cb.float().to(device),
+                x_proj=need(g.mat(m + "x_proj"), m + "x_proj"), dt_proj=need(g.mat(m + "dt_proj"), m + "dt_proj"),
+                dt_proj_b=need(g.vec(m + "dt_proj.bias"), m + "dt_proj.bias"),
+                A_log=need(g.vec(m + "A_log"), m + "A_log").float(), D=need(g.vec(m + "D"), m + "D").float(),
+                out_proj=need(g.mat(m + "out_proj"), m + "out_proj"), out_proj_b=opt(m + "out_proj.bias"),
+                dt_norm=opt(m + "dt_layernorm.weight"), b_norm=opt(m + "b_layernorm.weight"),
+                c_norm=opt(m + "c_layernorm.weight"))
+            blocks.append(HybridBlock("mamba1", norm, mamba=lw))
+        else:
+            a = p + "self_attn."
+            q, k, v = (need(g.mat(a + n), a + n) for n in ("q_proj", "k_proj", "v_proj"))
+            lw = LayerWeights(ln1=norm, ln2=norm, wqkv=torch.cat([q, k, v], 0).contiguous(),
+                              wo=need(g.mat(a + "o_proj"), a + "o_proj"))
+            attn_layers.append(lw)
+            blocks.append(HybridBlock("attention", norm, attn=lw))
+        f = p + "feed_forward."
+        fn = need(g.vec(p + "pre_ff_layernorm.weight"), p + "pre_ff_layernorm.weight")
+        if src.has(f + "router.weight"):
+            gus = [_cat_rows([g.mat(f"{f}experts.{e}.gate_proj"), g.mat(f"{f}experts.{e}.up_proj")])
+                   for e in range(cfg.num_experts)]
+            downs = [g.mat(f"{f}experts.{e}.down_proj") for e in range(cfg.num_experts)]
+            moe = LayerWeights(ln1=fn, ln2=fn, wqkv=None, wo=None, router_w=need(g.mat(f + "router"), f + "router"),
+                               experts_gate_up=_stack(gus).to(device), experts_down=_stack(downs).to(device))
+            blocks.append(HybridBlock("moe", fn, moe=moe))
+        else:
+            blocks.append(HybridBlock("mlp", fn, up=_cat_rows([need(g.mat(f + "gate_proj"), f + "gate_proj"),
+                                                               need(g.mat(f + "up_proj"), f + "up_proj")]),
+                                      down=need(g.mat(f + "down_proj"), f + "down_proj"), gated=True))
+    embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")
+    head = g.mat("lm_head") if src.has("lm_head.weight") and not cfg.tie_word_embeddings else None
+    return HybridWeights(embed=embed, blocks=blocks,
+                         final_norm=need(g.vec("model.final_layernorm.weight"), "model.final_layernorm.weight"),
+                         lm_head=embed if head is None else head.to(device), layers=attn_layers)
+
+
 def hybrid_config_dict(cfg: ModelConfig) -> dict:
     d = mamba_dims(cfg)
     return dict(model_type="nemotron_h", vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
@@ -254,8 +319,14 @@ class HybridModel:
         assert self.comm.tp_size == 1, "the hybrid executor is single-GPU"
         self.device = weights.final_norm.device
         mamba_layers = [b.mamba for b in weights.blocks if b.kind == "mamba2"]
-        self.ssm = Mamba2Model(cfg, Mamba2Weights(weights.embed, mamba_layers, weights.final_norm, weights.lm_head),
-                               max_seqs=max_seqs, comm=self.comm)
+        mamba1_layers = [b.mamba for b in weights.blocks if b.kind == "mamba1"]
+        if mamba1_layers:                       # Jamba: first-generation mixers
+            from .mamba1 import Mamba1Model
+            self.ssm = Mamba1Model(cfg, Mamba2Weights(weights.embed, mamba1_layers, weights.final_norm, weights.lm_head),
+                                   max_seqs=max_seqs, comm=self.comm)
+        else:
+            self.ssm = Mamba2Model(cfg, Mamba2Weights(weights.embed, mamba_layers, weights.final_norm, weights.lm_head),
+                                   max_seqs=max_seqs, comm=self.comm)
         self.attn = DecoderModel(cfg, ModelWeights(weights.embed, weights.layers, weights.final_norm, weights.lm_head),
                                  comm=self.comm, kv_bits=kv_bits)
         self.Hq, self.Hkv, self.D = self.attn.Hq, self.attn.Hkv, self.attn.D
@@ -282,9 +353,12 @@ class HybridModel:
 
         for blk in self.w.blocks:
             x = ops.rmsnorm(h, blk.norm, eps, 0.0)
-            if blk.kind == "mamba2":
+            if blk.kind in ("mamba2", "mamba1"):
                 h = add(self.ssm._mixer(mi, blk.mamba, x, pieces), blk.mamba.out_proj)
                 mi += 1
+            elif blk.kind == "moe":
+                from .moe import moe_forward
+                h = moe_forward(cfg, blk.moe, x, h, self.comm)
             elif blk.kind == "attention":
                 h = add(self.attn._attention(ai, blk.attn, x, b, kv_layers[ai]), blk.attn.wo, blk.attn.bo)
                 ai += 1

@@ -41,6 +41,9 @@ class Mamba1LayerWeights:
     out_proj: torch.Tensor    # [H, Di]
     in_proj_b: torch.Tensor | None = None
     out_proj_b: torch.Tensor | None = None
+    dt_norm: torch.Tensor | None = None      # Jamba: RMSNorm on the low-rank dt, on B and on C
+    b_norm: torch.Tensor | None = None
+    c_norm: torch.Tensor | None = None
 
 
 def mamba1_dims(cfg: ModelConfig) -> dict:
@@ -154,8 +157,12 @@ class Mamba1Model(Mamba2Model):
                                      True, max_len)                         # [T, Di]
         z = proj[:, Di:]
         ssm = ops.linear(xs, lw.x_proj)                                     # [T, R + 2N]
-        dt = ops.linear(ssm[:, :R].contiguous(), lw.dt_proj, bias=lw.dt_proj_b)   # [T, Di]; softplus in the scan
-        Bm, Cm = ssm[:, R:R + N].contiguous(), ssm[:, R + N:].contiguous()
+        dt_low, Bm, Cm = ssm[:, :R].contiguous(), ssm[:, R:R + N].contiguous(), ssm[:, R + N:].contiguous()
+        if lw.dt_norm is not None:
+            eps = self.cfg.rms_norm_eps
+            dt_low, Bm, Cm = (ops.rmsnorm(dt_low, lw.dt_norm, eps, 0.0), ops.rmsnorm(Bm, lw.b_norm, eps, 0.0),
+                              ops.rmsnorm(Cm, lw.c_norm, eps, 0.0))
+        dt = ops.linear(dt_low, lw.dt_proj, bias=lw.dt_proj_b)              # [T, Di]; softplus in the scan
         y = torch.empty_like(xs)
         dec_slots, pf = self._host_pieces
         st_all = self.ssm_state[li]
