@@ -496,6 +496,36 @@ def _granitemoehybrid(c: ModelConfig, raw: dict) -> None:
         c.partial_rotary_factor = 0.0
 
 
+def _qwen3_next(c: ModelConfig, raw: dict) -> None:
+    """Qwen3-Next: Gated DeltaNet layers and gated full-attention layers (per-head (1 + w) q/k norms,
+    rotary embedding on a quarter of each head, sigmoid output gate), each followed by a MoE with a
+    gated shared expert (or a dense MLP); norms are stored as (weight - 1)
+    (reference src/models/qwen3_next.rs). Runs on the hybrid executor as ``L`` / ``A`` + ``E`` / ``G``."""
+    n = c.num_hidden_layers
+    types = raw.get("layer_types")
+    if not types:
+        iv = int(raw.get("full_attention_interval", 4))
+        types = ["full_attention" if (i + 1) % iv == 0 else "linear_attention" for i in range(n)]
+    c.num_experts = int(raw.get("num_experts", 0) or 0)
+    c.moe_route_mode = "softmax_topk"
+    c.norm_topk_prob = bool(raw.get("norm_topk_prob", True))
+    step = int(raw.get("decoder_sparse_step", 1) or 1)
+    dense = set(raw.get("mlp_only_layers") or [])
+    pat = ""
+    for i, t in enumerate(types):
+        pat += "A" if t == "full_attention" else "L"
+        pat += "E" if (c.num_experts > 0 and i not in dense and (i + 1) % step == 0) else "G"
+    c.extra["hybrid_pattern"], c.extra["hybrid_layout"] = pat, "qwen3_next"
+    c.extra["gdn"] = dict(k_heads=int(raw.get("linear_num_key_heads", 16)), v_heads=int(raw.get("linear_num_value_heads", 32)),
+                          k_dim=int(raw.get("linear_key_head_dim", 128)), v_dim=int(raw.get("linear_value_head_dim", 128)),
+                          d_conv=int(raw.get("linear_conv_kernel_dim", 4)))
+    c.qk_norm = True
+    if "partial_rotary_factor" not in raw and not (raw.get("rope_parameters") or {}).get("partial_rotary_factor"):
+        c.partial_rotary_factor = 0.25
+    c.layer_types = None
+    c.sliding_window = 0
+
+
 def _jamba(c: ModelConfig, raw: dict) -> None:
     """Jamba: first-generation Mamba mixers (with RMSNorm on dt / B / C) and attention without
     positional encoding, interleaved by ``attn_layer_period / offset``; every layer ends in a gated
@@ -770,7 +800,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
 
 

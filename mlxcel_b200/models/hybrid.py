@@ -39,6 +39,7 @@ class HybridBlock:
     up: torch.Tensor | None = None              # plain MLP [I, H]; gated MLP: [2I, H] (gate rows first)
     down: torch.Tensor | None = None            # [H, I]
     gated: bool = False
+    out_gate: torch.Tensor | None = None        # gated attention (Qwen3-Next): [Hq * D, H] sigmoid gate projection
 
 
 @dataclass
@@ -50,12 +51,13 @@ class HybridWeights:
     layers: list = field(default_factory=list)  # the attention blocks' LayerWeights (= KV-pool layers)
 
 
-_KINDS = {"M": "mamba2", "m": "mamba1", "*": "attention", "-": "mlp", "G": "mlp", "E": "moe"}   # G: gated MLP
+_KINDS = {"M": "mamba2", "m": "mamba1", "L": "gdn", "*": "attention", "A": "attention", "-": "mlp", "G": "mlp",
+          "E": "moe"}   # G: gated MLP, A: attention with an output gate, L: Gated DeltaNet
 
 
 def block_kinds(cfg: ModelConfig) -> list[str]:
     pat = cfg.extra["hybrid_pattern"]
-    per_layer = 2 if cfg.extra.get("hybrid_layout") in ("granite", "jamba") else 1
+    per_layer = 2 if cfg.extra.get("hybrid_layout") in ("granite", "jamba", "qwen3_next") else 1
     if len(pat) != cfg.num_hidden_layers * per_layer:
         raise ValueError(f"hybrid pattern has {len(pat)} entries for {cfg.num_hidden_layers} layers")
     try:
@@ -259,6 +261,76 @@ def load_jamba_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu
                          lm_head=embed if head is None else head.to(device), layers=attn_layers)
 
 
+def load_qwen3_next_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
+    """Qwen3-Next checkpoint: ``model.layers.N.{input_layernorm, linear_attn.* | self_attn.*,
+    post_attention_layernorm, mlp.(gate + experts.E.* + shared_expert.* + shared_expert_gate | gate_proj ...)}``.
+    Layer norms, the final norm and the per-head q/k norms are stored as (weight - 1): one is added
+    here. ``q_proj`` carries query and output gate interleaved per head; they are separated."""
+    from ..loading.checkpoint import TensorSource, _Getter, _cat_rows, _stack
+    from .gdn import GdnLayerWeights, gdn_dims, regroup_ba, regroup_qkvz
+
+    src = TensorSource(path)
+    g = _Getter(src, cfg, dtype, dequantize=True)
+    d = gdn_dims(cfg)
+    Hq, D = cfg.num_attention_heads, cfg.head_dim
+
+    def need(t, name):
+        if t is None:
+            raise KeyError(f"{path}: missing tensor {name}")
+        return t.to(device)
+
+    def plus1(name):
+        return (need(g.vec(name), name).float() + 1.0).to(dtype)
+
+    blocks, attn_layers = [], []
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        norm = plus1(p + "input_layernorm.weight")
+        if src.has(p + "linear_attn.in_proj_qkvz.weight"):
+            m = p + "linear_attn."
+            cw = need(g.vec(m + "conv1d.weight"), m + "conv1d.weight")
+            cw = cw.reshape(d["conv_dim"], d["K"]) if cw.dim() == 2 or cw.shape[1] == 1 else cw.squeeze(-1)
+            lw = GdnLayerWeights(
+                norm=norm, in_proj=regroup_qkvz(need(g.mat(m + "in_proj_qkvz"), m + "in_proj_qkvz"), d),
+                in_proj_ba=regroup_ba(need(g.mat(m + "in_proj_ba"), m + "in_proj_ba"), d), conv_w=cw.float(),
+                dt_bias=need(g.vec(m + "dt_bias"), m + "dt_bias").float(),
+                A_log=need(g.vec(m + "A_log"), m + "A_log").float(),
+                gnorm=need(g.vec(m + "norm.weight"), m + "norm.weight"),
+                out_proj=need(g.mat(m + "out_proj"), m + "out_proj"))
+            blocks.append(HybridBlock("gdn", norm, mamba=lw))
+        else:
+            a = p + "self_attn."
+            qg = need(g.mat(a + "q_proj"), a + "q_proj").view(Hq, 2, D, -1)          # per head: query rows, gate rows
+            q, gate = qg[:, 0].reshape(Hq * D, -1), qg[:, 1].reshape(Hq * D, -1).contiguous()
+            k, v = need(g.mat(a + "k_proj"), a + "k_proj"), need(g.mat(a + "v_proj"), a + "v_proj")
+            lw = LayerWeights(ln1=norm, ln2=norm, wqkv=torch.cat([q, k, v], 0).contiguous(),
+                              wo=need(g.mat(a + "o_proj"), a + "o_proj"), q_norm=plus1(a + "q_norm.weight"),
+                              k_norm=plus1(a + "k_norm.weight"))
+            attn_layers.append(lw)
+            blocks.append(HybridBlock("attention", norm, attn=lw, out_gate=gate))
+        f = p + "mlp."
+        fn = plus1(p + "post_attention_layernorm.weight")
+        if src.has(f + "gate.weight"):
+            gus = [_cat_rows([g.mat(f"{f}experts.{e}.gate_proj"), g.mat(f"{f}experts.{e}.up_proj")])
+                   for e in range(cfg.num_experts)]
+            downs = [g.mat(f"{f}experts.{e}.down_proj") for e in range(cfg.num_experts)]
+            moe = LayerWeights(ln1=fn, ln2=fn, wqkv=None, wo=None, router_w=need(g.mat(f + "gate"), f + "gate"),
+                               experts_gate_up=_stack(gus).to(device), experts_down=_stack(downs).to(device))
+            if src.has(f + "shared_expert.gate_proj.weight"):
+                moe.shared_gate_up = _cat_rows([g.mat(f + "shared_expert.gate_proj"), g.mat(f + "shared_expert.up_proj")]).to(device)
+                moe.shared_down = need(g.mat(f + "shared_expert.down_proj"), f + "shared_expert.down_proj")
+                moe.shared_gate = need(g.mat(f + "shared_expert_gate"), f + "shared_expert_gate")
+            blocks.append(HybridBlock("moe", fn, moe=moe))
+        else:
+            blocks.append(HybridBlock("mlp", fn, up=_cat_rows([need(g.mat(f + "gate_proj"), f + "gate_proj"),
+                                                               need(g.mat(f + "up_proj"), f + "up_proj")]),
+                                      down=need(g.mat(f + "down_proj"), f + "down_proj"), gated=True))
+    embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")
+    head = g.mat("lm_head") if src.has("lm_head.weight") and not cfg.tie_word_embeddings else None
+    return HybridWeights(embed=embed, blocks=blocks, final_norm=plus1("model.norm.weight"),
+                         lm_head=embed if head is None else head.to(device), layers=attn_layers)
+
+
 def hybrid_config_dict(cfg: ModelConfig) -> dict:
     d = mamba_dims(cfg)
     return dict(model_type="nemotron_h", vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
@@ -320,7 +392,12 @@ class HybridModel:
         self.device = weights.final_norm.device
         mamba_layers = [b.mamba for b in weights.blocks if b.kind == "mamba2"]
         mamba1_layers = [b.mamba for b in weights.blocks if b.kind == "mamba1"]
-        if mamba1_layers:                       # Jamba: first-generation mixers
+        gdn_layers = [b.mamba for b in weights.blocks if b.kind == "gdn"]
+        if gdn_layers:                          # Qwen3-Next: Gated DeltaNet mixers
+            from .gdn import GdnModel
+            self.ssm = GdnModel(cfg, Mamba2Weights(weights.embed, gdn_layers, weights.final_norm, weights.lm_head),
+                                max_seqs=max_seqs, comm=self.comm)
+        elif mamba1_layers:                     # Jamba: first-generation mixers
             from .mamba1 import Mamba1Model
             self.ssm = Mamba1Model(cfg, Mamba2Weights(weights.embed, mamba1_layers, weights.final_norm, weights.lm_head),
                                    max_seqs=max_seqs, comm=self.comm)
@@ -353,14 +430,17 @@ class HybridModel:
 
         for blk in self.w.blocks:
             x = ops.rmsnorm(h, blk.norm, eps, 0.0)
-            if blk.kind in ("mamba2", "mamba1"):
+            if blk.kind in ("mamba2", "mamba1", "gdn"):
                 h = add(self.ssm._mixer(mi, blk.mamba, x, pieces), blk.mamba.out_proj)
                 mi += 1
             elif blk.kind == "moe":
                 from .moe import moe_forward
                 h = moe_forward(cfg, blk.moe, x, h, self.comm)
             elif blk.kind == "attention":
-                h = add(self.attn._attention(ai, blk.attn, x, b, kv_layers[ai]), blk.attn.wo, blk.attn.bo)
+                a = self.attn._attention(ai, blk.attn, x, b, kv_layers[ai])
+                if blk.out_gate is not None:     # Qwen3-Next: sigmoid gate computed from the block input
+                    a = (a.float() * torch.sigmoid(ops.linear(x, blk.out_gate).float())).to(a.dtype)
+                h = add(a, blk.attn.wo, blk.attn.bo)
                 ai += 1
             elif blk.gated:
                 h = add(ops.glu_linear(x, blk.up, blk.up.shape[0] // 2, "silu"), blk.down)
