@@ -276,3 +276,83 @@ def test_tiny_mamba1_engine_gpu_matches_cpu():
     from mlxcel_b200.ops import _lib
     torch.cuda.synchronize()
     assert _lib.read_status(torch.device(DEV)) == 0
+
+
+def _tiny_hf_hybrid(name):
+    """A tiny random checkpoint of a hybrid family written by transformers (skipped where it is missing)."""
+    import tempfile
+    transformers = pytest.importorskip("transformers")
+    from transformers import AutoConfig, AutoModelForCausalLM
+    common = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=2,
+                  num_key_value_heads=1, vocab_size=512, max_position_embeddings=256, pad_token_id=0)   # head size 64
+    kw = {
+        "jamba": dict(attn_layer_period=4, attn_layer_offset=2, expert_layer_period=2, expert_layer_offset=1,
+                      num_experts=8, num_experts_per_tok=2, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2,
+                      mamba_dt_rank=8, use_mamba_kernels=False),
+        "qwen3_next": dict(head_dim=64, layer_types=["linear_attention", "linear_attention", "full_attention",
+                                                     "linear_attention"],
+                           linear_conv_kernel_dim=4, linear_key_head_dim=32, linear_value_head_dim=32,
+                           linear_num_key_heads=2, linear_num_value_heads=4, num_experts=8, num_experts_per_tok=2,
+                           moe_intermediate_size=128, shared_expert_intermediate_size=128, decoder_sparse_step=1,
+                           mlp_only_layers=[1]),
+        "granitemoehybrid": dict(shared_intermediate_size=256, layer_types=["mamba", "attention", "mamba", "mamba"],
+                                 num_local_experts=0, mamba_n_heads=8, mamba_d_head=32, mamba_d_state=32,
+                                 mamba_n_groups=2, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=8,
+                                 embedding_multiplier=2.0, residual_multiplier=0.5, attention_multiplier=0.125,
+                                 logits_scaling=2.0),
+    }[name]
+    torch.manual_seed(0)
+    try:
+        model = AutoModelForCausalLM.from_config(AutoConfig.for_model(name, **common, **kw)).float()
+    except (KeyError, ValueError, ImportError) as e:
+        pytest.skip(f"transformers cannot build {name}: {e}")
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2 and "A_log" not in n:
+                p.normal_(0, 0.05)
+    d = tempfile.mkdtemp(prefix=f"hyb_{name}_")
+    model.save_pretrained(d, safe_serialization=True)
+    return d
+
+
+@pytest.mark.parametrize("name", ["jamba", "qwen3_next", "granitemoehybrid"])
+def test_hybrid_checkpoints_gpu_matches_cpu(name):
+    """Hybrid layouts end to end on the GPU (bf16 kernels) against this package's fp32 CPU path, from a
+    checkpoint written by transformers: prompt logits, then a short greedy run through the engine."""
+    from mlxcel_b200.cache.kv_pool import KVPool
+    from mlxcel_b200.config import ModelConfig
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.models import hybrid
+    from mlxcel_b200.models.decoder import StepBatch
+
+    d = _tiny_hf_hybrid(name)
+    cfg = ModelConfig.from_path(d)
+    load = {"jamba": hybrid.load_jamba_weights, "qwen3_next": hybrid.load_qwen3_next_weights,
+            "granitemoehybrid": hybrid.load_granite_hybrid_weights}[name]
+    T = 40
+    ids = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+
+    def logits(dev, dtype):
+        m = hybrid.HybridModel(cfg, load(d, cfg, dtype=dtype, device=dev), max_seqs=4)
+        pool = KVPool(cfg, 8, 16, device=dev, dtype=dtype, num_layers=m.num_kv_layers)
+        b = StepBatch(token_ids=ids.to(dev), positions=torch.arange(T, dtype=torch.int32, device=dev),
+                      slot_mapping=torch.arange(T, dtype=torch.int32, device=dev), num_prefill_seqs=1,
+                      pf_block_tables=torch.arange(8, dtype=torch.int32, device=dev)[None],
+                      pf_cu_q=torch.tensor([0, T], dtype=torch.int32, device=dev),
+                      pf_context_lens=torch.tensor([T], dtype=torch.int32, device=dev), pf_max_q_len=T,
+                      pf_cu_q_host=[0, T], logits_rows=torch.tensor([T - 1, T // 2], device=dev))
+        b.seq_ids, b.pf_starts = [0], [0]
+        return m.forward(b, pool.layers).float().cpu(), m
+
+    lc, _ = logits("cpu", torch.float32)
+    lg, m16 = logits(DEV, torch.bfloat16)
+    assert (lc - lg).abs().max().item() < 0.06 * lc.abs().max().item() + 0.04, name
+    m16.release_seq(0)
+    eng = Engine(m16, cfg, EngineConfig(num_blocks=64, block_size=16, max_batch=8, max_model_len=256,
+                                        max_num_batched_tokens=32))
+    outs = eng.generate([ids[:37].tolist(), ids[5:12].tolist()], SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
+    assert all(len(s.output) == 6 for s in outs) and not m16.ssm.slot_of
+    from mlxcel_b200.ops import _lib
+    torch.cuda.synchronize()
+    assert _lib.read_status(torch.device(DEV)) == 0
