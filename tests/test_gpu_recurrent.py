@@ -294,7 +294,7 @@ def _tiny_hf_hybrid(name):
                            linear_conv_kernel_dim=4, linear_key_head_dim=32, linear_value_head_dim=32,
                            linear_num_key_heads=2, linear_num_value_heads=4, num_experts=8, num_experts_per_tok=2,
                            moe_intermediate_size=128, shared_expert_intermediate_size=128, decoder_sparse_step=1,
-                           mlp_only_layers=[1]),
+                           mlp_only_layers=[0, 1, 2, 3]),     # dense MLPs: no expert choice that bf16 could flip
         "granitemoehybrid": dict(shared_intermediate_size=256, layer_types=["mamba", "attention", "mamba", "mamba"],
                                  num_local_experts=0, mamba_n_heads=8, mamba_d_head=32, mamba_d_state=32,
                                  mamba_n_groups=2, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=8,
