@@ -157,11 +157,28 @@ def cmd_run(a):
         msgs.append({"role": "assistant", "content": "".join(parts)})
 
 
+def _encoder_checkpoint(path: str) -> bool:
+    cj = os.path.join(path, "config.json")
+    return os.path.exists(cj) and json.load(open(cj)).get("model_type") in ("bert",)
+
+
 def cmd_serve(a):
     import uvicorn
 
     from .server.app import ServerState, create_app
     from .server.worker import ModelWorker
+    if _encoder_checkpoint(a.model):            # encoder checkpoints get the embeddings-only server
+        import torch
+
+        from .models.encoder import BertEncoder
+        from .server.embeddings import create_embedding_app
+        from .tokenizer import load_tokenizer
+        dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        enc = BertEncoder.from_pretrained(a.model, device=dev)
+        app = create_embedding_app(enc, load_tokenizer(a.model), a.alias or os.path.basename(a.model.rstrip("/")),
+                                   set(a.api_key or []))
+        uvicorn.run(app, host=a.host, port=a.port, log_level="info" if a.verbose else "warning")
+        return
     llm = load_llm(a)
     worker = ModelWorker(llm.engine, llm.tokenizer, a.alias or os.path.basename(a.model.rstrip("/")))
     keys = set(a.api_key or [])

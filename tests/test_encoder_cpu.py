@@ -1,0 +1,54 @@
+"""BERT-family encoder embeddings: hidden states against transformers, and the embeddings-only server."""
+import tempfile
+
+import pytest
+import torch
+from fastapi.testclient import TestClient
+
+transformers = pytest.importorskip("transformers")
+
+from mlxcel_b200.models.encoder import BertEncoder  # noqa: E402
+from mlxcel_b200.server.embeddings import create_embedding_app  # noqa: E402
+from mlxcel_b200.tokenizer import ByteTokenizer  # noqa: E402
+
+
+def _tiny_bert():
+    from transformers import BertConfig, BertModel
+    torch.manual_seed(0)
+    m = BertModel(BertConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                             vocab_size=300, max_position_embeddings=64)).float().eval()
+    with torch.no_grad():
+        for _, p in m.named_parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.08)
+            else:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tempfile.mkdtemp(prefix="bert_")
+    m.save_pretrained(d, safe_serialization=True)
+    return m, d
+
+
+def test_bert_hidden_states_match_transformers():
+    m, d = _tiny_bert()
+    ids = torch.randint(0, 300, (19,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = m(ids[None]).last_hidden_state[0]
+    enc = BertEncoder.from_pretrained(d, dtype=torch.float32)
+    got = enc.hidden_states(ids.tolist())
+    assert (got - want).abs().max().item() < 1e-4
+    v = enc.embed(ids.tolist(), "cls")
+    assert abs(v.norm().item() - 1.0) < 1e-5 and torch.allclose(v, want[0] / want[0].norm(), atol=1e-5)
+
+
+def test_embedding_server_routes():
+    _, d = _tiny_bert()
+    enc = BertEncoder.from_pretrained(d, dtype=torch.float32)
+    app = create_embedding_app(enc, ByteTokenizer(300), "tiny-bert", api_keys={"k"})
+    with TestClient(app) as c:
+        assert c.post("/v1/embeddings", json=dict(input="hi")).status_code == 401
+        h = {"authorization": "Bearer k"}
+        r = c.post("/v1/embeddings", json=dict(input=["hello", "world!"]), headers=h).json()
+        assert len(r["data"]) == 2 and len(r["data"][0]["embedding"]) == 64 and r["usage"]["prompt_tokens"] > 0
+        one = c.post("/embedding", json=dict(content="hello"), headers=h).json()
+        assert one[0]["embedding"] == pytest.approx(r["data"][0]["embedding"], abs=1e-6)
+        assert c.get("/v1/models", headers=h).json()["data"][0]["id"] == "tiny-bert"
