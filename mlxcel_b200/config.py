@@ -658,6 +658,28 @@ def _dots1(c: ModelConfig, raw: dict) -> None:
     c.qk_norm = True
 
 
+def _phimoe(c: ModelConfig, raw: dict) -> None:
+    """Phi-3.5-MoE: LayerNorm with bias, biased attention projections and LM head, top-2 SparseMixer
+    routing (reference src/models/phimoe.rs)."""
+    c.extra["norm"] = "layernorm"
+    c.attention_bias = True
+    c.moe_route_mode = "sparsemixer"
+    c.num_experts_per_tok = 2
+    c.moe_intermediate_size = c.intermediate_size
+    c.extra["router_jitter"] = float(raw.get("router_jitter_noise", 0.01))
+
+
+def _hunyuan_dense(c: ModelConfig, raw: dict) -> None:
+    """Hunyuan dense: Llama layout with per-head q/k RMSNorm applied after the rotary embedding
+    (reference src/models/hunyuan_v1_dense.rs)."""
+    c.qk_norm = True
+    c.extra["qk_norm_after_rope"] = True
+    rs = c.rope_scaling or {}
+    if rs.get("alpha") and rs.get("rope_type", rs.get("type")) in ("dynamic", None):
+        # NTK-alpha scaling: the base grows by alpha^(D / (D - 2))
+        c.rope_theta = c.rope_theta * float(rs["alpha"]) ** (c.head_dim / (c.head_dim - 2))
+
+
 def _arcee(c: ModelConfig, raw: dict) -> None:
     """Llama layout with a plain MLP up -> relu^2 -> down (reference src/models/arcee.rs)."""
     c.extra["mlp"] = "plain"
@@ -792,10 +814,10 @@ def _nemotron_h(c: ModelConfig, raw: dict) -> None:
 
 FAMILIES = {
     "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _smollm3, "seed_oss": _plain,
-    "helium": _interleaved_rope, "internlm3": _plain, "exaone4": _exaone4,
+    "helium": _interleaved_rope, "internlm3": _plain, "exaone4": _exaone4, "hunyuan_v1_dense": _hunyuan_dense,
     "ernie4_5": _interleaved_rope, "apertus": _apertus, "minicpm": _minicpm, "mimo": _qwen2, "yi": _plain,
     "qwen2": _qwen2, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
-    "mixtral": _mixtral, "olmoe": _olmoe,
+    "mixtral": _mixtral, "phimoe": _phimoe, "olmoe": _olmoe,
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,

@@ -236,8 +236,8 @@ def _load_attention(g: _Getter, cfg: ModelConfig, p: str, lw_kwargs: dict) -> No
     ob = a + (".o_proj" if g.has(a + ".o_proj") else ".dense")      # Phi names the output projection "dense"
     lw_kwargs["wo"] = g.mat(ob)
     lw_kwargs["bo"] = g.vec(ob + ".bias")
-    lw_kwargs["q_norm"] = g.vec(a + ".q_norm.weight")
-    lw_kwargs["k_norm"] = g.vec(a + ".k_norm.weight")
+    lw_kwargs["q_norm"] = g.vec(_first_name(g.src, a + ".q_norm.weight", a + ".query_layernorm.weight"))
+    lw_kwargs["k_norm"] = g.vec(_first_name(g.src, a + ".k_norm.weight", a + ".key_layernorm.weight"))
     if cfg.norm_weight_bias and lw_kwargs["q_norm"] is not None:
         # Gemma 3 stores the per-head norms as (weight - 1) like its other norms; the fused
         # q/k-norm + RoPE kernel takes plain gains

@@ -199,6 +199,18 @@ class DecoderModel:
         local = window > 0 and self.inv_freq_local is not None
         layer_index = self.layer_range[li] if li < len(self.layer_range) else li
         rot_dim = 0 if layer_index in self.nope_layers else cfg.rot_dim    # layers without positional encoding
+        if q_norm is not None and cfg.extra.get("qk_norm_after_rope") and rot_dim:
+            # Hunyuan: the per-head q/k norms come AFTER the rotation; the fused kernel norms before it, so
+            # rotate and normalise here and let the kernel only append
+            from ..ops import reference as ref
+            T0, nqk = qkv.shape[0], self.Hq + self.Hkv
+            x3 = qkv.view(T0, self.Hq + 2 * self.Hkv, self.D)
+            rot = ref.apply_rope(x3[:, :nqk], b.positions, self.inv_freq, rot_dim, cfg.rope_traditional, self.mscale)
+            qn = ref.head_rmsnorm(rot[:, :self.Hq], q_norm, cfg.rms_norm_eps)
+            kn = ref.head_rmsnorm(rot[:, self.Hq:], k_norm, cfg.rms_norm_eps)
+            qkv = torch.cat([qn.to(qkv.dtype), kn.to(qkv.dtype), x3[:, nqk:]], dim=1).reshape(T0, -1).contiguous()
+            q_norm = k_norm = None
+            rot_dim = 0
         ops.rope_append(qkv, b.positions, b.slot_mapping, self.inv_freq_local if local else self.inv_freq, kv,
                         Hq=self.Hq, Hkv=self.Hkv, D=self.D, rot_dim=rot_dim,
                         traditional=cfg.rope_traditional, mscale=1.0 if local else self.mscale,

@@ -25,7 +25,10 @@ def _dense(w):
 
 def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -> torch.Tensor:
     """Returns the new residual stream ``h + moe(x)`` (bf16 [T, H])."""
-    if cfg.moe_route_mode == "sigmoid_group":
+    if cfg.moe_route_mode == "sparsemixer":
+        logits = ops.linear(x, lw.router_w, bias=lw.router_b)
+        ids, wts = moe_ops.route_sparsemixer(logits, cfg.extra.get("router_jitter", 0.01))
+    elif cfg.moe_route_mode == "sigmoid_group":
         r = cfg.extra["moe_routing"]
         logits = x.float() @ lw.router_w.float().t()            # the router runs in fp32
         ids, wts = moe_ops.route_sigmoid_grouped(logits, cfg.num_experts_per_tok, lw.router_b, r["n_group"],

@@ -78,6 +78,24 @@ def route_sigmoid_grouped(logits: torch.Tensor, k: int, bias: torch.Tensor | Non
     return ids.to(torch.int32).contiguous(), (w * scale).contiguous()
 
 
+def route_sparsemixer(logits: torch.Tensor, jitter_eps: float = 0.01):
+    """Phi-MoE's inference-time SparseMixer (top-2): the first expert is the arg-max; its weight is its
+    softmax probability among the experts whose logit lies within a relative margin ``2 * jitter_eps``
+    of the maximum. The second expert and its weight come from the same rule with the first expert
+    removed. Weights are not renormalised. Plain tensor ops on [T, E]
+    (reference src/models/phimoe.rs). Returns (ids int32 [T, 2], weights fp32 [T, 2])."""
+    s = logits.float()
+    ids, ws = [], []
+    for _ in range(2):
+        top, idx = s.max(dim=-1, keepdim=True)
+        factor = logits.float().abs().clamp(min=top)
+        masked = s.masked_fill(((top - logits.float()) / factor) > 2 * jitter_eps, float("-inf"))
+        ws.append(torch.softmax(masked, dim=-1).gather(-1, idx))
+        ids.append(idx)
+        s = s.scatter(-1, idx, float("-inf"))
+    return torch.cat(ids, -1).to(torch.int32).contiguous(), torch.cat(ws, -1).contiguous()
+
+
 # ----------------------------------------------------------------------------- CUDA
 def route(logits: torch.Tensor, k: int, mode: str = "topk_softmax", norm_topk: bool = True):
     """Router logits [T, E] → (expert ids [T, k] int32, weights [T, k] fp32)."""
