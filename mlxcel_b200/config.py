@@ -680,6 +680,17 @@ def _hunyuan_dense(c: ModelConfig, raw: dict) -> None:
         c.rope_theta = c.rope_theta * float(rs["alpha"]) ** (c.head_dim / (c.head_dim - 2))
 
 
+def _hunyuan_moe(c: ModelConfig, raw: dict) -> None:
+    """Hunyuan MoE (Hunyuan-A13B): the dense layout plus softmax top-k experts (renormalised) and an
+    always-on shared MLP (reference src/models/hunyuan_moe.rs)."""
+    _hunyuan_dense(c, raw)
+    c.moe_route_mode, c.norm_topk_prob = "softmax_topk", True
+    k = raw.get("moe_topk", 2)
+    c.num_experts_per_tok = int(k[0] if isinstance(k, (list, tuple)) else k)
+    c.moe_intermediate_size = c.intermediate_size
+    c.shared_expert_intermediate_size = c.intermediate_size
+
+
 def _arcee(c: ModelConfig, raw: dict) -> None:
     """Llama layout with a plain MLP up -> relu^2 -> down (reference src/models/arcee.rs)."""
     c.extra["mlp"] = "plain"
@@ -815,6 +826,7 @@ def _nemotron_h(c: ModelConfig, raw: dict) -> None:
 FAMILIES = {
     "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _smollm3, "seed_oss": _plain,
     "helium": _interleaved_rope, "internlm3": _plain, "exaone4": _exaone4, "hunyuan_v1_dense": _hunyuan_dense,
+    "hunyuan_v1_moe": _hunyuan_moe,
     "ernie4_5": _interleaved_rope, "apertus": _apertus, "minicpm": _minicpm, "mimo": _qwen2, "yi": _plain,
     "qwen2": _qwen2, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "mixtral": _mixtral, "phimoe": _phimoe, "olmoe": _olmoe,

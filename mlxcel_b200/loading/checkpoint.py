@@ -268,7 +268,7 @@ def _load_dense_mlp(g: _Getter, p: str, lw: LayerWeights) -> None:
 def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
     E = cfg.num_experts
     # router
-    rb = _first(g, p + ".mlp.router", p + ".mlp.gate", p + ".block_sparse_moe.gate",
+    rb = _first(g, p + ".mlp.router", p + ".mlp.gate.wg", p + ".mlp.gate", p + ".block_sparse_moe.gate",
                 p + ".block_sparse_moe.router.layer")
     r = g.mat(rb)
     if isinstance(r, QuantizedTensor):   # routers are small: keep them dense
@@ -314,7 +314,8 @@ def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
             gus.append(_cat_rows([g.mat(f"{root}.{e}.{names[0]}"), g.mat(f"{root}.{e}.{names[1]}")]))
             downs.append(g.mat(f"{root}.{e}.{names[2]}"))
         lw.experts_gate_up, lw.experts_down = _stack(gus), _stack(downs)
-    sh = p + (".mlp.shared_experts" if g.has(p + ".mlp.shared_experts.gate_proj") else ".mlp.shared_expert")
+    sh = next((p + n for n in (".mlp.shared_experts", ".mlp.shared_mlp") if g.has(p + n + ".gate_proj")),
+              p + ".mlp.shared_expert")
     if g.has(sh + ".gate_proj"):
         lw.shared_gate_up = _cat_rows([g.mat(sh + ".gate_proj"), g.mat(sh + ".up_proj")])
         lw.shared_down = g.mat(sh + ".down_proj")
@@ -369,7 +370,7 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
             lw.post_attn_norm = g.vec(f"{p}.{names[0]}.weight")
             lw.ln2 = g.vec(f"{p}.{names[1]}.weight")
             lw.post_mlp_norm = g.vec(f"{p}.{names[2]}.weight")
-        if cfg.is_moe and _first(g, p + ".mlp.router", p + ".mlp.gate", p + ".block_sparse_moe.gate",
+        if cfg.is_moe and _first(g, p + ".mlp.router", p + ".mlp.gate.wg", p + ".mlp.gate", p + ".block_sparse_moe.gate",
                                  p + ".block_sparse_moe.router.layer"):
             _load_moe(g, cfg, p, lw)
         else:

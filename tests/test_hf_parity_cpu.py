@@ -35,6 +35,7 @@ FAMILIES = {
                        attention_multiplier=0.2, logits_scaling=3.0),
     "mixtral": dict(num_local_experts=4, num_experts_per_tok=2),
     "phimoe": dict(num_local_experts=4, num_experts_per_tok=2), "hunyuan_v1_dense": dict(head_dim=16),
+    "hunyuan_v1_moe": dict(head_dim=16, num_experts=4, moe_topk=2, pad_token_id=0),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                       shared_expert_intermediate_size=96, decoder_sparse_step=1),
     "qwen3_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48, head_dim=32,
