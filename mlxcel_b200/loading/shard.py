@@ -57,6 +57,8 @@ def _cat_rows(parts):
 def shard_layer(cfg: ModelConfig, lw: LayerWeights, rank: int, tp: int, ep_rank: int = 0,
                 ep: int = 1) -> LayerWeights:
     D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    if getattr(lw, "mla", None) is not None and tp > 1:
+        raise NotImplementedError("tensor-parallel sharding of multi-head latent attention")
     if Hq % tp:
         raise ValueError("attention heads must divide the tensor-parallel degree")
     hq = Hq // tp
