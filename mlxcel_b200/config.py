@@ -526,6 +526,37 @@ def _qwen3_next(c: ModelConfig, raw: dict) -> None:
     c.sliding_window = 0
 
 
+def _falcon_h1(c: ModelConfig, raw: dict) -> None:
+    """Falcon-H1: every layer runs a Mamba2 mixer and rotary attention in parallel on the same normed
+    input, then a gated MLP; the muP multipliers of the checkpoint (embedding, mixer input / per-segment
+    / output, attention input / key / output, MLP gate / down, LM head) are folded into the weights at
+    load (reference src/models/falcon_h1.rs). Runs on the hybrid executor as ``P`` + ``G`` per layer."""
+    hs = c.hidden_size
+    P = int(raw.get("mamba_d_head", 64))
+    d_inner = int(raw.get("mamba_d_ssm") or raw.get("mamba_expand", 2) * hs)
+    G = int(raw.get("mamba_n_groups", 1))
+    lim = raw.get("time_step_limit") or (0.0, float("inf"))
+    mode = "none"
+    if raw.get("mamba_rms_norm", False):
+        mode = "norm_then_gate" if raw.get("mamba_norm_before_gate", True) else "gate_then_norm"
+    c.extra["mamba"] = dict(d_inner=d_inner, head_dim=P, n_groups=G, d_state=int(raw.get("mamba_d_state", 128)),
+                            d_conv=int(raw.get("mamba_d_conv", 4)), time_step_limit=(_num(lim[0]), _num(lim[1])),
+                            norm_groups=G, gate_mode=mode)
+    c.extra["hybrid_pattern"], c.extra["hybrid_layout"] = "PG" * c.num_hidden_layers, "falcon_h1"
+    c.embed_scale = float(raw.get("embedding_multiplier", 1.0))
+    c.extra["logits_scaling"] = 1.0 / float(raw.get("lm_head_multiplier", 1.0))
+    sm = raw.get("ssm_multipliers") or [1.0] * 5
+    mm = raw.get("mlp_multipliers") or [1.0, 1.0]
+    c.extra["falcon_mup"] = dict(ssm_in=float(raw.get("ssm_in_multiplier", 1.0)), ssm=[float(v) for v in sm],
+                                 ssm_out=float(raw.get("ssm_out_multiplier", 1.0)),
+                                 attn_in=float(raw.get("attention_in_multiplier", 1.0)),
+                                 key=float(raw.get("key_multiplier", 1.0)),
+                                 attn_out=float(raw.get("attention_out_multiplier", 1.0)),
+                                 gate=float(mm[0]), down=float(mm[1]))
+    c.layer_types = None
+    c.sliding_window = 0
+
+
 def _jamba(c: ModelConfig, raw: dict) -> None:
     """Jamba: first-generation Mamba mixers (with RMSNorm on dt / B / C) and attention without
     positional encoding, interleaved by ``attn_layer_period / offset``; every layer ends in a gated
@@ -834,7 +865,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
 }
 
 

@@ -51,13 +51,13 @@ class HybridWeights:
     layers: list = field(default_factory=list)  # the attention blocks' LayerWeights (= KV-pool layers)
 
 
-_KINDS = {"M": "mamba2", "m": "mamba1", "L": "gdn", "*": "attention", "A": "attention", "-": "mlp", "G": "mlp",
+_KINDS = {"M": "mamba2", "m": "mamba1", "L": "gdn", "P": "parallel", "*": "attention", "A": "attention", "-": "mlp", "G": "mlp",
           "E": "moe"}   # G: gated MLP, A: attention with an output gate, L: Gated DeltaNet
 
 
 def block_kinds(cfg: ModelConfig) -> list[str]:
     pat = cfg.extra["hybrid_pattern"]
-    per_layer = 2 if cfg.extra.get("hybrid_layout") in ("granite", "jamba", "qwen3_next") else 1
+    per_layer = 2 if cfg.extra.get("hybrid_layout") in ("granite", "jamba", "qwen3_next", "falcon_h1") else 1
     if len(pat) != cfg.num_hidden_layers * per_layer:
         raise ValueError(f"hybrid pattern has {len(pat)} entries for {cfg.num_hidden_layers} layers")
     try:
@@ -331,6 +331,64 @@ def load_qwen3_next_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device
                          lm_head=embed if head is None else head.to(device), layers=attn_layers)
 
 
+def load_falcon_h1_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
+    """Falcon-H1 checkpoint: ``model.layers.N.{input_layernorm, mamba.*, self_attn.*, pre_ff_layernorm,
+    feed_forward.*}``. Every muP multiplier of the config is a constant factor on one projection's
+    input or output, so it is multiplied into that projection's weight here and the executor runs
+    plain blocks."""
+    from ..loading.checkpoint import TensorSource, _Getter, _cat_rows
+
+    src = TensorSource(path)
+    g = _Getter(src, cfg, dtype, dequantize=True)
+    d = mamba_dims(cfg)
+    mup = cfg.extra["falcon_mup"]
+    di, gn = d["d_inner"], d["G"] * d["N"]
+    seg = torch.cat([torch.full((n,), v) for n, v in zip((di, di, gn, gn, d["heads"]), mup["ssm"])]) * mup["ssm_in"]
+
+    def need(t, name):
+        if t is None:
+            raise KeyError(f"{path}: missing tensor {name}")
+        return t.to(device)
+
+    def scaled(name, factor):
+        w = need(g.mat(name), name)
+        return w if factor == 1.0 else (w.float() * factor).to(w.dtype)
+
+    blocks, attn_layers = [], []
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        norm = need(g.vec(p + "input_layernorm.weight"), p + "input_layernorm.weight")
+        m = p + "mamba."
+        cw = need(g.vec(m + "conv1d.weight"), m + "conv1d.weight")
+        cw = cw.reshape(d["conv_dim"], d["K"]) if cw.dim() == 2 or cw.shape[1] == 1 else cw.squeeze(-1)
+        cb = g.vec(m + "conv1d.bias")
+        w_in = need(g.mat(m + "in_proj"), m + "in_proj")
+        gn_w = g.vec(m + "norm.weight")
+        mw = Mamba2LayerWeights(
+            norm=norm, in_proj=(w_in.float() * seg.to(w_in.device).unsqueeze(1)).to(w_in.dtype), conv_w=cw.float(),
+            conv_b=None if cb is None else cb.float().to(device),
+            dt_bias=need(g.vec(m + "dt_bias"), m + "dt_bias").float(), A_log=need(g.vec(m + "A_log"), m + "A_log").float(),
+            D=need(g.vec(m + "D"), m + "D").float(),
+            gnorm=torch.ones(di, dtype=dtype, device=device) if gn_w is None else gn_w.to(device),
+            out_proj=scaled(m + "out_proj", mup["ssm_out"]))
+        a = p + "self_attn."
+        q, k, v = (scaled(a + "q_proj", mup["attn_in"]), scaled(a + "k_proj", mup["attn_in"] * mup["key"]),
+                   scaled(a + "v_proj", mup["attn_in"]))
+        aw = LayerWeights(ln1=norm, ln2=norm, wqkv=torch.cat([q, k, v], 0).contiguous(),
+                          wo=scaled(a + "o_proj", mup["attn_out"]))
+        attn_layers.append(aw)
+        blocks.append(HybridBlock("parallel", norm, mamba=mw, attn=aw))
+        f = p + "feed_forward."
+        blocks.append(HybridBlock("mlp", need(g.vec(p + "pre_ff_layernorm.weight"), p + "pre_ff_layernorm.weight"),
+                                  up=_cat_rows([scaled(f + "gate_proj", mup["gate"]), need(g.mat(f + "up_proj"), f + "up_proj")]),
+                                  down=scaled(f + "down_proj", mup["down"]), gated=True))
+    embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")
+    head = g.mat("lm_head") if src.has("lm_head.weight") and not cfg.tie_word_embeddings else None
+    return HybridWeights(embed=embed, blocks=blocks,
+                         final_norm=need(g.vec("model.final_layernorm.weight"), "model.final_layernorm.weight"),
+                         lm_head=embed if head is None else head.to(device), layers=attn_layers)
+
+
 def hybrid_config_dict(cfg: ModelConfig) -> dict:
     d = mamba_dims(cfg)
     return dict(model_type="nemotron_h", vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
@@ -390,7 +448,7 @@ class HybridModel:
         self.comm = comm or LocalComm()
         assert self.comm.tp_size == 1, "the hybrid executor is single-GPU"
         self.device = weights.final_norm.device
-        mamba_layers = [b.mamba for b in weights.blocks if b.kind == "mamba2"]
+        mamba_layers = [b.mamba for b in weights.blocks if b.kind in ("mamba2", "parallel")]
         mamba1_layers = [b.mamba for b in weights.blocks if b.kind == "mamba1"]
         gdn_layers = [b.mamba for b in weights.blocks if b.kind == "gdn"]
         if gdn_layers:                          # Qwen3-Next: Gated DeltaNet mixers
@@ -433,6 +491,12 @@ class HybridModel:
             if blk.kind in ("mamba2", "mamba1", "gdn"):
                 h = add(self.ssm._mixer(mi, blk.mamba, x, pieces), blk.mamba.out_proj)
                 mi += 1
+            elif blk.kind == "parallel":         # Falcon-H1: Mamba2 mixer and attention side by side
+                ym = ops.linear(self.ssm._mixer(mi, blk.mamba, x, pieces), blk.mamba.out_proj)
+                ya = ops.linear(self.attn._attention(ai, blk.attn, x, b, kv_layers[ai]), blk.attn.wo, bias=blk.attn.bo)
+                h = (h.float() + ym.float() + ya.float()).to(h.dtype)
+                mi += 1
+                ai += 1
             elif blk.kind == "moe":
                 from .moe import moe_forward
                 h = moe_forward(cfg, blk.moe, x, h, self.comm)

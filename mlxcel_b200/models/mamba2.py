@@ -182,6 +182,7 @@ class Mamba2Model:
         lim = cfg.extra["mamba"].get("time_step_limit", (0.0, float("inf")))
         self.dt_limit = (float(lim[0]), float(lim[1]))
         self.norm_groups = int(cfg.extra["mamba"].get("norm_groups", 1))   # Nemotron-H: one norm per B/C group
+        self.gate_mode = cfg.extra["mamba"].get("gate_mode", "gate_then_norm")
 
     # ------------------------------------------------------------------ state slots
     def _slot(self, seq_id: int, resets: bool) -> int:
@@ -215,7 +216,15 @@ class Mamba2Model:
         conv = rops.causal_conv_varlen(xBC, self.conv_state[li], slots, cu, reset, lw.conv_w, lw.conv_b, True, max_len)
         y = rops.ssm_scan_varlen(self.ssm_state[li], slots, cu, reset, conv[:, :di], dt, self.A[li],
                                  conv[:, di:di + GN], conv[:, di + GN:], lw.D, lw.dt_bias, True, self.dt_limit, nd)
-        return rops.gated_rmsnorm(y, z, lw.gnorm, self.cfg.rms_norm_eps, self.norm_groups)
+        mode = self.gate_mode
+        if mode == "gate_then_norm":           # Mamba2, Nemotron-H, Granite: RMSNorm(y * silu(z))
+            return rops.gated_rmsnorm(y, z, lw.gnorm, self.cfg.rms_norm_eps, self.norm_groups)
+        if mode == "none":                      # Falcon-H1 without the mixer norm: y * silu(z)
+            return (y.float() * torch.nn.functional.silu(z.float())).to(y.dtype)
+        # norm_then_gate: grouped RMSNorm(y) * weight, then * silu(z)
+        v = y.float().reshape(y.shape[0], self.norm_groups, -1)
+        v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.cfg.rms_norm_eps)).reshape(y.shape[0], -1)
+        return (v * lw.gnorm.float() * torch.nn.functional.silu(z.float())).to(y.dtype)
 
     def pieces(self, b: StepBatch):
         """Per-step description of the ragged batch for the mixer kernels: (slots, cu, reset) as int32

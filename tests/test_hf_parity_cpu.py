@@ -412,3 +412,63 @@ def test_qwen3_next_hybrid_matches_transformers():
         for i, tok in enumerate(o.output):
             row = lg[n0 - 1 + i]
             assert row[tok].item() >= row.max().item() - 2e-3
+
+
+@pytest.mark.parametrize("mixer_norm", [False, True])
+def test_falcon_h1_hybrid_matches_transformers(mixer_norm):
+    """Falcon-H1 (Mamba2 mixer and rotary attention in parallel, gated MLP, muP multipliers folded into
+    the weights at load) on the hybrid executor: prompt logits and teacher-forced engine decoding."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.models.hybrid import HybridModel, load_falcon_h1_weights
+
+    torch.manual_seed(0)
+    try:
+        hc = AutoConfig.for_model(
+            "falcon_h1", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256, mamba_d_ssm=128,
+            mamba_n_heads=8, mamba_d_head=16, mamba_n_groups=2, mamba_d_state=16, mamba_d_conv=4, mamba_chunk_size=8,
+            mamba_rms_norm=mixer_norm, mamba_norm_before_gate=True, embedding_multiplier=2.0, lm_head_multiplier=0.5,
+            ssm_multipliers=[0.5, 1.5, 0.7, 1.2, 0.9], ssm_in_multiplier=1.3, ssm_out_multiplier=0.8,
+            attention_in_multiplier=1.1, key_multiplier=0.6, attention_out_multiplier=0.9, mlp_multipliers=[0.7, 1.4],
+            pad_token_id=0)
+        model = AutoModelForCausalLM.from_config(hc).float().eval()
+    except (KeyError, ValueError, ImportError) as e:
+        pytest.skip(f"transformers cannot build falcon_h1: {e}")
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.08)
+            elif "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tempfile.mkdtemp(prefix="parity_falcon_h1_")
+    model.save_pretrained(d, safe_serialization=True)
+    T = 24
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0]
+    cfg = ModelConfig.from_path(d)
+    assert cfg.extra["hybrid_pattern"] == "PGPG"
+    ours = HybridModel(cfg, load_falcon_h1_weights(d, cfg, dtype=torch.float32), max_seqs=4)
+    pool = KVPool(cfg, 8, 16, device="cpu", dtype=torch.float32, num_layers=ours.num_kv_layers)
+    b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
+                  slot_mapping=torch.arange(T, dtype=torch.int32), num_prefill_seqs=1,
+                  pf_block_tables=torch.arange(8, dtype=torch.int32)[None],
+                  pf_cu_q=torch.tensor([0, T], dtype=torch.int32),
+                  pf_context_lens=torch.tensor([T], dtype=torch.int32), pf_max_q_len=T, pf_cu_q_host=[0, T],
+                  logits_rows=torch.arange(T))
+    b.seq_ids, b.pf_starts = [0], [0]
+    got = ours.forward(b, pool.layers).float()
+    assert (got - want).abs().max().item() < 2e-3 * max(want.abs().max().item(), 1.0)
+    ours.release_seq(0)
+    eng = Engine(ours, cfg, EngineConfig(num_blocks=64, block_size=16, max_batch=4, max_model_len=256,
+                                         max_num_batched_tokens=16))
+    outs = eng.generate([ids.tolist(), ids[:7].tolist()], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
+    for o, n0 in zip(outs, (T, 7)):
+        with torch.no_grad():
+            lg = model(torch.cat([ids[:n0], torch.tensor(o.output)])[None]).logits[0]
+        for i, tok in enumerate(o.output):
+            row = lg[n0 - 1 + i]
+            assert row[tok].item() >= row.max().item() - 2e-3
