@@ -1,19 +1,26 @@
-"""Hybrid state-space / attention language models (Nemotron-H layout) on the serving engine.
+"""Hybrid state-space / attention language models on the serving engine.
 
-A model is a flat list of pre-norm residual blocks, each with ONE mixer chosen by a pattern string
-(``hybrid_override_pattern``, e.g. ``"M-M-M-M*-M-M-M-M-"``):
+A model is a flat list of pre-norm residual blocks; the family decides the list (``block_kinds``):
 
-* ``M``  Mamba2 mixer (``models/mamba2.py``: per-sequence conv / SSM state slots, ragged kernels),
-* ``*``  grouped-query attention over the paged KV pool, without positional encoding,
-* ``-``  MLP  ``down(relu(up(x))^2)``  (or a gated SwiGLU MLP when the checkpoint has ``gate_proj``).
+=====  ===============================================================================================
+``M``  Mamba2 mixer (``models/mamba2.py``)                       Nemotron-H, Granite-4 hybrid
+``m``  first-generation Mamba mixer (``models/mamba1.py``)       Jamba
+``L``  Gated DeltaNet mixer (``models/gdn.py``)                  Qwen3-Next
+``P``  Mamba2 mixer and attention side by side                   Falcon-H1
+``*``  grouped-query attention over the paged KV pool (NoPE or RoPE per family)
+``A``  the same with per-head (1 + w) q/k norms and a sigmoid output gate    Qwen3-Next
+``-``  plain MLP ``down(relu(up(x))^2)``                         Nemotron-H
+``G``  gated (SwiGLU) MLP
+``E``  mixture of experts (``models/moe.py``)                    Jamba, Qwen3-Next
+=====  ===============================================================================================
 
-Reference: src/models/nemotron_h.rs (block kinds and weight names ``backbone.layers.N.mixer.*``),
-src/models/granitemoehybrid.rs and src/models/falcon_h1.rs for the same idea with other layouts.
+Nemotron-H gives one block per layer through ``hybrid_override_pattern`` (``"M-M-M*-..."``); the other
+families have a mixer block and an MLP / MoE block per layer. Reference: src/models/nemotron_h.rs,
+granitemoehybrid.rs, jamba.rs, falcon_h1.rs, qwen3_next.rs.
 
-Only the attention blocks own KV-pool layers (``num_kv_layers``); the engine sizes its pool from
-that. The executor composes the two existing ones: a :class:`Mamba2Model` for the state slots and
-the mixer, a :class:`DecoderModel` for the attention path (RoPE switched off through
-``partial_rotary_factor = 0``). Single GPU.
+Only the attention blocks own KV-pool layers (``num_kv_layers``); the engine sizes its pool from that.
+The executor composes existing ones: a recurrent-mixer model (Mamba2 / Mamba / Gated DeltaNet) for the
+per-sequence state slots and its mixer, a :class:`DecoderModel` for the attention path. Single GPU.
 """
 from __future__ import annotations
 
