@@ -202,6 +202,34 @@ def create_app(state: ServerState) -> FastAPI:
         return dict(id_slot=slot_id, filename=name, n_restored=len(toks), n_read=len(raw),
                     timings=dict(restore_ms=(time.perf_counter() - t0) * 1e3))
 
+    @app.post("/v1/internal/kv/export")
+    async def kv_export(body: dict):
+        """Prefill role of a disaggregated deployment: prefill the prompt (text or token ids) and return
+        its KV blocks as one binary blob for ``/v1/internal/kv/import`` of a decode-role server."""
+        from fastapi.responses import Response
+
+        from ..engine.handoff import export_prefix
+        prompt = body.get("prompt", body.get("tokens"))
+        if prompt is None:
+            return _err(400, "prompt (text or token ids) is required")
+        ids = _prompt_ids(prompt)
+        try:
+            blob = state.worker.run_exclusive(lambda: export_prefix(state.worker.engine, ids))
+        except ValueError as e:
+            return _err(400, str(e))
+        return Response(content=blob, media_type="application/octet-stream",
+                        headers={"x-kv-tokens": str(len(ids))})
+
+    @app.post("/v1/internal/kv/import")
+    async def kv_import(request: Request):
+        from ..engine.handoff import import_prefix
+        blob = await request.body()
+        try:
+            n = state.worker.run_exclusive(lambda: import_prefix(state.worker.engine, blob))
+        except ValueError as e:
+            return _err(400, str(e))
+        return {"cached_tokens": n}
+
     @app.get("/metrics")
     async def metrics():
         from .metrics import render_metrics

@@ -50,3 +50,33 @@ def test_snapshot_restore_roundtrip():
     while eng.has_work():
         eng.step()
     assert s2.output == want and s2.num_cached == 48 and eng.stats["prefill_tokens"] < 2 * 50
+
+
+def test_kv_handoff_between_engines():
+    """Disaggregated roles: engine A prefills and exports a prompt's KV blocks, engine B imports the
+    blob and generates from the cache with the same result as a local run."""
+    from mlxcel_b200.engine.handoff import export_prefix, import_prefix, parse_blob
+
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, seed=2, dtype=torch.float32, std=0.05)
+
+    def engine():
+        return Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=2, max_num_batched_tokens=128, num_blocks=32,
+                                                              max_model_len=256, cuda_graphs=False))
+
+    prompt = list(range(3, 60))
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    a, b = engine(), engine()
+    want = a.generate([prompt], sp)[0].output
+    a.bm.reset_prefix_cache()
+    blob = export_prefix(a, prompt)
+    head, snap = parse_blob(blob)
+    assert len(snap.tokens) == 48 and head["geometry"]["layers"] == cfg.num_hidden_layers
+    assert import_prefix(b, blob) == 48
+    out = b.generate([prompt], sp)[0]
+    assert out.output == want and out.num_cached == 48
+    other = Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=2, max_num_batched_tokens=128, num_blocks=32,
+                                                           max_model_len=256, cuda_graphs=False, block_size=32))
+    import pytest
+    with pytest.raises(ValueError):
+        import_prefix(other, blob)

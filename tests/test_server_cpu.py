@@ -184,3 +184,30 @@ def test_slot_save_restore_erase(tmp_path):
         assert c.post(f"/slots/{slot}?action=restore", json=dict(filename="missing.bin")).status_code == 404
         assert c.post(f"/slots/{slot}?action=bogus").status_code == 400
     worker.shutdown()
+
+
+def test_kv_handoff_routes_between_two_servers():
+    """A prefill-role server exports a prompt's KV blocks, a decode-role server imports them and then
+    answers the same prompt from its cache with the same text."""
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, seed=0, dtype=torch.float32, std=0.05)
+    tk = ByteTokenizer(cfg.vocab_size)
+
+    def server():
+        eng = Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=4, max_num_batched_tokens=256, num_blocks=128,
+                                                             max_model_len=512, cuda_graphs=False))
+        worker = ModelWorker(eng, tk, "tiny")
+        return worker, TestClient(create_app(ServerState(worker, tk, "tiny")))
+
+    (wa, ca), (wb, cb) = server(), server()
+    prompt = "In a hole in the ground there lived a hobbit. Not a nasty, dirty, wet hole."
+    with ca, cb:
+        want = ca.post("/completion", json=dict(prompt=prompt, n_predict=5, temperature=0)).json()["content"]
+        r = ca.post("/v1/internal/kv/export", json=dict(prompt=prompt))
+        assert r.status_code == 200 and r.content[:5] == b"MXKV1"
+        assert cb.post("/v1/internal/kv/import", content=r.content).json()["cached_tokens"] >= 64
+        got = cb.post("/completion", json=dict(prompt=prompt, n_predict=5, temperature=0)).json()
+        assert got["content"] == want and got["timings"]["cache_n"] >= 64
+        assert cb.post("/v1/internal/kv/import", content=b"garbage").status_code == 400
+    wa.shutdown()
+    wb.shutdown()
