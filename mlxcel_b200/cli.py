@@ -159,7 +159,49 @@ def cmd_run(a):
 
 def _encoder_checkpoint(path: str) -> bool:
     cj = os.path.join(path, "config.json")
-    return os.path.exists(cj) and json.load(open(cj)).get("model_type") in ("bert",)
+    return os.path.exists(cj) and json.load(open(cj)).get("model_type") in ("bert", "modernbert")
+
+
+def cmd_embed(a):
+    """Offline counterpart of ``/v1/embeddings``: one vector per ``-p`` input, and the cosine matrix when
+    there are several (reference src/main.rs:251, ``mlxcel embed``)."""
+    import torch
+
+    texts = list(a.prompt or [])
+    if not texts:
+        raise SystemExit("embed: give at least one -p/--prompt")
+    if a.instruction:
+        texts = [f"Instruct: {a.instruction}\nQuery: {t}" for t in texts]
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    if _encoder_checkpoint(a.model):
+        from .models.encoder import load_encoder
+        from .tokenizer import load_tokenizer
+        enc, tok = load_encoder(a.model, device=dev), load_tokenizer(a.model)
+        vecs = [enc.embed(tok.encode(t, add_special_tokens=True) or [0], a.pooling or "mean", False) for t in texts]
+    else:
+        from types import SimpleNamespace
+
+        from .server.embeddings import embed_texts
+        llm = load_llm(a)
+        state = SimpleNamespace(worker=SimpleNamespace(engine=llm.engine), tokenizer=llm.tokenizer)
+        vecs = [torch.tensor(v) for v in embed_texts(state, texts, a.pooling or "last")[0]]
+    vecs = torch.stack([v.float().cpu() for v in vecs])
+    if a.dimensions:
+        vecs = vecs[:, : a.dimensions]
+    if a.embd_normalize != "none":
+        vecs = vecs / vecs.norm(dim=-1, keepdim=True).clamp_min(1e-12)
+    unit = vecs / vecs.norm(dim=-1, keepdim=True).clamp_min(1e-12)
+    sim = (unit @ unit.T).tolist() if len(texts) > 1 else None
+    if a.json:
+        print(json.dumps(dict(embeddings=vecs.tolist(), cosine=sim)))
+        return
+    for t, v in zip(texts, vecs.tolist()):
+        head = ", ".join(f"{x:+.4f}" for x in v[:8])
+        print(f"{t!r}: dim={len(v)} [{head}{', ...' if len(v) > 8 else ''}]")
+    if sim:
+        print("cosine similarity:")
+        for row in sim:
+            print("  " + " ".join(f"{x:6.3f}" for x in row))
 
 
 def cmd_serve(a):
@@ -170,11 +212,11 @@ def cmd_serve(a):
     if _encoder_checkpoint(a.model):            # encoder checkpoints get the embeddings-only server
         import torch
 
-        from .models.encoder import BertEncoder
+        from .models.encoder import load_encoder
         from .server.embeddings import create_embedding_app
         from .tokenizer import load_tokenizer
         dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
-        enc = BertEncoder.from_pretrained(a.model, device=dev)
+        enc = load_encoder(a.model, device=dev)
         app = create_embedding_app(enc, load_tokenizer(a.model), a.alias or os.path.basename(a.model.rstrip("/")),
                                    set(a.api_key or []))
         uvicorn.run(app, host=a.host, port=a.port, log_level="info" if a.verbose else "warning")
@@ -310,6 +352,15 @@ def main(argv=None):
     p.add_argument("--api-key", action="append")
     p.add_argument("-v", "--verbose", action="store_true")
     p.set_defaults(fn=cmd_router)
+    p = sub.add_parser("embed", help="embed texts and print the vectors")
+    _add_model_args(p)
+    p.add_argument("-p", "--prompt", action="append")
+    p.add_argument("--instruction", default=None)
+    p.add_argument("--pooling", choices=["mean", "cls", "last"], default=None)
+    p.add_argument("--embd-normalize", choices=["l2", "none"], default="l2")
+    p.add_argument("--dimensions", type=int, default=None)
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_embed)
     p = sub.add_parser("inspect", help="memory estimate")
     _add_model_args(p)
     p.set_defaults(fn=cmd_inspect)

@@ -101,3 +101,93 @@ class BertEncoder:
         h = self.hidden_states(ids).float()
         v = h[0] if pooling == "cls" else h.mean(0)
         return v / v.norm().clamp_min(1e-12) if normalize else v
+
+
+class ModernBertEncoder:
+    """ModernBERT: pre-norm blocks with bias-free LayerNorm, fused Wqkv, rotary embedding (one base for
+    the global layers, another for the local ones), bidirectional attention that is windowed
+    (``|i - j| <= local_attention // 2``) on all but every ``global_attn_every_n_layers``-th layer, and a
+    GeGLU MLP ``Wo(act(a) * b)`` with ``[a | b] = Wi(x)`` (reference src/embeddings/, src/models/modernbert.rs)."""
+
+    def __init__(self, cfg: dict, tensors: dict, dtype=torch.bfloat16, device="cpu"):
+        from ..ops.reference import rope_inv_freq
+
+        self.heads, self.hidden = int(cfg["num_attention_heads"]), int(cfg["hidden_size"])
+        self.eps = float(cfg.get("norm_eps", 1e-5))
+        self.act = {"gelu": "gelu", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "silu": "silu"}.get(
+            cfg.get("hidden_activation", "gelu"), "gelu")
+        self.max_len = int(cfg.get("max_position_embeddings", 8192))
+        self.device = torch.device(device)
+        n = int(cfg["num_hidden_layers"])
+        every = int(cfg.get("global_attn_every_n_layers", 3))
+        types = cfg.get("layer_types") or ["full_attention" if i % every == 0 else "sliding_attention" for i in range(n)]
+        self.local = [t != "full_attention" for t in types]
+        self.window = int(cfg.get("local_attention", 128)) // 2
+        rp = cfg.get("rope_parameters") or {}
+        g_theta = float((rp.get("full_attention") or {}).get("rope_theta", cfg.get("global_rope_theta", 160000.0)))
+        l_theta = float((rp.get("sliding_attention") or {}).get("rope_theta", cfg.get("local_rope_theta", 10000.0)))
+        D = self.hidden // self.heads
+        self.inv_global = rope_inv_freq(D, g_theta, None)[0].to(self.device)
+        self.inv_local = rope_inv_freq(D, l_theta, None)[0].to(self.device)
+        pre = "model." if any(k.startswith("model.") for k in tensors) else ""
+
+        def t(name):
+            return tensors[pre + name].to(dtype).to(self.device).contiguous()
+
+        def opt(name):
+            return t(name) if pre + name in tensors else None
+
+        self.word, self.emb_norm = t("embeddings.tok_embeddings.weight"), t("embeddings.norm.weight")
+        self.final_norm = t("final_norm.weight")
+        self.layers = [dict(attn_norm=opt(f"layers.{i}.attn_norm.weight"), wqkv=t(f"layers.{i}.attn.Wqkv.weight"),
+                            wo=t(f"layers.{i}.attn.Wo.weight"), mlp_norm=t(f"layers.{i}.mlp_norm.weight"),
+                            wi=t(f"layers.{i}.mlp.Wi.weight"), wo2=t(f"layers.{i}.mlp.Wo.weight")) for i in range(n)]
+
+    @staticmethod
+    def from_pretrained(path, dtype=torch.bfloat16, device="cpu") -> "ModernBertEncoder":
+        from ..loading.checkpoint import TensorSource
+
+        cfg = json.loads((Path(path) / "config.json").read_text())
+        src = TensorSource(path)
+        return ModernBertEncoder(cfg, {k: src.get(k) for k in src.keys()}, dtype, device)
+
+    @torch.inference_mode()
+    def hidden_states(self, ids: list[int]) -> torch.Tensor:
+        from ..ops.reference import apply_rope
+
+        ids = ids[: self.max_len]
+        T, H, nh = len(ids), self.hidden, self.heads
+        D = H // nh
+        tok = torch.tensor(ids, dtype=torch.long, device=self.device)
+        pos = torch.arange(T, device=self.device)
+        far = (pos[:, None] - pos[None, :]).abs() > self.window            # True = masked out on local layers
+        h = rops.layernorm(self.word[tok], self.emb_norm, None, self.eps)
+        for lw, local in zip(self.layers, self.local):
+            x = h if lw["attn_norm"] is None else rops.layernorm(h, lw["attn_norm"], None, self.eps)
+            qkv = ops.linear(x, lw["wqkv"]).view(T, 3, nh, D)
+            inv = self.inv_local if local else self.inv_global
+            q = apply_rope(qkv[:, 0], pos, inv, D, False).to(h.dtype)
+            k = apply_rope(qkv[:, 1], pos, inv, D, False).to(h.dtype)
+            q, k, v = (t.transpose(0, 1).unsqueeze(0) for t in (q, k, qkv[:, 2]))
+            mask = (~far)[None, None] if local else None
+            a = F.scaled_dot_product_attention(q, k, v, attn_mask=mask).squeeze(0).transpose(0, 1).reshape(T, H)
+            h = ops.linear(a.contiguous(), lw["wo"], residual=h)
+            u = ops.linear(rops.layernorm(h, lw["mlp_norm"], None, self.eps), lw["wi"])
+            half = u.shape[1] // 2
+            g = rops.activation(u[:, :half].contiguous(), self.act)
+            h = ops.linear((g.float() * u[:, half:].float()).to(h.dtype), lw["wo2"], residual=h)
+        return rops.layernorm(h, self.final_norm, None, self.eps)
+
+    def embed(self, ids: list[int], pooling: str = "mean", normalize: bool = True) -> torch.Tensor:
+        h = self.hidden_states(ids).float()
+        v = h[0] if pooling == "cls" else h.mean(0)
+        return v / v.norm().clamp_min(1e-12) if normalize else v
+
+
+def load_encoder(path, dtype=torch.bfloat16, device="cpu"):
+    """The encoder class for a checkpoint's ``model_type`` (bert, modernbert)."""
+    mt = json.loads((Path(path) / "config.json").read_text()).get("model_type")
+    cls = {"bert": BertEncoder, "modernbert": ModernBertEncoder}.get(mt)
+    if cls is None:
+        raise ValueError(f"unsupported encoder model_type {mt!r}")
+    return cls.from_pretrained(path, dtype, device)

@@ -52,3 +52,45 @@ def test_embedding_server_routes():
         one = c.post("/embedding", json=dict(content="hello"), headers=h).json()
         assert one[0]["embedding"] == pytest.approx(r["data"][0]["embedding"], abs=1e-6)
         assert c.get("/v1/models", headers=h).json()["data"][0]["id"] == "tiny-bert"
+
+
+def test_modernbert_hidden_states_match_transformers():
+    from transformers import ModernBertConfig, ModernBertModel
+
+    from mlxcel_b200.models.encoder import ModernBertEncoder, load_encoder
+
+    torch.manual_seed(0)
+    m = ModernBertModel(ModernBertConfig(hidden_size=64, intermediate_size=96, num_hidden_layers=4, num_attention_heads=4,
+                                         vocab_size=300, max_position_embeddings=128, local_attention=8,
+                                         global_attn_every_n_layers=3, pad_token_id=0)).float().eval()
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.08)
+            else:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tempfile.mkdtemp()
+    m.save_pretrained(d)
+    ids = torch.randint(1, 300, (29,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = m(ids[None]).last_hidden_state[0]
+    enc = load_encoder(d, dtype=torch.float32)
+    assert isinstance(enc, ModernBertEncoder) and any(enc.local) and not all(enc.local)
+    got = enc.hidden_states(ids.tolist())
+    assert (got - want).abs().max().item() < 2e-5 * max(1.0, want.abs().max().item())
+    e = enc.embed(ids.tolist())
+    assert abs(e.norm().item() - 1.0) < 1e-5
+
+
+def test_embed_cli_prints_vectors_and_cosine(capsys):
+    import json
+
+    from mlxcel_b200 import cli
+
+    _, d = _tiny_bert()
+    cli.main(["embed", "-m", d, "--device", "cpu", "-p", "hello there", "-p", "general kenobi", "--json",
+              "--dimensions", "32"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert len(out["embeddings"]) == 2 and len(out["embeddings"][0]) == 32
+    assert abs(sum(x * x for x in out["embeddings"][0]) - 1.0) < 1e-4
+    assert abs(out["cosine"][0][0] - 1.0) < 1e-5 and abs(out["cosine"][0][1] - out["cosine"][1][0]) < 1e-6
