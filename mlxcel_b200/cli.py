@@ -204,6 +204,85 @@ def cmd_embed(a):
             print("  " + " ".join(f"{x:6.3f}" for x in row))
 
 
+def _load_encoder_and_tokenizer(a):
+    import torch
+
+    from .models.encoder import load_encoder
+    from .tokenizer import load_tokenizer
+    if not _encoder_checkpoint(a.model):
+        raise SystemExit(f"{a.model}: not an encoder checkpoint (bert, modernbert)")
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    return load_encoder(a.model, device=dev), load_tokenizer(a.model)
+
+
+def cmd_rerank(a):
+    """Offline counterpart of ``/v1/rerank`` (reference src/main.rs:281, ``mlxcel rerank``)."""
+    from .server.embeddings import rerank_scores
+    enc, tok = _load_encoder_and_tokenizer(a)
+    scores = rerank_scores(enc, tok, a.query, a.document)
+    order = sorted(range(len(scores)), key=lambda i: -scores[i])
+    if a.json:
+        print(json.dumps(dict(results=[dict(index=i, relevance_score=scores[i]) for i in order])))
+        return
+    for rank, i in enumerate(order, 1):
+        print(f"{rank:2d}. [{i}] {scores[i]:.4f}  {a.document[i][:80]}")
+
+
+def cmd_tag(a):
+    """Entity spans and a redacted copy from a token-classification checkpoint (reference
+    src/main.rs:298, ``mlxcel tag``)."""
+    from .server.embeddings import tag_text
+    enc, tok = _load_encoder_and_tokenizer(a)
+    keep = {k.strip() for k in (a.keep or "").split(",") if k.strip()}
+    res = tag_text(enc, tok, a.text, keep, a.replacement)
+    if a.json:
+        print(json.dumps(res))
+        return
+    for sp in res["spans"]:
+        print(f"{sp['entity']:<16} {sp['score']:.3f}  {sp['text']!r}")
+    print(res["redacted"])
+
+
+def cmd_list(a):
+    """Models of the local store (reference src/main.rs:161, ``mlxcel list``)."""
+    from . import store
+    models = store.list_models(a.models_dir, a.sort)
+    if a.json:
+        print(json.dumps(store.as_json(models)))
+    elif a.quiet:
+        for m in models:
+            print(m.repo_id)
+    elif not models:
+        print(f"no models under {store.store_root(a.models_dir)}")
+    else:
+        print(store.format_table(models, a.verbose))
+
+
+def cmd_rm(a):
+    """Remove one model of the local store (reference src/main.rs:328, ``mlxcel rm``)."""
+    from . import store
+    target = store.model_path(a.repo_id, a.models_dir)
+    if not a.yes:
+        if input(f"remove {target}? [y/N] ").strip().lower() not in ("y", "yes"):
+            print("kept")
+            return
+    try:
+        freed = store.remove_model(a.repo_id, a.models_dir)
+    except (FileNotFoundError, ValueError) as ex:
+        raise SystemExit(str(ex))
+    print(f"removed {a.repo_id} ({store.human_size(freed)} freed)")
+
+
+def cmd_download(a):
+    """Bring a repository into the local store, reusing a HuggingFace cache copy (reference
+    src/main.rs:199, ``mlxcel download``)."""
+    from . import store
+    try:
+        print(store.download_model(a.repo_id, a.models_dir, a.local_dir))
+    except (RuntimeError, ValueError) as ex:
+        raise SystemExit(str(ex))
+
+
 def cmd_serve(a):
     import uvicorn
 
@@ -361,6 +440,38 @@ def main(argv=None):
     p.add_argument("--dimensions", type=int, default=None)
     p.add_argument("--json", action="store_true")
     p.set_defaults(fn=cmd_embed)
+    p = sub.add_parser("rerank", help="score documents against a query")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("--device", default=None)
+    p.add_argument("-q", "--query", required=True)
+    p.add_argument("-d", "--document", action="append", required=True)
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_rerank)
+    p = sub.add_parser("tag", help="tag and redact entities with a token-classification checkpoint")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("--device", default=None)
+    p.add_argument("--keep", default=None, help="comma-separated entity names left in the redacted copy")
+    p.add_argument("--replacement", default=None)
+    p.add_argument("--json", action="store_true")
+    p.add_argument("text")
+    p.set_defaults(fn=cmd_tag)
+    p = sub.add_parser("list", aliases=["ls"], help="models in the local store")
+    p.add_argument("--models-dir", default=None)
+    p.add_argument("--json", action="store_true")
+    p.add_argument("-q", "--quiet", action="store_true")
+    p.add_argument("-v", "--verbose", action="store_true")
+    p.add_argument("--sort", choices=["name", "size", "modified"], default="name")
+    p.set_defaults(fn=cmd_list)
+    p = sub.add_parser("rm", help="remove a model from the local store")
+    p.add_argument("repo_id")
+    p.add_argument("--models-dir", default=None)
+    p.add_argument("-y", "--yes", action="store_true")
+    p.set_defaults(fn=cmd_rm)
+    p = sub.add_parser("download", help="bring a repository into the local store (HuggingFace cache reuse; no network fetch)")
+    p.add_argument("repo_id")
+    p.add_argument("--models-dir", default=None)
+    p.add_argument("--local-dir", default=None)
+    p.set_defaults(fn=cmd_download)
     p = sub.add_parser("inspect", help="memory estimate")
     _add_model_args(p)
     p.set_defaults(fn=cmd_inspect)
@@ -379,6 +490,9 @@ def main(argv=None):
     p.add_argument("--group-size", type=int, default=64)
     p.set_defaults(fn=cmd_random_init)
     a = ap.parse_args(argv)
+    if isinstance(getattr(a, "model", None), str):          # owner/name ids resolve through the local store
+        from .store import resolve_model
+        a.model = resolve_model(a.model)
     a.fn(a)
 
 

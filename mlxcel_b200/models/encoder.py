@@ -54,7 +54,14 @@ class BertEncoder:
 
         e = "embeddings."
         self.word, self.pos = t(e + "word_embeddings.weight"), t(e + "position_embeddings.weight")
-        self.type0 = t(e + "token_type_embeddings.weight")[0] if pre + e + "token_type_embeddings.weight" in tensors else None
+        self.type_emb = t(e + "token_type_embeddings.weight") if pre + e + "token_type_embeddings.weight" in tensors else None
+        self.type0 = None if self.type_emb is None else self.type_emb[0]
+        # optional heads: tanh pooler over [CLS] and a linear classifier (sequence- or token-level)
+        head = lambda n: tensors[n].to(dtype).to(self.device).contiguous() if n in tensors else None  # noqa: E731
+        self.pooler = (head(pre + "pooler.dense.weight"), head(pre + "pooler.dense.bias"))
+        self.classifier = (head("classifier.weight"), head("classifier.bias"))
+        self.token_head = any("TokenClassification" in a for a in cfg.get("architectures") or [])
+        self.id2label = {int(k): v for k, v in (cfg.get("id2label") or {}).items()}
         self.emb_ln = (t(e + "LayerNorm.weight"), t(e + "LayerNorm.bias"))
         self.layers = []
         for i in range(int(cfg["num_hidden_layers"])):
@@ -78,13 +85,16 @@ class BertEncoder:
         return BertEncoder(cfg, {k: src.get(k) for k in src.keys()}, dtype, device)
 
     @torch.inference_mode()
-    def hidden_states(self, ids: list[int]) -> torch.Tensor:
-        """Final hidden states [T, H] of one text (no padding: one text per call)."""
+    def hidden_states(self, ids: list[int], type_ids: list[int] | None = None) -> torch.Tensor:
+        """Final hidden states [T, H] of one text (no padding: one text per call). ``type_ids`` marks the
+        segments of a sentence pair (0 / 1); all zeros when absent."""
         ids = ids[: self.max_len]
         T, H, nh = len(ids), self.hidden, self.heads
         tok = torch.tensor(ids, dtype=torch.long, device=self.device)
         h = self.word[tok].float() + self.pos[:T].float()
-        if self.type0 is not None:
+        if self.type_emb is not None and type_ids is not None:
+            h = h + self.type_emb[torch.tensor(type_ids[:T], dtype=torch.long, device=self.device)].float()
+        elif self.type0 is not None:
             h = h + self.type0.float()
         h = rops.layernorm(h.to(self.word.dtype), *self.emb_ln, self.eps)
         for lw in self.layers:
@@ -101,6 +111,38 @@ class BertEncoder:
         h = self.hidden_states(ids).float()
         v = h[0] if pooling == "cls" else h.mean(0)
         return v / v.norm().clamp_min(1e-12) if normalize else v
+
+    @torch.inference_mode()
+    def sequence_logits(self, ids: list[int], type_ids: list[int] | None = None) -> torch.Tensor:
+        """Cross-encoder head: ``classifier(tanh(pooler([CLS])))`` -> [num_labels] fp32 (a reranker's
+        relevance score is logit 0 of a one-label head)."""
+        if self.classifier[0] is None or self.token_head:
+            raise ValueError("checkpoint has no sequence-classification head")
+        v = self.hidden_states(ids, type_ids)[:1]
+        if self.pooler[0] is not None:
+            v = torch.tanh(ops.linear(v, self.pooler[0], bias=self.pooler[1]).float()).to(v.dtype)
+        return ops.linear(v, self.classifier[0], bias=self.classifier[1])[0].float()
+
+    @torch.inference_mode()
+    def token_logits(self, ids: list[int]) -> torch.Tensor:
+        """Token-classification head: one row of label logits per token, [T, num_labels] fp32."""
+        if self.classifier[0] is None or not self.token_head:
+            raise ValueError("checkpoint has no token-classification head")
+        return ops.linear(self.hidden_states(ids), self.classifier[0], bias=self.classifier[1]).float()
+
+
+def bio_spans(labels: list[str]) -> list[tuple[int, int, str]]:
+    """Merge per-token BIO / BIOES labels into ``(first token, one past last token, entity)`` spans:
+    ``B-X`` / ``S-X`` opens a span, ``I-X`` / ``E-X`` of the same entity extends it, anything else closes it."""
+    out, start, ent = [], None, None
+    for i, lab in enumerate(list(labels) + ["O"]):
+        tag, _, name = lab.partition("-")
+        if start is not None and not (tag in ("I", "E") and name == ent):
+            out.append((start, i, ent))
+            start = ent = None
+        if start is None and lab != "O" and name:
+            start, ent = i, name                    # a stray I-X also opens a span, as taggers commonly emit
+    return out
 
 
 class ModernBertEncoder:

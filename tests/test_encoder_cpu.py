@@ -94,3 +94,75 @@ def test_embed_cli_prints_vectors_and_cosine(capsys):
     assert len(out["embeddings"]) == 2 and len(out["embeddings"][0]) == 32
     assert abs(sum(x * x for x in out["embeddings"][0]) - 1.0) < 1e-4
     assert abs(out["cosine"][0][0] - 1.0) < 1e-5 and abs(out["cosine"][0][1] - out["cosine"][1][0]) < 1e-6
+
+
+def _randomise(m):
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.08)
+            else:
+                p.add_(torch.randn_like(p) * 0.1)
+    return m.float().eval()
+
+
+_BERT = dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128, vocab_size=300,
+             max_position_embeddings=64)
+
+
+def test_cross_encoder_head_matches_transformers_and_reranks(capsys):
+    import json
+
+    from transformers import BertConfig, BertForSequenceClassification
+
+    from mlxcel_b200 import cli
+    from mlxcel_b200.models.encoder import load_encoder
+    from mlxcel_b200.server.embeddings import pair_ids, rerank_scores
+
+    torch.manual_seed(0)
+    m = _randomise(BertForSequenceClassification(BertConfig(num_labels=1, **_BERT)))
+    d = tempfile.mkdtemp()
+    m.save_pretrained(d)
+    ids = torch.randint(1, 300, (21,), generator=torch.Generator().manual_seed(2))
+    tt = torch.tensor([0] * 9 + [1] * 12)
+    with torch.no_grad():
+        want = m(ids[None], token_type_ids=tt[None]).logits[0]
+    enc = load_encoder(d, dtype=torch.float32)
+    assert (enc.sequence_logits(ids.tolist(), tt.tolist()) - want).abs().max().item() < 1e-5
+    tok = ByteTokenizer()
+    pi, pt = pair_ids(tok, "query", "a document", 64)
+    assert len(pi) == len(pt) and pt[0] == 0 and pt[-1] == 1
+    scores = rerank_scores(enc, tok, "query", ["doc one", "another"])
+    assert len(scores) == 2 and all(0.0 < s < 1.0 for s in scores)
+    cli.main(["rerank", "-m", d, "--device", "cpu", "-q", "query", "-d", "doc one", "-d", "another", "--json"])
+    res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["results"]
+    assert [r["index"] for r in res] == sorted(range(2), key=lambda i: -scores[i])
+    app = create_embedding_app(enc, tok, "ce")
+    r = TestClient(app).post("/v1/rerank", json=dict(query="query", documents=["doc one", "another"], top_n=1))
+    assert r.status_code == 200 and len(r.json()["results"]) == 1
+
+
+def test_token_classification_head_and_tagging():
+    from transformers import BertConfig, BertForTokenClassification
+
+    from mlxcel_b200.models.encoder import bio_spans, load_encoder
+    from mlxcel_b200.server.embeddings import tag_text
+
+    labels = {0: "O", 1: "B-PER", 2: "I-PER", 3: "B-LOC", 4: "I-LOC"}
+    torch.manual_seed(0)
+    m = _randomise(BertForTokenClassification(BertConfig(num_labels=5, id2label=labels,
+                                                         label2id={v: k for k, v in labels.items()}, **_BERT)))
+    d = tempfile.mkdtemp()
+    m.save_pretrained(d)
+    ids = torch.randint(1, 300, (17,), generator=torch.Generator().manual_seed(3))
+    with torch.no_grad():
+        want = m(ids[None]).logits[0]
+    enc = load_encoder(d, dtype=torch.float32)
+    assert enc.token_head and (enc.token_logits(ids.tolist()) - want).abs().max().item() < 1e-5
+    assert bio_spans(["O", "B-PER", "I-PER", "O", "I-LOC", "B-LOC", "B-LOC", "I-LOC"]) == \
+        [(1, 3, "PER"), (4, 5, "LOC"), (5, 6, "LOC"), (6, 8, "LOC")]
+    assert bio_spans(["S-X", "B-Y", "E-Y"]) == [(0, 1, "X"), (1, 3, "Y")]
+    res = tag_text(enc, ByteTokenizer(), "Sarah lives in Paris", keep=None, replacement="#")
+    assert isinstance(res["redacted"], str) and all(s["end_token"] > s["start_token"] for s in res["spans"])
+    with pytest.raises(ValueError):
+        enc.sequence_logits(ids.tolist())
