@@ -474,13 +474,15 @@ def _olmo1(c: ModelConfig, raw: dict) -> None:
 
 def _granitemoehybrid(c: ModelConfig, raw: dict) -> None:
     """Granite 4 hybrid: every layer is a Mamba2 or an attention mixer followed by a gated shared
-    MLP, with Granite's embedding / residual / attention / logit multipliers; attention carries RoPE
+    MLP (plus top-k routed experts when ``num_local_experts > 0``), with Granite's embedding / residual / attention / logit multipliers; attention carries RoPE
     only when ``position_embedding_type == "rope"`` (reference src/models/granitemoehybrid.rs).
     Runs on the hybrid executor as the block pattern ``MG`` / ``*G`` per layer."""
     _granite(c, raw)
-    if int(raw.get("num_local_experts", 0) or 0) > 0:
-        raise ValueError("granitemoehybrid with routed experts is not supported (dense shared MLP only)")
-    c.num_experts = 0
+    c.num_experts = int(raw.get("num_local_experts", 0) or 0)
+    if c.num_experts:
+        c.moe_route_mode = "topk_softmax"
+        c.moe_intermediate_size = c.intermediate_size
+        c.num_experts_per_tok = int(raw.get("num_experts_per_tok", c.num_experts_per_tok or 2))
     P = int(raw.get("mamba_d_head", 64))
     heads = int(raw.get("mamba_n_heads", raw.get("mamba_expand", 2) * c.hidden_size // P))
     lim = raw.get("time_step_limit") or (0.0, float("inf"))
@@ -488,7 +490,7 @@ def _granitemoehybrid(c: ModelConfig, raw: dict) -> None:
                             d_state=int(raw.get("mamba_d_state", 128)), d_conv=int(raw.get("mamba_d_conv", 4)),
                             time_step_limit=(_num(lim[0]), _num(lim[1])), norm_groups=1)
     types = raw.get("layer_types") or ["mamba"] * c.num_hidden_layers
-    c.extra["hybrid_pattern"] = "".join(("M" if t == "mamba" else "*") + "G" for t in types)
+    c.extra["hybrid_pattern"] = "".join(("M" if t == "mamba" else "*") + ("E" if c.num_experts else "G") for t in types)
     c.extra["hybrid_layout"] = "granite"
     c.extra["mlp_size"] = int(raw.get("shared_intermediate_size", c.intermediate_size))
     c.layer_types = None
@@ -830,7 +832,9 @@ def _mamba2(c: ModelConfig, raw: dict) -> None:
 def _nemotron_h(c: ModelConfig, raw: dict) -> None:
     """Hybrid Mamba2 / attention / MLP stack chosen per layer by ``hybrid_override_pattern``
     (reference src/models/nemotron_h.rs). Attention has no positional encoding; the Mamba2 gated
-    norm is applied per B/C group; the MLP is ``down(relu(up(x))^2)``."""
+    norm is applied per B/C group; the MLP is ``down(relu(up(x))^2)``; ``E`` blocks are a mixture of such
+    plain experts (sigmoid scores, selection bias, group-limited top-k, scaled weights) plus one shared
+    expert, optionally between two latent projections."""
     hs = c.hidden_size
     P = int(raw.get("mamba_head_dim", 64))
     heads = int(raw.get("mamba_num_heads", raw.get("expand", 2) * hs // P))
@@ -849,6 +853,13 @@ def _nemotron_h(c: ModelConfig, raw: dict) -> None:
         raise ValueError("nemotron_h config needs hybrid_override_pattern or layers_block_type")
     c.extra["hybrid_pattern"] = str(pat)
     c.num_hidden_layers = len(pat)
+    if "E" in pat:                               # MoE blocks: DeepSeek-V3 style routing over plain relu^2 experts
+        c.num_experts = int(raw.get("n_routed_experts", 0) or 0)
+        c.num_experts_per_tok = int(raw.get("num_experts_per_tok", 2))
+        c.moe_intermediate_size = int(raw.get("moe_intermediate_size", c.intermediate_size))
+        c.norm_topk_prob = bool(raw.get("norm_topk_prob", True))
+        c.extra["moe_routing"] = dict(n_group=int(raw.get("n_group", 1) or 1), topk_group=int(raw.get("topk_group", 1) or 1),
+                                      scale=float(raw.get("routed_scaling_factor", 1.0)))
     c.partial_rotary_factor = 0.0
     c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", False))
     c.hidden_act = "relu2"

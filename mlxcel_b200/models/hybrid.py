@@ -47,6 +47,8 @@ class HybridBlock:
     down: torch.Tensor | None = None            # [H, I]
     gated: bool = False
     out_gate: torch.Tensor | None = None        # gated attention (Qwen3-Next): [Hq * D, H] sigmoid gate projection
+    latent_in: torch.Tensor | None = None       # Nemotron-H MoE: optional projections around the routed experts
+    latent_out: torch.Tensor | None = None      #   ([latent, H] and [H, latent]); up / down hold the shared expert
 
 
 @dataclass
@@ -141,6 +143,25 @@ def load_hybrid_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cp
                               bo=None if bo is None else bo.to(device))
             attn_layers.append(lw)
             blocks.append(HybridBlock(kind, norm, attn=lw))
+        elif kind == "moe":
+            # plain (non-gated) experts stored stacked [E, I, in] / [E, in, I], fp32 router with a
+            # selection bias, one always-on shared expert, optional latent projections
+            E = cfg.num_experts
+            if src.has(m + "experts.up_proj"):
+                ups, downs = src.get(m + "experts.up_proj"), src.get(m + "experts.down_proj")
+            else:
+                ups = torch.stack([g.mat(f"{m}experts.{e}.up_proj") for e in range(E)])
+                downs = torch.stack([g.mat(f"{m}experts.{e}.down_proj") for e in range(E)])
+            bias = g.vec(m + "gate.e_score_correction_bias")
+            moe = LayerWeights(ln1=norm, ln2=norm, wqkv=None, wo=None, router_w=need(g.mat(m + "gate"), m + "gate"),
+                               router_b=None if bias is None else bias.float().to(device),
+                               experts_gate_up=ups.to(dtype).to(device).contiguous(),
+                               experts_down=downs.to(dtype).to(device).contiguous())
+            opt = lambda n: None if g.mat(n) is None else g.mat(n).to(device)  # noqa: E731
+            blocks.append(HybridBlock("moe_plain", norm, moe=moe,
+                                      up=need(g.mat(m + "shared_experts.up_proj"), m + "shared_experts.up_proj"),
+                                      down=need(g.mat(m + "shared_experts.down_proj"), m + "shared_experts.down_proj"),
+                                      latent_in=opt(m + "fc1_latent_proj"), latent_out=opt(m + "fc2_latent_proj")))
         else:
             up = need(g.mat(m + "up_proj"), m + "up_proj")
             gate = g.mat(m + "gate_proj")
@@ -157,8 +178,9 @@ def load_hybrid_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cp
 
 def load_granite_hybrid_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
     """Granite 4 hybrid checkpoint: ``model.layers.N.{input_layernorm, mamba.* | self_attn.*,
-    post_attention_layernorm, shared_mlp.input_linear / output_linear}``; each layer becomes a mixer
-    block and a gated-MLP block."""
+    post_attention_layernorm, shared_mlp.input_linear / output_linear [, block_sparse_moe.{router.layer,
+    input_linear, output_linear}]}``; each layer becomes a mixer block and a gated-MLP block, or a MoE
+    block (routed experts plus the shared MLP) when the checkpoint has routed experts."""
     from ..loading.checkpoint import TensorSource, _Getter
 
     src = TensorSource(path)
@@ -195,9 +217,19 @@ def load_granite_hybrid_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, de
             attn_layers.append(lw)
             blocks.append(HybridBlock("attention", norm, attn=lw))
         s = p + "shared_mlp."
-        blocks.append(HybridBlock("mlp", need(g.vec(p + "post_attention_layernorm.weight"), p + "post_attention_layernorm"),
-                                  up=need(g.mat(s + "input_linear"), s + "input_linear"),
-                                  down=need(g.mat(s + "output_linear"), s + "output_linear"), gated=True))
+        fn = need(g.vec(p + "post_attention_layernorm.weight"), p + "post_attention_layernorm")
+        up, down = need(g.mat(s + "input_linear"), s + "input_linear"), need(g.mat(s + "output_linear"), s + "output_linear")
+        e = p + "block_sparse_moe."
+        if cfg.num_experts and src.has(e + "input_linear.weight"):
+            # routed experts stored fused ([E, 2I, H] gate rows first, [E, H, I]) beside the shared MLP
+            moe = LayerWeights(ln1=fn, ln2=fn, wqkv=None, wo=None,
+                               router_w=need(g.mat(e + "router.layer"), e + "router.layer"),
+                               experts_gate_up=src.get(e + "input_linear.weight").to(dtype).to(device).contiguous(),
+                               experts_down=src.get(e + "output_linear.weight").to(dtype).to(device).contiguous(),
+                               shared_gate_up=up, shared_down=down)
+            blocks.append(HybridBlock("moe", fn, moe=moe))
+        else:
+            blocks.append(HybridBlock("mlp", fn, up=up, down=down, gated=True))
     embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")
     head = g.mat("lm_head") if src.has("lm_head.weight") and not cfg.tie_word_embeddings else None
     return HybridWeights(embed=embed, blocks=blocks, final_norm=need(g.vec("model.norm.weight"), "model.norm.weight"),
@@ -506,7 +538,24 @@ class HybridModel:
                 ai += 1
             elif blk.kind == "moe":
                 from .moe import moe_forward
-                h = moe_forward(cfg, blk.moe, x, h, self.comm)
+                if rm == 1.0:
+                    h = moe_forward(cfg, blk.moe, x, h, self.comm)
+                else:                            # Granite: (experts + shared MLP) scaled into the stream
+                    y = moe_forward(cfg, blk.moe, x, torch.zeros_like(h), self.comm)
+                    h = (h.float() + y.float() * rm).to(h.dtype)
+            elif blk.kind == "moe_plain":        # Nemotron-H: plain relu^2 experts + shared expert
+                from ..ops import moe as moe_ops
+                r, lw = cfg.extra["moe_routing"], blk.moe
+                ids, wts = moe_ops.route_sigmoid_grouped(x.float() @ lw.router_w.float().t(), cfg.num_experts_per_tok,
+                                                         lw.router_b, r["n_group"], r["topk_group"], cfg.norm_topk_prob,
+                                                         r["scale"])
+                xin = x if blk.latent_in is None else ops.linear(x, blk.latent_in)
+                y = moe_ops.moe_experts(xin, ids, wts.to(torch.float32), lw.experts_gate_up, lw.experts_down,
+                                        lw.experts_gate_up.shape[1], "relu2", gated=False)
+                if blk.latent_out is not None:
+                    y = ops.linear(y, blk.latent_out)
+                sh = ops.linear(rops.relu2(ops.linear(x, blk.up)), blk.down)
+                h = (h.float() + y.float() + sh.float()).to(h.dtype)
             elif blk.kind == "attention":
                 a = self.attn._attention(ai, blk.attn, x, b, kv_layers[ai])
                 if blk.out_gate is not None:     # Qwen3-Next: sigmoid gate computed from the block input

@@ -28,13 +28,14 @@ def route_ref(logits: torch.Tensor, k: int, mode: str, norm_topk: bool):
 
 
 def moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up=None, b_down=None,
-            e_begin=0, alpha=1.702, limit=7.0, dequant=None):
+            e_begin=0, alpha=1.702, limit=7.0, dequant=None, gated=True):
     """Dense statement: for every (token, slot) routed to a local expert, run that expert's
-    gated MLP and accumulate the weighted result in fp32. Returns fp32 [T, H]."""
+    gated MLP (plain ``down(act(up x))`` when ``gated`` is false; ``w_gate_up`` then holds the up rows
+    only) and accumulate the weighted result in fp32. Returns fp32 [T, H]."""
     T, H = x.shape
     El = w_gate_up.shape[0]
     out = torch.zeros(T, w_down.shape[1], dtype=torch.float32, device=x.device)
-    epi = _ACT_TO_EPI[act]
+    epi = _ACT_TO_EPI[act] if gated else None
     for el in range(El):
         e = e_begin + el
         tok, slot = torch.nonzero(ids == e, as_tuple=True)
@@ -44,7 +45,11 @@ def moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up=None, b_down=N
         gu = xe @ w_gate_up[el].float().t()
         if b_gate_up is not None:
             gu = gu + b_gate_up[el].float()
-        a = ref.glu_act(epi, gu[:, :inter], gu[:, inter:2 * inter], alpha, limit).to(x.dtype).float()
+        if gated:
+            a = ref.glu_act(epi, gu[:, :inter], gu[:, inter:2 * inter], alpha, limit).to(x.dtype).float()
+        else:
+            from . import recurrent as rops
+            a = rops.activation(gu.to(x.dtype), act).float()
         y = a @ w_down[el].float().t()
         if b_down is not None:
             y = y + b_down[el].float()
@@ -153,8 +158,10 @@ def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_o
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up, w_down, inter: int,
                 act: str, b_gate_up=None, b_down=None, e_begin: int = 0, residual=None,
-                alpha: float = 1.702, limit: float = 7.0, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Weighted sum over the LOCAL experts [e_begin, e_begin + E_local) of their gated MLPs,
+                alpha: float = 1.702, limit: float = 7.0, out: torch.Tensor | None = None,
+                gated: bool = True) -> torch.Tensor:
+    """Weighted sum over the LOCAL experts [e_begin, e_begin + E_local) of their gated MLPs (plain
+    ``down(act(up x))`` experts when ``gated`` is false: grouped GEMM, activation kernel, grouped GEMM),
     plus ``residual`` when given. Returns bf16 [T, H] (written into ``out`` when given; rows whose
     experts are all elsewhere come out as the residual, or zero)."""
     T, H = x.shape
@@ -167,7 +174,7 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up
             w_gate_up = quant.dequantize_ref(w_gate_up)
         if isinstance(w_down, QuantizedTensor):
             w_down = quant.dequantize_ref(w_down)
-        o = moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up, b_down, e_begin, alpha, limit)
+        o = moe_ref(x, ids, wts, w_gate_up, w_down, inter, act, b_gate_up, b_down, e_begin, alpha, limit, gated=gated)
         if residual is not None:
             o = o + residual.float()
         if out is not None:
@@ -190,7 +197,11 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up
                                   pairs, H, st)
     _lib.check(rc, "mx_moe_gather_rows_n")
     _lib.count_launch(2)
-    a = grouped_linear(xs, w_gate_up, offsets, inter, b_gate_up, act, alpha, limit)
+    if gated:
+        a = grouped_linear(xs, w_gate_up, offsets, inter, b_gate_up, act, alpha, limit)
+    else:
+        from . import recurrent as rops
+        a = rops.activation(grouped_linear(xs, w_gate_up, offsets, inter, b_gate_up, None), act)
     y = grouped_linear(a, w_down, offsets, w_down.shape[1], b_down, None)
     if out is None:
         out = torch.empty(T, w_down.shape[1], dtype=x.dtype, device=dev)

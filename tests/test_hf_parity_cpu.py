@@ -118,9 +118,11 @@ def test_logits_match_transformers(name):
     assert err < 2e-3 * max(want.abs().max().item(), 1.0), f"{name}: max abs error {err:.3e}"
 
 
-def test_nemotron_h_hybrid_matches_transformers():
-    """Hybrid Mamba2 / attention stack against transformers' NemotronH (mamba and attention blocks;
-    its MoE blocks are not covered). transformers' pure-PyTorch mixer path is itself only accurate to
+@pytest.mark.parametrize("pattern,latent,tol", [("M*MM", None, 4e-3), ("ME*E", None, 4e-3), ("*E*E", 32, 2e-5)])
+def test_nemotron_h_hybrid_matches_transformers(pattern, latent, tol):
+    """Hybrid Mamba2 / attention / MoE stack against transformers' NemotronH (MoE blocks: plain relu^2
+    experts, sigmoid group-limited routing with a selection bias, a shared expert, optional latent
+    projections; without Mamba blocks the match is to rounding). transformers' pure-PyTorch mixer path is itself only accurate to
     ~1e-4 relative on the scan output (a float64 statement of the recurrence agrees with this
     package to 3e-8 and with transformers to 3e-5), hence the looser bound."""
     from transformers import AutoConfig, AutoModelForCausalLM
@@ -130,9 +132,12 @@ def test_nemotron_h_hybrid_matches_transformers():
     torch.manual_seed(0)
     try:
         hc = AutoConfig.for_model("nemotron_h", hidden_size=64, intermediate_size=128, num_hidden_layers=4,
-                                  hybrid_override_pattern="M*MM", num_attention_heads=4, num_key_value_heads=2,
+                                  hybrid_override_pattern=pattern, num_attention_heads=4, num_key_value_heads=2,
                                   head_dim=16, vocab_size=300, max_position_embeddings=256, mamba_num_heads=8,
-                                  mamba_head_dim=16, ssm_state_size=16, n_groups=2, conv_kernel=4, chunk_size=8)
+                                  mamba_head_dim=16, ssm_state_size=16, n_groups=2, conv_kernel=4, chunk_size=8,
+                                  n_routed_experts=8, num_experts_per_tok=3, moe_intermediate_size=48,
+                                  moe_shared_expert_intermediate_size=80, n_group=4, topk_group=2, norm_topk_prob=True,
+                                  routed_scaling_factor=1.7, moe_latent_size=latent)
         model = AutoModelForCausalLM.from_config(hc).float().eval()
     except (KeyError, ValueError, ImportError) as e:
         pytest.skip(f"transformers cannot build nemotron_h: {e}")
@@ -144,6 +149,9 @@ def test_nemotron_h_hybrid_matches_transformers():
                 p.add_(torch.randn_like(p) * 0.1)
             elif "dt_bias" in n:
                 p.uniform_(-2.0, 0.0)               # keeps dt above transformers' time_step_min floor
+        for n, buf in model.named_buffers():
+            if "e_score_correction_bias" in n:
+                buf.normal_(0, 0.1)
     d = tempfile.mkdtemp(prefix="parity_nemotron_h_")
     model.save_pretrained(d, safe_serialization=True)
     T = 24
@@ -151,7 +159,7 @@ def test_nemotron_h_hybrid_matches_transformers():
     with torch.no_grad():
         want = model(ids[None]).logits[0]
     cfg = ModelConfig.from_path(d)
-    assert cfg.extra["hybrid_pattern"] == "M*MM" and cfg.extra["mamba"]["norm_groups"] == 2
+    assert cfg.extra["hybrid_pattern"] == pattern and cfg.extra["mamba"]["norm_groups"] == 2
     ours = HybridModel(cfg, load_hybrid_weights(d, cfg, dtype=torch.float32), max_seqs=2)
     pool = KVPool(cfg, 8, 16, device="cpu", dtype=torch.float32, num_layers=ours.num_kv_layers)
     b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
@@ -163,13 +171,14 @@ def test_nemotron_h_hybrid_matches_transformers():
     b.seq_ids, b.pf_starts = [0], [0]
     got = ours.forward(b, pool.layers).float()
     err = (got - want).abs().max().item()
-    assert err < 4e-3 * max(want.abs().max().item(), 1.0), f"max abs error {err:.3e}"
+    assert err < tol * max(want.abs().max().item(), 1.0), f"max abs error {err:.3e}"
 
 
-@pytest.mark.parametrize("pos", [None, "rope"])
-def test_granite_hybrid_matches_transformers(pos):
-    """Granite 4 hybrid (Mamba2 / attention mixers + gated shared MLP per layer, Granite multipliers,
-    attention with or without RoPE) on the hybrid executor, and a greedy run through the LLM front end."""
+@pytest.mark.parametrize("pos,experts", [(None, 0), ("rope", 0), ("rope", 4)])
+def test_granite_hybrid_matches_transformers(pos, experts):
+    """Granite 4 hybrid (Mamba2 / attention mixers + gated shared MLP per layer, with or without routed
+    experts beside it, Granite multipliers, attention with or without RoPE) on the hybrid executor, and
+    a greedy run through the LLM front end."""
     from transformers import AutoConfig, AutoModelForCausalLM
 
     from mlxcel_b200.engine.engine import EngineConfig
@@ -182,7 +191,8 @@ def test_granite_hybrid_matches_transformers(pos):
         hc = AutoConfig.for_model(
             "granitemoehybrid", hidden_size=64, intermediate_size=128, shared_intermediate_size=96, num_hidden_layers=4,
             num_attention_heads=4, num_key_value_heads=2, vocab_size=300, max_position_embeddings=256,
-            layer_types=["mamba", "attention", "mamba", "mamba"], num_local_experts=0, mamba_n_heads=8, mamba_d_head=16,
+            layer_types=["mamba", "attention", "mamba", "mamba"], num_local_experts=experts, num_experts_per_tok=2,
+            mamba_n_heads=8, mamba_d_head=16,
             mamba_d_state=16, mamba_n_groups=2, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=8,
             embedding_multiplier=2.0, residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=3.0,
             position_embedding_type=pos)
@@ -202,7 +212,7 @@ def test_granite_hybrid_matches_transformers(pos):
     with torch.no_grad():
         want = model(ids[None]).logits[0]
     cfg = ModelConfig.from_path(d)
-    assert cfg.extra["hybrid_pattern"] == "MG*GMGMG" and (cfg.rot_dim > 0) == (pos == "rope")
+    assert cfg.extra["hybrid_pattern"] == ("ME*EMEME" if experts else "MG*GMGMG") and (cfg.rot_dim > 0) == (pos == "rope")
     ours = HybridModel(cfg, load_granite_hybrid_weights(d, cfg, dtype=torch.float32), max_seqs=2)
     pool = KVPool(cfg, 8, 16, device="cpu", dtype=torch.float32, num_layers=ours.num_kv_layers)
     b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
