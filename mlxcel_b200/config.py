@@ -865,6 +865,50 @@ def _nemotron_h(c: ModelConfig, raw: dict) -> None:
     c.hidden_act = "relu2"
 
 
+def _vaultgemma(c: ModelConfig, raw: dict) -> None:
+    """VaultGemma: the Gemma-2 block (soft-capped logits, alternating sliding / full attention,
+    (1 + w) norms) without the two post-norms (reference src/models/vaultgemma.rs)."""
+    _gemma(c, raw)
+    n = c.num_hidden_layers
+    if c.layer_types is None and c.sliding_window:
+        c.layer_types = ["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(n)]
+
+
+def _solar_open(c: ModelConfig, raw: dict) -> None:
+    """Solar Open: the GLM-4.5 MoE (sigmoid scores, selection bias, group-limited top-k, shared
+    experts) in every layer, full-rotary GQA attention without biases or q/k norms."""
+    _deepseek_routing(c, raw)
+    c.extra["first_k_dense"] = 0
+    c.attention_bias = False
+
+
+def _minimax_m2(c: ModelConfig, raw: dict) -> None:
+    """MiniMax-M2: q/k RMSNorm over the whole projection, partial rotary, sigmoid router scores with a
+    selection bias, top-k weights normalised to one, no shared experts (reference
+    src/models/minimax.rs)."""
+    c.qk_norm = True
+    c.extra["qk_norm_full"] = True
+    c.moe_route_mode = "sigmoid_group"
+    c.num_experts = int(raw.get("num_local_experts", raw.get("num_experts", 0)) or 0)
+    c.moe_intermediate_size = c.intermediate_size
+    c.norm_topk_prob = True
+    c.extra["moe_routing"] = dict(n_group=1, topk_group=1, scale=1.0, norm_min=0.0)
+    c.router_bias = True
+
+
+def _exaone_moe(c: ModelConfig, raw: dict) -> None:
+    """K-EXAONE: pre-norm blocks with the EXAONE-4 attention (per-head q/k RMSNorm, no positional
+    encoding on the full-attention layers of hybrid models) and DeepSeek-V3 style MoE layers after
+    ``first_k_dense_replace`` dense ones (reference src/models/exaone_moe.rs)."""
+    raw = dict(raw)
+    raw.setdefault("n_routed_experts", raw.get("num_experts", 0))
+    raw.setdefault("n_shared_experts", raw.get("num_shared_experts", 0))
+    _deepseek_routing(c, raw)
+    c.qk_norm = True
+    if c.sliding_window and c.layer_types:
+        c.extra["nope_layers"] = [i for i, t in enumerate(c.layer_types) if t != "sliding_attention"]
+
+
 FAMILIES = {
     "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _smollm3, "seed_oss": _plain,
     "helium": _interleaved_rope, "internlm3": _plain, "exaone4": _exaone4, "hunyuan_v1_dense": _hunyuan_dense,
@@ -877,6 +921,7 @@ FAMILIES = {
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
     "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe,
 }
 
 

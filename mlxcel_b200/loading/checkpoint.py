@@ -276,7 +276,8 @@ def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
         r = dequantize_ref(r, g.dtype)
     lw.router_w = r
     lw.router_b = g.vec(rb + ".bias")
-    for bias_name in (rb + ".e_score_correction_bias", p + ".mlp.moe_statics.e_score_correction_bias"):
+    for bias_name in (rb + ".e_score_correction_bias", p + ".mlp.moe_statics.e_score_correction_bias",
+                      p + ".mlp.e_score_correction_bias", p + ".block_sparse_moe.e_score_correction_bias"):
         if g.src.has(bias_name):                               # DeepSeek-V3 / ERNIE routing: selection bias (fp32)
             lw.router_b = g.src.get(bias_name).float().reshape(-1)
     # experts: stacked MLX switch layers, GPT-OSS fused tensors, or per-expert HF modules

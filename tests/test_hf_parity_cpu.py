@@ -60,6 +60,15 @@ FAMILIES = {
     "dots1": dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=48, n_shared_experts=2, n_group=2,
                   topk_group=1, first_k_dense_replace=1, routed_scaling_factor=2.0, head_dim=16),
     "gpt_oss": dict(num_local_experts=4, num_experts_per_tok=2, head_dim=16, **SLIDING),
+    "vaultgemma": dict(head_dim=16, sliding_window=8, query_pre_attn_scalar=16),
+    "solar_open": dict(n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=48, n_shared_experts=1, n_group=2,
+                       topk_group=1, routed_scaling_factor=1.5, head_dim=16, pad_token_id=0),
+    "minimax_m2": dict(num_local_experts=4, num_experts_per_tok=2, head_dim=16,
+                       rope_parameters=dict(rope_type="default", rope_theta=10000.0, partial_rotary_factor=0.5)),
+    "exaone_moe": dict(num_hidden_layers=4, head_dim=16, sliding_window=8,
+                       layer_types=["sliding_attention", "full_attention"] * 2, num_experts=8, num_experts_per_tok=2,
+                       moe_intermediate_size=48, num_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1,
+                       routed_scaling_factor=2.5),
     "mamba2": dict(num_heads=8, head_dim=16, state_size=16, n_groups=1, expand=2, conv_kernel=4, chunk_size=8),
 }
 
