@@ -909,6 +909,23 @@ def _exaone_moe(c: ModelConfig, raw: dict) -> None:
         c.extra["nope_layers"] = [i for i, t in enumerate(c.layer_types) if t != "sliding_attention"]
 
 
+def _lfm2(c: ModelConfig, raw: dict) -> None:
+    """LFM2: every layer is a gated short convolution or a GQA attention layer (per-head q/k RMSNorm,
+    full rotary) followed by a SwiGLU MLP (reference src/models/lfm2.rs). Runs on the hybrid executor
+    as ``CG`` / ``*G`` per layer."""
+    c.rms_norm_eps = float(raw.get("norm_eps", raw.get("block_norm_eps", 1e-5)))
+    c.qk_norm = True
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", raw.get("tie_embedding", True)))
+    types = raw.get("layer_types")
+    if not types:
+        full = set(raw.get("full_attn_idxs") or [])
+        types = ["full_attention" if i in full else "conv" for i in range(c.num_hidden_layers)]
+    c.extra["shortconv"] = dict(d_conv=int(raw.get("conv_L_cache", 3)), bias=bool(raw.get("conv_bias", False)))
+    c.extra["hybrid_pattern"] = "".join(("*" if t == "full_attention" else "C") + "G" for t in types)
+    c.extra["hybrid_layout"] = "lfm2"
+    c.layer_types = None
+
+
 FAMILIES = {
     "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _smollm3, "seed_oss": _plain,
     "helium": _interleaved_rope, "internlm3": _plain, "exaone4": _exaone4, "hunyuan_v1_dense": _hunyuan_dense,
@@ -921,7 +938,7 @@ FAMILIES = {
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
     "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
-    "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe,
+    "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2,
 }
 
 

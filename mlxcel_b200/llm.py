@@ -22,7 +22,7 @@ class LLM:
         """``fold_norms``: the weights belong to this object alone, so the executor may fold the
         RMSNorm weights into the projections in place (deferred RMSNorm, see DecoderModel)."""
         self.cfg = cfg
-        if cfg.model_type in ("mamba", "mamba2", "nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "falcon_h1"):
+        if cfg.model_type in ("mamba", "mamba2", "nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "falcon_h1", "lfm2"):
             from .models.hybrid import HybridModel
             from .models.mamba1 import Mamba1Model
             from .models.mamba2 import Mamba2Model
@@ -79,6 +79,10 @@ class LLM:
         if cfg.model_type == "falcon_h1":
             from .models.hybrid import load_falcon_h1_weights
             return LLM(cfg, load_falcon_h1_weights(path, cfg, device=device), engine_config, comm=comm,
+                       tokenizer=load_tokenizer(path))
+        if cfg.model_type == "lfm2":
+            from .models.hybrid import load_lfm2_weights
+            return LLM(cfg, load_lfm2_weights(path, cfg, device=device), engine_config, comm=comm,
                        tokenizer=load_tokenizer(path))
         if cfg.model_type == "qwen3_next":
             from .models.hybrid import load_qwen3_next_weights

@@ -60,13 +60,13 @@ class HybridWeights:
     layers: list = field(default_factory=list)  # the attention blocks' LayerWeights (= KV-pool layers)
 
 
-_KINDS = {"M": "mamba2", "m": "mamba1", "L": "gdn", "P": "parallel", "*": "attention", "A": "attention", "-": "mlp", "G": "mlp",
+_KINDS = {"M": "mamba2", "m": "mamba1", "L": "gdn", "C": "shortconv", "P": "parallel", "*": "attention", "A": "attention", "-": "mlp", "G": "mlp",
           "E": "moe"}   # G: gated MLP, A: attention with an output gate, L: Gated DeltaNet
 
 
 def block_kinds(cfg: ModelConfig) -> list[str]:
     pat = cfg.extra["hybrid_pattern"]
-    per_layer = 2 if cfg.extra.get("hybrid_layout") in ("granite", "jamba", "qwen3_next", "falcon_h1") else 1
+    per_layer = 2 if cfg.extra.get("hybrid_layout") in ("granite", "jamba", "qwen3_next", "falcon_h1", "lfm2") else 1
     if len(pat) != cfg.num_hidden_layers * per_layer:
         raise ValueError(f"hybrid pattern has {len(pat)} entries for {cfg.num_hidden_layers} layers")
     try:
@@ -300,6 +300,57 @@ def load_jamba_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu
                          lm_head=embed if head is None else head.to(device), layers=attn_layers)
 
 
+def load_lfm2_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
+    """LFM2 checkpoint: ``model.layers.N.{operator_norm, conv.(in_proj, conv, out_proj) | self_attn.(q_proj,
+    k_proj, v_proj, out_proj, q_layernorm, k_layernorm), ffn_norm, feed_forward.(w1, w3, w2)}`` and
+    ``model.embedding_norm`` as the final norm; each layer becomes a mixer block (gated short conv or
+    attention with per-head q/k RMSNorm) and a gated-MLP block (reference src/models/lfm2.rs)."""
+    from ..loading.checkpoint import TensorSource, _cat_rows, _Getter
+    from .shortconv import ShortConvLayerWeights
+
+    src = TensorSource(path)
+    g = _Getter(src, cfg, dtype, dequantize=True)
+    K, H = int(cfg.extra["shortconv"]["d_conv"]), cfg.hidden_size
+
+    def need(t, name):
+        if t is None:
+            raise KeyError(f"{path}: missing tensor {name}")
+        return t.to(device)
+
+    opt = lambda n: None if g.vec(n) is None else g.vec(n).to(device)  # noqa: E731
+    blocks, attn_layers = [], []
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        norm = need(g.vec(p + "operator_norm.weight"), p + "operator_norm.weight")
+        if src.has(p + "conv.in_proj.weight"):
+            c = p + "conv."
+            cw = need(g.vec(c + "conv.weight"), c + "conv.weight")
+            cw = cw.reshape(H, K) if cw.dim() == 2 or cw.shape[1] == 1 else cw.squeeze(-1)
+            cb = opt(c + "conv.bias")
+            lw = ShortConvLayerWeights(norm=norm, in_proj=need(g.mat(c + "in_proj"), c + "in_proj"), conv_w=cw.float(),
+                                       out_proj=need(g.mat(c + "out_proj"), c + "out_proj"), in_proj_b=opt(c + "in_proj.bias"),
+                                       conv_b=None if cb is None else cb.float(), out_proj_b=opt(c + "out_proj.bias"))
+            blocks.append(HybridBlock("shortconv", norm, mamba=lw))
+        else:
+            a = p + "self_attn."
+            q, k, v = (need(g.mat(a + n), a + n) for n in ("q_proj", "k_proj", "v_proj"))
+            lw = LayerWeights(ln1=norm, ln2=norm, wqkv=torch.cat([q, k, v], 0).contiguous(),
+                              wo=need(g.mat(a + "out_proj"), a + "out_proj"),
+                              q_norm=need(g.vec(a + "q_layernorm.weight"), a + "q_layernorm"),
+                              k_norm=need(g.vec(a + "k_layernorm.weight"), a + "k_layernorm"))
+            attn_layers.append(lw)
+            blocks.append(HybridBlock("attention", norm, attn=lw))
+        f = p + "feed_forward."
+        blocks.append(HybridBlock("mlp", need(g.vec(p + "ffn_norm.weight"), p + "ffn_norm.weight"),
+                                  up=_cat_rows([need(g.mat(f + "w1"), f + "w1"), need(g.mat(f + "w3"), f + "w3")]),
+                                  down=need(g.mat(f + "w2"), f + "w2"), gated=True))
+    embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")
+    head = g.mat("lm_head") if src.has("lm_head.weight") and not cfg.tie_word_embeddings else None
+    return HybridWeights(embed=embed, blocks=blocks,
+                         final_norm=need(g.vec("model.embedding_norm.weight"), "model.embedding_norm.weight"),
+                         lm_head=embed if head is None else head.to(device), layers=attn_layers)
+
+
 def load_qwen3_next_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
     """Qwen3-Next checkpoint: ``model.layers.N.{input_layernorm, linear_attn.* | self_attn.*,
     post_attention_layernorm, mlp.(gate + experts.E.* + shared_expert.* + shared_expert_gate | gate_proj ...)}``.
@@ -490,7 +541,12 @@ class HybridModel:
         mamba_layers = [b.mamba for b in weights.blocks if b.kind in ("mamba2", "parallel")]
         mamba1_layers = [b.mamba for b in weights.blocks if b.kind == "mamba1"]
         gdn_layers = [b.mamba for b in weights.blocks if b.kind == "gdn"]
-        if gdn_layers:                          # Qwen3-Next: Gated DeltaNet mixers
+        conv_layers = [b.mamba for b in weights.blocks if b.kind == "shortconv"]
+        if conv_layers:                         # LFM2: gated short convolutions
+            from .shortconv import ShortConvModel
+            self.ssm = ShortConvModel(cfg, Mamba2Weights(weights.embed, conv_layers, weights.final_norm, weights.lm_head),
+                                      max_seqs=max_seqs, comm=self.comm)
+        elif gdn_layers:                          # Qwen3-Next: Gated DeltaNet mixers
             from .gdn import GdnModel
             self.ssm = GdnModel(cfg, Mamba2Weights(weights.embed, gdn_layers, weights.final_norm, weights.lm_head),
                                 max_seqs=max_seqs, comm=self.comm)
@@ -527,8 +583,9 @@ class HybridModel:
 
         for blk in self.w.blocks:
             x = ops.rmsnorm(h, blk.norm, eps, 0.0)
-            if blk.kind in ("mamba2", "mamba1", "gdn"):
-                h = add(self.ssm._mixer(mi, blk.mamba, x, pieces), blk.mamba.out_proj)
+            if blk.kind in ("mamba2", "mamba1", "gdn", "shortconv"):
+                h = add(self.ssm._mixer(mi, blk.mamba, x, pieces), blk.mamba.out_proj,
+                        getattr(blk.mamba, "out_proj_b", None))
                 mi += 1
             elif blk.kind == "parallel":         # Falcon-H1: Mamba2 mixer and attention side by side
                 ym = ops.linear(self.ssm._mixer(mi, blk.mamba, x, pieces), blk.mamba.out_proj)

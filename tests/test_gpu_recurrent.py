@@ -300,6 +300,8 @@ def _tiny_hf_hybrid(name):
                                  mamba_n_groups=2, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=8,
                                  embedding_multiplier=2.0, residual_multiplier=0.5, attention_multiplier=0.125,
                                  logits_scaling=2.0),
+        "lfm2": dict(layer_types=["conv", "full_attention", "conv", "conv"], conv_L_cache=3, conv_bias=False,
+                     block_auto_adjust_ff_dim=False),
     }[name]
     torch.manual_seed(0)
     try:
@@ -315,7 +317,7 @@ def _tiny_hf_hybrid(name):
     return d
 
 
-@pytest.mark.parametrize("name", ["jamba", "qwen3_next", "granitemoehybrid"])
+@pytest.mark.parametrize("name", ["jamba", "qwen3_next", "granitemoehybrid", "lfm2"])
 def test_hybrid_checkpoints_gpu_matches_cpu(name):
     """Hybrid layouts end to end on the GPU (bf16 kernels) against this package's fp32 CPU path, from a
     checkpoint written by transformers: prompt logits, then a short greedy run through the engine."""
@@ -329,7 +331,7 @@ def test_hybrid_checkpoints_gpu_matches_cpu(name):
     d = _tiny_hf_hybrid(name)
     cfg = ModelConfig.from_path(d)
     load = {"jamba": hybrid.load_jamba_weights, "qwen3_next": hybrid.load_qwen3_next_weights,
-            "granitemoehybrid": hybrid.load_granite_hybrid_weights}[name]
+            "granitemoehybrid": hybrid.load_granite_hybrid_weights, "lfm2": hybrid.load_lfm2_weights}[name]
     T = 40
     ids = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
 

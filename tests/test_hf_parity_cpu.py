@@ -244,6 +244,60 @@ def test_granite_hybrid_matches_transformers(pos, experts):
         assert out == ref
 
 
+def test_lfm2_matches_transformers():
+    """LFM2 (gated short convolutions and q/k-normed attention layers + SwiGLU MLPs) on the hybrid
+    executor: prompt logits, then prefill in 8-token chunks and greedy decode through the LLM front end."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    from mlxcel_b200.engine.engine import EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.llm import LLM
+    from mlxcel_b200.models.hybrid import HybridModel, load_lfm2_weights
+
+    torch.manual_seed(0)
+    try:
+        hc = AutoConfig.for_model("lfm2", hidden_size=64, intermediate_size=128, num_hidden_layers=4,
+                                  num_attention_heads=4, num_key_value_heads=2, vocab_size=300,
+                                  max_position_embeddings=256, layer_types=["conv", "full_attention", "conv", "conv"],
+                                  conv_L_cache=3, conv_bias=False, block_auto_adjust_ff_dim=False, pad_token_id=0)
+        model = AutoModelForCausalLM.from_config(hc).float().eval()
+    except (KeyError, ValueError, ImportError) as e:
+        pytest.skip(f"transformers cannot build lfm2: {e}")
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.4 if "conv.conv" in n else 0.08)
+            elif "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tempfile.mkdtemp(prefix="parity_lfm2_")
+    model.save_pretrained(d, safe_serialization=True)
+    T = 24
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0]
+    cfg = ModelConfig.from_path(d)
+    assert cfg.extra["hybrid_pattern"] == "CG*GCGCG"
+    ours = HybridModel(cfg, load_lfm2_weights(d, cfg, dtype=torch.float32), max_seqs=2)
+    pool = KVPool(cfg, 8, 16, device="cpu", dtype=torch.float32, num_layers=ours.num_kv_layers)
+    b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
+                  slot_mapping=torch.arange(T, dtype=torch.int32), num_prefill_seqs=1,
+                  pf_block_tables=torch.arange(8, dtype=torch.int32)[None],
+                  pf_cu_q=torch.tensor([0, T], dtype=torch.int32),
+                  pf_context_lens=torch.tensor([T], dtype=torch.int32), pf_max_q_len=T, pf_cu_q_host=[0, T],
+                  logits_rows=torch.arange(T))
+    b.seq_ids, b.pf_starts = [0], [0]
+    got = ours.forward(b, pool.layers).float()
+    err = (got - want).abs().max().item()
+    assert err < 2e-3 * max(want.abs().max().item(), 1.0), f"max abs error {err:.3e}"
+    llm = LLM.from_pretrained(d, device="cpu", engine_config=EngineConfig(num_blocks=32, block_size=16, max_batch=4,
+                                                                           max_model_len=128, max_num_batched_tokens=8))
+    out = llm.generate(prompt_token_ids=[ids[:12].tolist()],
+                       sampling_params=SamplingParams(max_tokens=5, ignore_eos=True))[0].output
+    with torch.no_grad():
+        ref = model.generate(ids[None, :12], max_new_tokens=5, do_sample=False)[0, 12:].tolist()
+    assert out == ref
+
+
 @pytest.mark.parametrize("name", ["llama", "gemma3_text", "glm4_moe", "deepseek_v3", "cohere2", "olmo2"])
 def test_greedy_generation_matches_transformers(name):
     """Prefill + token-by-token decode through the engine (paged KV, chunked prefill of 16 tokens)
