@@ -283,6 +283,38 @@ def cmd_download(a):
         raise SystemExit(str(ex))
 
 
+def cmd_tune(a):
+    """Profile the launch knobs of the hot kernels and cache the winners (reference src/main.rs:348,
+    ``mlxcel tune``)."""
+    from . import autotune as at
+    names = a.op or list(at.OPS)
+    bad = [n for n in names if n not in at.OPS]
+    if bad:
+        raise SystemExit(f"unknown op {bad[0]!r}; known: {', '.join(at.OPS)}")
+    geo = at.Geometry()
+    if a.model:
+        from .config import ModelConfig, preset
+        cfg = preset(a.model.split(":", 1)[1]) if a.model.startswith("preset:") else ModelConfig.from_path(a.model)
+        geo = at.Geometry.from_config(cfg)
+    if a.dry_run:
+        rows = [r for n in names for r in at.OPS[n].matrix()]
+        if a.json:
+            print(json.dumps(dict(geometry=geo.key(), matrix=rows)))
+        else:
+            print(f"geometry {geo.key()}")
+            for r in rows:
+                print(f"  {r['op']:<26} {r['env']}={r['value']}{'  (default)' if r['default'] else ''}")
+        return
+    store = at.TacticStore(a.cache_file)
+    results = at.tune(names, geo, store, log=None if a.json else print)
+    if a.json:
+        print(json.dumps([r.__dict__ for r in results]))
+        return
+    for r in results:
+        print(f"{r.op}: {'kept default (' + r.skipped + ')' if r.skipped else f'{at.OPS[r.op].env}={r.value} ({r.us:.1f} us)'}")
+    print(f"wrote {store.path}; set {at.SWITCH}=cache to use it")
+
+
 def cmd_serve(a):
     import uvicorn
 
@@ -472,6 +504,13 @@ def main(argv=None):
     p.add_argument("--models-dir", default=None)
     p.add_argument("--local-dir", default=None)
     p.set_defaults(fn=cmd_download)
+    p = sub.add_parser("tune", help="profile kernel launch knobs and cache the winners")
+    p.add_argument("--op", action="append", default=None)
+    p.add_argument("-m", "--model", default=None, help="take the problem geometry from this checkpoint or preset")
+    p.add_argument("--dry-run", action="store_true", help="print the candidate matrix, profile nothing")
+    p.add_argument("--cache-file", default=None)
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_tune)
     p = sub.add_parser("inspect", help="memory estimate")
     _add_model_args(p)
     p.set_defaults(fn=cmd_inspect)
@@ -490,7 +529,7 @@ def main(argv=None):
     p.add_argument("--group-size", type=int, default=64)
     p.set_defaults(fn=cmd_random_init)
     a = ap.parse_args(argv)
-    if isinstance(getattr(a, "model", None), str):          # owner/name ids resolve through the local store
+    if isinstance(getattr(a, "model", None), str) and a.model:   # owner/name ids resolve through the local store
         from .store import resolve_model
         a.model = resolve_model(a.model)
     a.fn(a)

@@ -35,6 +35,10 @@ def load(required: bool = True):
         except Exception as e:  # pragma: no cover - build environment specific
             _LIB_ERR = f"build failed: {e}"
     if path.exists():
+        if os.environ.get("MLXCEL_B200_AUTOTUNE", "") in ("1", "cache"):
+            from .. import autotune      # cached launch knobs go into the environment before the library reads them
+
+            autotune.apply_cached()
         try:
             _LIB = ctypes.CDLL(str(path))
             _declare(_LIB)
