@@ -88,9 +88,53 @@ def load_llm(a):
         llm = LLM.from_preset(a.model.split(":", 1)[1], device=dev, engine_config=ecfg, comm=comm, dtype=dtype)
         from .tokenizer import ByteTokenizer
         llm.tokenizer = ByteTokenizer(llm.cfg.vocab_size)
-        return llm
-    return LLM.from_pretrained(a.model, device=dev, engine_config=ecfg, comm=comm, dequantize=a.dequantize,
-                               surgery=getattr(a, "surgery", None))
+    else:
+        llm = LLM.from_pretrained(a.model, device=dev, engine_config=ecfg, comm=comm, dequantize=a.dequantize,
+                                  surgery=getattr(a, "surgery", None))
+    attach_drafter(llm, a, dev)
+    return llm
+
+
+def attach_drafter(llm, a, dev) -> None:
+    """``--draft-model`` (a smaller model of the same vocabulary, or a drafter directory written by
+    ``split-mtp``) and ``--prompt-lookup`` put a speculative drafter on the engine; ``--draft-max`` is the
+    number of draft tokens per verify round (reference src/commands/generate.rs draft routing)."""
+    import os
+
+    import torch
+
+    draft, lookup = getattr(a, "draft_model", None), getattr(a, "prompt_lookup", False)
+    if not draft and not lookup:
+        return
+    eng = llm.engine
+    if getattr(eng.model, "recurrent", False):
+        raise SystemExit("speculative decoding needs a KV-cache model (recurrent state cannot be rolled back)")
+    eng.spec_k = max(1, int(getattr(a, "draft_max", 4))) + 1
+    if not draft:
+        from .speculative import PromptLookupDrafter
+        eng.drafter = PromptLookupDrafter()
+        return
+    from .loading.split_mtp import MARKER
+    dtype = eng.model.w.final_norm.dtype
+    nb = max(256, eng.ecfg.max_batch * ((eng.ecfg.max_model_len + eng.ecfg.block_size - 1) // eng.ecfg.block_size))
+    if os.path.exists(os.path.join(draft, MARKER)):
+        from .loading.split_mtp import load_mtp_weights
+        from .speculative import MTPDrafter
+        dcfg, w, _ = load_mtp_weights(draft, dtype=dtype, device=dev)
+        if dcfg.hidden_size != llm.cfg.hidden_size or dcfg.vocab_size != llm.cfg.vocab_size:
+            raise SystemExit(f"{draft}: the MTP drafter was split from a different model")
+        eng.drafter = MTPDrafter(eng.model, dcfg, w, num_blocks=nb, block_size=eng.ecfg.block_size)
+        return
+    from .config import ModelConfig
+    from .loading.checkpoint import load_model_weights
+    from .models.decoder import DecoderModel
+    from .speculative import DraftModelDrafter
+    dcfg = ModelConfig.from_path(draft)
+    if dcfg.vocab_size != llm.cfg.vocab_size:
+        raise SystemExit(f"{draft}: vocabulary size {dcfg.vocab_size} differs from the target's {llm.cfg.vocab_size}")
+    dw = load_model_weights(draft, dcfg, device=dev, dtype=dtype if dev == "cpu" else torch.bfloat16)
+    eng.drafter = DraftModelDrafter(DecoderModel(dcfg, dw), dcfg, num_blocks=nb, block_size=eng.ecfg.block_size,
+                                    max_model_len=eng.ecfg.max_model_len)
 
 
 def cmd_generate(a):
@@ -121,6 +165,10 @@ def cmd_generate(a):
     n = len(s.output)
     print(f"[prompt {len(ids)} tok, {len(ids) / max(ttft, 1e-9):.1f} tok/s | generated {n} tok, "
           f"{max(n - 1, 0) / max(dt - ttft, 1e-9):.1f} tok/s | finish: {s.finish_reason.value}]", file=sys.stderr)
+    st = llm.engine.stats
+    if llm.engine.drafter is not None:
+        print(f"[speculative: {st['spec_rounds']} verify rounds, {st['spec_accepted']} of {st['spec_drafted']} drafts "
+              f"accepted]", file=sys.stderr)
 
 
 def cmd_run(a):
@@ -313,6 +361,19 @@ def cmd_tune(a):
     for r in results:
         print(f"{r.op}: {'kept default (' + r.skipped + ')' if r.skipped else f'{at.OPS[r.op].env}={r.value} ({r.us:.1f} us)'}")
     print(f"wrote {store.path}; set {at.SWITCH}=cache to use it")
+
+
+def cmd_split_mtp(a):
+    """Write the MTP layers of a raw checkpoint as a drafter checkpoint (reference src/main.rs:362,
+    ``mlxcel split-mtp``)."""
+    from .loading.split_mtp import split_mtp_dir
+    try:
+        res = split_mtp_dir(a.model, a.output, a.block_size, a.q_bits, a.q_group_size, a.force)
+    except ValueError as ex:
+        raise SystemExit(str(ex))
+    print(json.dumps(res) if a.json else
+          f"wrote {a.output}: {res['layers']} MTP layer(s) from model.layers.{res['source_layer']}, {res['tensors']} tensors, "
+          f"{res['bytes'] / 1e6:.1f} MB, block size {res['block_size']}; pass it as --draft-model")
 
 
 def cmd_serve(a):
@@ -511,6 +572,15 @@ def main(argv=None):
     p.add_argument("--cache-file", default=None)
     p.add_argument("--json", action="store_true")
     p.set_defaults(fn=cmd_tune)
+    p = sub.add_parser("split-mtp", help="extract the MTP layers of a raw checkpoint into a drafter checkpoint")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-o", "--output", required=True)
+    p.add_argument("--block-size", type=int, default=None)
+    p.add_argument("--q-bits", type=int, default=None)
+    p.add_argument("--q-group-size", type=int, default=64)
+    p.add_argument("--force", action="store_true")
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_split_mtp)
     p = sub.add_parser("inspect", help="memory estimate")
     _add_model_args(p)
     p.set_defaults(fn=cmd_inspect)
