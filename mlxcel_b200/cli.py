@@ -34,6 +34,62 @@ def _add_model_args(p):
     p.add_argument("--draft-model", default=None)
     p.add_argument("--draft-max", type=int, default=4)
     p.add_argument("--prompt-lookup", action="store_true")
+    _add_compat_args(p)
+
+
+_COMPAT_NOOPS = [("-ngl", "--n-gpu-layers", "--gpu-layers"), ("-t", "--threads"), ("-tb", "--threads-batch"),
+                 ("-to", "--timeout"), ("--cache-reuse",), ("--defrag-thold",), ("-sm", "--split-mode"), ("-mg", "--main-gpu"),
+                 ("--numa",), ("--poll",), ("--threads-http",)]
+_COMPAT_NOOP_SWITCHES = [("--mlock",), ("--no-mmap",), ("-fa", "--flash-attn"), ("-cb", "--cont-batching"),
+                         ("-nocb", "--no-cont-batching"), ("--no-warmup",), ("--jinja",), ("--metrics",), ("--slots",),
+                         ("--no-slots",), ("--no-webui",), ("--no-context-shift",), ("--context-shift",), ("--no-kv-offload",),
+                         ("--embeddings", "--embedding"), ("--reranking", "--rerank"), ("--props",), ("--log-disable",)]
+
+
+def _add_compat_args(p):
+    """llama-server spellings (reference src/cli/*_compat.rs, compat/llama-server manifest). Flags with a
+    counterpart here are mapped onto it by :func:`_apply_compat`; flags about CPU threads, mmap, GPU layer
+    offload and the like have no meaning on this runtime and are accepted so that existing launch scripts
+    keep working (a note on stderr names the ones that were given)."""
+    g = p.add_argument_group("llama-server compatible spellings")
+    g.add_argument("-md", "--model-draft", dest="compat_model_draft", default=None, help="same as --draft-model")
+    g.add_argument("--draft", "--draft-n", dest="compat_draft_n", type=int, default=None, help="same as --draft-max")
+    g.add_argument("-b", "--batch-size", dest="compat_batch", type=int, default=None, help="same as --max-batch-tokens")
+    g.add_argument("-ub", "--ubatch-size", dest="compat_ubatch", type=int, default=None,
+                   help="same as --prefill-chunk-size")
+    g.add_argument("-ctk", "--cache-type-k", dest="compat_ctk", default=None, help="f16 | bf16 | q8_0: q8_0 means --kv-bits 8")
+    g.add_argument("-ctv", "--cache-type-v", dest="compat_ctv", default=None, help="f16 | bf16 | q8_0: q8_0 means --kv-bits 8")
+    g.add_argument("--no-cache-prompt", dest="compat_no_cache_prompt", action="store_true", help="same as --no-prompt-cache")
+    g.add_argument("--lookup-ngram-min", dest="compat_lookup", type=int, default=None, help="turns --prompt-lookup on")
+    for names in _COMPAT_NOOPS:
+        g.add_argument(*names, dest="compat_noop_" + names[-1].strip("-").replace("-", "_"), default=None, help="accepted, no effect")
+    for names in _COMPAT_NOOP_SWITCHES:
+        g.add_argument(*names, dest="compat_noop_" + names[-1].strip("-").replace("-", "_"), action="store_const", const=True,
+                       default=None, help="accepted, no effect")
+
+
+def _apply_compat(a) -> list[str]:
+    """Fold the llama-server spellings into the native options; returns the no-effect flags that were given."""
+    if getattr(a, "compat_model_draft", None) and not getattr(a, "draft_model", None):
+        a.draft_model = a.compat_model_draft
+    if getattr(a, "compat_draft_n", None) is not None:
+        a.draft_max = a.compat_draft_n
+    if getattr(a, "compat_batch", None) is not None:
+        a.max_batch_tokens = a.compat_batch
+    if getattr(a, "compat_ubatch", None) is not None:
+        a.prefill_chunk_size = a.compat_ubatch
+    types = [t for t in (getattr(a, "compat_ctk", None), getattr(a, "compat_ctv", None)) if t]
+    for t in types:
+        if t.lower() not in ("f16", "bf16", "f32", "q8_0", "int8", "fp8"):
+            raise SystemExit(f"cache type {t!r} is not supported (f16, bf16, q8_0)")
+    if any(t.lower() in ("q8_0", "int8", "fp8") for t in types) and not getattr(a, "kv_bits", 0):
+        a.kv_bits = 8
+    if getattr(a, "compat_no_cache_prompt", False):
+        a.no_prompt_cache = True
+    if getattr(a, "compat_lookup", None) is not None:
+        a.prompt_lookup = True
+    return sorted("--" + k[len("compat_noop_"):].replace("_", "-") for k, v in vars(a).items()
+                  if k.startswith("compat_noop_") and v is not None)
 
 
 def _add_sampling_args(p):
@@ -599,6 +655,9 @@ def main(argv=None):
     p.add_argument("--group-size", type=int, default=64)
     p.set_defaults(fn=cmd_random_init)
     a = ap.parse_args(argv)
+    ignored = _apply_compat(a)
+    if ignored:
+        print(f"accepted for llama-server compatibility, no effect on this runtime: {' '.join(ignored)}", file=sys.stderr)
     if isinstance(getattr(a, "model", None), str) and a.model:   # owner/name ids resolve through the local store
         from .store import resolve_model
         a.model = resolve_model(a.model)

@@ -146,3 +146,26 @@ def test_python_client_against_fake_transport():
     assert s.calls[0][3] == {"Authorization": "Bearer k"} and s.calls[2][2]["max_tokens"] == 4
     with pytest.raises(MlxcelError):
         c.detokenize([1])
+
+
+def test_llama_server_flag_spellings_map_onto_native_options(capsys):
+    """-md / --draft / -b / -ub / -ctk / --no-cache-prompt fold into the native options; CPU-thread, mmap and
+    GPU-offload flags are accepted and reported as having no effect."""
+    import argparse
+
+    from mlxcel_b200 import cli
+
+    ap = argparse.ArgumentParser()
+    cli._add_model_args(ap)
+    a = ap.parse_args(["-m", "x", "-md", "drafter", "--draft", "3", "-b", "512", "-ub", "128", "-ctk", "q8_0", "-ctv", "f16",
+                       "--no-cache-prompt", "-ngl", "99", "-fa", "--mlock", "-t", "8"])
+    ignored = cli._apply_compat(a)
+    assert (a.draft_model, a.draft_max, a.max_batch_tokens, a.prefill_chunk_size, a.kv_bits, a.no_prompt_cache) == \
+        ("drafter", 3, 512, 128, 8, True)
+    assert ignored == ["--flash-attn", "--gpu-layers", "--mlock", "--threads"]
+    b = ap.parse_args(["-m", "x", "--draft-model", "native", "-md", "compat", "--kv-bits", "16", "-ctk", "q8_0"])
+    cli._apply_compat(b)
+    assert b.draft_model == "native" and b.kv_bits == 16          # the native spelling wins
+    import pytest
+    with pytest.raises(SystemExit):
+        cli._apply_compat(ap.parse_args(["-m", "x", "-ctk", "q4_0"]))
