@@ -34,6 +34,12 @@ def _add_model_args(p):
     p.add_argument("--draft-model", default=None)
     p.add_argument("--draft-max", type=int, default=4)
     p.add_argument("--prompt-lookup", action="store_true")
+    p.add_argument("--rope-freq-base", type=float, default=None, help="RoPE base frequency (overrides the checkpoint)")
+    p.add_argument("--rope-scaling", choices=["none", "linear", "yarn"], default=None)
+    p.add_argument("--rope-scale", type=float, default=None, help="context scaling factor of --rope-scaling")
+    p.add_argument("--yarn-orig-ctx", type=int, default=None, help="original context length of the YaRN scaling")
+    p.add_argument("--override-kv", action="append", default=None, metavar="KEY=JSON",
+                   help="replace a config.json key before the model is built (repeatable)")
     _add_compat_args(p)
 
 
@@ -146,9 +152,34 @@ def load_llm(a):
         llm.tokenizer = ByteTokenizer(llm.cfg.vocab_size)
     else:
         llm = LLM.from_pretrained(a.model, device=dev, engine_config=ecfg, comm=comm, dequantize=a.dequantize,
-                                  surgery=getattr(a, "surgery", None))
+                                  surgery=getattr(a, "surgery", None), config_overrides=config_overrides(a))
     attach_drafter(llm, a, dev)
     return llm
+
+
+def config_overrides(a) -> dict | None:
+    """``--rope-freq-base``, ``--rope-scaling`` / ``--rope-scale`` / ``--yarn-orig-ctx`` and ``--override-kv`` as
+    config.json replacements (reference src/cli/rope.rs)."""
+    ov: dict = {}
+    if getattr(a, "rope_freq_base", None):
+        ov["rope_theta"] = float(a.rope_freq_base)
+    kind = getattr(a, "rope_scaling", None)
+    if kind == "none":
+        ov["rope_scaling"] = None
+    elif kind or getattr(a, "rope_scale", None):
+        sc = dict(rope_type=kind or "linear", factor=float(getattr(a, "rope_scale", None) or 1.0))
+        if getattr(a, "yarn_orig_ctx", None):
+            sc["original_max_position_embeddings"] = int(a.yarn_orig_ctx)
+        ov["rope_scaling"] = sc
+    for item in getattr(a, "override_kv", None) or []:
+        k, sep, v = item.partition("=")
+        if not sep:
+            raise SystemExit(f"--override-kv {item!r}: expected KEY=JSON")
+        try:
+            ov[k] = json.loads(v)
+        except ValueError:
+            ov[k] = v
+    return ov or None
 
 
 def attach_drafter(llm, a, dev) -> None:

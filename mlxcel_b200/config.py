@@ -245,11 +245,37 @@ class ModelConfig:
         return c
 
     @staticmethod
-    def from_path(path: str | Path) -> "ModelConfig":
+    def from_path(path: str | Path, overrides: dict | None = None) -> "ModelConfig":
+        """``overrides``: keys replaced in ``config.json`` before it is interpreted (the ``--rope-*`` and
+        ``--override-kv`` options; reference src/cli/rope.rs). RoPE keys also replace their copies inside
+        ``rope_parameters`` when the checkpoint uses that spelling."""
         p = Path(path)
         if p.is_dir():
             p = p / "config.json"
-        return ModelConfig.from_dict(json.loads(p.read_text()))
+        raw = json.loads(p.read_text())
+        if overrides:
+            raw = apply_config_overrides(raw, overrides)
+        return ModelConfig.from_dict(raw)
+
+
+def apply_config_overrides(raw: dict, overrides: dict) -> dict:
+    raw = json.loads(json.dumps(raw))
+    tgt = raw.get("text_config") if isinstance(raw.get("text_config"), dict) else raw
+    for k, v in overrides.items():
+        tgt[k] = v
+        rp = tgt.get("rope_parameters")
+        if isinstance(rp, dict) and k in ("rope_theta", "rope_scaling"):
+            flat = all(not isinstance(x, dict) for x in rp.values())
+            for d in ([rp] if flat else [x for x in rp.values() if isinstance(x, dict)]):
+                if k == "rope_theta":
+                    d["rope_theta"] = v
+                elif v is None:
+                    for kk in [kk for kk in d if kk not in ("rope_theta", "partial_rotary_factor")]:
+                        d.pop(kk)
+                    d["rope_type"] = "default"
+                else:
+                    d.update(v)
+    return raw
 
 
 # ----------------------------------------------------------------------------- families

@@ -59,11 +59,12 @@ class LLM:
 
     @staticmethod
     def from_pretrained(path: str | Path, *, device="cuda", engine_config: EngineConfig | None = None,
-                        comm=None, dequantize: bool = False, surgery: str | None = None) -> "LLM":
+                        comm=None, dequantize: bool = False, surgery: str | None = None,
+                        config_overrides: dict | None = None) -> "LLM":
         from .loading.checkpoint import load_model_weights
         from .tokenizer import load_tokenizer
 
-        cfg = ModelConfig.from_path(path)
+        cfg = ModelConfig.from_path(path, config_overrides)
         if cfg.model_type == "mamba2":
             from .models.mamba2 import load_mamba2_weights
             return LLM(cfg, load_mamba2_weights(path, cfg, device=device), engine_config, comm=comm,

@@ -169,3 +169,35 @@ def test_llama_server_flag_spellings_map_onto_native_options(capsys):
     import pytest
     with pytest.raises(SystemExit):
         cli._apply_compat(ap.parse_args(["-m", "x", "-ctk", "q4_0"]))
+
+
+def test_rope_and_kv_overrides_change_the_built_config(tmp_path):
+    import argparse
+    import json
+
+    from mlxcel_b200 import cli
+    from mlxcel_b200.config import ModelConfig
+
+    base = dict(model_type="llama", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, vocab_size=300, max_position_embeddings=256, rope_theta=10000.0,
+                rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                  original_max_position_embeddings=64))
+    (tmp_path / "config.json").write_text(json.dumps(base))
+    ap = argparse.ArgumentParser()
+    cli._add_model_args(ap)
+    a = ap.parse_args(["-m", "x", "--rope-freq-base", "500000", "--rope-scaling", "yarn", "--rope-scale", "4",
+                       "--yarn-orig-ctx", "64", "--override-kv", "rms_norm_eps=1e-4", "--override-kv", "sliding_window=null"])
+    ov = cli.config_overrides(a)
+    cfg = ModelConfig.from_path(tmp_path, ov)
+    assert cfg.rope_theta == 500000.0 and cfg.rope_scaling["rope_type"] == "yarn" and cfg.rope_scaling["factor"] == 4.0
+    assert cfg.rope_scaling["original_max_position_embeddings"] == 64 and cfg.rms_norm_eps == 1e-4
+    none = ModelConfig.from_path(tmp_path, cli.config_overrides(ap.parse_args(["-m", "x", "--rope-scaling", "none"])))
+    assert not none.rope_scaling and ModelConfig.from_path(tmp_path).rope_scaling["rope_type"] == "llama3"
+    # the rope_parameters spelling of newer checkpoints is rewritten as well
+    new = dict(base, rope_parameters=dict(rope_type="llama3", rope_theta=10000.0, factor=8.0, low_freq_factor=1.0,
+                                          high_freq_factor=4.0, original_max_position_embeddings=64))
+    new.pop("rope_theta"), new.pop("rope_scaling")
+    (tmp_path / "config.json").write_text(json.dumps(new))
+    cfg2 = ModelConfig.from_path(tmp_path, ov)
+    assert cfg2.rope_theta == 500000.0 and cfg2.rope_scaling["rope_type"] == "yarn" and cfg2.rope_scaling["factor"] == 4.0
+    assert cli.config_overrides(ap.parse_args(["-m", "x"])) is None
