@@ -242,7 +242,18 @@ def cmd_generate(a):
         sys.stdout.write(det.push(tok))
         sys.stdout.flush()
 
-    sid = llm.engine.add_request(ids, sp, on_token=on_token)
+    mask_fn = None
+    grammar = open(a.grammar_file).read() if getattr(a, "grammar_file", None) else getattr(a, "grammar", None)
+    schema = open(a.json_schema_file).read() if getattr(a, "json_schema_file", None) else getattr(a, "json_schema", None)
+    if grammar or schema or getattr(a, "regex", None):   # reference src/cli/grammar.rs: --grammar / --json-schema
+        from .server.structured import constraint_from_request
+        try:
+            con = constraint_from_request(tk, grammar=grammar, json_schema=json.loads(schema) if schema else None,
+                                          regex=getattr(a, "regex", None))
+        except ValueError as ex:
+            raise SystemExit(f"structured output: {ex}")
+        mask_fn = con.mask
+    sid = llm.engine.add_request(ids, sp, on_token=on_token, mask_fn=mask_fn)
     while llm.engine.has_work():
         llm.engine.step()
     s = llm.engine.seqs[sid]
@@ -574,6 +585,11 @@ def main(argv=None):
     _add_sampling_args(p)
     p.add_argument("-p", "--prompt", default=None)
     p.add_argument("--chat", action="store_true", help="wrap the prompt with the chat template")
+    p.add_argument("--grammar", default=None, help="GBNF grammar constraining the output")
+    p.add_argument("--grammar-file", default=None)
+    p.add_argument("-j", "--json-schema", default=None, help="JSON schema constraining the output ('{}' for any object)")
+    p.add_argument("-jf", "--json-schema-file", default=None)
+    p.add_argument("--regex", default=None, help="regular expression constraining the output")
     p.set_defaults(fn=cmd_generate)
     p = sub.add_parser("run", help="interactive chat")
     _add_model_args(p)

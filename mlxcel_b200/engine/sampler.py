@@ -43,7 +43,11 @@ class Sampler:
             if s.mask_fn is not None:
                 m = s.mask_fn(s)
                 if m is not None:
-                    work[i].masked_fill_(~m.to(work.device), float("-inf"))
+                    # the tokenizer's vocabulary may be shorter than the (padded) logits row: ids the
+                    # matcher does not know are never allowed
+                    n = min(m.numel(), work.shape[1])
+                    work[i, :n].masked_fill_(~m[:n].to(work.device), float("-inf"))
+                    work[i, n:] = float("-inf")
         if any(s.params.needs_history for s in seqs):
             H = max(min(len(s.tokens), s.params.repetition_context_size) for s in seqs
                     if s.params.needs_history)

@@ -364,9 +364,14 @@ def create_app(state: ServerState) -> FastAPI:
         sp = sampling_from_body(body, 16)
         ids = _prompt_ids(body.get("prompt", ""))
         cid, created = "cmpl-" + uuid.uuid4().hex[:24], int(time.time())
+        try:
+            constraint = constraint_from_request(tk, response_format=body.get("response_format"),
+                                                 grammar=body.get("grammar"), json_schema=body.get("json_schema"))
+        except ValueError as e:
+            return _err(400, str(e))
         if body.get("stream"):
             async def gen():
-                async for ev in _generate(state, ids, sp):
+                async for ev in _generate(state, ids, sp, constraint):
                     if ev.kind == "token" and ev.text:
                         yield _sse({"id": cid, "object": "text_completion", "created": created, "model": state.model_id,
                                     "choices": [{"index": 0, "text": ev.text, "finish_reason": None}]})
@@ -380,7 +385,7 @@ def create_app(state: ServerState) -> FastAPI:
                 yield b"data: [DONE]\n\n"
             return StreamingResponse(gen(), media_type="text/event-stream")
         try:
-            text, toks, lps, fin = await _run_text(ids, sp)
+            text, toks, lps, fin = await _run_text(ids, sp, constraint)
         except (RuntimeError, ValueError) as e:
             return _err(400, str(e))
         choice = {"index": 0, "text": text, "finish_reason": _finish_openai(fin.finish_reason, False)}

@@ -64,6 +64,8 @@ class Constraint:
             raise ValueError(f"invalid grammar: {err}")
         self.vocab = self.ll_tok.vocab_size
         self._consumed = 0
+        self._eos = [i for i in (tokenizer.eos_ids() if hasattr(tokenizer, "eos_ids") else [])
+                     if i is not None and 0 <= i < self.vocab]
 
     def mask(self, seq) -> torch.Tensor | None:
         """Boolean allow-mask [V] for the next token of ``seq`` (consumes tokens sampled since)."""
@@ -73,7 +75,13 @@ class Constraint:
             self.matcher.consume_token(seq.output[self._consumed])
             self._consumed += 1
         if self.matcher.is_stopped():
-            return None
+            # the grammar is complete: only an end-of-sequence token may follow, so the request ends
+            # here instead of running on unconstrained
+            if not self._eos:
+                return None
+            m = torch.zeros(self.vocab, dtype=torch.bool)
+            m[self._eos] = True
+            return m
         bits = llt.allocate_token_bitmask(1, self.vocab)
         llt.fill_next_token_bitmask(self.matcher, bits, 0)
         words = bits[0].to(torch.int64) & 0xFFFFFFFF
