@@ -211,3 +211,30 @@ def test_kv_handoff_routes_between_two_servers():
         assert cb.post("/v1/internal/kv/import", content=b"garbage").status_code == 400
     wa.shutdown()
     wb.shutdown()
+
+
+def test_secondary_routes(client):
+    """Routes beside the main completion paths: token counting, stored responses, cache reset, alias
+    paths, fill-in-the-middle on a tokenizer without FIM tokens."""
+    msgs = [{"role": "user", "content": "count me"}]
+    n = client.post("/v1/messages/count_tokens", json={"messages": msgs}).json()["input_tokens"]
+    assert n > len("count me")
+    m = client.post("/v1/responses/input_tokens", json={"input": "count me"}).json()["input_tokens"]
+    assert m > 0
+    r = client.post("/v1/responses", json={"input": "hi", "max_output_tokens": 4, "temperature": 0}).json()
+    got = client.get(f"/v1/responses/{r['id']}")
+    assert got.status_code == 200 and got.json()["id"] == r["id"] and not any(k.startswith("_") for k in got.json())
+    assert client.get("/v1/responses/resp_missing").status_code == 404
+    client.post("/v1/completions", json={"prompt": "x" * 64, "max_tokens": 2, "temperature": 0, "ignore_eos": True})
+    assert client.get("/v1/cache/stats").status_code == 200
+    assert client.post("/v1/cache/reset").json()["dropped_blocks"] >= 0
+    body = {"messages": msgs, "max_tokens": 3, "temperature": 0, "ignore_eos": True}
+    a, b = client.post("/chat/completions", json=body).json(), client.post("/v1/chat/completions", json=body).json()
+    assert a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
+    c = client.post("/completions", json={"prompt": "hello", "n_predict": 3, "temperature": 0, "ignore_eos": True}).json()
+    assert c["tokens_predicted"] == 3
+    assert client.post("/infill", json={"input_prefix": "def f(", "input_suffix": "return x"}).status_code == 501
+    e = client.post("/embeddings", json={"input": ["a", "bb"]})
+    assert e.status_code == 200 and len(e.json()["data"]) == 2
+    rr = client.post("/rerank", json={"query": "a", "documents": ["a", "zzz"]}).json()
+    assert len(rr["results"]) == 2 and client.post("/v1/reranking", json={"query": "a", "documents": ["a"]}).status_code == 200
