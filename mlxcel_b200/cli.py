@@ -269,21 +269,82 @@ def cmd_generate(a):
               f"accepted]", file=sys.stderr)
 
 
+REPL_HELP = """Available commands:
+  /bye, /exit    Exit the chat.
+  /clear         Reset the conversation (clears all prior turns).
+  /system TEXT   Replace the system prompt (clears the conversation).
+  /stats         Engine counters of this session.
+  /?, /help      Show this help.
+  \"\"\" ... \"\"\"    Wrap multiline input as one message."""
+
+
+def repl_turns(lines, system: str | None = None):
+    """The chat REPL's input grammar as a generator over input lines: yields ``("send", messages)`` for
+    every user message (the caller appends the assistant reply to ``messages``), ``("print", text)`` for
+    command output, and stops on /bye, /exit, an empty line or end of input. Slash commands and the
+    triple-quote multiline fence follow the reference's REPL (src/commands/chat.rs:449-500)."""
+    msgs = [{"role": "system", "content": system}] if system else []
+    it = iter(lines)
+    for line in it:
+        text = line.rstrip("\n")
+        if text.strip().startswith('"""'):
+            body = [text.strip()[3:]]
+            while not body[-1].rstrip().endswith('"""'):
+                nxt = next(it, None)
+                if nxt is None:
+                    break
+                body.append(nxt.rstrip("\n"))
+            text = "\n".join(body).rstrip()
+            text = text[:-3] if text.endswith('"""') else text
+            text = text.strip()
+            if not text:
+                continue
+        elif not text.strip():
+            return
+        elif text.startswith("/"):
+            cmd, _, rest = text.strip().partition(" ")
+            if cmd in ("/bye", "/exit"):
+                return
+            if cmd == "/clear":
+                del msgs[1 if msgs and msgs[0]["role"] == "system" else 0:]
+                yield "print", "Conversation cleared."
+            elif cmd == "/system":
+                msgs[:] = [{"role": "system", "content": rest.strip()}] if rest.strip() else []
+                yield "print", "System prompt set; conversation cleared."
+            elif cmd == "/stats":
+                yield "stats", None
+            elif cmd in ("/?", "/help"):
+                yield "print", REPL_HELP
+            else:
+                yield "print", f"Unknown command: {cmd}. Type /? for the list of commands."
+            continue
+        msgs.append({"role": "user", "content": text.strip()})
+        yield "send", msgs
+
+
 def cmd_run(a):
     llm = load_llm(a)
     tk = llm.tokenizer
     from .server.chat_template import render_chat
     from .tokenizer import IncrementalDetokenizer
-    msgs = [{"role": "system", "content": a.system}] if a.system else []
-    print("chat REPL — empty line or /exit to quit", file=sys.stderr)
-    while True:
-        try:
-            line = input("> ")
-        except EOFError:
-            break
-        if not line.strip() or line.strip() == "/exit":
-            break
-        msgs.append({"role": "user", "content": line})
+    print("chat REPL: empty line or /bye to quit, /? for commands", file=sys.stderr)
+
+    def lines():
+        while True:
+            try:
+                yield input("> ")
+            except EOFError:
+                return
+
+    for kind, payload in repl_turns(lines(), a.system):
+        if kind == "print":
+            print(payload)
+            continue
+        if kind == "stats":
+            st = llm.engine.stats
+            print(", ".join(f"{k}={st[k]}" for k in sorted(st) if isinstance(st[k], (int, float)) and st[k]))
+            continue
+        msgs = payload
         ids = tk.encode(render_chat(msgs, getattr(tk, "chat_template", None)))
         sp = _sampling(a)
         sp.stop_token_ids = [i for i in tk.eos_ids() if i is not None]
@@ -299,7 +360,9 @@ def cmd_run(a):
         llm.engine.add_request(ids, sp, on_token=on_token)
         while llm.engine.has_work():
             llm.engine.step()
-        print()
+        tail = det.flush()
+        parts.append(tail)
+        print(tail)
         msgs.append({"role": "assistant", "content": "".join(parts)})
 
 

@@ -201,3 +201,25 @@ def test_rope_and_kv_overrides_change_the_built_config(tmp_path):
     cfg2 = ModelConfig.from_path(tmp_path, ov)
     assert cfg2.rope_theta == 500000.0 and cfg2.rope_scaling["rope_type"] == "yarn" and cfg2.rope_scaling["factor"] == 4.0
     assert cli.config_overrides(ap.parse_args(["-m", "x"])) is None
+
+
+def test_repl_grammar_slash_commands_and_multiline():
+    from mlxcel_b200.cli import repl_turns
+
+    lines = ["hello", "/help", "/nope", '"""first', "second", 'third"""', "/clear", "again", "/system be brief", "x", "/bye",
+             "never read"]
+    seen = []
+    for kind, payload in repl_turns(lines, system="sys"):
+        if kind == "send":
+            seen.append(("send", [dict(m) for m in payload]))
+            payload.append({"role": "assistant", "content": "ok"})
+        else:
+            seen.append((kind, payload))
+    sends = [p for k, p in seen if k == "send"]
+    assert [m["content"] for m in sends[0]] == ["sys", "hello"]
+    assert sends[1][-1]["content"] == "first\nsecond\nthird" and len(sends[1]) == 4      # sys, hello, ok, multiline
+    assert [m["content"] for m in sends[2]] == ["sys", "again"]                          # /clear kept the system prompt
+    assert [m["content"] for m in sends[3]] == ["be brief", "x"] and len(sends) == 4
+    prints = [p for k, p in seen if k == "print"]
+    assert prints[0].startswith("Available commands") and "Unknown command: /nope" in prints[1]
+    assert list(repl_turns(["", "ignored"])) == []
