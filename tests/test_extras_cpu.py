@@ -223,3 +223,40 @@ def test_repl_grammar_slash_commands_and_multiline():
     prints = [p for k, p in seen if k == "print"]
     assert prints[0].startswith("Available commands") and "Unknown command: /nope" in prints[1]
     assert list(repl_turns(["", "ignored"])) == []
+
+
+def test_memory_estimate_of_recurrent_models_matches_the_built_model():
+    """State-space / hybrid presets: estimated parameters within 1 % of the tensors the model holds, the
+    per-sequence recurrent state equal to the executor's state slots, KV only for attention blocks."""
+    import torch
+
+    from mlxcel_b200.config import preset
+    from mlxcel_b200.models.hybrid import HybridModel, random_hybrid_weights
+    from mlxcel_b200.models.mamba1 import Mamba1Model, random_mamba1_weights
+    from mlxcel_b200.models.mamba2 import Mamba2Model, random_mamba2_weights
+    from mlxcel_b200.utils.memory import estimate_memory
+
+    def count(o, seen):
+        if isinstance(o, torch.Tensor):
+            if o.data_ptr() in seen:
+                return 0
+            seen.add(o.data_ptr())
+            return o.numel()
+        if isinstance(o, (list, tuple)):
+            return sum(count(x, seen) for x in o)
+        return sum(count(v, seen) for v in vars(o).values()) if hasattr(o, "__dict__") else 0
+
+    for name, make, cls in (("tiny-mamba2", random_mamba2_weights, Mamba2Model), ("tiny-mamba", random_mamba1_weights, Mamba1Model),
+                            ("tiny-nemotron-h", random_hybrid_weights, HybridModel)):
+        cfg = preset(name)
+        w = make(cfg, dtype=torch.float32)
+        est = estimate_memory(cfg, ctx=256, parallel=2)
+        real = count(w, set())
+        assert abs(est["parameters"] - real) < 0.01 * real, (name, est["parameters"], real)
+        m = cls(cfg, w, max_seqs=4)
+        ssm = getattr(m, "ssm", m)
+        per_seq = 4 * (ssm.conv_state[:, 0].numel() + ssm.ssm_state[:, 0].numel())
+        assert est["recurrent_state_bytes_per_seq"] == per_seq, name
+        assert est["recurrent_state_bytes"] == 2 * 2 * per_seq
+        assert (est["kv_bytes_per_token"] > 0) == (name == "tiny-nemotron-h")
+    assert estimate_memory(preset("tiny-llama"))["recurrent_state_bytes"] == 0
