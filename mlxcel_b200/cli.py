@@ -542,6 +542,26 @@ def cmd_serve(a):
 
     from .server.app import ServerState, create_app
     from .server.worker import ModelWorker
+    if not _encoder_checkpoint(a.model):        # preflight: does model + KV pool + activations fit (src/commands/serve.rs)
+        from .config import ModelConfig, preset
+        from .utils.memory import estimate_memory
+        cfg = (preset(a.model.split(":", 1)[1]) if a.model.startswith("preset:")
+               else ModelConfig.from_path(a.model, config_overrides(a)))
+        est = estimate_memory(cfg, ctx=a.ctx_size, parallel=a.parallel, kv_bits=a.kv_bits or 16, tp=a.tp,
+                              max_batch_tokens=a.max_batch_tokens, block_size=a.block_size)
+        if a.estimate_memory:
+            print(json.dumps(est, indent=1))
+            return
+        if not est["fits_b200"] and not a.no_preflight:
+            # the KV pool is paged and shared: what must fit is the weights plus ONE full-context sequence
+            one = estimate_memory(cfg, ctx=a.ctx_size, parallel=1, kv_bits=a.kv_bits or 16, tp=a.tp,
+                                  max_batch_tokens=a.max_batch_tokens, block_size=a.block_size)
+            if not one["fits_b200"]:
+                raise SystemExit(f"preflight: {one['total_gib']} GiB per GPU for the weights and one {a.ctx_size}-token "
+                                 f"sequence does not fit; lower --ctx-size, raise --tp, quantize the KV cache "
+                                 f"(--kv-bits 8), or pass --no-preflight")
+            print(f"preflight: {a.parallel} sequences of {a.ctx_size} tokens would need {est['total_gib']} GiB; the paged KV "
+                  f"pool takes what is free, long requests will queue", file=sys.stderr)
     if _encoder_checkpoint(a.model):            # encoder checkpoints get the embeddings-only server
         import torch
 
@@ -673,6 +693,9 @@ def main(argv=None):
     p.add_argument("--debug-trace", "--debug-pp-trace", dest="debug_trace", default=None, metavar="FILE",
                    help="write a Chrome trace of engine steps and pipeline stages (same as MLXCEL_B200_TRACE)")
     p.add_argument("--surgery", default=None, metavar="YAML", help="load-time weight edits (see loading/surgery.py)")
+    p.add_argument("--estimate-memory", action="store_true",
+                   help="print the memory estimate for this model and these options, then exit")
+    p.add_argument("--no-preflight", action="store_true", help="start even when the estimate does not fit the GPU")
     p.add_argument("--ssl-cert-file", default=None)
     p.add_argument("--ssl-key-file", default=None)
     p.add_argument("-v", "--verbose", action="store_true")

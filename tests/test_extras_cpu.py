@@ -260,3 +260,17 @@ def test_memory_estimate_of_recurrent_models_matches_the_built_model():
         assert est["recurrent_state_bytes"] == 2 * 2 * per_seq
         assert (est["kv_bytes_per_token"] > 0) == (name == "tiny-nemotron-h")
     assert estimate_memory(preset("tiny-llama"))["recurrent_state_bytes"] == 0
+
+
+def test_serve_preflight(capsys):
+    import json
+
+    import pytest
+
+    from mlxcel_b200 import cli
+
+    cli.main(["serve", "-m", "preset:llama-3.1-8b", "--estimate-memory", "-c", "8192", "--parallel", "8"])
+    est = json.loads(capsys.readouterr().out)
+    assert est["fits_b200"] and est["kv_pool_blocks"] == 8 * 512
+    with pytest.raises(SystemExit, match="does not fit"):
+        cli.main(["serve", "-m", "preset:llama-3.1-8b", "-c", "4000000", "--parallel", "1"])
