@@ -537,6 +537,23 @@ def cmd_split_mtp(a):
           f"{res['bytes'] / 1e6:.1f} MB, block size {res['block_size']}; pass it as --draft-model")
 
 
+def cmd_perplexity(a):
+    """Windowed perplexity of a text file (reference examples/perplexity.rs)."""
+    from .engine.scoring import perplexity
+    llm = load_llm(a)
+    text = open(a.file, encoding="utf-8").read() if a.file else sys.stdin.read()
+    ids = llm.tokenizer.encode(text, add_special_tokens=True)
+    if len(ids) < 2:
+        raise SystemExit("perplexity: the text has fewer than two tokens")
+    window = min(a.window, a.ctx_size)
+    res = perplexity(llm.model, llm.cfg, ids, window, a.stride, llm.engine.ecfg.block_size,
+                     progress=None if a.json else (lambda d, t: print(f"\r{d}/{t} tokens", end="", file=sys.stderr)))
+    if a.json:
+        print(json.dumps(res))
+    else:
+        print(f"\nperplexity {res['perplexity']:.4f} over {res['tokens']} tokens (window {res['window']}, stride {res['stride']})")
+
+
 def cmd_serve(a):
     import uvicorn
 
@@ -770,6 +787,13 @@ def main(argv=None):
     p.add_argument("--force", action="store_true")
     p.add_argument("--json", action="store_true")
     p.set_defaults(fn=cmd_split_mtp)
+    p = sub.add_parser("perplexity", help="windowed perplexity of a text file")
+    _add_model_args(p)
+    p.add_argument("-f", "--file", default=None, help="text file (stdin when absent)")
+    p.add_argument("--window", type=int, default=2048)
+    p.add_argument("--stride", type=int, default=None)
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_perplexity)
     p = sub.add_parser("inspect", help="memory estimate")
     _add_model_args(p)
     p.set_defaults(fn=cmd_inspect)

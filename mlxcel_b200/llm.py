@@ -101,6 +101,12 @@ class LLM:
         tok = load_tokenizer(path)
         return LLM(cfg, w, engine_config, comm=comm, tokenizer=tok, fold_norms=True)
 
+    # ------------------------------------------------------------------ scoring
+    def loglikelihoods(self, token_ids: list[int]):
+        """``log p(token[t] | token[:t])`` for t >= 1 (fp32 CPU tensor), without generating."""
+        from .engine.scoring import sequence_logprobs
+        return sequence_logprobs(self.model, self.cfg, token_ids, self.engine.ecfg.block_size)
+
     # ------------------------------------------------------------------ generation
     def generate(self, prompts=None, sampling_params: SamplingParams | list[SamplingParams] | None = None,
                  prompt_token_ids: list[list[int]] | None = None) -> list[Sequence]:
