@@ -386,7 +386,10 @@ def cmd_embed(a):
         from .models.encoder import load_encoder
         from .tokenizer import load_tokenizer
         enc, tok = load_encoder(a.model, device=dev), load_tokenizer(a.model)
-        vecs = [enc.embed(tok.encode(t, add_special_tokens=True) or [0], a.pooling or "mean", False) for t in texts]
+        vecs = [enc.embed(tok.encode(t, add_special_tokens=True) or [0], a.pooling or enc.default_pooling, False)
+                for t in texts]
+        if a.embd_normalize == "auto":
+            a.embd_normalize = "l2" if enc.default_normalize else "none"
     else:
         from types import SimpleNamespace
 
@@ -397,7 +400,7 @@ def cmd_embed(a):
     vecs = torch.stack([v.float().cpu() for v in vecs])
     if a.dimensions:
         vecs = vecs[:, : a.dimensions]
-    if a.embd_normalize != "none":
+    if a.embd_normalize in ("l2", "auto"):
         vecs = vecs / vecs.norm(dim=-1, keepdim=True).clamp_min(1e-12)
     unit = vecs / vecs.norm(dim=-1, keepdim=True).clamp_min(1e-12)
     sim = (unit @ unit.T).tolist() if len(texts) > 1 else None
@@ -735,7 +738,8 @@ def main(argv=None):
     p.add_argument("-p", "--prompt", action="append")
     p.add_argument("--instruction", default=None)
     p.add_argument("--pooling", choices=["mean", "cls", "last"], default=None)
-    p.add_argument("--embd-normalize", choices=["l2", "none"], default="l2")
+    p.add_argument("--embd-normalize", choices=["auto", "l2", "none"], default="auto",
+                   help="auto: what the checkpoint's modules.json declares (l2 when it says nothing)")
     p.add_argument("--dimensions", type=int, default=None)
     p.add_argument("--json", action="store_true")
     p.set_defaults(fn=cmd_embed)

@@ -109,7 +109,7 @@ class BertEncoder:
 
     def embed(self, ids: list[int], pooling: str = "mean", normalize: bool = True) -> torch.Tensor:
         h = self.hidden_states(ids).float()
-        v = h[0] if pooling == "cls" else h.mean(0)
+        v = h[0] if pooling == "cls" else h[-1] if pooling == "last" else h.mean(0)
         return v / v.norm().clamp_min(1e-12) if normalize else v
 
     @torch.inference_mode()
@@ -232,4 +232,31 @@ def load_encoder(path, dtype=torch.bfloat16, device="cpu"):
     cls = {"bert": BertEncoder, "modernbert": ModernBertEncoder}.get(mt)
     if cls is None:
         raise ValueError(f"unsupported encoder model_type {mt!r}")
-    return cls.from_pretrained(path, dtype, device)
+    enc = cls.from_pretrained(path, dtype, device)
+    enc.default_pooling, enc.default_normalize = sentence_transformers_defaults(path)
+    return enc
+
+
+def sentence_transformers_defaults(path) -> tuple[str, bool]:
+    """Pooling and normalisation a sentence-transformers checkpoint declares: ``1_Pooling/config.json``
+    (``pooling_mode_cls_token`` / ``pooling_mode_mean_tokens`` / ``pooling_mode_lasttoken``) and a
+    ``Normalize`` entry in ``modules.json``. Without those files: mean pooling, normalised (reference
+    src/embeddings/, pooling read the same way)."""
+    root = Path(path)
+    pooling, normalize = "mean", True
+    pc = root / "1_Pooling" / "config.json"
+    if pc.is_file():
+        c = json.loads(pc.read_text())
+        pooling = ("cls" if c.get("pooling_mode_cls_token") else "last" if c.get("pooling_mode_lasttoken") else "mean")
+    mj = root / "modules.json"
+    if mj.is_file():
+        normalize = any("Normalize" in str(m.get("type", "")) for m in json.loads(mj.read_text()))
+    return pooling, normalize
+
+
+def maxsim(query_vectors: torch.Tensor, doc_vectors: torch.Tensor) -> float:
+    """Late-interaction (ColBERT) relevance: for every query token the best cosine match among the document
+    tokens, summed over the query tokens. Inputs are per-token vectors [Tq, H] and [Td, H]."""
+    q = F.normalize(query_vectors.float(), dim=-1)
+    d = F.normalize(doc_vectors.float(), dim=-1)
+    return float((q @ d.T).max(dim=1).values.sum())

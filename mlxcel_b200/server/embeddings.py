@@ -129,7 +129,7 @@ def create_embedding_app(encoder, tokenizer, model_id: str, api_keys: set | None
     async def embeddings(body: dict):
         inp = body.get("input", body.get("content", ""))
         texts = [inp] if isinstance(inp, str) else list(inp)
-        vecs, ntok = run(texts, body.get("pooling", "mean"))
+        vecs, ntok = run(texts, body.get("pooling") or getattr(encoder, "default_pooling", "mean"))
         return {"object": "list", "model": model_id,
                 "data": [{"object": "embedding", "index": i, "embedding": v} for i, v in enumerate(vecs)],
                 "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}

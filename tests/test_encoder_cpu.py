@@ -166,3 +166,30 @@ def test_token_classification_head_and_tagging():
     assert isinstance(res["redacted"], str) and all(s["end_token"] > s["start_token"] for s in res["spans"])
     with pytest.raises(ValueError):
         enc.sequence_logits(ids.tolist())
+
+
+def test_sentence_transformers_pooling_defaults_and_maxsim(tmp_path, capsys):
+    import json
+    import shutil
+
+    from mlxcel_b200 import cli
+    from mlxcel_b200.models.encoder import load_encoder, maxsim
+
+    _, d = _tiny_bert()
+    st = tmp_path / "st"
+    shutil.copytree(d, st)
+    (st / "1_Pooling").mkdir()
+    (st / "1_Pooling" / "config.json").write_text(json.dumps(dict(pooling_mode_cls_token=True, pooling_mode_mean_tokens=False)))
+    (st / "modules.json").write_text(json.dumps([dict(idx=0, type="sentence_transformers.models.Transformer"),
+                                                 dict(idx=1, type="sentence_transformers.models.Pooling")]))
+    enc = load_encoder(str(st), dtype=torch.float32)
+    assert (enc.default_pooling, enc.default_normalize) == ("cls", False)
+    plain = load_encoder(d, dtype=torch.float32)
+    assert (plain.default_pooling, plain.default_normalize) == ("mean", True)
+    cli.main(["embed", "-m", str(st), "--device", "cpu", "-p", "hello", "--json"])
+    v = torch.tensor(json.loads(capsys.readouterr().out.strip().splitlines()[-1])["embeddings"][0])
+    ids = ByteTokenizer().encode("hello", add_special_tokens=True)
+    want = load_encoder(str(st)).hidden_states(ids)[0].float()           # [CLS] state, not normalised
+    assert torch.allclose(v, want, atol=1e-5) and abs(v.norm().item() - 1.0) > 1e-3
+    q, doc = enc.hidden_states([5, 6, 7]), enc.hidden_states([5, 6, 7, 8, 9])
+    assert abs(maxsim(q, q) - 3.0) < 1e-4 and maxsim(q, doc) <= 3.0 + 1e-5
