@@ -429,9 +429,20 @@ def _load_encoder_and_tokenizer(a):
 
 def cmd_rerank(a):
     """Offline counterpart of ``/v1/rerank`` (reference src/main.rs:281, ``mlxcel rerank``)."""
-    from .server.embeddings import rerank_scores
-    enc, tok = _load_encoder_and_tokenizer(a)
-    scores = rerank_scores(enc, tok, a.query, a.document)
+    if _encoder_checkpoint(a.model):
+        from .server.embeddings import rerank_scores
+        enc, tok = _load_encoder_and_tokenizer(a)
+        scores = rerank_scores(enc, tok, a.query, a.document)
+    else:                                          # a decoder LM: the generative yes/no reranker
+        from argparse import Namespace
+
+        from .engine.scoring import generative_rerank
+        ap = argparse.ArgumentParser()
+        _add_model_args(ap)
+        full = ap.parse_args(["-m", a.model] + (["--device", a.device] if a.device else []))
+        llm = load_llm(Namespace(**vars(full)))
+        scores = generative_rerank(llm.model, llm.cfg, llm.tokenizer, a.query, a.document, a.instruction,
+                                   llm.engine.ecfg.block_size, llm.engine.ecfg.max_model_len - 1)
     order = sorted(range(len(scores)), key=lambda i: -scores[i])
     if a.json:
         print(json.dumps(dict(results=[dict(index=i, relevance_score=scores[i]) for i in order])))
@@ -748,6 +759,7 @@ def main(argv=None):
     p.add_argument("--device", default=None)
     p.add_argument("-q", "--query", required=True)
     p.add_argument("-d", "--document", action="append", required=True)
+    p.add_argument("--instruction", default=None, help="task instruction of a generative reranker")
     p.add_argument("--json", action="store_true")
     p.set_defaults(fn=cmd_rerank)
     p = sub.add_parser("tag", help="tag and redact entities with a token-classification checkpoint")

@@ -295,13 +295,24 @@ def create_app(state: ServerState) -> FastAPI:
     @app.post("/v1/reranking")
     @app.post("/rerank")
     async def rerank(body: dict):
-        """Embedding reranker: cosine similarity between the query and every document (the
-        reference's cross-encoder / generative rerankers need their own checkpoints)."""
+        """Reranking with a decoder LM: cosine similarity between last-token embeddings of the query and
+        every document, or with ``"mode": "generative"`` the probability of "yes" after the yes/no
+        judgement prompt (Qwen3-Reranker style). Cross-encoder checkpoints are served by the encoder app."""
         from .embeddings import embed_texts
         query, docs = body.get("query", ""), list(body.get("documents", []))
         docs_txt = [d if isinstance(d, str) else d.get("text", "") for d in docs]
         if not query or not docs_txt:
             return _err(400, "query and documents are required")
+        if body.get("mode") == "generative":       # yes/no judgement prompt instead of embedding cosine
+            from ..engine.scoring import generative_rerank
+            eng = state.worker.engine
+            scores = await asyncio.get_running_loop().run_in_executor(
+                None, lambda: generative_rerank(eng.model, eng.cfg, tk, query, docs_txt, body.get("instruction"),
+                                                eng.ecfg.block_size, eng.ecfg.max_model_len - 1))
+            order = sorted(range(len(scores)), key=lambda i: -scores[i])[: int(body.get("top_n") or len(scores))]
+            return {"model": state.model_id, "object": "list", "results": [
+                {"index": i, "relevance_score": scores[i],
+                 **({"document": {"text": docs_txt[i]}} if body.get("return_documents") else {})} for i in order]}
         vecs, ntok = await asyncio.get_running_loop().run_in_executor(None, embed_texts, state, [query, *docs_txt])
         qv = vecs[0]
         scores = [sum(a * b for a, b in zip(qv, v)) for v in vecs[1:]]

@@ -61,3 +61,37 @@ def test_perplexity_cli(capsys, tmp_path):
     cli.main(["perplexity", "-m", "preset:tiny-llama", "--device", "cpu", "-f", str(f), "--window", "64", "--json"])
     res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert res["tokens"] > 200 and res["perplexity"] > 1.0 and res["window"] == 64
+
+
+def test_generative_rerank_scores_and_route(capsys):
+    """The yes/no reranker: scores are p(yes) of the judgement prompt (checked against a direct forward),
+    through the function, the CLI verb on a decoder preset and the server route."""
+    from fastapi.testclient import TestClient
+
+    from mlxcel_b200.engine.scoring import generative_rerank, prefill_hidden, rerank_prompt
+    from mlxcel_b200.server.app import ServerState, create_app
+    from mlxcel_b200.server.worker import ModelWorker
+    from mlxcel_b200.tokenizer import ByteTokenizer
+
+    llm = LLM.from_preset("tiny-llama", device="cpu", dtype=torch.float32,
+                          engine_config=EngineConfig(num_blocks=128, block_size=16, max_batch=2, max_model_len=1024))
+    tk = ByteTokenizer(llm.cfg.vocab_size)
+    docs = ["pandas are bears", "berlin is in germany"]
+    scores = generative_rerank(llm.model, llm.cfg, tk, "what is a panda?", docs)
+    assert len(scores) == 2 and all(0.0 < s < 1.0 for s in scores)
+    ids = tk.encode(rerank_prompt("what is a panda?", docs[0]))
+    lg = llm.model.logits(prefill_hidden(llm.model, llm.cfg, ids), torch.tensor([len(ids) - 1])).float()[0]
+    y, n = tk.encode("yes")[0], tk.encode("no")[0]
+    assert abs(scores[0] - float(torch.sigmoid(lg[y] - lg[n]))) < 1e-5
+    worker = ModelWorker(llm.engine, tk, "m")
+    try:
+        c = TestClient(create_app(ServerState(worker, tk, "m")))
+        r = c.post("/v1/rerank", json=dict(query="what is a panda?", documents=docs, mode="generative", top_n=1)).json()
+        best = max(range(2), key=lambda i: scores[i])
+        assert len(r["results"]) == 1 and r["results"][0]["index"] == best
+        assert abs(r["results"][0]["relevance_score"] - scores[best]) < 1e-5
+    finally:
+        worker.shutdown()
+    cli.main(["rerank", "-m", "preset:tiny-llama", "--device", "cpu", "-q", "q", "-d", "a", "-d", "b", "--json"])
+    res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["results"]
+    assert sorted(r["index"] for r in res) == [0, 1]
