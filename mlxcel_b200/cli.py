@@ -457,7 +457,7 @@ def cmd_tag(a):
     from .server.embeddings import tag_text
     enc, tok = _load_encoder_and_tokenizer(a)
     keep = {k.strip() for k in (a.keep or "").split(",") if k.strip()}
-    res = tag_text(enc, tok, a.text, keep, a.replacement)
+    res = tag_text(enc, tok, a.text, keep, a.replacement, a.argmax)
     if a.json:
         print(json.dumps(res))
         return
@@ -767,6 +767,7 @@ def main(argv=None):
     p.add_argument("--device", default=None)
     p.add_argument("--keep", default=None, help="comma-separated entity names left in the redacted copy")
     p.add_argument("--replacement", default=None)
+    p.add_argument("--argmax", action="store_true", help="per-token argmax instead of the BIO-constrained Viterbi path")
     p.add_argument("--json", action="store_true")
     p.add_argument("text")
     p.set_defaults(fn=cmd_tag)

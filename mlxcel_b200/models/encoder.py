@@ -145,6 +145,41 @@ def bio_spans(labels: list[str]) -> list[tuple[int, int, str]]:
     return out
 
 
+def bio_viterbi(log_probs: torch.Tensor, labels: list[str]) -> list[int]:
+    """Best label path under the BIO / BIOES grammar: ``I-X`` / ``E-X`` may only follow ``B-X`` or ``I-X``
+    of the same entity, ``B-X`` / ``I-X`` of a BIOES scheme may not be followed by ``O`` when the scheme
+    has ``E-`` tags, and a path may not start inside an entity. ``log_probs`` is [T, num_labels]
+    (reference src/token_classification/, viterbi decoding; ``--argmax`` turns it off)."""
+    T, L = log_probs.shape
+    parts = [lab.partition("-") for lab in labels]
+    tag, ent = [p[0] if p[1] else "O" for p in parts], [p[2] for p in parts]
+    bioes = any(t == "E" for t in tag)
+    neg = float("-inf")
+    trans = torch.zeros(L, L)
+    for a in range(L):
+        for b in range(L):
+            inside_a = tag[a] in ("B", "I")
+            if tag[b] in ("I", "E") and not (inside_a and ent[a] == ent[b]):
+                trans[a, b] = neg                    # continuing an entity that is not open
+            elif bioes and inside_a and not (tag[b] in ("I", "E") and ent[a] == ent[b]):
+                trans[a, b] = neg                    # BIOES: an open entity must be closed by its E tag
+    start = torch.tensor([neg if t in ("I", "E") else 0.0 for t in tag])
+    lp = log_probs.float().cpu()
+    score = start + lp[0]
+    back = []
+    for t in range(1, T):
+        cand = score[:, None] + trans                # [from, to]
+        best, arg = cand.max(dim=0)
+        back.append(arg)
+        score = best + lp[t]
+    if bioes:                                        # a path may not end inside an entity
+        score = score + torch.tensor([neg if t in ("B", "I") else 0.0 for t in tag])
+    path = [int(score.argmax())]
+    for arg in reversed(back):
+        path.append(int(arg[path[-1]]))
+    return path[::-1]
+
+
 class ModernBertEncoder:
     """ModernBERT: pre-norm blocks with bias-free LayerNorm, fused Wqkv, rotary embedding (one base for
     the global layers, another for the local ones), bidirectional attention that is windowed

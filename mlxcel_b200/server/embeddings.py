@@ -66,7 +66,8 @@ def rerank_scores(encoder, tokenizer, query: str, docs: list[str]) -> list[float
     return [float(q @ encoder.embed(tokenizer.encode(d, add_special_tokens=True) or [0])) for d in docs]
 
 
-def tag_text(encoder, tokenizer, text: str, keep: set[str] | None = None, replacement: str | None = None) -> dict:
+def tag_text(encoder, tokenizer, text: str, keep: set[str] | None = None, replacement: str | None = None,
+             argmax: bool = False) -> dict:
     """Token classification over one text: BIO spans with their decoded surface text and a redacted copy
     (every span not in ``keep`` replaced by ``replacement`` or ``[ENTITY]``). Reference src/main.rs:281
     (``mlxcel tag``)."""
@@ -75,7 +76,13 @@ def tag_text(encoder, tokenizer, text: str, keep: set[str] | None = None, replac
     ids = (tokenizer.encode(text, add_special_tokens=True) or [0])[: encoder.max_len]
     lg = encoder.token_logits(ids)
     prob = torch.softmax(lg, -1)
-    lab = [encoder.id2label.get(int(i), "O") for i in lg.argmax(-1)]
+    names = [encoder.id2label.get(i, "O") for i in range(lg.shape[1])]
+    if argmax:
+        path = lg.argmax(-1).tolist()
+    else:                                            # best path that is a valid BIO / BIOES sequence
+        from ..models.encoder import bio_viterbi
+        path = bio_viterbi(torch.log_softmax(lg, -1), names)
+    lab = [names[i] for i in path]
     spans, pieces, last = [], [], 0
     for s, e, ent in bio_spans(lab):
         surface = tokenizer.decode(ids[s:e], skip_special_tokens=True).strip()
@@ -148,7 +155,7 @@ def create_embedding_app(encoder, tokenizer, model_id: str, api_keys: set | None
         if not getattr(encoder, "token_head", False):
             return JSONResponse({"error": {"message": "model has no token-classification head"}}, 400)
         return tag_text(encoder, tokenizer, body.get("text", body.get("input", "")), set(body.get("keep") or []),
-                        body.get("replacement"))
+                        body.get("replacement"), bool(body.get("argmax", False)))
 
     @app.post("/embedding")
     async def embedding(body: dict):

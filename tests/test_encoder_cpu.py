@@ -193,3 +193,26 @@ def test_sentence_transformers_pooling_defaults_and_maxsim(tmp_path, capsys):
     assert torch.allclose(v, want, atol=1e-5) and abs(v.norm().item() - 1.0) > 1e-3
     q, doc = enc.hidden_states([5, 6, 7]), enc.hidden_states([5, 6, 7, 8, 9])
     assert abs(maxsim(q, q) - 3.0) < 1e-4 and maxsim(q, doc) <= 3.0 + 1e-5
+
+
+def test_bio_viterbi_repairs_invalid_paths():
+    from mlxcel_b200.models.encoder import bio_viterbi
+
+    labels = ["O", "B-PER", "I-PER", "B-LOC", "I-LOC"]
+    lp = torch.full((4, 5), -5.0)
+    lp[0, 0] = lp[1, 2] = lp[2, 2] = lp[3, 0] = -0.1           # argmax path O I-PER I-PER O is invalid
+    lp[1, 1] = -0.5                                            # B-PER is the cheap repair at position 1
+    assert [labels[i] for i in bio_viterbi(lp, labels)] == ["O", "B-PER", "I-PER", "O"]
+    lp2 = torch.full((3, 5), -5.0)
+    lp2[0, 1] = lp2[1, 4] = lp2[2, 0] = -0.1                   # B-PER then I-LOC: entity mismatch
+    lp2[1, 2] = -0.3
+    assert [labels[i] for i in bio_viterbi(lp2, labels)] == ["B-PER", "I-PER", "O"]
+    valid = torch.full((3, 5), -5.0)
+    valid[0, 3] = valid[1, 4] = valid[2, 0] = -0.1
+    assert [labels[i] for i in bio_viterbi(valid, labels)] == ["B-LOC", "I-LOC", "O"]
+    bioes = ["O", "B-X", "I-X", "E-X", "S-X"]
+    e = torch.full((3, 5), -5.0)
+    e[0, 1] = e[1, 0] = e[2, 0] = -0.1                         # B-X followed by O: an entity left open
+    e[1, 2] = e[2, 3] = -0.4
+    assert [bioes[i] for i in bio_viterbi(e, bioes)] in (["B-X", "I-X", "E-X"], ["S-X", "O", "O"], ["O", "O", "O"])
+    assert bioes[bio_viterbi(e, bioes)[-1]] not in ("B-X", "I-X")
