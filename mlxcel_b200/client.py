@@ -138,3 +138,97 @@ class ManagedServer:
 
     def __exit__(self, *exc) -> None:
         self.stop()
+
+
+class AsyncClient:
+    """asyncio counterpart of :class:`Client` over aiohttp (reference python/src/mlxcel: the async client)::
+
+        async with AsyncClient("http://127.0.0.1:8080") as c:
+            async for piece in c.chat_stream([{"role": "user", "content": "hi"}], max_tokens=32):
+                print(piece, end="")
+    """
+
+    def __init__(self, base_url: str = "http://127.0.0.1:8080", api_key: str | None = None, timeout: float = 600.0):
+        self.base = base_url.rstrip("/")
+        self.timeout = timeout
+        self.headers = {"Authorization": f"Bearer {api_key}"} if api_key else {}
+        self._session = None
+
+    async def __aenter__(self) -> "AsyncClient":
+        import aiohttp
+        self._session = aiohttp.ClientSession(headers=self.headers, timeout=aiohttp.ClientTimeout(total=self.timeout))
+        return self
+
+    async def __aexit__(self, *exc) -> None:
+        await self.close()
+
+    async def close(self) -> None:
+        if self._session is not None:
+            await self._session.close()
+            self._session = None
+
+    def _http(self):
+        if self._session is None:
+            raise MlxcelError("use 'async with AsyncClient(...)' (no open session)")
+        return self._session
+
+    async def _post(self, path: str, body: dict) -> dict:
+        async with self._http().post(self.base + path, json=body) as r:
+            if r.status >= 400:
+                raise MlxcelError(f"{path}: HTTP {r.status}: {(await r.text())[:500]}")
+            return await r.json()
+
+    async def _get(self, path: str) -> dict:
+        async with self._http().get(self.base + path) as r:
+            if r.status >= 400:
+                raise MlxcelError(f"{path}: HTTP {r.status}: {(await r.text())[:500]}")
+            return await r.json()
+
+    async def health(self) -> bool:
+        try:
+            return (await self._get("/health")).get("status") == "ok"
+        except Exception:
+            return False
+
+    async def models(self) -> list[str]:
+        return [m["id"] for m in (await self._get("/v1/models"))["data"]]
+
+    async def chat(self, messages: list[dict], **params) -> str:
+        r = await self._post("/v1/chat/completions", {"messages": messages, **params})
+        return r["choices"][0]["message"]["content"] or ""
+
+    async def chat_stream(self, messages: list[dict], **params):
+        body = {"messages": messages, "stream": True, **params}
+        async with self._http().post(self.base + "/v1/chat/completions", json=body) as r:
+            if r.status >= 400:
+                raise MlxcelError(f"/v1/chat/completions: HTTP {r.status}: {(await r.text())[:500]}")
+            async for raw in r.content:
+                line = raw.decode().strip()
+                if not line.startswith("data:"):
+                    continue
+                data = line[5:].strip()
+                if data == "[DONE]":
+                    return
+                ev = json.loads(data)
+                if "error" in ev:
+                    raise MlxcelError(str(ev["error"]))
+                for ch in ev.get("choices") or []:
+                    piece = (ch.get("delta") or {}).get("content")
+                    if piece:
+                        yield piece
+
+    async def complete(self, prompt: str, **params) -> str:
+        return (await self._post("/v1/completions", {"prompt": prompt, **params}))["choices"][0]["text"]
+
+    async def embed(self, texts: list[str] | str) -> list[list[float]]:
+        r = await self._post("/v1/embeddings", {"input": texts})
+        return [d["embedding"] for d in r["data"]]
+
+    async def rerank(self, query: str, documents: list[str], top_n: int | None = None, **params) -> list[dict]:
+        body = {"query": query, "documents": documents, **params}
+        if top_n:
+            body["top_n"] = top_n
+        return (await self._post("/v1/rerank", body))["results"]
+
+    async def tokenize(self, text: str) -> list[int]:
+        return (await self._post("/tokenize", {"content": text}))["tokens"]
