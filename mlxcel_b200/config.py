@@ -233,7 +233,15 @@ class ModelConfig:
         c.attn_logit_softcap = float(g("attn_logit_softcapping") or 0.0)
         c.final_logit_softcap = float(g("final_logit_softcapping") or 0.0)
         c.query_pre_attn_scalar = g("query_pre_attn_scalar")
-        c.quantization = QuantConfig.from_dict(g("quantization") or g("quantization_config"))
+        qc = g("quantization") or g("quantization_config")
+        if isinstance(g("quantization_config"), dict) and g("quantization_config").get("quant_method"):
+            qc = g("quantization_config")
+        if isinstance(qc, dict) and qc.get("quant_method") in ("fp8", "compressed-tensors", "fbgemm_fp8", "modelopt"):
+            # FP8 checkpoints: stored as float8 + scales, widened to bf16 at load (no packed groups)
+            if qc.get("weight_block_size"):
+                c.extra["fp8_block_size"] = tuple(int(x) for x in qc["weight_block_size"])
+            qc = None
+        c.quantization = QuantConfig.from_dict(qc)
         c.dtype = str(g("torch_dtype", g("dtype", "bfloat16")))
         fam(c, raw)
         if c.is_moe and not c.moe_intermediate_size:

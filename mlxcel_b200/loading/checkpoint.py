@@ -167,7 +167,26 @@ class _Getter:
             if qt.mode == "affine":
                 qt.scales, qt.biases = qt.scales.to(self.dtype), qt.biases.to(self.dtype)
             return qt
+        if w.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+            return self._dequant_fp8(base, w)
         return w.to(self.dtype)
+
+    def _dequant_fp8(self, base: str, w: torch.Tensor) -> torch.Tensor:
+        """FP8 checkpoints are widened at load (reference src/models/fp8_block.rs, fp8_ct.rs): block-scaled
+        weights carry ``weight_scale_inv`` with one fp32 factor per ``weight_block_size`` tile (DeepSeek-V3
+        style, 128 x 128 unless the config says otherwise); compressed-tensors style weights carry
+        ``weight_scale`` per tensor or per output channel. Either way ``w = fp8 * scale``."""
+        wf = w.float()
+        if self.src.has(base + ".weight_scale_inv"):
+            sc = self.src.get(base + ".weight_scale_inv").float()
+            bs = getattr(self.cfg.quantization, "block_size", None) or self.cfg.extra.get("fp8_block_size") or (128, 128)
+            if sc.dim() == 2 and wf.dim() == 2:
+                sc = sc.repeat_interleave(int(bs[0]), 0)[: wf.shape[0]].repeat_interleave(int(bs[1]), 1)[:, : wf.shape[1]]
+            wf = wf * sc
+        elif self.src.has(base + ".weight_scale"):
+            sc = self.src.get(base + ".weight_scale").float()
+            wf = wf * (sc.reshape(-1, 1) if sc.numel() == wf.shape[0] and wf.dim() == 2 else sc)
+        return wf.to(self.dtype)
 
 
 def _cat_rows(parts):

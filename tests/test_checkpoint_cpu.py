@@ -52,3 +52,63 @@ def test_roundtrip_quantized(tmp_path):
         assert _gen(cfg, w) == _gen(cfg2, w3)
         # reset to dense for the next mode
         w = random_weights(cfg, seed=2, dtype=torch.float32, std=0.05)
+
+
+def test_fp8_block_scaled_and_per_channel_checkpoints_load(tmp_path):
+    """DeepSeek-V3 style block-scaled FP8 (``weight_scale_inv`` per 128 x 128 tile, here 32 x 32) and
+    compressed-tensors style per-channel FP8 (``weight_scale``) are widened at load: the loaded matrices
+    equal fp8 * scale, and the logits equal those of a checkpoint holding the widened weights."""
+    import json
+
+    import torch
+    from safetensors.torch import load_file, save_file
+
+    from mlxcel_b200.config import ModelConfig, preset
+    from mlxcel_b200.loading.checkpoint import load_full_weights, save_checkpoint
+    from mlxcel_b200.models.weights import random_weights
+
+    cfg = preset("tiny-llama")
+    src = tmp_path / "bf16"
+    save_checkpoint(src, cfg.to_dict() | {"model_type": "llama"}, random_weights(cfg, seed=0, dtype=torch.bfloat16, std=0.05))
+    t = {k: v.clone() for k, v in load_file(str(src / "model.safetensors")).items()}
+    raw = json.loads((src / "config.json").read_text())
+    raw.pop("quantization", None)
+
+    def write(name, tensors, qc):
+        d = tmp_path / name
+        d.mkdir()
+        save_file(tensors, str(d / "model.safetensors"), metadata={"format": "pt"})
+        (d / "config.json").write_text(json.dumps(raw | {"quantization_config": qc}))
+        return d
+
+    B = 32
+    block, chan, wide = {}, {}, {}
+    for k, v in t.items():
+        if k.endswith("_proj.weight") and v.dim() == 2:
+            w = v.float()
+            n, kk = w.shape
+            pad = torch.zeros((n + B - 1) // B * B, (kk + B - 1) // B * B)
+            pad[:n, :kk] = w
+            tiles = pad.view(pad.shape[0] // B, B, pad.shape[1] // B, B)
+            sc = tiles.abs().amax(dim=(1, 3)).clamp_min(1e-8) / 448.0
+            q = (tiles / sc[:, None, :, None]).view_as(pad)[:n, :kk].to(torch.float8_e4m3fn)
+            block[k], block[k[:-7] + ".weight_scale_inv"] = q, sc
+            wide[k] = (q.float() * sc.repeat_interleave(B, 0)[:n].repeat_interleave(B, 1)[:, :kk]).to(torch.bfloat16)
+            cs = w.abs().amax(dim=1, keepdim=True).clamp_min(1e-8) / 448.0
+            chan[k], chan[k[:-7] + ".weight_scale"] = (w / cs).to(torch.float8_e4m3fn), cs
+        else:
+            block[k] = chan[k] = wide[k] = v
+    d_block = write("fp8_block", block, dict(quant_method="fp8", fmt="e4m3", weight_block_size=[B, B]))
+    d_chan = write("fp8_chan", chan, dict(quant_method="compressed-tensors", format="float-quantized"))
+    d_wide = write("wide", wide, None)
+    c_block = ModelConfig.from_path(d_block)
+    assert c_block.quantization.mode == "none" and c_block.extra["fp8_block_size"] == (B, B)
+    w_block = load_full_weights(d_block, c_block, dtype=torch.bfloat16)
+    w_wide = load_full_weights(d_wide, ModelConfig.from_path(d_wide), dtype=torch.bfloat16)
+    for a, b in zip(w_block.layers, w_wide.layers):
+        assert torch.equal(a.wqkv, b.wqkv) and torch.equal(a.w_down, b.w_down) and a.wqkv.dtype == torch.bfloat16
+    w_chan = load_full_weights(d_chan, ModelConfig.from_path(d_chan), dtype=torch.bfloat16)
+    ref = load_full_weights(src, ModelConfig.from_path(src), dtype=torch.bfloat16)
+    for a, b in zip(w_chan.layers, ref.layers):
+        err = (a.wo.float() - b.wo.float()).abs().max().item()
+        assert err < 0.07 * b.wo.float().abs().max().item()          # e4m3 keeps 3 mantissa bits
