@@ -243,6 +243,9 @@ class ModelConfig:
             qc = None
         c.quantization = QuantConfig.from_dict(qc)
         c.dtype = str(g("torch_dtype", g("dtype", "bfloat16")))
+        rs = c.rope_scaling
+        if rs and rs.get("rope_type", rs.get("type")) == "dynamic" and not rs.get("original_max_position_embeddings"):
+            c.rope_scaling = dict(rs, original_max_position_embeddings=int(g("max_position_embeddings", 0) or 0))
         fam(c, raw)
         if c.is_moe and not c.moe_intermediate_size:
             c.moe_intermediate_size = c.intermediate_size
@@ -356,7 +359,14 @@ def _gpt_oss(c: ModelConfig, raw: dict) -> None:
 
 
 def _phi3(c: ModelConfig, raw: dict) -> None:
-    pass  # fused qkv_proj / gate_up_proj names are handled by the weight-name sanitizer
+    # fused qkv_proj / gate_up_proj names are handled by the weight-name sanitizer; the long-context
+    # variants keep the lengths that longrope needs beside (not inside) the scaling block
+    rs = c.rope_scaling
+    if rs and rs.get("rope_type", rs.get("type")) in ("longrope", "su"):
+        rs = dict(rs)
+        rs.setdefault("original_max_position_embeddings", raw.get("original_max_position_embeddings"))
+        rs.setdefault("max_position_embeddings", raw.get("max_position_embeddings"))
+        c.rope_scaling = rs
 
 
 def _olmo2(c: ModelConfig, raw: dict) -> None:

@@ -22,6 +22,8 @@ class LLM:
         """``fold_norms``: the weights belong to this object alone, so the executor may fold the
         RMSNorm weights into the projections in place (deferred RMSNorm, see DecoderModel)."""
         self.cfg = cfg
+        if engine_config is not None:
+            cfg.extra.setdefault("served_context", int(engine_config.max_model_len))
         if cfg.model_type in ("mamba", "mamba2", "nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "falcon_h1", "lfm2"):
             from .models.hybrid import HybridModel
             from .models.mamba1 import Mamba1Model

@@ -115,7 +115,8 @@ class DecoderModel:
         self.D = cfg.head_dim
         self.I = cfg.intermediate_size // tp
         dev = weights.final_norm.device
-        inv, ms = rope_inv_freq(cfg.rot_dim, cfg.rope_theta, cfg.rope_scaling)
+        # served context (when the front end recorded it): longrope / dynamic-NTK tables depend on it
+        inv, ms = rope_inv_freq(cfg.rot_dim, cfg.rope_theta, cfg.rope_scaling, int(cfg.extra.get("served_context", 0) or 0))
         self.inv_freq = inv.to(dev)
         self.mscale = ms
         # sliding-window layers with their own RoPE base (Gemma 3: local 10k, global 1M with scaling)

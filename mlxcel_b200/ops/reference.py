@@ -58,7 +58,7 @@ def rope_inv_freq(head_dim_rot: int, theta: float, scaling: dict | None,
                   max_pos: int = 0) -> tuple[torch.Tensor, float]:
     """Per-pair inverse frequencies (fp32) and the q/k magnitude scale (YaRN mscale).
 
-    Implements plain, linear, llama3 and yarn scaling the way the reference builds its
+    Implements plain, linear, llama3, yarn, longrope (Phi-3) and dynamic-NTK scaling the way the reference builds its
     frequency tables (src/models/rope_utils.rs:343-400,608; src/models/gpt_oss.rs:269-305).
     """
     half = head_dim_rot // 2
@@ -103,7 +103,27 @@ def rope_inv_freq(head_dim_rot: int, theta: float, scaling: dict | None,
                 mscale = float(scaling["attention_factor"])
             elif factor > 1:
                 mscale = 0.1 * (float(ms) if ms else 1.0) * math.log(factor) + 1.0
-        elif kind in ("default", "dynamic", None):
+        elif kind in ("longrope", "su"):
+            # Phi-3 long context: per-pair divisors, the long set once the served context exceeds the
+            # original training length (the short set otherwise), and a magnitude scale
+            # sqrt(1 + ln(factor) / ln(original)) on the rotated q / k
+            orig = float(scaling.get("original_max_position_embeddings") or 4096)
+            total = float(scaling.get("max_position_embeddings") or max_pos or orig)
+            use_long = (max_pos or total) > orig
+            ext = torch.tensor(scaling["long_factor" if use_long else "short_factor"], dtype=torch.float64)
+            inv = inv / ext[:half]
+            f = float(scaling.get("factor") or total / orig)
+            if scaling.get("attention_factor") is not None:
+                mscale = float(scaling["attention_factor"])
+            elif f > 1.0:
+                mscale = math.sqrt(1.0 + math.log(f) / math.log(orig))
+        elif kind == "dynamic":
+            # dynamic NTK: the base grows with the served context beyond the original length
+            orig = float(scaling.get("original_max_position_embeddings") or max_pos or 0)
+            if max_pos and orig and max_pos > orig and head_dim_rot > 2:
+                base = theta * ((factor * max_pos / orig) - (factor - 1)) ** (head_dim_rot / (head_dim_rot - 2))
+                inv = 1.0 / (base ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim_rot))
+        elif kind in ("default", None):
             pass
         else:
             raise ValueError(f"unsupported rope scaling {kind}")

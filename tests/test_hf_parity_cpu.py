@@ -244,6 +244,48 @@ def test_granite_hybrid_matches_transformers(pos, experts):
         assert out == ref
 
 
+@pytest.mark.parametrize("kind,T", [("longrope", 24), ("longrope", 100), ("dynamic", 24), ("dynamic", 100)])
+def test_context_dependent_rope_scaling_matches_transformers(kind, T):
+    """Phi-3 longrope (short factors within the original length, long factors and the magnitude scale
+    beyond it) and dynamic-NTK scaling (base grows past the original length): tables are built for the
+    served context."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    from mlxcel_b200.loading.checkpoint import load_full_weights
+
+    torch.manual_seed(0)
+    if kind == "longrope":
+        rp = dict(rope_type="longrope", rope_theta=10000.0, short_factor=[1.0 + 0.05 * i for i in range(8)],
+                  long_factor=[1.5 + 0.3 * i for i in range(8)], original_max_position_embeddings=64)
+        hc = AutoConfig.for_model("phi3", **dict(BASE, pad_token_id=0, original_max_position_embeddings=64, rope_parameters=rp))
+    else:
+        hc = AutoConfig.for_model("llama", **dict(BASE, max_position_embeddings=64,
+                                                  rope_parameters=dict(rope_type="dynamic", rope_theta=10000.0, factor=4.0)))
+    model = AutoModelForCausalLM.from_config(hc).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.08)
+    d = tempfile.mkdtemp(prefix=f"parity_{kind}_")
+    model.save_pretrained(d, safe_serialization=True)
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0]
+    cfg = ModelConfig.from_path(d)
+    cfg.extra["served_context"] = T
+    ours = DecoderModel(cfg, load_full_weights(d, cfg, dtype=torch.float32))
+    nb = (T + 15) // 16
+    pool = KVPool(cfg, nb, 16, device="cpu", dtype=torch.float32)
+    b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
+                  slot_mapping=torch.arange(T, dtype=torch.int32), num_prefill_seqs=1,
+                  pf_block_tables=torch.arange(nb, dtype=torch.int32)[None], pf_cu_q=torch.tensor([0, T], dtype=torch.int32),
+                  pf_context_lens=torch.tensor([T], dtype=torch.int32), pf_max_q_len=T, pf_cu_q_host=[0, T],
+                  logits_rows=torch.arange(T))
+    got = ours.forward(b, pool.layers).float()
+    err = (got - want).abs().max().item()
+    assert err < 2e-3 * max(want.abs().max().item(), 1.0), f"{kind} T={T}: max abs error {err:.3e}"
+
+
 def test_lfm2_matches_transformers():
     """LFM2 (gated short convolutions and q/k-normed attention layers + SwiGLU MLPs) on the hybrid
     executor: prompt logits, then prefill in 8-token chunks and greedy decode through the LLM front end."""
