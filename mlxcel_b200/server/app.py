@@ -636,6 +636,15 @@ def create_app(state: ServerState) -> FastAPI:
                 "data": [{"object": "embedding", "index": i, "embedding": v} for i, v in enumerate(vecs)],
                 "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}
 
+    @app.post("/embedding")
+    async def embedding_native(body: dict):
+        """llama-server shape: ``[{"index": i, "embedding": [...]}, ...]`` for ``content`` (string or list)."""
+        from .embeddings import embed_texts
+        inp = body.get("content", body.get("input", ""))
+        texts = [inp] if isinstance(inp, str) else list(inp)
+        vecs, _ = await asyncio.get_running_loop().run_in_executor(None, embed_texts, state, texts)
+        return [{"index": i, "embedding": v} for i, v in enumerate(vecs)]
+
     return app
 
 

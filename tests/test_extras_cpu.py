@@ -274,3 +274,31 @@ def test_serve_preflight(capsys):
     assert est["fits_b200"] and est["kv_pool_blocks"] == 8 * 512
     with pytest.raises(SystemExit, match="does not fit"):
         cli.main(["serve", "-m", "preset:llama-3.1-8b", "-c", "4000000", "--parallel", "1"])
+
+
+def test_llama_server_compat_manifest_matches_the_parser_and_the_routes():
+    """compat/llama_server.json lists every option spelling with its treatment and the served routes; it
+    must agree with what the argument parser accepts and what the application registers."""
+    import argparse
+    import json
+    from pathlib import Path
+
+    from mlxcel_b200 import cli
+    from mlxcel_b200.server import app as app_mod
+
+    doc = json.loads((Path(__file__).resolve().parent.parent / "compat" / "llama_server.json").read_text())
+    ap = argparse.ArgumentParser()
+    cli._add_model_args(ap)
+    cli._add_sampling_args(ap)
+    known = {s: a for a in ap._actions for s in a.option_strings}
+    listed = {f for o in doc["options"] if o["status"] != "unsupported" for f in o["flags"]}
+    assert listed == set(known) - {"-h", "--help"}
+    for o in doc["options"]:
+        if o["status"] == "accepted-no-effect":
+            assert all(known[f].dest.startswith("compat_noop_") for f in o["flags"])
+        elif o["status"] == "unsupported":
+            assert o["flags"][0].split()[0] not in known and o["why"]
+    src = Path(app_mod.__file__).read_text()
+    for r in doc["routes"]:
+        path = r.split("?")[0].replace("{id}", "{slot_id}")
+        assert f'"{path}"' in src, r

@@ -236,5 +236,7 @@ def test_secondary_routes(client):
     assert client.post("/infill", json={"input_prefix": "def f(", "input_suffix": "return x"}).status_code == 501
     e = client.post("/embeddings", json={"input": ["a", "bb"]})
     assert e.status_code == 200 and len(e.json()["data"]) == 2
+    n = client.post("/embedding", json={"content": ["a", "bb"]}).json()
+    assert [x["index"] for x in n] == [0, 1] and len(n[0]["embedding"]) == len(e.json()["data"][0]["embedding"])
     rr = client.post("/rerank", json={"query": "a", "documents": ["a", "zzz"]}).json()
     assert len(rr["results"]) == 2 and client.post("/v1/reranking", json={"query": "a", "documents": ["a"]}).status_code == 200
