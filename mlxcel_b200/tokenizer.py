@@ -71,8 +71,11 @@ class HFTokenizer:
             if e is not None:
                 self._eos.update(e if isinstance(e, list) else [e])
         self.think_open, self.think_close = tok_id("<think>"), tok_id("</think>")
-        self.fim = {k: tok_id(v) for k, v in (("prefix", "<|fim_prefix|>"), ("suffix", "<|fim_suffix|>"),
-                                              ("middle", "<|fim_middle|>"))}
+        # fill-in-the-middle sentinels: Qwen / CodeGemma, StarCoder, CodeLlama and DeepSeek-Coder spellings
+        spellings = dict(prefix=("<|fim_prefix|>", "<fim_prefix>", "\u2581<PRE>", "<PRE>", "<\uff5cfim\u2581begin\uff5c>"),
+                         suffix=("<|fim_suffix|>", "<fim_suffix>", "\u2581<SUF>", "<SUF>", "<\uff5cfim\u2581hole\uff5c>"),
+                         middle=("<|fim_middle|>", "<fim_middle>", "\u2581<MID>", "<MID>", "<\uff5cfim\u2581end\uff5c>"))
+        self.fim = {k: next((i for i in map(tok_id, v) if i is not None), None) for k, v in spellings.items()}
 
     def encode(self, text: str, add_special_tokens: bool = False) -> list[int]:
         return self.tk.encode(text, add_special_tokens=add_special_tokens).ids

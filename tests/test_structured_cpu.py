@@ -19,17 +19,19 @@ SCHEMA = {"type": "object", "properties": {"a": {"type": "integer"}, "ok": {"typ
 
 @pytest.fixture(scope="module")
 def model_dir():
-    """tiny-llama random weights (vocabulary 1024) with a byte-level tokenizer of 257 entries."""
+    """tiny-llama random weights (vocabulary 1024) with a byte-level tokenizer of 260 entries."""
     from tokenizers import Tokenizer, decoders, models, pre_tokenizers
 
     d = Path(tempfile.mkdtemp(prefix="structured_"))
     cli.main(["random-init", "tiny-llama", str(d)])
     vocab = {ch: i for i, ch in enumerate(sorted(pre_tokenizers.ByteLevel.alphabet()))}
     vocab["<eos>"] = 256
+    for i, name in enumerate(("<fim_prefix>", "<fim_suffix>", "<fim_middle>")):      # StarCoder spelling
+        vocab[name] = 257 + i
     tok = Tokenizer(models.BPE(vocab=vocab, merges=[]))
     tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)
     tok.decoder = decoders.ByteLevel()
-    tok.add_special_tokens(["<eos>"])
+    tok.add_special_tokens(["<eos>", "<fim_prefix>", "<fim_suffix>", "<fim_middle>"])
     tok.save(str(d / "tokenizer.json"))
     (d / "tokenizer_config.json").write_text(json.dumps(dict(eos_token="<eos>", tokenizer_class="PreTrainedTokenizerFast")))
     return d
@@ -84,6 +86,10 @@ def test_server_response_format(model_dir):
         assert r.status_code == 200, r.text
         doc = json.loads(r.json()["choices"][0]["text"])
         assert set(doc) == {"a", "ok"}
+        fim = c.post("/infill", json=dict(input_prefix="def f(x):\n    ", input_suffix="\n    return y", n_predict=6,
+                                          temperature=0, ignore_eos=True))
+        assert fim.status_code == 200 and fim.json()["tokens_predicted"] == 6
+        assert llm.tokenizer.fim == dict(prefix=257, suffix=258, middle=259)
         r = c.post("/completion", json=dict(prompt="out:", n_predict=32, temperature=0.8, seed=5,
                                             grammar='root ::= "a" [0-9] [0-9]'))
         assert r.status_code == 200 and re.fullmatch(r"a[0-9]{2}", r.json()["content"])
