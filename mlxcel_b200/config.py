@@ -970,6 +970,14 @@ def _lfm2(c: ModelConfig, raw: dict) -> None:
     c.layer_types = None
 
 
+def _baichuan(c: ModelConfig, raw: dict) -> None:
+    """Baichuan (7B layout): Llama block with q, k, v fused in ``W_pack`` (reference src/models/baichuan.rs).
+    The 13B models replace RoPE by ALiBi, which no attention kernel here implements."""
+    if raw.get("alibi") or (c.hidden_size >= 5120 and "rope_theta" not in raw and raw.get("model_max_length")):
+        raise ValueError("baichuan checkpoints with ALiBi attention are not supported")
+    c.num_key_value_heads = c.num_attention_heads
+
+
 FAMILIES = {
     "llama": _plain, "mistral": _plain, "ministral": _plain, "smollm3": _smollm3, "seed_oss": _plain,
     "helium": _interleaved_rope, "internlm3": _plain, "exaone4": _exaone4, "hunyuan_v1_dense": _hunyuan_dense,
@@ -982,7 +990,7 @@ FAMILIES = {
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
     "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
-    "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2,
+    "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }
 
 

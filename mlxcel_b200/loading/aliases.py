@@ -27,8 +27,35 @@ def _neox_qkv(heads: int):
     return fix
 
 
+def _grouped_qkv(heads: int, kv_heads: int):
+    """InternLM2 stores wqkv per key/value group as [kv_heads, heads / kv_heads + 2, D, ...] (the group's
+    query heads, then its key head, then its value head); the executor wants all q rows, k rows, v rows."""
+    def fix(w: torch.Tensor) -> torch.Tensor:
+        rest = w.shape[1:]
+        g = heads // kv_heads
+        d = w.shape[0] // (kv_heads * (g + 2))
+        v = w.view(kv_heads, g + 2, d, *rest)
+        q, k, vv = v[:, :g].reshape(heads * d, *rest), v[:, g].reshape(kv_heads * d, *rest), v[:, g + 1].reshape(kv_heads * d, *rest)
+        return torch.cat([q, k, vv], 0).contiguous()
+    return fix
+
+
 def _rules(cfg) -> list[tuple[str, str, object]]:
     mt = cfg.model_type
+    if mt == "internlm2":
+        L = r"model\.layers\.(\d+)\."
+        return [(r"model\.tok_embeddings\.(\w+)", r"model.embed_tokens.\1", None),
+                (r"output\.(\w+)", r"lm_head.\1", None),
+                (L + r"attention_norm\.(\w+)", r"model.layers.\1.input_layernorm.\2", None),
+                (L + r"ffn_norm\.(\w+)", r"model.layers.\1.post_attention_layernorm.\2", None),
+                (L + r"attention\.wqkv\.(\w+)", r"model.layers.\1.self_attn.qkv_proj.\2",
+                 _grouped_qkv(cfg.num_attention_heads, cfg.num_key_value_heads)),
+                (L + r"attention\.wo\.(\w+)", r"model.layers.\1.self_attn.o_proj.\2", None),
+                (L + r"feed_forward\.w1\.(\w+)", r"model.layers.\1.mlp.gate_proj.\2", None),
+                (L + r"feed_forward\.w3\.(\w+)", r"model.layers.\1.mlp.up_proj.\2", None),
+                (L + r"feed_forward\.w2\.(\w+)", r"model.layers.\1.mlp.down_proj.\2", None)]
+    if mt == "baichuan":                            # W_pack is already q rows | k rows | v rows
+        return [(r"model\.layers\.(\d+)\.self_attn\.W_pack\.(\w+)", r"model.layers.\1.self_attn.qkv_proj.\2", None)]
     if mt == "gpt_neox":
         qkv = _neox_qkv(cfg.num_attention_heads)
         L = r"gpt_neox\.layers\.(\d+)\."

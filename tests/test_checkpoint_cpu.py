@@ -112,3 +112,59 @@ def test_fp8_block_scaled_and_per_channel_checkpoints_load(tmp_path):
     for a, b in zip(w_chan.layers, ref.layers):
         err = (a.wo.float() - b.wo.float()).abs().max().item()
         assert err < 0.07 * b.wo.float().abs().max().item()          # e4m3 keeps 3 mantissa bits
+
+
+def test_internlm2_and_baichuan_layouts_load_like_their_llama_form(tmp_path):
+    """The same weights written in InternLM2's layout (grouped wqkv, w1/w3/w2, tok_embeddings / output) and
+    in Baichuan's (W_pack) load into the executor layout of the plain Llama checkpoint they came from."""
+    import json
+
+    import torch
+    from safetensors.torch import load_file, save_file
+
+    from mlxcel_b200.config import ModelConfig, preset
+    from mlxcel_b200.loading.checkpoint import load_full_weights, save_checkpoint
+    from mlxcel_b200.models.weights import random_weights
+
+    cfg = preset("tiny-llama")
+    src = tmp_path / "llama"
+    save_checkpoint(src, cfg.to_dict() | {"model_type": "llama", "tie_word_embeddings": False},
+                    random_weights(ModelConfig.from_dict(cfg.to_dict() | {"tie_word_embeddings": False}), seed=0,
+                                   dtype=torch.bfloat16, std=0.05))
+    t = {k: v.clone() for k, v in load_file(str(src / "model.safetensors")).items()}
+    raw = json.loads((src / "config.json").read_text())
+    Hq, Hkv, D, L = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.num_hidden_layers
+    g = Hq // Hkv
+    il = {"model.tok_embeddings.weight": t["model.embed_tokens.weight"], "model.norm.weight": t["model.norm.weight"],
+          "output.weight": t["lm_head.weight"]}
+    for i in range(L):
+        p, o = f"model.layers.{i}.", f"model.layers.{i}."
+        q = t[p + "self_attn.q_proj.weight"].view(Hkv, g, D, -1)
+        k = t[p + "self_attn.k_proj.weight"].view(Hkv, 1, D, -1)
+        v = t[p + "self_attn.v_proj.weight"].view(Hkv, 1, D, -1)
+        il[o + "attention.wqkv.weight"] = torch.cat([q, k, v], 1).reshape((Hq + 2 * Hkv) * D, -1).contiguous()
+        il[o + "attention.wo.weight"] = t[p + "self_attn.o_proj.weight"]
+        il[o + "attention_norm.weight"], il[o + "ffn_norm.weight"] = t[p + "input_layernorm.weight"], t[p + "post_attention_layernorm.weight"]
+        for a, b in (("w1", "gate_proj"), ("w3", "up_proj"), ("w2", "down_proj")):
+            il[o + f"feed_forward.{a}.weight"] = t[p + f"mlp.{b}.weight"]
+    d = tmp_path / "internlm2"
+    d.mkdir()
+    save_file(il, str(d / "model.safetensors"), metadata={"format": "pt"})
+    (d / "config.json").write_text(json.dumps(raw | {"model_type": "internlm2"}))
+    ref = load_full_weights(src, ModelConfig.from_path(src), dtype=torch.bfloat16)
+    got = load_full_weights(d, ModelConfig.from_path(d), dtype=torch.bfloat16)
+    assert torch.equal(got.embed, ref.embed) and torch.equal(got.lm_head, ref.lm_head)
+    for a, b in zip(got.layers, ref.layers):
+        for f in ("wqkv", "wo", "w_gate_up", "w_down", "ln1", "ln2"):
+            assert torch.equal(getattr(a, f), getattr(b, f)), f
+    if Hq == Hkv:                                               # Baichuan is multi-head attention only
+        bc = dict(t)
+        for i in range(L):
+            p = f"model.layers.{i}.self_attn."
+            bc[p + "W_pack.weight"] = torch.cat([bc.pop(p + "q_proj.weight"), bc.pop(p + "k_proj.weight"), bc.pop(p + "v_proj.weight")])
+        d2 = tmp_path / "baichuan"
+        d2.mkdir()
+        save_file(bc, str(d2 / "model.safetensors"), metadata={"format": "pt"})
+        (d2 / "config.json").write_text(json.dumps(raw | {"model_type": "baichuan"}))
+        got2 = load_full_weights(d2, ModelConfig.from_path(d2), dtype=torch.bfloat16)
+        assert all(torch.equal(a.wqkv, b.wqkv) for a, b in zip(got2.layers, ref.layers))
