@@ -199,7 +199,10 @@ def attach_drafter(llm, a, dev) -> None:
     eng.spec_k = max(1, int(getattr(a, "draft_max", 4))) + 1
     if not draft:
         from .speculative import PromptLookupDrafter
-        eng.drafter = PromptLookupDrafter()
+        nmin = getattr(a, "compat_lookup", None)
+        eng.drafter = PromptLookupDrafter(min_ngram=max(1, int(nmin))) if nmin else PromptLookupDrafter()
+        if nmin and eng.drafter.max_ngram < eng.drafter.min_ngram:
+            eng.drafter.max_ngram = eng.drafter.min_ngram
         return
     from .loading.split_mtp import MARKER
     dtype = eng.model.w.final_norm.dtype
