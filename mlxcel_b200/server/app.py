@@ -395,6 +395,32 @@ def create_app(state: ServerState) -> FastAPI:
                         yield _sse({"error": {"message": ev.error}})
                 yield b"data: [DONE]\n\n"
             return StreamingResponse(gen(), media_type="text/event-stream")
+        if body.get("echo"):
+            # prompt scoring (what evaluation harnesses ask for): the prompt comes back with the log-probability
+            # of each of its tokens given the ones before; ``max_tokens: 0`` scores without generating
+            from ..engine.scoring import sequence_logprobs
+            eng = state.worker.engine
+            plp = await asyncio.get_running_loop().run_in_executor(
+                None, lambda: sequence_logprobs(eng.model, eng.cfg, ids, eng.ecfg.block_size).tolist())
+            ptoks = [tk.decode([t], skip_special_tokens=False) for t in ids]
+            offs, pos = [], 0
+            for piece in ptoks:
+                offs.append(pos)
+                pos += len(piece)
+            prompt_text = tk.decode(ids, skip_special_tokens=False)
+            gen_text, gen_toks, gen_lps, usage, reason = "", [], [], None, "length"
+            if int(body.get("max_tokens", 16) or 0) > 0:
+                try:
+                    gen_text, gen_toks, gen_lps, fin = await _run_text(ids, sp, constraint)
+                except (RuntimeError, ValueError) as e:
+                    return _err(400, str(e))
+                usage, reason = fin.usage, _finish_openai(fin.finish_reason, False)
+            choice = {"index": 0, "text": prompt_text + gen_text, "finish_reason": reason,
+                      "logprobs": {"tokens": ptoks + [tk.decode([t]) for t in gen_toks],
+                                   "token_logprobs": [None] + plp + (gen_lps if sp.logprobs else [None] * len(gen_toks)),
+                                   "text_offset": offs}}
+            return {"id": cid, "object": "text_completion", "created": created, "model": state.model_id, "choices": [choice],
+                    "usage": usage or {"prompt_tokens": len(ids), "completion_tokens": 0, "total_tokens": len(ids)}}
         try:
             text, toks, lps, fin = await _run_text(ids, sp, constraint)
         except (RuntimeError, ValueError) as e:

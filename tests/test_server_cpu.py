@@ -240,3 +240,21 @@ def test_secondary_routes(client):
     assert [x["index"] for x in n] == [0, 1] and len(n[0]["embedding"]) == len(e.json()["data"][0]["embedding"])
     rr = client.post("/rerank", json={"query": "a", "documents": ["a", "zzz"]}).json()
     assert len(rr["results"]) == 2 and client.post("/v1/reranking", json={"query": "a", "documents": ["a"]}).status_code == 200
+
+
+def test_completions_echo_scores_the_prompt(client):
+    """``echo`` + ``max_tokens: 0``: per-token prompt log-probabilities (the evaluation-harness request);
+    with generation, the greedy continuation's first token is the argmax the prompt scores imply."""
+    r = client.post("/v1/completions", json={"prompt": "hello world", "echo": True, "max_tokens": 0, "logprobs": 1}).json()
+    ch = r["choices"][0]
+    lp = ch["logprobs"]
+    n = r["usage"]["prompt_tokens"]
+    assert ch["text"].endswith("hello world") and len(lp["tokens"]) == n == len(lp["token_logprobs"]) == len(lp["text_offset"])
+    assert lp["token_logprobs"][0] is None and all(x <= 0.0 for x in lp["token_logprobs"][1:])
+    assert r["usage"]["completion_tokens"] == 0
+    longer = client.post("/v1/completions", json={"prompt": "hello world!", "echo": True, "max_tokens": 0}).json()
+    a, b = lp["token_logprobs"][1:], longer["choices"][0]["logprobs"]["token_logprobs"][1:n]
+    assert all(abs(x - y) < 1e-4 for x, y in zip(a, b))          # causal: a longer prompt scores its prefix the same
+    g = client.post("/v1/completions", json={"prompt": "hello world", "echo": True, "max_tokens": 3, "temperature": 0,
+                                             "ignore_eos": True, "logprobs": 1}).json()["choices"][0]
+    assert len(g["logprobs"]["tokens"]) == n + 3 and g["logprobs"]["token_logprobs"][n] is not None
