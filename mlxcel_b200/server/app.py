@@ -370,6 +370,27 @@ def create_app(state: ServerState) -> FastAPI:
         ids = tk.encode(prompt, add_special_tokens=True)
         return ids or [getattr(tk, "bos_token_id", 0) or 0]
 
+    async def _run_n(body: dict, ids, sp, constraint_factory):
+        """``n`` independent samples of one prompt, run concurrently (the engine batches them and the prefix
+        cache shares the prompt); sample i uses ``seed + i`` when a seed was given. Constraints are stateful,
+        so each sample gets its own."""
+        import copy
+        n = max(1, min(int(body.get("n", 1) or 1), state.worker.engine.ecfg.max_batch))
+        sps = []
+        for i in range(n):
+            spi = copy.deepcopy(sp)
+            if spi.seed is not None:
+                spi.seed = spi.seed + i
+            sps.append(spi)
+        return await asyncio.gather(*(_run_text(ids, spi, constraint_factory()) for spi in sps))
+
+    def _sum_usage(runs) -> dict:
+        u = dict(runs[0][3].usage)
+        extra = sum(r[3].usage["completion_tokens"] for r in runs[1:])
+        u["completion_tokens"] += extra
+        u["total_tokens"] += extra
+        return u
+
     @app.post("/v1/completions")
     async def completions(body: dict):
         sp = sampling_from_body(body, 16)
@@ -422,14 +443,18 @@ def create_app(state: ServerState) -> FastAPI:
             return {"id": cid, "object": "text_completion", "created": created, "model": state.model_id, "choices": [choice],
                     "usage": usage or {"prompt_tokens": len(ids), "completion_tokens": 0, "total_tokens": len(ids)}}
         try:
-            text, toks, lps, fin = await _run_text(ids, sp, constraint)
+            runs = await _run_n(body, ids, sp, lambda: constraint_from_request(
+                tk, response_format=body.get("response_format"), grammar=body.get("grammar"), json_schema=body.get("json_schema")))
         except (RuntimeError, ValueError) as e:
             return _err(400, str(e))
-        choice = {"index": 0, "text": text, "finish_reason": _finish_openai(fin.finish_reason, False)}
-        if sp.logprobs:
-            choice["logprobs"] = {"token_logprobs": lps, "tokens": [tk.decode([t]) for t in toks]}
+        choices = []
+        for i, (text, toks, lps, fin) in enumerate(runs):
+            choice = {"index": i, "text": text, "finish_reason": _finish_openai(fin.finish_reason, False)}
+            if sp.logprobs:
+                choice["logprobs"] = {"token_logprobs": lps, "tokens": [tk.decode([t]) for t in toks]}
+            choices.append(choice)
         return {"id": cid, "object": "text_completion", "created": created, "model": state.model_id,
-                "choices": [choice], "usage": fin.usage, "timings": fin.timings}
+                "choices": choices, "usage": _sum_usage(runs), "timings": runs[0][3].timings}
 
     @app.post("/completion")
     @app.post("/completions")
@@ -532,23 +557,27 @@ def create_app(state: ServerState) -> FastAPI:
                 yield b"data: [DONE]\n\n"
             return StreamingResponse(gen(), media_type="text/event-stream")
         try:
-            text, toks, lps, fin = await _run_text(ids, sp, constraint)
+            runs = await _run_n(body, ids, sp, lambda: constraint_from_request(
+                tk, response_format=body.get("response_format"), grammar=body.get("grammar")))
         except (RuntimeError, ValueError) as e:
             return _err(400, str(e))
-        reasoning, answer = split_reasoning(text)
-        calls = []
-        if use_tools:
-            answer, calls = parse_tool_calls(answer, allowed)
-        msg = {"role": "assistant", "content": answer if (answer or not calls) else None}
-        if reasoning:
-            msg["reasoning_content"] = reasoning
-        if calls:
-            msg["tool_calls"] = [c.to_openai() for c in calls]
-        choice = {"index": 0, "message": msg, "finish_reason": _finish_openai(fin.finish_reason, bool(calls))}
-        if sp.logprobs:
-            choice["logprobs"] = {"content": [{"token": tk.decode([t]), "logprob": lp} for t, lp in zip(toks, lps)]}
+        choices = []
+        for i, (text, toks, lps, fin) in enumerate(runs):
+            reasoning, answer = split_reasoning(text)
+            calls = []
+            if use_tools:
+                answer, calls = parse_tool_calls(answer, allowed)
+            msg = {"role": "assistant", "content": answer if (answer or not calls) else None}
+            if reasoning:
+                msg["reasoning_content"] = reasoning
+            if calls:
+                msg["tool_calls"] = [c.to_openai() for c in calls]
+            choice = {"index": i, "message": msg, "finish_reason": _finish_openai(fin.finish_reason, bool(calls))}
+            if sp.logprobs:
+                choice["logprobs"] = {"content": [{"token": tk.decode([t]), "logprob": lp} for t, lp in zip(toks, lps)]}
+            choices.append(choice)
         return {"id": cid, "object": "chat.completion", "created": created, "model": state.model_id,
-                "choices": [choice], "usage": fin.usage, "timings": fin.timings}
+                "choices": choices, "usage": _sum_usage(runs), "timings": runs[0][3].timings}
 
     # ------------------------------------------------------------------ responses API
     def _responses_messages(body: dict) -> list[dict]:

@@ -258,3 +258,18 @@ def test_completions_echo_scores_the_prompt(client):
     g = client.post("/v1/completions", json={"prompt": "hello world", "echo": True, "max_tokens": 3, "temperature": 0,
                                              "ignore_eos": True, "logprobs": 1}).json()["choices"][0]
     assert len(g["logprobs"]["tokens"]) == n + 3 and g["logprobs"]["token_logprobs"][n] is not None
+
+
+def test_n_choices(client):
+    """``n``: several samples of one prompt in one request; greedy samples coincide, seeded ones are
+    reproducible and use seed + index."""
+    g = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "temperature": 0, "ignore_eos": True, "n": 3}).json()
+    assert [c["index"] for c in g["choices"]] == [0, 1, 2] and len({c["text"] for c in g["choices"]}) == 1
+    assert g["usage"]["completion_tokens"] == 15
+    body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "temperature": 1.0, "seed": 11, "ignore_eos": True,
+            "n": 2}
+    a, b = client.post("/v1/chat/completions", json=body).json(), client.post("/v1/chat/completions", json=body).json()
+    ta, tb = [c["message"]["content"] for c in a["choices"]], [c["message"]["content"] for c in b["choices"]]
+    assert ta == tb and len(ta) == 2
+    one = client.post("/v1/chat/completions", json=dict(body, n=1, seed=12)).json()["choices"][0]["message"]["content"]
+    assert one == ta[1]                                           # sample 1 of seed 11 is sample 0 of seed 12
