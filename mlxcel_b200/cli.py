@@ -650,10 +650,38 @@ def cmd_inspect(a):
     print(json.dumps(est, indent=1))
 
 
-def cmd_arch(a):
+_HYBRID = {"nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "falcon_h1", "lfm2"}
+_STATE_SPACE = {"mamba", "mamba2"}
+_CHECKED_BY_READING = {"internlm3", "minicpm", "mimo", "yi", "kimi_k2"}       # no independent implementation at hand
+_CHECKED_BY_LAYOUT = {"internlm2", "baichuan"}                                 # round trip against the Llama form
+
+
+def arch_catalog() -> dict:
+    """What this build loads: every model family with its executor and how its layout was checked, the
+    encoder families, quantization formats, KV precisions and parallel modes (reference src/main.rs:174,
+    ``mlxcel arch``)."""
     from .config import FAMILIES
-    print(json.dumps({"families": sorted(FAMILIES), "quantization": ["affine", "mxfp4", "mxfp8"],
-                      "kv_bits": [16, 8], "parallelism": ["tp", "ep", "pp"]}, indent=1))
+    fams = []
+    for name in sorted(FAMILIES):
+        ex = "hybrid" if name in _HYBRID else "state-space" if name in _STATE_SPACE else "decoder"
+        how = ("reading" if name in _CHECKED_BY_READING else "layout round trip" if name in _CHECKED_BY_LAYOUT
+               else "transformers logits")
+        fams.append(dict(name=name, executor=ex, checked_against=how))
+    return {"families": fams, "encoders": ["bert", "modernbert"], "quantization": ["affine", "mxfp4", "mxfp8", "fp8 (widened at load)"],
+            "kv_bits": [16, 8], "parallelism": ["tp", "ep", "pp"]}
+
+
+def cmd_arch(a):
+    cat = arch_catalog()
+    if getattr(a, "json", False):
+        print(json.dumps(cat, indent=1))
+        return
+    w = max(len(f["name"]) for f in cat["families"])
+    print(f"{'FAMILY'.ljust(w)}  EXECUTOR     CHECKED AGAINST")
+    for f in cat["families"]:
+        print(f"{f['name'].ljust(w)}  {f['executor']:<11}  {f['checked_against']}")
+    print(f"encoders: {', '.join(cat['encoders'])}")
+    print(f"quantization: {', '.join(cat['quantization'])}; kv bits: {cat['kv_bits']}; parallelism: {', '.join(cat['parallelism'])}")
 
 
 def cmd_tokenize(a):
@@ -817,7 +845,8 @@ def main(argv=None):
     p = sub.add_parser("inspect", help="memory estimate")
     _add_model_args(p)
     p.set_defaults(fn=cmd_inspect)
-    p = sub.add_parser("arch", help="supported architectures")
+    p = sub.add_parser("arch", aliases=["supported"], help="supported architectures")
+    p.add_argument("--json", action="store_true")
     p.set_defaults(fn=cmd_arch)
     p = sub.add_parser("tokenize")
     p.add_argument("-m", "--model", required=True)

@@ -302,3 +302,19 @@ def test_llama_server_compat_manifest_matches_the_parser_and_the_routes():
     for r in doc["routes"]:
         path = r.split("?")[0].replace("{id}", "{slot_id}")
         assert f'"{path}"' in src, r
+
+
+def test_arch_catalog_lists_every_family(capsys):
+    import json
+
+    from mlxcel_b200 import cli
+    from mlxcel_b200.config import FAMILIES
+
+    cli.main(["arch", "--json"])
+    cat = json.loads(capsys.readouterr().out)
+    names = {f["name"]: f for f in cat["families"]}
+    assert set(names) == set(FAMILIES) and names["jamba"]["executor"] == "hybrid" and names["mamba2"]["executor"] == "state-space"
+    assert names["llama"]["checked_against"] == "transformers logits" and "modernbert" in cat["encoders"]
+    cli.main(["supported"])
+    out = capsys.readouterr().out
+    assert out.splitlines()[0].startswith("FAMILY") and "qwen3_next" in out
