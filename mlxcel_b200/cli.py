@@ -666,6 +666,8 @@ def arch_catalog() -> dict:
         ex = "hybrid" if name in _HYBRID else "state-space" if name in _STATE_SPACE else "decoder"
         how = ("reading" if name in _CHECKED_BY_READING else "layout round trip" if name in _CHECKED_BY_LAYOUT
                else "transformers logits")
+        if name == "gemma3":                     # the wrapper's text_config is the gemma3_text model
+            how = "transformers logits (as gemma3_text)"
         fams.append(dict(name=name, executor=ex, checked_against=how))
     return {"families": fams, "encoders": ["bert", "modernbert"], "quantization": ["affine", "mxfp4", "mxfp8", "fp8 (widened at load)"],
             "kv_bits": [16, 8], "parallelism": ["tp", "ep", "pp"]}
