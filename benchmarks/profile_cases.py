@@ -1,15 +1,15 @@
 """Small, self-terminating workloads for profiler captures and kernel timing.
 
-    python -m mlxcel_b200.utils.profile_cases gemm_decode      # M=64 projections, 6 distinct weights
-    python -m mlxcel_b200.utils.profile_cases gemm_prefill     # 8192 x 6144 x 4096
-    python -m mlxcel_b200.utils.profile_cases attn_decode      # B=64, ctx 1152, GQA 32/8, D=128
-    python -m mlxcel_b200.utils.profile_cases attn_prefill     # 8 x 1024-token prompts
-    python -m mlxcel_b200.utils.profile_cases decode_steps N   # N eager decode steps of the bench workload
-    python -m mlxcel_b200.utils.profile_cases kbench           # CUDA-event timings of the hot kernels (JSON lines)
-    python -m mlxcel_b200.utils.profile_cases gemm_graph       # decode GEMMs back to back inside a CUDA graph, us per kernel
-    python -m mlxcel_b200.utils.profile_cases gemm_phases      # per-CTA phase timestamps of the decode GEMMs
-    python -m mlxcel_b200.utils.profile_cases qgemm_graph      # 4-bit weights: fused dequant GEMM vs GEMV vs dequantise + GEMM
-    python -m mlxcel_b200.utils.profile_cases mamba2           # Mamba2-2.7B mixer kernels (decode B=64, prefill 8 x 1024) + engine run
+    python -m benchmarks.profile_cases gemm_decode      # M=64 projections, 6 distinct weights
+    python -m benchmarks.profile_cases gemm_prefill     # 8192 x 6144 x 4096
+    python -m benchmarks.profile_cases attn_decode      # B=64, ctx 1152, GQA 32/8, D=128
+    python -m benchmarks.profile_cases attn_prefill     # 8 x 1024-token prompts
+    python -m benchmarks.profile_cases decode_steps N   # N eager decode steps of the bench workload
+    python -m benchmarks.profile_cases kbench           # CUDA-event timings of the hot kernels (JSON lines)
+    python -m benchmarks.profile_cases gemm_graph       # decode GEMMs back to back inside a CUDA graph, us per kernel
+    python -m benchmarks.profile_cases gemm_phases      # per-CTA phase timestamps of the decode GEMMs
+    python -m benchmarks.profile_cases qgemm_graph      # 4-bit weights: fused dequant GEMM vs GEMV vs dequantise + GEMM
+    python -m benchmarks.profile_cases mamba2           # Mamba2-2.7B mixer kernels (decode B=64, prefill 8 x 1024) + engine run
 
 Every case holds at most a few GB on the device and launches a handful of kernels, so that a
 capture with ``ncu --set full -k regex:<kernel> -c <n>`` ends by itself. ``decode_steps`` brackets
@@ -23,8 +23,8 @@ import sys
 
 import torch
 
-from .. import ops
-from ..ops import KVLayer
+from mlxcel_b200 import ops
+from mlxcel_b200.ops import KVLayer
 
 DEV = "cuda"
 
@@ -77,8 +77,8 @@ def attn_prefill(S=8, qlen=1024, Hq=32, Hkv=8, D=128, reps=2):
 
 
 def decode_steps(n_steps=2, requests=64, prompt_len=1024, model="llama-3.1-8b"):
-    from ..engine import EngineConfig, SamplingParams
-    from ..llm import LLM
+    from mlxcel_b200.engine import EngineConfig, SamplingParams
+    from mlxcel_b200.llm import LLM
     ecfg = EngineConfig(max_batch=requests, max_num_batched_tokens=8192, prefill_chunk_alone=2048,
                         prefill_chunk_contended=prompt_len, max_prefill_seqs=8, prefix_cache=False,
                         max_model_len=prompt_len + 300, cuda_graphs=False, lookahead=False,
@@ -215,7 +215,7 @@ def gemm_phases(M=64):
 
     import numpy as np
 
-    from ..ops import _lib
+    from mlxcel_b200.ops import _lib
     if os.environ.get("MLXCEL_B200_GEMM_TRACE") != "1":
         raise SystemExit("set MLXCEL_B200_GEMM_TRACE=1")
     names = ["entry", "setup", "loads0", "tile0", "mma_end", "acc_ready", "stored", "exit", "phaseB_begin", "phaseB_end"]
@@ -255,7 +255,7 @@ def qgemm_graph():
     4 rotating weight copies): the fused dequant GEMM (packed weights unpacked by the GEMM's transform
     warps), the GEMV kernel (M <= 8) and dequantise-then-GEMM, with the time the packed weight stream
     alone would take at the measured copy bandwidth."""
-    from ..ops import quant
+    from mlxcel_b200.ops import quant
     nrep, ncopy = 16, 4
 
     def graph_time(fn):
@@ -309,7 +309,7 @@ def qgemm_graph():
 
 def qgemm_decode(M=32):
     """Three launches of the fused dequant GEMM (affine 4-bit, group 64) at M tokens, 4096 x 14336."""
-    from ..ops import quant
+    from mlxcel_b200.ops import quant
     quant._QMV_MAX_M = 0
     x = _bf(M, 14336)
     out = torch.empty(M, 4096, dtype=torch.bfloat16, device=DEV)
@@ -324,7 +324,7 @@ def mamba2(engine_run=1):
     64 requests of 1024 prompt + 64 generated tokens through the engine."""
     import time
 
-    from ..ops import recurrent as R
+    from mlxcel_b200.ops import recurrent as R
 
     H, P, N, G, K, hid = 80, 64, 128, 1, 4, 2560
     di, cd = H * P, H * P + 2 * G * N
@@ -373,9 +373,9 @@ def mamba2(engine_run=1):
                               scan_us_per_token_step=round(t_scan * 1e3 / max(lens), 3))), flush=True)
     if not engine_run:
         return
-    from ..engine.engine import EngineConfig
-    from ..engine.params import SamplingParams
-    from ..llm import LLM
+    from mlxcel_b200.engine.engine import EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.llm import LLM
 
     del state, conv_state
     llm = LLM.from_preset("mamba2-2.7b", engine_config=EngineConfig(max_batch=64, max_model_len=2048, block_size=16,

@@ -1,7 +1,7 @@
 """Multi-rank timing of the fused GEMM + collective kernels against GEMM + NCCL.
 
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 \\
-        -m mlxcel_b200.utils.profile_comm [decode|prefill|ep]
+        -m benchmarks.profile_comm [decode|prefill|ep]
 
 Every case runs 16 dependent launches over 4 rotating weight shards inside one CUDA graph (CUDA
 events around the replay, median of 7, MAX over ranks). Printed per shape: the fused kernel, the
@@ -25,17 +25,17 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-from .. import ops
-from ..ops import _lib
-from ..parallel.tp import TPComm
+from mlxcel_b200 import ops
+from mlxcel_b200.ops import _lib
+from mlxcel_b200.parallel.tp import TPComm
 
 HBM_GBS, BF16_TFLOPS, NVLINK_GBS = 6551.4, 1658.9, 770.0
 
 
 def ep_main(rank: int, world: int, dev: torch.device) -> None:
-    from ..ops import moe as moe_ops
+    from mlxcel_b200.ops import moe as moe_ops
     from ..parallel.ep_a2a import EpAllToAll
-    from ..parallel.symm import SymmetricHeap
+    from mlxcel_b200.parallel.symm import SymmetricHeap
 
     E, k, H, I = 128, 4, 2880, 2880
     epr = E // world
@@ -159,6 +159,12 @@ def main() -> None:
         return ep_main(rank, world, dev)
     comm = TPComm(dist.group.WORLD, dev, backend="fused", max_tokens=8192, hidden=4096, vocab=131072)
     assert comm.backend == "fused"
+    # second channel set on the peer-store protocol, so that one run shows NVLS (multimem) beside it
+    comm_peer = None
+    if comm.fused.nvls:
+        os.environ["MLXCEL_B200_NVLS"] = "0"
+        comm_peer = TPComm(dist.group.WORLD, dev, backend="fused", max_tokens=8192, hidden=4096, vocab=131072)
+        os.environ["MLXCEL_B200_NVLS"] = "1"
     nrep, ncopy = 16, 4
 
     def graph_time(fn):
@@ -200,6 +206,12 @@ def main() -> None:
         hb.zero_()
         tmp = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         fused = graph_time(lambda: [comm.fused.gemm_allreduce(x, ws[i % ncopy], None, hb) for i in range(nrep)])
+        fused_peer = None
+        if comm_peer is not None:
+            hb2 = comm_peer.fused.hidden_buffer(M, N)
+            hb2.zero_()
+            fused_peer = graph_time(lambda: [comm_peer.fused.gemm_allreduce(x, ws[i % ncopy], None, hb2)
+                                             for i in range(nrep)])
 
         def base():
             for i in range(nrep):
@@ -212,7 +224,9 @@ def main() -> None:
             nv_bytes = 2 * M * N * 2 * (world - 1) // world   # two-shot: reduce-scatter + all-gather
         roof = max(N * K * 2 / (HBM_GBS * 1e3), 2.0 * M * N * K / (BF16_TFLOPS * 1e6), nv_bytes / (NVLINK_GBS * 1e3))
         if rank == 0:
-            print(json.dumps(dict(case=name, world=world, M=M, N=N, K_per_rank=K, fused_us=round(fused, 1),
+            print(json.dumps(dict(case=name, world=world, M=M, N=N, K_per_rank=K, nvls=bool(comm.fused.nvls),
+                                  fused_us=round(fused, 1),
+                                  fused_peer_store_us=round(fused_peer, 1) if fused_peer is not None else None,
                                   gemm_plus_nccl_us=round(nccl, 1), gemm_alone_us=round(alone, 1),
                                   roofline_us=round(roof, 1), fused_of_roofline=round(roof / fused, 2))), flush=True)
         if os.environ.get("MLXCEL_B200_GEMM_TRACE") == "1":

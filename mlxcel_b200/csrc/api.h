@@ -36,6 +36,28 @@ extern "C" {
 #define MX_EPI_GEGLU 4           // out = gelu_tanh(acc_gate) * acc_up
 #define MX_EPI_CLIPPED_SWIGLU 5  // gpt-oss: (min(g,l)) * sigmoid(a*g) * (clamp(u,-l,l) + 1)
 
+// Optional per-call extras of the GEMM entry points (pass NULL for a plain dense GEMM). Everything a
+// call needs travels in its own arguments: there is no per-thread or per-process pending state, so
+// several host threads (e.g. the engines of a multi-model router) can launch GEMMs concurrently.
+typedef struct MxGemmExtras {
+  // Quantized weights: `w` = packed weights re-tiled for the kernel (see gemm.cu), ldw ignored.
+  // wq: 0 dense bf16, 1 affine 4-bit, 2 affine 8-bit, 3 mxfp4; q_group: elements per scale group.
+  // The call returns -9 when M > 256 (use dequantise + GEMM).
+  int wq;
+  int q_group;
+  // Deferred RMSNorm: scale output rows by the 1/rms that `ssq_in` describes (consumer) and / or
+  // leave per-tile sums of squares of the result in `ssq_out` (producer). Either may be NULL.
+  const void* ssq_in;
+  void* ssq_out;
+  float ssq_eps;
+  float ssq_inv_dim;
+  // mx_gemm_comm only: multicast (NVLS) addresses of the channel's flags, its receive area and the
+  // replicated output. flags_mc == NULL selects the peer-store protocol.
+  void* flags_mc;
+  void* recv_mc;
+  void* out_mc;
+} MxGemmExtras;
+
 // out[M, N] = epilogue(x[M, K] @ w[N(+N), K]^T). bf16 operands, fp32 accumulation on the
 // 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operand tiles brought by TMA).
 // For the gated epilogues `w` holds gate rows at [0, N) and up rows at [glu_offset, glu_offset + N).
@@ -43,7 +65,11 @@ extern "C" {
 int mx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual,
                  int M, int N, int K, int ldx, int ldw, int ldo, int ldr, int epilogue,
                  int out_fp32, int glu_offset, float glu_alpha, float glu_limit, void* workspace,
-                 long long ws_bytes, int force_mode, int force_splits, void* stream);
+                 long long ws_bytes, int force_mode, int force_splits, void* stream,
+                 const MxGemmExtras* extras);
+
+/* Sum of squares of every row of x [rows, dim] (bf16) as a one-partial ssq buffer (see MxGemmExtras). */
+int mx_row_ssq(const void* x, int rows, int dim, long long ldx, void* ssq, void* stream);
 
 // Fused GEMM + collective over a symmetric heap of peer-mapped memory (tensor parallelism).
 // mode 1: one-shot all-reduce (M <= 256): out = residual + bias + sum over ranks of x_r @ w_r^T.
@@ -51,31 +77,25 @@ int mx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, cons
 // mode 3: all-gather of output columns (M <= 256): out_peer[r][t, rank * N + n].
 // flags_peer / recv_peer / out_peer: host arrays of `world` device addresses of the same heap
 // offset on each rank; ctl (16 words) / expect (8200 words): this rank's channel words (zeroed).
-/* Quantized weights for the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread (`w` = packed
- * rows, ldw = bytes per packed row); wq: 1 affine 4-bit, 2 affine 8-bit, 3 mxfp4. The call returns
- * -9 when M > 256 (use dequantise + GEMM). */
-void mx_gemm_set_quant(const void* scales, const void* biases, int group, int wq);
-
-/* Deferred RMSNorm for the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread: scale output
- * rows by the 1/rms that `ssq_in` describes (consumer) and / or leave per-tile sums of squares of
- * the result in `ssq_out` (producer). Either may be NULL. Buffer layout in gemm.cu. */
-void mx_gemm_set_row_norm(const void* ssq_in, float eps, float inv_dim, void* ssq_out);
-/* Sum of squares of every row of x [rows, dim] (bf16) as a one-partial ssq buffer (see above). */
-int mx_row_ssq(const void* x, int rows, int dim, long long ldx, void* ssq, void* stream);
-
+// With extras->flags_mc set the cross-rank traffic goes through NVSwitch multicast (multimem
+// ld_reduce / st / red) instead of per-peer stores; results are then equal across ranks up to the
+// switch's fp32 summation order instead of bitwise equal.
 int mx_gemm_comm(const void* x, const void* w, void* out, const void* bias, const void* residual,
                  int M, int N, int K, int ldx, int ldw, int ldo, int ldr, int mode, int rank,
                  int world, const void* const* flags_peer, const void* const* recv_peer,
                  const void* const* out_peer, void* ctl, void* expect, long long parity_stride,
-                 long long rank_stride, void* workspace, long long ws_bytes, void* stream);
+                 long long rank_stride, void* workspace, long long ws_bytes, void* stream,
+                 const MxGemmExtras* extras);
 
 // Stand-alone all-reduce over the symmetric heap (same channel protocol as mx_gemm_comm):
 // out = residual + sum over ranks of x, n bf16 elements. mode 1 one-shot (local out), mode 2
 // two-shot (results stored into every out_peer). status: device status word (int).
+// flags_mc / recv_mc / out_mc: NVLS multicast addresses of the channel (NULL = peer stores).
 int mx_allreduce_comm(const void* x, const void* residual, void* out, long long n, int mode, int rank,
                       int world, const void* const* flags_peer, const void* const* recv_peer,
                       const void* const* out_peer, void* ctl, void* expect, long long parity_stride,
-                      long long rank_stride, void* status, void* stream);
+                      long long rank_stride, void* status, void* stream, void* flags_mc, void* recv_mc,
+                      void* out_mc);
 
 // Bytes of workspace the no-scratch-allocation path needs at most for mx_gemm_bf16.
 long long mx_gemm_workspace_bytes(void);
@@ -208,7 +228,7 @@ int mx_moe_combine_n(const void* y, const int* sorted_pair, const int* total_row
 int mx_grouped_gemm_bf16(const void* x, const void* w, void* out, const void* bias,
                          const int* expert_offsets, int E, int N, int K, int max_rows,
                          int epilogue, int glu_offset, float glu_alpha, float glu_limit,
-                         void* workspace, long long ws_bytes, void* stream);
+                         void* workspace, long long ws_bytes, void* stream, const MxGemmExtras* extras);
 
 // Reads and clears the device status word of a workspace (host-synchronous).
 int mx_read_status(void* workspace, int clear);

@@ -10,6 +10,13 @@
 //   two-shot (mode 2): chunk c is owned by rank c % world: partials go to the owner only, the owner
 //     sums (+ residual) and stores the result into every peer's output; a per-call completion
 //     counter tells each rank when all chunks have landed.
+// With multicast (NVLS) addresses of the channel (flags_mc != NULL) the traffic goes through the
+// NVSwitch instead of per-peer stores:
+//   one-shot: the chunk is copied into THIS rank's slot 0 (local stores), one multimem.red bumps
+//     the chunk flag on every rank, and after `world` arrivals every rank pulls the sum of all
+//     replicas with multimem.ld_reduce (fp32 accumulation in the switch).
+//   two-shot: chunks stay local the same way, the owner pulls the reduced chunk with
+//     multimem.ld_reduce, adds the residual and writes every rank's output with one multimem.st.
 // Receive slots are double-buffered by call parity. Waits are bounded and report through `status`.
 #include "api.h"
 #include "common.cuh"
@@ -35,6 +42,10 @@ struct ArParams {
   __nv_bfloat16* recv_peer[kArMaxRanks];
   __nv_bfloat16* out_peer[kArMaxRanks];
   long long parity_stride, rank_stride;
+  int nvls;
+  uint32_t* flags_mc;
+  __nv_bfloat16* recv_mc;
+  __nv_bfloat16* out_mc;
 };
 
 __device__ __forceinline__ void ar_signal(uint32_t* addr) {
@@ -67,15 +78,18 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p)
   for (long long c = blockIdx.x; c < chunks; c += gridDim.x) {
     const long long e0 = c * kChunkElems;
     const int owner = static_cast<int>(c % p.world);
-    const long long slot_off = (p.mode == 1) ? e0 : (c / p.world) * kChunkElems;
+    // NVLS: every chunk keeps its own place in the local half (slot 0 spans the whole tensor)
+    const long long slot_off = (p.mode == 1 || p.nvls) ? e0 : (c / p.world) * kChunkElems;
     // ---- push
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
       const long long e = e0 + (static_cast<long long>(it) * kArThreads + threadIdx.x) * 8;
       if (e < p.n) {
         const uint4 v = *reinterpret_cast<const uint4*>(p.x + e);
-        const size_t off = pbase + p.rank * static_cast<size_t>(p.rank_stride) + slot_off + (e - e0);
-        if (p.mode == 1) {
+        const size_t off = pbase + (p.nvls ? 0 : p.rank * static_cast<size_t>(p.rank_stride)) + slot_off + (e - e0);
+        if (p.nvls) {
+          *reinterpret_cast<uint4*>(p.recv_peer[p.rank] + off) = v;
+        } else if (p.mode == 1) {
           for (int pr = 0; pr < p.world; ++pr) *reinterpret_cast<uint4*>(p.recv_peer[pr] + off) = v;
         } else {
           *reinterpret_cast<uint4*>(p.recv_peer[owner] + off) = v;
@@ -83,7 +97,9 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p)
       }
     }
     __syncthreads();   // then one releasing thread per peer signals (release is cumulative)
-    if (p.mode == 1) {
+    if (p.mode == 1 && p.nvls) {
+      if (threadIdx.x == 0) multimem_signal_add(p.flags_mc + c, 1u);
+    } else if (p.mode == 1) {
       if (threadIdx.x < p.world) ar_signal(p.flags_peer[threadIdx.x] + c);
     } else if (threadIdx.x == 0) {
       ar_signal(p.flags_peer[owner] + c);
@@ -113,7 +129,16 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p)
                 acc[2 * j + 1] = bf16_hi(w4[j]);
               }
             }
-            for (int r = 0; r < p.world; ++r) {
+            if (p.nvls) {
+              const uint4 a = multimem_ld_reduce_bf16x8(p.recv_mc + pbase + slot_off + (e - e0));
+              const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                acc[2 * j] += bf16_lo(w4[j]);
+                acc[2 * j + 1] += bf16_hi(w4[j]);
+              }
+            }
+            for (int r = 0; r < (p.nvls ? 0 : p.world); ++r) {
               const uint4 a = __ldcg(reinterpret_cast<const uint4*>(
                   p.recv_peer[p.rank] + pbase + r * static_cast<size_t>(p.rank_stride) + slot_off + (e - e0)));
               const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
@@ -130,6 +155,8 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p)
             o.w = pack_bf16(acc[6], acc[7]);
             if (p.mode == 1) {
               *reinterpret_cast<uint4*>(p.out + e) = o;
+            } else if (p.nvls) {
+              multimem_st_16(p.out_mc + e, o);
             } else {
               for (int pr = 0; pr < p.world; ++pr) *reinterpret_cast<uint4*>(p.out_peer[pr] + e) = o;
             }
@@ -138,7 +165,11 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p)
       }
       if (p.mode == 2) {
         __syncthreads();
-        if (threadIdx.x < p.world) ar_signal(p.flags_peer[threadIdx.x] + kArDoneIdx);
+        if (p.nvls) {
+          if (threadIdx.x == 0) multimem_signal_add(p.flags_mc + kArDoneIdx, 1u);
+        } else if (threadIdx.x < p.world) {
+          ar_signal(p.flags_peer[threadIdx.x] + kArDoneIdx);
+        }
       }
     }
     __syncthreads();
@@ -169,19 +200,24 @@ using namespace mx;
 // mode 1: one-shot (out is local); mode 2: two-shot (results land in every out_peer, which must be
 // the same heap offset on every rank; `out` is ignored). rank_stride (elements) must hold n for
 // mode 1 and ceil(chunks / world) * 8192 for mode 2. status: device status word.
+// flags_mc / recv_mc / out_mc: multicast addresses of the same flags / receive area / output, or
+// NULL for the peer-store protocol.
 extern "C" int mx_allreduce_comm(const void* x, const void* residual, void* out, long long n, int mode,
                                  int rank, int world, const void* const* flags_peer,
                                  const void* const* recv_peer, const void* const* out_peer, void* ctl,
                                  void* expect, long long parity_stride, long long rank_stride,
-                                 void* status, void* stream_) {
+                                 void* status, void* stream_, void* flags_mc, void* recv_mc,
+                                 void* out_mc) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (n <= 0) return 0;
   if (n % 8 || world < 1 || world > kArMaxRanks || rank < 0 || rank >= world) return -1;
   if (mode != 1 && mode != 2) return -1;
   const long long chunks = (n + kChunkElems - 1) / kChunkElems;
   if (chunks > kArMaxChunks) return -5;
+  const bool nvls = flags_mc != nullptr && recv_mc != nullptr && (mode == 1 || out_mc != nullptr) &&
+                    chunks * kChunkElems <= (mode == 1 ? rank_stride : parity_stride);
   if (mode == 1 && n > rank_stride) return -5;
-  if (mode == 2 && ((chunks + world - 1) / world) * kChunkElems > rank_stride) return -5;
+  if (mode == 2 && !nvls && ((chunks + world - 1) / world) * kChunkElems > rank_stride) return -5;
   ArParams p{};
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
@@ -200,6 +236,10 @@ extern "C" int mx_allreduce_comm(const void* x, const void* residual, void* out,
   }
   p.parity_stride = parity_stride;
   p.rank_stride = rank_stride;
+  p.nvls = nvls ? 1 : 0;
+  p.flags_mc = static_cast<uint32_t*>(flags_mc);
+  p.recv_mc = static_cast<__nv_bfloat16*>(recv_mc);
+  p.out_mc = static_cast<__nv_bfloat16*>(out_mc);
   // every CTA must be resident at once (peers wait on each other's chunks)
   int sms = 148;
   int dev = 0;

@@ -281,6 +281,29 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// ----------------------------------------------------------------------------- NVLS (multimem)
+// A multicast address names the same offset of a symmetric buffer on every GPU of the group; the
+// NVSwitch executes the access on all replicas. ld_reduce returns the element-wise sum of the
+// replicas (accumulated in fp32 inside the switch), st writes every replica, red adds to every
+// replica. Addresses must be aligned to the access size (16 bytes for the vector forms).
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_16(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// Release at system scope, then add `v` to the word in every replica (one instruction signals all ranks).
+__device__ __forceinline__ void multimem_signal_add(uint32_t* mc, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+
 // ----------------------------------------------------------------------------- dependent launch
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
 // may start (be scheduled, run its prologue) while the previous kernel of the stream is still

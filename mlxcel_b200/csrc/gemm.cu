@@ -61,6 +61,19 @@ struct CommParams {
   __nv_bfloat16* out_peer[kMaxRanks];
   long long parity_stride;  // elements between the two receive halves
   long long rank_stride;    // elements between source-rank slots
+  // NVLS variants (nvls != 0): multicast addresses of the same flags / receive area / output.
+  //   COMM 1: the bf16 partial stays in THIS rank's receive half (one slot, no per-source slots),
+  //           one multimem.red bumps the tile's flag on every rank, and after `world` arrivals each
+  //           rank pulls the sum of all replicas with multimem.ld_reduce (fp32 accumulation in the
+  //           switch) instead of 7 peer pushes and an 8-way local sum.
+  //   COMM 2: partial tiles stay local (slot = tile), the owner pulls the reduced tile with
+  //           multimem.ld_reduce and writes the finished tile to every rank with one multimem.st.
+  //   COMM 3: the logits tile is written to every rank's gathered output with multimem.st.
+  // TMA never touches these addresses; all multimem accesses are plain ld / st / red forms.
+  int nvls;
+  uint32_t* flags_mc;
+  __nv_bfloat16* recv_mc;
+  __nv_bfloat16* out_mc;
 };
 
 // Release at system scope: the writes of the whole CTA are ordered before the flag update when
@@ -1033,15 +1046,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                 for (int g = 0; g < PU; ++g) emit_ssq(tl0 + g * 8 + tsub, o[g]);
               }
             } else if constexpr (COMM == 1) {
-              // bf16 partial (no bias / residual yet) into every peer's slot [rank]
+              // bf16 partial (no bias / residual yet) into every peer's slot [rank]; with NVLS it
+              // stays in this rank's own receive half and the peers pull the sum through the switch
               const size_t base = comm_parity * static_cast<size_t>(p.comm.parity_stride) +
-                                  p.comm.rank * static_cast<size_t>(p.comm.rank_stride);
+                                  (p.comm.nvls ? 0 : p.comm.rank * static_cast<size_t>(p.comm.rank_stride));
 #pragma unroll
               for (int g = 0; g < PU; ++g) {
                 const int tl = tl0 + g * 8 + tsub;
                 if (tl < t_end) {
                   const size_t off = base + static_cast<size_t>(it.out_tok0 + tl) * p.N + n;
-                  for (int pr = 0; pr < p.comm.world; ++pr) store_bf16x8(p.comm.recv_peer[pr] + off, o[g]);
+                  if (p.comm.nvls) {
+                    store_bf16x8(p.comm.recv_peer[p.comm.rank] + off, o[g]);
+                  } else {
+                    for (int pr = 0; pr < p.comm.world; ++pr) store_bf16x8(p.comm.recv_peer[pr] + off, o[g]);
+                  }
                 }
               }
             } else {  // COMM == 3: logits tile (+ bias) into every peer's gathered output
@@ -1051,7 +1069,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                 if (tl < t_end) {
                   const size_t off = static_cast<size_t>(it.out_tok0 + tl) * p.ldo +
                                      static_cast<size_t>(p.comm.rank) * p.N + n;
-                  for (int pr = 0; pr < p.comm.world; ++pr) store_bf16x8(p.comm.out_peer[pr] + off, o[g]);
+                  if (p.comm.nvls && vec) {
+                    uint4 pk;
+                    pk.x = pack_bf16(o[g][0], o[g][1]);
+                    pk.y = pack_bf16(o[g][2], o[g][3]);
+                    pk.z = pack_bf16(o[g][4], o[g][5]);
+                    pk.w = pack_bf16(o[g][6], o[g][7]);
+                    multimem_st_16(p.comm.out_mc + off, pk);   // one store, the switch writes every rank
+                  } else {
+                    for (int pr = 0; pr < p.comm.world; ++pr) store_bf16x8(p.comm.out_peer[pr] + off, o[g]);
+                  }
                 }
               }
             }
@@ -1064,7 +1091,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           const CommParams& cm = p.comm;
           named_bar_sync(1, 128);
           if (epi_tid == 0) stamp(11);
-          if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + tile, 1u);
+          if (cm.nvls) {
+            if (epi_tid == 0) multimem_signal_add(cm.flags_mc + tile, 1u);
+          } else if (epi_tid < cm.world) {
+            signal_add_sys(cm.flags_peer[epi_tid] + tile, 1u);
+          }
           // one signal per peer from every split CTA of the tile; expect[] advances once per call
           // (by this CTA when the tile is not split, else by the last split CTA to leave, below)
           const uint32_t comm_target = cm.expect[tile] + static_cast<uint32_t>(cm.world * p.splits);
@@ -1075,7 +1106,65 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           }
           named_bar_sync(1, 128);
           if (epi_tid == 0) stamp(10);
-          if (*last_flag != 0 && nvalid > 0) {
+          // bias + residual + store (+ sums of squares) of G token rows per thread
+          auto finish_rows = [&](int tl0, auto& o) {
+            constexpr int G = static_cast<int>(sizeof(o) / sizeof(o[0]));
+            if (bias_p != nullptr) {
+#pragma unroll
+              for (int g = 0; g < G; ++g) {
+                if (tl0 + g * 8 + tsub < t_end) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    if (j < nvalid) o[g][j] += __bfloat162float(bias_p[n + j]);
+                }
+              }
+            }
+            if (p.residual != nullptr) {
+#pragma unroll
+              for (int g = 0; g < G; ++g) {
+                const int tl = tl0 + g * 8 + tsub;
+                if (tl < t_end)
+                  add_bf16x8(p.residual + static_cast<size_t>(it.out_tok0 + tl) * p.ldr + n, o[g]);
+              }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              const int tl = tl0 + g * 8 + tsub;
+              if (tl < t_end) store_out(static_cast<size_t>(it.out_tok0 + tl) * p.ldo + n, o[g]);
+            }
+            if (p.ssq_out != nullptr) {
+#pragma unroll
+              for (int g = 0; g < G; ++g) emit_ssq(tl0 + g * 8 + tsub, o[g]);
+            }
+          };
+          if (*last_flag != 0 && nvalid > 0 && cm.nvls) {
+            // the switch sums the `world` replicas of these 16 bytes in fp32 and returns bf16; four
+            // token rows per thread are requested together (one NVLink round trip per batch)
+            const __nv_bfloat16* base = cm.recv_mc + comm_parity * static_cast<size_t>(cm.parity_stride);
+            constexpr int GRPN = 4;
+#pragma unroll 1
+            for (int tl0 = t_begin; tl0 < t_end; tl0 += 8 * GRPN) {
+              uint4 a[GRPN];
+#pragma unroll
+              for (int g = 0; g < GRPN; ++g) {
+                const int tl = tl0 + g * 8 + tsub;
+                a[g] = make_uint4(0u, 0u, 0u, 0u);
+                if (tl < t_end)
+                  a[g] = multimem_ld_reduce_bf16x8(base + static_cast<size_t>(it.out_tok0 + tl) * p.N + n);
+              }
+              float o[GRPN][8];
+#pragma unroll
+              for (int g = 0; g < GRPN; ++g) {
+                const uint32_t w4[4] = {a[g].x, a[g].y, a[g].z, a[g].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  o[g][2 * j] = bf16_lo(w4[j]);
+                  o[g][2 * j + 1] = bf16_hi(w4[j]);
+                }
+              }
+              finish_rows(tl0, o);
+            }
+          } else if (*last_flag != 0 && nvalid > 0) {
             // every rank sums the same bf16 partials in rank order: bitwise identical results
             const __nv_bfloat16* base = cm.recv_peer[cm.rank] +
                                         comm_parity * static_cast<size_t>(cm.parity_stride);
@@ -1115,36 +1204,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                         o[g][j] += __uint_as_float(static_cast<uint32_t>(raw) << 16);
                       }
                   }
-                  if (bias_p != nullptr) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                      if (j < nvalid) o[g][j] += __bfloat162float(bias_p[n + j]);
-                  }
                 }
               }
-              if (p.residual != nullptr) {
-#pragma unroll
-                for (int g = 0; g < GRPC; ++g) {
-                  const int tl = tl0 + g * 8 + tsub;
-                  if (tl < t_end)
-                    add_bf16x8(p.residual + static_cast<size_t>(it.out_tok0 + tl) * p.ldr + n, o[g]);
-                }
-              }
-#pragma unroll
-              for (int g = 0; g < GRPC; ++g) {
-                const int tl = tl0 + g * 8 + tsub;
-                if (tl < t_end) store_out(static_cast<size_t>(it.out_tok0 + tl) * p.ldo + n, o[g]);
-              }
-              if (p.ssq_out != nullptr) {
-#pragma unroll
-                for (int g = 0; g < GRPC; ++g) emit_ssq(tl0 + g * 8 + tsub, o[g]);
-              }
+              finish_rows(tl0, o);
             }
           }
         } else {  // COMM == 3
           const CommParams& cm = p.comm;
           named_bar_sync(1, 128);
-          if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
+          if (cm.nvls) {
+            if (epi_tid == 0) multimem_signal_add(cm.flags_mc + kCommDoneIdx, 1u);
+          } else if (epi_tid < cm.world) {
+            signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
+          }
         }
         if (p.splits > 1) {
           // Leave the tile: the last split CTA to get here (all of them have read the partials
@@ -1197,12 +1269,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           if (row_ok) {
             if constexpr (COMM == 2) {
               // partial tile row -> the owner's slot [rank][tile / world]
+              // (NVLS: the partial tile stays in this rank's own receive half, slot = tile; the
+              // owner pulls the sum of all ranks' slots through the switch)
               const int owner = comm2_owner(tile, p.comm.world);
-              __nv_bfloat16* dst = p.comm.recv_peer[owner] +
-                                   comm_parity * static_cast<size_t>(p.comm.parity_stride) +
-                                   p.comm.rank * static_cast<size_t>(p.comm.rank_stride) +
-                                   static_cast<size_t>(tile / p.comm.world) * (kLaneRows * BN) +
-                                   static_cast<size_t>(row) * BN + c * CW;
+              __nv_bfloat16* dst =
+                  p.comm.nvls
+                      ? p.comm.recv_peer[p.comm.rank] + comm_parity * static_cast<size_t>(p.comm.parity_stride) +
+                            static_cast<size_t>(tile) * (kLaneRows * BN) + static_cast<size_t>(row) * BN + c * CW
+                      : p.comm.recv_peer[owner] + comm_parity * static_cast<size_t>(p.comm.parity_stride) +
+                            p.comm.rank * static_cast<size_t>(p.comm.rank_stride) +
+                            static_cast<size_t>(tile / p.comm.world) * (kLaneRows * BN) +
+                            static_cast<size_t>(row) * BN + c * CW;
 #pragma unroll
               for (int j8 = 0; j8 < CW; j8 += 8) {
                 uint4 pk;
@@ -1314,7 +1391,58 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
           }
           named_bar_sync(1, 128);
           const int m = lane_idx;
-          if (*last_flag != 0 && row_ok) {
+          if (*last_flag != 0 && cm.nvls) {
+            // The tile slot is one contiguous [128][BN] bf16 array on every rank: the 128 threads
+            // walk it in 16-byte pieces (a warp reads 512 contiguous bytes per request), eight
+            // pieces per thread in flight; the switch returns the fp32-accumulated sum of the
+            // replicas, bias and residual are added, and one multimem.st writes every rank's output.
+            const __nv_bfloat16* base = cm.recv_mc + comm_parity * static_cast<size_t>(cm.parity_stride) +
+                                        static_cast<size_t>(tile) * (kLaneRows * BN);
+            constexpr int PIECES = kLaneRows * BN / 8;       // 16-byte pieces of the tile
+            constexpr int PER_ROW = BN / 8;
+            constexpr int UNR = 8;
+            const int rows_valid = min(kLaneRows, it.tok_valid);
+            const int nfeat = min(BN, it.feat_valid);
+#pragma unroll 1
+            for (int i0 = epi_tid; i0 < rows_valid * PER_ROW; i0 += 128 * UNR) {
+              uint4 a[UNR];
+#pragma unroll
+              for (int u = 0; u < UNR; ++u) {
+                const int i = i0 + u * 128;
+                a[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (i < rows_valid * PER_ROW && i < PIECES && (i % PER_ROW) * 8 < nfeat)
+                  a[u] = multimem_ld_reduce_bf16x8(base + static_cast<size_t>(i) * 8);
+              }
+#pragma unroll
+              for (int u = 0; u < UNR; ++u) {
+                const int i = i0 + u * 128;
+                const int r = i / PER_ROW, j = (i % PER_ROW) * 8;
+                if (i < rows_valid * PER_ROW && j < nfeat) {
+                  const uint32_t w4[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+                  float o[8];
+#pragma unroll
+                  for (int q4 = 0; q4 < 4; ++q4) o[2 * q4] = bf16_lo(w4[q4]), o[2 * q4 + 1] = bf16_hi(w4[q4]);
+                  if (p.bias != nullptr) {
+#pragma unroll
+                    for (int q8 = 0; q8 < 8; ++q8) o[q8] += __bfloat162float(p.bias[it.feat0 + j + q8]);
+                  }
+                  const size_t tok = static_cast<size_t>(it.out_tok0 + r);
+                  if (p.residual != nullptr) {
+                    const uint4 rs = *reinterpret_cast<const uint4*>(p.residual + tok * p.ldr + it.feat0 + j);
+                    const uint32_t r4[4] = {rs.x, rs.y, rs.z, rs.w};
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) o[2 * q4] += bf16_lo(r4[q4]), o[2 * q4 + 1] += bf16_hi(r4[q4]);
+                  }
+                  uint4 pk;
+                  pk.x = pack_bf16(o[0], o[1]);
+                  pk.y = pack_bf16(o[2], o[3]);
+                  pk.z = pack_bf16(o[4], o[5]);
+                  pk.w = pack_bf16(o[6], o[7]);
+                  multimem_st_16(cm.out_mc + tok * p.ldo + it.feat0 + j, pk);
+                }
+              }
+            }
+          } else if (*last_flag != 0 && row_ok) {
             const __nv_bfloat16* base = cm.recv_peer[cm.rank] +
                                         comm_parity * static_cast<size_t>(cm.parity_stride) +
                                         static_cast<size_t>(tile / cm.world) * (kLaneRows * BN) +
@@ -1338,7 +1466,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
             }
           }
           named_bar_sync(1, 128);
-          if (epi_tid < cm.world) signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
+          if (cm.nvls) {
+            if (epi_tid == 0) multimem_signal_add(cm.flags_mc + kCommDoneIdx, 1u);
+          } else if (epi_tid < cm.world) {
+            signal_add_sys(cm.flags_peer[epi_tid] + kCommDoneIdx, 1u);
+          }
         }
       }
       acc ^= 1;
@@ -1583,15 +1715,30 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
       for (int r = 0; r < p.comm.world; ++r) ok = ok && al16(p.comm.recv_peer[r]) && al16(p.comm.out_peer[r]);
     }
     p.vec_ok = ok ? 1 : 0;
+    if (COMM != 0 && p.comm.nvls) {
+      // the multimem forms move 16 bytes: they need the vector layout and aligned multicast addresses
+      bool mc_ok = ok && p.comm.flags_mc != nullptr && (COMM == 3 || al16(p.comm.recv_mc)) &&
+                   (COMM == 1 || al16(p.comm.out_mc));
+      if (COMM == 1) mc_ok = mc_ok && p.comm.recv_mc != nullptr && (p.N % 8 == 0);
+      if (COMM == 2)
+        mc_ok = mc_ok && p.comm.recv_mc != nullptr && p.comm.out_mc != nullptr &&
+                static_cast<long long>(p.tiles_lane) * p.tiles_col * kLaneRows * BN <= p.comm.parity_stride;
+      if (COMM == 3) mc_ok = mc_ok && p.comm.out_mc != nullptr;
+      if (!mc_ok) p.comm.nvls = 0;
+    }
   }
   auto kern = gemm_bf16_kernel<BN, SWAP, GLU, COMM, GROUPED, WQ>;
-  static bool configured = false;
-  if (!configured) {
+  // function attributes are per device: a process that drives several GPUs sets them on each
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!configured[dev]) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
     prefer_max_shared(kern);
-    configured = true;
+    configured[dev] = true;
   }
   return static_cast<int>(launch_kernel(kern, dim3(grid), dim3(gemm_threads(WQ)), smem, stream, ml, mc, p));
 }
@@ -1603,59 +1750,7 @@ using namespace mx;
 extern "C" long long mx_gemm_workspace_bytes(void) { return 64ll << 20; }
 
 namespace {
-struct PendingRowNorm {
-  const float* ssq_in = nullptr;
-  float* ssq_out = nullptr;
-  float eps = 0.f, inv_dim = 0.f;
-};
-thread_local PendingRowNorm g_row_norm;
-
-// Moves the pending request into the launch parameters (one-shot).
-int take_row_norm(mx::GemmParams& p, bool swap, int N, int comm_mode) {
-  const PendingRowNorm r = g_row_norm;
-  g_row_norm = PendingRowNorm{};
-  p.ssq_in = r.ssq_in;
-  p.ssq_out = r.ssq_out;
-  p.ssq_eps = r.eps;
-  p.ssq_inv_dim = r.inv_dim;
-  if (r.ssq_out != nullptr) {
-    if (comm_mode == 2 || comm_mode == 3) return -6;   // producers: plain and one-shot all-reduce only
-    if (swap && (N % 128) != 0) return -6;
-  }
-  if (r.ssq_in != nullptr && comm_mode != 0) return -6;
-  return 0;
-}
-}  // namespace
-
-namespace {
-struct PendingQuant {
-  const void* scales = nullptr;
-  const void* biases = nullptr;
-  int group = 0, wq = 0;
-};
-thread_local PendingQuant g_quant;
-}  // namespace
-
-// Quantized weights for the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread: `w` of that
-// call then points to the weights RE-TILED for this kernel (built once at load time from the
-// checkpoint tensors, mlxcel_b200.ops.quant.tile_for_gemm): block (t, kb) holds 128 rows x
-// (64 * bits / 8) bytes of packed values (rows zero-padded to a multiple of 128), then the
-// block's scales [2 halves of the k-block][128 rows] and, for affine, biases, as extra rows of
-// the same width; blocks are ordered [row tile t][k-block kb]. One TMA box brings a whole block.
-// `scales` / `biases` / `group` of this call are unused (kept for callers of the row-major
-// kernels); ldw is ignored. The kernel dequantises the blocks in its transform warps (M <= 256
-// only; the call returns -9 for larger M, which the caller serves by dequantise + GEMM).
-// wq: 1 affine 4-bit, 2 affine 8-bit, 3 mxfp4 (e2m1 values, e8m0 scale bytes).
-// Replaces the reference's qmm / qmv kernels for M > 8 (mlx/backend/cuda/quantized/qmm_*.cu in its
-// MLX overlay) with a tcgen05 path.
-extern "C" void mx_gemm_set_quant(const void* scales, const void* biases, int group, int wq) {
-  g_quant.scales = scales;
-  g_quant.biases = biases;
-  g_quant.group = group;
-  g_quant.wq = wq;
-}
-
-// Deferred RMSNorm around the NEXT mx_gemm_bf16 / mx_gemm_comm call of this host thread.
+// Deferred RMSNorm request of one call (MxGemmExtras) -> launch parameters.
 //   ssq_in  (consumer): the GEMM input is an un-normalised residual stream whose norm weight was
 //           folded into W; every output row t is multiplied by rsqrt(sum_p ssq_in[p][t] * inv_dim +
 //           eps) before bias / activation.
@@ -1664,21 +1759,50 @@ extern "C" void mx_gemm_set_quant(const void* scales, const void* biases, int gr
 // Buffer layout (fp32 words): [0] partial count (written by the producer), [1] tokens per partial
 // row (set by the owner of the buffer), data from word 8. No counterpart in the reference, where
 // the norm is its own kernel (src/lib/mlxcel-core/cpp/fused_norm.cpp).
-extern "C" void mx_gemm_set_row_norm(const void* ssq_in, float eps, float inv_dim, void* ssq_out) {
-  g_row_norm.ssq_in = static_cast<const float*>(ssq_in);
-  g_row_norm.ssq_out = static_cast<float*>(ssq_out);
-  g_row_norm.eps = eps;
-  g_row_norm.inv_dim = inv_dim;
+int take_row_norm(mx::GemmParams& p, const MxGemmExtras* ex, bool swap, int N, int comm_mode) {
+  if (ex == nullptr) return 0;
+  p.ssq_in = static_cast<const float*>(ex->ssq_in);
+  p.ssq_out = static_cast<float*>(ex->ssq_out);
+  p.ssq_eps = ex->ssq_eps;
+  p.ssq_inv_dim = ex->ssq_inv_dim;
+  if (p.ssq_out != nullptr) {
+    if (comm_mode == 2 || comm_mode == 3) return -6;   // producers: plain and one-shot all-reduce only
+    if (swap && (N % 128) != 0) return -6;
+  }
+  if (p.ssq_in != nullptr && comm_mode != 0) return -6;
+  return 0;
 }
+struct QuantArgs {
+  int group = 0, wq = 0;
+};
+// Quantized weights of one call (MxGemmExtras.wq != 0): `w` then points to the weights RE-TILED
+// for this kernel (built once at load time from the checkpoint tensors,
+// mlxcel_b200.ops.quant.tile_for_gemm): block (t, kb) holds 128 rows x (64 * bits / 8) bytes of
+// packed values (rows zero-padded to a multiple of 128), then the block's scales [2 halves of the
+// k-block][128 rows] and, for affine, biases, as extra rows of the same width; blocks are ordered
+// [row tile t][k-block kb]. One TMA box brings a whole block; ldw is ignored. The kernel
+// dequantises the blocks in its transform warps (M <= 256 only; the call returns -9 for larger M,
+// which the caller serves by dequantise + GEMM).
+// wq: 1 affine 4-bit, 2 affine 8-bit, 3 mxfp4 (e2m1 values, e8m0 scale bytes).
+// Replaces the reference's qmm / qmv kernels for M > 8 (mlx/backend/cuda/quantized/qmm_*.cu in its
+// MLX overlay) with a tcgen05 path.
+QuantArgs take_quant(const MxGemmExtras* ex) {
+  QuantArgs q;
+  if (ex != nullptr) {
+    q.group = ex->q_group;
+    q.wq = ex->wq;
+  }
+  return q;
+}
+}  // namespace
 
 extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void* bias,
                             const void* residual, int M, int N, int K, int ldx, int ldw, int ldo,
                             int ldr, int epilogue, int out_fp32, int glu_offset, float glu_alpha,
                             float glu_limit, void* workspace, long long ws_bytes, int force_mode,
-                            int force_splits, void* stream_) {
+                            int force_splits, void* stream_, const MxGemmExtras* extras) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const PendingQuant quant = g_quant;   // one-shot
-  g_quant = PendingQuant{};
+  const QuantArgs quant = take_quant(extras);
   if (M <= 0 || N <= 0 || K <= 0) return -1;
   if ((K % 8) || (ldx % 8) || (quant.wq == 0 && (ldw % 8))) return -1;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
@@ -1713,9 +1837,7 @@ extern "C" int mx_gemm_bf16(const void* x, const void* w, void* out, const void*
   p.num_kb = (K + kBK - 1) / kBK;
   p.splits = 1;
   p.kb_per_split = p.num_kb;
-  if (const int rn = take_row_norm(p, swap, N, 0); rn != 0) return rn;
-  p.q_scales = quant.scales;
-  p.q_biases = static_cast<const __nv_bfloat16*>(quant.biases);
+  if (const int rn = take_row_norm(p, extras, swap, N, 0); rn != 0) return rn;
   p.q_group = quant.group;
   p.q_groups_per_row = quant.wq != 0 ? K / quant.group : 0;
   p.q_rows = w_rows;
@@ -1828,10 +1950,9 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
                             int ldr, int mode, int rank, int world, const void* const* flags_peer,
                             const void* const* recv_peer, const void* const* out_peer, void* ctl,
                             void* expect, long long parity_stride, long long rank_stride,
-                            void* workspace, long long ws_bytes, void* stream_) {
+                            void* workspace, long long ws_bytes, void* stream_, const MxGemmExtras* extras) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const PendingQuant quant = g_quant;   // one-shot
-  g_quant = PendingQuant{};
+  const QuantArgs quant = take_quant(extras);
   if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
     return -1;
   if ((K % 8) || (ldx % 8) || (quant.wq == 0 && (ldw % 8)) || (N % 8) || (ldo % 8)) return -1;
@@ -1872,9 +1993,13 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
   }
   p.comm.parity_stride = parity_stride;
   p.comm.rank_stride = rank_stride;
-  if (const int rn = take_row_norm(p, swap, N, mode); rn != 0) return rn;
-  p.q_scales = quant.scales;
-  p.q_biases = static_cast<const __nv_bfloat16*>(quant.biases);
+  if (const int rn = take_row_norm(p, extras, swap, N, mode); rn != 0) return rn;
+  if (extras != nullptr && extras->flags_mc != nullptr) {
+    p.comm.nvls = 1;   // withdrawn in launch_gemm when the layout does not allow 16-byte multimem accesses
+    p.comm.flags_mc = static_cast<uint32_t*>(extras->flags_mc);
+    p.comm.recv_mc = static_cast<__nv_bfloat16*>(extras->recv_mc);
+    p.comm.out_mc = static_cast<__nv_bfloat16*>(extras->out_mc);
+  }
   p.q_group = quant.group;
   p.q_groups_per_row = quant.wq != 0 ? K / quant.group : 0;
   p.q_rows = N;
@@ -1963,10 +2088,10 @@ extern "C" int mx_gemm_comm(const void* x, const void* w, void* out, const void*
 extern "C" int mx_grouped_gemm_bf16(const void* x, const void* w, void* out, const void* bias,
                                     const int* expert_offsets, int E, int N, int K, int max_rows,
                                     int epilogue, int glu_offset, float glu_alpha, float glu_limit,
-                                    void* workspace, long long ws_bytes, void* stream_) {
+                                    void* workspace, long long ws_bytes, void* stream_,
+                                    const MxGemmExtras* extras) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const PendingQuant quant = g_quant;   // one-shot
-  g_quant = PendingQuant{};
+  const QuantArgs quant = take_quant(extras);
   if (E <= 0 || N <= 0 || K <= 0 || max_rows <= 0) return 0;
   if ((K % 8) || (N % 8)) return -1;
   if (workspace == nullptr || ws_bytes < MX_WS_PARTIAL_OFFSET) return -2;

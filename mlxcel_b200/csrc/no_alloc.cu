@@ -65,12 +65,40 @@ extern "C" int mx_gemm_bf16_static(const void* x, const void* w, void* out, cons
     scratch = st.ptr[dev];
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  // The array still holds the previous call's words: the status word and the tile arrival
-  // counters have to start at zero, the partial tiles are fully rewritten before they are read.
-  cudaError_t e = cudaMemsetAsync(scratch, 0, MX_WS_COUNTER_OFFSET + MX_WS_COUNTER_BYTES, stream);
+  // The array still holds the previous call's words: the tile arrival counters have to start at
+  // zero, the partial tiles are fully rewritten before they are read. The status word is left
+  // alone: a bounded wait that ran out in an earlier call stays visible until
+  // mx_gemm_bf16_static_status reads (and clears) it.
+  cudaError_t e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + MX_WS_COUNTER_OFFSET, 0,
+                                  MX_WS_COUNTER_BYTES, stream);
   if (e != cudaSuccess) return static_cast<int>(e);
   // force_mode 2: the weight-rows-on-lanes split-K kernel, the one that needs scratch.
   return mx_gemm_bf16(x, w, out, bias, residual, M, N, K, ldx, ldw, ldo, ldr, epilogue, out_fp32,
                       glu_offset, glu_alpha, glu_limit, scratch, MX_STATIC_SCRATCH_BYTES, 2, 0,
-                      stream_);
+                      stream_, nullptr);
+}
+
+extern "C" int mx_gemm_bf16_static_status(int clear) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MX_STATIC_ERR_SYMBOL;
+  StaticScratchState& st = static_scratch_state();
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> g(st.mu);
+    if (!st.ready[dev]) return 0;   // nothing was ever launched through the static entry point here
+    scratch = st.ptr[dev];
+  }
+  // The status word is the first int of the scratch array. A plain synchronous copy: it waits for
+  // the work queued so far on the device, reads four bytes into host memory and allocates nothing.
+  int code = 0;
+  if (cudaMemcpy(&code, static_cast<unsigned char*>(scratch) + MX_WS_STATUS_OFFSET, sizeof(int),
+                 cudaMemcpyDeviceToHost) != cudaSuccess)
+    return MX_STATIC_ERR_SYMBOL;
+  if (clear && code != 0) {
+    const int zero = 0;
+    if (cudaMemcpy(static_cast<unsigned char*>(scratch) + MX_WS_STATUS_OFFSET, &zero, sizeof(int),
+                   cudaMemcpyHostToDevice) != cudaSuccess)
+      return MX_STATIC_ERR_SYMBOL;
+  }
+  return code;
 }

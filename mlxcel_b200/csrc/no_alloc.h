@@ -19,7 +19,8 @@
 //    (cudaGetSymbolAddress, with that device current) and clears its control words. That first
 //    call synchronises with the device, so make it before any stream capture begins.
 //  * Every call shares the one scratch array and the array keeps what the previous call left
-//    in it. Each call re-clears, on the caller's stream, the words that have to start at zero.
+//    in it. Each call re-clears, on the caller's stream, the words that have to start at zero
+//    (the tile counters; the status word is kept until mx_gemm_bf16_static_status clears it).
 //    Two calls whose kernels overlap on the GPU (different streams, no ordering between them)
 //    race on the scratch: order them on one stream or with events.
 //  * The function calls no cudaMalloc / cudaFree and no allocating library routine.
@@ -45,6 +46,15 @@ int mx_gemm_bf16_static(const void* x, const void* w, void* out, const void* bia
                         const void* residual, int M, int N, int K, int ldx, int ldw, int ldo,
                         int ldr, int epilogue, int out_fp32, int glu_offset, float glu_alpha,
                         float glu_limit, void* stream);
+
+// The kernel's waits are bounded: a wait that runs out records a code (1xx pipeline, 2xx flag) in
+// the status word at the start of the scratch array and the kernel returns normally, so the launch
+// itself reports success. This call reads that word for the current device (0 = every launch so
+// far completed normally) and, with clear != 0, resets it. It synchronises with the device (a
+// four-byte copy to the host), allocates nothing, and must not be made during stream capture.
+// While the word is non-zero, later launches give up their waits at once: read and clear it
+// before retrying.
+int mx_gemm_bf16_static_status(int clear);
 
 // Human-readable text for a return code of mx_gemm_bf16_static.
 const char* mx_gemm_bf16_static_error(int code);

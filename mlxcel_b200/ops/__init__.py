@@ -60,15 +60,6 @@ class RowNorm:
     dim: int      # length of the normalised rows (the GEMM's K when nothing is sharded)
 
 
-def _set_row_norm(row_norm, ssq_out) -> None:
-    if row_norm is None and ssq_out is None:
-        return
-    _lib.load().mx_gemm_set_row_norm(row_norm.ssq.buf.data_ptr() if row_norm is not None else None,
-                                     float(row_norm.eps) if row_norm is not None else 0.0,
-                                     1.0 / row_norm.dim if row_norm is not None else 0.0,
-                                     ssq_out.buf.data_ptr() if ssq_out is not None else None)
-
-
 def row_ssq(x: torch.Tensor, ssq: SsqBuffer) -> None:
     """Starts a deferred-RMSNorm chain: sums of squares of the rows of ``x`` (one partial)."""
     rows, dim = x.shape
@@ -99,11 +90,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         return out
     epi = EPI_RESIDUAL if residual is not None else (EPI_BIAS if bias is not None else EPI_NONE)
     ws = _lib.workspace(x.device)
-    _set_row_norm(row_norm, ssq_out)
+    ex = _lib.gemm_extras(row_norm=row_norm, ssq_out=ssq_out)
     _lib_call("mx_gemm_bf16", x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias),
               _lib.ptr(residual), M, N, K, x.stride(0), w.stride(0), out.stride(0),
               residual.stride(0) if residual is not None else 0, epi, 1 if out_fp32 else 0, 0,
-              0.0, 0.0, ws.data_ptr(), ws.numel(), force_mode, force_splits, _lib.stream())
+              0.0, 0.0, ws.data_ptr(), ws.numel(), force_mode, force_splits, _lib.stream(),
+              _lib.ref_or_null(ex))
     return out
 
 
@@ -123,10 +115,11 @@ def glu_linear(x: torch.Tensor, w: torch.Tensor, inter: int, act: str = "silu",
     if M == 0:
         return out
     ws = _lib.workspace(x.device)
-    _set_row_norm(row_norm, None)
+    ex = _lib.gemm_extras(row_norm=row_norm)
     _lib_call("mx_gemm_bf16", x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias), None, M,
               inter, K, x.stride(0), w.stride(0), out.stride(0), 0, epi, 0, inter, float(alpha),
-              float(limit), ws.data_ptr(), ws.numel(), force_mode, force_splits, _lib.stream())
+              float(limit), ws.data_ptr(), ws.numel(), force_mode, force_splits, _lib.stream(),
+              _lib.ref_or_null(ex))
     return out
 
 

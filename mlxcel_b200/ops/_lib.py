@@ -61,10 +61,11 @@ _f = ctypes.c_float
 def _declare(lib) -> None:
     sig = {
         "mx_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f,
-                         _vp, _ll, _i, _i, _vp],
+                         _vp, _ll, _i, _i, _vp, _vp],
         "mx_gemm_comm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp,
-                         _vp, _vp, _vp, _ll, _ll, _vp, _ll, _vp],
-        "mx_allreduce_comm": [_vp, _vp, _vp, _ll, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp],
+                         _vp, _vp, _vp, _ll, _ll, _vp, _ll, _vp, _vp],
+        "mx_allreduce_comm": [_vp, _vp, _vp, _ll, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp,
+                              _vp, _vp, _vp],
         "mx_row_ssq": [_vp, _i, _i, _ll, _vp, _vp],
         "mx_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
         "mx_head_rmsnorm": [_vp, _vp, _i, _i, _i, _ll, _f, _vp],
@@ -91,7 +92,7 @@ def _declare(lib) -> None:
         "mx_moe_combine_n": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
         "mx_qmv": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
         "mx_grouped_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _ll,
-                                 _vp],
+                                 _vp, _vp],
     }
     for name, args in sig.items():
         fn = getattr(lib, name, None)
@@ -108,18 +109,41 @@ def _declare(lib) -> None:
     if fn is not None:
         fn.restype = _ll
         fn.argtypes = [_i, _i, _i, _i]
-    fn = getattr(lib, "mx_gemm_set_quant", None)
-    if fn is not None:
-        fn.restype = None
-        fn.argtypes = [_vp, _vp, _i, _i]
-    fn = getattr(lib, "mx_gemm_set_row_norm", None)
-    if fn is not None:
-        fn.restype = None
-        fn.argtypes = [_vp, _f, _f, _vp]
     fn = getattr(lib, "mx_build_info", None)
     if fn is not None:
         fn.restype = ctypes.c_char_p
         fn.argtypes = []
+
+
+class GemmExtras(ctypes.Structure):
+    """Mirror of ``MxGemmExtras`` (csrc/api.h): the optional per-call arguments of the GEMM entry
+    points — packed-weight format, deferred-RMSNorm buffers, NVLS multicast addresses."""
+
+    _fields_ = [("wq", _i), ("q_group", _i), ("ssq_in", _vp), ("ssq_out", _vp), ("ssq_eps", _f),
+                ("ssq_inv_dim", _f), ("flags_mc", _vp), ("recv_mc", _vp), ("out_mc", _vp)]
+
+
+def gemm_extras(wq: int = 0, q_group: int = 0, row_norm=None, ssq_out=None, flags_mc: int = 0,
+                recv_mc: int = 0, out_mc: int = 0):
+    """Builds the extras argument of one GEMM call (``None`` when the call needs none). The returned
+    object must stay referenced until the call returns (pass ``ctypes.byref`` of it)."""
+    if not (wq or row_norm is not None or ssq_out is not None or flags_mc):
+        return None
+    ex = GemmExtras()
+    ex.wq, ex.q_group = int(wq), int(q_group)
+    if row_norm is not None:
+        ex.ssq_in = row_norm.ssq.buf.data_ptr()
+        ex.ssq_eps = float(row_norm.eps)
+        ex.ssq_inv_dim = 1.0 / row_norm.dim
+    if ssq_out is not None:
+        ex.ssq_out = ssq_out.buf.data_ptr()
+    if flags_mc:
+        ex.flags_mc, ex.recv_mc, ex.out_mc = flags_mc or None, recv_mc or None, out_mc or None
+    return ex
+
+
+def ref_or_null(ex):
+    return ctypes.byref(ex) if ex is not None else None
 
 
 class KernelError(RuntimeError):

@@ -139,10 +139,11 @@ def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_o
         wq = {("affine", 4): 1, ("mxfp4", 4): 3}.get((w.mode, w.bits), 0)
         if wq and quant._FUSED_QGEMM and K % 64 == 0 and w.group_size in (32, 64, 128):
             tiles = quant.tile_experts_for_gemm(w, n_out if act else None)
-            lib.mx_gemm_set_quant(None, None, w.group_size, wq)
+            ex = _lib.gemm_extras(wq=wq, q_group=w.group_size)
             rc = lib.mx_grouped_gemm_bf16(xs.data_ptr(), tiles.data_ptr(), out.data_ptr(), _lib.ptr(bias),
                                           offsets.data_ptr(), E, n_out, K, rows, epi, n_out if act else 0,
-                                          float(alpha), float(limit), ws.data_ptr(), ws.numel(), _lib.stream())
+                                          float(alpha), float(limit), ws.data_ptr(), ws.numel(), _lib.stream(),
+                                          _lib.ref_or_null(ex))
             if rc != -9:
                 _lib.count_launch()
                 _lib.check(rc, "mx_grouped_gemm_bf16 (packed experts)")
@@ -150,7 +151,7 @@ def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_o
         w = quant.dequantize(w)
     rc = lib.mx_grouped_gemm_bf16(xs.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias),
                                   offsets.data_ptr(), E, n_out, K, rows, epi, n_out if act else 0,
-                                  float(alpha), float(limit), ws.data_ptr(), ws.numel(), _lib.stream())
+                                  float(alpha), float(limit), ws.data_ptr(), ws.numel(), _lib.stream(), None)
     _lib.count_launch()
     _lib.check(rc, "mx_grouped_gemm_bf16")
     return out

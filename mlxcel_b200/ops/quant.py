@@ -259,12 +259,10 @@ def tile_experts_for_gemm(qt: QuantizedTensor, glu_inter: int | None = None) -> 
     return tiles
 
 
-def set_quant(qt: QuantizedTensor, wq: int):
-    """Announce re-tiled packed weights to the next GEMM call (see mx_gemm_set_quant); returns the
-    pointer to pass as ``w``."""
+def quant_extras(qt: QuantizedTensor, wq: int, **kw):
+    """(pointer to the re-tiled packed weights, extras describing them) for one GEMM call."""
     tiles = tile_for_gemm(qt)
-    _lib.load().mx_gemm_set_quant(None, None, qt.group_size, wq)
-    return tiles.data_ptr()
+    return tiles.data_ptr(), _lib.gemm_extras(wq=wq, q_group=qt.group_size, **kw)
 
 
 def _fused_qgemm(x, qt, wq, out, bias, residual, inter=None, act=None, alpha=1.702, limit=7.0):
@@ -281,11 +279,11 @@ def _fused_qgemm(x, qt, wq, out, bias, residual, inter=None, act=None, alpha=1.7
         epi = _ACT_TO_EPI[act]
     ws = _lib.workspace(x.device)
     lib = _lib.load()
-    w_ptr = set_quant(qt, wq)
+    w_ptr, ex = quant_extras(qt, wq)
     rc = lib.mx_gemm_bf16(x.data_ptr(), w_ptr, out.data_ptr(), _lib.ptr(bias), _lib.ptr(residual), M, N, K,
                           x.stride(0), 0, out.stride(0),
                           residual.stride(0) if residual is not None else 0, epi, 0, inter or 0, float(alpha),
-                          float(limit), ws.data_ptr(), ws.numel(), 0, 0, _lib.stream())
+                          float(limit), ws.data_ptr(), ws.numel(), 0, 0, _lib.stream(), _lib.ref_or_null(ex))
     _lib.count_launch()
     _lib.check(rc, "mx_gemm_bf16 (packed weights)")
     return out

@@ -4,7 +4,10 @@ One allocation per rank from ``torch.distributed._symmetric_memory`` (CUDA VMM m
 handles are exchanged at rendezvous) gives every rank the device addresses of every peer's
 buffer. Regions are carved at identical offsets on all ranks, so "the same tensor on rank r" is
 ``peer_base[r] + offset``. Kernels use plain peer loads/stores and ``red.release.sys`` /
-``ld.acquire.sys`` flags on these addresses — never TMA from a peer's memory.
+``ld.acquire.sys`` flags on these addresses — never TMA from a peer's memory. Where the
+allocation also has an NVSwitch multicast mapping (NVLS), ``mc_base + offset`` names the same
+region on ALL ranks at once and the kernels use ``multimem.ld_reduce`` / ``multimem.st`` /
+``multimem.red`` on it (``MLXCEL_B200_NVLS=0`` keeps the peer-store protocol).
 
 Channel layout (per fused op kind): 4 control words + 8193 consumed-arrival words (local use) +
 8193 arrival flags (written by peers) + an optional double-buffered receive area.
@@ -13,6 +16,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -42,6 +46,20 @@ class SymmetricHeap:
         self.handle = symm_mem.rendezvous(self.buf, group.group_name if hasattr(group, "group_name") else group)
         self.peer_base = [int(p) for p in self.handle.buffer_ptrs]
         assert self.peer_base[self.rank] == self.buf.data_ptr()
+        # NVLS: multicast address of the same buffer (0 when the fabric / driver has no multicast
+        # support or the mapping was not created)
+        self.mc_base = 0
+        if os.environ.get("MLXCEL_B200_NVLS", "1") != "0":
+            try:
+                mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+            except Exception:
+                mc = 0
+            self.mc_base = mc
+        # every rank must take the same protocol: all ranks need the mapping
+        flag = torch.tensor([1 if self.mc_base else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 0:
+            self.mc_base = 0
         self.offset = 0
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
@@ -58,6 +76,10 @@ class SymmetricHeap:
     def view(self, offset: int, shape, dtype) -> torch.Tensor:
         n = math.prod(shape) * _ELEM[dtype]
         return self.buf[offset:offset + n].view(dtype).view(*shape)
+
+    def mc_ptr(self, offset: int) -> int:
+        """Multicast address of a region (0 without NVLS)."""
+        return self.mc_base + offset if self.mc_base else 0
 
     def peer_ptrs(self, offset: int):
         """ctypes array of this region's address on every rank."""
@@ -76,12 +98,14 @@ class _Channel:
         self.expect = words[_CTL_WORDS:_CTL_WORDS + _MAX_TILES + 8]
         self.flags_off = self.ctl_off + 4 * (_CTL_WORDS + _MAX_TILES + 8)
         self.flags_peer = heap.peer_ptrs(self.flags_off)
+        self.flags_mc = heap.mc_ptr(self.flags_off)
         self.recv_bytes = recv_bytes
         if recv_bytes:
             self.recv_off = heap.alloc(2 * recv_bytes)
             self.recv_peer = heap.peer_ptrs(self.recv_off)
+            self.recv_mc = heap.mc_ptr(self.recv_off)
         else:
-            self.recv_off, self.recv_peer = 0, None
+            self.recv_off, self.recv_peer, self.recv_mc = 0, None, 0
 
     def reset(self) -> None:
         self.heap.view(self.ctl_off, (_CHANNEL_WORDS,), torch.int32).zero_()
@@ -126,9 +150,12 @@ class FusedOps:
         # replicated residual stream and gathered logits live in the heap
         self.h_off = heap.alloc(max_tokens * hidden * 2)
         self.h_peer = heap.peer_ptrs(self.h_off)
+        self.h_mc = heap.mc_ptr(self.h_off)
         self.vocab_cap = vocab
         self.logits_off = heap.alloc(small_m * vocab * 2)
         self.logits_peer = heap.peer_ptrs(self.logits_off)
+        self.logits_mc = heap.mc_ptr(self.logits_off)
+        self.nvls = bool(heap.mc_base)
         torch.cuda.synchronize(heap.device)
         dist.barrier(group=heap.group)
 
@@ -164,23 +191,24 @@ class FusedOps:
         res = residual  # read locally by the reducing rank; may alias `out` (in-place update)
         if ssq_out is not None:
             assert mode == 1, "per-tile sums of squares come out of the one-shot epilogue only"
-            from .. import ops
-            ops._set_row_norm(None, ssq_out)
+        mc = dict(flags_mc=ch.flags_mc, recv_mc=ch.recv_mc, out_mc=self.h_mc) if self.nvls else {}
         if qt is not None:
             # packed weights: dequantised by the kernel's transform warps (one-shot all-reduce only),
             # i.e. quantized GEMV/GEMM -> all-reduce in one kernel
             from ..ops import quant
             wq = quant.fused_wq(qt, M, K)
             assert wq and mode == 1, "fused quantized row-parallel GEMM: covered formats, M <= 256"
-            w_ptr, ldw = quant.set_quant(qt, wq), 0
+            w_ptr, ex = quant.quant_extras(qt, wq, ssq_out=ssq_out, **mc)
+            ldw = 0
         else:
             w_ptr, ldw = w.data_ptr(), w.stride(0)
+            ex = _lib.gemm_extras(ssq_out=ssq_out, **mc)
         rc = lib.mx_gemm_comm(x.data_ptr(), w_ptr, out.data_ptr(), _lib.ptr(bias), _lib.ptr(res),
                               M, N, K, x.stride(0), ldw, out.stride(0),
                               res.stride(0) if res is not None else 0, mode, self.rank, self.world,
                               ch.flags_peer, ch.recv_peer, self.h_peer, ch.ctl.data_ptr(),
                               ch.expect.data_ptr(), self.world * stride, stride, ws.data_ptr(),
-                              ws.numel(), _lib.stream())
+                              ws.numel(), _lib.stream(), _lib.ref_or_null(ex))
         _lib.count_launch()
         _lib.check(rc, "mx_gemm_comm")
         return out
@@ -199,9 +227,11 @@ class FusedOps:
             if x.dim() != 2 or x.shape[0] > self.max_tokens or x.shape[1] > self.hidden:
                 raise ValueError("all_reduce shape exceeds the symmetric buffers")
             out = self.hidden_buffer(x.shape[0], x.shape[1])
+        mc = (ch.flags_mc, ch.recv_mc, self.h_mc) if self.nvls else (None, None, None)
         rc = lib.mx_allreduce_comm(x.data_ptr(), _lib.ptr(residual), out.data_ptr(), n, mode, self.rank,
                                    self.world, ch.flags_peer, ch.recv_peer, self.h_peer, ch.ctl.data_ptr(),
-                                   ch.expect.data_ptr(), self.world * stride, stride, ws.data_ptr(), _lib.stream())
+                                   ch.expect.data_ptr(), self.world * stride, stride, ws.data_ptr(), _lib.stream(),
+                                   *mc)
         _lib.count_launch()
         _lib.check(rc, "mx_allreduce_comm")
         return out
@@ -216,10 +246,12 @@ class FusedOps:
         ws = _lib.workspace(x.device)
         out = self.heap.view(self.logits_off, (M, self.world * N), torch.bfloat16)
         ch = self.ch_ag
+        ex = _lib.gemm_extras(flags_mc=ch.flags_mc, out_mc=self.logits_mc) if self.nvls else None
         rc = lib.mx_gemm_comm(x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias), None, M, N, K,
                               x.stride(0), w.stride(0), out.stride(0), 0, 3, self.rank, self.world,
                               ch.flags_peer, None, self.logits_peer, ch.ctl.data_ptr(),
-                              ch.expect.data_ptr(), 0, 0, ws.data_ptr(), ws.numel(), _lib.stream())
+                              ch.expect.data_ptr(), 0, 0, ws.data_ptr(), ws.numel(), _lib.stream(),
+                              _lib.ref_or_null(ex))
         _lib.count_launch()
         _lib.check(rc, "mx_gemm_comm")
         return out

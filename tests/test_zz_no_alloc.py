@@ -38,6 +38,15 @@ def _symbol():
     return fn, err
 
 
+def _status(clear: int = 1) -> int:
+    """The bounded-wait status word of the library's own scratch array (0 = every launch completed)."""
+    from mlxcel_b200.ops import _lib
+
+    lib = ctypes.CDLL(str(_lib.lib_path()))
+    lib.mx_gemm_bf16_static_status.argtypes, lib.mx_gemm_bf16_static_status.restype = [ctypes.c_int], ctypes.c_int
+    return lib.mx_gemm_bf16_static_status(clear)
+
+
 def test_static_scratch_gemm_matches_regular_entry_point_twice():
     from mlxcel_b200 import ops
 
@@ -60,6 +69,40 @@ def test_static_scratch_gemm_matches_regular_entry_point_twice():
             torch.cuda.synchronize()
             _close(out, want)
             assert torch.equal(out, want), f"call {call}: split-K sum order must match"
+            # and against plain PyTorch in fp32 (the regular entry point runs the same kernel)
+            _close(out, x.float() @ w.float().t() + res.float())
+            assert _status() == 0
+
+
+def test_static_scratch_gemm_other_shapes_against_fp32():
+    """Two column tiles (M = 192), a gated epilogue, and a shape whose preferred split count does not
+    fit the 8 MiB array (the dispatcher trims it), each against the fp32 product, twice."""
+    from mlxcel_b200 import ops
+
+    fn, err = _symbol()
+    dev = torch.device("cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=dev).manual_seed(1)
+    for (M, N, K, gated) in [(192, 512, 2048, False), (40, 256, 1024, True), (256, 3072, 4096, False)]:
+        x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+        rows = 2 * N if gated else N
+        w = (torch.randn(rows, K, generator=g, device=dev) * 0.03).to(torch.bfloat16)
+        acc = x.float() @ w.float().t()
+        if gated:
+            want32 = torch.nn.functional.silu(acc[:, :N]) * acc[:, N:]
+            want = ops.glu_linear(x, w, N, "silu", force_mode=2)
+        else:
+            want32 = acc
+            want = ops.linear(x, w, force_mode=2)
+        for call in range(2):
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+            rc = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), None, None, M, N, K, K, K, N, 0,
+                    3 if gated else 0, 0, N if gated else 0, 0.0, 0.0, stream)
+            assert rc == 0, err(rc)
+            torch.cuda.synchronize()
+            _close(out, want32, rtol=3e-2, atol=3e-2)
+            _close(out, want)
+            assert _status() == 0
 
 
 def test_static_scratch_gemm_refuses_oversize():
