@@ -28,9 +28,12 @@ def _add_model_args(p):
     p.add_argument("--block-size", type=int, default=16)
     p.add_argument("--no-prompt-cache", action="store_true")
     p.add_argument("--no-cuda-graphs", action="store_true")
+    p.add_argument("--no-warmup", action="store_true", help="serve: skip the one-token request made before listening")
     p.add_argument("--dequantize", action="store_true", help="dequantize quantized checkpoints at load")
-    p.add_argument("--tp", type=int, default=1)
-    p.add_argument("--pp", type=int, default=1)
+    p.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (launch with torch.distributed.run)")
+    p.add_argument("--pp", type=int, default=1, help="pipeline stages; world size = tp * pp")
+    p.add_argument("--pp-layers", default=None, help="comma-separated layer counts per stage (default: equal split)")
+    p.add_argument("--pp-micro-batches", type=int, default=2, help="micro-batches a step is cut into")
     p.add_argument("--draft-model", default=None)
     p.add_argument("--draft-max", type=int, default=4)
     p.add_argument("--prompt-lookup", action="store_true")
@@ -47,7 +50,7 @@ _COMPAT_NOOPS = [("-ngl", "--n-gpu-layers", "--gpu-layers"), ("-t", "--threads")
                  ("-to", "--timeout"), ("--cache-reuse",), ("--defrag-thold",), ("-sm", "--split-mode"), ("-mg", "--main-gpu"),
                  ("--numa",), ("--poll",), ("--threads-http",)]
 _COMPAT_NOOP_SWITCHES = [("--mlock",), ("--no-mmap",), ("-fa", "--flash-attn"), ("-cb", "--cont-batching"),
-                         ("-nocb", "--no-cont-batching"), ("--no-warmup",), ("--jinja",), ("--metrics",), ("--slots",),
+                         ("-nocb", "--no-cont-batching"), ("--jinja",), ("--metrics",), ("--slots",),
                          ("--no-slots",), ("--no-webui",), ("--no-context-shift",), ("--context-shift",), ("--no-kv-offload",),
                          ("--embeddings", "--embedding"), ("--reranking", "--rerank"), ("--props",), ("--log-disable",)]
 
@@ -132,19 +135,32 @@ def load_llm(a):
     from .llm import LLM
 
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    # several processes (torch.distributed.run): pick this rank's GPU and join the job
+    from .parallel.control import init_distributed
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    tp, pp = max(1, int(getattr(a, "tp", 1))), max(1, int(getattr(a, "pp", 1)))
+    if tp * pp > 1 and world != tp * pp:
+        raise SystemExit(f"--tp {tp} --pp {pp} needs {tp * pp} processes: launch with "
+                         f"`python -m torch.distributed.run --nproc-per-node {tp * pp} -m mlxcel_b200.cli ...`")
+    if world > 1 and tp * pp == 1:
+        raise SystemExit(f"{world} processes were launched but neither --tp nor --pp was given")
+    a._control_group = None
+    if world > 1:
+        dev, a._control_group = init_distributed(dev)
     ecfg = EngineConfig(max_batch=a.parallel, max_num_batched_tokens=a.max_batch_tokens,
                         prefill_chunk_alone=a.prefill_chunk_size, prefill_chunk_contended=min(512, a.prefill_chunk_size),
                         block_size=a.block_size, kv_bits=a.kv_bits or 16, num_blocks=a.kv_cache_blocks,
                         prefix_cache=not a.no_prompt_cache, max_model_len=a.ctx_size,
                         cuda_graphs=not a.no_cuda_graphs and dev != "cpu")
     comm = None
-    if a.tp > 1:
+    if pp > 1:
+        return _load_pipeline(a, dev, ecfg, tp, pp)
+    if tp > 1:
         import torch.distributed as dist
 
-        if not dist.is_initialized():
-            raise SystemExit("--tp N needs a launch with torch.distributed.run --nproc-per-node N")
         from .parallel.tp import TPComm
-        comm = TPComm(dist.group.WORLD, torch.device(dev), backend="fused")
+        on_gpu = str(dev).startswith("cuda")
+        comm = TPComm(dist.group.WORLD, torch.device(dev), backend="fused" if on_gpu else "nccl")
     if a.model.startswith("preset:"):
         dtype = torch.bfloat16 if dev != "cpu" else torch.float32
         llm = LLM.from_preset(a.model.split(":", 1)[1], device=dev, engine_config=ecfg, comm=comm, dtype=dtype)
@@ -155,6 +171,62 @@ def load_llm(a):
                                   surgery=getattr(a, "surgery", None), config_overrides=config_overrides(a))
     attach_drafter(llm, a, dev)
     return llm
+
+
+def _load_pipeline(a, dev, ecfg, tp: int, pp: int):
+    """``--pp P`` (optionally with ``--tp T``): rank = stage * T + tp_rank; every stage holds a contiguous
+    layer range (``--pp-layers`` or an equal split), tensor-parallel inside the stage over its own
+    process group, activations between stages over send / recv (reference
+    src/distributed/pipeline/runtime.rs:100-199, partition*.rs)."""
+    import torch
+    import torch.distributed as dist
+
+    from .config import ModelConfig, preset
+    from .llm import LLM
+    from .loading.shard import partition_layers
+    from .models.weights import random_weights
+    from .parallel.pp import PipelineContext, PipelineModel
+    from .parallel.tp import TPComm
+
+    rank = dist.get_rank()
+    stage, tp_rank = rank // tp, rank % tp
+    tp_group = None
+    for st in range(pp):                              # every rank creates every group, in the same order
+        grp = dist.new_group(list(range(st * tp, (st + 1) * tp)))
+        if st == stage:
+            tp_group = grp
+    on_gpu = str(dev).startswith("cuda")
+    comm = TPComm(tp_group, torch.device(dev), backend="fused" if on_gpu else "nccl") if tp > 1 else None
+    is_preset = a.model.startswith("preset:")
+    cfg = preset(a.model.split(":", 1)[1]) if is_preset else ModelConfig.from_path(a.model, config_overrides(a))
+    if getattr(a, "pp_layers", None):
+        counts = [int(x) for x in str(a.pp_layers).split(",")]
+        if len(counts) != pp or sum(counts) != cfg.num_hidden_layers or min(counts) < 1:
+            raise SystemExit(f"--pp-layers {a.pp_layers}: expected {pp} positive counts summing to {cfg.num_hidden_layers}")
+        ranges, lo = [], 0
+        for c in counts:
+            ranges.append(range(lo, lo + c))
+            lo += c
+    else:
+        ranges = partition_layers(cfg.num_hidden_layers, pp)
+    if is_preset:
+        dtype = torch.bfloat16 if on_gpu else torch.float32
+        w = random_weights(cfg, seed=0, dtype=dtype, device=dev, tp_rank=tp_rank, tp_size=tp, ep_rank=tp_rank,
+                           ep_size=tp, layers=ranges[stage], vocab_parallel=tp > 1 and cfg.vocab_size % tp == 0)
+        from .tokenizer import ByteTokenizer
+        tok = ByteTokenizer(cfg.vocab_size)
+    else:
+        from .loading.checkpoint import load_model_weights
+        from .tokenizer import load_tokenizer
+        w = load_model_weights(a.model, cfg, device=dev, comm=comm, dequantize=a.dequantize, layers=ranges[stage],
+                               surgery=getattr(a, "surgery", None), dtype=torch.bfloat16 if on_gpu else torch.float32)
+        tok = load_tokenizer(a.model)
+    ctx = PipelineContext(dist.group.WORLD, stage, pp, tp_size=tp, tp_rank=tp_rank)
+    model = PipelineModel(cfg, w, ctx, comm=comm, num_micro=max(1, int(getattr(a, "pp_micro_batches", 2))),
+                          layer_range=ranges[stage], kv_bits=ecfg.kv_bits)
+    if getattr(a, "draft_model", None) or getattr(a, "prompt_lookup", False):
+        raise SystemExit("speculative decoding is not available with --pp (the drafter needs the last stage's state)")
+    return LLM(cfg, w, ecfg, comm=comm, tokenizer=tok, model=model)
 
 
 def config_overrides(a) -> dict | None:
@@ -241,9 +313,13 @@ def cmd_generate(a):
     det = IncrementalDetokenizer(tk, ids)
     t0 = time.perf_counter()
 
+    lead = int(os.environ.get("RANK", "0")) == 0      # several ranks run the same request in lockstep; one prints
+
     def on_token(seq, tok):
-        sys.stdout.write(det.push(tok))
-        sys.stdout.flush()
+        piece = det.push(tok)
+        if lead:
+            sys.stdout.write(piece)
+            sys.stdout.flush()
 
     mask_fn = None
     grammar = open(a.grammar_file).read() if getattr(a, "grammar_file", None) else getattr(a, "grammar", None)
@@ -260,6 +336,9 @@ def cmd_generate(a):
     while llm.engine.has_work():
         llm.engine.step()
     s = llm.engine.seqs[sid]
+    if not lead:
+        _leave_distributed()
+        return
     sys.stdout.write(det.flush() + "\n")
     dt = time.perf_counter() - t0
     ttft = (s.first_token_time - s.arrival) if s.first_token_time else 0.0
@@ -270,6 +349,23 @@ def cmd_generate(a):
     if llm.engine.drafter is not None:
         print(f"[speculative: {st['spec_rounds']} verify rounds, {st['spec_accepted']} of {st['spec_drafted']} drafts "
               f"accepted]", file=sys.stderr)
+    _leave_distributed()
+
+
+def _leave_distributed() -> None:
+    """End of a multi-process command: meet the other ranks once more, then leave without tearing
+    the communicator down under live symmetric-memory mappings (seen to block for minutes)."""
+    if int(os.environ.get("WORLD_SIZE", "1")) <= 1:
+        return
+    import torch
+    import torch.distributed as dist
+    if dist.is_initialized():
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 REPL_HELP = """Available commands:
@@ -609,13 +705,29 @@ def cmd_serve(a):
         uvicorn.run(app, host=a.host, port=a.port, log_level="info" if a.verbose else "warning")
         return
     llm = load_llm(a)
-    worker = ModelWorker(llm.engine, llm.tokenizer, a.alias or os.path.basename(a.model.rstrip("/")))
+    control = None
+    if getattr(a, "_control_group", None) is not None:
+        # several processes serve the model together: rank 0 listens, schedules and broadcasts a step
+        # descriptor per engine step; the other ranks run the executor loop (parallel/control.py)
+        from .parallel.control import ControlPlane
+        control = ControlPlane(a._control_group)
+    budget = a.reasoning_budget if a.reasoning_budget is not None else os.environ.get(
+        "LLAMA_ARG_THINK_BUDGET", os.environ.get("LLAMA_ARG_REASONING_BUDGET"))
+    worker = ModelWorker(llm.engine, llm.tokenizer, a.alias or os.path.basename(a.model.rstrip("/")), control=control,
+                         hang_timeout=float(a.decode_hang_timeout), failfast=True)
+    if control is not None and not control.is_leader:
+        worker.follow()
+        _leave_distributed()
+        return
+    if not a.no_warmup:
+        _startup_warmup(worker, llm)
     keys = set(a.api_key or [])
     if a.api_key_file:
         keys |= {l.strip() for l in open(a.api_key_file) if l.strip()}
     state = ServerState(worker, llm.tokenizer, worker.model_id, api_keys=keys,
                         chat_template=open(a.chat_template_file).read() if a.chat_template_file else None)
     state.slot_save_path = a.slot_save_path
+    state.default_thinking_budget = int(budget) if budget not in (None, "") else None
     from .lora import LoraManager
     from .models.weights import QuantizedTensor
     if not any(isinstance(lw.wqkv, QuantizedTensor) for lw in llm.model.w.layers):
@@ -626,6 +738,30 @@ def cmd_serve(a):
             state.lora.add(path, float(sc) if sc else 1.0)
     uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="info" if a.verbose else "warning",
                 ssl_certfile=a.ssl_cert_file, ssl_keyfile=a.ssl_key_file)
+
+
+def _startup_warmup(worker, llm) -> None:
+    """One short greedy request before the listener opens (the reference's start-up warm-up,
+    src/server/startup.rs:2237): kernels are loaded, tensor maps and CUDA graphs for batch 1 exist and
+    the first client does not pay for them. Skipped with --no-warmup."""
+    import queue as _q
+
+    from .engine import SamplingParams
+    from .server.worker import GenRequest
+    out: _q.Queue = _q.Queue()
+    bos = [i for i in (getattr(llm.tokenizer, "bos_id", None),) if i is not None] or [0]
+    worker.submit(GenRequest(prompt_ids=bos * 4, params=SamplingParams(max_tokens=2, ignore_eos=True), out=out,
+                             request_id="warmup"))
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < 600:
+        try:
+            ev = out.get(timeout=1.0)
+        except _q.Empty:
+            continue
+        if ev.kind in ("done", "error"):
+            if ev.kind == "error":
+                print(f"warm-up request failed: {ev.error}", file=sys.stderr)
+            return
 
 
 def cmd_router(a):
@@ -760,6 +896,10 @@ def main(argv=None):
     p.add_argument("--estimate-memory", action="store_true",
                    help="print the memory estimate for this model and these options, then exit")
     p.add_argument("--no-preflight", action="store_true", help="start even when the estimate does not fit the GPU")
+    p.add_argument("--reasoning-budget", type=int, default=None,
+                   help="default thinking-token budget of requests that give none (-1 unlimited, 0 close at once)")
+    p.add_argument("--decode-hang-timeout", type=float, default=0.0,
+                   help="seconds after which a step that has not returned fails its requests (0 = off)")
     p.add_argument("--ssl-cert-file", default=None)
     p.add_argument("--ssl-key-file", default=None)
     p.add_argument("-v", "--verbose", action="store_true")

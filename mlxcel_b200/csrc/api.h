@@ -166,13 +166,15 @@ int mx_argmax(const void* logits, int logits_fp32, long long row_stride, int* ou
               void* stream);
 
 // Fused sampler over [B, V] logits. Per-row parameters: temperature (0 = greedy), top_k
-// (0 = off), top_p (1 = off), min_p (0 = off). Filters are evaluated on the untempered
-// softmax, the draw uses Gumbel-max noise from a Philox-4x32-10 stream keyed by
-// (seed[row], step[row]). logit_bias: optional [B, V] or NULL. out_logprob: optional [B].
+// (0 = off), top_p (1 = off), min_p (0 = off), top_n_sigma (0 = off; optional array), typical_p
+// (1 = off; optional array). Chain: top-k -> top-p -> min-p -> top-n-sigma on the untempered
+// softmax, then typical-p on what survived; the draw uses Gumbel-max noise from a
+// Philox-4x32-10 stream keyed by (seed[row], step[row]). out_logprob: optional [B].
 int mx_sample(const void* logits, int logits_fp32, long long row_stride, const float* temperature,
-              const int* top_k, const float* top_p, const float* min_p,
-              const unsigned long long* seeds, const unsigned long long* steps, int* out_tokens,
-              float* out_logprob, float* scratch, int B, int V, void* stream);
+              const int* top_k, const float* top_p, const float* min_p, const float* typical_p,
+              const float* top_n_sigma, const unsigned long long* seeds,
+              const unsigned long long* steps, int* out_tokens, float* out_logprob, int B, int V,
+              void* stream);
 long long mx_sample_scratch_floats(int B, int V);
 
 // Repetition / frequency / presence penalties applied in place to fp32 or bf16 logits, given

@@ -2,7 +2,7 @@
 // penalties and the speculative-decoding verify walk. One CTA per logits row; every pass
 // streams the row from L2 with 16-byte loads, nothing is sorted.
 //
-// top-k / top-p / min-p thresholds are found by bisection over the order-preserving integer
+// top-k / top-p / min-p / typical-p cuts are found by bisection over the order-preserving integer
 // image of the float logits (32 rounds, each a count or a probability-mass reduction), so the
 // kept set is exact and deterministic, ties included. The draw is softmax-free: argmax of
 // logit / T + Gumbel noise from Philox-4x32-10 keyed by (seed, step, element index).
@@ -139,6 +139,7 @@ __global__ void __launch_bounds__(kSampThreads)
 sample_kernel(const void* __restrict__ logits, long long row_stride,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ min_p,
+              const float* __restrict__ typical_p, const float* __restrict__ top_n_sigma,
               const unsigned long long* __restrict__ seeds,
               const unsigned long long* __restrict__ steps, int* __restrict__ out_tokens,
               float* __restrict__ out_logprob, int V) {
@@ -150,6 +151,8 @@ sample_kernel(const void* __restrict__ logits, long long row_stride,
   const int k = top_k ? top_k[b] : 0;
   const float tp = top_p ? top_p[b] : 1.f;
   const float mp = min_p ? min_p[b] : 0.f;
+  const float typ = typical_p ? typical_p[b] : 1.f;
+  const float nsig = top_n_sigma ? top_n_sigma[b] : 0.f;
 
   // pass 1: max
   ArgMax best{-INFINITY, 0x7fffffff};
@@ -211,8 +214,68 @@ sample_kernel(const void* __restrict__ logits, long long row_stride,
     const uint32_t key = float_key(m + __logf(mp));
     thr = max(thr, key);
   }
+  if (nsig > 0.f) {
+    // top-n-sigma: keep logits within nsig standard deviations (unbiased, over the finite logits of
+    // the whole row) of the maximum
+    float s1 = 0.f, s2 = 0.f, cnt = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float l = sane(load_logit<FP32>(row, i));
+      if (l > -INFINITY) {
+        const float d = l - m;
+        s1 += d, s2 += d * d, cnt += 1.f;
+      }
+    }
+    s1 = block_sum(s1, red_f);
+    s2 = block_sum(s2, red_f);
+    cnt = block_sum(cnt, red_f);
+    if (cnt > 1.5f) {
+      const float var = fmaxf(0.f, (s2 - s1 * s1 / cnt) / (cnt - 1.f));
+      thr = max(thr, float_key(m - nsig * sqrtf(var)));
+    }
+  }
   // Never filter out the most likely token.
   thr = min(thr, float_key(m));
+
+  // typical-p (locally typical sampling) on the distribution that survived the filters above:
+  // tokens are ranked by |(-log p) - H| and the smallest set reaching typical_p of the mass is
+  // kept. The cut is found by bisection over the bit pattern of that (non-negative) deviation.
+  float typ_logzk = 0.f, typ_ent = 0.f;
+  uint32_t typ_cut = 0xFFFFFFFFu;
+  const bool use_typ = typ < 1.f;
+  if (use_typ) {
+    float zk = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float l = sane(load_logit<FP32>(row, i));
+      if (float_key(l) >= thr && l > -INFINITY) zk += __expf(l - m);
+    }
+    zk = block_sum(zk, red_f);
+    typ_logzk = __logf(zk);
+    float ent = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float l = sane(load_logit<FP32>(row, i));
+      if (float_key(l) >= thr && l > -INFINITY) {
+        const float lp = l - m - typ_logzk;
+        ent -= __expf(lp) * lp;
+      }
+    }
+    typ_ent = block_sum(ent, red_f);
+    // largest cut with mass{dev < cut} < typ; then mass{dev <= cut} >= typ
+    uint32_t cut = 0u;
+    for (int bit = 30; bit >= 0; --bit) {
+      const uint32_t cand = cut | (1u << bit);
+      float mass = 0.f;
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float l = sane(load_logit<FP32>(row, i));
+        if (float_key(l) >= thr && l > -INFINITY) {
+          const float lp = l - m - typ_logzk;
+          if (__float_as_uint(fabsf(-lp - typ_ent)) < cand) mass += __expf(lp);
+        }
+      }
+      mass = block_sum(mass, red_f);
+      if (mass < typ) cut = cand;
+    }
+    typ_cut = cut;
+  }
 
   // draw: argmax(l / T + gumbel)
   const unsigned long long seed = seeds ? seeds[b] : 0ull;
@@ -229,7 +292,10 @@ sample_kernel(const void* __restrict__ logits, long long row_stride,
       const int i = gidx * 4 + j;
       if (i < V) {
         const float l = sane(load_logit<FP32>(row, i));
-        if (float_key(l) >= thr && l > -INFINITY) {
+        bool in = float_key(l) >= thr && l > -INFINITY;
+        if (in && use_typ)
+          in = __float_as_uint(fabsf(-(l - m - typ_logzk) - typ_ent)) <= typ_cut || i == best.i;
+        if (in) {
           const float g = -__logf(-__logf(u01(c[j])));
           pick = argmax_combine(pick, ArgMax{l * invT + g, i});
         }
@@ -313,19 +379,19 @@ extern "C" long long mx_sample_scratch_floats(int, int) { return 0; }
 
 extern "C" int mx_sample(const void* logits, int logits_fp32, long long row_stride,
                          const float* temperature, const int* top_k, const float* top_p,
-                         const float* min_p, const unsigned long long* seeds,
-                         const unsigned long long* steps, int* out_tokens, float* out_logprob,
-                         float*, int B, int V, void* stream_) {
+                         const float* min_p, const float* typical_p, const float* top_n_sigma,
+                         const unsigned long long* seeds, const unsigned long long* steps,
+                         int* out_tokens, float* out_logprob, int B, int V, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (B <= 0) return 0;
   if (logits_fp32)
     sample_kernel<true><<<B, kSampThreads, 0, stream>>>(logits, row_stride, temperature, top_k,
-                                                        top_p, min_p, seeds, steps, out_tokens,
-                                                        out_logprob, V);
+                                                        top_p, min_p, typical_p, top_n_sigma, seeds,
+                                                        steps, out_tokens, out_logprob, V);
   else
     sample_kernel<false><<<B, kSampThreads, 0, stream>>>(logits, row_stride, temperature, top_k,
-                                                         top_p, min_p, seeds, steps, out_tokens,
-                                                         out_logprob, V);
+                                                         top_p, min_p, typical_p, top_n_sigma, seeds,
+                                                         steps, out_tokens, out_logprob, V);
   return static_cast<int>(cudaGetLastError());
 }
 

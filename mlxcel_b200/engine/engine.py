@@ -48,6 +48,11 @@ class Sequence:
     on_token: Callable | None = None
     mask_fn: Callable | None = None   # structured output: fn(seq) -> bool mask [V] or None
     user_data: object = None
+    think_open: bool = False          # inside a reasoning block (thinking budget bookkeeping)
+    think_count: int = 0              # tokens generated inside the current block
+    think_forced: int = 0             # end-of-thinking tokens this engine forced
+    draft_n: int = 0                  # speculative decoding: drafted / accepted tokens of this request
+    draft_n_accepted: int = 0
 
     @property
     def tokens(self) -> list[int]:
@@ -95,6 +100,11 @@ class Engine:
             # per-sequence recurrent state lives in the model, not in the block pool: a cached prefix has
             # no state to resume from, and the state slot indices change from step to step
             e.prefix_cache = e.cuda_graphs = e.lookahead = False
+        self.pipeline = getattr(model, "ctx", None) is not None
+        if self.pipeline:
+            # stages exchange activations with send / recv inside the forward pass: no graph capture,
+            # and the token ids come back from the last stage, so nothing can be fed back on the device
+            e.cuda_graphs = e.lookahead = False
         if e.num_blocks <= 0:
             e.num_blocks = self._auto_num_blocks(tp, nl)
         # fp32 models (CPU oracles) keep fp32 keys / values; everything else stores bf16 (or 8-bit)
@@ -113,6 +123,8 @@ class Engine:
         self._graphs: dict[tuple, tuple] = {}
         self.drafter = None          # speculative drafter (see mlxcel_b200.speculative)
         self.spec_k = 4              # block size K: K-1 draft tokens + 1 bonus token per round
+        self._last_spec = self._spec_now = False
+        self._evicted: list[Sequence] = []   # rows the scheduler had to end (pool exhausted), reported by step()
         self._alloc_buffers()
         self.stats = dict(steps=0, decode_steps=0, prefill_tokens=0, decode_tokens=0, preemptions=0,
                           graph_replays=0, prefix_hit_tokens=0, h2d_bytes=0, d2h_bytes=0,
@@ -129,7 +141,12 @@ class Engine:
         else:
             n = 2048
         need = (e.max_model_len // e.block_size + 2) * e.max_batch * 2
-        return max(64, min(n, need))
+        n = max(64, min(n, need))
+        if tp > 1 or getattr(self.model, "ctx", None) is not None:
+            # every rank sizes the pool from its own free memory; schedulers in lockstep need one size
+            from ..parallel.control import agree_min
+            n = agree_min(n)
+        return n
 
     def _alloc_buffers(self) -> None:
         e = self.ecfg
@@ -174,10 +191,24 @@ class Engine:
             raise ValueError(f"prompt of {len(prompt)} tokens exceeds max_model_len {self.ecfg.max_model_len}")
         if len(self.waiting) >= self.ecfg.max_queue_depth:
             raise RuntimeError("queue full")
+        # a prompt that cannot fit the KV pool even when it runs alone would park forever
+        bs = self.ecfg.block_size
+        usable = self.ecfg.num_blocks - int(self.ecfg.num_blocks * self.ecfg.watermark) - 1
+        if (len(prompt) + 1 + bs - 1) // bs > usable:
+            raise ValueError(f"prompt of {len(prompt)} tokens needs {(len(prompt) + bs) // bs} KV blocks; "
+                             f"the pool has {usable} usable blocks of {bs} tokens")
         sid = self._next_id
         self._next_id += 1
         s = Sequence(sid, list(prompt), params, arrival=time.perf_counter(), on_token=on_token,
                      mask_fn=mask_fn, user_data=user_data)
+        if params.thinking_cap is not None and params.think_start_id is not None:
+            # a generation prompt may already have opened the reasoning block
+            for t in reversed(prompt):
+                if t == params.think_end_id:
+                    break
+                if t == params.think_start_id:
+                    s.think_open = True
+                    break
         self.seqs[sid] = s
         if params.priority > 0:
             # priority lanes: insert before the first lower-priority request
@@ -249,7 +280,9 @@ class Engine:
                 i += 1
                 continue
             if not (e.preemption and self._preempt_one()):
-                raise RuntimeError("KV pool exhausted and nothing to preempt")
+                # nothing left to reclaim: the row has reached what the pool can hold
+                self._finish(s, FinishReason.LENGTH)
+                self._evicted.append(s)
             decode = [s for s in self.running if s.status == SeqStatus.DECODING]
             i = 0
         parked = [s for s in self.running if s.status == SeqStatus.PREFILLING]
@@ -261,12 +294,20 @@ class Engine:
         st.decode_ticks_since_prefill_grant = self._decode_ticks_since_grant
         st.prefill_grant_interval = e.prefill_grant_interval
         st.mixed_steps = e.mixed_steps
+        # A verify round alternates with classic work (admission, a parked prefill): the tick policy
+        # never grants two rounds in a row while classic work waits (tick_policy.rs:284-356).
+        st.speculative_ready = (self.drafter is not None and bool(decode)
+                                and all(self._spec_row_ok(s) for s in decode))
+        st.last_was_speculative = self._last_spec
         if self.waiting:
             nxt = self.waiting[0]
             st.blocks_available = self.bm.can_allocate(
                 self.bm.blocks_needed(nxt.seq_id, nxt.total_len + 1) if self.bm.has_seq(nxt.seq_id)
                 else (nxt.total_len + e.block_size) // e.block_size, True)
         d = decide_tick(st)
+        self._last_spec = self._spec_now = d.action == TickAction.SpeculativeRound
+        if self._spec_now:
+            return decode, []
         pieces: list[tuple[Sequence, int, int]] = []
         run_decode = d.action in (TickAction.Decode, TickAction.MixedStep)
         run_prefill = d.action in (TickAction.Prefill, TickAction.MixedStep)
@@ -309,6 +350,10 @@ class Engine:
                         self.bm.free_seq(s.seq_id)
                         s.status, s.num_computed = SeqStatus.QUEUED, 0
                         self.waiting.appendleft(s)
+                    elif len(self.running) == 1 and not decode_rows:
+                        # a lone parked prefill that cannot get its next blocks would park forever
+                        self._finish(s, FinishReason.ERROR)
+                        self._evicted.append(s)
                     break
                 if s not in self.running:
                     self.running.append(s)
@@ -460,8 +505,8 @@ class Engine:
         for s in decode:
             p = s.params
             if not (p.greedy and not p.needs_history and not p.logit_bias and s.mask_fn is None
-                    and not p.logprobs):
-                return False
+                    and not p.logprobs and p.thinking_cap is None):
+                return False       # (a forced end-of-thinking token cannot be fed back on the device)
         return True
 
     def _can_pipeline(self, inf) -> bool:
@@ -575,14 +620,22 @@ class Engine:
             self._inflight = nxt
             return fin
         decode, pieces = self._schedule()
+        if self._evicted:
+            ended, self._evicted = self._evicted, []
+            if not decode and not pieces:
+                return ended
+            return ended + self._run_scheduled(decode, pieces)
+        return self._run_scheduled(decode, pieces)
+
+    def _run_scheduled(self, decode, pieces) -> list[Sequence]:
         if not decode and not pieces:
             return []
         if self._lookahead_eligible(decode, pieces):
             self._inflight = self._launch_lookahead(decode, from_device=False)
             if self._inflight is not None:
                 return []
-        if (self.drafter is not None and decode and not pieces and
-                all(s.params.greedy and s.mask_fn is None and not s.params.needs_history for s in decode)):
+        if self._spec_now:
+            self._spec_now = False
             return self._spec_step(decode)
         b, R = self._build_batch(decode, pieces)
         nd = len(decode)
@@ -601,7 +654,10 @@ class Engine:
                 logits = self.model.forward(b, self.pool.layers)
         # rows: decode rows first, then prefill rows that completed their prompt
         sample_seqs = list(decode) + [s for (s, start, cnt) in pieces if start + cnt >= s.total_len]
-        toks, lps = self.sampler.sample(logits, sample_seqs)
+        if self.pipeline:
+            toks, lps = self.model.sample_and_share(logits, sample_seqs, self.sampler)
+        else:
+            toks, lps = self.sampler.sample(logits, sample_seqs)
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += nd
         self.stats["prefill_tokens"] += sum(p[2] for p in pieces)
@@ -612,7 +668,7 @@ class Engine:
             s.num_computed = s.total_len
         now = time.perf_counter()
         for i, s in enumerate(sample_seqs):
-            tok = int(toks[i])
+            tok = self._thinking_override(s, int(toks[i]))
             if s.status == SeqStatus.PREFILLING:
                 s.status = SeqStatus.DECODING
             if s.first_token_time is None:
@@ -626,6 +682,30 @@ class Engine:
                 self._finish(s, reason)
                 finished.append(s)
         return finished
+
+    def _thinking_override(self, s: Sequence, tok: int) -> int:
+        """Thinking-budget enforcement on the sampled token (the reference's scheduler hook,
+        src/server/batch/scheduler/run_loop.rs:58-71 with the rules of src/server/thinking_budget.rs):
+        inside a reasoning block the tokens are counted, and once the cap is reached the next token
+        is replaced by the end-of-thinking token. The forced token is an ordinary generated token
+        afterwards (streamed, counted, part of the history)."""
+        p = s.params
+        cap = p.thinking_cap
+        if cap is None:
+            return tok
+        if s.think_open:
+            if tok == p.think_end_id:
+                s.think_open = False
+            elif s.think_count >= cap:
+                s.think_open = False
+                s.think_forced += 1
+                self.stats["thinking_forced"] = self.stats.get("thinking_forced", 0) + 1
+                return p.think_end_id
+            else:
+                s.think_count += 1
+        elif p.think_start_id is not None and tok == p.think_start_id:
+            s.think_open, s.think_count = True, 0
+        return tok
 
     def _finish_step(self, s: Sequence, tok: int, lp) -> FinishReason | None:
         """Shared finish rule: an EOS / stop token is not pushed to the output
@@ -648,6 +728,14 @@ class Engine:
         return None
 
     # ------------------------------------------------------------------ speculative decoding
+    @staticmethod
+    def _spec_row_ok(s: Sequence) -> bool:
+        """Greedy acceptance (draft == argmax of the target) is exact only for rows that decode
+        greedily without per-step logit edits."""
+        p = s.params
+        return (p.greedy and s.mask_fn is None and not p.needs_history and not p.logit_bias
+                and not p.logprobs and p.thinking_cap is None)
+
     def _spec_step(self, decode: list[Sequence]) -> list[Sequence]:
         """One verify round for every decoding row (the reference's verify_round,
         src/lib/mlxcel-core/src/engine/verify_round.rs:170-305 and mtp/walk.rs:15-95): forward
@@ -667,20 +755,36 @@ class Engine:
         need_h = getattr(self.drafter, "needs_hidden", False)
         h = self.model.forward_hidden(b, self.pool.layers)
         logits = self.model.logits(h, b.logits_rows)
-        target = ops.argmax(logits).cpu().tolist()
+        walk = None
+        if logits.is_cuda and K > 1 and all(len(drafts[s.seq_id]) == K - 1 for s in decode):
+            # every row carries a full block: argmax + accept walk on the device, and the host reads
+            # back two ints per row (accepted length, token at the first mismatch) instead of the
+            # K target tokens of every row
+            dt = torch.tensor([drafts[s.seq_id] for s in decode], dtype=torch.int32).to(logits.device, non_blocking=True)
+            _, acc, nxt = ops.spec_verify(logits.view(len(decode), K, logits.shape[-1]), dt)
+            walk = torch.stack([acc, nxt]).cpu().tolist()
+            self.stats["d2h_bytes"] += 8 * len(decode)
+        else:
+            target = ops.argmax(logits).cpu().tolist()
         self.stats["steps"] += 1
         self.stats["spec_rounds"] += 1
         finished, now, row0 = [], time.perf_counter(), 0
         accepted_info = []
-        for (s, start, cnt) in pieces:
+        for i, (s, start, cnt) in enumerate(pieces):
             d = drafts[s.seq_id]
-            tgt = target[row0:row0 + cnt]
-            a = 0
-            while a < len(d) and d[a] == tgt[a]:
-                a += 1
-            emitted = d[:a] + [tgt[a]]
+            if walk is not None:
+                a = int(walk[0][i])
+                emitted = d[:a] + [int(walk[1][i])]
+            else:
+                tgt = target[row0:row0 + cnt]
+                a = 0
+                while a < len(d) and d[a] == tgt[a]:
+                    a += 1
+                emitted = d[:a] + [tgt[a]]
             self.stats["spec_drafted"] += len(d)
             self.stats["spec_accepted"] += a
+            s.draft_n += len(d)
+            s.draft_n_accepted += a
             if hasattr(self.drafter, "record"):
                 self.drafter.record(s.seq_id, len(d), a)
             L = s.total_len

@@ -63,7 +63,13 @@ class SamplingParams:
     loop_max_pattern: int = 0
     loop_min_pattern: int = 4
     loop_min_count: int = 8
+    # Thinking-token budget (src/server/thinking_budget.rs): None or -1 = unbounded, 0 = the first
+    # reasoning token is replaced by the end-of-thinking token, N > 0 = at most N tokens inside the
+    # block (the opening token is not counted), after which the next token is forced to be the
+    # end-of-thinking token. The ids come from the tokenizer (filled in by the front end).
     thinking_budget: int | None = None
+    think_start_id: int | None = None
+    think_end_id: int | None = None
     priority: int = 0
 
     @property
@@ -73,14 +79,22 @@ class SamplingParams:
         return self.top_k == 1 or (self.temperature <= 0.0 and self.dynatemp_range <= 0.0)
 
     @property
+    def thinking_cap(self) -> int | None:
+        """Effective cap of the reasoning block, or None when nothing has to be enforced."""
+        b = self.thinking_budget
+        if b is None or int(b) < 0 or self.think_end_id is None:
+            return None
+        return int(b)
+
+    @property
     def needs_history(self) -> bool:
         return (self.repetition_penalty != 1.0 or self.frequency_penalty != 0.0 or
                 self.presence_penalty != 0.0 or self.dry_multiplier > 0.0)
 
     @property
     def fused_eligible(self) -> bool:
-        """Rows whose chain is exactly bias/penalties → top-k/top-p/min-p → temperature draw can
-        go through the fused CUDA sampler; the rest take the extended chain."""
-        return (self.typical_p >= 1.0 and self.top_n_sigma <= 0.0 and self.xtc_probability <= 0.0 and
+        """Rows whose chain is bias/penalties → top-k/top-p/min-p/top-n-sigma → typical-p →
+        temperature draw go through the fused CUDA sampler; the rest take the extended chain."""
+        return (self.xtc_probability <= 0.0 and
                 self.mirostat == 0 and self.dynatemp_range <= 0.0 and self.dry_multiplier <= 0.0 and
                 not self.logit_bias and self.top_logprobs == 0)

@@ -3,9 +3,10 @@
 Chain order follows the reference (docs/architecture.md:48-51 and
 src/lib/mlxcel-core/src/generate.rs:1296-1340): token bias and penalties → top-k / top-p / min-p
 evaluated on the untempered distribution → one temperature scale applied only to the final draw.
-Rows whose parameters are expressible by the fused kernel go through ``ops.sample`` in one launch
-(``fused_eligible``); the rest (typical-p, top-n-sigma, XTC, mirostat, dynamic temperature, DRY,
-top-logprobs) take the extended chain below, row by row, on device tensors.
+Rows whose parameters are expressible by the fused kernel (top-k, top-p, min-p, top-n-sigma,
+typical-p, temperature) go through ``ops.sample`` in one launch (``fused_eligible``); the rest
+(XTC, mirostat, dynamic temperature, DRY, top-logprobs) take the extended chain below, row by
+row, on device tensors.
 """
 from __future__ import annotations
 
@@ -75,11 +76,16 @@ class Sampler:
             tk = torch.tensor([seqs[i].params.top_k for i in fused], dtype=torch.int32)
             tp = torch.tensor([seqs[i].params.top_p for i in fused], dtype=torch.float32)
             mp = torch.tensor([seqs[i].params.min_p for i in fused], dtype=torch.float32)
+            ty = ns = None
+            if any(seqs[i].params.typical_p < 1.0 or seqs[i].params.top_n_sigma > 0.0 for i in fused):
+                ty = torch.tensor([seqs[i].params.typical_p for i in fused], dtype=torch.float32)
+                ns = torch.tensor([seqs[i].params.top_n_sigma for i in fused], dtype=torch.float32)
             seeds = torch.tensor([_seed_of(seqs[i]) for i in fused], dtype=torch.int64)
             steps = torch.tensor([len(seqs[i].output) for i in fused], dtype=torch.int64)
             d = work.device
             t, lp = ops.sample(sel.contiguous(), temp.to(d), tk.to(d), tp.to(d), mp.to(d), seeds.to(d),
-                               steps.to(d))
+                               steps.to(d), ty.to(d) if ty is not None else None,
+                               ns.to(d) if ns is not None else None)
             t, lp = t.cpu().tolist(), lp.cpu().tolist()
             for j, i in enumerate(fused):
                 toks[i], lps[i] = t[j], lp[j]

@@ -18,13 +18,16 @@ from .models.weights import ModelWeights, random_weights
 
 class LLM:
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, engine_config: EngineConfig | None = None,
-                 comm=None, tokenizer=None, fold_norms: bool = False):
+                 comm=None, tokenizer=None, fold_norms: bool = False, model=None):
         """``fold_norms``: the weights belong to this object alone, so the executor may fold the
-        RMSNorm weights into the projections in place (deferred RMSNorm, see DecoderModel)."""
+        RMSNorm weights into the projections in place (deferred RMSNorm, see DecoderModel).
+        ``model``: an executor built by the caller (a pipeline stage) instead of the default one."""
         self.cfg = cfg
         if engine_config is not None:
             cfg.extra.setdefault("served_context", int(engine_config.max_model_len))
-        if cfg.model_type in ("mamba", "mamba2", "nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "falcon_h1", "lfm2"):
+        if model is not None:
+            self.model = model
+        elif cfg.model_type in ("mamba", "mamba2", "nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "falcon_h1", "lfm2"):
             from .models.hybrid import HybridModel
             from .models.mamba1 import Mamba1Model
             from .models.mamba2 import Mamba2Model

@@ -294,19 +294,20 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
            top_p: torch.Tensor, min_p: torch.Tensor, seeds: torch.Tensor,
-           steps: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+           steps: torch.Tensor, typical_p: torch.Tensor | None = None,
+           top_n_sigma: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """Fused filter + Gumbel-max draw. Per-row parameter tensors live on the logits' device:
-    temperature/top_p/min_p fp32, top_k int32, seeds/steps int64 (read as uint64)."""
+    temperature/top_p/min_p/typical_p/top_n_sigma fp32, top_k int32, seeds/steps int64 (read as uint64)."""
     if not logits.is_cuda:
-        return ref.sample(logits, temperature, top_k, top_p, min_p, seeds, steps)
+        return ref.sample(logits, temperature, top_k, top_p, min_p, seeds, steps, typical_p, top_n_sigma)
     B, V = logits.shape
     toks = torch.empty(B, dtype=torch.int32, device=logits.device)
     lps = torch.empty(B, dtype=torch.float32, device=logits.device)
     if B:
         _lib_call("mx_sample", logits.data_ptr(), 1 if logits.dtype == torch.float32 else 0,
                   logits.stride(0), temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(),
-                  min_p.data_ptr(), seeds.data_ptr(), steps.data_ptr(), toks.data_ptr(),
-                  lps.data_ptr(), None, B, V, _lib.stream())
+                  min_p.data_ptr(), _lib.ptr(typical_p), _lib.ptr(top_n_sigma), seeds.data_ptr(),
+                  steps.data_ptr(), toks.data_ptr(), lps.data_ptr(), B, V, _lib.stream())
     return toks, lps
 
 

@@ -79,7 +79,7 @@ def _declare(lib) -> None:
                                 _i, _i, _i, _f, _vp, _vp],
         "mx_embedding": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "mx_argmax": [_vp, _i, _ll, _vp, _i, _i, _vp],
-        "mx_sample": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+        "mx_sample": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
         "mx_apply_penalties": [_vp, _i, _ll, _vp, _i, _vp, _vp, _vp, _i, _i, _vp],
         "mx_spec_verify": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
         "mx_swiglu": [_vp, _vp, _i, _i, _i, _f, _f, _vp],

@@ -336,7 +336,33 @@ def filter_mask(logits_row: torch.Tensor, top_k: int, top_p: float, min_p: float
     return keep
 
 
-def sample(logits, temperature, top_k, top_p, min_p, seeds, steps):
+def typical_mask(l: torch.Tensor, keep: torch.Tensor, typical_p: float) -> torch.Tensor:
+    """Locally typical filter on the kept distribution: rank by |(-log p) - H|, keep the smallest
+    set whose mass reaches ``typical_p`` (the most likely token always stays)."""
+    lk = torch.where(keep & (l > float("-inf")), l, torch.full_like(l, float("-inf")))
+    logp = torch.log_softmax(lk.double(), 0)
+    p = logp.exp()
+    ent = -(p * torch.where(p > 0, logp, torch.zeros_like(logp))).sum()
+    dev = torch.where(p > 0, (-logp - ent).abs(), torch.full_like(logp, float("inf")))
+    order = torch.argsort(dev, stable=True)
+    cum = torch.cumsum(p[order], 0)
+    last = int((cum < typical_p).sum())
+    out = torch.zeros_like(keep)
+    out[order[: last + 1]] = True
+    # tokens tied with the cut belong to the set as well (the kernel cuts by value, not by rank)
+    out |= (dev <= dev[order[min(last, dev.numel() - 1)]]) & (p > 0)
+    out[l.argmax()] = True
+    return out & keep
+
+
+def sigma_mask(l: torch.Tensor, n_sigma: float) -> torch.Tensor:
+    fin = l[torch.isfinite(l)]
+    if fin.numel() < 2:
+        return torch.ones_like(l, dtype=torch.bool)
+    return l >= l.max() - n_sigma * fin.std()
+
+
+def sample(logits, temperature, top_k, top_p, min_p, seeds, steps, typical_p=None, top_n_sigma=None):
     """Row-wise sampler with the same Philox/Gumbel stream as the CUDA kernel."""
     B, V = logits.shape
     toks = torch.zeros(B, dtype=torch.int32)
@@ -350,6 +376,11 @@ def sample(logits, temperature, top_k, top_p, min_p, seeds, steps):
             t = int(l.argmax())
         else:
             keep = filter_mask(l, k, float(top_p[b]), float(min_p[b]))
+            if top_n_sigma is not None and float(top_n_sigma[b]) > 0:
+                keep &= sigma_mask(l, float(top_n_sigma[b]))
+                keep[l.argmax()] = True
+            if typical_p is not None and float(typical_p[b]) < 1.0:
+                keep = typical_mask(l, keep, float(typical_p[b]))
             g = gumbel_noise(V, int(seeds[b]), int(steps[b]))
             score = torch.where(keep & (l > float("-inf")), l / T + g, torch.full_like(l, float("-inf")))
             t = int(score.argmax())

@@ -5,8 +5,8 @@ every stage and only the residual stream ``[tokens, hidden]`` moves between stag
 batch is cut into micro-batches along sequences; stage s works on micro-batch i+1 while stage
 s+1 works on micro-batch i (GPipe-style fill/drain, the reference's schedule in
 src/distributed/pipeline/schedule.rs), sends are issued on a side stream so they overlap the next
-micro-batch's compute. The last stage computes the logits and broadcasts them so that all ranks
-sample the same tokens. Where the reference moves JSON+base64 tensors over TCP
+micro-batch's compute. The last stage computes the logits, samples, and broadcasts the sampled
+token ids so that every rank's scheduler advances identically. Where the reference moves JSON+base64 tensors over TCP
 (src/distributed/pipeline/runtime.rs:1081-1207), stages here are GPUs of one NVSwitch domain.
 
 With tensor parallelism inside a stage (TP × PP) rank = stage * tp + tp_rank; a rank exchanges
@@ -116,13 +116,28 @@ class PipelineModel(DecoderModel):
             else:
                 with span("pp.send", cat="pipeline", stage=ctx.stage, micro=i):
                     self._send(h)
-        V = self.cfg.vocab_size
-        if ctx.is_last:
-            logits = self.logits(h_full, b.logits_rows).contiguous()
-        else:
-            logits = torch.empty(R, V, dtype=self.w.final_norm.dtype, device=self.device)
         if ctx.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(ctx.comm_stream)
-        # every rank samples from the same logits
-        dist.broadcast(logits, ctx.last_stage_rank0 + (ctx.tp_rank if ctx.is_last else 0) * 0, group=ctx.group)
-        return logits
+        # only the last stage has logits; the sampled token ids are what travels back
+        # (see sample_and_share), not [rows, vocab] logits
+        return self.logits(h_full, b.logits_rows).contiguous() if ctx.is_last else None
+
+    def sample_and_share(self, logits, seqs, sampler):
+        """Sample on the last stage and broadcast the token ids (and log-probabilities when a row
+        asks for them) to every rank: R * 4 bytes per step instead of R * vocab logits."""
+        ctx = self.ctx
+        R = len(seqs)
+        want_lp = any(s.params.logprobs for s in seqs)
+        if ctx.is_last:
+            toks, lps = sampler.sample(logits, seqs)
+            t = torch.tensor(toks, dtype=torch.int32, device=self.device)
+            lp = torch.tensor([float(x) if x is not None else 0.0 for x in (lps or [0.0] * R)],
+                              dtype=torch.float32, device=self.device) if want_lp else None
+        else:
+            t = torch.empty(R, dtype=torch.int32, device=self.device)
+            lp = torch.empty(R, dtype=torch.float32, device=self.device) if want_lp else None
+        dist.broadcast(t, ctx.last_stage_rank0, group=ctx.group)
+        if lp is not None:
+            dist.broadcast(lp, ctx.last_stage_rank0, group=ctx.group)
+        ctx.stats["token_bytes"] = ctx.stats.get("token_bytes", 0) + 4 * R
+        return t.cpu().tolist(), (lp.cpu().tolist() if lp is not None else None)

@@ -165,7 +165,7 @@ def create_app(state: ServerState) -> FastAPI:
             return _err(400, "action must be save, restore or erase")
         t0 = time.perf_counter()
         if action == "erase":
-            n = state.worker.run_exclusive(lambda: state.worker.engine.bm.reset_prefix_cache())
+            n = state.worker.run_exclusive(lambda: state.worker.engine.bm.reset_prefix_cache(), name="cache_reset")
             return dict(id_slot=slot_id, n_erased=n)
         if not state.slot_save_path:
             return _err(501, "This server does not support slots action. Start it with `--slot-save-path`",

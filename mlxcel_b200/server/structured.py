@@ -41,6 +41,8 @@ class Constraint:
         import llguidance
         import llguidance.hf
 
+        # what rebuilds this constraint elsewhere (follower ranks of a multi-process engine)
+        self.spec = dict(json_schema=json_schema, regex=regex, lark=lark, gbnf=gbnf, json_object=json_object)
         tk = getattr(tokenizer, "tk", None)
         if tk is None:
             raise ValueError("structured output needs an HF tokenizer")

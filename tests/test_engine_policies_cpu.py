@@ -1,0 +1,97 @@
+"""Engine policies on the CPU path: thinking-token budget, speculative rounds alternating with
+classic work, and requests that exceed what the KV pool can hold."""
+import pytest
+import torch
+
+from mlxcel_b200.config import preset
+from mlxcel_b200.engine import Engine, EngineConfig, FinishReason, SamplingParams
+from mlxcel_b200.models.decoder import DecoderModel
+from mlxcel_b200.models.weights import random_weights
+from mlxcel_b200.speculative import DraftModelDrafter
+
+
+def _engine(**kw):
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, seed=4, dtype=torch.float32, std=0.05)
+    base = dict(max_batch=4, max_num_batched_tokens=128, num_blocks=96, max_model_len=384, cuda_graphs=False)
+    base.update(kw)
+    return cfg, w, Engine(DecoderModel(cfg, w), cfg, EngineConfig(**base))
+
+
+START, END = 1000, 1001    # stand-ins for <think> / </think> (the random model never needs to emit them)
+
+
+def _prompt(cfg, n=12, seed=2):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 900, (n,), generator=g).tolist()
+
+
+@pytest.mark.parametrize("budget", [0, 5])
+def test_thinking_budget_forces_the_end_token(budget):
+    """The prompt opens the reasoning block; after ``budget`` tokens inside it the next token is the
+    end-of-thinking token, and sampling resumes normally afterwards (thinking_budget.rs value rules)."""
+    cfg, w, eng = _engine()
+    free = eng.generate([_prompt(cfg) + [START]], SamplingParams(max_tokens=12, ignore_eos=True))[0].output
+    assert END not in free
+    cfg, w, eng = _engine()
+    sp = SamplingParams(max_tokens=12, ignore_eos=True, thinking_budget=budget, think_start_id=START, think_end_id=END)
+    s = eng.generate([_prompt(cfg) + [START]], sp)[0]
+    assert s.output[:budget] == free[:budget]            # untouched up to the cap
+    assert s.output[budget] == END and s.think_forced == 1
+    assert s.output.count(END) == 1 and len(s.output) == 12
+    assert eng.stats["thinking_forced"] == 1
+
+
+def test_thinking_budget_unbounded_and_outside_block():
+    cfg, w, eng = _engine()
+    base = eng.generate([_prompt(cfg)], SamplingParams(max_tokens=10, ignore_eos=True))[0].output
+    for b in (None, -1):
+        cfg, w, eng = _engine()
+        sp = SamplingParams(max_tokens=10, ignore_eos=True, thinking_budget=b, think_start_id=START, think_end_id=END)
+        assert eng.generate([_prompt(cfg) + [START]], sp)[0].think_forced == 0
+    # a budget without an open block changes nothing
+    cfg, w, eng = _engine()
+    sp = SamplingParams(max_tokens=10, ignore_eos=True, thinking_budget=2, think_start_id=START, think_end_id=END)
+    assert eng.generate([_prompt(cfg)], sp)[0].output == base
+
+
+def test_prompt_larger_than_the_pool_is_refused_and_long_rows_end_by_length():
+    cfg, w, eng = _engine(num_blocks=4, max_model_len=384)
+    with pytest.raises(ValueError, match="KV blocks"):
+        eng.add_request(list(range(100)), SamplingParams(max_tokens=4))
+    # fits at first, then outgrows the pool while decoding: ends with LENGTH instead of spinning
+    cfg, w, eng = _engine(num_blocks=4, max_model_len=384)
+    s = eng.generate([_prompt(cfg, 20)], SamplingParams(max_tokens=200, ignore_eos=True))[0]
+    assert s.finish_reason == FinishReason.LENGTH and 0 < len(s.output) < 200
+    assert not eng.has_work()
+
+
+def test_speculative_rounds_alternate_with_admission():
+    """With requests still queued the tick policy never grants two verify rounds in a row
+    (tick_policy.rs:284-356); greedy output is unchanged."""
+    cfg, w, eng = _engine(max_batch=2)
+    prompts = [_prompt(cfg, n, seed=n) for n in (9, 14, 11, 17)]
+    sp = SamplingParams(max_tokens=16, ignore_eos=True)
+    want = [s.output for s in eng.generate(prompts, sp)]
+    cfg, w, eng = _engine(max_batch=2)
+    eng.drafter = DraftModelDrafter(DecoderModel(cfg, w), cfg, num_blocks=96, max_model_len=384)
+    actions = []
+    orig = eng._spec_step
+
+    def spy(decode):
+        actions.append(("spec", len(eng.waiting)))
+        return orig(decode)
+    eng._spec_step = spy
+    ids = [eng.add_request(p, sp) for p in prompts]
+    prev_spec_while_waiting = False
+    while eng.has_work():
+        n0 = len(actions)
+        waiting_before = len(eng.waiting)
+        eng.step()
+        was_spec = len(actions) > n0
+        if was_spec and waiting_before > 0:
+            assert not prev_spec_while_waiting, "two speculative rounds in a row while requests wait"
+        prev_spec_while_waiting = was_spec and waiting_before > 0
+    got = [eng.seqs[i].output for i in ids]
+    assert got == want and eng.stats["spec_rounds"] > 0
+    assert all(eng.seqs[i].draft_n >= eng.seqs[i].draft_n_accepted > 0 for i in ids)

@@ -10,7 +10,7 @@ def test_every_env_var_is_documented():
     doc = (ROOT / "docs" / "environment-variables.md").read_text()
     pat = re.compile(r"MLXCEL_B200_[A-Z0-9_]+")
     used = set()
-    files = [ROOT / "bench.py", ROOT / "__graft_entry__.py"]
+    files = [ROOT / "bench.py", ROOT / "__graft_entry__.py"] + list((ROOT / "benchmarks").glob("*.py"))
     for ext in ("*.py", "*.cu", "*.cuh", "*.h", "*.cpp"):
         files += list((ROOT / "mlxcel_b200").rglob(ext))
     for f in files:

@@ -315,6 +315,46 @@ def test_sample_matches_reference_stream():
         _close(lp, lpr, rtol=1e-3, atol=1e-3)
 
 
+def test_sample_typical_p_and_top_n_sigma_match_reference():
+    """The typical-p and top-n-sigma stages of the fused sampler against the PyTorch reference chain:
+    the same Philox stream, so the drawn tokens agree unless a token sits on a cut's boundary (the
+    kernel evaluates the cuts in fp32, the reference in fp64); every drawn token must lie in the
+    reference's kept set for a slightly wider cut."""
+    B, V = 8, 5000
+    g = torch.Generator().manual_seed(5)
+    lg = (torch.randn(B, V, generator=g) * 3).float().to(DEV)
+    temp = torch.tensor([1.0, 0.8, 1.2, 1.0, 1.0, 0.7, 1.0, 1.5], device=DEV)
+    tk = torch.tensor([0, 0, 50, 0, 0, 0, 200, 0], dtype=torch.int32, device=DEV)
+    tp = torch.tensor([1.0, 1.0, 1.0, 0.95, 1.0, 1.0, 1.0, 1.0], device=DEV)
+    mp = torch.zeros(B, device=DEV)
+    ty = torch.tensor([0.2, 0.5, 0.9, 0.6, 1.0, 1.0, 0.7, 0.95], device=DEV)
+    ns = torch.tensor([0.0, 0.0, 0.0, 0.0, 1.0, 2.0, 1.5, 0.0], device=DEV)
+    seeds = torch.arange(11, 11 + B, dtype=torch.int64, device=DEV)
+    wide = []
+    for b in range(B):
+        l = lg[b].cpu()
+        keep = ref.filter_mask(l, int(tk[b]), float(tp[b]), float(mp[b]))
+        if float(ns[b]) > 0:
+            keep &= ref.sigma_mask(l, float(ns[b]) * 1.02)
+            keep[l.argmax()] = True
+        if float(ty[b]) < 1.0:
+            keep = ref.typical_mask(l, keep, min(1.0, float(ty[b]) + 0.02))
+        wide.append(keep)
+    same = total = 0
+    for step in range(24):
+        steps = torch.full((B,), step, dtype=torch.int64, device=DEV)
+        got, lp = ops.sample(lg, temp, tk, tp, mp, seeds, steps, ty, ns)
+        want, lpr = ref.sample(lg, temp, tk, tp, mp, seeds, steps, ty, ns)
+        got, want = got.cpu().tolist(), want.cpu().tolist()
+        for b in range(B):
+            assert bool(wide[b][got[b]]), (b, step, got[b])
+            same += got[b] == want[b]
+            total += 1
+    assert same >= 0.9 * total, (same, total)
+    # the filters bite: a tight typical-p keeps far fewer tokens than the vocabulary
+    assert int(wide[0].sum()) < V // 4
+
+
 def test_sample_distribution_chi_square():
     V, N = 16, 4000
     probs = torch.softmax(torch.randn(V), 0)
