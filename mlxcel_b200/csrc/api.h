@@ -97,6 +97,16 @@ int mx_allreduce_comm(const void* x, const void* residual, void* out, long long 
                       long long rank_stride, void* status, void* stream, void* flags_mc, void* recv_mc,
                       void* out_mc);
 
+// Quantized GEMV -> all-reduce in one kernel (M <= 8 tokens; bits 4 / 8; mode 0 affine, 1 mxfp4,
+// 2 mxfp8): out = residual + bias + sum over ranks of x_r @ dequant(w_r)^T. Channel arguments as in
+// mx_allreduce_comm. Returns -9 for shapes it does not cover.
+int mx_qmv_allreduce(const void* x, const void* w, const void* scales, const void* biases, void* out,
+                     const void* residual, const void* lin_bias, int M, int N, int K, int bits, int group,
+                     int mode, int ldx, int ldo, int ldr, int rank, int world,
+                     const void* const* flags_peer, const void* const* recv_peer, void* ctl, void* expect,
+                     long long parity_stride, long long rank_stride, void* status, void* flags_mc,
+                     void* recv_mc, void* stream);
+
 // Bytes of workspace the no-scratch-allocation path needs at most for mx_gemm_bf16.
 long long mx_gemm_workspace_bytes(void);
 

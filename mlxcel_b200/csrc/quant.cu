@@ -100,20 +100,17 @@ constexpr int kQmvWarps = 8;
 
 // BITS in {4, 8}. One lane consumes one uint4 of packed weights per step:
 // 32 values (4-bit) or 16 values (8-bit), all inside one quantization group (group >= 32).
+// Dot products of weight row n with M activation rows, lanes striding the packed row. After the
+// call every lane holds the warp-reduced sums in acc[0..M).
 template <int BITS, int MODE, int M>
-__global__ void __launch_bounds__(kQmvWarps * 32)
-qmv_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ w,
-           const void* __restrict__ scales, const __nv_bfloat16* __restrict__ biases,
-           __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
-           const __nv_bfloat16* __restrict__ lin_bias, int N, int K, int group, int ldx, int ldo) {
+__device__ __forceinline__ void qmv_row_dot(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ w,
+                                            const void* __restrict__ scales,
+                                            const __nv_bfloat16* __restrict__ biases, int n, int K, int group,
+                                            int ldx, int lane, float (&acc)[M]) {
   constexpr int VPL = 128 / BITS;  // values per lane per step
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * kQmvWarps + warp;
-  if (n >= N) return;
   const int words_per_row = K * BITS / 32;
   const uint4* row = reinterpret_cast<const uint4*>(w + static_cast<size_t>(n) * words_per_row);
   const int groups_per_row = K / group;
-  float acc[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) acc[m] = 0.f;
   const int steps = K / VPL;  // uint4 chunks per row
@@ -158,6 +155,21 @@ qmv_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ w,
   }
 #pragma unroll
   for (int m = 0; m < M; ++m) acc[m] = warp_sum(acc[m]);
+}
+
+// BITS in {4, 8}. One lane consumes one uint4 of packed weights per step:
+// 32 values (4-bit) or 16 values (8-bit), all inside one quantization group (group >= 32).
+template <int BITS, int MODE, int M>
+__global__ void __launch_bounds__(kQmvWarps * 32)
+qmv_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ w,
+           const void* __restrict__ scales, const __nv_bfloat16* __restrict__ biases,
+           __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
+           const __nv_bfloat16* __restrict__ lin_bias, int N, int K, int group, int ldx, int ldo) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * kQmvWarps + warp;
+  if (n >= N) return;
+  float acc[M];
+  qmv_row_dot<BITS, MODE, M>(x, w, scales, biases, n, K, group, ldx, lane, acc);
   if (lane == 0) {
     const float lb = lin_bias ? __bfloat162float(lin_bias[n]) : 0.f;
 #pragma unroll
@@ -165,6 +177,146 @@ qmv_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ w,
       float v = acc[m] + lb;
       if (residual) v += __bfloat162float(residual[static_cast<size_t>(m) * ldo + n]);
       out[static_cast<size_t>(m) * ldo + n] = __float2bfloat16(v);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- qmv -> all-reduce
+// Row-parallel quantized projection at decode batch sizes (M <= 8) under tensor parallelism: the
+// GEMV over this rank's K shard and the cross-rank sum of the partial rows in ONE kernel. A block
+// computes 8 consecutive output features (one warp each) for all M tokens = one 16-byte piece per
+// token. Phase 1 (all of a block's groups): bf16 partials go into this rank's receive half (NVLS)
+// or into slot [rank] of every peer (peer stores); the group's flag is bumped on every rank.
+// Phase 2: wait for `world` arrivals, pull the sum with multimem.ld_reduce (or add the `world`
+// local slots in rank order), add bias and residual, store. Phase 1 never waits, so blocks that
+// are not resident yet cannot be waited on by resident ones of the same rank.
+// Same channel words as the GEMM epilogues (ctl / expect / flags, receive halves by call parity).
+// Replaces the reference's qmv kernels followed by its reduce_sum
+// (overlays/cuda/.../quantized/qmm/qmv.cu:661-728, src/distributed/tensor_parallel/llama_runtime.rs:3133).
+constexpr int kQmvMaxRanks = 8;
+constexpr int kQmvMaxGroups = 8192;
+struct QmvCommParams {
+  int rank, world, nvls;
+  uint32_t* ctl;
+  uint32_t* expect;
+  int* status;
+  uint32_t* flags_peer[kQmvMaxRanks];
+  __nv_bfloat16* recv_peer[kQmvMaxRanks];
+  uint32_t* flags_mc;
+  __nv_bfloat16* recv_mc;
+  long long parity_stride, rank_stride;
+};
+
+__device__ __forceinline__ bool qmv_wait_flag(const uint32_t* addr, uint32_t target, int* status) {
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+      if (static_cast<int32_t>(v - target) >= 0) return true;
+    }
+    if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      atomicCAS(status, 0, kErrPeerFlagWait);
+      return false;
+    }
+  }
+}
+
+template <int BITS, int MODE, int M>
+__global__ void __launch_bounds__(kQmvWarps * 32)
+qmv_allreduce_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ w,
+                     const void* __restrict__ scales, const __nv_bfloat16* __restrict__ biases,
+                     __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
+                     const __nv_bfloat16* __restrict__ lin_bias, int N, int K, int group, int ldx, int ldo,
+                     int ldr, const QmvCommParams cm) {
+  __shared__ int ok_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int groups = N / kQmvWarps;      // N is a multiple of 8
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t parity = *reinterpret_cast<volatile uint32_t*>(cm.ctl) & 1u;
+  const size_t pbase = parity * static_cast<size_t>(cm.parity_stride);
+  // ---- phase 1: partial rows -> receive areas, one flag bump per group
+  for (int gi = blockIdx.x; gi < groups; gi += gridDim.x) {
+    const int n = gi * kQmvWarps + warp;
+    float acc[M];
+    qmv_row_dot<BITS, MODE, M>(x, w, scales, biases, n, K, group, ldx, lane, acc);
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const __nv_bfloat16 v = __float2bfloat16(acc[m]);
+        const size_t off = pbase + static_cast<size_t>(m) * N + n;
+        if (cm.nvls) {
+          cm.recv_peer[cm.rank][off] = v;
+        } else {
+          const size_t so = off + cm.rank * static_cast<size_t>(cm.rank_stride);
+          for (int pr = 0; pr < cm.world; ++pr) cm.recv_peer[pr][so] = v;
+        }
+      }
+    }
+    __syncthreads();   // the block's stores are ordered before the releasing signal below
+    if (cm.nvls) {
+      if (threadIdx.x == 0) multimem_signal_add(cm.flags_mc + gi, 1u);
+    } else if (threadIdx.x < cm.world) {
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cm.flags_peer[threadIdx.x] + gi) : "memory");
+    }
+  }
+  // ---- phase 2: wait, reduce, finish
+  for (int gi = blockIdx.x; gi < groups; gi += gridDim.x) {
+    if (threadIdx.x == 0) {
+      const uint32_t target = cm.expect[gi] + static_cast<uint32_t>(cm.world);
+      ok_s = qmv_wait_flag(cm.flags_peer[cm.rank] + gi, target, cm.status) ? 1 : 0;
+      cm.expect[gi] = target;
+    }
+    __syncthreads();
+    if (ok_s && threadIdx.x < M) {
+      const int m = threadIdx.x, n0 = gi * kQmvWarps;
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = 0.f;
+      if (cm.nvls) {
+        const uint4 a = multimem_ld_reduce_bf16x8(cm.recv_mc + pbase + static_cast<size_t>(m) * N + n0);
+        const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[2 * j] = bf16_lo(w4[j]), o[2 * j + 1] = bf16_hi(w4[j]);
+      } else {
+        for (int r = 0; r < cm.world; ++r) {
+          const uint4 a = __ldcg(reinterpret_cast<const uint4*>(
+              cm.recv_peer[cm.rank] + pbase + r * static_cast<size_t>(cm.rank_stride) + static_cast<size_t>(m) * N + n0));
+          const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[2 * j] += bf16_lo(w4[j]), o[2 * j + 1] += bf16_hi(w4[j]);
+        }
+      }
+      if (lin_bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += __bfloat162float(lin_bias[n0 + j]);
+      }
+      if (residual != nullptr) {
+        const uint4 rs = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(m) * ldr + n0);
+        const uint32_t r4[4] = {rs.x, rs.y, rs.z, rs.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[2 * j] += bf16_lo(r4[j]), o[2 * j + 1] += bf16_hi(r4[j]);
+      }
+      uint4 pk;
+      pk.x = pack_bf16(o[0], o[1]);
+      pk.y = pack_bf16(o[2], o[3]);
+      pk.z = pack_bf16(o[4], o[5]);
+      pk.w = pack_bf16(o[6], o[7]);
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * ldo + n0) = pk;
+    }
+    __syncthreads();
+  }
+  // ---- per-call completion: the last block to finish advances the channel's call counter
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(cm.ctl + 1, 1u);
+    if (prev == gridDim.x - 1) {
+      cm.ctl[1] = 0u;
+      __threadfence();
+      atomicAdd(cm.ctl, 1u);
     }
   }
 }
@@ -210,6 +362,83 @@ extern "C" int mx_dequantize(const void* w, const void* scales, const void* bias
       static_cast<const uint32_t*>(w), scales, static_cast<const __nv_bfloat16*>(biases),
       static_cast<__nv_bfloat16*>(out), N, K, bits, group, mode);
   return static_cast<int>(cudaGetLastError());
+}
+
+template <int BITS, int MODE>
+static int launch_qmv_ar(const void* x, const void* w, const void* scales, const void* biases, void* out,
+                         const void* residual, const void* lin_bias, int M, int N, int K, int group, int ldx,
+                         int ldo, int ldr, const QmvCommParams& cm, cudaStream_t st) {
+  const int groups = N / kQmvWarps;
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+#define MX_QMV_AR(M_)                                                                                  \
+  case M_: {                                                                                           \
+    auto kern = qmv_allreduce_kernel<BITS, MODE, M_>;                                                  \
+    int per_sm = 0;                                                                                    \
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kQmvWarps * 32, 0);                   \
+    if (per_sm < 1) per_sm = 1;                                                                        \
+    /* blocks wait on peers in phase 2: keep the grid within what is resident at once */              \
+    const int grid = groups < per_sm * sms ? groups : per_sm * sms;                                    \
+    return static_cast<int>(launch_kernel(kern, dim3(grid), dim3(kQmvWarps * 32), 0, st,              \
+        static_cast<const __nv_bfloat16*>(x), static_cast<const uint32_t*>(w), scales,                 \
+        static_cast<const __nv_bfloat16*>(biases), static_cast<__nv_bfloat16*>(out),                   \
+        static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(lin_bias), N, K, \
+        group, ldx, ldo, ldr, cm));                                                                    \
+  }
+  switch (M) {
+    MX_QMV_AR(1) MX_QMV_AR(2) MX_QMV_AR(3) MX_QMV_AR(4) MX_QMV_AR(5) MX_QMV_AR(6) MX_QMV_AR(7) MX_QMV_AR(8)
+    default: return -1;
+  }
+#undef MX_QMV_AR
+}
+
+// Quantized GEMV -> all-reduce in one kernel (see qmv_allreduce_kernel). Same shape rules as mx_qmv
+// plus N % 8 == 0, 16-byte aligned out / residual rows, N / 8 <= 8192 flag words. flags_peer /
+// recv_peer: host arrays of `world` device addresses; ctl / expect: this rank's channel words;
+// rank_stride >= M * N elements (peer-store protocol: one slot per source rank), parity_stride =
+// distance between the two receive halves. flags_mc / recv_mc: multicast addresses or NULL.
+// Returns -9 when the shape is not covered (the caller takes the GEMM path).
+extern "C" int mx_qmv_allreduce(const void* x, const void* w, const void* scales, const void* biases, void* out,
+                                const void* residual, const void* lin_bias, int M, int N, int K, int bits,
+                                int group, int mode, int ldx, int ldo, int ldr, int rank, int world,
+                                const void* const* flags_peer, const void* const* recv_peer, void* ctl,
+                                void* expect, long long parity_stride, long long rank_stride, void* status,
+                                void* flags_mc, void* recv_mc, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 8 || (bits != 4 && bits != 8) || world < 1 || world > kQmvMaxRanks || rank < 0 || rank >= world) return -9;
+  const int vpl = 128 / bits;
+  if (K % vpl || group % vpl || K % group || (ldx % 8) || (N % 8) || (ldo % 8) || (residual && (ldr % 8))) return -9;
+  if (N / kQmvWarps > kQmvMaxGroups || static_cast<long long>(M) * N > rank_stride) return -9;
+  auto mis = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) != 0; };
+  if (mis(w) || mis(x) || mis(out) || (residual && mis(residual))) return -9;
+  if ((static_cast<long long>(K) * bits / 8) % 16 || (parity_stride % 8) || (rank_stride % 8)) return -9;
+  QmvCommParams cm{};
+  cm.rank = rank;
+  cm.world = world;
+  cm.ctl = static_cast<uint32_t*>(ctl);
+  cm.expect = static_cast<uint32_t*>(expect);
+  cm.status = static_cast<int*>(status);
+  for (int r = 0; r < world; ++r) {
+    cm.flags_peer[r] = static_cast<uint32_t*>(const_cast<void*>(flags_peer[r]));
+    cm.recv_peer[r] = static_cast<__nv_bfloat16*>(const_cast<void*>(recv_peer[r]));
+    if (mis(cm.recv_peer[r])) return -9;
+  }
+  cm.nvls = (flags_mc != nullptr && recv_mc != nullptr && !mis(recv_mc)) ? 1 : 0;
+  cm.flags_mc = static_cast<uint32_t*>(flags_mc);
+  cm.recv_mc = static_cast<__nv_bfloat16*>(recv_mc);
+  cm.parity_stride = parity_stride;
+  cm.rank_stride = rank_stride;
+  if (mode == kAffine) {
+    return bits == 4 ? launch_qmv_ar<4, kAffine>(x, w, scales, biases, out, residual, lin_bias, M, N, K, group, ldx, ldo, ldr, cm, stream)
+                     : launch_qmv_ar<8, kAffine>(x, w, scales, biases, out, residual, lin_bias, M, N, K, group, ldx, ldo, ldr, cm, stream);
+  }
+  if (mode == kMxfp4 && bits == 4)
+    return launch_qmv_ar<4, kMxfp4>(x, w, scales, biases, out, residual, lin_bias, M, N, K, group, ldx, ldo, ldr, cm, stream);
+  if (mode == kMxfp8 && bits == 8)
+    return launch_qmv_ar<8, kMxfp8>(x, w, scales, biases, out, residual, lin_bias, M, N, K, group, ldx, ldo, ldr, cm, stream);
+  return -9;
 }
 
 // GEMV path of quantized linears (M <= 8, bits in {4, 8}, group >= 128 / bits and K a multiple of

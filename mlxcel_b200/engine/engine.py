@@ -647,9 +647,15 @@ class Engine:
                 self.stats["decode_steps"] += 1
         if logits is None:
             if self.drafter is not None and getattr(self.drafter, "needs_hidden", False):
-                h = self.model.forward_hidden(b, self.pool.layers)
-                logits = self.model.logits(h, b.logits_rows)
-                self.drafter.on_forward(self, decode, pieces, h)
+                if self.pipeline:
+                    # the residual stream exists on the last stage only, and so does the drafter
+                    h = self.model.pipeline_hidden(b, self.pool.layers)
+                    logits = self.model.logits(h, b.logits_rows) if h is not None else None
+                else:
+                    h = self.model.forward_hidden(b, self.pool.layers)
+                    logits = self.model.logits(h, b.logits_rows)
+                if h is not None:
+                    self.drafter.on_forward(self, decode, pieces, h)
             else:
                 logits = self.model.forward(b, self.pool.layers)
         # rows: decode rows first, then prefill rows that completed their prompt
@@ -743,6 +749,11 @@ class Engine:
         accepted drafts plus the target token at the first mismatch, roll the KV back."""
         K = self.spec_k
         props = self.drafter.propose(self, decode, K - 1)
+        if self.pipeline:
+            # proposals come from the stage that holds the drafter; every scheduler needs them
+            flat = [[len(d)] + list(d) + [0] * (K - 1 - len(d)) for d in props]
+            flat = self.model.share_ints(flat, (len(decode), K))
+            props = [row[1:1 + row[0]] for row in flat]
         drafts, pieces = {}, []
         for s, d in zip(decode, props):
             room = min(s.params.max_tokens - len(s.output) - 1, self.ecfg.max_model_len - s.total_len - 1)
@@ -753,10 +764,19 @@ class Engine:
             pieces.append((s, s.total_len - 1, 1 + len(d)))
         b, R = self._build_batch([], pieces, drafts=drafts, all_rows=True)
         need_h = getattr(self.drafter, "needs_hidden", False)
-        h = self.model.forward_hidden(b, self.pool.layers)
-        logits = self.model.logits(h, b.logits_rows)
+        if self.pipeline:
+            h = self.model.pipeline_hidden(b, self.pool.layers)
+            logits = self.model.logits(h, b.logits_rows) if h is not None else None
+            # argmax of every verify row on the last stage, shared with the other stages (R ints)
+            target = self.model.share_ints(ops.argmax(logits).cpu().tolist() if logits is not None else None, (R,))
+            walk = None
+        else:
+            h = self.model.forward_hidden(b, self.pool.layers)
+            logits = self.model.logits(h, b.logits_rows)
         walk = None
-        if logits.is_cuda and K > 1 and all(len(drafts[s.seq_id]) == K - 1 for s in decode):
+        if self.pipeline:
+            pass
+        elif logits.is_cuda and K > 1 and all(len(drafts[s.seq_id]) == K - 1 for s in decode):
             # every row carries a full block: argmax + accept walk on the device, and the host reads
             # back two ints per row (accepted length, token at the first mismatch) instead of the
             # K target tokens of every row
@@ -814,7 +834,7 @@ class Engine:
                 finished.append(s)
             row0 += cnt
         self.stats["decode_tokens"] += sum(k + 1 for _, _, k in accepted_info)
-        if need_h:
+        if need_h and h is not None:
             self.drafter.on_verify(self, accepted_info, h)
         for s in finished:
             self.drafter.release(s.seq_id)

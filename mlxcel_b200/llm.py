@@ -44,7 +44,9 @@ class LLM:
     # ------------------------------------------------------------------ constructors
     @staticmethod
     def from_preset(name: str, *, device="cuda", seed: int = 0, engine_config: EngineConfig | None = None,
-                    comm=None, dtype=torch.bfloat16) -> "LLM":
+                    comm=None, dtype=torch.bfloat16, quantize: dict | None = None) -> "LLM":
+        """``quantize``: ``dict(dense=(mode, bits, group), experts=(mode, bits, group), lm_head=bool)`` packs the
+        random weights into MLX quantization formats layer by layer (see ops.quant.quantize_model_weights)."""
         cfg = preset(name)
         if cfg.model_type == "mamba2":
             from .models.mamba2 import random_mamba2_weights
@@ -57,9 +59,21 @@ class LLM:
             return LLM(cfg, random_hybrid_weights(cfg, seed=seed, dtype=dtype, device=device), engine_config, comm=comm)
         tp = comm.tp_size if comm is not None else 1
         rank = comm.tp_rank if comm is not None else 0
+        hook = None
+        if quantize:
+            from types import SimpleNamespace
+
+            from .ops import quant
+
+            def hook(lw):
+                quant.quantize_model_weights(SimpleNamespace(layers=[lw], lm_head=None, embed=None),
+                                             dense=quantize.get("dense"), experts=quantize.get("experts"))
         w = random_weights(cfg, seed=seed, dtype=dtype, device=device, tp_rank=rank, tp_size=tp,
                            ep_rank=getattr(comm, "ep_rank", 0), ep_size=getattr(comm, "ep_size", 1),
-                           vocab_parallel=tp > 1 and cfg.vocab_size % tp == 0)
+                           vocab_parallel=tp > 1 and cfg.vocab_size % tp == 0, layer_hook=hook)
+        if quantize and quantize.get("lm_head") and quantize.get("dense") and w.lm_head is not w.embed:
+            from .ops import quant
+            w.lm_head = quant.quantize_chunked(w.lm_head, *quantize["dense"])
         return LLM(cfg, w, engine_config, comm=comm, fold_norms=True)
 
     @staticmethod

@@ -120,7 +120,7 @@ def _randn(shape, std, gen, dtype, device):
 def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, device="cpu",
                    tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0, ep_size: int = 1,
                    layers: range | None = None, std: float = 0.02,
-                   vocab_parallel: bool = False) -> ModelWeights:
+                   vocab_parallel: bool = False, layer_hook=None) -> ModelWeights:
     """Random-init N(0, std) weights of the architecture, already sharded for (tp, ep, pp).
 
     Every rank draws from its own generator stream (seed, rank) directly at shard shape: the
@@ -210,6 +210,8 @@ def random_weights(cfg: ModelConfig, *, seed: int = 0, dtype=torch.bfloat16, dev
                 lw.b_down = _randn((H,), std, shared, dtype, dev)
             if cfg.hidden_act == "xielu":
                 lw.act_params = (0.8, 0.8, 0.5, -1e-6)
+        if layer_hook is not None:
+            layer_hook(lw)        # e.g. quantize this layer before the next one is drawn (peak memory)
         lws.append(lw)
     if cfg.tie_word_embeddings:
         lm_head = embed[tp_rank * Vl:(tp_rank + 1) * Vl] if vocab_parallel else embed

@@ -119,6 +119,45 @@ def quantize(w: torch.Tensor, mode: str = "affine", bits: int = 4, group_size: i
     raise ValueError(mode)
 
 
+def quantize_chunked(w: torch.Tensor, mode: str = "affine", bits: int = 4, group_size: int = 64,
+                     max_elems: int = 1 << 24) -> QuantizedTensor:
+    """:func:`quantize` over slices of the leading dimension, so that the integer temporaries of the
+    packing stay small next to large (stacked-expert, vocabulary-sized) tensors."""
+    lead = w.shape[0]
+    per = max(1, w.numel() // max(lead, 1))
+    step = max(1, max_elems // per)
+    if step >= lead:
+        return quantize(w, mode, bits, group_size, dtype=w.dtype if w.dtype != torch.float32 else torch.bfloat16)
+    parts = [quantize(w[i:i + step], mode, bits, group_size,
+                      dtype=w.dtype if w.dtype != torch.float32 else torch.bfloat16) for i in range(0, lead, step)]
+    cat = lambda xs: torch.cat(xs, dim=0) if xs[0] is not None else None  # noqa: E731
+    p0 = parts[0]
+    return QuantizedTensor(cat([p.packed for p in parts]), cat([p.scales for p in parts]),
+                           cat([p.biases for p in parts]), p0.bits, p0.group_size, p0.mode)
+
+
+def quantize_model_weights(w, dense: tuple | None = None, experts: tuple | None = None, lm_head: bool = False):
+    """Quantize a model's projections in place: ``dense`` = (mode, bits, group) for qkv / o / gate-up /
+    down (and the LM head when ``lm_head``), ``experts`` = the same for the stacked expert matrices.
+    Tensors whose input dimension is not a multiple of the group stay as they are. This is how the
+    synthetic benchmark configurations get MLX-format packed weights out of random bf16 ones."""
+    def q(v, spec):
+        if v is None or spec is None or isinstance(v, QuantizedTensor) or v.shape[-1] % spec[2]:
+            return v
+        return quantize_chunked(v, *spec)
+
+    for lw in w.layers:
+        for name in ("wqkv", "wo", "w_gate_up", "w_down"):
+            setattr(lw, name, q(getattr(lw, name), dense))
+        for name in ("experts_gate_up", "experts_down"):
+            setattr(lw, name, q(getattr(lw, name), experts))
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+    if lm_head and dense is not None and w.lm_head is not w.embed:
+        w.lm_head = q(w.lm_head, dense)
+    return w
+
+
 # ----------------------------------------------------------------------------- dequantize
 def dequantize_ref(qt: QuantizedTensor, dtype=torch.float32) -> torch.Tensor:
     *lead, out, inn = qt.shape

@@ -93,11 +93,11 @@ class PipelineModel(DecoderModel):
         ctx.stats["recv_bytes"] += h.numel() * h.element_size()
         return h
 
-    def forward(self, b: StepBatch, kv_layers) -> torch.Tensor:
+    def pipeline_hidden(self, b: StepBatch, kv_layers) -> torch.Tensor | None:
+        """Runs the step through all stages in micro-batches. The last stage returns the residual
+        stream of the whole batch ``[T, H]``; the others return None."""
         ctx = self.ctx
         T = b.num_tokens
-        rows_host = getattr(b, "logits_rows_host", None)
-        R = len(rows_host) if rows_host is not None else (b.logits_rows.shape[0] if b.logits_rows is not None else T)
         micro = split_batch(b, self.num_micro)
         h_full = torch.empty(T, self.cfg.hidden_size, dtype=self.w.final_norm.dtype, device=self.device) \
             if ctx.is_last else None
@@ -118,9 +118,23 @@ class PipelineModel(DecoderModel):
                     self._send(h)
         if ctx.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(ctx.comm_stream)
+        return h_full
+
+    def forward(self, b: StepBatch, kv_layers) -> torch.Tensor | None:
         # only the last stage has logits; the sampled token ids are what travels back
         # (see sample_and_share), not [rows, vocab] logits
-        return self.logits(h_full, b.logits_rows).contiguous() if ctx.is_last else None
+        h = self.pipeline_hidden(b, kv_layers)
+        return self.logits(h, b.logits_rows).contiguous() if self.ctx.is_last else None
+
+    def share_ints(self, values, shape) -> list:
+        """Broadcast a small int tensor (drafts, verify results) from the last stage to every rank."""
+        ctx = self.ctx
+        if ctx.is_last:
+            t = torch.as_tensor(values, dtype=torch.int32).reshape(shape).to(self.device)
+        else:
+            t = torch.empty(shape, dtype=torch.int32, device=self.device)
+        dist.broadcast(t, ctx.last_stage_rank0, group=ctx.group)
+        return t.cpu().tolist()
 
     def sample_and_share(self, logits, seqs, sampler):
         """Sample on the last stage and broadcast the token ids (and log-probabilities when a row
@@ -141,3 +155,27 @@ class PipelineModel(DecoderModel):
             dist.broadcast(lp, ctx.last_stage_rank0, group=ctx.group)
         ctx.stats["token_bytes"] = ctx.stats.get("token_bytes", 0) + 4 * R
         return t.cpu().tolist(), (lp.cpu().tolist() if lp is not None else None)
+
+
+class RemoteDrafter:
+    """Drafter stand-in on the stages that do not hold the last layers: a hidden-state drafter (MTP
+    head) lives on the last stage, which broadcasts its proposals; the other stages only take part
+    in that broadcast and keep no drafter state."""
+
+    needs_hidden = True
+    remote = True
+
+    def propose(self, engine, seqs, max_draft):
+        return [[] for _ in seqs]
+
+    def on_forward(self, engine, decode, pieces, hidden) -> None:
+        pass
+
+    def on_verify(self, engine, accepted_info, hidden) -> None:
+        pass
+
+    def record(self, *a) -> None:
+        pass
+
+    def release(self, seq_id: int) -> None:
+        pass

@@ -120,11 +120,12 @@ class FusedOps:
         """Heap bytes the channels and buffers below take (what ``SymmetricHeap`` must be sized for)."""
         ctl = _align(_CHANNEL_WORDS * 4)
         one = _align(2 * world * small_m * hidden * 2)
+        qmv = _align(2 * world * 8 * hidden * 2)
         tiles = ((max_tokens + 127) // 128) * ((hidden + 255) // 256)
         two = _align(2 * world * ((tiles + world - 1) // world) * 128 * 256 * 2)
         chunks = (max_tokens * hidden + 8191) // 8192
         ar_two = _align(2 * world * ((chunks + world - 1) // world) * 8192 * 2)
-        return (5 * ctl + 2 * one + two + ar_two + _align(max_tokens * hidden * 2) + _align(small_m * vocab * 2)
+        return (6 * ctl + 2 * one + two + ar_two + qmv + _align(max_tokens * hidden * 2) + _align(small_m * vocab * 2)
                 + (4 << 20))
 
     def __init__(self, heap: SymmetricHeap, max_tokens: int = 8192, hidden: int = 8192,
@@ -147,6 +148,9 @@ class FusedOps:
         chunks = (max_tokens * hidden + 8191) // 8192
         self.ar_two_stride = ((chunks + W - 1) // W) * 8192
         self.ch_ar_two = _Channel(heap, W * self.ar_two_stride * 2)
+        # quantized GEMV -> all-reduce (up to 8 token rows)
+        self.qmv_stride = 8 * hidden
+        self.ch_qmv = _Channel(heap, W * self.qmv_stride * 2)
         # replicated residual stream and gathered logits live in the heap
         self.h_off = heap.alloc(max_tokens * hidden * 2)
         self.h_peer = heap.peer_ptrs(self.h_off)
@@ -163,7 +167,7 @@ class FusedOps:
         """Zero every channel on all ranks (after a bounded wait reported a failure)."""
         torch.cuda.synchronize(self.heap.device)
         dist.barrier(group=self.heap.group)
-        for ch in (self.ch_one, self.ch_two, self.ch_ag, self.ch_ar_one, self.ch_ar_two):
+        for ch in (self.ch_one, self.ch_two, self.ch_ag, self.ch_ar_one, self.ch_ar_two, self.ch_qmv):
             ch.reset()
         torch.cuda.synchronize(self.heap.device)
         dist.barrier(group=self.heap.group)
@@ -211,6 +215,33 @@ class FusedOps:
                               ws.numel(), _lib.stream(), _lib.ref_or_null(ex))
         _lib.count_launch()
         _lib.check(rc, "mx_gemm_comm")
+        return out
+
+    def qmv_allreduce(self, x: torch.Tensor, qt, bias, residual) -> torch.Tensor | None:
+        """Row-parallel quantized projection for up to 8 token rows: GEMV over this rank's packed
+        shard and the cross-rank sum in one kernel. Returns None when the shape is not covered."""
+        from ..ops.quant import _MODE_ID
+
+        M, K = x.shape
+        N = qt.shape[-2]
+        if M > 8 or qt.bits not in (4, 8) or qt.packed.dim() != 2 or M * N > self.qmv_stride or x.stride(1) != 1:
+            return None
+        lib = _lib.load()
+        ws = _lib.workspace(x.device)
+        out = self.hidden_buffer(M, N)
+        ch = self.ch_qmv
+        mc = (ch.flags_mc or None, ch.recv_mc or None) if self.nvls else (None, None)
+        rc = lib.mx_qmv_allreduce(x.data_ptr(), qt.packed.data_ptr(), qt.scales.data_ptr(), _lib.ptr(qt.biases),
+                                  out.data_ptr(), _lib.ptr(residual), _lib.ptr(bias), M, N, K, qt.bits, qt.group_size,
+                                  _MODE_ID[qt.mode], x.stride(0), out.stride(0),
+                                  residual.stride(0) if residual is not None else 0, self.rank, self.world,
+                                  ch.flags_peer, ch.recv_peer, ch.ctl.data_ptr(), ch.expect.data_ptr(),
+                                  self.world * self.qmv_stride, self.qmv_stride, ws.data_ptr(), mc[0], mc[1],
+                                  _lib.stream())
+        if rc == -9:
+            return None
+        _lib.count_launch()
+        _lib.check(rc, "mx_qmv_allreduce")
         return out
 
     def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:

@@ -33,6 +33,8 @@ from ..ops import _lib
 # pieces of 32 different rows per instruction), but inside a serving step the fused path wins
 # (TP2 p50 TTFT 387 ms vs 444 ms): no separate residual pass, no extra launches. Set to 0 to compare.
 _FUSED_PREFILL = os.environ.get("MLXCEL_B200_FUSED_PREFILL", "1") == "1"
+# Largest token count served by the fused quantized GEMV -> all-reduce kernel (0 = always the GEMM form).
+_QMV_AR_MAX_M = int(os.environ.get("MLXCEL_B200_QMV_AR_MAX_M", "8"))
 
 
 class TPComm:
@@ -79,6 +81,13 @@ class TPComm:
         if self.tp_size == 1:
             return _linear_any(x, w, bias=bias, residual=residual, out=residual, ssq_out=ssq_out)
         fused_ok = self.backend == "fused"
+        if fused_ok and isinstance(w, QuantizedTensor) and x.is_cuda and x.shape[0] <= _QMV_AR_MAX_M:
+            # a handful of rows: bandwidth-bound GEMV with the all-reduce in its epilogue
+            y = self.fused.qmv_allreduce(x, w, bias, residual)
+            if y is not None:
+                if ssq_out is not None:
+                    ops.row_ssq(y, ssq_out)
+                return y
         if fused_ok and isinstance(w, QuantizedTensor):
             from ..ops import quant
             fused_ok = (x.is_cuda and x.shape[0] <= self.fused.small_m and w.packed.dim() == 2
@@ -107,9 +116,10 @@ class TPComm:
 
     def lm_head(self, x, w):
         """Vocab-parallel LM head: fused GEMM → all-gather when available."""
-        if self.tp_size > 1 and self.backend == "fused":
+        if (self.tp_size > 1 and self.backend == "fused" and x.shape[0] <= self.fused.small_m
+                and self.tp_size * w.shape[0] <= self.fused.vocab_cap):
             return self.fused.gemm_allgather(x, w)
-        return self.gather_logits(ops.linear(x, w))
+        return self.gather_logits(ops.linear(x, w))      # many rows at once (scoring): GEMM + NCCL all-gather
 
     def embed(self, ids, table, scale, vocab_start: int = 0):
         return ops.embedding(ids, table, scale)

@@ -2,11 +2,12 @@
 Each test spawns one process per GPU (NCCL for bootstrap), prints which test ran at which world
 size, and is skipped on boxes with one GPU.
 
-Error bounds come from an fp32 reduction of the same shards: a fused result may differ from the
-fp32 sum of the per-rank products by the bf16 rounding of each partial tile (the kernels round
-partials to bf16 before they cross NVLink) plus the rounding of the result itself, i.e. by at most
-``2^-8 * (sum_r |partial_r| + |result|)`` per element (bf16 keeps 8 significant bits; 2^-8 leaves
-a factor 2 of slack over round-to-nearest).
+Error bounds come from an fp32 reduction of the same shards. bf16 keeps 8 significant bits, so one
+round-to-nearest changes a value v by at most ``u |v|`` with ``u = 2^-8``. A fused result differs
+from the fp32 sum of the per-rank products by the rounding of each partial tile (the kernels round
+partials to bf16 before they cross NVLink), by the rounding of the result itself and, on the NVLS
+path, by the rounding of the sum the switch returns (it accumulates in fp32 and hands back bf16):
+at most ``u (sum_r |partial_r| + [|sum_r partial_r|] + |result|)`` per element.
 """
 import os
 import socket
@@ -39,8 +40,11 @@ def _run(name: str, world: int, body: str, timeout: int = 600, nvls: bool = Fals
         from mlxcel_b200.ops import _lib
         from mlxcel_b200.parallel.tp import TPComm
         EPS = 2.0 ** -8
-        def bound(parts_abs_sum, want):
-            return EPS * (parts_abs_sum + want.abs()) + 1e-3
+        def bound(parts_abs_sum, want, switch_sum=None):
+            b = parts_abs_sum + want.abs()
+            if switch_sum is not None:
+                b = b + switch_sum.abs()
+            return 1.01 * EPS * b + 1e-3
     """ % ROOT) + textwrap.dedent(body) + textwrap.dedent("""
         torch.cuda.synchronize()
         st = _lib.read_status(dev)
@@ -95,23 +99,24 @@ _FUSED_BODY = """
         parts = [x[:, r * 512:(r + 1) * 512].float() @ w[:, r * 512:(r + 1) * 512].float().t() for r in range(world)]
         want = sum(parts) + bias.float() + res.float()           # the fp32 reduction
         pabs = sum(p.abs() for p in parts)
+        sw = sum(parts) if nvls else None                        # what the switch rounds on the NVLS path
         for rep in range(3):
             got = comm.row_parallel_linear(x[:, ks].contiguous(), w[:, ks].contiguous(), bias, res.clone())
             torch.cuda.synchronize()
             diff = (got.float() - want).abs()
-            assert bool((diff <= bound(pabs, want)).all()), (M, rep, diff.max().item())
+            assert bool((diff <= bound(pabs, want, sw if M <= 256 else None)).all()), (M, rep, diff.max().item())
             worst = max(worst, diff.max().item())
             ref0 = got.clone(); dist.broadcast(ref0, 0)
             if nvls:
                 # every rank asks the switch for its own sum: equal up to the result's rounding
-                assert bool(((ref0.float() - got.float()).abs() <= EPS * want.abs() + 1e-3).all()), (M, rep)
+                assert bool(((ref0.float() - got.float()).abs() <= 2 * EPS * (want.abs() + sw.abs()) + 1e-3).all()), (M, rep)
             else:
                 assert torch.equal(ref0, got), (M, rep)          # rank-ordered sums: bitwise identical
             if M > 256:   # the fused two-shot kernel: one owner reduces, everyone receives the same bits
                 got2 = comm.fused.gemm_allreduce(x[:, ks].contiguous(), w[:, ks].contiguous(), bias, res.clone())
                 torch.cuda.synchronize()
                 d2 = (got2.float() - want).abs()
-                assert bool((d2 <= bound(pabs, want)).all()), (M, rep, d2.max().item())
+                assert bool((d2 <= bound(pabs, want, sw)).all()), (M, rep, d2.max().item())
                 ref0 = got2.clone(); dist.broadcast(ref0, 0)
                 assert torch.equal(ref0, got2), (M, rep)
         # quantized row-parallel projection -> all-reduce in one kernel (packed 4-bit shards)
@@ -124,11 +129,27 @@ _FUSED_BODY = """
             dist.all_gather(wparts, wdq.contiguous())
             qparts = [x[:, r * 512:(r + 1) * 512].float() @ wparts[r].t() for r in range(world)]
             want_q = sum(qparts) + bias.float() + res.float()
+            # the GEMM form rounds every dequantised weight to bf16 before the MMA: an error of up to
+            # u on each product, i.e. on sum_k |x_k| |w_k| (no cancellation), on top of the partial rounding
+            prod_abs = sum(x[:, r * 512:(r + 1) * 512].float().abs() @ wparts[r].abs().t() for r in range(world))
+            qbound = bound(sum(p.abs() for p in qparts), want_q, sum(qparts) if nvls else None) + EPS * prod_abs
             got_q = comm.row_parallel_linear(x[:, ks].contiguous(), qts, bias, res.clone())
             torch.cuda.synchronize()
             dq = (got_q.float() - want_q).abs()
-            # the dequantised weight tile is itself rounded to bf16 before the MMA: one more EPS on the products
-            assert bool((dq <= bound(2 * sum(p.abs() for p in qparts), want_q)).all()), (M, "q4", dq.max().item())
+            assert bool((dq <= qbound).all()), (M, "q4", dq.max().item())
+            if M <= 8:
+                # M <= 8 took the GEMV -> all-reduce kernel above; the GEMM form of the same projection must agree
+                import mlxcel_b200.parallel.tp as tpm
+                old, tpm._QMV_AR_MAX_M = tpm._QMV_AR_MAX_M, 0
+                got_g = comm.row_parallel_linear(x[:, ks].contiguous(), qts, bias, res.clone())
+                tpm._QMV_AR_MAX_M = old
+                torch.cuda.synchronize()
+                dg = (got_g.float() - want_q).abs()
+                assert bool((dg <= qbound).all()), (M, "q4 gemm", dg.max().item())
+                for rep in range(2):      # repeated calls reuse the channel (parity, flags)
+                    again = comm.row_parallel_linear(x[:, ks].contiguous(), qts, bias, res.clone())
+                    torch.cuda.synchronize()
+                    assert bool(((again.float() - got_q.float()).abs() <= 2 * EPS * (want_q.abs() + sum(qparts).abs()) + 1e-3).all()), (M, rep)
         # stand-alone all-reduce (one-shot for small, two-shot for large tensors)
         part = torch.randn(M, N, device=dev).to(torch.bfloat16) * (rank + 1)
         aparts = [torch.empty_like(part) for _ in range(world)]
@@ -136,7 +157,7 @@ _FUSED_BODY = """
         want_ar = sum(p.float() for p in aparts)
         got_ar = comm.all_reduce(part.clone())
         torch.cuda.synchronize()
-        assert bool(((got_ar.float() - want_ar).abs() <= EPS * want_ar.abs() + 1e-3).all()), M
+        assert bool(((got_ar.float() - want_ar).abs() <= 2.02 * EPS * want_ar.abs() + 1e-3).all()), M
         # all-gather of a vocab-parallel projection
         if M <= 256:
             Vl = 1024
@@ -145,7 +166,7 @@ _FUSED_BODY = """
             lg = comm.lm_head(xs, wl[rank * Vl:(rank + 1) * Vl].contiguous())
             torch.cuda.synchronize()
             wantl = xs.float() @ wl.float().t()
-            assert bool(((lg.float() - wantl).abs() <= EPS * wantl.abs() + 1e-3).all())
+            assert bool(((lg.float() - wantl).abs() <= 1.01 * EPS * wantl.abs() + 1e-3).all())
     if rank == 0:
         print("INFO fused GEMM->all-reduce max |err| vs the fp32 reduction: %.4f (world %d, nvls %s)" % (worst, world, nvls),
               flush=True)
@@ -183,7 +204,7 @@ def test_tp_engine_fused_matches_nccl_and_single_gpu(nvls):
         single = [s.output for s in Engine(single_model, cfg, ec()).generate(prompts, sp)]
         outs = {}
         for backend in ("nccl", "fused"):
-            comm = TPComm(dist.group.WORLD, dev, backend=backend, max_tokens=512, hidden=512, vocab=2048)
+            comm = TPComm(dist.group.WORLD, dev, backend=backend, max_tokens=512, hidden=512, vocab=4096)
             w = shard_weights(cfg, full, comm.tp_rank, comm.tp_size)
             model = DecoderModel(cfg, w, comm=comm)
             lp = sequence_logprobs(model, cfg, prompts[3])

@@ -49,20 +49,34 @@ ranges = partition_layers(cfg.num_hidden_layers, PP)
 w = shard_weights(cfg, full, tp_rank, TP, layers=ranges[stage], vocab_parallel=TP > 1)
 ctx = PipelineContext(dist.group.WORLD, stage, PP, tp_size=TP, tp_rank=tp_rank)
 model = PipelineModel(cfg, w, ctx, comm=comm, num_micro=2, layer_range=ranges[stage])
-got = [s.output for s in Engine(model, cfg, ec()).generate(prompts, sp)]
+eng = Engine(model, cfg, ec())
+if os.environ.get("TEST_MTP") == "1":
+    # the MTP head lives on the last stage; the other stages take part in the draft broadcast only
+    from mlxcel_b200.speculative import MTPDrafter, random_mtp_weights
+    from mlxcel_b200.parallel.pp import RemoteDrafter
+    if ctx.is_last:
+        mw = random_mtp_weights(cfg, dtype=torch.float32, std=0.05, tp_rank=tp_rank, tp_size=TP)
+        eng.drafter = MTPDrafter(model, cfg, mw, num_blocks=64)
+    else:
+        eng.drafter = RemoteDrafter()
+    eng.spec_k = 4
+got = [s.output for s in eng.generate(prompts, sp)]
 assert got == want, (rank, got, want)
 assert ctx.stats["microbatches"] > 0
+if os.environ.get("TEST_MTP") == "1":
+    assert eng.stats["spec_rounds"] > 0 and eng.stats["spec_drafted"] > 0, eng.stats
+assert ctx.stats.get("token_bytes", 0) > 0 or os.environ.get("TEST_MTP") == "1"
 dist.barrier()
 if rank == 0:
     print("PP_CPU_OK")
 """
 
 
-@pytest.mark.parametrize("world,tp", [(2, 1), (4, 2)])
-def test_pipeline_gloo(tmp_path, world, tp):
+@pytest.mark.parametrize("world,tp,mtp", [(2, 1, 0), (4, 2, 0), (2, 1, 1), (4, 2, 1)])
+def test_pipeline_gloo(tmp_path, world, tp, mtp):
     script = tmp_path / "pp_cpu.py"
     script.write_text(textwrap.dedent(BODY % ROOT))
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", TEST_TP=str(tp), OMP_NUM_THREADS="2")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", TEST_TP=str(tp), OMP_NUM_THREADS="2", TEST_MTP=str(mtp))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(script)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
