@@ -101,6 +101,46 @@ def _apply_compat(a) -> list[str]:
                   if k.startswith("compat_noop_") and v is not None)
 
 
+# llama-server's environment spellings (reference docs/environment-variables.md:36-60): value of the
+# variable -> default of the option; precedence stays command line > environment > built-in default.
+LLAMA_ARG_ENV = {
+    "LLAMA_ARG_MODEL": ("model", str), "LLAMA_ARG_CTX_SIZE": ("ctx_size", int), "LLAMA_ARG_N_PARALLEL": ("parallel", int),
+    "LLAMA_ARG_BATCH": ("max_batch_tokens", int), "LLAMA_ARG_UBATCH": ("prefill_chunk_size", int),
+    "LLAMA_ARG_HOST": ("host", str), "LLAMA_ARG_PORT": ("port", int), "LLAMA_ARG_ALIAS": ("alias", str),
+    "LLAMA_ARG_N_PREDICT": ("max_tokens", int), "LLAMA_ARG_MODEL_DRAFT": ("draft_model", str),
+    "LLAMA_ARG_DRAFT_MAX": ("draft_max", int), "LLAMA_ARG_CHAT_TEMPLATE_FILE": ("chat_template_file", str),
+    "LLAMA_ARG_THINK_BUDGET": ("reasoning_budget", int), "LLAMA_ARG_REASONING_BUDGET": ("reasoning_budget", int),
+    "LLAMA_ARG_SLOT_SAVE_PATH": ("slot_save_path", str), "LLAMA_ARG_API_KEY_FILE": ("api_key_file", str),
+    "LLAMA_ARG_NO_WARMUP": ("no_warmup", "flag"), "LLAMA_ARG_TEMP": ("temperature", float),
+    "LLAMA_ARG_TOP_K": ("top_k", int), "LLAMA_ARG_TOP_P": ("top_p", float), "LLAMA_ARG_SEED": ("seed", int),
+}
+
+
+def _apply_env_aliases(subparsers) -> None:
+    """Every sub-command that has the option takes the variable's value as that option's default
+    (and ``-m`` stops being required when LLAMA_ARG_MODEL names the model)."""
+    for name, (dest, kind) in LLAMA_ARG_ENV.items():
+        raw = os.environ.get(name)
+        if raw is None or raw == "":
+            continue
+        try:
+            val = (raw.lower() not in ("0", "false", "no", "off")) if kind == "flag" else kind(raw)
+        except ValueError:
+            raise SystemExit(f"{name}={raw!r}: expected {kind.__name__}")
+        for parser in subparsers.choices.values():
+            for act in parser._actions:
+                if act.dest == dest:
+                    act.default = val
+                    if dest == "model":
+                        act.required = False
+    key = os.environ.get("LLAMA_ARG_API_KEY") or os.environ.get("LLAMA_API_KEY")
+    if key:
+        for parser in subparsers.choices.values():
+            for act in parser._actions:
+                if act.dest == "api_key" and not act.default:
+                    act.default = [key]
+
+
 def _add_sampling_args(p):
     p.add_argument("-n", "--n-predict", "--max-tokens", dest="max_tokens", type=int, default=256)
     p.add_argument("--temp", "--temperature", dest="temperature", type=float, default=0.0)
@@ -728,6 +768,11 @@ def cmd_serve(a):
                         chat_template=open(a.chat_template_file).read() if a.chat_template_file else None)
     state.slot_save_path = a.slot_save_path
     state.default_thinking_budget = int(budget) if budget not in (None, "") else None
+    state.cors_origins = list(a.cors_origin or ["*"])
+    state.settings_enabled = bool(a.enable_settings)
+    from .server.extras import LogControl
+    verbosity = a.log_verbosity if a.log_verbosity is not None else (2 if a.verbose else 1)
+    state.log = LogControl(dest=a.log_file, fmt=a.log_format, verbosity=verbosity, redact=not a.no_log_redact)
     from .lora import LoraManager
     from .models.weights import QuantizedTensor
     if not any(isinstance(lw.wqkv, QuantizedTensor) for lw in llm.model.w.layers):
@@ -736,8 +781,14 @@ def cmd_serve(a):
         for spec in getattr(a, "lora", None) or []:
             path, _, sc = spec.partition("=")
             state.lora.add(path, float(sc) if sc else 1.0)
-    uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="info" if a.verbose else "warning",
-                ssl_certfile=a.ssl_cert_file, ssl_keyfile=a.ssl_key_file)
+    listen = dict(uds=a.listen_unix) if a.listen_unix else dict(host=a.host, port=a.port)
+    try:
+        uvicorn.run(create_app(state), log_level="info" if a.verbose else "warning",
+                    ssl_certfile=a.ssl_cert_file, ssl_keyfile=a.ssl_key_file, **listen)
+    finally:
+        worker.shutdown()        # under a control plane this also broadcasts the stop to the other ranks
+        if control is not None:
+            _leave_distributed()
 
 
 def _startup_warmup(worker, llm) -> None:
@@ -902,6 +953,15 @@ def main(argv=None):
                    help="seconds after which a step that has not returned fails its requests (0 = off)")
     p.add_argument("--ssl-cert-file", default=None)
     p.add_argument("--ssl-key-file", default=None)
+    p.add_argument("--cors-origin", action="append", default=None, metavar="ORIGIN",
+                   help="origin allowed by CORS (repeatable; default: any)")
+    p.add_argument("--enable-settings", action="store_true", help="serve GET/POST /v1/settings (needs --api-key)")
+    p.add_argument("--log-file", default=None, help="write the server log there instead of stderr")
+    p.add_argument("--log-format", choices=["text", "json"], default="text")
+    p.add_argument("-lv", "--log-verbosity", "--verbosity", dest="log_verbosity", type=int, default=None,
+                   help="0 errors, 1 warnings, 2 requests, 3 debug")
+    p.add_argument("--no-log-redact", action="store_true", help="log request bodies verbatim (default: shape only)")
+    p.add_argument("--listen-unix", default=None, metavar="PATH", help="listen on a Unix domain socket instead of host:port")
     p.add_argument("-v", "--verbose", action="store_true")
     p.set_defaults(fn=cmd_serve)
     p = sub.add_parser("router", help="HTTP server over a pool of models (loaded on demand, LRU eviction)")
@@ -1002,6 +1062,7 @@ def main(argv=None):
     p.add_argument("--bits", type=int, default=4)
     p.add_argument("--group-size", type=int, default=64)
     p.set_defaults(fn=cmd_random_init)
+    _apply_env_aliases(sub)
     a = ap.parse_args(argv)
     ignored = _apply_compat(a)
     if ignored:

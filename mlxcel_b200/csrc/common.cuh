@@ -294,6 +294,17 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
                : "memory");
   return v;
 }
+// fp32 variant: the sum of the replicas' four floats, added in fp32 by the switch (no narrowing).
+// The bf16 form above returns its fp32 sum TRUNCATED to bf16 (round toward zero, measured on
+// NVSwitch with B200), so latency-bound paths that can afford 4 bytes per value use this one.
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const void* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ void multimem_st_16(void* mc, const uint4& v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y),
                "r"(v.z), "r"(v.w)

@@ -62,10 +62,10 @@ struct CommParams {
   long long parity_stride;  // elements between the two receive halves
   long long rank_stride;    // elements between source-rank slots
   // NVLS variants (nvls != 0): multicast addresses of the same flags / receive area / output.
-  //   COMM 1: the bf16 partial stays in THIS rank's receive half (one slot, no per-source slots),
-  //           one multimem.red bumps the tile's flag on every rank, and after `world` arrivals each
-  //           rank pulls the sum of all replicas with multimem.ld_reduce (fp32 accumulation in the
-  //           switch) instead of 7 peer pushes and an 8-way local sum.
+  //   COMM 1: the partial stays, in fp32, in THIS rank's receive half (one slot, no per-source
+  //           slots), one multimem.red bumps the tile's flag on every rank, and after `world`
+  //           arrivals each rank pulls the fp32 sum of all replicas with multimem.ld_reduce instead
+  //           of 7 peer pushes and an 8-way local sum. No bf16 rounding before the cross-rank sum.
   //   COMM 2: partial tiles stay local (slot = tile), the owner pulls the reduced tile with
   //           multimem.ld_reduce and writes the finished tile to every rank with one multimem.st.
   //   COMM 3: the logits tile is written to every rank's gathered output with multimem.st.
@@ -1056,7 +1056,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
                 if (tl < t_end) {
                   const size_t off = base + static_cast<size_t>(it.out_tok0 + tl) * p.N + n;
                   if (p.comm.nvls) {
-                    store_bf16x8(p.comm.recv_peer[p.comm.rank] + off, o[g]);
+                    // fp32 partials (the switch adds them in fp32 and returns fp32): the only rounding
+                    // on this path is the final one to bf16. The half holds world * rank_stride bf16
+                    // elements, M * N floats fit (checked on the host).
+                    float* dstf = reinterpret_cast<float*>(p.comm.recv_peer[p.comm.rank] +
+                                                           comm_parity * static_cast<size_t>(p.comm.parity_stride)) +
+                                  static_cast<size_t>(it.out_tok0 + tl) * p.N + n;
+                    reinterpret_cast<float4*>(dstf)[0] = make_float4(o[g][0], o[g][1], o[g][2], o[g][3]);
+                    reinterpret_cast<float4*>(dstf)[1] = make_float4(o[g][4], o[g][5], o[g][6], o[g][7]);
                   } else {
                     for (int pr = 0; pr < p.comm.world; ++pr) store_bf16x8(p.comm.recv_peer[pr] + off, o[g]);
                   }
@@ -1138,29 +1145,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_lane,
             }
           };
           if (*last_flag != 0 && nvalid > 0 && cm.nvls) {
-            // the switch sums the `world` replicas of these 16 bytes in fp32 and returns bf16; four
-            // token rows per thread are requested together (one NVLink round trip per batch)
-            const __nv_bfloat16* base = cm.recv_mc + comm_parity * static_cast<size_t>(cm.parity_stride);
-            constexpr int GRPN = 4;
+            // the switch adds the `world` replicas of each float in fp32; two 16-byte requests per
+            // token row, two token rows per thread in flight (one NVLink round trip per batch)
+            const float* basef = reinterpret_cast<const float*>(cm.recv_mc + comm_parity * static_cast<size_t>(cm.parity_stride));
+            constexpr int GRPN = 2;
 #pragma unroll 1
             for (int tl0 = t_begin; tl0 < t_end; tl0 += 8 * GRPN) {
-              uint4 a[GRPN];
+              float4 a[GRPN][2];
 #pragma unroll
               for (int g = 0; g < GRPN; ++g) {
                 const int tl = tl0 + g * 8 + tsub;
-                a[g] = make_uint4(0u, 0u, 0u, 0u);
-                if (tl < t_end)
-                  a[g] = multimem_ld_reduce_bf16x8(base + static_cast<size_t>(it.out_tok0 + tl) * p.N + n);
+                a[g][0] = a[g][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (tl < t_end) {
+                  const float* src = basef + static_cast<size_t>(it.out_tok0 + tl) * p.N + n;
+                  a[g][0] = multimem_ld_reduce_f32x4(src);
+                  a[g][1] = multimem_ld_reduce_f32x4(src + 4);
+                }
               }
               float o[GRPN][8];
 #pragma unroll
               for (int g = 0; g < GRPN; ++g) {
-                const uint32_t w4[4] = {a[g].x, a[g].y, a[g].z, a[g].w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  o[g][2 * j] = bf16_lo(w4[j]);
-                  o[g][2 * j + 1] = bf16_hi(w4[j]);
-                }
+                o[g][0] = a[g][0].x, o[g][1] = a[g][0].y, o[g][2] = a[g][0].z, o[g][3] = a[g][0].w;
+                o[g][4] = a[g][1].x, o[g][5] = a[g][1].y, o[g][6] = a[g][1].z, o[g][7] = a[g][1].w;
               }
               finish_rows(tl0, o);
             }
@@ -1719,7 +1725,9 @@ static int launch_gemm(const CUtensorMap& ml, const CUtensorMap& mc, GemmParams 
       // the multimem forms move 16 bytes: they need the vector layout and aligned multicast addresses
       bool mc_ok = ok && p.comm.flags_mc != nullptr && (COMM == 3 || al16(p.comm.recv_mc)) &&
                    (COMM == 1 || al16(p.comm.out_mc));
-      if (COMM == 1) mc_ok = mc_ok && p.comm.recv_mc != nullptr && (p.N % 8 == 0);
+      if (COMM == 1)
+        mc_ok = mc_ok && p.comm.recv_mc != nullptr && (p.N % 8 == 0) &&
+                2ll * p.M * p.N <= p.comm.parity_stride;   // fp32 partials in the bf16-sized half
       if (COMM == 2)
         mc_ok = mc_ok && p.comm.recv_mc != nullptr && p.comm.out_mc != nullptr &&
                 static_cast<long long>(p.tiles_lane) * p.tiles_col * kLaneRows * BN <= p.comm.parity_stride;

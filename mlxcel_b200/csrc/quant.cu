@@ -249,7 +249,8 @@ qmv_allreduce_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __rest
         const __nv_bfloat16 v = __float2bfloat16(acc[m]);
         const size_t off = pbase + static_cast<size_t>(m) * N + n;
         if (cm.nvls) {
-          cm.recv_peer[cm.rank][off] = v;
+          // fp32 partial: the switch adds in fp32, nothing is rounded before the cross-rank sum
+          reinterpret_cast<float*>(cm.recv_peer[cm.rank] + pbase)[static_cast<size_t>(m) * N + n] = acc[m];
         } else {
           const size_t so = off + cm.rank * static_cast<size_t>(cm.rank_stride);
           for (int pr = 0; pr < cm.world; ++pr) cm.recv_peer[pr][so] = v;
@@ -277,10 +278,9 @@ qmv_allreduce_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __rest
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = 0.f;
       if (cm.nvls) {
-        const uint4 a = multimem_ld_reduce_bf16x8(cm.recv_mc + pbase + static_cast<size_t>(m) * N + n0);
-        const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) o[2 * j] = bf16_lo(w4[j]), o[2 * j + 1] = bf16_hi(w4[j]);
+        const float* src = reinterpret_cast<const float*>(cm.recv_mc + pbase) + static_cast<size_t>(m) * N + n0;
+        const float4 a = multimem_ld_reduce_f32x4(src), b = multimem_ld_reduce_f32x4(src + 4);
+        o[0] = a.x, o[1] = a.y, o[2] = a.z, o[3] = a.w, o[4] = b.x, o[5] = b.y, o[6] = b.z, o[7] = b.w;
       } else {
         for (int r = 0; r < cm.world; ++r) {
           const uint4 a = __ldcg(reinterpret_cast<const uint4*>(
@@ -411,6 +411,7 @@ extern "C" int mx_qmv_allreduce(const void* x, const void* w, const void* scales
   const int vpl = 128 / bits;
   if (K % vpl || group % vpl || K % group || (ldx % 8) || (N % 8) || (ldo % 8) || (residual && (ldr % 8))) return -9;
   if (N / kQmvWarps > kQmvMaxGroups || static_cast<long long>(M) * N > rank_stride) return -9;
+  if (world > 1 && 2ll * M * N > parity_stride) return -9;   // fp32 partials (NVLS) live in the bf16-sized half
   auto mis = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) != 0; };
   if (mis(w) || mis(x) || mis(out) || (residual && mis(residual))) return -9;
   if ((static_cast<long long>(K) * bits / 8) % 16 || (parity_stride % 8) || (rank_stride % 8)) return -9;

@@ -61,8 +61,28 @@ def sampling_from_body(b: dict, default_max: int = 512) -> SamplingParams:
         top_logprobs=int(g("top_logprobs", 0) or 0), logit_bias=lb, min_tokens=int(g("min_tokens", 0) or 0),
         loop_max_pattern=int(g("max_pattern_size", 0) or 0), loop_min_pattern=int(g("min_pattern_size", 4) or 4),
         loop_min_count=int(g("min_count", 8) or 8),
-        thinking_budget=g("thinking_budget_tokens", g("thinking_token_budget", g("thinking_budget"))),
+        thinking_budget=_thinking_budget(b, int(mt)),
     )
+
+
+def _thinking_budget(b: dict, max_tokens: int) -> int | None:
+    """Per-request thinking budget (primary spelling ``thinking_budget_tokens``, vLLM's
+    ``thinking_token_budget`` and Qwen's ``thinking_budget``): -1 / absent = unbounded, 0 = close the
+    block at once, N > 0 = cap. Other negatives and caps beyond ``max_tokens`` are request errors
+    (src/server/thinking_budget.rs value rules)."""
+    raw = b.get("thinking_budget_tokens", b.get("thinking_token_budget", b.get("thinking_budget")))
+    if raw is None:
+        return None
+    try:
+        v = int(raw)
+    except (TypeError, ValueError):
+        raise ValueError(f"thinking_budget_tokens must be an integer (got {raw!r})")
+    if v < -1:
+        raise ValueError(f"thinking_budget_tokens must be >= -1 (got {v}); use -1 for unlimited, 0 for immediate "
+                         f"end, or a positive cap")
+    if v > max_tokens > 0:
+        raise ValueError(f"thinking_budget_tokens ({v}) exceeds max_tokens ({max_tokens})")
+    return v          # -1 stays explicit: it switches a server-side default off for this request
 
 
 class ServerState:
@@ -72,7 +92,8 @@ class ServerState:
         self.api_keys = api_keys or set()
         self.chat_template = chat_template or getattr(tokenizer, "chat_template", None)
         self.started = time.time()
-        self.responses: dict[str, dict] = {}
+        from .extras import ResponsesStore
+        self.responses = ResponsesStore()             # LRU + TTL (responses_store.rs)
         self.lora = None      # LoraManager when the weights are dense
         self.slot_save_path: str | None = None     # --slot-save-path: directory for /slots/{id}?action=save
 
@@ -84,22 +105,43 @@ class ServerState:
     def eos_params(self, sp: SamplingParams) -> SamplingParams:
         ids = [i for i in self.tokenizer.eos_ids() if i is not None]
         sp.stop_token_ids = sorted(set(sp.stop_token_ids) | set(ids))
+        # thinking budget: request value, else the live / start-up default; the block's token ids come
+        # from the tokenizer (no ids, nothing to enforce)
+        settings = getattr(self, "settings", None) or {}
+        if sp.thinking_budget is None:
+            d = settings.get("thinking_budget", getattr(self, "default_thinking_budget", None))
+            sp.thinking_budget = None if d in (None, -1) else int(d)
+        sp.think_start_id = getattr(self.tokenizer, "think_open", None)
+        sp.think_end_id = getattr(self.tokenizer, "think_close", None)
+        from .extras import REQUEST_CTX
+        ctx = REQUEST_CTX.get()
+        if ctx.get("priority") and not sp.priority:
+            sp.priority = int(ctx["priority"])        # X-Priority header -> priority lane of the queue
         return sp
 
 
-async def _generate(state: ServerState, prompt_ids, sp, constraint=None):
-    """Async generator of GenEvents for one request."""
+async def _generate(state: ServerState, prompt_ids, sp, constraint=None, public_id: str | None = None):
+    """Async generator of GenEvents for one request. ``public_id`` (a chat / response id) makes the
+    request reachable for ``/v1/chat/completions/control`` and ``/v1/responses/{id}/cancel``."""
     q: asyncio.Queue = asyncio.Queue()
     req = GenRequest(prompt_ids=prompt_ids, params=state.eos_params(sp), loop=asyncio.get_running_loop(), out=q,
                      constraint=constraint, request_id=uuid.uuid4().hex)
+    inflight = getattr(state, "inflight", None)
+    if public_id and inflight is not None:
+        inflight[public_id] = req
     state.worker.submit(req)
     try:
         while True:
             ev = await q.get()
+            if ev.kind == "done" and getattr(state, "hist", None) and ev.timings:
+                state.hist["ttft"].observe(ev.timings["prompt_ms"] / 1e3)
+                state.hist["decode_tps"].observe(ev.timings["predicted_per_second"])
             yield ev
             if ev.kind in ("done", "error"):
                 return
     finally:
+        if public_id and inflight is not None:
+            inflight.pop(public_id, None)
         if req.seq_id is not None and req.seq_id in state.worker.by_seq:
             state.worker.cancel(req)
 
@@ -126,9 +168,25 @@ def create_app(state: ServerState) -> FastAPI:
                 request.headers.get("x-api-key", "")
             if key not in state.api_keys:
                 return _err(401, "invalid API key", "authentication_error")
-        resp = await call_next(request)
-        resp.headers.setdefault("Access-Control-Allow-Origin", "*")
-        return resp
+        return await call_next(request)
+
+    from .extras import install_extras, tee_stream, REQUEST_CTX
+    install_extras(app, state)      # CORS (outermost: preflights never reach the key check), logging, settings, ...
+
+    @app.exception_handler(ValueError)
+    async def bad_request(request: Request, exc: ValueError):
+        return _err(400, str(exc))
+
+    _parse_sampling = globals()["sampling_from_body"]
+
+    def sampling_from_body(b: dict, default_max: int = 512) -> SamplingParams:
+        """Request body -> sampling parameters, with the live defaults of ``/v1/settings`` filled in."""
+        st = state.settings
+        if st.get("default_max_tokens") and not any(k in b for k in ("max_tokens", "max_completion_tokens", "n_predict")):
+            default_max = int(st["default_max_tokens"])
+        if st.get("default_temperature") is not None and b.get("temperature") is None:
+            b = {**b, "temperature": st["default_temperature"]}
+        return _parse_sampling(b, default_max)
 
     # ------------------------------------------------------------------ basic
     @app.get("/health")
@@ -347,9 +405,9 @@ def create_app(state: ServerState) -> FastAPI:
         return {"input_tokens": len(tk.encode(state.render(msgs)))}
 
     # ------------------------------------------------------------------ completions
-    async def _run_text(prompt_ids, sp, constraint=None):
+    async def _run_text(prompt_ids, sp, constraint=None, public_id=None):
         text, lps, toks, final = [], [], [], None
-        async for ev in _generate(state, prompt_ids, sp, constraint):
+        async for ev in _generate(state, prompt_ids, sp, constraint, public_id=public_id):
             if ev.kind == "token":
                 text.append(ev.text)
                 toks.append(ev.token_id)
@@ -533,7 +591,7 @@ def create_app(state: ServerState) -> FastAPI:
                 n_calls = 0
                 yield _sse({**base, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""},
                                                  "finish_reason": None}]})
-                async for ev in _generate(state, ids, sp, constraint):
+                async for ev in _generate(state, ids, sp, constraint, public_id=cid):
                     if ev.kind in ("token", "done"):
                         text, calls = (filt.feed(ev.text) if filt else (ev.text, []))
                         if ev.kind == "done" and filt:
@@ -555,7 +613,9 @@ def create_app(state: ServerState) -> FastAPI:
                     elif ev.kind == "error":
                         yield _sse({"error": {"message": ev.error, "type": "server_error"}})
                 yield b"data: [DONE]\n\n"
-            return StreamingResponse(gen(), media_type="text/event-stream")
+            conv = REQUEST_CTX.get().get("conversation_id")
+            return StreamingResponse(tee_stream(state, gen(), conv), media_type="text/event-stream",
+                                     headers={"X-Conversation-Id": conv} if conv else None)
         try:
             runs = await _run_n(body, ids, sp, lambda: constraint_from_request(
                 tk, response_format=body.get("response_format"), grammar=body.get("grammar")))
@@ -581,22 +641,7 @@ def create_app(state: ServerState) -> FastAPI:
 
     # ------------------------------------------------------------------ responses API
     def _responses_messages(body: dict) -> list[dict]:
-        msgs = []
-        if body.get("instructions"):
-            msgs.append({"role": "system", "content": body["instructions"]})
-        prev = body.get("previous_response_id")
-        if prev and prev in state.responses:
-            msgs += state.responses[prev]["_messages"]
-        inp = body.get("input", "")
-        if isinstance(inp, str):
-            msgs.append({"role": "user", "content": inp})
-        else:
-            for item in inp:
-                c = item.get("content", "")
-                if isinstance(c, list):
-                    c = "".join(p.get("text", "") for p in c if isinstance(p, dict))
-                msgs.append({"role": item.get("role", "user"), "content": c})
-        return msgs
+        return _responses_input_messages(state, body)
 
     @app.post("/v1/responses")
     async def responses(body: dict):
@@ -609,24 +654,52 @@ def create_app(state: ServerState) -> FastAPI:
         b2["max_tokens"] = body.get("max_output_tokens", 512)
         sp = sampling_from_body(b2, 512)
         rid = "resp_" + uuid.uuid4().hex[:24]
+        created = int(time.time())
+
+        async def run() -> dict:
+            text, toks, lps, fin = await _run_text(ids or [0], sp, public_id=rid)
+            reasoning, answer = split_reasoning(text)
+            out = {"id": rid, "object": "response", "created_at": created, "status": "completed",
+                   "model": state.model_id,
+                   "output": [{"type": "message", "id": "msg_" + uuid.uuid4().hex[:24], "role": "assistant",
+                               "status": "completed",
+                               "content": [{"type": "output_text", "text": answer, "annotations": []}]}],
+                   "output_text": answer,
+                   "usage": {"input_tokens": fin.usage["prompt_tokens"], "output_tokens": fin.usage["completion_tokens"],
+                             "total_tokens": fin.usage["total_tokens"]}}
+            if body.get("store", True) or body.get("background"):
+                cur = state.responses.get(rid)
+                if cur is not None and cur.get("status") == "cancelled":
+                    return cur                      # cancelled while it ran: keep the cancelled record
+                state.responses[rid] = {**out, "_messages": msgs + [{"role": "assistant", "content": answer}]}
+            return out
+
+        if body.get("background"):
+            # background mode: the response object comes back at once (status "queued"), the generation
+            # runs as a task of the server; GET /v1/responses/{id} polls, POST .../cancel stops it
+            stub = {"id": rid, "object": "response", "created_at": created, "status": "queued", "model": state.model_id,
+                    "output": [], "background": True, "_messages": msgs}
+            state.responses[rid] = stub
+
+            async def job():
+                stub["status"] = "in_progress"
+                try:
+                    await run()
+                except asyncio.CancelledError:
+                    stub["status"] = "cancelled"
+                    raise
+                except Exception as e:
+                    cur = state.responses.get(rid) or stub
+                    if cur.get("status") != "cancelled":
+                        cur["status"], cur["error"] = "failed", {"message": str(e)}
+                finally:
+                    state.background.pop(rid, None)
+            state.background[rid] = asyncio.create_task(job())
+            return {k: v for k, v in stub.items() if not k.startswith("_")}
         try:
-            text, toks, lps, fin = await _run_text(ids or [0], sp)
+            return await run()
         except (RuntimeError, ValueError) as e:
             return _err(400, str(e))
-        reasoning, answer = split_reasoning(text)
-        out = {"id": rid, "object": "response", "created_at": int(time.time()), "status": "completed",
-               "model": state.model_id,
-               "output": [{"type": "message", "id": "msg_" + uuid.uuid4().hex[:24], "role": "assistant",
-                           "status": "completed",
-                           "content": [{"type": "output_text", "text": answer, "annotations": []}]}],
-               "output_text": answer,
-               "usage": {"input_tokens": fin.usage["prompt_tokens"], "output_tokens": fin.usage["completion_tokens"],
-                         "total_tokens": fin.usage["total_tokens"]}}
-        if body.get("store", True):
-            state.responses[rid] = {**out, "_messages": msgs + [{"role": "assistant", "content": answer}]}
-            while len(state.responses) > 256:
-                state.responses.pop(next(iter(state.responses)))
-        return out
 
     @app.get("/v1/responses/{rid}")
     async def get_response(rid: str):
@@ -701,6 +774,27 @@ def create_app(state: ServerState) -> FastAPI:
         return [{"index": i, "embedding": v} for i, v in enumerate(vecs)]
 
     return app
+
+
+def _responses_input_messages(state, body: dict) -> list[dict]:
+    """Responses API ``instructions`` / ``previous_response_id`` / ``input`` -> chat messages."""
+    msgs = []
+    if body.get("instructions"):
+        msgs.append({"role": "system", "content": body["instructions"]})
+    prev = body.get("previous_response_id")
+    prev_obj = state.responses.get(prev) if prev else None
+    if prev_obj is not None:
+        msgs += prev_obj.get("_messages", [])
+    inp = body.get("input", "")
+    if isinstance(inp, str):
+        msgs.append({"role": "user", "content": inp})
+    else:
+        for item in inp:
+            c = item.get("content", "")
+            if isinstance(c, list):
+                c = "".join(p.get("text", "") for p in c if isinstance(p, dict))
+            msgs.append({"role": item.get("role", "user"), "content": c})
+    return msgs
 
 
 def _stop_type(reason: str) -> str:

@@ -39,4 +39,18 @@ def render_metrics(state) -> str:
     m("mlxcel_cuda_graph_replays_total", "counter", "Decode steps served by CUDA graph replay.", e.stats["graph_replays"])
     m("mlxcel_batch_decode_tokens_total", "counter", "Tokens produced by decode rows.", e.stats["decode_tokens"])
     m("mlxcel_batch_prefill_tokens_total", "counter", "Prompt tokens run through prefill.", e.stats["prefill_tokens"])
+    m("mlxcel_spec_decode_rounds_total", "counter", "Speculative verify rounds.", e.stats.get("spec_rounds", 0))
+    m("mlxcel_spec_decode_drafted_total", "counter", "Draft tokens proposed.", e.stats.get("spec_drafted", 0))
+    m("mlxcel_spec_decode_accepted_total", "counter", "Draft tokens accepted.", e.stats.get("spec_accepted", 0))
+    m("mlxcel_thinking_forced_total", "counter", "End-of-thinking tokens forced by a thinking budget.",
+      e.stats.get("thinking_forced", 0))
+    m("mlxcel_step_hangs_total", "counter", "Engine steps that exceeded the hang timeout.", c.get("hangs", 0))
+    rs = getattr(getattr(state, "responses", None), "stats", None)
+    if rs:
+        m("mlxcel_responses_store_entries", "gauge", "Stored Responses API objects.", len(state.responses))
+        m("mlxcel_responses_store_expired_total", "counter", "Stored responses dropped by TTL.", rs["expired"])
+    hist = getattr(state, "hist", None)
+    if hist:
+        lines += hist["ttft"].render("mlxcel_request_ttft_seconds", "Time to first token per request.")
+        lines += hist["decode_tps"].render("mlxcel_request_decode_tokens_per_second", "Decode throughput per request.")
     return "\n".join(lines) + "\n"

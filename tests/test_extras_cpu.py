@@ -298,7 +298,7 @@ def test_llama_server_compat_manifest_matches_the_parser_and_the_routes():
             assert all(known[f].dest.startswith("compat_noop_") for f in o["flags"])
         elif o["status"] == "unsupported":
             assert o["flags"][0].split()[0] not in known and o["why"]
-    src = Path(app_mod.__file__).read_text()
+    src = Path(app_mod.__file__).read_text() + (Path(app_mod.__file__).parent / "extras.py").read_text()
     for r in doc["routes"]:
         path = r.split("?")[0].replace("{id}", "{slot_id}")
         assert f'"{path}"' in src, r

@@ -4,10 +4,12 @@ size, and is skipped on boxes with one GPU.
 
 Error bounds come from an fp32 reduction of the same shards. bf16 keeps 8 significant bits, so one
 round-to-nearest changes a value v by at most ``u |v|`` with ``u = 2^-8``. A fused result differs
-from the fp32 sum of the per-rank products by the rounding of each partial tile (the kernels round
-partials to bf16 before they cross NVLink), by the rounding of the result itself and, on the NVLS
-path, by the rounding of the sum the switch returns (it accumulates in fp32 and hands back bf16):
-at most ``u (sum_r |partial_r| + [|sum_r partial_r|] + |result|)`` per element.
+from the fp32 sum of the per-rank products by the rounding of each partial tile (the peer-store
+kernels round partials to bf16 before they cross NVLink) and by the rounding of the result itself:
+at most ``u (sum_r |partial_r| + |result|)`` per element. The one-shot NVLS kernels keep fp32
+partials and let the switch add them in fp32, so only ``u |result|`` remains there. The two-shot
+NVLS kernel moves bf16 partials and the switch hands its fp32 sum back TRUNCATED to bf16
+(measured), which adds ``2u |sum_r partial_r|``.
 """
 import os
 import socket
@@ -41,9 +43,11 @@ def _run(name: str, world: int, body: str, timeout: int = 600, nvls: bool = Fals
         from mlxcel_b200.parallel.tp import TPComm
         EPS = 2.0 ** -8
         def bound(parts_abs_sum, want, switch_sum=None):
-            b = parts_abs_sum + want.abs()
+            b = want.abs()
+            if parts_abs_sum is not None:
+                b = b + parts_abs_sum
             if switch_sum is not None:
-                b = b + switch_sum.abs()
+                b = b + 2 * switch_sum.abs()
             return 1.01 * EPS * b + 1e-3
     """ % ROOT) + textwrap.dedent(body) + textwrap.dedent("""
         torch.cuda.synchronize()
@@ -99,17 +103,25 @@ _FUSED_BODY = """
         parts = [x[:, r * 512:(r + 1) * 512].float() @ w[:, r * 512:(r + 1) * 512].float().t() for r in range(world)]
         want = sum(parts) + bias.float() + res.float()           # the fp32 reduction
         pabs = sum(p.abs() for p in parts)
-        sw = sum(parts) if nvls else None                        # what the switch rounds on the NVLS path
+        sw = sum(parts) if nvls else None                        # what the switch narrows on the two-shot NVLS path
         for rep in range(3):
             got = comm.row_parallel_linear(x[:, ks].contiguous(), w[:, ks].contiguous(), bias, res.clone())
             torch.cuda.synchronize()
             diff = (got.float() - want).abs()
-            assert bool((diff <= bound(pabs, want, sw if M <= 256 else None)).all()), (M, rep, diff.max().item())
+            # row_parallel_linear: one-shot for M <= 256 (NVLS: fp32 partials), two-shot above
+            bnd = bound(None, want) if (nvls and M <= 256) else bound(pabs, want, sw)
+            if not bool((diff <= bnd).all()):
+                i = int((diff - bnd).argmax())
+                r_, c_ = divmod(i, N)
+                detail = dict(M=M, rep=rep, diff=diff[r_, c_].item(), bound=bnd[r_, c_].item(), got=got[r_, c_].item(),
+                              want=want[r_, c_].item(), parts=[p[r_, c_].item() for p in parts],
+                              bias=bias[c_].item(), res=res[r_, c_].item(), bad=int((diff > bnd).sum()))
+                raise AssertionError(f"DETAIL {detail}")
             worst = max(worst, diff.max().item())
             ref0 = got.clone(); dist.broadcast(ref0, 0)
             if nvls:
                 # every rank asks the switch for its own sum: equal up to the result's rounding
-                assert bool(((ref0.float() - got.float()).abs() <= 2 * EPS * (want.abs() + sw.abs()) + 1e-3).all()), (M, rep)
+                assert bool(((ref0.float() - got.float()).abs() <= 2 * EPS * want.abs() + 1e-3).all()), (M, rep)
             else:
                 assert torch.equal(ref0, got), (M, rep)          # rank-ordered sums: bitwise identical
             if M > 256:   # the fused two-shot kernel: one owner reduces, everyone receives the same bits
@@ -132,7 +144,7 @@ _FUSED_BODY = """
             # the GEMM form rounds every dequantised weight to bf16 before the MMA: an error of up to
             # u on each product, i.e. on sum_k |x_k| |w_k| (no cancellation), on top of the partial rounding
             prod_abs = sum(x[:, r * 512:(r + 1) * 512].float().abs() @ wparts[r].abs().t() for r in range(world))
-            qbound = bound(sum(p.abs() for p in qparts), want_q, sum(qparts) if nvls else None) + EPS * prod_abs
+            qbound = bound(None if nvls else sum(p.abs() for p in qparts), want_q) + EPS * prod_abs
             got_q = comm.row_parallel_linear(x[:, ks].contiguous(), qts, bias, res.clone())
             torch.cuda.synchronize()
             dq = (got_q.float() - want_q).abs()
@@ -149,7 +161,7 @@ _FUSED_BODY = """
                 for rep in range(2):      # repeated calls reuse the channel (parity, flags)
                     again = comm.row_parallel_linear(x[:, ks].contiguous(), qts, bias, res.clone())
                     torch.cuda.synchronize()
-                    assert bool(((again.float() - got_q.float()).abs() <= 2 * EPS * (want_q.abs() + sum(qparts).abs()) + 1e-3).all()), (M, rep)
+                    assert bool(((again.float() - got_q.float()).abs() <= 2 * EPS * want_q.abs() + 1e-3).all()), (M, rep)
         # stand-alone all-reduce (one-shot for small, two-shot for large tensors)
         part = torch.randn(M, N, device=dev).to(torch.bfloat16) * (rank + 1)
         aparts = [torch.empty_like(part) for _ in range(world)]
@@ -157,7 +169,7 @@ _FUSED_BODY = """
         want_ar = sum(p.float() for p in aparts)
         got_ar = comm.all_reduce(part.clone())
         torch.cuda.synchronize()
-        assert bool(((got_ar.float() - want_ar).abs() <= 2.02 * EPS * want_ar.abs() + 1e-3).all()), M
+        assert bool(((got_ar.float() - want_ar).abs() <= 3.03 * EPS * want_ar.abs() + 1e-3).all()), M
         # all-gather of a vocab-parallel projection
         if M <= 256:
             Vl = 1024
