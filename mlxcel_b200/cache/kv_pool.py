@@ -3,7 +3,9 @@
 A block id addresses the same slot in every layer, so a sequence has one block table for the
 whole model. ``kv_bits=8`` stores uint8 values plus a bf16 (scale, bias) pair per 64 elements
 (``--kv-bits 8 --kv-group-size 64`` of the reference, src/cli/batch_quant_args.rs:33-80), written
-by the fused RoPE+append kernel and dequantized inside the attention kernels.
+by the fused RoPE+append kernel and dequantized inside the attention kernels. ``kv_bits=4`` is the
+same affine scheme with 16 levels, two codes per byte (``[..., D / 2]`` bytes per row); the
+reference rejects uniform 4-bit KV (its 4-bit mode is TurboQuant), so this mode has no counterpart.
 """
 from __future__ import annotations
 
@@ -16,8 +18,8 @@ from ..ops import KVLayer
 class KVPool:
     def __init__(self, cfg: ModelConfig, num_blocks: int, block_size: int = 16, *, kv_bits: int = 16,
                  device="cpu", dtype=torch.bfloat16, tp_size: int = 1, num_layers: int | None = None):
-        if kv_bits not in (16, 8):
-            raise ValueError("kv_bits must be 16 or 8")
+        if kv_bits not in (16, 8, 4):
+            raise ValueError("kv_bits must be 16, 8 or 4")
         self.cfg, self.num_blocks, self.block_size, self.kv_bits = cfg, num_blocks, block_size, kv_bits
         self.Hkv = max(1, cfg.num_key_value_heads // tp_size)
         self.D = cfg.head_dim
@@ -31,9 +33,10 @@ class KVPool:
                 km = vm = None
             else:
                 if self.D % 64:
-                    raise ValueError("8-bit KV needs head_dim % 64 == 0")
-                k = torch.zeros(shape, dtype=torch.uint8, device=device)
-                v = torch.zeros(shape, dtype=torch.uint8, device=device)
+                    raise ValueError("quantized KV needs head_dim % 64 == 0")
+                qshape = shape if kv_bits == 8 else (num_blocks, self.Hkv, block_size, self.D // 2)
+                k = torch.zeros(qshape, dtype=torch.uint8, device=device)
+                v = torch.zeros(qshape, dtype=torch.uint8, device=device)
                 mshape = (num_blocks, self.Hkv, block_size, self.D // 64, 2)
                 km = torch.zeros(mshape, dtype=torch.bfloat16, device=device)
                 vm = torch.zeros(mshape, dtype=torch.bfloat16, device=device)
@@ -44,8 +47,8 @@ class KVPool:
                         num_layers: int | None = None) -> int:
         Hkv = max(1, cfg.num_key_value_heads // tp_size)
         L = cfg.num_hidden_layers if num_layers is None else num_layers
-        per_tok = Hkv * cfg.head_dim * (2 if kv_bits == 16 else 1)
-        if kv_bits == 8:
+        per_tok = Hkv * cfg.head_dim * kv_bits // 8
+        if kv_bits != 16:
             per_tok += Hkv * (cfg.head_dim // 64) * 4
         return 2 * per_tok * block_size * L
 

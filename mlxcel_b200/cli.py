@@ -23,7 +23,7 @@ def _add_model_args(p):
     p.add_argument("--parallel", "-np", type=int, default=4, help="concurrent sequences (slots)")
     p.add_argument("--max-batch-tokens", type=int, default=8192)
     p.add_argument("--prefill-chunk-size", type=int, default=2048)
-    p.add_argument("--kv-bits", type=int, default=0, choices=[0, 8, 16])
+    p.add_argument("--kv-bits", type=int, default=0, choices=[0, 4, 8, 16])
     p.add_argument("--kv-cache-blocks", type=int, default=0)
     p.add_argument("--block-size", type=int, default=16)
     p.add_argument("--no-prompt-cache", action="store_true")
@@ -89,10 +89,12 @@ def _apply_compat(a) -> list[str]:
         a.prefill_chunk_size = a.compat_ubatch
     types = [t for t in (getattr(a, "compat_ctk", None), getattr(a, "compat_ctv", None)) if t]
     for t in types:
-        if t.lower() not in ("f16", "bf16", "f32", "q8_0", "int8", "fp8"):
-            raise SystemExit(f"cache type {t!r} is not supported (f16, bf16, q8_0)")
+        if t.lower() not in ("f16", "bf16", "f32", "q8_0", "int8", "fp8", "q4_0", "q4_1"):
+            raise SystemExit(f"cache type {t!r} is not supported (f16, bf16, q8_0, q4_0)")
     if any(t.lower() in ("q8_0", "int8", "fp8") for t in types) and not getattr(a, "kv_bits", 0):
         a.kv_bits = 8
+    if any(t.lower() in ("q4_0", "q4_1") for t in types) and not getattr(a, "kv_bits", 0):
+        a.kv_bits = 4
     if getattr(a, "compat_no_cache_prompt", False):
         a.no_prompt_cache = True
     if getattr(a, "compat_lookup", None) is not None:
@@ -857,7 +859,7 @@ def arch_catalog() -> dict:
             how = "transformers logits (as gemma3_text)"
         fams.append(dict(name=name, executor=ex, checked_against=how))
     return {"families": fams, "encoders": ["bert", "modernbert"], "quantization": ["affine", "mxfp4", "mxfp8", "fp8 (widened at load)"],
-            "kv_bits": [16, 8], "parallelism": ["tp", "ep", "pp"]}
+            "kv_bits": [16, 8, 4], "parallelism": ["tp", "ep", "pp"]}
 
 
 def cmd_arch(a):

@@ -57,6 +57,11 @@ __device__ __forceinline__ void load8(const void* pool, size_t elem_off, float (
       f[2 * j] = bf16_lo(w[j]);
       f[2 * j + 1] = bf16_hi(w[j]);
     }
+  } else if (KV_BITS == 4) {
+    // two values per byte, even element in the low nibble: 8 elements = one 32-bit word
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(pool) + (elem_off >> 1));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = static_cast<float>((w >> (4 * j)) & 0xFu);
   } else {
     const uint2 a = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(pool) + elem_off);
     const uint32_t w[2] = {a.x, a.y};
@@ -152,7 +157,7 @@ paged_decode_kernel(const DecodeParams p) {
 #pragma unroll 2
           for (int d0 = grp * 64; d0 < grp * 64 + 64; d0 += 8) {
             float kf[8];
-            load8<8>(p.k_pool, base + d0, kf);
+            load8<KV_BITS>(p.k_pool, base + d0, kf);
 #pragma unroll
             for (int g = 0; g < G; ++g) {
               const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][d0]);
@@ -433,8 +438,8 @@ paged_prefill_kernel(const PrefillParams p) {
         float kf[8], vf[8];
         uint4 ko = make_uint4(0, 0, 0, 0), vo = make_uint4(0, 0, 0, 0);
         if (ok) {
-          load8<8>(p.k_pool, row * D + c * 8, kf);
-          load8<8>(p.v_pool, row * D + c * 8, vf);
+          load8<KV_BITS>(p.k_pool, row * D + c * 8, kf);
+          load8<KV_BITS>(p.v_pool, row * D + c * 8, vf);
           const int grp = (c * 8) / 64;
           const __nv_bfloat16* km = p.k_meta + row * (D / 64) * 2 + grp * 2;
           const __nv_bfloat16* vm = p.v_meta + row * (D / 64) * 2 + grp * 2;
@@ -714,8 +719,8 @@ paged_decode_mma_kernel(const DecodeParams p, const int G) {
           uint4 ko = make_uint4(0, 0, 0, 0), vo = make_uint4(0, 0, 0, 0);
           if (ok) {
             float kf[8], vf[8];
-            load8<8>(p.k_pool, row * D + c * 8, kf);
-            load8<8>(p.v_pool, row * D + c * 8, vf);
+            load8<KV_BITS>(p.k_pool, row * D + c * 8, kf);
+            load8<KV_BITS>(p.v_pool, row * D + c * 8, vf);
             const int gq = (c * 8) / 64;
             const __nv_bfloat16* km = p.k_meta + row * (D / 64) * 2 + gq * 2;
             const __nv_bfloat16* vm = p.v_meta + row * (D / 64) * 2 + gq * 2;
@@ -1057,6 +1062,9 @@ extern "C" int mx_paged_decode(const void* q, long long q_stride, const void* k_
     if (kv_bits == 8)
       return D == 128 ? launch_decode_mma<128, 8>(p, G, grid, stream)
                       : launch_decode_mma<64, 8>(p, G, grid, stream);
+    if (kv_bits == 4)
+      return D == 128 ? launch_decode_mma<128, 4>(p, G, grid, stream)
+                      : launch_decode_mma<64, 4>(p, G, grid, stream);
     return -1;
   }
   if (kv_bits == 16) return launch_decode<16>(p, D, G, grid, stream);
@@ -1102,5 +1110,6 @@ extern "C" int mx_paged_prefill(const void* q, long long q_stride, const void* k
   if (grid > 0x7fffffffll) return -1;
   if (kv_bits == 16) return launch_prefill<16>(p, D, G, static_cast<int>(grid), stream);
   if (kv_bits == 8) return launch_prefill<8>(p, D, G, static_cast<int>(grid), stream);
+  if (kv_bits == 4) return launch_prefill<4>(p, D, G, static_cast<int>(grid), stream);
   return -1;
 }

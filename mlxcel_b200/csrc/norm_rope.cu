@@ -1,5 +1,5 @@
 // Memory-bound row kernels: residual-add + RMSNorm, per-head RMSNorm, RoPE + paged KV append
-// (with optional 8-bit affine KV quantization), embedding gather, gated activations.
+// (with optional 8-bit / 4-bit affine KV quantization), embedding gather, gated activations.
 //
 // Parity targets in the reference: fused_add_rms_norm (src/lib/mlxcelverse/kernels/fused_norm.h:17-77),
 // fused_rope_qk_append (src/lib/mlxcelverse/kernels/fused_rope_append.h:17-114) and the per-token
@@ -232,6 +232,37 @@ __global__ void rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* _
     if (KV_BITS == 16) {
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(is_k ? k_pool : v_pool) + row * D;
       for (int i = lane; i < D; i += 32) dst[i] = __float2bfloat16(st[i]);
+    } else if (KV_BITS == 4) {
+      // 4-bit affine, groups of 64 along D: q = round((x - min) / scale), scale = (max - min) / 15;
+      // element i of a row lives in byte i / 2 (even elements in the low nibble), D / 2 bytes per row.
+      uint8_t* dst = reinterpret_cast<uint8_t*>(is_k ? k_pool : v_pool) + row * (D / 2);
+      __nv_bfloat16* meta = (is_k ? k_meta : v_meta) + row * (D / 64) * 2;
+      for (int g = 0; g < D / 64; ++g) {
+        const float a = st[g * 64 + lane], b = st[g * 64 + 32 + lane];
+        float mn = fminf(a, b), mxv = fmaxf(a, b);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+          mxv = fmaxf(mxv, __shfl_xor_sync(0xffffffffu, mxv, o));
+        }
+        float scale = __bfloat162float(__float2bfloat16((mxv - mn) / 15.0f));
+        const float bias = __bfloat162float(__float2bfloat16(mn));
+        if (scale == 0.f) scale = 1.0f;
+        const float inv = 1.0f / scale;
+        const int qa = min(15, max(0, __float2int_rn((a - bias) * inv)));
+        const int qb = min(15, max(0, __float2int_rn((b - bias) * inv)));
+        // neighbouring lanes share a byte: the even lane stores (own | odd neighbour << 4)
+        const int qa_hi = __shfl_down_sync(0xffffffffu, qa, 1);
+        const int qb_hi = __shfl_down_sync(0xffffffffu, qb, 1);
+        if ((lane & 1) == 0) {
+          dst[g * 32 + (lane >> 1)] = static_cast<uint8_t>(qa | (qa_hi << 4));
+          dst[g * 32 + 16 + (lane >> 1)] = static_cast<uint8_t>(qb | (qb_hi << 4));
+        }
+        if (lane == 0) {
+          meta[g * 2] = __float2bfloat16(scale);
+          meta[g * 2 + 1] = __float2bfloat16(bias);
+        }
+      }
     } else {
       // 8-bit affine, groups of 64 along D: q = round((x - min) / scale), scale = (max - min) / 255.
       uint8_t* dst = reinterpret_cast<uint8_t*>(is_k ? k_pool : v_pool) + row * D;
@@ -516,8 +547,8 @@ extern "C" int mx_rope_append(void* qkv, const int* positions, const int* slot_m
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (T <= 0) return 0;
   if (D > kMaxHeadDim || D % 2 || rot_dim > D || rot_dim % 2) return -1;
-  if (kv_bits == 8 && D % 64) return -1;
-  if (kv_bits != 16 && kv_bits != 8) return -1;
+  if ((kv_bits == 8 || kv_bits == 4) && D % 64) return -1;
+  if (kv_bits != 16 && kv_bits != 8 && kv_bits != 4) return -1;
   // Few tokens (decode): few heads per warp for parallelism; many tokens (prefill): all heads of a
   // token in one warp so the sin / cos evaluation is shared 40-fold.
   const int slots = Hq + 2 * Hkv;
@@ -558,7 +589,12 @@ extern "C" int mx_rope_append(void* qkv, const int* positions, const int* slot_m
   auto KN = static_cast<const __nv_bfloat16*>(k_norm_w);
   MX_PREFER_SHARED(rope_append_kernel<16>);
   MX_PREFER_SHARED(rope_append_kernel<8>);
-  if (kv_bits == 16)
+  MX_PREFER_SHARED(rope_append_kernel<4>);
+  if (kv_bits == 4)
+    launch_kernel(rope_append_kernel<4>, dim3(blocks), dim3(kRopeWarps * 32), 0, stream, Q, positions,
+                  slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv, D, rot_dim,
+                  block_size, rope_mode, mscale, hpw);
+  else if (kv_bits == 16)
     launch_kernel(rope_append_kernel<16>, dim3(blocks), dim3(kRopeWarps * 32), 0, stream, Q, positions,
                   slot_mapping, inv_freq, k_pool, v_pool, KM, VM, QN, KN, norm_eps, T, Hq, Hkv, D, rot_dim,
                   block_size, rope_mode, mscale, hpw);

@@ -83,6 +83,8 @@ class EngineConfig:
     mixed_steps: bool = True
     preemption: bool = True
     lookahead: bool = True               # submit decode step n+1 before reading step n (greedy rows)
+    window_release: bool = True          # sliding-window layers get their own block pool and give back
+    #                                      the blocks that fell out of the window (RotatingKVCache role)
     status_check_interval: int = 64      # steps between reads of the device status word (0 = never)
 
 
@@ -109,10 +111,36 @@ class Engine:
             e.num_blocks = self._auto_num_blocks(tp, nl)
         # fp32 models (CPU oracles) keep fp32 keys / values; everything else stores bf16 (or 8-bit)
         wdt = getattr(getattr(model.w, "final_norm", None), "dtype", torch.bfloat16)
+        kv_dtype = torch.float32 if wdt == torch.float32 else torch.bfloat16
+        # Sliding-window layers (gpt-oss alternates 128-token windows with full layers, Mistral / Gemma
+        # have them too) never attend beyond their window: they get a pool of their own whose blocks
+        # are returned once every token in them is out of reach, instead of holding the whole
+        # context (the reference's RotatingKVCache, src/lib/mlxcel-core/src/cache.rs:4397). The
+        # window pool has no prefix index (a released block cannot be shared), so prefix caching
+        # is off for such models — the reference does the same for its model-owned mixed caches.
+        self.win_layers = self._window_layers() if e.window_release else None
+        self.bm_win = self.pool_win = None
+        self.window = 0
+        if self.win_layers is not None:
+            e.prefix_cache = False
+            self.window = max(self.win_layers)
+            n_win = sum(1 for w in self.win_layers if w > 0)
+            per_pf = (self.window + max(e.prefill_chunk_alone, e.prefill_chunk_contended) + e.block_size - 1) // e.block_size + 2
+            per_dec = (self.window + self.spec_k_max + e.block_size - 1) // e.block_size + 3
+            self.win_blocks_prefill = per_pf
+            nb_win = min(e.num_blocks, e.max_prefill_seqs * per_pf + e.max_batch * per_dec + 8)
+            self.pool_win = KVPool(cfg, nb_win, e.block_size, kv_bits=e.kv_bits, device=self.device, dtype=kv_dtype,
+                                   tp_size=tp, num_layers=n_win)
+            self.bm_win = BlockManager(nb_win, e.block_size, False, 0.0)
+            nl = nl - n_win
         self.pool = KVPool(cfg, e.num_blocks, e.block_size, kv_bits=e.kv_bits, device=self.device,
-                           dtype=torch.float32 if wdt == torch.float32 else torch.bfloat16,
-                           tp_size=tp, num_layers=nl)
+                           dtype=kv_dtype, tp_size=tp, num_layers=nl)
         self.bm = BlockManager(e.num_blocks, e.block_size, e.prefix_cache, e.watermark)
+        if self.win_layers is None:
+            self.kv_layers = self.pool.layers
+        else:
+            full, win = iter(self.pool.layers), iter(self.pool_win.layers)
+            self.kv_layers = [next(win) if w > 0 else next(full) for w in self.win_layers]
         self.sampler = Sampler(cfg.vocab_size, self.device)
         self.max_blocks_per_seq = (e.max_model_len + e.block_size - 1) // e.block_size
         self.waiting: deque[Sequence] = deque()
@@ -131,6 +159,46 @@ class Engine:
                           graph_kernel_launches=0, spec_rounds=0, spec_drafted=0, spec_accepted=0)
 
     # ------------------------------------------------------------------ setup
+    spec_k_max = 16          # most tokens a verify round may append beyond the current one
+
+    def _window_layers(self) -> list[int] | None:
+        """Window size per layer of this executor (0 = full attention), or None when no layer has one
+        or the executor does not take per-pool tables."""
+        m = self.model
+        if self.recurrent or not hasattr(m, "layer_range") or not hasattr(m, "_attend") or self.pipeline:
+            return None
+        ws = [int(self.cfg.layer_window(i)) for i in m.layer_range]
+        return ws if any(w > 0 for w in ws) else None
+
+    # The window pool mirrors the main block manager: same sequences, same token counts.
+    def _kv_create(self, seq_id: int) -> None:
+        self.bm.create(seq_id, 0)
+        if self.bm_win is not None:
+            self.bm_win.create(seq_id, 0)
+
+    def _kv_free(self, seq_id: int) -> None:
+        self.bm.free_seq(seq_id)
+        if self.bm_win is not None:
+            self.bm_win.free_seq(seq_id)
+
+    def _kv_reserve(self, seq_id: int, total: int) -> bool:
+        if not self.bm.reserve(seq_id, total):
+            return False
+        return self.bm_win is None or self.bm_win.reserve(seq_id, total)
+
+    def _kv_truncate(self, seq_id: int, n: int) -> None:
+        self.bm.truncate(seq_id, n)
+        if self.bm_win is not None:
+            self.bm_win.truncate(seq_id, n)
+
+    def _release_window(self, seqs) -> None:
+        """After a step: blocks of the window pool whose tokens no later query can reach go back."""
+        if self.bm_win is None:
+            return
+        for s in seqs:
+            if s.status != SeqStatus.FINISHED and self.bm_win.has_seq(s.seq_id):
+                self.bm_win.release_front(s.seq_id, s.num_computed - self.window)
+
     def _auto_num_blocks(self, tp: int, nl: int) -> int:
         e = self.ecfg
         per_block = KVPool.bytes_per_block(self.cfg, e.block_size, e.kv_bits, tp, nl)
@@ -164,6 +232,12 @@ class Engine:
         self.h_tokens, self.d_tokens = host(T, torch.int32), dev(T, torch.int32)
         self.h_pos, self.d_pos = host(T, torch.int32), dev(T, torch.int32)
         self.h_slots, self.d_slots = host(T, torch.int32), dev(T, torch.int32)
+        if self.bm_win is not None:      # the window pool's slots and tables travel beside the main ones
+            self.h_slots_w, self.d_slots_w = host(T, torch.int32), dev(T, torch.int32)
+            self.h_dec_tables_w, self.d_dec_tables_w = host((B, MB), torch.int32), dev((B, MB), torch.int32)
+            self.h_pf_tables_w, self.d_pf_tables_w = host((S, MB), torch.int32), dev((S, MB), torch.int32)
+            self.np_slots_w = self.h_slots_w.numpy()
+            self.np_dec_tables_w, self.np_pf_tables_w = self.h_dec_tables_w.numpy(), self.h_pf_tables_w.numpy()
         self.h_dec_tables, self.d_dec_tables = host((B, MB), torch.int32), dev((B, MB), torch.int32)
         self.h_dec_lens, self.d_dec_lens = host(B, torch.int32), dev(B, torch.int32)
         self.h_pf_tables, self.d_pf_tables = host((S, MB), torch.int32), dev((S, MB), torch.int32)
@@ -173,7 +247,8 @@ class Engine:
         self.h_out, self.d_out = host(B + S, torch.int32), dev(B + S, torch.int32)
         # second staging set + token read-back buffers for the lookahead pipeline
         self.la_host = [dict(pos=host(B, torch.int32), slots=host(B, torch.int32), lens=host(B, torch.int32),
-                             tables=host((B, MB), torch.int32), out=host(B, torch.int32)) for _ in range(2)]
+                             tables=host((B, MB), torch.int32), out=host(B, torch.int32),
+                             slots_w=host(B, torch.int32), tables_w=host((B, MB), torch.int32)) for _ in range(2)]
         self._inflight = None
         self._la_parity = 0
         self.np_dec_tables = self.h_dec_tables.numpy()
@@ -243,7 +318,7 @@ class Engine:
             # donate computed full blocks to the prefix cache, then drop our references
             toks = np.asarray(s.tokens[: s.num_computed], dtype=np.int32)
             self.bm.commit(s.seq_id, toks, s.num_computed)
-            self.bm.free_seq(s.seq_id)
+            self._kv_free(s.seq_id)
         if s in self.running:
             self.running.remove(s)
         if self.recurrent:
@@ -258,7 +333,7 @@ class Engine:
             return False
         victim = min(cands, key=lambda s: (len(s.output), -s.seq_id))
         self.running.remove(victim)
-        self.bm.free_seq(victim.seq_id)
+        self._kv_free(victim.seq_id)
         if self.recurrent:
             self.model.release_seq(victim.seq_id)
         victim.num_computed = 0
@@ -276,7 +351,7 @@ class Engine:
         i = 0
         while i < len(decode):
             s = decode[i]
-            if self.bm.reserve(s.seq_id, s.total_len):
+            if self._kv_reserve(s.seq_id, s.total_len):
                 i += 1
                 continue
             if not (e.preemption and self._preempt_one()):
@@ -326,9 +401,12 @@ class Engine:
                 need_blocks = (s.total_len + e.block_size) // e.block_size
                 if not self.bm.can_allocate(need_blocks, True) and (self.running or cands):
                     break
+                if (self.bm_win is not None and (self.running or cands)
+                        and not self.bm_win.can_allocate(min(need_blocks, self.win_blocks_prefill), False)):
+                    break
                 self.waiting.popleft()
                 if not self.bm.has_seq(s.seq_id):
-                    self.bm.create(s.seq_id, 0)
+                    self._kv_create(s.seq_id)
                     toks = np.asarray(s.tokens, dtype=np.int32)
                     hit = self.bm.match_prefix(s.seq_id, toks)
                     s.num_computed = s.num_cached = hit
@@ -344,10 +422,10 @@ class Engine:
                 piece = min(piece, budget)
                 if piece <= 0:
                     break
-                if not self.bm.reserve(s.seq_id, s.num_computed + piece):
+                if not self._kv_reserve(s.seq_id, s.num_computed + piece):
                     if s not in self.running:
                         # could not get blocks after all: back to the queue
-                        self.bm.free_seq(s.seq_id)
+                        self._kv_free(s.seq_id)
                         s.status, s.num_computed = SeqStatus.QUEUED, 0
                         self.waiting.appendleft(s)
                     elif len(self.running) == 1 and not decode_rows:
@@ -381,10 +459,14 @@ class Engine:
             tok[i] = s.output[-1] if s.output else s.prompt[-1]
             pos[i] = L - 1
             self.bm.fill_slots(s.seq_id, L - 1, 1, self.np_slots, i)
+            if self.bm_win is not None:
+                self.bm_win.fill_slots(s.seq_id, L - 1, 1, self.np_slots_w, i)
             self.h_dec_lens[i] = L
         max_len = max((s.total_len for s in decode), default=0)
         if nd:
             self.bm.fill_tables([s.seq_id for s in decode], self.np_dec_tables)
+            if self.bm_win is not None:
+                self.bm_win.fill_tables([s.seq_id for s in decode], self.np_dec_tables_w)
         t = nd
         cu = [0]
         max_q = 0
@@ -394,6 +476,8 @@ class Engine:
             tok[t:t + count] = toks[start:start + count]
             pos[t:t + count] = np.arange(start, start + count, dtype=np.int32)
             self.bm.fill_slots(s.seq_id, start, count, self.np_slots, t)
+            if self.bm_win is not None:
+                self.bm_win.fill_slots(s.seq_id, start, count, self.np_slots_w, t)
             self.h_pf_lens[j] = start + count
             t += count
             cu.append(t - nd)
@@ -404,6 +488,8 @@ class Engine:
                 rows.append(t - 1)
         if pieces:
             self.bm.fill_tables([p[0].seq_id for p in pieces], self.np_pf_tables)
+            if self.bm_win is not None:
+                self.bm_win.fill_tables([p[0].seq_id for p in pieces], self.np_pf_tables_w)
             self.h_cu[: len(cu)] = torch.tensor(cu, dtype=torch.int32)
         R = len(rows)
         self.h_rows[:R] = torch.tensor(rows, dtype=torch.int64)
@@ -420,6 +506,14 @@ class Engine:
             self.d_pf_lens[:sp].copy_(self.h_pf_lens[:sp], non_blocking=nb)
             self.d_cu[: sp + 1].copy_(self.h_cu[: sp + 1], non_blocking=nb)
         self.d_rows[:R].copy_(self.h_rows[:R], non_blocking=nb)
+        win = self.bm_win is not None
+        if win:
+            self.d_slots_w[:t].copy_(self.h_slots_w[:t], non_blocking=nb)
+            if nd:
+                self.d_dec_tables_w[:nd].copy_(self.h_dec_tables_w[:nd], non_blocking=nb)
+            if sp:
+                self.d_pf_tables_w[:sp].copy_(self.h_pf_tables_w[:sp], non_blocking=nb)
+            self.stats["h2d_bytes"] += 4 * t + (nd + sp) * self.max_blocks_per_seq * 4
         mb4 = self.max_blocks_per_seq * 4 + 4
         self.stats["h2d_bytes"] += 12 * t + nd * mb4 + sp * mb4 + (sp + 1) * 4 + R * 8
         self.stats["d2h_bytes"] += R * 4
@@ -430,7 +524,10 @@ class Engine:
                       num_prefill_seqs=sp, pf_block_tables=self.d_pf_tables[:sp] if sp else None,
                       pf_cu_q=self.d_cu[: sp + 1] if sp else None,
                       pf_context_lens=self.d_pf_lens[:sp] if sp else None, pf_max_q_len=max_q,
-                      pf_cu_q_host=cu if sp else None, logits_rows=self.d_rows[:R])
+                      pf_cu_q_host=cu if sp else None, logits_rows=self.d_rows[:R],
+                      slot_mapping_win=self.d_slots_w[:t] if win else None,
+                      dec_block_tables_win=self.d_dec_tables_w[:nd] if (win and nd) else None,
+                      pf_block_tables_win=self.d_pf_tables_w[:sp] if (win and sp) else None)
         b.logits_rows_host = rows
         b.seq_ids = [s.seq_id for s in decode] + [p[0].seq_id for p in pieces]
         b.pf_starts = [p[1] for p in pieces]
@@ -458,13 +555,18 @@ class Engine:
             self.d_slots[nd:bp].fill_(-1)
             self.d_dec_lens[nd:bp].zero_()
             self.d_dec_tables[nd:bp].zero_()
+            if self.bm_win is not None:
+                self.d_slots_w[nd:bp].fill_(-1)
+                self.d_dec_tables_w[nd:bp].zero_()
         ent = self._graphs.get(key)
         if ent is None:
             b = StepBatch(token_ids=self.d_tokens[:bp], positions=self.d_pos[:bp],
                           slot_mapping=self.d_slots[:bp], num_decode=bp,
                           dec_block_tables=self.d_dec_tables[:bp], dec_context_lens=self.d_dec_lens[:bp],
-                          dec_max_len=max_len, logits_rows=None)
-            fwd = lambda: self.model.forward(b, self.pool.layers)  # noqa: E731
+                          dec_max_len=max_len, logits_rows=None,
+                          slot_mapping_win=self.d_slots_w[:bp] if self.bm_win is not None else None,
+                          dec_block_tables_win=self.d_dec_tables_w[:bp] if self.bm_win is not None else None)
+            fwd = lambda: self.model.forward(b, self.kv_layers)  # noqa: E731
             # warm-up outside capture (sets function attributes, fills descriptor caches)
             s = torch.cuda.Stream(device=self.device)
             s.wait_stream(torch.cuda.current_stream())
@@ -527,7 +629,7 @@ class Engine:
         nd = len(seqs)
         extra = 1 if from_device else 0
         for s in seqs:
-            if not self.bm.reserve(s.seq_id, s.total_len + extra):
+            if not self._kv_reserve(s.seq_id, s.total_len + extra):
                 return None
         par = self._la_parity
         self._la_parity ^= 1
@@ -539,8 +641,14 @@ class Engine:
             pos[i] = L - 1
             lens[i] = L
             self.bm.fill_slots(s.seq_id, L - 1, 1, slots, i)
+            if self.bm_win is not None:
+                self.bm_win.fill_slots(s.seq_id, L - 1, 1, hb["slots_w"].numpy(), i)
             max_len = max(max_len, L)
         self.bm.fill_tables([s.seq_id for s in seqs], hb["tables"].numpy())
+        if self.bm_win is not None:
+            self.bm_win.fill_tables([s.seq_id for s in seqs], hb["tables_w"].numpy())
+            self.d_slots_w[:nd].copy_(hb["slots_w"][:nd], non_blocking=True)
+            self.d_dec_tables_w[:nd].copy_(hb["tables_w"][:nd], non_blocking=True)
         if not from_device:
             tok = self.h_tokens.numpy()
             for i, s in enumerate(seqs):
@@ -582,6 +690,7 @@ class Engine:
             if reason is not None:
                 self._finish(s, reason)
                 finished.append(s)
+        self._release_window(inf["seqs"])
         return finished
 
     # ------------------------------------------------------------------ step
@@ -649,15 +758,15 @@ class Engine:
             if self.drafter is not None and getattr(self.drafter, "needs_hidden", False):
                 if self.pipeline:
                     # the residual stream exists on the last stage only, and so does the drafter
-                    h = self.model.pipeline_hidden(b, self.pool.layers)
+                    h = self.model.pipeline_hidden(b, self.kv_layers)
                     logits = self.model.logits(h, b.logits_rows) if h is not None else None
                 else:
-                    h = self.model.forward_hidden(b, self.pool.layers)
+                    h = self.model.forward_hidden(b, self.kv_layers)
                     logits = self.model.logits(h, b.logits_rows)
                 if h is not None:
                     self.drafter.on_forward(self, decode, pieces, h)
             else:
-                logits = self.model.forward(b, self.pool.layers)
+                logits = self.model.forward(b, self.kv_layers)
         # rows: decode rows first, then prefill rows that completed their prompt
         sample_seqs = list(decode) + [s for (s, start, cnt) in pieces if start + cnt >= s.total_len]
         if self.pipeline:
@@ -672,6 +781,7 @@ class Engine:
             s.num_computed += cnt
         for s in decode:
             s.num_computed = s.total_len
+        self._release_window([p[0] for p in pieces] + list(decode))
         now = time.perf_counter()
         for i, s in enumerate(sample_seqs):
             tok = self._thinking_override(s, int(toks[i]))
@@ -758,20 +868,20 @@ class Engine:
         for s, d in zip(decode, props):
             room = min(s.params.max_tokens - len(s.output) - 1, self.ecfg.max_model_len - s.total_len - 1)
             d = list(d[: max(0, room)])
-            if not self.bm.reserve(s.seq_id, s.total_len + len(d)):
+            if not self._kv_reserve(s.seq_id, s.total_len + len(d)):
                 d = []
             drafts[s.seq_id] = d
             pieces.append((s, s.total_len - 1, 1 + len(d)))
         b, R = self._build_batch([], pieces, drafts=drafts, all_rows=True)
         need_h = getattr(self.drafter, "needs_hidden", False)
         if self.pipeline:
-            h = self.model.pipeline_hidden(b, self.pool.layers)
+            h = self.model.pipeline_hidden(b, self.kv_layers)
             logits = self.model.logits(h, b.logits_rows) if h is not None else None
             # argmax of every verify row on the last stage, shared with the other stages (R ints)
             target = self.model.share_ints(ops.argmax(logits).cpu().tolist() if logits is not None else None, (R,))
             walk = None
         else:
-            h = self.model.forward_hidden(b, self.pool.layers)
+            h = self.model.forward_hidden(b, self.kv_layers)
             logits = self.model.logits(h, b.logits_rows)
         walk = None
         if self.pipeline:
@@ -826,7 +936,7 @@ class Engine:
             s.num_computed = L + kept
             accepted_info.append((s, row0, kept))
             if s.status != SeqStatus.FINISHED:
-                self.bm.truncate(s.seq_id, L + kept)
+                self._kv_truncate(s.seq_id, L + kept)
                 if reason is not None:
                     self._finish(s, reason)
                     finished.append(s)
@@ -834,6 +944,7 @@ class Engine:
                 finished.append(s)
             row0 += cnt
         self.stats["decode_tokens"] += sum(k + 1 for _, _, k in accepted_info)
+        self._release_window(decode)
         if need_h and h is not None:
             self.drafter.on_verify(self, accepted_info, h)
         for s in finished:

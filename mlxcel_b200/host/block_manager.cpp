@@ -67,6 +67,7 @@ struct Sequence {
   int num_hashed = 0;       // leading full blocks already registered
   Hash128 last_hash;        // hash of block num_hashed - 1
   uint64_t salt = 0;
+  int front_released = 0;   // leading table entries given back by release_front (stored as -1)
 };
 
 class BlockManager {
@@ -210,19 +211,42 @@ class BlockManager {
     if (new_len >= s.num_tokens) return;
     const int keep = (new_len + block_size_ - 1) / block_size_;
     while (static_cast<int>(s.blocks.size()) > keep) {
-      release(s.blocks.back());
+      if (s.blocks.back() >= 0) release(s.blocks.back());
       s.blocks.pop_back();
     }
+    s.front_released = std::min<int>(s.front_released, static_cast<int>(s.blocks.size()));
     s.num_tokens = new_len;
     const int full = new_len / block_size_;
     if (s.num_hashed > full) truncate_hash(s, full);
+  }
+
+  // Sliding-window pools: give back every block whose tokens all lie before `first_needed_token`
+  // (they can never be attended again). The entries stay in the table as -1 so that positions keep
+  // indexing it; fill_tables writes block 0 there (the kernels mask those positions). Returns the
+  // number of blocks released. Not meant for pools with a prefix index (released blocks of a
+  // shared prefix would break the chain); such pools never call it.
+  int release_front(int64_t id, int first_needed_token) {
+    Sequence& s = get(id);
+    const int upto = std::min<int>(std::max(0, first_needed_token) / block_size_, static_cast<int>(s.blocks.size()));
+    int n = 0;
+    for (int b = s.front_released; b < upto; ++b) {
+      if (s.blocks[b] >= 0) {
+        release(s.blocks[b]);
+        s.blocks[b] = -1;
+        ++n;
+      }
+    }
+    s.front_released = std::max(s.front_released, upto);
+    front_released_ += n;
+    return n;
   }
 
   void free_seq(int64_t id) {
     auto it = seqs_.find(id);
     if (it == seqs_.end()) return;
     // Release from the tail so that leaf blocks are evicted before their parents.
-    for (auto b = it->second.blocks.rbegin(); b != it->second.blocks.rend(); ++b) release(*b);
+    for (auto b = it->second.blocks.rbegin(); b != it->second.blocks.rend(); ++b)
+      if (*b >= 0) release(*b);
     seqs_.erase(it);
   }
 
@@ -248,6 +272,7 @@ class BlockManager {
       if (n > width) throw std::invalid_argument("table too narrow");
       int32_t* row = &buf(i, 0);
       std::memcpy(row, s.blocks.data(), sizeof(int32_t) * n);
+      for (int b = 0; b < s.front_released && b < n; ++b) row[b] = 0;   // released by a sliding window
       if (n < width) std::memset(row + n, 0, sizeof(int32_t) * (width - n));
     }
   }
@@ -262,6 +287,7 @@ class BlockManager {
       const int pos = start + i;
       const int bi = pos / block_size_;
       if (bi >= static_cast<int>(s.blocks.size())) throw std::out_of_range("slot beyond reservation");
+      if (s.blocks[bi] < 0) throw std::out_of_range("slot in a block released by the sliding window");
       buf(out_offset + i) = s.blocks[bi] * block_size_ + pos % block_size_;
     }
   }
@@ -274,6 +300,7 @@ class BlockManager {
     d["cached"] = static_cast<int>(lru_.size());
     d["registered"] = static_cast<int>(index_.size());
     d["sequences"] = static_cast<int>(seqs_.size());
+    d["front_released"] = front_released_;
     d["prefix_hits"] = hits_;
     d["prefix_queries"] = queries_;
     d["evictions"] = evictions_;
@@ -360,7 +387,7 @@ class BlockManager {
   std::list<int> lru_;
   std::unordered_map<Hash128, int, Hash128Hasher> index_;
   std::unordered_map<int64_t, Sequence> seqs_;
-  long long hits_ = 0, queries_ = 0, evictions_ = 0, cow_copies_ = 0;
+  long long hits_ = 0, queries_ = 0, evictions_ = 0, cow_copies_ = 0, front_released_ = 0;
 };
 
 }  // namespace
@@ -390,6 +417,7 @@ PYBIND11_MODULE(_mlxcel_host, m) {
       .def("fork", &BlockManager::fork)
       .def("truncate", &BlockManager::truncate)
       .def("free_seq", &BlockManager::free_seq)
+      .def("release_front", &BlockManager::release_front)
       .def("reset_prefix_cache", &BlockManager::reset_prefix_cache)
       .def("fill_tables", &BlockManager::fill_tables)
       .def("fill_slots", &BlockManager::fill_slots)

@@ -81,15 +81,7 @@ class TensorSource:
         if alias is not None:
             t = self._get_raw(alias[0])
             return alias[1](t) if alias[1] is not None else t
-        f = self.index[name]
-        h = self._handles.get(f)
-        if h is None:
-            real = (self.dir / f).resolve()
-            if not str(real).startswith(str(self.dir.resolve())) and not real.exists():
-                raise FileNotFoundError(f)
-            h = self._open(str(self.dir / f), framework="pt")
-            self._handles[f] = h
-        return h.get_tensor(name)
+        return self._handle(name).get_tensor(name)
 
     def footprint(self) -> int:
         """Bytes of all tensors (header-only would need the raw header; sizes via slices)."""
@@ -103,11 +95,22 @@ class TensorSource:
                           "F8_E4M3": 1, "I64": 8}.get(sl.get_dtype(), 2)
         return total
 
+    def _shard_path(self, f: str) -> Path:
+        """A shard named by the index must be a file inside the checkpoint directory: an entry such
+        as ``../../x.safetensors`` (or a symlink leading elsewhere) is refused, whether or not the
+        target exists."""
+        root = self.dir.resolve()
+        real = (self.dir / f).resolve()
+        if not real.is_relative_to(root):
+            raise ValueError(f"weight_map entry {f!r} points outside the checkpoint directory")
+        if not real.is_file():
+            raise FileNotFoundError(str(self.dir / f))
+        return real
+
     def _handle(self, name):
-        self.get  # noqa: B018 - ensure attribute exists
         f = self.index[name]
         if f not in self._handles:
-            self._handles[f] = self._open(str(self.dir / f), framework="pt")
+            self._handles[f] = self._open(str(self._shard_path(f)), framework="pt")
         return self._handles[f]
 
 

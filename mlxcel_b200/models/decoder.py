@@ -50,6 +50,11 @@ class StepBatch:
     embeds: torch.Tensor | None = None             # optional [T, H] input embeddings (VLM / MTP)
     seq_ids: list | None = None                    # host: sequence id per decode row, then per prefill piece
     pf_starts: list | None = None                  # host: first position of every prefill piece
+    # Sliding-window layers with their own block pool (blocks behind the window are given back):
+    # slots and block tables of that pool. None = every layer uses the tables above.
+    slot_mapping_win: torch.Tensor | None = None
+    dec_block_tables_win: torch.Tensor | None = None
+    pf_block_tables_win: torch.Tensor | None = None
 
     @property
     def num_tokens(self) -> int:
@@ -212,13 +217,16 @@ class DecoderModel:
             qkv = torch.cat([qn.to(qkv.dtype), kn.to(qkv.dtype), x3[:, nqk:]], dim=1).reshape(T0, -1).contiguous()
             q_norm = k_norm = None
             rot_dim = 0
-        ops.rope_append(qkv, b.positions, b.slot_mapping, self.inv_freq_local if local else self.inv_freq, kv,
+        use_win = window > 0 and b.slot_mapping_win is not None     # this layer's KV lives in the window pool
+        ops.rope_append(qkv, b.positions, b.slot_mapping_win if use_win else b.slot_mapping,
+                        self.inv_freq_local if local else self.inv_freq, kv,
                         Hq=self.Hq, Hkv=self.Hkv, D=self.D, rot_dim=rot_dim,
                         traditional=cfg.rope_traditional, mscale=1.0 if local else self.mscale,
                         q_norm_w=q_norm, k_norm_w=k_norm, norm_eps=cfg.rms_norm_eps)
-        return self._attend(qkv, b, kv, window, lw.sinks)
+        return self._attend(qkv, b, kv, window, lw.sinks, use_win)
 
-    def _attend(self, qkv: torch.Tensor, b: StepBatch, kv: KVLayer, window: int, sinks) -> torch.Tensor:
+    def _attend(self, qkv: torch.Tensor, b: StepBatch, kv: KVLayer, window: int, sinks,
+                use_win: bool = False) -> torch.Tensor:
         """Paged attention of the step's rows (decode rows first, then the prefill pieces) over the
         keys / values just appended; ``qkv`` carries the (rotated) queries in its first Hq * D columns."""
         cfg = self.cfg
@@ -228,14 +236,16 @@ class DecoderModel:
         nd = b.num_decode
         common = dict(Hq=self.Hq, Hkv=self.Hkv, D=self.D, scale=cfg.attn_scale, window=window,
                       sinks=sinks, softcap=cfg.attn_logit_softcap)
+        dec_tables = b.dec_block_tables_win if use_win else b.dec_block_tables
+        pf_tables = b.pf_block_tables_win if use_win else b.pf_block_tables
         if nd > 0:
-            o = ops.paged_decode(q[:nd], kv, b.dec_block_tables, b.dec_context_lens,
+            o = ops.paged_decode(q[:nd], kv, dec_tables, b.dec_context_lens,
                                  max_len=b.dec_max_len, out=attn[:nd] if attn.is_cuda else None,
                                  **common)
             if not attn.is_cuda:
                 attn[:nd] = o
         if b.num_prefill_seqs > 0:
-            o = ops.paged_prefill(q[nd:], kv, b.pf_block_tables, b.pf_cu_q, b.pf_context_lens,
+            o = ops.paged_prefill(q[nd:], kv, pf_tables, b.pf_cu_q, b.pf_context_lens,
                                   max_q_len=b.pf_max_q_len, out=attn[nd:] if attn.is_cuda else None,
                                   **common)
             if not attn.is_cuda:

@@ -170,6 +170,26 @@ def quantize_kv8(x: torch.Tensor):
     return q.reshape(x.shape), meta
 
 
+def quantize_kv4(x: torch.Tensor):
+    """[..., D] float → (uint8 [..., D/2] with two 4-bit codes per byte, even element in the low
+    nibble; meta bf16 [..., D/64, 2]) affine per group of 64 with 16 levels."""
+    D = x.shape[-1]
+    g = x.float().reshape(*x.shape[:-1], D // 64, 64)
+    mn, mx = g.amin(-1, keepdim=True), g.amax(-1, keepdim=True)
+    scale = ((mx - mn) / 15.0).to(torch.bfloat16).float()
+    bias = mn.to(torch.bfloat16).float()
+    scale = torch.where(scale == 0, torch.ones_like(scale), scale)
+    q = torch.round((g - bias) / scale).clamp(0, 15).to(torch.uint8).reshape(*x.shape[:-1], D // 2, 2)
+    packed = q[..., 0] | (q[..., 1] << 4)
+    meta = torch.cat([scale, bias], dim=-1).to(torch.bfloat16)
+    return packed, meta
+
+
+def dequantize_kv4(packed: torch.Tensor, meta: torch.Tensor) -> torch.Tensor:
+    q = torch.stack([packed & 0xF, packed >> 4], dim=-1).reshape(*packed.shape[:-1], packed.shape[-1] * 2)
+    return dequantize_kv8(q, meta)
+
+
 def dequantize_kv8(q: torch.Tensor, meta: torch.Tensor) -> torch.Tensor:
     D = q.shape[-1]
     g = q.float().reshape(*q.shape[:-1], D // 64, 64)
@@ -198,8 +218,9 @@ def rope_append(qkv, positions, slot_mapping, inv_freq, kv, *, Hq, Hkv, D, rot_d
         kv.k[blk, :, off] = kw.to(kv.k.dtype)
         kv.v[blk, :, off] = vw.to(kv.v.dtype)
     else:
-        kq, km = quantize_kv8(kw)
-        vq, vm = quantize_kv8(vw)
+        qz = quantize_kv4 if kv.kv_bits == 4 else quantize_kv8
+        kq, km = qz(kw)
+        vq, vm = qz(vw)
         kv.k[blk, :, off] = kq
         kv.v[blk, :, off] = vq
         kv.k_meta[blk, :, off] = km
@@ -214,8 +235,9 @@ def _gather_kv(kv, table: torch.Tensor, n: int):
         k = kv.k[idx].float()
         v = kv.v[idx].float()
     else:
-        k = dequantize_kv8(kv.k[idx], kv.k_meta[idx])
-        v = dequantize_kv8(kv.v[idx], kv.v_meta[idx])
+        dq = dequantize_kv4 if kv.kv_bits == 4 else dequantize_kv8
+        k = dq(kv.k[idx], kv.k_meta[idx])
+        v = dq(kv.v[idx], kv.v_meta[idx])
     # [nb, Hkv, bs, D] -> [Hkv, nb*bs, D]
     k = k.permute(1, 0, 2, 3).reshape(k.shape[1], -1, k.shape[-1])[:, :n]
     v = v.permute(1, 0, 2, 3).reshape(v.shape[1], -1, v.shape[-1])[:, :n]

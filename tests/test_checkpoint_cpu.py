@@ -168,3 +168,32 @@ def test_internlm2_and_baichuan_layouts_load_like_their_llama_form(tmp_path):
         (d2 / "config.json").write_text(json.dumps(raw | {"model_type": "baichuan"}))
         got2 = load_full_weights(d2, ModelConfig.from_path(d2), dtype=torch.bfloat16)
         assert all(torch.equal(a.wqkv, b.wqkv) for a, b in zip(got2.layers, ref.layers))
+
+
+def test_index_entries_outside_the_checkpoint_directory_are_refused(tmp_path):
+    """A weight_map entry may not lead out of the model directory: neither by ``..`` nor into a
+    sibling directory whose name merely starts with the model's."""
+    import json
+
+    import pytest
+    import torch
+    from safetensors.torch import save_file
+
+    from mlxcel_b200.loading.checkpoint import TensorSource
+
+    model = tmp_path / "foo"
+    evil = tmp_path / "foo-evil"
+    model.mkdir()
+    evil.mkdir()
+    save_file({"a": torch.ones(2)}, str(model / "ok.safetensors"))
+    save_file({"b": torch.ones(2)}, str(evil / "x.safetensors"))
+    (model / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": {"a": "ok.safetensors", "b": "../foo-evil/x.safetensors", "c": "missing.safetensors"}}))
+    src = TensorSource(model)
+    assert src.get("a").sum().item() == 2
+    with pytest.raises(ValueError, match="outside"):
+        src.get("b")
+    with pytest.raises(ValueError, match="outside"):
+        src.footprint()
+    with pytest.raises(FileNotFoundError):
+        src.get("c")

@@ -95,3 +95,38 @@ def test_speculative_rounds_alternate_with_admission():
     got = [eng.seqs[i].output for i in ids]
     assert got == want and eng.stats["spec_rounds"] > 0
     assert all(eng.seqs[i].draft_n >= eng.seqs[i].draft_n_accepted > 0 for i in ids)
+
+
+def test_sliding_window_layers_release_blocks_behind_the_window():
+    """gpt-oss style alternating layers: the windowed layers live in their own pool and give back
+    every block that fell out of the window; tokens are identical to keeping everything."""
+    cfg = preset("tiny-gpt-oss")            # sliding_window 32 on every other layer, sinks, MoE
+    w = random_weights(cfg, seed=5, dtype=torch.float32, std=0.05)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (150, 47, 90)]
+    sp = SamplingParams(max_tokens=40, ignore_eos=True)
+
+    def run(release):
+        eng = Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=4, max_num_batched_tokens=128, num_blocks=96,
+                                                             max_model_len=384, cuda_graphs=False, prefill_chunk_alone=64,
+                                                             prefill_chunk_contended=32, window_release=release))
+        peak = [0]
+        ids = [eng.add_request(p, sp) for p in prompts]
+        while eng.has_work():
+            eng.step()
+            if eng.bm_win is not None:
+                st = eng.bm_win.stats()
+                peak[0] = max(peak[0], st["num_blocks"] - st["free"])
+        return [eng.seqs[i].output for i in ids], eng, peak[0]
+
+    keep, eng0, _ = run(False)
+    rel, eng1, peak = run(True)
+    assert eng0.bm_win is None and eng1.bm_win is not None
+    assert rel == keep
+    st = eng1.bm_win.stats()
+    assert st["front_released"] > 0 and st["free"] == st["num_blocks"]        # everything returned at the end
+    # the three sequences end at 190 / 87 / 130 tokens = 27 blocks of 16; the window pool never held
+    # more than window + chunk per prefilling row plus the window per decoding row
+    assert peak <= 3 * ((32 + 64) // 16 + 3) and peak < 27, peak
+    assert eng1.pool_win.num_blocks <= eng1.pool.num_blocks
+    assert len(eng1.pool.layers) + len(eng1.pool_win.layers) == cfg.num_hidden_layers

@@ -168,7 +168,10 @@ def test_llama_server_flag_spellings_map_onto_native_options(capsys):
     assert b.draft_model == "native" and b.kv_bits == 16          # the native spelling wins
     import pytest
     with pytest.raises(SystemExit):
-        cli._apply_compat(ap.parse_args(["-m", "x", "-ctk", "q4_0"]))
+        cli._apply_compat(ap.parse_args(["-m", "x", "-ctk", "q5_1"]))
+    c4 = ap.parse_args(["-m", "x", "-ctk", "q4_0"])
+    cli._apply_compat(c4)
+    assert c4.kv_bits == 4
 
 
 def test_rope_and_kv_overrides_change_the_built_config(tmp_path):
