@@ -212,6 +212,11 @@ def load_llm(a):
         llm = LLM.from_pretrained(a.model, device=dev, engine_config=ecfg, comm=comm, dequantize=a.dequantize,
                                   surgery=getattr(a, "surgery", None), config_overrides=config_overrides(a))
     attach_drafter(llm, a, dev)
+    if llm.engine.drafter is not None:
+        from .speculative import SpecPolicy
+        eng = llm.engine
+        key = f"{a.model}|{type(eng.drafter).__name__}|K{eng.spec_k}|{dev}"
+        eng.spec_policy = SpecPolicy(key=key)
     return llm
 
 

@@ -152,6 +152,7 @@ class Engine:
         self.drafter = None          # speculative drafter (see mlxcel_b200.speculative)
         self.spec_k = 4              # block size K: K-1 draft tokens + 1 bonus token per round
         self._last_spec = self._spec_now = False
+        self.spec_policy = None      # optional speculative.policy.SpecPolicy (adaptive on / off)
         self._evicted: list[Sequence] = []   # rows the scheduler had to end (pool exhausted), reported by step()
         self._alloc_buffers()
         self.stats = dict(steps=0, decode_steps=0, prefill_tokens=0, decode_tokens=0, preemptions=0,
@@ -323,6 +324,8 @@ class Engine:
             self.running.remove(s)
         if self.recurrent:
             self.model.release_seq(s.seq_id)
+        if self.spec_policy is not None and reason != FinishReason.CANCELLED:
+            self.spec_policy.on_request_finished()
 
     def _preempt_one(self) -> bool:
         """Reclaim blocks by recompute-preempting the least progressed running row
@@ -372,7 +375,8 @@ class Engine:
         # A verify round alternates with classic work (admission, a parked prefill): the tick policy
         # never grants two rounds in a row while classic work waits (tick_policy.rs:284-356).
         st.speculative_ready = (self.drafter is not None and bool(decode)
-                                and all(self._spec_row_ok(s) for s in decode))
+                                and all(self._spec_row_ok(s) for s in decode)
+                                and (self.spec_policy is None or self.spec_policy.allow()))
         st.last_was_speculative = self._last_spec
         if self.waiting:
             nxt = self.waiting[0]
@@ -746,6 +750,7 @@ class Engine:
         if self._spec_now:
             self._spec_now = False
             return self._spec_step(decode)
+        t_step = time.perf_counter()
         b, R = self._build_batch(decode, pieces)
         nd = len(decode)
         logits = None
@@ -776,6 +781,8 @@ class Engine:
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += nd
         self.stats["prefill_tokens"] += sum(p[2] for p in pieces)
+        if self.spec_policy is not None and self.drafter is not None and nd and not pieces:
+            self.spec_policy.record_classic((time.perf_counter() - t_step) * 1e3, nd)
         finished: list[Sequence] = []
         for s, _, cnt in pieces:
             s.num_computed += cnt
@@ -858,6 +865,7 @@ class Engine:
         ``[pending, d0 .. d(K-2)]``, accept drafts while they equal the target argmax, emit the
         accepted drafts plus the target token at the first mismatch, roll the KV back."""
         K = self.spec_k
+        t_round = time.perf_counter()
         props = self.drafter.propose(self, decode, K - 1)
         if self.pipeline:
             # proposals come from the stage that holds the drafter; every scheduler needs them
@@ -945,6 +953,8 @@ class Engine:
             row0 += cnt
         self.stats["decode_tokens"] += sum(k + 1 for _, _, k in accepted_info)
         self._release_window(decode)
+        if self.spec_policy is not None:
+            self.spec_policy.record_spec((time.perf_counter() - t_round) * 1e3, sum(k + 1 for _, _, k in accepted_info))
         if need_h and h is not None:
             self.drafter.on_verify(self, accepted_info, h)
         for s in finished:

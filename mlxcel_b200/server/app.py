@@ -343,11 +343,26 @@ def create_app(state: ServerState) -> FastAPI:
         eng = state.worker.engine
         dr = getattr(eng, "drafter", None)
         st = eng.stats
+        pol = getattr(eng, "spec_policy", None)
         return {"drafter": type(dr).__name__ if dr is not None else None,
-                "max_draft": getattr(eng.ecfg, "spec_max_draft", 0),
+                "max_draft": max(0, eng.spec_k - 1) if dr is not None else 0,
                 "rounds": st.get("spec_rounds", 0), "drafted": st.get("spec_drafted", 0),
                 "accepted": st.get("spec_accepted", 0),
-                "acceptance": (st.get("spec_accepted", 0) / st["spec_drafted"]) if st.get("spec_drafted") else None}
+                "acceptance": (st.get("spec_accepted", 0) / st["spec_drafted"]) if st.get("spec_drafted") else None,
+                "policy": pol.snapshot() if pol is not None else None}
+
+    @app.post("/v1/internal/mtp-policy")
+    async def mtp_policy_set(body: dict):
+        """``{"mode": "on" | "off" | "auto" | "reset"}``: pin speculation on or off, start a new profile, or
+        also forget the persisted verdict (reference docs/mtp-policy-api.md)."""
+        pol = getattr(state.worker.engine, "spec_policy", None)
+        if pol is None:
+            return _err(400, "no speculative drafter is attached to this server")
+        try:
+            state.worker.run_exclusive(lambda: pol.force(str(body.get("mode", ""))))
+        except ValueError as e:
+            return _err(400, str(e))
+        return await mtp_policy()
 
     @app.post("/v1/rerank")
     @app.post("/v1/reranking")

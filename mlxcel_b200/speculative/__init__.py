@@ -7,6 +7,7 @@ one target forward and keeps the longest prefix that equals the target's greedy 
 from .prompt_lookup import PromptLookupDrafter  # noqa: F401
 from .draft_model import DraftModelDrafter  # noqa: F401
 from .mtp import MTPDrafter, MTPWeights, random_mtp_weights  # noqa: F401
+from .policy import SpecPolicy, exactness_probe  # noqa: F401
 
 
 class Drafter:

@@ -130,3 +130,57 @@ def test_sliding_window_layers_release_blocks_behind_the_window():
     assert peak <= 3 * ((32 + 64) // 16 + 3) and peak < 27, peak
     assert eng1.pool_win.num_blocks <= eng1.pool.num_blocks
     assert len(eng1.pool.layers) + len(eng1.pool_win.layers) == cfg.num_hidden_layers
+
+
+def test_adaptive_speculation_policy_profiles_then_decides(tmp_path):
+    from mlxcel_b200.speculative import SpecPolicy
+    t = [0.0]
+    pol = SpecPolicy(key="m|d|K4|cpu", profile_requests=2, classic_probes=2, cache_dir=str(tmp_path), clock=lambda: t[0])
+    assert pol.state.mode == "profiling" and pol.allow()
+    for _ in range(4):
+        pol.record_spec(10.0, 12)            # 1.2 tok/ms
+    assert not pol.allow()                   # a classic probe step is due after 4 rounds
+    pol.record_classic(10.0, 8)              # 0.8 tok/ms
+    assert pol.allow()
+    pol.on_request_finished()
+    assert pol.state.mode == "profiling"
+    pol.on_request_finished()
+    assert pol.state.mode == "enabled" and "tok/ms" in pol.state.verdict_reason
+    # the verdict is persisted per key and picked up by the next process
+    again = SpecPolicy(key="m|d|K4|cpu", cache_dir=str(tmp_path))
+    assert again.state.mode == "enabled" and "persisted" in again.state.verdict_reason
+    other = SpecPolicy(key="other", cache_dir=str(tmp_path))
+    assert other.state.mode == "profiling"
+    # a drafter that does not pay is switched off; forcing and resetting work
+    slow = SpecPolicy(key="slow", profile_requests=1, cache_dir=str(tmp_path))
+    slow.record_spec(10.0, 4)
+    slow.record_classic(10.0, 8)
+    slow.on_request_finished()
+    assert slow.state.mode == "disabled" and not slow.allow()
+    slow.force("on")
+    assert slow.allow()
+    slow.force("reset")
+    assert slow.state.mode == "profiling" and not slow.path.exists()
+    with pytest.raises(ValueError):
+        slow.force("sideways")
+
+
+def test_exactness_probe_and_policy_on_the_engine(tmp_path):
+    """Block verification equals chain decoding on the fp32 CPU path, so the probe passes; with the
+    policy attached the engine profiles, decides, and greedy output stays the same."""
+    from mlxcel_b200.speculative import SpecPolicy, exactness_probe
+    cfg, w, eng = _engine()
+    assert exactness_probe(eng, _prompt(cfg, 10), k=4, tokens=10) is True
+    assert eng.drafter is None and not eng.has_work()
+    prompts = [_prompt(cfg, n, seed=n) for n in (9, 14, 11)]
+    sp = SamplingParams(max_tokens=40, ignore_eos=True)
+    want = [s.output for s in eng.generate(prompts, sp)]
+    cfg, w, eng = _engine()
+    eng.drafter = DraftModelDrafter(DecoderModel(cfg, w), cfg, num_blocks=96, max_model_len=384)
+    eng.spec_policy = SpecPolicy(key="t", profile_requests=2, classic_probes=1, cache_dir=str(tmp_path))
+    got = [s.output for s in eng.generate(prompts, sp)]
+    assert got == want
+    st = eng.spec_policy.state
+    assert st.spec_rounds > 0 and st.classic_steps >= 1 and st.mode in ("enabled", "disabled")
+    eng.spec_policy.state.exact = False           # a failed probe keeps speculation off
+    assert not eng.spec_policy.allow()
