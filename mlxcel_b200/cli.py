@@ -836,6 +836,68 @@ def cmd_router(a):
     uvicorn.run(app, host=a.host, port=a.port, log_level="info" if a.verbose else "warning")
 
 
+def cmd_front(a):
+    """One listener in front of several servers (server/front.py): given URLs, or ``--dp N`` replicas
+    that this process starts itself, one per GPU, and stops again when it exits."""
+    import signal
+    import subprocess
+    import urllib.request
+
+    import uvicorn
+
+    from .server.front import create_front_app
+    replicas, children = list(a.replica_url or []), []
+    if a.dp:
+        rest = [x for x in (a.serve_args or []) if x != "--"]
+        if not rest:
+            raise SystemExit("front --dp N needs the serve arguments after '--' (at least -m MODEL)")
+        for i in range(a.dp):
+            port = a.base_port + i
+            env = dict(os.environ)
+            if not a.no_pin_gpus:
+                env["CUDA_VISIBLE_DEVICES"] = str(a.first_gpu + i)
+            children.append(subprocess.Popen([sys.executable, "-m", "mlxcel_b200.cli", "serve", *rest,
+                                              "--host", "127.0.0.1", "--port", str(port)], env=env))
+            replicas.append(f"http://127.0.0.1:{port}")
+
+    def stop_children(*_):
+        for c in children:
+            if c.poll() is None:
+                c.terminate()
+        for c in children:
+            try:
+                c.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                c.kill()
+
+    try:
+        if children:        # wait until every replica answers /health (loading a large checkpoint takes minutes)
+            deadline = time.monotonic() + a.start_timeout
+            pending = list(zip(children, replicas[-len(children):]))
+            while pending and time.monotonic() < deadline:
+                for c, u in list(pending):
+                    if c.poll() is not None:
+                        raise SystemExit(f"replica {u} exited with code {c.returncode} while starting")
+                    try:
+                        with urllib.request.urlopen(u + "/health", timeout=2) as r:
+                            if r.status == 200:
+                                pending.remove((c, u))
+                    except OSError:
+                        pass
+                if pending:
+                    time.sleep(0.5)
+            if pending:
+                raise SystemExit(f"replicas not ready after {a.start_timeout} s: {[u for _, u in pending]}")
+
+            def on_term(*_):
+                raise SystemExit(0)
+            signal.signal(signal.SIGTERM, on_term)
+        app = create_front_app(replicas=replicas, prefill=a.prefill_url, decode=a.decode_url, cooldown_s=a.cooldown)
+        uvicorn.run(app, host=a.host, port=a.port, log_level="info" if a.verbose else "warning")
+    finally:
+        stop_children()
+
+
 def cmd_inspect(a):
     from .config import ModelConfig, preset
     from .utils.memory import estimate_memory
@@ -984,6 +1046,21 @@ def main(argv=None):
     p.add_argument("--api-key", action="append")
     p.add_argument("-v", "--verbose", action="store_true")
     p.set_defaults(fn=cmd_router)
+    p = sub.add_parser("front", help="one listener in front of data-parallel replicas or prefill/decode servers")
+    p.add_argument("--replica-url", action="append", default=None, metavar="URL", help="a running server of the model (repeatable)")
+    p.add_argument("--prefill-url", action="append", default=None, metavar="URL", help="prefill-role server (disaggregated serving)")
+    p.add_argument("--decode-url", action="append", default=None, metavar="URL", help="decode-role server (disaggregated serving)")
+    p.add_argument("--dp", type=int, default=0, help="start this many replicas here, one per GPU; serve arguments follow '--'")
+    p.add_argument("--first-gpu", type=int, default=0)
+    p.add_argument("--no-pin-gpus", action="store_true", help="do not set CUDA_VISIBLE_DEVICES for the replicas (CPU replicas)")
+    p.add_argument("--base-port", type=int, default=18080, help="replica i listens on 127.0.0.1:(base+i)")
+    p.add_argument("--start-timeout", type=float, default=1800.0)
+    p.add_argument("--cooldown", type=float, default=5.0, help="seconds a failed backend stays out of the rotation")
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=8080)
+    p.add_argument("-v", "--verbose", action="store_true")
+    p.add_argument("serve_args", nargs=argparse.REMAINDER)
+    p.set_defaults(fn=cmd_front)
     p = sub.add_parser("embed", help="embed texts and print the vectors")
     _add_model_args(p)
     p.add_argument("-p", "--prompt", action="append")
