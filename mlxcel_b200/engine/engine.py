@@ -376,6 +376,7 @@ class Engine:
         # never grants two rounds in a row while classic work waits (tick_policy.rs:284-356).
         st.speculative_ready = (self.drafter is not None and bool(decode)
                                 and all(self._spec_row_ok(s) for s in decode)
+                                and (not self.pipeline or all(s.params.greedy for s in decode))
                                 and (self.spec_policy is None or self.spec_policy.allow()))
         st.last_was_speculative = self._last_spec
         if self.waiting:
@@ -853,10 +854,15 @@ class Engine:
     # ------------------------------------------------------------------ speculative decoding
     @staticmethod
     def _spec_row_ok(s: Sequence) -> bool:
-        """Greedy acceptance (draft == argmax of the target) is exact only for rows that decode
-        greedily without per-step logit edits."""
+        """Rows a verify round is exact for. Greedy rows: a draft is accepted when it equals the
+        target's argmax. Sampled rows whose chain the fused sampler expresses (temperature, top-k,
+        top-p, min-p, typical-p, top-n-sigma): *sampler-match* acceptance — every verify position
+        is drawn with the row's own seed and step counter, and a draft is accepted when it equals
+        that draw, so the emitted tokens are exactly the ones classic decoding would have drawn
+        (docs/speculative-acceptance.md:18-35). Rows with per-step logit edits (penalties over the
+        history, masks, bias) or per-step state (mirostat) are not eligible."""
         p = s.params
-        return (p.greedy and s.mask_fn is None and not p.needs_history and not p.logit_bias
+        return ((p.greedy or p.fused_eligible) and s.mask_fn is None and not p.needs_history and not p.logit_bias
                 and not p.logprobs and p.thinking_cap is None)
 
     def _spec_step(self, decode: list[Sequence]) -> list[Sequence]:
@@ -892,8 +898,17 @@ class Engine:
             h = self.model.forward_hidden(b, self.kv_layers)
             logits = self.model.logits(h, b.logits_rows)
         walk = None
+        all_greedy = all(s.params.greedy for s in decode)
         if self.pipeline:
             pass
+        elif not all_greedy:
+            # sampler-match: one draw per verify row with the owner's seed and the step it stands for
+            owners, offs = [], []
+            for s, _, cnt in pieces:
+                owners += [s] * cnt
+                offs += list(range(cnt))
+            target, _ = self.sampler.sample(logits, owners, step_offsets=offs)
+            self.stats["spec_sampled_rounds"] = self.stats.get("spec_sampled_rounds", 0) + 1
         elif logits.is_cuda and K > 1 and all(len(drafts[s.seq_id]) == K - 1 for s in decode):
             # every row carries a full block: argmax + accept walk on the device, and the host reads
             # back two ints per row (accepted length, token at the first mismatch) instead of the

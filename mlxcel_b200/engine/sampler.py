@@ -23,7 +23,11 @@ class Sampler:
         self.device = device
         self._mirostat_mu: dict[int, float] = {}
 
-    def sample(self, logits: torch.Tensor, seqs) -> tuple[list[int], list | None]:
+    def sample(self, logits: torch.Tensor, seqs, step_offsets: list[int] | None = None
+               ) -> tuple[list[int], list | None]:
+        """One token per logits row. ``step_offsets`` (speculative verify blocks) lets one sequence own
+        several rows: row i is drawn as that sequence's step ``len(output) + step_offsets[i]``, so the
+        draw at each position is the one classic decoding would make there."""
         R = len(seqs)
         if R == 0:
             return [], None
@@ -81,7 +85,8 @@ class Sampler:
                 ty = torch.tensor([seqs[i].params.typical_p for i in fused], dtype=torch.float32)
                 ns = torch.tensor([seqs[i].params.top_n_sigma for i in fused], dtype=torch.float32)
             seeds = torch.tensor([_seed_of(seqs[i]) for i in fused], dtype=torch.int64)
-            steps = torch.tensor([len(seqs[i].output) for i in fused], dtype=torch.int64)
+            steps = torch.tensor([len(seqs[i].output) + (step_offsets[i] if step_offsets else 0) for i in fused],
+                                 dtype=torch.int64)
             d = work.device
             t, lp = ops.sample(sel.contiguous(), temp.to(d), tk.to(d), tp.to(d), mp.to(d), seeds.to(d),
                                steps.to(d), ty.to(d) if ty is not None else None,

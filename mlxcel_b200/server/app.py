@@ -20,7 +20,7 @@ from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 from ..engine import SamplingParams
 from .chat_template import TemplateRenderError, render_chat
 from .structured import constraint_from_request
-from .tool_calls import ToolCallStreamFilter, parse_tool_calls, split_reasoning
+from .tool_calls import IncrementalToolCallStreamer, parse_tool_calls, split_reasoning
 from .worker import GenRequest, ModelWorker
 
 
@@ -602,26 +602,22 @@ def create_app(state: ServerState) -> FastAPI:
             include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
 
             async def gen():
-                filt = ToolCallStreamFilter(allowed) if use_tools else None
-                n_calls = 0
+                # tool calls stream as they are generated: the name first, then argument fragments
+                filt = IncrementalToolCallStreamer(allowed) if use_tools else None
                 yield _sse({**base, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""},
                                                  "finish_reason": None}]})
                 async for ev in _generate(state, ids, sp, constraint, public_id=cid):
                     if ev.kind in ("token", "done"):
-                        text, calls = (filt.feed(ev.text) if filt else (ev.text, []))
-                        if ev.kind == "done" and filt:
-                            t2, c2 = filt.flush()
-                            text, calls = text + t2, calls + c2
+                        text, calls = (filt.feed(ev.text, final=ev.kind == "done") if filt else (ev.text, []))
                         if text:
                             yield _sse({**base, "choices": [{"index": 0, "delta": {"content": text},
                                                              "finish_reason": None}]})
-                        for c in calls:
-                            yield _sse({**base, "choices": [{"index": 0, "delta": {"tool_calls": [c.to_openai(n_calls)]},
+                        for d in calls:
+                            yield _sse({**base, "choices": [{"index": 0, "delta": {"tool_calls": [d]},
                                                              "finish_reason": None}]})
-                            n_calls += 1
                         if ev.kind == "done":
                             yield _sse({**base, "choices": [{"index": 0, "delta": {},
-                                                             "finish_reason": _finish_openai(ev.finish_reason, n_calls > 0)}],
+                                                             "finish_reason": _finish_openai(ev.finish_reason, bool(filt and filt.n))}],
                                         "timings": ev.timings})
                             if include_usage:
                                 yield _sse({**base, "choices": [], "usage": ev.usage})

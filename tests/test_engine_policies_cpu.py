@@ -184,3 +184,24 @@ def test_exactness_probe_and_policy_on_the_engine(tmp_path):
     assert st.spec_rounds > 0 and st.classic_steps >= 1 and st.mode in ("enabled", "disabled")
     eng.spec_policy.state.exact = False           # a failed probe keeps speculation off
     assert not eng.spec_policy.allow()
+
+
+def test_sampler_match_acceptance_reproduces_classic_sampling():
+    """Sampled rows in a verify round draw every position with their own seed and step counter, so the
+    text equals what the same seeds give without a drafter, and the drafts still save steps."""
+    cfg, w, eng = _engine()
+    prompts = [_prompt(cfg, n, seed=n) for n in (9, 14, 11)]
+    sps = [SamplingParams(max_tokens=24, ignore_eos=True, temperature=0.7, top_k=20, top_p=0.9, seed=11 + i) for i in range(2)]
+    sps.append(SamplingParams(max_tokens=24, ignore_eos=True))         # a greedy row in the same rounds
+    want = [s.output for s in eng.generate(prompts, sps)]
+    assert want[0] != want[1]
+    cfg, w, eng = _engine()
+    eng.drafter = DraftModelDrafter(DecoderModel(cfg, w), cfg, num_blocks=96, max_model_len=384)
+    got = [s.output for s in eng.generate(prompts, sps)]
+    assert got == want
+    assert eng.stats["spec_sampled_rounds"] > 0 and eng.stats["spec_accepted"] > 0
+    # penalties over the history keep a row out of verify rounds
+    cfg, w, eng = _engine()
+    eng.drafter = DraftModelDrafter(DecoderModel(cfg, w), cfg, num_blocks=96, max_model_len=384)
+    eng.generate(prompts[:1], SamplingParams(max_tokens=8, ignore_eos=True, temperature=0.7, repetition_penalty=1.3, seed=3))
+    assert eng.stats["spec_rounds"] == 0
