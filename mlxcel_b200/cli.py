@@ -760,8 +760,12 @@ def cmd_serve(a):
         control = ControlPlane(a._control_group)
     budget = a.reasoning_budget if a.reasoning_budget is not None else os.environ.get(
         "LLAMA_ARG_THINK_BUDGET", os.environ.get("LLAMA_ARG_REASONING_BUDGET"))
+    sleep_idle = float(getattr(a, "sleep_idle_seconds", -1) or -1)
+    if sleep_idle > 0 and (control is not None or getattr(a, "lora", None)):
+        raise SystemExit("--sleep-idle-seconds works with one process and without --lora (both keep the weights referenced)")
     worker = ModelWorker(llm.engine, llm.tokenizer, a.alias or os.path.basename(a.model.rstrip("/")), control=control,
-                         hang_timeout=float(a.decode_hang_timeout), failfast=True)
+                         hang_timeout=float(a.decode_hang_timeout), failfast=True,
+                         engine_factory=(lambda: load_llm(a).engine) if sleep_idle > 0 else None, sleep_idle=max(sleep_idle, 0.0))
     if control is not None and not control.is_leader:
         worker.follow()
         _leave_distributed()
@@ -782,13 +786,15 @@ def cmd_serve(a):
     state.log = LogControl(dest=a.log_file, fmt=a.log_format, verbosity=verbosity, redact=not a.no_log_redact)
     from .lora import LoraManager
     from .models.weights import QuantizedTensor
-    if not any(isinstance(lw.wqkv, QuantizedTensor) for lw in llm.model.w.layers):
+    if sleep_idle <= 0 and not any(isinstance(lw.wqkv, QuantizedTensor) for lw in llm.model.w.layers):
         comm = llm.model.comm
         state.lora = LoraManager(llm.cfg, llm.model.w, comm.tp_rank, comm.tp_size)
         for spec in getattr(a, "lora", None) or []:
             path, _, sc = spec.partition("=")
             state.lora.add(path, float(sc) if sc else 1.0)
     listen = dict(uds=a.listen_unix) if a.listen_unix else dict(host=a.host, port=a.port)
+    if sleep_idle > 0:
+        del llm                     # the worker holds the only reference to the engine, so sleeping frees it
     try:
         uvicorn.run(create_app(state), log_level="info" if a.verbose else "warning",
                     ssl_certfile=a.ssl_cert_file, ssl_keyfile=a.ssl_key_file, **listen)
@@ -1020,6 +1026,8 @@ def main(argv=None):
                    help="default thinking-token budget of requests that give none (-1 unlimited, 0 close at once)")
     p.add_argument("--decode-hang-timeout", type=float, default=0.0,
                    help="seconds after which a step that has not returned fails its requests (0 = off)")
+    p.add_argument("--sleep-idle-seconds", type=float, default=-1,
+                   help="unload the model after this many seconds without a request; the next request loads it again (-1 = never)")
     p.add_argument("--ssl-cert-file", default=None)
     p.add_argument("--ssl-key-file", default=None)
     p.add_argument("--cors-origin", action="append", default=None, metavar="ORIGIN",

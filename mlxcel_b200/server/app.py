@@ -203,8 +203,9 @@ def create_app(state: ServerState) -> FastAPI:
 
     @app.get("/props")
     async def props():
-        e = state.worker.engine
+        e = state.worker.view()
         return {"model_path": state.model_id, "total_slots": e.ecfg.max_batch, "chat_template": state.chat_template or "",
+                "is_sleeping": bool(getattr(state.worker, "sleeping", False)),
                 "default_generation_settings": {"n_ctx": e.ecfg.max_model_len, "params": {}},
                 "build_info": "mlxcel_b200 0.1.0", "bos_token": getattr(tk, "bos_token", None),
                 "eos_token": getattr(tk, "eos_token", None)}
@@ -295,7 +296,7 @@ def create_app(state: ServerState) -> FastAPI:
 
     @app.get("/v1/cache/stats")
     async def cache_stats():
-        return dict(state.worker.engine.bm.stats())
+        return dict(state.worker.view().bm.stats())
 
     @app.post("/v1/cache/reset")
     async def cache_reset():

@@ -303,7 +303,7 @@ def install_extras(app, state) -> None:
     async def get_settings():
         if not getattr(state, "settings_enabled", False):
             return _err(404, "live settings are disabled (start the server with --enable-settings)", "not_found_error")
-        e = state.worker.engine.ecfg
+        e = state.worker.view().ecfg
         return {**state.settings, "log_verbosity": state.log.verbosity, "log_format": state.log.fmt,
                 "log_redact": state.log.redact, "prefill_chunk_size": e.prefill_chunk_alone,
                 "max_queue_depth": e.max_queue_depth, "cors_origins": state.cors_origins}
@@ -323,7 +323,7 @@ def install_extras(app, state) -> None:
             return _err(400, f"bad value: {e}")
         if vals.get("thinking_budget") is not None and vals["thinking_budget"] < -1:
             return _err(400, "thinking_budget must be >= -1")
-        e = state.worker.engine.ecfg
+        e = state.worker.view().ecfg
         for k, v in vals.items():
             if k in ("default_max_tokens", "default_temperature", "thinking_budget"):
                 state.settings[k] = v

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 def render_metrics(state) -> str:
     w = state.worker
-    c, e = w.counters, w.engine
+    c, e = w.counters, w.view()
     bm = e.bm.stats()
     lines = []
 
@@ -27,6 +27,7 @@ def render_metrics(state) -> str:
     m("llamacpp:n_decode_total", "counter", "Total number of decode steps.", e.stats["steps"])
     m("llamacpp:prompt_tokens_cached_total", "counter", "Prompt tokens served from the prefix cache.",
       e.stats["prefix_hit_tokens"])
+    m("mlxcel_model_sleeping", "gauge", "1 while the idle model is unloaded.", int(getattr(w, "sleeping", False)))
     m("mlxcel_requests_total", "counter", "Requests admitted.", c["requests"])
     m("mlxcel_request_errors_total", "counter", "Requests that ended in an error.", c["errors"])
     m("mlxcel_requests_cancelled_total", "counter", "Requests cancelled by the client.", c["cancelled"])

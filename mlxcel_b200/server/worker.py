@@ -52,7 +52,7 @@ class GenRequest:
 
 class ModelWorker:
     def __init__(self, engine: Engine, tokenizer, model_id: str = "model", control=None, start: bool = True,
-                 hang_timeout: float = 0.0, failfast: bool = False):
+                 hang_timeout: float = 0.0, failfast: bool = False, engine_factory=None, sleep_idle: float = 0.0):
         """``control``: a :class:`mlxcel_b200.parallel.control.ControlPlane` when several processes run
         the engine together. On the leader the worker thread broadcasts what it drained from its inbox
         before every step; on the other ranks :meth:`follow` replaces the thread and applies the
@@ -60,9 +60,18 @@ class ModelWorker:
         seconds fails the requests in flight and marks the worker unhealthy (the reference's decode
         hang timeout, src/server/model_provider.rs:3002-3036). ``failfast``: an exception that escapes
         the worker loop ends the process instead of leaving a server that accepts requests and never
-        answers (src/worker_failfast.rs)."""
+        answers (src/worker_failfast.rs). ``sleep_idle`` > 0 with an ``engine_factory``: after that
+        many seconds without a request the engine (weights, KV pool, graphs) is dropped and its device
+        memory returned; the next request builds it again through the factory before it is admitted
+        (``--sleep-idle-seconds``, src/server/model_worker.rs:259-288). ``sleeping`` is what `/props`
+        reports as ``is_sleeping``."""
+        self.engine_factory, self.sleep_idle = engine_factory, float(sleep_idle)
+        self.sleeping = False
+        self._wake_lock = threading.Lock()
+        self._last_activity = time.monotonic()
+        self.sleep_snapshot: dict = {}
         self.recent: dict[int, list[int]] = {}    # slot id -> tokens of its last finished sequence
-        self.engine, self.tokenizer, self.model_id = engine, tokenizer, model_id
+        self._engine, self.tokenizer, self.model_id = engine, tokenizer, model_id
         self.control = control
         self.hang_timeout, self.failfast = hang_timeout, failfast
         self._step_started: float | None = None
@@ -80,6 +89,59 @@ class ModelWorker:
             threading.Thread(target=self._watchdog, name="step-watchdog", daemon=True).start()
         if start and (control is None or control.is_leader):
             self.thread.start()
+
+    # ------------------------------------------------------------------ idle sleep
+    @property
+    def engine(self) -> Engine:
+        """The live engine; touching it while the worker sleeps loads the model again."""
+        if self._engine is None:
+            self._wake()
+        return self._engine
+
+    @engine.setter
+    def engine(self, value) -> None:
+        self._engine = value
+
+    def view(self):
+        """What read-only routes (`/props`, `/metrics`, cache statistics) look at: the live engine, or
+        while the worker sleeps a frozen copy of its last counters so that a scrape does not load the
+        model."""
+        eng = self._engine
+        if eng is not None:
+            return eng
+        from types import SimpleNamespace
+        snap = self.sleep_snapshot
+        return SimpleNamespace(bm=SimpleNamespace(stats=lambda: dict(snap["kv"])), stats=snap["stats"], running=[],
+                               waiting=[], ecfg=snap["ecfg"], spec_policy=None, drafter=None)
+
+    def _sleep(self) -> None:
+        with self._wake_lock:
+            if self._engine is None or self._engine.has_work():
+                return
+            eng = self._engine
+            self.sleep_snapshot = dict(kv=dict(eng.bm.stats()), stats=dict(eng.stats), slept_at=time.time(),
+                                       ecfg=eng.ecfg)
+            self._engine = None
+            self.sleeping = True
+            self.recent.clear()
+            del eng
+            import gc
+            gc.collect()
+            import torch
+            if torch.cuda.is_available():
+                torch.cuda.empty_cache()
+            self.counters["sleeps"] = self.counters.get("sleeps", 0) + 1
+
+    def _wake(self) -> None:
+        with self._wake_lock:
+            if self._engine is not None:
+                return
+            t0 = time.monotonic()
+            self._engine = self.engine_factory()
+            self.sleeping = False
+            self._last_activity = time.monotonic()
+            self.counters["wakes"] = self.counters.get("wakes", 0) + 1
+            self.counters["wake_seconds"] = self.counters.get("wake_seconds", 0.0) + (time.monotonic() - t0)
 
     # ------------------------------------------------------------------ client side
     def submit(self, req: GenRequest) -> None:
@@ -342,16 +404,27 @@ class ModelWorker:
             raise
 
     def _loop(self) -> None:
-        eng = self.engine
+        can_sleep = self.sleep_idle > 0 and self.engine_factory is not None and self.control is None
         while self.running:
-            items = self._drain(block=not eng.has_work())
+            eng = self._engine
+            items = self._drain(block=eng is None or not eng.has_work())
+            if items:
+                self._last_activity = time.monotonic()
+                if eng is None and not all(isinstance(i, tuple) and i[0] == "stop" for i in items):
+                    self._wake()
+            elif can_sleep and eng is not None and not eng.has_work() and \
+                    time.monotonic() - self._last_activity > self.sleep_idle:
+                self._sleep()
+                continue
             if self.control is not None:
                 if not self._lead(items):
                     return
             elif not self._apply_local(items):
                 return
-            if eng.has_work():
+            eng = self._engine
+            if eng is not None and eng.has_work():
                 self._step_once()
+                self._last_activity = time.monotonic()
 
     def follow(self) -> None:
         """Executor loop of a non-leader rank: apply the leader's descriptors, check lockstep, step.
@@ -368,6 +441,8 @@ class ModelWorker:
     # ------------------------------------------------------------------ introspection
     def slots(self) -> list[dict]:
         out = []
+        if self._engine is None:
+            return out
         for i, s in enumerate(self.engine.running):
             out.append(dict(id=i, id_task=s.seq_id, is_processing=True, n_prompt=len(s.prompt),
                             n_decoded=len(s.output), state=s.status.value))

@@ -178,3 +178,57 @@ def test_metrics_have_histograms(server):
     text = c.get("/metrics").text
     assert 'mlxcel_request_ttft_seconds_bucket{le="+Inf"}' in text and "mlxcel_request_ttft_seconds_count" in text
     assert "mlxcel_spec_decode_rounds_total" in text and "mlxcel_responses_store_entries" in text
+
+
+def test_idle_worker_unloads_the_model_and_the_next_request_loads_it_again():
+    """--sleep-idle-seconds: the engine is dropped after the idle window, read-only routes answer from
+    the frozen counters without waking it, and the next request gets the same greedy text."""
+    import queue as _q
+    import time as _t
+
+    import torch as _torch
+
+    from mlxcel_b200.config import preset
+    from mlxcel_b200.engine import Engine, EngineConfig, SamplingParams
+    from mlxcel_b200.models.decoder import DecoderModel
+    from mlxcel_b200.models.weights import random_weights
+    from mlxcel_b200.server.metrics import render_metrics
+    from mlxcel_b200.server.worker import GenRequest, ModelWorker
+    from mlxcel_b200.tokenizer import ByteTokenizer
+    cfg = preset("tiny-llama")
+    built = []
+
+    def factory():
+        w = random_weights(cfg, seed=0, dtype=_torch.float32, std=0.05)
+        built.append(1)
+        return Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=2, max_num_batched_tokens=64, num_blocks=32,
+                                                              max_model_len=128, cuda_graphs=False))
+    tk = ByteTokenizer(cfg.vocab_size)
+    worker = ModelWorker(factory(), tk, "tiny", engine_factory=factory, sleep_idle=0.4)
+
+    def ask():
+        out = _q.Queue()
+        worker.submit(GenRequest(prompt_ids=[5, 6, 7, 8], params=SamplingParams(max_tokens=5, ignore_eos=True), out=out))
+        text = ""
+        while True:
+            ev = out.get(timeout=60)
+            if ev.kind == "token":
+                text += ev.text
+            if ev.kind in ("done", "error"):
+                assert ev.kind == "done"
+                return text + (ev.text or "")
+    try:
+        first = ask()
+        deadline = _t.monotonic() + 20
+        while not worker.sleeping and _t.monotonic() < deadline:
+            _t.sleep(0.05)
+        assert worker.sleeping and worker._engine is None
+        v = worker.view()
+        assert v.ecfg.max_batch == 2 and v.bm.stats()["num_blocks"] == 32 and worker.slots() == []
+        from types import SimpleNamespace
+        assert "mlxcel_model_sleeping 1" in render_metrics(SimpleNamespace(worker=worker, hist=None))
+        assert worker.sleeping and len(built) == 1                 # looking did not wake it
+        assert ask() == first
+        assert not worker.sleeping and len(built) == 2 and worker.counters["wakes"] == 1
+    finally:
+        worker.shutdown()
