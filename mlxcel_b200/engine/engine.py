@@ -53,10 +53,15 @@ class Sequence:
     think_forced: int = 0             # end-of-thinking tokens this engine forced
     draft_n: int = 0                  # speculative decoding: drafted / accepted tokens of this request
     draft_n_accepted: int = 0
+    mm_embeds: list | None = None     # [(start, rows)] media rows replacing placeholder embeddings
+    prompt_keys: list | None = None   # prompt ids with media placeholders salted (prefix-cache keys)
 
     @property
     def tokens(self) -> list[int]:
         return self.prompt + self.output
+
+    def key_tokens(self) -> list[int]:
+        return self.tokens if self.prompt_keys is None else self.prompt_keys + self.output
 
     @property
     def total_len(self) -> int:
@@ -259,9 +264,16 @@ class Engine:
     # ------------------------------------------------------------------ request API
     def add_request(self, prompt: list[int], params: SamplingParams | None = None,
                     on_token: Callable | None = None, mask_fn: Callable | None = None,
-                    user_data=None) -> int:
+                    user_data=None, mm_embeds: list | None = None, key_tokens: list[int] | None = None) -> int:
+        """``mm_embeds``: ``[(start, rows[n, hidden])]`` — rows that replace the token embeddings of
+        prompt positions ``start .. start+n`` (image / audio placeholders). ``key_tokens``: what the
+        prefix cache hashes instead of the prompt ids (placeholders salted by media content)."""
         if not prompt:
             raise ValueError("empty prompt")
+        if mm_embeds and (self.recurrent or self.pipeline):
+            raise ValueError("media inputs need the attention executor on one pipeline stage")
+        if key_tokens is not None and len(key_tokens) != len(prompt):
+            raise ValueError("key_tokens must have one entry per prompt token")
         params = params or SamplingParams()
         if len(prompt) + 1 > self.ecfg.max_model_len:
             raise ValueError(f"prompt of {len(prompt)} tokens exceeds max_model_len {self.ecfg.max_model_len}")
@@ -277,6 +289,9 @@ class Engine:
         self._next_id += 1
         s = Sequence(sid, list(prompt), params, arrival=time.perf_counter(), on_token=on_token,
                      mask_fn=mask_fn, user_data=user_data)
+        if mm_embeds:
+            s.mm_embeds = [(int(st), rows.to(self.device)) for st, rows in mm_embeds]
+            s.prompt_keys = list(key_tokens) if key_tokens is not None else None
         if params.thinking_cap is not None and params.think_start_id is not None:
             # a generation prompt may already have opened the reasoning block
             for t in reversed(prompt):
@@ -317,7 +332,7 @@ class Engine:
         s.status, s.finish_reason, s.finish_time = SeqStatus.FINISHED, reason, time.perf_counter()
         if self.bm.has_seq(s.seq_id):
             # donate computed full blocks to the prefix cache, then drop our references
-            toks = np.asarray(s.tokens[: s.num_computed], dtype=np.int32)
+            toks = np.asarray(s.key_tokens()[: s.num_computed], dtype=np.int32)
             self.bm.commit(s.seq_id, toks, s.num_computed)
             self._kv_free(s.seq_id)
         if s in self.running:
@@ -412,7 +427,7 @@ class Engine:
                 self.waiting.popleft()
                 if not self.bm.has_seq(s.seq_id):
                     self._kv_create(s.seq_id)
-                    toks = np.asarray(s.tokens, dtype=np.int32)
+                    toks = np.asarray(s.key_tokens(), dtype=np.int32)
                     hit = self.bm.match_prefix(s.seq_id, toks)
                     s.num_computed = s.num_cached = hit
                     self.stats["prefix_hit_tokens"] += hit
@@ -534,9 +549,25 @@ class Engine:
                       dec_block_tables_win=self.d_dec_tables_w[:nd] if (win and nd) else None,
                       pf_block_tables_win=self.d_pf_tables_w[:sp] if (win and sp) else None)
         b.logits_rows_host = rows
+        if any(p[0].mm_embeds for p in pieces):
+            b.embeds = self._media_embeds(b, nd, pieces)
         b.seq_ids = [s.seq_id for s in decode] + [p[0].seq_id for p in pieces]
         b.pf_starts = [p[1] for p in pieces]
         return b, R
+
+    def _media_embeds(self, b: StepBatch, nd: int, pieces) -> torch.Tensor:
+        """Input embeddings of a step that covers media placeholders: the token embeddings with the
+        rows of every placeholder position replaced by the connector's output."""
+        m = self.model
+        h = m.comm.embed(b.token_ids, m.w.embed, self.cfg.embed_scale).clone()
+        t = nd
+        for s, start, count in pieces:
+            for st, rows in s.mm_embeds or ():
+                lo, hi = max(st, start), min(st + rows.shape[0], start + count)
+                if lo < hi:
+                    h[t + lo - start: t + hi - start] = rows[lo - st: hi - st].to(h.dtype)
+            t += count
+        return h
 
     # ------------------------------------------------------------------ cuda graphs
     def _decode_graph(self, nd: int, max_len: int) -> torch.Tensor | None:

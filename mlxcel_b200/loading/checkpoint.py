@@ -362,6 +362,12 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
     pre = "model." if any(k.startswith("model.") for k in src.keys()) else ""
     if any(k.startswith("language_model.model.") for k in src.keys()):
         pre = "language_model.model."
+    else:
+        # vision-language wrappers nest the language model (``model.language_model.``,
+        # ``model.language_model.model.``, ...): take the prefix of its embedding table
+        nested = [k for k in src.keys() if k.endswith(".embed_tokens.weight") and "language_model" in k]
+        if len(nested) == 1:
+            pre = nested[0][: -len("embed_tokens.weight")]
     emb = g.mat(pre + "embed_tokens")
     if isinstance(emb, QuantizedTensor):
         from ..ops.quant import dequantize_ref

@@ -1,0 +1,134 @@
+"""Vision-language path against Hugging Face transformers (CPU, fp32): vision towers, connectors,
+placeholder expansion, media rows in the embedding stream, and greedy decoding through the engine
+with the image span split across prefill chunks."""
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from mlxcel_b200.config import ModelConfig  # noqa: E402
+from mlxcel_b200.engine import Engine, EngineConfig, SamplingParams  # noqa: E402
+from mlxcel_b200.loading.checkpoint import load_full_weights  # noqa: E402
+from mlxcel_b200.models.decoder import DecoderModel  # noqa: E402
+from mlxcel_b200.models.vision import ViTTower, VisionConfig  # noqa: E402
+from mlxcel_b200.multimodal import ImageProcessor, VisionLanguage, is_vlm_checkpoint, load_image  # noqa: E402
+
+IMG_TOKEN = 290
+
+
+def _image(seed=0, w=40, h=30):
+    from PIL import Image
+    rng = np.random.default_rng(seed)
+    return Image.fromarray(rng.integers(0, 256, (h, w, 3), dtype=np.uint8), "RGB")
+
+
+@pytest.mark.parametrize("kind", ["clip", "siglip"])
+def test_vit_towers_match_transformers(kind):
+    from transformers import CLIPVisionConfig, CLIPVisionModel, SiglipVisionConfig, SiglipVisionModel
+    torch.manual_seed(0)
+    kw = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, image_size=28, patch_size=7)
+    hc, cls = (CLIPVisionConfig(**kw), CLIPVisionModel) if kind == "clip" else (SiglipVisionConfig(**kw), SiglipVisionModel)
+    m = cls(hc).eval()
+    sd = {k.removeprefix("vision_model."): v for k, v in m.state_dict().items()}
+    px = torch.randn(2, 3, 28, 28)
+    with torch.no_grad():
+        out = m(pixel_values=px, output_hidden_states=True)
+    for fl in (-1, -2):
+        vc = VisionConfig.from_dict(hc.to_dict(), {"vision_feature_layer": fl})
+        got = ViTTower(vc, sd, dtype=torch.float32).forward(px)
+        want = out.last_hidden_state if (fl == -1 and kind == "siglip") else out.hidden_states[fl]
+        if kind == "clip":
+            want = want[:, 1:]
+        assert (got - want).abs().max().item() < 1e-4
+
+
+def test_image_processor_matches_transformers_clip_processor():
+    from transformers import CLIPImageProcessor
+    hp = CLIPImageProcessor(size={"shortest_edge": 28}, crop_size={"height": 28, "width": 28})
+    imgs = [_image(1, 50, 37), _image(2, 31, 64)]
+    want = torch.tensor(np.stack(hp(imgs)["pixel_values"]))
+    got = ImageProcessor(hp.to_dict(), 28)(imgs)
+    # the bicubic resize rounds to 8-bit levels; PIL and the tensor resize of transformers may differ by one level
+    one_level = 1 / 255 / min(hp.image_std)
+    diff = (got - want).abs()
+    assert got.shape == want.shape and diff.max().item() <= one_level * 1.01 and diff.mean().item() < 0.1 * one_level
+
+
+def test_load_image_sources_and_refusals(tmp_path):
+    import base64
+    import io
+    img = _image(3)
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    b64 = base64.b64encode(buf.getvalue()).decode()
+    assert load_image("data:image/png;base64," + b64).size == img.size
+    assert load_image(b64).size == img.size and load_image(buf.getvalue()).size == img.size
+    p = tmp_path / "media" / "a.png"
+    p.parent.mkdir()
+    p.write_bytes(buf.getvalue())
+    assert load_image(str(p), media_root=str(p.parent)).size == img.size
+    with pytest.raises(ValueError, match="outside"):
+        load_image(str(p), media_root=str(tmp_path / "other"))
+    with pytest.raises(ValueError, match="remote"):
+        load_image("https://example.com/x.png")
+    with pytest.raises(ValueError):
+        load_image("not an image at all")
+
+
+def _tiny_llava():
+    from transformers import CLIPVisionConfig, LlamaConfig, LlavaConfig, LlavaForConditionalGeneration
+    torch.manual_seed(0)
+    vc = CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                          image_size=28, patch_size=7)
+    tc = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, vocab_size=300, max_position_embeddings=256)
+    cfg = LlavaConfig(vision_config=vc, text_config=tc, image_token_index=IMG_TOKEN, vision_feature_layer=-2,
+                      vision_feature_select_strategy="default", projector_hidden_act="gelu")
+    m = LlavaForConditionalGeneration(cfg).eval()
+    d = tempfile.mkdtemp(prefix="vlm_llava_")
+    m.save_pretrained(d, safe_serialization=True)
+    return m, d
+
+
+def test_llava_greedy_matches_transformers_through_the_engine():
+    m, d = _tiny_llava()
+    assert is_vlm_checkpoint(d)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    vl.processor = ImageProcessor(dict(size={"shortest_edge": 28}, crop_size={"height": 28, "width": 28}), 28)
+    imgs = [_image(5), _image(6, 33, 52)]
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [IMG_TOKEN] + text(7) + [IMG_TOKEN] + text(4)
+    ids, spans, keys, _ = vl.prepare(prompt, imgs)
+    assert len(ids) == 16 + 2 * 16 and [s for s, _ in spans] == [5, 5 + 16 + 7]
+    assert all(k < 0 for k, t in zip(keys, ids) if t == IMG_TOKEN) and len(keys) == len(ids)
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=vl.processor(imgs), max_new_tokens=8,
+                          do_sample=False)[0, len(ids):].tolist()
+    cfg = ModelConfig.from_path(d)
+    w = load_full_weights(d, cfg, dtype=torch.float32)
+    for chunk in (256, 12):          # 12: both image spans straddle chunk boundaries
+        eng = Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=2, max_num_batched_tokens=64, num_blocks=32,
+                                                             max_model_len=128, cuda_graphs=False,
+                                                             prefill_chunk_alone=chunk, prefill_chunk_contended=chunk))
+        sid = eng.add_request(ids, SamplingParams(max_tokens=8, ignore_eos=True), mm_embeds=spans, key_tokens=keys)
+        while eng.has_work():
+            eng.step()
+        assert eng.seqs[sid].output == want, chunk
+    # prefix cache: the same text with the same images hits, with another image it does not
+    eng.release(sid)
+    ids2, spans2, keys2, _ = vl.prepare(prompt, imgs)
+    sid2 = eng.add_request(ids2, SamplingParams(max_tokens=8, ignore_eos=True), mm_embeds=spans2, key_tokens=keys2)
+    while eng.has_work():
+        eng.step()
+    assert eng.seqs[sid2].output == want and eng.seqs[sid2].num_cached >= 32
+    ids3, spans3, keys3, _ = vl.prepare(prompt, [_image(9), imgs[1]])
+    sid3 = eng.add_request(ids3, SamplingParams(max_tokens=8, ignore_eos=True), mm_embeds=spans3, key_tokens=keys3)
+    while eng.has_work():
+        eng.step()
+    assert eng.seqs[sid3].num_cached < 16           # only the text before the first image can match
+    with pytest.raises(ValueError, match="placeholders"):
+        vl.prepare(prompt, imgs[:1])
