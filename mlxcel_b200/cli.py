@@ -350,10 +350,21 @@ def cmd_generate(a):
     llm = load_llm(a)
     tk = llm.tokenizer
     prompt = a.prompt if a.prompt is not None else sys.stdin.read()
+    mm = {}
+    if getattr(a, "image", None):
+        vision = getattr(llm, "vision", None)
+        if vision is None:
+            raise SystemExit("--image needs a vision-language checkpoint")
+        if prompt.count(vision.placeholder_text) == 0:       # images first, then the text (the usual layout)
+            prompt = vision.placeholder_text * len(a.image) + "\n" + prompt
     if a.chat:
         from .server.chat_template import render_chat
         prompt = render_chat([{"role": "user", "content": prompt}], getattr(tk, "chat_template", None))
     ids = tk.encode(prompt, add_special_tokens=not a.chat)
+    if getattr(a, "image", None):
+        from .multimodal import load_image
+        ids, spans, keys, _ = llm.vision.prepare(ids, [load_image(x) for x in a.image])
+        mm = dict(mm_embeds=spans, key_tokens=keys)
     sp = _sampling(a)
     sp.stop_token_ids = [i for i in tk.eos_ids() if i is not None]
     from .tokenizer import IncrementalDetokenizer
@@ -379,7 +390,7 @@ def cmd_generate(a):
         except ValueError as ex:
             raise SystemExit(f"structured output: {ex}")
         mask_fn = con.mask
-    sid = llm.engine.add_request(ids, sp, on_token=on_token, mask_fn=mask_fn)
+    sid = llm.engine.add_request(ids, sp, on_token=on_token, mask_fn=mask_fn, **mm)
     while llm.engine.has_work():
         llm.engine.step()
     s = llm.engine.seqs[sid]
@@ -778,6 +789,8 @@ def cmd_serve(a):
     state = ServerState(worker, llm.tokenizer, worker.model_id, api_keys=keys,
                         chat_template=open(a.chat_template_file).read() if a.chat_template_file else None)
     state.slot_save_path = a.slot_save_path
+    worker.vision = getattr(llm, "vision", None)
+    state.media_path, state.allow_remote_media = a.media_path, bool(a.allow_remote_media)
     state.default_thinking_budget = int(budget) if budget not in (None, "") else None
     state.cors_origins = list(a.cors_origin or ["*"])
     state.settings_enabled = bool(a.enable_settings)
@@ -999,6 +1012,8 @@ def main(argv=None):
     p.add_argument("-j", "--json-schema", default=None, help="JSON schema constraining the output ('{}' for any object)")
     p.add_argument("-jf", "--json-schema-file", default=None)
     p.add_argument("--regex", default=None, help="regular expression constraining the output")
+    p.add_argument("--image", action="append", default=None, metavar="FILE",
+                   help="image for a vision-language checkpoint (repeatable; one per placeholder, or placed before the prompt)")
     p.set_defaults(fn=cmd_generate)
     p = sub.add_parser("run", help="interactive chat")
     _add_model_args(p)
@@ -1026,6 +1041,8 @@ def main(argv=None):
                    help="default thinking-token budget of requests that give none (-1 unlimited, 0 close at once)")
     p.add_argument("--decode-hang-timeout", type=float, default=0.0,
                    help="seconds after which a step that has not returned fails its requests (0 = off)")
+    p.add_argument("--media-path", default=None, help="directory image paths in requests must lie in (default: any readable path)")
+    p.add_argument("--allow-remote-media", action="store_true", help="fetch http(s) image URLs named by requests")
     p.add_argument("--sleep-idle-seconds", type=float, default=-1,
                    help="unload the model after this many seconds without a request; the next request loads it again (-1 = never)")
     p.add_argument("--ssl-cert-file", default=None)

@@ -1008,12 +1008,14 @@ class Engine:
         return finished
 
     # ------------------------------------------------------------------ convenience
-    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams] | None = None
-                 ) -> list[Sequence]:
-        """Run the given prompts to completion (continuous batching) and return them in order."""
+    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams] | None = None,
+                 media: list | None = None) -> list[Sequence]:
+        """Run the given prompts to completion (continuous batching) and return them in order.
+        ``media[i]``: ``dict(mm_embeds=..., key_tokens=...)`` of prompt i, or None."""
         if not isinstance(params, list):
             params = [params or SamplingParams()] * len(prompts)
-        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        media = media or [None] * len(prompts)
+        ids = [self.add_request(p, sp, **(mm or {})) for p, sp, mm in zip(prompts, params, media)]
         while self.has_work():
             self.step()
         return [self.seqs[i] for i in ids]

@@ -118,7 +118,11 @@ class LLM:
                        tokenizer=load_tokenizer(path))
         w = load_model_weights(path, cfg, device=device, comm=comm, dequantize=dequantize, surgery=surgery)
         tok = load_tokenizer(path)
-        return LLM(cfg, w, engine_config, comm=comm, tokenizer=tok, fold_norms=True)
+        llm = LLM(cfg, w, engine_config, comm=comm, tokenizer=tok, fold_norms=True)
+        from .multimodal import VisionLanguage, is_vlm_checkpoint
+        if is_vlm_checkpoint(path):
+            llm.vision = VisionLanguage.from_checkpoint(path, dtype=w.final_norm.dtype, device=device)
+        return llm
 
     # ------------------------------------------------------------------ scoring
     def loglikelihoods(self, token_ids: list[int]):
@@ -128,14 +132,30 @@ class LLM:
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompts=None, sampling_params: SamplingParams | list[SamplingParams] | None = None,
-                 prompt_token_ids: list[list[int]] | None = None) -> list[Sequence]:
+                 prompt_token_ids: list[list[int]] | None = None, images: list[list] | None = None) -> list[Sequence]:
+        """``images[i]``: the images of prompt i (paths, data URLs, bytes or PIL images), one per image
+        placeholder of that prompt, for vision-language checkpoints."""
         if prompt_token_ids is None:
             if self.tokenizer is None:
                 raise ValueError("text prompts need a tokenizer; pass prompt_token_ids")
             if isinstance(prompts, str):
                 prompts = [prompts]
             prompt_token_ids = [self.tokenizer.encode(p) for p in prompts]
-        outs = self.engine.generate(prompt_token_ids, sampling_params)
+        media = None
+        if images is not None and any(images):
+            vision = getattr(self, "vision", None)
+            if vision is None:
+                raise ValueError("this model takes no image input")
+            from .multimodal import load_image
+            media, prompt_token_ids = [], list(prompt_token_ids)
+            for i, imgs in enumerate(images):
+                if not imgs:
+                    media.append(None)
+                    continue
+                ids, spans, keys, _ = vision.prepare(prompt_token_ids[i], [load_image(x) for x in imgs])
+                prompt_token_ids[i] = ids
+                media.append(dict(mm_embeds=spans, key_tokens=keys))
+        outs = self.engine.generate(prompt_token_ids, sampling_params, media=media)
         for s in outs:
             self.engine.release(s.seq_id)
         return outs

@@ -49,6 +49,9 @@ class VisionLanguage:
         self.tower, self.connector, self.processor = tower, connector, processor
         self.image_token_id = int(image_token_id)
         self.model_type = model_type
+        # what stands for one image in prompt text when the chat template does not place it itself
+        self.placeholder_text = {"llava": "<image>", "qwen2_vl": "<|vision_start|><|image_pad|><|vision_end|>",
+                                 "qwen2_5_vl": "<|vision_start|><|image_pad|><|vision_end|>"}.get(model_type, "<image>")
         self.stats = dict(images=0, image_tokens=0, encode_seconds=0.0)
 
     @staticmethod

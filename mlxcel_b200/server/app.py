@@ -120,12 +120,18 @@ class ServerState:
         return sp
 
 
+class PromptWithMedia(list):
+    """Prompt token ids that carry the decoded images of their placeholder tokens to the worker."""
+
+    media: list | None = None
+
+
 async def _generate(state: ServerState, prompt_ids, sp, constraint=None, public_id: str | None = None):
     """Async generator of GenEvents for one request. ``public_id`` (a chat / response id) makes the
     request reachable for ``/v1/chat/completions/control`` and ``/v1/responses/{id}/cancel``."""
     q: asyncio.Queue = asyncio.Queue()
     req = GenRequest(prompt_ids=prompt_ids, params=state.eos_params(sp), loop=asyncio.get_running_loop(), out=q,
-                     constraint=constraint, request_id=uuid.uuid4().hex)
+                     constraint=constraint, request_id=uuid.uuid4().hex, media=getattr(prompt_ids, "media", None))
     inflight = getattr(state, "inflight", None)
     if public_id and inflight is not None:
         inflight[public_id] = req
@@ -578,9 +584,31 @@ def create_app(state: ServerState) -> FastAPI:
         kwargs = dict(body.get("chat_template_kwargs") or {})
         if body.get("reasoning_effort"):
             kwargs.setdefault("reasoning_effort", body["reasoning_effort"])
-        text = state.render(body.get("messages", []), tools=tools, **kwargs)
+        messages, images = body.get("messages", []), []
+        vision = getattr(state.worker, "vision", None)
+        has_media = any(isinstance(m.get("content"), list) and any(isinstance(p, dict) and p.get("type") in
+                        ("image_url", "image", "input_image") for p in m["content"]) for m in messages)
+        if has_media:
+            if vision is None:
+                raise TemplateRenderError("this model takes no image input")
+            from .chat_template import extract_media
+            messages, sources = extract_media(messages, vision.placeholder_text, state.chat_template)
+            from ..multimodal import load_image
+            try:
+                images = [load_image(src, media_root=getattr(state, "media_path", None),
+                                     allow_remote=bool(getattr(state, "allow_remote_media", False))) for src in sources]
+            except ValueError as e:
+                raise TemplateRenderError(str(e)) from e
+        text = state.render(messages, tools=tools, **kwargs)
         ids = tk.encode(text, add_special_tokens=False)
-        return ids or [getattr(tk, "bos_token_id", 0) or 0], tools
+        ids = ids or [getattr(tk, "bos_token_id", 0) or 0]
+        if images:
+            ids = PromptWithMedia(ids)
+            ids.media = images
+            n_ph = sum(1 for t in ids if t == vision.image_token_id)
+            if n_ph != len(images):
+                raise TemplateRenderError(f"the rendered prompt has {n_ph} image placeholders for {len(images)} images")
+        return ids, tools
 
     @app.post("/v1/chat/completions")
     @app.post("/chat/completions")

@@ -73,6 +73,42 @@ def normalize_messages(messages: list[dict]) -> list[dict]:
     return out
 
 
+_IMAGE_PART_TYPES = ("image_url", "image", "input_image")
+
+
+def extract_media(messages: list[dict], placeholder: str, template: str | None) -> tuple[list[dict], list]:
+    """Pull the images out of OpenAI-style content parts. Returns the messages to render and the image
+    sources in prompt order. A template that handles ``{"type": "image"}`` parts itself (the templates
+    vision-language checkpoints ship) gets them in that form; otherwise every image part becomes the
+    model's placeholder text inside a flattened string content."""
+    native = bool(template) and ("'image'" in template or '"image"' in template)
+    out, images = [], []
+    for m in messages:
+        c = m.get("content")
+        if not isinstance(c, list) or not any(isinstance(p, dict) and p.get("type") in _IMAGE_PART_TYPES for p in c):
+            out.append(m)
+            continue
+        parts, text = [], ""
+        for p in c:
+            kind = p.get("type") if isinstance(p, dict) else None
+            if kind in _IMAGE_PART_TYPES:
+                src = p.get("image_url") or p.get("image") or p.get("url")
+                if isinstance(src, dict):
+                    src = src.get("url")
+                if src is None:
+                    raise TemplateRenderError("an image part carries no image_url")
+                images.append(src)
+                parts.append({"type": "image"})
+                text += placeholder
+            elif kind in ("text", "input_text"):
+                parts.append({"type": "text", "text": p.get("text", "")})
+                text += p.get("text", "")
+        m = dict(m)
+        m["content"] = parts if native else text
+        out.append(m)
+    return out, images
+
+
 def render_chat(messages: list[dict], template: str | None = None, *, add_generation_prompt: bool = True,
                 tools: list | None = None, bos_token: str = "", eos_token: str = "", **kwargs) -> str:
     src = template or CHATML

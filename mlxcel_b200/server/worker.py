@@ -48,6 +48,7 @@ class GenRequest:
     stopper: StopMatcher | None = None
     t_submit: float = field(default_factory=time.perf_counter)
     n_emitted: int = 0
+    media: list | None = None          # decoded images, one per placeholder token of prompt_ids
 
 
 class ModelWorker:
@@ -65,6 +66,7 @@ class ModelWorker:
         memory returned; the next request builds it again through the factory before it is admitted
         (``--sleep-idle-seconds``, src/server/model_worker.rs:259-288). ``sleeping`` is what `/props`
         reports as ``is_sleeping``."""
+        self.vision = None                  # multimodal.VisionLanguage of a vision-language checkpoint
         self.engine_factory, self.sleep_idle = engine_factory, float(sleep_idle)
         self.sleeping = False
         self._wake_lock = threading.Lock()
@@ -187,8 +189,18 @@ class ModelWorker:
             return
         try:
             mask_fn = (lambda s, c=req.constraint: c.mask(s)) if req.constraint is not None else None
+            mm = {}
+            if req.media:
+                # tower + connector run here, on the engine's thread and stream, between two steps
+                if self.vision is None:
+                    raise ValueError("this model takes no image input")
+                if self.control is not None:
+                    raise ValueError("image input needs a single-process server")
+                req.prompt_ids, spans, keys, _ = self.vision.prepare(req.prompt_ids, req.media)
+                req.media = None
+                mm = dict(mm_embeds=spans, key_tokens=keys)
             sid = self.engine.add_request(req.prompt_ids, req.params, on_token=self._on_token, mask_fn=mask_fn,
-                                          user_data=req)
+                                          user_data=req, **mm)
         except Exception as e:
             self.counters["errors"] += 1
             self._emit(req, GenEvent("error", error=str(e)))

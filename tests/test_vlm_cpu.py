@@ -132,3 +132,75 @@ def test_llava_greedy_matches_transformers_through_the_engine():
     assert eng.seqs[sid3].num_cached < 16           # only the text before the first image can match
     with pytest.raises(ValueError, match="placeholders"):
         vl.prepare(prompt, imgs[:1])
+
+
+class _ImageByteTokenizer:
+    """Byte tokenizer that maps the text ``<image>`` to the placeholder id (what a real tokenizer's added
+    token does)."""
+
+    def __new__(cls, vocab):
+        from mlxcel_b200.tokenizer import ByteTokenizer
+
+        class T(ByteTokenizer):
+            def encode(self, text, add_special_tokens=False):
+                out = []
+                for i, piece in enumerate(text.split("<image>")):
+                    if i:
+                        out.append(IMG_TOKEN)
+                    out += list(piece.encode("utf-8"))
+                return ([self.bos_token_id] + out) if add_special_tokens else out
+        return T(vocab)
+
+
+def test_chat_route_takes_image_parts_and_equals_the_direct_run():
+    import base64
+    import io
+
+    from fastapi.testclient import TestClient
+
+    from mlxcel_b200.server.app import ServerState, create_app
+    from mlxcel_b200.server.chat_template import render_chat
+    from mlxcel_b200.server.worker import ModelWorker
+    m, d = _tiny_llava()
+    cfg = ModelConfig.from_path(d)
+    w = load_full_weights(d, cfg, dtype=torch.float32)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    vl.processor = ImageProcessor(dict(size={"shortest_edge": 28}, crop_size={"height": 28, "width": 28}), 28)
+    tk = _ImageByteTokenizer(cfg.vocab_size)
+
+    def engine():
+        return Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=2, max_num_batched_tokens=128, num_blocks=64,
+                                                              max_model_len=512, cuda_graphs=False))
+    img = _image(7)
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    messages = [{"role": "user", "content": [{"type": "text", "text": "what is this? "},
+                                             {"type": "image_url", "image_url": {"url": url}}]}]
+    # direct: the text the route renders, expanded and run on a fresh engine
+    text = render_chat([{"role": "user", "content": "what is this? <image>"}], None)
+    ids, spans, keys, _ = vl.prepare(tk.encode(text), [img])
+    eng = engine()
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    sid = eng.add_request(ids, sp, mm_embeds=spans, key_tokens=keys)
+    while eng.has_work():
+        eng.step()
+    want = tk.decode(eng.seqs[sid].output)
+    worker = ModelWorker(engine(), tk, "tiny-llava")
+    worker.vision = vl
+    try:
+        client = TestClient(create_app(ServerState(worker, tk, "tiny-llava")))
+        r = client.post("/v1/chat/completions", json={"messages": messages, "max_tokens": 6, "temperature": 0,
+                                                      "ignore_eos": True})
+        assert r.status_code == 200, r.text
+        out = r.json()
+        assert out["choices"][0]["message"]["content"] == want
+        assert out["usage"]["prompt_tokens"] == len(ids)            # placeholders count as expanded
+        # a second image without a second placeholder, and a model without a tower, are client errors
+        bad = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+            {"type": "image_url", "image_url": {"url": "https://example.com/a.png"}}]}]})
+        assert bad.status_code == 400 and "remote" in bad.text
+        worker.vision = None
+        assert client.post("/v1/chat/completions", json={"messages": messages}).status_code == 400
+    finally:
+        worker.shutdown()
