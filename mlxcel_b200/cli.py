@@ -363,8 +363,7 @@ def cmd_generate(a):
     ids = tk.encode(prompt, add_special_tokens=not a.chat)
     if getattr(a, "image", None):
         from .multimodal import load_image
-        ids, spans, keys, _ = llm.vision.prepare(ids, [load_image(x) for x in a.image])
-        mm = dict(mm_embeds=spans, key_tokens=keys)
+        ids, mm = llm.vision.prepare(ids, [load_image(x) for x in a.image])
     sp = _sampling(a)
     sp.stop_token_ids = [i for i in tk.eos_ids() if i is not None]
     from .tokenizer import IncrementalDetokenizer

@@ -300,6 +300,18 @@ def _qwen2(c: ModelConfig, raw: dict) -> None:
         c.sliding_window = 0
 
 
+def _qwen2_vl(c: ModelConfig, raw: dict) -> None:
+    """Language model of Qwen2-VL / Qwen2.5-VL: Qwen2 blocks with multimodal rotary positions (each
+    rotary frequency belongs to the temporal, height or width section)."""
+    _qwen2(c, raw)
+    for rec in (raw.get("rope_parameters"), raw.get("rope_scaling")):
+        if isinstance(rec, dict) and rec.get("mrope_section"):
+            c.extra["mrope_section"] = [int(x) for x in rec["mrope_section"]]
+    rs = c.rope_scaling
+    if isinstance(rs, dict) and rs.get("rope_type", rs.get("type")) in ("mrope", "default", None):
+        c.rope_scaling = None                 # "mrope" names the position layout, not a frequency scaling
+
+
 def _qwen3(c: ModelConfig, raw: dict) -> None:
     c.qk_norm = True
     c.sliding_window = 0 if not raw.get("use_sliding_window", False) else c.sliding_window
@@ -983,7 +995,8 @@ FAMILIES = {
     "helium": _interleaved_rope, "internlm3": _plain, "exaone4": _exaone4, "hunyuan_v1_dense": _hunyuan_dense,
     "hunyuan_v1_moe": _hunyuan_moe,
     "ernie4_5": _interleaved_rope, "apertus": _apertus, "minicpm": _minicpm, "mimo": _qwen2, "yi": _plain,
-    "qwen2": _qwen2, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
+    "qwen2": _qwen2, "qwen2_vl": _qwen2_vl, "qwen2_vl_text": _qwen2_vl, "qwen2_5_vl": _qwen2_vl,
+    "qwen2_5_vl_text": _qwen2_vl, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "mixtral": _mixtral, "phimoe": _phimoe, "olmoe": _olmoe,
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,

@@ -55,6 +55,8 @@ class Sequence:
     draft_n_accepted: int = 0
     mm_embeds: list | None = None     # [(start, rows)] media rows replacing placeholder embeddings
     prompt_keys: list | None = None   # prompt ids with media placeholders salted (prefix-cache keys)
+    rope_pos: object = None           # int32 [3, len(prompt)]: (t, h, w) rotary positions of the prompt
+    rope_delta: int = 0               # rotary position minus token index for tokens after the prompt
 
     @property
     def tokens(self) -> list[int]:
@@ -264,10 +266,14 @@ class Engine:
     # ------------------------------------------------------------------ request API
     def add_request(self, prompt: list[int], params: SamplingParams | None = None,
                     on_token: Callable | None = None, mask_fn: Callable | None = None,
-                    user_data=None, mm_embeds: list | None = None, key_tokens: list[int] | None = None) -> int:
+                    user_data=None, mm_embeds: list | None = None, key_tokens: list[int] | None = None,
+                    rope_pos=None, rope_delta: int = 0) -> int:
         """``mm_embeds``: ``[(start, rows[n, hidden])]`` — rows that replace the token embeddings of
         prompt positions ``start .. start+n`` (image / audio placeholders). ``key_tokens``: what the
-        prefix cache hashes instead of the prompt ids (placeholders salted by media content)."""
+        prefix cache hashes instead of the prompt ids (placeholders salted by media content).
+        ``rope_pos`` ([3, len(prompt)] ints) / ``rope_delta``: multimodal rotary positions (temporal,
+        height, width) of the prompt tokens and the offset ``rotary position - token index`` of every
+        later token (Qwen2-VL family; text-only prompts need neither)."""
         if not prompt:
             raise ValueError("empty prompt")
         if mm_embeds and (self.recurrent or self.pipeline):
@@ -292,6 +298,9 @@ class Engine:
         if mm_embeds:
             s.mm_embeds = [(int(st), rows.to(self.device)) for st, rows in mm_embeds]
             s.prompt_keys = list(key_tokens) if key_tokens is not None else None
+        if rope_pos is not None:
+            s.rope_pos = np.asarray(rope_pos, dtype=np.int32).reshape(3, len(prompt))
+            s.rope_delta = int(rope_delta)
         if params.thinking_cap is not None and params.think_start_id is not None:
             # a generation prompt may already have opened the reasoning block
             for t in reversed(prompt):
@@ -477,7 +486,7 @@ class Engine:
         for i, s in enumerate(decode):
             L = s.total_len
             tok[i] = s.output[-1] if s.output else s.prompt[-1]
-            pos[i] = L - 1
+            pos[i] = L - 1 + s.rope_delta
             self.bm.fill_slots(s.seq_id, L - 1, 1, self.np_slots, i)
             if self.bm_win is not None:
                 self.bm_win.fill_slots(s.seq_id, L - 1, 1, self.np_slots_w, i)
@@ -490,11 +499,22 @@ class Engine:
         t = nd
         cu = [0]
         max_q = 0
+        pos3 = None                      # [3, T] rotary positions when a piece carries multimodal ones
         rows: list[int] = list(range(nd))
         for j, (s, start, count) in enumerate(pieces):
             toks = s.tokens + drafts[s.seq_id] if (drafts and s.seq_id in drafts) else s.tokens
             tok[t:t + count] = toks[start:start + count]
             pos[t:t + count] = np.arange(start, start + count, dtype=np.int32)
+            if s.rope_pos is not None:
+                if pos3 is None:
+                    pos3 = np.zeros((3, self.h_pos.shape[0]), dtype=np.int32)
+                    pos3[:, :t] = pos[None, :t]
+                n_in = max(0, min(start + count, len(s.prompt)) - start)       # rows still inside the prompt
+                pos3[:, t:t + n_in] = s.rope_pos[:, start:start + n_in]
+                pos3[:, t + n_in:t + count] = pos[None, t + n_in:t + count] + s.rope_delta
+                pos[t:t + count] = pos3[0, t:t + count]
+            elif pos3 is not None:
+                pos3[:, t:t + count] = pos[None, t:t + count]
             self.bm.fill_slots(s.seq_id, start, count, self.np_slots, t)
             if self.bm_win is not None:
                 self.bm_win.fill_slots(s.seq_id, start, count, self.np_slots_w, t)
@@ -551,6 +571,8 @@ class Engine:
         b.logits_rows_host = rows
         if any(p[0].mm_embeds for p in pieces):
             b.embeds = self._media_embeds(b, nd, pieces)
+        if pos3 is not None:
+            b.positions3 = torch.from_numpy(pos3[:, :t].copy()).to(self.device)
         b.seq_ids = [s.seq_id for s in decode] + [p[0].seq_id for p in pieces]
         b.pf_starts = [p[1] for p in pieces]
         return b, R

@@ -152,9 +152,8 @@ class LLM:
                 if not imgs:
                     media.append(None)
                     continue
-                ids, spans, keys, _ = vision.prepare(prompt_token_ids[i], [load_image(x) for x in imgs])
-                prompt_token_ids[i] = ids
-                media.append(dict(mm_embeds=spans, key_tokens=keys))
+                prompt_token_ids[i], mm = vision.prepare(prompt_token_ids[i], [load_image(x) for x in imgs])
+                media.append(mm)
         outs = self.engine.generate(prompt_token_ids, sampling_params, media=media)
         for s in outs:
             self.engine.release(s.seq_id)

@@ -55,6 +55,9 @@ class StepBatch:
     slot_mapping_win: torch.Tensor | None = None
     dec_block_tables_win: torch.Tensor | None = None
     pf_block_tables_win: torch.Tensor | None = None
+    # Multimodal rotary positions [3, T] (temporal, height, width) when a row's three components
+    # differ (image tokens of the Qwen2-VL family); ``positions`` then holds the temporal one.
+    positions3: torch.Tensor | None = None
 
     @property
     def num_tokens(self) -> int:
@@ -216,6 +219,15 @@ class DecoderModel:
             kn = ref.head_rmsnorm(rot[:, self.Hq:], k_norm, cfg.rms_norm_eps)
             qkv = torch.cat([qn.to(qkv.dtype), kn.to(qkv.dtype), x3[:, nqk:]], dim=1).reshape(T0, -1).contiguous()
             q_norm = k_norm = None
+            rot_dim = 0
+        if b.positions3 is not None and rot_dim and cfg.extra.get("mrope_section"):
+            # rows with three different rotary positions: rotate here (each frequency takes the position
+            # of its section), the kernel only appends
+            from ..ops import reference as ref
+            T0, nqk = qkv.shape[0], self.Hq + self.Hkv
+            x3 = qkv.view(T0, self.Hq + 2 * self.Hkv, self.D)
+            rot = ref.apply_mrope(x3[:, :nqk], b.positions3, self.inv_freq, cfg.extra["mrope_section"], self.mscale)
+            qkv = torch.cat([rot.to(qkv.dtype), x3[:, nqk:]], dim=1).reshape(T0, -1).contiguous()
             rot_dim = 0
         use_win = window > 0 and b.slot_mapping_win is not None     # this layer's KV lives in the window pool
         ops.rope_append(qkv, b.positions, b.slot_mapping_win if use_win else b.slot_mapping,

@@ -1,0 +1,216 @@
+"""Qwen2-VL vision side: dynamic-resolution processor, vision transformer with 2-D rotary positions,
+patch merger, and the 3-D rotary positions of the language model's prompt
+(reference: src/vision/encoders/qwen2_vl*.rs, src/vision/processors/qwen2_vl*.rs, src/models/qwen2_vl.rs).
+
+An image is resized so both sides are multiples of ``patch * merge`` (28) inside a pixel budget, cut
+into 14 x 14 patches (the single frame is repeated over the temporal patch of 2), and the patches
+are ordered merge-window by merge-window so that every 2 x 2 neighbourhood is contiguous: the merger
+then folds 4 consecutive rows into one language-model token. The language model sees, per image, a
+grid of (h/2) x (w/2) tokens whose rotary positions are (t, row, col) offsets from the running text
+position; text after the image continues at ``max(position) + 1``.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from ..ops import recurrent as rops
+from .vlm import VisionLanguage, _sub
+
+
+def smart_resize(h: int, w: int, factor: int = 28, min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280):
+    """Both sides multiples of ``factor``, area within [min_pixels, max_pixels], aspect ratio kept."""
+    if max(h, w) / min(h, w) > 200:
+        raise ValueError("aspect ratio above 200 is not supported")
+    hb = max(factor, round(h / factor) * factor)
+    wb = max(factor, round(w / factor) * factor)
+    if hb * wb > max_pixels:
+        beta = math.sqrt((h * w) / max_pixels)
+        hb = max(factor, math.floor(h / beta / factor) * factor)
+        wb = max(factor, math.floor(w / beta / factor) * factor)
+    elif hb * wb < min_pixels:
+        beta = math.sqrt(min_pixels / (h * w))
+        hb = math.ceil(h * beta / factor) * factor
+        wb = math.ceil(w * beta / factor) * factor
+    return hb, wb
+
+
+class Qwen2ImageProcessor:
+    def __init__(self, cfg: dict | None = None, patch: int = 14, merge: int = 2, temporal: int = 2):
+        cfg = dict(cfg or {})
+        self.patch = int(cfg.get("patch_size", patch))
+        self.merge = int(cfg.get("merge_size", merge))
+        self.temporal = int(cfg.get("temporal_patch_size", temporal))
+        size = cfg.get("size") or {}
+        self.min_pixels = int(cfg.get("min_pixels", size.get("shortest_edge", 56 * 56)))
+        self.max_pixels = int(cfg.get("max_pixels", size.get("longest_edge", 28 * 28 * 1280)))
+        self.mean = np.asarray(cfg.get("image_mean", [0.48145466, 0.4578275, 0.40821073]), dtype=np.float32)
+        self.std = np.asarray(cfg.get("image_std", [0.26862954, 0.26130258, 0.27577711]), dtype=np.float32)
+
+    def __call__(self, images: list):
+        """PIL images → (patch rows float32 [sum gh*gw, C * temporal * patch * patch], grids [(1, gh, gw)])."""
+        from PIL import Image
+        p, m, tp = self.patch, self.merge, self.temporal
+        rows, grids = [], []
+        for img in images:
+            w, h = img.size
+            nh, nw = smart_resize(h, w, p * m, self.min_pixels, self.max_pixels)
+            a = np.asarray(img.resize((nw, nh), Image.Resampling.BICUBIC), dtype=np.float32) / 255.0
+            a = ((a - self.mean) / self.std).transpose(2, 0, 1)                 # [C, H, W]
+            a = np.repeat(a[None], tp, axis=0)                                  # the frame fills the temporal patch
+            gh, gw = nh // p, nw // p
+            C = a.shape[1]
+            x = a.reshape(1, tp, C, gh // m, m, p, gw // m, m, p)
+            x = x.transpose(0, 3, 6, 4, 7, 2, 1, 5, 8)                          # [1, gh/m, gw/m, m, m, C, tp, p, p]
+            rows.append(torch.from_numpy(np.ascontiguousarray(x.reshape(gh * gw, C * tp * p * p))))
+            grids.append((1, gh, gw))
+        return torch.cat(rows), grids
+
+
+class Qwen2VisionTower:
+    """Patch embedding → blocks (LayerNorm, attention with 2-D rotary positions restricted to the
+    image, quick-GELU MLP) → merger (LayerNorm, fold merge^2 rows, two linears with GELU)."""
+
+    def __init__(self, vc: dict, tensors: dict, dtype=torch.bfloat16, device="cpu"):
+        self.dtype, self.device = dtype, torch.device(device)
+        self.depth, self.dim, self.heads = int(vc["depth"]), int(vc["embed_dim"]), int(vc["num_heads"])
+        self.patch, self.merge = int(vc.get("patch_size", 14)), int(vc.get("spatial_merge_size", 2))
+        self.act = {"quick_gelu": "quick_gelu", "gelu": "gelu", "gelu_pytorch_tanh": "gelu_tanh"}.get(
+            vc.get("hidden_act", "quick_gelu"), "quick_gelu")
+
+        def t(n):
+            return tensors[n].to(dtype).to(self.device).contiguous()
+
+        pw = t("patch_embed.proj.weight")
+        self.patch_w = pw.reshape(pw.shape[0], -1).contiguous()
+        self.blocks = []
+        for i in range(self.depth):
+            b = f"blocks.{i}."
+            self.blocks.append({k: t(b + n) for k, n in dict(
+                n1w="norm1.weight", n1b="norm1.bias", wqkv="attn.qkv.weight", bqkv="attn.qkv.bias",
+                wo="attn.proj.weight", bo="attn.proj.bias", n2w="norm2.weight", n2b="norm2.bias",
+                w1="mlp.fc1.weight", b1="mlp.fc1.bias", w2="mlp.fc2.weight", b2="mlp.fc2.bias").items()})
+        self.ln_q = (t("merger.ln_q.weight"), t("merger.ln_q.bias"))
+        self.m1 = (t("merger.mlp.0.weight"), t("merger.mlp.0.bias"))
+        self.m2 = (t("merger.mlp.2.weight"), t("merger.mlp.2.bias"))
+        D = self.dim // self.heads
+        self.inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D // 2, 2, dtype=torch.float32) / (D // 2)))
+
+    def _rot_angles(self, grids) -> torch.Tensor:
+        """[rows, D/2] rotary angles: the first D/4 frequencies turn with the patch's row, the rest with
+        its column, rows listed in merge-window order."""
+        m, out = self.merge, []
+        for t_, gh, gw in grids:
+            hp = torch.arange(gh)[:, None].expand(gh, gw).reshape(gh // m, m, gw // m, m).permute(0, 2, 1, 3).flatten()
+            wp = torch.arange(gw)[None, :].expand(gh, gw).reshape(gh // m, m, gw // m, m).permute(0, 2, 1, 3).flatten()
+            ang = torch.cat([hp[:, None].float() * self.inv_freq[None], wp[:, None].float() * self.inv_freq[None]], dim=1)
+            out.append(ang.repeat(t_, 1))
+        return torch.cat(out)
+
+    @torch.no_grad()
+    def forward(self, rows: torch.Tensor, grids) -> torch.Tensor:
+        """``rows`` [R, C*tp*p*p] → [R / merge^2, text_hidden]."""
+        from ..models.vision import _act
+        x = ops.linear(rows.to(self.device, self.dtype).contiguous(), self.patch_w)
+        R, H, D = x.shape[0], self.heads, self.dim // self.heads
+        ang = self._rot_angles(grids).to(self.device)
+        cos = torch.cat([ang.cos(), ang.cos()], dim=1)[:, None, :]       # [R, 1, D]
+        sin = torch.cat([ang.sin(), ang.sin()], dim=1)[:, None, :]
+        sizes = [t_ * gh * gw for t_, gh, gw in grids]
+
+        def rot(v):            # [R, H, D] float32
+            half = D // 2
+            return v * cos + torch.cat([-v[..., half:], v[..., :half]], dim=-1) * sin
+        for b in self.blocks:
+            y = rops.layernorm(x, b["n1w"], b["n1b"], 1e-6)
+            qkv = ops.linear(y, b["wqkv"], bias=b["bqkv"]).view(R, 3, H, D)
+            q, k, v = rot(qkv[:, 0].float()), rot(qkv[:, 1].float()), qkv[:, 2].float()
+            outs, o0 = [], 0
+            for n in sizes:                                    # attention never crosses images
+                qi, ki, vi = (z[o0:o0 + n].transpose(0, 1)[None] for z in (q, k, v))
+                outs.append(F.scaled_dot_product_attention(qi, ki, vi)[0].transpose(0, 1).reshape(n, H * D))
+                o0 += n
+            a = torch.cat(outs).to(self.dtype).contiguous()
+            x = ops.linear(a, b["wo"], bias=b["bo"], residual=x)
+            y = rops.layernorm(x, b["n2w"], b["n2b"], 1e-6)
+            x = ops.linear(_act(ops.linear(y, b["w1"], bias=b["b1"]), self.act), b["w2"], bias=b["b2"], residual=x)
+        y = rops.layernorm(x, *self.ln_q, 1e-6).view(R // self.merge ** 2, self.dim * self.merge ** 2).contiguous()
+        y = rops.activation(ops.linear(y, *self.m1), "gelu")
+        return ops.linear(y, *self.m2)
+
+
+class Qwen2VisionLanguage(VisionLanguage):
+    def __init__(self, tower: Qwen2VisionTower, processor: Qwen2ImageProcessor, image_token_id: int, model_type: str):
+        super().__init__(tower, None, processor, image_token_id, model_type)
+
+    @torch.no_grad()
+    def encode_grids(self, images: list):
+        import time
+        t0 = time.perf_counter()
+        rows, grids = self.processor(images)
+        out = self.tower.forward(rows, grids)
+        m2 = self.tower.merge ** 2
+        parts, o = [], 0
+        for t_, gh, gw in grids:
+            n = t_ * gh * gw // m2
+            parts.append(out[o:o + n])
+            o += n
+        self.stats["images"] += len(images)
+        self.stats["image_tokens"] += int(out.shape[0])
+        self.stats["encode_seconds"] += time.perf_counter() - t0
+        return parts, grids
+
+    def encode(self, images: list) -> list[torch.Tensor]:
+        return self.encode_grids(images)[0] if images else []
+
+    def prepare(self, prompt_ids: list[int], images: list):
+        import hashlib
+        n_ph = sum(1 for t in prompt_ids if t == self.image_token_id)
+        if n_ph != len(images):
+            raise ValueError(f"the prompt has {n_ph} image placeholders for {len(images)} images")
+        parts, grids = self.encode_grids(images) if images else ([], [])
+        m = self.tower.merge
+        ids, keys, spans, pos = [], [], [], [[], [], []]
+        nxt, it = 0, iter(zip(parts, grids))                 # nxt: rotary position of the next text token
+        for t in prompt_ids:
+            if t != self.image_token_id:
+                ids.append(t)
+                keys.append(t)
+                for c in range(3):
+                    pos[c].append(nxt)
+                nxt += 1
+                continue
+            rows, (t_, gh, gw) = next(it)
+            lh, lw = gh // m, gw // m
+            n = int(rows.shape[0])
+            salt = int.from_bytes(hashlib.sha1(rows.detach().float().cpu().numpy().tobytes()).digest()[:4], "little")
+            spans.append((len(ids), rows))
+            ids += [self.image_token_id] * n
+            keys += [-(2 + ((salt + j) & 0x3FFFFFFF)) for j in range(n)]
+            for ti in range(t_):
+                for r in range(lh):
+                    for c in range(lw):
+                        pos[0].append(nxt + ti)
+                        pos[1].append(nxt + r)
+                        pos[2].append(nxt + c)
+            nxt += max(t_, lh, lw)
+        mm = dict(mm_embeds=spans, key_tokens=keys)
+        if images:
+            mm.update(rope_pos=np.asarray(pos, dtype=np.int32), rope_delta=nxt - len(ids))
+        return ids, mm
+
+
+def build_qwen2_vision(path, raw: dict, src, dtype, device) -> Qwen2VisionLanguage:
+    import json
+    from pathlib import Path
+    if raw.get("model_type") == "qwen2_5_vl":
+        raise ValueError("qwen2_5_vl: the windowed vision tower of Qwen2.5-VL is not built; Qwen2-VL checkpoints load")
+    tower = Qwen2VisionTower(raw["vision_config"], _sub(src, "model.visual.", "visual."), dtype, device)
+    f = Path(path) / "preprocessor_config.json"
+    proc = Qwen2ImageProcessor(json.loads(f.read_text()) if f.exists() else None, tower.patch, tower.merge,
+                               int(raw["vision_config"].get("temporal_patch_size", 2)))
+    return Qwen2VisionLanguage(tower, proc, raw.get("image_token_id", 151655), raw["model_type"])

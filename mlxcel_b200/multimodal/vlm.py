@@ -92,9 +92,9 @@ class VisionLanguage:
         return [rows[i] for i in range(rows.shape[0])]
 
     def prepare(self, prompt_ids: list[int], images: list):
-        """Returns ``(ids, spans, keys, extra)``: the prompt with every placeholder expanded,
-        ``spans = [(start, rows)]``, the key tokens for prefix hashing, and per-request extras for the
-        decoder (3-D rotary positions for the Qwen2-VL family; None otherwise)."""
+        """Returns ``(ids, mm)``: the prompt with every placeholder expanded and the keyword arguments
+        `Engine.add_request` takes for it — ``mm_embeds = [(start, rows)]``, ``key_tokens`` for prefix
+        hashing, and for the Qwen2-VL family ``rope_pos`` / ``rope_delta`` (3-D rotary positions)."""
         n_ph = sum(1 for t in prompt_ids if t == self.image_token_id)
         if n_ph != len(images):
             raise ValueError(f"the prompt has {n_ph} image placeholders for {len(images)} images")
@@ -112,4 +112,4 @@ class VisionLanguage:
             spans.append((len(ids), rows))
             ids += [self.image_token_id] * n
             keys += [-(2 + ((salt + j) & 0x3FFFFFFF)) for j in range(n)]
-        return ids, spans, keys, None
+        return ids, dict(mm_embeds=spans, key_tokens=keys)

@@ -151,6 +151,23 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
     return out * mscale
 
 
+def apply_mrope(x: torch.Tensor, positions3: torch.Tensor, inv_freq: torch.Tensor, sections, mscale: float = 1.0
+                ) -> torch.Tensor:
+    """Multimodal rotary embedding (Qwen2-VL): ``positions3`` [3, T] holds temporal / height / width
+    positions; frequency i of the head's D/2 takes the position of the section it falls in
+    (``sections`` = frequencies per component, e.g. [16, 24, 24]). Half-split (non-interleaved) layout.
+    x: [T, H, D] → rotated fp32 tensor."""
+    xf = x.float()
+    half = xf.shape[-1] // 2
+    which = torch.repeat_interleave(torch.arange(len(sections), device=xf.device),
+                                    torch.tensor(list(sections), device=xf.device))[:half]      # [half] -> 0/1/2
+    pos = positions3.float().to(xf.device)[which]                   # [half, T]
+    ang = pos.t() * inv_freq.float()[None, :half]                   # [T, half]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    a, b = xf[..., :half], xf[..., half:]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1) * mscale
+
+
 def head_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     xf = x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()

@@ -196,9 +196,8 @@ class ModelWorker:
                     raise ValueError("this model takes no image input")
                 if self.control is not None:
                     raise ValueError("image input needs a single-process server")
-                req.prompt_ids, spans, keys, _ = self.vision.prepare(req.prompt_ids, req.media)
+                req.prompt_ids, mm = self.vision.prepare(req.prompt_ids, req.media)
                 req.media = None
-                mm = dict(mm_embeds=spans, key_tokens=keys)
             sid = self.engine.add_request(req.prompt_ids, req.params, on_token=self._on_token, mask_fn=mask_fn,
                                           user_data=req, **mm)
         except Exception as e:

