@@ -98,7 +98,9 @@ class ViTTower:
 
         e = "embeddings."
         pw = t(e + "patch_embedding.weight")                     # [hidden, C, p, p]
-        self.patch_w = pw.reshape(pw.shape[0], -1).contiguous()   # one GEMM over unfolded patches
+        pw = pw.reshape(pw.shape[0], -1)                          # one GEMM over unfolded patches
+        self.k_pad = (-pw.shape[1]) % 8                           # the GEMM's TMA rows need 16-byte strides
+        self.patch_w = F.pad(pw, (0, self.k_pad)).contiguous()
         self.patch_b = t(e + "patch_embedding.bias", False)
         self.cls = t(e + "class_embedding", False)
         self.pos = t(e + "position_embedding.weight")
@@ -142,7 +144,8 @@ class ViTTower:
         gh, gw = H // p, W // p
         x = pixels.to(self.device, self.dtype)
         # unfold into [N * gh * gw, C * p * p] rows in the conv weight's (C, p, p) order
-        x = x.reshape(N, C, gh, p, gw, p).permute(0, 2, 4, 1, 3, 5).reshape(N * gh * gw, C * p * p).contiguous()
+        x = x.reshape(N, C, gh, p, gw, p).permute(0, 2, 4, 1, 3, 5).reshape(N * gh * gw, C * p * p)
+        x = F.pad(x, (0, self.k_pad)).contiguous()
         h = ops.linear(x, self.patch_w, bias=self.patch_b).view(N, gh * gw, c.hidden)
         if self.cls is not None:
             h = torch.cat([self.cls.view(1, 1, -1).expand(N, 1, -1), h], dim=1)

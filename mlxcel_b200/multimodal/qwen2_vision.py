@@ -86,7 +86,9 @@ class Qwen2VisionTower:
             return tensors[n].to(dtype).to(self.device).contiguous()
 
         pw = t("patch_embed.proj.weight")
-        self.patch_w = pw.reshape(pw.shape[0], -1).contiguous()
+        pw = pw.reshape(pw.shape[0], -1)
+        self.k_pad = (-pw.shape[1]) % 8                  # the GEMM's TMA rows need 16-byte strides
+        self.patch_w = F.pad(pw, (0, self.k_pad)).contiguous()
         self.blocks = []
         for i in range(self.depth):
             b = f"blocks.{i}."
@@ -115,7 +117,7 @@ class Qwen2VisionTower:
     def forward(self, rows: torch.Tensor, grids) -> torch.Tensor:
         """``rows`` [R, C*tp*p*p] → [R / merge^2, text_hidden]."""
         from ..models.vision import _act
-        x = ops.linear(rows.to(self.device, self.dtype).contiguous(), self.patch_w)
+        x = ops.linear(F.pad(rows.to(self.device, self.dtype), (0, self.k_pad)).contiguous(), self.patch_w)
         R, H, D = x.shape[0], self.heads, self.dim // self.heads
         ang = self._rot_angles(grids).to(self.device)
         cos = torch.cat([ang.cos(), ang.cos()], dim=1)[:, None, :]       # [R, 1, D]

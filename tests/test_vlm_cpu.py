@@ -78,13 +78,13 @@ def test_load_image_sources_and_refusals(tmp_path):
         load_image("not an image at all")
 
 
-def _tiny_llava():
+def _tiny_llava(hidden=64, heads=4, kv=2):
     from transformers import CLIPVisionConfig, LlamaConfig, LlavaConfig, LlavaForConditionalGeneration
     torch.manual_seed(0)
     vc = CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
                           image_size=28, patch_size=7)
-    tc = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
-                     num_key_value_heads=2, vocab_size=300, max_position_embeddings=256)
+    tc = LlamaConfig(hidden_size=hidden, intermediate_size=2 * hidden, num_hidden_layers=2, num_attention_heads=heads,
+                     num_key_value_heads=kv, vocab_size=300, max_position_embeddings=256)
     cfg = LlavaConfig(vision_config=vc, text_config=tc, image_token_index=IMG_TOKEN, vision_feature_layer=-2,
                       vision_feature_select_strategy="default", projector_hidden_act="gelu")
     m = LlavaForConditionalGeneration(cfg).eval()
@@ -207,14 +207,14 @@ def test_chat_route_takes_image_parts_and_equals_the_direct_run():
         worker.shutdown()
 
 
-def _tiny_qwen2_vl():
+def _tiny_qwen2_vl(hidden=64, heads=4, kv=2, sections=(2, 3, 3)):
     from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
     torch.manual_seed(0)
     cfg = Qwen2VLConfig(
-        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
-                         num_key_value_heads=2, vocab_size=300, max_position_embeddings=512,
-                         rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}),
-        vision_config=dict(depth=2, embed_dim=32, hidden_size=64, num_heads=4, mlp_ratio=2, patch_size=14,
+        text_config=dict(hidden_size=hidden, intermediate_size=2 * hidden, num_hidden_layers=2, num_attention_heads=heads,
+                         num_key_value_heads=kv, vocab_size=300, max_position_embeddings=512,
+                         rope_scaling={"type": "mrope", "mrope_section": list(sections)}),
+        vision_config=dict(depth=2, embed_dim=32, hidden_size=hidden, num_heads=4, mlp_ratio=2, patch_size=14,
                            spatial_merge_size=2, temporal_patch_size=2, in_channels=3),
         image_token_id=IMG_TOKEN, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
     m = Qwen2VLForConditionalGeneration(cfg).eval()
