@@ -729,7 +729,8 @@ def cmd_serve(a):
 
     from .server.app import ServerState, create_app
     from .server.worker import ModelWorker
-    if not _encoder_checkpoint(a.model):        # preflight: does model + KV pool + activations fit (src/commands/serve.rs)
+    from .audio.transcribe import is_whisper_checkpoint as _is_whisper
+    if not _encoder_checkpoint(a.model) and not _is_whisper(a.model):        # preflight: does model + KV pool + activations fit (src/commands/serve.rs)
         from .config import ModelConfig, preset
         from .utils.memory import estimate_memory
         cfg = (preset(a.model.split(":", 1)[1]) if a.model.startswith("preset:")
@@ -749,6 +750,17 @@ def cmd_serve(a):
                                  f"(--kv-bits 8), or pass --no-preflight")
             print(f"preflight: {a.parallel} sequences of {a.ctx_size} tokens would need {est['total_gib']} GiB; the paged KV "
                   f"pool takes what is free, long requests will queue", file=sys.stderr)
+    from .audio.transcribe import is_whisper_checkpoint
+    if is_whisper_checkpoint(a.model):          # speech-to-text checkpoints get the audio routes
+        import torch
+
+        from .audio.transcribe import Transcriber
+        from .server.audio import create_audio_app
+        dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        tr = Transcriber.from_pretrained(a.model, torch.bfloat16 if dev != "cpu" else torch.float32, dev)
+        app = create_audio_app(tr, a.alias or os.path.basename(a.model.rstrip("/")), set(a.api_key or []))
+        uvicorn.run(app, host=a.host, port=a.port, log_level="info" if a.verbose else "warning")
+        return
     if _encoder_checkpoint(a.model):            # encoder checkpoints get the embeddings-only server
         import torch
 
@@ -852,6 +864,22 @@ def cmd_router(a):
                             default=a.default_model,
                             engine_defaults=dict(ctx_size=a.ctx_size, parallel=a.parallel))
     uvicorn.run(app, host=a.host, port=a.port, log_level="info" if a.verbose else "warning")
+
+
+def cmd_transcribe(a):
+    """Speech to text for WAV files with a Whisper checkpoint."""
+    import torch
+
+    from .audio import decode_audio
+    from .audio.transcribe import Transcriber
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    tr = Transcriber.from_pretrained(a.model, torch.bfloat16 if dev != "cpu" else torch.float32, dev)
+    for f in a.files:
+        r = tr.transcribe(decode_audio(open(f, "rb").read()), language=a.language, task="translate" if a.translate else "transcribe")
+        if a.json:
+            print(json.dumps(dict(file=f, **{k: r[k] for k in ("text", "language", "duration")})))
+        else:
+            print(r["text"])
 
 
 def cmd_front(a):
@@ -1070,6 +1098,14 @@ def main(argv=None):
     p.add_argument("--api-key", action="append")
     p.add_argument("-v", "--verbose", action="store_true")
     p.set_defaults(fn=cmd_router)
+    p = sub.add_parser("transcribe", help="speech to text for WAV files (Whisper checkpoints)")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("files", nargs="+")
+    p.add_argument("--language", default=None, help="spoken language (default: detected from the first 30 s)")
+    p.add_argument("--translate", action="store_true", help="translate to English instead of transcribing")
+    p.add_argument("--device", default=None)
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_transcribe)
     p = sub.add_parser("front", help="one listener in front of data-parallel replicas or prefill/decode servers")
     p.add_argument("--replica-url", action="append", default=None, metavar="URL", help="a running server of the model (repeatable)")
     p.add_argument("--prefill-url", action="append", default=None, metavar="URL", help="prefill-role server (disaggregated serving)")
