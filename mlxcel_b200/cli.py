@@ -524,7 +524,7 @@ def cmd_run(a):
 
 def _encoder_checkpoint(path: str) -> bool:
     cj = os.path.join(path, "config.json")
-    return os.path.exists(cj) and json.load(open(cj)).get("model_type") in ("bert", "modernbert")
+    return os.path.exists(cj) and json.load(open(cj)).get("model_type") in ("bert", "modernbert", "deberta-v2")
 
 
 def cmd_embed(a):

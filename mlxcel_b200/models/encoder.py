@@ -262,9 +262,10 @@ class ModernBertEncoder:
 
 
 def load_encoder(path, dtype=torch.bfloat16, device="cpu"):
-    """The encoder class for a checkpoint's ``model_type`` (bert, modernbert)."""
+    """The encoder class for a checkpoint's ``model_type`` (bert, modernbert, deberta-v2)."""
     mt = json.loads((Path(path) / "config.json").read_text()).get("model_type")
-    cls = {"bert": BertEncoder, "modernbert": ModernBertEncoder}.get(mt)
+    from .deberta import DebertaV2Encoder
+    cls = {"bert": BertEncoder, "modernbert": ModernBertEncoder, "deberta-v2": DebertaV2Encoder}.get(mt)
     if cls is None:
         raise ValueError(f"unsupported encoder model_type {mt!r}")
     enc = cls.from_pretrained(path, dtype, device)

@@ -216,3 +216,31 @@ def test_bio_viterbi_repairs_invalid_paths():
     e[1, 2] = e[2, 3] = -0.4
     assert [bioes[i] for i in bio_viterbi(e, bioes)] in (["B-X", "I-X", "E-X"], ["S-X", "O", "O"], ["O", "O", "O"])
     assert bioes[bio_viterbi(e, bioes)[-1]] not in ("B-X", "I-X")
+
+
+@pytest.mark.parametrize("share,buckets", [(True, 8), (False, -1)])
+def test_deberta_v2_matches_transformers(share, buckets):
+    """Disentangled attention (content-to-position and position-to-content terms over log-bucketed
+    relative positions, shared or dedicated positional projections) and the cross-encoder head."""
+    import tempfile
+
+    from transformers import DebertaV2Config, DebertaV2ForSequenceClassification
+
+    from mlxcel_b200.models.encoder import load_encoder
+    torch.manual_seed(0)
+    hc = DebertaV2Config(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                         max_position_embeddings=64, relative_attention=True, pos_att_type=["p2c", "c2p"],
+                         share_att_key=share, position_buckets=buckets, norm_rel_ebd="layer_norm",
+                         position_biased_input=False, max_relative_positions=-1 if buckets > 0 else 32, num_labels=1)
+    m = DebertaV2ForSequenceClassification(hc).eval()
+    d = tempfile.mkdtemp(prefix="deberta_")
+    m.save_pretrained(d, safe_serialization=True)
+    enc = load_encoder(d, dtype=torch.float32)
+    ids = torch.randint(0, 300, (1, 37), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = m.deberta(ids).last_hidden_state[0]
+        want_logit = m(ids).logits[0]
+    assert (enc.hidden_states(ids[0].tolist()) - want).abs().max().item() < 1e-4
+    assert (enc.classify(ids[0].tolist()) - want_logit).abs().max().item() < 1e-4
+    v = enc.embed(ids[0].tolist())
+    assert abs(float(v.norm()) - 1.0) < 1e-5
