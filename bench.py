@@ -132,6 +132,10 @@ def main() -> None:
     ap.add_argument("--no-mtp", action="store_true", help="config 5 without the drafter (classic decoding)")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--tp-backend", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--ep-mode", default="replicated", choices=["replicated", "a2a"],
+                    help="config 4 on several GPUs: 'replicated' = tensor-parallel attention, tokens on every rank, "
+                         "experts sharded, all-reduce combine; 'a2a' = data-parallel attention (every rank serves "
+                         "requests / N of the batch), MoE rows exchanged by the dispatch / combine kernels")
     ap.add_argument("--watchdog", type=int, default=1500,
                     help="seconds without finishing a round before every thread's stack is dumped and the "
                          "process exits (a stuck multi-rank run then ends by itself)")
@@ -172,6 +176,7 @@ def main() -> None:
 
     comm = None
     pp = 1
+    dp = 1                      # data-parallel ranks (each serves requests / dp of the batch)
     if args.config == 5 and world > 1:
         pp = 2
     tp = world // pp
@@ -188,19 +193,27 @@ def main() -> None:
                 grp = dist.new_group(list(range(st * tp, (st + 1) * tp)))
                 if st == stage:
                     group = grp
-        if tp > 1:
+        if args.config == 4 and args.ep_mode == "a2a":
+            from mlxcel_b200.config import preset as _cp
+            from mlxcel_b200.parallel.dp_ep import DpEpComm
+            c4 = _cp(args.model)
+            comm = DpEpComm(group, dev, hidden=c4.hidden_size, top_k=c4.num_experts_per_tok, num_experts=c4.num_experts,
+                            max_tokens=8192)
+            dp = world
+            tp = 1
+        elif tp > 1:
             hidden = {"llama-3.1-8b": 4096, "qwen3-32b": 5120, "gpt-oss-120b": 2880}.get(args.model, 8192)
             comm = TPComm(group, dev, backend=args.tp_backend, hidden=max(4096, hidden), max_tokens=8192)
 
     max_len = args.prompt_len + args.output_len + 16
     chunk = preset["chunk"]
-    ecfg = EngineConfig(max_batch=args.requests, max_num_batched_tokens=8192,
+    ecfg = EngineConfig(max_batch=max(1, args.requests // dp), max_num_batched_tokens=8192,
                         prefill_chunk_alone=chunk or max(2048, args.prompt_len),
                         prefill_chunk_contended=chunk or max(512, args.prompt_len),
                         max_prefill_seqs=16 if chunk else 8,
                         block_size=16, kv_bits=args.kv_bits, prefix_cache=False,
                         max_model_len=max_len, cuda_graphs=not args.no_graphs,
-                        num_blocks=(max_len // 16 + 2) * args.requests + 64)
+                        num_blocks=(max_len // 16 + 2) * max(1, args.requests // dp) + 64)
     drafter_note = None
     if pp > 1:
         import torch.distributed as dist
@@ -250,10 +263,12 @@ def main() -> None:
 
     # Synthetic prompts live in pinned host memory; every engine step copies that step's token
     # ids / positions / slots / page tables host→device and reads the sampled tokens back.
-    g = torch.Generator().manual_seed(1234)
+    g = torch.Generator().manual_seed(1234 + (rank if dp > 1 else 0))
     vocab = llm.cfg.vocab_size
 
     def make_prompts(n_req: int) -> list[list[int]]:
+        if dp > 1:              # this rank's share of the batch
+            n_req = n_req // dp + (1 if rank < n_req % dp else 0)
         return torch.randint(0, vocab, (n_req, args.prompt_len), generator=g).tolist()
 
     def barrier():
@@ -324,6 +339,14 @@ def main() -> None:
             t = torch.tensor([dev_ms, wall_s], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dev_ms, wall_s = float(t[0]), float(t[1])
+            if dp > 1:          # every rank produced its own tokens: the job's output is their sum
+                c = torch.tensor([n_out, n_out2, launches, h2d, d2h], device=dev, dtype=torch.float64)
+                dist.all_reduce(c)
+                n_out, n_out2, launches, h2d, d2h = (float(v) for v in c)
+                gathered = [None] * world
+                dist.all_gather_object(gathered, (ttft, tpot))
+                ttft = [v for a, _ in gathered for v in a]
+                tpot = [v for _, b in gathered for v in b]
         return dict(value=n_out / (dev_ms / 1e3), ms_per_step=dev_ms / steps, e2e=n_out2 / wall_s, h2d=h2d, d2h=d2h,
                     launches=launches, clocks=clocks, spec=spec,
                     ttft=statistics.median(ttft) if ttft else None, tpot=statistics.median(tpot) if tpot else None)
@@ -348,6 +371,8 @@ def main() -> None:
         value = m["value"]
         if args.config == 5:
             par = f"tp{tp}xpp{pp}"
+        elif args.config == 4 and dp > 1:
+            par = f"dp{dp} attention + ep{dp} experts (all-to-all dispatch / combine)"
         elif args.config == 4:
             par = f"ep{args.gpus} (attention tp{args.gpus})"
         else:

@@ -110,6 +110,14 @@ class Engine:
             # no state to resume from, and the state slot indices change from step to step
             e.prefix_cache = e.cuda_graphs = e.lookahead = False
         self.pipeline = getattr(model, "ctx", None) is not None
+        # token-sharded expert parallelism (parallel/dp_ep.py): ticks are taken in lockstep with the
+        # other ranks; the lookahead pipeline (two forwards in flight) does not fit that
+        self.dp_lockstep = getattr(getattr(model, "comm", None), "a2a", None) is not None
+        self.dp_active = True
+        if self.dp_lockstep:
+            # a graph's capture runs one extra warm-up forward on this rank alone, which the other
+            # ranks' exchanges would wait for: steps are launched eagerly in this mode
+            e.lookahead = e.cuda_graphs = False
         if self.pipeline:
             # stages exchange activations with send / recv inside the forward pass: no graph capture,
             # and the token ids come back from the last stage, so nothing can be fed back on the device
@@ -779,7 +787,24 @@ class Engine:
                 return self._step()
         return self._step()
 
+    def _dp_step(self) -> list[Sequence]:
+        """One tick of a data-parallel rank whose MoE layers exchange rows with the other ranks: all
+        ranks run exactly one forward pass per tick in which anyone has work (a null forward here when
+        this rank has nothing scheduled), none when everybody is idle."""
+        self.dp_active = self.model.comm.any_work(self.has_work()) > 0
+        if not self.dp_active:
+            return []
+        decode, pieces = self._schedule() if self.has_work() else ([], [])
+        ended, self._evicted = self._evicted, []
+        if not decode and not pieces:
+            self.model.forward_null()
+            self.stats["null_forwards"] = self.stats.get("null_forwards", 0) + 1
+            return ended
+        return ended + self._run_scheduled(decode, pieces)
+
     def _step(self) -> list[Sequence]:
+        if self.dp_lockstep:
+            return self._dp_step()
         if self._inflight is not None:
             inf = self._inflight
             nxt = self._launch_lookahead(inf["seqs"], from_device=True) if self._can_pipeline(inf) else None
@@ -1038,6 +1063,13 @@ class Engine:
             params = [params or SamplingParams()] * len(prompts)
         media = media or [None] * len(prompts)
         ids = [self.add_request(p, sp, **(mm or {})) for p, sp, mm in zip(prompts, params, media)]
+        if self.dp_lockstep:
+            # ticks are collective: keep stepping (null forwards once this rank is done) until every
+            # rank has finished its own requests
+            while True:
+                self.step()
+                if not self.dp_active:
+                    break
         while self.has_work():
             self.step()
         return [self.seqs[i] for i in ids]

@@ -132,12 +132,13 @@ def shard_layer(cfg: ModelConfig, lw: LayerWeights, rank: int, tp: int, ep_rank:
 
 
 def shard_weights(cfg: ModelConfig, full: ModelWeights, rank: int, tp: int, *, ep: int | None = None,
-                  layers: range | None = None, vocab_parallel: bool = True) -> ModelWeights:
+                  layers: range | None = None, vocab_parallel: bool = True, ep_rank: int | None = None) -> ModelWeights:
     """Slice a full (unsharded) model for tensor-parallel rank ``rank`` of ``tp`` (experts are
     expert-parallel over the same ranks unless ``ep`` says otherwise) and pipeline layers ``layers``."""
     ep = tp if ep is None else ep
     idx = layers if layers is not None else range(len(full.layers))
-    lws = [shard_layer(cfg, full.layers[i], rank, tp, rank % ep, ep) for i in idx]
+    # ``ep_rank`` given: expert sharding independent of the tensor-parallel rank (data-parallel attention)
+    lws = [shard_layer(cfg, full.layers[i], rank, tp, rank % ep if ep_rank is None else ep_rank, ep) for i in idx]
     V = cfg.vocab_size
     lm_head = full.lm_head
     if vocab_parallel and tp > 1 and V % tp == 0:

@@ -321,6 +321,15 @@ class DecoderModel:
         from .moe import moe_forward
         return moe_forward(self.cfg, lw, x, h, self.comm)
 
+    def forward_null(self) -> None:
+        """A forward pass without tokens (token-sharded expert parallelism): only the exchanges of the
+        MoE layers run, so that the other ranks' rows are served."""
+        from .moe import moe_null
+        dev, dt = self.w.final_norm.device, self.w.final_norm.dtype
+        for lw in self.w.layers:
+            if lw.router_w is not None:
+                moe_null(self.cfg, lw, self.comm, dt, dev)
+
     # ------------------------------------------------------------------ forward
     def forward_hidden(self, b: StepBatch, kv_layers: list[KVLayer],
                        hidden_in: torch.Tensor | None = None) -> torch.Tensor:

@@ -23,6 +23,27 @@ def _dense(w):
     return w
 
 
+def _shared_expert(cfg, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+    si = lw.shared_gate_up.shape[0] // 2 if not isinstance(lw.shared_gate_up, QuantizedTensor) \
+        else lw.shared_gate_up.shape[-2] // 2
+    a = ops.glu_linear(x, _dense(lw.shared_gate_up), si, cfg.hidden_act)
+    s = ops.linear(a, _dense(lw.shared_down))
+    if lw.shared_gate is not None:
+        g = torch.sigmoid(ops.linear(x, lw.shared_gate).float())
+        s = (s.float() * g).to(s.dtype)
+    return s
+
+
+def moe_null(cfg, lw: LayerWeights, comm, dtype, device) -> None:
+    """This rank's part of a MoE layer when it has no tokens this tick: it sends nothing, serves the
+    rows the other ranks route to its experts, and reads nothing back."""
+    k, H = cfg.num_experts_per_tok, cfg.hidden_size
+    gu, dn = lw.experts_gate_up, lw.experts_down
+    comm.a2a.moe(torch.empty(0, H, dtype=dtype, device=device), torch.empty(0, k, dtype=torch.int32, device=device),
+                 torch.empty(0, k, dtype=torch.float32, device=device), gu, dn, gu.shape[-2] // 2, cfg.hidden_act,
+                 lw.experts_gate_up_b, lw.experts_down_b, residual=None, alpha=cfg.swiglu_alpha, limit=cfg.swiglu_limit)
+
+
 def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -> torch.Tensor:
     """Returns the new residual stream ``h + moe(x)`` (bf16 [T, H])."""
     if cfg.moe_route_mode == "sparsemixer":
@@ -37,6 +58,15 @@ def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -
     else:
         logits = ops.linear(x, lw.router_w, bias=lw.router_b)
         ids, wts = moe_ops.route(logits, cfg.num_experts_per_tok, cfg.moe_route_mode, cfg.norm_topk_prob)
+    a2a = getattr(comm, "a2a", None)
+    if a2a is not None:
+        # token-sharded ranks: rows travel to the experts' owners and come back (parallel/dp_ep.py)
+        gu, dn = lw.experts_gate_up, lw.experts_down
+        out = a2a.moe(x, ids.int().contiguous(), wts.float().contiguous(), gu, dn, gu.shape[-2] // 2, cfg.hidden_act,
+                      lw.experts_gate_up_b, lw.experts_down_b, residual=h, alpha=cfg.swiglu_alpha, limit=cfg.swiglu_limit)
+        if lw.shared_gate_up is not None:
+            out = (out.float() + _shared_expert(cfg, lw, x).float()).to(out.dtype)
+        return out
     ep, ep_rank = comm.ep_size, comm.ep_rank
     # packed expert weights stay packed: the grouped GEMM unpacks the tiles of routed experts only
     gate_up, down = lw.experts_gate_up, lw.experts_down
@@ -47,14 +77,7 @@ def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -
                               lw.experts_down_b, e_begin=ep_rank * El, residual=h if first else None,
                               alpha=cfg.swiglu_alpha, limit=cfg.swiglu_limit)
     if lw.shared_gate_up is not None:
-        si = lw.shared_gate_up.shape[0] // 2 if not isinstance(lw.shared_gate_up, QuantizedTensor) \
-            else lw.shared_gate_up.shape[-2] // 2
-        a = ops.glu_linear(x, _dense(lw.shared_gate_up), si, cfg.hidden_act)
-        s = ops.linear(a, _dense(lw.shared_down))
-        if lw.shared_gate is not None:
-            g = torch.sigmoid(ops.linear(x, lw.shared_gate).float())
-            s = (s.float() * g).to(s.dtype)
-        out = (out.float() + s.float()).to(out.dtype)
+        out = (out.float() + _shared_expert(cfg, lw, x).float()).to(out.dtype)
     if ep > 1:
         out = comm.all_reduce(out)
     return out
