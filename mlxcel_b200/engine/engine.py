@@ -165,6 +165,7 @@ class Engine:
         self._decode_ticks_since_grant = 0
         self._graphs: dict[tuple, tuple] = {}
         self.drafter = None          # speculative drafter (see mlxcel_b200.speculative)
+        self.d_drafts = self.h_drafts = None
         self.spec_k = 4              # block size K: K-1 draft tokens + 1 bonus token per round
         self._last_spec = self._spec_now = False
         self.spec_policy = None      # optional speculative.policy.SpecPolicy (adaptive on / off)
@@ -966,37 +967,42 @@ class Engine:
             pieces.append((s, s.total_len - 1, 1 + len(d)))
         b, R = self._build_batch([], pieces, drafts=drafts, all_rows=True)
         need_h = getattr(self.drafter, "needs_hidden", False)
+        walk = None
+        all_greedy = all(s.params.greedy for s in decode)
+        full = K > 1 and all(len(drafts[s.seq_id]) == K - 1 for s in decode)
         if self.pipeline:
             h = self.model.pipeline_hidden(b, self.kv_layers)
             logits = self.model.logits(h, b.logits_rows) if h is not None else None
             # argmax of every verify row on the last stage, shared with the other stages (R ints)
             target = self.model.share_ints(ops.argmax(logits).cpu().tolist() if logits is not None else None, (R,))
-            walk = None
+        elif self.is_cuda and all_greedy and full:
+            # every row carries a full block: argmax + accept walk on the device, and the host reads
+            # back two ints per row (accepted length, token at the first mismatch) instead of the
+            # K target tokens of every row. The whole verify pass (forward, LM head, walk) is one
+            # CUDA graph per (rows, K).
+            nd = len(decode)
+            if self.d_drafts is None or self.d_drafts.shape[1] != K - 1:
+                self.d_drafts = torch.zeros(self.ecfg.max_batch, K - 1, dtype=torch.int32, device=self.device)
+                self.h_drafts = torch.zeros(self.ecfg.max_batch, K - 1, dtype=torch.int32,
+                                            pin_memory=True)
+            self.h_drafts[:nd] = torch.tensor([drafts[s.seq_id] for s in decode], dtype=torch.int32)
+            self.d_drafts[:nd].copy_(self.h_drafts[:nd], non_blocking=True)
+            h, acc, nxt = self._verify_pass(b, nd, K)
+            walk = torch.stack([acc, nxt]).cpu().tolist()
+            self.stats["d2h_bytes"] += 8 * nd
         else:
             h = self.model.forward_hidden(b, self.kv_layers)
             logits = self.model.logits(h, b.logits_rows)
-        walk = None
-        all_greedy = all(s.params.greedy for s in decode)
-        if self.pipeline:
-            pass
-        elif not all_greedy:
-            # sampler-match: one draw per verify row with the owner's seed and the step it stands for
-            owners, offs = [], []
-            for s, _, cnt in pieces:
-                owners += [s] * cnt
-                offs += list(range(cnt))
-            target, _ = self.sampler.sample(logits, owners, step_offsets=offs)
-            self.stats["spec_sampled_rounds"] = self.stats.get("spec_sampled_rounds", 0) + 1
-        elif logits.is_cuda and K > 1 and all(len(drafts[s.seq_id]) == K - 1 for s in decode):
-            # every row carries a full block: argmax + accept walk on the device, and the host reads
-            # back two ints per row (accepted length, token at the first mismatch) instead of the
-            # K target tokens of every row
-            dt = torch.tensor([drafts[s.seq_id] for s in decode], dtype=torch.int32).to(logits.device, non_blocking=True)
-            _, acc, nxt = ops.spec_verify(logits.view(len(decode), K, logits.shape[-1]), dt)
-            walk = torch.stack([acc, nxt]).cpu().tolist()
-            self.stats["d2h_bytes"] += 8 * len(decode)
-        else:
-            target = ops.argmax(logits).cpu().tolist()
+            if not all_greedy:
+                # sampler-match: one draw per verify row with the owner's seed and the step it stands for
+                owners, offs = [], []
+                for s, _, cnt in pieces:
+                    owners += [s] * cnt
+                    offs += list(range(cnt))
+                target, _ = self.sampler.sample(logits, owners, step_offsets=offs)
+                self.stats["spec_sampled_rounds"] = self.stats.get("spec_sampled_rounds", 0) + 1
+            else:
+                target = ops.argmax(logits).cpu().tolist()
         self.stats["steps"] += 1
         self.stats["spec_rounds"] += 1
         finished, now, row0 = [], time.perf_counter(), 0
@@ -1053,6 +1059,41 @@ class Engine:
         for s in finished:
             self.drafter.release(s.seq_id)
         return finished
+
+    def _verify_pass(self, b: StepBatch, nd: int, K: int):
+        """Forward of ``nd`` verify blocks of ``K`` rows, LM head over every row and the accept walk
+        against ``d_drafts``; replayed from a CUDA graph per (nd, K) when graphs are on (the batch
+        lives in the engine's fixed device buffers, so a replay sees the current step's contents).
+        Returns (hidden [nd * K, H], accepted [nd], next token [nd])."""
+        V = None
+
+        def run():
+            h = self.model.forward_hidden(b, self.kv_layers)
+            logits = self.model.logits(h, b.logits_rows)
+            _, acc, nxt = ops.spec_verify(logits.view(nd, K, logits.shape[-1]), self.d_drafts[:nd])
+            return h, acc, nxt
+        if not self.ecfg.cuda_graphs or b.embeds is not None or b.positions3 is not None:
+            return run()
+        key = ("verify", nd, K)
+        ent = self._graphs.get(key)
+        if ent is None:
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                run()                       # warm-up outside capture (descriptor caches, lazy buffers)
+            torch.cuda.current_stream().wait_stream(side)
+            from ..ops import _lib
+            n0 = _lib.launches()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = run()
+            ent = (g, out, _lib.launches() - n0)
+            self._graphs[key] = ent
+        ent[0].replay()
+        self.stats["graph_replays"] += 1
+        self.stats["verify_graph_replays"] = self.stats.get("verify_graph_replays", 0) + 1
+        self.stats["graph_kernel_launches"] += ent[2]
+        return ent[1]
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams] | None = None,
