@@ -971,8 +971,11 @@ def arch_catalog() -> dict:
         if name == "gemma3":                     # the wrapper's text_config is the gemma3_text model
             how = "transformers logits (as gemma3_text)"
         fams.append(dict(name=name, executor=ex, checked_against=how))
-    return {"families": fams, "encoders": ["bert", "modernbert"], "quantization": ["affine", "mxfp4", "mxfp8", "fp8 (widened at load)"],
-            "kv_bits": [16, 8, 4], "parallelism": ["tp", "ep", "pp"]}
+    return {"families": fams, "encoders": ["bert", "modernbert", "deberta-v2"],
+            "vision_language": ["llava (clip / siglip tower)", "qwen2_vl"], "speech": ["whisper"],
+            "quantization": ["affine", "mxfp4", "mxfp8", "fp8 (widened at load)"],
+            "kv_bits": [16, 8, 4], "parallelism": ["tp", "ep (replicated tokens)", "dp attention + ep (all-to-all)", "pp", "tp x pp",
+                                                   "dp replicas (front)", "prefill / decode disaggregation (front)"]}
 
 
 def cmd_arch(a):
@@ -985,6 +988,7 @@ def cmd_arch(a):
     for f in cat["families"]:
         print(f"{f['name'].ljust(w)}  {f['executor']:<11}  {f['checked_against']}")
     print(f"encoders: {', '.join(cat['encoders'])}")
+    print(f"vision-language: {', '.join(cat['vision_language'])}; speech: {', '.join(cat['speech'])}")
     print(f"quantization: {', '.join(cat['quantization'])}; kv bits: {cat['kv_bits']}; parallelism: {', '.join(cat['parallelism'])}")
 
 
