@@ -157,6 +157,7 @@ def main() -> None:
     dist.init_process_group("nccl", device_id=dev)
     if mode == "ep":
         return ep_main(rank, world, dev)
+    os.environ.setdefault("MLXCEL_B200_NVLS_ONESHOT", "1")       # "fused_us" = everything through the switch
     comm = TPComm(dist.group.WORLD, dev, backend="fused", max_tokens=8192, hidden=4096, vocab=131072)
     assert comm.backend == "fused"
     # second channel set on the peer-store protocol, so that one run shows NVLS (multimem) beside it

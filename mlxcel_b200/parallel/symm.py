@@ -160,6 +160,16 @@ class FusedOps:
         self.logits_peer = heap.peer_ptrs(self.logits_off)
         self.logits_mc = heap.mc_ptr(self.logits_off)
         self.nvls = bool(heap.mc_base)
+        # Transport per algorithm. Two-shot (prefill-sized) reductions and the all-gather go through the
+        # switch: each byte leaves a GPU once (measured at 8 ranks, M = 8192: 290 us against 998 us with
+        # peer stores and 471 us for GEMM + NCCL). One-shot (decode-sized) reductions stay on peer
+        # stores: there every rank needs the whole sum, so in-switch reduction makes each GPU serve
+        # its partial to all requesters and moves more bytes than pushing it once per peer (measured at
+        # 8 ranks, M = 64: 42 us against 26 us; at 2 ranks 24 against 20).
+        # MLXCEL_B200_NVLS_ONESHOT=1 forces the switch for one-shot reductions too.
+        import os
+        self.nvls_two = self.nvls
+        self.nvls_one = self.nvls and os.environ.get("MLXCEL_B200_NVLS_ONESHOT", "0") == "1"
         torch.cuda.synchronize(heap.device)
         dist.barrier(group=heap.group)
 
@@ -195,7 +205,8 @@ class FusedOps:
         res = residual  # read locally by the reducing rank; may alias `out` (in-place update)
         if ssq_out is not None:
             assert mode == 1, "per-tile sums of squares come out of the one-shot epilogue only"
-        mc = dict(flags_mc=ch.flags_mc, recv_mc=ch.recv_mc, out_mc=self.h_mc) if self.nvls else {}
+        use_mc = self.nvls_one if mode == 1 else self.nvls_two
+        mc = dict(flags_mc=ch.flags_mc, recv_mc=ch.recv_mc, out_mc=self.h_mc) if use_mc else {}
         if qt is not None:
             # packed weights: dequantised by the kernel's transform warps (one-shot all-reduce only),
             # i.e. quantized GEMV/GEMM -> all-reduce in one kernel
@@ -230,7 +241,7 @@ class FusedOps:
         ws = _lib.workspace(x.device)
         out = self.hidden_buffer(M, N)
         ch = self.ch_qmv
-        mc = (ch.flags_mc or None, ch.recv_mc or None) if self.nvls else (None, None)
+        mc = (ch.flags_mc or None, ch.recv_mc or None) if self.nvls_one else (None, None)
         rc = lib.mx_qmv_allreduce(x.data_ptr(), qt.packed.data_ptr(), qt.scales.data_ptr(), _lib.ptr(qt.biases),
                                   out.data_ptr(), _lib.ptr(residual), _lib.ptr(bias), M, N, K, qt.bits, qt.group_size,
                                   _MODE_ID[qt.mode], x.stride(0), out.stride(0),
@@ -258,7 +269,7 @@ class FusedOps:
             if x.dim() != 2 or x.shape[0] > self.max_tokens or x.shape[1] > self.hidden:
                 raise ValueError("all_reduce shape exceeds the symmetric buffers")
             out = self.hidden_buffer(x.shape[0], x.shape[1])
-        mc = (ch.flags_mc, ch.recv_mc, self.h_mc) if self.nvls else (None, None, None)
+        mc = (ch.flags_mc, ch.recv_mc, self.h_mc) if (self.nvls_one if mode == 1 else self.nvls_two) else (None, None, None)
         rc = lib.mx_allreduce_comm(x.data_ptr(), _lib.ptr(residual), out.data_ptr(), n, mode, self.rank,
                                    self.world, ch.flags_peer, ch.recv_peer, self.h_peer, ch.ctl.data_ptr(),
                                    ch.expect.data_ptr(), self.world * stride, stride, ws.data_ptr(), _lib.stream(),

@@ -67,7 +67,8 @@ def _run(name: str, world: int, body: str, timeout: int = 600, nvls: bool = Fals
     with open(path, "w") as f:
         f.write(script)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", MLXCEL_B200_REQUIRE_FUSED="1",
-               MLXCEL_B200_NVLS="1" if nvls else "0")
+               MLXCEL_B200_NVLS="1" if nvls else "0",
+               MLXCEL_B200_NVLS_ONESHOT="1" if nvls else "0")     # the nvls variants cover the in-switch one-shot path too
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), path]
