@@ -166,6 +166,13 @@ def main() -> None:
         os.environ["MLXCEL_B200_NVLS"] = "0"
         comm_peer = TPComm(dist.group.WORLD, dev, backend="fused", max_tokens=8192, hidden=4096, vocab=131072)
         os.environ["MLXCEL_B200_NVLS"] = "1"
+    # third channel set whose one-shot limit is 8 rows: decode-sized cases then take the two-shot
+    # (reduce-scatter + broadcast through the switch) kernel, for comparison with the one-shot ones
+    fused_two = None
+    if comm.fused.nvls:
+        from mlxcel_b200.parallel.symm import FusedOps, SymmetricHeap
+        heap2 = SymmetricHeap(dist.group.WORLD, dev, FusedOps.required_bytes(world, 8192, 4096, 8 * 1024, small_m=8))
+        fused_two = FusedOps(heap2, 8192, 4096, 8 * 1024, small_m=8)
     nrep, ncopy = 16, 4
 
     def graph_time(fn):
@@ -214,6 +221,16 @@ def main() -> None:
             fused_peer = graph_time(lambda: [comm_peer.fused.gemm_allreduce(x, ws[i % ncopy], None, hb2)
                                              for i in range(nrep)])
 
+        two_shot = None
+        if fused_two is not None and M <= 256:
+            hb3 = fused_two.hidden_buffer(M, N)
+            hb3.zero_()
+            try:
+                two_shot = graph_time(lambda: [fused_two.gemm_allreduce(x, ws[i % ncopy], None, hb3) for i in range(nrep)])
+            except Exception as e:          # shape not covered by the two-shot kernel: report the rest
+                if rank == 0:
+                    print(f"two-shot at M={M} not measured: {e}", flush=True)
+
         def base():
             for i in range(nrep):
                 ops.linear(x, ws[i % ncopy], out=tmp)
@@ -228,6 +245,7 @@ def main() -> None:
             print(json.dumps(dict(case=name, world=world, M=M, N=N, K_per_rank=K, nvls=bool(comm.fused.nvls),
                                   fused_us=round(fused, 1),
                                   fused_peer_store_us=round(fused_peer, 1) if fused_peer is not None else None,
+                                  fused_two_shot_switch_us=round(two_shot, 1) if two_shot is not None else None,
                                   gemm_plus_nccl_us=round(nccl, 1), gemm_alone_us=round(alone, 1),
                                   roofline_us=round(roof, 1), fused_of_roofline=round(roof / fused, 2))), flush=True)
         if os.environ.get("MLXCEL_B200_GEMM_TRACE") == "1":
