@@ -59,12 +59,57 @@ def _pool(B, ctx, Hkv, D, bs=16):
     return kv, tab
 
 
-def attn_decode(B=64, ctx=1152, Hq=32, Hkv=8, D=128, reps=3):
-    kv, tab = _pool(B, ctx, Hkv, D)
+def _qpool(B, ctx, Hkv, D, bits, bs=16):
+    """Quantized pool (8- or 4-bit affine per 64 values): random codes, scales / offsets of plausible size."""
+    nbs = (ctx + bs - 1) // bs
+    nb = B * nbs + 8
+    shape = (nb, Hkv, bs, D if bits == 8 else D // 2)
+    k = torch.randint(0, 256, shape, dtype=torch.uint8, device=DEV)
+    v = torch.randint(0, 256, shape, dtype=torch.uint8, device=DEV)
+    meta = lambda: torch.stack([_bf(nb, Hkv, bs, D // 64, scale=0.01).abs() + 0.005,          # noqa: E731
+                                _bf(nb, Hkv, bs, D // 64, scale=0.5)], dim=-1).contiguous()
+    kv = KVLayer(k, v, meta(), meta(), bs, bits)
+    tab = torch.randperm(nb - 8, device=DEV)[: B * nbs].reshape(B, nbs).to(torch.int32)
+    return kv, tab
+
+
+def attn_decode(B=64, ctx=1152, Hq=32, Hkv=8, D=128, reps=3, bits=16):
+    """``bits`` 8 / 4: the quantized-KV variants of the decode kernel (positional argument 7)."""
+    kv, tab = _pool(B, ctx, Hkv, D) if bits == 16 else _qpool(B, ctx, Hkv, D, bits)
     cl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
     q = _bf(B, Hq * D)
     for _ in range(reps):
         ops.paged_decode(q, kv, tab, cl, Hq=Hq, Hkv=Hkv, D=D, scale=1 / math.sqrt(D), max_len=ctx)
+
+
+def attn_decode_kv(B=64, ctx=1152, Hq=32, Hkv=8, D=128):
+    """CUDA-event time of the decode kernel at 16 / 8 / 4-bit KV (L2 flushed between launches) with the
+    bytes each variant has to read: codes plus one bf16 scale and offset per 64 values."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+
+    def timeit(fn, n=10):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(n):
+            flush.zero_()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2]
+    cl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+    q = _bf(B, Hq * D)
+    for bits in (16, 8, 4):
+        kv, tab = _pool(B, ctx, Hkv, D) if bits == 16 else _qpool(B, ctx, Hkv, D, bits)
+        t = timeit(lambda: ops.paged_decode(q, kv, tab, cl, Hq=Hq, Hkv=Hkv, D=D, scale=1 / math.sqrt(D), max_len=ctx))
+        per_tok = Hkv * 2 * (D * bits // 8 + (0 if bits == 16 else D // 64 * 4))
+        by = B * ctx * per_tok
+        print(json.dumps(dict(op="attn_decode_kv", kv_bits=bits, B=B, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, us=round(t * 1e3, 1),
+                              mbytes=round(by / 1e6, 1), gbs=round(by / t / 1e6, 1))), flush=True)
 
 
 def attn_prefill(S=8, qlen=1024, Hq=32, Hkv=8, D=128, reps=2):

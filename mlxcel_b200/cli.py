@@ -32,6 +32,10 @@ def _add_model_args(p):
     p.add_argument("--dequantize", action="store_true", help="dequantize quantized checkpoints at load")
     p.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (launch with torch.distributed.run)")
     p.add_argument("--pp", type=int, default=1, help="pipeline stages; world size = tp * pp")
+    p.add_argument("--ep-mode", choices=["replicated", "a2a"], default="replicated",
+                   help="mixture-of-experts models on several processes: 'replicated' shards experts under --tp (tokens on "
+                        "every rank, all-reduce combine); 'a2a' makes every process a server of its own requests (port + "
+                        "rank) whose MoE layers exchange rows with the others (put `front` before them)")
     p.add_argument("--pp-layers", default=None, help="comma-separated layer counts per stage (default: equal split)")
     p.add_argument("--pp-micro-batches", type=int, default=2, help="micro-batches a step is cut into")
     p.add_argument("--draft-model", default=None)
@@ -184,9 +188,15 @@ def load_llm(a):
     if tp * pp > 1 and world != tp * pp:
         raise SystemExit(f"--tp {tp} --pp {pp} needs {tp * pp} processes: launch with "
                          f"`python -m torch.distributed.run --nproc-per-node {tp * pp} -m mlxcel_b200.cli ...`")
+    a._control_group = None
+    dp_ep = getattr(a, "ep_mode", "replicated") == "a2a"
+    if dp_ep and world > 1:
+        # data-parallel attention + expert-parallel MoE: every rank is a server of its own (own listener,
+        # own requests), the ranks only share the routed experts
+        dev, _ = init_distributed(dev)
+        return _load_dp_ep(a, dev, ecfg_args=None)
     if world > 1 and tp * pp == 1:
         raise SystemExit(f"{world} processes were launched but neither --tp nor --pp was given")
-    a._control_group = None
     if world > 1:
         dev, a._control_group = init_distributed(dev)
     ecfg = EngineConfig(max_batch=a.parallel, max_num_batched_tokens=a.max_batch_tokens,
@@ -217,6 +227,45 @@ def load_llm(a):
         eng = llm.engine
         key = f"{a.model}|{type(eng.drafter).__name__}|K{eng.spec_k}|{dev}"
         eng.spec_policy = SpecPolicy(key=key)
+    return llm
+
+
+def _load_dp_ep(a, dev, ecfg_args=None):
+    """One rank of ``serve --ep-mode a2a`` under ``torch.distributed.run``: a complete engine for this
+    rank's own requests whose MoE layers exchange rows with the other ranks (parallel/dp_ep.py)."""
+    import torch
+    import torch.distributed as dist
+
+    from .config import ModelConfig, preset
+    from .engine import EngineConfig
+    from .llm import LLM
+    from .loading.checkpoint import _to_device, load_full_weights
+    from .loading.shard import shard_weights
+    from .parallel.dp_ep import DpEpComm
+    rank, world = dist.get_rank(), dist.get_world_size()
+    is_preset = a.model.startswith("preset:")
+    cfg = preset(a.model.split(":", 1)[1]) if is_preset else ModelConfig.from_path(a.model, config_overrides(a))
+    if not cfg.is_moe:
+        raise SystemExit("--ep-mode a2a needs a mixture-of-experts model")
+    ecfg = EngineConfig(max_batch=a.parallel, max_num_batched_tokens=a.max_batch_tokens,
+                        prefill_chunk_alone=a.prefill_chunk_size, prefill_chunk_contended=min(512, a.prefill_chunk_size),
+                        block_size=a.block_size, kv_bits=a.kv_bits or 16, num_blocks=a.kv_cache_blocks,
+                        prefix_cache=not a.no_prompt_cache, max_model_len=a.ctx_size, cuda_graphs=False)
+    comm = DpEpComm(dist.group.WORLD, dev, hidden=cfg.hidden_size, top_k=cfg.num_experts_per_tok,
+                    num_experts=cfg.num_experts, max_tokens=a.max_batch_tokens)
+    if is_preset:
+        from .models.weights import random_weights
+        from .tokenizer import ByteTokenizer
+        dtype = torch.bfloat16 if str(dev) != "cpu" else torch.float32
+        full = random_weights(cfg, seed=0, dtype=dtype)          # the same weights on every rank, then sharded
+        w = _to_device(shard_weights(cfg, full, 0, 1, ep=world, ep_rank=rank, vocab_parallel=False), dev)
+        llm = LLM(cfg, w, ecfg, comm=comm, tokenizer=ByteTokenizer(cfg.vocab_size))
+    else:
+        from .tokenizer import load_tokenizer
+        full = load_full_weights(a.model, cfg, dequantize=a.dequantize, surgery=getattr(a, "surgery", None))
+        w = _to_device(shard_weights(cfg, full, 0, 1, ep=world, ep_rank=rank, vocab_parallel=False), dev)
+        llm = LLM(cfg, w, ecfg, comm=comm, tokenizer=load_tokenizer(a.model))
+    a.port = a.port + rank                      # one listener per rank; `front` balances over them
     return llm
 
 

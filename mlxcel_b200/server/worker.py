@@ -416,9 +416,14 @@ class ModelWorker:
 
     def _loop(self) -> None:
         can_sleep = self.sleep_idle > 0 and self.engine_factory is not None and self.control is None
+        # data-parallel ranks that share experts tick together: this worker steps even without work of
+        # its own (its engine then runs a null forward for the others), and idles briefly when no rank
+        # has any
+        dp = self._engine is not None and getattr(self._engine, "dp_lockstep", False)
+        can_sleep = can_sleep and not dp
         while self.running:
             eng = self._engine
-            items = self._drain(block=eng is None or not eng.has_work())
+            items = self._drain(block=not dp and (eng is None or not eng.has_work()))
             if items:
                 self._last_activity = time.monotonic()
                 if eng is None and not all(isinstance(i, tuple) and i[0] == "stop" for i in items):
@@ -433,7 +438,11 @@ class ModelWorker:
             elif not self._apply_local(items):
                 return
             eng = self._engine
-            if eng is not None and eng.has_work():
+            if dp:
+                self._step_once()
+                if not eng.dp_active:
+                    time.sleep(0.002)
+            elif eng is not None and eng.has_work():
                 self._step_once()
                 self._last_activity = time.monotonic()
 

@@ -87,3 +87,62 @@ def test_dp_ep_ranks_match_the_single_process_engine(world):
     assert all(got[r][3] > 0 for r in range(world))
     if world == 4:
         assert got[2][2] == got[2][1] - 1           # the rank without requests ran a null forward in every working tick
+
+
+def test_serve_ep_mode_a2a_gives_every_rank_its_own_listener():
+    """`torch.distributed.run ... serve --ep-mode a2a`: rank r listens on port + r, serves its own requests,
+    and the text equals what a single-process server of the same preset answers."""
+    import json
+    import signal
+    import socket
+    import subprocess
+    import time
+    import urllib.request
+
+    def free_port():
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            return s.getsockname()[1]
+
+    def ask(port, prompt):
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions",
+                                     data=json.dumps({"prompt": prompt, "max_tokens": 8, "temperature": 0, "ignore_eos": True}).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return json.loads(r.read())["choices"][0]["text"]
+
+    def wait_up(port, proc):
+        for _ in range(600):
+            if proc.poll() is not None:
+                raise AssertionError(f"server exited with {proc.returncode}")
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                    if r.status == 200:
+                        return
+            except OSError:
+                time.sleep(0.5)
+        raise AssertionError("server did not come up")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    common = ["-m", "preset:tiny-gpt-oss", "--device", "cpu", "--no-warmup", "-c", "256", "--no-preflight"]
+    p1 = free_port()
+    single = subprocess.Popen([sys.executable, "-m", "mlxcel_b200.cli", "serve", *common, "--port", str(p1)], env=env)
+    base = free_port()
+    duo = subprocess.Popen([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                            "--master-addr", "127.0.0.1", "--master-port", str(free_port()), "-m", "mlxcel_b200.cli",
+                            "serve", *common, "--ep-mode", "a2a", "--port", str(base)], env=env, start_new_session=True)
+    try:
+        wait_up(p1, single)
+        wait_up(base, duo)
+        wait_up(base + 1, duo)
+        want = [ask(p1, "hello there"), ask(p1, "another prompt, longer than the first one")]
+        assert ask(base, "hello there") == want[0]
+        assert ask(base + 1, "another prompt, longer than the first one") == want[1]
+        assert ask(base + 1, "hello there") == want[0]
+    finally:
+        single.terminate()
+        os.killpg(duo.pid, signal.SIGTERM)
+        for p in (single, duo):
+            try:
+                p.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                p.kill()
