@@ -145,6 +145,100 @@ class Qwen2VisionTower:
         return ops.linear(y, *self.m2)
 
 
+class Qwen25VisionTower:
+    """Qwen2.5-VL tower: the Qwen2-VL layout with RMSNorm, a SwiGLU MLP and *windowed* attention. The
+    merged-token groups (merge x merge patches) of an image are reordered window by window
+    (``window_size`` pixels per side); most blocks attend inside a window, the blocks listed in
+    ``fullatt_block_indexes`` over the whole image; the merger's output is put back into raster
+    order (reference: src/vision/encoders/qwen2_5_vl*.rs)."""
+
+    def __init__(self, vc: dict, tensors: dict, dtype=torch.bfloat16, device="cpu"):
+        self.dtype, self.device = dtype, torch.device(device)
+        self.depth, self.dim, self.heads = int(vc["depth"]), int(vc["hidden_size"]), int(vc["num_heads"])
+        self.patch, self.merge = int(vc.get("patch_size", 14)), int(vc.get("spatial_merge_size", 2))
+        self.window = int(vc.get("window_size", 112))
+        self.full_blocks = set(int(i) for i in vc.get("fullatt_block_indexes", [7, 15, 23, 31]))
+        self.act = {"silu": "silu", "gelu": "gelu", "gelu_pytorch_tanh": "gelu_tanh"}.get(vc.get("hidden_act", "silu"), "silu")
+
+        def t(n):
+            return tensors[n].to(dtype).to(self.device).contiguous()
+
+        pw = t("patch_embed.proj.weight")
+        pw = pw.reshape(pw.shape[0], -1)
+        self.k_pad = (-pw.shape[1]) % 8
+        self.patch_w = F.pad(pw, (0, self.k_pad)).contiguous()
+        self.blocks = []
+        for i in range(self.depth):
+            b = f"blocks.{i}."
+            blk = {k: t(b + n) for k, n in dict(
+                n1="norm1.weight", wqkv="attn.qkv.weight", bqkv="attn.qkv.bias", wo="attn.proj.weight", bo="attn.proj.bias",
+                n2="norm2.weight", wd="mlp.down_proj.weight", bd="mlp.down_proj.bias").items()}
+            blk["wgu"] = torch.cat([t(b + "mlp.gate_proj.weight"), t(b + "mlp.up_proj.weight")]).contiguous()
+            blk["bgu"] = torch.cat([t(b + "mlp.gate_proj.bias"), t(b + "mlp.up_proj.bias")]).contiguous()
+            self.blocks.append(blk)
+        self.ln_q = t("merger.ln_q.weight")
+        self.m1 = (t("merger.mlp.0.weight"), t("merger.mlp.0.bias"))
+        self.m2 = (t("merger.mlp.2.weight"), t("merger.mlp.2.bias"))
+        D = self.dim // self.heads
+        self.inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D // 2, 2, dtype=torch.float32) / (D // 2)))
+
+    _rot_angles = Qwen2VisionTower._rot_angles
+
+    def _windows(self, grids):
+        """Order of the merged-token groups (window by window) and the group count of every window."""
+        ws = self.window // self.merge // self.patch
+        order, sizes, base = [], [], 0
+        for t_, gh, gw in grids:
+            lh, lw = gh // self.merge, gw // self.merge
+            idx = torch.arange(t_ * lh * lw).reshape(t_, lh, lw)
+            for ti in range(t_):
+                for r0 in range(0, lh, ws):
+                    for c0 in range(0, lw, ws):
+                        win = idx[ti, r0:r0 + ws, c0:c0 + ws].reshape(-1)
+                        order.append(win + base)
+                        sizes.append(int(win.numel()))
+            base += t_ * lh * lw
+        return torch.cat(order), sizes
+
+    @torch.no_grad()
+    def forward(self, rows: torch.Tensor, grids) -> torch.Tensor:
+        from ..models.vision import _act
+        x = ops.linear(F.pad(rows.to(self.device, self.dtype), (0, self.k_pad)).contiguous(), self.patch_w)
+        R, H, D = x.shape[0], self.heads, self.dim // self.heads
+        unit = self.merge ** 2
+        order, win_groups = self._windows(grids)
+        order = order.to(self.device)
+        x = x.view(R // unit, unit, self.dim)[order].reshape(R, self.dim).contiguous()
+        ang = self._rot_angles(grids).to(self.device).view(R // unit, unit, -1)[order].reshape(R, -1)
+        cos = torch.cat([ang.cos(), ang.cos()], dim=1)[:, None, :]
+        sin = torch.cat([ang.sin(), ang.sin()], dim=1)[:, None, :]
+        full_sizes = [gh * gw for t_, gh, gw in grids for _ in range(t_)]
+        win_sizes = [g * unit for g in win_groups]
+
+        def rot(v):
+            half = D // 2
+            return v * cos + torch.cat([-v[..., half:], v[..., :half]], dim=-1) * sin
+        for li, b in enumerate(self.blocks):
+            y = ops.rmsnorm(x, b["n1"], 1e-6, 0.0)
+            qkv = ops.linear(y, b["wqkv"], bias=b["bqkv"]).view(R, 3, H, D)
+            q, k, v = rot(qkv[:, 0].float()), rot(qkv[:, 1].float()), qkv[:, 2].float()
+            outs, o0 = [], 0
+            for n in (full_sizes if li in self.full_blocks else win_sizes):
+                qi, ki, vi = (z[o0:o0 + n].transpose(0, 1)[None] for z in (q, k, v))
+                outs.append(F.scaled_dot_product_attention(qi, ki, vi)[0].transpose(0, 1).reshape(n, H * D))
+                o0 += n
+            a = torch.cat(outs).to(self.dtype).contiguous()
+            x = ops.linear(a, b["wo"], bias=b["bo"], residual=x)
+            y = ops.rmsnorm(x, b["n2"], 1e-6, 0.0)
+            gu = ops.linear(y, b["wgu"], bias=b["bgu"])
+            inter = gu.shape[1] // 2
+            u = (_act(gu[:, :inter].contiguous(), self.act).float() * gu[:, inter:].float()).to(self.dtype)
+            x = ops.linear(u.contiguous(), b["wd"], bias=b["bd"], residual=x)
+        y = ops.rmsnorm(x, self.ln_q, 1e-6, 0.0).view(R // unit, self.dim * unit).contiguous()
+        y = ops.linear(rops.activation(ops.linear(y, *self.m1), "gelu"), *self.m2)
+        return y[torch.argsort(order)]
+
+
 class Qwen2VisionLanguage(VisionLanguage):
     def __init__(self, tower: Qwen2VisionTower, processor: Qwen2ImageProcessor, image_token_id: int, model_type: str):
         super().__init__(tower, None, processor, image_token_id, model_type)
@@ -209,9 +303,8 @@ class Qwen2VisionLanguage(VisionLanguage):
 def build_qwen2_vision(path, raw: dict, src, dtype, device) -> Qwen2VisionLanguage:
     import json
     from pathlib import Path
-    if raw.get("model_type") == "qwen2_5_vl":
-        raise ValueError("qwen2_5_vl: the windowed vision tower of Qwen2.5-VL is not built; Qwen2-VL checkpoints load")
-    tower = Qwen2VisionTower(raw["vision_config"], _sub(src, "model.visual.", "visual."), dtype, device)
+    cls = Qwen25VisionTower if raw.get("model_type") == "qwen2_5_vl" else Qwen2VisionTower
+    tower = cls(raw["vision_config"], _sub(src, "model.visual.", "visual."), dtype, device)
     f = Path(path) / "preprocessor_config.json"
     proc = Qwen2ImageProcessor(json.loads(f.read_text()) if f.exists() else None, tower.patch, tower.merge,
                                int(raw["vision_config"].get("temporal_patch_size", 2)))

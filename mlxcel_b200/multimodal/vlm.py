@@ -8,7 +8,7 @@ those, so two requests share cached KV blocks only when text AND images are the 
 (the reference's placeholder expansion and media hashing: src/multimodal/prompt*.rs,
 src/multimodal/runtime*.rs).
 
-Supported wrappers: ``llava`` (CLIP or SigLIP tower, two-layer MLP connector) and ``qwen2_vl`` /
+Supported wrappers: ``llava`` (CLIP or SigLIP tower, two-layer MLP connector), ``qwen2_vl`` and
 ``qwen2_5_vl`` (see `qwen2_vision.py`). The language model is loaded by the ordinary decoder loader
 from the same checkpoint (its tensors live under ``language_model``).
 """

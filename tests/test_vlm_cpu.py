@@ -274,3 +274,45 @@ def test_qwen2_vl_greedy_matches_transformers_through_the_engine():
         p2 = eng.seqs[side].prompt
         want_side = m.generate(input_ids=torch.tensor([p2]), max_new_tokens=8, do_sample=False)[0, len(p2):].tolist()
     assert eng.seqs[side].output == want_side
+
+
+def test_qwen2_5_vl_windowed_tower_and_greedy_match_transformers():
+    from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+
+    from mlxcel_b200.multimodal.qwen2_vision import Qwen2ImageProcessor
+    torch.manual_seed(0)
+    cfg = Qwen2_5_VLConfig(
+        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, vocab_size=300, max_position_embeddings=512,
+                         rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}),
+        vision_config=dict(depth=3, hidden_size=32, out_hidden_size=64, num_heads=4, intermediate_size=48, patch_size=14,
+                           spatial_merge_size=2, temporal_patch_size=2, in_channels=3, window_size=56,
+                           fullatt_block_indexes=[1]),
+        image_token_id=IMG_TOKEN, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    m = Qwen2_5_VLForConditionalGeneration(cfg).eval()
+    d = tempfile.mkdtemp(prefix="vlm_qwen25vl_")
+    m.save_pretrained(d, safe_serialization=True)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    vl.processor = Qwen2ImageProcessor(dict(min_pixels=56 * 56, max_pixels=28 * 28 * 36))
+    imgs = [_image(5, 150, 100), _image(6, 60, 170)]          # grids that do not divide into whole windows
+    rows, grids = vl.processor(imgs)
+    with torch.no_grad():
+        want_feats = m.model.visual(rows, grid_thw=torch.tensor(grids)).pooler_output
+    got_feats = torch.cat(vl.encode(imgs))
+    assert got_feats.shape == want_feats.shape and (got_feats - want_feats).abs().max().item() < 1e-4
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [292, IMG_TOKEN, 293] + text(7) + [292, IMG_TOKEN, 293] + text(4)
+    ids, mm = vl.prepare(prompt, imgs)
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=rows, image_grid_thw=torch.tensor(grids),
+                          mm_token_type_ids=torch.tensor([[int(t == IMG_TOKEN) for t in ids]]),
+                          max_new_tokens=8, do_sample=False)[0, len(ids):].tolist()
+    c = ModelConfig.from_path(d)
+    w = load_full_weights(d, c, dtype=torch.float32)
+    eng = Engine(DecoderModel(c, w), c, EngineConfig(max_batch=2, max_num_batched_tokens=64, num_blocks=32, max_model_len=256,
+                                                     cuda_graphs=False, prefill_chunk_alone=24, prefill_chunk_contended=24))
+    sid = eng.add_request(ids, SamplingParams(max_tokens=8, ignore_eos=True), **mm)
+    while eng.has_work():
+        eng.step()
+    assert eng.seqs[sid].output == want
