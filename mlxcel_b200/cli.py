@@ -395,10 +395,40 @@ def attach_drafter(llm, a, dev) -> None:
                                     max_model_len=eng.ecfg.max_model_len)
 
 
+def _generate_diffusion(a, llm, tk, prompt: str) -> None:
+    """``generate --diffusion``: block-unmasking decoding of a masked-diffusion checkpoint (engine/diffusion.py)."""
+    from .engine.diffusion import DiffusionGenerator, DiffusionOptions
+    mask_id = a.mask_token_id
+    if mask_id is None:
+        mask_id = (getattr(tk, "special", None) or {}).get("<|mask|>", llm.cfg.extra.get("mask_token_id"))
+    if mask_id is None:
+        raise SystemExit("--diffusion needs --mask-token-id (the tokenizer names no <|mask|> token)")
+    if a.chat:
+        from .server.chat_template import render_chat
+        prompt = render_chat([{"role": "user", "content": prompt}], getattr(tk, "chat_template", None))
+    ids = tk.encode(prompt, add_special_tokens=not a.chat)
+    sp = _sampling(a)
+    gen = DiffusionGenerator(llm.model, llm.cfg, mask_id, max_len=min(a.ctx_size, len(ids) + sp.max_tokens + 2 * a.block_length))
+    t0 = time.perf_counter()
+
+    def show(block):
+        sys.stdout.write(tk.decode(block))
+        sys.stdout.flush()
+    out = gen.generate(ids, DiffusionOptions(max_new_tokens=sp.max_tokens, block_length=a.block_length, steps=a.diffusion_steps,
+                                             threshold=a.diffusion_threshold, min_threshold=a.diffusion_threshold,
+                                             temperature=sp.temperature, eos_token_ids=[i for i in tk.eos_ids() if i is not None],
+                                             seed=sp.seed or 0), on_block=show)
+    dt = time.perf_counter() - t0
+    print(f"\n[{len(out)} tokens in {gen.stats['blocks']} blocks, {gen.stats['forwards']} forward passes, "
+          f"{len(out) / max(dt, 1e-9):.1f} tok/s]", file=sys.stderr)
+
+
 def cmd_generate(a):
     llm = load_llm(a)
     tk = llm.tokenizer
     prompt = a.prompt if a.prompt is not None else sys.stdin.read()
+    if getattr(a, "diffusion", False):
+        return _generate_diffusion(a, llm, tk, prompt)
     mm = {}
     if getattr(a, "image", None):
         vision = getattr(llm, "vision", None)
@@ -1092,6 +1122,12 @@ def main(argv=None):
     p.add_argument("-j", "--json-schema", default=None, help="JSON schema constraining the output ('{}' for any object)")
     p.add_argument("-jf", "--json-schema-file", default=None)
     p.add_argument("--regex", default=None, help="regular expression constraining the output")
+    p.add_argument("--diffusion", action="store_true",
+                   help="block-unmasking decoding for masked-diffusion checkpoints (LLaDA-style) instead of next-token decoding")
+    p.add_argument("--mask-token-id", type=int, default=None)
+    p.add_argument("--block-length", type=int, default=32)
+    p.add_argument("--diffusion-steps", type=int, default=32)
+    p.add_argument("--diffusion-threshold", type=float, default=0.95)
     p.add_argument("--image", action="append", default=None, metavar="FILE",
                    help="image for a vision-language checkpoint (repeatable; one per placeholder, or placed before the prompt)")
     p.set_defaults(fn=cmd_generate)
