@@ -440,7 +440,61 @@ def mamba2(engine_run=1):
                           steps=llm.engine.stats["steps"])), flush=True)
 
 
-CASES = dict(mamba2=mamba2, qgemm_decode=qgemm_decode, qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
+def moe_decode(T=128, E=128, k=4, H=2880, inter=2880, reps=0):
+    """One gpt-oss-120b shaped MoE block at decode (T rows, top-k of E mxfp4 experts): the grouped
+    weight-streaming GEMV against the tensor-core grouped GEMM with unpack warps, both in a CUDA graph
+    of 8 launches over 4 rotating weight copies (CUDA events around the replay, median of 7).
+    ``reps`` > 0: just run the GEMV path that many times (for a profiler capture)."""
+    import os
+
+    from mlxcel_b200.models.weights import QuantizedTensor
+    from mlxcel_b200.ops import moe as moe_ops
+
+    def rand_q(n_rows, kdim):
+        packed = torch.randint(0, 2 ** 31 - 1, (E, n_rows, kdim // 8), dtype=torch.int32, device=DEV).view(torch.uint32)
+        scales = torch.randint(118, 124, (E, n_rows, kdim // 32), dtype=torch.uint8, device=DEV)
+        return QuantizedTensor(packed, scales, None, 4, 32, "mxfp4")
+    ncopy = 1 if reps else 4
+    wgu = [rand_q(2 * inter, H) for _ in range(ncopy)]
+    wd = [rand_q(H, inter) for _ in range(ncopy)]
+    x = _bf(T, H)
+    ids, wts = moe_ops.route(_bf(T, E), k, "topk_softmax", True)
+    bgu, bd = _bf(E, 2 * inter, scale=0.1), _bf(E, H, scale=0.1)
+    run = lambda i: moe_ops.moe_experts(x, ids, wts, wgu[i % ncopy], wd[i % ncopy], inter, "clipped_swiglu", bgu, bd)  # noqa: E731
+    if reps:
+        for i in range(reps):
+            run(i)
+        return
+    packed_bytes = E * (2 * inter * H + H * inter) // 2 * 33 // 32
+
+    def graph_us(n=8):
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            for i in range(2):
+                run(i)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                for i in range(n):
+                    run(i)
+        ts = []
+        for _ in range(7):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[3] * 1e3 / n
+    for label, limit in (("gemv", 1 << 20), ("tensor_core_gemm", 0)):
+        moe_ops._QGEMV_MAX_ROWS = limit
+        us = graph_us()
+        print(json.dumps(dict(op="moe_decode", path=label, T=T, E=E, k=k, H=H, inter=inter, us=round(us, 1),
+                              packed_mbytes=round(packed_bytes / 1e6, 1), gbs=round(packed_bytes / us / 1e3, 1))), flush=True)
+
+
+CASES = dict(mamba2=mamba2, moe_decode=moe_decode, attn_decode_kv=attn_decode_kv, qgemm_decode=qgemm_decode, qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
              attn_prefill=attn_prefill, decode_steps=decode_steps, kbench=kbench)
 
 if __name__ == "__main__":

@@ -248,6 +248,12 @@ int mx_read_status(void* workspace, int clear);
 // Library / build information.
 const char* mx_build_info(void);
 
+
+// Grouped 4-bit GEMV over MLX-packed expert weights for decode-sized groups (few rows per expert).
+// -9 = shape not covered (the caller falls back to the grouped GEMM).
+int mx_moe_qgemv(const void* xs, const void* w, const void* scales, const void* biases, const void* lin_bias,
+                 const int* offsets, void* out, int E, int n_out, int K, int group, int mode, int epi,
+                 float alpha, float limit, const void* residual, long long ldo, long long ldr, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -367,6 +367,14 @@ __device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr,
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(sz)
                : "memory");
 }
+// 4-, 8- or 16-byte asynchronous copy (cache-all variant: the only one that takes sizes below 16);
+// a false predicate zero-fills the destination.
+template <int BYTES>
+__device__ __forceinline__ void cp_async_small(uint32_t smem_addr, const void* gptr, bool pred) {
+  const int sz = pred ? BYTES : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(smem_addr), "l"(gptr), "n"(BYTES), "r"(sz)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -630,6 +638,16 @@ paged_decode_mma_kernel(const DecodeParams p, const int G) {
   constexpr int TILE_BYTES = kDmKeys * D * 2;            // one K (or V) group in bf16
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;            // K + V
   constexpr int WARP_BYTES = kDmStages * STAGE_BYTES;
+  // Quantized pools: a ring stage holds the RAW group (K codes, V codes, K and V scale/offset
+  // pairs), fetched with cp.async like the bf16 tiles so that the ring keeps several groups in
+  // flight; the group being consumed is expanded to bf16 into one tile pair per warp that sits
+  // behind the ring. (Expanding at load time, with plain loads, serialised every group on its own
+  // memory latency: 225 us instead of 57 us for the bf16 pool on 64 x 1152 keys.)
+  constexpr int RAW_ROW = D * KV_BITS / 8;               // code bytes per key
+  constexpr int META_ROW = (D / 64) * 4;                 // (scale, offset) bf16 pairs per key
+  constexpr int RAW_STAGE = ((2 * kDmKeys * (RAW_ROW + META_ROW)) + 127) / 128 * 128;
+  constexpr bool kQuant = KV_BITS != 16;
+  static_assert(!kQuant || kDmStages * RAW_STAGE + STAGE_BYTES <= WARP_BYTES, "raw ring + expanded tile fit the ring");
   extern __shared__ __align__(128) uint8_t dm_smem[];
   uint8_t* q_sm = dm_smem;                               // [16][D] bf16 (swizzled)
   uint8_t* kv_sm = dm_smem + 16 * D * 2;                 // 4 warps x stages x (K, V)
@@ -697,47 +715,64 @@ paged_decode_mma_kernel(const DecodeParams p, const int G) {
     if (grp < s_end) {
       const size_t row16 = (static_cast<size_t>(blk16) * p.Hkv + h) * kDmKeys;
       const int rows_ok = len - grp * kDmKeys;  // rows below this index hold real keys
+      if constexpr (!kQuant) {
 #pragma unroll
-      for (int it = 0; it < (kDmKeys * CH) / 32; ++it) {
-        const int i = lane + it * 32;
-        const int r = i / CH, c = i - r * CH;
-        const bool ok = r < rows_ok;
-        size_t row;
-        if (BS16) {
-          row = row16 + r;
-        } else {
-          const int key = grp * kDmKeys + r;
-          const int blk = ok ? table[key / p.block_size] : 0;
-          row = (static_cast<size_t>(blk) * p.Hkv + h) * p.block_size + (ok ? key % p.block_size : 0);
-        }
-        if (KV_BITS == 16) {
+        for (int it = 0; it < (kDmKeys * CH) / 32; ++it) {
+          const int i = lane + it * 32;
+          const int r = i / CH, c = i - r * CH;
+          const bool ok = r < rows_ok;
+          size_t row;
+          if (BS16) {
+            row = row16 + r;
+          } else {
+            const int key = grp * kDmKeys + r;
+            const int blk = ok ? table[key / p.block_size] : 0;
+            row = (static_cast<size_t>(blk) * p.Hkv + h) * p.block_size + (ok ? key % p.block_size : 0);
+          }
           cp_async16(smem_u32(ks) + swz<D>(r, c),
                      static_cast<const __nv_bfloat16*>(p.k_pool) + row * D + c * 8, ok);
           cp_async16(smem_u32(vs) + swz<D>(r, c),
                      static_cast<const __nv_bfloat16*>(p.v_pool) + row * D + c * 8, ok);
-        } else {
-          uint4 ko = make_uint4(0, 0, 0, 0), vo = make_uint4(0, 0, 0, 0);
-          if (ok) {
-            float kf[8], vf[8];
-            load8<KV_BITS>(p.k_pool, row * D + c * 8, kf);
-            load8<KV_BITS>(p.v_pool, row * D + c * 8, vf);
-            const int gq = (c * 8) / 64;
-            const __nv_bfloat16* km = p.k_meta + row * (D / 64) * 2 + gq * 2;
-            const __nv_bfloat16* vm = p.v_meta + row * (D / 64) * 2 + gq * 2;
-            const float ksc = __bfloat162float(km[0]), kbi = __bfloat162float(km[1]);
-            const float vsc = __bfloat162float(vm[0]), vbi = __bfloat162float(vm[1]);
+        }
+      }
+      if constexpr (kQuant) {
+        // raw stage: [K codes 16 x RAW_ROW][V codes][K meta 16 x META_ROW][V meta]
+        uint8_t* raw = my_sm + stage * RAW_STAGE;
+        constexpr int CHQ = RAW_ROW / 16;                // 16-byte pieces of codes per key
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              kf[j] = kf[j] * ksc + kbi;
-              vf[j] = vf[j] * vsc + vbi;
+        for (int it = 0; it < (kDmKeys * CHQ + 31) / 32; ++it) {
+          const int i = lane + it * 32;
+          if (i < kDmKeys * CHQ) {
+            const int r = i / CHQ, c = i - r * CHQ;
+            const bool ok = r < rows_ok;
+            size_t row;
+            if (BS16) {
+              row = row16 + r;
+            } else {
+              const int key = grp * kDmKeys + r;
+              const int blk = ok ? table[key / p.block_size] : 0;
+              row = (static_cast<size_t>(blk) * p.Hkv + h) * p.block_size + (ok ? key % p.block_size : 0);
             }
-            ko = make_uint4(pack_bf16(kf[0], kf[1]), pack_bf16(kf[2], kf[3]), pack_bf16(kf[4], kf[5]),
-                            pack_bf16(kf[6], kf[7]));
-            vo = make_uint4(pack_bf16(vf[0], vf[1]), pack_bf16(vf[2], vf[3]), pack_bf16(vf[4], vf[5]),
-                            pack_bf16(vf[6], vf[7]));
+            cp_async16(smem_u32(raw) + r * RAW_ROW + c * 16,
+                       static_cast<const uint8_t*>(p.k_pool) + row * RAW_ROW + c * 16, ok);
+            cp_async16(smem_u32(raw) + kDmKeys * RAW_ROW + r * RAW_ROW + c * 16,
+                       static_cast<const uint8_t*>(p.v_pool) + row * RAW_ROW + c * 16, ok);
           }
-          *reinterpret_cast<uint4*>(ks + swz<D>(r, c)) = ko;
-          *reinterpret_cast<uint4*>(vs + swz<D>(r, c)) = vo;
+        }
+        {
+          const int r = lane & 15;
+          const bool ok = r < rows_ok;
+          size_t row;
+          if (BS16) {
+            row = row16 + r;
+          } else {
+            const int key = grp * kDmKeys + r;
+            const int blk = ok ? table[key / p.block_size] : 0;
+            row = (static_cast<size_t>(blk) * p.Hkv + h) * p.block_size + (ok ? key % p.block_size : 0);
+          }
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(lane < 16 ? p.k_meta : p.v_meta) + row * META_ROW;
+          const uint32_t dst = smem_u32(raw) + 2 * kDmKeys * RAW_ROW + (lane < 16 ? 0 : kDmKeys * META_ROW) + r * META_ROW;
+          cp_async_small<META_ROW>(dst, src, ok);
         }
       }
     }
@@ -767,7 +802,42 @@ paged_decode_mma_kernel(const DecodeParams p, const int G) {
     }
     cp_async_wait<kDmStages - 1>();
     __syncwarp();
-    const uint32_t ks = smem_u32(my_sm + stage * STAGE_BYTES);
+    uint32_t ks = smem_u32(my_sm + stage * STAGE_BYTES);
+    if constexpr (kQuant) {
+      // expand the raw group of this stage into the warp's bf16 tile pair
+      const uint8_t* raw = my_sm + stage * RAW_STAGE;
+      uint8_t* tile = my_sm + kDmStages * RAW_STAGE;
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {
+        const uint8_t* codes = raw + kv * kDmKeys * RAW_ROW;
+        const uint8_t* meta = raw + 2 * kDmKeys * RAW_ROW + kv * kDmKeys * META_ROW;
+        uint8_t* dst = tile + kv * TILE_BYTES;
+#pragma unroll
+        for (int it = 0; it < (kDmKeys * CH) / 32; ++it) {
+          const int i = lane + it * 32;
+          const int r = i / CH, c = i - r * CH;
+          float f[8];
+          if (KV_BITS == 8) {
+            const uint2 a = *reinterpret_cast<const uint2*>(codes + r * RAW_ROW + c * 8);
+            const uint32_t w[2] = {a.x, a.y};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = static_cast<float>((w[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+          } else {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(codes + r * RAW_ROW + c * 4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = static_cast<float>((w >> (4 * j)) & 0xFu);
+          }
+          const uint32_t m = *reinterpret_cast<const uint32_t*>(meta + r * META_ROW + ((c * 8) / 64) * 4);
+          const float sc = bf16_lo(m), bi = bf16_hi(m);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = f[j] * sc + bi;
+          *reinterpret_cast<uint4*>(dst + swz<D>(r, c)) =
+              make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+        }
+      }
+      __syncwarp();
+      ks = smem_u32(tile);
+    }
     const uint32_t vs = ks + TILE_BYTES;
     float sacc[2][4];
 #pragma unroll

@@ -68,6 +68,7 @@ def _declare(lib) -> None:
                               _vp, _vp, _vp],
         "mx_qmv_allreduce": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                              _vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _vp],
+        "mx_moe_qgemv": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _ll, _ll, _vp],
         "mx_row_ssq": [_vp, _i, _i, _ll, _vp, _vp],
         "mx_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
         "mx_head_rmsnorm": [_vp, _vp, _i, _i, _i, _ll, _f, _vp],

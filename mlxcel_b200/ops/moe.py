@@ -7,6 +7,8 @@ src/models/gpt_oss.rs:402-446 of the reference.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib, reference as ref
@@ -117,11 +119,17 @@ def route(logits: torch.Tensor, k: int, mode: str = "topk_softmax", norm_topk: b
     return ids, wts
 
 
+_QGEMV_MAX_ROWS = int(os.environ.get("MLXCEL_B200_MOE_QGEMV_MAX_ROWS", "8"))
+
+
 def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_out: int,
                    bias: torch.Tensor | None = None, act: str | None = None, alpha: float = 1.702,
-                   limit: float = 7.0, out: torch.Tensor | None = None) -> torch.Tensor:
+                   limit: float = 7.0, out: torch.Tensor | None = None, rows_hint: int | None = None) -> torch.Tensor:
     """Rows [offsets[e], offsets[e+1]) of ``xs`` times expert e's matrix ``w[e]``. With ``act``
-    the expert matrices hold gate rows then up rows and the gated activation is fused."""
+    the expert matrices hold gate rows then up rows and the gated activation is fused.
+    ``rows_hint``: how many of the rows are expected to be in use (defaults to all of them); packed
+    4-bit experts with at most ``MLXCEL_B200_MOE_QGEMV_MAX_ROWS`` rows per expert on average take the
+    weight-streaming grouped GEMV instead of the tensor-core GEMM."""
     from ..models.weights import QuantizedTensor
     from . import quant
 
@@ -137,6 +145,18 @@ def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_o
         # warps) when few rows are routed to each expert; only experts that received tokens are
         # read, at 4 bits per weight. Otherwise: dequantise all experts, dense grouped GEMM.
         wq = {("affine", 4): 1, ("mxfp4", 4): 3}.get((w.mode, w.bits), 0)
+        used = rows if rows_hint is None else min(rows, rows_hint)
+        if (wq and _QGEMV_MAX_ROWS > 0 and used <= _QGEMV_MAX_ROWS * E and w.packed.dim() == 3 and K % 32 == 0
+                and (bias is None or bias.dtype == torch.bfloat16)):
+            epi_gv = _ACT_TO_EPI[act] if act else (1 if bias is not None else 0)
+            rc = lib.mx_moe_qgemv(xs.data_ptr(), w.packed.data_ptr(), w.scales.data_ptr(), _lib.ptr(w.biases),
+                                  _lib.ptr(bias), offsets.data_ptr(), out.data_ptr(), E, n_out, K, w.group_size,
+                                  0 if w.mode == "affine" else 1, epi_gv, float(alpha), float(limit), None, 0, 0,
+                                  _lib.stream())
+            if rc != -9:
+                _lib.count_launch()
+                _lib.check(rc, "mx_moe_qgemv")
+                return out
         if wq and quant._FUSED_QGEMM and K % 64 == 0 and w.group_size in (32, 64, 128):
             tiles = quant.tile_experts_for_gemm(w, n_out if act else None)
             ex = _lib.gemm_extras(wq=wq, q_group=w.group_size)
@@ -160,7 +180,7 @@ def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_o
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up, w_down, inter: int,
                 act: str, b_gate_up=None, b_down=None, e_begin: int = 0, residual=None,
                 alpha: float = 1.702, limit: float = 7.0, out: torch.Tensor | None = None,
-                gated: bool = True) -> torch.Tensor:
+                gated: bool = True, rows_hint: int | None = None) -> torch.Tensor:
     """Weighted sum over the LOCAL experts [e_begin, e_begin + E_local) of their gated MLPs (plain
     ``down(act(up x))`` experts when ``gated`` is false: grouped GEMM, activation kernel, grouped GEMM),
     plus ``residual`` when given. Returns bf16 [T, H] (written into ``out`` when given; rows whose
@@ -199,11 +219,11 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up
     _lib.check(rc, "mx_moe_gather_rows_n")
     _lib.count_launch(2)
     if gated:
-        a = grouped_linear(xs, w_gate_up, offsets, inter, b_gate_up, act, alpha, limit)
+        a = grouped_linear(xs, w_gate_up, offsets, inter, b_gate_up, act, alpha, limit, rows_hint=rows_hint)
     else:
         from . import recurrent as rops
         a = rops.activation(grouped_linear(xs, w_gate_up, offsets, inter, b_gate_up, None), act)
-    y = grouped_linear(a, w_down, offsets, w_down.shape[1], b_down, None)
+    y = grouped_linear(a, w_down, offsets, w_down.shape[1], b_down, None, rows_hint=rows_hint)
     if out is None:
         out = torch.empty(T, w_down.shape[1], dtype=x.dtype, device=dev)
     assert out.shape == (T, w_down.shape[1]) and out.is_contiguous() and out.dtype == x.dtype

@@ -335,10 +335,38 @@ def qglu_linear(x: torch.Tensor, qt: QuantizedTensor, inter: int, act: str, bias
     from . import swiglu
 
     M, K = x.shape
+    if (x.is_cuda and _QGEMV4 and 0 < M <= 8 and qt.bits == 4 and qt.mode in ("affine", "mxfp4") and qt.packed.dim() == 2
+            and K % 32 == 0 and x.is_contiguous() and (bias is None or bias.dtype == torch.bfloat16)):
+        # decode-sized: gate and up rows streamed once, activation in the epilogue (one launch)
+        from . import _ACT_TO_EPI
+        out = torch.empty(M, inter, dtype=torch.bfloat16, device=x.device)
+        rc = _lib.load().mx_moe_qgemv(x.data_ptr(), qt.packed.data_ptr(), qt.scales.data_ptr(), _lib.ptr(qt.biases),
+                                      _lib.ptr(bias), _row_offsets(x.device, M).data_ptr(), out.data_ptr(), 1, inter, K,
+                                      qt.group_size, 0 if qt.mode == "affine" else 1, _ACT_TO_EPI[act], float(alpha),
+                                      float(limit), None, 0, 0, _lib.stream())
+        if rc == 0:
+            _lib.count_launch()
+            return out
+        if rc != -9:
+            _lib.check(rc, "mx_moe_qgemv (dense, gated)")
     wq = fused_wq(qt, M, K) if x.is_cuda else 0
     if wq and x.stride(1) == 1 and M > 0 and inter % 128 == 0:   # gate / up start on tile boundaries
         return _fused_qgemm(x, qt, wq, None, bias, None, inter=inter, act=act, alpha=alpha, limit=limit)
     return swiglu(qlinear(x, qt, bias=bias), inter, act, alpha, limit)
+
+
+_QGEMV4 = os.environ.get("MLXCEL_B200_QGEMV4", "1") != "0"
+_OFFSETS: dict = {}
+
+
+def _row_offsets(device, M: int) -> torch.Tensor:
+    """Device tensor [0, M]: the one-group offsets the grouped GEMV takes for a dense projection."""
+    key = (device.index, M)
+    t = _OFFSETS.get(key)
+    if t is None:
+        t = torch.tensor([0, M], dtype=torch.int32, device=device)
+        _OFFSETS[key] = t
+    return t
 
 
 def qlinear(x: torch.Tensor, qt: QuantizedTensor, bias=None, residual=None, out=None) -> torch.Tensor:
@@ -354,6 +382,22 @@ def qlinear(x: torch.Tensor, qt: QuantizedTensor, bias=None, residual=None, out=
     M, K = x.shape
     N = qt.shape[-2]
     lib = _lib.load()
+    if (_QGEMV4 and 0 < M <= 8 and qt.bits == 4 and qt.mode in ("affine", "mxfp4") and qt.packed.dim() == 2 and K % 32 == 0
+            and x.is_contiguous() and (bias is None or bias.dtype == torch.bfloat16)):
+        # weight-streaming 4-bit GEMV (half2 arithmetic, activations in registers): the grouped
+        # expert kernel with one group of M rows
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        rc = lib.mx_moe_qgemv(x.data_ptr(), qt.packed.data_ptr(), qt.scales.data_ptr(), _lib.ptr(qt.biases),
+                              _lib.ptr(bias), _row_offsets(x.device, M).data_ptr(), out.data_ptr(), 1, N, K,
+                              qt.group_size, 0 if qt.mode == "affine" else 1, 1 if bias is not None else 0, 0.0, 0.0,
+                              _lib.ptr(residual), out.stride(0), residual.stride(0) if residual is not None else 0,
+                              _lib.stream())
+        if rc == 0:
+            _lib.count_launch()
+            return out
+        if rc != -9:
+            _lib.check(rc, "mx_moe_qgemv (dense)")
     if M > _QMV_MAX_M or qt.bits not in (4, 8):
         wq = fused_wq(qt, M, K)
         if wq and x.stride(1) == 1 and M > 0:

@@ -155,8 +155,11 @@ class EpAllToAll:
                      alpha: float = 1.702, limit: float = 7.0) -> None:
         """Wait for every source's rows, run this rank's experts over them, publish the outputs."""
         self._call(1)
+        # rows in use are known on the device only; with balanced routing a rank receives about as many
+        # rows as it sends, which is what picks the decode (weight-streaming) or prefill expert kernels
         moe_ops.moe_experts(self.recv, self.ids_eff, self.ones, w_gate_up, w_down, inter, act, b_gate_up, b_down,
-                            e_begin=self.rank * self.epr, alpha=alpha, limit=limit, out=self.ret)
+                            e_begin=self.rank * self.epr, alpha=alpha, limit=limit, out=self.ret,
+                            rows_hint=max(1, self._T * self.k))
         self._call(2)
 
     def combine(self, wts: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
