@@ -115,9 +115,7 @@ class Engine:
         self.dp_lockstep = getattr(getattr(model, "comm", None), "a2a", None) is not None
         self.dp_active = True
         if self.dp_lockstep:
-            # a graph's capture runs one extra warm-up forward on this rank alone, which the other
-            # ranks' exchanges would wait for: steps are launched eagerly in this mode
-            e.lookahead = e.cuda_graphs = False
+            e.lookahead = False
         if self.pipeline:
             # stages exchange activations with send / recv inside the forward pass: no graph capture,
             # and the token ids come back from the last stage, so nothing can be fed back on the device
@@ -634,11 +632,21 @@ class Engine:
                           slot_mapping_win=self.d_slots_w[:bp] if self.bm_win is not None else None,
                           dec_block_tables_win=self.d_dec_tables_w[:bp] if self.bm_win is not None else None)
             fwd = lambda: self.model.forward(b, self.kv_layers)  # noqa: E731
-            # warm-up outside capture (sets function attributes, fills descriptor caches)
+            # warm-up outside capture (sets function attributes, fills descriptor caches). With
+            # token-sharded experts this pass is this rank's alone, so it runs "dry": no exchange
+            # with the other ranks (the capture below records kernels without running them, and the
+            # replay is the tick's one real forward).
+            a2a = getattr(self.model.comm, "a2a", None)
             s = torch.cuda.Stream(device=self.device)
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
-                fwd()
+                if a2a is not None:
+                    a2a.dry = True
+                try:
+                    fwd()
+                finally:
+                    if a2a is not None:
+                        a2a.dry = False
             torch.cuda.current_stream().wait_stream(s)
             from ..ops import _lib
             n0 = _lib.launches()

@@ -93,6 +93,7 @@ class DpEpComm(LocalComm):
             self.host_group = host_group or dist.new_group(list(range(self.ep_size)), backend="gloo")
         else:
             self.a2a = GlooAllToAll(group, epr)
+            self.a2a.dry = False
             self.host_group = host_group or group
 
     def any_work(self, mine: bool) -> int:

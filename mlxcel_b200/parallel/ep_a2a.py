@@ -83,6 +83,10 @@ class EpAllToAll:
         self.ids_eff = torch.full((rows, 1), -1, dtype=torch.int32, device=dev)
         self.ones = torch.ones(rows, 1, dtype=torch.float32, device=dev)
         self._T = 0
+        # dry: a forward pass that must not talk to the other ranks (the warm-up before a CUDA-graph
+        # capture is a pass of this rank alone). The exchanges are skipped, the local expert kernels
+        # still run (their lazy set-up is what the warm-up is for) and the layer returns its residual.
+        self.dry = False
         self._build_call()
 
     # ------------------------------------------------------------------ constructors
@@ -173,6 +177,11 @@ class EpAllToAll:
     def moe(self, x, ids, wts, w_gate_up, w_down, inter: int, act: str, b_gate_up=None, b_down=None,
             residual=None, alpha: float = 1.702, limit: float = 7.0) -> torch.Tensor:
         """One expert-parallel MoE layer (collective over the ranks of the heap)."""
+        if self.dry:
+            moe_ops.moe_experts(self.recv, self.ids_eff, self.ones, w_gate_up, w_down, inter, act, b_gate_up, b_down,
+                                e_begin=self.rank * self.epr, alpha=alpha, limit=limit, out=self.ret,
+                                rows_hint=max(1, x.shape[0] * self.k))
+            return residual.clone() if residual is not None else torch.zeros_like(x)
         self.dispatch(x, ids)
         self.expert_stage(w_gate_up, w_down, inter, act, b_gate_up, b_down, alpha, limit)
         return self.combine(wts, residual)
