@@ -1051,7 +1051,7 @@ def arch_catalog() -> dict:
             how = "transformers logits (as gemma3_text)"
         fams.append(dict(name=name, executor=ex, checked_against=how))
     return {"families": fams, "encoders": ["bert", "modernbert", "deberta-v2"],
-            "vision_language": ["llava (clip / siglip tower)", "qwen2_vl", "qwen2_5_vl"], "speech": ["whisper"],
+            "vision_language": ["llava (clip / siglip tower)", "qwen2_vl", "qwen2_5_vl", "idefics3 / smolvlm (one tile per image)"], "speech": ["whisper"],
             "quantization": ["affine", "mxfp4", "mxfp8", "fp8 (widened at load)"],
             "kv_bits": [16, 8, 4], "parallelism": ["tp", "ep (replicated tokens)", "dp attention + ep (all-to-all)", "pp", "tp x pp",
                                                    "dp replicas (front)", "prefill / decode disaggregation (front)"]}

@@ -365,7 +365,7 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
     else:
         # vision-language wrappers nest the language model (``model.language_model.``,
         # ``model.language_model.model.``, ...): take the prefix of its embedding table
-        nested = [k for k in src.keys() if k.endswith(".embed_tokens.weight") and "language_model" in k]
+        nested = [k for k in src.keys() if k.endswith(".embed_tokens.weight") and ("language_model" in k or "text_model" in k)]
         if len(nested) == 1:
             pre = nested[0][: -len("embed_tokens.weight")]
     emb = g.mat(pre + "embed_tokens")

@@ -65,7 +65,7 @@ class VisionConfig:
     def from_dict(v: dict, wrapper: dict | None = None) -> "VisionConfig":
         wrapper = wrapper or {}
         mt = v.get("model_type", "clip_vision_model")
-        kind = "siglip" if "siglip" in mt else "clip"
+        kind = "siglip" if any(t in mt for t in ("siglip", "idefics3", "smolvlm")) else "clip"
         c = VisionConfig(kind=kind, hidden=int(v.get("hidden_size", 768)), layers=int(v.get("num_hidden_layers", 12)),
                          heads=int(v.get("num_attention_heads", 12)), intermediate=int(v.get("intermediate_size", 3072)),
                          patch=int(v.get("patch_size", 14)), image_size=int(v.get("image_size", 224)),

@@ -8,7 +8,8 @@ those, so two requests share cached KV blocks only when text AND images are the 
 (the reference's placeholder expansion and media hashing: src/multimodal/prompt*.rs,
 src/multimodal/runtime*.rs).
 
-Supported wrappers: ``llava`` (CLIP or SigLIP tower, two-layer MLP connector), ``qwen2_vl`` and
+Supported wrappers: ``llava`` (CLIP or SigLIP tower, two-layer MLP connector), ``idefics3`` /
+``smolvlm`` (SigLIP-layout tower, pixel-shuffle connector, one tile per image), ``qwen2_vl`` and
 ``qwen2_5_vl`` (see `qwen2_vision.py`). The language model is loaded by the ordinary decoder loader
 from the same checkpoint (its tensors live under ``language_model``).
 """
@@ -20,10 +21,10 @@ from pathlib import Path
 
 import torch
 
-from ..models.vision import LlavaConnector, ViTTower, VisionConfig
+from ..models.vision import LlavaConnector, PixelShuffleConnector, ViTTower, VisionConfig
 from .images import ImageProcessor
 
-SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl")
+SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "idefics3", "smolvlm")
 
 
 def is_vlm_checkpoint(path: str | Path) -> bool:
@@ -51,7 +52,10 @@ class VisionLanguage:
         self.model_type = model_type
         # what stands for one image in prompt text when the chat template does not place it itself
         self.placeholder_text = {"llava": "<image>", "qwen2_vl": "<|vision_start|><|image_pad|><|vision_end|>",
-                                 "qwen2_5_vl": "<|vision_start|><|image_pad|><|vision_end|>"}.get(model_type, "<image>")
+                                 "qwen2_5_vl": "<|vision_start|><|image_pad|><|vision_end|>",
+                                 "idefics3": "<fake_token_around_image><global-img><image><fake_token_around_image>",
+                                 "smolvlm": "<fake_token_around_image><global-img><image><fake_token_around_image>"}.get(
+                                     model_type, "<image>")
         self.stats = dict(images=0, image_tokens=0, encode_seconds=0.0)
 
     @staticmethod
@@ -68,6 +72,16 @@ class VisionLanguage:
                                   raw.get("projector_hidden_act", "gelu"), dtype, device)
             proc = ImageProcessor.from_path(path, vc.image_size)
             return VisionLanguage(tower, conn, proc, raw.get("image_token_index", raw.get("image_token_id", 32000)), mt)
+        if mt in ("idefics3", "smolvlm"):
+            # SigLIP-layout tower, pixel-shuffle connector. One tile per image (the whole image resized
+            # to the tower's square input); the multi-tile split of large images is not done.
+            vc = VisionConfig.from_dict(raw["vision_config"], {})
+            vc.feature_layer, vc.drop_cls = -1, False
+            tower = ViTTower(vc, _sub(src, "model.vision_model.", "vision_model."), dtype, device)
+            conn = PixelShuffleConnector(_sub(src, "model.connector.", "connector."), int(raw.get("scale_factor", 2)), dtype, device)
+            proc = ImageProcessor(dict(size={"height": vc.image_size, "width": vc.image_size}, do_center_crop=False,
+                                       resample=1, image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5]), vc.image_size)
+            return VisionLanguage(tower, conn, proc, raw.get("image_token_id", 128257), mt)
         if mt in ("qwen2_vl", "qwen2_5_vl"):
             from .qwen2_vision import build_qwen2_vision
             return build_qwen2_vision(path, raw, src, dtype, device)

@@ -316,3 +316,40 @@ def test_qwen2_5_vl_windowed_tower_and_greedy_match_transformers():
     while eng.has_work():
         eng.step()
     assert eng.seqs[sid].output == want
+
+
+def test_idefics3_single_tile_matches_transformers():
+    """Idefics3 / SmolVLM layout: SigLIP-style tower with its post-LayerNorm, pixel-shuffle connector
+    (4 patches -> 1 token), Llama text model under ``model.text_model``."""
+    from transformers import Idefics3Config, Idefics3ForConditionalGeneration
+    torch.manual_seed(0)
+    cfg = Idefics3Config(
+        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, image_size=32,
+                           patch_size=8),
+        text_config=dict(model_type="llama", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, vocab_size=300, max_position_embeddings=256, pad_token_id=0),
+        image_token_id=IMG_TOKEN, scale_factor=2, pad_token_id=0)
+    m = Idefics3ForConditionalGeneration(cfg).eval()
+    d = tempfile.mkdtemp(prefix="vlm_idefics3_")
+    m.save_pretrained(d, safe_serialization=True)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    imgs = [_image(5, 50, 41), _image(6, 33, 60)]
+    px = vl.processor(imgs)
+    assert px.shape == (2, 3, 32, 32)
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(1, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [IMG_TOKEN] + text(7) + [IMG_TOKEN] + text(4)
+    ids, mm = vl.prepare(prompt, imgs)
+    assert len(ids) == 16 + 2 * 4                     # 16 patches fold into 4 tokens per image
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=px[None],
+                          pixel_attention_mask=torch.ones(1, 2, 32, 32, dtype=torch.bool), max_new_tokens=8,
+                          do_sample=False)[0, len(ids):].tolist()
+    c = ModelConfig.from_path(d)
+    w = load_full_weights(d, c, dtype=torch.float32)
+    eng = Engine(DecoderModel(c, w), c, EngineConfig(max_batch=2, max_num_batched_tokens=64, num_blocks=32, max_model_len=128,
+                                                     cuda_graphs=False))
+    sid = eng.add_request(ids, SamplingParams(max_tokens=8, ignore_eos=True), **mm)
+    while eng.has_work():
+        eng.step()
+    assert eng.seqs[sid].output == want
