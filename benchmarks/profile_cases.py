@@ -333,17 +333,21 @@ def qgemm_graph():
             qts.append(quant.quantize(w, "affine", 4, 64))
             del w
         packed_bytes = qts[0].nbytes()
-        for M in (1, 8, 32, 64):
+        for M in (1, 4, 8, 32, 64):
             x = _bf(M, K)
             out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
             r = dict(M=M, N=N, K=K, packed_MB=round(packed_bytes / 1e6, 1),
                      stream_us_at_measured_copy_bw=round(packed_bytes / 6.5514e6, 1))
             old = quant._QMV_MAX_M
+            if M <= 8:      # the half2 weight-streaming GEMV (what the library picks for 4-bit, M <= 8)
+                r["gemv4_us"] = round(graph_time(lambda: [quant.qlinear(x, qts[i % ncopy], out=out) for i in range(nrep)]), 1)
+            quant._QGEMV4 = False
             quant._QMV_MAX_M = 0
             r["fused_qgemm_us"] = round(graph_time(lambda: [quant.qlinear(x, qts[i % ncopy], out=out) for i in range(nrep)]), 1)
             quant._QMV_MAX_M = old
-            if M <= 8:
+            if M <= 8:      # the older one-warp-per-row fp32 GEMV
                 r["qmv_us"] = round(graph_time(lambda: [quant.qlinear(x, qts[i % ncopy], out=out) for i in range(nrep)]), 1)
+            quant._QGEMV4 = True
             quant._FUSED_QGEMM = False
             if M > 8:
                 r["dequant_then_gemm_us"] = round(

@@ -9,12 +9,13 @@
 //
 //   grid  = (output-feature blocks, local experts); a block whose expert got no rows returns at once,
 //           so only routed experts are read.
-//   warp  = kFeat output features (gate row + up row each when gated). Lanes stride the packed row
-//           in 16-byte pieces (32 weights), `kUnroll` pieces in flight per lane and row.
-//   x     = the expert's token rows live in REGISTERS as half2, already in the order the nibble pairs
-//           come out of a word ((j, j + 4) of each 8-nibble word), `kTok` tokens per pass; every
-//           weight row of the warp reuses them. More tokens = more passes over the block's rows
-//           (which then come from L2).
+//   warp  = 8 weight rows (8 output features, or 4 features x (gate, up) when gated). Lanes stride the
+//           packed rows in 16-byte pieces (32 weights); the 8 rows' pieces are requested together.
+//   x     = up to 4 token rows per pass. The block stages a K slab of them in shared memory as
+//           half2, already in the order the nibble pairs come out of a word ((j, j + 4) of each
+//           8-nibble word); a lane pulls its piece of all 4 tokens into registers once and uses it
+//           for the 8 rows. More than 4 rows for an expert = more passes over the block's weight
+//           rows (which then come from L2).
 //   math  = two nibbles become one half2 with three integer ops and one exact half2 fix-up
 //           (affine: 0x6400 | q is 1024 + q; mxfp4: sign / exponent / mantissa bits land in the
 //           half's fields and 2^14 restores the exponent bias), products accumulate in half2 over
@@ -28,9 +29,9 @@
 namespace mx {
 
 constexpr int kGvWarps = 8;     // warps per block
-constexpr int kGvFeat = 2;      // output features per warp
-constexpr int kGvTok = 2;       // token rows per pass (registers)
-constexpr int kGvUnroll = 2;    // 16-byte pieces per lane per slab
+constexpr int kGvRows = 8;      // weight rows per warp: 8 features, or 4 features x (gate, up) when gated
+constexpr int kGvTok = 4;       // token rows per pass
+constexpr int kGvSlab = 128;    // 16-byte pieces (32 weights each) of K staged per slab: 4 per lane
 
 __device__ __forceinline__ float gv_e8m0(uint8_t s) {
   if (s == 255) return __uint_as_float(0x7fc00000u);
@@ -78,88 +79,102 @@ struct GvParams {
 
 template <int MODE>
 __global__ void __launch_bounds__(kGvWarps * 32) moe_qgemv_kernel(const GvParams p) {
+  // activations of the current token pass and K slab, as half2 in nibble-pair order:
+  // xs[token][quarter][piece] (16 bytes each: consecutive lanes read consecutive chunks)
+  __shared__ uint4 xs[kGvTok][4][kGvSlab];
+  __shared__ float xsum_s[kGvTok][kGvSlab];
   const int e = blockIdx.y;
   const int row0 = p.offsets[e], m_e = p.offsets[e + 1] - row0;
   if (m_e <= 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int f0 = (blockIdx.x * kGvWarps + warp) * kGvFeat;       // first output feature of this warp
-  if (f0 >= p.n_out) return;
   const bool gated = p.epi >= MX_EPI_SWIGLU;
-  constexpr int kRows = kGvFeat * 2;                              // weight rows per warp (gate + up)
-  const int nrows = gated ? kRows : kGvFeat;
-  const int pieces = p.K >> 5;                                    // 16-byte pieces (32 weights) per row
+  const int feats = gated ? kGvRows / 2 : kGvRows;               // output features per warp
+  const int f0 = (blockIdx.x * kGvWarps + warp) * feats;
+  const int pieces = p.K >> 5;
   const int words_per_row = p.K >> 3;
   const int groups_per_row = p.K / p.group;
   const size_t ebase = static_cast<size_t>(e) * p.N;
+  // weight row of local row r: features first (gate), then their up rows
+  const uint4* wrow[kGvRows];
+  size_t grow[kGvRows];
+  bool rlive[kGvRows];
+#pragma unroll
+  for (int r = 0; r < kGvRows; ++r) {
+    const int feat = f0 + (gated ? (r % (kGvRows / 2)) : r);
+    rlive[r] = feat < p.n_out;
+    const int n = rlive[r] ? ((gated && r >= kGvRows / 2) ? p.n_out + feat : feat) : 0;
+    wrow[r] = reinterpret_cast<const uint4*>(p.w + (ebase + n) * words_per_row);
+    grow[r] = (ebase + n) * groups_per_row;
+  }
 
   for (int t0 = 0; t0 < m_e; t0 += kGvTok) {
-    float acc[kRows][kGvTok];
+    float acc[kGvRows][kGvTok];
 #pragma unroll
-    for (int r = 0; r < kRows; ++r)
+    for (int r = 0; r < kGvRows; ++r)
 #pragma unroll
       for (int t = 0; t < kGvTok; ++t) acc[r][t] = 0.f;
 
-    for (int slab = 0; slab * 32 * kGvUnroll < pieces; ++slab) {
-      // ---- this lane's activations of the slab: kUnroll pieces x 16 half2 per token
-      __half2 xr[kGvTok][kGvUnroll][16];
-      float xsum[kGvTok][kGvUnroll];
-      bool live[kGvUnroll];
+    for (int s0 = 0; s0 < pieces; s0 += kGvSlab) {
+      const int np = min(kGvSlab, pieces - s0);
+      __syncthreads();                                            // the previous slab is consumed
+      for (int i = threadIdx.x; i < kGvTok * np; i += kGvWarps * 32) {
+        const int t = i / np, c = i - t * np;
+        uint4 v[4];
 #pragma unroll
-      for (int u = 0; u < kGvUnroll; ++u) {
-        const int c = (slab * kGvUnroll + u) * 32 + lane;
-        live[u] = c < pieces;
+        for (int q = 0; q < 4; ++q) v[q] = make_uint4(0, 0, 0, 0);
+        if (t0 + t < m_e) {
+          const uint4* src = reinterpret_cast<const uint4*>(p.xs + static_cast<size_t>(row0 + t0 + t) * p.K +
+                                                            (static_cast<size_t>(s0 + c) << 5));
+#pragma unroll
+          for (int q = 0; q < 4; ++q) v[q] = src[q];
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {                             // 8 activations <-> one weight word
+          const float a[8] = {bf16_lo(v[q].x), bf16_hi(v[q].x), bf16_lo(v[q].y), bf16_hi(v[q].y),
+                              bf16_lo(v[q].z), bf16_hi(v[q].z), bf16_lo(v[q].w), bf16_hi(v[q].w)};
+          __half2 h[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            h[j] = __floats2half2_rn(a[j], a[j + 4]);             // nibbles (j, j + 4) of the word
+            sum += a[j] + a[j + 4];
+          }
+          xs[t][q][c] = *reinterpret_cast<uint4*>(h);
+        }
+        xsum_s[t][c] = sum;
+      }
+      __syncthreads();
+      // ---- this lane's pieces of the slab against the warp's rows
+      for (int c = lane; c < np; c += 32) {
+        uint4 pk[kGvRows];
+        float sc[kGvRows], bi[kGvRows];
+#pragma unroll
+        for (int r = 0; r < kGvRows; ++r) {
+          pk[r] = make_uint4(0, 0, 0, 0);
+          sc[r] = bi[r] = 0.f;
+          if (rlive[r]) {
+            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(pk[r].x), "=r"(pk[r].y), "=r"(pk[r].z), "=r"(pk[r].w) : "l"(wrow[r] + s0 + c));
+            const size_t g = grow[r] + ((s0 + c) << 5) / p.group;
+            if (MODE == 0) {
+              sc[r] = __bfloat162float(static_cast<const __nv_bfloat16*>(p.scales)[g]);
+              bi[r] = __bfloat162float(p.biases[g]);
+            } else {
+              sc[r] = gv_e8m0(static_cast<const uint8_t*>(p.scales)[g]);
+            }
+          }
+        }
+        __half2 xr[kGvTok][16];
+        float xsum[kGvTok];
 #pragma unroll
         for (int t = 0; t < kGvTok; ++t) {
-          xsum[t][u] = 0.f;
-          const bool tok = live[u] && (t0 + t) < m_e;
-          const uint4* src = reinterpret_cast<const uint4*>(p.xs + static_cast<size_t>(row0 + t0 + t) * p.K + (c << 5));
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {                           // 8 activations = one weight word
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (tok) v = src[q];
-            const float a[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y),
-                                bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              xr[t][u][q * 4 + j] = __floats2half2_rn(a[j], a[j + 4]);
-              xsum[t][u] += a[j] + a[j + 4];
-            }
-          }
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(&xr[t][q * 4]) = xs[t][q][c];
+          xsum[t] = xsum_s[t][c];
         }
-      }
-      // ---- every weight row of the warp against those registers: all loads first (kRows x kUnroll
-      //      16-byte pieces in flight per lane), then the arithmetic
-      uint4 pk[kRows][kGvUnroll];
-      float sc[kRows][kGvUnroll], bi[kRows][kGvUnroll];
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        const int feat = f0 + (r % kGvFeat);
-        const bool row_live = r < nrows && feat < p.n_out;
-        const int n = (r < kGvFeat) ? feat : p.n_out + feat;      // gate rows first, then up rows
-        const uint4* wrow = reinterpret_cast<const uint4*>(p.w + (ebase + n) * words_per_row);
-#pragma unroll
-        for (int u = 0; u < kGvUnroll; ++u) {
-          const int c = (slab * kGvUnroll + u) * 32 + lane;
-          pk[r][u] = make_uint4(0, 0, 0, 0);
-          sc[r][u] = bi[r][u] = 0.f;
-          if (row_live && live[u]) {
-            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(pk[r][u].x), "=r"(pk[r][u].y), "=r"(pk[r][u].z), "=r"(pk[r][u].w) : "l"(wrow + c));
-            const size_t g = (ebase + n) * groups_per_row + (c << 5) / p.group;
-            if (MODE == 0) {
-              sc[r][u] = __bfloat162float(static_cast<const __nv_bfloat16*>(p.scales)[g]);
-              bi[r][u] = __bfloat162float(p.biases[g]);
-            } else {
-              sc[r][u] = gv_e8m0(static_cast<const uint8_t*>(p.scales)[g]);
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-#pragma unroll
-        for (int u = 0; u < kGvUnroll; ++u) {
-          const uint32_t words[4] = {pk[r][u].x, pk[r][u].y, pk[r][u].z, pk[r][u].w};
+        for (int r = 0; r < kGvRows; ++r) {
+          const uint32_t words[4] = {pk[r].x, pk[r].y, pk[r].z, pk[r].w};
           __half2 h[kGvTok][2];
 #pragma unroll
           for (int t = 0; t < kGvTok; ++t) h[t][0] = h[t][1] = __floats2half2_rn(0.f, 0.f);
@@ -169,49 +184,45 @@ __global__ void __launch_bounds__(kGvWarps * 32) moe_qgemv_kernel(const GvParams
             for (int j = 0; j < 4; ++j) {
               const __half2 wv = gv_pair<MODE>(words[q] >> (4 * j));
 #pragma unroll
-              for (int t = 0; t < kGvTok; ++t) h[t][q >> 1] = __hfma2(wv, xr[t][u][q * 4 + j], h[t][q >> 1]);
+              for (int t = 0; t < kGvTok; ++t) h[t][q >> 1] = __hfma2(wv, xr[t][q * 4 + j], h[t][q >> 1]);
             }
           }
 #pragma unroll
           for (int t = 0; t < kGvTok; ++t) {
             const float2 a = __half22float2(h[t][0]), b = __half22float2(h[t][1]);
-            const float dot = (a.x + a.y) + (b.x + b.y);
-            acc[r][t] += sc[r][u] * dot + bi[r][u] * xsum[t][u];
+            acc[r][t] += sc[r] * ((a.x + a.y) + (b.x + b.y)) + bi[r] * xsum[t];
           }
         }
       }
     }
-    // ---- reduce over lanes, finish, store
+    // ---- reduce over lanes, finish, store: lane (f, t) writes feature f of token t
 #pragma unroll
-    for (int r = 0; r < kRows; ++r)
+    for (int r = 0; r < kGvRows; ++r)
 #pragma unroll
       for (int t = 0; t < kGvTok; ++t) acc[r][t] = warp_sum(acc[r][t]);
-    if (lane < kGvFeat * kGvTok) {
-      const int fi = lane % kGvFeat, t = lane / kGvFeat;
-      const int feat = f0 + fi;
-      if (feat < p.n_out && (t0 + t) < m_e) {
-        float g = 0.f, u = 0.f;
+    const int fi = lane % feats, t = lane / feats;
+    if (t < kGvTok && f0 + fi < p.n_out && t0 + t < m_e) {
+      float g = 0.f, u = 0.f;
 #pragma unroll
-        for (int r = 0; r < kGvFeat; ++r)
+      for (int r = 0; r < kGvRows; ++r)
 #pragma unroll
-          for (int tt = 0; tt < kGvTok; ++tt)
-            if (r == fi && tt == t) {
-              g = acc[r][tt];
-              u = acc[r + kGvFeat][tt];
-            }
-        float v;
-        if (gated) {
-          if (p.lin_bias) {
-            g += __bfloat162float(p.lin_bias[ebase + feat]);
-            u += __bfloat162float(p.lin_bias[ebase + p.n_out + feat]);
-          }
-          v = gv_glu(p.epi, g, u, p.alpha, p.limit);
-        } else {
-          v = g + (p.lin_bias ? __bfloat162float(p.lin_bias[ebase + feat]) : 0.f);
-          if (p.residual) v += __bfloat162float(p.residual[static_cast<size_t>(row0 + t0 + t) * p.ldr + feat]);
+        for (int tt = 0; tt < kGvTok; ++tt) {
+          if (tt == t && r == fi) g = acc[r][tt];
+          if (tt == t && r == fi + kGvRows / 2) u = acc[r][tt];
         }
-        p.out[static_cast<size_t>(row0 + t0 + t) * p.ldo + feat] = __float2bfloat16(v);
+      const int feat = f0 + fi;
+      float v;
+      if (gated) {
+        if (p.lin_bias) {
+          g += __bfloat162float(p.lin_bias[ebase + feat]);
+          u += __bfloat162float(p.lin_bias[ebase + p.n_out + feat]);
+        }
+        v = gv_glu(p.epi, g, u, p.alpha, p.limit);
+      } else {
+        v = g + (p.lin_bias ? __bfloat162float(p.lin_bias[ebase + feat]) : 0.f);
+        if (p.residual) v += __bfloat162float(p.residual[static_cast<size_t>(row0 + t0 + t) * p.ldr + feat]);
       }
+      p.out[static_cast<size_t>(row0 + t0 + t) * p.ldo + feat] = __float2bfloat16(v);
     }
   }
 }
@@ -249,7 +260,8 @@ extern "C" int mx_moe_qgemv(const void* xs, const void* w, const void* scales, c
   p.out = static_cast<__nv_bfloat16*>(out);
   p.E = E, p.N = gated ? 2 * n_out : n_out, p.K = K, p.group = group, p.n_out = n_out, p.epi = epi;
   p.alpha = alpha, p.limit = limit;
-  const dim3 grid((n_out + kGvWarps * kGvFeat - 1) / (kGvWarps * kGvFeat), E);
+  const int per_block = kGvWarps * (gated ? kGvRows / 2 : kGvRows);
+  const dim3 grid((n_out + per_block - 1) / per_block, E);
   if (grid.y > 65535) return -9;
   cudaError_t err = mode == 0 ? launch_kernel(moe_qgemv_kernel<0>, grid, dim3(kGvWarps * 32), 0, stream, p)
                               : launch_kernel(moe_qgemv_kernel<1>, grid, dim3(kGvWarps * 32), 0, stream, p);

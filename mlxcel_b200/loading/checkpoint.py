@@ -260,6 +260,9 @@ def _load_attention(g: _Getter, cfg: ModelConfig, p: str, lw_kwargs: dict) -> No
     lw_kwargs["bo"] = g.vec(ob + ".bias")
     lw_kwargs["q_norm"] = g.vec(_first_name(g.src, a + ".q_norm.weight", a + ".query_layernorm.weight"))
     lw_kwargs["k_norm"] = g.vec(_first_name(g.src, a + ".k_norm.weight", a + ".key_layernorm.weight"))
+    if lw_kwargs["q_norm"] is None and cfg.extra.get("qk_norm_no_params"):
+        lw_kwargs["q_norm"] = torch.ones(cfg.head_dim, dtype=g.dtype)       # norms without gains
+        lw_kwargs["k_norm"] = torch.ones(cfg.head_dim, dtype=g.dtype)
     if cfg.norm_weight_bias and lw_kwargs["q_norm"] is not None:
         # Gemma 3 stores the per-head norms as (weight - 1) like its other norms; the fused
         # q/k-norm + RoPE kernel takes plain gains

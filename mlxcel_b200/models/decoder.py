@@ -125,6 +125,8 @@ class DecoderModel:
         dev = weights.final_norm.device
         # served context (when the front end recorded it): longrope / dynamic-NTK tables depend on it
         inv, ms = rope_inv_freq(cfg.rot_dim, cfg.rope_theta, cfg.rope_scaling, int(cfg.extra.get("served_context", 0) or 0))
+        if cfg.extra.get("rope_negate"):
+            inv = -inv                       # the pair rotates the other way (x2, -x1 instead of -x2, x1)
         self.inv_freq = inv.to(dev)
         self.mscale = ms
         # sliding-window layers with their own RoPE base (Gemma 3: local 10k, global 1M with scaling)
@@ -343,6 +345,8 @@ class DecoderModel:
             h = self.comm.embed(b.token_ids, w.embed, cfg.embed_scale)
             if w.extra.get("pos_embed") is not None:          # learned absolute positions (GPT-2 family)
                 h = (h.float() + w.extra["pos_embed"].index_select(0, b.positions.long()).float()).to(h.dtype)
+            if cfg.extra.get("embed_norm"):                   # a (gain-free) norm between embedding and blocks
+                h = ops.rmsnorm(h, torch.ones_like(w.final_norm), cfg.rms_norm_eps, 0.0)
         eps, wb = cfg.rms_norm_eps, cfg.norm_weight_bias
         res_mult = cfg.extra.get("residual_multiplier", 1.0)
         if self.fold_attn and h.is_cuda and h.shape[0] <= self._ssq.max_tokens and h.dtype == torch.bfloat16:

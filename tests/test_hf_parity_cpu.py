@@ -69,6 +69,15 @@ FAMILIES = {
                        layer_types=["sliding_attention", "full_attention"] * 2, num_experts=8, num_experts_per_tok=2,
                        moe_intermediate_size=48, num_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1,
                        routed_scaling_factor=2.5),
+    "code_llama": {}, "nanochat": dict(final_logit_softcapping=15.0),
+    "cwm": dict(num_hidden_layers=4, sliding_window=8, head_dim=16,
+                layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
+                rope_parameters=dict(rope_type="llama3", rope_theta=10000.0, factor=4.0, high_freq_factor=4.0,
+                                     low_freq_factor=1.0, original_max_position_embeddings=64)),
+    "glm4_moe_lite": dict(moe_intermediate_size=48, num_key_value_heads=4, n_routed_experts=8, num_experts_per_tok=2,
+                          n_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1, routed_scaling_factor=1.8,
+                          q_lora_rank=24, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                          pad_token_id=0),
     "mamba2": dict(num_heads=8, head_dim=16, state_size=16, n_groups=1, expand=2, conv_kernel=4, chunk_size=8),
 }
 
