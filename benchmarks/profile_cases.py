@@ -339,7 +339,9 @@ def qgemm_graph():
             r = dict(M=M, N=N, K=K, packed_MB=round(packed_bytes / 1e6, 1),
                      stream_us_at_measured_copy_bw=round(packed_bytes / 6.5514e6, 1))
             old = quant._QMV_MAX_M
-            if M <= 8:      # the half2 weight-streaming GEMV (what the library picks for 4-bit, M <= 8)
+            keep = quant._QGEMV4
+            if M <= 8:      # the grouped mma.sync weight-streaming kernel used as a dense GEMV (one group)
+                quant._QGEMV4 = True
                 r["gemv4_us"] = round(graph_time(lambda: [quant.qlinear(x, qts[i % ncopy], out=out) for i in range(nrep)]), 1)
             quant._QGEMV4 = False
             quant._QMV_MAX_M = 0
@@ -347,7 +349,7 @@ def qgemm_graph():
             quant._QMV_MAX_M = old
             if M <= 8:      # the older one-warp-per-row fp32 GEMV
                 r["qmv_us"] = round(graph_time(lambda: [quant.qlinear(x, qts[i % ncopy], out=out) for i in range(nrep)]), 1)
-            quant._QGEMV4 = True
+            quant._QGEMV4 = keep
             quant._FUSED_QGEMM = False
             if M > 8:
                 r["dequant_then_gemm_us"] = round(

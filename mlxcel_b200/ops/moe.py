@@ -119,7 +119,7 @@ def route(logits: torch.Tensor, k: int, mode: str = "topk_softmax", norm_topk: b
     return ids, wts
 
 
-_QGEMV_MAX_ROWS = int(os.environ.get("MLXCEL_B200_MOE_QGEMV_MAX_ROWS", "8"))
+_QGEMV_MAX_ROWS = int(os.environ.get("MLXCEL_B200_MOE_QGEMV_MAX_ROWS", "16"))
 
 
 def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_out: int,
