@@ -493,9 +493,11 @@ def moe_decode(T=128, E=128, k=4, H=2880, inter=2880, reps=0):
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1))
         return sorted(ts)[3] * 1e3 / n
-    for label, limit in (("gemv", 1 << 20), ("tensor_core_gemm", 0)):
-        moe_ops._QGEMV_MAX_ROWS = limit
-        us = graph_us()
+    for label, limit, expand in (("gemv", 1 << 20, 0), ("tensor_core_gemm", 0, 0), ("expand_then_dense_gemm", 0, 1)):
+        if label == "gemv" and T * k > 64 * E:
+            continue                      # prefill-sized: the streaming kernel is not a candidate
+        moe_ops._QGEMV_MAX_ROWS, moe_ops._DEQUANT_MIN_ROWS = limit, expand
+        us = graph_us(2 if T * k > 64 * E else 8)
         print(json.dumps(dict(op="moe_decode", path=label, T=T, E=E, k=k, H=H, inter=inter, us=round(us, 1),
                               packed_mbytes=round(packed_bytes / 1e6, 1), gbs=round(packed_bytes / us / 1e3, 1))), flush=True)
 

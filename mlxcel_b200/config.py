@@ -647,6 +647,12 @@ def _granitemoe(c: ModelConfig, raw: dict) -> None:
     c.moe_intermediate_size = c.intermediate_size
 
 
+def _granitemoeshared(c: ModelConfig, raw: dict) -> None:
+    """GraniteMoE with an always-on shared gated MLP beside the routed experts (reference src/models/granitemoe*.rs)."""
+    _granitemoe(c, raw)
+    c.shared_expert_intermediate_size = int(raw.get("shared_intermediate_size", 0) or 0)
+
+
 def _deepseek_routing(c: ModelConfig, raw: dict) -> None:
     """Sigmoid scores + correction bias + group-limited top-k + scaled weights, shared experts always
     on, the first ``first_k_dense_replace`` layers dense (DeepSeek-V3 routing; reference
@@ -1016,7 +1022,7 @@ FAMILIES = {
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
     "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
-    "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
+    "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }
 

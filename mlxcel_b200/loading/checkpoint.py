@@ -342,7 +342,11 @@ def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
         lw.experts_gate_up, lw.experts_down = _stack(gus), _stack(downs)
     sh = next((p + n for n in (".mlp.shared_experts", ".mlp.shared_mlp") if g.has(p + n + ".gate_proj")),
               p + ".mlp.shared_expert")
-    if g.has(sh + ".gate_proj"):
+    if g.src.has(p + ".shared_mlp.input_linear.weight"):
+        # GraniteMoE-shared: an always-on gated MLP stored fused ([2S, H], gate rows first)
+        lw.shared_gate_up = g.mat(p + ".shared_mlp.input_linear")
+        lw.shared_down = g.mat(p + ".shared_mlp.output_linear")
+    elif g.has(sh + ".gate_proj"):
         lw.shared_gate_up = _cat_rows([g.mat(sh + ".gate_proj"), g.mat(sh + ".up_proj")])
         lw.shared_down = g.mat(sh + ".down_proj")
         sg = g.mat(p + ".mlp.shared_expert_gate")

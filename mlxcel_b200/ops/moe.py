@@ -120,6 +120,10 @@ def route(logits: torch.Tensor, k: int, mode: str = "topk_softmax", norm_topk: b
 
 
 _QGEMV_MAX_ROWS = int(os.environ.get("MLXCEL_B200_MOE_QGEMV_MAX_ROWS", "16"))
+# From this many rows per expert (on average) packed experts are expanded to bf16 once and run
+# through the dense grouped GEMM: at prefill sizes the expansion (one pass over the layer's experts) is
+# cheaper than unpacking every tile again for every row block inside the GEMM.
+_DEQUANT_MIN_ROWS = int(os.environ.get("MLXCEL_B200_MOE_DEQUANT_MIN_ROWS", "64"))
 
 
 def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_out: int,
@@ -157,7 +161,8 @@ def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, n_o
                 _lib.count_launch()
                 _lib.check(rc, "mx_moe_qgemv")
                 return out
-        if wq and quant._FUSED_QGEMM and K % 64 == 0 and w.group_size in (32, 64, 128):
+        expand = _DEQUANT_MIN_ROWS > 0 and used >= _DEQUANT_MIN_ROWS * E
+        if wq and quant._FUSED_QGEMM and not expand and K % 64 == 0 and w.group_size in (32, 64, 128):
             tiles = quant.tile_experts_for_gemm(w, n_out if act else None)
             ex = _lib.gemm_extras(wq=wq, q_group=w.group_size)
             rc = lib.mx_grouped_gemm_bf16(xs.data_ptr(), tiles.data_ptr(), out.data_ptr(), _lib.ptr(bias),

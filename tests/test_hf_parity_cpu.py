@@ -69,6 +69,8 @@ FAMILIES = {
                        layer_types=["sliding_attention", "full_attention"] * 2, num_experts=8, num_experts_per_tok=2,
                        moe_intermediate_size=48, num_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1,
                        routed_scaling_factor=2.5),
+    "granitemoeshared": dict(num_local_experts=4, num_experts_per_tok=2, shared_intermediate_size=96, embedding_multiplier=2.0,
+                             residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=3.0),
     "code_llama": {}, "nanochat": dict(final_logit_softcapping=15.0),
     "cwm": dict(num_hidden_layers=4, sliding_window=8, head_dim=16,
                 layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
