@@ -29,9 +29,9 @@ __device__ __forceinline__ float e8m0_to_float(uint8_t s) {
 }
 __device__ __forceinline__ float e2m1_to_float(uint32_t nib) {
   // sign | 2-bit exponent | 1-bit mantissa: {0, .5, 1, 1.5, 2, 3, 4, 6}
-  const float tab[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-  const float v = tab[nib & 7u];
-  return (nib & 8u) ? -v : v;
+  const uint32_t ee = (nib >> 1) & 3u, m = nib & 1u;
+  const uint32_t mag = ee ? (((ee + 126u) << 23) | (m << 22)) : (m ? 0x3F000000u : 0u);
+  return __uint_as_float(mag | ((nib & 8u) << 28));
 }
 __device__ __forceinline__ float e4m3_to_float(uint32_t b) {
   const uint32_t sign = (b & 0x80u) << 24;
@@ -93,6 +93,45 @@ __global__ void dequantize_kernel(const uint32_t* __restrict__ w, const void* __
   o.z = pack_bf16(f[4], f[5]);
   o.w = pack_bf16(f[6], f[7]);
   *reinterpret_cast<uint4*>(out + r * K + k0) = o;
+}
+
+// 4-bit formats, 32 values (one 16-byte piece, inside one group) per thread: direct nibble
+// extraction with the format fixed at compile time and 64 contiguous output bytes per thread. The
+// generic kernel above spends its time on per-value bit-stream arithmetic (measured 0.6 TB/s of
+// output on 128 stacked experts); expanding a layer's experts before a prefill-sized grouped GEMM
+// needs this to run at memory speed.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+dequantize4_kernel(const uint4* __restrict__ w, const void* __restrict__ scales,
+                   const __nv_bfloat16* __restrict__ biases, uint4* __restrict__ out, long long pieces,
+                   int pieces_per_row, int group) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= pieces) return;
+  const long long r = idx / pieces_per_row;
+  const int c = static_cast<int>(idx - r * pieces_per_row);
+  uint4 pk;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w) : "l"(w + idx));
+  const long long g = r * (static_cast<long long>(pieces_per_row) * 32 / group) + (c * 32) / group;
+  float sc, bi = 0.f;
+  if (MODE == kAffine) {
+    sc = __bfloat162float(static_cast<const __nv_bfloat16*>(scales)[g]);
+    bi = __bfloat162float(biases[g]);
+  } else {
+    sc = e8m0_to_float(static_cast<const uint8_t*>(scales)[g]);
+  }
+  const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t nib = (words[q] >> (4 * j)) & 0xFu;
+      f[j] = (MODE == kAffine) ? static_cast<float>(nib) * sc + bi : e2m1_to_float(nib) * sc;
+    }
+    out[idx * 4 + q] = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]),
+                                  pack_bf16(f[6], f[7]));
+  }
 }
 
 // ----------------------------------------------------------------------------- qmv
@@ -354,6 +393,21 @@ extern "C" int mx_dequantize(const void* w, const void* scales, const void* bias
   if (mode == kAffine && !(bits == 2 || bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8)) return -1;
   if (mode == kMxfp4 && bits != 4) return -1;
   if (mode == kMxfp8 && bits != 8) return -1;
+  if (bits == 4 && K % 32 == 0 && group % 32 == 0 && (mode == kAffine || mode == kMxfp4) &&
+      (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const long long pieces = N * (K / 32);
+    const long long nb = (pieces + 255) / 256;
+    if (nb > 0x7fffffffll) return -1;
+    if (mode == kAffine)
+      dequantize4_kernel<kAffine><<<static_cast<int>(nb), 256, 0, stream>>>(
+          static_cast<const uint4*>(w), scales, static_cast<const __nv_bfloat16*>(biases), static_cast<uint4*>(out),
+          pieces, K / 32, group);
+    else
+      dequantize4_kernel<kMxfp4><<<static_cast<int>(nb), 256, 0, stream>>>(
+          static_cast<const uint4*>(w), scales, static_cast<const __nv_bfloat16*>(biases), static_cast<uint4*>(out),
+          pieces, K / 32, group);
+    return static_cast<int>(cudaGetLastError());
+  }
   const long long total = N * (K / 8);
   const int threads = 256;
   const long long blocks = (total + threads - 1) / threads;
