@@ -792,6 +792,15 @@ def _arcee(c: ModelConfig, raw: dict) -> None:
     c.hidden_act = "relu2"
 
 
+def _ministral3(c: ModelConfig, raw: dict) -> None:
+    """Ministral 3: the Mistral layout with YaRN frequencies and a position-dependent query scale
+    ``1 + beta * log(1 + floor(pos / original_max_position))`` (reference src/models/ministral3.rs)."""
+    rp = raw.get("rope_parameters") or raw.get("rope_scaling") or {}
+    if rp.get("llama_4_scaling_beta"):
+        c.extra["llama4_attn_scale"] = (float(rp["llama_4_scaling_beta"]),
+                                        int(rp.get("original_max_position_embeddings") or c.max_position_embeddings))
+
+
 def _nanochat(c: ModelConfig, raw: dict) -> None:
     """nanochat: RMSNorm without gains everywhere (blocks, final, and per-head q/k norms applied AFTER the
     rotary embedding), plain MLP fc1 -> relu^2 -> fc2, logit soft cap (reference src/models/nanochat.rs)."""
@@ -1022,7 +1031,7 @@ FAMILIES = {
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
     "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
-    "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
+    "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }
 

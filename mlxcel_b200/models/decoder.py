@@ -206,6 +206,13 @@ class DecoderModel:
             kn = ops.rmsnorm(qkv[:, nq:nq + nk].contiguous(), k_norm, cfg.rms_norm_eps, 0.0)
             qkv = torch.cat([qn, kn, qkv[:, nq + nk:]], dim=1)
             q_norm = k_norm = None
+        if cfg.extra.get("llama4_attn_scale"):
+            # queries grow with the logarithm of their position block (a scalar per row commutes with
+            # the rotation, so it is applied before the fused RoPE + append kernel)
+            beta, orig = cfg.extra["llama4_attn_scale"]
+            sc = 1.0 + beta * torch.log1p(torch.floor(b.positions.float() / orig))
+            nq = self.Hq * self.D
+            qkv = torch.cat([(qkv[:, :nq].float() * sc[:, None]).to(qkv.dtype), qkv[:, nq:]], dim=1)
         window = cfg.layer_window(self.layer_range[li] if li < len(self.layer_range) else li)
         local = window > 0 and self.inv_freq_local is not None
         layer_index = self.layer_range[li] if li < len(self.layer_range) else li

@@ -98,11 +98,16 @@ def rope_inv_freq(head_dim_rot: int, theta: float, scaling: dict | None,
             ramp = ((torch.arange(half, dtype=torch.float64) - lo) / (hi - lo)).clamp(0, 1)
             extrap_w = 1.0 - ramp
             inv = inv / factor * (1 - extrap_w) + inv * extrap_w
-            ms = scaling.get("mscale")
+            ms, mad = scaling.get("mscale"), scaling.get("mscale_all_dim")
+
+            def yarn_ms(m):
+                return 0.1 * float(m) * math.log(factor) + 1.0 if factor > 1 else 1.0
             if scaling.get("attention_factor") is not None:
                 mscale = float(scaling["attention_factor"])
-            elif factor > 1:
-                mscale = 0.1 * (float(ms) if ms else 1.0) * math.log(factor) + 1.0
+            elif ms and mad:
+                mscale = yarn_ms(ms) / yarn_ms(mad)        # both given: only their ratio scales q and k
+            else:
+                mscale = yarn_ms(1.0)
         elif kind in ("longrope", "su"):
             # Phi-3 long context: per-pair divisors, the long set once the served context exceeds the
             # original training length (the short set otherwise), and a magnitude scale

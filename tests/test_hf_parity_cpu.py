@@ -71,6 +71,9 @@ FAMILIES = {
                        routed_scaling_factor=2.5),
     "granitemoeshared": dict(num_local_experts=4, num_experts_per_tok=2, shared_intermediate_size=96, embedding_multiplier=2.0,
                              residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=3.0),
+    "ministral3": dict(head_dim=16, rope_parameters=dict(rope_type="yarn", rope_theta=10000.0, factor=4.0,
+                                                       original_max_position_embeddings=8, beta_fast=32.0, beta_slow=1.0,
+                                                       mscale=1.0, mscale_all_dim=1.0, llama_4_scaling_beta=0.1)),
     "code_llama": {}, "nanochat": dict(final_logit_softcapping=15.0),
     "cwm": dict(num_hidden_layers=4, sliding_window=8, head_dim=16,
                 layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
