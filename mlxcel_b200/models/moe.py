@@ -73,9 +73,12 @@ def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -
     El = gate_up.shape[0]
     inter = gate_up.shape[-2] // 2
     first = ep_rank == 0 or ep == 1
+    # with balanced routing 1 / ep of the (token, k) pairs land on this rank's experts: that estimate
+    # picks the decode or the prefill expert kernels
+    hint = max(1, x.shape[0] * ids.shape[1] // ep) if ep > 1 else None
     out = moe_ops.moe_experts(x, ids, wts, gate_up, down, inter, cfg.hidden_act, lw.experts_gate_up_b,
                               lw.experts_down_b, e_begin=ep_rank * El, residual=h if first else None,
-                              alpha=cfg.swiglu_alpha, limit=cfg.swiglu_limit)
+                              alpha=cfg.swiglu_alpha, limit=cfg.swiglu_limit, rows_hint=hint)
     if lw.shared_gate_up is not None:
         out = (out.float() + _shared_expert(cfg, lw, x).float()).to(out.dtype)
     if ep > 1:
