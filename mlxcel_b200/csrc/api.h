@@ -226,6 +226,14 @@ int mx_moe_route(const void* logits, int* topk_ids, float* topk_w, int T, int E,
 // MoE token permutation helpers: count tokens per expert, exclusive scan, scatter rows.
 int mx_moe_align(const int* topk_ids, int* expert_offsets, int* sorted_row, int* sorted_token,
                  int T, int k, int E, int e_begin, int e_end, void* stream);
+// The same with the pair count read on the device (*n_pairs_dev <= max_tokens * k) and, when
+// token_map is given, sorted_token[r] = token_map[token] (tokens are a compacted list of rows).
+int mx_moe_align_n(const int* topk_ids, const int* n_pairs_dev, const int* token_map, int* expert_offsets,
+                   int* sorted_row, int* sorted_token, int max_tokens, int k, int e_begin, int e_end,
+                   void* stream);
+// out[sorted_token[r]] = y[r] for r < *total_rows (inverse of the gather for one pair per token).
+int mx_moe_scatter_rows_n(const void* y, const int* sorted_token, const int* total_rows, void* out,
+                          int max_rows, int dim, void* stream);
 // Rows are bounded by `max_rows` on the host; the true row count is read on the device from
 // total_rows (= expert_offsets[E_local]) so the MoE block needs no host synchronisation.
 int mx_moe_gather_rows_n(const void* x, const int* sorted_token, const int* total_rows, void* out,

@@ -9,8 +9,11 @@
 //                 counter and nothing is negotiated between ranks. The last CTA publishes the row
 //                 counts and raises this rank's flag on every destination (release, system scope).
 //   ep_recv       destination side: waits (bounded) for all sources' flags of this epoch and turns the
-//                 per-source counts into the expert id of every receive row (-1 for unused rows), which
-//                 is what the grouped expert GEMM's alignment kernel consumes.
+//                 per-source counts into a COMPACT list of the rows in use: expert id and receive-row
+//                 index of each, and their number, all on the device. The receive area is sized for
+//                 the worst case (every source sends all its pairs here), so the expert stage must
+//                 never walk it whole: its alignment, gather and scatter kernels are bounded by that
+//                 number.
 //   (grouped gate/up + down GEMMs over the received rows, see moe.cu / gemm.cu)
 //   ep_ready      raises this rank's "outputs ready" flag on every source.
 //   ep_combine    weighted sum + transfer in one pass: waits for the owners' flags, then reads each
@@ -50,7 +53,9 @@ struct EpParams {
   int* cnt;                      // [world] rows sent to each destination (zero between calls)
   uint32_t* ticket;              // CTA completion counter (zero between calls)
   int* route;                    // [T * k]: dst * cap + slot
-  int* ids_eff;                  // [world * cap] expert id of every receive row, -1 = unused
+  int* ids_eff;                  // [world * cap] expert id of the i-th row in use (compact list)
+  int* rowmap;                   // [world * cap] receive-row index of the i-th row in use
+  int* nrecv;                    // number of rows in use
   // own symmetric regions
   const int* meta;               // [world * cap] expert ids as written by the sources
   const int* count;              // [world] rows written by each source
@@ -152,21 +157,34 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
   if (threadIdx.x == 0) *p.ticket = 0u;
 }
 
-// ids_eff[i] = expert of receive row i, or -1 beyond the rows its source wrote this epoch.
+// Compact list of the rows in use, source after source: entry base[s] + slot is row s * cap + slot.
 __global__ void __launch_bounds__(kEpThreads) ep_recv_kernel(const EpParams p) {
-  __shared__ int cnt[kEpMaxRanks];
+  __shared__ int cnt[kEpMaxRanks], base[kEpMaxRanks + 1];
   __shared__ int ok;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if (threadIdx.x < p.world) {
     if (!ep_flag_wait(&p.dflag[threadIdx.x], *p.epoch, p.status)) ok = 0;
-    cnt[threadIdx.x] = *reinterpret_cast<const volatile int*>(&p.count[threadIdx.x]);
+    cnt[threadIdx.x] = min(max(*reinterpret_cast<const volatile int*>(&p.count[threadIdx.x]), 0), p.cap);
   }
   __syncthreads();
-  const int total = p.world * p.cap;
-  for (int i = blockIdx.x * kEpThreads + threadIdx.x; i < total; i += gridDim.x * kEpThreads) {
-    const int s = i / p.cap, slot = i - s * p.cap;
-    p.ids_eff[i] = (ok && slot < cnt[s]) ? *reinterpret_cast<const volatile int*>(&p.meta[i]) : -1;
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int s = 0; s < p.world; ++s) {
+      base[s] = acc;
+      acc += ok ? cnt[s] : 0;
+    }
+    base[p.world] = acc;
+    if (blockIdx.x == 0) *p.nrecv = acc;
+  }
+  __syncthreads();
+  if (!ok) return;
+  for (int s = 0; s < p.world; ++s) {
+    for (int slot = blockIdx.x * kEpThreads + threadIdx.x; slot < cnt[s]; slot += gridDim.x * kEpThreads) {
+      const int row = s * p.cap + slot;
+      p.ids_eff[base[s] + slot] = *reinterpret_cast<const volatile int*>(&p.meta[row]);
+      p.rowmap[base[s] + slot] = row;
+    }
   }
 }
 
@@ -250,7 +268,7 @@ using namespace mx;
 struct MxEpCall {
   int rank, world, T, k, H, experts_per_rank, cap;
   unsigned int reserved;
-  unsigned long long epoch, status, x, ids, wts, residual, out, cnt, ticket, route, ids_eff;
+  unsigned long long epoch, status, x, ids, wts, residual, out, cnt, ticket, route, ids_eff, rowmap, nrecv;
   unsigned long long meta, count, dflag, cflag;
   unsigned long long recv_peer[kEpMaxRanks], meta_peer[kEpMaxRanks], count_peer[kEpMaxRanks],
       dflag_peer[kEpMaxRanks], cflag_peer[kEpMaxRanks], ret_peer[kEpMaxRanks];
@@ -275,6 +293,8 @@ static int ep_fill(const MxEpCall* c, EpParams& p) {
   p.ticket = static_cast<uint32_t*>(ptr(c->ticket));
   p.route = static_cast<int*>(ptr(c->route));
   p.ids_eff = static_cast<int*>(ptr(c->ids_eff));
+  p.rowmap = static_cast<int*>(ptr(c->rowmap));
+  p.nrecv = static_cast<int*>(ptr(c->nrecv));
   p.meta = static_cast<const int*>(ptr(c->meta));
   p.count = static_cast<const int*>(ptr(c->count));
   p.dflag = static_cast<const uint32_t*>(ptr(c->dflag));
@@ -313,10 +333,9 @@ extern "C" int mx_ep_a2a(const void* call, int stage, void* stream_) {
           dim3(ep_grid((static_cast<long long>(p.T) * p.k + kEpRowsPerCta - 1) / kEpRowsPerCta * (kEpThreads / 32))),
           dim3(kEpThreads), 0, stream, p));
     case 1:
-      if (p.ids_eff == nullptr) return -1;
-      return static_cast<int>(launch_kernel(ep_recv_kernel,
-                                            dim3(ep_grid((static_cast<long long>(p.world) * p.cap + 31) / 32)),
-                                            dim3(kEpThreads), 0, stream, p));
+      if (p.ids_eff == nullptr || p.rowmap == nullptr || p.nrecv == nullptr) return -1;
+      // a few CTAs: the rows in use are normally a small part of the receive area
+      return static_cast<int>(launch_kernel(ep_recv_kernel, dim3(32), dim3(kEpThreads), 0, stream, p));
     case 2:
       return static_cast<int>(launch_kernel(ep_ready_kernel, dim3(1), dim3(32), 0, stream, p));
     case 3:

@@ -101,8 +101,12 @@ __global__ void moe_route_kernel(const __nv_bfloat16* __restrict__ logits, int* 
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ topk_ids, int* __restrict__ expert_offsets,
                  int* __restrict__ sorted_pair, int* __restrict__ sorted_token, int pairs, int k,
-                 int e_begin, int e_end) {
+                 int e_begin, int e_end, const int* __restrict__ n_pairs_dev,
+                 const int* __restrict__ token_map) {
   extern __shared__ int sh[];
+  // n_pairs_dev: the pair count lives on the device (at most ``pairs``); token_map: the row of x that
+  // token i stands for (a compacted list of rows of a larger buffer)
+  if (n_pairs_dev) pairs = min(pairs, max(*n_pairs_dev, 0));
   const int El = e_end - e_begin;
   int* count = sh;            // [El]
   int* cursor = sh + El;      // [El]
@@ -137,7 +141,7 @@ moe_align_kernel(const int* __restrict__ topk_ids, int* __restrict__ expert_offs
       if (hit) {
         const int r = pos + __popc(m & ((1u << lane) - 1u));
         sorted_pair[r] = i;
-        sorted_token[r] = i / k;
+        sorted_token[r] = token_map ? token_map[i / k] : i / k;
       }
       pos += __popc(m);
     }
@@ -148,11 +152,27 @@ __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x,
                                        const int* __restrict__ sorted_token,
                                        const int* __restrict__ total_rows,
                                        __nv_bfloat16* __restrict__ out, int dim) {
-  const int r = blockIdx.x;
-  if (r >= *total_rows) return;
-  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(sorted_token[r]) * dim);
-  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * dim);
-  for (int v = threadIdx.x; v < dim / 8; v += blockDim.x) dst[v] = src[v];
+  const int total = *total_rows;
+  for (int r = blockIdx.x; r < total; r += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(sorted_token[r]) * dim);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * dim);
+    for (int v = threadIdx.x; v < dim / 8; v += blockDim.x) dst[v] = src[v];
+  }
+}
+
+// out[sorted_token[r], :] = y[r, :] for the rows in use (the inverse of the gather when every token
+// has one pair, as the receive rows of the all-to-all path do: nothing is summed, unused rows of
+// ``out`` are left alone).
+__global__ void moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ y,
+                                        const int* __restrict__ sorted_token,
+                                        const int* __restrict__ total_rows,
+                                        __nv_bfloat16* __restrict__ out, int dim) {
+  const int total = *total_rows;
+  for (int r = blockIdx.x; r < total; r += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(y + static_cast<size_t>(r) * dim);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(sorted_token[r]) * dim);
+    for (int v = threadIdx.x; v < dim / 8; v += blockDim.x) dst[v] = src[v];
+  }
 }
 
 // inv_row[pair] = sorted row of the pair or -1 (not routed to a local expert)
@@ -237,7 +257,22 @@ extern "C" int mx_moe_align(const int* topk_ids, int* expert_offsets, int* sorte
   const int El = e_end - e_begin;
   if (El <= 0 || El > 4096) return -1;
   moe_align_kernel<<<1, 1024, 2 * El * sizeof(int), stream>>>(topk_ids, expert_offsets, sorted_row,
-                                                              sorted_token, T * k, k, e_begin, e_end);
+                                                              sorted_token, T * k, k, e_begin, e_end,
+                                                              nullptr, nullptr);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// As mx_moe_align with the number of (token, slot) pairs read on the device (n_pairs_dev, at most
+// max_tokens * k) and, optionally, sorted_token[r] = token_map[token] instead of the token's index.
+extern "C" int mx_moe_align_n(const int* topk_ids, const int* n_pairs_dev, const int* token_map,
+                              int* expert_offsets, int* sorted_row, int* sorted_token, int max_tokens,
+                              int k, int e_begin, int e_end, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int El = e_end - e_begin;
+  if (El <= 0 || El > 4096 || n_pairs_dev == nullptr) return -1;
+  moe_align_kernel<<<1, 1024, 2 * El * sizeof(int), stream>>>(topk_ids, expert_offsets, sorted_row,
+                                                              sorted_token, max_tokens * k, k, e_begin,
+                                                              e_end, n_pairs_dev, token_map);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -248,9 +283,18 @@ extern "C" int mx_moe_gather_rows_n(const void* x, const int* sorted_token, cons
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (max_rows <= 0) return 0;
   if (dim % 8) return -1;
-  moe_gather_rows_kernel<<<max_rows, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
-                                                       sorted_token, total_rows,
-                                                       static_cast<__nv_bfloat16*>(out), dim);
+  moe_gather_rows_kernel<<<min(max_rows, 148 * 16), 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), sorted_token, total_rows, static_cast<__nv_bfloat16*>(out), dim);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mx_moe_scatter_rows_n(const void* y, const int* sorted_token, const int* total_rows,
+                                     void* out, int max_rows, int dim, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (max_rows <= 0) return 0;
+  if (dim % 8) return -1;
+  moe_scatter_rows_kernel<<<min(max_rows, 148 * 16), 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(y), sorted_token, total_rows, static_cast<__nv_bfloat16*>(out), dim);
   return static_cast<int>(cudaGetLastError());
 }
 

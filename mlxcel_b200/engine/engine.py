@@ -800,11 +800,12 @@ class Engine:
         """One tick of a data-parallel rank whose MoE layers exchange rows with the other ranks: all
         ranks run exactly one forward pass per tick in which anyone has work (a null forward here when
         this rank has nothing scheduled), none when everybody is idle."""
-        self.dp_active = self.model.comm.any_work(self.has_work()) > 0
-        if not self.dp_active:
-            return []
         decode, pieces = self._schedule() if self.has_work() else ([], [])
+        tokens = len(decode) + sum(p[2] for p in pieces)
+        self.dp_active = self.model.comm.any_work(self.has_work(), tokens) > 0
         ended, self._evicted = self._evicted, []
+        if not self.dp_active:
+            return ended
         if not decode and not pieces:
             self.model.forward_null()
             self.stats["null_forwards"] = self.stats.get("null_forwards", 0) + 1
@@ -842,7 +843,9 @@ class Engine:
         b, R = self._build_batch(decode, pieces)
         nd = len(decode)
         logits = None
-        if not pieces and nd:
+        # a decode graph holds the expert kernels chosen for decode-sized groups; in a tick in which
+        # another data-parallel rank prefills, this rank's experts get that rank's rows too
+        if not pieces and nd and not (self.dp_lockstep and getattr(self.model.comm, "heavy", False)):
             gl = self._decode_graph(nd, b.dec_max_len)
             if gl is not None:
                 logits = gl[:nd]

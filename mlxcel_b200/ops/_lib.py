@@ -92,6 +92,8 @@ def _declare(lib) -> None:
         "mx_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
         "mx_moe_align": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
         "mx_moe_gather_rows_n": [_vp, _vp, _vp, _vp, _i, _i, _vp],
+        "mx_moe_align_n": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+        "mx_moe_scatter_rows_n": [_vp, _vp, _vp, _vp, _i, _i, _vp],
         "mx_moe_combine_n": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
         "mx_qmv": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
         "mx_grouped_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _ll,

@@ -241,3 +241,45 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate_up
     _lib.count_launch(3)
     _lib.check(rc, "mx_moe_combine_n")
     return out
+
+
+def moe_experts_rows(x: torch.Tensor, ids_c: torch.Tensor, row_map: torch.Tensor, n_rows: torch.Tensor, w_gate_up,
+                     w_down, inter: int, act: str, b_gate_up=None, b_down=None, e_begin: int = 0,
+                     alpha: float = 1.702, limit: float = 7.0, out: torch.Tensor | None = None,
+                     rows_hint: int | None = None) -> torch.Tensor:
+    """The local experts' gated MLPs over a COMPACT LIST of rows of a larger buffer: entry i (for
+    i < ``n_rows[0]``, a count that lives on the device) is row ``row_map[i]`` of ``x`` and goes to expert
+    ``ids_c[i]``; its output is written to the same row of ``out``. Rows that are not in the list are
+    neither read nor written, and every kernel's work is bounded by the count, not by the size of
+    ``x``: this is the expert stage of the all-to-all path, whose receive area is sized for the worst
+    case (every rank sends all its pairs to one rank) while a step fills a small part of it."""
+    R, H = x.shape
+    El = w_gate_up.shape[0]
+    if out is None:
+        out = torch.zeros(R, w_down.shape[1], dtype=x.dtype, device=x.device)
+    if not x.is_cuda:
+        n = int(n_rows[0])
+        rows = row_map[:n].long()
+        o = moe_experts(x[rows], ids_c[:n].view(n, 1), torch.ones(n, 1), w_gate_up, w_down, inter, act, b_gate_up,
+                        b_down, e_begin=e_begin, alpha=alpha, limit=limit)
+        out[rows] = o.to(out.dtype)
+        return out
+    dev, lib, st = x.device, _lib.load(), _lib.stream()
+    offsets = torch.empty(El + 1, dtype=torch.int32, device=dev)
+    sorted_pair = torch.empty(R, dtype=torch.int32, device=dev)
+    sorted_row = torch.empty(R, dtype=torch.int32, device=dev)
+    rc = lib.mx_moe_align_n(ids_c.data_ptr(), n_rows.data_ptr(), row_map.data_ptr(), offsets.data_ptr(),
+                            sorted_pair.data_ptr(), sorted_row.data_ptr(), R, 1, e_begin, e_begin + El, st)
+    _lib.check(rc, "mx_moe_align_n")
+    total = offsets[El:]
+    xs = torch.empty(R, H, dtype=x.dtype, device=dev)
+    rc = lib.mx_moe_gather_rows_n(x.data_ptr(), sorted_row.data_ptr(), total.data_ptr(), xs.data_ptr(), R, H, st)
+    _lib.check(rc, "mx_moe_gather_rows_n")
+    a = grouped_linear(xs, w_gate_up, offsets, inter, b_gate_up, act, alpha, limit, rows_hint=rows_hint)
+    y = grouped_linear(a, w_down, offsets, w_down.shape[1], b_down, None, rows_hint=rows_hint)
+    assert out.shape == (R, w_down.shape[1]) and out.is_contiguous() and out.dtype == x.dtype
+    rc = lib.mx_moe_scatter_rows_n(y.data_ptr(), sorted_row.data_ptr(), total.data_ptr(), out.data_ptr(), R,
+                                   w_down.shape[1], st)
+    _lib.check(rc, "mx_moe_scatter_rows_n")
+    _lib.count_launch(3)
+    return out

@@ -95,9 +95,21 @@ class DpEpComm(LocalComm):
             self.a2a = GlooAllToAll(group, epr)
             self.a2a.dry = False
             self.host_group = host_group or group
+        self.tick_tokens, self.heavy = 0, False
 
-    def any_work(self, mine: bool) -> int:
-        """How many ranks have work this tick (one small host all-reduce)."""
-        t = torch.tensor([1 if mine else 0], dtype=torch.int32)
+    def any_work(self, mine: bool, tokens: int = 0) -> int:
+        """How many ranks have work this tick (one small host all-reduce). The same message sums the
+        ranks' token counts of the tick: every rank's experts see rows of all ranks, so the expected
+        rows per rank (what picks the weight-streaming or the dense expert kernels) is a global
+        figure, not this rank's. ``heavy`` afterwards says whether that figure is beyond the
+        weight-streaming kernel's range (a rank that decodes while another one prefills)."""
+        t = torch.tensor([1 if mine else 0, int(tokens)], dtype=torch.int64)
         dist.all_reduce(t, group=self.host_group)
-        return int(t.item())
+        self.tick_tokens = int(t[1])
+        k = getattr(self.a2a, "k", 1)
+        hint = max(1, -(-self.tick_tokens * k // self.ep_size))
+        if hasattr(self.a2a, "rows_hint"):
+            self.a2a.rows_hint = hint
+        from ..ops import moe as moe_ops
+        self.heavy = hint > moe_ops._QGEMV_MAX_ROWS * getattr(self.a2a, "epr", 1)
+        return int(t[0])

@@ -37,7 +37,7 @@ class _EpCall(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_int) for n in ("rank", "world", "T", "k", "H", "experts_per_rank", "cap")]
                 + [("reserved", ctypes.c_uint)]
                 + [(n, ctypes.c_ulonglong) for n in ("epoch", "status", "x", "ids", "wts", "residual", "out", "cnt", "ticket",
-                                                     "route", "ids_eff", "meta", "count", "dflag", "cflag")]
+                                                     "route", "ids_eff", "rowmap", "nrecv", "meta", "count", "dflag", "cflag")]
                 + [(n, ctypes.c_ulonglong * _MAX_RANKS) for n in ("recv_peer", "meta_peer", "count_peer",
                                                                   "dflag_peer", "cflag_peer", "ret_peer")])
 
@@ -80,13 +80,19 @@ class EpAllToAll:
         self.ret = local[self.lay["ret"]:self.lay["ret"] + rows * hidden * 2].view(torch.bfloat16).view(rows, hidden)
         self.cnt = torch.zeros(world + 2, dtype=torch.int32, device=dev)          # [world] counters, ticket, epoch
         self.route = torch.full((max_tokens * k,), -1, dtype=torch.int32, device=dev)
+        # compact list of the receive rows in use (expert id, row index) and their number: the receive
+        # area is sized for the worst case, the expert stage only ever touches the rows that arrived
         self.ids_eff = torch.full((rows, 1), -1, dtype=torch.int32, device=dev)
-        self.ones = torch.ones(rows, 1, dtype=torch.float32, device=dev)
+        self.rowmap = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.nrecv = torch.zeros(1, dtype=torch.int32, device=dev)
         self._T = 0
         # dry: a forward pass that must not talk to the other ranks (the warm-up before a CUDA-graph
         # capture is a pass of this rank alone). The exchanges are skipped, the local expert kernels
         # still run (their lazy set-up is what the warm-up is for) and the layer returns its residual.
         self.dry = False
+        # expected rows at this rank this step when the caller knows better than "as many as I send"
+        # (token counts differ between data-parallel ranks); picks the expert kernels
+        self.rows_hint: int | None = None
         self._build_call()
 
     # ------------------------------------------------------------------ constructors
@@ -121,6 +127,7 @@ class EpAllToAll:
         c.cnt, c.ticket = self.cnt.data_ptr(), self.cnt.data_ptr() + 4 * self.world
         c.epoch = self.cnt.data_ptr() + 4 * (self.world + 1)
         c.route, c.ids_eff = self.route.data_ptr(), self.ids_eff.data_ptr()
+        c.rowmap, c.nrecv = self.rowmap.data_ptr(), self.nrecv.data_ptr()
         me = self.bases[self.rank]
         c.meta, c.count = me + self.lay["meta"], me + self.lay["count"]
         c.dflag, c.cflag = me + self.lay["dflag"], me + self.lay["cflag"]
@@ -161,9 +168,9 @@ class EpAllToAll:
         self._call(1)
         # rows in use are known on the device only; with balanced routing a rank receives about as many
         # rows as it sends, which is what picks the decode (weight-streaming) or prefill expert kernels
-        moe_ops.moe_experts(self.recv, self.ids_eff, self.ones, w_gate_up, w_down, inter, act, b_gate_up, b_down,
-                            e_begin=self.rank * self.epr, alpha=alpha, limit=limit, out=self.ret,
-                            rows_hint=max(1, self._T * self.k))
+        moe_ops.moe_experts_rows(self.recv, self.ids_eff, self.rowmap, self.nrecv, w_gate_up, w_down, inter, act,
+                                 b_gate_up, b_down, e_begin=self.rank * self.epr, alpha=alpha, limit=limit,
+                                 out=self.ret, rows_hint=max(1, self.rows_hint or self._T * self.k))
         self._call(2)
 
     def combine(self, wts: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
@@ -178,9 +185,10 @@ class EpAllToAll:
             residual=None, alpha: float = 1.702, limit: float = 7.0) -> torch.Tensor:
         """One expert-parallel MoE layer (collective over the ranks of the heap)."""
         if self.dry:
-            moe_ops.moe_experts(self.recv, self.ids_eff, self.ones, w_gate_up, w_down, inter, act, b_gate_up, b_down,
-                                e_begin=self.rank * self.epr, alpha=alpha, limit=limit, out=self.ret,
-                                rows_hint=max(1, x.shape[0] * self.k))
+            self.nrecv.zero_()
+            moe_ops.moe_experts_rows(self.recv, self.ids_eff, self.rowmap, self.nrecv, w_gate_up, w_down, inter, act,
+                                     b_gate_up, b_down, e_begin=self.rank * self.epr, alpha=alpha, limit=limit,
+                                     out=self.ret, rows_hint=max(1, x.shape[0] * self.k))
             return residual.clone() if residual is not None else torch.zeros_like(x)
         self.dispatch(x, ids)
         self.expert_stage(w_gate_up, w_down, inter, act, b_gate_up, b_down, alpha, limit)

@@ -11,12 +11,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.mark.parametrize("world,E,k,H,I,act", [(4, 8, 2, 256, 128, "silu"), (2, 6, 3, 320, 192, "clipped_swiglu"),
-                                               (8, 32, 4, 2880, 256, "clipped_swiglu")])
-def test_ep_dispatch_combine_emulated(world, E, k, H, I, act):
+@pytest.mark.parametrize("world,E,k,H,I,act,slack", [(4, 8, 2, 256, 128, "silu", 1), (2, 6, 3, 320, 192, "clipped_swiglu", 1),
+                                                     (8, 32, 4, 2880, 256, "clipped_swiglu", 1),
+                                                     (8, 32, 4, 512, 256, "clipped_swiglu", 32)])
+def test_ep_dispatch_combine_emulated(world, E, k, H, I, act, slack):
+    """``slack``: the receive area is that many times larger than any step fills (as in serving, where
+    it is sized for the longest prefill step and a decode step uses a sliver of it)."""
     epr = E // world
     Ts = [5, 0, 64, 33, 1, 17, 40, 8][:world]
-    Tmax = max(Ts)
+    Tmax = max(Ts) * slack
     cap = Tmax * k
     eps = EpAllToAll.emulated(world, torch.device(DEV), H, cap, epr, Tmax, k)
     g = torch.Generator().manual_seed(world + E)
