@@ -502,7 +502,58 @@ def moe_decode(T=128, E=128, k=4, H=2880, inter=2880, reps=0):
                               packed_mbytes=round(packed_bytes / 1e6, 1), gbs=round(packed_bytes / us / 1e3, 1))), flush=True)
 
 
-CASES = dict(mamba2=mamba2, moe_decode=moe_decode, attn_decode_kv=attn_decode_kv, qgemm_decode=qgemm_decode, qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
+def ep_stage(T=16, world=8, max_tokens=8192, E=128, k=4, H=2880, inter=2880):
+    """The all-to-all MoE layer of one data-parallel rank at serving sizes, with the ``world`` ranks
+    emulated on this GPU (their stages run rank after rank, so no kernel waits on another): T rows
+    per rank, receive areas sized for ``max_tokens`` rows per rank (what the engine allocates), E mxfp4
+    experts in all. CUDA events around rank 0's dispatch, expert stage and combine, median of 7
+    layers; the other ranks' stages run in between, untimed."""
+    from mlxcel_b200.models.weights import QuantizedTensor
+    from mlxcel_b200.ops import moe as moe_ops
+    from mlxcel_b200.parallel.ep_a2a import EpAllToAll
+
+    epr = E // world
+    eps = EpAllToAll.emulated(world, torch.device(DEV), H, max_tokens * k, epr, max_tokens, k)
+
+    def rand_q(n_rows, kdim):
+        packed = torch.randint(0, 2 ** 31 - 1, (epr, n_rows, kdim // 8), dtype=torch.int32, device=DEV).view(torch.uint32)
+        scales = torch.randint(118, 124, (epr, n_rows, kdim // 32), dtype=torch.uint8, device=DEV)
+        return QuantizedTensor(packed, scales, None, 4, 32, "mxfp4")
+    wgu, wd = rand_q(2 * inter, H), rand_q(H, inter)          # one shard, used by every emulated rank
+    bgu, bd = _bf(epr, 2 * inter, scale=0.1), _bf(epr, H, scale=0.1)
+    x = _bf(T, H)
+    ids, wts = moe_ops.route(_bf(T, E), k, "topk_softmax", True)
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    rec = dict(dispatch=[], experts=[], combine=[])
+    for it in range(9):
+        marks = [ev() for _ in range(6)]
+        torch.cuda.synchronize()
+        marks[0].record()
+        eps[0].dispatch(x, ids)
+        marks[1].record()
+        for r in range(1, world):
+            eps[r].dispatch(x, ids)
+        marks[2].record()
+        eps[0].expert_stage(wgu, wd, inter, "clipped_swiglu", bgu, bd)
+        marks[3].record()
+        for r in range(1, world):
+            eps[r].expert_stage(wgu, wd, inter, "clipped_swiglu", bgu, bd)
+        marks[4].record()
+        out = eps[0].combine(wts, x)
+        marks[5].record()
+        for r in range(1, world):
+            eps[r].combine(wts, x)
+        torch.cuda.synchronize()
+        if it >= 2:
+            rec["dispatch"].append(marks[0].elapsed_time(marks[1]) * 1e3)
+            rec["experts"].append(marks[2].elapsed_time(marks[3]) * 1e3)
+            rec["combine"].append(marks[4].elapsed_time(marks[5]) * 1e3)
+    med = {n: round(sorted(v)[len(v) // 2], 1) for n, v in rec.items()}
+    print(json.dumps(dict(op="ep_stage", T=T, world=world, cap=max_tokens * k, E=E, k=k, H=H, inter=inter,
+                          eager_us=med, finite=bool(torch.isfinite(out.float()).all()))), flush=True)
+
+
+CASES = dict(ep_stage=ep_stage, mamba2=mamba2, moe_decode=moe_decode, attn_decode_kv=attn_decode_kv, qgemm_decode=qgemm_decode, qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
              attn_prefill=attn_prefill, decode_steps=decode_steps, kbench=kbench)
 
 if __name__ == "__main__":
