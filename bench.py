@@ -366,6 +366,11 @@ def main() -> None:
         extra["speculative"] = {"kind": drafter_note, "rounds": sd["spec_rounds"], "drafted": sd["spec_drafted"],
                                 "accepted": sd["spec_accepted"],
                                 "acceptance": round(sd["spec_accepted"] / sd["spec_drafted"], 4) if sd["spec_drafted"] else None}
+    if os.environ.get("MLXCEL_B200_STEP_TIMING", "0") == "1":
+        # whole-run sums of the engine's per-step event timings (warm-up rounds included): the gap between
+        # wall and device time is host work, which the lookahead pipeline hides where it is on
+        extra["step_timing"] = {k: round(v, 1) if isinstance(v, float) else v for k, v in eng.stats.items()
+                                if k.endswith(("_gpu_ms", "_wall_ms", "_timed_steps", "tick_sync_ms", "null_forwards"))}
     status = _lib.read_status(dev)
     if rank == 0:
         value = m["value"]

@@ -558,7 +558,9 @@ def _qwen3_next(c: ModelConfig, raw: dict) -> None:
     """Qwen3-Next: Gated DeltaNet layers and gated full-attention layers (per-head (1 + w) q/k norms,
     rotary embedding on a quarter of each head, sigmoid output gate), each followed by a MoE with a
     gated shared expert (or a dense MLP); norms are stored as (weight - 1)
-    (reference src/models/qwen3_next.rs). Runs on the hybrid executor as ``L`` / ``A`` + ``E`` / ``G``."""
+    (reference src/models/qwen3_next.rs). Runs on the hybrid executor as ``L`` / ``A`` + ``E`` / ``G``.
+    Qwen3.5 (dense) and Qwen3.5-MoE language models are the same stack with the linear-attention input
+    projection stored as four matrices (reference src/models/qwen3_5.rs)."""
     n = c.num_hidden_layers
     types = raw.get("layer_types")
     if not types:
@@ -1030,7 +1032,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

@@ -13,6 +13,7 @@ kernel reads is a persistent device tensor that the host refreshes from pinned m
 """
 from __future__ import annotations
 
+import os
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -169,6 +170,9 @@ class Engine:
         self.spec_policy = None      # optional speculative.policy.SpecPolicy (adaptive on / off)
         self._evicted: list[Sequence] = []   # rows the scheduler had to end (pool exhausted), reported by step()
         self._alloc_buffers()
+        # MLXCEL_B200_STEP_TIMING=1: CUDA events around every non-pipelined step; the sums land in stats
+        # as {decode,mixed}_{gpu_ms,wall_ms,timed_steps} (the gap between the two is host time)
+        self._step_timing = self.is_cuda and os.environ.get("MLXCEL_B200_STEP_TIMING", "0") == "1"
         self.stats = dict(steps=0, decode_steps=0, prefill_tokens=0, decode_tokens=0, preemptions=0,
                           graph_replays=0, prefix_hit_tokens=0, h2d_bytes=0, d2h_bytes=0,
                           graph_kernel_launches=0, spec_rounds=0, spec_drafted=0, spec_accepted=0)
@@ -802,7 +806,9 @@ class Engine:
         this rank has nothing scheduled), none when everybody is idle."""
         decode, pieces = self._schedule() if self.has_work() else ([], [])
         tokens = len(decode) + sum(p[2] for p in pieces)
+        t0 = time.perf_counter()
         self.dp_active = self.model.comm.any_work(self.has_work(), tokens) > 0
+        self.stats["tick_sync_ms"] = self.stats.get("tick_sync_ms", 0.0) + (time.perf_counter() - t0) * 1e3
         ended, self._evicted = self._evicted, []
         if not self.dp_active:
             return ended
@@ -843,6 +849,10 @@ class Engine:
         b, R = self._build_batch(decode, pieces)
         nd = len(decode)
         logits = None
+        timing = self._step_timing
+        if timing:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
         # a decode graph holds the expert kernels chosen for decode-sized groups; in a tick in which
         # another data-parallel rank prefills, this rank's experts get that rank's rows too
         if not pieces and nd and not (self.dp_lockstep and getattr(self.model.comm, "heavy", False)):
@@ -869,6 +879,15 @@ class Engine:
             toks, lps = self.model.sample_and_share(logits, sample_seqs, self.sampler)
         else:
             toks, lps = self.sampler.sample(logits, sample_seqs)
+        if timing:
+            # device time of the forward pass + sampling against the wall time of the whole step
+            ev1.record()
+            ev1.synchronize()
+            kind = "decode" if not pieces else "mixed"
+            st = self.stats
+            st[f"{kind}_timed_steps"] = st.get(f"{kind}_timed_steps", 0) + 1
+            st[f"{kind}_gpu_ms"] = st.get(f"{kind}_gpu_ms", 0.0) + ev0.elapsed_time(ev1)
+            st[f"{kind}_wall_ms"] = st.get(f"{kind}_wall_ms", 0.0) + (time.perf_counter() - t_step) * 1e3
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += nd
         self.stats["prefill_tokens"] += sum(p[2] for p in pieces)

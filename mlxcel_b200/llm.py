@@ -27,7 +27,8 @@ class LLM:
             cfg.extra.setdefault("served_context", int(engine_config.max_model_len))
         if model is not None:
             self.model = model
-        elif cfg.model_type in ("mamba", "mamba2", "nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "falcon_h1", "lfm2"):
+        elif cfg.model_type in ("mamba", "mamba2", "nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "qwen3_5", "qwen3_5_text",
+                                "qwen3_5_moe", "qwen3_5_moe_text", "falcon_h1", "lfm2"):
             from .models.hybrid import HybridModel
             from .models.mamba1 import Mamba1Model
             from .models.mamba2 import Mamba2Model
@@ -104,7 +105,7 @@ class LLM:
             from .models.hybrid import load_lfm2_weights
             return LLM(cfg, load_lfm2_weights(path, cfg, device=device), engine_config, comm=comm,
                        tokenizer=load_tokenizer(path))
-        if cfg.model_type == "qwen3_next":
+        if cfg.extra.get("hybrid_layout") == "qwen3_next":
             from .models.hybrid import load_qwen3_next_weights
             return LLM(cfg, load_qwen3_next_weights(path, cfg, device=device), engine_config, comm=comm,
                        tokenizer=load_tokenizer(path))

@@ -372,17 +372,25 @@ def load_qwen3_next_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device
     def plus1(name):
         return (need(g.vec(name), name).float() + 1.0).to(dtype)
 
+    # Qwen3.5 checkpoints keep the language model under ``model.language_model`` and store the
+    # linear-attention input projection as four matrices already ordered q | k | v, z, b, a
+    root = "model.language_model." if src.has("model.language_model.embed_tokens.weight") else "model."
     blocks, attn_layers = [], []
     for i in range(cfg.num_hidden_layers):
-        p = f"model.layers.{i}."
+        p = f"{root}layers.{i}."
         norm = plus1(p + "input_layernorm.weight")
-        if src.has(p + "linear_attn.in_proj_qkvz.weight"):
+        if src.has(p + "linear_attn.out_proj.weight"):
             m = p + "linear_attn."
             cw = need(g.vec(m + "conv1d.weight"), m + "conv1d.weight")
             cw = cw.reshape(d["conv_dim"], d["K"]) if cw.dim() == 2 or cw.shape[1] == 1 else cw.squeeze(-1)
+            if src.has(m + "in_proj_qkvz.weight"):
+                in_proj = regroup_qkvz(need(g.mat(m + "in_proj_qkvz"), m + "in_proj_qkvz"), d)
+                in_ba = regroup_ba(need(g.mat(m + "in_proj_ba"), m + "in_proj_ba"), d)
+            else:
+                in_proj = torch.cat([need(g.mat(m + n), m + n) for n in ("in_proj_qkv", "in_proj_z")], 0).contiguous()
+                in_ba = torch.cat([need(g.mat(m + n), m + n) for n in ("in_proj_b", "in_proj_a")], 0).contiguous()
             lw = GdnLayerWeights(
-                norm=norm, in_proj=regroup_qkvz(need(g.mat(m + "in_proj_qkvz"), m + "in_proj_qkvz"), d),
-                in_proj_ba=regroup_ba(need(g.mat(m + "in_proj_ba"), m + "in_proj_ba"), d), conv_w=cw.float(),
+                norm=norm, in_proj=in_proj, in_proj_ba=in_ba, conv_w=cw.float(),
                 dt_bias=need(g.vec(m + "dt_bias"), m + "dt_bias").float(),
                 A_log=need(g.vec(m + "A_log"), m + "A_log").float(),
                 gnorm=need(g.vec(m + "norm.weight"), m + "norm.weight"),
@@ -415,9 +423,9 @@ def load_qwen3_next_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device
             blocks.append(HybridBlock("mlp", fn, up=_cat_rows([need(g.mat(f + "gate_proj"), f + "gate_proj"),
                                                                need(g.mat(f + "up_proj"), f + "up_proj")]),
                                       down=need(g.mat(f + "down_proj"), f + "down_proj"), gated=True))
-    embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")
+    embed = need(g.mat(root + "embed_tokens"), root + "embed_tokens")
     head = g.mat("lm_head") if src.has("lm_head.weight") and not cfg.tie_word_embeddings else None
-    return HybridWeights(embed=embed, blocks=blocks, final_norm=plus1("model.norm.weight"),
+    return HybridWeights(embed=embed, blocks=blocks, final_norm=plus1(root + "norm.weight"),
                          lm_head=embed if head is None else head.to(device), layers=attn_layers)
 
 

@@ -601,3 +601,53 @@ def test_falcon_h1_hybrid_matches_transformers(mixer_norm):
         for i, tok in enumerate(o.output):
             row = lg[n0 - 1 + i]
             assert row[tok].item() >= row.max().item() - 2e-3
+
+
+@pytest.mark.parametrize("mt", ["qwen3_5_text", "qwen3_5_moe_text"])
+def test_qwen3_5_matches_transformers(mt):
+    """Qwen3.5 language models (dense and MoE): the Qwen3-Next stack with the linear-attention input
+    projection stored as four matrices and the weights under ``model.language_model``."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.models.hybrid import HybridModel, load_qwen3_next_weights
+
+    torch.manual_seed(0)
+    moe = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
+               shared_expert_intermediate_size=96) if "moe" in mt else {}
+    try:
+        hc = AutoConfig.for_model(
+            mt, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=32, vocab_size=300, max_position_embeddings=256,
+            layer_types=["linear_attention", "linear_attention", "full_attention", "linear_attention"],
+            linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=24, linear_num_key_heads=2,
+            linear_num_value_heads=4, pad_token_id=0, **moe)
+        model = AutoModelForCausalLM.from_config(hc).float().eval()
+    except (KeyError, ValueError, ImportError) as e:
+        pytest.skip(f"transformers cannot build {mt}: {e}")
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.08)
+            elif "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tempfile.mkdtemp(prefix=f"parity_{mt}_")
+    model.save_pretrained(d, safe_serialization=True)
+    T = 24
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0]
+    cfg = ModelConfig.from_path(d)
+    assert cfg.extra["hybrid_pattern"] == ("LELEAELE" if moe else "LGLGAGLG") and cfg.rot_dim == 8
+    ours = HybridModel(cfg, load_qwen3_next_weights(d, cfg, dtype=torch.float32), max_seqs=4)
+    eng = Engine(ours, cfg, EngineConfig(num_blocks=64, block_size=16, max_batch=4, max_model_len=256,
+                                         max_num_batched_tokens=16))
+    outs = eng.generate([ids.tolist(), ids[:7].tolist()], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
+    for o, n0 in zip(outs, (T, 7)):
+        with torch.no_grad():
+            lg = model(torch.cat([ids[:n0], torch.tensor(o.output)])[None]).logits[0]
+        for i, tok in enumerate(o.output):
+            row = lg[n0 - 1 + i]
+            assert row[tok].item() >= row.max().item() - 2e-3
+    assert want.shape == (T, 300)
