@@ -766,6 +766,33 @@ def _phimoe(c: ModelConfig, raw: dict) -> None:
     c.extra["router_jitter"] = float(raw.get("router_jitter_noise", 0.01))
 
 
+def _dbrx(c: ModelConfig, raw: dict) -> None:
+    """DBRX: bias-free LayerNorm, one fused ``Wqkv`` whose output is clamped to +-clip_qkv, rotary GQA
+    attention, top-k of 16 gated experts with softmax over all experts renormalised over the chosen
+    ones (= softmax over the k logits) (reference src/models/dbrx.rs). The config nests its fields under
+    ``attn_config`` / ``ffn_config`` and uses the MPT names."""
+    a, f = raw.get("attn_config") or {}, raw.get("ffn_config") or {}
+    c.hidden_size = int(raw.get("d_model", c.hidden_size))
+    c.num_attention_heads = int(raw.get("n_heads", c.num_attention_heads))
+    c.num_hidden_layers = int(raw.get("n_layers", c.num_hidden_layers))
+    c.num_key_value_heads = int(a.get("kv_n_heads", c.num_attention_heads))
+    c.head_dim = c.hidden_size // c.num_attention_heads
+    c.max_position_embeddings = int(raw.get("max_seq_len", c.max_position_embeddings))
+    c.rope_theta = float(a.get("rope_theta", 10000.0))
+    c.rms_norm_eps = 1e-5
+    c.extra["norm"] = "layernorm"
+    if a.get("clip_qkv"):
+        c.extra["clip_qkv"] = float(a["clip_qkv"])
+    c.num_experts = int(f.get("moe_num_experts", 16))
+    c.num_experts_per_tok = int(f.get("moe_top_k", 4))
+    c.intermediate_size = c.moe_intermediate_size = int(f.get("ffn_hidden_size", 4 * c.hidden_size))
+    c.hidden_act = (f.get("ffn_act_fn") or {}).get("name", "silu")
+    c.moe_route_mode = "topk_softmax"
+    if f.get("moe_normalize_expert_weights") not in (1, 1.0):
+        raise ValueError("dbrx: only moe_normalize_expert_weights = 1 is supported")
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", False))
+
+
 def _hunyuan_dense(c: ModelConfig, raw: dict) -> None:
     """Hunyuan dense: Llama layout with per-head q/k RMSNorm applied after the rotary embedding
     (reference src/models/hunyuan_v1_dense.rs)."""
@@ -1032,7 +1059,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "dbrx": _dbrx, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

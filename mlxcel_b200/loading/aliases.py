@@ -84,6 +84,27 @@ def _rules(cfg) -> list[tuple[str, str, object]]:
                 (L + r"mlp\.c_fc\.bias", r"model.layers.\1.mlp.fc1.bias", None),
                 (L + r"mlp\.c_proj\.weight", r"model.layers.\1.mlp.fc2.weight", tr),
                 (L + r"mlp\.c_proj\.bias", r"model.layers.\1.mlp.fc2.bias", None)]
+    if mt == "dbrx":
+        E = cfg.num_experts
+        L = r"transformer\.blocks\.(\d+)\."
+        M = r"model.layers.\1."
+        stacked = lambda w: w.view(E, w.shape[0] // E, w.shape[1]).contiguous()                  # noqa: E731
+        stacked_t = lambda w: w.view(E, w.shape[0] // E, w.shape[1]).transpose(1, 2).contiguous()  # noqa: E731
+        return [(r"transformer\.wte\.(\w+)", r"model.embed_tokens.\1", None),
+                (r"transformer\.norm_f\.(\w+)", r"model.norm.\1", None),
+                (L + r"norm_attn_norm\.norm_1\.(\w+)", M + r"input_layernorm.\2", None),
+                (L + r"norm_attn_norm\.norm_2\.(\w+)", M + r"post_attention_layernorm.\2", None),
+                (L + r"norm_attn_norm\.attn\.Wqkv\.(\w+)", M + r"self_attn.qkv_proj.\2", None),
+                (L + r"norm_attn_norm\.attn\.out_proj\.(\w+)", M + r"self_attn.o_proj.\2", None),
+                (L + r"ffn\.router\.layer\.(\w+)", M + r"mlp.router.\2", None),
+                # original checkpoints: w1 / v1 / w2 stacked as [E * I, H] (w2 is used transposed)
+                (L + r"ffn\.experts\.mlp\.w1", M + r"mlp.experts.gate_proj.weight", stacked),
+                (L + r"ffn\.experts\.mlp\.v1", M + r"mlp.experts.up_proj.weight", stacked),
+                (L + r"ffn\.experts\.mlp\.w2", M + r"mlp.experts.down_proj.weight", stacked_t),
+                # converted checkpoints: one Linear per expert and projection
+                (L + r"ffn\.experts\.(\d+)\.w1\.(\w+)", M + r"mlp.experts.\2.gate_proj.\3", None),
+                (L + r"ffn\.experts\.(\d+)\.v1\.(\w+)", M + r"mlp.experts.\2.up_proj.\3", None),
+                (L + r"ffn\.experts\.(\d+)\.w2\.(\w+)", M + r"mlp.experts.\2.down_proj.\3", None)]
     return []
 
 

@@ -208,7 +208,8 @@ def _cat_rows(parts):
                                torch.cat([p.scales for p in parts], dim=-2),
                                None if q.biases is None else torch.cat([p.biases for p in parts], dim=-2),
                                q.bits, q.group_size, q.mode)
-    return torch.cat(parts, dim=0)
+    # rows are the second-to-last axis (stacked expert tensors carry the expert axis in front)
+    return torch.cat(parts, dim=0 if parts[0].dim() < 2 else -2)
 
 
 def _stack(parts):

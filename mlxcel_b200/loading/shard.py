@@ -22,7 +22,8 @@ def _rows(t, lo: int, hi: int):
         return QuantizedTensor(t.packed[..., lo:hi, :].contiguous(), t.scales[..., lo:hi, :].contiguous(),
                                None if t.biases is None else t.biases[..., lo:hi, :].contiguous(),
                                t.bits, t.group_size, t.mode)
-    return t[lo:hi].contiguous()
+    # stacked expert tensors [E, rows, cols]: rows are the middle axis
+    return (t[lo:hi] if t.dim() < 3 else t[:, lo:hi]).contiguous()
 
 
 def _cols(t, lo: int, hi: int):

@@ -142,6 +142,7 @@ class DecoderModel:
         self.fold_attn = self.fold_mlp = False
         self.nope_layers = frozenset(cfg.extra.get("nope_layers", ()))
         self.layernorm = cfg.extra.get("norm") == "layernorm"
+        self.clip_qkv = float(cfg.extra.get("clip_qkv") or 0.0)
         self.plain_mlp = cfg.extra.get("mlp") == "plain"
         self.general = self.layernorm or self.plain_mlp or bool(cfg.extra.get("parallel_block"))
         # Folding rewrites the projection weights in place, so only the owner of the weights asks for
@@ -196,6 +197,8 @@ class DecoderModel:
         if lw.mla is not None:
             return self._attention_mla(li, lw, x, b, kv)
         qkv = _linear_any(x, lw.wqkv, bias=lw.bqkv, row_norm=row_norm)
+        if self.clip_qkv:                                   # DBRX: symmetric clamp of the fused projection
+            qkv = qkv.clamp_(-self.clip_qkv, self.clip_qkv)
         q_norm, k_norm = lw.q_norm, lw.k_norm
         if q_norm is not None and cfg.extra.get("qk_norm_full"):
             # OLMo-2 / OLMoE: RMSNorm over the whole q and k projections (not per head), before RoPE

@@ -70,3 +70,90 @@ def test_preemption_recompute_keeps_tokens():
     tight = _eng(cfg, w, num_blocks=9, prefix_cache=False, watermark=0.0)   # 144 slots for 150 tokens
     got = [s.output for s in tight.generate(prompts, sp)]
     assert got == want and tight.stats["preemptions"] >= 1
+
+
+def test_dbrx_checkpoint_matches_a_plain_statement_of_the_model(tmp_path):
+    """DBRX from its original checkpoint layout (MPT names, nested config, experts stacked as
+    [E * I, H] with w2 used transposed): logits against a direct PyTorch statement of the model
+    written here (bias-free LayerNorm, clamped fused Wqkv, rotary GQA attention, softmax over all
+    experts -> top-k -> L1 renormalisation)."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from mlxcel_b200.llm import LLM
+
+    torch.manual_seed(0)
+    H, Hq, Hkv, D, I, E, k, V, L, clip = 64, 4, 2, 16, 48, 4, 2, 200, 2, 0.6
+    cfgd = dict(model_type="dbrx", d_model=H, n_heads=Hq, n_layers=L, max_seq_len=256, vocab_size=V,
+                attn_config=dict(kv_n_heads=Hkv, clip_qkv=clip, rope_theta=10000.0),
+                ffn_config=dict(ffn_hidden_size=I, moe_num_experts=E, moe_top_k=k, moe_normalize_expert_weights=1.0,
+                                ffn_act_fn=dict(name="silu")), tie_word_embeddings=False)
+    r = lambda *s, sc=0.15: torch.randn(*s) * sc  # noqa: E731
+    t = {"transformer.wte.weight": r(V, H, sc=0.5), "transformer.norm_f.weight": 1 + r(H, sc=0.1), "lm_head.weight": r(V, H)}
+    for i in range(L):
+        b = f"transformer.blocks.{i}."
+        t[b + "norm_attn_norm.norm_1.weight"] = 1 + r(H, sc=0.1)
+        t[b + "norm_attn_norm.norm_2.weight"] = 1 + r(H, sc=0.1)
+        t[b + "norm_attn_norm.attn.Wqkv.weight"] = r((Hq + 2 * Hkv) * D, H, sc=0.3)
+        t[b + "norm_attn_norm.attn.out_proj.weight"] = r(H, Hq * D)
+        t[b + "ffn.router.layer.weight"] = r(E, H, sc=0.5)
+        for n in ("w1", "v1", "w2"):
+            t[b + f"ffn.experts.mlp.{n}"] = r(E * I, H)
+    (tmp_path / "config.json").write_text(json.dumps(cfgd))
+    save_file({n: v.contiguous() for n, v in t.items()}, str(tmp_path / "model.safetensors"))
+
+    T = 19
+    ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(2))
+    F = torch.nn.functional
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.arange(T).float()[:, None] * inv[None]
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+    rot = lambda x: x * cos[:, None] + torch.cat([-x[..., D // 2:], x[..., :D // 2]], -1) * sin[:, None]  # noqa: E731
+    h = t["transformer.wte.weight"][ids]
+    for i in range(L):
+        b = f"transformer.blocks.{i}."
+        x = F.layer_norm(h, (H,), t[b + "norm_attn_norm.norm_1.weight"], None, 1e-5)
+        qkv = (x @ t[b + "norm_attn_norm.attn.Wqkv.weight"].t()).clamp(-clip, clip)
+        q, kk, v = qkv.split([Hq * D, Hkv * D, Hkv * D], -1)
+        q, kk, v = rot(q.view(T, Hq, D)), rot(kk.view(T, Hkv, D)), v.view(T, Hkv, D)
+        kk, v = kk.repeat_interleave(Hq // Hkv, 1), v.repeat_interleave(Hq // Hkv, 1)
+        sc = torch.einsum("qhd,khd->hqk", q, kk) / D ** 0.5
+        sc = sc.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        a = torch.einsum("hqk,khd->qhd", sc.softmax(-1), v).reshape(T, Hq * D)
+        h = h + a @ t[b + "norm_attn_norm.attn.out_proj.weight"].t()
+        x = F.layer_norm(h, (H,), t[b + "norm_attn_norm.norm_2.weight"], None, 1e-5)
+        p = (x @ t[b + "ffn.router.layer.weight"].t()).softmax(-1)
+        w, idx = p.topk(k, -1)
+        w = w / w.sum(-1, keepdim=True)
+        w1, v1, w2 = (t[b + f"ffn.experts.mlp.{n}"].view(E, I, H) for n in ("w1", "v1", "w2"))
+        y = torch.zeros_like(x)
+        for tok in range(T):
+            for s in range(k):
+                e = int(idx[tok, s])
+                y[tok] += w[tok, s] * ((F.silu(x[tok] @ w1[e].t()) * (x[tok] @ v1[e].t())) @ w2[e])
+        h = h + y
+    want = F.layer_norm(h, (H,), t["transformer.norm_f.weight"], None, 1e-5) @ t["lm_head.weight"].t()
+    assert (qkv.abs() == clip).any()                      # the clamp is active in this test
+
+    from mlxcel_b200.cache.kv_pool import KVPool
+    from mlxcel_b200.loading.checkpoint import load_full_weights
+    from mlxcel_b200.models.decoder import StepBatch
+    cfg = ModelConfig.from_path(str(tmp_path))
+    assert cfg.num_experts == E and cfg.extra["clip_qkv"] == clip and cfg.num_key_value_heads == Hkv
+    model = DecoderModel(cfg, load_full_weights(str(tmp_path), cfg, dtype=torch.float32))
+    pool = KVPool(cfg, 4, 16, device="cpu", dtype=torch.float32, num_layers=L)
+    sb = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32), slot_mapping=torch.arange(T, dtype=torch.int32),
+                   num_prefill_seqs=1, pf_block_tables=torch.arange(4, dtype=torch.int32)[None],
+                   pf_cu_q=torch.tensor([0, T], dtype=torch.int32), pf_context_lens=torch.tensor([T], dtype=torch.int32),
+                   pf_max_q_len=T, pf_cu_q_host=[0, T], logits_rows=torch.arange(T))
+    got = model.forward(sb, pool.layers).float()
+    assert (got - want).abs().max().item() < 2e-3 * max(1.0, want.abs().max().item())
+    # and through the public loader + engine (bf16 weights): the first greedy token agrees
+    llm = LLM.from_pretrained(str(tmp_path), device="cpu",
+                              engine_config=EngineConfig(max_batch=2, max_num_batched_tokens=64, num_blocks=32,
+                                                         max_model_len=128, cuda_graphs=False))
+    out = llm.generate(prompt_token_ids=[ids.tolist()], sampling_params=SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True))[0]
+    top2 = want[-1].topk(2).values
+    if float(top2[0] - top2[1]) > 0.05:
+        assert out.output[0] == int(want[-1].argmax())
