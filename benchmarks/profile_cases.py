@@ -502,6 +502,62 @@ def moe_decode(T=128, E=128, k=4, H=2880, inter=2880, reps=0):
                               packed_mbytes=round(packed_bytes / 1e6, 1), gbs=round(packed_bytes / us / 1e3, 1))), flush=True)
 
 
+def prefill_helpers(T=8192, Hq=64, Hkv=8, D=64, E=128, k=4):
+    """CUDA-event times (L2 flushed between launches, median of 9) of two helper kernels of a prefill step
+    at gpt-oss-120b sizes, each in both of its forms: the register-resident RoPE + KV-append kernel
+    (8-byte against 2/4-byte accesses) and the MoE alignment kernel (slice-per-warp against
+    scan-per-expert)."""
+    from mlxcel_b200.ops import KVLayer, _lib, moe as moe_ops, reference as ref
+
+    lib = _lib.load()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+
+    def timeit(fn, n=9):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(n):
+            flush.zero_()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return round(sorted(ts)[n // 2], 1)
+    bs = 16
+    nb = T // bs + 1
+    qkv = _bf(T, (Hq + 2 * Hkv) * D)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    slots = torch.arange(T, dtype=torch.int32, device=DEV)
+    inv = ref.rope_inv_freq(D, 150000.0, None)[0].to(DEV)
+    kv = KVLayer(torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device=DEV),
+                 torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device=DEV), None, None, bs, 16)
+    rope = lambda: ops.rope_append(qkv, pos, slots, inv, kv, Hq=Hq, Hkv=Hkv, D=D, rot_dim=D)  # noqa: E731
+    out = dict(op="prefill_helpers", T=T, heads=[Hq, Hkv, D], rope_mbytes=round((2 * qkv.numel() * 2) / 1e6, 1))
+    for name, on in (("rope_vec8_us", 1), ("rope_narrow_us", 0)):
+        lib.mx_set_rope_vec(on)
+        out[name] = timeit(rope)
+    lib.mx_set_rope_vec(1)
+    ids, _ = moe_ops.route(_bf(T, E), k, "topk_softmax", True)
+    offs = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    sp = torch.empty(T * k, dtype=torch.int32, device=DEV)
+    stok = torch.empty(T * k, dtype=torch.int32, device=DEV)
+    st = _lib.stream()
+    align = lambda: lib.mx_moe_align(ids.data_ptr(), offs.data_ptr(), sp.data_ptr(), stok.data_ptr(), T, k, 0, 0, E, st)  # noqa: E731
+    res = {}
+    for name, on in (("align_slices_us", 1), ("align_scan_us", 0)):
+        lib.mx_set_moe_align_fast(on)
+        out[name] = timeit(align)
+        torch.cuda.synchronize()
+        res[name] = (offs.clone(), sp.clone(), stok.clone())
+    lib.mx_set_moe_align_fast(1)
+    a, b = res["align_slices_us"], res["align_scan_us"]
+    out["align_forms_agree"] = bool(all(torch.equal(x, y) for x, y in zip(a, b)))
+    print(json.dumps(out), flush=True)
+
+
 def ep_stage(T=16, world=8, max_tokens=8192, E=128, k=4, H=2880, inter=2880):
     """The all-to-all MoE layer of one data-parallel rank at serving sizes, with the ``world`` ranks
     emulated on this GPU (their stages run rank after rank, so no kernel waits on another): T rows
@@ -553,7 +609,7 @@ def ep_stage(T=16, world=8, max_tokens=8192, E=128, k=4, H=2880, inter=2880):
                           eager_us=med, finite=bool(torch.isfinite(out.float()).all()))), flush=True)
 
 
-CASES = dict(ep_stage=ep_stage, mamba2=mamba2, moe_decode=moe_decode, attn_decode_kv=attn_decode_kv, qgemm_decode=qgemm_decode, qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
+CASES = dict(prefill_helpers=prefill_helpers, ep_stage=ep_stage, mamba2=mamba2, moe_decode=moe_decode, attn_decode_kv=attn_decode_kv, qgemm_decode=qgemm_decode, qgemm_graph=qgemm_graph, gemm_graph=gemm_graph, gemm_phases=gemm_phases, gemm_decode=gemm_decode, gemm_prefill=gemm_prefill, attn_decode=attn_decode,
              attn_prefill=attn_prefill, decode_steps=decode_steps, kbench=kbench)
 
 if __name__ == "__main__":

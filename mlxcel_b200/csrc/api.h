@@ -128,6 +128,8 @@ int mx_head_rmsnorm(void* x, const void* weight, int tokens, int heads, int head
 // per (token, head, group of 64) scale+bias sidecars (kv_bits = 8) of layout
 // [num_blocks, Hkv, block_size, D/64, 2] bf16.
 // q_norm_w / k_norm_w: optional per-head RMSNorm weights [D] applied before RoPE (Qwen3).
+// 0 selects the 2/4-byte-access form of the register-resident rope + append kernel.
+void mx_set_rope_vec(int on);
 int mx_rope_append(void* qkv, const int* positions, const int* slot_mapping, const float* inv_freq,
                    void* k_pool, void* v_pool, void* k_meta, void* v_meta, const void* q_norm_w,
                    const void* k_norm_w, float norm_eps, int T, int Hq, int Hkv, int D,
@@ -224,6 +226,8 @@ int mx_moe_route(const void* logits, int* topk_ids, float* topk_w, int T, int E,
                  int norm_topk, void* stream);
 
 // MoE token permutation helpers: count tokens per expert, exclusive scan, scatter rows.
+// 0 selects the scan-per-expert form of the alignment kernel (always used above 256 local experts).
+void mx_set_moe_align_fast(int on);
 int mx_moe_align(const int* topk_ids, int* expert_offsets, int* sorted_row, int* sorted_token,
                  int T, int k, int E, int e_begin, int e_end, void* stream);
 // The same with the pair count read on the device (*n_pairs_dev <= max_tokens * k) and, when

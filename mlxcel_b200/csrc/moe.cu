@@ -148,6 +148,84 @@ moe_align_kernel(const int* __restrict__ topk_ids, int* __restrict__ expert_offs
   }
 }
 
+// The same result (stable in token order) for up to kAlignFastMaxExperts local experts, without the
+// scatter's scan of all pairs per expert: warp w owns a contiguous slice of the pairs, counts its
+// pairs per expert, a scan over (expert, warp) gives every warp its first row of every expert, and
+// the warp then walks its slice once, 32 pairs per step, ranking equal experts inside a step with
+// __match_any_sync. 32768 pairs over 128 experts: 32 steps per warp instead of 4096.
+constexpr int kAlignFastMaxExperts = 256;
+
+__global__ void __launch_bounds__(1024)
+moe_align_fast_kernel(const int* __restrict__ topk_ids, int* __restrict__ expert_offsets,
+                      int* __restrict__ sorted_pair, int* __restrict__ sorted_token, int pairs, int k,
+                      int e_begin, int e_end, const int* __restrict__ n_pairs_dev,
+                      const int* __restrict__ token_map) {
+  extern __shared__ int sh[];
+  const int El = e_end - e_begin;
+  if (n_pairs_dev) pairs = min(pairs, max(*n_pairs_dev, 0));
+  int* wcount = sh;                    // [32][El]: pairs of warp w for expert e, then its first row
+  int* total = sh + 32 * El;           // [El]
+  for (int i = threadIdx.x; i < 32 * El; i += blockDim.x) wcount[i] = 0;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = ((pairs + 31) / 32 + 31) / 32 * 32;      // per warp, a multiple of 32
+  const int begin = warp * chunk, end = min(pairs, begin + chunk);
+  int* mine = wcount + warp * El;
+  for (int base = begin; base < end; base += 32) {
+    const int i = base + lane;
+    const int e = i < end ? topk_ids[i] : -1;
+    const bool hit = e >= e_begin && e < e_end;
+    const int key = hit ? e - e_begin : El + lane;           // lanes without a local expert match nobody
+    const unsigned m = __match_any_sync(0xffffffffu, key);
+    if (hit && (m & ((1u << lane) - 1u)) == 0u) mine[key] += __popc(m);   // lowest lane of each group
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < El; e += blockDim.x) {
+    int acc = 0;
+    for (int w = 0; w < 32; ++w) acc += wcount[w * El + e];
+    total[e] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < El; ++e) {
+      expert_offsets[e] = acc;
+      const int t = total[e];
+      total[e] = acc;
+      acc += t;
+    }
+    expert_offsets[El] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < El; e += blockDim.x) {
+    int run = total[e];
+    for (int w = 0; w < 32; ++w) {
+      const int c = wcount[w * El + e];
+      wcount[w * El + e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  for (int base = begin; base < end; base += 32) {
+    const int i = base + lane;
+    const int e = i < end ? topk_ids[i] : -1;
+    const bool hit = e >= e_begin && e < e_end;
+    const int key = hit ? e - e_begin : El + lane;
+    const unsigned m = __match_any_sync(0xffffffffu, key);
+    const unsigned before = m & ((1u << lane) - 1u);
+    int r = 0;
+    if (hit) r = mine[key] + __popc(before);
+    __syncwarp();                                            // everybody has read the cursor
+    if (hit) {
+      sorted_pair[r] = i;
+      sorted_token[r] = token_map ? token_map[i / k] : i / k;
+      if (before == 0u) mine[key] += __popc(m);
+    }
+    __syncwarp();
+  }
+}
+
 __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x,
                                        const int* __restrict__ sorted_token,
                                        const int* __restrict__ total_rows,
@@ -236,6 +314,10 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y,
 
 using namespace mx;
 
+// Switch for the slice-per-warp alignment kernel (on unless MLXCEL_B200_MOE_ALIGN_FAST=0 at load).
+static int g_align_fast = 1;
+extern "C" void mx_set_moe_align_fast(int on) { g_align_fast = on ? 1 : 0; }
+
 extern "C" int mx_moe_route(const void* logits, int* topk_ids, float* topk_w, int T, int E, int k,
                             int mode, int norm_topk, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -256,9 +338,14 @@ extern "C" int mx_moe_align(const int* topk_ids, int* expert_offsets, int* sorte
   (void)E;
   const int El = e_end - e_begin;
   if (El <= 0 || El > 4096) return -1;
-  moe_align_kernel<<<1, 1024, 2 * El * sizeof(int), stream>>>(topk_ids, expert_offsets, sorted_row,
-                                                              sorted_token, T * k, k, e_begin, e_end,
-                                                              nullptr, nullptr);
+  if (g_align_fast && El <= kAlignFastMaxExperts)
+    moe_align_fast_kernel<<<1, 1024, 33 * El * sizeof(int), stream>>>(topk_ids, expert_offsets, sorted_row,
+                                                                     sorted_token, T * k, k, e_begin, e_end,
+                                                                     nullptr, nullptr);
+  else
+    moe_align_kernel<<<1, 1024, 2 * El * sizeof(int), stream>>>(topk_ids, expert_offsets, sorted_row,
+                                                                sorted_token, T * k, k, e_begin, e_end,
+                                                                nullptr, nullptr);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -270,9 +357,14 @@ extern "C" int mx_moe_align_n(const int* topk_ids, const int* n_pairs_dev, const
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int El = e_end - e_begin;
   if (El <= 0 || El > 4096 || n_pairs_dev == nullptr) return -1;
-  moe_align_kernel<<<1, 1024, 2 * El * sizeof(int), stream>>>(topk_ids, expert_offsets, sorted_row,
-                                                              sorted_token, max_tokens * k, k, e_begin,
-                                                              e_end, n_pairs_dev, token_map);
+  if (g_align_fast && El <= kAlignFastMaxExperts)
+    moe_align_fast_kernel<<<1, 1024, 33 * El * sizeof(int), stream>>>(topk_ids, expert_offsets, sorted_row,
+                                                                     sorted_token, max_tokens * k, k, e_begin,
+                                                                     e_end, n_pairs_dev, token_map);
+  else
+    moe_align_kernel<<<1, 1024, 2 * El * sizeof(int), stream>>>(topk_ids, expert_offsets, sorted_row,
+                                                                sorted_token, max_tokens * k, k, e_begin,
+                                                                e_end, n_pairs_dev, token_map);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -42,6 +42,10 @@ def load(required: bool = True):
         try:
             _LIB = ctypes.CDLL(str(path))
             _declare(_LIB)
+            if os.environ.get("MLXCEL_B200_ROPE_VEC", "1") == "0" and hasattr(_LIB, "mx_set_rope_vec"):
+                _LIB.mx_set_rope_vec(0)
+            if os.environ.get("MLXCEL_B200_MOE_ALIGN_FAST", "1") == "0" and hasattr(_LIB, "mx_set_moe_align_fast"):
+                _LIB.mx_set_moe_align_fast(0)
             return _LIB
         except OSError as e:
             _LIB_ERR = str(e)

@@ -109,6 +109,38 @@ def _pool(nb, Hkv, bs, D, bits):
                    torch.zeros(nb, Hkv, bs, D // 64, 2, dtype=torch.bfloat16, device=DEV), bs, bits)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,qk", [(64, 8, 64, False), (32, 8, 128, True), (10, 2, 64, True)])
+@pytest.mark.parametrize("vec", ["1", "0"])
+def test_rope_append_prefill_sized(Hq, Hkv, D, qk, vec):
+    """Enough tokens that a warp owns several heads (the launch grows heads-per-warp with T): both
+    forms of the register-resident kernel against the fp32 statement."""
+    from mlxcel_b200.ops import _lib
+    T, bs = 2100, 16
+    nb = (T + bs - 1) // bs + 2
+    qkv = _bf(T, (Hq + 2 * Hkv) * D, seed=14)
+    pos = torch.randint(0, 9000, (T,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(nb * bs, device=DEV)[:T].to(torch.int32)
+    slots[::97] = -1
+    inv, _ = ref.rope_inv_freq(D, 150000.0, None)
+    inv = inv.to(DEV)
+    qn = _bf(D, seed=5) if qk else None
+    kn = _bf(D, seed=6) if qk else None
+    kv = _pool(nb, Hkv, bs, D, 16)
+    kv_ref = _clone_pool(kv)
+    q_ref = qkv.clone()
+    _lib.load().mx_set_rope_vec(int(vec))
+    try:
+        ops.rope_append(qkv, pos, slots, inv, kv, Hq=Hq, Hkv=Hkv, D=D, rot_dim=D, traditional=False,
+                        mscale=1.0, q_norm_w=qn, k_norm_w=kn, norm_eps=1e-6)
+    finally:
+        _lib.load().mx_set_rope_vec(1)
+    ref.rope_append(q_ref, pos, slots, inv, kv_ref, Hq=Hq, Hkv=Hkv, D=D, rot_dim=D, traditional=False,
+                    mscale=1.0, q_norm_w=qn, k_norm_w=kn, norm_eps=1e-6)
+    _close(qkv[:, : Hq * D], q_ref[:, : Hq * D], rtol=2e-2, atol=3e-2)
+    _close(kv.k, kv_ref.k, rtol=2e-2, atol=3e-2)
+    assert torch.equal(kv.v, kv_ref.v)
+
+
 def _clone_pool(kv):
     c = lambda t: None if t is None else t.clone()  # noqa: E731
     return KVLayer(c(kv.k), c(kv.v), c(kv.k_meta), c(kv.v_meta), kv.block_size, kv.kv_bits)
@@ -117,6 +149,7 @@ def _clone_pool(kv):
 @pytest.mark.parametrize("Hq,Hkv,D,rot,trad,qk", [
     (8, 2, 128, 128, False, False), (4, 4, 64, 64, True, False), (8, 1, 128, 64, False, True),
     (16, 2, 64, 64, False, True), (4, 2, 256, 256, False, False), (4, 1, 256, 0, False, True),
+    (8, 2, 64, 64, False, False), (8, 2, 128, 128, False, True), (5, 1, 64, 64, False, True), (3, 1, 128, 128, False, False),
 ])
 @pytest.mark.parametrize("bits", [16, 8, 4])
 def test_rope_append(Hq, Hkv, D, rot, trad, qk, bits):
