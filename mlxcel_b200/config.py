@@ -766,6 +766,42 @@ def _phimoe(c: ModelConfig, raw: dict) -> None:
     c.extra["router_jitter"] = float(raw.get("router_jitter_noise", 0.01))
 
 
+def _llama4(c: ModelConfig, raw: dict) -> None:
+    """Llama 4 language model (Scout / Maverick): interleaved (pairwise) rotary embedding on most
+    layers and none on every ``no_rope_layer_interval``-th, weightless per-head RMS ("L2") norm of q
+    and k on the rotary layers, a position-dependent query temperature on the others, and MoE layers
+    (``moe_layers``) whose router takes the sigmoid of the top-1 logit and scales the expert's INPUT
+    with it, beside an always-on shared expert; the other layers are dense MLPs of
+    ``intermediate_size_mlp`` (reference src/models/llama4.rs, llama4_helpers.rs). The rotary layers
+    attend inside chunks of ``attention_chunk_size`` tokens; contexts are served up to that size,
+    where chunked and full attention coincide."""
+    c.num_experts = int(raw.get("num_local_experts", 16))
+    c.num_experts_per_tok = int(raw.get("num_experts_per_tok", 1))
+    if c.num_experts_per_tok != 1:
+        raise ValueError("llama4: only top-1 routing is supported (the router score scales the expert input)")
+    c.moe_intermediate_size = int(raw.get("intermediate_size", 8192))
+    c.intermediate_size = int(raw.get("intermediate_size_mlp", 16384))
+    c.moe_route_mode = "sigmoid_input"
+    c.rope_traditional = True
+    flags = raw.get("no_rope_layers")
+    if not flags:
+        iv = int(raw.get("no_rope_layer_interval", 4))
+        flags = [int((i + 1) % iv != 0) for i in range(c.num_hidden_layers)]
+    c.extra["nope_layers"] = [i for i, f in enumerate(flags) if not f]
+    if raw.get("use_qk_norm", True):
+        c.qk_norm = True
+        c.extra["qk_norm_no_params"] = True
+        c.extra["qk_norm_rope_layers_only"] = True
+    if raw.get("attn_temperature_tuning", True):
+        c.extra["nope_query_temperature"] = (float(raw.get("attn_scale", 0.1)), float(raw.get("floor_scale", 8192)))
+    chunk = raw.get("attention_chunk_size")
+    if chunk:
+        c.extra["attention_chunk_size"] = int(chunk)
+        c.max_position_embeddings = min(c.max_position_embeddings, int(chunk))
+    c.sliding_window = 0
+    c.layer_types = None
+
+
 def _dbrx(c: ModelConfig, raw: dict) -> None:
     """DBRX: bias-free LayerNorm, one fused ``Wqkv`` whose output is clamped to +-clip_qkv, rotary GQA
     attention, top-k of 16 gated experts with softmax over all experts renormalised over the chosen
@@ -1059,7 +1095,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "dbrx": _dbrx, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

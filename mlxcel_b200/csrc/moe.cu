@@ -154,6 +154,7 @@ moe_align_kernel(const int* __restrict__ topk_ids, int* __restrict__ expert_offs
 // the warp then walks its slice once, 32 pairs per step, ranking equal experts inside a step with
 // __match_any_sync. 32768 pairs over 128 experts: 32 steps per warp instead of 4096.
 constexpr int kAlignFastMaxExperts = 256;
+constexpr int kAlignBatch = 8;
 
 __global__ void __launch_bounds__(1024)
 moe_align_fast_kernel(const int* __restrict__ topk_ids, int* __restrict__ expert_offsets,
@@ -171,14 +172,25 @@ moe_align_fast_kernel(const int* __restrict__ topk_ids, int* __restrict__ expert
   const int chunk = ((pairs + 31) / 32 + 31) / 32 * 32;      // per warp, a multiple of 32
   const int begin = warp * chunk, end = min(pairs, begin + chunk);
   int* mine = wcount + warp * El;
-  for (int base = begin; base < end; base += 32) {
-    const int i = base + lane;
-    const int e = i < end ? topk_ids[i] : -1;
-    const bool hit = e >= e_begin && e < e_end;
-    const int key = hit ? e - e_begin : El + lane;           // lanes without a local expert match nobody
-    const unsigned m = __match_any_sync(0xffffffffu, key);
-    if (hit && (m & ((1u << lane) - 1u)) == 0u) mine[key] += __popc(m);   // lowest lane of each group
-    __syncwarp();
+  // kAlignBatch steps per batch: their expert ids are loaded together (independent loads, one trip to
+  // memory), then the steps run in order
+  for (int base0 = begin; base0 < end; base0 += 32 * kAlignBatch) {
+    int eb[kAlignBatch];
+#pragma unroll
+    for (int u = 0; u < kAlignBatch; ++u) {
+      const int i = base0 + u * 32 + lane;
+      eb[u] = i < end ? topk_ids[i] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < kAlignBatch; ++u) {
+      if (base0 + u * 32 >= end) break;                      // warp-uniform
+      const int e = eb[u];
+      const bool hit = e >= e_begin && e < e_end;
+      const int key = hit ? e - e_begin : El + lane;         // lanes without a local expert match nobody
+      const unsigned m = __match_any_sync(0xffffffffu, key);
+      if (hit && (m & ((1u << lane) - 1u)) == 0u) mine[key] += __popc(m);   // lowest lane of each group
+      __syncwarp();
+    }
   }
   __syncthreads();
   for (int e = threadIdx.x; e < El; e += blockDim.x) {
@@ -207,22 +219,32 @@ moe_align_fast_kernel(const int* __restrict__ topk_ids, int* __restrict__ expert
     }
   }
   __syncthreads();
-  for (int base = begin; base < end; base += 32) {
-    const int i = base + lane;
-    const int e = i < end ? topk_ids[i] : -1;
-    const bool hit = e >= e_begin && e < e_end;
-    const int key = hit ? e - e_begin : El + lane;
-    const unsigned m = __match_any_sync(0xffffffffu, key);
-    const unsigned before = m & ((1u << lane) - 1u);
-    int r = 0;
-    if (hit) r = mine[key] + __popc(before);
-    __syncwarp();                                            // everybody has read the cursor
-    if (hit) {
-      sorted_pair[r] = i;
-      sorted_token[r] = token_map ? token_map[i / k] : i / k;
-      if (before == 0u) mine[key] += __popc(m);
+  for (int base0 = begin; base0 < end; base0 += 32 * kAlignBatch) {
+    int eb[kAlignBatch];
+#pragma unroll
+    for (int u = 0; u < kAlignBatch; ++u) {
+      const int i = base0 + u * 32 + lane;
+      eb[u] = i < end ? topk_ids[i] : -1;
     }
-    __syncwarp();
+#pragma unroll
+    for (int u = 0; u < kAlignBatch; ++u) {
+      if (base0 + u * 32 >= end) break;                      // warp-uniform
+      const int i = base0 + u * 32 + lane;
+      const int e = eb[u];
+      const bool hit = e >= e_begin && e < e_end;
+      const int key = hit ? e - e_begin : El + lane;
+      const unsigned m = __match_any_sync(0xffffffffu, key);
+      const unsigned before = m & ((1u << lane) - 1u);
+      int r = 0;
+      if (hit) r = mine[key] + __popc(before);
+      __syncwarp();                                          // everybody has read the cursor
+      if (hit) {
+        sorted_pair[r] = i;
+        sorted_token[r] = token_map ? token_map[i / k] : i / k;
+        if (before == 0u) mine[key] += __popc(m);
+      }
+      __syncwarp();
+    }
   }
 }
 

@@ -84,6 +84,16 @@ def _rules(cfg) -> list[tuple[str, str, object]]:
                 (L + r"mlp\.c_fc\.bias", r"model.layers.\1.mlp.fc1.bias", None),
                 (L + r"mlp\.c_proj\.weight", r"model.layers.\1.mlp.fc2.weight", tr),
                 (L + r"mlp\.c_proj\.bias", r"model.layers.\1.mlp.fc2.bias", None)]
+    if mt in ("llama4", "llama4_text"):
+        # ``feed_forward`` is this family's name of the MLP / MoE block; the routed experts are stored
+        # as [E, H, 2I] (gate columns, then up columns) and [E, I, H], i.e. transposed Linear weights
+        half = lambda which: (lambda w: w[..., : w.shape[-1] // 2].transpose(1, 2).contiguous() if which == 0  # noqa: E731
+                              else w[..., w.shape[-1] // 2:].transpose(1, 2).contiguous())
+        P = r"(.*layers\.\d+\.)feed_forward\."
+        return [(P + r"experts\.gate_up_proj", r"\1mlp.experts.gate_proj.weight", half(0)),
+                (P + r"experts\.gate_up_proj", r"\1mlp.experts.up_proj.weight", half(1)),
+                (P + r"experts\.down_proj", r"\1mlp.experts.down_proj.weight", lambda w: w.transpose(1, 2).contiguous()),
+                (P + r"((?!experts\.).*)", r"\1mlp.\2", None)]
     if mt == "dbrx":
         E = cfg.num_experts
         L = r"transformer\.blocks\.(\d+)\."
@@ -115,7 +125,6 @@ def aliases_for(cfg, keys) -> dict:
         return out
     for k in keys:
         for pat, rep, fn in rules:
-            if pat.match(k):
-                out[pat.sub(rep, k)] = (k, fn)
-                break
+            if pat.match(k):                     # (one tensor may be presented under several names)
+                out.setdefault(pat.sub(rep, k), (k, fn))
     return out

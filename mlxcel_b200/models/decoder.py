@@ -220,6 +220,15 @@ class DecoderModel:
         local = window > 0 and self.inv_freq_local is not None
         layer_index = self.layer_range[li] if li < len(self.layer_range) else li
         rot_dim = 0 if layer_index in self.nope_layers else cfg.rot_dim    # layers without positional encoding
+        if not rot_dim and cfg.extra.get("qk_norm_rope_layers_only"):
+            q_norm = k_norm = None                              # Llama 4: q/k norm on the rotary layers only
+        if not rot_dim and cfg.extra.get("nope_query_temperature"):
+            # Llama 4: queries of the layers without positions grow with the logarithm of their
+            # position block, which keeps long-context attention from flattening
+            a_s, floor_s = cfg.extra["nope_query_temperature"]
+            sc = 1.0 + a_s * torch.log1p(torch.floor((b.positions.float() + 1.0) / floor_s))
+            nq = self.Hq * self.D
+            qkv = torch.cat([(qkv[:, :nq].float() * sc[:, None]).to(qkv.dtype), qkv[:, nq:]], dim=1)
         if q_norm is not None and cfg.extra.get("qk_norm_after_rope") and rot_dim:
             # Hunyuan: the per-head q/k norms come AFTER the rotation; the fused kernel norms before it, so
             # rotate and normalise here and let the kernel only append

@@ -55,9 +55,18 @@ def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -
         ids, wts = moe_ops.route_sigmoid_grouped(logits, cfg.num_experts_per_tok, lw.router_b, r["n_group"],
                                                  r["topk_group"], cfg.norm_topk_prob, r["scale"], r.get("score", "sigmoid"),
                                                  r.get("norm_min", 1e-20), r.get("group_score", "top2sum"))
+    elif cfg.moe_route_mode == "sigmoid_input":
+        # Llama 4: top-1 expert; the sigmoid of its logit scales the expert's INPUT (so it passes
+        # through the activation), the output is summed unweighted
+        logits = ops.linear(x, lw.router_w, bias=lw.router_b)
+        top, ids = logits.float().topk(1, dim=-1)
+        x_shared, x = x, (x.float() * torch.sigmoid(top)).to(x.dtype)
+        ids, wts = ids.to(torch.int32).contiguous(), torch.ones_like(top)
     else:
         logits = ops.linear(x, lw.router_w, bias=lw.router_b)
         ids, wts = moe_ops.route(logits, cfg.num_experts_per_tok, cfg.moe_route_mode, cfg.norm_topk_prob)
+    if cfg.moe_route_mode != "sigmoid_input":
+        x_shared = x
     a2a = getattr(comm, "a2a", None)
     if a2a is not None:
         # token-sharded ranks: rows travel to the experts' owners and come back (parallel/dp_ep.py)
@@ -65,7 +74,7 @@ def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -
         out = a2a.moe(x, ids.int().contiguous(), wts.float().contiguous(), gu, dn, gu.shape[-2] // 2, cfg.hidden_act,
                       lw.experts_gate_up_b, lw.experts_down_b, residual=h, alpha=cfg.swiglu_alpha, limit=cfg.swiglu_limit)
         if lw.shared_gate_up is not None:
-            out = (out.float() + _shared_expert(cfg, lw, x).float()).to(out.dtype)
+            out = (out.float() + _shared_expert(cfg, lw, x_shared).float()).to(out.dtype)
         return out
     ep, ep_rank = comm.ep_size, comm.ep_rank
     # packed expert weights stay packed: the grouped GEMM unpacks the tiles of routed experts only
@@ -80,7 +89,7 @@ def moe_forward(cfg, lw: LayerWeights, x: torch.Tensor, h: torch.Tensor, comm) -
                               lw.experts_down_b, e_begin=ep_rank * El, residual=h if first else None,
                               alpha=cfg.swiglu_alpha, limit=cfg.swiglu_limit, rows_hint=hint)
     if lw.shared_gate_up is not None:
-        out = (out.float() + _shared_expert(cfg, lw, x).float()).to(out.dtype)
+        out = (out.float() + _shared_expert(cfg, lw, x_shared).float()).to(out.dtype)
     if ep > 1:
         out = comm.all_reduce(out)
     return out
