@@ -766,6 +766,21 @@ def _phimoe(c: ModelConfig, raw: dict) -> None:
     c.extra["router_jitter"] = float(raw.get("router_jitter_noise", 0.01))
 
 
+def _bitnet(c: ModelConfig, raw: dict) -> None:
+    """BitNet b1.58: the Llama layout with an RMSNorm of the attention output in front of ``o_proj``
+    (``attn_sub_norm``), one of ``relu(gate)^2 * up`` in front of ``down_proj`` (``ffn_sub_norm``), and
+    every projection stored as ternary weights packed four to a byte with one scale
+    (reference src/models/bitnet.rs). The packed projections are expanded to bf16 at load (their
+    values are exactly representable) and run on the dense GEMMs; like the reference's
+    ``bitlinear_matmul`` the activations are not quantized."""
+    c.hidden_act = "relu2"
+    c.extra["sub_norms"] = True
+    qc = raw.get("quantization_config") or {}
+    # packed scales divide the output unless the checkpoint was written by the "autobitlinear" class
+    c.extra["bitlinear_invert_scale"] = (qc.get("linear_class") or "bitlinear") != "autobitlinear"
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
+
+
 def _llama4(c: ModelConfig, raw: dict) -> None:
     """Llama 4 language model (Scout / Maverick): interleaved (pairwise) rotary embedding on most
     layers and none on every ``no_rope_layer_interval``-th, weightless per-head RMS ("L2") norm of q
@@ -1095,7 +1110,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

@@ -159,6 +159,8 @@ class _Getter:
         if not self.src.has(name):
             return None
         w = self.src.get(name)
+        if w.dtype == torch.uint8 and self.src.has(base + ".weight_scale"):
+            return self._unpack_bitlinear(base, w)
         sname = base + ".scales"
         if self.src.has(sname) and w.dtype in (torch.uint32, torch.int32, torch.uint8):
             scales = self.src.get(sname)
@@ -172,6 +174,17 @@ class _Getter:
             return qt
         if w.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
             return self._dequant_fp8(base, w)
+        return w.to(self.dtype)
+
+    def _unpack_bitlinear(self, base: str, packed: torch.Tensor) -> torch.Tensor:
+        """BitLinear storage: ternary weights {-1, 0, +1} as 2-bit codes (value + 1), four OUTPUT rows to a
+        byte (bits 2i..2i+1 of packed row r hold output row r + i * N / 4), and one scale that divides
+        (or, for ``autobitlinear`` checkpoints, multiplies) the output. Expanded to a dense matrix with
+        the scale folded in."""
+        rows = [((packed >> (2 * i)) & 3).to(torch.int8) - 1 for i in range(4)]
+        w = torch.cat(rows, 0).float()
+        scale = self.src.get(base + ".weight_scale").float().reshape(-1)[0]
+        w = w / scale if self.cfg.extra.get("bitlinear_invert_scale", True) else w * scale
         return w.to(self.dtype)
 
     def _dequant_fp8(self, base: str, w: torch.Tensor) -> torch.Tensor:
@@ -414,6 +427,8 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
             _load_dense_mlp(g, p, lw)
         if cfg.extra.get("norm_plus_one"):                      # LayerNorm1P: stored as (weight - 1)
             lw.ln1, lw.ln2 = lw.ln1 + 1.0, lw.ln2 + 1.0
+        lw.attn_sub_norm = g.vec(p + ".self_attn.attn_sub_norm.weight")
+        lw.ffn_sub_norm = g.vec(p + ".mlp.ffn_sub_norm.weight")
         if src.has(p + ".mlp.act_fn.alpha_p"):                 # xIELU (Apertus): stored before softplus
             sp = torch.nn.functional.softplus
             beta = float(src.get(p + ".mlp.act_fn.beta")) if src.has(p + ".mlp.act_fn.beta") else 0.5

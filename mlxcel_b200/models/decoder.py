@@ -144,7 +144,10 @@ class DecoderModel:
         self.layernorm = cfg.extra.get("norm") == "layernorm"
         self.clip_qkv = float(cfg.extra.get("clip_qkv") or 0.0)
         self.plain_mlp = cfg.extra.get("mlp") == "plain"
-        self.general = self.layernorm or self.plain_mlp or bool(cfg.extra.get("parallel_block"))
+        self.sub_norms = bool(cfg.extra.get("sub_norms"))
+        if self.sub_norms and self.comm.tp_size != 1:
+            raise NotImplementedError("sub-layer norms span the whole projection input: not sharded across tensor-parallel ranks")
+        self.general = self.layernorm or self.plain_mlp or bool(cfg.extra.get("parallel_block")) or self.sub_norms
         # Folding rewrites the projection weights in place, so only the owner of the weights asks for
         # it (the LLM front end does; weights shared with another executor must stay untouched).
         if fold_norms and dev.type == "cuda" and os.environ.get("MLXCEL_B200_FOLD_NORMS", "1") != "0":
@@ -335,6 +338,12 @@ class DecoderModel:
                 ap, an, beta, eps_x = lw.act_params or (0.8, 0.8, 0.5, -1e-6)
                 return rops.xielu(u, ap, an, beta, eps_x)
             return rops.activation(u, cfg.hidden_act)
+        if cfg.hidden_act == "relu2":           # BitNet: relu(gate)^2 * up, then its own norm
+            from ..ops import recurrent as rops
+            gu = _linear_any(x, lw.w_gate_up, bias=lw.b_gate_up)
+            inter = gu.shape[1] // 2
+            m = (rops.activation(gu[:, :inter].contiguous(), "relu2").float() * gu[:, inter:].float()).to(gu.dtype)
+            return ops.rmsnorm(m, lw.ffn_sub_norm, cfg.rms_norm_eps, 0.0) if lw.ffn_sub_norm is not None else m
         return _glu_any(x, lw.w_gate_up, self.I, cfg.hidden_act, lw.b_gate_up, cfg.swiglu_alpha,
                         cfg.swiglu_limit, row_norm=row_norm)
 
@@ -428,6 +437,8 @@ class DecoderModel:
         for li, lw in enumerate(self.w.layers):
             x = self._norm(h, lw.ln1, lw.ln1_b)
             a = self._attention(li, lw, x, b, kv_layers[li])
+            if lw.attn_sub_norm is not None:                 # BitNet: norm between attention and o_proj
+                a = ops.rmsnorm(a, lw.attn_sub_norm, cfg.rms_norm_eps, 0.0)
             if parallel:
                 # one norm feeds both branches (Cohere, Phi) unless the layer has a second one (GPT-NeoX)
                 xm = x if lw.ln2 is lw.ln1 else self._norm(h, lw.ln2, lw.ln2_b)

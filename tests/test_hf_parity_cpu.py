@@ -84,6 +84,7 @@ FAMILIES = {
                           q_lora_rank=24, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
                           pad_token_id=0),
     "mamba2": dict(num_heads=8, head_dim=16, state_size=16, n_groups=1, expand=2, conv_kernel=4, chunk_size=8),
+    "bitnet": dict(tie_word_embeddings=False),
     "llama4_text": dict(intermediate_size=48, intermediate_size_mlp=96, num_hidden_layers=4, head_dim=16, num_local_experts=4,
                         num_experts_per_tok=1, interleave_moe_layer_step=2, no_rope_layer_interval=4, attention_chunk_size=128,
                         floor_scale=8, attn_scale=0.1, use_qk_norm=True, pad_token_id=0),

@@ -157,3 +157,65 @@ def test_dbrx_checkpoint_matches_a_plain_statement_of_the_model(tmp_path):
     top2 = want[-1].topk(2).values
     if float(top2[0] - top2[1]) > 0.05:
         assert out.output[0] == int(want[-1].argmax())
+
+
+def test_bitnet_packed_checkpoint_equals_its_dense_expansion(tmp_path):
+    """A BitNet checkpoint with BitLinear storage (uint8, four output rows per byte, one scale that
+    divides the output) gives the logits of the same model saved with dense ternary / scale weights."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from mlxcel_b200.cache.kv_pool import KVPool
+    from mlxcel_b200.loading.checkpoint import load_full_weights
+    from mlxcel_b200.models.decoder import StepBatch
+
+    torch.manual_seed(0)
+    H, Hq, Hkv, D, I, V, L = 64, 4, 2, 16, 96, 200, 2
+    cfgd = dict(model_type="bitnet", hidden_size=H, num_attention_heads=Hq, num_key_value_heads=Hkv, num_hidden_layers=L,
+                intermediate_size=I, vocab_size=V, max_position_embeddings=128, rms_norm_eps=1e-5, rope_theta=10000.0,
+                hidden_act="relu2", tie_word_embeddings=True)
+    dense, packed = {}, {}
+
+    def put_linear(name, n, k):
+        tern = torch.randint(-1, 2, (n, k))
+        scale = torch.rand(1) * 20 + 5
+        dense[name + ".weight"] = tern.float() / scale
+        codes = (tern + 1).to(torch.uint8).view(4, n // 4, k)            # output row r + i * n / 4 -> bits 2i of row r
+        packed[name + ".weight"] = (codes[0] | (codes[1] << 2) | (codes[2] << 4) | (codes[3] << 6)).contiguous()
+        packed[name + ".weight_scale"] = scale
+
+    def put(name, t):
+        dense[name] = packed[name] = t
+
+    put("model.embed_tokens.weight", torch.randn(V, H) * 0.5)
+    put("model.norm.weight", 1 + torch.randn(H) * 0.1)
+    for i in range(L):
+        p = f"model.layers.{i}."
+        put(p + "input_layernorm.weight", 1 + torch.randn(H) * 0.1)
+        put(p + "post_attention_layernorm.weight", 1 + torch.randn(H) * 0.1)
+        put(p + "self_attn.attn_sub_norm.weight", 1 + torch.randn(H) * 0.1)
+        put(p + "mlp.ffn_sub_norm.weight", 1 + torch.randn(I) * 0.1)
+        for n, (rows, cols) in dict(q_proj=(Hq * D, H), k_proj=(Hkv * D, H), v_proj=(Hkv * D, H), o_proj=(H, Hq * D)).items():
+            put_linear(p + "self_attn." + n, rows, cols)
+        for n, (rows, cols) in dict(gate_proj=(I, H), up_proj=(I, H), down_proj=(H, I)).items():
+            put_linear(p + "mlp." + n, rows, cols)
+    logits = []
+    T = 17
+    ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(3))
+    for name, tensors in (("dense", dense), ("packed", packed)):
+        d = tmp_path / name
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps(cfgd))
+        save_file({k: v.contiguous() for k, v in tensors.items()}, str(d / "model.safetensors"))
+        cfg = ModelConfig.from_path(str(d))
+        model = DecoderModel(cfg, load_full_weights(str(d), cfg, dtype=torch.float32))
+        pool = KVPool(cfg, 4, 16, device="cpu", dtype=torch.float32, num_layers=L)
+        sb = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32), slot_mapping=torch.arange(T, dtype=torch.int32),
+                       num_prefill_seqs=1, pf_block_tables=torch.arange(4, dtype=torch.int32)[None],
+                       pf_cu_q=torch.tensor([0, T], dtype=torch.int32), pf_context_lens=torch.tensor([T], dtype=torch.int32),
+                       pf_max_q_len=T, pf_cu_q_host=[0, T], logits_rows=torch.arange(T))
+        logits.append(model.forward(sb, pool.layers).float())
+        assert model.w.layers[0].attn_sub_norm is not None and model.w.layers[0].ffn_sub_norm is not None
+    assert torch.isfinite(logits[0]).all() and logits[0].abs().max() > 0.1
+    assert (logits[0] - logits[1]).abs().max().item() < 1e-4 * max(1.0, logits[0].abs().max().item())
