@@ -121,7 +121,7 @@ def _infer_quant(packed: torch.Tensor, scales: torch.Tensor, biases, qc: QuantCo
     words = packed.shape[-1]
     if biases is not None:
         mode = "affine"
-    elif qc is not None and qc.mode in ("mxfp4", "mxfp8"):
+    elif qc is not None and qc.mode in ("mxfp4", "mxfp8", "nvfp4"):
         mode = qc.mode
     elif qc is not None and qc.bits == 8:
         mode = "mxfp8"
@@ -132,9 +132,13 @@ def _infer_quant(packed: torch.Tensor, scales: torch.Tensor, biases, qc: QuantCo
     for bits, g in cands:
         inn = groups * g
         if words * 32 == bits * inn:
-            if mode == "mxfp4" and bits != 4:
+            if mode in ("mxfp4", "nvfp4") and bits != 4:
                 continue
             if mode == "mxfp8" and bits != 8:
+                continue
+            if mode == "mxfp4" and g == 16:
+                mode = "nvfp4"                   # 4-bit floats in groups of 16 carry e4m3 scales
+            if mode == "nvfp4" and g != 16:
                 continue
             return QuantizedTensor(packed.view(torch.int32) if packed.dtype != torch.int32 else packed,
                                    scales, biases, bits, g, mode)
@@ -166,7 +170,8 @@ class _Getter:
             scales = self.src.get(sname)
             biases = self.src.get(base + ".biases") if self.src.has(base + ".biases") else None
             qt = _infer_quant(w, scales, biases, self.cfg.quantization.for_module(base))
-            if self.deq:
+            if self.deq or qt.mode == "nvfp4":
+                # (nvfp4: no kernel reads e4m3 group scales; the matrix is expanded once at load)
                 from ..ops.quant import dequantize_ref
                 return dequantize_ref(qt, self.dtype)
             if qt.mode == "affine":

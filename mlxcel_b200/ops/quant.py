@@ -95,6 +95,19 @@ def quantize_mxfp4(w: torch.Tensor) -> QuantizedTensor:
     return QuantizedTensor(packed, s8, None, 4, 32, "mxfp4")
 
 
+def quantize_nvfp4(w: torch.Tensor) -> QuantizedTensor:
+    """e2m1 values with one e4m3 scale (amax / 6, rounded to fp8) per 16 inputs (MLX mode ``nvfp4``)."""
+    *lead, out, inn = w.shape
+    g = w.float().reshape(*lead, out, inn // 16, 16)
+    s8 = (g.abs().amax(-1, keepdim=True) / 6.0).clamp(2.0 ** -9, 448.0).to(torch.float8_e4m3fn)
+    x = (g / s8.float()).clamp(-6.0, 6.0)
+    tab = _E2M1.to(w.device)
+    idx = (x.abs().unsqueeze(-1) - tab).abs().argmin(-1)
+    code = idx | ((x < 0).to(torch.int64) << 3)
+    packed = pack_bits(code.reshape(*lead, out, inn), 4)
+    return QuantizedTensor(packed, s8.view(torch.uint8).squeeze(-1), None, 4, 16, "nvfp4")
+
+
 def quantize_mxfp8(w: torch.Tensor) -> QuantizedTensor:
     *lead, out, inn = w.shape
     g = w.float().reshape(*lead, out, inn // 32, 32)
@@ -116,6 +129,8 @@ def quantize(w: torch.Tensor, mode: str = "affine", bits: int = 4, group_size: i
         return quantize_mxfp4(w)
     if mode == "mxfp8":
         return quantize_mxfp8(w)
+    if mode == "nvfp4":
+        return quantize_nvfp4(w)
     raise ValueError(mode)
 
 
@@ -167,8 +182,11 @@ def dequantize_ref(qt: QuantizedTensor, dtype=torch.float32) -> torch.Tensor:
         v = q.float().reshape(*lead, out, inn // g, g) * qt.scales.float().unsqueeze(-1) + \
             qt.biases.float().unsqueeze(-1)
     else:
-        sc = torch.pow(2.0, qt.scales.float() - 127.0).unsqueeze(-1)
-        if qt.mode == "mxfp4":
+        if qt.mode == "nvfp4":                  # the scale byte is an e4m3 number, not an exponent
+            sc = qt.scales.view(torch.float8_e4m3fn).float().unsqueeze(-1)
+        else:
+            sc = torch.pow(2.0, qt.scales.float() - 127.0).unsqueeze(-1)
+        if qt.mode in ("mxfp4", "nvfp4"):
             tab = _E2M1.to(q.device)
             val = tab[(q & 7)] * torch.where((q & 8) != 0, -1.0, 1.0)
         else:

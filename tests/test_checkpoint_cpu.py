@@ -197,3 +197,28 @@ def test_index_entries_outside_the_checkpoint_directory_are_refused(tmp_path):
         src.footprint()
     with pytest.raises(FileNotFoundError):
         src.get("c")
+
+
+def test_nvfp4_checkpoint_is_expanded_at_load(tmp_path):
+    """MLX ``nvfp4`` (e2m1 codes, one e4m3 scale per 16 inputs): the quantizer's values survive the
+    checkpoint round trip, with and without the mode named in the config, as dense matrices."""
+    cfg = ModelConfig.from_dict(LLAMA)
+    w = random_weights(cfg, seed=5, dtype=torch.float32, std=0.05)
+    want = {}
+    for li, lw in enumerate(w.layers):
+        for name in ("wqkv", "wo", "w_gate_up", "w_down"):
+            q = quant.quantize(getattr(lw, name), "nvfp4", 4, 16)
+            assert q.scales.dtype == torch.uint8 and q.group_size == 16
+            deq = quant.dequantize_ref(q, torch.float32)
+            rel = (deq - getattr(lw, name)).abs().max() / getattr(lw, name).abs().max()
+            assert rel < 0.3                                         # 4-bit floats: coarse, but the right numbers
+            want[(li, name)] = deq
+            setattr(lw, name, q)
+    for named in (True, False):
+        d = tmp_path / f"nvfp4_{int(named)}"
+        save_checkpoint(d, LLAMA, w, quantization=dict(mode="nvfp4", bits=4, group_size=16) if named else None)
+        cfg2 = ModelConfig.from_path(d)
+        w2 = load_full_weights(d, cfg2, dtype=torch.float32)
+        for (li, name), t in want.items():
+            got = getattr(w2.layers[li], name)
+            assert isinstance(got, torch.Tensor) and torch.equal(got, t)
