@@ -111,10 +111,134 @@ class SPTokenizer:
         return [self.eos_token_id] if self.eos_token_id >= 0 else []
 
 
+class TiktokenTokenizer:
+    """Byte-level BPE from a tiktoken vocabulary file (``tiktoken.model`` / ``*.tiktoken``: one
+    ``base64(token bytes) rank`` pair per line), as shipped by the Kimi and some Qwen / Llama-3 original
+    checkpoints (reference: the tiktoken branch of the tokenizer loader, src/server/state.rs:723-760).
+    Control tokens come from ``tokenizer_config.json`` (``added_tokens_decoder``) and sit above the
+    ranks. Text is split by the vocabulary's pre-tokenization pattern, each piece's bytes are merged
+    greedily by rank (lowest rank first), and control-token literals in the text map to their ids."""
+
+    # the pattern of the cl100k / Llama-3 family; a checkpoint may carry its own as ``pat_str`` in
+    # tokenizer_config.json
+    DEFAULT_PATTERN = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|"
+                       r"\s*[\r\n]+|\s+(?!\S)|\s+")
+
+    def __init__(self, path: Path):
+        import base64
+
+        import regex
+
+        f = next((c for c in [path / "tiktoken.model", *sorted(path.glob("*.tiktoken"))] if c.exists()), None)
+        if f is None:
+            raise FileNotFoundError(f"{path}: no tiktoken vocabulary")
+        self.ranks: dict[bytes, int] = {}
+        for line in f.read_text().splitlines():
+            if line.strip():
+                tok, rank = line.split()
+                self.ranks[base64.b64decode(tok)] = int(rank)
+        self.by_id: dict[int, bytes] = {r: b for b, r in self.ranks.items()}
+        cfg = json.loads((path / "tokenizer_config.json").read_text()) if (path / "tokenizer_config.json").exists() else {}
+        self.config = cfg
+        self.chat_template = cfg.get("chat_template")
+        if (path / "chat_template.jinja").exists():
+            self.chat_template = (path / "chat_template.jinja").read_text()
+        self.special: dict[str, int] = {}
+        for i, ent in (cfg.get("added_tokens_decoder") or {}).items():
+            self.special[ent["content"] if isinstance(ent, dict) else str(ent)] = int(i)
+        self.special_by_id = {i: t for t, i in self.special.items()}
+        self.vocab_size = max([*self.by_id, *self.special_by_id, -1]) + 1
+        self.pattern = regex.compile(cfg.get("pat_str") or self.DEFAULT_PATTERN)
+        self._special_re = (regex.compile("|".join(regex.escape(t) for t in sorted(self.special, key=len, reverse=True)))
+                            if self.special else None)
+
+        def name(v):
+            return v.get("content") if isinstance(v, dict) else v
+        self.bos_token, self.eos_token = name(cfg.get("bos_token")), name(cfg.get("eos_token"))
+        self.bos_token_id, self.eos_token_id = self.special.get(self.bos_token), self.special.get(self.eos_token)
+        self._eos = set([self.eos_token_id] if self.eos_token_id is not None else [])
+        gen = path / "generation_config.json"
+        if gen.exists():
+            e = json.loads(gen.read_text()).get("eos_token_id")
+            if e is not None:
+                self._eos.update(e if isinstance(e, list) else [e])
+        self.think_open, self.think_close = self.special.get("<think>"), self.special.get("</think>")
+        self.fim = dict(prefix=None, suffix=None, middle=None)
+        self._cache: dict[bytes, list[int]] = {}
+
+    def control_id(self, literal: str) -> int | None:
+        return self.special.get(literal)
+
+    def _bpe(self, piece: bytes) -> list[int]:
+        hit = self._cache.get(piece)
+        if hit is not None:
+            return hit
+        if piece in self.ranks:
+            out = [self.ranks[piece]]
+        else:
+            parts = [piece[i:i + 1] for i in range(len(piece))]
+            while len(parts) > 1:
+                best, at = None, -1
+                for i in range(len(parts) - 1):
+                    r = self.ranks.get(parts[i] + parts[i + 1])
+                    if r is not None and (best is None or r < best):
+                        best, at = r, i
+                if best is None:
+                    break
+                parts[at:at + 2] = [parts[at] + parts[at + 1]]
+            out = [self.ranks[p] for p in parts]
+        if len(self._cache) < 1 << 16:
+            self._cache[piece] = out
+        return out
+
+    def _encode_plain(self, text: str) -> list[int]:
+        ids: list[int] = []
+        for m in self.pattern.finditer(text):
+            ids += self._bpe(m.group().encode("utf-8"))
+        return ids
+
+    def encode(self, text: str, add_special_tokens: bool = False) -> list[int]:
+        ids = [self.bos_token_id] if add_special_tokens and self.bos_token_id is not None else []
+        if self._special_re is None:
+            return ids + self._encode_plain(text)
+        pos = 0
+        for m in self._special_re.finditer(text):
+            ids += self._encode_plain(text[pos:m.start()])
+            ids.append(self.special[m.group()])
+            pos = m.end()
+        return ids + self._encode_plain(text[pos:])
+
+    def token_bytes(self, i: int) -> bytes:
+        b = self.by_id.get(int(i))
+        return b if b is not None else self.special_by_id.get(int(i), "").encode("utf-8")
+
+    def decode(self, ids, skip_special_tokens: bool = True) -> str:
+        out = bytearray()
+        for i in ids:
+            b = self.by_id.get(int(i))
+            if b is not None:
+                out += b
+            elif not skip_special_tokens:
+                out += self.special_by_id.get(int(i), "").encode("utf-8")
+        return out.decode("utf-8", errors="replace")
+
+    def eos_ids(self) -> list[int]:
+        return sorted(self._eos)
+
+    def fingerprint(self) -> str:
+        import hashlib
+        h = hashlib.sha256()
+        for b, r in sorted(self.ranks.items(), key=lambda kv: kv[1]):
+            h.update(b + b"\0" + str(r).encode())
+        return h.hexdigest()[:16]
+
+
 def load_tokenizer(path: str | Path):
     p = Path(path)
     if (p / "tokenizer.json").exists():
         return HFTokenizer(p)
+    if (p / "tiktoken.model").exists() or any(p.glob("*.tiktoken")):
+        return TiktokenTokenizer(p)
     if (p / "tokenizer.model").exists():
         return SPTokenizer(p)
     vocab = 260

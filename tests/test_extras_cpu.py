@@ -321,3 +321,32 @@ def test_arch_catalog_lists_every_family(capsys):
     cli.main(["supported"])
     out = capsys.readouterr().out
     assert out.splitlines()[0].startswith("FAMILY") and "qwen3_next" in out
+
+
+def test_tiktoken_vocabulary_files_load_and_round_trip(tmp_path):
+    """A tiktoken-format vocabulary (base64 token + rank per line) with control tokens from
+    tokenizer_config.json: merges follow the ranks (lowest first), control literals map to their ids,
+    decoding restores the text, and the incremental detokenizer streams it."""
+    import base64
+    import json
+
+    from mlxcel_b200.tokenizer import IncrementalDetokenizer, TiktokenTokenizer, load_tokenizer
+
+    toks = [bytes([i]) for i in range(256)] + [b"he", b"ll", b"hell", b"hello", b" w", b"or", b" wor", b"ld", b" world", "é".encode()]
+    (tmp_path / "tiktoken.model").write_text("\n".join(f"{base64.b64encode(t).decode()} {r}" for r, t in enumerate(toks)))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps(dict(
+        added_tokens_decoder={"266": dict(content="<|im_end|>"), "267": dict(content="<|bos|>"), "268": dict(content="<think>")},
+        bos_token="<|bos|>", eos_token=dict(content="<|im_end|>"))))
+    tk = load_tokenizer(tmp_path)
+    assert isinstance(tk, TiktokenTokenizer) and tk.vocab_size == 269
+    assert tk.encode("hello world") == [259, 264]
+    assert tk.encode("hell") == [258] and tk.encode("hel") == [256, ord("l")]
+    assert tk.encode("hello<|im_end|>", add_special_tokens=True) == [267, 259, 266]
+    assert tk.eos_ids() == [266] and tk.think_open == 268 and tk.control_id("<|bos|>") == 267
+    text = "hello world, héllo\n\n  wörld 12345!"
+    ids = tk.encode(text)
+    assert tk.decode(ids) == text and all(0 <= i < 266 for i in ids)
+    assert tk.decode([259, 266]) == "hello" and tk.decode([259, 266], skip_special_tokens=False) == "hello<|im_end|>"
+    det = IncrementalDetokenizer(tk)
+    assert "".join(det.push(i) for i in ids) + det.flush() == text
+    assert len(tk.fingerprint()) == 16
