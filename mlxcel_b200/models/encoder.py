@@ -261,15 +261,89 @@ class ModernBertEncoder:
         return v / v.norm().clamp_min(1e-12) if normalize else v
 
 
+class SiglipTextEncoder:
+    """SigLIP text tower: token + learned position embeddings, pre-LayerNorm blocks with biased
+    projections and tanh-GELU MLPs, bidirectional attention, a final LayerNorm, and the sentence vector
+    ``head(last token)`` that is compared with the image tower's pooled output
+    (reference src/models/siglip_text.rs). Loads a text-only checkpoint (``siglip_text_model``) or the
+    text half of a full SigLIP checkpoint."""
+
+    def __init__(self, cfg: dict, tensors: dict, dtype=torch.bfloat16, device="cpu"):
+        cfg = cfg.get("text_config") or cfg
+        self.device, self.dtype = torch.device(device), dtype
+        self.hidden, self.heads = int(cfg.get("hidden_size", 768)), int(cfg.get("num_attention_heads", 12))
+        self.eps = float(cfg.get("layer_norm_eps", 1e-6))
+        self.max_len = int(cfg.get("max_position_embeddings", 64))
+        act = cfg.get("hidden_act", "gelu_pytorch_tanh")
+        self.act = "gelu_tanh" if "tanh" in act else "gelu"
+        root = next((r for r in ("text_model.", "model.text_model.", "") if r + "embeddings.token_embedding.weight" in tensors), None)
+        if root is None:
+            raise KeyError("no SigLIP text tower in this checkpoint")
+
+        def t(name):
+            return tensors[root + name].to(dtype).to(self.device).contiguous()
+        self.word, self.pos = t("embeddings.token_embedding.weight"), t("embeddings.position_embedding.weight")
+        self.layers = []
+        for i in range(int(cfg.get("num_hidden_layers", 12))):
+            p, a = f"encoder.layers.{i}.", f"encoder.layers.{i}.self_attn."
+            self.layers.append(EncoderLayer(
+                wqkv=torch.cat([t(a + f"{n}_proj.weight") for n in "qkv"]).contiguous(),
+                bqkv=torch.cat([t(a + f"{n}_proj.bias") for n in "qkv"]).contiguous(),
+                wo=t(a + "out_proj.weight"), bo=t(a + "out_proj.bias"),
+                ln1_w=t(p + "layer_norm1.weight"), ln1_b=t(p + "layer_norm1.bias"),
+                w1=t(p + "mlp.fc1.weight"), b1=t(p + "mlp.fc1.bias"), w2=t(p + "mlp.fc2.weight"), b2=t(p + "mlp.fc2.bias"),
+                ln2_w=t(p + "layer_norm2.weight"), ln2_b=t(p + "layer_norm2.bias")))
+        self.final_ln = (t("final_layer_norm.weight"), t("final_layer_norm.bias"))
+        self.head = (t("head.weight"), t("head.bias")) if root + "head.weight" in tensors else None
+
+    @staticmethod
+    def from_pretrained(path, dtype=torch.bfloat16, device="cpu") -> "SiglipTextEncoder":
+        from ..loading.checkpoint import TensorSource
+
+        cfg = json.loads((Path(path) / "config.json").read_text())
+        src = TensorSource(path)
+        return SiglipTextEncoder(cfg, {k: src.get(k) for k in src.keys() if "vision_model" not in k}, dtype, device)
+
+    @torch.inference_mode()
+    def hidden_states(self, ids: list[int]) -> torch.Tensor:
+        ids = ids[: self.max_len]
+        T, H, nh = len(ids), self.hidden, self.heads
+        tok = torch.tensor(ids, dtype=torch.long, device=self.device)
+        h = (self.word[tok].float() + self.pos[:T].float()).to(self.dtype)
+        for lw in self.layers:
+            y = rops.layernorm(h, lw.ln1_w, lw.ln1_b, self.eps)
+            qkv = ops.linear(y, lw.wqkv, bias=lw.bqkv).view(T, 3, nh, H // nh)
+            q, k, v = (qkv[:, j].transpose(0, 1).unsqueeze(0) for j in range(3))
+            a = F.scaled_dot_product_attention(q, k, v).squeeze(0).transpose(0, 1).reshape(T, H).contiguous()
+            h = ops.linear(a, lw.wo, bias=lw.bo, residual=h)
+            y = rops.layernorm(h, lw.ln2_w, lw.ln2_b, self.eps)
+            h = ops.linear(rops.activation(ops.linear(y, lw.w1, bias=lw.b1), self.act), lw.w2, bias=lw.b2, residual=h)
+        return rops.layernorm(h, *self.final_ln, self.eps)
+
+    def embed(self, ids: list[int], pooling: str = "last", normalize: bool = True) -> torch.Tensor:
+        """``pooling="last"`` (the model's own sentence vector: the head over the last token), ``"mean"`` or
+        ``"cls"`` over the final hidden states."""
+        h = self.hidden_states(ids)
+        if pooling == "last":
+            v = h[-1:]
+            v = (ops.linear(v, self.head[0], bias=self.head[1]) if self.head is not None else v)[0].float()
+        else:
+            v = h.float()[0] if pooling == "cls" else h.float().mean(0)
+        return v / v.norm().clamp_min(1e-12) if normalize else v
+
+
 def load_encoder(path, dtype=torch.bfloat16, device="cpu"):
-    """The encoder class for a checkpoint's ``model_type`` (bert, modernbert, deberta-v2)."""
+    """The encoder class for a checkpoint's ``model_type`` (bert, modernbert, deberta-v2, siglip text)."""
     mt = json.loads((Path(path) / "config.json").read_text()).get("model_type")
     from .deberta import DebertaV2Encoder
-    cls = {"bert": BertEncoder, "modernbert": ModernBertEncoder, "deberta-v2": DebertaV2Encoder}.get(mt)
+    cls = {"bert": BertEncoder, "modernbert": ModernBertEncoder, "deberta-v2": DebertaV2Encoder,
+           "siglip_text_model": SiglipTextEncoder, "siglip": SiglipTextEncoder}.get(mt)
     if cls is None:
         raise ValueError(f"unsupported encoder model_type {mt!r}")
     enc = cls.from_pretrained(path, dtype, device)
     enc.default_pooling, enc.default_normalize = sentence_transformers_defaults(path)
+    if cls is SiglipTextEncoder and not (Path(path) / "1_Pooling" / "config.json").is_file():
+        enc.default_pooling = "last"
     return enc
 
 

@@ -244,3 +244,35 @@ def test_deberta_v2_matches_transformers(share, buckets):
     assert (enc.classify(ids[0].tolist()) - want_logit).abs().max().item() < 1e-4
     v = enc.embed(ids[0].tolist())
     assert abs(float(v.norm()) - 1.0) < 1e-5
+
+
+def test_siglip_text_tower_matches_transformers(tmp_path):
+    """SigLIP text encoder, from a text-only checkpoint and from the text half of a full SigLIP
+    checkpoint: final hidden states and the pooled sentence vector (head over the last token)."""
+    from transformers import SiglipConfig, SiglipModel, SiglipTextConfig, SiglipTextModel
+
+    from mlxcel_b200.models.encoder import SiglipTextEncoder, load_encoder
+
+    torch.manual_seed(0)
+    tc = dict(vocab_size=120, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+              max_position_embeddings=16)
+    ids = [5, 17, 99, 3, 42, 7, 1]
+    text = SiglipTextModel(SiglipTextConfig(**tc)).float().eval()
+    full = SiglipModel(SiglipConfig(text_config=tc, vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                                                                       num_attention_heads=2, image_size=16, patch_size=8))).float().eval()
+    for name, model, tower in (("text", text, text.text_model), ("full", full, full.text_model)):
+        with torch.no_grad():
+            for p in model.parameters():
+                if p.dim() >= 2:
+                    p.normal_(0, 0.1)
+                else:
+                    p.add_(torch.randn_like(p) * 0.1)
+            out = tower(input_ids=torch.tensor([ids]))
+        d = tmp_path / name
+        model.save_pretrained(d, safe_serialization=True)
+        enc = load_encoder(d, dtype=torch.float32)
+        assert isinstance(enc, SiglipTextEncoder) and enc.default_pooling == "last"
+        assert (enc.hidden_states(ids) - out.last_hidden_state[0]).abs().max() < 2e-4
+        assert (enc.embed(ids, "last", normalize=False) - out.pooler_output[0]).abs().max() < 2e-4
+        v = enc.embed(ids)
+        assert abs(float(v.norm()) - 1.0) < 1e-5
