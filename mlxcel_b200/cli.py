@@ -26,6 +26,13 @@ def _add_model_args(p):
     p.add_argument("--kv-bits", type=int, default=0, choices=[0, 4, 8, 16])
     p.add_argument("--kv-cache-blocks", type=int, default=0)
     p.add_argument("--block-size", type=int, default=16)
+    p.add_argument("--max-kv-size", type=int, default=0,
+                   help="KV window bound of one sequence in tokens (0 = the context size): a sequence that reaches it "
+                        "ends with finish reason 'length', or keeps going under --context-shift")
+    p.add_argument("--context-shift", dest="context_shift", action="store_true", default=False,
+                   help="at the KV bound drop the oldest blocks behind the first --keep tokens and go on generating")
+    p.add_argument("--no-context-shift", dest="context_shift", action="store_false")
+    p.add_argument("--keep", type=int, default=0, help="tokens at the start of a sequence that context shifting never drops")
     p.add_argument("--no-prompt-cache", action="store_true")
     p.add_argument("--no-cuda-graphs", action="store_true")
     p.add_argument("--no-warmup", action="store_true", help="serve: skip the one-token request made before listening")
@@ -55,7 +62,7 @@ _COMPAT_NOOPS = [("-ngl", "--n-gpu-layers", "--gpu-layers"), ("-t", "--threads")
                  ("--numa",), ("--poll",), ("--threads-http",)]
 _COMPAT_NOOP_SWITCHES = [("--mlock",), ("--no-mmap",), ("-fa", "--flash-attn"), ("-cb", "--cont-batching"),
                          ("-nocb", "--no-cont-batching"), ("--jinja",), ("--metrics",), ("--slots",),
-                         ("--no-slots",), ("--no-webui",), ("--no-context-shift",), ("--context-shift",), ("--no-kv-offload",),
+                         ("--no-slots",), ("--no-webui",), ("--no-kv-offload",),
                          ("--embeddings", "--embedding"), ("--reranking", "--rerank"), ("--props",), ("--log-disable",)]
 
 
@@ -203,6 +210,8 @@ def load_llm(a):
                         prefill_chunk_alone=a.prefill_chunk_size, prefill_chunk_contended=min(512, a.prefill_chunk_size),
                         block_size=a.block_size, kv_bits=a.kv_bits or 16, num_blocks=a.kv_cache_blocks,
                         prefix_cache=not a.no_prompt_cache, max_model_len=a.ctx_size,
+                        max_kv_size=getattr(a, "max_kv_size", 0), context_shift=getattr(a, "context_shift", False),
+                        n_keep=getattr(a, "keep", 0) or 0,
                         cuda_graphs=not a.no_cuda_graphs and dev != "cpu")
     comm = None
     if pp > 1:

@@ -86,6 +86,14 @@ class EngineConfig:
     prefix_cache: bool = True
     max_queue_depth: int = 4096
     max_model_len: int = 8192
+    # KV window bound of one sequence (0 = max_model_len). Without context_shift a sequence ends with
+    # finish reason "length" when prompt + generated + 1 reaches it; with context_shift the oldest
+    # blocks behind the first n_keep tokens are dropped instead and generation goes on (the keys that
+    # stay keep their rotary positions; reference --max-kv-size / --context-shift / --keep,
+    # src/server/batch/finish.rs:37-65, cache.rs trim_front_keep_sink)
+    max_kv_size: int = 0
+    context_shift: bool = False
+    n_keep: int = 0
     cuda_graphs: bool = True
     prefill_grant_interval: int = 16
     mixed_steps: bool = True
@@ -157,6 +165,18 @@ class Engine:
             self.kv_layers = [next(win) if w > 0 else next(full) for w in self.win_layers]
         self.sampler = Sampler(cfg.vocab_size, self.device)
         self.max_blocks_per_seq = (e.max_model_len + e.block_size - 1) // e.block_size
+        self._ctx_shift = bool(e.context_shift) and not self.recurrent
+        if self._ctx_shift:
+            if self.bm_win is not None:
+                raise ValueError("context shift is not available for models with a sliding-window KV pool "
+                                 "(their window layers already drop old blocks)")
+            if getattr(self, "pipeline", None):
+                raise ValueError("context shift is not available under pipeline parallelism")
+            cap = e.max_model_len - e.block_size
+            e.max_kv_size = min(e.max_kv_size, cap) if e.max_kv_size > 0 else cap
+            if e.max_kv_size < 4 * e.block_size + e.n_keep:
+                raise ValueError("max_kv_size is too small for context shifting (needs n_keep + 4 blocks)")
+            e.lookahead = False          # a step in flight holds the table it was launched with
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []      # PREFILLING or DECODING, in admission order
         self.seqs: dict[int, Sequence] = {}
@@ -211,7 +231,18 @@ class Engine:
             self.bm_win.truncate(seq_id, n)
 
     def _release_window(self, seqs) -> None:
-        """After a step: blocks of the window pool whose tokens no later query can reach go back."""
+        """After a step: blocks of the window pool whose tokens no later query can reach go back; with
+        context shifting, sequences that reached the KV bound drop their oldest blocks behind n_keep."""
+        if self._ctx_shift:
+            e = self.ecfg
+            for s in seqs:
+                if s.status == SeqStatus.DECODING and self.bm.has_seq(s.seq_id) \
+                        and s.total_len - self.bm.shifted(s.seq_id) + 1 >= e.max_kv_size:
+                    # one block of headroom more than needed, so that this happens once per block
+                    cut = self.bm.shift_front(s.seq_id, e.n_keep, e.max_kv_size - 2 * e.block_size)
+                    if cut:
+                        self.stats["context_shifts"] = self.stats.get("context_shifts", 0) + 1
+                        self.stats["context_shift_tokens"] = self.stats.get("context_shift_tokens", 0) + cut
         if self.bm_win is None:
             return
         for s in seqs:
@@ -369,6 +400,12 @@ class Engine:
         cands = [s for s in self.running]
         if len(cands) <= 1:
             return False
+        if self._ctx_shift:
+            # a sequence whose context was shifted cannot be recomputed from its tokens (part of its
+            # history is gone from the cache on purpose): it is never the victim
+            cands = [s for s in cands if not (self.bm.has_seq(s.seq_id) and self.bm.shifted(s.seq_id))]
+            if not cands:
+                return False
         victim = min(cands, key=lambda s: (len(s.output), -s.seq_id))
         self.running.remove(victim)
         self._kv_free(victim.seq_id)
@@ -409,7 +446,7 @@ class Engine:
         st.mixed_steps = e.mixed_steps
         # A verify round alternates with classic work (admission, a parked prefill): the tick policy
         # never grants two rounds in a row while classic work waits (tick_policy.rs:284-356).
-        st.speculative_ready = (self.drafter is not None and bool(decode)
+        st.speculative_ready = (self.drafter is not None and bool(decode) and not self._ctx_shift
                                 and all(self._spec_row_ok(s) for s in decode)
                                 and (not self.pipeline or all(s.params.greedy for s in decode))
                                 and (self.spec_policy is None or self.spec_policy.allow()))
@@ -501,8 +538,9 @@ class Engine:
             self.bm.fill_slots(s.seq_id, L - 1, 1, self.np_slots, i)
             if self.bm_win is not None:
                 self.bm_win.fill_slots(s.seq_id, L - 1, 1, self.np_slots_w, i)
-            self.h_dec_lens[i] = L
-        max_len = max((s.total_len for s in decode), default=0)
+            # (after a context shift the table holds fewer tokens than the sequence has seen)
+            self.h_dec_lens[i] = L - (self.bm.shifted(s.seq_id) if self._ctx_shift else 0)
+        max_len = int(self.h_dec_lens[:nd].max()) if nd else 0
         if nd:
             self.bm.fill_tables([s.seq_id for s in decode], self.np_dec_tables)
             if self.bm_win is not None:
@@ -953,8 +991,11 @@ class Engine:
             s.logprobs.append(float(lp))
         if len(s.output) >= p.max_tokens:
             return FinishReason.LENGTH
-        if s.total_len + 1 > self.ecfg.max_model_len:
-            return FinishReason.LENGTH
+        if not self._ctx_shift:
+            if s.total_len + 1 > self.ecfg.max_model_len:
+                return FinishReason.LENGTH
+            if self.ecfg.max_kv_size > 0 and s.total_len + 1 >= self.ecfg.max_kv_size and not s.mm_embeds:
+                return FinishReason.LENGTH
         if p.loop_max_pattern > 0 and _tail_loop(s.output, p.loop_min_pattern, p.loop_max_pattern,
                                                  p.loop_min_count):
             return FinishReason.REPETITION_LOOP

@@ -68,6 +68,11 @@ struct Sequence {
   Hash128 last_hash;        // hash of block num_hashed - 1
   uint64_t salt = 0;
   int front_released = 0;   // leading table entries given back by release_front (stored as -1)
+  // Context shift: `shifted` tokens (whole blocks) were cut out of the table behind the first
+  // `keep_tokens` tokens. Callers keep counting tokens absolutely; positions >= keep_tokens + shifted
+  // live at table index (pos - shifted) / block_size.
+  int shifted = 0;
+  int keep_tokens = 0;
 };
 
 class BlockManager {
@@ -88,12 +93,17 @@ class BlockManager {
   int watermark_blocks() const { return watermark_blocks_; }
   bool has_seq(int64_t id) const { return seqs_.count(id) != 0; }
   int seq_len(int64_t id) const { return get(id).num_tokens; }
+  int shifted(int64_t id) const {
+    auto it = seqs_.find(id);
+    return it == seqs_.end() ? 0 : it->second.shifted;
+  }
   std::vector<int> seq_blocks(int64_t id) const { return get(id).blocks; }
 
   int blocks_needed(int64_t id, int total_tokens) const {
     auto it = seqs_.find(id);
     const int have = it == seqs_.end() ? 0 : static_cast<int>(it->second.blocks.size());
-    const int need = (total_tokens + block_size_ - 1) / block_size_;
+    const int cut = it == seqs_.end() ? 0 : it->second.shifted;
+    const int need = (std::max(0, total_tokens - cut) + block_size_ - 1) / block_size_;
     return std::max(0, need - have);
   }
 
@@ -153,6 +163,7 @@ class BlockManager {
               int num_computed) {
     if (!prefix_cache_) return;
     Sequence& s = get(id);
+    if (s.shifted > 0) return;          // the block chain has a hole: nothing more of it is shareable
     const int32_t* t = tokens.data();
     const int n = std::min<int>(num_computed, static_cast<int>(tokens.size()));
     const int full = std::min<int>(n / block_size_, static_cast<int>(s.blocks.size()));
@@ -209,7 +220,9 @@ class BlockManager {
   void truncate(int64_t id, int new_len) {
     Sequence& s = get(id);
     if (new_len >= s.num_tokens) return;
-    const int keep = (new_len + block_size_ - 1) / block_size_;
+    if (s.shifted > 0 && new_len < s.keep_tokens + s.shifted)
+      throw std::invalid_argument("truncate below a context shift");
+    const int keep = (new_len - s.shifted + block_size_ - 1) / block_size_;
     while (static_cast<int>(s.blocks.size()) > keep) {
       if (s.blocks.back() >= 0) release(s.blocks.back());
       s.blocks.pop_back();
@@ -239,6 +252,31 @@ class BlockManager {
     s.front_released = std::max(s.front_released, upto);
     front_released_ += n;
     return n;
+  }
+
+  // Context shift: cut whole blocks out of the table behind the first `keep_tokens` tokens (rounded
+  // up to a block) so that at most `max_live` tokens stay, and give them back. The keys that stay
+  // keep the rotary position they were written with, and the caller keeps counting tokens
+  // absolutely (see Sequence::shifted). Returns the number of tokens cut. Such a sequence is no
+  // longer registered in the prefix index (its block chain has a hole).
+  int shift_front(int64_t id, int keep_tokens, int max_live) {
+    Sequence& s = get(id);
+    if (s.front_released > 0) throw std::invalid_argument("context shift on a sliding-window pool");
+    const int live = s.num_tokens - s.shifted;
+    if (live <= max_live) return 0;
+    const int keep_blocks = s.shifted > 0 ? s.keep_tokens / block_size_
+                                          : (std::max(0, keep_tokens) + block_size_ - 1) / block_size_;
+    // never touch the block that is being written
+    const int last_full = std::max(0, live - 1) / block_size_;
+    const int drop = std::min((live - max_live + block_size_ - 1) / block_size_, last_full - keep_blocks);
+    if (drop <= 0) return 0;
+    if (s.num_hashed > keep_blocks) truncate_hash(s, keep_blocks);
+    for (int b = keep_blocks; b < keep_blocks + drop; ++b) release(s.blocks[b]);
+    s.blocks.erase(s.blocks.begin() + keep_blocks, s.blocks.begin() + keep_blocks + drop);
+    if (s.shifted == 0) s.keep_tokens = keep_blocks * block_size_;
+    s.shifted += drop * block_size_;
+    shifted_tokens_ += static_cast<long long>(drop) * block_size_;
+    return drop * block_size_;
   }
 
   void free_seq(int64_t id) {
@@ -284,7 +322,11 @@ class BlockManager {
     auto buf = out.mutable_unchecked<1>();
     if (out_offset + count > buf.shape(0)) throw std::invalid_argument("slot buffer");
     for (int i = 0; i < count; ++i) {
-      const int pos = start + i;
+      int pos = start + i;
+      if (s.shifted > 0 && pos >= s.keep_tokens) {
+        if (pos < s.keep_tokens + s.shifted) throw std::out_of_range("slot in a range cut by a context shift");
+        pos -= s.shifted;
+      }
       const int bi = pos / block_size_;
       if (bi >= static_cast<int>(s.blocks.size())) throw std::out_of_range("slot beyond reservation");
       if (s.blocks[bi] < 0) throw std::out_of_range("slot in a block released by the sliding window");
@@ -301,6 +343,7 @@ class BlockManager {
     d["registered"] = static_cast<int>(index_.size());
     d["sequences"] = static_cast<int>(seqs_.size());
     d["front_released"] = front_released_;
+    d["shifted_tokens"] = shifted_tokens_;
     d["prefix_hits"] = hits_;
     d["prefix_queries"] = queries_;
     d["evictions"] = evictions_;
@@ -387,7 +430,7 @@ class BlockManager {
   std::list<int> lru_;
   std::unordered_map<Hash128, int, Hash128Hasher> index_;
   std::unordered_map<int64_t, Sequence> seqs_;
-  long long hits_ = 0, queries_ = 0, evictions_ = 0, cow_copies_ = 0, front_released_ = 0;
+  long long hits_ = 0, queries_ = 0, evictions_ = 0, cow_copies_ = 0, front_released_ = 0, shifted_tokens_ = 0;
 };
 
 }  // namespace
@@ -418,6 +461,8 @@ PYBIND11_MODULE(_mlxcel_host, m) {
       .def("truncate", &BlockManager::truncate)
       .def("free_seq", &BlockManager::free_seq)
       .def("release_front", &BlockManager::release_front)
+      .def("shift_front", &BlockManager::shift_front, py::arg("seq_id"), py::arg("keep_tokens"), py::arg("max_live"))
+      .def("shifted", &BlockManager::shifted)
       .def("reset_prefix_cache", &BlockManager::reset_prefix_cache)
       .def("fill_tables", &BlockManager::fill_tables)
       .def("fill_slots", &BlockManager::fill_slots)

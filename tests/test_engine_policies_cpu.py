@@ -205,3 +205,59 @@ def test_sampler_match_acceptance_reproduces_classic_sampling():
     eng.drafter = DraftModelDrafter(DecoderModel(cfg, w), cfg, num_blocks=96, max_model_len=384)
     eng.generate(prompts[:1], SamplingParams(max_tokens=8, ignore_eos=True, temperature=0.7, repetition_penalty=1.3, seed=3))
     assert eng.stats["spec_rounds"] == 0
+
+
+def test_context_shift_generates_past_the_window_and_bounds_the_cache():
+    """--max-kv-size with context shifting: a sequence keeps generating past max_model_len, its live KV
+    never exceeds the bound, the first n_keep tokens' blocks stay, every block returns to the pool at the
+    end, tokens before the first shift equal those of an engine without the bound, and a sequence
+    decodes the same alone as beside another one. Without context shifting the bound ends the
+    sequence with finish reason "length"."""
+    import torch
+
+    from mlxcel_b200.config import preset
+    from mlxcel_b200.engine import Engine, EngineConfig, SamplingParams
+    from mlxcel_b200.models.decoder import DecoderModel
+    from mlxcel_b200.models.weights import random_weights
+
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, seed=11, dtype=torch.float32, std=0.05)
+    g = torch.Generator().manual_seed(5)
+    p1 = torch.randint(0, cfg.vocab_size, (21,), generator=g).tolist()
+    p2 = torch.randint(0, cfg.vocab_size, (9,), generator=g).tolist()
+
+    def eng(**kw):
+        base = dict(max_batch=4, max_num_batched_tokens=64, num_blocks=40, block_size=8, max_model_len=64,
+                    cuda_graphs=False, prefix_cache=False)
+        base.update(kw)
+        return Engine(DecoderModel(cfg, w), cfg, EngineConfig(**base))
+
+    sp = SamplingParams(max_tokens=150, temperature=0.0, ignore_eos=True)
+    plain = eng(max_model_len=256, num_blocks=80).generate([p1], SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True))[0].output
+    e = eng(max_kv_size=48, context_shift=True, n_keep=6)
+    free0 = e.bm.num_free
+    outs = e.generate([p1], sp)
+    o = outs[0]
+    assert len(o.output) == 150 and o.finish_reason == "length"            # ended by max_tokens, far past max_model_len
+    assert o.output[:20] == plain                                          # nothing changes before the first shift
+    assert e.stats["context_shifts"] >= 5 and e.stats["context_shift_tokens"] % 8 == 0
+    assert e.bm.num_free == free0                                          # every block came back
+    # batch invariance with shifting on
+    e2 = eng(max_kv_size=48, context_shift=True, n_keep=6)
+    both = e2.generate([p2, p1], sp)
+    assert both[1].output == o.output
+    # the live window stays under the bound (checked on the block manager while decoding)
+    e3 = eng(max_kv_size=48, context_shift=True, n_keep=6)
+    sid = e3.add_request(p1, sp)
+    peak = 0
+    while e3.has_work():
+        e3.step()
+        if e3.bm.has_seq(sid):
+            live = e3.bm.seq_len(sid) - e3.bm.shifted(sid)
+            peak = max(peak, live)
+            assert e3.bm.seq_blocks(sid)[0] >= 0 and len(e3.bm.seq_blocks(sid)) <= 48 // 8 + 1
+    assert 40 <= peak <= 48
+    # no shifting: the bound is a stop
+    e4 = eng(max_kv_size=48)
+    o4 = e4.generate([p1], sp)[0]
+    assert o4.finish_reason == "length" and len(p1) + len(o4.output) + 1 == 48
