@@ -881,6 +881,21 @@ def _ministral3(c: ModelConfig, raw: dict) -> None:
                                         int(rp.get("original_max_position_embeddings") or c.max_position_embeddings))
 
 
+def _mistral4(c: ModelConfig, raw: dict) -> None:
+    """Mistral 4 (Mistral Small 4 / Large 3 line): multi-head latent attention with the Ministral-3
+    position-dependent query scale and no YaRN factor in the softmax scale, softmax router limited to
+    the best groups (sum of each group's two best scores), normalised and scaled weights, shared
+    experts, dense layers first; experts stored fused as [E, 2I, H] / [E, H, I]
+    (reference src/models/mistral4.rs)."""
+    _deepseek_routing(c, raw)
+    c.router_bias = False
+    c.extra["moe_routing"].update(score="softmax", group_score="top2sum", norm_min=1e-20)
+    _deepseek_mla(c, raw)
+    qk = int(raw["qk_nope_head_dim"]) + int(raw["qk_rope_head_dim"])
+    c.query_pre_attn_scalar = float(qk)                 # plain 1 / sqrt(qk): no mscale^2 factor here
+    _ministral3(c, raw)
+
+
 def _nanochat(c: ModelConfig, raw: dict) -> None:
     """nanochat: RMSNorm without gains everywhere (blocks, final, and per-head q/k norms applied AFTER the
     rotary embedding), plain MLP fc1 -> relu^2 -> fc2, logit soft cap (reference src/models/nanochat.rs)."""
@@ -1110,7 +1125,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "mistral4": _mistral4, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

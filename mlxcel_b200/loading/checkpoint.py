@@ -340,6 +340,10 @@ def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
         # GraniteMoE: fused [E, 2I, H] (gate rows first) and [E, H, I]
         lw.experts_gate_up = g.src.get(p + ".block_sparse_moe.input_linear.weight").to(g.dtype).contiguous()
         lw.experts_down = g.src.get(p + ".block_sparse_moe.output_linear.weight").to(g.dtype).contiguous()
+    elif g.src.has(p + ".mlp.experts.gate_up_proj") and cfg.model_type != "gpt_oss":
+        # fused expert tensors already in Linear orientation: [E, 2I, H] (gate rows, then up rows), [E, H, I]
+        lw.experts_gate_up = g.src.get(p + ".mlp.experts.gate_up_proj").to(g.dtype).contiguous()
+        lw.experts_down = g.src.get(p + ".mlp.experts.down_proj").to(g.dtype).contiguous()
     elif g.src.has(p + ".mlp.experts.gate_up_proj"):
         # GPT-OSS HF layout: [E, H, 2I] with gate/up interleaved along the last dim
         gu = g.src.get(p + ".mlp.experts.gate_up_proj").to(g.dtype)

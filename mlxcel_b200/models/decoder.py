@@ -310,6 +310,10 @@ class DecoderModel:
         kvb = _linear_any(ops.rmsnorm(ckv[:, :lat].contiguous(), w["kv_a_norm"], 1e-6, 0.0), w["kv_b"]).view(T, Hq, nope + vd)
         q_rot = ref.apply_rope(q[..., nope:], b.positions, self.inv_freq_mla, r, m["interleave"], self.mscale)
         k_rot = ref.apply_rope(ckv[:, lat:].view(T, 1, r), b.positions, self.inv_freq_mla, r, m["interleave"], self.mscale)
+        if cfg.extra.get("llama4_attn_scale"):           # Mistral 4: queries grow with the log of their position block
+            beta, orig = cfg.extra["llama4_attn_scale"]
+            sc = (1.0 + beta * torch.log1p(torch.floor(b.positions.float() / orig)))[:, None, None]
+            q, q_rot = (q.float() * sc).to(q.dtype), (q_rot.float() * sc).to(q_rot.dtype)
         qkv = torch.zeros(T, 3 * Hq, Dp, dtype=x.dtype, device=x.device)
         qkv[:, :Hq, :nope] = q[..., :nope]
         qkv[:, :Hq, nope:nope + r] = q_rot.to(x.dtype)

@@ -85,6 +85,13 @@ FAMILIES = {
                           pad_token_id=0),
     "mamba2": dict(num_heads=8, head_dim=16, state_size=16, n_groups=1, expand=2, conv_kernel=4, chunk_size=8),
     "bitnet": dict(tie_word_embeddings=False),
+    "mistral4": dict(moe_intermediate_size=48, num_key_value_heads=4, n_routed_experts=8, num_local_experts=8,
+                     num_experts_per_tok=2, n_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1,
+                     routed_scaling_factor=1.5, q_lora_rank=24, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                     v_head_dim=16, pad_token_id=0,
+                     rope_parameters=dict(rope_type="yarn", rope_theta=10000.0, factor=4.0, original_max_position_embeddings=8,
+                                          beta_fast=32.0, beta_slow=1.0, mscale=1.0, mscale_all_dim=1.0,
+                                          llama_4_scaling_beta=0.1)),
     "llama4_text": dict(intermediate_size=48, intermediate_size_mlp=96, num_hidden_layers=4, head_dim=16, num_local_experts=4,
                         num_experts_per_tok=1, interleave_moe_layer_step=2, no_rope_layer_interval=4, attention_chunk_size=128,
                         floor_scale=8, attn_scale=0.1, use_qk_norm=True, pad_token_id=0),
@@ -101,7 +108,12 @@ def _hf_model(name: str):
             kw.pop(k)
     torch.manual_seed(0)
     try:
-        model = AutoModelForCausalLM.from_config(AutoConfig.for_model(name, **kw)).float().eval()
+        hc = AutoConfig.for_model(name, **kw)
+        if name == "mistral4":                                       # not in the causal-LM auto mapping
+            from transformers.models.mistral4.modeling_mistral4 import Mistral4ForCausalLM
+            model = Mistral4ForCausalLM(hc).float().eval()
+        else:
+            model = AutoModelForCausalLM.from_config(hc).float().eval()
     except (KeyError, ValueError, ImportError) as e:                 # this transformers has no such family
         pytest.skip(f"transformers cannot build {name}: {e}")
     with torch.no_grad():
