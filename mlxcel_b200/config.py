@@ -881,6 +881,32 @@ def _ministral3(c: ModelConfig, raw: dict) -> None:
                                         int(rp.get("original_max_position_embeddings") or c.max_position_embeddings))
 
 
+def _afmoe(c: ModelConfig, raw: dict) -> None:
+    """Arcee AFM MoE (Trinity): norms before and after both the attention and the MLP / MoE block,
+    per-head q/k RMSNorm, rotary embedding on the sliding-window layers only, a sigmoid output gate on
+    the attention (``gate_proj``), sigmoid router with a selection bias, normalised and scaled
+    weights, shared experts, ``num_dense_layers`` dense layers first, optional muP input scaling
+    (reference src/models/afmoe.rs)."""
+    n = c.num_hidden_layers
+    c.post_norms = True
+    c.extra["post_norm_names"] = ("post_attention_layernorm", "pre_mlp_layernorm", "post_mlp_layernorm")
+    c.qk_norm = True
+    if c.layer_types is None:
+        every = int(raw.get("global_attn_every_n_layers", 4) or 4)
+        c.layer_types = ["full_attention" if (i + 1) % every == 0 else "sliding_attention" for i in range(n)]
+    c.extra["nope_layers"] = [i for i, t in enumerate(c.layer_types) if t != "sliding_attention"]
+    c.extra["attn_output_gate"] = True
+    c.num_experts = int(raw.get("num_experts", 0) or 0)
+    c.moe_route_mode = "sigmoid_group"
+    c.norm_topk_prob = True
+    c.extra["moe_routing"] = dict(n_group=1, topk_group=1, scale=float(raw.get("route_scale", 1.0) or 1.0), norm_min=1e-20)
+    c.extra["first_k_dense"] = int(raw.get("num_dense_layers", 0) or 0)
+    c.shared_expert_intermediate_size = c.moe_intermediate_size * int(raw.get("num_shared_experts", 0) or 0)
+    c.router_bias = True
+    if raw.get("mup_enabled"):
+        c.embed_scale = math.sqrt(c.hidden_size)
+
+
 def _mistral4(c: ModelConfig, raw: dict) -> None:
     """Mistral 4 (Mistral Small 4 / Large 3 line): multi-head latent attention with the Ministral-3
     position-dependent query scale and no YaRN factor in the softmax scale, softmax router limited to
@@ -1125,7 +1151,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "mistral4": _mistral4, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

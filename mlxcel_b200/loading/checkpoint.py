@@ -312,7 +312,7 @@ def _load_dense_mlp(g: _Getter, p: str, lw: LayerWeights) -> None:
 def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
     E = cfg.num_experts
     # router
-    rb = _first(g, p + ".mlp.router", p + ".mlp.gate.wg", p + ".mlp.gate", p + ".block_sparse_moe.gate",
+    rb = _first(g, p + ".mlp.router.gate", p + ".mlp.router", p + ".mlp.gate.wg", p + ".mlp.gate", p + ".block_sparse_moe.gate",
                 p + ".block_sparse_moe.router.layer")
     r = g.mat(rb)
     if isinstance(r, QuantizedTensor):   # routers are small: keep them dense
@@ -320,7 +320,7 @@ def _load_moe(g: _Getter, cfg: ModelConfig, p: str, lw: LayerWeights) -> None:
         r = dequantize_ref(r, g.dtype)
     lw.router_w = r
     lw.router_b = g.vec(rb + ".bias")
-    for bias_name in (rb + ".e_score_correction_bias", p + ".mlp.moe_statics.e_score_correction_bias",
+    for bias_name in (rb + ".e_score_correction_bias", p + ".mlp.expert_bias", p + ".mlp.moe_statics.e_score_correction_bias",
                       p + ".mlp.e_score_correction_bias", p + ".block_sparse_moe.e_score_correction_bias"):
         if g.src.has(bias_name):                               # DeepSeek-V3 / ERNIE routing: selection bias (fp32)
             lw.router_b = g.src.get(bias_name).float().reshape(-1)
@@ -429,13 +429,15 @@ def load_full_weights(path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16, 
             lw.post_attn_norm = g.vec(f"{p}.{names[0]}.weight")
             lw.ln2 = g.vec(f"{p}.{names[1]}.weight")
             lw.post_mlp_norm = g.vec(f"{p}.{names[2]}.weight")
-        if cfg.is_moe and _first(g, p + ".mlp.router", p + ".mlp.gate.wg", p + ".mlp.gate", p + ".block_sparse_moe.gate",
+        if cfg.is_moe and _first(g, p + ".mlp.router.gate", p + ".mlp.router", p + ".mlp.gate.wg", p + ".mlp.gate", p + ".block_sparse_moe.gate",
                                  p + ".block_sparse_moe.router.layer"):
             _load_moe(g, cfg, p, lw)
         else:
             _load_dense_mlp(g, p, lw)
         if cfg.extra.get("norm_plus_one"):                      # LayerNorm1P: stored as (weight - 1)
             lw.ln1, lw.ln2 = lw.ln1 + 1.0, lw.ln2 + 1.0
+        if cfg.extra.get("attn_output_gate"):
+            lw.attn_gate = g.mat(p + ".self_attn.gate_proj")
         lw.attn_sub_norm = g.vec(p + ".self_attn.attn_sub_norm.weight")
         lw.ffn_sub_norm = g.vec(p + ".mlp.ffn_sub_norm.weight")
         if src.has(p + ".mlp.act_fn.alpha_p"):                 # xIELU (Apertus): stored before softplus

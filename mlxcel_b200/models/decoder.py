@@ -144,6 +144,8 @@ class DecoderModel:
         self.layernorm = cfg.extra.get("norm") == "layernorm"
         self.clip_qkv = float(cfg.extra.get("clip_qkv") or 0.0)
         self.plain_mlp = cfg.extra.get("mlp") == "plain"
+        if cfg.extra.get("attn_output_gate") and self.comm.tp_size != 1:
+            raise NotImplementedError("the attention output gate is not sharded across tensor-parallel ranks")
         self.sub_norms = bool(cfg.extra.get("sub_norms"))
         if self.sub_norms and self.comm.tp_size != 1:
             raise NotImplementedError("sub-layer norms span the whole projection input: not sharded across tensor-parallel ranks")
@@ -403,6 +405,8 @@ class DecoderModel:
             kv = kv_layers[li]
             x = ops.rmsnorm(h, lw.ln1, eps, wb)
             a = self._attention(li, lw, x, b, kv)
+            if lw.attn_gate is not None:                    # AFMoE: sigmoid gate from the layer input
+                a = (a.float() * torch.sigmoid(_linear_any(x, lw.attn_gate).float())).to(a.dtype)
             if cfg.post_norms or res_mult != 1.0:
                 o = self.comm.row_parallel_linear(a, lw.wo, lw.bo, None)
                 if cfg.post_norms:
@@ -416,6 +420,9 @@ class DecoderModel:
             if cfg.is_moe and lw.router_w is not None and res_mult != 1.0:              # GraniteMoE: scaled expert branch
                 o = self._moe(lw, x, torch.zeros_like(h))
                 h = (h.float() + o.float() * res_mult).to(h.dtype)
+            elif cfg.is_moe and lw.router_w is not None and cfg.post_norms:     # AFMoE: a norm after the MoE block
+                o = ops.rmsnorm(self._moe(lw, x, torch.zeros_like(h)), lw.post_mlp_norm, eps, wb)
+                h = (h.float() + o.float()).to(h.dtype)
             elif cfg.is_moe and lw.router_w is not None:
                 h = self._moe(lw, x, h)
             else:

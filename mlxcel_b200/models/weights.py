@@ -65,6 +65,7 @@ class LayerWeights:
     ln2_b: torch.Tensor | None = None
     mla: dict | None = None                      # multi-head latent attention projections (DeepSeek)
     act_params: tuple | None = None              # xIELU: (alpha_p, alpha_n, beta, eps) of this layer
+    attn_gate: object | None = None              # AFMoE: sigmoid gate on the attention output, [Hq * D, H]
     attn_sub_norm: torch.Tensor | None = None    # BitNet: RMSNorm of the attention output before o_proj
     ffn_sub_norm: torch.Tensor | None = None     # BitNet: RMSNorm of act(gate) * up before down_proj
     # dense MLP

@@ -85,6 +85,9 @@ FAMILIES = {
                           pad_token_id=0),
     "mamba2": dict(num_heads=8, head_dim=16, state_size=16, n_groups=1, expand=2, conv_kernel=4, chunk_size=8),
     "bitnet": dict(tie_word_embeddings=False),
+    "afmoe": dict(num_hidden_layers=4, head_dim=16, moe_intermediate_size=48, num_dense_layers=1, num_experts=8,
+                  num_experts_per_tok=2, num_shared_experts=1, route_scale=1.5, global_attn_every_n_layers=2, sliding_window=8,
+                  mup_enabled=True, pad_token_id=0),
     "mistral4": dict(moe_intermediate_size=48, num_key_value_heads=4, n_routed_experts=8, num_local_experts=8,
                      num_experts_per_tok=2, n_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1,
                      routed_scaling_factor=1.5, q_lora_rank=24, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8,
@@ -118,10 +121,12 @@ def _hf_model(name: str):
         pytest.skip(f"transformers cannot build {name}: {e}")
     with torch.no_grad():
         for n, buf in model.named_buffers():
-            if "e_score_correction_bias" in n:
+            if "e_score_correction_bias" in n or "expert_bias" in n:
                 buf.copy_(torch.randn_like(buf) * 0.2)               # a selection bias that changes the choice
         for n, p in model.named_parameters():
-            if p.dim() >= 2:
+            if "expert_bias" in n:
+                p.copy_(torch.randn_like(p) * 0.2)                   # a selection bias that changes the choice
+            elif p.dim() >= 2:
                 p.normal_(0, 0.08)                                   # logits with some spread
             elif ("norm" in n or "ln" in n) and "bias" not in n:
                 p.add_(torch.randn_like(p) * 0.1)                    # gains that are not all one
