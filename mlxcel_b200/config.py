@@ -705,6 +705,20 @@ def _deepseek_v3(c: ModelConfig, raw: dict) -> None:
     _deepseek_mla(c, raw)
 
 
+def _glm_moe_dsa(c: ModelConfig, raw: dict) -> None:
+    """GLM-5 / DeepSeek-V3.2 layout: the DeepSeek-V3 model (latent attention, sigmoid group-limited
+    routing) with half-split rotary pairs and a sparse-attention indexer that keeps the ``index_topk``
+    best keys of every query. Contexts are served up to ``index_topk`` tokens, where the selection
+    keeps every key and attention is dense; the indexer itself is not built
+    (reference src/models/glm_moe_dsa.rs, deepseek_v32.rs)."""
+    raw = dict(raw)
+    raw.setdefault("rope_interleave", False)
+    _deepseek_v3(c, raw)
+    topk = int(raw.get("index_topk", 2048) or 2048)
+    c.extra["dsa_index_topk"] = topk
+    c.max_position_embeddings = min(c.max_position_embeddings, topk)
+
+
 def _deepseek_v2(c: ModelConfig, raw: dict) -> None:
     """DeepSeek-V2 / V2-Lite: multi-head latent attention, softmax routing (greedy or limited to the
     groups with the best single score), weights not normalised, shared experts
@@ -1151,7 +1165,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

@@ -85,6 +85,10 @@ FAMILIES = {
                           pad_token_id=0),
     "mamba2": dict(num_heads=8, head_dim=16, state_size=16, n_groups=1, expand=2, conv_kernel=4, chunk_size=8),
     "bitnet": dict(tie_word_embeddings=False),
+    "glm_moe_dsa": dict(moe_intermediate_size=48, num_key_value_heads=4, n_routed_experts=8, num_experts_per_tok=2,
+                        n_shared_experts=1, n_group=2, topk_group=1, mlp_layer_types=["dense", "sparse"], routed_scaling_factor=1.8,
+                        q_lora_rank=24, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                        index_topk=64, index_head_dim=16, index_n_heads=2, pad_token_id=0),
     "afmoe": dict(num_hidden_layers=4, head_dim=16, moe_intermediate_size=48, num_dense_layers=1, num_experts=8,
                   num_experts_per_tok=2, num_shared_experts=1, route_scale=1.5, global_attn_every_n_layers=2, sliding_window=8,
                   mup_enabled=True, pad_token_id=0),
@@ -119,6 +123,10 @@ def _hf_model(name: str):
             model = AutoModelForCausalLM.from_config(hc).float().eval()
     except (KeyError, ValueError, ImportError) as e:                 # this transformers has no such family
         pytest.skip(f"transformers cannot build {name}: {e}")
+    if name == "glm_moe_dsa":
+        # with sdpa and no padding mask this transformers version hands the indexer's (all-zero) mask to
+        # the attention in place of the causal one; the eager path combines the two
+        model.config._attn_implementation = "eager"
     with torch.no_grad():
         for n, buf in model.named_buffers():
             if "e_score_correction_bias" in n or "expert_bias" in n:
