@@ -895,6 +895,33 @@ def _ministral3(c: ModelConfig, raw: dict) -> None:
                                         int(rp.get("original_max_position_embeddings") or c.max_position_embeddings))
 
 
+def _recurrent_gemma(c: ModelConfig, raw: dict) -> None:
+    """RecurrentGemma (Griffin): residual blocks whose temporal mixer is an RG-LRU recurrent block or
+    local multi-query attention (``block_types`` repeated over the layers), each followed by a gated
+    tanh-GELU MLP with biases; Gemma conventions elsewhere ((1 + w) norms, sqrt(hidden) embedding
+    scale, tied head, logit soft cap) (reference src/models/recurrent_gemma.rs). Runs on the hybrid
+    executor as ``R`` / ``*`` + ``G``."""
+    n = c.num_hidden_layers
+    types = list(raw.get("block_types") or ("recurrent", "recurrent", "attention"))
+    kinds = (types * n)[:n]
+    c.extra["hybrid_pattern"] = "".join(("R" if k == "recurrent" else "*") + "G" for k in kinds)
+    c.extra["hybrid_layout"] = "recurrent_gemma"
+    c.extra["rglru"] = dict(width=int(raw.get("lru_width") or c.hidden_size), heads=c.num_attention_heads,
+                            d_conv=int(raw.get("conv1d_width", 4)))
+    c.num_key_value_heads = int(raw.get("num_key_value_heads") or 1)
+    c.head_dim = int(raw.get("head_dim") or c.hidden_size // c.num_attention_heads)
+    c.partial_rotary_factor = float(raw.get("partial_rotary_factor", 0.5))
+    c.sliding_window = int(raw.get("attention_window_size", 2048))
+    c.layer_types = None
+    c.intermediate_size = int(raw.get("intermediate_size", 3 * c.hidden_size)) // 2     # the config counts gate + up
+    c.hidden_act = "gelu_tanh"
+    c.embed_scale = math.sqrt(c.hidden_size)
+    c.final_logit_softcap = float(raw.get("logits_soft_cap", 30.0) or 0.0)
+    c.rms_norm_eps = float(raw.get("rms_norm_eps", 1e-6))
+    c.tie_word_embeddings = bool(raw.get("tie_word_embeddings", True))
+    c.attention_bias = bool(raw.get("attention_bias", False))
+
+
 def _afmoe(c: ModelConfig, raw: dict) -> None:
     """Arcee AFM MoE (Trinity): norms before and after both the attention and the MLP / MoE block,
     per-head q/k RMSNorm, rotary embedding on the sliding-window layers only, a sigmoid output gate on
@@ -1165,7 +1192,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "recurrent_gemma": _recurrent_gemma, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

@@ -46,6 +46,9 @@ class HybridBlock:
     up: torch.Tensor | None = None              # plain MLP [I, H]; gated MLP: [2I, H] (gate rows first)
     down: torch.Tensor | None = None            # [H, I]
     gated: bool = False
+    act: str = "silu"                           # activation of a gated MLP block
+    up_b: torch.Tensor | None = None            # MLP biases (RecurrentGemma)
+    down_b: torch.Tensor | None = None
     out_gate: torch.Tensor | None = None        # gated attention (Qwen3-Next): [Hq * D, H] sigmoid gate projection
     latent_in: torch.Tensor | None = None       # Nemotron-H MoE: optional projections around the routed experts
     latent_out: torch.Tensor | None = None      #   ([latent, H] and [H, latent]); up / down hold the shared expert
@@ -60,13 +63,14 @@ class HybridWeights:
     layers: list = field(default_factory=list)  # the attention blocks' LayerWeights (= KV-pool layers)
 
 
-_KINDS = {"M": "mamba2", "m": "mamba1", "L": "gdn", "C": "shortconv", "P": "parallel", "*": "attention", "A": "attention", "-": "mlp", "G": "mlp",
+_KINDS = {"M": "mamba2", "m": "mamba1", "L": "gdn", "C": "shortconv", "R": "rglru", "P": "parallel", "*": "attention", "A": "attention", "-": "mlp", "G": "mlp",
           "E": "moe"}   # G: gated MLP, A: attention with an output gate, L: Gated DeltaNet
 
 
 def block_kinds(cfg: ModelConfig) -> list[str]:
     pat = cfg.extra["hybrid_pattern"]
-    per_layer = 2 if cfg.extra.get("hybrid_layout") in ("granite", "jamba", "qwen3_next", "falcon_h1", "lfm2") else 1
+    per_layer = 2 if cfg.extra.get("hybrid_layout") in ("granite", "jamba", "qwen3_next", "falcon_h1", "lfm2",
+                                                             "recurrent_gemma") else 1
     if len(pat) != cfg.num_hidden_layers * per_layer:
         raise ValueError(f"hybrid pattern has {len(pat)} entries for {cfg.num_hidden_layers} layers")
     try:
@@ -429,6 +433,70 @@ def load_qwen3_next_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device
                          lm_head=embed if head is None else head.to(device), layers=attn_layers)
 
 
+def load_recurrent_gemma_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
+    """RecurrentGemma checkpoint: ``model.layers.N.{temporal_pre_norm, temporal_block.*, channel_pre_norm,
+    mlp_block.*}``. Norms are stored as (weight - 1); the RG-LRU gate blocks are stored as
+    [heads, in, out] and are transposed to Linear orientation here."""
+    from ..loading.checkpoint import TensorSource, _Getter, _cat_rows
+    from .rglru import RglruLayerWeights
+
+    src = TensorSource(path)
+    g = _Getter(src, cfg, dtype, dequantize=True)
+    W, K = int(cfg.extra["rglru"]["width"]), int(cfg.extra["rglru"]["d_conv"])
+
+    def need(t, name):
+        if t is None:
+            raise KeyError(f"{path}: missing tensor {name}")
+        return t.to(device)
+
+    def vec(name):
+        return need(g.vec(name), name)
+
+    def plus1(name):
+        return (vec(name).float() + 1.0).to(dtype)
+
+    blocks, attn_layers = [], []
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        t = p + "temporal_block."
+        norm = plus1(p + "temporal_pre_norm.weight")
+        if src.has(t + "rg_lru.recurrent_param"):
+            cw = vec(t + "conv_1d.weight")
+            lw = RglruLayerWeights(
+                norm=norm, linear_y=need(g.mat(t + "linear_y"), t + "linear_y"), linear_y_b=vec(t + "linear_y.bias"),
+                linear_x=need(g.mat(t + "linear_x"), t + "linear_x"), linear_x_b=vec(t + "linear_x.bias"),
+                conv_w=cw.reshape(W, K).float(), conv_b=vec(t + "conv_1d.bias").float(),
+                gate_in_w=vec(t + "rg_lru.input_gate_weight").transpose(1, 2).contiguous(),
+                gate_in_b=vec(t + "rg_lru.input_gate_bias").reshape(-1),
+                gate_rec_w=vec(t + "rg_lru.recurrent_gate_weight").transpose(1, 2).contiguous(),
+                gate_rec_b=vec(t + "rg_lru.recurrent_gate_bias").reshape(-1),
+                decay=vec(t + "rg_lru.recurrent_param").float(),
+                out_proj=need(g.mat(t + "linear_out"), t + "linear_out"), out_proj_b=g.vec(t + "linear_out.bias"))
+            blocks.append(HybridBlock("rglru", norm, mamba=lw))
+        else:
+            bs = [g.vec(t + f"{n}_proj.bias") for n in "qkv"]
+            lw = LayerWeights(ln1=norm, ln2=norm,
+                              wqkv=_cat_rows([need(g.mat(t + f"{n}_proj"), t + f"{n}_proj") for n in "qkv"]),
+                              bqkv=torch.cat(bs).to(device) if all(b is not None for b in bs) else None,
+                              wo=need(g.mat(t + "o_proj"), t + "o_proj"), bo=g.vec(t + "o_proj.bias"))
+            if lw.bo is not None:
+                lw.bo = lw.bo.to(device)
+            attn_layers.append(lw)
+            blocks.append(HybridBlock("attention", norm, attn=lw))
+        m = p + "mlp_block."
+        bg, bu = g.vec(m + "gate_proj.bias"), g.vec(m + "up_proj.bias")
+        blocks.append(HybridBlock("mlp", plus1(p + "channel_pre_norm.weight"),
+                                  up=_cat_rows([need(g.mat(m + "gate_proj"), m + "gate_proj"),
+                                                need(g.mat(m + "up_proj"), m + "up_proj")]),
+                                  down=need(g.mat(m + "down_proj"), m + "down_proj"), gated=True, act="gelu_tanh",
+                                  up_b=torch.cat([bg, bu]).to(device) if bg is not None and bu is not None else None,
+                                  down_b=None if g.vec(m + "down_proj.bias") is None else g.vec(m + "down_proj.bias").to(device)))
+    embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")
+    head = g.mat("lm_head") if src.has("lm_head.weight") and not cfg.tie_word_embeddings else None
+    return HybridWeights(embed=embed, blocks=blocks, final_norm=plus1("model.final_norm.weight"),
+                         lm_head=embed if head is None else head.to(device), layers=attn_layers)
+
+
 def load_falcon_h1_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu") -> HybridWeights:
     """Falcon-H1 checkpoint: ``model.layers.N.{input_layernorm, mamba.*, self_attn.*, pre_ff_layernorm,
     feed_forward.*}``. Every muP multiplier of the config is a constant factor on one projection's
@@ -550,7 +618,12 @@ class HybridModel:
         mamba1_layers = [b.mamba for b in weights.blocks if b.kind == "mamba1"]
         gdn_layers = [b.mamba for b in weights.blocks if b.kind == "gdn"]
         conv_layers = [b.mamba for b in weights.blocks if b.kind == "shortconv"]
-        if conv_layers:                         # LFM2: gated short convolutions
+        rglru_layers = [b.mamba for b in weights.blocks if b.kind == "rglru"]
+        if rglru_layers:                        # RecurrentGemma: RG-LRU recurrent blocks
+            from .rglru import RglruModel
+            self.ssm = RglruModel(cfg, Mamba2Weights(weights.embed, rglru_layers, weights.final_norm, weights.lm_head),
+                                  max_seqs=max_seqs, comm=self.comm)
+        elif conv_layers:                         # LFM2: gated short convolutions
             from .shortconv import ShortConvModel
             self.ssm = ShortConvModel(cfg, Mamba2Weights(weights.embed, conv_layers, weights.final_norm, weights.lm_head),
                                       max_seqs=max_seqs, comm=self.comm)
@@ -591,7 +664,7 @@ class HybridModel:
 
         for blk in self.w.blocks:
             x = ops.rmsnorm(h, blk.norm, eps, 0.0)
-            if blk.kind in ("mamba2", "mamba1", "gdn", "shortconv"):
+            if blk.kind in ("mamba2", "mamba1", "gdn", "shortconv", "rglru"):
                 h = add(self.ssm._mixer(mi, blk.mamba, x, pieces), blk.mamba.out_proj,
                         getattr(blk.mamba, "out_proj_b", None))
                 mi += 1
@@ -628,7 +701,7 @@ class HybridModel:
                 h = add(a, blk.attn.wo, blk.attn.bo)
                 ai += 1
             elif blk.gated:
-                h = add(ops.glu_linear(x, blk.up, blk.up.shape[0] // 2, "silu"), blk.down)
+                h = add(ops.glu_linear(x, blk.up, blk.up.shape[0] // 2, blk.act, bias=blk.up_b), blk.down, blk.down_b)
             else:
                 h = add(rops.relu2(ops.linear(x, blk.up)), blk.down)
         return h
@@ -636,7 +709,9 @@ class HybridModel:
     def logits(self, h: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:
         lg = self.ssm.logits(h, rows)
         ls = self.cfg.extra.get("logits_scaling", 1.0)
-        return lg if ls == 1.0 else (lg.float() / ls).to(lg.dtype)
+        lg = lg if ls == 1.0 else (lg.float() / ls).to(lg.dtype)
+        cap = self.cfg.final_logit_softcap
+        return lg if cap <= 0 else (torch.tanh(lg.float() / cap) * cap).to(lg.dtype)
 
     def forward(self, b: StepBatch, kv_layers=None) -> torch.Tensor:
         return self.logits(self.forward_hidden(b, kv_layers), b.logits_rows)

@@ -302,7 +302,14 @@ def _tiny_hf_hybrid(name):
                                  logits_scaling=2.0),
         "lfm2": dict(layer_types=["conv", "full_attention", "conv", "conv"], conv_L_cache=3, conv_bias=False,
                      block_auto_adjust_ff_dim=False),
+        "recurrent_gemma": dict(head_dim=64, lru_width=128, attention_window_size=32, conv1d_width=4, intermediate_size=512),
+        "qwen3_5_text": dict(head_dim=64, layer_types=["linear_attention", "linear_attention", "full_attention",
+                                                       "linear_attention"],
+                             linear_conv_kernel_dim=4, linear_key_head_dim=32, linear_value_head_dim=32,
+                             linear_num_key_heads=2, linear_num_value_heads=4),
     }[name]
+    if name == "recurrent_gemma":
+        common = {k: v for k, v in common.items() if k != "intermediate_size"}
     torch.manual_seed(0)
     try:
         model = AutoModelForCausalLM.from_config(AutoConfig.for_model(name, **common, **kw)).float()
@@ -310,14 +317,14 @@ def _tiny_hf_hybrid(name):
         pytest.skip(f"transformers cannot build {name}: {e}")
     with torch.no_grad():
         for n, p in model.named_parameters():
-            if p.dim() >= 2 and "A_log" not in n:
+            if p.dim() >= 2 and "A_log" not in n and "recurrent_param" not in n:
                 p.normal_(0, 0.05)
     d = tempfile.mkdtemp(prefix=f"hyb_{name}_")
     model.save_pretrained(d, safe_serialization=True)
     return d
 
 
-@pytest.mark.parametrize("name", ["jamba", "qwen3_next", "granitemoehybrid", "lfm2"])
+@pytest.mark.parametrize("name", ["jamba", "qwen3_next", "granitemoehybrid", "lfm2", "recurrent_gemma", "qwen3_5_text"])
 def test_hybrid_checkpoints_gpu_matches_cpu(name):
     """Hybrid layouts end to end on the GPU (bf16 kernels) against this package's fp32 CPU path, from a
     checkpoint written by transformers: prompt logits, then a short greedy run through the engine."""
@@ -331,7 +338,8 @@ def test_hybrid_checkpoints_gpu_matches_cpu(name):
     d = _tiny_hf_hybrid(name)
     cfg = ModelConfig.from_path(d)
     load = {"jamba": hybrid.load_jamba_weights, "qwen3_next": hybrid.load_qwen3_next_weights,
-            "granitemoehybrid": hybrid.load_granite_hybrid_weights, "lfm2": hybrid.load_lfm2_weights}[name]
+            "granitemoehybrid": hybrid.load_granite_hybrid_weights, "lfm2": hybrid.load_lfm2_weights,
+            "recurrent_gemma": hybrid.load_recurrent_gemma_weights, "qwen3_5_text": hybrid.load_qwen3_next_weights}[name]
     T = 40
     ids = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
 

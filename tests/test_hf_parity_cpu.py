@@ -680,3 +680,57 @@ def test_qwen3_5_matches_transformers(mt):
             row = lg[n0 - 1 + i]
             assert row[tok].item() >= row.max().item() - 2e-3
     assert want.shape == (T, 300)
+
+
+def test_recurrent_gemma_matches_transformers():
+    """RecurrentGemma (RG-LRU recurrent blocks mapped onto the selective-scan op, local multi-query
+    attention with half-rotary heads, biased gated MLPs, soft-capped logits) on the hybrid executor:
+    prompt logits, then chunked prefill + batched decode through the engine checked teacher-forced."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.models.hybrid import HybridModel, load_recurrent_gemma_weights
+
+    torch.manual_seed(0)
+    hc = AutoConfig.for_model("recurrent_gemma", hidden_size=64, intermediate_size=192, num_hidden_layers=5, num_attention_heads=4,
+                              num_key_value_heads=1, head_dim=16, vocab_size=300, lru_width=64, attention_window_size=16,
+                              conv1d_width=4, logits_soft_cap=30.0, pad_token_id=0)
+    model = AutoModelForCausalLM.from_config(hc).float().eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "recurrent_param" in n:
+                continue
+            if p.dim() >= 2:
+                p.normal_(0, 0.1)
+            else:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tempfile.mkdtemp(prefix="parity_recurrent_gemma_")
+    model.save_pretrained(d, safe_serialization=True)
+    T = 24
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None], use_cache=False).logits[0]
+    cfg = ModelConfig.from_path(d)
+    assert cfg.extra["hybrid_pattern"] == "RGRG*GRGRG" and cfg.rot_dim == 8 and cfg.sliding_window == 16
+    ours = HybridModel(cfg, load_recurrent_gemma_weights(d, cfg, dtype=torch.float32), max_seqs=4)
+    pool = KVPool(cfg, 8, 16, device="cpu", dtype=torch.float32, num_layers=ours.num_kv_layers)
+    b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
+                  slot_mapping=torch.arange(T, dtype=torch.int32), num_prefill_seqs=1,
+                  pf_block_tables=torch.arange(8, dtype=torch.int32)[None],
+                  pf_cu_q=torch.tensor([0, T], dtype=torch.int32),
+                  pf_context_lens=torch.tensor([T], dtype=torch.int32), pf_max_q_len=T, pf_cu_q_host=[0, T],
+                  logits_rows=torch.arange(T))
+    b.seq_ids, b.pf_starts = [0], [0]
+    got = ours.forward(b, pool.layers).float()
+    assert (got - want).abs().max().item() < 2e-3 * max(want.abs().max().item(), 1.0)
+    ours.release_seq(0)
+    eng = Engine(ours, cfg, EngineConfig(num_blocks=64, block_size=16, max_batch=4, max_model_len=256,
+                                         max_num_batched_tokens=16))
+    outs = eng.generate([ids.tolist(), ids[:7].tolist()], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
+    for o, n0 in zip(outs, (T, 7)):
+        with torch.no_grad():
+            lg = model(torch.cat([ids[:n0], torch.tensor(o.output)])[None], use_cache=False).logits[0]
+        for i, tok in enumerate(o.output):
+            row = lg[n0 - 1 + i]
+            assert row[tok].item() >= row.max().item() - 2e-3
