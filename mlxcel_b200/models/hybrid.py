@@ -471,7 +471,7 @@ def load_recurrent_gemma_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, d
                 gate_rec_w=vec(t + "rg_lru.recurrent_gate_weight").transpose(1, 2).contiguous(),
                 gate_rec_b=vec(t + "rg_lru.recurrent_gate_bias").reshape(-1),
                 decay=vec(t + "rg_lru.recurrent_param").float(),
-                out_proj=need(g.mat(t + "linear_out"), t + "linear_out"), out_proj_b=g.vec(t + "linear_out.bias"))
+                out_proj=need(g.mat(t + "linear_out"), t + "linear_out"), out_proj_b=vec(t + "linear_out.bias"))
             blocks.append(HybridBlock("rglru", norm, mamba=lw))
         else:
             bs = [g.vec(t + f"{n}_proj.bias") for n in "qkv"]
@@ -491,6 +491,12 @@ def load_recurrent_gemma_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, d
                                   down=need(g.mat(m + "down_proj"), m + "down_proj"), gated=True, act="gelu_tanh",
                                   up_b=torch.cat([bg, bu]).to(device) if bg is not None and bu is not None else None,
                                   down_b=None if g.vec(m + "down_proj.bias") is None else g.vec(m + "down_proj.bias").to(device)))
+    for blk in blocks:                      # every tensor a kernel will read lives on the executor's device
+        for obj in (blk, blk.mamba, blk.attn):
+            if obj is not None:
+                for k, v in list(vars(obj).items()):
+                    if isinstance(v, torch.Tensor) and v.device != torch.device(device):
+                        setattr(obj, k, v.to(device))
     embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")
     head = g.mat("lm_head") if src.has("lm_head.weight") and not cfg.tie_word_embeddings else None
     return HybridWeights(embed=embed, blocks=blocks, final_norm=plus1("model.final_norm.weight"),
