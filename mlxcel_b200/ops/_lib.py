@@ -165,7 +165,13 @@ def check(rc: int, name: str) -> None:
 
 
 def ptr(t: torch.Tensor | None) -> int | None:
-    return None if t is None else t.data_ptr()
+    """Address of an optional kernel operand. A pageable host tensor here would hand a kernel a pointer
+    it cannot read (an illegal-address fault that takes the context down), so it is refused."""
+    if t is None:
+        return None
+    if not t.is_cuda and not t.is_pinned():
+        raise ValueError(f"a host tensor (shape {tuple(t.shape)}, {t.dtype}) was passed to a CUDA kernel")
+    return t.data_ptr()
 
 
 def stream() -> int:

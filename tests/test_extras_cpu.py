@@ -350,3 +350,16 @@ def test_tiktoken_vocabulary_files_load_and_round_trip(tmp_path):
     det = IncrementalDetokenizer(tk)
     assert "".join(det.push(i) for i in ids) + det.flush() == text
     assert len(tk.fingerprint()) == 16
+
+
+def test_host_tensors_are_refused_as_kernel_operands():
+    """An optional kernel operand that lives in pageable host memory is refused before any launch (the
+    kernel would fault on it and take the CUDA context down)."""
+    import pytest as _pytest
+    import torch
+
+    from mlxcel_b200.ops import _lib
+
+    assert _lib.ptr(None) is None
+    with _pytest.raises(ValueError, match="host tensor"):
+        _lib.ptr(torch.zeros(4))
