@@ -392,6 +392,20 @@ def attach_drafter(llm, a, dev) -> None:
             raise SystemExit(f"{draft}: the MTP drafter was split from a different model")
         eng.drafter = MTPDrafter(eng.model, dcfg, w, num_blocks=nb, block_size=eng.ecfg.block_size)
         return
+    from .speculative.dflash import is_dflash_dir
+    if is_dflash_dir(draft):
+        # a block drafter that conditions on the target's hidden states (one forward per block)
+        from .speculative.dflash import DFlashDrafter, load_dflash
+        dcfg, w, info = load_dflash(draft, dtype=dtype, device=dev)
+        if dcfg.hidden_size != llm.cfg.hidden_size or dcfg.vocab_size != llm.cfg.vocab_size:
+            raise SystemExit(f"{draft}: the block drafter was trained for a different target")
+        if not hasattr(eng.model, "capture_layers") or max(info["target_layers"]) >= llm.cfg.num_hidden_layers:
+            raise SystemExit(f"{draft}: the block drafter needs the decoder executor's hidden states of layers {info['target_layers']}")
+        block = min(info["block"], eng.spec_k_max)
+        eng.drafter = DFlashDrafter(eng.model, dcfg, w, info["target_layers"], info["mask_token_id"], num_blocks=nb,
+                                    block=block, block_size=eng.ecfg.block_size)
+        eng.spec_k = block
+        return
     from .config import ModelConfig
     from .loading.checkpoint import load_model_weights
     from .models.decoder import DecoderModel

@@ -1158,9 +1158,12 @@ class Engine:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 out = run()
-            ent = (g, out, _lib.launches() - n0)
+            # hidden states a drafter asked the executor to keep live in the graph's buffers too
+            ent = (g, out, _lib.launches() - n0, list(getattr(self.model, "captured", ())))
             self._graphs[key] = ent
         ent[0].replay()
+        if ent[3]:
+            self.model.captured = list(ent[3])
         self.stats["graph_replays"] += 1
         self.stats["verify_graph_replays"] = self.stats.get("verify_graph_replays", 0) + 1
         self.stats["graph_kernel_launches"] += ent[2]

@@ -142,6 +142,10 @@ class DecoderModel:
         self.fold_attn = self.fold_mlp = False
         self.nope_layers = frozenset(cfg.extra.get("nope_layers", ()))
         self.layernorm = cfg.extra.get("norm") == "layernorm"
+        # residual stream after these layers is kept in ``captured`` by every forward (block drafters
+        # condition on several depths of the target, see speculative/dflash.py)
+        self.capture_layers: tuple = ()
+        self.captured: list = []
         self.clip_qkv = float(cfg.extra.get("clip_qkv") or 0.0)
         self.plain_mlp = cfg.extra.get("mlp") == "plain"
         if cfg.extra.get("attn_output_gate") and self.comm.tp_size != 1:
@@ -383,6 +387,7 @@ class DecoderModel:
                 h = ops.rmsnorm(h, torch.ones_like(w.final_norm), cfg.rms_norm_eps, 0.0)
         eps, wb = cfg.rms_norm_eps, cfg.norm_weight_bias
         res_mult = cfg.extra.get("residual_multiplier", 1.0)
+        self.captured = []
         if self.fold_attn and h.is_cuda and h.shape[0] <= self._ssq.max_tokens and h.dtype == torch.bfloat16:
             return self._forward_folded(h, b, kv_layers)
         if self.fold_attn:
@@ -436,7 +441,12 @@ class DecoderModel:
                     h = (h.float() + o.float()).to(h.dtype) if not h.is_cuda else h.add_(o)
                 else:
                     h = self.comm.row_parallel_linear(m, lw.w_down, lw.b_down, h)
+            self._capture(li, h)
         return h
+
+    def _capture(self, li: int, h: torch.Tensor) -> None:
+        if self.capture_layers and (self.layer_range[li] if li < len(self.layer_range) else li) in self.capture_layers:
+            self.captured.append(h.clone())       # (later layers may add into h in place)
 
     def _forward_general(self, h: torch.Tensor, b: StepBatch, kv_layers: list[KVLayer]) -> torch.Tensor:
         """Layer loop of the less common layouts, without the fusions of the main path: LayerNorm
@@ -463,6 +473,7 @@ class DecoderModel:
                     h = self._moe(lw, x, h)
                 else:
                     h = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, h)
+            self._capture(li, h)
         return h
 
     def _forward_folded(self, h: torch.Tensor, b: StepBatch, kv_layers: list[KVLayer]) -> torch.Tensor:
@@ -486,6 +497,7 @@ class DecoderModel:
                     h = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, h)
                 if li + 1 < len(self.w.layers):
                     ops.row_ssq(h, ssq)
+            self._capture(li, h)
         return h
 
     def logits(self, h: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:

@@ -8,6 +8,7 @@ from .prompt_lookup import PromptLookupDrafter  # noqa: F401
 from .draft_model import DraftModelDrafter  # noqa: F401
 from .mtp import MTPDrafter, MTPWeights, random_mtp_weights  # noqa: F401
 from .policy import SpecPolicy, exactness_probe  # noqa: F401
+from .dflash import DFlashDrafter, DFlashWeights, random_dflash_weights  # noqa: F401
 
 
 class Drafter:
