@@ -922,6 +922,39 @@ def _recurrent_gemma(c: ModelConfig, raw: dict) -> None:
     c.attention_bias = bool(raw.get("attention_bias", False))
 
 
+def _exaone(c: ModelConfig, raw: dict) -> None:
+    """EXAONE 3.x: the Llama architecture under GPT-2 style names (``transformer.h.N.attn.attention.*``,
+    ``mlp.c_fc_0 / c_fc_1 / c_proj``, ``ln_1 / ln_2``, ``wte``, ``ln_f``), presented to the loader
+    through aliases (reference src/models/exaone.rs)."""
+    c.num_hidden_layers = int(raw.get("num_layers", c.num_hidden_layers))
+    c.rms_norm_eps = float(raw.get("layer_norm_epsilon", raw.get("rms_norm_eps", 1e-5)))
+    c.hidden_act = "silu"
+
+
+def _telechat3(c: ModelConfig, raw: dict) -> None:
+    """TeleChat3: the Llama decoder with YaRN frequencies (its config spells the type
+    ``telechat3-yarn``) and optional biases on q / k / v / o (reference src/models/telechat3.rs)."""
+    rs = c.rope_scaling
+    if rs and str(rs.get("rope_type", rs.get("type", ""))).endswith("yarn"):
+        rs = dict(rs)
+        rs["rope_type"] = "yarn"
+        rs.pop("type", None)
+        c.rope_scaling = rs
+    c.attention_bias = bool(raw.get("attention_bias", False))
+
+
+def _deepseek_v1(c: ModelConfig, raw: dict) -> None:
+    """DeepSeek-MoE (v1): Llama attention; MoE layers with softmax top-k routing (weights not
+    normalised unless the config says so, scaled by ``routed_scaling_factor``), always-on shared
+    experts, the first ``first_k_dense_replace`` layers dense (reference src/models/deepseek.rs)."""
+    if int(raw.get("moe_layer_freq", 1) or 1) != 1:
+        raise ValueError("deepseek with moe_layer_freq != 1 is not supported")
+    _deepseek_routing(c, raw)
+    c.router_bias = False
+    c.norm_topk_prob = bool(raw.get("norm_topk_prob", False))
+    c.extra["moe_routing"].update(score="softmax", group_score="max", n_group=1, topk_group=1)
+
+
 def _afmoe(c: ModelConfig, raw: dict) -> None:
     """Arcee AFM MoE (Trinity): norms before and after both the attention and the MLP / MoE block,
     per-head q/k RMSNorm, rotary embedding on the sliding-window layers only, a sigmoid output gate on
@@ -1192,7 +1225,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "recurrent_gemma": _recurrent_gemma, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "exaone": _exaone, "telechat3": _telechat3, "deepseek": _deepseek_v1, "recurrent_gemma": _recurrent_gemma, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

@@ -94,6 +94,18 @@ def _rules(cfg) -> list[tuple[str, str, object]]:
                 (P + r"experts\.gate_up_proj", r"\1mlp.experts.up_proj.weight", half(1)),
                 (P + r"experts\.down_proj", r"\1mlp.experts.down_proj.weight", lambda w: w.transpose(1, 2).contiguous()),
                 (P + r"((?!experts\.).*)", r"\1mlp.\2", None)]
+    if mt == "exaone":
+        L = r"transformer\.h\.(\d+)\."
+        M = r"model.layers.\1."
+        return [(r"transformer\.wte\.(\w+)", r"model.embed_tokens.\1", None),
+                (r"transformer\.ln_f\.(\w+)", r"model.norm.\1", None),
+                (L + r"ln_1\.(\w+)", M + r"input_layernorm.\2", None),
+                (L + r"ln_2\.(\w+)", M + r"post_attention_layernorm.\2", None),
+                (L + r"attn\.attention\.(q_proj|k_proj|v_proj)\.(\w+)", M + r"self_attn.\2.\3", None),
+                (L + r"attn\.attention\.out_proj\.(\w+)", M + r"self_attn.o_proj.\2", None),
+                (L + r"mlp\.c_fc_0\.(\w+)", M + r"mlp.gate_proj.\2", None),
+                (L + r"mlp\.c_fc_1\.(\w+)", M + r"mlp.up_proj.\2", None),
+                (L + r"mlp\.c_proj\.(\w+)", M + r"mlp.down_proj.\2", None)]
     if mt == "dbrx":
         E = cfg.num_experts
         L = r"transformer\.blocks\.(\d+)\."

@@ -222,3 +222,65 @@ def test_nvfp4_checkpoint_is_expanded_at_load(tmp_path):
         for (li, name), t in want.items():
             got = getattr(w2.layers[li], name)
             assert isinstance(got, torch.Tensor) and torch.equal(got, t)
+
+
+def test_exaone_telechat3_and_deepseek_v1_load_through_their_own_names(tmp_path):
+    """EXAONE 3.x names (``transformer.h.N.attn.attention.*``, ``c_fc_0 / c_fc_1 / c_proj``) load into the
+    executor layout of the Llama checkpoint they were written from; a TeleChat3 config (``telechat3-yarn``)
+    gives the frequencies of the same config spelled ``yarn``; a DeepSeek-MoE (v1) config parses to
+    softmax routing with shared experts and runs."""
+    import json
+
+    import torch
+    from safetensors.torch import load_file, save_file
+
+    from mlxcel_b200.config import ModelConfig, preset
+    from mlxcel_b200.loading.checkpoint import load_full_weights, save_checkpoint
+    from mlxcel_b200.models.weights import random_weights
+    from mlxcel_b200.ops.reference import rope_inv_freq
+
+    cfg = preset("tiny-llama")
+    src = tmp_path / "llama"
+    base = ModelConfig.from_dict(cfg.to_dict() | {"tie_word_embeddings": False})
+    save_checkpoint(src, cfg.to_dict() | {"model_type": "llama", "tie_word_embeddings": False},
+                    random_weights(base, seed=0, dtype=torch.bfloat16, std=0.05))
+    t = load_file(str(src / "model.safetensors"))
+    raw = json.loads((src / "config.json").read_text())
+    ex = {"transformer.wte.weight": t["model.embed_tokens.weight"], "transformer.ln_f.weight": t["model.norm.weight"],
+          "lm_head.weight": t["lm_head.weight"]}
+    for i in range(cfg.num_hidden_layers):
+        p, o = f"model.layers.{i}.", f"transformer.h.{i}."
+        for n in ("q_proj", "k_proj", "v_proj"):
+            ex[o + f"attn.attention.{n}.weight"] = t[p + f"self_attn.{n}.weight"]
+        ex[o + "attn.attention.out_proj.weight"] = t[p + "self_attn.o_proj.weight"]
+        ex[o + "ln_1.weight"], ex[o + "ln_2.weight"] = t[p + "input_layernorm.weight"], t[p + "post_attention_layernorm.weight"]
+        for a, b in (("c_fc_0", "gate_proj"), ("c_fc_1", "up_proj"), ("c_proj", "down_proj")):
+            ex[o + f"mlp.{a}.weight"] = t[p + f"mlp.{b}.weight"]
+    d = tmp_path / "exaone"
+    d.mkdir()
+    save_file({k: v.contiguous() for k, v in ex.items()}, str(d / "model.safetensors"), metadata={"format": "pt"})
+    r2 = {k: v for k, v in raw.items() if k != "num_hidden_layers"} | {"model_type": "exaone", "num_layers": cfg.num_hidden_layers,
+                                                                        "layer_norm_epsilon": raw.get("rms_norm_eps", 1e-5)}
+    (d / "config.json").write_text(json.dumps(r2))
+    ref = load_full_weights(src, ModelConfig.from_path(src), dtype=torch.bfloat16)
+    c2 = ModelConfig.from_path(d)
+    got = load_full_weights(d, c2, dtype=torch.bfloat16)
+    assert c2.num_hidden_layers == cfg.num_hidden_layers and torch.equal(got.embed, ref.embed) and torch.equal(got.final_norm, ref.final_norm)
+    for a, b in zip(got.layers, ref.layers):
+        for f in ("wqkv", "wo", "w_gate_up", "w_down", "ln1", "ln2"):
+            assert torch.equal(getattr(a, f), getattr(b, f)), f
+    ys = dict(factor=4.0, original_max_position_embeddings=64, beta_fast=32, beta_slow=1)
+    ct = ModelConfig.from_dict(raw | {"model_type": "telechat3", "rope_scaling": ys | {"rope_type": "telechat3-yarn"}, "attention_bias": True})
+    cy = ModelConfig.from_dict(raw | {"model_type": "llama", "rope_scaling": ys | {"rope_type": "yarn"}})
+    fa, ma = rope_inv_freq(ct.rot_dim, ct.rope_theta, ct.rope_scaling)
+    fb, mb = rope_inv_freq(cy.rot_dim, cy.rope_theta, cy.rope_scaling)
+    assert torch.equal(fa, fb) and ma == mb and ct.attention_bias and not torch.equal(fa, rope_inv_freq(cy.rot_dim, cy.rope_theta, None)[0])
+    cd = ModelConfig.from_dict(dict(model_type="deepseek", hidden_size=64, intermediate_size=128, moe_intermediate_size=32,
+                                    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, vocab_size=200,
+                                    n_routed_experts=4, num_experts_per_tok=2, n_shared_experts=2, first_k_dense_replace=1,
+                                    routed_scaling_factor=1.0, norm_topk_prob=False))
+    assert cd.is_moe and cd.extra["moe_routing"]["score"] == "softmax" and cd.shared_expert_intermediate_size == 64
+    assert cd.extra["first_k_dense"] == 1 and not cd.norm_topk_prob
+    w = random_weights(cd, seed=1, dtype=torch.float32, std=0.05)
+    assert w.layers[0].router_w is None and w.layers[1].router_w is not None and w.layers[1].shared_gate_up is not None
+    assert len(_gen(cd, w)) == 6
