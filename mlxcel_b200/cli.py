@@ -1055,7 +1055,7 @@ def cmd_inspect(a):
 
 
 _HYBRID = {"nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe",
-           "qwen3_5_moe_text", "falcon_h1", "lfm2", "recurrent_gemma"}
+           "qwen3_5_moe_text", "falcon_h1", "lfm2", "lfm2_moe", "recurrent_gemma"}
 _STATE_SPACE = {"mamba", "mamba2"}
 _CHECKED_BY_READING = {"internlm3", "minicpm", "mimo", "yi", "kimi_k2", "deepseek"}       # no independent implementation at hand
 _CHECKED_BY_LAYOUT = {"internlm2", "baichuan", "exaone", "telechat3"}                                 # round trip against the Llama form

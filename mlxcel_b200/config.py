@@ -1200,7 +1200,18 @@ def _lfm2(c: ModelConfig, raw: dict) -> None:
         full = set(raw.get("full_attn_idxs") or [])
         types = ["full_attention" if i in full else "conv" for i in range(c.num_hidden_layers)]
     c.extra["shortconv"] = dict(d_conv=int(raw.get("conv_L_cache", 3)), bias=bool(raw.get("conv_bias", False)))
-    c.extra["hybrid_pattern"] = "".join(("*" if t == "full_attention" else "C") + "G" for t in types)
+    # LFM2-MoE: the feed-forward of the layers behind the first num_dense_layers is a sparse MoE
+    # (sigmoid scores + selection bias, top-k, normalised and scaled weights)
+    c.num_experts = int(raw.get("num_experts", 0) or 0) if c.model_type == "lfm2_moe" else 0
+    dense = int(raw.get("num_dense_layers", 0) or 0) if c.num_experts else len(types)
+    if c.num_experts:
+        c.moe_route_mode = "sigmoid_group"
+        c.norm_topk_prob = bool(raw.get("norm_topk_prob", True))
+        c.moe_intermediate_size = int(raw.get("moe_intermediate_size", c.intermediate_size))
+        c.extra["moe_routing"] = dict(n_group=1, topk_group=1, scale=float(raw.get("routed_scaling_factor", 1.0)), norm_min=1e-6)
+        c.router_bias = bool(raw.get("use_expert_bias", True))
+    c.extra["hybrid_pattern"] = "".join(("*" if t == "full_attention" else "C") + ("G" if i < dense else "E")
+                                        for i, t in enumerate(types))
     c.extra["hybrid_layout"] = "lfm2"
     c.layer_types = None
 
@@ -1225,7 +1236,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "exaone": _exaone, "telechat3": _telechat3, "deepseek": _deepseek_v1, "recurrent_gemma": _recurrent_gemma, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "lfm2_moe": _lfm2, "exaone": _exaone, "telechat3": _telechat3, "deepseek": _deepseek_v1, "recurrent_gemma": _recurrent_gemma, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

@@ -28,7 +28,7 @@ class LLM:
         if model is not None:
             self.model = model
         elif cfg.model_type in ("mamba", "mamba2", "nemotron_h", "granitemoehybrid", "jamba", "qwen3_next", "qwen3_5", "qwen3_5_text",
-                                "qwen3_5_moe", "qwen3_5_moe_text", "falcon_h1", "lfm2", "recurrent_gemma"):
+                                "qwen3_5_moe", "qwen3_5_moe_text", "falcon_h1", "lfm2", "lfm2_moe", "recurrent_gemma"):
             from .models.hybrid import HybridModel
             from .models.mamba1 import Mamba1Model
             from .models.mamba2 import Mamba2Model
@@ -101,7 +101,7 @@ class LLM:
             from .models.hybrid import load_falcon_h1_weights
             return LLM(cfg, load_falcon_h1_weights(path, cfg, device=device), engine_config, comm=comm,
                        tokenizer=load_tokenizer(path))
-        if cfg.model_type == "lfm2":
+        if cfg.model_type in ("lfm2", "lfm2_moe"):
             from .models.hybrid import load_lfm2_weights
             return LLM(cfg, load_lfm2_weights(path, cfg, device=device), engine_config, comm=comm,
                        tokenizer=load_tokenizer(path))

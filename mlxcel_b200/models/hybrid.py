@@ -345,7 +345,18 @@ def load_lfm2_weights(path, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu"
             attn_layers.append(lw)
             blocks.append(HybridBlock("attention", norm, attn=lw))
         f = p + "feed_forward."
-        blocks.append(HybridBlock("mlp", need(g.vec(p + "ffn_norm.weight"), p + "ffn_norm.weight"),
+        fn = need(g.vec(p + "ffn_norm.weight"), p + "ffn_norm.weight")
+        if src.has(f + "gate.weight"):              # LFM2-MoE: routed experts w1 (gate) / w3 (up) / w2 (down)
+            from ..loading.checkpoint import _stack
+            gus = [_cat_rows([g.mat(f"{f}experts.{e}.w1"), g.mat(f"{f}experts.{e}.w3")]) for e in range(cfg.num_experts)]
+            downs = [g.mat(f"{f}experts.{e}.w2") for e in range(cfg.num_experts)]
+            moe = LayerWeights(ln1=fn, ln2=fn, wqkv=None, wo=None, router_w=need(g.mat(f + "gate"), f + "gate"),
+                               experts_gate_up=_stack(gus).to(device), experts_down=_stack(downs).to(device))
+            if src.has(f + "expert_bias"):
+                moe.router_b = src.get(f + "expert_bias").float().reshape(-1).to(device)
+            blocks.append(HybridBlock("moe", fn, moe=moe))
+            continue
+        blocks.append(HybridBlock("mlp", fn,
                                   up=_cat_rows([need(g.mat(f + "w1"), f + "w1"), need(g.mat(f + "w3"), f + "w3")]),
                                   down=need(g.mat(f + "w2"), f + "w2"), gated=True))
     embed = need(g.mat("model.embed_tokens"), "model.embed_tokens")

@@ -734,3 +734,51 @@ def test_recurrent_gemma_matches_transformers():
         for i, tok in enumerate(o.output):
             row = lg[n0 - 1 + i]
             assert row[tok].item() >= row.max().item() - 2e-3
+
+
+def test_lfm2_moe_matches_transformers():
+    """LFM2-MoE: the LFM2 stack whose later layers route their feed-forward over experts (sigmoid
+    scores + selection bias, normalised and scaled top-k weights)."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    from mlxcel_b200.models.hybrid import HybridModel, load_lfm2_weights
+
+    torch.manual_seed(0)
+    try:
+        hc = AutoConfig.for_model("lfm2_moe", hidden_size=64, intermediate_size=128, moe_intermediate_size=48, num_hidden_layers=4,
+                                  num_attention_heads=4, num_key_value_heads=2, vocab_size=300, max_position_embeddings=256,
+                                  num_dense_layers=1, num_experts=4, num_experts_per_tok=2, use_expert_bias=True,
+                                  routed_scaling_factor=1.5, norm_topk_prob=True,
+                                  layer_types=["conv", "full_attention", "conv", "conv"], conv_L_cache=3, pad_token_id=0)
+        model = AutoModelForCausalLM.from_config(hc).float().eval()
+    except (KeyError, ValueError, ImportError) as e:
+        pytest.skip(f"transformers cannot build lfm2_moe: {e}")
+    with torch.no_grad():
+        for n, buf in model.named_buffers():
+            if "expert_bias" in n:
+                buf.copy_(torch.randn_like(buf) * 0.2)
+        for n, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.4 if "conv.conv" in n else 0.08)
+            elif "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tempfile.mkdtemp(prefix="parity_lfm2_moe_")
+    model.save_pretrained(d, safe_serialization=True)
+    T = 24
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0]
+    cfg = ModelConfig.from_path(d)
+    assert cfg.extra["hybrid_pattern"] == "CG*ECECE" and cfg.num_experts == 4
+    ours = HybridModel(cfg, load_lfm2_weights(d, cfg, dtype=torch.float32), max_seqs=2)
+    pool = KVPool(cfg, 8, 16, device="cpu", dtype=torch.float32, num_layers=ours.num_kv_layers)
+    b = StepBatch(token_ids=ids.int(), positions=torch.arange(T, dtype=torch.int32),
+                  slot_mapping=torch.arange(T, dtype=torch.int32), num_prefill_seqs=1,
+                  pf_block_tables=torch.arange(8, dtype=torch.int32)[None],
+                  pf_cu_q=torch.tensor([0, T], dtype=torch.int32),
+                  pf_context_lens=torch.tensor([T], dtype=torch.int32), pf_max_q_len=T, pf_cu_q_host=[0, T],
+                  logits_rows=torch.arange(T))
+    b.seq_ids, b.pf_starts = [0], [0]
+    got = ours.forward(b, pool.layers).float()
+    err = (got - want).abs().max().item()
+    assert err < 2e-3 * max(want.abs().max().item(), 1.0), f"max abs error {err:.3e}"
