@@ -312,6 +312,20 @@ def _qwen2_vl(c: ModelConfig, raw: dict) -> None:
         c.rope_scaling = None                 # "mrope" names the position layout, not a frequency scaling
 
 
+def _qwen3_vl(c: ModelConfig, raw: dict) -> None:
+    """Language model of Qwen3-VL: Qwen3 blocks (per-head q/k norm) with interleaved multimodal rotary
+    positions; visual features of intermediate tower depths are added to the first layers' outputs
+    (DeepStack, carried with the media rows)."""
+    _qwen3(c, raw)
+    for rec in (raw.get("rope_parameters"), raw.get("rope_scaling")):
+        if isinstance(rec, dict) and rec.get("mrope_section"):
+            c.extra["mrope_section"] = [int(x) for x in rec["mrope_section"]]
+            c.extra["mrope_interleaved"] = bool(rec.get("mrope_interleaved", True))
+    rs = c.rope_scaling
+    if isinstance(rs, dict) and rs.get("rope_type", rs.get("type")) in ("mrope", "default", None):
+        c.rope_scaling = None
+
+
 def _qwen3(c: ModelConfig, raw: dict) -> None:
     c.qk_norm = True
     c.sliding_window = 0 if not raw.get("use_sliding_window", False) else c.sliding_window
@@ -1230,7 +1244,7 @@ FAMILIES = {
     "hunyuan_v1_moe": _hunyuan_moe,
     "ernie4_5": _interleaved_rope, "apertus": _apertus, "minicpm": _minicpm, "mimo": _qwen2, "yi": _plain,
     "qwen2": _qwen2, "qwen2_vl": _qwen2_vl, "qwen2_vl_text": _qwen2_vl, "qwen2_5_vl": _qwen2_vl,
-    "qwen2_5_vl_text": _qwen2_vl, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
+    "qwen2_5_vl_text": _qwen2_vl, "qwen3_vl": _qwen3_vl, "qwen3_vl_text": _qwen3_vl, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "mixtral": _mixtral, "phimoe": _phimoe, "olmoe": _olmoe,
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,

@@ -631,13 +631,23 @@ class Engine:
         rows of every placeholder position replaced by the connector's output."""
         m = self.model
         h = m.comm.embed(b.token_ids, m.w.embed, self.cfg.embed_scale).clone()
+        H = h.shape[1]
         t = nd
+        deep = None
         for s, start, count in pieces:
             for st, rows in s.mm_embeds or ():
                 lo, hi = max(st, start), min(st + rows.shape[0], start + count)
                 if lo < hi:
-                    h[t + lo - start: t + hi - start] = rows[lo - st: hi - st].to(h.dtype)
+                    h[t + lo - start: t + hi - start] = rows[lo - st: hi - st, :H].to(h.dtype)
+                    # rows wider than the hidden size carry features for the first layers' outputs (DeepStack)
+                    extra = rows.shape[1] // H - 1
+                    if extra > 0:
+                        if deep is None:
+                            deep = [torch.zeros_like(h) for _ in range(extra)]
+                        for j in range(min(extra, len(deep))):
+                            deep[j][t + lo - start: t + hi - start] = rows[lo - st: hi - st, (j + 1) * H:(j + 2) * H].to(h.dtype)
             t += count
+        b.deepstack = deep
         return h
 
     # ------------------------------------------------------------------ cuda graphs

@@ -48,6 +48,7 @@ class StepBatch:
     pf_cu_q_host: list | None = None               # host copy of pf_cu_q (micro-batch splitting)
     logits_rows: torch.Tensor | None = None        # [R] int64 rows of the hidden state to project
     embeds: torch.Tensor | None = None             # optional [T, H] input embeddings (VLM / MTP)
+    deepstack: list | None = None                  # [T, H] per early layer: visual features added to the stream after it
     seq_ids: list | None = None                    # host: sequence id per decode row, then per prefill piece
     pf_starts: list | None = None                  # host: first position of every prefill piece
     # Sliding-window layers with their own block pool (blocks behind the window are given back):
@@ -256,7 +257,8 @@ class DecoderModel:
             from ..ops import reference as ref
             T0, nqk = qkv.shape[0], self.Hq + self.Hkv
             x3 = qkv.view(T0, self.Hq + 2 * self.Hkv, self.D)
-            rot = ref.apply_mrope(x3[:, :nqk], b.positions3, self.inv_freq, cfg.extra["mrope_section"], self.mscale)
+            rot = ref.apply_mrope(x3[:, :nqk], b.positions3, self.inv_freq, cfg.extra["mrope_section"], self.mscale,
+                                  interleaved=bool(cfg.extra.get("mrope_interleaved")))
             qkv = torch.cat([rot.to(qkv.dtype), x3[:, nqk:]], dim=1).reshape(T0, -1).contiguous()
             rot_dim = 0
         use_win = window > 0 and b.slot_mapping_win is not None     # this layer's KV lives in the window pool
@@ -441,8 +443,18 @@ class DecoderModel:
                     h = (h.float() + o.float()).to(h.dtype) if not h.is_cuda else h.add_(o)
                 else:
                     h = self.comm.row_parallel_linear(m, lw.w_down, lw.b_down, h)
+            h = self._deepstack(li, h, b)
             self._capture(li, h)
         return h
+
+    def _deepstack(self, li: int, h: torch.Tensor, b: StepBatch) -> torch.Tensor:
+        """Qwen3-VL DeepStack: the image rows of the first few layers' outputs get visual features of
+        intermediate vision-tower depths added (zero rows elsewhere)."""
+        ds = b.deepstack
+        if ds is None:
+            return h
+        g = self.layer_range[li] if li < len(self.layer_range) else li
+        return (h.float() + ds[g].float()).to(h.dtype) if g < len(ds) else h
 
     def _capture(self, li: int, h: torch.Tensor) -> None:
         if self.capture_layers and (self.layer_range[li] if li < len(self.layer_range) else li) in self.capture_layers:
@@ -473,6 +485,7 @@ class DecoderModel:
                     h = self._moe(lw, x, h)
                 else:
                     h = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, h)
+            h = self._deepstack(li, h, b)
             self._capture(li, h)
         return h
 
@@ -497,6 +510,10 @@ class DecoderModel:
                     h = self.comm.row_parallel_linear(self._mlp(lw, x), lw.w_down, lw.b_down, h)
                 if li + 1 < len(self.w.layers):
                     ops.row_ssq(h, ssq)
+            h2 = self._deepstack(li, h, b)
+            if h2 is not h:                          # the stream changed behind the kernels that keep its sums of squares
+                h = h2
+                ops.row_ssq(h, ssq)
             self._capture(li, h)
         return h
 

@@ -239,6 +239,106 @@ class Qwen25VisionTower:
         return y[torch.argsort(order)]
 
 
+class Qwen3VisionTower(Qwen2VisionTower):
+    """Qwen3-VL tower: biased patch embedding plus a learned position table interpolated bilinearly to
+    the image's patch grid, full attention per image with the same 2-D rotary positions, tanh-GELU
+    MLPs, a merger that norms before folding, and DeepStack mergers (norm after folding) over the
+    outputs of ``deepstack_visual_indexes``. ``forward`` returns [R / merge^2, (1 + n_deep) * text_hidden]:
+    the merged tokens followed by one feature block per DeepStack level, which the engine adds to the
+    first language-model layers' outputs at the image rows (reference: src/vision/encoders/qwen3_vl*.rs)."""
+
+    def __init__(self, vc: dict, tensors: dict, dtype=torch.bfloat16, device="cpu"):
+        self.dtype, self.device = dtype, torch.device(device)
+        self.depth, self.dim, self.heads = int(vc["depth"]), int(vc["hidden_size"]), int(vc["num_heads"])
+        self.patch, self.merge = int(vc.get("patch_size", 16)), int(vc.get("spatial_merge_size", 2))
+        self.act = {"gelu": "gelu", "gelu_pytorch_tanh": "gelu_tanh", "quick_gelu": "quick_gelu"}.get(
+            vc.get("hidden_act", "gelu_pytorch_tanh"), "gelu_tanh")
+        self.deep_idx = [int(i) for i in vc.get("deepstack_visual_indexes", ())]
+
+        def t(n):
+            return tensors[n].to(dtype).to(self.device).contiguous()
+
+        pw = t("patch_embed.proj.weight")
+        pw = pw.reshape(pw.shape[0], -1)
+        self.k_pad = (-pw.shape[1]) % 8
+        self.patch_w = F.pad(pw, (0, self.k_pad)).contiguous()
+        self.patch_b = t("patch_embed.proj.bias")
+        self.pos_table = t("pos_embed.weight")
+        self.side = int(round(self.pos_table.shape[0] ** 0.5))
+        self.blocks = []
+        for i in range(self.depth):
+            b = f"blocks.{i}."
+            self.blocks.append({k: t(b + n) for k, n in dict(
+                n1w="norm1.weight", n1b="norm1.bias", wqkv="attn.qkv.weight", bqkv="attn.qkv.bias",
+                wo="attn.proj.weight", bo="attn.proj.bias", n2w="norm2.weight", n2b="norm2.bias",
+                w1="mlp.linear_fc1.weight", b1="mlp.linear_fc1.bias", w2="mlp.linear_fc2.weight", b2="mlp.linear_fc2.bias").items()})
+
+        def merger(p):
+            return dict(nw=t(p + "norm.weight"), nb=t(p + "norm.bias"), w1=t(p + "linear_fc1.weight"), b1=t(p + "linear_fc1.bias"),
+                        w2=t(p + "linear_fc2.weight"), b2=t(p + "linear_fc2.bias"))
+        self.merger = merger("merger.")
+        self.deep_mergers = [merger(f"deepstack_merger_list.{j}.") for j in range(len(self.deep_idx))]
+        D = self.dim // self.heads
+        self.inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D // 2, 2, dtype=torch.float32) / (D // 2)))
+
+    def _pos_embed(self, grids) -> torch.Tensor:
+        """The learned side x side table read bilinearly at each image's gh x gw patch centres, rows in
+        merge-window order (fp32)."""
+        tab, n, m = self.pos_table.float(), self.side, self.merge
+        out = []
+        for t_, gh, gw in grids:
+            hi, wi = torch.linspace(0, n - 1, gh), torch.linspace(0, n - 1, gw)
+            hf, wf = hi.int(), wi.int()
+            hc, wc = (hf + 1).clip(max=n - 1), (wf + 1).clip(max=n - 1)
+            dh, dw = (hi - hf)[:, None], (wi - wf)[None, :]
+            e = lambda a, b: tab[(a[:, None] * n + b[None, :]).long().flatten().to(tab.device)].view(gh, gw, -1)  # noqa: E731
+            dh, dw = dh.to(tab.device)[..., None], dw.to(tab.device)[..., None]
+            pe = e(hf, wf) * (1 - dh) * (1 - dw) + e(hf, wc) * (1 - dh) * dw + e(hc, wf) * dh * (1 - dw) + e(hc, wc) * dh * dw
+            pe = pe.view(gh // m, m, gw // m, m, -1).permute(0, 2, 1, 3, 4).reshape(gh * gw, -1)
+            out.append(pe.repeat(t_, 1))
+        return torch.cat(out)
+
+    def _merge(self, x: torch.Tensor, mw: dict, post: bool) -> torch.Tensor:
+        R, wide = x.shape[0], self.dim * self.merge ** 2
+        if post:
+            y = rops.layernorm(x.view(R // self.merge ** 2, wide).contiguous(), mw["nw"], mw["nb"], 1e-6)
+        else:
+            y = rops.layernorm(x, mw["nw"], mw["nb"], 1e-6).view(R // self.merge ** 2, wide).contiguous()
+        return ops.linear(rops.activation(ops.linear(y, mw["w1"], bias=mw["b1"]), "gelu"), mw["w2"], bias=mw["b2"])
+
+    @torch.no_grad()
+    def forward(self, rows: torch.Tensor, grids) -> torch.Tensor:
+        from ..models.vision import _act
+        x = ops.linear(F.pad(rows.to(self.device, self.dtype), (0, self.k_pad)).contiguous(), self.patch_w, bias=self.patch_b)
+        x = (x.float() + self._pos_embed(grids).to(self.device)).to(self.dtype)
+        R, H, D = x.shape[0], self.heads, self.dim // self.heads
+        ang = self._rot_angles(grids).to(self.device)
+        cos = torch.cat([ang.cos(), ang.cos()], dim=1)[:, None, :]
+        sin = torch.cat([ang.sin(), ang.sin()], dim=1)[:, None, :]
+        sizes = [gh * gw for t_, gh, gw in grids for _ in range(t_)]          # attention stays inside a frame
+
+        def rot(v):
+            half = D // 2
+            return v * cos + torch.cat([-v[..., half:], v[..., :half]], dim=-1) * sin
+        deep = []
+        for li, b in enumerate(self.blocks):
+            y = rops.layernorm(x, b["n1w"], b["n1b"], 1e-6)
+            qkv = ops.linear(y, b["wqkv"], bias=b["bqkv"]).view(R, 3, H, D)
+            q, k, v = rot(qkv[:, 0].float()), rot(qkv[:, 1].float()), qkv[:, 2].float()
+            outs, o0 = [], 0
+            for n in sizes:
+                qi, ki, vi = (z[o0:o0 + n].transpose(0, 1)[None] for z in (q, k, v))
+                outs.append(F.scaled_dot_product_attention(qi, ki, vi)[0].transpose(0, 1).reshape(n, H * D))
+                o0 += n
+            a = torch.cat(outs).to(self.dtype).contiguous()
+            x = ops.linear(a, b["wo"], bias=b["bo"], residual=x)
+            y = rops.layernorm(x, b["n2w"], b["n2b"], 1e-6)
+            x = ops.linear(_act(ops.linear(y, b["w1"], bias=b["b1"]), self.act), b["w2"], bias=b["b2"], residual=x)
+            if li in self.deep_idx:
+                deep.append(self._merge(x, self.deep_mergers[self.deep_idx.index(li)], post=True))
+        return torch.cat([self._merge(x, self.merger, post=False)] + deep, dim=1)
+
+
 class Qwen2VisionLanguage(VisionLanguage):
     def __init__(self, tower: Qwen2VisionTower, processor: Qwen2ImageProcessor, image_token_id: int, model_type: str):
         super().__init__(tower, None, processor, image_token_id, model_type)
@@ -303,9 +403,13 @@ class Qwen2VisionLanguage(VisionLanguage):
 def build_qwen2_vision(path, raw: dict, src, dtype, device) -> Qwen2VisionLanguage:
     import json
     from pathlib import Path
-    cls = Qwen25VisionTower if raw.get("model_type") == "qwen2_5_vl" else Qwen2VisionTower
+    mt = raw.get("model_type")
+    cls = Qwen3VisionTower if mt == "qwen3_vl" else Qwen25VisionTower if mt == "qwen2_5_vl" else Qwen2VisionTower
     tower = cls(raw["vision_config"], _sub(src, "model.visual.", "visual."), dtype, device)
     f = Path(path) / "preprocessor_config.json"
-    proc = Qwen2ImageProcessor(json.loads(f.read_text()) if f.exists() else None, tower.patch, tower.merge,
+    pc = json.loads(f.read_text()) if f.exists() else None
+    if pc is None and mt == "qwen3_vl":           # this family normalises to [-1, 1]
+        pc = dict(image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5])
+    proc = Qwen2ImageProcessor(pc, tower.patch, tower.merge,
                                int(raw["vision_config"].get("temporal_patch_size", 2)))
     return Qwen2VisionLanguage(tower, proc, raw.get("image_token_id", 151655), raw["model_type"])

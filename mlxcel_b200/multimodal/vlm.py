@@ -10,7 +10,7 @@ src/multimodal/runtime*.rs).
 
 Supported wrappers: ``llava`` (CLIP or SigLIP tower, two-layer MLP connector), ``idefics3`` /
 ``smolvlm`` (SigLIP-layout tower, pixel-shuffle connector, one tile per image), ``qwen2_vl`` and
-``qwen2_5_vl`` (see `qwen2_vision.py`). The language model is loaded by the ordinary decoder loader
+``qwen2_5_vl`` and ``qwen3_vl`` (see `qwen2_vision.py`). The language model is loaded by the ordinary decoder loader
 from the same checkpoint (its tensors live under ``language_model``).
 """
 from __future__ import annotations
@@ -24,7 +24,7 @@ import torch
 from ..models.vision import LlavaConnector, PixelShuffleConnector, ViTTower, VisionConfig
 from .images import ImageProcessor
 
-SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "idefics3", "smolvlm")
+SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "idefics3", "smolvlm")
 
 
 def is_vlm_checkpoint(path: str | Path) -> bool:
@@ -53,6 +53,7 @@ class VisionLanguage:
         # what stands for one image in prompt text when the chat template does not place it itself
         self.placeholder_text = {"llava": "<image>", "qwen2_vl": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "qwen2_5_vl": "<|vision_start|><|image_pad|><|vision_end|>",
+                                 "qwen3_vl": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "idefics3": "<fake_token_around_image><global-img><image><fake_token_around_image>",
                                  "smolvlm": "<fake_token_around_image><global-img><image><fake_token_around_image>"}.get(
                                      model_type, "<image>")
@@ -82,7 +83,7 @@ class VisionLanguage:
             proc = ImageProcessor(dict(size={"height": vc.image_size, "width": vc.image_size}, do_center_crop=False,
                                        resample=1, image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5]), vc.image_size)
             return VisionLanguage(tower, conn, proc, raw.get("image_token_id", 128257), mt)
-        if mt in ("qwen2_vl", "qwen2_5_vl"):
+        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl"):
             from .qwen2_vision import build_qwen2_vision
             return build_qwen2_vision(path, raw, src, dtype, device)
         raise ValueError(f"unsupported vision-language model_type {mt!r}; supported: {SUPPORTED}")

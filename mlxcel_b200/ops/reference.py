@@ -156,16 +156,23 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
     return out * mscale
 
 
-def apply_mrope(x: torch.Tensor, positions3: torch.Tensor, inv_freq: torch.Tensor, sections, mscale: float = 1.0
-                ) -> torch.Tensor:
+def apply_mrope(x: torch.Tensor, positions3: torch.Tensor, inv_freq: torch.Tensor, sections, mscale: float = 1.0,
+                interleaved: bool = False) -> torch.Tensor:
     """Multimodal rotary embedding (Qwen2-VL): ``positions3`` [3, T] holds temporal / height / width
     positions; frequency i of the head's D/2 takes the position of the section it falls in
-    (``sections`` = frequencies per component, e.g. [16, 24, 24]). Half-split (non-interleaved) layout.
-    x: [T, H, D] → rotated fp32 tensor."""
+    (``sections`` = frequencies per component, e.g. [16, 24, 24]). ``interleaved`` (Qwen3-VL, Qwen3.5):
+    the components alternate T H W T H W ... over the first 3 * sections[1] (height) and
+    3 * sections[2] (width) frequencies and the rest are temporal, instead of three contiguous
+    chunks. Half-split (non-interleaved) pair layout. x: [T, H, D] → rotated fp32 tensor."""
     xf = x.float()
     half = xf.shape[-1] // 2
-    which = torch.repeat_interleave(torch.arange(len(sections), device=xf.device),
-                                    torch.tensor(list(sections), device=xf.device))[:half]      # [half] -> 0/1/2
+    if interleaved:
+        which = torch.zeros(half, dtype=torch.long, device=xf.device)
+        for comp, offset in ((1, 1), (2, 2)):
+            which[offset:int(sections[comp]) * 3:3] = comp
+    else:
+        which = torch.repeat_interleave(torch.arange(len(sections), device=xf.device),
+                                        torch.tensor(list(sections), device=xf.device))[:half]  # [half] -> 0/1/2
     pos = positions3.float().to(xf.device)[which]                   # [half, T]
     ang = pos.t() * inv_freq.float()[None, :half]                   # [T, half]
     cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
