@@ -21,6 +21,10 @@ def _run(d, kind, device, dtype):
     if kind == "llava":
         vl.processor = ImageProcessor(dict(size={"shortest_edge": 28}, crop_size={"height": 28, "width": 28}), 28)
         ph = [t.IMG_TOKEN]
+    elif kind == "qwen3_vl":
+        vl.processor = Qwen2ImageProcessor(dict(min_pixels=64 * 64, max_pixels=32 * 32 * 16, patch_size=16,
+                                                image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5]))
+        ph = [292, t.IMG_TOKEN, 293]
     else:
         vl.processor = Qwen2ImageProcessor(dict(min_pixels=56 * 56, max_pixels=28 * 28 * 16))
         ph = [292, t.IMG_TOKEN, 293]
@@ -41,14 +45,15 @@ def _run(d, kind, device, dtype):
     return eng.seqs[sid].output, rows
 
 
-@pytest.mark.parametrize("kind", ["llava", "qwen2_vl"])
+@pytest.mark.parametrize("kind", ["llava", "qwen2_vl", "qwen3_vl"])
 def test_vlm_gpu_matches_cpu(kind):
     import sys
     from pathlib import Path
     sys.path.insert(0, str(Path(__file__).parent))
     import test_vlm_cpu as t
     # head size 64 (what the paged attention kernels serve)
-    m, d = t._tiny_llava(128, 2, 1) if kind == "llava" else t._tiny_qwen2_vl(128, 2, 1, (8, 12, 12))
+    m, d = (t._tiny_llava(128, 2, 1) if kind == "llava" else t._tiny_qwen3_vl(128, 2, 1, 64, (12, 10, 10)) if kind == "qwen3_vl"
+            else t._tiny_qwen2_vl(128, 2, 1, (8, 12, 12)))
     want, rows_cpu = _run(d, kind, "cpu", torch.float32)
     got, rows_gpu = _run(d, kind, "cuda", torch.bfloat16)
     # connector output: bf16 operands, fp32 accumulation

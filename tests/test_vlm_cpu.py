@@ -223,6 +223,28 @@ def _tiny_qwen2_vl(hidden=64, heads=4, kv=2, sections=(2, 3, 3)):
     return m, d
 
 
+def _tiny_qwen3_vl(hidden=64, heads=4, kv=2, head_dim=16, sections=(3, 3, 2)):
+    from transformers import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+    torch.manual_seed(0)
+    cfg = Qwen3VLConfig(
+        text_config=dict(hidden_size=hidden, intermediate_size=2 * hidden, num_hidden_layers=3, num_attention_heads=heads,
+                         head_dim=head_dim, num_key_value_heads=kv, vocab_size=300, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": list(sections),
+                                          "mrope_interleaved": True}),
+        vision_config=dict(depth=3, hidden_size=32, out_hidden_size=hidden, num_heads=4, intermediate_size=48, patch_size=16,
+                           spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=36,
+                           deepstack_visual_indexes=[0, 2]),
+        image_token_id=IMG_TOKEN, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    m = Qwen3VLForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "visual" in n and p.dim() >= 2:
+                p.normal_(0, 0.08)
+    d = tempfile.mkdtemp(prefix="vlm_qwen3vl_")
+    m.save_pretrained(d, safe_serialization=True)
+    return m, d
+
+
 def test_qwen2_vl_processor_matches_transformers():
     from transformers.models.qwen2_vl.image_processing_qwen2_vl import Qwen2VLImageProcessor
 
