@@ -1073,7 +1073,7 @@ def arch_catalog() -> dict:
                else "transformers logits")
         if name == "gemma3":                     # the wrapper's text_config is the gemma3_text model
             how = "transformers logits (as gemma3_text)"
-        if name in ("qwen3_5", "qwen3_5_moe", "llama4", "qwen2_vl", "qwen2_5_vl", "qwen3_vl"):
+        if name in ("qwen3_5", "qwen3_5_moe", "llama4", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe"):
             how = f"transformers logits (as {name}_text)"
         if name == "deepseek_v32":
             how = "transformers logits (as glm_moe_dsa)"

@@ -177,6 +177,9 @@ class ModelConfig:
                 if k in raw and k not in inner:
                     inner[k] = raw[k]
             inner.setdefault("model_type", raw.get("model_type", "llama"))
+            if "tie_word_embeddings" in raw:
+                # the wrapper owns the LM head: its flag says whether the head is the embedding table
+                inner["tie_word_embeddings"] = raw["tie_word_embeddings"]
             raw = inner
         mt = raw.get("model_type", "llama")
         fam = FAMILIES.get(mt)
@@ -324,6 +327,13 @@ def _qwen3_vl(c: ModelConfig, raw: dict) -> None:
     rs = c.rope_scaling
     if isinstance(rs, dict) and rs.get("rope_type", rs.get("type")) in ("mrope", "default", None):
         c.rope_scaling = None
+
+
+def _qwen3_vl_moe(c: ModelConfig, raw: dict) -> None:
+    """Language model of Qwen3-VL-MoE: the Qwen3-MoE blocks under Qwen3-VL's positions and DeepStack."""
+    _qwen3_vl(c, raw)
+    c.moe_route_mode = "softmax_topk"
+    c.norm_topk_prob = bool(raw.get("norm_topk_prob", True))
 
 
 def _qwen3(c: ModelConfig, raw: dict) -> None:
@@ -1244,7 +1254,7 @@ FAMILIES = {
     "hunyuan_v1_moe": _hunyuan_moe,
     "ernie4_5": _interleaved_rope, "apertus": _apertus, "minicpm": _minicpm, "mimo": _qwen2, "yi": _plain,
     "qwen2": _qwen2, "qwen2_vl": _qwen2_vl, "qwen2_vl_text": _qwen2_vl, "qwen2_5_vl": _qwen2_vl,
-    "qwen2_5_vl_text": _qwen2_vl, "qwen3_vl": _qwen3_vl, "qwen3_vl_text": _qwen3_vl, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
+    "qwen2_5_vl_text": _qwen2_vl, "qwen3_vl": _qwen3_vl, "qwen3_vl_text": _qwen3_vl, "qwen3_vl_moe": _qwen3_vl_moe, "qwen3_vl_moe_text": _qwen3_vl_moe, "qwen3": _qwen3, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "mixtral": _mixtral, "phimoe": _phimoe, "olmoe": _olmoe,
     "gemma": _gemma, "gemma2": _gemma2, "gemma3_text": _gemma3, "gemma3": _gemma3,
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,

@@ -404,11 +404,11 @@ def build_qwen2_vision(path, raw: dict, src, dtype, device) -> Qwen2VisionLangua
     import json
     from pathlib import Path
     mt = raw.get("model_type")
-    cls = Qwen3VisionTower if mt == "qwen3_vl" else Qwen25VisionTower if mt == "qwen2_5_vl" else Qwen2VisionTower
+    cls = Qwen3VisionTower if mt in ("qwen3_vl", "qwen3_vl_moe") else Qwen25VisionTower if mt == "qwen2_5_vl" else Qwen2VisionTower
     tower = cls(raw["vision_config"], _sub(src, "model.visual.", "visual."), dtype, device)
     f = Path(path) / "preprocessor_config.json"
     pc = json.loads(f.read_text()) if f.exists() else None
-    if pc is None and mt == "qwen3_vl":           # this family normalises to [-1, 1]
+    if pc is None and mt in ("qwen3_vl", "qwen3_vl_moe"):           # this family normalises to [-1, 1]
         pc = dict(image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5])
     proc = Qwen2ImageProcessor(pc, tower.patch, tower.merge,
                                int(raw["vision_config"].get("temporal_patch_size", 2)))

@@ -24,7 +24,7 @@ import torch
 from ..models.vision import LlavaConnector, PixelShuffleConnector, ViTTower, VisionConfig
 from .images import ImageProcessor
 
-SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "idefics3", "smolvlm")
+SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "idefics3", "smolvlm")
 
 
 def is_vlm_checkpoint(path: str | Path) -> bool:
@@ -54,6 +54,7 @@ class VisionLanguage:
         self.placeholder_text = {"llava": "<image>", "qwen2_vl": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "qwen2_5_vl": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "qwen3_vl": "<|vision_start|><|image_pad|><|vision_end|>",
+                                 "qwen3_vl_moe": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "idefics3": "<fake_token_around_image><global-img><image><fake_token_around_image>",
                                  "smolvlm": "<fake_token_around_image><global-img><image><fake_token_around_image>"}.get(
                                      model_type, "<image>")
@@ -83,7 +84,7 @@ class VisionLanguage:
             proc = ImageProcessor(dict(size={"height": vc.image_size, "width": vc.image_size}, do_center_crop=False,
                                        resample=1, image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5]), vc.image_size)
             return VisionLanguage(tower, conn, proc, raw.get("image_token_id", 128257), mt)
-        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl"):
+        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe"):
             from .qwen2_vision import build_qwen2_vision
             return build_qwen2_vision(path, raw, src, dtype, device)
         raise ValueError(f"unsupported vision-language model_type {mt!r}; supported: {SUPPORTED}")

@@ -437,3 +437,50 @@ def test_qwen3_vl_tower_deepstack_and_greedy_match_transformers():
         p2 = eng.seqs[side].prompt
         want_side = m.generate(input_ids=torch.tensor([p2]), max_new_tokens=6, do_sample=False)[0, len(p2):].tolist()
     assert eng.seqs[side].output == want_side
+
+
+def test_qwen3_vl_moe_greedy_matches_transformers():
+    """Qwen3-VL-MoE: the same tower and positions over Qwen3-MoE blocks."""
+    from transformers import Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration
+
+    from mlxcel_b200.multimodal.qwen2_vision import Qwen2ImageProcessor
+    torch.manual_seed(0)
+    cfg = Qwen3VLMoeConfig(
+        text_config=dict(hidden_size=64, intermediate_size=128, moe_intermediate_size=48, num_experts=4, num_experts_per_tok=2,
+                         decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True, num_hidden_layers=3,
+                         num_attention_heads=4, head_dim=16, num_key_value_heads=2, vocab_size=300, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [3, 3, 2],
+                                          "mrope_interleaved": True}),
+        vision_config=dict(depth=2, hidden_size=32, out_hidden_size=64, num_heads=4, intermediate_size=48, patch_size=16,
+                           spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=36,
+                           deepstack_visual_indexes=[1]),
+        image_token_id=IMG_TOKEN, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    m = Qwen3VLMoeForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() >= 2 and ("visual" in n or "experts" in n or "gate" in n):
+                p.normal_(0, 0.08)
+    d = tempfile.mkdtemp(prefix="vlm_qwen3vlmoe_")
+    m.save_pretrained(d, safe_serialization=True)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    vl.processor = Qwen2ImageProcessor(dict(min_pixels=64 * 64, max_pixels=32 * 32 * 36, patch_size=16,
+                                            image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5]))
+    imgs = [_image(5, 150, 100)]
+    rows, grids = vl.processor(imgs)
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(6) + [292, IMG_TOKEN, 293] + text(5)
+    ids, mm = vl.prepare(prompt, imgs)
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=rows, image_grid_thw=torch.tensor(grids),
+                          mm_token_type_ids=torch.tensor([[int(t == IMG_TOKEN) for t in ids]]),
+                          max_new_tokens=8, do_sample=False)[0, len(ids):].tolist()
+    c = ModelConfig.from_path(d)
+    assert c.is_moe and c.num_experts == 4 and c.extra["mrope_interleaved"]
+    w = load_full_weights(d, c, dtype=torch.float32)
+    eng = Engine(DecoderModel(c, w), c, EngineConfig(max_batch=2, max_num_batched_tokens=64, num_blocks=32, max_model_len=256,
+                                                     cuda_graphs=False, prefill_chunk_alone=16, prefill_chunk_contended=16))
+    sid = eng.add_request(ids, SamplingParams(max_tokens=8, ignore_eos=True), **mm)
+    while eng.has_work():
+        eng.step()
+    assert eng.seqs[sid].output == want
