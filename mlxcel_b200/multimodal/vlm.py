@@ -10,21 +10,26 @@ src/multimodal/runtime*.rs).
 
 Supported wrappers: ``llava`` (CLIP or SigLIP tower, two-layer MLP connector), ``idefics3`` /
 ``smolvlm`` (SigLIP-layout tower, pixel-shuffle connector, one tile per image), ``qwen2_vl`` and
-``qwen2_5_vl`` and ``qwen3_vl`` (see `qwen2_vision.py`). The language model is loaded by the ordinary decoder loader
+``qwen2_5_vl`` and ``qwen3_vl`` (see `qwen2_vision.py`), ``internvl`` (InternViT tower, pixel-shuffle +
+MLP connector, one tile per image) and ``mistral3`` (Pixtral tower at the image's own aspect ratio,
+patch-merging connector; the prompt carries one row of image tokens per patch row, closed by a
+break token, the last by an end token). The language model is loaded by the ordinary decoder loader
 from the same checkpoint (its tensors live under ``language_model``).
 """
 from __future__ import annotations
 
 import hashlib
 import json
+import math
 from pathlib import Path
 
 import torch
 
-from ..models.vision import LlavaConnector, PixelShuffleConnector, ViTTower, VisionConfig
+from ..models.vision import (InternVLConnector, InternViTTower, LlavaConnector, Mistral3Connector, PixelShuffleConnector,
+                             PixtralTower, ViTTower, VisionConfig)
 from .images import ImageProcessor
 
-SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "idefics3", "smolvlm")
+SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "idefics3", "smolvlm", "internvl", "mistral3")
 
 
 def is_vlm_checkpoint(path: str | Path) -> bool:
@@ -56,7 +61,8 @@ class VisionLanguage:
                                  "qwen3_vl": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "qwen3_vl_moe": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "idefics3": "<fake_token_around_image><global-img><image><fake_token_around_image>",
-                                 "smolvlm": "<fake_token_around_image><global-img><image><fake_token_around_image>"}.get(
+                                 "smolvlm": "<fake_token_around_image><global-img><image><fake_token_around_image>",
+                                 "internvl": "<img><IMG_CONTEXT></img>", "mistral3": "[IMG]"}.get(
                                      model_type, "<image>")
         self.stats = dict(images=0, image_tokens=0, encode_seconds=0.0)
 
@@ -84,6 +90,23 @@ class VisionLanguage:
             proc = ImageProcessor(dict(size={"height": vc.image_size, "width": vc.image_size}, do_center_crop=False,
                                        resample=1, image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5]), vc.image_size)
             return VisionLanguage(tower, conn, proc, raw.get("image_token_id", 128257), mt)
+        if mt == "internvl":
+            v = raw["vision_config"]
+            fl = raw.get("vision_feature_layer", -1)
+            tower = InternViTTower(v, _sub(src, "model.vision_tower.", "vision_tower."), int(fl if not isinstance(fl, list) else fl[-1]),
+                                   raw.get("vision_feature_select_strategy", "default") == "default", dtype, device)
+            conn = InternVLConnector(_sub(src, "model.multi_modal_projector.", "multi_modal_projector."),
+                                     float(raw.get("downsample_ratio", 0.5)), raw.get("projector_hidden_act", "gelu"), dtype, device)
+            f = path / "preprocessor_config.json"
+            pc = json.loads(f.read_text()) if f.exists() else {}
+            # one tile per image: the whole image resized to the tower's square input (the tiling of
+            # large images into several crops plus a thumbnail is not done)
+            proc = ImageProcessor(dict(size={"height": tower.image_size, "width": tower.image_size}, do_center_crop=False,
+                                       resample=pc.get("resample", 3), image_mean=pc.get("image_mean", [0.485, 0.456, 0.406]),
+                                       image_std=pc.get("image_std", [0.229, 0.224, 0.225])), tower.image_size)
+            return VisionLanguage(tower, conn, proc, raw.get("image_token_id", 151667), mt)
+        if mt == "mistral3":
+            return PixtralVisionLanguage.build(path, raw, src, dtype, device)
         if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe"):
             from .qwen2_vision import build_qwen2_vision
             return build_qwen2_vision(path, raw, src, dtype, device)
@@ -128,4 +151,89 @@ class VisionLanguage:
             spans.append((len(ids), rows))
             ids += [self.image_token_id] * n
             keys += [-(2 + ((salt + j) & 0x3FFFFFFF)) for j in range(n)]
+        return ids, dict(mm_embeds=spans, key_tokens=keys)
+
+
+class PixtralVisionLanguage(VisionLanguage):
+    """Mistral3 / Pixtral: every image keeps its aspect ratio (longest edge capped, sides rounded up to
+    whole merged patches), and its placeholder expands to one run of image tokens per row of merged
+    patches, each run followed by the break token and the last by the end token — those two are
+    ordinary vocabulary entries, only the image tokens take the connector's rows
+    (the reference's src/loading/vlm_pixtral.rs, src/vision/encoders/pixtral.rs)."""
+
+    @staticmethod
+    def build(path, raw, src, dtype, device) -> "PixtralVisionLanguage":
+        v = raw["vision_config"]
+        fl = raw.get("vision_feature_layer", -1)
+        tower = PixtralTower(v, _sub(src, "model.vision_tower.", "vision_tower."), int(fl if not isinstance(fl, list) else fl[-1]),
+                             dtype, device)
+        conn = Mistral3Connector(_sub(src, "model.multi_modal_projector.", "multi_modal_projector."),
+                                 int(raw.get("spatial_merge_size", 2)), float((raw.get("text_config") or {}).get("rms_norm_eps", 1e-5)),
+                                 raw.get("projector_hidden_act", "gelu"), dtype, device)
+        f = path / "preprocessor_config.json"
+        pc = json.loads(f.read_text()) if f.exists() else {}
+        vl = PixtralVisionLanguage(tower, conn, None, raw.get("image_token_index", raw.get("image_token_id", 10)), "mistral3")
+        size = pc.get("size") or {}
+        vl.longest_edge = int(size.get("longest_edge", tower.image_size))
+        vl.mean = pc.get("image_mean", [0.48145466, 0.4578275, 0.40821073])
+        vl.std = pc.get("image_std", [0.26862954, 0.26130258, 0.27577711])
+        vl.break_id = int(raw.get("image_break_token_id", pc.get("image_break_token_id", 12)))
+        vl.end_id = int(raw.get("image_end_token_id", pc.get("image_end_token_id", 13)))
+        return vl
+
+    def pixels(self, img) -> torch.Tensor:
+        """Resize so the longest edge fits, sides rounded up to whole merged patches (bicubic), normalise."""
+        import numpy as np
+        from PIL import Image
+        unit = self.tower.patch * self.connector.s
+        w, h = img.size
+        ratio = max(h / self.longest_edge, w / self.longest_edge)
+        if ratio > 1:
+            h, w = int(math.floor(h / ratio)), int(math.floor(w / ratio))
+        nh, nw = max(1, -(-h // unit)) * unit, max(1, -(-w // unit)) * unit
+        a = np.asarray(img.convert("RGB").resize((nw, nh), Image.Resampling.BICUBIC), dtype=np.float32) / 255.0
+        a = (a - np.asarray(self.mean, dtype=np.float32)) / np.asarray(self.std, dtype=np.float32)
+        return torch.from_numpy(np.ascontiguousarray(a.transpose(2, 0, 1))).float()
+
+    @torch.no_grad()
+    def encode(self, images: list) -> list:
+        """One ``(rows [th * tw, text_hidden], th, tw)`` per image."""
+        import time
+        t0 = time.perf_counter()
+        out = []
+        for img in images:
+            px = img if isinstance(img, torch.Tensor) else self.pixels(img)
+            gh, gw = px.shape[1] // self.tower.patch, px.shape[2] // self.tower.patch
+            rows = self.connector.forward_one(self.tower.forward_one(px), gh, gw)
+            out.append((rows, gh // self.connector.s, gw // self.connector.s))
+            self.stats["image_tokens"] += int(rows.shape[0])
+        self.stats["images"] += len(images)
+        self.stats["encode_seconds"] += time.perf_counter() - t0
+        return out
+
+    def tokens_for(self, image) -> int:
+        px = image if isinstance(image, torch.Tensor) else self.pixels(image)
+        unit = self.tower.patch * self.connector.s
+        return (px.shape[1] // unit) * (px.shape[2] // unit + 1)
+
+    def prepare(self, prompt_ids: list[int], images: list):
+        n_ph = sum(1 for t in prompt_ids if t == self.image_token_id)
+        if n_ph != len(images):
+            raise ValueError(f"the prompt has {n_ph} image placeholders for {len(images)} images")
+        it = iter(self.encode(images))
+        ids, keys, spans = [], [], []
+        for t in prompt_ids:
+            if t != self.image_token_id:
+                ids.append(t)
+                keys.append(t)
+                continue
+            rows, th, tw = next(it)
+            salt = int.from_bytes(hashlib.sha1(rows.detach().float().cpu().numpy().tobytes()).digest()[:4], "little")
+            for r in range(th):
+                spans.append((len(ids), rows[r * tw:(r + 1) * tw]))
+                ids += [self.image_token_id] * tw
+                keys += [-(2 + ((salt + r * tw + j) & 0x3FFFFFFF)) for j in range(tw)]
+                closing = self.end_id if r == th - 1 else self.break_id
+                ids.append(closing)
+                keys.append(closing)
         return ids, dict(mm_embeds=spans, key_tokens=keys)

@@ -484,3 +484,95 @@ def test_qwen3_vl_moe_greedy_matches_transformers():
     while eng.has_work():
         eng.step()
     assert eng.seqs[sid].output == want
+
+
+def _run_engine(d, ids, mm, n=8, chunk=256):
+    cfg = ModelConfig.from_path(d)
+    w = load_full_weights(d, cfg, dtype=torch.float32)
+    eng = Engine(DecoderModel(cfg, w), cfg, EngineConfig(max_batch=2, max_num_batched_tokens=128, num_blocks=64,
+                                                         max_model_len=256, cuda_graphs=False,
+                                                         prefill_chunk_alone=chunk, prefill_chunk_contended=chunk))
+    sid = eng.add_request(ids, SamplingParams(max_tokens=n, ignore_eos=True), **mm)
+    while eng.has_work():
+        eng.step()
+    return eng.seqs[sid].output
+
+
+@pytest.mark.parametrize("norm_type,qk_norm", [("layer_norm", False), ("rms_norm", True)])
+def test_internvl_greedy_matches_transformers_through_the_engine(norm_type, qk_norm):
+    from transformers import InternVLConfig, InternVLForConditionalGeneration, InternVLVisionConfig, Qwen2Config
+    torch.manual_seed(0)
+    vc = InternVLVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                              image_size=[28, 28], patch_size=[7, 7], norm_type=norm_type, use_qk_norm=qk_norm,
+                              attention_bias=not qk_norm, layer_scale_init_value=0.5, use_mean_pooling=qk_norm)
+    tc = Qwen2Config(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, vocab_size=300, max_position_embeddings=256)
+    cfg = InternVLConfig(vision_config=vc, text_config=tc, image_token_id=IMG_TOKEN, downsample_ratio=0.5)
+    m = InternVLForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n_, p_ in m.named_parameters():
+            if "lambda_" in n_ or "position_embeddings" in n_ or "cls_token" in n_:
+                p_.copy_(torch.randn_like(p_) * 0.3)
+    d = tempfile.mkdtemp(prefix="vlm_internvl_")
+    m.save_pretrained(d, safe_serialization=True)
+    assert is_vlm_checkpoint(d)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    imgs = [_image(5), _image(6, 33, 52)]
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [IMG_TOKEN] + text(7) + [IMG_TOKEN] + text(4)
+    ids, mm = vl.prepare(prompt, imgs)
+    assert len(ids) == 16 + 2 * 4              # a 4 x 4 patch grid folds to 2 x 2 tokens per image
+    with torch.no_grad():
+        feats = m.model.get_image_features(vl.processor(imgs), vision_feature_layer=-1,
+                                           vision_feature_select_strategy="default").pooler_output
+    torch.testing.assert_close(torch.stack([r for _, r in mm["mm_embeds"]]), feats, rtol=1e-4, atol=1e-4)
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=vl.processor(imgs), max_new_tokens=8,
+                          do_sample=False)[0, len(ids):].tolist()
+    assert _run_engine(d, ids, mm) == want
+    assert _run_engine(d, ids, mm, chunk=7) == want
+
+
+def test_mistral3_pixtral_greedy_matches_transformers_through_the_engine():
+    from transformers import Mistral3Config, Mistral3ForConditionalGeneration, MistralConfig, PixtralVisionConfig
+    torch.manual_seed(0)
+    vc = PixtralVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                             image_size=64, patch_size=4, head_dim=8)
+    tc = MistralConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, vocab_size=300, max_position_embeddings=256, head_dim=16, sliding_window=None)
+    cfg = Mistral3Config(vision_config=vc, text_config=tc, image_token_index=IMG_TOKEN, spatial_merge_size=2,
+                         vision_feature_layer=-1)
+    m = Mistral3ForConditionalGeneration(cfg).eval()
+    d = tempfile.mkdtemp(prefix="vlm_mistral3_")
+    m.save_pretrained(d, safe_serialization=True)
+    assert is_vlm_checkpoint(d)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    vl.longest_edge, vl.break_id, vl.end_id = 32, 281, 282
+    imgs = [_image(5, 24, 16), _image(6, 33, 52)]        # 24 x 16 stays; 33 x 52 shrinks to fit 32 and rounds to 24 x 32
+    px = [vl.pixels(i) for i in imgs]
+    assert [tuple(p.shape[1:]) for p in px] == [(16, 24), (32, 24)]
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [IMG_TOKEN] + text(7) + [IMG_TOKEN] + text(4)
+    ids, mm = vl.prepare(prompt, imgs)
+    n_img = sum(1 for t in ids if t == IMG_TOKEN)
+    assert n_img == sum((p.shape[1] // 8) * (p.shape[2] // 8) for p in px)
+    assert ids.count(282) == 2 and ids.count(281) == sum(p.shape[1] // 8 - 1 for p in px)
+    assert vl.tokens_for(imgs[0]) == (16 // 8) * (24 // 8 + 1)
+    # the oracle takes the images padded into one batch plus their true sizes
+    H, W = max(p.shape[1] for p in px), max(p.shape[2] for p in px)
+    batch = torch.zeros(2, 3, H, W)
+    for i, p in enumerate(px):
+        batch[i, :, :p.shape[1], :p.shape[2]] = p
+    sizes = torch.tensor([list(p.shape[1:]) for p in px])
+    with torch.no_grad():
+        feats = m.model.get_image_features(batch, image_sizes=sizes, vision_feature_layer=-1).pooler_output
+    feats = torch.cat(list(feats)) if not isinstance(feats, torch.Tensor) else feats
+    torch.testing.assert_close(torch.cat([r for _, r in mm["mm_embeds"]]), feats.reshape(-1, feats.shape[-1]), rtol=1e-4, atol=1e-4)
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=batch,
+                          image_sizes=torch.tensor([list(p.shape[1:]) for p in px]), max_new_tokens=8,
+                          do_sample=False)[0, len(ids):].tolist()
+    assert _run_engine(d, ids, mm) == want
+    assert _run_engine(d, ids, mm, chunk=5) == want
