@@ -258,7 +258,8 @@ class DecoderModel:
             T0, nqk = qkv.shape[0], self.Hq + self.Hkv
             x3 = qkv.view(T0, self.Hq + 2 * self.Hkv, self.D)
             rot = ref.apply_mrope(x3[:, :nqk], b.positions3, self.inv_freq, cfg.extra["mrope_section"], self.mscale,
-                                  interleaved=bool(cfg.extra.get("mrope_interleaved")))
+                                  interleaved=bool(cfg.extra.get("mrope_interleaved")), rot_dim=rot_dim,
+                                  traditional=cfg.rope_traditional)
             qkv = torch.cat([rot.to(qkv.dtype), x3[:, nqk:]], dim=1).reshape(T0, -1).contiguous()
             rot_dim = 0
         use_win = window > 0 and b.slot_mapping_win is not None     # this layer's KV lives in the window pool

@@ -339,6 +339,102 @@ class Qwen3VisionTower(Qwen2VisionTower):
         return torch.cat([self._merge(x, self.merger, post=False)] + deep, dim=1)
 
 
+class Glm4vVisionTower(Qwen2VisionTower):
+    """GLM-4.1V tower (transformers `Glm4vVisionModel`; the reference's src/vision/encoders/glm4v.rs): biased
+    patch embedding, RMSNorm, a learned position table sampled bicubically at each patch centre, blocks
+    of RMSNorm + attention under the Qwen2-VL 2-D rotary positions + bias-free gated MLP, RMSNorm, a
+    strided convolution that folds every merge x merge group into one row, and a merger (linear,
+    LayerNorm, GELU, gated MLP). Rows come in merge-window order like the Qwen2-VL tower's."""
+
+    def __init__(self, vc: dict, tensors: dict, dtype=torch.bfloat16, device="cpu"):
+        self.dtype, self.device = dtype, torch.device(device)
+        self.depth, self.dim, self.heads = int(vc["depth"]), int(vc["hidden_size"]), int(vc["num_heads"])
+        self.patch, self.merge = int(vc.get("patch_size", 14)), int(vc.get("spatial_merge_size", 2))
+        self.eps = float(vc.get("rms_norm_eps", 1e-5))
+        self.act = {"silu": "silu", "gelu": "gelu", "gelu_pytorch_tanh": "gelu_tanh"}.get(vc.get("hidden_act", "silu"), "silu")
+
+        def t(n, required=True):
+            if n not in tensors and not required:
+                return None
+            return tensors[n].to(dtype).to(self.device).contiguous()
+
+        pw = t("patch_embed.proj.weight")
+        pw = pw.reshape(pw.shape[0], -1)
+        self.k_pad = (-pw.shape[1]) % 8
+        self.patch_w = F.pad(pw, (0, self.k_pad)).contiguous()
+        self.patch_b = t("patch_embed.proj.bias")
+        self.post_conv = t("post_conv_layernorm.weight")
+        self.pos_table = t("embeddings.position_embedding.weight")
+        self.side = int(round(self.pos_table.shape[0] ** 0.5))
+        self.blocks = []
+        for i in range(self.depth):
+            b = f"blocks.{i}."
+            self.blocks.append(dict(
+                n1=t(b + "norm1.weight"), n2=t(b + "norm2.weight"), wqkv=t(b + "attn.qkv.weight"), bqkv=t(b + "attn.qkv.bias", False),
+                wo=t(b + "attn.proj.weight"),
+                wgu=torch.cat([t(b + "mlp.gate_proj.weight"), t(b + "mlp.up_proj.weight")]).contiguous(),
+                wd=t(b + "mlp.down_proj.weight")))
+        self.post_ln = t("post_layernorm.weight")
+        dw = t("downsample.weight")                                   # [out, C, m, m]
+        self.down_w, self.down_b = dw.reshape(dw.shape[0], -1).contiguous(), t("downsample.bias")
+        self.mg = dict(proj=t("merger.proj.weight"), nw=t("merger.post_projection_norm.weight"), nb=t("merger.post_projection_norm.bias"),
+                       wgu=torch.cat([t("merger.gate_proj.weight"), t("merger.up_proj.weight")]).contiguous(),
+                       wd=t("merger.down_proj.weight"))
+        D = self.dim // self.heads
+        self.inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D // 2, 2, dtype=torch.float32) / (D // 2)))
+
+    def _pos_embed(self, grids) -> torch.Tensor:
+        tab = self.pos_table.float().view(self.side, self.side, -1).permute(2, 0, 1)[None]
+        m, out = self.merge, []
+        for t_, gh, gw in grids:
+            hp = torch.arange(gh)[:, None].expand(gh, gw).reshape(gh // m, m, gw // m, m).permute(0, 2, 1, 3).flatten()
+            wp = torch.arange(gw)[None, :].expand(gh, gw).reshape(gh // m, m, gw // m, m).permute(0, 2, 1, 3).flatten()
+            grid = torch.stack([(wp.float() + 0.5) / gw * 2 - 1, (hp.float() + 0.5) / gh * 2 - 1], dim=-1)[None, :, None, :]
+            pe = F.grid_sample(tab, grid.to(tab.device), mode="bicubic", align_corners=False, padding_mode="border")
+            out.append(pe[0, :, :, 0].t().repeat(t_, 1))
+        return torch.cat(out)
+
+    def _gated(self, y, wgu, wd, residual=None):
+        from ..models.vision import _act
+        gu = ops.linear(y, wgu)
+        inter = gu.shape[1] // 2
+        u = (_act(gu[:, :inter].contiguous(), self.act).float() * gu[:, inter:].float()).to(self.dtype).contiguous()
+        return ops.linear(u, wd, residual=residual)
+
+    @torch.no_grad()
+    def forward(self, rows: torch.Tensor, grids) -> torch.Tensor:
+        x = ops.linear(F.pad(rows.to(self.device, self.dtype), (0, self.k_pad)).contiguous(), self.patch_w, bias=self.patch_b)
+        x = ops.rmsnorm(x, self.post_conv, self.eps)
+        x = (x.float() + self._pos_embed(grids).to(self.device)).to(self.dtype)
+        R, H, D = x.shape[0], self.heads, self.dim // self.heads
+        ang = self._rot_angles(grids).to(self.device)
+        cos = torch.cat([ang.cos(), ang.cos()], dim=1)[:, None, :]
+        sin = torch.cat([ang.sin(), ang.sin()], dim=1)[:, None, :]
+        sizes = [gh * gw for t_, gh, gw in grids for _ in range(t_)]
+
+        def rot(v):
+            half = D // 2
+            return v * cos + torch.cat([-v[..., half:], v[..., :half]], dim=-1) * sin
+        for b in self.blocks:
+            y = ops.rmsnorm(x, b["n1"], self.eps)
+            qkv = ops.linear(y, b["wqkv"], bias=b["bqkv"]).view(R, 3, H, D)
+            q, k, v = rot(qkv[:, 0].float()), rot(qkv[:, 1].float()), qkv[:, 2].float()
+            outs, o0 = [], 0
+            for n in sizes:
+                qi, ki, vi = (z[o0:o0 + n].transpose(0, 1)[None] for z in (q, k, v))
+                outs.append(F.scaled_dot_product_attention(qi, ki, vi)[0].transpose(0, 1).reshape(n, H * D))
+                o0 += n
+            x = ops.linear(torch.cat(outs).to(self.dtype).contiguous(), b["wo"], residual=x)
+            x = self._gated(ops.rmsnorm(x, b["n2"], self.eps), b["wgu"], b["wd"], residual=x)
+        x = ops.rmsnorm(x, self.post_ln, self.eps)
+        unit = self.merge ** 2
+        y = x.view(R // unit, unit, self.dim).transpose(1, 2).reshape(R // unit, self.dim * unit).contiguous()
+        y = ops.linear(y, self.down_w, bias=self.down_b)
+        y = ops.linear(y, self.mg["proj"])
+        y = rops.activation(rops.layernorm(y, self.mg["nw"], self.mg["nb"], 1e-5), "gelu")
+        return self._gated(y, self.mg["wgu"], self.mg["wd"])
+
+
 class Qwen2VisionLanguage(VisionLanguage):
     def __init__(self, tower: Qwen2VisionTower, processor: Qwen2ImageProcessor, image_token_id: int, model_type: str):
         super().__init__(tower, None, processor, image_token_id, model_type)
@@ -404,7 +500,8 @@ def build_qwen2_vision(path, raw: dict, src, dtype, device) -> Qwen2VisionLangua
     import json
     from pathlib import Path
     mt = raw.get("model_type")
-    cls = Qwen3VisionTower if mt in ("qwen3_vl", "qwen3_vl_moe") else Qwen25VisionTower if mt == "qwen2_5_vl" else Qwen2VisionTower
+    cls = (Qwen3VisionTower if mt in ("qwen3_vl", "qwen3_vl_moe") else Qwen25VisionTower if mt == "qwen2_5_vl"
+           else Glm4vVisionTower if mt == "glm4v" else Qwen2VisionTower)
     tower = cls(raw["vision_config"], _sub(src, "model.visual.", "visual."), dtype, device)
     f = Path(path) / "preprocessor_config.json"
     pc = json.loads(f.read_text()) if f.exists() else None

@@ -10,7 +10,7 @@ src/multimodal/runtime*.rs).
 
 Supported wrappers: ``llava`` (CLIP or SigLIP tower, two-layer MLP connector), ``idefics3`` /
 ``smolvlm`` (SigLIP-layout tower, pixel-shuffle connector, one tile per image), ``qwen2_vl`` and
-``qwen2_5_vl`` and ``qwen3_vl`` (see `qwen2_vision.py`), ``internvl`` (InternViT tower, pixel-shuffle +
+``qwen2_5_vl``, ``qwen3_vl`` and ``glm4v`` (see `qwen2_vision.py`), ``internvl`` (InternViT tower, pixel-shuffle +
 MLP connector, one tile per image) and ``mistral3`` (Pixtral tower at the image's own aspect ratio,
 patch-merging connector; the prompt carries one row of image tokens per patch row, closed by a
 break token, the last by an end token). The language model is loaded by the ordinary decoder loader
@@ -29,7 +29,7 @@ from ..models.vision import (InternVLConnector, InternViTTower, LlavaConnector, 
                              PixtralTower, ViTTower, VisionConfig)
 from .images import ImageProcessor
 
-SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "idefics3", "smolvlm", "internvl", "mistral3")
+SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "idefics3", "smolvlm", "internvl", "mistral3", "glm4v")
 
 
 def is_vlm_checkpoint(path: str | Path) -> bool:
@@ -62,7 +62,7 @@ class VisionLanguage:
                                  "qwen3_vl_moe": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "idefics3": "<fake_token_around_image><global-img><image><fake_token_around_image>",
                                  "smolvlm": "<fake_token_around_image><global-img><image><fake_token_around_image>",
-                                 "internvl": "<img><IMG_CONTEXT></img>", "mistral3": "[IMG]"}.get(
+                                 "internvl": "<img><IMG_CONTEXT></img>", "glm4v": "<|begin_of_image|><|image|><|end_of_image|>", "mistral3": "[IMG]"}.get(
                                      model_type, "<image>")
         self.stats = dict(images=0, image_tokens=0, encode_seconds=0.0)
 
@@ -107,7 +107,7 @@ class VisionLanguage:
             return VisionLanguage(tower, conn, proc, raw.get("image_token_id", 151667), mt)
         if mt == "mistral3":
             return PixtralVisionLanguage.build(path, raw, src, dtype, device)
-        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe"):
+        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "glm4v"):
             from .qwen2_vision import build_qwen2_vision
             return build_qwen2_vision(path, raw, src, dtype, device)
         raise ValueError(f"unsupported vision-language model_type {mt!r}; supported: {SUPPORTED}")

@@ -157,27 +157,35 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
 
 
 def apply_mrope(x: torch.Tensor, positions3: torch.Tensor, inv_freq: torch.Tensor, sections, mscale: float = 1.0,
-                interleaved: bool = False) -> torch.Tensor:
+                interleaved: bool = False, rot_dim: int | None = None, traditional: bool = False) -> torch.Tensor:
     """Multimodal rotary embedding (Qwen2-VL): ``positions3`` [3, T] holds temporal / height / width
-    positions; frequency i of the head's D/2 takes the position of the section it falls in
-    (``sections`` = frequencies per component, e.g. [16, 24, 24]). ``interleaved`` (Qwen3-VL, Qwen3.5):
-    the components alternate T H W T H W ... over the first 3 * sections[1] (height) and
-    3 * sections[2] (width) frequencies and the rest are temporal, instead of three contiguous
-    chunks. Half-split (non-interleaved) pair layout. x: [T, H, D] → rotated fp32 tensor."""
+    positions; frequency i of the rotated width's half takes the position of the section it falls in
+    (``sections`` = frequencies per component, e.g. [16, 24, 24]; further sections cycle T H W again).
+    ``interleaved`` (Qwen3-VL, Qwen3.5): the components alternate T H W T H W ... over the first
+    3 * sections[1] (height) and 3 * sections[2] (width) frequencies and the rest are temporal, instead
+    of contiguous chunks. ``rot_dim`` rotates only the head's first columns (GLM-4V: half of each head);
+    ``traditional`` pairs columns (2i, 2i + 1) instead of (i, i + rot_dim / 2). x: [T, H, D] → fp32."""
     xf = x.float()
-    half = xf.shape[-1] // 2
+    rd = int(rot_dim or xf.shape[-1])
+    half = rd // 2
     if interleaved:
         which = torch.zeros(half, dtype=torch.long, device=xf.device)
         for comp, offset in ((1, 1), (2, 2)):
             which[offset:int(sections[comp]) * 3:3] = comp
     else:
-        which = torch.repeat_interleave(torch.arange(len(sections), device=xf.device),
+        which = torch.repeat_interleave(torch.arange(len(sections), device=xf.device) % 3,
                                         torch.tensor(list(sections), device=xf.device))[:half]  # [half] -> 0/1/2
     pos = positions3.float().to(xf.device)[which]                   # [half, T]
     ang = pos.t() * inv_freq.float()[None, :half]                   # [T, half]
     cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
-    a, b = xf[..., :half], xf[..., half:]
-    return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1) * mscale
+    if traditional:
+        a, b = xf[..., 0:rd:2], xf[..., 1:rd:2]
+        rot = torch.stack([a * cos - b * sin, b * cos + a * sin], dim=-1).flatten(-2)
+    else:
+        a, b = xf[..., :half], xf[..., half:rd]
+        rot = torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+    rot = rot * mscale
+    return rot if rd == xf.shape[-1] else torch.cat([rot, xf[..., rd:]], dim=-1)
 
 
 def head_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
