@@ -6,6 +6,11 @@ whole model. ``kv_bits=8`` stores uint8 values plus a bf16 (scale, bias) pair pe
 by the fused RoPE+append kernel and dequantized inside the attention kernels. ``kv_bits=4`` is the
 same affine scheme with 16 levels, two codes per byte (``[..., D / 2]`` bytes per row); the
 reference rejects uniform 4-bit KV (its 4-bit mode is TurboQuant), so this mode has no counterpart.
+
+Multi-head latent attention with ``cfg.extra["mla_latent"]`` keeps ONE entry per token and layer,
+``[normalised latent (kv_lora_rank) | rotary key (qk_rope_head_dim)]`` (576 values for DeepSeek-V3
+instead of 2 * heads * head_dim), in the K slab with a single head; the V slab is empty
+(the reference's MLA cache, src/lib/mlxcel-core/src/mla/cache.rs:253).
 """
 from __future__ import annotations
 
@@ -26,8 +31,17 @@ class KVPool:
         L = cfg.num_hidden_layers if num_layers is None else num_layers
         shape = (num_blocks, self.Hkv, block_size, self.D)
         self.layers: list[KVLayer] = []
+        self.latent = bool(cfg.extra.get("mla_latent"))
+        if self.latent:
+            if kv_bits != 16:
+                raise ValueError("the latent MLA cache stores 16-bit entries (kv_bits must be 16)")
+            self.Hkv, self.D = 1, self.latent_width(cfg)
         for _ in range(L):
-            if kv_bits == 16:
+            if self.latent:
+                k = torch.zeros((num_blocks, 1, block_size, self.D), dtype=dtype, device=device)
+                v = torch.zeros((num_blocks, 1, block_size, 0), dtype=dtype, device=device)
+                km = vm = None
+            elif kv_bits == 16:
                 k = torch.zeros(shape, dtype=dtype, device=device)
                 v = torch.zeros(shape, dtype=dtype, device=device)
                 km = vm = None
@@ -43,10 +57,17 @@ class KVPool:
             self.layers.append(KVLayer(k, v, km, vm, block_size, kv_bits))
 
     @staticmethod
+    def latent_width(cfg: ModelConfig) -> int:
+        m = cfg.extra["mla"]
+        return int(m["kv_lora_rank"]) + int(m["rope"])
+
+    @staticmethod
     def bytes_per_block(cfg: ModelConfig, block_size: int, kv_bits: int = 16, tp_size: int = 1,
                         num_layers: int | None = None) -> int:
         Hkv = max(1, cfg.num_key_value_heads // tp_size)
         L = cfg.num_hidden_layers if num_layers is None else num_layers
+        if cfg.extra.get("mla_latent"):
+            return KVPool.latent_width(cfg) * 2 * block_size * L
         per_tok = Hkv * cfg.head_dim * kv_bits // 8
         if kv_bits != 16:
             per_tok += Hkv * (cfg.head_dim // 64) * 4

@@ -32,6 +32,9 @@ def _add_model_args(p):
     p.add_argument("--context-shift", dest="context_shift", action="store_true", default=False,
                    help="at the KV bound drop the oldest blocks behind the first --keep tokens and go on generating")
     p.add_argument("--no-context-shift", dest="context_shift", action="store_false")
+    p.add_argument("--mla-latent-cache", dest="mla_latent_cache", action="store_true", default=False,
+                   help="multi-head latent attention models: cache one [latent | rotary key] entry per token "
+                        "(absorbed attention) instead of per-head keys and values")
     p.add_argument("--keep", type=int, default=0, help="tokens at the start of a sequence that context shifting never drops")
     p.add_argument("--no-prompt-cache", action="store_true")
     p.add_argument("--no-cuda-graphs", action="store_true")
@@ -211,6 +214,7 @@ def load_llm(a):
                         block_size=a.block_size, kv_bits=a.kv_bits or 16, num_blocks=a.kv_cache_blocks,
                         prefix_cache=not a.no_prompt_cache, max_model_len=a.ctx_size,
                         max_kv_size=getattr(a, "max_kv_size", 0), context_shift=getattr(a, "context_shift", False),
+                        mla_latent_cache=getattr(a, "mla_latent_cache", False),
                         n_keep=getattr(a, "keep", 0) or 0,
                         cuda_graphs=not a.no_cuda_graphs and dev != "cpu")
     comm = None

@@ -92,6 +92,7 @@ class EngineConfig:
     # stay keep their rotary positions; reference --max-kv-size / --context-shift / --keep,
     # src/server/batch/finish.rs:37-65, cache.rs trim_front_keep_sink)
     max_kv_size: int = 0
+    mla_latent_cache: bool = False       # MLA models: one [latent | rotary key] entry per token instead of per-head K / V
     context_shift: bool = False
     n_keep: int = 0
     cuda_graphs: bool = True
@@ -128,6 +129,12 @@ class Engine:
         if self.pipeline:
             # stages exchange activations with send / recv inside the forward pass: no graph capture,
             # and the token ids come back from the last stage, so nothing can be fed back on the device
+            e.cuda_graphs = e.lookahead = False
+        if e.mla_latent_cache:
+            if not cfg.extra.get("mla"):
+                raise ValueError("mla_latent_cache is for multi-head latent attention models (DeepSeek-V2 / V3 layout)")
+            # the absorbed attention is composed of batched matrix products with data-dependent shapes
+            cfg.extra["mla_latent"] = True
             e.cuda_graphs = e.lookahead = False
         if e.num_blocks <= 0:
             e.num_blocks = self._auto_num_blocks(tp, nl)

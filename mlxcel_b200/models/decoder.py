@@ -205,6 +205,8 @@ class DecoderModel:
                    kv: KVLayer, row_norm=None) -> torch.Tensor:
         cfg = self.cfg
         if lw.mla is not None:
+            if cfg.extra.get("mla_latent"):
+                return self._attention_mla_latent(li, lw, x, b, kv)
             return self._attention_mla(li, lw, x, b, kv)
         qkv = _linear_any(x, lw.wqkv, bias=lw.bqkv, row_norm=row_norm)
         if self.clip_qkv:                                   # DBRX: symmetric clamp of the fused projection
@@ -303,7 +305,7 @@ class DecoderModel:
         normalised latent through kv_b, one rotary key part shared by all heads. Keys [k_nope | k_rot]
         and values are zero-padded to the pool's head size and stored per head, so the ordinary paged
         kernels serve it; the attention output is cut back to v_head_dim. The absorbed form over a
-        latent cache (one 576-wide entry per token instead of 2 * heads * D) is not built."""
+        latent cache (one 576-wide entry per token instead of 2 * heads * D) is `_attention_mla_latent`."""
         from ..ops import reference as ref
 
         cfg, m, w = self.cfg, self.cfg.extra["mla"], lw.mla
@@ -334,6 +336,82 @@ class DecoderModel:
                         traditional=False, mscale=1.0, q_norm_w=None, k_norm_w=None, norm_eps=cfg.rms_norm_eps)
         attn = self._attend(qkv, b, kv, 0, None)
         return attn.view(T, Hq, Dp)[..., :vd].reshape(T, Hq * vd)
+
+    def _attention_mla_latent(self, li: int, lw: LayerWeights, x: torch.Tensor, b: StepBatch, kv: KVLayer) -> torch.Tensor:
+        """Multi-head latent attention in its absorbed form over a latent cache (the reference's
+        src/lib/mlxcel-core/src/mla/cache.rs:253 and its absorbed decode kernel): the pool keeps one entry
+        ``[normalised latent | rotary key]`` per token; the per-head key up-projection is folded into the
+        query (``q_lat = q_nope W_uk``) and the value up-projection is applied to the attention output
+        (``out = (P latent) W_uv``), so neither per-head keys nor values are ever materialised for the
+        context. Scores are ``q_lat . latent + q_rot . k_rot`` — the same numbers as the expanded form.
+        The attention itself is batched matrix products over the gathered pages (library GEMMs; a
+        hand-written absorbed-decode kernel is not built): decode rows gather their whole block table
+        and mask beyond the context length, prefill pieces are walked one by one under a causal mask."""
+        from ..ops import reference as ref
+
+        cfg, m, w = self.cfg, self.cfg.extra["mla"], lw.mla
+        Hq = self.Hq
+        nope, r, vd, lat = m["nope"], m["rope"], m["v"], m["kv_lora_rank"]
+        T, dev = x.shape[0], x.device
+        if w.get("q_a") is not None:
+            q = _linear_any(ops.rmsnorm(_linear_any(x, w["q_a"], bias=w.get("q_a_b")), w["q_a_norm"], 1e-6, 0.0), w["q_b"])
+        else:
+            q = _linear_any(x, w["q"])
+        q = q.view(T, Hq, nope + r)
+        ckv = _linear_any(x, w["kv_a"], bias=w.get("kv_a_b"))
+        c = ops.rmsnorm(ckv[:, :lat].contiguous(), w["kv_a_norm"], 1e-6, 0.0)
+        q_rot = ref.apply_rope(q[..., nope:], b.positions, self.inv_freq_mla, r, m["interleave"], self.mscale)
+        k_rot = ref.apply_rope(ckv[:, lat:].view(T, 1, r), b.positions, self.inv_freq_mla, r, m["interleave"], self.mscale)
+        q_nope = q[..., :nope]
+        if cfg.extra.get("llama4_attn_scale"):
+            beta, orig = cfg.extra["llama4_attn_scale"]
+            sc = (1.0 + beta * torch.log1p(torch.floor(b.positions.float() / orig)))[:, None, None]
+            q_nope, q_rot = (q_nope.float() * sc).to(q.dtype), (q_rot.float() * sc).to(q_rot.dtype)
+        wkv = w.get("kv_b_split")
+        if wkv is None:
+            dense = w["kv_b"]
+            if not isinstance(dense, torch.Tensor) or dense.dim() != 2 or dense.shape[1] != lat:
+                raise NotImplementedError("the latent MLA cache needs a dense kv_b projection (quantized kv_b is not absorbed)")
+            dense = dense.view(Hq, nope + vd, lat)
+            wkv = w["kv_b_split"] = (dense[:, :nope].contiguous(), dense[:, nope:].contiguous())     # W_uk, W_uv
+        w_uk, w_uv = wkv
+        # entry of the new tokens → their slots (padding rows carry slot -1 and are dropped)
+        entry = torch.cat([c, k_rot.view(T, r).to(c.dtype)], dim=1)
+        W = lat + r
+        flat = kv.k.view(-1, W)
+        ok = b.slot_mapping >= 0
+        flat.index_copy_(0, b.slot_mapping[ok].long(), entry[ok].to(flat.dtype))
+        # queries in latent space: [T, Hq, lat + r]
+        q_lat = torch.einsum("thn,hnl->thl", q_nope.float(), w_uk.float())
+        qq = torch.cat([q_lat, q_rot.float()], dim=-1)
+        scale = float(cfg.attn_scale)
+        out_lat = torch.zeros(T, Hq, lat, dtype=torch.float32, device=dev)
+        bs = kv.block_size
+        nd = b.num_decode
+        if nd > 0:
+            tab = b.dec_block_tables[:nd].clamp(min=0).long()
+            ctx = kv.k[tab].view(nd, -1, W).float()                              # [nd, blocks * bs, W]
+            s = torch.einsum("nhw,nsw->nhs", qq[:nd], ctx) * scale
+            live = torch.arange(ctx.shape[1], device=dev)[None, :] < b.dec_context_lens[:nd, None]
+            s = s.masked_fill(~live[:, None, :], float("-inf"))
+            p = torch.softmax(s, dim=-1).nan_to_num(0.0)                        # a padding row has no live key
+            out_lat[:nd] = torch.einsum("nhs,nsl->nhl", p, ctx[..., :lat])
+        if b.num_prefill_seqs > 0:
+            cu = b.pf_cu_q_host if b.pf_cu_q_host is not None else b.pf_cu_q.tolist()
+            lens = b.pf_context_lens.tolist()
+            for i in range(b.num_prefill_seqs):
+                r0, r1, L = nd + int(cu[i]), nd + int(cu[i + 1]), int(lens[i])
+                n = r1 - r0
+                if n <= 0:
+                    continue
+                nb = (L + bs - 1) // bs
+                ctx = kv.k[b.pf_block_tables[i, :nb].long()].view(-1, W)[:L].float()
+                s = torch.einsum("thw,sw->ths", qq[r0:r1], ctx) * scale
+                qpos = torch.arange(L - n, L, device=dev)
+                s = s.masked_fill((torch.arange(L, device=dev)[None, :] > qpos[:, None])[:, None, :], float("-inf"))
+                out_lat[r0:r1] = torch.einsum("ths,sl->thl", torch.softmax(s, dim=-1), ctx[:, :lat])
+        out = torch.einsum("thl,hvl->thv", out_lat, w_uv.float())
+        return out.reshape(T, Hq * vd).to(x.dtype)
 
     def _norm(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
         """The model's normalisation: RMSNorm (with Gemma's +1) or LayerNorm (bias optional)."""

@@ -782,3 +782,45 @@ def test_lfm2_moe_matches_transformers():
     got = ours.forward(b, pool.layers).float()
     err = (got - want).abs().max().item()
     assert err < 2e-3 * max(want.abs().max().item(), 1.0), f"max abs error {err:.3e}"
+
+
+@pytest.mark.parametrize("name", ["deepseek_v2", "deepseek_v3"])
+def test_mla_latent_cache_matches_the_expanded_form_and_transformers(name):
+    """The absorbed attention over one [latent | rotary key] entry per token: same tokens as the expanded
+    per-head cache, every one transformers' argmax, with several sequences decoding together (batched
+    gather with masked tails), chunked prefill and a preempted sequence recomputed."""
+    from mlxcel_b200.cache.kv_pool import KVPool
+    from mlxcel_b200.engine.engine import Engine, EngineConfig
+    from mlxcel_b200.engine.params import SamplingParams
+    from mlxcel_b200.loading.checkpoint import load_full_weights
+
+    model = _hf_model(name)
+    d = tempfile.mkdtemp(prefix=f"latent_{name}_")
+    model.save_pretrained(d, safe_serialization=True)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(3, 300, (n,), generator=g).tolist() for n in (37, 5, 21)]
+    outs = {}
+    for latent in (False, True):
+        cfg = ModelConfig.from_path(d)
+        eng = Engine(DecoderModel(cfg, load_full_weights(d, cfg, dtype=torch.float32)), cfg,
+                     EngineConfig(num_blocks=64, block_size=16, max_batch=4, max_model_len=256, max_num_batched_tokens=16,
+                                  cuda_graphs=False, mla_latent_cache=latent))
+        if latent:
+            m = cfg.extra["mla"]
+            assert eng.pool.layers[0].k.shape[1:] == (1, 16, m["kv_lora_rank"] + m["rope"]) and eng.pool.layers[0].v.numel() == 0
+            full = ModelConfig.from_path(d)
+            assert KVPool.bytes_per_block(cfg, 16) * 4 < KVPool.bytes_per_block(full, 16)
+        outs[latent] = [r.output for r in eng.generate(prompts, SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True))]
+    assert outs[True] == outs[False]
+    for p, out in zip(prompts, outs[True]):
+        with torch.no_grad():
+            lg = model(torch.tensor(p + out)[None]).logits[0]
+        for i, tok in enumerate(out):
+            row = lg[len(p) - 1 + i]
+            assert row[tok].item() >= row.max().item() - 2e-3, (i, tok, int(row.argmax()))
+    with pytest.raises(ValueError, match="latent"):
+        from mlxcel_b200.config import ModelConfig as MC
+        lc = MC.from_dict(dict(model_type="llama", hidden_size=64, num_hidden_layers=1, num_attention_heads=4, vocab_size=64,
+                               intermediate_size=128))
+        from mlxcel_b200.models.weights import random_weights
+        Engine(DecoderModel(lc, random_weights(lc, dtype=torch.float32)), lc, EngineConfig(num_blocks=8, mla_latent_cache=True, cuda_graphs=False))
