@@ -457,9 +457,17 @@ def cmd_generate(a):
     if getattr(a, "diffusion", False):
         return _generate_diffusion(a, llm, tk, prompt)
     mm = {}
+    if getattr(a, "audio", None):
+        front = getattr(llm, "vision", None)
+        if getattr(front, "modality", None) != "audio":
+            raise SystemExit("--audio needs a speech-language checkpoint (voxtral, qwen2_audio)")
+        if getattr(a, "image", None):
+            raise SystemExit("--audio and --image do not combine")
+        if prompt.count(front.placeholder_text) == 0:
+            prompt = front.placeholder_text * len(a.audio) + "\n" + prompt
     if getattr(a, "image", None):
         vision = getattr(llm, "vision", None)
-        if vision is None:
+        if vision is None or getattr(vision, "modality", "image") != "image":
             raise SystemExit("--image needs a vision-language checkpoint")
         if prompt.count(vision.placeholder_text) == 0:       # images first, then the text (the usual layout)
             prompt = vision.placeholder_text * len(a.image) + "\n" + prompt
@@ -470,6 +478,11 @@ def cmd_generate(a):
     if getattr(a, "image", None):
         from .multimodal import load_image
         ids, mm = llm.vision.prepare(ids, [load_image(x) for x in a.image])
+    if getattr(a, "audio", None):
+        from pathlib import Path as _P
+
+        from .audio.wav import decode_audio
+        ids, mm = llm.vision.prepare(ids, [decode_audio(_P(x).read_bytes(), 16000) for x in a.audio])
     sp = _sampling(a)
     sp.stop_token_ids = [i for i in tk.eos_ids() if i is not None]
     from .tokenizer import IncrementalDetokenizer
@@ -1085,7 +1098,7 @@ def arch_catalog() -> dict:
             how = "a plain PyTorch statement of the model (the transformers implementation is not usable)"
         fams.append(dict(name=name, executor=ex, checked_against=how))
     return {"families": fams, "encoders": ["bert", "modernbert", "deberta-v2", "siglip text"],
-            "vision_language": ["llava (clip / siglip tower)", "qwen2_vl", "qwen2_5_vl", "qwen3_vl (DeepStack)", "idefics3 / smolvlm (one tile per image)", "internvl (one tile per image)", "mistral3 (pixtral tower)", "glm4v"], "speech": ["whisper"],
+            "vision_language": ["llava (clip / siglip tower)", "qwen2_vl", "qwen2_5_vl", "qwen3_vl (DeepStack)", "idefics3 / smolvlm (one tile per image)", "internvl (one tile per image)", "mistral3 (pixtral tower)", "glm4v"], "speech": ["whisper"], "speech_language": ["voxtral", "qwen2_audio (clips up to one 30 s chunk)"],
             "quantization": ["affine", "mxfp4", "mxfp8", "fp8 (widened at load)", "nvfp4 (expanded at load)",
                              "bitlinear ternary (expanded at load)"],
             "kv_bits": [16, 8, 4], "parallelism": ["tp", "ep (replicated tokens)", "dp attention + ep (all-to-all)", "pp", "tp x pp",
@@ -1165,6 +1178,8 @@ def main(argv=None):
     p.add_argument("--diffusion-threshold", type=float, default=0.95)
     p.add_argument("--image", action="append", default=None, metavar="FILE",
                    help="image for a vision-language checkpoint (repeatable; one per placeholder, or placed before the prompt)")
+    p.add_argument("--audio", action="append", default=None, metavar="FILE",
+                   help="WAV clip for a speech-language checkpoint (repeatable; one per placeholder, or placed before the prompt)")
     p.set_defaults(fn=cmd_generate)
     p = sub.add_parser("run", help="interactive chat")
     _add_model_args(p)

@@ -127,6 +127,10 @@ class LLM:
         from .multimodal import VisionLanguage, is_vlm_checkpoint
         if is_vlm_checkpoint(path):
             llm.vision = VisionLanguage.from_checkpoint(path, dtype=w.final_norm.dtype, device=device)
+        from .multimodal.audio_lm import AudioLanguage, is_audio_lm_checkpoint
+        if is_audio_lm_checkpoint(path):
+            # speech-language checkpoints use the same media front-end slot: prompts carry audio placeholders
+            llm.vision = AudioLanguage.from_checkpoint(path, dtype=w.final_norm.dtype, device=device)
         return llm
 
     # ------------------------------------------------------------------ scoring

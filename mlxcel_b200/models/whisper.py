@@ -71,9 +71,12 @@ class _Attn:
 
 
 class WhisperModel:
-    def __init__(self, cfg: WhisperConfig, tensors: dict, dtype=torch.bfloat16, device="cpu"):
+    def __init__(self, cfg: WhisperConfig, tensors: dict, dtype=torch.bfloat16, device="cpu", *, encoder_only: bool = False,
+                 prefix: str | None = None):
+        """``encoder_only`` builds the audio encoder alone (speech-language models keep a Whisper encoder
+        in front of a projector and a text decoder); ``prefix`` names where its tensors live."""
         self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
-        pre = "model." if any(k.startswith("model.") for k in tensors) else ""
+        pre = prefix if prefix is not None else ("model." if any(k.startswith("model.") for k in tensors) else "")
 
         def t(n):
             return tensors[pre + n].to(dtype).to(self.device).contiguous()
@@ -81,7 +84,7 @@ class WhisperModel:
         def ln(p):
             return t(p + ".weight"), t(p + ".bias")
 
-        e = "encoder."
+        e = "" if encoder_only else "encoder."
         # conv weights [out, in, 3] -> GEMM weights over frames unfolded as (tap, channel)
         self.c1w = t(e + "conv1.weight").permute(0, 2, 1).reshape(cfg.d_model, -1).contiguous()
         self.c1b = t(e + "conv1.bias")
@@ -93,6 +96,8 @@ class WhisperModel:
                          w2=t(f"{e}layers.{i}.fc2.weight"), b2=t(f"{e}layers.{i}.fc2.bias"),
                          ln2=ln(f"{e}layers.{i}.final_layer_norm")) for i in range(cfg.enc_layers)]
         self.enc_ln = ln(e + "layer_norm")
+        if encoder_only:
+            return
         d = "decoder."
         self.tok = t(d + "embed_tokens.weight")
         self.dec_pos = t(d + "embed_positions.weight")
@@ -128,16 +133,20 @@ class WhisperModel:
         y = rops.activation(ops.linear(cols, w, bias=b), "gelu")
         return y.view(B, -1, w.shape[0])
 
-    def _mha(self, q, k, v, heads: int, causal: bool = False) -> torch.Tensor:
-        """q [B, Tq, d], k / v [B, Tk, d] → [B * Tq, d]."""
+    def _mha(self, q, k, v, heads: int, causal: bool = False, key_len: int | None = None) -> torch.Tensor:
+        """q [B, Tq, d], k / v [B, Tk, d] → [B * Tq, d]. ``key_len`` hides the keys from that index on
+        (the zero-padded tail of a clip shorter than its chunk)."""
         B, Tq, d = q.shape
         D = d // heads
-        sp = lambda z: z.view(B, -1, heads, D).transpose(1, 2)    # noqa: E731
-        o = F.scaled_dot_product_attention(sp(q), sp(k), sp(v), is_causal=causal and Tq > 1)
+        sp = lambda z: z.reshape(B, -1, heads, D).transpose(1, 2)    # noqa: E731
+        mask = None
+        if key_len is not None and key_len < k.shape[1]:
+            mask = (torch.arange(k.shape[1], device=q.device) < key_len).view(1, 1, 1, -1)
+        o = F.scaled_dot_product_attention(sp(q), sp(k), sp(v), attn_mask=mask, is_causal=causal and Tq > 1)
         return o.transpose(1, 2).reshape(B * Tq, d).contiguous()
 
     @torch.no_grad()
-    def encode(self, mel: torch.Tensor) -> torch.Tensor:
+    def encode(self, mel: torch.Tensor, key_len: int | None = None, final_norm: bool = True) -> torch.Tensor:
         """[B, n_mels, frames] → [B, frames / 2, d_model]."""
         c = self.cfg
         x = mel.to(self.device, self.dtype).transpose(1, 2).contiguous()
@@ -148,11 +157,11 @@ class WhisperModel:
             a = L["attn"]
             y = rops.layernorm(h, *L["ln1"], 1e-5)
             qkv = ops.linear(y, a.wqkv, bias=a.bqkv).view(B, T, 3, d)
-            o = self._mha(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], c.enc_heads)
+            o = self._mha(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], c.enc_heads, key_len=key_len)
             h = ops.linear(o, a.wo, bias=a.bo, residual=h)
             y = rops.layernorm(h, *L["ln2"], 1e-5)
             h = ops.linear(rops.activation(ops.linear(y, L["w1"], bias=L["b1"]), c.act), L["w2"], bias=L["b2"], residual=h)
-        return rops.layernorm(h, *self.enc_ln, 1e-5).view(B, T, d)
+        return (rops.layernorm(h, *self.enc_ln, 1e-5) if final_norm else h).view(B, T, d)
 
     # ------------------------------------------------------------------ decoder
     def _cross_kv(self, enc: torch.Tensor):

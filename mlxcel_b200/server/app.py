@@ -579,6 +579,22 @@ def create_app(state: ServerState) -> FastAPI:
         return {"content": text, "tokens_predicted": fin.usage["completion_tokens"], "timings": fin.timings}
 
     # ------------------------------------------------------------------ chat completions
+    def _load_audio(src):
+        """An ``input_audio`` part's base64 payload (or a ``data:`` URL) → 16 kHz mono samples."""
+        import base64
+
+        from ..audio.wav import decode_audio
+        if not isinstance(src, str):
+            raise ValueError("audio must be base64 text or a data: URL")
+        if src.startswith("data:"):
+            src = src.partition(",")[2]
+        elif src.startswith(("http://", "https://", "file://", "/")):
+            raise ValueError("audio must be sent inline (base64); URLs and paths are not fetched")
+        try:
+            return decode_audio(base64.b64decode(src), 16000)
+        except Exception as e:
+            raise ValueError(f"audio could not be decoded: {e}") from None
+
     def _chat_prompt(body: dict):
         tools = body.get("tools")
         kwargs = dict(body.get("chat_template_kwargs") or {})
@@ -586,17 +602,26 @@ def create_app(state: ServerState) -> FastAPI:
             kwargs.setdefault("reasoning_effort", body["reasoning_effort"])
         messages, images = body.get("messages", []), []
         vision = getattr(state.worker, "vision", None)
-        has_media = any(isinstance(m.get("content"), list) and any(isinstance(p, dict) and p.get("type") in
-                        ("image_url", "image", "input_image") for p in m["content"]) for m in messages)
+        audio_in = getattr(vision, "modality", "image") == "audio"
+        part_types = ("input_audio", "audio_url", "audio") if audio_in else ("image_url", "image", "input_image")
+        other = ("image_url", "image", "input_image") if audio_in else ("input_audio", "audio_url", "audio")
+        parts_of = lambda kinds: any(isinstance(m.get("content"), list) and any(  # noqa: E731
+            isinstance(p, dict) and p.get("type") in kinds for p in m["content"]) for m in messages)
+        if parts_of(other) and (vision is not None or other[0] == "input_audio"):
+            raise TemplateRenderError("this model takes no audio input" if other[0] == "input_audio" else "this model takes no image input")
+        has_media = parts_of(part_types)
         if has_media:
             if vision is None:
                 raise TemplateRenderError("this model takes no image input")
             from .chat_template import extract_media
-            messages, sources = extract_media(messages, vision.placeholder_text, state.chat_template)
-            from ..multimodal import load_image
+            messages, sources = extract_media(messages, vision.placeholder_text, state.chat_template, audio=audio_in)
             try:
-                images = [load_image(src, media_root=getattr(state, "media_path", None),
-                                     allow_remote=bool(getattr(state, "allow_remote_media", False))) for src in sources]
+                if audio_in:
+                    images = [_load_audio(src) for src in sources]
+                else:
+                    from ..multimodal import load_image
+                    images = [load_image(src, media_root=getattr(state, "media_path", None),
+                                         allow_remote=bool(getattr(state, "allow_remote_media", False))) for src in sources]
             except ValueError as e:
                 raise TemplateRenderError(str(e)) from e
         text = state.render(messages, tools=tools, **kwargs)
@@ -607,7 +632,7 @@ def create_app(state: ServerState) -> FastAPI:
             ids.media = images
             n_ph = sum(1 for t in ids if t == vision.image_token_id)
             if n_ph != len(images):
-                raise TemplateRenderError(f"the rendered prompt has {n_ph} image placeholders for {len(images)} images")
+                raise TemplateRenderError(f"the rendered prompt has {n_ph} media placeholders for {len(images)} attachments")
         return ids, tools
 
     @app.post("/v1/chat/completions")

@@ -76,29 +76,35 @@ def normalize_messages(messages: list[dict]) -> list[dict]:
 _IMAGE_PART_TYPES = ("image_url", "image", "input_image")
 
 
-def extract_media(messages: list[dict], placeholder: str, template: str | None) -> tuple[list[dict], list]:
+_AUDIO_PART_TYPES = ("input_audio", "audio_url", "audio")
+
+
+def extract_media(messages: list[dict], placeholder: str, template: str | None, audio: bool = False) -> tuple[list[dict], list]:
     """Pull the images out of OpenAI-style content parts. Returns the messages to render and the image
     sources in prompt order. A template that handles ``{"type": "image"}`` parts itself (the templates
     vision-language checkpoints ship) gets them in that form; otherwise every image part becomes the
     model's placeholder text inside a flattened string content."""
-    native = bool(template) and ("'image'" in template or '"image"' in template)
+    kinds = _AUDIO_PART_TYPES if audio else _IMAGE_PART_TYPES
+    tag = "audio" if audio else "image"
+    native = bool(template) and (f"'{tag}'" in template or f'"{tag}"' in template)
     out, images = [], []
     for m in messages:
         c = m.get("content")
-        if not isinstance(c, list) or not any(isinstance(p, dict) and p.get("type") in _IMAGE_PART_TYPES for p in c):
+        if not isinstance(c, list) or not any(isinstance(p, dict) and p.get("type") in kinds for p in c):
             out.append(m)
             continue
         parts, text = [], ""
         for p in c:
             kind = p.get("type") if isinstance(p, dict) else None
-            if kind in _IMAGE_PART_TYPES:
-                src = p.get("image_url") or p.get("image") or p.get("url")
+            if kind in kinds:
+                src = (p.get("input_audio") or p.get("audio_url") or p.get("audio") or p.get("url")) if audio else \
+                    (p.get("image_url") or p.get("image") or p.get("url"))
                 if isinstance(src, dict):
-                    src = src.get("url")
+                    src = src.get("data") or src.get("url")
                 if src is None:
-                    raise TemplateRenderError("an image part carries no image_url")
+                    raise TemplateRenderError(f"an {tag} part carries no data")
                 images.append(src)
-                parts.append({"type": "image"})
+                parts.append({"type": tag})
                 text += placeholder
             elif kind in ("text", "input_text"):
                 parts.append({"type": "text", "text": p.get("text", "")})
