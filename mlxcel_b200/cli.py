@@ -1001,6 +1001,25 @@ def cmd_transcribe(a):
             print(r["text"])
 
 
+def cmd_depth(a):
+    """Monocular depth for image files with a Depth Anything checkpoint: a 16-bit PNG per image (depth scaled to
+    the full range; nearer is brighter for relative depth) and one JSON line with the value range."""
+    import numpy as np
+    import torch
+    from PIL import Image
+
+    from .models.depth_anything import DepthAnything
+    from .multimodal import load_image
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    m = DepthAnything.from_pretrained(a.model, torch.bfloat16 if dev != "cpu" else torch.float32, dev)
+    for f in a.files:
+        d = m.estimate(load_image(f), short_side=a.short_side)
+        lo, hi = float(d.min()), float(d.max())
+        out = os.path.splitext(f)[0] + ".depth.png" if a.out_dir is None else os.path.join(a.out_dir, os.path.basename(f) + ".depth.png")
+        Image.fromarray(((d - lo) / max(hi - lo, 1e-12) * 65535.0).astype(np.uint16)).save(out)
+        print(json.dumps(dict(file=f, out=out, min=lo, max=hi, height=int(d.shape[0]), width=int(d.shape[1]), metric=m.metric)))
+
+
 def cmd_front(a):
     """One listener in front of several servers (server/front.py): given URLs, or ``--dp N`` replicas
     that this process starts itself, one per GPU, and stops again when it exits."""
@@ -1098,7 +1117,7 @@ def arch_catalog() -> dict:
             how = "a plain PyTorch statement of the model (the transformers implementation is not usable)"
         fams.append(dict(name=name, executor=ex, checked_against=how))
     return {"families": fams, "encoders": ["bert", "modernbert", "deberta-v2", "siglip text"],
-            "vision_language": ["llava (clip / siglip tower)", "qwen2_vl", "qwen2_5_vl", "qwen3_vl (DeepStack)", "idefics3 / smolvlm (one tile per image)", "internvl (one tile per image)", "mistral3 (pixtral tower)", "glm4v"], "speech": ["whisper"], "speech_language": ["voxtral", "qwen2_audio (clips up to one 30 s chunk)"],
+            "vision_language": ["llava (clip / siglip tower)", "qwen2_vl", "qwen2_5_vl", "qwen3_vl (DeepStack)", "idefics3 / smolvlm (one tile per image)", "internvl (one tile per image)", "mistral3 (pixtral tower)", "glm4v"], "speech": ["whisper"], "dense_prediction": ["depth_anything (dinov2 backbone)"], "speech_language": ["voxtral", "qwen2_audio (clips up to one 30 s chunk)"],
             "quantization": ["affine", "mxfp4", "mxfp8", "fp8 (widened at load)", "nvfp4 (expanded at load)",
                              "bitlinear ternary (expanded at load)"],
             "kv_bits": [16, 8, 4], "parallelism": ["tp", "ep (replicated tokens)", "dp attention + ep (all-to-all)", "pp", "tp x pp",
@@ -1245,6 +1264,13 @@ def main(argv=None):
     p.add_argument("--device", default=None)
     p.add_argument("--json", action="store_true")
     p.set_defaults(fn=cmd_transcribe)
+    p = sub.add_parser("depth", help="monocular depth maps for image files (Depth Anything checkpoints)")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("files", nargs="+")
+    p.add_argument("--short-side", type=int, default=518, help="the shorter image side is resized to this many pixels")
+    p.add_argument("--out-dir", default=None, help="where the PNGs go (default: beside each image)")
+    p.add_argument("--device", default=None)
+    p.set_defaults(fn=cmd_depth)
     p = sub.add_parser("front", help="one listener in front of data-parallel replicas or prefill/decode servers")
     p.add_argument("--replica-url", action="append", default=None, metavar="URL", help="a running server of the model (repeatable)")
     p.add_argument("--prefill-url", action="append", default=None, metavar="URL", help="prefill-role server (disaggregated serving)")
