@@ -362,6 +362,31 @@ class InternVLConnector:
         return ops.linear(u, self.w2, bias=self.b2).view(N, T // (s * s), -1)
 
 
+class Cohere2VisionConnector:
+    """Command A Vision / Aya Vision layout: pixel shuffle by ``downsample_factor``, one biased linear to
+    twice the gated width, ``silu(gate) * x`` over its two halves (the gate is the second half), one
+    biased linear (`Cohere2VisionMultiModalProjector`)."""
+
+    def __init__(self, tensors: dict, factor: int = 2, dtype=torch.bfloat16, device="cpu"):
+        t = lambda n: tensors[n].to(dtype).to(device).contiguous()  # noqa: E731
+        self.s = int(factor)
+        self.w1, self.b1, self.w2, self.b2 = t("linear_1.weight"), t("linear_1.bias"), t("linear_2.weight"), t("linear_2.bias")
+
+    def tokens_out(self, tokens_in: int) -> int:
+        return tokens_in // (self.s * self.s)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        N, T, H = x.shape
+        g, s = int(math.isqrt(T)), self.s
+        x = x.reshape(N, g, g // s, s * H).permute(0, 2, 1, 3)
+        x = x.reshape(N, g // s, g // s, s * s * H).permute(0, 2, 1, 3)
+        x = x.reshape(N * (T // (s * s)), s * s * H).contiguous()
+        u = ops.linear(x, self.w1, bias=self.b1)
+        half = u.shape[1] // 2
+        u = (_act(u[:, half:].contiguous(), "silu").float() * u[:, :half].float()).to(x.dtype).contiguous()
+        return ops.linear(u, self.w2, bias=self.b2).view(N, T // (s * s), -1)
+
+
 # ----------------------------------------------------------------------------- Pixtral (Mistral3)
 class PixtralTower:
     """Pixtral's vision transformer (transformers `PixtralVisionModel`; the reference's

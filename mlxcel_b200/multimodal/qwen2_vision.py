@@ -501,7 +501,7 @@ def build_qwen2_vision(path, raw: dict, src, dtype, device) -> Qwen2VisionLangua
     from pathlib import Path
     mt = raw.get("model_type")
     cls = (Qwen3VisionTower if mt in ("qwen3_vl", "qwen3_vl_moe") else Qwen25VisionTower if mt == "qwen2_5_vl"
-           else Glm4vVisionTower if mt == "glm4v" else Qwen2VisionTower)
+           else Glm4vVisionTower if mt in ("glm4v", "glm4v_moe") else Qwen2VisionTower)
     tower = cls(raw["vision_config"], _sub(src, "model.visual.", "visual."), dtype, device)
     f = Path(path) / "preprocessor_config.json"
     pc = json.loads(f.read_text()) if f.exists() else None

@@ -25,11 +25,11 @@ from pathlib import Path
 
 import torch
 
-from ..models.vision import (InternVLConnector, InternViTTower, LlavaConnector, Mistral3Connector, PixelShuffleConnector,
+from ..models.vision import (Cohere2VisionConnector, InternVLConnector, InternViTTower, LlavaConnector, Mistral3Connector, PixelShuffleConnector,
                              PixtralTower, ViTTower, VisionConfig)
 from .images import ImageProcessor
 
-SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "idefics3", "smolvlm", "internvl", "mistral3", "glm4v")
+SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "idefics3", "smolvlm", "internvl", "mistral3", "glm4v", "glm4v_moe", "cohere2_vision")
 
 
 def is_vlm_checkpoint(path: str | Path) -> bool:
@@ -62,7 +62,8 @@ class VisionLanguage:
                                  "qwen3_vl_moe": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "idefics3": "<fake_token_around_image><global-img><image><fake_token_around_image>",
                                  "smolvlm": "<fake_token_around_image><global-img><image><fake_token_around_image>",
-                                 "internvl": "<img><IMG_CONTEXT></img>", "glm4v": "<|begin_of_image|><|image|><|end_of_image|>", "mistral3": "[IMG]"}.get(
+                                 "internvl": "<img><IMG_CONTEXT></img>", "glm4v": "<|begin_of_image|><|image|><|end_of_image|>", "glm4v_moe": "<|begin_of_image|><|image|><|end_of_image|>",
+                                 "cohere2_vision": "<|START_OF_IMG|><|IMG_PATCH|><|END_OF_IMG|>", "mistral3": "[IMG]"}.get(
                                      model_type, "<image>")
         self.stats = dict(images=0, image_tokens=0, encode_seconds=0.0)
 
@@ -105,9 +106,20 @@ class VisionLanguage:
                                        resample=pc.get("resample", 3), image_mean=pc.get("image_mean", [0.485, 0.456, 0.406]),
                                        image_std=pc.get("image_std", [0.229, 0.224, 0.225])), tower.image_size)
             return VisionLanguage(tower, conn, proc, raw.get("image_token_id", 151667), mt)
+        if mt == "cohere2_vision":
+            # SigLIP tower (last state), one tile per image: the split of large images into several crops
+            # plus a thumbnail is not done
+            vc = VisionConfig.from_dict(raw["vision_config"], {})
+            vc.kind, vc.feature_layer, vc.drop_cls = "siglip", -1, False
+            tower = ViTTower(vc, _sub(src, "model.vision_tower.vision_model.", "vision_tower.vision_model."), dtype, device)
+            conn = Cohere2VisionConnector(_sub(src, "model.multi_modal_projector.", "multi_modal_projector."),
+                                          int(raw.get("downsample_factor", 2)), dtype, device)
+            proc = ImageProcessor(dict(size={"height": vc.image_size, "width": vc.image_size}, do_center_crop=False,
+                                       resample=3, image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5]), vc.image_size)
+            return VisionLanguage(tower, conn, proc, raw.get("image_token_id", 255036), mt)
         if mt == "mistral3":
             return PixtralVisionLanguage.build(path, raw, src, dtype, device)
-        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "glm4v"):
+        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "glm4v", "glm4v_moe"):
             from .qwen2_vision import build_qwen2_vision
             return build_qwen2_vision(path, raw, src, dtype, device)
         raise ValueError(f"unsupported vision-language model_type {mt!r}; supported: {SUPPORTED}")

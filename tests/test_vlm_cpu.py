@@ -619,3 +619,73 @@ def test_glm4v_tower_and_greedy_match_transformers():
     assert cfg2.extra["mrope_section"] == [1, 2, 1] and cfg2.rope_traditional and cfg2.rot_dim == 8
     assert _run_engine(d, ids, mm) == want
     assert _run_engine(d, ids, mm, chunk=10) == want
+
+
+def test_cohere2_vision_greedy_matches_transformers_through_the_engine():
+    from transformers import Cohere2Config, Cohere2VisionConfig, Cohere2VisionForConditionalGeneration, SiglipVisionConfig
+    torch.manual_seed(0)
+    vc = SiglipVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, image_size=28,
+                            patch_size=7)
+    tc = Cohere2Config(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                       vocab_size=300, max_position_embeddings=256, sliding_window=64, logit_scale=0.25)
+    cfg = Cohere2VisionConfig(vision_config=vc, text_config=tc, image_token_id=IMG_TOKEN, downsample_factor=2,
+                              alignment_intermediate_size=96)
+    m = Cohere2VisionForConditionalGeneration(cfg).eval()
+    d = tempfile.mkdtemp(prefix="vlm_cohere2v_")
+    m.save_pretrained(d, safe_serialization=True)
+    assert is_vlm_checkpoint(d)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    imgs = [_image(5), _image(6, 33, 52)]
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [IMG_TOKEN] + text(7) + [IMG_TOKEN] + text(4)
+    ids, mm = vl.prepare(prompt, imgs)
+    assert len(ids) == 16 + 2 * 4
+    with torch.no_grad():
+        feats = m.model.get_image_features(vl.processor(imgs)).pooler_output
+    torch.testing.assert_close(torch.stack([r for _, r in mm["mm_embeds"]]), feats.reshape(2, 4, -1), rtol=1e-4, atol=1e-4)
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=vl.processor(imgs), max_new_tokens=8,
+                          do_sample=False)[0, len(ids):].tolist()
+    assert _run_engine(d, ids, mm) == want
+    assert _run_engine(d, ids, mm, chunk=7) == want
+
+
+def test_glm4v_moe_greedy_matches_transformers_through_the_engine():
+    from transformers import Glm4vMoeConfig, Glm4vMoeForConditionalGeneration
+
+    from mlxcel_b200.multimodal.qwen2_vision import Qwen2ImageProcessor
+    torch.manual_seed(0)
+    cfg = Glm4vMoeConfig(
+        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, vocab_size=300, max_position_embeddings=512, head_dim=16,
+                         moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2, n_shared_experts=1,
+                         first_k_dense_replace=1, n_group=1, topk_group=1, routed_scaling_factor=1.5, norm_topk_prob=True,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [1, 2, 1],
+                                          "partial_rotary_factor": 0.5}),
+        vision_config=dict(depth=2, hidden_size=32, out_hidden_size=64, num_heads=4, intermediate_size=48, patch_size=14,
+                           spatial_merge_size=2, temporal_patch_size=2, in_channels=3, image_size=84, attention_bias=False),
+        image_token_id=IMG_TOKEN, video_token_id=291, image_start_token_id=292, image_end_token_id=293)
+    m = Glm4vMoeForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n_, p_ in m.named_parameters():
+            if "visual" in n_ or "mlp.gate" in n_ or "experts" in n_:
+                p_.normal_(0, 0.08) if p_.dim() >= 2 else p_.add_(torch.randn_like(p_) * 0.1)
+    d = tempfile.mkdtemp(prefix="vlm_glm4vmoe_")
+    m.save_pretrained(d, safe_serialization=True)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    vl.processor = Qwen2ImageProcessor(dict(min_pixels=56 * 56, max_pixels=28 * 28 * 16))
+    imgs = [_image(5, 90, 61), _image(6, 50, 130)]
+    rows, grids = vl.processor(imgs)
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [292, IMG_TOKEN, 293] + text(7) + [292, IMG_TOKEN, 293] + text(4)
+    ids, mm = vl.prepare(prompt, imgs)
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=rows, image_grid_thw=torch.tensor(grids),
+                          mm_token_type_ids=torch.tensor([[int(t == IMG_TOKEN) for t in ids]]),
+                          max_new_tokens=8, do_sample=False)[0, len(ids):].tolist()
+    cfg2 = ModelConfig.from_path(d)
+    assert cfg2.extra["mrope_section"] == [1, 2, 1] and not cfg2.rope_traditional and cfg2.num_experts == 4
+    assert _run_engine(d, ids, mm) == want
+    assert _run_engine(d, ids, mm, chunk=10) == want
