@@ -1061,6 +1061,19 @@ def _glm4v(c: ModelConfig, raw: dict) -> None:
         c.rope_scaling = None
 
 
+def _paddleocr_vl(c: ModelConfig, raw: dict) -> None:
+    """Language model of PaddleOCR-VL: Llama-layout blocks (optional projection biases) with multimodal
+    rotary positions in half-split pairs."""
+    c.attention_bias = bool(raw.get("use_bias", False))
+    c.mlp_bias = bool(raw.get("use_bias", False))
+    for rec in (raw.get("rope_parameters"), raw.get("rope_scaling")):
+        if isinstance(rec, dict) and rec.get("mrope_section"):
+            c.extra["mrope_section"] = [int(x) for x in rec["mrope_section"]]
+    rs = c.rope_scaling
+    if isinstance(rs, dict) and rs.get("rope_type", rs.get("type")) in ("mrope", "default", None):
+        c.rope_scaling = None
+
+
 def _glm4v_moe(c: ModelConfig, raw: dict) -> None:
     """Language model of GLM-4.5V: GLM-4.5 MoE blocks (half-split rotary pairs on half of each head) with
     multimodal rotary positions."""
@@ -1284,7 +1297,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "lfm2_moe": _lfm2, "exaone": _exaone, "telechat3": _telechat3, "deepseek": _deepseek_v1, "recurrent_gemma": _recurrent_gemma, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "glm4v": _glm4v, "glm4v_text": _glm4v, "glm4v_moe": _glm4v_moe, "glm4v_moe_text": _glm4v_moe, "cohere2_vision": _cohere2, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "lfm2_moe": _lfm2, "exaone": _exaone, "telechat3": _telechat3, "deepseek": _deepseek_v1, "recurrent_gemma": _recurrent_gemma, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "glm4v": _glm4v, "glm4v_text": _glm4v, "glm4v_moe": _glm4v_moe, "glm4v_moe_text": _glm4v_moe, "cohere2_vision": _cohere2, "paddleocr_vl": _paddleocr_vl, "paddleocr_vl_text": _paddleocr_vl, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

@@ -435,6 +435,112 @@ class Glm4vVisionTower(Qwen2VisionTower):
         return self._gated(y, self.mg["wgu"], self.mg["wd"])
 
 
+class RasterImageProcessor(Qwen2ImageProcessor):
+    """The Qwen2-VL resize and normalisation with patches listed row by row (no merge-window order) and
+    no temporal patch: rows are ``[C * patch * patch]`` (PaddleOCR-VL)."""
+
+    def __call__(self, images: list):
+        from PIL import Image
+        p, m = self.patch, self.merge
+        rows, grids = [], []
+        for img in images:
+            w, h = img.size
+            nh, nw = smart_resize(h, w, p * m, self.min_pixels, self.max_pixels)
+            a = np.asarray(img.resize((nw, nh), Image.Resampling.BICUBIC), dtype=np.float32) / 255.0
+            a = ((a - self.mean) / self.std).transpose(2, 0, 1)
+            gh, gw, C = nh // p, nw // p, a.shape[0]
+            x = a.reshape(C, gh, p, gw, p).transpose(1, 3, 0, 2, 4)
+            rows.append(torch.from_numpy(np.ascontiguousarray(x.reshape(gh * gw, C * p * p))))
+            grids.append((1, gh, gw))
+        return torch.cat(rows), grids
+
+
+class PaddleOcrVisionTower(Qwen2VisionTower):
+    """PaddleOCR-VL tower (transformers `PaddleOCRVisionModel` + `PaddleOCRProjector`; the reference's
+    src/vision/encoders/paddleocr_vl.rs): SigLIP-layout blocks over patches in raster order, a learned
+    position table resized bilinearly to the image's grid, 2-D rotary positions (row / column
+    halves), a final LayerNorm; the projector norms each patch, folds merge x merge neighbours and
+    applies linear, GELU, linear."""
+
+    def __init__(self, vc: dict, tensors: dict, proj: dict, dtype=torch.bfloat16, device="cpu"):
+        self.dtype, self.device = dtype, torch.device(device)
+        self.depth, self.dim, self.heads = int(vc["num_hidden_layers"]), int(vc["hidden_size"]), int(vc["num_attention_heads"])
+        self.patch, self.merge = int(vc.get("patch_size", 14)), int(vc.get("spatial_merge_size", 2))
+        self.eps = float(vc.get("layer_norm_eps", 1e-6))
+        self.act = {"gelu_pytorch_tanh": "gelu_tanh", "gelu": "gelu", "quick_gelu": "quick_gelu"}.get(
+            vc.get("hidden_act", "gelu_pytorch_tanh"), "gelu_tanh")
+
+        def t(n, src=tensors):
+            return src[n].to(dtype).to(self.device).contiguous()
+
+        pw = t("embeddings.patch_embedding.weight")
+        pw = pw.reshape(pw.shape[0], -1)
+        self.k_pad = (-pw.shape[1]) % 8
+        self.patch_w = F.pad(pw, (0, self.k_pad)).contiguous()
+        self.patch_b = t("embeddings.patch_embedding.bias")
+        self.pos_table = t("embeddings.position_embedding.weight")
+        self.side = int(round(self.pos_table.shape[0] ** 0.5))
+        self.blocks = []
+        for i in range(self.depth):
+            b, a = f"encoder.layers.{i}.", f"encoder.layers.{i}.self_attn."
+            self.blocks.append(dict(
+                n1=(t(b + "layer_norm1.weight"), t(b + "layer_norm1.bias")), n2=(t(b + "layer_norm2.weight"), t(b + "layer_norm2.bias")),
+                wqkv=torch.cat([t(a + "q_proj.weight"), t(a + "k_proj.weight"), t(a + "v_proj.weight")]).contiguous(),
+                bqkv=torch.cat([t(a + "q_proj.bias"), t(a + "k_proj.bias"), t(a + "v_proj.bias")]).contiguous(),
+                wo=t(a + "out_proj.weight"), bo=t(a + "out_proj.bias"),
+                w1=t(b + "mlp.fc1.weight"), b1=t(b + "mlp.fc1.bias"), w2=t(b + "mlp.fc2.weight"), b2=t(b + "mlp.fc2.bias")))
+        self.post_ln = (t("post_layernorm.weight"), t("post_layernorm.bias"))
+        self.pj = dict(nw=t("pre_norm.weight", proj), nb=t("pre_norm.bias", proj), w1=t("linear_1.weight", proj), b1=t("linear_1.bias", proj),
+                       w2=t("linear_2.weight", proj), b2=t("linear_2.bias", proj))
+        D = self.dim // self.heads
+        self.inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D // 2, 2, dtype=torch.float32) / (D // 2)))
+
+    @torch.no_grad()
+    def forward(self, rows: torch.Tensor, grids) -> torch.Tensor:
+        from ..models.vision import _act
+        x = ops.linear(F.pad(rows.to(self.device, self.dtype), (0, self.k_pad)).contiguous(), self.patch_w, bias=self.patch_b)
+        tab = self.pos_table.float().view(1, self.side, self.side, -1).permute(0, 3, 1, 2)
+        pos, ang = [], []
+        for t_, gh, gw in grids:
+            pe = F.interpolate(tab, size=(gh, gw), mode="bilinear", align_corners=False)
+            pos.append(pe.permute(0, 2, 3, 1).reshape(gh * gw, -1).repeat(t_, 1))
+            hp = torch.arange(gh)[:, None].expand(gh, gw).flatten().float()
+            wp = torch.arange(gw)[None, :].expand(gh, gw).flatten().float()
+            ang.append(torch.cat([hp[:, None] * self.inv_freq[None], wp[:, None] * self.inv_freq[None]], dim=1).repeat(t_, 1))
+        x = (x.float() + torch.cat(pos).to(self.device)).to(self.dtype)
+        ang = torch.cat(ang).to(self.device)
+        cos = torch.cat([ang.cos(), ang.cos()], dim=1)[:, None, :]
+        sin = torch.cat([ang.sin(), ang.sin()], dim=1)[:, None, :]
+        R, H, D = x.shape[0], self.heads, self.dim // self.heads
+        sizes = [gh * gw for t_, gh, gw in grids for _ in range(t_)]
+
+        def rot(v):
+            half = D // 2
+            return v * cos + torch.cat([-v[..., half:], v[..., :half]], dim=-1) * sin
+        for b in self.blocks:
+            y = rops.layernorm(x, *b["n1"], self.eps)
+            qkv = ops.linear(y, b["wqkv"], bias=b["bqkv"]).view(R, 3, H, D)
+            q, k, v = rot(qkv[:, 0].float()), rot(qkv[:, 1].float()), qkv[:, 2].float()
+            outs, o0 = [], 0
+            for n in sizes:
+                qi, ki, vi = (z[o0:o0 + n].transpose(0, 1)[None] for z in (q, k, v))
+                outs.append(F.scaled_dot_product_attention(qi, ki, vi)[0].transpose(0, 1).reshape(n, H * D))
+                o0 += n
+            x = ops.linear(torch.cat(outs).to(self.dtype).contiguous(), b["wo"], bias=b["bo"], residual=x)
+            y = rops.layernorm(x, *b["n2"], self.eps)
+            x = ops.linear(_act(ops.linear(y, b["w1"], bias=b["b1"]), self.act), b["w2"], bias=b["b2"], residual=x)
+        x = rops.layernorm(x, *self.post_ln, self.eps)
+        x = rops.layernorm(x, self.pj["nw"], self.pj["nb"], 1e-5)
+        m, out, o0 = self.merge, [], 0
+        for t_, gh, gw in grids:
+            n = t_ * gh * gw
+            y = x[o0:o0 + n].view(t_, gh // m, m, gw // m, m, self.dim).transpose(2, 3).reshape(n // (m * m), m * m * self.dim)
+            out.append(y)
+            o0 += n
+        y = torch.cat(out).contiguous()
+        return ops.linear(rops.activation(ops.linear(y, self.pj["w1"], bias=self.pj["b1"]), "gelu"), self.pj["w2"], bias=self.pj["b2"])
+
+
 class Qwen2VisionLanguage(VisionLanguage):
     def __init__(self, tower: Qwen2VisionTower, processor: Qwen2ImageProcessor, image_token_id: int, model_type: str):
         super().__init__(tower, None, processor, image_token_id, model_type)
@@ -500,6 +606,13 @@ def build_qwen2_vision(path, raw: dict, src, dtype, device) -> Qwen2VisionLangua
     import json
     from pathlib import Path
     mt = raw.get("model_type")
+    if mt == "paddleocr_vl":
+        vc = raw["vision_config"]
+        tower = PaddleOcrVisionTower(vc, _sub(src, "model.visual.vision_model.", "visual.vision_model."),
+                                     _sub(src, "mlp_AR.", "model.projector.", "projector."), dtype, device)
+        f = Path(path) / "preprocessor_config.json"
+        pc = json.loads(f.read_text()) if f.exists() else dict(image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5])
+        return Qwen2VisionLanguage(tower, RasterImageProcessor(pc, tower.patch, tower.merge, 1), raw.get("image_token_id", 100295), mt)
     cls = (Qwen3VisionTower if mt in ("qwen3_vl", "qwen3_vl_moe") else Qwen25VisionTower if mt == "qwen2_5_vl"
            else Glm4vVisionTower if mt in ("glm4v", "glm4v_moe") else Qwen2VisionTower)
     tower = cls(raw["vision_config"], _sub(src, "model.visual.", "visual."), dtype, device)

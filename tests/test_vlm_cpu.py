@@ -689,3 +689,45 @@ def test_glm4v_moe_greedy_matches_transformers_through_the_engine():
     assert cfg2.extra["mrope_section"] == [1, 2, 1] and not cfg2.rope_traditional and cfg2.num_experts == 4
     assert _run_engine(d, ids, mm) == want
     assert _run_engine(d, ids, mm, chunk=10) == want
+
+
+def test_paddleocr_vl_tower_and_greedy_match_transformers():
+    from transformers import PaddleOCRVLConfig, PaddleOCRVLForConditionalGeneration
+
+    from mlxcel_b200.multimodal.qwen2_vision import RasterImageProcessor
+    torch.manual_seed(0)
+    cfg = PaddleOCRVLConfig(
+        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, vocab_size=300, max_position_embeddings=512, head_dim=16,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [2, 3, 3]}),
+        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, patch_size=14,
+                           image_size=84, spatial_merge_size=2),
+        image_token_id=IMG_TOKEN, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    m = PaddleOCRVLForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n_, p_ in m.named_parameters():
+            if "visual" in n_ or "projector" in n_:
+                p_.normal_(0, 0.08) if p_.dim() >= 2 else p_.add_(torch.randn_like(p_) * 0.1)
+    d = tempfile.mkdtemp(prefix="vlm_paddleocr_")
+    m.save_pretrained(d, safe_serialization=True)
+    assert is_vlm_checkpoint(d)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    vl.processor = RasterImageProcessor(dict(min_pixels=56 * 56, max_pixels=28 * 28 * 16, image_mean=[0.5] * 3, image_std=[0.5] * 3), 14, 2, 1)
+    imgs = [_image(5, 90, 61), _image(6, 50, 130)]
+    rows, grids = vl.processor(imgs)
+    px = rows.view(rows.shape[0], 3, 14, 14)
+    with torch.no_grad():
+        want_feats = m.model.get_image_features(px, torch.tensor(grids)).pooler_output
+    want_feats = torch.cat(list(want_feats)) if not isinstance(want_feats, torch.Tensor) else want_feats
+    got_feats = torch.cat(vl.encode(imgs))
+    assert got_feats.shape == want_feats.shape and (got_feats - want_feats).abs().max().item() < 1e-4
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [292, IMG_TOKEN, 293] + text(7) + [292, IMG_TOKEN, 293] + text(4)
+    ids, mm = vl.prepare(prompt, imgs)
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=px, image_grid_thw=torch.tensor(grids),
+                          mm_token_type_ids=torch.tensor([[int(t == IMG_TOKEN) for t in ids]]),
+                          max_new_tokens=8, do_sample=False)[0, len(ids):].tolist()
+    assert _run_engine(d, ids, mm) == want
+    assert _run_engine(d, ids, mm, chunk=10) == want
