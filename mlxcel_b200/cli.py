@@ -1117,7 +1117,7 @@ def arch_catalog() -> dict:
             how = "a plain PyTorch statement of the model (the transformers implementation is not usable)"
         fams.append(dict(name=name, executor=ex, checked_against=how))
     return {"families": fams, "encoders": ["bert", "modernbert", "deberta-v2", "siglip text"],
-            "vision_language": ["llava (clip / siglip tower)", "qwen2_vl", "qwen2_5_vl", "qwen3_vl (DeepStack)", "idefics3 / smolvlm (one tile per image)", "internvl (one tile per image)", "mistral3 (pixtral tower)", "glm4v", "glm4v_moe", "cohere2_vision (one tile per image)", "paddleocr_vl"], "speech": ["whisper"], "dense_prediction": ["depth_anything (dinov2 backbone)"], "speech_language": ["voxtral", "qwen2_audio (clips up to one 30 s chunk)"],
+            "vision_language": ["llava (clip / siglip tower)", "qwen2_vl", "qwen2_5_vl", "qwen3_vl (DeepStack)", "idefics3 / smolvlm (one tile per image)", "internvl (one tile per image)", "mistral3 (pixtral tower)", "glm4v", "glm4v_moe", "cohere2_vision (one tile per image)", "paddleocr_vl", "glm_ocr"], "speech": ["whisper"], "dense_prediction": ["depth_anything (dinov2 backbone)"], "speech_language": ["voxtral", "qwen2_audio (clips up to one 30 s chunk)"],
             "quantization": ["affine", "mxfp4", "mxfp8", "fp8 (widened at load)", "nvfp4 (expanded at load)",
                              "bitlinear ternary (expanded at load)"],
             "kv_bits": [16, 8, 4], "parallelism": ["tp", "ep (replicated tokens)", "dp attention + ep (all-to-all)", "pp", "tp x pp",

@@ -1061,6 +1061,12 @@ def _glm4v(c: ModelConfig, raw: dict) -> None:
         c.rope_scaling = None
 
 
+def _glm_ocr(c: ModelConfig, raw: dict) -> None:
+    """Language model of GLM-OCR: the GLM-4V one without biases on q / k / v."""
+    _glm4v(c, raw)
+    c.attention_bias = False
+
+
 def _paddleocr_vl(c: ModelConfig, raw: dict) -> None:
     """Language model of PaddleOCR-VL: Llama-layout blocks (optional projection biases) with multimodal
     rotary positions in half-split pairs."""
@@ -1297,7 +1303,7 @@ FAMILIES = {
     "gpt_oss": _gpt_oss, "phi3": _phi3, "olmo2": _olmo2, "olmo3": _olmo2,
     "mamba": _mamba1, "mamba2": _mamba2, "nemotron_h": _nemotron_h, "granite": _granite, "starcoder2": _starcoder2, "stablelm": _stablelm, "cohere": _cohere,
     "deepseek_v2": _deepseek_v2, "deepseek_v3": _deepseek_v3, "kimi_k2": _deepseek_v3, "glm4_moe": _glm4_moe, "dots1": _dots1, "ernie4_5_moe": _ernie4_5_moe,
-    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "lfm2_moe": _lfm2, "exaone": _exaone, "telechat3": _telechat3, "deepseek": _deepseek_v1, "recurrent_gemma": _recurrent_gemma, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "glm4v": _glm4v, "glm4v_text": _glm4v, "glm4v_moe": _glm4v_moe, "glm4v_moe_text": _glm4v_moe, "cohere2_vision": _cohere2, "paddleocr_vl": _paddleocr_vl, "paddleocr_vl_text": _paddleocr_vl, "nemotron": _nemotron,
+    "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gpt_bigcode": _gpt2, "phi": _phi, "olmo": _olmo1, "granitemoe": _granitemoe, "granitemoehybrid": _granitemoehybrid, "jamba": _jamba, "bitnet": _bitnet, "lfm2_moe": _lfm2, "exaone": _exaone, "telechat3": _telechat3, "deepseek": _deepseek_v1, "recurrent_gemma": _recurrent_gemma, "glm_moe_dsa": _glm_moe_dsa, "deepseek_v32": _glm_moe_dsa, "mistral4": _mistral4, "afmoe": _afmoe, "dbrx": _dbrx, "llama4": _llama4, "llama4_text": _llama4, "qwen3_next": _qwen3_next, "qwen3_5": _qwen3_next, "qwen3_5_text": _qwen3_next, "qwen3_5_moe": _qwen3_next, "qwen3_5_moe_text": _qwen3_next, "falcon_h1": _falcon_h1, "cohere2": _cohere2, "arcee": _arcee, "glm": _glm, "glm4": _glm4, "glm4v": _glm4v, "glm4v_text": _glm4v, "glm4v_moe": _glm4v_moe, "glm4v_moe_text": _glm4v_moe, "cohere2_vision": _cohere2, "paddleocr_vl": _paddleocr_vl, "glm_ocr": _glm_ocr, "glm_ocr_text": _glm_ocr, "paddleocr_vl_text": _paddleocr_vl, "nemotron": _nemotron,
     "ministral3": _ministral3, "granitemoeshared": _granitemoeshared, "nanochat": _nanochat, "code_llama": _plain, "cwm": _plain, "glm4_moe_lite": _deepseek_v3,
     "vaultgemma": _vaultgemma, "solar_open": _solar_open, "minimax_m2": _minimax_m2, "exaone_moe": _exaone_moe, "lfm2": _lfm2, "internlm2": _plain, "baichuan": _baichuan,
 }

@@ -363,17 +363,22 @@ class Glm4vVisionTower(Qwen2VisionTower):
         self.k_pad = (-pw.shape[1]) % 8
         self.patch_w = F.pad(pw, (0, self.k_pad)).contiguous()
         self.patch_b = t("patch_embed.proj.bias")
-        self.post_conv = t("post_conv_layernorm.weight")
-        self.pos_table = t("embeddings.position_embedding.weight")
-        self.side = int(round(self.pos_table.shape[0] ** 0.5))
+        # GLM-OCR drops the norm after the patch embedding and the position table, norms q and k per head,
+        # and carries biases on the output projection and the MLP
+        self.post_conv = t("post_conv_layernorm.weight", False)
+        self.pos_table = t("embeddings.position_embedding.weight", False)
+        self.side = int(round(self.pos_table.shape[0] ** 0.5)) if self.pos_table is not None else 0
         self.blocks = []
         for i in range(self.depth):
             b = f"blocks.{i}."
+            bg, bu = t(b + "mlp.gate_proj.bias", False), t(b + "mlp.up_proj.bias", False)
             self.blocks.append(dict(
                 n1=t(b + "norm1.weight"), n2=t(b + "norm2.weight"), wqkv=t(b + "attn.qkv.weight"), bqkv=t(b + "attn.qkv.bias", False),
-                wo=t(b + "attn.proj.weight"),
+                wo=t(b + "attn.proj.weight"), bo=t(b + "attn.proj.bias", False),
+                qn=t(b + "attn.q_norm.weight", False), kn=t(b + "attn.k_norm.weight", False),
                 wgu=torch.cat([t(b + "mlp.gate_proj.weight"), t(b + "mlp.up_proj.weight")]).contiguous(),
-                wd=t(b + "mlp.down_proj.weight")))
+                bgu=None if bg is None else torch.cat([bg, bu]).contiguous(),
+                wd=t(b + "mlp.down_proj.weight"), bd=t(b + "mlp.down_proj.bias", False)))
         self.post_ln = t("post_layernorm.weight")
         dw = t("downsample.weight")                                   # [out, C, m, m]
         self.down_w, self.down_b = dw.reshape(dw.shape[0], -1).contiguous(), t("downsample.bias")
@@ -394,18 +399,20 @@ class Glm4vVisionTower(Qwen2VisionTower):
             out.append(pe[0, :, :, 0].t().repeat(t_, 1))
         return torch.cat(out)
 
-    def _gated(self, y, wgu, wd, residual=None):
+    def _gated(self, y, wgu, wd, residual=None, bgu=None, bd=None):
         from ..models.vision import _act
-        gu = ops.linear(y, wgu)
+        gu = ops.linear(y, wgu, bias=bgu)
         inter = gu.shape[1] // 2
         u = (_act(gu[:, :inter].contiguous(), self.act).float() * gu[:, inter:].float()).to(self.dtype).contiguous()
-        return ops.linear(u, wd, residual=residual)
+        return ops.linear(u, wd, bias=bd, residual=residual)
 
     @torch.no_grad()
     def forward(self, rows: torch.Tensor, grids) -> torch.Tensor:
         x = ops.linear(F.pad(rows.to(self.device, self.dtype), (0, self.k_pad)).contiguous(), self.patch_w, bias=self.patch_b)
-        x = ops.rmsnorm(x, self.post_conv, self.eps)
-        x = (x.float() + self._pos_embed(grids).to(self.device)).to(self.dtype)
+        if self.post_conv is not None:
+            x = ops.rmsnorm(x, self.post_conv, self.eps)
+        if self.pos_table is not None:
+            x = (x.float() + self._pos_embed(grids).to(self.device)).to(self.dtype)
         R, H, D = x.shape[0], self.heads, self.dim // self.heads
         ang = self._rot_angles(grids).to(self.device)
         cos = torch.cat([ang.cos(), ang.cos()], dim=1)[:, None, :]
@@ -418,14 +425,18 @@ class Glm4vVisionTower(Qwen2VisionTower):
         for b in self.blocks:
             y = ops.rmsnorm(x, b["n1"], self.eps)
             qkv = ops.linear(y, b["wqkv"], bias=b["bqkv"]).view(R, 3, H, D)
-            q, k, v = rot(qkv[:, 0].float()), rot(qkv[:, 1].float()), qkv[:, 2].float()
+            q, k, v = qkv[:, 0].float(), qkv[:, 1].float(), qkv[:, 2].float()
+            if b["qn"] is not None:
+                hn = lambda z, w: z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + self.eps) * w.float()  # noqa: E731
+                q, k = hn(q, b["qn"]), hn(k, b["kn"])
+            q, k = rot(q), rot(k)
             outs, o0 = [], 0
             for n in sizes:
                 qi, ki, vi = (z[o0:o0 + n].transpose(0, 1)[None] for z in (q, k, v))
                 outs.append(F.scaled_dot_product_attention(qi, ki, vi)[0].transpose(0, 1).reshape(n, H * D))
                 o0 += n
-            x = ops.linear(torch.cat(outs).to(self.dtype).contiguous(), b["wo"], residual=x)
-            x = self._gated(ops.rmsnorm(x, b["n2"], self.eps), b["wgu"], b["wd"], residual=x)
+            x = ops.linear(torch.cat(outs).to(self.dtype).contiguous(), b["wo"], bias=b["bo"], residual=x)
+            x = self._gated(ops.rmsnorm(x, b["n2"], self.eps), b["wgu"], b["wd"], residual=x, bgu=b["bgu"], bd=b["bd"])
         x = ops.rmsnorm(x, self.post_ln, self.eps)
         unit = self.merge ** 2
         y = x.view(R // unit, unit, self.dim).transpose(1, 2).reshape(R // unit, self.dim * unit).contiguous()
@@ -614,7 +625,7 @@ def build_qwen2_vision(path, raw: dict, src, dtype, device) -> Qwen2VisionLangua
         pc = json.loads(f.read_text()) if f.exists() else dict(image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5])
         return Qwen2VisionLanguage(tower, RasterImageProcessor(pc, tower.patch, tower.merge, 1), raw.get("image_token_id", 100295), mt)
     cls = (Qwen3VisionTower if mt in ("qwen3_vl", "qwen3_vl_moe") else Qwen25VisionTower if mt == "qwen2_5_vl"
-           else Glm4vVisionTower if mt in ("glm4v", "glm4v_moe") else Qwen2VisionTower)
+           else Glm4vVisionTower if mt in ("glm4v", "glm4v_moe", "glm_ocr") else Qwen2VisionTower)
     tower = cls(raw["vision_config"], _sub(src, "model.visual.", "visual."), dtype, device)
     f = Path(path) / "preprocessor_config.json"
     pc = json.loads(f.read_text()) if f.exists() else None

@@ -29,7 +29,7 @@ from ..models.vision import (Cohere2VisionConnector, InternVLConnector, InternVi
                              PixtralTower, ViTTower, VisionConfig)
 from .images import ImageProcessor
 
-SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "idefics3", "smolvlm", "internvl", "mistral3", "glm4v", "glm4v_moe", "cohere2_vision", "paddleocr_vl")
+SUPPORTED = ("llava", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "idefics3", "smolvlm", "internvl", "mistral3", "glm4v", "glm4v_moe", "cohere2_vision", "paddleocr_vl", "glm_ocr")
 
 
 def is_vlm_checkpoint(path: str | Path) -> bool:
@@ -62,7 +62,7 @@ class VisionLanguage:
                                  "qwen3_vl_moe": "<|vision_start|><|image_pad|><|vision_end|>",
                                  "idefics3": "<fake_token_around_image><global-img><image><fake_token_around_image>",
                                  "smolvlm": "<fake_token_around_image><global-img><image><fake_token_around_image>",
-                                 "internvl": "<img><IMG_CONTEXT></img>", "glm4v": "<|begin_of_image|><|image|><|end_of_image|>", "glm4v_moe": "<|begin_of_image|><|image|><|end_of_image|>",
+                                 "internvl": "<img><IMG_CONTEXT></img>", "glm4v": "<|begin_of_image|><|image|><|end_of_image|>", "glm4v_moe": "<|begin_of_image|><|image|><|end_of_image|>", "glm_ocr": "<|begin_of_image|><|image|><|end_of_image|>",
                                  "cohere2_vision": "<|START_OF_IMG|><|IMG_PATCH|><|END_OF_IMG|>",
                                  "paddleocr_vl": "<|IMAGE_START|><|IMAGE_PLACEHOLDER|><|IMAGE_END|>", "mistral3": "[IMG]"}.get(
                                      model_type, "<image>")
@@ -120,7 +120,7 @@ class VisionLanguage:
             return VisionLanguage(tower, conn, proc, raw.get("image_token_id", 255036), mt)
         if mt == "mistral3":
             return PixtralVisionLanguage.build(path, raw, src, dtype, device)
-        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "glm4v", "glm4v_moe", "paddleocr_vl"):
+        if mt in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "glm4v", "glm4v_moe", "paddleocr_vl", "glm_ocr"):
             from .qwen2_vision import build_qwen2_vision
             return build_qwen2_vision(path, raw, src, dtype, device)
         raise ValueError(f"unsupported vision-language model_type {mt!r}; supported: {SUPPORTED}")

@@ -731,3 +731,43 @@ def test_paddleocr_vl_tower_and_greedy_match_transformers():
                           max_new_tokens=8, do_sample=False)[0, len(ids):].tolist()
     assert _run_engine(d, ids, mm) == want
     assert _run_engine(d, ids, mm, chunk=10) == want
+
+
+def test_glm_ocr_tower_and_greedy_match_transformers():
+    from transformers import GlmOcrConfig, GlmOcrForConditionalGeneration
+
+    from mlxcel_b200.multimodal.qwen2_vision import Qwen2ImageProcessor
+    torch.manual_seed(0)
+    cfg = GlmOcrConfig(
+        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, vocab_size=300, max_position_embeddings=512, head_dim=16,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [1, 2, 1],
+                                          "partial_rotary_factor": 0.5}),
+        vision_config=dict(depth=3, hidden_size=32, out_hidden_size=64, num_heads=4, intermediate_size=48, patch_size=14,
+                           spatial_merge_size=2, temporal_patch_size=2, in_channels=3, image_size=84, attention_bias=True),
+        image_token_id=IMG_TOKEN, video_token_id=291, image_start_token_id=292, image_end_token_id=293)
+    m = GlmOcrForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n_, p_ in m.named_parameters():
+            if "visual" in n_:
+                p_.normal_(0, 0.08) if p_.dim() >= 2 else p_.add_(torch.randn_like(p_) * 0.1)
+    d = tempfile.mkdtemp(prefix="vlm_glmocr_")
+    m.save_pretrained(d, safe_serialization=True)
+    vl = VisionLanguage.from_checkpoint(d, dtype=torch.float32)
+    vl.processor = Qwen2ImageProcessor(dict(min_pixels=56 * 56, max_pixels=28 * 28 * 16))
+    imgs = [_image(5, 90, 61), _image(6, 50, 130)]
+    rows, grids = vl.processor(imgs)
+    with torch.no_grad():
+        want_feats = m.model.visual(rows, grid_thw=torch.tensor(grids)).pooler_output
+    got_feats = torch.cat(vl.encode(imgs))
+    assert got_feats.shape == want_feats.shape and (got_feats - want_feats).abs().max().item() < 1e-4
+    g = torch.Generator().manual_seed(3)
+    text = lambda n: torch.randint(0, 280, (n,), generator=g).tolist()  # noqa: E731
+    prompt = text(5) + [292, IMG_TOKEN, 293] + text(7) + [292, IMG_TOKEN, 293] + text(4)
+    ids, mm = vl.prepare(prompt, imgs)
+    with torch.no_grad():
+        want = m.generate(input_ids=torch.tensor([ids]), pixel_values=rows, image_grid_thw=torch.tensor(grids),
+                          mm_token_type_ids=torch.tensor([[int(t == IMG_TOKEN) for t in ids]]),
+                          max_new_tokens=8, do_sample=False)[0, len(ids):].tolist()
+    assert _run_engine(d, ids, mm) == want
+    assert _run_engine(d, ids, mm, chunk=10) == want
